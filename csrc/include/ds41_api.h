@@ -1,0 +1,112 @@
+// C ABI of libds41_kernels.so.  Every entry point is asynchronous on the given stream, allocates
+// nothing, works on caller-owned device buffers and returns a raw cudaError_t value (0 = success).
+// Kernels that wait (mbarrier, peer flags) take an `int status[4]` device word: a wait that runs out
+// writes {code, where, block, detail} there and the kernel returns instead of hanging.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---------------------------------------------------------------------------------------------------
+// Tensor-core GEMM  D[m,n] = sum_k A[m,k] * B[n,k]  (tcgen05 + TMA + TMEM).  Strides in elements.
+//   kind      0 bf16, 1 fp8-e4m3 (unscaled), 2 MX fp8 (UE8M0 per 32 elements; scale atoms sfa/sfb)
+//   out_mode  0 bf16 [m,n] | 1 f32 [m,n] | 2 bf16 [n,m] | 3 f32 [n,m]
+//             4 bf16 [n,m] = silu(min(gate,L)) * clamp(up,-L,L) * row_w[b][n] with gate = A rows [m],
+//               up = A rows [up_row_offset + m]   (fused expert FC1)
+//             5 f32 [n,m] written only where row_w[b][n] != 0 (expert FC2)
+//   k_splits  > 1 writes fp32 planes [split][batch][rows][ldo] into split_workspace (modes 1 and 3)
+//   batch_map / n_active: grouped execution - logical batch b uses A batch batch_map[b]; only b < *n_active run
+//   b_batch_kind: B batch coordinate 0 = same as A, 1 = always 0 (shared activations), 2 = logical b
+typedef struct ds41_gemm_args {
+  const void* A;
+  const void* B;
+  void* out;
+  void* split_workspace;
+  const void* sfa;
+  const void* sfb;
+  const int* batch_map;
+  const int* n_active;
+  const float* row_w;
+  int* status;
+  long long lda, ldb, ldo;
+  long long a_batch_stride, b_batch_stride, out_batch_stride;
+  long long sfa_batch_stride, sfb_batch_stride;
+  int M, N, K, batch;
+  int a_batches;
+  int kind, out_mode, k_splits, bn;
+  int b_batch_kind;
+  int up_row_offset;
+  int row_w_ld;
+  float act_limit;
+} ds41_gemm_args;
+
+int ds41_gemm_tc(const ds41_gemm_args* args, void* stream);
+
+// ---------------------------------------------------------------------------------------------------
+// Hyper-connections and embedding (hc.cu)
+int ds41_embed_streams(const int* tokens, const void* embed, void* streams, float* pre, int rows, int H, int mult,
+                       int vocab, void* stream);
+// part_bases: HOST array of n_ranks device pointers (fp32 planes [n_splits][rows][H], local or peer memory);
+// wait_flags: DEVICE array of n_ranks flag pointers, wait_epoch: device word holding the value to wait for.
+int ds41_hc_post_mix(const void* streams_in, void* streams_out, const float* const* part_bases, int n_ranks,
+                     int n_splits, long long split_stride, const float* post, const float* comb, const float* fn,
+                     float* partial, int rows, int H, const uint32_t* const* wait_flags, const uint32_t* wait_epoch,
+                     int* status, void* stream);
+int ds41_hc_finish(const float* partial, int n_slices, const float* scale, const float* base, const float* pre_in,
+                   const void* streams, const float* norm_w, float* next_pre, float* post, float* comb, void* xn,
+                   float* tap_mean, int rows, int H, int iters, float hc_eps, float norm_eps, void* stream);
+
+// ---------------------------------------------------------------------------------------------------
+// Attention-side projections' epilogues and cache writes (attn_ops.cu)
+int ds41_qkv_post(const float* planes, int splits, int rows, int ntot, int Q, int D, int rope_dim, int extra_f32,
+                  int index_heads, float index_scale, const float* q_norm_w, const float* kv_norm_w,
+                  const float* inv_freq, const int* row_pos, const int* row_slot, void* q_lat, void* win, int ring,
+                  float* extras, float eps, void* stream);
+int ds41_compress(const float* extras, int extra_stride, int rows, int D, int ID, int rope_dim, int ratio,
+                  const int* row_pos, const int* row_slot, float* pending, const float* comp_norm_w, const void* wk,
+                  const float* k_norm_w, const float* inv_freq, const float* inv_freq_idx, const int* page_table,
+                  int max_pages, int page_rows, void* comp_pool, void* idx_pool, float eps, void* stream);
+
+// ---------------------------------------------------------------------------------------------------
+// Indexer, top-k and sparse attention (sparse_attn.cu)
+int ds41_index_score(const void* q, long long ldq, int q_off, const float* w, int w_stride, int w_off,
+                     const void* idx_pool, const int* page_table, int max_pages, int page_rows, const int* row_pos,
+                     const int* row_slot, const float* inv_freq_idx, int rows, int IH, int ID, int ratio,
+                     float* scores, int max_keys, void* stream);
+int ds41_topk_select(const float* scores, int max_keys, const int* row_pos, const int* row_slot, int ratio, int k,
+                     int* sel, int* n_sel, int rows, void* stream);
+int ds41_attend(const void* q, long long ldq, int q_off, int rows, int heads, int D, int window, int ring,
+                const int* row_pos, const int* row_slot, const void* win, const void* comp_pool, const int* sel,
+                const int* n_sel, int k, const int* page_table, int max_pages, int page_rows, const float* inv_freq,
+                int rope_dim, float scale, int n_splits, const int* row_hi, float* part_o, float* part_ml,
+                const float* sink, void* out, long long ldo, void* stream);
+
+// ---------------------------------------------------------------------------------------------------
+// Router / experts (moe.cu)
+int ds41_router_select(const float* planes, int splits, int rows, int ntot, int E, int I_sh, int topk,
+                       const float* bias, float route_scale, float limit, int* ids, float* weights, void* shared_act,
+                       void* stream);
+int ds41_moe_plan(const int* ids, const float* weights, const int* row_slot, int rows, int topk, int e0, int e1,
+                  int max_active, int row_w_ld, int* active, int* n_active, float* row_w, int* slot_of,
+                  void* stream);
+int ds41_moe_combine(const float* fc2, const int* slot_of, const float* shared, int shared_splits, int rows,
+                     int topk, int H, float* out, void* stream);
+int ds41_signal(uint32_t* epoch, uint32_t* flag, void* stream);
+int ds41_reduce_planes(const float* planes, int splits, long long plane, void* out, int as_bf16, long long n,
+                       void* stream);
+
+// ---------------------------------------------------------------------------------------------------
+// Head epilogues (sampler.cu)
+int ds41_argmax_rows(const float* logits, long long ld, int rows, int vocab_local, int vocab_offset,
+                     const uint32_t* mask, int mask_words, float* best_val, int* best_idx, int* row_status,
+                     void* stream);
+int ds41_argmax_merge(const float* const* vals, const int* const* idxs, int n_ranks, int rows, int* out,
+                      const uint32_t* const* wait_flags, const uint32_t* wait_epoch, int* status, void* stream);
+int ds41_spec_accept(const int* inputs, const int* chosen, const int* first, const int* count, int reqs,
+                     int max_emit, int eos, int* accepted, int* emit, int* n_emit, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

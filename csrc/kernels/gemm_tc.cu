@@ -1,0 +1,465 @@
+// Tensor-core GEMM for sm_100a:  D[m,n] = sum_k A[m,k] * B[n,k]   (both operands K-major)
+//
+// One persistent warp-specialised kernel: warp 0 streams A/B tiles with TMA into a multi-stage
+// shared-memory ring, warp 1 issues tcgen05.mma into double-buffered TMEM accumulators, warps 2-5
+// drain TMEM with tcgen05.ld and write the result.  Kinds: bf16, fp8 e4m3 (unscaled) and MX
+// block-scaled fp8 (UE8M0 scale per 32 elements, scale factors copied into TMEM with tcgen05.cp).
+// Split-K writes fp32 partial planes; "transposed" output serves the swap-AB decode orientation
+// where the weight matrix is the M operand and the few token rows are the N operand.
+//
+// Capability parity: replaces the reference's AOT block-scaled dense GEMMs
+// (native/include/ds41rt_v41_fp8.h:6-47) and its cuBLAS fallbacks (native/cuda/kernels/v41_attention_ops.cu:130-155).
+#include <cuda.h>
+
+#include "ds41_api.h"
+#include "ds41_ptx.cuh"
+#include "ds41_tma.h"
+
+namespace ds41 {
+
+constexpr int kBM = 128;
+constexpr int kTileKBytes = 128;       // one 128-byte swizzle span of K per stage
+constexpr int kGemmThreads = 192;
+
+struct GemmParams {
+  int M, N, K;            // K in elements
+  int batch;
+  int k_splits;
+  int out_mode;           // 0 bf16 [m,n]; 1 f32 [m,n]; 2 bf16 [n,m]; 3 f32 [n,m];
+                          // 4 (DUAL) bf16 [n,m] = swiglu(gate,up)*row_w; 5 f32 [n,m] where row_w != 0
+  long long ldo;          // leading dimension of the output in elements
+  long long out_batch_stride;
+  long long out_split_stride;
+  void* out;
+  const uint8_t* sfa;     // MX kinds: scale-factor atoms of A / B
+  const uint8_t* sfb;
+  long long sfa_batch_stride;
+  long long sfb_batch_stride;
+  // grouped (MoE) extensions
+  const int* batch_map;   // optional: A-operand batch coordinate of logical batch b
+  const int* n_active;    // optional device scalar: only logical batches < *n_active run
+  int b_batch_kind;       // B-operand batch coordinate: 0 = same as A, 1 = always 0, 2 = logical b
+  int up_row_offset;      // DUAL: row offset of the second ("up") A tile (= intermediate size)
+  const float* row_w;     // modes 4/5: per (logical batch, n) weight, [batch][row_w_ld]
+  int row_w_ld;
+  float act_limit;        // mode 4: SwiGLU clamp
+  int* status;
+};
+
+template <int BN, int KIND, int DUAL = 0>
+struct GemmCfg {
+  static constexpr int kElemBytes = (KIND == 0) ? 2 : 1;
+  static constexpr int kBK = kTileKBytes / kElemBytes;                 // elements of K per stage
+  static constexpr int kATile = kBM * kTileKBytes;                     // 16 KiB
+  static constexpr int kABytes = kATile * (DUAL ? 2 : 1);
+  static constexpr int kBBytes = BN * kTileKBytes;
+  static constexpr int kSfBytes = (KIND == 2) ? (512 + 512 * ((BN + 127) / 128)) : 0;
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
+  static constexpr int kStagesRaw = (200 * 1024) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kSfCols = (KIND == 2) ? (4 + 4 * ((BN + 127) / 128)) : 0;   // TMEM columns per stage
+  static constexpr int kAccCols = (BN < 32 ? 32 : BN) * (DUAL ? 2 : 1);
+  static constexpr int kTmemNeeded = 2 * kAccCols + kStages * kSfCols;
+  static constexpr int kTmemCols = kTmemNeeded <= 32 ? 32 : kTmemNeeded <= 64 ? 64 : kTmemNeeded <= 128 ? 128
+                                   : kTmemNeeded <= 256 ? 256 : 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static_assert(kTmemNeeded <= 512, "TMEM budget exceeded");
+  static_assert(kStages >= 2, "not enough shared memory for two stages");
+};
+
+template <int BN, int KIND, int DUAL>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  using Cfg = GemmCfg<BN, KIND, DUAL>;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint8_t* bar_base = smem + S * Cfg::kStageBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(bar_base);
+  uint64_t* empty = full + S;
+  uint64_t* acc_full = empty + S;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int m_tiles = (p.M + kBM - 1) / kBM;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int kb_total = (p.K + Cfg::kBK - 1) / Cfg::kBK;
+  const int kb_per_split = (kb_total + p.k_splits - 1) / p.k_splits;
+  int batch_run = p.batch;
+  if (p.n_active != nullptr) batch_run = min(batch_run, *p.n_active);
+  const long long tiles = 1ll * m_tiles * n_tiles * p.k_splits * batch_run;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
+    mbar_init_fence();
+  }
+  __syncwarp();
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------ TMA producer
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+      long long r = t;
+      const int mt = static_cast<int>(r % m_tiles); r /= m_tiles;
+      const int nt = static_cast<int>(r % n_tiles); r /= n_tiles;
+      const int sp = static_cast<int>(r % p.k_splits); r /= p.k_splits;
+      const int b = static_cast<int>(r);
+      const int kb0 = sp * kb_per_split;
+      const int kb1 = min(kb_total, kb0 + kb_per_split);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(&empty[stage], phase ^ 1, p.status, 100)) { ok = false; break; }
+        uint8_t* sa = smem + stage * Cfg::kStageBytes;
+        uint8_t* sb = sa + Cfg::kABytes;
+        mbar_expect_tx(&full[stage], Cfg::kABytes + Cfg::kBBytes + Cfg::kSfBytes);
+        const int ba = p.batch_map != nullptr ? p.batch_map[b] : b;
+        const int bb = p.b_batch_kind == 0 ? ba : (p.b_batch_kind == 1 ? 0 : b);
+        tma_load_3d(sa, &tmA, &full[stage], kb * Cfg::kBK, mt * kBM, ba);
+        if constexpr (DUAL) tma_load_3d(sa + Cfg::kATile, &tmA, &full[stage], kb * Cfg::kBK, p.up_row_offset + mt * kBM, ba);
+        tma_load_3d(sb, &tmB, &full[stage], kb * Cfg::kBK, nt * BN, bb);
+        if constexpr (KIND == 2) {
+          // scale-factor atoms: [row_atom][k_atom][512 B]; one k_atom per stage (128 elements of K)
+          uint8_t* ssf = sb + Cfg::kBBytes;
+          const long long ka = kb;
+          const long long n_ka = kb_total;
+          bulk_load(ssf, p.sfa + ba * p.sfa_batch_stride + (1ll * mt * n_ka + ka) * 512, 512, &full[stage]);
+          constexpr int kAtomsB = (BN + 127) / 128;
+#pragma unroll
+          for (int a = 0; a < kAtomsB; ++a) {
+            const long long ra = (1ll * nt * BN) / 128 + a;
+            bulk_load(ssf + 512 + a * 512, p.sfb + bb * p.sfb_batch_stride + (ra * n_ka + ka) * 512, 512,
+                      &full[stage]);
+          }
+        }
+        if (++stage == S) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------------------------------------ MMA issuer
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    constexpr uint32_t kFmt = (KIND == 0) ? 1u : 0u;   // bf16 / e4m3
+    constexpr uint32_t idesc = umma_idesc(kBM, BN, kFmt, kFmt);
+    for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+      const int nt = static_cast<int>((t / m_tiles) % n_tiles);
+      long long r = t / (1ll * m_tiles * n_tiles);
+      const int sp = static_cast<int>(r % p.k_splits);
+      const int kb0 = sp * kb_per_split;
+      const int kb1 = min(kb_total, kb0 + kb_per_split);
+      if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, p.status, 200)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * Cfg::kAccCols;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(&full[stage], phase, p.status, 201)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+        const uint32_t sb = sa + Cfg::kABytes;
+        const uint64_t adesc = umma_desc_sw128(sa);
+        const uint64_t bdesc = umma_desc_sw128(sb);
+        if constexpr (KIND == 2) {
+          const uint32_t ssf = sb + Cfg::kBBytes;
+          const uint32_t sf_t = tmem_base + 2 * Cfg::kAccCols + stage * Cfg::kSfCols;
+          tmem_cp_32x128b_warpx4(sf_t, umma_desc_plain(ssf, 16, 128));
+          constexpr int kAtomsB = (BN + 127) / 128;
+#pragma unroll
+          for (int a = 0; a < kAtomsB; ++a)
+            tmem_cp_32x128b_warpx4(sf_t + 4 + 4 * a, umma_desc_plain(ssf + 512 + 512 * a, 16, 128));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t id = umma_idesc_bs(kBM, BN, 0, 0, 1, k, k);
+            // B scale columns: rows of this n-tile start (nt*BN % 128)/32 columns into the atom
+            const uint32_t sfb_t = sf_t + 4 + ((static_cast<uint32_t>(nt) * BN) & 127u) / 32u;
+            umma_mxf8(d_tmem, adesc + 2 * k, bdesc + 2 * k, id, (kb > kb0 || k > 0) ? 1u : 0u, sf_t, sfb_t);
+            static_assert(!(KIND == 2 && DUAL), "dual MX tiles are provided by the grouped expert kernel");
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < kTileKBytes / 32; ++k) {
+            const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
+            if constexpr (KIND == 0) umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
+            else umma_f8(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
+            if constexpr (DUAL) {
+              const uint64_t adesc2 = umma_desc_sw128(sa + Cfg::kATile);
+              if constexpr (KIND == 0) umma_bf16(d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, idesc, accum);
+              else umma_f8(d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, idesc, accum);
+            }
+          }
+        }
+        tc_commit(&empty[stage]);       // frees the smem stage when these MMAs retire
+        if (++stage == S) { stage = 0; phase ^= 1; }
+      }
+      if (ok) tc_commit(&acc_full[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  } else if (warp >= 2) {
+    // ------------------------------------------------------------ epilogue (4 warps)
+    const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+      long long r = t;
+      const int mt = static_cast<int>(r % m_tiles); r /= m_tiles;
+      const int nt = static_cast<int>(r % n_tiles); r /= n_tiles;
+      const int sp = static_cast<int>(r % p.k_splits); r /= p.k_splits;
+      const int b = static_cast<int>(r);
+      if (!mbar_wait(&acc_full[acc], acc_phase, p.status, 300)) { ok = false; break; }
+      tc_fence_after();
+      const int m = mt * kBM + quad * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * Cfg::kAccCols;
+      const long long obase = b * p.out_batch_stride + sp * p.out_split_stride;
+      constexpr int kChunk = BN >= 32 ? 32 : BN;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += kChunk) {
+        uint32_t v[32];
+        if constexpr (kChunk == 32) {
+          tmem_ld_32x32(t_row + c, v);
+        } else if constexpr (kChunk == 16) {
+          uint32_t v16[16];
+          tmem_ld_32x16(t_row + c, v16);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = v16[j];
+        } else {
+          uint32_t v8[8];
+          tmem_ld_32x8(t_row + c, v8);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = v8[j];
+        }
+        tmem_wait_ld();
+        const int n0 = nt * BN + c;
+        if (p.out_mode == 0) {
+          if (m < p.M) {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + obase + 1ll * m * p.ldo + n0;
+            if (n0 + kChunk <= p.N && (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < kChunk; j += 8) {
+                uint4 q;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                q.x = *reinterpret_cast<uint32_t*>(&h0);
+                q.y = *reinterpret_cast<uint32_t*>(&h1);
+                q.z = *reinterpret_cast<uint32_t*>(&h2);
+                q.w = *reinterpret_cast<uint32_t*>(&h3);
+                *reinterpret_cast<uint4*>(o + j) = q;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < kChunk; ++j)
+                if (n0 + j < p.N) o[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+            }
+          }
+        } else if (p.out_mode == 1) {
+          if (m < p.M) {
+            float* o = reinterpret_cast<float*>(p.out) + obase + 1ll * m * p.ldo + n0;
+            if (n0 + kChunk <= p.N && (p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < kChunk; j += 4)
+                *reinterpret_cast<uint4*>(o + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < kChunk; ++j)
+                if (n0 + j < p.N) o[j] = __uint_as_float(v[j]);
+            }
+          }
+        } else if (p.out_mode == 2) {
+          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + obase + m;
+          if (m < p.M) {
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j)
+              if (n0 + j < p.N) o[1ll * (n0 + j) * p.ldo] = __float2bfloat16_rn(__uint_as_float(v[j]));
+          }
+        } else if (p.out_mode == 3) {
+          float* o = reinterpret_cast<float*>(p.out) + obase + m;
+          if (m < p.M) {
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j)
+              if (n0 + j < p.N) o[1ll * (n0 + j) * p.ldo] = __uint_as_float(v[j]);
+          }
+        } else if (p.out_mode == 4) {
+          if constexpr (DUAL) {
+            // v = gate chunk; fetch the matching up chunk from the second accumulator half
+            uint32_t u[32];
+            if constexpr (kChunk == 32) {
+              tmem_ld_32x32(t_row + Cfg::kAccCols / 2 + c, u);
+            } else {
+              uint32_t u16[16];
+              tmem_ld_32x16(t_row + Cfg::kAccCols / 2 + c, u16);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) u[j] = u16[j];
+            }
+            tmem_wait_ld();
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + obase + m;
+            const float* rw = p.row_w + 1ll * b * p.row_w_ld;
+            if (m < p.M) {
+#pragma unroll
+              for (int j = 0; j < kChunk; ++j) {
+                if (n0 + j < p.N) {
+                  const float gte = fminf(bf16_round(__uint_as_float(v[j])), p.act_limit);
+                  const float upv = fminf(fmaxf(bf16_round(__uint_as_float(u[j])), -p.act_limit), p.act_limit);
+                  const float act = gte / (1.0f + __expf(-gte)) * upv * rw[n0 + j];
+                  o[1ll * (n0 + j) * p.ldo] = __float2bfloat16_rn(act);
+                }
+              }
+            }
+          }
+        } else {
+          float* o = reinterpret_cast<float*>(p.out) + obase + m;
+          const float* rw = p.row_w + 1ll * b * p.row_w_ld;
+          if (m < p.M) {
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j)
+              if (n0 + j < p.N && rw[n0 + j] != 0.f) o[1ll * (n0 + j) * p.ldo] = __uint_as_float(v[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != kStatusOk) {
+    // A wait gave up: let copies that may still be in flight land before the CTA's memory goes away.
+    const long long start = clock64();
+    while (clock64() - start < 2000000ll) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 0) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+template <int BN, int KIND, int DUAL = 0>
+static cudaError_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
+                               cudaStream_t stream) {
+  using Cfg = GemmCfg<BN, KIND, DUAL>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, KIND, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  gemm_tc_kernel<BN, KIND, DUAL><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, p);
+  return cudaGetLastError();
+}
+
+template <int KIND>
+static cudaError_t dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
+                               cudaStream_t stream) {
+  if (p.out_mode == 4) {
+    if constexpr (KIND != 2) {
+      switch (bn) {
+        case 16: return launch_gemm<16, KIND, 1>(tmA, tmB, p, grid, stream);
+        case 32: return launch_gemm<32, KIND, 1>(tmA, tmB, p, grid, stream);
+        case 64: return launch_gemm<64, KIND, 1>(tmA, tmB, p, grid, stream);
+        case 128: return launch_gemm<128, KIND, 1>(tmA, tmB, p, grid, stream);
+        default: return cudaErrorInvalidValue;
+      }
+    }
+    return cudaErrorInvalidValue;
+  }
+  switch (bn) {
+    case 16: return launch_gemm<16, KIND>(tmA, tmB, p, grid, stream);
+    case 32: return launch_gemm<32, KIND>(tmA, tmB, p, grid, stream);
+    case 64: return launch_gemm<64, KIND>(tmA, tmB, p, grid, stream);
+    case 128: return launch_gemm<128, KIND>(tmA, tmB, p, grid, stream);
+    case 256:
+      if constexpr (KIND != 2) return launch_gemm<256, KIND>(tmA, tmB, p, grid, stream);
+      return cudaErrorInvalidValue;
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace ds41
+
+using namespace ds41;
+
+extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
+  if (a == nullptr) return cudaErrorInvalidValue;
+  const int M = a->M, N = a->N, K = a->K, batch = a->batch, kind = a->kind, out_mode = a->out_mode;
+  const int k_splits = a->k_splits, bn = a->bn;
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0 || k_splits <= 0 || kind < 0 || kind > 2 || out_mode < 0 ||
+      out_mode > 5)
+    return cudaErrorInvalidValue;
+  const int elem = kind == 0 ? 2 : 1;
+  const int bk = kTileKBytes / elem;
+  const int kb_total = (K + bk - 1) / bk;
+  if (kb_total % k_splits != 0) return cudaErrorInvalidValue;            // every split must own K blocks
+  if (kind == 2 && (K % 128 != 0 || a->sfa == nullptr || a->sfb == nullptr)) return cudaErrorInvalidValue;
+  if (kind == 2 && bn < 32 && N > bn) return cudaErrorInvalidValue;      // 16-row scale tiles cannot be lane-shifted
+  if (k_splits > 1 && out_mode != 1 && out_mode != 3) return cudaErrorInvalidValue;   // partials are fp32
+  if ((out_mode == 4 || out_mode == 5) && a->row_w == nullptr) return cudaErrorInvalidValue;
+  CUtensorMap tmA, tmB;
+  const TmaDtype dt = kind == 0 ? TmaDtype::kBF16 : TmaDtype::kU8;
+  const int a_rows = out_mode == 4 ? a->up_row_offset + M : M;           // dual tiles address gate and up rows
+  const int a_batches = a->a_batches > 0 ? a->a_batches : batch;
+  const int b_batches = a->b_batch_kind == 1 ? 1 : (a->b_batch_kind == 0 ? a_batches : batch);
+  cudaError_t e = make_tensor_map_3d(&tmA, a->A, dt, K, a_rows, a_batches, a->lda * elem, a->a_batch_stride * elem,
+                                     bk, kBM, true);
+  if (e != cudaSuccess) return e;
+  e = make_tensor_map_3d(&tmB, a->B, dt, K, N, b_batches, a->ldb * elem, a->b_batch_stride * elem, bk, bn, true);
+  if (e != cudaSuccess) return e;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.batch = batch; p.k_splits = k_splits; p.out_mode = out_mode;
+  p.ldo = a->ldo; p.out_batch_stride = a->out_batch_stride;
+  p.out = k_splits > 1 ? a->split_workspace : a->out;
+  if (p.out == nullptr) return cudaErrorInvalidValue;
+  // split planes are laid out [split][batch][rows][ldo]
+  const long long plane = (out_mode == 1 ? 1ll * M : 1ll * N) * a->ldo;
+  p.out_split_stride = k_splits > 1 ? plane * batch : 0;
+  if (k_splits > 1) p.out_batch_stride = plane;
+  p.sfa = static_cast<const uint8_t*>(a->sfa);
+  p.sfb = static_cast<const uint8_t*>(a->sfb);
+  p.sfa_batch_stride = a->sfa_batch_stride;
+  p.sfb_batch_stride = a->sfb_batch_stride;
+  p.batch_map = a->batch_map;
+  p.n_active = a->n_active;
+  p.b_batch_kind = a->b_batch_kind;
+  p.up_row_offset = a->up_row_offset;
+  p.row_w = a->row_w;
+  p.row_w_ld = a->row_w_ld;
+  p.act_limit = a->act_limit;
+  p.status = a->status;
+  const long long tiles = 1ll * ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn) * k_splits * batch;
+  const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (kind) {
+    case 0: return dispatch_bn<0>(bn, tmA, tmB, p, grid, s);
+    case 1: return dispatch_bn<1>(bn, tmA, tmB, p, grid, s);
+    default: return dispatch_bn<2>(bn, tmA, tmB, p, grid, s);
+  }
+}

@@ -1,0 +1,271 @@
+// Hyper-connection (mHC) kernels and the embedding fan-out.
+//
+// Residual state is `mult` (=4) streams per token: streams[rows][mult][H] bf16.  Per sublayer:
+//   mixes    : proj = (flat(streams) . fn[j]) * rsqrt(mean(flat^2)+norm_eps), j < 2*mult + mult^2
+//              pre  = sigmoid(proj*scale0+base)+eps, post = 2*sigmoid(proj*scale1+base),
+//              comb = Sinkhorn(softmax rows), indexed [source][destination]
+//   collapse : x = sum_s pre_in[s]*streams[s]  (pre_in comes from the PREVIOUS sublayer's mixes)
+//   expand   : streams'[d] = post[d]*sublayer + sum_s comb[s][d]*streams[s]
+// (behaviour of the reference's native/cuda/kernels/v41_hc.cu:6-29,70-120 and
+//  rust/crates/ds41rt-daemon/src/v41_hc.rs:153-225).
+//
+// Layout of the fused pipeline here:
+//   hc_post_mix  : expand with the sublayer output given as a sum of partial planes (this GPU's split-K
+//                  planes and, for tensor parallelism, every peer's planes read over NVLink), write the new
+//                  streams, and accumulate this column slice's contribution to the NEXT mixes projection.
+//   hc_finish    : reduce the slice partials in fixed order, compute pre/post/comb, collapse with the
+//                  incoming pre and apply the RMSNorm weight -> normalised bf16 rows for the GEMMs.
+#include "ds41_api.h"
+#include "ds41_ptx.cuh"
+
+namespace ds41 {
+
+constexpr int kHcMaxMult = 4;
+constexpr int kHcProj = 2 * kHcMaxMult + kHcMaxMult * kHcMaxMult;   // 24
+constexpr int kHcSlice = 128;                                       // columns of H per block
+constexpr int kHcRowsPerBlock = 4;
+constexpr int kHcPartialStride = kHcProj + 1;                       // 24 dots + sum of squares
+
+struct PartList {
+  const float* base[8];     // per rank: planes [n_splits][rows][H] fp32
+  int n_ranks;
+  int n_splits;
+  long long split_stride;   // elements between split planes
+};
+
+__global__ void embed_streams_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ embed,
+                                     __nv_bfloat16* __restrict__ streams, float* __restrict__ pre, int rows, int H,
+                                     int mult, int vocab) {
+  const int r = blockIdx.x;
+  int tok = tokens[r];
+  if (tok < 0 || tok >= vocab) tok = 0;
+  const uint4* src = reinterpret_cast<const uint4*>(embed + 1ll * tok * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    const uint4 v = src[i];
+    for (int s = 0; s < mult; ++s) reinterpret_cast<uint4*>(streams + (1ll * r * mult + s) * H)[i] = v;
+  }
+  if (threadIdx.x < mult) pre[r * mult + threadIdx.x] = threadIdx.x == 0 ? 1.0f : 0.0f;
+}
+
+// grid (H / kHcSlice, ceil(rows / kHcRowsPerBlock)), 256 threads.
+// parts.n_ranks == 0: no expand, mixes are computed on `streams_in` as they are.
+__global__ void __launch_bounds__(256)
+hc_post_mix_kernel(const __nv_bfloat16* __restrict__ streams_in, __nv_bfloat16* __restrict__ streams_out,
+                   PartList parts, const float* __restrict__ post, const float* __restrict__ comb,
+                   const float* __restrict__ fn, float* __restrict__ partial, int rows, int H,
+                   const uint32_t* const* __restrict__ wait_flags, const uint32_t* __restrict__ wait_epoch, int* status) {
+  __shared__ float xs[kHcRowsPerBlock][kHcMaxMult][kHcSlice];
+  const int c0 = blockIdx.x * kHcSlice;
+  const int r0 = blockIdx.y * kHcRowsPerBlock;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+
+  if (wait_flags != nullptr && parts.n_ranks > 1) {
+    // every peer publishes "my partial planes for this step are complete" by raising its flag
+    if (tid < parts.n_ranks) flag_wait_ge(wait_flags[tid], *wait_epoch, status, 400 + tid);
+    __syncthreads();
+  }
+  // ---- expand (or plain load) into shared memory, bf16-rounded like the stored streams
+  for (int idx = tid; idx < kHcRowsPerBlock * kHcSlice; idx += blockDim.x) {
+    const int rr = idx / kHcSlice, c = idx % kHcSlice;
+    const int r = r0 + rr;
+    float out[kHcMaxMult] = {0.f, 0.f, 0.f, 0.f};
+    if (r < rows) {
+      float s_in[kHcMaxMult];
+#pragma unroll
+      for (int s = 0; s < kHcMaxMult; ++s)
+        s_in[s] = __bfloat162float(streams_in[(1ll * r * kHcMaxMult + s) * H + c0 + c]);
+      if (parts.n_ranks > 0) {
+        float sub = 0.f;
+        for (int k = 0; k < parts.n_ranks; ++k)
+          for (int sp = 0; sp < parts.n_splits; ++sp)
+            sub += parts.base[k][sp * parts.split_stride + 1ll * r * H + c0 + c];
+        sub = bf16_round(sub);
+#pragma unroll
+        for (int d = 0; d < kHcMaxMult; ++d) {
+          float acc = 0.f;
+#pragma unroll
+          for (int s = 0; s < kHcMaxMult; ++s) acc = fmaf(comb[r * 16 + s * 4 + d], s_in[s], acc);
+          out[d] = bf16_round(fmaf(post[r * 4 + d], sub, acc));
+        }
+#pragma unroll
+        for (int d = 0; d < kHcMaxMult; ++d)
+          streams_out[(1ll * r * kHcMaxMult + d) * H + c0 + c] = __float2bfloat16_rn(out[d]);
+      } else {
+#pragma unroll
+        for (int d = 0; d < kHcMaxMult; ++d) out[d] = s_in[d];
+      }
+    }
+#pragma unroll
+    for (int d = 0; d < kHcMaxMult; ++d) xs[rr][d][c] = out[d];
+  }
+  __syncthreads();
+  // ---- partial mixes: warp w owns projections w, w+8, w+16
+  float dot[3][kHcRowsPerBlock];
+  float sq[kHcRowsPerBlock];
+#pragma unroll
+  for (int j = 0; j < 3; ++j)
+#pragma unroll
+    for (int rr = 0; rr < kHcRowsPerBlock; ++rr) dot[j][rr] = 0.f;
+#pragma unroll
+  for (int rr = 0; rr < kHcRowsPerBlock; ++rr) sq[rr] = 0.f;
+  for (int idx = lane; idx < kHcMaxMult * kHcSlice; idx += 32) {
+    const int d = idx / kHcSlice, c = idx % kHcSlice;
+    const long long kcol = 1ll * d * H + c0 + c;
+    float f[3];
+#pragma unroll
+    for (int j = 0; j < 3; ++j) f[j] = fn[1ll * (warp + 8 * j) * (kHcMaxMult * H) + kcol];
+#pragma unroll
+    for (int rr = 0; rr < kHcRowsPerBlock; ++rr) {
+      const float x = xs[rr][d][c];
+#pragma unroll
+      for (int j = 0; j < 3; ++j) dot[j][rr] = fmaf(x, f[j], dot[j][rr]);
+      if (warp == 0) sq[rr] = fmaf(x, x, sq[rr]);
+    }
+  }
+#pragma unroll
+  for (int rr = 0; rr < kHcRowsPerBlock; ++rr) {
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      const float v = warp_sum(dot[j][rr]);
+      if (lane == 0 && r0 + rr < rows)
+        partial[(1ll * blockIdx.x * rows + r0 + rr) * kHcPartialStride + warp + 8 * j] = v;
+    }
+    if (warp == 0) {
+      const float v = warp_sum(sq[rr]);
+      if (lane == 0 && r0 + rr < rows) partial[(1ll * blockIdx.x * rows + r0 + rr) * kHcPartialStride + kHcProj] = v;
+    }
+  }
+}
+
+// One block per row.  Produces next_pre/post/comb from the slice partials, then the collapsed,
+// normalised row.  `norm_w` may be null (no weight).
+__global__ void __launch_bounds__(256)
+hc_finish_kernel(const float* __restrict__ partial, int n_slices, const float* __restrict__ scale,
+                 const float* __restrict__ base, const float* __restrict__ pre_in,
+                 const __nv_bfloat16* __restrict__ streams, const float* __restrict__ norm_w,
+                 float* __restrict__ next_pre, float* __restrict__ post, float* __restrict__ comb,
+                 __nv_bfloat16* __restrict__ xn, float* __restrict__ tap_mean, int rows, int H, int iters,
+                 float hc_eps, float norm_eps) {
+  __shared__ float proj[kHcProj + 1];
+  __shared__ float warp_part[8];
+  __shared__ float inv_rms;
+  const int r = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid <= kHcProj) {
+    float acc = 0.f;
+    for (int s = 0; s < n_slices; ++s) acc += partial[(1ll * s * rows + r) * kHcPartialStride + tid];
+    proj[tid] = acc;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const float inv = rsqrtf(proj[kHcProj] / (4.0f * H) + norm_eps);
+    if (lane < 4) {
+      const float a = fmaf(proj[lane] * inv, scale[0], base[lane]);
+      const float b = fmaf(proj[lane + 4] * inv, scale[1], base[lane + 4]);
+      next_pre[r * 4 + lane] = 1.0f / (1.0f + __expf(-a)) + hc_eps;
+      post[r * 4 + lane] = 2.0f / (1.0f + __expf(-b));
+    }
+    // comb: lane = s*4 + d for lanes < 16
+    float v = lane < 16 ? fmaf(proj[8 + lane] * inv, scale[2], base[8 + lane]) : 0.f;
+    float mx = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    v = __expf(v - mx);
+    float sum = v + __shfl_xor_sync(0xffffffffu, v, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    v = v / sum + hc_eps;
+    sum = v + __shfl_xor_sync(0xffffffffu, v, 4);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+    v /= sum + hc_eps;
+    for (int it = 1; it < iters; ++it) {
+      sum = v + __shfl_xor_sync(0xffffffffu, v, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      v /= sum + hc_eps;
+      sum = v + __shfl_xor_sync(0xffffffffu, v, 4);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+      v /= sum + hc_eps;
+    }
+    if (lane < 16) comb[r * 16 + lane] = v;
+  }
+  // ---- collapse with the incoming pre + RMSNorm
+  const float p0 = pre_in[r * 4 + 0], p1 = pre_in[r * 4 + 1], p2 = pre_in[r * 4 + 2], p3 = pre_in[r * 4 + 3];
+  const __nv_bfloat16* s0 = streams + 1ll * r * 4 * H;
+  float local_sq = 0.f;
+  // H <= 256 * 2 * 16: keep this thread's collapsed values in registers
+  constexpr int kMaxPairs = 16;
+  float2 keep[kMaxPairs];
+  int np = 0;
+  for (int i = tid; i < H / 2 && np < kMaxPairs; i += 256, ++np) {
+    const float2 a = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(s0)[i]);
+    const float2 b = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(s0 + H)[i]);
+    const float2 c = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(s0 + 2 * H)[i]);
+    const float2 d = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(s0 + 3 * H)[i]);
+    float2 x;
+    x.x = bf16_round(fmaf(p3, d.x, fmaf(p2, c.x, fmaf(p1, b.x, p0 * a.x))));
+    x.y = bf16_round(fmaf(p3, d.y, fmaf(p2, c.y, fmaf(p1, b.y, p0 * a.y))));
+    if (tap_mean != nullptr) {
+      tap_mean[1ll * r * H + 2 * i] = 0.25f * (a.x + b.x + c.x + d.x);
+      tap_mean[1ll * r * H + 2 * i + 1] = 0.25f * (a.y + b.y + c.y + d.y);
+    }
+    keep[np] = x;
+    local_sq = fmaf(x.x, x.x, fmaf(x.y, x.y, local_sq));
+  }
+  local_sq = warp_sum(local_sq);
+  if (lane == 0) warp_part[warp] = local_sq;
+  __syncthreads();
+  if (tid == 0) {
+    float t = 0.f;
+    for (int w = 0; w < 8; ++w) t += warp_part[w];
+    inv_rms = rsqrtf(t / H + norm_eps);
+  }
+  __syncthreads();
+  const float inv = inv_rms;
+  np = 0;
+  for (int i = tid; i < H / 2 && np < kMaxPairs; i += 256, ++np) {
+    float wx = 1.f, wy = 1.f;
+    if (norm_w != nullptr) { wx = norm_w[2 * i]; wy = norm_w[2 * i + 1]; }
+    reinterpret_cast<__nv_bfloat162*>(xn + 1ll * r * H)[i] =
+        __floats2bfloat162_rn(keep[np].x * inv * wx, keep[np].y * inv * wy);
+  }
+}
+
+}  // namespace ds41
+
+using namespace ds41;
+
+extern "C" int ds41_embed_streams(const int* tokens, const void* embed, void* streams, float* pre, int rows, int H,
+                                  int mult, int vocab, void* stream) {
+  if (rows <= 0 || H % 8 != 0 || mult != kHcMaxMult) return cudaErrorInvalidValue;
+  embed_streams_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      tokens, static_cast<const __nv_bfloat16*>(embed), static_cast<__nv_bfloat16*>(streams), pre, rows, H, mult,
+      vocab);
+  return cudaGetLastError();
+}
+
+extern "C" int ds41_hc_post_mix(const void* streams_in, void* streams_out, const float* const* part_bases,
+                                int n_ranks, int n_splits, long long split_stride, const float* post,
+                                const float* comb, const float* fn, float* partial, int rows, int H,
+                                const uint32_t* const* wait_flags, const uint32_t* wait_epoch, int* status, void* stream) {
+  if (rows <= 0 || H % kHcSlice != 0 || n_ranks < 0 || n_ranks > 8) return cudaErrorInvalidValue;
+  PartList parts{};
+  parts.n_ranks = n_ranks;
+  parts.n_splits = n_splits;
+  parts.split_stride = split_stride;
+  for (int i = 0; i < n_ranks; ++i) parts.base[i] = part_bases[i];
+  dim3 grid(H / kHcSlice, (rows + kHcRowsPerBlock - 1) / kHcRowsPerBlock);
+  hc_post_mix_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(streams_in), static_cast<__nv_bfloat16*>(streams_out), parts, post, comb, fn,
+      partial, rows, H, wait_flags, wait_epoch, status);
+  return cudaGetLastError();
+}
+
+extern "C" int ds41_hc_finish(const float* partial, int n_slices, const float* scale, const float* base,
+                              const float* pre_in, const void* streams, const float* norm_w, float* next_pre,
+                              float* post, float* comb, void* xn, float* tap_mean, int rows, int H, int iters,
+                              float hc_eps, float norm_eps, void* stream) {
+  if (rows <= 0 || H % 2 != 0 || H > 256 * 2 * 16) return cudaErrorInvalidValue;
+  hc_finish_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      partial, n_slices, scale, base, pre_in, static_cast<const __nv_bfloat16*>(streams), norm_w, next_pre, post,
+      comb, static_cast<__nv_bfloat16*>(xn), tap_mean, rows, H, iters, hc_eps, norm_eps);
+  return cudaGetLastError();
+}

@@ -1,0 +1,544 @@
+// Lightning-indexer scoring, exact top-k selection and sparse latent attention (decode / small-batch form).
+//
+//  index_score : score[r][c] = sum_h w[r][h] * relu(q[r][h] . key[c])   over the visible compressed rows
+//                (native/cuda/kernels/v41_index_scores.cu:36-103)
+//  topk_select : exact top-k by (score desc, row asc), emitted in ascending row order, all rows when
+//                n_visible <= k (native/cuda/kernels/v41_index_topk.cu:25-124 semantics)
+//  attend      : MQA over {window ring rows [pos-W+1, pos]} U {selected compressed rows}; K == V == one
+//                latent of width D whose tail is rotary; per-head sink logit joins the softmax denominator;
+//                keys are split across CTAs (64 per CTA) and merged, inverse RoPE applied to the output
+//                (native/cuda/kernels/v41_sparse_attention.cu:89-381 semantics)
+// The attention tiles use warp-level mma (m16n8k16 bf16): this kernel is latency/bandwidth bound at
+// decode batch sizes, each CTA touching 64 gathered 1 KiB rows.
+#include "ds41_api.h"
+#include "ds41_ptx.cuh"
+
+namespace ds41 {
+
+__device__ __forceinline__ void rope_cs2(int pos, float inv_freq, float* c, float* s) {
+  const double a = static_cast<double>(pos) * static_cast<double>(inv_freq);
+  const double two_pi = 6.283185307179586476925286766559;
+  const double red = a - floor(a / two_pi) * two_pi;
+  sincosf(static_cast<float>(red), s, c);
+}
+
+__device__ __forceinline__ long long pool_row(const int* page_table, int max_pages, int page_rows, int slot, int id) {
+  const int page = page_table[1ll * slot * max_pages + id / page_rows];
+  return page < 0 ? -1ll : 1ll * page * page_rows + id % page_rows;
+}
+
+// ---------------------------------------------------------------------------------------- index score
+struct IndexScoreParams {
+  const __nv_bfloat16* q;     // [rows][ldq], index heads start at column q_off: [IH][ID]
+  long long ldq;
+  int q_off;
+  const float* w;             // [rows][w_stride], head weights at column w_off
+  int w_stride, w_off;
+  const __nv_bfloat16* idx_pool;
+  const int* page_table;
+  int max_pages, page_rows;
+  const int* row_pos;
+  const int* row_slot;
+  const float* inv_freq_idx;  // [ID/4]
+  int rows, IH, ID, ratio;
+  float* scores;              // [rows][max_keys]
+  int max_keys;
+};
+
+// grid (blocks_x, rows), 256 threads; IH <= 32, ID <= 128
+__global__ void __launch_bounds__(256) index_score_kernel(IndexScoreParams p) {
+  __shared__ float qs[32][129];
+  __shared__ float ws[32];
+  __shared__ float kbuf[8][128];
+  const int r = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int pos = p.row_pos[r], slot = p.row_slot[r];
+  if (slot < 0) return;
+  const int n_vis = min((pos + 1) / p.ratio, p.max_keys);
+  if (blockIdx.x * 8 >= n_vis) return;
+  const int rope0 = p.ID - p.ID / 2;
+  for (int idx = tid; idx < p.IH * p.ID / 2; idx += 256) {
+    const int h = idx / (p.ID / 2), i = idx % (p.ID / 2);
+    const float2 v = __bfloat1622float2(
+        *reinterpret_cast<const __nv_bfloat162*>(p.q + 1ll * r * p.ldq + p.q_off + h * p.ID + 2 * i));
+    float a = v.x, b = v.y;
+    const int t = 2 * i - rope0;
+    if (t >= 0) {
+      float c, s;
+      rope_cs2(pos, p.inv_freq_idx[t / 2], &c, &s);
+      const float ra = a * c - b * s, rb = b * c + a * s;
+      a = bf16_round(ra);
+      b = bf16_round(rb);
+    }
+    qs[h][2 * i] = a;
+    qs[h][2 * i + 1] = b;
+  }
+  if (tid < 32) ws[tid] = tid < p.IH ? p.w[1ll * r * p.w_stride + p.w_off + tid] : 0.f;
+  __syncthreads();
+  for (int c = blockIdx.x * 8 + warp; c < n_vis; c += gridDim.x * 8) {
+    const long long phys = pool_row(p.page_table, p.max_pages, p.page_rows, slot, c);
+    __syncwarp();
+    for (int d = lane * 2; d < p.ID; d += 64) {
+      float2 v = make_float2(0.f, 0.f);
+      if (phys >= 0) v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p.idx_pool + phys * p.ID + d));
+      kbuf[warp][d] = v.x;
+      kbuf[warp][d + 1] = v.y;
+    }
+    __syncwarp();
+    float acc = 0.f;
+    if (lane < p.IH) {
+      for (int d = 0; d < p.ID; ++d) acc = fmaf(qs[lane][d], kbuf[warp][d], acc);
+      acc = fmaxf(acc, 0.f) * ws[lane];
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) p.scores[1ll * r * p.max_keys + c] = phys >= 0 ? acc : -INFINITY;
+  }
+}
+
+// ---------------------------------------------------------------------------------------- top-k
+__device__ __forceinline__ uint32_t orderable(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// exclusive scan over 1024 threads; returns this thread's exclusive prefix, *total gets the block sum
+__device__ __forceinline__ int block_excl_scan_1024(int v, int* warp_tot /*[32]*/, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int n = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += n;
+  }
+  __syncthreads();
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int t = warp_tot[lane];
+    int ti = t;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, ti, o);
+      if (lane >= o) ti += n;
+    }
+    warp_tot[lane] = ti - t;   // exclusive warp offsets
+    if (lane == 31) *total = ti;
+  }
+  __syncthreads();
+  return warp_tot[warp] + incl - v;
+}
+
+struct TopkParams {
+  const float* scores;   // [rows][max_keys]
+  int max_keys;
+  const int* row_pos;
+  const int* row_slot;
+  int ratio, k;
+  int* sel;              // [rows][k]  ascending ids, -1 padded
+  int* n_sel;            // [rows]
+};
+
+__global__ void __launch_bounds__(1024) topk_select_kernel(TopkParams p) {
+  __shared__ int hist[256];
+  __shared__ int warp_tot[32];
+  __shared__ int s_total;
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_need;
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const int pos = p.row_pos[r];
+  int* out = p.sel + 1ll * r * p.k;
+  if (p.row_slot[r] < 0) {
+    for (int i = tid; i < p.k; i += 1024) out[i] = -1;
+    if (tid == 0) p.n_sel[r] = 0;
+    return;
+  }
+  const int n = min((pos + 1) / p.ratio, p.max_keys);
+  if (n <= p.k) {
+    for (int i = tid; i < p.k; i += 1024) out[i] = i < n ? i : -1;
+    if (tid == 0) p.n_sel[r] = n;
+    return;
+  }
+  const float* sc = p.scores + 1ll * r * p.max_keys;
+  // ---- radix select of the k-th largest key (4 passes of 8 bits)
+  uint32_t prefix = 0, mask = 0;
+  int need = p.k;
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    if (tid < 256) hist[tid] = 0;
+    __syncthreads();
+    for (int i = tid; i < n; i += 1024) {
+      const uint32_t u = orderable(sc[i]);
+      if ((u & mask) == prefix) atomicAdd(&hist[(u >> shift) & 255], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int cum = 0, d = 255;
+      for (; d > 0; --d) {
+        if (cum + hist[d] >= need) break;
+        cum += hist[d];
+      }
+      s_prefix = prefix | (static_cast<uint32_t>(d) << shift);
+      s_need = need - cum;
+    }
+    __syncthreads();
+    prefix = s_prefix;
+    need = s_need;
+    mask |= 0xFFu << shift;
+    __syncthreads();
+  }
+  const uint32_t thr = prefix;      // exact key of the k-th largest element; `need` of the equal ones are kept
+  // ---- ordered compaction (ascending row id): keep key > thr, and the first `need` keys == thr
+  int base = 0, eq_base = 0;
+  for (int c0 = 0; c0 < n; c0 += 1024) {
+    const int i = c0 + tid;
+    uint32_t u = 0;
+    if (i < n) u = orderable(sc[i]);
+    const int is_eq = (i < n && u == thr) ? 1 : 0;
+    int eq_total;
+    const int eq_rank = eq_base + block_excl_scan_1024(is_eq, warp_tot, &s_total);
+    __syncthreads();
+    eq_total = s_total;
+    const int keep = (i < n && (u > thr || (is_eq && eq_rank < need))) ? 1 : 0;
+    const int at = base + block_excl_scan_1024(keep, warp_tot, &s_total);
+    __syncthreads();
+    if (keep && at < p.k) out[at] = i;
+    base += s_total;
+    eq_base += eq_total;
+    __syncthreads();
+  }
+  if (tid == 0) p.n_sel[r] = min(base, p.k);
+}
+
+// ---------------------------------------------------------------------------------------- attention
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+               : "=r"(r0), "=r"(r1)
+               : "r"(smem_u32(smem_row)));
+}
+
+struct AttendParams {
+  const __nv_bfloat16* q;      // [rows][ldq]; local head h at column q_off + h*D
+  long long ldq;
+  int q_off;
+  int rows, heads, window, ring;
+  const int* row_pos;
+  const int* row_slot;
+  const __nv_bfloat16* win;    // [slots][ring][D]
+  const __nv_bfloat16* comp_pool;   // may be null (window-only layer)
+  const int* sel;              // [rows][k]
+  const int* n_sel;            // [rows]
+  int k;
+  const int* page_table;
+  int max_pages, page_rows;
+  const float* inv_freq;       // [rope_dim/2]
+  int rope_dim;
+  float scale;
+  int n_splits;
+  const int* row_hi;           // optional [rows]: highest visible window position (>= pos); null = causal
+  float* part_o;               // [rows][n_splits][heads][D]
+  float* part_ml;              // [rows][n_splits][heads][2]
+};
+
+constexpr int kKeysPerCta = 64;
+
+template <int D>
+__global__ void __launch_bounds__(512) attend_kernel(AttendParams p) {
+  constexpr int LD = D + 8;                                // padded row (bf16 elements)
+  extern __shared__ __align__(16) uint8_t smem_attn[];
+  const int n_mt = (p.heads + 15) / 16;
+  __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_attn);                 // [64][LD]
+  __nv_bfloat16* sQ = sK + kKeysPerCta * LD;                                         // [16*n_mt][LD]
+  float* sS = reinterpret_cast<float*>(sQ + 16 * n_mt * LD);                         // [16*n_mt][65]
+  __nv_bfloat16* sP = reinterpret_cast<__nv_bfloat16*>(sS + 16 * n_mt * 65);         // [16*n_mt][72]
+  float* sCos = reinterpret_cast<float*>(sP + 16 * n_mt * 72);                       // [rope_dim/2] x2
+  float* sSin = sCos + 64;
+  const __nv_bfloat16** sPtr = reinterpret_cast<const __nv_bfloat16**>(sSin + 64);   // [64]
+
+  const int split = blockIdx.x, r = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nthreads = blockDim.x;
+  const int pos = p.row_pos[r], slot = p.row_slot[r];
+  const int g = lane >> 2, t4 = lane & 3;
+  float* ml_out = p.part_ml + ((1ll * r * p.n_splits + split) * p.heads) * 2;
+  float* o_out = p.part_o + ((1ll * r * p.n_splits + split) * p.heads) * D;
+
+  int n_w = 0, n_s = 0, hi_pos = pos, lo_pos = 0;
+  if (slot >= 0) {
+    // drafter rows may see later rows of their own block: row_hi gives the highest visible position
+    if (p.row_hi != nullptr) hi_pos = max(pos, p.row_hi[r]);
+    lo_pos = max(0, pos - p.window + 1);
+    n_w = hi_pos - lo_pos + 1;
+    n_s = (p.comp_pool != nullptr && p.n_sel != nullptr) ? p.n_sel[r] : 0;
+  }
+  const int n_keys = n_w + n_s;
+  const int k0 = split * kKeysPerCta;
+  const int k_cnt = max(0, min(kKeysPerCta, n_keys - k0));
+  if (k_cnt == 0) {
+    for (int h = tid; h < p.heads; h += nthreads) {
+      ml_out[2 * h] = -INFINITY;
+      ml_out[2 * h + 1] = 0.f;
+    }
+    return;
+  }
+  // ---- key pointers + rope table
+  if (tid < kKeysPerCta) {
+    const __nv_bfloat16* ptr = nullptr;
+    const int j = k0 + tid;
+    if (tid < k_cnt) {
+      if (j < n_w) {
+        const int kp = lo_pos + j;
+        ptr = p.win + (1ll * slot * p.ring + (kp % p.ring)) * D;
+      } else {
+        const int id = p.sel[1ll * r * p.k + (j - n_w)];
+        const long long phys = id < 0 ? -1 : pool_row(p.page_table, p.max_pages, p.page_rows, slot, id);
+        if (phys >= 0) ptr = p.comp_pool + phys * D;
+      }
+    }
+    sPtr[tid] = ptr;
+  }
+  if (tid < p.rope_dim / 2) rope_cs2(pos, p.inv_freq[tid], &sCos[tid], &sSin[tid]);
+  __syncthreads();
+  // ---- K tile (zero-filled beyond k_cnt)
+  for (int idx = tid; idx < kKeysPerCta * (D / 8); idx += nthreads) {
+    const int key = idx / (D / 8), ch = idx % (D / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    const __nv_bfloat16* src = sPtr[key];
+    if (src != nullptr) v = *reinterpret_cast<const uint4*>(src + ch * 8);
+    *reinterpret_cast<uint4*>(sK + key * LD + ch * 8) = v;
+  }
+  // ---- Q tile with RoPE on the tail (zero rows for padding heads)
+  const int rope0 = D - p.rope_dim;
+  for (int idx = tid; idx < 16 * n_mt * (D / 2); idx += nthreads) {
+    const int h = idx / (D / 2), i = idx % (D / 2);
+    float a = 0.f, b = 0.f;
+    if (h < p.heads) {
+      const float2 v = __bfloat1622float2(
+          *reinterpret_cast<const __nv_bfloat162*>(p.q + 1ll * r * p.ldq + p.q_off + 1ll * h * D + 2 * i));
+      a = v.x;
+      b = v.y;
+      const int t = 2 * i - rope0;
+      if (t >= 0) {
+        const float c = sCos[t / 2], s = sSin[t / 2];
+        const float ra = a * c - b * s, rb = b * c + a * s;
+        a = ra;
+        b = rb;
+      }
+    }
+    *reinterpret_cast<__nv_bfloat162*>(sQ + h * LD + 2 * i) = __floats2bfloat162_rn(a, b);
+  }
+  __syncthreads();
+  const int mt = warp % n_mt, part = warp / n_mt;     // part in 0..3
+  // ---- S = Q K^T for 16 heads x 16 keys per warp
+  {
+    float c[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    const __nv_bfloat16* qa = sQ + (mt * 16 + g) * LD + 2 * t4;
+    const __nv_bfloat16* kb = sK + (part * 16 + g) * LD + 2 * t4;
+#pragma unroll 4
+    for (int kk = 0; kk < D; kk += 16) {
+      uint32_t a[4];
+      a[0] = *reinterpret_cast<const uint32_t*>(qa + kk);
+      a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + kk);
+      a[2] = *reinterpret_cast<const uint32_t*>(qa + kk + 8);
+      a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + kk + 8);
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb + nt * 8 * LD + kk);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kb + nt * 8 * LD + kk + 8);
+        mma_bf16_16816(c[nt], a, b0, b1);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const int key = part * 16 + nt * 8 + 2 * t4;
+      float* s0 = sS + (mt * 16 + g) * 65 + key;
+      float* s1 = sS + (mt * 16 + g + 8) * 65 + key;
+      s0[0] = key < k_cnt ? c[nt][0] * p.scale : -INFINITY;
+      s0[1] = key + 1 < k_cnt ? c[nt][1] * p.scale : -INFINITY;
+      s1[0] = key < k_cnt ? c[nt][2] * p.scale : -INFINITY;
+      s1[1] = key + 1 < k_cnt ? c[nt][3] * p.scale : -INFINITY;
+    }
+  }
+  __syncthreads();
+  // ---- per-head softmax statistics over this CTA's keys; P in bf16
+  for (int row = warp; row < 16 * n_mt; row += (nthreads >> 5)) {
+    const float v0 = sS[row * 65 + lane], v1 = sS[row * 65 + lane + 32];
+    const float m = warp_max(fmaxf(v0, v1));
+    const float e0 = __expf(v0 - m), e1 = __expf(v1 - m);
+    const __nv_bfloat16 b0 = __float2bfloat16_rn(e0), b1 = __float2bfloat16_rn(e1);
+    const float l = warp_sum(__bfloat162float(b0) + __bfloat162float(b1));
+    sP[row * 72 + lane] = b0;
+    sP[row * 72 + lane + 32] = b1;
+    if (lane == 0 && row < p.heads) {
+      ml_out[2 * row] = m;
+      ml_out[2 * row + 1] = l;
+    }
+  }
+  __syncthreads();
+  // ---- O = P V : warp (mt, part) owns dims [part*D/4, (part+1)*D/4)
+  {
+    constexpr int NT = D / 32;
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[nt][j] = 0.f;
+    const int d_base = part * (D / 4);
+#pragma unroll
+    for (int kk = 0; kk < kKeysPerCta; kk += 16) {
+      uint32_t a[4];
+      const __nv_bfloat16* pa = sP + (mt * 16 + g) * 72 + kk + 2 * t4;
+      a[0] = *reinterpret_cast<const uint32_t*>(pa);
+      a[1] = *reinterpret_cast<const uint32_t*>(pa + 8 * 72);
+      a[2] = *reinterpret_cast<const uint32_t*>(pa + 8);
+      a[3] = *reinterpret_cast<const uint32_t*>(pa + 8 * 72 + 8);
+      const __nv_bfloat16* vrow = sK + (kk + (lane & 15)) * LD + d_base;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        uint32_t b0, b1;
+        ldmatrix_x2_trans(b0, b1, vrow + nt * 8);
+        mma_bf16_16816(acc[nt], a, b0, b1);
+      }
+    }
+    const int h0 = mt * 16 + g, h1 = h0 + 8;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int d = d_base + nt * 8 + 2 * t4;
+      if (h0 < p.heads) *reinterpret_cast<float2*>(o_out + 1ll * h0 * D + d) = make_float2(acc[nt][0], acc[nt][1]);
+      if (h1 < p.heads) *reinterpret_cast<float2*>(o_out + 1ll * h1 * D + d) = make_float2(acc[nt][2], acc[nt][3]);
+    }
+  }
+}
+
+struct MergeParams {
+  const float* part_o;
+  const float* part_ml;
+  const float* sink;        // [heads] (this rank's heads)
+  const int* row_pos;
+  const int* row_slot;
+  const float* inv_freq;
+  int rope_dim, heads, D, n_splits;
+  __nv_bfloat16* out;       // [rows][ldo], head h at column h*D
+  long long ldo;
+};
+
+// grid (heads, rows), 128 threads
+__global__ void __launch_bounds__(128) attend_merge_kernel(MergeParams p) {
+  const int h = blockIdx.x, r = blockIdx.y, tid = threadIdx.x;
+  const float sink = p.sink[h];
+  float m = sink;
+  for (int s = 0; s < p.n_splits; ++s) m = fmaxf(m, p.part_ml[((1ll * r * p.n_splits + s) * p.heads + h) * 2]);
+  float denom = __expf(sink - m);
+  for (int s = 0; s < p.n_splits; ++s) {
+    const float* ml = p.part_ml + ((1ll * r * p.n_splits + s) * p.heads + h) * 2;
+    if (ml[1] > 0.f) denom += ml[1] * __expf(ml[0] - m);
+  }
+  const int pos = p.row_pos[r];
+  const int rope0 = p.D - p.rope_dim;
+  const bool live = p.row_slot[r] >= 0;
+  for (int i = tid; i < p.D / 2; i += 128) {
+    float a = 0.f, b = 0.f;
+    for (int s = 0; s < p.n_splits; ++s) {
+      const float* ml = p.part_ml + ((1ll * r * p.n_splits + s) * p.heads + h) * 2;
+      if (ml[1] > 0.f) {
+        const float w = __expf(ml[0] - m);
+        const float2 v = *reinterpret_cast<const float2*>(p.part_o + ((1ll * r * p.n_splits + s) * p.heads + h) * p.D + 2 * i);
+        a = fmaf(w, v.x, a);
+        b = fmaf(w, v.y, b);
+      }
+    }
+    a /= denom;
+    b /= denom;
+    const int t = 2 * i - rope0;
+    if (t >= 0) {
+      float c, s;
+      rope_cs2(pos, p.inv_freq[t / 2], &c, &s);
+      const float ra = a * c + b * s, rb = b * c - a * s;     // inverse rotation
+      a = ra;
+      b = rb;
+    }
+    if (!live) { a = 0.f; b = 0.f; }
+    *reinterpret_cast<__nv_bfloat162*>(p.out + 1ll * r * p.ldo + 1ll * h * p.D + 2 * i) = __floats2bfloat162_rn(a, b);
+  }
+}
+
+template <int D>
+static size_t attend_smem(int heads) {
+  const int n_mt = (heads + 15) / 16;
+  const int LD = D + 8;
+  return size_t(kKeysPerCta) * LD * 2 + size_t(16) * n_mt * LD * 2 + size_t(16) * n_mt * 65 * 4 +
+         size_t(16) * n_mt * 72 * 2 + 128 * 4 + 64 * 8 + 64;
+}
+
+template <int D>
+static cudaError_t launch_attend(const AttendParams& p, cudaStream_t stream) {
+  const int n_mt = (p.heads + 15) / 16;
+  const size_t smem = attend_smem<D>(p.heads);
+  static size_t configured[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && configured[dev] < smem) {
+    cudaError_t e = cudaFuncSetAttribute(attend_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    configured[dev] = 200 * 1024;
+  }
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  dim3 grid(p.n_splits, p.rows);
+  attend_kernel<D><<<grid, 128 * n_mt, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace ds41
+
+using namespace ds41;
+
+extern "C" int ds41_index_score(const void* q, long long ldq, int q_off, const float* w, int w_stride, int w_off,
+                                const void* idx_pool, const int* page_table, int max_pages, int page_rows,
+                                const int* row_pos, const int* row_slot, const float* inv_freq_idx, int rows, int IH,
+                                int ID, int ratio, float* scores, int max_keys, void* stream) {
+  if (rows <= 0 || IH > 32 || ID > 128 || (ID & 3)) return cudaErrorInvalidValue;
+  IndexScoreParams p{static_cast<const __nv_bfloat16*>(q), ldq, q_off, w, w_stride, w_off,
+                     static_cast<const __nv_bfloat16*>(idx_pool), page_table, max_pages, page_rows, row_pos,
+                     row_slot, inv_freq_idx, rows, IH, ID, ratio, scores, max_keys};
+  int bx = (max_keys + 7) / 8;
+  if (bx > 256) bx = 256;
+  dim3 grid(bx, rows);
+  index_score_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError();
+}
+
+extern "C" int ds41_topk_select(const float* scores, int max_keys, const int* row_pos, const int* row_slot,
+                                int ratio, int k, int* sel, int* n_sel, int rows, void* stream) {
+  if (rows <= 0 || k <= 0) return cudaErrorInvalidValue;
+  TopkParams p{scores, max_keys, row_pos, row_slot, ratio, k, sel, n_sel};
+  topk_select_kernel<<<rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError();
+}
+
+extern "C" int ds41_attend(const void* q, long long ldq, int q_off, int rows, int heads, int D, int window, int ring,
+                           const int* row_pos, const int* row_slot, const void* win, const void* comp_pool,
+                           const int* sel, const int* n_sel, int k, const int* page_table, int max_pages,
+                           int page_rows, const float* inv_freq, int rope_dim, float scale, int n_splits,
+                           const int* row_hi, float* part_o, float* part_ml, const float* sink, void* out,
+                           long long ldo, void* stream) {
+  if (rows <= 0 || heads <= 0 || heads > 64 || rope_dim > 128 || (rope_dim & 1) || n_splits <= 0)
+    return cudaErrorInvalidValue;
+  AttendParams p{static_cast<const __nv_bfloat16*>(q), ldq, q_off, rows, heads, window, ring, row_pos, row_slot,
+                 static_cast<const __nv_bfloat16*>(win), static_cast<const __nv_bfloat16*>(comp_pool), sel, n_sel, k,
+                 page_table, max_pages, page_rows, inv_freq, rope_dim, scale, n_splits, row_hi, part_o, part_ml};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (D == 512) e = launch_attend<512>(p, s);
+  else if (D == 128) e = launch_attend<128>(p, s);
+  else return cudaErrorInvalidValue;
+  if (e != cudaSuccess) return e;
+  MergeParams m{part_o, part_ml, sink, row_pos, row_slot, inv_freq, rope_dim, heads, D, n_splits,
+                static_cast<__nv_bfloat16*>(out), ldo};
+  dim3 grid(heads, rows);
+  attend_merge_kernel<<<grid, 128, 0, s>>>(m);
+  return cudaGetLastError();
+}

@@ -1,0 +1,597 @@
+"""GPU execution of the DS41 architecture with the hand-written sm_100a kernels.
+
+`DS41Engine` owns one rank's weight shards, caches and step buffers and enqueues one
+"rows" pass (a decode step, a speculative verification chunk or a prefill chunk) as a fixed
+sequence of kernel launches on the current stream - the sequence is CUDA-graph capturable
+because every buffer is static and every data-dependent quantity (routes, selections, active
+experts) stays on the device.
+
+Parallel layout (world = tensor/expert-parallel degree on one NVSwitch box):
+  * attention heads and wo_a groups sharded by rank, wo_b column-sharded -> fp32 partial planes
+  * routed experts sharded by rank (EP), shared expert intermediate-sharded (TP) -> one partial plane
+  * the partial planes live in symmetric memory; the next hyper-connection kernel sums every rank's
+    plane with P2P loads in fixed rank order (deterministic one-shot all-reduce fused into the consumer)
+  * vocabulary head row-sharded; greedy candidates merged through symmetric memory
+
+Per-layer order of operations follows rust/crates/ds41rt-daemon/src/v41_backbone_execution.rs:615-677
+and v41_hc.rs:153-225 (see models/reference.py for the mathematics).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config import ModelConfig, rope_inv_freq
+from ..ops import gemm as G
+from ..ops import lib
+from ..parallel.fabric import Fabric, SymBuffer
+
+BF16 = torch.bfloat16
+F32 = torch.float32
+I32 = torch.int32
+
+
+@dataclass
+class LayerWeights:
+    # hyper-connections
+    hc_attn_fn: torch.Tensor = None
+    hc_attn_scale: torch.Tensor = None
+    hc_attn_base: torch.Tensor = None
+    hc_ffn_fn: torch.Tensor = None
+    hc_ffn_scale: torch.Tensor = None
+    hc_ffn_base: torch.Tensor = None
+    attn_norm: torch.Tensor = None
+    ffn_norm: torch.Tensor = None
+    # attention
+    w_qkv: torch.Tensor = None          # [Q + D (+2D|D) (+IH), H]
+    q_norm: torch.Tensor = None
+    kv_norm: torch.Tensor = None
+    w_qb: torch.Tensor = None           # [HL*D (+IH*ID), Q]
+    wo_a: torch.Tensor = None           # [G_local, o_lora, hpg*D]
+    wo_b: torch.Tensor = None           # [H, G_local*o_lora]
+    sink: torch.Tensor = None
+    # compressor / indexer
+    comp_norm: Optional[torch.Tensor] = None
+    wk_idx: Optional[torch.Tensor] = None
+    k_norm: Optional[torch.Tensor] = None
+    # MoE
+    w_gate_sh: torch.Tensor = None      # [E + 2*I_sh, H]
+    gate_bias: torch.Tensor = None
+    w2_sh: torch.Tensor = None          # [H, I_sh]
+    w13: torch.Tensor = None            # [E_local, 2I, H]
+    w2: torch.Tensor = None             # [E_local, H, I]
+    n_experts: int = 0
+    topk: int = 0
+    extra_cols: int = 0
+    index_heads_cols: int = 0
+    ratio: int = 0                      # > 0: this layer produces a compressed source
+
+
+class EngineWeights:
+    """One rank's shard of the model in kernel layout."""
+
+    def __init__(self, cfg: ModelConfig, rank: int, world: int, device):
+        self.cfg, self.rank, self.world, self.device = cfg, rank, world, device
+        self.layers: List[LayerWeights] = []
+        self.embed = None
+        self.head = None           # [V_local, H]
+        self.final_norm = None
+        assert cfg.n_heads % world == 0 and cfg.o_groups % world == 0 and cfg.n_experts % world == 0
+        assert cfg.vocab % world == 0 and cfg.inter % world == 0
+        self.HL = cfg.n_heads // world
+        self.GL = cfg.o_groups // world
+        self.I_sh = cfg.inter // world
+        self.V_local = cfg.vocab // world
+
+    @staticmethod
+    def from_fp32(cfg: ModelConfig, w: Dict[str, torch.Tensor], rank: int, world: int, device,
+                  prefix: str = "layers", n_layers: Optional[int] = None, n_experts: Optional[int] = None,
+                  topk: Optional[int] = None) -> "EngineWeights":
+        ew = EngineWeights(cfg, rank, world, device)
+        D, H = cfg.head_dim, cfg.hidden
+        dev = lambda t, dt=BF16: t.to(device=device, dtype=dt).contiguous()
+        ew.embed = dev(w["embed.weight"])
+        v0 = rank * ew.V_local
+        ew.head = dev(w["head.weight"][v0:v0 + ew.V_local])
+        ew.final_norm = dev(w["norm.weight"], F32)
+        n_layers = cfg.n_layers if n_layers is None else n_layers
+        E = cfg.n_experts if n_experts is None else n_experts
+        k = cfg.topk if topk is None else topk
+        assert E % world == 0
+        EL = E // world
+        h0, h1 = rank * ew.HL, (rank + 1) * ew.HL
+        g0, g1 = rank * ew.GL, (rank + 1) * ew.GL
+        for l in range(n_layers):
+            p = f"{prefix}.{l}"
+            lw = LayerWeights(n_experts=E, topk=k)
+            for kind in ("attn", "ffn"):
+                setattr(lw, f"hc_{kind}_fn", dev(w[f"{p}.hc_{kind}_fn"], F32))
+                setattr(lw, f"hc_{kind}_scale", dev(w[f"{p}.hc_{kind}_scale"], F32))
+                setattr(lw, f"hc_{kind}_base", dev(w[f"{p}.hc_{kind}_base"], F32))
+            lw.attn_norm = dev(w[f"{p}.attn_norm.weight"], F32)
+            lw.ffn_norm = dev(w[f"{p}.ffn_norm.weight"], F32)
+            parts = [w[f"{p}.attn.wq_a.weight"], w[f"{p}.attn.wkv.weight"]]
+            extra = 0
+            is_source = prefix == "layers" and l in cfg.source_layers
+            is_index = prefix == "layers" and l in cfg.index_layers
+            if is_source:
+                lw.ratio = cfg.source_layers[l]
+                parts.append(w[f"{p}.attn.compressor.wkv.weight"])
+                extra += D
+                if lw.ratio == 2:
+                    parts.append(w[f"{p}.attn.compressor.wgate.weight"])
+                    extra += D
+                lw.comp_norm = dev(w[f"{p}.attn.compressor.norm.weight"], F32)
+                lw.wk_idx = dev(w[f"{p}.attn.indexer.wk.weight"])
+                lw.k_norm = dev(w[f"{p}.attn.indexer.k_norm.weight"], F32)
+            if is_index:
+                parts.append(w[f"{p}.attn.indexer.weights_proj.weight"])
+                extra += cfg.index_heads
+                lw.index_heads_cols = cfg.index_heads
+            lw.extra_cols = extra
+            lw.w_qkv = dev(torch.cat(parts, 0))
+            lw.q_norm = dev(w[f"{p}.attn.q_norm.weight"], F32)
+            lw.kv_norm = dev(w[f"{p}.attn.kv_norm.weight"], F32)
+            qb = [w[f"{p}.attn.wq_b.weight"][h0 * D:h1 * D]]
+            if is_index:
+                qb.append(w[f"{p}.attn.indexer.wq_b.weight"])
+            lw.w_qb = dev(torch.cat(qb, 0))
+            wo_a = w[f"{p}.attn.wo_a.weight"].view(cfg.o_groups, cfg.o_lora, cfg.heads_per_group * D)
+            lw.wo_a = dev(wo_a[g0:g1])
+            lw.wo_b = dev(w[f"{p}.attn.wo_b.weight"][:, g0 * cfg.o_lora:g1 * cfg.o_lora])
+            lw.sink = dev(w[f"{p}.attn.attn_sink"][h0:h1], F32)
+            i0, i1 = rank * ew.I_sh, (rank + 1) * ew.I_sh
+            lw.w_gate_sh = dev(torch.cat([w[f"{p}.ffn.gate.weight"], w[f"{p}.ffn.shared_experts.w1.weight"][i0:i1],
+                                          w[f"{p}.ffn.shared_experts.w3.weight"][i0:i1]], 0))
+            lw.gate_bias = dev(w[f"{p}.ffn.gate.bias"], F32)
+            lw.w2_sh = dev(w[f"{p}.ffn.shared_experts.w2.weight"][:, i0:i1])
+            e0 = rank * EL
+            lw.w13 = dev(torch.stack([torch.cat([w[f"{p}.ffn.experts.{e}.w1.weight"],
+                                                 w[f"{p}.ffn.experts.{e}.w3.weight"]], 0)
+                                      for e in range(e0, e0 + EL)], 0))
+            lw.w2 = dev(torch.stack([w[f"{p}.ffn.experts.{e}.w2.weight"] for e in range(e0, e0 + EL)], 0))
+            ew.layers.append(lw)
+        return ew
+
+    @staticmethod
+    def random(cfg: ModelConfig, rank: int, world: int, device, seed: int = 0, std: float = 0.02,
+               router_std: Optional[float] = None) -> "EngineWeights":
+        """Random-init shard generated directly on the device (for models too large to stage on the host)."""
+        ew = EngineWeights(cfg, rank, world, device)
+        D, H, Q = cfg.head_dim, cfg.hidden, cfg.q_lora
+        gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
+        shared_gen = torch.Generator(device=device).manual_seed(seed * 1000 + 999)   # replicated tensors
+
+        def rnd(shape, g=gen, s=std, dt=BF16):
+            chunk = torch.empty(shape, dtype=dt, device=device)
+            flat = chunk.view(-1)
+            step = 1 << 26
+            for i in range(0, flat.numel(), step):
+                n = min(step, flat.numel() - i)
+                flat[i:i + n] = (torch.randn(n, generator=g, device=device, dtype=F32) * s).to(dt)
+            return chunk
+
+        ones = lambda n: torch.ones(n, dtype=F32, device=device)
+        ew.embed = rnd((cfg.vocab, H), shared_gen)
+        ew.head = rnd((ew.V_local, H))
+        ew.final_norm = ones(H)
+        EL = cfg.n_experts // world
+        nproj = 2 * cfg.hc_mult + cfg.hc_mult ** 2
+        for l in range(cfg.n_layers):
+            lw = LayerWeights(n_experts=cfg.n_experts, topk=cfg.topk)
+            for kind in ("attn", "ffn"):
+                setattr(lw, f"hc_{kind}_fn", rnd((nproj, cfg.hc_mult * H), shared_gen, 0.5, F32))
+                setattr(lw, f"hc_{kind}_scale", ones(3))
+                setattr(lw, f"hc_{kind}_base", rnd((nproj,), shared_gen, 0.5, F32))
+            lw.attn_norm, lw.ffn_norm = ones(H), ones(H)
+            extra = 0
+            if l in cfg.source_layers:
+                lw.ratio = cfg.source_layers[l]
+                extra += D * (2 if lw.ratio == 2 else 1)
+                lw.comp_norm = ones(D)
+                lw.wk_idx = rnd((cfg.index_dim, D), shared_gen)
+                lw.k_norm = ones(cfg.index_dim)
+            if l in cfg.index_layers:
+                extra += cfg.index_heads
+                lw.index_heads_cols = cfg.index_heads
+            lw.extra_cols = extra
+            lw.w_qkv = rnd((Q + D + extra, H), shared_gen)
+            lw.q_norm, lw.kv_norm = ones(Q), ones(D)
+            nqb = ew.HL * D + (cfg.index_heads * cfg.index_dim if l in cfg.index_layers else 0)
+            lw.w_qb = rnd((nqb, Q))
+            lw.wo_a = rnd((ew.GL, cfg.o_lora, cfg.heads_per_group * D))
+            lw.wo_b = rnd((H, ew.GL * cfg.o_lora))
+            lw.sink = rnd((ew.HL,), gen, 0.5, F32)
+            lw.w_gate_sh = rnd((cfg.n_experts + 2 * ew.I_sh, H), shared_gen)
+            if router_std is not None:
+                lw.w_gate_sh[:cfg.n_experts] = rnd((cfg.n_experts, H), shared_gen, router_std / math.sqrt(H) * 1.0)
+            lw.gate_bias = rnd((cfg.n_experts,), shared_gen, 0.01, F32)
+            lw.w2_sh = rnd((H, ew.I_sh))
+            lw.w13 = rnd((EL, 2 * cfg.inter, H))
+            lw.w2 = rnd((EL, H, cfg.inter))
+            ew.layers.append(lw)
+        return ew
+
+    def nbytes(self) -> int:
+        total = 0
+        for t in [self.embed, self.head, self.final_norm]:
+            total += t.numel() * t.element_size()
+        for lw in self.layers:
+            for v in vars(lw).values():
+                if isinstance(v, torch.Tensor):
+                    total += v.numel() * v.element_size()
+        return total
+
+
+class KVCache:
+    """Window rings, paged compressed pools and the page table for `slots` concurrent requests.
+
+    A page covers `page_tokens` token positions; a source with compress ratio r stores
+    page_tokens / r rows per page, so every source shares one page table
+    (sizing rule: native counterpart rust/crates/ds41rt-daemon/src/v41_native_serve/memory.rs:9-13,137)."""
+
+    def __init__(self, cfg: ModelConfig, n_layers: int, slots: int, max_ctx: int, device, page_tokens: int = 64,
+                 n_pages: Optional[int] = None, spec_slack: int = 16):
+        self.cfg, self.slots, self.max_ctx, self.page_tokens = cfg, slots, max_ctx, page_tokens
+        D = cfg.head_dim
+        ring = cfg.window + spec_slack
+        self.ring = ring
+        self.max_pages = (max_ctx + page_tokens - 1) // page_tokens
+        self.n_pages = n_pages if n_pages is not None else self.max_pages * slots
+        self.win = torch.zeros(n_layers, slots, ring, D, dtype=BF16, device=device)
+        self.comp: Dict[int, torch.Tensor] = {}
+        self.idx: Dict[int, torch.Tensor] = {}
+        self.pending: Dict[int, torch.Tensor] = {}
+        self.page_rows: Dict[int, int] = {}
+        for src, ratio in cfg.source_layers.items():
+            if src >= n_layers:
+                continue
+            pr = page_tokens // ratio
+            self.page_rows[src] = pr
+            self.comp[src] = torch.zeros(self.n_pages * pr, D, dtype=BF16, device=device)
+            self.idx[src] = torch.zeros(self.n_pages * pr, cfg.index_dim, dtype=BF16, device=device)
+            if ratio == 2:
+                self.pending[src] = torch.zeros(slots, 4, 2 * D, dtype=F32, device=device)
+        self.page_table_host = torch.full((slots, self.max_pages), -1, dtype=I32)
+        self.page_table = self.page_table_host.to(device)
+        self.free_pages = list(range(self.n_pages - 1, -1, -1))
+        self.pages_of: Dict[int, List[int]] = {s: [] for s in range(slots)}
+
+    def ensure(self, slot: int, n_tokens: int) -> bool:
+        """Make sure `slot` has pages for positions [0, n_tokens).  Returns False when the pool is exhausted."""
+        need = (n_tokens + self.page_tokens - 1) // self.page_tokens
+        have = len(self.pages_of[slot])
+        if need <= have:
+            return True
+        if need > self.max_pages or need - have > len(self.free_pages):
+            return False
+        for i in range(have, need):
+            pg = self.free_pages.pop()
+            self.pages_of[slot].append(pg)
+            self.page_table_host[slot, i] = pg
+        self.page_table[slot, :need].copy_(self.page_table_host[slot, :need], non_blocking=True)
+        return True
+
+    def release(self, slot: int):
+        self.free_pages.extend(reversed(self.pages_of[slot]))
+        self.pages_of[slot] = []
+        self.page_table_host[slot].fill_(-1)
+        self.page_table[slot].fill_(-1)
+
+    def nbytes(self) -> int:
+        ts = [self.win] + list(self.comp.values()) + list(self.idx.values()) + list(self.pending.values())
+        return sum(t.numel() * t.element_size() for t in ts)
+
+
+class DS41Engine:
+    def __init__(self, cfg: ModelConfig, weights: EngineWeights, fabric: Optional[Fabric] = None, *,
+                 max_rows: int = 8, slots: int = 1, max_ctx: int = 4096, page_tokens: int = 64,
+                 n_pages: Optional[int] = None, row_hi: bool = False):
+        self.cfg, self.w = cfg, weights
+        self.fabric = fabric or Fabric.single(weights.device)
+        self.rank, self.world = self.fabric.rank, self.fabric.world
+        self.device = dev = weights.device
+        self.max_rows = R = max_rows
+        self.n_layers = len(weights.layers)
+        H, D, Q = cfg.hidden, cfg.head_dim, cfg.q_lora
+        self.k = lib.kernels()
+        self.cache = KVCache(cfg, self.n_layers, slots, max_ctx, dev, page_tokens, n_pages)
+        self.HL, self.GL, self.I_sh, self.V_local = weights.HL, weights.GL, weights.I_sh, weights.V_local
+        E = weights.layers[0].n_experts if weights.layers else cfg.n_experts
+        self.E, self.topk = E, (weights.layers[0].topk if weights.layers else cfg.topk)
+        self.EL = E // self.world
+        self.max_active = min(R * self.topk, self.EL)
+        z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=dev)
+        # inputs
+        self.in_tokens = z((R,), I32)
+        self.row_pos = z((R,), I32)
+        self.row_slot = z((R,), I32)
+        self.row_hi = z((R,), I32) if row_hi else None
+        # residual state
+        self.streams = z((R, cfg.hc_mult, H), BF16)
+        self.pre = [z((R, 4), F32), z((R, 4), F32)]
+        self.post = z((R, 4), F32)
+        self.comb = z((R, 16), F32)
+        self.n_slices = H // 128
+        self.hc_partial = z((self.n_slices, R, 25), F32)
+        self.xn = z((R, H), BF16)
+        self.taps = z((3, R, H), F32) if cfg.dspark is not None else None
+        # attention
+        max_extra = max([lw.extra_cols for lw in weights.layers] + [0])
+        self.ntot_qkv = Q + D + max_extra
+        self.max_splits = 16
+        self.planes_qkv = z((self.max_splits, R, self.ntot_qkv), F32)
+        self.q_lat = z((R, Q), BF16)
+        self.extras = z((R, max(max_extra, 1)), F32)
+        self.nqb = self.HL * D + cfg.index_heads * cfg.index_dim
+        self.qb_out = z((R, self.nqb), BF16)
+        self.max_keys = max_ctx
+        self.scores = z((R, self.max_keys), F32)
+        self.sel = z((R, cfg.index_topk), I32)
+        self.n_sel = z((R,), I32)
+        self.n_splits_attn = (cfg.window + 16 + cfg.index_topk + 63) // 64
+        self.part_o = z((R, self.n_splits_attn, self.HL, D), F32)
+        self.part_ml = z((R, self.n_splits_attn, self.HL, 2), F32)
+        self.attn_out = z((R, self.HL * D), BF16)
+        self.oa = z((R, self.GL * cfg.o_lora), BF16)
+        # MoE
+        self.ntot_gate = E + 2 * self.I_sh
+        self.planes_gate = z((self.max_splits, R, self.ntot_gate), F32)
+        self.ids = z((R, self.topk), I32)
+        self.route_w = z((R, self.topk), F32)
+        self.shared_act = z((R, self.I_sh), BF16)
+        self.active = z((self.max_active,), I32)
+        self.n_active = z((1,), I32)
+        self.row_w = z((self.max_active, R), F32)
+        self.slot_of = z((R, self.topk), I32)
+        self.act = z((self.max_active, R, cfg.inter), BF16)
+        self.fc2 = z((self.max_active, R, H), F32)
+        self.planes_shared = z((self.max_splits, R, H), F32)
+        # head
+        self.logits = z((R, self.V_local), F32)
+        self.chosen = z((R,), I32)
+        self.status = lib.new_status(dev)
+        # symmetric buffers: [attn planes | moe plane | flag | best_val | best_idx]
+        self.o_plane_bytes = self.max_splits * R * H * 4
+        self.moe_plane_bytes = R * H * 4
+        off_flag = self.o_plane_bytes + self.moe_plane_bytes
+        off_best = off_flag + 256
+        total = off_best + 2 * R * 4 + 256
+        self.sym: SymBuffer = self.fabric.alloc(total)
+        self.planes_o = self.sym.view(F32, (self.max_splits, R, H), 0)
+        self.moe_plane = self.sym.view(F32, (R, H), self.o_plane_bytes)
+        self.flag = self.sym.view(torch.int32, (1,), off_flag)
+        self.best_val = self.sym.view(F32, (R,), off_best)
+        self.best_idx = self.sym.view(I32, (R,), off_best + R * 4)
+        self.epoch = z((1,), I32)
+        peers = self.sym.peer_ptrs
+        self._o_bases = (C.c_void_p * self.world)(*[p for p in peers])
+        self._moe_bases = (C.c_void_p * self.world)(*[p + self.o_plane_bytes for p in peers])
+        self._val_ptrs = (C.c_void_p * self.world)(*[p + off_best for p in peers])
+        self._idx_ptrs = (C.c_void_p * self.world)(*[p + off_best + R * 4 for p in peers])
+        self.flag_ptrs = torch.tensor([p + off_flag for p in peers], dtype=torch.int64, device=dev)
+        # rope tables
+        self.inv_plain = torch.tensor(rope_inv_freq(cfg.rope_plain, cfg.rope_dim), dtype=F32, device=dev)
+        self.inv_long = torch.tensor(rope_inv_freq(cfg.rope_long, cfg.rope_dim), dtype=F32, device=dev)
+        self.inv_idx = torch.tensor(rope_inv_freq(cfg.rope_long, cfg.index_dim // 2), dtype=F32, device=dev)
+        self.layer_prefix_plain = False   # drafter blocks use the plain rope
+        self.launches = 0
+
+    # ------------------------------------------------------------------ helpers
+    def _inv(self, layer: int) -> torch.Tensor:
+        if self.layer_prefix_plain or self.cfg.compress_ratios[layer] == 0:
+            return self.inv_plain
+        return self.inv_long
+
+    def _ck(self, err, what):
+        self.launches += 1
+        lib.check(err, what)
+
+    def set_rows(self, tokens, positions, slots, row_hi=None):
+        """Host -> device copy of one pass's inputs (lists or CPU tensors)."""
+        n = len(tokens)
+        assert n <= self.max_rows
+        pad = self.max_rows - n
+        t = torch.tensor(list(tokens) + [0] * pad, dtype=I32)
+        p = torch.tensor(list(positions) + [0] * pad, dtype=I32)
+        s = torch.tensor(list(slots) + [-1] * pad, dtype=I32)
+        self.in_tokens.copy_(t, non_blocking=True)
+        self.row_pos.copy_(p, non_blocking=True)
+        self.row_slot.copy_(s, non_blocking=True)
+        if self.row_hi is not None:
+            h = torch.tensor(list(row_hi if row_hi is not None else positions) + [0] * pad, dtype=I32)
+            self.row_hi.copy_(h, non_blocking=True)
+
+    def _post_mix(self, rows, part_bases, n_ranks, n_splits, split_stride, fn, sync):
+        k, st = self.k, lib.stream()
+        wait_flags = lib.ptr(self.flag_ptrs) if (sync and self.world > 1) else lib.ptr(None)
+        self._ck(k.ds41_hc_post_mix(
+            lib.ptr(self.streams), lib.ptr(self.streams), part_bases, n_ranks, n_splits, C.c_longlong(split_stride),
+            lib.ptr(self.post), lib.ptr(self.comb), lib.ptr(fn), lib.ptr(self.hc_partial), rows, self.cfg.hidden,
+            wait_flags, lib.ptr(self.epoch), lib.ptr(self.status), st), "hc_post_mix")
+
+    def _finish(self, rows, scale, base, pre_in, norm_w, next_pre, tap=None):
+        cfg = self.cfg
+        self._ck(self.k.ds41_hc_finish(
+            lib.ptr(self.hc_partial), self.n_slices, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
+            lib.ptr(self.streams), lib.ptr(norm_w), lib.ptr(next_pre), lib.ptr(self.post), lib.ptr(self.comb),
+            lib.ptr(self.xn), lib.ptr(tap), rows, cfg.hidden, cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps),
+            C.c_float(cfg.norm_eps), lib.stream()), "hc_finish")
+
+    def _signal(self):
+        if self.world > 1:
+            self._ck(self.k.ds41_signal(lib.ptr(self.epoch), lib.ptr(self.flag), lib.stream()), "signal")
+
+    # ------------------------------------------------------------------ one pass over `rows` rows
+    def forward_rows(self, rows: int, *, embed: bool = True, head: bool = True, first_layer: int = 0,
+                     last_layer: Optional[int] = None):
+        cfg, k, st = self.cfg, self.k, lib.stream
+        H, D, Q = cfg.hidden, cfg.head_dim, cfg.q_lora
+        R = rows
+        last_layer = self.n_layers if last_layer is None else last_layer
+        cur = 0
+        if embed:
+            self._ck(k.ds41_embed_streams(lib.ptr(self.in_tokens), lib.ptr(self.w.embed), lib.ptr(self.streams),
+                                          lib.ptr(self.pre[0]), R, H, cfg.hc_mult, cfg.vocab, st()), "embed")
+        if first_layer < last_layer:
+            self._post_mix(R, None, 0, 0, 0, self.w.layers[first_layer].hc_attn_fn, sync=False)
+        tap_i = 0
+        for l in range(first_layer, last_layer):
+            lw = self.w.layers[l]
+            inv = self._inv(l)
+            # ---------------- attention sublayer
+            tap = None
+            if self.taps is not None and cfg.dspark is not None and not self.layer_prefix_plain \
+                    and l in cfg.dspark.tap_layers and tap_i < self.taps.shape[0]:
+                tap = self.taps[tap_i]
+                tap_i += 1
+            self._finish(R, lw.hc_attn_scale, lw.hc_attn_base, self.pre[cur], lw.attn_norm, self.pre[cur ^ 1], tap)
+            cur ^= 1
+            ntot = lw.w_qkv.shape[0]
+            s_qkv = G.pick_splits(ntot, H, max_splits=self.max_splits)
+            G.linear_planes(self.xn[:R], lw.w_qkv, self.planes_qkv.view(-1)[: s_qkv * R * ntot].view(s_qkv, R, ntot),
+                            s_qkv, status=self.status)
+            self.launches += 1
+            self._ck(k.ds41_qkv_post(
+                lib.ptr(self.planes_qkv), s_qkv, R, ntot, Q, D, cfg.rope_dim, lw.extra_cols, lw.index_heads_cols,
+                C.c_float(cfg.index_weight_scale), lib.ptr(lw.q_norm), lib.ptr(lw.kv_norm), lib.ptr(inv),
+                lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.q_lat), lib.ptr(self.cache.win[l]),
+                self.cache.ring, lib.ptr(self.extras), C.c_float(cfg.norm_eps), st()), "qkv_post")
+            src = None if self.layer_prefix_plain else cfg.source_of(l)
+            if lw.ratio:
+                self._ck(k.ds41_compress(
+                    lib.ptr(self.extras), lw.extra_cols, R, D, cfg.index_dim, cfg.rope_dim, lw.ratio,
+                    lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.cache.pending.get(l)),
+                    lib.ptr(lw.comp_norm), lib.ptr(lw.wk_idx), lib.ptr(lw.k_norm), lib.ptr(inv), lib.ptr(self.inv_idx),
+                    lib.ptr(self.cache.page_table), self.cache.max_pages, self.cache.page_rows[l],
+                    lib.ptr(self.cache.comp[l]), lib.ptr(self.cache.idx[l]), C.c_float(cfg.norm_eps), st()),
+                    "compress")
+            nqb = lw.w_qb.shape[0]
+            G.gemm_raw(lw.w_qb, self.q_lat, self.qb_out, nqb, R, Q, lda=Q, ldb=Q, ldo=self.nqb, out_mode=2,
+                       status=self.status)
+            self.launches += 1
+            if lw.index_heads_cols and src is not None:
+                ratio = cfg.source_layers[src]
+                self._ck(k.ds41_index_score(
+                    lib.ptr(self.qb_out), C.c_longlong(self.nqb), self.HL * D, lib.ptr(self.extras), lw.extra_cols,
+                    lw.extra_cols - cfg.index_heads, lib.ptr(self.cache.idx[src]), lib.ptr(self.cache.page_table),
+                    self.cache.max_pages, self.cache.page_rows[src], lib.ptr(self.row_pos), lib.ptr(self.row_slot),
+                    lib.ptr(self.inv_idx), R, cfg.index_heads, cfg.index_dim, ratio, lib.ptr(self.scores),
+                    self.max_keys, st()), "index_score")
+                self._ck(k.ds41_topk_select(lib.ptr(self.scores), self.max_keys, lib.ptr(self.row_pos),
+                                            lib.ptr(self.row_slot), ratio, cfg.index_topk, lib.ptr(self.sel),
+                                            lib.ptr(self.n_sel), R, st()), "topk")
+            self._ck(k.ds41_attend(
+                lib.ptr(self.qb_out), C.c_longlong(self.nqb), 0, R, self.HL, D, cfg.window, self.cache.ring,
+                lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.cache.win[l]),
+                lib.ptr(self.cache.comp[src]) if src is not None else lib.ptr(None),
+                lib.ptr(self.sel), lib.ptr(self.n_sel), cfg.index_topk, lib.ptr(self.cache.page_table),
+                self.cache.max_pages, self.cache.page_rows[src] if src is not None else 1, lib.ptr(inv), cfg.rope_dim,
+                C.c_float(cfg.softmax_scale), self.n_splits_attn, lib.ptr(self.row_hi), lib.ptr(self.part_o),
+                lib.ptr(self.part_ml), lib.ptr(lw.sink), lib.ptr(self.attn_out), C.c_longlong(self.HL * D), st()),
+                "attend")
+            self.launches += 1
+            # grouped wo_a: batch = local groups
+            kg = cfg.heads_per_group * D
+            G.gemm_raw(lw.wo_a, self.attn_out, self.oa, cfg.o_lora, R, kg, lda=kg, ldb=self.HL * D,
+                       ldo=self.GL * cfg.o_lora, out_mode=2, batch=self.GL, a_batch_stride=cfg.o_lora * kg,
+                       b_batch_stride=kg, out_batch_stride=cfg.o_lora, status=self.status)
+            ko = self.GL * cfg.o_lora
+            s_o = G.pick_splits(H, ko, max_splits=self.max_splits)
+            G.linear_planes(self.oa[:R], lw.wo_b, self.planes_o.view(-1)[: s_o * R * H].view(s_o, R, H), s_o,
+                            status=self.status)
+            self.launches += 2
+            self._signal()
+            self._post_mix(R, self._o_bases, self.world, s_o, R * H, lw.hc_ffn_fn, sync=True)
+            # ---------------- MoE sublayer
+            self._finish(R, lw.hc_ffn_scale, lw.hc_ffn_base, self.pre[cur], lw.ffn_norm, self.pre[cur ^ 1])
+            cur ^= 1
+            ng = lw.w_gate_sh.shape[0]
+            s_g = G.pick_splits(ng, H, max_splits=self.max_splits)
+            G.linear_planes(self.xn[:R], lw.w_gate_sh, self.planes_gate.view(-1)[: s_g * R * ng].view(s_g, R, ng),
+                            s_g, status=self.status)
+            self.launches += 1
+            self._ck(k.ds41_router_select(
+                lib.ptr(self.planes_gate), s_g, R, ng, lw.n_experts, self.I_sh, lw.topk, lib.ptr(lw.gate_bias),
+                C.c_float(cfg.route_scale), C.c_float(cfg.swiglu_limit), lib.ptr(self.ids), lib.ptr(self.route_w),
+                lib.ptr(self.shared_act), st()), "router_select")
+            EL = lw.n_experts // self.world
+            self._ck(k.ds41_moe_plan(
+                lib.ptr(self.ids), lib.ptr(self.route_w), lib.ptr(self.row_slot), R, lw.topk, self.rank * EL,
+                (self.rank + 1) * EL, self.max_active, self.max_rows, lib.ptr(self.active), lib.ptr(self.n_active),
+                lib.ptr(self.row_w), lib.ptr(self.slot_of), st()), "moe_plan")
+            I = cfg.inter
+            bn = G.pick_bn(R)
+            # FC1: act[slot][row][i] = swiglu(W1 x, W3 x) * route weight
+            G.gemm_raw(lw.w13, self.xn, self.act, I, R, H, lda=H, ldb=H, ldo=I, out_mode=4, bn=bn,
+                       batch=self.max_active, a_batches=EL, a_batch_stride=2 * I * H, out_batch_stride=R * I,
+                       batch_map=self.active, n_active=self.n_active, b_batch_kind=1, up_row_offset=I,
+                       row_w=self.row_w, row_w_ld=self.max_rows, act_limit=cfg.swiglu_limit, status=self.status)
+            # FC2: fc2[slot][row][h]
+            G.gemm_raw(lw.w2, self.act, self.fc2, H, R, I, lda=I, ldb=I, ldo=H, out_mode=5, bn=bn,
+                       batch=self.max_active, a_batches=EL, a_batch_stride=H * I, b_batch_stride=R * I,
+                       out_batch_stride=R * H, batch_map=self.active, n_active=self.n_active, b_batch_kind=2,
+                       row_w=self.row_w, row_w_ld=self.max_rows, status=self.status)
+            s_s = G.pick_splits(H, self.I_sh, max_splits=self.max_splits)
+            G.linear_planes(self.shared_act[:R], lw.w2_sh,
+                            self.planes_shared.view(-1)[: s_s * R * H].view(s_s, R, H), s_s, status=self.status)
+            self.launches += 3
+            self._ck(k.ds41_moe_combine(lib.ptr(self.fc2), lib.ptr(self.slot_of), lib.ptr(self.planes_shared), s_s,
+                                        R, lw.topk, H, lib.ptr(self.moe_plane), st()), "moe_combine")
+            self._signal()
+            nxt = self.w.layers[l + 1].hc_attn_fn if l + 1 < self.n_layers else self.w.layers[0].hc_attn_fn
+            self._post_mix(R, self._moe_bases, self.world, 1, 0, nxt, sync=True)
+        self._cur = cur
+        if head:
+            self.head_rows(R)
+
+    def head_rows(self, rows: int, mask: Optional[torch.Tensor] = None):
+        """collapse -> final norm -> vocabulary shard GEMM -> greedy candidate (+ cross-rank merge)."""
+        cfg, k, st = self.cfg, self.k, lib.stream
+        lw0 = self.w.layers[0]
+        cur = self._cur
+        self._finish(rows, lw0.hc_attn_scale, lw0.hc_attn_base, self.pre[cur], self.w.final_norm, self.pre[cur ^ 1])
+        G.gemm_raw(self.w.head, self.xn, self.logits, self.V_local, rows, cfg.hidden, lda=cfg.hidden, ldb=cfg.hidden,
+                   ldo=self.V_local, out_mode=3, status=self.status)
+        self.launches += 1
+        self._ck(k.ds41_argmax_rows(
+            lib.ptr(self.logits), C.c_longlong(self.V_local), rows, self.V_local, self.rank * self.V_local,
+            lib.ptr(mask), 0 if mask is None else mask.shape[-1], lib.ptr(self.best_val), lib.ptr(self.best_idx),
+            lib.ptr(None), st()), "argmax_rows")
+        self._signal()
+        wait_flags = lib.ptr(self.flag_ptrs) if self.world > 1 else lib.ptr(None)
+        self._ck(k.ds41_argmax_merge(self._val_ptrs, self._idx_ptrs, self.world, rows, lib.ptr(self.chosen),
+                                     wait_flags, lib.ptr(self.epoch), lib.ptr(self.status), st()), "argmax_merge")
+
+    # ------------------------------------------------------------------ convenience drivers
+    def prefill(self, slot: int, tokens: List[int], start: int = 0, chunk: Optional[int] = None) -> int:
+        """Run the prompt through the engine in chunks of up to max_rows rows; returns the greedy next token."""
+        chunk = chunk or self.max_rows
+        assert self.cache.ensure(slot, start + len(tokens) + 1)
+        nxt = -1
+        for c0 in range(0, len(tokens), chunk):
+            part = tokens[c0:c0 + chunk]
+            pos = list(range(start + c0, start + c0 + len(part)))
+            self.set_rows(part, pos, [slot] * len(part))
+            last = c0 + chunk >= len(tokens)
+            self.forward_rows(self.max_rows if len(part) == self.max_rows else len(part), head=last)
+            if last:
+                nxt = int(self.chosen[len(part) - 1].item())
+        return nxt
+
+    def logits_rows(self, rows: int) -> torch.Tensor:
+        """Full-vocabulary fp32 logits of the last pass (gathers vocabulary shards over the process group)."""
+        local = self.logits[:rows].clone()
+        if self.world == 1:
+            return local
+        import torch.distributed as dist
+        parts = [torch.empty_like(local) for _ in range(self.world)]
+        dist.all_gather(parts, local, group=self.fabric.group)
+        return torch.cat(parts, dim=1)
+
+    def check_status(self, what: str = "engine pass"):
+        lib.raise_on_status(self.status, what)

@@ -1,0 +1,106 @@
+"""ctypes bindings for libds41_kernels.so / libds41_core.so.
+
+The kernels library is a plain C ABI: every call is asynchronous on the current
+torch CUDA stream, allocation-free, and returns a cudaError_t.  `kernels()` builds
+the library on first use when it is missing and raises loudly if it cannot be
+loaded on a CUDA machine - there is no silent PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import torch
+
+_LIBDIR = Path(__file__).resolve().parent.parent / "_lib"
+_kernels = None
+_core = None
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("A", C.c_void_p), ("B", C.c_void_p), ("out", C.c_void_p), ("split_workspace", C.c_void_p),
+        ("sfa", C.c_void_p), ("sfb", C.c_void_p), ("batch_map", C.c_void_p), ("n_active", C.c_void_p),
+        ("row_w", C.c_void_p), ("status", C.c_void_p),
+        ("lda", C.c_longlong), ("ldb", C.c_longlong), ("ldo", C.c_longlong),
+        ("a_batch_stride", C.c_longlong), ("b_batch_stride", C.c_longlong), ("out_batch_stride", C.c_longlong),
+        ("sfa_batch_stride", C.c_longlong), ("sfb_batch_stride", C.c_longlong),
+        ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("batch", C.c_int), ("a_batches", C.c_int),
+        ("kind", C.c_int), ("out_mode", C.c_int), ("k_splits", C.c_int), ("bn", C.c_int),
+        ("b_batch_kind", C.c_int), ("up_row_offset", C.c_int), ("row_w_ld", C.c_int), ("act_limit", C.c_float),
+    ]
+
+
+def _load(name: str, builder: str):
+    path = _LIBDIR / name
+    if not path.exists() or os.environ.get("DS41_REBUILD"):
+        from .. import build
+        getattr(build, builder)()
+    return C.CDLL(str(path), mode=C.RTLD_GLOBAL)
+
+
+def kernels():
+    global _kernels
+    if _kernels is None:
+        lib = _load("libds41_kernels.so", "build_kernels")
+        for fn in dir_functions():
+            getattr(lib, fn).restype = C.c_int
+        _kernels = lib
+    return _kernels
+
+
+def core():
+    global _core
+    if _core is None:
+        _core = _load("libds41_core.so", "build_core")
+    return _core
+
+
+def dir_functions():
+    return [
+        "ds41_gemm_tc", "ds41_embed_streams", "ds41_hc_post_mix", "ds41_hc_finish", "ds41_qkv_post",
+        "ds41_compress", "ds41_index_score", "ds41_topk_select", "ds41_attend", "ds41_router_select",
+        "ds41_moe_plan", "ds41_moe_combine", "ds41_signal", "ds41_reduce_planes", "ds41_argmax_rows",
+        "ds41_argmax_merge", "ds41_spec_accept",
+    ]
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def check(err: int, what: str):
+    if err != 0:
+        raise KernelError(f"{what}: cudaError {err}")
+
+
+def ptr(t) -> C.c_void_p:
+    if t is None:
+        return C.c_void_p(0)
+    if isinstance(t, int):
+        return C.c_void_p(t)
+    return C.c_void_p(t.data_ptr())
+
+
+def stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+STATUS_NAMES = {0: "ok", 1: "mbarrier wait timed out", 2: "flag wait timed out", 3: "bad argument"}
+
+
+def new_status(device) -> torch.Tensor:
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+def read_status(status: torch.Tensor):
+    """Synchronising read of a kernel status word -> (code, where, block, detail)."""
+    vals = status.tolist()
+    return tuple(vals)
+
+
+def raise_on_status(status: torch.Tensor, what: str = "kernel"):
+    code, where, block, detail = read_status(status)
+    if code != 0:
+        raise KernelError(f"{what}: {STATUS_NAMES.get(code, code)} at site {where}, block {block}, detail {detail}")

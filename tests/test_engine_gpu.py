@@ -1,0 +1,96 @@
+"""End-to-end: tiny DS41 model on the GPU engine vs the CPU fp32 oracle (prefill + greedy decode)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(cfg_name="tiny", max_rows=8, max_ctx=512):
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.weights import init_weights
+    from ds41rt_b200.models.reference import ReferenceModel
+    from ds41rt_b200.models.ds41 import EngineWeights, DS41Engine
+    cfg = getattr(ModelConfig, cfg_name)()
+    w = init_weights(cfg, seed=0)
+    # the engine stores matrices in bf16: give the oracle the same rounded values
+    wr = {k: (v.bfloat16().float() if v.dim() == 2 and not k.endswith("_fn") else v) for k, v in w.items()}
+    ref = ReferenceModel(cfg, wr)
+    ew = EngineWeights.from_fp32(cfg, wr, 0, 1, torch.device("cuda"))
+    eng = DS41Engine(cfg, ew, max_rows=max_rows, slots=2, max_ctx=max_ctx)
+    return cfg, ref, eng
+
+
+def test_prefill_logits_match_oracle():
+    cfg, ref, eng = _setup(max_rows=8)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (128,), generator=g)
+    with torch.no_grad():
+        want = ref.forward(prompt)
+    assert eng.cache.ensure(0, 200)
+    got = []
+    toks = prompt.tolist()
+    for c0 in range(0, len(toks), 8):
+        part = toks[c0:c0 + 8]
+        eng.set_rows(part, list(range(c0, c0 + len(part))), [0] * len(part))
+        eng.forward_rows(len(part))
+        got.append(eng.logits_rows(len(part)).cpu())
+    torch.cuda.synchronize()
+    eng.check_status()
+    got = torch.cat(got, 0)
+    err = (got - want).abs().max(dim=1).values
+    scale = want.abs().max()
+    print("max logit err per position (first/last 5):", err[:5].tolist(), err[-5:].tolist(), "scale", float(scale))
+    assert float(err.max()) < 0.06 * float(scale)
+    agree = (got.argmax(-1) == want.argmax(-1)).float().mean()
+    assert float(agree) > 0.9
+
+
+def test_greedy_decode_matches_oracle():
+    cfg, ref, eng = _setup(max_rows=8)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (128,), generator=g)
+    with torch.no_grad():
+        want_tokens, want_logits = ref.generate_greedy(prompt, 32)
+    nxt = eng.prefill(0, prompt.tolist())
+    out = [nxt]
+    pos = len(prompt)
+    errs = []
+    # teacher-force the oracle's tokens so every step's logits are comparable
+    for i in range(31):
+        eng.cache.ensure(0, pos + 2)
+        eng.set_rows([int(want_tokens[i])], [pos], [0])
+        eng.forward_rows(1)
+        errs.append(float((eng.logits_rows(1).cpu()[0] - want_logits[i + 1]).abs().max()))
+        out.append(int(eng.chosen[0].item()))
+        pos += 1
+    eng.check_status()
+    scale = float(want_logits.abs().max())
+    print("decode max logit err", max(errs), "scale", scale)
+    assert max(errs) < 0.06 * scale
+    match = sum(int(a == int(b)) for a, b in zip(out, want_tokens.tolist()))
+    assert match >= 29
+
+
+def test_verify_rows_equal_single_steps():
+    """A 5-row verification chunk must give the same tokens as five single-row steps (position-indexed caches)."""
+    cfg, ref, eng = _setup(max_rows=8)
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, cfg.vocab, (77,), generator=g).tolist()
+    nxt = eng.prefill(0, prompt)
+    seq = [nxt]
+    pos = len(prompt)
+    for _ in range(5):
+        eng.cache.ensure(0, pos + 2)
+        eng.set_rows([seq[-1]], [pos], [0])
+        eng.forward_rows(1)
+        seq.append(int(eng.chosen[0].item()))
+        pos += 1
+    # replay the same 5 inputs as one chunk on slot 1 after an identical prefill
+    nxt2 = eng.prefill(1, prompt)
+    assert nxt2 == nxt
+    eng.cache.ensure(1, len(prompt) + 8)
+    eng.set_rows(seq[:5], list(range(len(prompt), len(prompt) + 5)), [1] * 5)
+    eng.forward_rows(5)
+    chunk = eng.chosen[:5].tolist()
+    eng.check_status()
+    assert chunk == seq[1:6]

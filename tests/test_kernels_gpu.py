@@ -1,0 +1,186 @@
+"""Individual CUDA kernels vs plain PyTorch fp32 references of the same op."""
+import ctypes as C
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_topk_select_exact():
+    from ds41rt_b200.ops import lib
+    k = lib.kernels()
+    rows, max_keys, topk = 4, 5000, 512
+    torch.manual_seed(0)
+    scores = torch.randn(rows, max_keys, device="cuda")
+    scores[1, :3000] = scores[1, :3000].round()            # many ties
+    pos = torch.tensor([4999, 2999, 300, 4000], dtype=torch.int32, device="cuda")
+    slot = torch.tensor([0, 0, 0, -1], dtype=torch.int32, device="cuda")
+    sel = torch.zeros(rows, topk, dtype=torch.int32, device="cuda")
+    n_sel = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    lib.check(k.ds41_topk_select(lib.ptr(scores), max_keys, lib.ptr(pos), lib.ptr(slot), 1, topk, lib.ptr(sel),
+                                 lib.ptr(n_sel), rows, lib.stream()), "topk")
+    torch.cuda.synchronize()
+    for r in range(3):
+        n = int(pos[r]) + 1
+        got = sel[r, : int(n_sel[r])].tolist()
+        if n <= topk:
+            assert got == list(range(n))
+            continue
+        s = scores[r, :n].cpu()
+        order = torch.sort(s, descending=True, stable=True).indices[:topk]
+        assert got == sorted(order.tolist())
+        assert int(n_sel[r]) == topk
+    assert int(n_sel[3]) == 0
+
+
+def _attend_ref(q, keys, sink, scale):
+    # q [H, D], keys [n, D]
+    logits = (q @ keys.t()) * scale
+    m = torch.maximum(logits.amax(-1, keepdim=True), sink[:, None])
+    e = torch.exp(logits - m)
+    return (e / (e.sum(-1, keepdim=True) + torch.exp(sink[:, None] - m))) @ keys
+
+
+@pytest.mark.parametrize("D,heads,rope", [(128, 8, 32), (512, 16, 64), (512, 64, 64)])
+def test_sparse_attention(D, heads, rope):
+    from ds41rt_b200.ops import lib
+    from ds41rt_b200.config import RopeConfig, rope_inv_freq
+    from ds41rt_b200.models.reference import apply_rope
+    k = lib.kernels()
+    torch.manual_seed(0)
+    rows, window, ring, topk, page_rows, max_pages = 3, 128, 144, 64, 32, 16
+    positions = [700, 701, 50]
+    slots = [0, 0, 1]
+    win = torch.randn(2, ring, D, device="cuda").bfloat16()
+    pool = torch.randn(max_pages * 2 * page_rows, D, device="cuda").bfloat16()
+    page_table = torch.arange(2 * max_pages, dtype=torch.int32, device="cuda").view(2, max_pages).flip(1).contiguous()
+    sel = torch.full((rows, topk), -1, dtype=torch.int32, device="cuda")
+    n_sel = torch.tensor([64, 40, 0], dtype=torch.int32, device="cuda")
+    sel[0] = torch.sort(torch.randperm(300)[:64]).values.int().cuda()
+    sel[1, :40] = torch.sort(torch.randperm(300)[:40]).values.int().cuda()
+    q = torch.randn(rows, heads * D, device="cuda").bfloat16()
+    sink = torch.randn(heads, device="cuda")
+    inv = torch.tensor(rope_inv_freq(RopeConfig(), rope), device="cuda")
+    n_splits = (window + 16 + topk + 63) // 64
+    part_o = torch.zeros(rows, n_splits, heads, D, device="cuda")
+    part_ml = torch.zeros(rows, n_splits, heads, 2, device="cuda")
+    out = torch.zeros(rows, heads * D, device="cuda", dtype=torch.bfloat16)
+    pos_t = torch.tensor(positions, dtype=torch.int32, device="cuda")
+    slot_t = torch.tensor(slots, dtype=torch.int32, device="cuda")
+    scale = D ** -0.5
+    lib.check(k.ds41_attend(lib.ptr(q), C.c_longlong(heads * D), 0, rows, heads, D, window, ring, lib.ptr(pos_t),
+                            lib.ptr(slot_t), lib.ptr(win), lib.ptr(pool), lib.ptr(sel), lib.ptr(n_sel), topk,
+                            lib.ptr(page_table), max_pages, page_rows, lib.ptr(inv), rope, C.c_float(scale), n_splits,
+                            lib.ptr(None), lib.ptr(part_o), lib.ptr(part_ml), lib.ptr(sink), lib.ptr(out),
+                            C.c_longlong(heads * D), lib.stream()), "attend")
+    torch.cuda.synchronize()
+    for r in range(rows):
+        pos, slot = positions[r], slots[r]
+        lo = max(0, pos - window + 1)
+        keys = [win[slot, p % ring] for p in range(lo, pos + 1)]
+        for j in range(int(n_sel[r])):
+            i = int(sel[r, j])
+            phys = int(page_table[slot, i // page_rows]) * page_rows + i % page_rows
+            keys.append(pool[phys])
+        keys = torch.stack(keys).float()
+        qr = apply_rope(q[r].float().view(heads, D).cpu(), torch.tensor(pos), inv.cpu(), rope).cuda()
+        qr = qr.bfloat16().float()
+        want = _attend_ref(qr, keys, sink, scale)
+        want = apply_rope(want.cpu(), torch.tensor(pos), inv.cpu(), rope, inverse=True).cuda()
+        got = out[r].float().view(heads, D)
+        err = float((got - want).abs().max())
+        assert err < 3e-2 * float(want.abs().max()) + 2e-3, (r, err)
+
+
+def test_hc_kernels_match_oracle():
+    from ds41rt_b200.ops import lib
+    from ds41rt_b200.models import reference as R
+    k = lib.kernels()
+    torch.manual_seed(0)
+    rows, H = 5, 512
+    streams = torch.randn(rows, 4, H, device="cuda").bfloat16()
+    sub = torch.randn(2, rows, H, device="cuda")           # two split planes
+    fn = torch.randn(24, 4 * H, device="cuda") * 0.5
+    scale = torch.tensor([1.0, 0.7, 1.3], device="cuda")
+    base = torch.randn(24, device="cuda") * 0.5
+    pre_in = torch.rand(rows, 4, device="cuda")
+    norm_w = torch.rand(H, device="cuda") + 0.5
+    # reference: mixes on the ORIGINAL streams give post/comb for the expand
+    pre0, post0, comb0 = R.hc_mixes(streams.float().cpu(), fn.cpu(), scale.cpu(), base.cpu(), 4, 20, 1e-6, 1e-20)
+    subsum = sub.sum(0).bfloat16().float().cpu()
+    new_streams = R.hc_expand(streams.float().cpu(), subsum, post0, comb0).bfloat16().float()
+    pre1, post1, comb1 = R.hc_mixes(new_streams, fn.cpu(), scale.cpu(), base.cpu(), 4, 20, 1e-6, 1e-20)
+    xn = R.rmsnorm(R.hc_collapse(new_streams, pre_in.cpu()), norm_w.cpu(), 1e-20)
+    # kernels
+    st = lib.new_status("cuda")
+    s_dev = streams.clone()
+    partial = torch.zeros(H // 128, rows, 25, device="cuda")
+    bases = (C.c_void_p * 1)(sub.data_ptr())
+    post_d, comb_d = post0.cuda().contiguous(), comb0.reshape(rows, 16).cuda().contiguous()
+    lib.check(k.ds41_hc_post_mix(lib.ptr(s_dev), lib.ptr(s_dev), bases, 1, 2, C.c_longlong(rows * H), lib.ptr(post_d),
+                                 lib.ptr(comb_d), lib.ptr(fn), lib.ptr(partial), rows, H, lib.ptr(None), lib.ptr(None),
+                                 lib.ptr(st), lib.stream()), "post_mix")
+    next_pre = torch.zeros(rows, 4, device="cuda")
+    post = torch.zeros(rows, 4, device="cuda")
+    comb = torch.zeros(rows, 16, device="cuda")
+    xn_d = torch.zeros(rows, H, device="cuda", dtype=torch.bfloat16)
+    lib.check(k.ds41_hc_finish(lib.ptr(partial), H // 128, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
+                               lib.ptr(s_dev), lib.ptr(norm_w), lib.ptr(next_pre), lib.ptr(post), lib.ptr(comb),
+                               lib.ptr(xn_d), lib.ptr(None), rows, H, 20, C.c_float(1e-6), C.c_float(1e-20),
+                               lib.stream()), "finish")
+    torch.cuda.synchronize()
+    assert (s_dev.float().cpu() - new_streams).abs().max() < 0.05
+    assert (next_pre.cpu() - pre1).abs().max() < 2e-2
+    assert (post.cpu() - post1).abs().max() < 2e-2
+    assert (comb.cpu().view(rows, 4, 4) - comb1).abs().max() < 2e-2
+    assert (xn_d.float().cpu() - xn).abs().max() < 5e-2
+
+
+def test_router_select_and_plan():
+    from ds41rt_b200.ops import lib
+    from ds41rt_b200.models import reference as R
+    k = lib.kernels()
+    torch.manual_seed(0)
+    rows, E, I_sh, topk = 6, 384, 64, 6
+    planes = torch.randn(2, rows, E + 2 * I_sh, device="cuda")
+    bias = torch.randn(E, device="cuda") * 0.01
+    ids = torch.zeros(rows, topk, dtype=torch.int32, device="cuda")
+    wts = torch.zeros(rows, topk, device="cuda")
+    act = torch.zeros(rows, I_sh, device="cuda", dtype=torch.bfloat16)
+    lib.check(k.ds41_router_select(lib.ptr(planes), 2, rows, E + 2 * I_sh, E, I_sh, topk, lib.ptr(bias),
+                                   C.c_float(1.5), C.c_float(10.0), lib.ptr(ids), lib.ptr(wts), lib.ptr(act),
+                                   lib.stream()), "router")
+    torch.cuda.synchronize()
+    logits = planes.sum(0)[:, :E].cpu()
+    score = torch.sqrt(torch.nn.functional.softplus(logits))
+    order = torch.sort(score + bias.cpu(), dim=-1, descending=True, stable=True).indices[:, :topk]
+    sel = torch.gather(score, 1, order)
+    want_w = sel / sel.sum(-1, keepdim=True) * 1.5
+    assert ids.cpu().tolist() == order.tolist()
+    assert (wts.cpu() - want_w).abs().max() < 1e-5
+    gsum = planes.sum(0).cpu()
+    want_act = R.swiglu_clamped(gsum[:, E:E + I_sh].bfloat16().float(), gsum[:, E + I_sh:].bfloat16().float(), 10.0)
+    assert (act.float().cpu() - want_act).abs().max() < 2e-2
+    # plan for a rank owning experts [96, 192)
+    slot = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    max_active = 36
+    active = torch.zeros(max_active, dtype=torch.int32, device="cuda")
+    n_active = torch.zeros(1, dtype=torch.int32, device="cuda")
+    row_w = torch.zeros(max_active, 8, device="cuda")
+    slot_of = torch.zeros(rows, topk, dtype=torch.int32, device="cuda")
+    lib.check(k.ds41_moe_plan(lib.ptr(ids), lib.ptr(wts), lib.ptr(slot), rows, topk, 96, 192, max_active, 8,
+                              lib.ptr(active), lib.ptr(n_active), lib.ptr(row_w), lib.ptr(slot_of), lib.stream()),
+              "plan")
+    torch.cuda.synchronize()
+    local = sorted({int(e) - 96 for e in order.flatten().tolist() if 96 <= e < 192})
+    assert int(n_active) == len(local)
+    assert active[: len(local)].tolist() == local
+    for r in range(rows):
+        for j in range(topk):
+            e = int(order[r, j])
+            s = int(slot_of[r, j])
+            if 96 <= e < 192:
+                assert local[s] == e - 96 and abs(float(row_w[s, r]) - float(want_w[r, j])) < 1e-5
+            else:
+                assert s == -1
