@@ -184,7 +184,7 @@ class EngineWeights:
         for l in range(cfg.n_layers):
             lw = LayerWeights(n_experts=cfg.n_experts, topk=cfg.topk)
             for kind in ("attn", "ffn"):
-                setattr(lw, f"hc_{kind}_fn", rnd((nproj, cfg.hc_mult * H), shared_gen, 0.5, F32))
+                setattr(lw, f"hc_{kind}_fn", rnd((nproj, cfg.hc_mult * H), shared_gen, std, F32))
                 setattr(lw, f"hc_{kind}_scale", ones(3))
                 setattr(lw, f"hc_{kind}_base", rnd((nproj,), shared_gen, 0.5, F32))
             lw.attn_norm, lw.ffn_norm = ones(H), ones(H)
@@ -380,6 +380,7 @@ class DS41Engine:
         self.inv_idx = torch.tensor(rope_inv_freq(cfg.rope_long, cfg.index_dim // 2), dtype=F32, device=dev)
         self.layer_prefix_plain = False   # drafter blocks use the plain rope
         self.launches = 0
+        self.debug = None   # set to a list to record per-layer routing / selection decisions
 
     # ------------------------------------------------------------------ helpers
     def _inv(self, layer: int) -> torch.Tensor:
@@ -519,6 +520,9 @@ class DS41Engine:
                 lib.ptr(self.planes_gate), s_g, R, ng, lw.n_experts, self.I_sh, lw.topk, lib.ptr(lw.gate_bias),
                 C.c_float(cfg.route_scale), C.c_float(cfg.swiglu_limit), lib.ptr(self.ids), lib.ptr(self.route_w),
                 lib.ptr(self.shared_act), st()), "router_select")
+            if self.debug is not None:
+                self.debug.append({"layer": l, "ids": self.ids[:R].clone(), "sel": self.sel[:R].clone(),
+                                   "n_sel": self.n_sel[:R].clone()})
             EL = lw.n_experts // self.world
             self._ck(k.ds41_moe_plan(
                 lib.ptr(self.ids), lib.ptr(self.route_w), lib.ptr(self.row_slot), R, lw.topk, self.rank * EL,

@@ -117,6 +117,9 @@ class LayerTrace:
     experts: torch.Tensor = None
     route_w: torch.Tensor = None
     streams_out: torch.Tensor = None
+    x_ffn_norm: torch.Tensor = None
+    moe_out: torch.Tensor = None
+    route_logits: torch.Tensor = None
 
 
 class ReferenceModel:
@@ -283,6 +286,8 @@ class ReferenceModel:
         streams = hc_expand(streams, f, post, comb)
         if trace is not None:
             trace.streams_out = streams
+            trace.x_ffn_norm, trace.moe_out = xn, f
+            trace.route_logits = xn @ self._g(f"{p}.ffn.gate.weight").t()
         return streams, next_pre
 
     # ------------------------------------------------------------------ full forward

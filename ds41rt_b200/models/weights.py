@@ -97,7 +97,7 @@ def init_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02, with_dspark
         elif name.endswith("_base"):
             t = torch.randn(shape, generator=g) * 0.5
         elif name.endswith("_fn"):
-            t = torch.randn(shape, generator=g) * 0.5
+            t = torch.randn(shape, generator=g) * std      # keeps the mixes' pre-activations O(1)
         elif name.endswith("attn_sink"):
             t = torch.randn(shape, generator=g) * 0.5
         elif name.endswith("gate.bias"):
