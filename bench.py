@@ -1,0 +1,215 @@
+#!/usr/bin/env python
+"""Headline benchmark: C1 greedy decode tokens/s of a DeepSeek-V4.1-Flash-shaped model.
+
+Config (BASELINE.json config 2): full Flash architecture, random-init weights, routed experts FP8 E4M3 with
+128x128 power-of-two block scales and 1x128 activation scales, dense/attention weights bf16, EP<N> experts and
+TP<N> attention over N GPUs of one node, a 4096-token random-id prompt and greedy decode.  Where the full model
+does not fit the N GPUs' memory the model is layer-truncated (the JSON line says how many layers ran).
+
+  python bench.py --gpus N --steps K --warmup W          (N > 1: launched by torch.distributed.run)
+  python bench.py --impl reference ...                   (prints the reference arm's availability line)
+
+Prints ONE JSON line on rank 0.  `value` is device-timed (CUDA events, max over ranks) with the chosen token
+fed back on the device; `e2e` is the same metric through DecodeSession.step(): per step the inputs are copied
+from pinned host memory and the chosen token is read back.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+BASELINE_C1_DECODE = 146.12   # reference README.md:39 (1 RTX PRO 6000 + 4 DGX Spark, dSpark on)
+LAYERS_FOR_GPUS = {1: 11, 2: 22, 4: 40, 8: 40}
+
+
+def reference_arm():
+    why = ("reference is a Rust/CMake engine whose kernels are AOT-exported for SM120/SM121 only and whose "
+           "sparkinfer/xgrammar submodules and Rust toolchain are absent; pip install of /root/reference finds no "
+           "Python project to build")
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+class ClockSampler:
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+                 "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+                 "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                     f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                   "samples": len(sm)}
+        return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = fit to memory)")
+    ap.add_argument("--prompt", type=int, default=4096)
+    ap.add_argument("--model", default="flash", choices=["flash", "small", "tiny"])
+    ap.add_argument("--expert-dtype", default="mxfp8", choices=["mxfp8", "bf16"])
+    ap.add_argument("--prefill-chunk", type=int, default=64)
+    ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the host-loop measurement (0 = --steps)")
+    ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly (for per-kernel profiling)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+
+    import torch
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    from ds41rt_b200.parallel.fabric import Fabric
+    from ds41rt_b200.runtime.session import DecodeSession
+
+    fabric = Fabric.create()
+    world, rank = fabric.world, fabric.rank
+    if world != args.gpus:
+        if rank == 0:
+            print(f"bench.py: --gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run",
+                  file=sys.stderr)
+        return 2
+    dev = fabric.device
+    if args.model == "flash":
+        n_layers = args.layers or LAYERS_FOR_GPUS.get(world, 40)
+        cfg = ModelConfig.flash(n_layers)
+    else:
+        cfg = getattr(ModelConfig, args.model)()
+        n_layers = cfg.n_layers
+    W, K = max(args.warmup, 3), args.steps
+    e2e_steps = args.e2e_steps or K
+    total_new = W + K + W + e2e_steps + 8
+    max_ctx = (args.prompt + total_new + 63) // 64 * 64
+
+    t0 = time.time()
+    weights = EngineWeights.random(cfg, rank, world, dev, seed=0, expert_dtype=args.expert_dtype)
+    eng = DS41Engine(cfg, weights, fabric, max_rows=args.prefill_chunk, slots=1, max_ctx=max_ctx)
+    sess = DecodeSession(eng, use_graphs=not args.no_graph)
+    g = torch.Generator().manual_seed(1234)
+    prompt = torch.randint(3, cfg.vocab - 600, (args.prompt,), generator=g).tolist()
+    assert eng.cache.ensure(0, max_ctx)
+    first = eng.prefill(0, prompt, chunk=args.prefill_chunk)
+    torch.cuda.synchronize()
+    eng.check_status("prefill")
+    setup_s = time.time() - t0
+
+    # ---------------- device-timed decode: K graph replays, token fed back on the device
+    pos = args.prompt
+    eng.set_rows([first], [pos], [0])
+    sess.graph(1, feedback=True)
+    before = eng.launches
+    sess.run_device_loop(1, W)
+    if args.no_graph:
+        sess.launches_per_graph[(1, True)] = (eng.launches - before) // W
+    fabric.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(dev.index or 0)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    sess.run_device_loop(1, K)
+    ev1.record()
+    torch.cuda.synchronize()
+    fabric.barrier()
+    ms = fabric.all_reduce_max(ev0.elapsed_time(ev1))
+    clocks = sampler.stop() if rank == 0 else {}
+    eng.check_status("timed decode")
+    pos += W + K
+    launches = sess.launches_per_graph.get((1, True), 0) * K
+
+    # ---------------- end to end through the public stepping API (pinned H2D in, D2H out, every step)
+    tok = int(eng.in_tokens[0].item())
+    for _ in range(W):
+        tok = sess.step([tok], [pos], [0])[0]
+        pos += 1
+    sess.h2d_bytes = sess.d2h_bytes = 0
+    fabric.barrier()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    for _ in range(e2e_steps):
+        tok = sess.step([tok], [pos], [0])[0]
+        pos += 1
+    torch.cuda.synchronize()
+    e2e_s = fabric.all_reduce_max(time.perf_counter() - t1)
+    eng.check_status("e2e decode")
+
+    if rank == 0:
+        value = K / (ms / 1e3)
+        line = {
+            "metric": "decode tok/s C1 (greedy, target-only)", "value": round(value, 2), "unit": "tok/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": round(value / BASELINE_C1_DECODE, 3),
+            "dtype": "bf16 dense / fp8-e4m3 experts (fp32 accumulate)", "data": "synthetic",
+            "config": {"model": f"DeepSeek-V4.1-Flash-shaped ({cfg.name})", "layers": n_layers,
+                       "layers_full_model": 40, "global_batch": 1, "seq_len": args.prompt,
+                       "prompt_tokens": args.prompt, "parallelism": f"tp{world}+ep{world}",
+                       "experts": "fp8 e4m3, 128x128 ue8m0 block scales, 1x128 activation scales"
+                       if args.expert_dtype == "mxfp8" else "bf16",
+                       "l2": "no flush: every step streams more weight bytes than the 126 MB L2",
+                       "weights_gb_per_gpu": round(weights.nbytes() / 1e9, 2),
+                       "kv_gb_per_gpu": round(eng.cache.nbytes() / 1e9, 3), "setup_s": round(setup_s, 1)},
+            "clocks": clocks,
+            "e2e": {"value": round(e2e_steps / e2e_s, 2), "unit": "tok/s", "steps": e2e_steps,
+                    "h2d_bytes_per_step": sess.h2d_bytes // max(e2e_steps, 1),
+                    "d2h_bytes_per_step": sess.d2h_bytes // max(e2e_steps, 1)},
+            "gpu_launches": launches,
+            "impl": "ours",
+        }
+        print(json.dumps(line))
+    fabric.barrier()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

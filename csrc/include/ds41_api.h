@@ -104,8 +104,15 @@ int ds41_argmax_rows(const float* logits, long long ld, int rows, int vocab_loca
                      void* stream);
 int ds41_argmax_merge(const float* const* vals, const int* const* idxs, int n_ranks, int rows, int* out,
                       const uint32_t* const* wait_flags, const uint32_t* wait_epoch, int* status, void* stream);
+int ds41_decode_feedback(const int* chosen, int* tokens, int* pos, int rows, void* stream);
 int ds41_spec_accept(const int* inputs, const int* chosen, const int* first, const int* count, int reqs,
                      int max_emit, int eos, int* accepted, int* emit, int* n_emit, void* stream);
+
+// ---------------------------------------------------------------------------------------------------
+// Quantisation (quant.cu).  sf: scale atoms [batch][ceil(rows/128)][K/128][512]; group 32 or 128.
+int ds41_act_quant_mx(const void* x, long long ldx, long long x_batch_stride, void* q, long long ldq,
+                      long long q_batch_stride, void* sf, long long sf_batch_stride, int rows, int K, int batch,
+                      int group, const int* n_active, void* stream);
 
 #ifdef __cplusplus
 }

@@ -53,11 +53,14 @@ struct GemmCfg {
   static constexpr int kATile = kBM * kTileKBytes;                     // 16 KiB
   static constexpr int kABytes = kATile * (DUAL ? 2 : 1);
   static constexpr int kBBytes = BN * kTileKBytes;
-  static constexpr int kSfBytes = (KIND == 2) ? (512 + 512 * ((BN + 127) / 128)) : 0;
+  static constexpr int kAtomsA = DUAL ? 2 : 1;
+  static constexpr int kAtomsB = (BN + 127) / 128;
+  // scale-factor atoms (512 B each), padded so every stage keeps its 1024-byte tile alignment
+  static constexpr int kSfBytes = (KIND == 2) ? ((512 * (kAtomsA + kAtomsB) + 1023) / 1024 * 1024) : 0;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
   static constexpr int kStagesRaw = (200 * 1024) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kSfCols = (KIND == 2) ? (4 + 4 * ((BN + 127) / 128)) : 0;   // TMEM columns per stage
+  static constexpr int kSfCols = (KIND == 2) ? 4 * (kAtomsA + kAtomsB) : 0;           // TMEM columns per stage
   static constexpr int kAccCols = (BN < 32 ? 32 : BN) * (DUAL ? 2 : 1);
   static constexpr int kTmemNeeded = 2 * kAccCols + kStages * kSfCols;
   static constexpr int kTmemCols = kTmemNeeded <= 32 ? 32 : kTmemNeeded <= 64 ? 64 : kTmemNeeded <= 128 ? 128
@@ -133,7 +136,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!mbar_wait(&empty[stage], phase ^ 1, p.status, 100)) { ok = false; break; }
         uint8_t* sa = smem + stage * Cfg::kStageBytes;
         uint8_t* sb = sa + Cfg::kABytes;
-        mbar_expect_tx(&full[stage], Cfg::kABytes + Cfg::kBBytes + Cfg::kSfBytes);
+        mbar_expect_tx(&full[stage], Cfg::kABytes + Cfg::kBBytes + (KIND == 2 ? 512 * (Cfg::kAtomsA + Cfg::kAtomsB) : 0));
         const int ba = p.batch_map != nullptr ? p.batch_map[b] : b;
         const int bb = p.b_batch_kind == 0 ? ba : (p.b_batch_kind == 1 ? 0 : b);
         tma_load_3d(sa, &tmA, &full[stage], kb * Cfg::kBK, mt * kBM, ba);
@@ -145,11 +148,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const long long ka = kb;
           const long long n_ka = kb_total;
           bulk_load(ssf, p.sfa + ba * p.sfa_batch_stride + (1ll * mt * n_ka + ka) * 512, 512, &full[stage]);
-          constexpr int kAtomsB = (BN + 127) / 128;
+          if constexpr (DUAL) {
+            const long long mt_up = p.up_row_offset / 128 + mt;
+            bulk_load(ssf + 512, p.sfa + ba * p.sfa_batch_stride + (mt_up * n_ka + ka) * 512, 512, &full[stage]);
+          }
 #pragma unroll
-          for (int a = 0; a < kAtomsB; ++a) {
+          for (int a = 0; a < Cfg::kAtomsB; ++a) {
             const long long ra = (1ll * nt * BN) / 128 + a;
-            bulk_load(ssf + 512 + a * 512, p.sfb + bb * p.sfb_batch_stride + (ra * n_ka + ka) * 512, 512,
+            bulk_load(ssf + 512 * (Cfg::kAtomsA + a), p.sfb + bb * p.sfb_batch_stride + (ra * n_ka + ka) * 512, 512,
                       &full[stage]);
           }
         }
@@ -184,18 +190,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if constexpr (KIND == 2) {
           const uint32_t ssf = sb + Cfg::kBBytes;
           const uint32_t sf_t = tmem_base + 2 * Cfg::kAccCols + stage * Cfg::kSfCols;
-          tmem_cp_32x128b_warpx4(sf_t, umma_desc_plain(ssf, 16, 128));
-          constexpr int kAtomsB = (BN + 127) / 128;
 #pragma unroll
-          for (int a = 0; a < kAtomsB; ++a)
-            tmem_cp_32x128b_warpx4(sf_t + 4 + 4 * a, umma_desc_plain(ssf + 512 + 512 * a, 16, 128));
+          for (int a = 0; a < Cfg::kAtomsA + Cfg::kAtomsB; ++a)
+            tmem_cp_32x128b_warpx4(sf_t + 4 * a, umma_desc_plain(ssf + 512 * a, 16, 128));
+          // B scale columns: rows of this n-tile start (nt*BN % 128)/32 columns into the atom
+          const uint32_t sfb_t = sf_t + 4 * Cfg::kAtomsA + ((static_cast<uint32_t>(nt) * BN) & 127u) / 32u;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint32_t id = umma_idesc_bs(kBM, BN, 0, 0, 1, k, k);
-            // B scale columns: rows of this n-tile start (nt*BN % 128)/32 columns into the atom
-            const uint32_t sfb_t = sf_t + 4 + ((static_cast<uint32_t>(nt) * BN) & 127u) / 32u;
-            umma_mxf8(d_tmem, adesc + 2 * k, bdesc + 2 * k, id, (kb > kb0 || k > 0) ? 1u : 0u, sf_t, sfb_t);
-            static_assert(!(KIND == 2 && DUAL), "dual MX tiles are provided by the grouped expert kernel");
+            const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
+            umma_mxf8(d_tmem, adesc + 2 * k, bdesc + 2 * k, id, accum, sf_t, sfb_t);
+            if constexpr (DUAL) {
+              const uint64_t adesc2 = umma_desc_sw128(sa + Cfg::kATile);
+              umma_mxf8(d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, id, accum, sf_t + 4, sfb_t);
+            }
           }
         } else {
 #pragma unroll
@@ -381,16 +389,15 @@ template <int KIND>
 static cudaError_t dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
                                cudaStream_t stream) {
   if (p.out_mode == 4) {
-    if constexpr (KIND != 2) {
-      switch (bn) {
-        case 16: return launch_gemm<16, KIND, 1>(tmA, tmB, p, grid, stream);
-        case 32: return launch_gemm<32, KIND, 1>(tmA, tmB, p, grid, stream);
-        case 64: return launch_gemm<64, KIND, 1>(tmA, tmB, p, grid, stream);
-        case 128: return launch_gemm<128, KIND, 1>(tmA, tmB, p, grid, stream);
-        default: return cudaErrorInvalidValue;
-      }
+    switch (bn) {
+      case 16: return launch_gemm<16, KIND, 1>(tmA, tmB, p, grid, stream);
+      case 32: return launch_gemm<32, KIND, 1>(tmA, tmB, p, grid, stream);
+      case 64: return launch_gemm<64, KIND, 1>(tmA, tmB, p, grid, stream);
+      case 128:
+        if constexpr (KIND != 2) return launch_gemm<128, KIND, 1>(tmA, tmB, p, grid, stream);
+        return cudaErrorInvalidValue;
+      default: return cudaErrorInvalidValue;
     }
-    return cudaErrorInvalidValue;
   }
   switch (bn) {
     case 16: return launch_gemm<16, KIND>(tmA, tmB, p, grid, stream);

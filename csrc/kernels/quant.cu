@@ -1,0 +1,83 @@
+// Activation quantisation for the block-scaled tensor-core GEMMs.
+//
+//  act_quant_mx : bf16 [batch][rows][K] -> E4M3 payload + UE8M0 scales written directly in the 512-byte
+//                 scale-factor atom layout the MX GEMM copies into TMEM
+//                 (byte = (row%32)*16 + ((row/32)%4)*4 + kblock%4, atoms [row/128][K/128]).
+//                 `group` = 32 gives one scale per 32 elements (MX); `group` = 128 gives the 1x128
+//                 activation-scale geometry (the same exponent is written to the four 32-blocks).
+//                 scale = smallest power of two >= amax/448  (quantise contract of the reference's
+//                 native/include/ds41rt_v41_experts.h:55-62 and native/cuda/kernels/v41_kv.cu:15-46).
+#include "ds41_api.h"
+#include "ds41_ptx.cuh"
+
+namespace ds41 {
+
+__device__ __forceinline__ uint32_t ue8m0_ceil_exp(float x) {
+  x = fmaxf(x, 1.17549435e-38f);
+  const uint32_t bits = __float_as_uint(x);
+  uint32_t e = (bits >> 23) & 0xFF;
+  if (bits & 0x7FFFFF) ++e;
+  return e > 254 ? 254 : e;
+}
+
+struct ActQuantParams {
+  const __nv_bfloat16* x;
+  long long ldx, x_batch_stride;
+  uint8_t* q;
+  long long ldq, q_batch_stride;
+  uint8_t* sf;
+  long long sf_batch_stride;
+  int rows, K, batch, group;
+  const int* n_active;
+};
+
+// one warp per (row, 128-wide K chunk); 8 warps per block
+__global__ void __launch_bounds__(256) act_quant_mx_kernel(ActQuantParams p) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int chunks = p.K / 128;
+  const long long item = 1ll * blockIdx.x * 8 + warp;
+  const int b = blockIdx.y;
+  if (p.n_active != nullptr && b >= *p.n_active) return;
+  if (item >= 1ll * p.rows * chunks) return;
+  const int r = static_cast<int>(item / chunks), kc = static_cast<int>(item % chunks);
+  const __nv_bfloat16* src = p.x + b * p.x_batch_stride + 1ll * r * p.ldx + kc * 128 + lane * 4;
+  const uint2 raw = *reinterpret_cast<const uint2*>(src);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(c.x), fabsf(c.y)));
+  // 8 lanes share a 32-element block
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+  if (p.group == 128) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 16));
+  }
+  const uint32_t e = ue8m0_ceil_exp(amax * (1.0f / 448.0f));
+  const float inv = __uint_as_float((254u - e) << 23);          // 2^-(e-127)
+  const __nv_fp8x4_e4m3 packed(make_float4(a.x * inv, a.y * inv, c.x * inv, c.y * inv));
+  *reinterpret_cast<uint32_t*>(p.q + b * p.q_batch_stride + 1ll * r * p.ldq + kc * 128 + lane * 4) =
+      *reinterpret_cast<const uint32_t*>(&packed);
+  if ((lane & 7) == 0) {
+    const int kb = lane >> 3;
+    uint8_t* atom = p.sf + b * p.sf_batch_stride + (1ll * (r / 128) * chunks + kc) * 512;
+    atom[(r % 32) * 16 + ((r / 32) % 4) * 4 + kb] = static_cast<uint8_t>(e);
+  }
+}
+
+}  // namespace ds41
+
+using namespace ds41;
+
+extern "C" int ds41_act_quant_mx(const void* x, long long ldx, long long x_batch_stride, void* q, long long ldq,
+                                 long long q_batch_stride, void* sf, long long sf_batch_stride, int rows, int K,
+                                 int batch, int group, const int* n_active, void* stream) {
+  if (rows <= 0 || K <= 0 || K % 128 != 0 || batch <= 0 || (group != 32 && group != 128) || (ldx & 3) || (ldq & 3))
+    return cudaErrorInvalidValue;
+  ActQuantParams p{static_cast<const __nv_bfloat16*>(x), ldx, x_batch_stride, static_cast<uint8_t*>(q), ldq,
+                   q_batch_stride, static_cast<uint8_t*>(sf), sf_batch_stride, rows, K, batch, group, n_active};
+  const long long items = 1ll * rows * (K / 128);
+  dim3 grid(static_cast<unsigned>((items + 7) / 8), batch);
+  act_quant_mx_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError();
+}

@@ -118,9 +118,24 @@ __global__ void spec_accept_kernel(AcceptParams p) {
   p.n_emit[q] = min(emitted, p.max_emit);
 }
 
+// Device-side feedback for back-to-back decode steps: next input token = chosen token, position + 1.
+__global__ void decode_feedback_kernel(const int* chosen, int* tokens, int* pos, int rows) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r < rows) {
+    tokens[r] = chosen[r];
+    pos[r] += 1;
+  }
+}
+
 }  // namespace ds41
 
 using namespace ds41;
+
+extern "C" int ds41_decode_feedback(const int* chosen, int* tokens, int* pos, int rows, void* stream) {
+  if (rows <= 0) return cudaErrorInvalidValue;
+  decode_feedback_kernel<<<(rows + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(chosen, tokens, pos, rows);
+  return cudaGetLastError();
+}
 
 extern "C" int ds41_argmax_rows(const float* logits, long long ld, int rows, int vocab_local, int vocab_offset,
                                 const uint32_t* mask, int mask_words, float* best_val, int* best_idx,

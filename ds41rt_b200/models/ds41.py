@@ -64,6 +64,8 @@ class LayerWeights:
     w2_sh: torch.Tensor = None          # [H, I_sh]
     w13: torch.Tensor = None            # [E_local, 2I, H]
     w2: torch.Tensor = None             # [E_local, H, I]
+    w13_sf: Optional[torch.Tensor] = None   # MX experts: scale atoms [E_local, 2I/128, H/128, 512]
+    w2_sf: Optional[torch.Tensor] = None    # [E_local, H/128, I/128, 512]
     n_experts: int = 0
     topk: int = 0
     extra_cols: int = 0
@@ -71,8 +73,30 @@ class LayerWeights:
     ratio: int = 0                      # > 0: this layer produces a compressed source
 
 
+def quantize_expert_stack(w: torch.Tensor, device):
+    """[E, n, k] fp32 -> (E4M3 payload on device, scale atoms [E, n/128, k/128, 512]) with 128x128 power-of-two
+    block scales expanded to the per-row / per-32 granularity of the MX tensor-core path."""
+    from ..ops import quant_ref as Q
+    from ..ops.mx import pack_sf_atoms
+    qs, sfs = [], []
+    for e in range(w.shape[0]):
+        q, ex = Q.quant_weight_fp8_ue8m0_block(w[e], 128)
+        qs.append(q)
+        sfs.append(pack_sf_atoms(Q.expand_block_scales(ex, 128)))
+    return torch.stack(qs).to(device).contiguous(), torch.stack(sfs).to(device).contiguous()
+
+
+def dequantize_expert(q: torch.Tensor, sf_atoms: torch.Tensor) -> torch.Tensor:
+    """Inverse of quantize_expert_stack for one expert (used by tests to feed the oracle)."""
+    from ..ops import quant_ref as Q
+    from ..ops.mx import unpack_sf_atoms
+    e = unpack_sf_atoms(sf_atoms.cpu(), q.shape[0])
+    return Q.dequant_mxfp8(q.cpu(), e)
+
+
 class EngineWeights:
     """One rank's shard of the model in kernel layout."""
+    expert_dtype = "bf16"
 
     def __init__(self, cfg: ModelConfig, rank: int, world: int, device):
         self.cfg, self.rank, self.world, self.device = cfg, rank, world, device
@@ -90,8 +114,11 @@ class EngineWeights:
     @staticmethod
     def from_fp32(cfg: ModelConfig, w: Dict[str, torch.Tensor], rank: int, world: int, device,
                   prefix: str = "layers", n_layers: Optional[int] = None, n_experts: Optional[int] = None,
-                  topk: Optional[int] = None) -> "EngineWeights":
+                  topk: Optional[int] = None, expert_dtype: str = "bf16") -> "EngineWeights":
+        """Build one rank's shard from an fp32 name->tensor dict.  expert_dtype "mxfp8" stores routed
+        experts as E4M3 with power-of-two 128x128 block scales (consumed by the block-scaled GEMM)."""
         ew = EngineWeights(cfg, rank, world, device)
+        ew.expert_dtype = expert_dtype
         D, H = cfg.head_dim, cfg.hidden
         dev = lambda t, dt=BF16: t.to(device=device, dtype=dt).contiguous()
         ew.embed = dev(w["embed.weight"])
@@ -150,18 +177,25 @@ class EngineWeights:
             lw.gate_bias = dev(w[f"{p}.ffn.gate.bias"], F32)
             lw.w2_sh = dev(w[f"{p}.ffn.shared_experts.w2.weight"][:, i0:i1])
             e0 = rank * EL
-            lw.w13 = dev(torch.stack([torch.cat([w[f"{p}.ffn.experts.{e}.w1.weight"],
-                                                 w[f"{p}.ffn.experts.{e}.w3.weight"]], 0)
-                                      for e in range(e0, e0 + EL)], 0))
-            lw.w2 = dev(torch.stack([w[f"{p}.ffn.experts.{e}.w2.weight"] for e in range(e0, e0 + EL)], 0))
+            w13 = torch.stack([torch.cat([w[f"{p}.ffn.experts.{e}.w1.weight"],
+                                          w[f"{p}.ffn.experts.{e}.w3.weight"]], 0) for e in range(e0, e0 + EL)], 0)
+            w2 = torch.stack([w[f"{p}.ffn.experts.{e}.w2.weight"] for e in range(e0, e0 + EL)], 0)
+            if expert_dtype == "mxfp8":
+                lw.w13, lw.w13_sf = quantize_expert_stack(w13, device)
+                lw.w2, lw.w2_sf = quantize_expert_stack(w2, device)
+            else:
+                lw.w13, lw.w2 = dev(w13), dev(w2)
             ew.layers.append(lw)
         return ew
 
     @staticmethod
     def random(cfg: ModelConfig, rank: int, world: int, device, seed: int = 0, std: float = 0.02,
-               router_std: Optional[float] = None) -> "EngineWeights":
-        """Random-init shard generated directly on the device (for models too large to stage on the host)."""
+               router_std: Optional[float] = None, expert_dtype: str = "bf16") -> "EngineWeights":
+        """Random-init shard generated directly on the device (for models too large to stage on the host).
+        expert_dtype "mxfp8": E4M3 payloads ~ N(0, 48^2) with every 128x128 block scale 2^-11 (dequantised
+        std 0.0234), the statistics an amax-scaled quantisation of N(0, 0.02) weights produces."""
         ew = EngineWeights(cfg, rank, world, device)
+        ew.expert_dtype = expert_dtype
         D, H, Q = cfg.head_dim, cfg.hidden, cfg.q_lora
         gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
         shared_gen = torch.Generator(device=device).manual_seed(seed * 1000 + 999)   # replicated tensors
@@ -211,8 +245,24 @@ class EngineWeights:
                 lw.w_gate_sh[:cfg.n_experts] = rnd((cfg.n_experts, H), shared_gen, router_std / math.sqrt(H) * 1.0)
             lw.gate_bias = rnd((cfg.n_experts,), shared_gen, 0.01, F32)
             lw.w2_sh = rnd((H, ew.I_sh))
-            lw.w13 = rnd((EL, 2 * cfg.inter, H))
-            lw.w2 = rnd((EL, H, cfg.inter))
+            if expert_dtype == "mxfp8":
+                def rnd8(shape):
+                    out = torch.empty(shape, dtype=torch.float8_e4m3fn, device=device)
+                    flat = out.view(-1)
+                    step = 1 << 26
+                    for i in range(0, flat.numel(), step):
+                        n = min(step, flat.numel() - i)
+                        flat[i:i + n] = (torch.randn(n, generator=gen, device=device, dtype=F32) * 48.0).clamp(
+                            -448, 448).to(torch.float8_e4m3fn)
+                    return out
+                I = cfg.inter
+                lw.w13 = rnd8((EL, 2 * I, H))
+                lw.w2 = rnd8((EL, H, I))
+                lw.w13_sf = torch.full((EL, 2 * I // 128, H // 128, 512), 127 - 11, dtype=torch.uint8, device=device)
+                lw.w2_sf = torch.full((EL, H // 128, I // 128, 512), 127 - 11, dtype=torch.uint8, device=device)
+            else:
+                lw.w13 = rnd((EL, 2 * cfg.inter, H))
+                lw.w2 = rnd((EL, H, cfg.inter))
             ew.layers.append(lw)
         return ew
 
@@ -349,6 +399,14 @@ class DS41Engine:
         self.row_w = z((self.max_active, R), F32)
         self.slot_of = z((R, self.topk), I32)
         self.act = z((self.max_active, R, cfg.inter), BF16)
+        self.mx = weights.expert_dtype == "mxfp8"
+        if self.mx:
+            assert H % 128 == 0 and cfg.inter % 128 == 0
+            ra = (R + 127) // 128
+            self.xq = z((R, H), torch.uint8)
+            self.xq_sf = z((ra, H // 128, 512), torch.uint8)
+            self.actq = z((self.max_active, R, cfg.inter), torch.uint8)
+            self.actq_sf = z((self.max_active, ra, cfg.inter // 128, 512), torch.uint8)
         self.fc2 = z((self.max_active, R, H), F32)
         self.planes_shared = z((self.max_splits, R, H), F32)
         # head
@@ -530,16 +588,37 @@ class DS41Engine:
                 lib.ptr(self.row_w), lib.ptr(self.slot_of), st()), "moe_plan")
             I = cfg.inter
             bn = G.pick_bn(R)
-            # FC1: act[slot][row][i] = swiglu(W1 x, W3 x) * route weight
-            G.gemm_raw(lw.w13, self.xn, self.act, I, R, H, lda=H, ldb=H, ldo=I, out_mode=4, bn=bn,
-                       batch=self.max_active, a_batches=EL, a_batch_stride=2 * I * H, out_batch_stride=R * I,
-                       batch_map=self.active, n_active=self.n_active, b_batch_kind=1, up_row_offset=I,
-                       row_w=self.row_w, row_w_ld=self.max_rows, act_limit=cfg.swiglu_limit, status=self.status)
-            # FC2: fc2[slot][row][h]
-            G.gemm_raw(lw.w2, self.act, self.fc2, H, R, I, lda=I, ldb=I, ldo=H, out_mode=5, bn=bn,
-                       batch=self.max_active, a_batches=EL, a_batch_stride=H * I, b_batch_stride=R * I,
-                       out_batch_stride=R * H, batch_map=self.active, n_active=self.n_active, b_batch_kind=2,
-                       row_w=self.row_w, row_w_ld=self.max_rows, status=self.status)
+            # FC1: act[slot][row][i] = swiglu(W1 x, W3 x) * route weight;  FC2: fc2[slot][row][h]
+            if self.mx:
+                ra = (R + 127) // 128
+                self._ck(k.ds41_act_quant_mx(lib.ptr(self.xn), C.c_longlong(H), C.c_longlong(0), lib.ptr(self.xq),
+                                             C.c_longlong(H), C.c_longlong(0), lib.ptr(self.xq_sf), C.c_longlong(0),
+                                             R, H, 1, 128, lib.ptr(None), st()), "act_quant x")
+                G.gemm_raw(lw.w13, self.xq, self.act, I, R, H, lda=H, ldb=H, ldo=I, kind=2, out_mode=4, bn=bn,
+                           batch=self.max_active, a_batches=EL, a_batch_stride=2 * I * H, out_batch_stride=R * I,
+                           batch_map=self.active, n_active=self.n_active, b_batch_kind=1, up_row_offset=I,
+                           row_w=self.row_w, row_w_ld=self.max_rows, act_limit=cfg.swiglu_limit,
+                           sfa=lw.w13_sf, sfa_batch_stride=lw.w13_sf[0].numel(), sfb=self.xq_sf, status=self.status)
+                sf_slot = ra * (I // 128) * 512
+                self._ck(k.ds41_act_quant_mx(lib.ptr(self.act), C.c_longlong(I), C.c_longlong(R * I),
+                                             lib.ptr(self.actq), C.c_longlong(I), C.c_longlong(R * I),
+                                             lib.ptr(self.actq_sf), C.c_longlong(sf_slot), R, I, self.max_active, 128,
+                                             lib.ptr(self.n_active), st()), "act_quant act")
+                G.gemm_raw(lw.w2, self.actq, self.fc2, H, R, I, lda=I, ldb=I, ldo=H, kind=2, out_mode=5, bn=bn,
+                           batch=self.max_active, a_batches=EL, a_batch_stride=H * I, b_batch_stride=R * I,
+                           out_batch_stride=R * H, batch_map=self.active, n_active=self.n_active, b_batch_kind=2,
+                           row_w=self.row_w, row_w_ld=self.max_rows, sfa=lw.w2_sf,
+                           sfa_batch_stride=lw.w2_sf[0].numel(), sfb=self.actq_sf, sfb_batch_stride=sf_slot,
+                           status=self.status)
+            else:
+                G.gemm_raw(lw.w13, self.xn, self.act, I, R, H, lda=H, ldb=H, ldo=I, out_mode=4, bn=bn,
+                           batch=self.max_active, a_batches=EL, a_batch_stride=2 * I * H, out_batch_stride=R * I,
+                           batch_map=self.active, n_active=self.n_active, b_batch_kind=1, up_row_offset=I,
+                           row_w=self.row_w, row_w_ld=self.max_rows, act_limit=cfg.swiglu_limit, status=self.status)
+                G.gemm_raw(lw.w2, self.act, self.fc2, H, R, I, lda=I, ldb=I, ldo=H, out_mode=5, bn=bn,
+                           batch=self.max_active, a_batches=EL, a_batch_stride=H * I, b_batch_stride=R * I,
+                           out_batch_stride=R * H, batch_map=self.active, n_active=self.n_active, b_batch_kind=2,
+                           row_w=self.row_w, row_w_ld=self.max_rows, status=self.status)
             s_s = G.pick_splits(H, self.I_sh, max_splits=self.max_splits)
             G.linear_planes(self.shared_act[:R], lw.w2_sh,
                             self.planes_shared.view(-1)[: s_s * R * H].view(s_s, R, H), s_s, status=self.status)

@@ -198,3 +198,27 @@ def quant_kv_fp4_e4m3_16(x: torch.Tensor):
 
 def dequant_kv_fp4_e4m3_16(packed: torch.Tensor, bs: torch.Tensor) -> torch.Tensor:
     return e2m1_decode(unpack_fp4(packed)) * bs.float().repeat_interleave(16, -1)
+
+
+# ----------------------------------------------------------------------------- FP8 + UE8M0 block scales (128x128)
+def quant_weight_fp8_ue8m0_block(w: torch.Tensor, block: int = 128):
+    """E4M3 payload with one power-of-two scale per `block` x `block` tile (scale = ceil_pow2(amax/448)).
+    Returns (q [n,k] float8, e [n/block, k/block] uint8)."""
+    n, k = w.shape
+    assert n % block == 0 and k % block == 0
+    g = w.float().view(n // block, block, k // block, block)
+    amax = g.abs().amax(dim=(1, 3))
+    e = ue8m0_ceil(amax / E4M3_MAX)
+    q = to_e4m3(g / ue8m0_to_float(e)[:, None, :, None]).view(n, k)
+    return q, e
+
+
+def expand_block_scales(e: torch.Tensor, block: int = 128, mx: int = 32) -> torch.Tensor:
+    """[n/block, k/block] tile exponents -> per-row per-32 exponents [n, k/32] (what the MX GEMM consumes)."""
+    return e.repeat_interleave(block, 0).repeat_interleave(block // mx, 1).contiguous()
+
+
+def quant_act_fp8_ue8m0(x: torch.Tensor, group: int = 128):
+    """Row-wise E4M3 payload with a power-of-two scale per `group` elements; exponents returned per 32."""
+    q, e = quant_mxfp8(x, group)
+    return q, e.repeat_interleave(group // 32, -1).contiguous()

@@ -123,3 +123,67 @@ def test_verify_rows_equal_single_steps():
     chunk = eng.chosen[:5].tolist()
     eng.check_status()
     assert chunk == seq[1:6]
+
+
+def test_mxfp8_experts_match_oracle():
+    """Routed experts stored as FP8 E4M3 + 128x128 power-of-two block scales, run through the block-scaled
+    tcgen05 path, vs the oracle evaluated on the dequantised weights."""
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.weights import init_weights
+    from ds41rt_b200.models.reference import ReferenceModel
+    from ds41rt_b200.models.ds41 import EngineWeights, DS41Engine, dequantize_expert
+    cfg = ModelConfig.tiny()
+    w = init_weights(cfg, seed=0)
+    wr = {k: (v.bfloat16().float() if v.dim() == 2 and not k.endswith("_fn") else v) for k, v in w.items()}
+    ew = EngineWeights.from_fp32(cfg, wr, 0, 1, torch.device("cuda"), expert_dtype="mxfp8")
+    I = cfg.inter
+    for l, lw in enumerate(ew.layers):
+        for e in range(cfg.n_experts):
+            w13 = dequantize_expert(lw.w13[e], lw.w13_sf[e])
+            wr[f"layers.{l}.ffn.experts.{e}.w1.weight"] = w13[:I]
+            wr[f"layers.{l}.ffn.experts.{e}.w3.weight"] = w13[I:]
+            wr[f"layers.{l}.ffn.experts.{e}.w2.weight"] = dequantize_expert(lw.w2[e], lw.w2_sf[e])
+    ref = ReferenceModel(cfg, wr)
+    eng = DS41Engine(cfg, ew, max_rows=8, slots=1, max_ctx=256)
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, cfg.vocab, (40,), generator=g)
+    with torch.no_grad():
+        want, traces = ref.forward(prompt, return_trace=True)
+    eng.cache.ensure(0, 64)
+    got, same = [], []
+    toks = prompt.tolist()
+    for c0 in range(0, len(toks), 8):
+        part = toks[c0:c0 + 8]
+        eng.debug = []
+        eng.set_rows(part, list(range(c0, c0 + len(part))), [0] * len(part))
+        eng.forward_rows(len(part))
+        got.append(eng.logits_rows(len(part)).cpu())
+        same.append(_decisions_match(cfg, traces, eng.debug, c0, len(part), None))
+    eng.check_status()
+    got, same = torch.cat(got, 0), torch.cat(same, 0)
+    err = (got - want).abs().max(dim=1).values
+    scale = float(want.abs().max())
+    print("mx: same", int(same.sum()), "of", len(same), "max err", float(err[same].max()), "scale", scale)
+    assert int(same.sum()) >= 0.6 * len(same)
+    # fp8 activations (1x128 scales) add quantisation noise on top of bf16
+    assert float(err[same].max()) < 0.08 * scale
+
+
+def test_cuda_graph_decode_matches_eager():
+    from ds41rt_b200.runtime.session import DecodeSession
+    cfg, ref, eng = _setup(max_rows=8)
+    g = torch.Generator().manual_seed(7)
+    prompt = torch.randint(0, cfg.vocab, (50,), generator=g).tolist()
+    sess = DecodeSession(eng, use_graphs=True)
+    out_graph = sess.generate(prompt, 12, slot=0)
+    sess2 = DecodeSession(eng, use_graphs=False)
+    out_eager = sess2.generate(prompt, 12, slot=1)
+    assert out_graph == out_eager
+    # device feedback loop reproduces the host loop
+    nxt = eng.prefill(0, prompt)
+    eng.cache.ensure(0, len(prompt) + 16)
+    eng.set_rows([nxt], [len(prompt)], [0])
+    sess.run_device_loop(1, 5)
+    torch.cuda.synchronize()
+    assert int(eng.row_pos[0]) == len(prompt) + 5
+    assert int(eng.in_tokens[0]) == out_graph[5]

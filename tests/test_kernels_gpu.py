@@ -184,3 +184,22 @@ def test_router_select_and_plan():
                 assert local[s] == e - 96 and abs(float(row_w[s, r]) - float(want_w[r, j])) < 1e-5
             else:
                 assert s == -1
+
+
+@pytest.mark.parametrize("group", [32, 128])
+def test_act_quant_mx(group):
+    from ds41rt_b200.ops import lib, quant_ref as Q
+    from ds41rt_b200.ops.mx import unpack_sf_atoms
+    k = lib.kernels()
+    rows, K = 37, 512
+    x = (torch.randn(rows, K, device="cuda") * torch.exp(torch.randn(rows, 1, device="cuda"))).bfloat16()
+    q = torch.zeros(rows, K, dtype=torch.uint8, device="cuda")
+    sf = torch.zeros(1, K // 128, 512, dtype=torch.uint8, device="cuda")
+    lib.check(k.ds41_act_quant_mx(lib.ptr(x), C.c_longlong(K), C.c_longlong(0), lib.ptr(q), C.c_longlong(K),
+                                  C.c_longlong(0), lib.ptr(sf), C.c_longlong(0), rows, K, 1, group, lib.ptr(None),
+                                  lib.stream()), "act_quant")
+    torch.cuda.synchronize()
+    wq, we = Q.quant_act_fp8_ue8m0(x.float().cpu(), group)
+    got_e = unpack_sf_atoms(sf.cpu(), rows)
+    assert torch.equal(got_e, we)
+    assert torch.equal(q.cpu().view(torch.float8_e4m3fn).float(), wq.float())
