@@ -40,6 +40,7 @@ typedef struct ds41_gemm_args {
   int up_row_offset;
   int row_w_ld;
   float act_limit;
+  int static_operand;   // 1: A is a weight matrix, 2: B is (prefetched ahead of the stream dependency), 0: neither
 } ds41_gemm_args;
 
 int ds41_gemm_tc(const ds41_gemm_args* args, void* stream);
@@ -56,7 +57,8 @@ int ds41_hc_post_mix(const void* streams_in, void* streams_out, const float* con
                      int* status, void* stream);
 int ds41_hc_finish(const float* partial, int n_slices, const float* scale, const float* base, const float* pre_in,
                    const void* streams, const float* norm_w, float* next_pre, float* post, float* comb, void* xn,
-                   float* tap_mean, int rows, int H, int iters, float hc_eps, float norm_eps, void* stream);
+                   float* tap_mean, void* xq, void* xq_sf, int rows, int H, int iters, float hc_eps, float norm_eps,
+                   void* stream);
 
 // ---------------------------------------------------------------------------------------------------
 // Attention-side projections' epilogues and cache writes (attn_ops.cu)

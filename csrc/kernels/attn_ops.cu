@@ -9,6 +9,7 @@
 // pos / ratio), so rows written for drafts that are later rejected are simply rewritten when the position
 // is processed again and never read before that - no proposal overlay or commit copy is needed.
 #include "ds41_api.h"
+#include "ds41_launch.cuh"
 #include "ds41_ptx.cuh"
 
 namespace ds41 {
@@ -51,49 +52,66 @@ struct QkvPostParams {
   float eps;
 };
 
+// grid (rows, 2): block y == 0 normalises the q latent, y == 1 handles kv (norm + RoPE + ring write) and extras.
 __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostParams p) {
   __shared__ float scratch[8];
   const int r = blockIdx.x, tid = threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   const long long plane = 1ll * p.rows * p.ntot;
   const float* row0 = p.planes + 1ll * r * p.ntot;
-  // ---- q latent
-  float vals[8];
-  float sq = 0.f;
-  int n = 0;
-  for (int c = tid; c < p.Q && n < 8; c += 256, ++n) {
-    float a = 0.f;
-    for (int s = 0; s < p.splits; ++s) a += row0[s * plane + c];
-    a = bf16_round(a);
-    vals[n] = a;
-    sq = fmaf(a, a, sq);
-  }
-  float tot = block_sum_256(sq, scratch);
-  float inv = rsqrtf(tot / p.Q + p.eps);
-  n = 0;
-  for (int c = tid; c < p.Q && n < 8; c += 256, ++n)
-    p.q_lat[1ll * r * p.Q + c] = __float2bfloat16_rn(vals[n] * inv * p.q_norm_w[c]);
-  // ---- kv: thread handles adjacent pairs so RoPE stays in-thread
-  float2 kvv[4];
-  sq = 0.f;
-  n = 0;
-  for (int i = tid; i < p.D / 2 && n < 4; i += 256, ++n) {
-    float a = 0.f, b = 0.f;
-    for (int s = 0; s < p.splits; ++s) {
-      a += row0[s * plane + p.Q + 2 * i];
-      b += row0[s * plane + p.Q + 2 * i + 1];
+  if (blockIdx.y == 0) {
+    // ---- q latent (Q <= 2048: up to 8 columns per thread, all split loads issued together)
+    float vals[8];
+    float sq = 0.f;
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const int c = tid + 256 * n;
+      float a = 0.f;
+      if (c < p.Q) {
+        for (int s = 0; s < p.splits; ++s) a += row0[s * plane + c];
+        a = bf16_round(a);
+      }
+      vals[n] = a;
+      sq = fmaf(a, a, sq);
     }
-    a = bf16_round(a);
-    b = bf16_round(b);
+    const float tot = block_sum_256(sq, scratch);
+    const float inv = rsqrtf(tot / p.Q + p.eps);
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const int c = tid + 256 * n;
+      if (c < p.Q) p.q_lat[1ll * r * p.Q + c] = __float2bfloat16_rn(vals[n] * inv * p.q_norm_w[c]);
+    }
+    return;
+  }
+  // ---- kv: thread handles adjacent pairs so RoPE stays in-thread (D <= 2048)
+  float2 kvv[4];
+  float sq = 0.f;
+#pragma unroll
+  for (int n = 0; n < 4; ++n) {
+    const int i = tid + 256 * n;
+    float a = 0.f, b = 0.f;
+    if (i < p.D / 2) {
+      for (int s = 0; s < p.splits; ++s) {
+        const float2 v = *reinterpret_cast<const float2*>(row0 + s * plane + p.Q + 2 * i);
+        a += v.x;
+        b += v.y;
+      }
+      a = bf16_round(a);
+      b = bf16_round(b);
+    }
     kvv[n] = make_float2(a, b);
     sq = fmaf(a, a, fmaf(b, b, sq));
   }
-  tot = block_sum_256(sq, scratch);
-  inv = rsqrtf(tot / p.D + p.eps);
+  const float tot = block_sum_256(sq, scratch);
+  const float inv = rsqrtf(tot / p.D + p.eps);
   const int pos = p.row_pos[r];
   const int slot = p.row_slot[r];
   __nv_bfloat16* dst = p.win + (1ll * slot * p.ring + (pos % p.ring)) * p.D;
-  n = 0;
-  for (int i = tid; i < p.D / 2 && n < 4; i += 256, ++n) {
+#pragma unroll
+  for (int n = 0; n < 4; ++n) {
+    const int i = tid + 256 * n;
+    if (i >= p.D / 2) continue;
     float a = bf16_round(kvv[n].x * inv * p.kv_norm_w[2 * i]);
     float b = bf16_round(kvv[n].y * inv * p.kv_norm_w[2 * i + 1]);
     const int t = 2 * i - (p.D - p.rope_dim);
@@ -141,6 +159,8 @@ __global__ void __launch_bounds__(256) compress_kernel(CompressParams p) {
   __shared__ float latent[1024];
   __shared__ float ikey[256];
   const int r = blockIdx.x, tid = threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   const int pos = p.row_pos[r], slot = p.row_slot[r];
   if (slot < 0) return;
   const float* cur = p.extras + 1ll * r * p.extra_stride;
@@ -231,8 +251,8 @@ extern "C" int ds41_qkv_post(const float* planes, int splits, int rows, int ntot
   QkvPostParams p{planes, splits, rows, ntot, Q, D, rope_dim, extra_f32, index_heads, index_scale, q_norm_w,
                   kv_norm_w, inv_freq, row_pos, row_slot, static_cast<__nv_bfloat16*>(q_lat),
                   static_cast<__nv_bfloat16*>(win), ring, extras, eps};
-  qkv_post_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return cudaGetLastError();
+  if ((Q + D) & 1) return cudaErrorInvalidValue;   // kv columns are read as aligned float2
+  return launch_pdl(qkv_post_kernel, dim3(rows, 2), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
 }
 
 extern "C" int ds41_compress(const float* extras, int extra_stride, int rows, int D, int ID, int rope_dim, int ratio,
@@ -245,6 +265,5 @@ extern "C" int ds41_compress(const float* extras, int extra_stride, int rows, in
   CompressParams p{extras, extra_stride, rows, D, ID, rope_dim, ratio, row_pos, row_slot, pending, comp_norm_w,
                    static_cast<const __nv_bfloat16*>(wk), k_norm_w, inv_freq, inv_freq_idx, page_table, max_pages,
                    page_rows, static_cast<__nv_bfloat16*>(comp_pool), static_cast<__nv_bfloat16*>(idx_pool), eps};
-  compress_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(compress_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
 }

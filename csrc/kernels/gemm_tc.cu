@@ -12,6 +12,7 @@
 #include <cuda.h>
 
 #include "ds41_api.h"
+#include "ds41_launch.cuh"
 #include "ds41_ptx.cuh"
 #include "ds41_tma.h"
 
@@ -43,6 +44,7 @@ struct GemmParams {
   const float* row_w;     // modes 4/5: per (logical batch, n) weight, [batch][row_w_ld]
   int row_w_ld;
   float act_limit;        // mode 4: SwiGLU clamp
+  int static_operand;     // 1: A holds weights, 2: B holds weights (may be fetched before the dependency wait)
   int* status;
 };
 
@@ -92,8 +94,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int n_tiles = (p.N + BN - 1) / BN;
   const int kb_total = (p.K + Cfg::kBK - 1) / Cfg::kBK;
   const int kb_per_split = (kb_total + p.k_splits - 1) / p.k_splits;
+  pdl_launch_dependents();
   int batch_run = p.batch;
-  if (p.n_active != nullptr) batch_run = min(batch_run, *p.n_active);
+  if (p.n_active != nullptr) {
+    pdl_wait();                       // the active-expert count is produced by an earlier kernel
+    batch_run = min(batch_run, *p.n_active);
+  }
   const long long tiles = 1ll * m_tiles * n_tiles * p.k_splits * batch_run;
 
   if (threadIdx.x == 0) {
@@ -124,6 +130,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    constexpr uint32_t kStageTx = Cfg::kABytes + Cfg::kBBytes + (KIND == 2 ? 512 * (Cfg::kAtomsA + Cfg::kAtomsB) : 0);
+    // Weight tiles of the first stages do not depend on the previous kernel: fetch them before waiting for it.
+    int prefetched = 0;
+    if (p.static_operand != 0 && p.n_active == nullptr && p.batch_map == nullptr && blockIdx.x < tiles) {
+      long long r = blockIdx.x;
+      const int mt = static_cast<int>(r % m_tiles); r /= m_tiles;
+      const int nt = static_cast<int>(r % n_tiles); r /= n_tiles;
+      const int sp = static_cast<int>(r % p.k_splits); r /= p.k_splits;
+      const int b = static_cast<int>(r);
+      const int kb0 = sp * kb_per_split;
+      const int kb1 = min(kb_total, kb0 + kb_per_split);
+      prefetched = min(S, kb1 - kb0);
+      for (int i = 0; i < prefetched; ++i) {
+        uint8_t* sa = smem + i * Cfg::kStageBytes;
+        mbar_expect_tx(&full[i], kStageTx);
+        if (p.static_operand == 1) {
+          tma_load_3d(sa, &tmA, &full[i], (kb0 + i) * Cfg::kBK, mt * kBM, b);
+          if constexpr (DUAL)
+            tma_load_3d(sa + Cfg::kATile, &tmA, &full[i], (kb0 + i) * Cfg::kBK, p.up_row_offset + mt * kBM, b);
+        } else {
+          tma_load_3d(sa + Cfg::kABytes, &tmB, &full[i], (kb0 + i) * Cfg::kBK, nt * BN, p.b_batch_kind == 1 ? 0 : b);
+        }
+      }
+    }
+    pdl_wait();
     for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
       long long r = t;
       const int mt = static_cast<int>(r % m_tiles); r /= m_tiles;
@@ -133,15 +164,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int kb0 = sp * kb_per_split;
       const int kb1 = min(kb_total, kb0 + kb_per_split);
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait(&empty[stage], phase ^ 1, p.status, 100)) { ok = false; break; }
+        const bool early = prefetched > 0;      // this stage's barrier is armed and its weight tile is in flight
+        if (early) --prefetched;
+        if (!early && !mbar_wait(&empty[stage], phase ^ 1, p.status, 100)) { ok = false; break; }
         uint8_t* sa = smem + stage * Cfg::kStageBytes;
         uint8_t* sb = sa + Cfg::kABytes;
-        mbar_expect_tx(&full[stage], Cfg::kABytes + Cfg::kBBytes + (KIND == 2 ? 512 * (Cfg::kAtomsA + Cfg::kAtomsB) : 0));
+        if (!early) mbar_expect_tx(&full[stage], kStageTx);
         const int ba = p.batch_map != nullptr ? p.batch_map[b] : b;
         const int bb = p.b_batch_kind == 0 ? ba : (p.b_batch_kind == 1 ? 0 : b);
-        tma_load_3d(sa, &tmA, &full[stage], kb * Cfg::kBK, mt * kBM, ba);
-        if constexpr (DUAL) tma_load_3d(sa + Cfg::kATile, &tmA, &full[stage], kb * Cfg::kBK, p.up_row_offset + mt * kBM, ba);
-        tma_load_3d(sb, &tmB, &full[stage], kb * Cfg::kBK, nt * BN, bb);
+        if (!early || p.static_operand != 1) {
+          tma_load_3d(sa, &tmA, &full[stage], kb * Cfg::kBK, mt * kBM, ba);
+          if constexpr (DUAL)
+            tma_load_3d(sa + Cfg::kATile, &tmA, &full[stage], kb * Cfg::kBK, p.up_row_offset + mt * kBM, ba);
+        }
+        if (!early || p.static_operand != 2) tma_load_3d(sb, &tmB, &full[stage], kb * Cfg::kBK, nt * BN, bb);
         if constexpr (KIND == 2) {
           // scale-factor atoms: [row_atom][k_atom][512 B]; one k_atom per stage (128 elements of K)
           uint8_t* ssf = sb + Cfg::kBBytes;
@@ -381,8 +417,7 @@ static cudaError_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, c
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  gemm_tc_kernel<BN, KIND, DUAL><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, p);
-  return cudaGetLastError();
+  return launch_pdl(gemm_tc_kernel<BN, KIND, DUAL>, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, tmA, tmB, p);
 }
 
 template <int KIND>
@@ -425,7 +460,7 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   const int elem = kind == 0 ? 2 : 1;
   const int bk = kTileKBytes / elem;
   const int kb_total = (K + bk - 1) / bk;
-  if (kb_total % k_splits != 0) return cudaErrorInvalidValue;            // every split must own K blocks
+  if (1ll * (k_splits - 1) * ((kb_total + k_splits - 1) / k_splits) >= kb_total) return cudaErrorInvalidValue;   // no empty split
   if (kind == 2 && (K % 128 != 0 || a->sfa == nullptr || a->sfb == nullptr)) return cudaErrorInvalidValue;
   if (kind == 2 && bn < 32 && N > bn) return cudaErrorInvalidValue;      // 16-row scale tiles cannot be lane-shifted
   if (k_splits > 1 && out_mode != 1 && out_mode != 3) return cudaErrorInvalidValue;   // partials are fp32
@@ -460,6 +495,7 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   p.row_w = a->row_w;
   p.row_w_ld = a->row_w_ld;
   p.act_limit = a->act_limit;
+  p.static_operand = a->static_operand;
   p.status = a->status;
   const long long tiles = 1ll * ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn) * k_splits * batch;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());

@@ -16,6 +16,7 @@
 //   hc_finish    : reduce the slice partials in fixed order, compute pre/post/comb, collapse with the
 //                  incoming pre and apply the RMSNorm weight -> normalised bf16 rows for the GEMMs.
 #include "ds41_api.h"
+#include "ds41_launch.cuh"
 #include "ds41_ptx.cuh"
 
 namespace ds41 {
@@ -36,6 +37,8 @@ struct PartList {
 __global__ void embed_streams_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ embed,
                                      __nv_bfloat16* __restrict__ streams, float* __restrict__ pre, int rows, int H,
                                      int mult, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   int tok = tokens[r];
   if (tok < 0 || tok >= vocab) tok = 0;
@@ -59,6 +62,8 @@ hc_post_mix_kernel(const __nv_bfloat16* __restrict__ streams_in, __nv_bfloat16* 
   const int r0 = blockIdx.y * kHcRowsPerBlock;
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (wait_flags != nullptr && parts.n_ranks > 1) {
     // every peer publishes "my partial planes for this step are complete" by raising its flag
@@ -109,6 +114,7 @@ hc_post_mix_kernel(const __nv_bfloat16* __restrict__ streams_in, __nv_bfloat16* 
     for (int rr = 0; rr < kHcRowsPerBlock; ++rr) dot[j][rr] = 0.f;
 #pragma unroll
   for (int rr = 0; rr < kHcRowsPerBlock; ++rr) sq[rr] = 0.f;
+#pragma unroll 8
   for (int idx = lane; idx < kHcMaxMult * kHcSlice; idx += 32) {
     const int d = idx / kHcSlice, c = idx % kHcSlice;
     const long long kcol = 1ll * d * H + c0 + c;
@@ -139,23 +145,28 @@ hc_post_mix_kernel(const __nv_bfloat16* __restrict__ streams_in, __nv_bfloat16* 
 }
 
 // One block per row.  Produces next_pre/post/comb from the slice partials, then the collapsed,
-// normalised row.  `norm_w` may be null (no weight).
+// normalised row.  `norm_w` may be null (no weight).  When `xq` is given the normalised row is also emitted
+// as E4M3 with one power-of-two scale per 128 columns, written in the MX GEMM's scale-atom layout.
 __global__ void __launch_bounds__(256)
 hc_finish_kernel(const float* __restrict__ partial, int n_slices, const float* __restrict__ scale,
                  const float* __restrict__ base, const float* __restrict__ pre_in,
                  const __nv_bfloat16* __restrict__ streams, const float* __restrict__ norm_w,
                  float* __restrict__ next_pre, float* __restrict__ post, float* __restrict__ comb,
-                 __nv_bfloat16* __restrict__ xn, float* __restrict__ tap_mean, int rows, int H, int iters,
-                 float hc_eps, float norm_eps) {
+                 __nv_bfloat16* __restrict__ xn, float* __restrict__ tap_mean, uint8_t* __restrict__ xq,
+                 uint8_t* __restrict__ xq_sf, int rows, int H, int iters, float hc_eps, float norm_eps) {
   __shared__ float proj[kHcProj + 1];
   __shared__ float warp_part[8];
   __shared__ float inv_rms;
   const int r = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid <= kHcProj) {
+  pdl_launch_dependents();
+  pdl_wait();
+  // ---- slice partials: warp w reduces values w, w+8, w+16 (+24); fixed shuffle tree -> deterministic
+  for (int j = warp; j <= kHcProj; j += 8) {
     float acc = 0.f;
-    for (int s = 0; s < n_slices; ++s) acc += partial[(1ll * s * rows + r) * kHcPartialStride + tid];
-    proj[tid] = acc;
+    for (int s = lane; s < n_slices; s += 32) acc += partial[(1ll * s * rows + r) * kHcPartialStride + j];
+    acc = warp_sum(acc);
+    if (lane == 0) proj[j] = acc;
   }
   __syncthreads();
   if (warp == 0) {
@@ -187,28 +198,39 @@ hc_finish_kernel(const float* __restrict__ partial, int n_slices, const float* _
     }
     if (lane < 16) comb[r * 16 + lane] = v;
   }
-  // ---- collapse with the incoming pre + RMSNorm
+  // ---- collapse with the incoming pre + RMSNorm; each thread owns up to 3 groups of 8 columns
   const float p0 = pre_in[r * 4 + 0], p1 = pre_in[r * 4 + 1], p2 = pre_in[r * 4 + 2], p3 = pre_in[r * 4 + 3];
   const __nv_bfloat16* s0 = streams + 1ll * r * 4 * H;
+  constexpr int kMaxItems = 3;               // H <= 256 * 3 * 8 = 6144
+  float keep[kMaxItems][8];
   float local_sq = 0.f;
-  // H <= 256 * 2 * 16: keep this thread's collapsed values in registers
-  constexpr int kMaxPairs = 16;
-  float2 keep[kMaxPairs];
-  int np = 0;
-  for (int i = tid; i < H / 2 && np < kMaxPairs; i += 256, ++np) {
-    const float2 a = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(s0)[i]);
-    const float2 b = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(s0 + H)[i]);
-    const float2 c = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(s0 + 2 * H)[i]);
-    const float2 d = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(s0 + 3 * H)[i]);
-    float2 x;
-    x.x = bf16_round(fmaf(p3, d.x, fmaf(p2, c.x, fmaf(p1, b.x, p0 * a.x))));
-    x.y = bf16_round(fmaf(p3, d.y, fmaf(p2, c.y, fmaf(p1, b.y, p0 * a.y))));
-    if (tap_mean != nullptr) {
-      tap_mean[1ll * r * H + 2 * i] = 0.25f * (a.x + b.x + c.x + d.x);
-      tap_mean[1ll * r * H + 2 * i + 1] = 0.25f * (a.y + b.y + c.y + d.y);
+  const int n_items = H / 8;
+#pragma unroll
+  for (int n = 0; n < kMaxItems; ++n) {
+    const int i = tid + 256 * n;
+    if (i < n_items) {
+      uint4 raw[4];
+#pragma unroll
+      for (int s = 0; s < 4; ++s) raw[s] = *reinterpret_cast<const uint4*>(s0 + 1ll * s * H + 8 * i);
+      const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&raw[0]);
+      const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&raw[1]);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[2]);
+      const __nv_bfloat162* h3 = reinterpret_cast<const __nv_bfloat162*>(&raw[3]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 a = __bfloat1622float2(h0[q]), b = __bfloat1622float2(h1[q]);
+        const float2 c = __bfloat1622float2(h2[q]), d = __bfloat1622float2(h3[q]);
+        const float x = bf16_round(fmaf(p3, d.x, fmaf(p2, c.x, fmaf(p1, b.x, p0 * a.x))));
+        const float y = bf16_round(fmaf(p3, d.y, fmaf(p2, c.y, fmaf(p1, b.y, p0 * a.y))));
+        keep[n][2 * q] = x;
+        keep[n][2 * q + 1] = y;
+        local_sq = fmaf(x, x, fmaf(y, y, local_sq));
+        if (tap_mean != nullptr) {
+          tap_mean[1ll * r * H + 8 * i + 2 * q] = 0.25f * (a.x + b.x + c.x + d.x);
+          tap_mean[1ll * r * H + 8 * i + 2 * q + 1] = 0.25f * (a.y + b.y + c.y + d.y);
+        }
+      }
     }
-    keep[np] = x;
-    local_sq = fmaf(x.x, x.x, fmaf(x.y, x.y, local_sq));
   }
   local_sq = warp_sum(local_sq);
   if (lane == 0) warp_part[warp] = local_sq;
@@ -220,12 +242,53 @@ hc_finish_kernel(const float* __restrict__ partial, int n_slices, const float* _
   }
   __syncthreads();
   const float inv = inv_rms;
-  np = 0;
-  for (int i = tid; i < H / 2 && np < kMaxPairs; i += 256, ++np) {
-    float wx = 1.f, wy = 1.f;
-    if (norm_w != nullptr) { wx = norm_w[2 * i]; wy = norm_w[2 * i + 1]; }
-    reinterpret_cast<__nv_bfloat162*>(xn + 1ll * r * H)[i] =
-        __floats2bfloat162_rn(keep[np].x * inv * wx, keep[np].y * inv * wy);
+#pragma unroll
+  for (int n = 0; n < kMaxItems; ++n) {
+    const int i = tid + 256 * n;
+    const bool live = i < n_items;
+    float y[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float w = (live && norm_w != nullptr) ? norm_w[8 * i + q] : 1.f;
+      y[q] = live ? bf16_round(keep[n][q] * inv * w) : 0.f;
+    }
+    if (live) {
+      uint4 o;
+      __nv_bfloat162 t0 = __floats2bfloat162_rn(y[0], y[1]), t1 = __floats2bfloat162_rn(y[2], y[3]);
+      __nv_bfloat162 t2 = __floats2bfloat162_rn(y[4], y[5]), t3 = __floats2bfloat162_rn(y[6], y[7]);
+      o.x = *reinterpret_cast<uint32_t*>(&t0); o.y = *reinterpret_cast<uint32_t*>(&t1);
+      o.z = *reinterpret_cast<uint32_t*>(&t2); o.w = *reinterpret_cast<uint32_t*>(&t3);
+      *reinterpret_cast<uint4*>(xn + 1ll * r * H + 8 * i) = o;
+    }
+    if (xq != nullptr) {
+      // 16 consecutive lanes hold one 128-column group (H is a multiple of 128, so groups never straddle `live`)
+      float amax = 0.f;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) amax = fmaxf(amax, fabsf(y[q]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
+      float sc = fmaxf(amax * (1.0f / 448.0f), 1.17549435e-38f);
+      uint32_t bits = __float_as_uint(sc);
+      uint32_t e = (bits >> 23) & 0xFF;
+      if (bits & 0x7FFFFF) ++e;
+      if (e > 254) e = 254;
+      const float qs = __uint_as_float((254u - e) << 23);
+      if (live) {
+        const __nv_fp8x4_e4m3 lo(make_float4(y[0] * qs, y[1] * qs, y[2] * qs, y[3] * qs));
+        const __nv_fp8x4_e4m3 hi(make_float4(y[4] * qs, y[5] * qs, y[6] * qs, y[7] * qs));
+        uint2 o;
+        o.x = *reinterpret_cast<const uint32_t*>(&lo);
+        o.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(xq + 1ll * r * H + 8 * i) = o;
+        if ((i & 15) == 0) {
+          const int kc = i / 16;
+          uint8_t* atom = xq_sf + (1ll * (r / 128) * (H / 128) + kc) * 512;
+          *reinterpret_cast<uint32_t*>(atom + (r % 32) * 16 + ((r / 32) % 4) * 4) = e * 0x01010101u;
+        }
+      }
+    }
   }
 }
 
@@ -236,10 +299,9 @@ using namespace ds41;
 extern "C" int ds41_embed_streams(const int* tokens, const void* embed, void* streams, float* pre, int rows, int H,
                                   int mult, int vocab, void* stream) {
   if (rows <= 0 || H % 8 != 0 || mult != kHcMaxMult) return cudaErrorInvalidValue;
-  embed_streams_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      tokens, static_cast<const __nv_bfloat16*>(embed), static_cast<__nv_bfloat16*>(streams), pre, rows, H, mult,
-      vocab);
-  return cudaGetLastError();
+  return launch_pdl(embed_streams_kernel, dim3(rows), dim3(128), 0, static_cast<cudaStream_t>(stream), tokens,
+                    static_cast<const __nv_bfloat16*>(embed), static_cast<__nv_bfloat16*>(streams), pre, rows, H,
+                    mult, vocab);
 }
 
 extern "C" int ds41_hc_post_mix(const void* streams_in, void* streams_out, const float* const* part_bases,
@@ -253,19 +315,19 @@ extern "C" int ds41_hc_post_mix(const void* streams_in, void* streams_out, const
   parts.split_stride = split_stride;
   for (int i = 0; i < n_ranks; ++i) parts.base[i] = part_bases[i];
   dim3 grid(H / kHcSlice, (rows + kHcRowsPerBlock - 1) / kHcRowsPerBlock);
-  hc_post_mix_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(streams_in), static_cast<__nv_bfloat16*>(streams_out), parts, post, comb, fn,
-      partial, rows, H, wait_flags, wait_epoch, status);
-  return cudaGetLastError();
+  return launch_pdl(hc_post_mix_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const __nv_bfloat16*>(streams_in), static_cast<__nv_bfloat16*>(streams_out), parts,
+                    post, comb, fn, partial, rows, H, wait_flags, wait_epoch, status);
 }
 
 extern "C" int ds41_hc_finish(const float* partial, int n_slices, const float* scale, const float* base,
                               const float* pre_in, const void* streams, const float* norm_w, float* next_pre,
-                              float* post, float* comb, void* xn, float* tap_mean, int rows, int H, int iters,
-                              float hc_eps, float norm_eps, void* stream) {
-  if (rows <= 0 || H % 2 != 0 || H > 256 * 2 * 16) return cudaErrorInvalidValue;
-  hc_finish_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      partial, n_slices, scale, base, pre_in, static_cast<const __nv_bfloat16*>(streams), norm_w, next_pre, post,
-      comb, static_cast<__nv_bfloat16*>(xn), tap_mean, rows, H, iters, hc_eps, norm_eps);
-  return cudaGetLastError();
+                              float* post, float* comb, void* xn, float* tap_mean, void* xq, void* xq_sf, int rows,
+                              int H, int iters, float hc_eps, float norm_eps, void* stream) {
+  if (rows <= 0 || H % 8 != 0 || H > 256 * 3 * 8 || (xq != nullptr && (H % 128 != 0 || xq_sf == nullptr)))
+    return cudaErrorInvalidValue;
+  return launch_pdl(hc_finish_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), partial, n_slices,
+                    scale, base, pre_in, static_cast<const __nv_bfloat16*>(streams), norm_w, next_pre, post, comb,
+                    static_cast<__nv_bfloat16*>(xn), tap_mean, static_cast<uint8_t*>(xq),
+                    static_cast<uint8_t*>(xq_sf), rows, H, iters, hc_eps, norm_eps);
 }

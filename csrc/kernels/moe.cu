@@ -12,6 +12,7 @@
 //                  this rank's fp32 partial plane (the cross-rank sum happens in hc_post_mix).
 //                  (reduction-order contract of native/cuda/kernels/v41_route_reduce.cu:13-34)
 #include "ds41_api.h"
+#include "ds41_launch.cuh"
 #include "ds41_ptx.cuh"
 
 namespace ds41 {
@@ -35,8 +36,24 @@ __global__ void __launch_bounds__(512) router_select_kernel(RouterParams p) {
   __shared__ int chosen[16];
   __shared__ float chosen_score[16];
   const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
   const long long plane = 1ll * p.rows * p.ntot;
   const float* row0 = p.planes + 1ll * r * p.ntot;
+  if (blockIdx.y == 1) {
+    // second block of the row: the shared expert's clamp-SwiGLU activation
+    for (int i = tid; i < p.I_sh; i += 512) {
+      float g = 0.f, u = 0.f;
+      for (int s = 0; s < p.splits; ++s) {
+        g += row0[s * plane + p.E + i];
+        u += row0[s * plane + p.E + p.I_sh + i];
+      }
+      g = fminf(bf16_round(g), p.limit);
+      u = fminf(fmaxf(bf16_round(u), -p.limit), p.limit);
+      p.shared_act[1ll * r * p.I_sh + i] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
+    }
+    return;
+  }
   if (tid < p.E) {
     float a = 0.f;
     for (int s = 0; s < p.splits; ++s) a += row0[s * plane + tid];
@@ -79,16 +96,6 @@ __global__ void __launch_bounds__(512) router_select_kernel(RouterParams p) {
       p.weights[r * p.topk + k] = chosen_score[k] / (sum + 1e-20f) * p.route_scale;
     }
   }
-  for (int i = tid; i < p.I_sh; i += 512) {
-    float g = 0.f, u = 0.f;
-    for (int s = 0; s < p.splits; ++s) {
-      g += row0[s * plane + p.E + i];
-      u += row0[s * plane + p.E + p.I_sh + i];
-    }
-    g = fminf(bf16_round(g), p.limit);
-    u = fminf(fmaxf(bf16_round(u), -p.limit), p.limit);
-    p.shared_act[1ll * r * p.I_sh + i] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
-  }
 }
 
 struct PlanParams {
@@ -109,6 +116,8 @@ __global__ void __launch_bounds__(512) moe_plan_kernel(PlanParams p) {
   __shared__ int slot_of_expert[512];
   __shared__ int warp_tot[16];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
   used[tid] = 0;
   __syncthreads();
   for (int i = tid; i < p.rows * p.topk; i += 512) {
@@ -159,6 +168,8 @@ struct CombineParams {
 __global__ void __launch_bounds__(256) moe_combine_kernel(CombineParams p) {
   const int r = blockIdx.y;
   const int c = (blockIdx.x * 256 + threadIdx.x) * 4;
+  pdl_launch_dependents();
+  pdl_wait();
   if (c >= p.H) return;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int k = 0; k < p.topk; ++k) {
@@ -178,6 +189,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(CombineParams p) {
 
 // ---- publish "this rank's partial planes are complete": bump the rank-local epoch and store it to the flag
 __global__ void signal_kernel(uint32_t* epoch, uint32_t* flag) {
+  pdl_launch_dependents();
+  pdl_wait();
   if (threadIdx.x == 0) {
     const uint32_t e = *epoch + 1;
     *epoch = e;
@@ -190,6 +203,8 @@ __global__ void signal_kernel(uint32_t* epoch, uint32_t* flag) {
 __global__ void reduce_planes_kernel(const float* planes, int splits, long long plane, void* out, int as_bf16,
                                      long long n) {
   const long long i = (1ll * blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  pdl_launch_dependents();
+  pdl_wait();
   if (i >= n) return;
   float a = 0.f, b = 0.f;
   for (int s = 0; s < splits; ++s) {
@@ -215,8 +230,7 @@ extern "C" int ds41_router_select(const float* planes, int splits, int rows, int
   if (rows <= 0 || E > 512 || topk > 16 || E + 2 * I_sh > ntot) return cudaErrorInvalidValue;
   RouterParams p{planes, splits, rows, ntot, E, I_sh, topk, bias, route_scale, limit, ids, weights,
                  static_cast<__nv_bfloat16*>(shared_act)};
-  router_select_kernel<<<rows, 512, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(router_select_kernel, dim3(rows, I_sh > 0 ? 2 : 1), dim3(512), 0, static_cast<cudaStream_t>(stream), p);
 }
 
 extern "C" int ds41_moe_plan(const int* ids, const float* weights, const int* row_slot, int rows, int topk, int e0,
@@ -224,8 +238,7 @@ extern "C" int ds41_moe_plan(const int* ids, const float* weights, const int* ro
                              int* slot_of, void* stream) {
   if (rows <= 0 || e1 - e0 > 512 || e1 <= e0 || row_w_ld < rows) return cudaErrorInvalidValue;
   PlanParams p{ids, weights, row_slot, rows, topk, e0, e1, max_active, row_w_ld, active, n_active, row_w, slot_of};
-  moe_plan_kernel<<<1, 512, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(moe_plan_kernel, dim3(1), dim3(512), 0, static_cast<cudaStream_t>(stream), p);
 }
 
 extern "C" int ds41_moe_combine(const float* fc2, const int* slot_of, const float* shared, int shared_splits,
@@ -233,20 +246,17 @@ extern "C" int ds41_moe_combine(const float* fc2, const int* slot_of, const floa
   if (rows <= 0 || (H & 3)) return cudaErrorInvalidValue;
   CombineParams p{fc2, slot_of, shared, shared_splits, rows, topk, H, out};
   dim3 grid((H / 4 + 255) / 256, rows);
-  moe_combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(moe_combine_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), p);
 }
 
 extern "C" int ds41_signal(uint32_t* epoch, uint32_t* flag, void* stream) {
-  signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(epoch, flag);
-  return cudaGetLastError();
+  return launch_pdl(signal_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), epoch, flag);
 }
 
 extern "C" int ds41_reduce_planes(const float* planes, int splits, long long plane, void* out, int as_bf16,
                                   long long n, void* stream) {
   if (n <= 0 || splits <= 0) return cudaErrorInvalidValue;
   const long long threads = (n + 1) / 2;
-  reduce_planes_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      planes, splits, plane, out, as_bf16, n);
-  return cudaGetLastError();
+  return launch_pdl(reduce_planes_kernel, dim3(static_cast<unsigned>((threads + 255) / 256)), dim3(256), 0,
+                    static_cast<cudaStream_t>(stream), planes, splits, plane, out, as_bf16, n);
 }

@@ -8,6 +8,7 @@
 //                 scale = smallest power of two >= amax/448  (quantise contract of the reference's
 //                 native/include/ds41rt_v41_experts.h:55-62 and native/cuda/kernels/v41_kv.cu:15-46).
 #include "ds41_api.h"
+#include "ds41_launch.cuh"
 #include "ds41_ptx.cuh"
 
 namespace ds41 {
@@ -37,6 +38,8 @@ __global__ void __launch_bounds__(256) act_quant_mx_kernel(ActQuantParams p) {
   const int chunks = p.K / 128;
   const long long item = 1ll * blockIdx.x * 8 + warp;
   const int b = blockIdx.y;
+  pdl_launch_dependents();
+  pdl_wait();
   if (p.n_active != nullptr && b >= *p.n_active) return;
   if (item >= 1ll * p.rows * chunks) return;
   const int r = static_cast<int>(item / chunks), kc = static_cast<int>(item % chunks);
@@ -78,6 +81,5 @@ extern "C" int ds41_act_quant_mx(const void* x, long long ldx, long long x_batch
                    q_batch_stride, static_cast<uint8_t*>(sf), sf_batch_stride, rows, K, batch, group, n_active};
   const long long items = 1ll * rows * (K / 128);
   dim3 grid(static_cast<unsigned>((items + 7) / 8), batch);
-  act_quant_mx_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(act_quant_mx_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), p);
 }

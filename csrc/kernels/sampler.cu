@@ -9,6 +9,7 @@
 //                  target's choice after draft j-1; emits accepted count and the tokens to emit
 //                  (rust/crates/ds41rt-core/src/dspark_verify.rs:18-52)
 #include "ds41_api.h"
+#include "ds41_launch.cuh"
 #include "ds41_ptx.cuh"
 
 namespace ds41 {
@@ -29,6 +30,8 @@ __global__ void __launch_bounds__(1024) argmax_rows_kernel(ArgmaxParams p) {
   __shared__ int wi[32];
   __shared__ int bad;
   const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
   if (tid == 0) bad = 0;
   __syncthreads();
   float v = -INFINITY;
@@ -71,6 +74,8 @@ struct MergeArgs {
   int* status;
 };
 __global__ void argmax_merge_kernel(MergeArgs p) {
+  pdl_launch_dependents();
+  pdl_wait();
   if (p.wait_flags != nullptr && p.n_ranks > 1) {
     if (threadIdx.x < p.n_ranks) flag_wait_ge(p.wait_flags[threadIdx.x], *p.wait_epoch, p.status, 500 + threadIdx.x);
     __syncthreads();
@@ -102,6 +107,8 @@ struct AcceptParams {
 };
 __global__ void spec_accept_kernel(AcceptParams p) {
   const int q = blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   if (q >= p.reqs) return;
   const int f = p.first[q], n = p.count[q];
   int acc = 0;
@@ -121,6 +128,8 @@ __global__ void spec_accept_kernel(AcceptParams p) {
 // Device-side feedback for back-to-back decode steps: next input token = chosen token, position + 1.
 __global__ void decode_feedback_kernel(const int* chosen, int* tokens, int* pos, int rows) {
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   if (r < rows) {
     tokens[r] = chosen[r];
     pos[r] += 1;
@@ -133,8 +142,8 @@ using namespace ds41;
 
 extern "C" int ds41_decode_feedback(const int* chosen, int* tokens, int* pos, int rows, void* stream) {
   if (rows <= 0) return cudaErrorInvalidValue;
-  decode_feedback_kernel<<<(rows + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(chosen, tokens, pos, rows);
-  return cudaGetLastError();
+  return launch_pdl(decode_feedback_kernel, dim3((rows + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream),
+                    chosen, tokens, pos, rows);
 }
 
 extern "C" int ds41_argmax_rows(const float* logits, long long ld, int rows, int vocab_local, int vocab_offset,
@@ -142,8 +151,7 @@ extern "C" int ds41_argmax_rows(const float* logits, long long ld, int rows, int
                                 int* row_status, void* stream) {
   if (rows <= 0 || vocab_local <= 0) return cudaErrorInvalidValue;
   ArgmaxParams p{logits, ld, vocab_local, vocab_offset, mask, mask_words, best_val, best_idx, row_status};
-  argmax_rows_kernel<<<rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(argmax_rows_kernel, dim3(rows), dim3(1024), 0, static_cast<cudaStream_t>(stream), p);
 }
 
 extern "C" int ds41_argmax_merge(const float* const* vals, const int* const* idxs, int n_ranks, int rows, int* out,
@@ -154,14 +162,12 @@ extern "C" int ds41_argmax_merge(const float* const* vals, const int* const* idx
   for (int k = 0; k < n_ranks; ++k) { p.vals[k] = vals[k]; p.idxs[k] = idxs[k]; }
   p.n_ranks = n_ranks; p.rows = rows; p.out = out;
   p.wait_flags = wait_flags; p.wait_epoch = wait_epoch; p.status = status;
-  argmax_merge_kernel<<<(rows + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(argmax_merge_kernel, dim3((rows + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream), p);
 }
 
 extern "C" int ds41_spec_accept(const int* inputs, const int* chosen, const int* first, const int* count, int reqs,
                                 int max_emit, int eos, int* accepted, int* emit, int* n_emit, void* stream) {
   if (reqs <= 0 || max_emit <= 0) return cudaErrorInvalidValue;
   AcceptParams p{inputs, chosen, first, count, reqs, max_emit, eos, accepted, emit, n_emit};
-  spec_accept_kernel<<<(reqs + 63) / 64, 64, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(spec_accept_kernel, dim3((reqs + 63) / 64), dim3(64), 0, static_cast<cudaStream_t>(stream), p);
 }

@@ -11,6 +11,7 @@
 // The attention tiles use warp-level mma (m16n8k16 bf16): this kernel is latency/bandwidth bound at
 // decode batch sizes, each CTA touching 64 gathered 1 KiB rows.
 #include "ds41_api.h"
+#include "ds41_launch.cuh"
 #include "ds41_ptx.cuh"
 
 namespace ds41 {
@@ -51,6 +52,8 @@ __global__ void __launch_bounds__(256) index_score_kernel(IndexScoreParams p) {
   __shared__ float ws[32];
   __shared__ float kbuf[8][128];
   const int r = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  pdl_launch_dependents();
+  pdl_wait();
   const int pos = p.row_pos[r], slot = p.row_slot[r];
   if (slot < 0) return;
   const int n_vis = min((pos + 1) / p.ratio, p.max_keys);
@@ -144,6 +147,8 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(TopkParams p) {
   __shared__ uint32_t s_prefix;
   __shared__ int s_need;
   const int r = blockIdx.x, tid = threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   const int pos = p.row_pos[r];
   int* out = p.sel + 1ll * r * p.k;
   if (p.row_slot[r] < 0) {
@@ -245,27 +250,37 @@ struct AttendParams {
 };
 
 constexpr int kKeysPerCta = 64;
+constexpr int kHeadsPerCta = 16;
 
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+// grid (n_splits, rows, ceil(heads/16)), 128 threads: one CTA = 64 keys x 16 heads.
 template <int D>
-__global__ void __launch_bounds__(512) attend_kernel(AttendParams p) {
+__global__ void __launch_bounds__(128) attend_kernel(AttendParams p) {
   constexpr int LD = D + 8;                                // padded row (bf16 elements)
   extern __shared__ __align__(16) uint8_t smem_attn[];
-  const int n_mt = (p.heads + 15) / 16;
   __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_attn);                 // [64][LD]
-  __nv_bfloat16* sQ = sK + kKeysPerCta * LD;                                         // [16*n_mt][LD]
-  float* sS = reinterpret_cast<float*>(sQ + 16 * n_mt * LD);                         // [16*n_mt][65]
-  __nv_bfloat16* sP = reinterpret_cast<__nv_bfloat16*>(sS + 16 * n_mt * 65);         // [16*n_mt][72]
-  float* sCos = reinterpret_cast<float*>(sP + 16 * n_mt * 72);                       // [rope_dim/2] x2
+  __nv_bfloat16* sQ = sK + kKeysPerCta * LD;                                         // [16][LD]
+  float* sS = reinterpret_cast<float*>(sQ + kHeadsPerCta * LD);                      // [16][65]
+  __nv_bfloat16* sP = reinterpret_cast<__nv_bfloat16*>(sS + kHeadsPerCta * 65);      // [16][72]
+  float* sCos = reinterpret_cast<float*>(sP + kHeadsPerCta * 72);                    // [64]
   float* sSin = sCos + 64;
   const __nv_bfloat16** sPtr = reinterpret_cast<const __nv_bfloat16**>(sSin + 64);   // [64]
 
-  const int split = blockIdx.x, r = blockIdx.y;
+  const int split = blockIdx.x, r = blockIdx.y, h_base = blockIdx.z * kHeadsPerCta;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int nthreads = blockDim.x;
-  const int pos = p.row_pos[r], slot = p.row_slot[r];
   const int g = lane >> 2, t4 = lane & 3;
-  float* ml_out = p.part_ml + ((1ll * r * p.n_splits + split) * p.heads) * 2;
-  float* o_out = p.part_o + ((1ll * r * p.n_splits + split) * p.heads) * D;
+  const int n_heads = min(kHeadsPerCta, p.heads - h_base);
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pos = p.row_pos[r], slot = p.row_slot[r];
+  float* ml_out = p.part_ml + ((1ll * r * p.n_splits + split) * p.heads + h_base) * 2;
+  float* o_out = p.part_o + ((1ll * r * p.n_splits + split) * p.heads + h_base) * D;
 
   int n_w = 0, n_s = 0, hi_pos = pos, lo_pos = 0;
   if (slot >= 0) {
@@ -279,9 +294,9 @@ __global__ void __launch_bounds__(512) attend_kernel(AttendParams p) {
   const int k0 = split * kKeysPerCta;
   const int k_cnt = max(0, min(kKeysPerCta, n_keys - k0));
   if (k_cnt == 0) {
-    for (int h = tid; h < p.heads; h += nthreads) {
-      ml_out[2 * h] = -INFINITY;
-      ml_out[2 * h + 1] = 0.f;
+    if (tid < n_heads) {
+      ml_out[2 * tid] = -INFINITY;
+      ml_out[2 * tid + 1] = 0.f;
     }
     return;
   }
@@ -300,45 +315,47 @@ __global__ void __launch_bounds__(512) attend_kernel(AttendParams p) {
       }
     }
     sPtr[tid] = ptr;
+  } else if (tid - kKeysPerCta < p.rope_dim / 2) {
+    rope_cs2(pos, p.inv_freq[tid - kKeysPerCta], &sCos[tid - kKeysPerCta], &sSin[tid - kKeysPerCta]);
   }
-  if (tid < p.rope_dim / 2) rope_cs2(pos, p.inv_freq[tid], &sCos[tid], &sSin[tid]);
   __syncthreads();
-  // ---- K tile (zero-filled beyond k_cnt)
-  for (int idx = tid; idx < kKeysPerCta * (D / 8); idx += nthreads) {
+  // ---- K tile: asynchronous 16-byte copies straight into shared memory (zero-filled beyond k_cnt)
+#pragma unroll 8
+  for (int idx = tid; idx < kKeysPerCta * (D / 8); idx += 128) {
     const int key = idx / (D / 8), ch = idx % (D / 8);
-    uint4 v = make_uint4(0, 0, 0, 0);
     const __nv_bfloat16* src = sPtr[key];
-    if (src != nullptr) v = *reinterpret_cast<const uint4*>(src + ch * 8);
-    *reinterpret_cast<uint4*>(sK + key * LD + ch * 8) = v;
+    __nv_bfloat16* dst = sK + key * LD + ch * 8;
+    if (src != nullptr) cp_async_16(dst, src + ch * 8);
+    else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
   }
   // ---- Q tile with RoPE on the tail (zero rows for padding heads)
   const int rope0 = D - p.rope_dim;
-  for (int idx = tid; idx < 16 * n_mt * (D / 2); idx += nthreads) {
-    const int h = idx / (D / 2), i = idx % (D / 2);
-    float a = 0.f, b = 0.f;
-    if (h < p.heads) {
-      const float2 v = __bfloat1622float2(
-          *reinterpret_cast<const __nv_bfloat162*>(p.q + 1ll * r * p.ldq + p.q_off + 1ll * h * D + 2 * i));
-      a = v.x;
-      b = v.y;
-      const int t = 2 * i - rope0;
-      if (t >= 0) {
-        const float c = sCos[t / 2], s = sSin[t / 2];
-        const float ra = a * c - b * s, rb = b * c + a * s;
-        a = ra;
-        b = rb;
+#pragma unroll 4
+  for (int idx = tid; idx < kHeadsPerCta * (D / 8); idx += 128) {
+    const int h = idx / (D / 8), ch = idx % (D / 8);
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (h < n_heads)
+      raw = *reinterpret_cast<const uint4*>(p.q + 1ll * r * p.ldq + p.q_off + 1ll * (h_base + h) * D + ch * 8);
+    if (ch * 8 >= rope0 && h < n_heads) {
+      __nv_bfloat162* v = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __bfloat1622float2(v[q]);
+        const int t = (ch * 8 + 2 * q - rope0) / 2;
+        const float c = sCos[t], sn = sSin[t];
+        v[q] = __floats2bfloat162_rn(f.x * c - f.y * sn, f.y * c + f.x * sn);
       }
     }
-    *reinterpret_cast<__nv_bfloat162*>(sQ + h * LD + 2 * i) = __floats2bfloat162_rn(a, b);
+    *reinterpret_cast<uint4*>(sQ + h * LD + ch * 8) = raw;
   }
+  cp_async_wait_all();
   __syncthreads();
-  const int mt = warp % n_mt, part = warp / n_mt;     // part in 0..3
-  // ---- S = Q K^T for 16 heads x 16 keys per warp
+  // ---- S = Q K^T: warp w owns keys [16w, 16w+16)
   {
     float c[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    const __nv_bfloat16* qa = sQ + (mt * 16 + g) * LD + 2 * t4;
-    const __nv_bfloat16* kb = sK + (part * 16 + g) * LD + 2 * t4;
-#pragma unroll 4
+    const __nv_bfloat16* qa = sQ + g * LD + 2 * t4;
+    const __nv_bfloat16* kb = sK + (warp * 16 + g) * LD + 2 * t4;
+#pragma unroll 8
     for (int kk = 0; kk < D; kk += 16) {
       uint32_t a[4];
       a[0] = *reinterpret_cast<const uint32_t*>(qa + kk);
@@ -354,9 +371,9 @@ __global__ void __launch_bounds__(512) attend_kernel(AttendParams p) {
     }
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
-      const int key = part * 16 + nt * 8 + 2 * t4;
-      float* s0 = sS + (mt * 16 + g) * 65 + key;
-      float* s1 = sS + (mt * 16 + g + 8) * 65 + key;
+      const int key = warp * 16 + nt * 8 + 2 * t4;
+      float* s0 = sS + g * 65 + key;
+      float* s1 = sS + (g + 8) * 65 + key;
       s0[0] = key < k_cnt ? c[nt][0] * p.scale : -INFINITY;
       s0[1] = key + 1 < k_cnt ? c[nt][1] * p.scale : -INFINITY;
       s1[0] = key < k_cnt ? c[nt][2] * p.scale : -INFINITY;
@@ -364,8 +381,10 @@ __global__ void __launch_bounds__(512) attend_kernel(AttendParams p) {
     }
   }
   __syncthreads();
-  // ---- per-head softmax statistics over this CTA's keys; P in bf16
-  for (int row = warp; row < 16 * n_mt; row += (nthreads >> 5)) {
+  // ---- per-head softmax statistics over this CTA's keys; P in bf16 (4 head rows per warp)
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = warp * 4 + i;
     const float v0 = sS[row * 65 + lane], v1 = sS[row * 65 + lane + 32];
     const float m = warp_max(fmaxf(v0, v1));
     const float e0 = __expf(v0 - m), e1 = __expf(v1 - m);
@@ -373,13 +392,13 @@ __global__ void __launch_bounds__(512) attend_kernel(AttendParams p) {
     const float l = warp_sum(__bfloat162float(b0) + __bfloat162float(b1));
     sP[row * 72 + lane] = b0;
     sP[row * 72 + lane + 32] = b1;
-    if (lane == 0 && row < p.heads) {
+    if (lane == 0 && row < n_heads) {
       ml_out[2 * row] = m;
       ml_out[2 * row + 1] = l;
     }
   }
   __syncthreads();
-  // ---- O = P V : warp (mt, part) owns dims [part*D/4, (part+1)*D/4)
+  // ---- O = P V : warp w owns dims [w*D/4, (w+1)*D/4)
   {
     constexpr int NT = D / 32;
     float acc[NT][4];
@@ -387,11 +406,11 @@ __global__ void __launch_bounds__(512) attend_kernel(AttendParams p) {
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[nt][j] = 0.f;
-    const int d_base = part * (D / 4);
+    const int d_base = warp * (D / 4);
 #pragma unroll
     for (int kk = 0; kk < kKeysPerCta; kk += 16) {
       uint32_t a[4];
-      const __nv_bfloat16* pa = sP + (mt * 16 + g) * 72 + kk + 2 * t4;
+      const __nv_bfloat16* pa = sP + g * 72 + kk + 2 * t4;
       a[0] = *reinterpret_cast<const uint32_t*>(pa);
       a[1] = *reinterpret_cast<const uint32_t*>(pa + 8 * 72);
       a[2] = *reinterpret_cast<const uint32_t*>(pa + 8);
@@ -404,12 +423,12 @@ __global__ void __launch_bounds__(512) attend_kernel(AttendParams p) {
         mma_bf16_16816(acc[nt], a, b0, b1);
       }
     }
-    const int h0 = mt * 16 + g, h1 = h0 + 8;
+    const int h0 = g, h1 = g + 8;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int d = d_base + nt * 8 + 2 * t4;
-      if (h0 < p.heads) *reinterpret_cast<float2*>(o_out + 1ll * h0 * D + d) = make_float2(acc[nt][0], acc[nt][1]);
-      if (h1 < p.heads) *reinterpret_cast<float2*>(o_out + 1ll * h1 * D + d) = make_float2(acc[nt][2], acc[nt][3]);
+      if (h0 < n_heads) *reinterpret_cast<float2*>(o_out + 1ll * h0 * D + d) = make_float2(acc[nt][0], acc[nt][1]);
+      if (h1 < n_heads) *reinterpret_cast<float2*>(o_out + 1ll * h1 * D + d) = make_float2(acc[nt][2], acc[nt][3]);
     }
   }
 }
@@ -426,33 +445,45 @@ struct MergeParams {
   long long ldo;
 };
 
-// grid (heads, rows), 128 threads
+// grid (heads, rows), 128 threads; n_splits <= 32
 __global__ void __launch_bounds__(128) attend_merge_kernel(MergeParams p) {
+  __shared__ float s_w[32];
+  __shared__ float s_denom;
   const int h = blockIdx.x, r = blockIdx.y, tid = threadIdx.x;
-  const float sink = p.sink[h];
-  float m = sink;
-  for (int s = 0; s < p.n_splits; ++s) m = fmaxf(m, p.part_ml[((1ll * r * p.n_splits + s) * p.heads + h) * 2]);
-  float denom = __expf(sink - m);
-  for (int s = 0; s < p.n_splits; ++s) {
-    const float* ml = p.part_ml + ((1ll * r * p.n_splits + s) * p.heads + h) * 2;
-    if (ml[1] > 0.f) denom += ml[1] * __expf(ml[0] - m);
+  pdl_launch_dependents();
+  pdl_wait();
+  if (tid < 32) {
+    // one warp: all splits' (m, l) at once, then the combined max and denominator
+    const float sink = p.sink[h];
+    float m_s = -INFINITY, l_s = 0.f;
+    if (tid < p.n_splits) {
+      const float* ml = p.part_ml + ((1ll * r * p.n_splits + tid) * p.heads + h) * 2;
+      m_s = ml[0];
+      l_s = ml[1];
+    }
+    const float m = fmaxf(warp_max(l_s > 0.f ? m_s : -INFINITY), sink);
+    const float w = l_s > 0.f ? __expf(m_s - m) : 0.f;
+    const float denom = warp_sum(w * l_s) + __expf(sink - m);
+    s_w[tid] = w;
+    if (tid == 0) s_denom = denom;
   }
+  __syncthreads();
+  const float inv_denom = 1.0f / s_denom;
   const int pos = p.row_pos[r];
   const int rope0 = p.D - p.rope_dim;
   const bool live = p.row_slot[r] >= 0;
   for (int i = tid; i < p.D / 2; i += 128) {
     float a = 0.f, b = 0.f;
     for (int s = 0; s < p.n_splits; ++s) {
-      const float* ml = p.part_ml + ((1ll * r * p.n_splits + s) * p.heads + h) * 2;
-      if (ml[1] > 0.f) {
-        const float w = __expf(ml[0] - m);
+      const float w = s_w[s];
+      if (w > 0.f) {
         const float2 v = *reinterpret_cast<const float2*>(p.part_o + ((1ll * r * p.n_splits + s) * p.heads + h) * p.D + 2 * i);
         a = fmaf(w, v.x, a);
         b = fmaf(w, v.y, b);
       }
     }
-    a /= denom;
-    b /= denom;
+    a *= inv_denom;
+    b *= inv_denom;
     const int t = 2 * i - rope0;
     if (t >= 0) {
       float c, s;
@@ -467,29 +498,20 @@ __global__ void __launch_bounds__(128) attend_merge_kernel(MergeParams p) {
 }
 
 template <int D>
-static size_t attend_smem(int heads) {
-  const int n_mt = (heads + 15) / 16;
-  const int LD = D + 8;
-  return size_t(kKeysPerCta) * LD * 2 + size_t(16) * n_mt * LD * 2 + size_t(16) * n_mt * 65 * 4 +
-         size_t(16) * n_mt * 72 * 2 + 128 * 4 + 64 * 8 + 64;
-}
-
-template <int D>
 static cudaError_t launch_attend(const AttendParams& p, cudaStream_t stream) {
-  const int n_mt = (p.heads + 15) / 16;
-  const size_t smem = attend_smem<D>(p.heads);
-  static size_t configured[64] = {0};
+  constexpr int LD = D + 8;
+  constexpr size_t smem = size_t(kKeysPerCta) * LD * 2 + size_t(kHeadsPerCta) * LD * 2 + size_t(kHeadsPerCta) * 65 * 4 +
+                          size_t(kHeadsPerCta) * 72 * 2 + 128 * 4 + 64 * 8 + 64;
+  static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && configured[dev] < smem) {
-    cudaError_t e = cudaFuncSetAttribute(attend_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(attend_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return e;
-    configured[dev] = 200 * 1024;
+    configured[dev] = true;
   }
-  if (smem > 200 * 1024) return cudaErrorInvalidValue;
-  dim3 grid(p.n_splits, p.rows);
-  attend_kernel<D><<<grid, 128 * n_mt, smem, stream>>>(p);
-  return cudaGetLastError();
+  dim3 grid(p.n_splits, p.rows, (p.heads + kHeadsPerCta - 1) / kHeadsPerCta);
+  return launch_pdl(attend_kernel<D>, grid, dim3(128), smem, stream, p);
 }
 
 }  // namespace ds41
@@ -506,17 +528,14 @@ extern "C" int ds41_index_score(const void* q, long long ldq, int q_off, const f
                      row_slot, inv_freq_idx, rows, IH, ID, ratio, scores, max_keys};
   int bx = (max_keys + 7) / 8;
   if (bx > 256) bx = 256;
-  dim3 grid(bx, rows);
-  index_score_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(index_score_kernel, dim3(bx, rows), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
 }
 
 extern "C" int ds41_topk_select(const float* scores, int max_keys, const int* row_pos, const int* row_slot,
                                 int ratio, int k, int* sel, int* n_sel, int rows, void* stream) {
   if (rows <= 0 || k <= 0) return cudaErrorInvalidValue;
   TopkParams p{scores, max_keys, row_pos, row_slot, ratio, k, sel, n_sel};
-  topk_select_kernel<<<rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(topk_select_kernel, dim3(rows), dim3(1024), 0, static_cast<cudaStream_t>(stream), p);
 }
 
 extern "C" int ds41_attend(const void* q, long long ldq, int q_off, int rows, int heads, int D, int window, int ring,
@@ -525,7 +544,7 @@ extern "C" int ds41_attend(const void* q, long long ldq, int q_off, int rows, in
                            int page_rows, const float* inv_freq, int rope_dim, float scale, int n_splits,
                            const int* row_hi, float* part_o, float* part_ml, const float* sink, void* out,
                            long long ldo, void* stream) {
-  if (rows <= 0 || heads <= 0 || heads > 64 || rope_dim > 128 || (rope_dim & 1) || n_splits <= 0)
+  if (rows <= 0 || heads <= 0 || rope_dim > 128 || (rope_dim & 7) || n_splits <= 0 || n_splits > 32)
     return cudaErrorInvalidValue;
   AttendParams p{static_cast<const __nv_bfloat16*>(q), ldq, q_off, rows, heads, window, ring, row_pos, row_slot,
                  static_cast<const __nv_bfloat16*>(win), static_cast<const __nv_bfloat16*>(comp_pool), sel, n_sel, k,
@@ -538,7 +557,5 @@ extern "C" int ds41_attend(const void* q, long long ldq, int q_off, int rows, in
   if (e != cudaSuccess) return e;
   MergeParams m{part_o, part_ml, sink, row_pos, row_slot, inv_freq, rope_dim, heads, D, n_splits,
                 static_cast<__nv_bfloat16*>(out), ldo};
-  dim3 grid(heads, rows);
-  attend_merge_kernel<<<grid, 128, 0, s>>>(m);
-  return cudaGetLastError();
+  return launch_pdl(attend_merge_kernel, dim3(heads, rows), dim3(128), 0, s, m);
 }

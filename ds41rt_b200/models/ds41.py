@@ -473,12 +473,13 @@ class DS41Engine:
             lib.ptr(self.post), lib.ptr(self.comb), lib.ptr(fn), lib.ptr(self.hc_partial), rows, self.cfg.hidden,
             wait_flags, lib.ptr(self.epoch), lib.ptr(self.status), st), "hc_post_mix")
 
-    def _finish(self, rows, scale, base, pre_in, norm_w, next_pre, tap=None):
+    def _finish(self, rows, scale, base, pre_in, norm_w, next_pre, tap=None, quant=False):
         cfg = self.cfg
         self._ck(self.k.ds41_hc_finish(
             lib.ptr(self.hc_partial), self.n_slices, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
             lib.ptr(self.streams), lib.ptr(norm_w), lib.ptr(next_pre), lib.ptr(self.post), lib.ptr(self.comb),
-            lib.ptr(self.xn), lib.ptr(tap), rows, cfg.hidden, cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps),
+            lib.ptr(self.xn), lib.ptr(tap), lib.ptr(self.xq if quant else None),
+            lib.ptr(self.xq_sf if quant else None), rows, cfg.hidden, cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps),
             C.c_float(cfg.norm_eps), lib.stream()), "hc_finish")
 
     def _signal(self):
@@ -531,7 +532,7 @@ class DS41Engine:
                     "compress")
             nqb = lw.w_qb.shape[0]
             G.gemm_raw(lw.w_qb, self.q_lat, self.qb_out, nqb, R, Q, lda=Q, ldb=Q, ldo=self.nqb, out_mode=2,
-                       status=self.status)
+                       status=self.status, static_operand=1)
             self.launches += 1
             if lw.index_heads_cols and src is not None:
                 ratio = cfg.source_layers[src]
@@ -558,7 +559,7 @@ class DS41Engine:
             kg = cfg.heads_per_group * D
             G.gemm_raw(lw.wo_a, self.attn_out, self.oa, cfg.o_lora, R, kg, lda=kg, ldb=self.HL * D,
                        ldo=self.GL * cfg.o_lora, out_mode=2, batch=self.GL, a_batch_stride=cfg.o_lora * kg,
-                       b_batch_stride=kg, out_batch_stride=cfg.o_lora, status=self.status)
+                       b_batch_stride=kg, out_batch_stride=cfg.o_lora, status=self.status, static_operand=1)
             ko = self.GL * cfg.o_lora
             s_o = G.pick_splits(H, ko, max_splits=self.max_splits)
             G.linear_planes(self.oa[:R], lw.wo_b, self.planes_o.view(-1)[: s_o * R * H].view(s_o, R, H), s_o,
@@ -567,7 +568,8 @@ class DS41Engine:
             self._signal()
             self._post_mix(R, self._o_bases, self.world, s_o, R * H, lw.hc_ffn_fn, sync=True)
             # ---------------- MoE sublayer
-            self._finish(R, lw.hc_ffn_scale, lw.hc_ffn_base, self.pre[cur], lw.ffn_norm, self.pre[cur ^ 1])
+            self._finish(R, lw.hc_ffn_scale, lw.hc_ffn_base, self.pre[cur], lw.ffn_norm, self.pre[cur ^ 1],
+                         quant=self.mx)
             cur ^= 1
             ng = lw.w_gate_sh.shape[0]
             s_g = G.pick_splits(ng, H, max_splits=self.max_splits)
@@ -591,9 +593,6 @@ class DS41Engine:
             # FC1: act[slot][row][i] = swiglu(W1 x, W3 x) * route weight;  FC2: fc2[slot][row][h]
             if self.mx:
                 ra = (R + 127) // 128
-                self._ck(k.ds41_act_quant_mx(lib.ptr(self.xn), C.c_longlong(H), C.c_longlong(0), lib.ptr(self.xq),
-                                             C.c_longlong(H), C.c_longlong(0), lib.ptr(self.xq_sf), C.c_longlong(0),
-                                             R, H, 1, 128, lib.ptr(None), st()), "act_quant x")
                 G.gemm_raw(lw.w13, self.xq, self.act, I, R, H, lda=H, ldb=H, ldo=I, kind=2, out_mode=4, bn=bn,
                            batch=self.max_active, a_batches=EL, a_batch_stride=2 * I * H, out_batch_stride=R * I,
                            batch_map=self.active, n_active=self.n_active, b_batch_kind=1, up_row_offset=I,
@@ -639,7 +638,7 @@ class DS41Engine:
         cur = self._cur
         self._finish(rows, lw0.hc_attn_scale, lw0.hc_attn_base, self.pre[cur], self.w.final_norm, self.pre[cur ^ 1])
         G.gemm_raw(self.w.head, self.xn, self.logits, self.V_local, rows, cfg.hidden, lda=cfg.hidden, ldb=cfg.hidden,
-                   ldo=self.V_local, out_mode=3, status=self.status)
+                   ldo=self.V_local, out_mode=3, status=self.status, static_operand=1)
         self.launches += 1
         self._ck(k.ds41_argmax_rows(
             lib.ptr(self.logits), C.c_longlong(self.V_local), rows, self.V_local, self.rank * self.V_local,

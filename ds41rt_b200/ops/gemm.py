@@ -25,26 +25,23 @@ def pick_bn(rows: int) -> int:
     return 128
 
 
-def pick_splits(m: int, k: int, kind: int = 0, target_ctas: int = 120, max_splits: int = 16, n_tiles: int = 1,
+def pick_splits(m: int, k: int, kind: int = 0, max_ctas: int = 148, max_splits: int = 16, n_tiles: int = 1,
                 batch: int = 1) -> int:
-    """Smallest divisor of the K-block count that gives the grid at least `target_ctas` tiles."""
+    """Largest split-K factor that keeps the grid within one wave of `max_ctas` CTAs (no empty split)."""
     bk = 128 // _ELEM[kind]
     kb = (k + bk - 1) // bk
-    m_tiles = (m + 127) // 128
-    best = 1
-    for s in range(1, max_splits + 1):
-        if kb % s:
-            continue
-        best = s
-        if m_tiles * n_tiles * batch * s >= target_ctas:
-            break
-    return best
+    tiles = ((m + 127) // 128) * n_tiles * batch
+    s = max(1, min(max_splits, kb, max_ctas // max(tiles, 1)))
+    while s > 1 and (s - 1) * ((kb + s - 1) // s) >= kb:
+        s -= 1
+    return s
 
 
 def gemm_raw(A, B, out, M, N, K, *, lda, ldb, ldo, kind=0, out_mode=0, k_splits=1, bn=None, batch=1,
              a_batch_stride=0, b_batch_stride=0, out_batch_stride=0, a_batches=0, split_workspace=None,
              sfa=None, sfb=None, sfa_batch_stride=0, sfb_batch_stride=0, batch_map=None, n_active=None,
-             b_batch_kind=0, up_row_offset=0, row_w=None, row_w_ld=0, act_limit=10.0, status=None):
+             b_batch_kind=0, up_row_offset=0, row_w=None, row_w_ld=0, act_limit=10.0, status=None,
+             static_operand=0):
     a = lib.GemmArgs()
     a.A, a.B, a.out = lib.ptr(A), lib.ptr(B), lib.ptr(out)
     a.split_workspace = lib.ptr(split_workspace)
@@ -56,6 +53,7 @@ def gemm_raw(A, B, out, M, N, K, *, lda, ldb, ldo, kind=0, out_mode=0, k_splits=
     a.M, a.N, a.K, a.batch, a.a_batches = M, N, K, batch, a_batches
     a.kind, a.out_mode, a.k_splits, a.bn = kind, out_mode, k_splits, bn or pick_bn(N)
     a.b_batch_kind, a.up_row_offset, a.row_w_ld, a.act_limit = b_batch_kind, up_row_offset, row_w_ld, act_limit
+    a.static_operand = static_operand
     lib.check(lib.kernels().ds41_gemm_tc(C.byref(a), lib.stream()), "ds41_gemm_tc")
 
 
@@ -71,10 +69,10 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     f32 = out.dtype == torch.float32
     if rows <= 128:
         gemm_raw(w, x, out, N, rows, K, lda=w.stride(0), ldb=x.stride(0), ldo=out.stride(0),
-                 out_mode=3 if f32 else 2, status=status)
+                 out_mode=3 if f32 else 2, status=status, static_operand=1)
     else:
         gemm_raw(x, w, out, rows, N, K, lda=x.stride(0), ldb=w.stride(0), ldo=out.stride(0),
-                 out_mode=1 if f32 else 0, bn=256 if N >= 256 else 128, status=status)
+                 out_mode=1 if f32 else 0, bn=256 if N >= 256 else 128, status=status, static_operand=2)
     return out
 
 
@@ -84,7 +82,8 @@ def linear_planes(x: torch.Tensor, w: torch.Tensor, planes: torch.Tensor, splits
     N = w.shape[0]
     assert planes.dtype == torch.float32 and planes.is_contiguous()
     if splits == 1:
-        gemm_raw(w, x, planes, N, rows, K, lda=w.stride(0), ldb=x.stride(0), ldo=N, out_mode=3, status=status)
+        gemm_raw(w, x, planes, N, rows, K, lda=w.stride(0), ldb=x.stride(0), ldo=N, out_mode=3, status=status,
+                 static_operand=1)
     else:
         gemm_raw(w, x, None, N, rows, K, lda=w.stride(0), ldb=x.stride(0), ldo=N, out_mode=3, k_splits=splits,
-                 split_workspace=planes, status=status)
+                 split_workspace=planes, status=status, static_operand=1)

@@ -29,6 +29,7 @@ class GemmArgs(C.Structure):
         ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("batch", C.c_int), ("a_batches", C.c_int),
         ("kind", C.c_int), ("out_mode", C.c_int), ("k_splits", C.c_int), ("bn", C.c_int),
         ("b_batch_kind", C.c_int), ("up_row_offset", C.c_int), ("row_w_ld", C.c_int), ("act_limit", C.c_float),
+        ("static_operand", C.c_int),
     ]
 
 

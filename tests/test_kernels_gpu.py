@@ -127,7 +127,7 @@ def test_hc_kernels_match_oracle():
     xn_d = torch.zeros(rows, H, device="cuda", dtype=torch.bfloat16)
     lib.check(k.ds41_hc_finish(lib.ptr(partial), H // 128, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
                                lib.ptr(s_dev), lib.ptr(norm_w), lib.ptr(next_pre), lib.ptr(post), lib.ptr(comb),
-                               lib.ptr(xn_d), lib.ptr(None), rows, H, 20, C.c_float(1e-6), C.c_float(1e-20),
+                               lib.ptr(xn_d), lib.ptr(None), lib.ptr(None), lib.ptr(None), rows, H, 20, C.c_float(1e-6), C.c_float(1e-20),
                                lib.stream()), "finish")
     torch.cuda.synchronize()
     assert (s_dev.float().cpu() - new_streams).abs().max() < 0.05
