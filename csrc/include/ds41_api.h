@@ -60,6 +60,40 @@ int ds41_hc_finish(const float* partial, int n_slices, const float* scale, const
                    float* tap_mean, void* xq, void* xq_sf, int rows, int H, int iters, float hc_eps, float norm_eps,
                    void* stream);
 
+// Fused small-batch step (hc_step.cu): expand with the sublayer's partial planes, next mixes, collapse with the
+// known `pre_in`, RMSNorm (+ optional E4M3/scale-atom output) in one launch.  part_bases: HOST array of device
+// pointers; wait_flags: DEVICE array of peer flag pointers.  `tickets` [rows] must be zero before the first call.
+typedef struct ds41_hc_step_args {
+  const void* streams_in;
+  void* streams_out;
+  const float* const* part_bases;
+  const float* post;
+  const float* comb;
+  const float* pre_in;
+  const float* fn;
+  const float* scale;
+  const float* base;
+  const float* norm_w;
+  float* partial;        // [H/128][rows][26]
+  float* xc;             // [rows][H]
+  float* next_pre;
+  float* post_out;
+  float* comb_out;
+  void* xn;
+  float* tap_mean;
+  void* xq;
+  void* xq_sf;
+  unsigned int* tickets;
+  const uint32_t* const* wait_flags;
+  const uint32_t* wait_epoch;
+  int* status;
+  long long split_stride;
+  int n_ranks, n_splits;
+  int rows, H, iters;
+  float hc_eps, norm_eps;
+} ds41_hc_step_args;
+int ds41_hc_step(const ds41_hc_step_args* args, void* stream);
+
 // ---------------------------------------------------------------------------------------------------
 // Attention-side projections' epilogues and cache writes (attn_ops.cu)
 int ds41_qkv_post(const float* planes, int splits, int rows, int ntot, int Q, int D, int rope_dim, int extra_f32,

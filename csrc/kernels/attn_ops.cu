@@ -18,7 +18,7 @@ __device__ __forceinline__ void rope_cs(int pos, float inv_freq, float* c, float
   // reduce the angle in double so positions up to 2^20 keep fp32-accurate sin/cos
   const double a = static_cast<double>(pos) * static_cast<double>(inv_freq);
   const double two_pi = 6.283185307179586476925286766559;
-  const double red = a - floor(a / two_pi) * two_pi;
+  const double red = a - floor(a * 0.15915494309189533576888376337251) * two_pi;
   sincosf(static_cast<float>(red), s, c);
 }
 
@@ -69,6 +69,7 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostParams p) {
       const int c = tid + 256 * n;
       float a = 0.f;
       if (c < p.Q) {
+#pragma unroll 4
         for (int s = 0; s < p.splits; ++s) a += row0[s * plane + c];
         a = bf16_round(a);
       }
@@ -92,6 +93,7 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostParams p) {
     const int i = tid + 256 * n;
     float a = 0.f, b = 0.f;
     if (i < p.D / 2) {
+#pragma unroll 4
       for (int s = 0; s < p.splits; ++s) {
         const float2 v = *reinterpret_cast<const float2*>(row0 + s * plane + p.Q + 2 * i);
         a += v.x;

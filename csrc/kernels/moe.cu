@@ -44,6 +44,7 @@ __global__ void __launch_bounds__(512) router_select_kernel(RouterParams p) {
     // second block of the row: the shared expert's clamp-SwiGLU activation
     for (int i = tid; i < p.I_sh; i += 512) {
       float g = 0.f, u = 0.f;
+#pragma unroll 4
       for (int s = 0; s < p.splits; ++s) {
         g += row0[s * plane + p.E + i];
         u += row0[s * plane + p.E + p.I_sh + i];
@@ -56,6 +57,7 @@ __global__ void __launch_bounds__(512) router_select_kernel(RouterParams p) {
   }
   if (tid < p.E) {
     float a = 0.f;
+#pragma unroll 4
     for (int s = 0; s < p.splits; ++s) a += row0[s * plane + tid];
     const float sp = a > 20.f ? a : log1pf(__expf(a));
     const float sc = sqrtf(sp);

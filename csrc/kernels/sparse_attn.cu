@@ -19,7 +19,7 @@ namespace ds41 {
 __device__ __forceinline__ void rope_cs2(int pos, float inv_freq, float* c, float* s) {
   const double a = static_cast<double>(pos) * static_cast<double>(inv_freq);
   const double two_pi = 6.283185307179586476925286766559;
-  const double red = a - floor(a / two_pi) * two_pi;
+  const double red = a - floor(a * 0.15915494309189533576888376337251) * two_pi;
   sincosf(static_cast<float>(red), s, c);
 }
 

@@ -369,6 +369,11 @@ class DS41Engine:
         self.n_slices = H // 128
         self.hc_partial = z((self.n_slices, R, 25), F32)
         self.xn = z((R, H), BF16)
+        self.coef = [(z((R, 4), F32), z((R, 16), F32)), (z((R, 4), F32), z((R, 16), F32))]
+        self.step_partial = z((self.n_slices, R, 26), F32)
+        self.xc = z((R, H), F32)
+        self.tickets = z((R,), I32)
+        self.fused_rows = 16      # passes of at most this many rows use the fused hyper-connection step
         self.taps = z((3, R, H), F32) if cfg.dspark is not None else None
         # attention
         max_extra = max([lw.extra_cols for lw in weights.layers] + [0])
@@ -482,23 +487,58 @@ class DS41Engine:
             lib.ptr(self.xq_sf if quant else None), rows, cfg.hidden, cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps),
             C.c_float(cfg.norm_eps), lib.stream()), "hc_finish")
 
+    def _step(self, rows, part_bases, n_ranks, n_splits, split_stride, coef_in, pre_in, fn, scale, base, norm_w,
+              next_pre, coef_out, tap=None, quant=False, sync=False):
+        cfg = self.cfg
+        a = lib.HcStepArgs()
+        a.streams_in = a.streams_out = lib.ptr(self.streams)
+        a.part_bases = C.cast(part_bases, C.c_void_p) if part_bases is not None else None
+        a.post, a.comb = lib.ptr(coef_in[0]), lib.ptr(coef_in[1])
+        a.pre_in, a.fn, a.scale, a.base, a.norm_w = (lib.ptr(pre_in), lib.ptr(fn), lib.ptr(scale), lib.ptr(base),
+                                                     lib.ptr(norm_w))
+        a.partial, a.xc = lib.ptr(self.step_partial), lib.ptr(self.xc)
+        a.next_pre, a.post_out, a.comb_out = lib.ptr(next_pre), lib.ptr(coef_out[0]), lib.ptr(coef_out[1])
+        a.xn, a.tap_mean = lib.ptr(self.xn), lib.ptr(tap)
+        a.xq, a.xq_sf = lib.ptr(self.xq if quant else None), lib.ptr(self.xq_sf if quant else None)
+        a.tickets = lib.ptr(self.tickets)
+        a.wait_flags = lib.ptr(self.flag_ptrs) if (sync and self.world > 1) else None
+        a.wait_epoch, a.status = lib.ptr(self.epoch), lib.ptr(self.status)
+        a.split_stride, a.n_ranks, a.n_splits = split_stride, n_ranks, n_splits
+        a.rows, a.H, a.iters, a.hc_eps, a.norm_eps = rows, cfg.hidden, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.norm_eps
+        self._ck(self.k.ds41_hc_step(C.byref(a), lib.stream()), "hc_step")
+
     def _signal(self):
         if self.world > 1:
             self._ck(self.k.ds41_signal(lib.ptr(self.epoch), lib.ptr(self.flag), lib.stream()), "signal")
 
     # ------------------------------------------------------------------ one pass over `rows` rows
+    def _hc(self, rows, pending, fn, scale, base, norm_w, tap=None, quant=False):
+        """Close the pending sublayer (expand with its partial planes) and open the next one
+        (mixes -> collapse -> RMSNorm into self.xn).  One fused launch for small passes, two otherwise."""
+        cur = self._cur
+        bases, n_ranks, n_splits, stride = pending if pending is not None else (None, 0, 0, 0)
+        if rows <= self.fused_rows:
+            cc = self._ccur
+            self._step(rows, bases, n_ranks, n_splits, stride, self.coef[cc], self.pre[cur], fn, scale, base, norm_w,
+                       self.pre[cur ^ 1], self.coef[cc ^ 1], tap=tap, quant=quant, sync=pending is not None)
+            self._ccur = cc ^ 1
+        else:
+            self._post_mix(rows, bases, n_ranks, n_splits, stride, fn, sync=pending is not None)
+            self._finish(rows, scale, base, self.pre[cur], norm_w, self.pre[cur ^ 1], tap, quant)
+        self._cur = cur ^ 1
+
     def forward_rows(self, rows: int, *, embed: bool = True, head: bool = True, first_layer: int = 0,
                      last_layer: Optional[int] = None):
         cfg, k, st = self.cfg, self.k, lib.stream
         H, D, Q = cfg.hidden, cfg.head_dim, cfg.q_lora
         R = rows
         last_layer = self.n_layers if last_layer is None else last_layer
-        cur = 0
         if embed:
+            self._cur, self._ccur = 0, 0
             self._ck(k.ds41_embed_streams(lib.ptr(self.in_tokens), lib.ptr(self.w.embed), lib.ptr(self.streams),
                                           lib.ptr(self.pre[0]), R, H, cfg.hc_mult, cfg.vocab, st()), "embed")
-        if first_layer < last_layer:
-            self._post_mix(R, None, 0, 0, 0, self.w.layers[first_layer].hc_attn_fn, sync=False)
+        pending = None
+        fused = R <= self.fused_rows
         tap_i = 0
         for l in range(first_layer, last_layer):
             lw = self.w.layers[l]
@@ -509,8 +549,7 @@ class DS41Engine:
                     and l in cfg.dspark.tap_layers and tap_i < self.taps.shape[0]:
                 tap = self.taps[tap_i]
                 tap_i += 1
-            self._finish(R, lw.hc_attn_scale, lw.hc_attn_base, self.pre[cur], lw.attn_norm, self.pre[cur ^ 1], tap)
-            cur ^= 1
+            self._hc(R, pending, lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, lw.attn_norm, tap=tap)
             ntot = lw.w_qkv.shape[0]
             s_qkv = G.pick_splits(ntot, H, max_splits=self.max_splits)
             G.linear_planes(self.xn[:R], lw.w_qkv, self.planes_qkv.view(-1)[: s_qkv * R * ntot].view(s_qkv, R, ntot),
@@ -566,11 +605,9 @@ class DS41Engine:
                             status=self.status)
             self.launches += 2
             self._signal()
-            self._post_mix(R, self._o_bases, self.world, s_o, R * H, lw.hc_ffn_fn, sync=True)
+            pending = (self._o_bases, self.world, s_o, R * H)
             # ---------------- MoE sublayer
-            self._finish(R, lw.hc_ffn_scale, lw.hc_ffn_base, self.pre[cur], lw.ffn_norm, self.pre[cur ^ 1],
-                         quant=self.mx)
-            cur ^= 1
+            self._hc(R, pending, lw.hc_ffn_fn, lw.hc_ffn_scale, lw.hc_ffn_base, lw.ffn_norm, quant=self.mx)
             ng = lw.w_gate_sh.shape[0]
             s_g = G.pick_splits(ng, H, max_splits=self.max_splits)
             G.linear_planes(self.xn[:R], lw.w_gate_sh, self.planes_gate.view(-1)[: s_g * R * ng].view(s_g, R, ng),
@@ -625,9 +662,8 @@ class DS41Engine:
             self._ck(k.ds41_moe_combine(lib.ptr(self.fc2), lib.ptr(self.slot_of), lib.ptr(self.planes_shared), s_s,
                                         R, lw.topk, H, lib.ptr(self.moe_plane), st()), "moe_combine")
             self._signal()
-            nxt = self.w.layers[l + 1].hc_attn_fn if l + 1 < self.n_layers else self.w.layers[0].hc_attn_fn
-            self._post_mix(R, self._moe_bases, self.world, 1, 0, nxt, sync=True)
-        self._cur = cur
+            pending = (self._moe_bases, self.world, 1, 0)
+        self._pending = pending
         if head:
             self.head_rows(R)
 
@@ -635,8 +671,9 @@ class DS41Engine:
         """collapse -> final norm -> vocabulary shard GEMM -> greedy candidate (+ cross-rank merge)."""
         cfg, k, st = self.cfg, self.k, lib.stream
         lw0 = self.w.layers[0]
-        cur = self._cur
-        self._finish(rows, lw0.hc_attn_scale, lw0.hc_attn_base, self.pre[cur], self.w.final_norm, self.pre[cur ^ 1])
+        self._hc(rows, getattr(self, "_pending", None), lw0.hc_attn_fn, lw0.hc_attn_scale, lw0.hc_attn_base,
+                 self.w.final_norm)
+        self._pending = None
         G.gemm_raw(self.w.head, self.xn, self.logits, self.V_local, rows, cfg.hidden, lda=cfg.hidden, ldb=cfg.hidden,
                    ldo=self.V_local, out_mode=3, status=self.status, static_operand=1)
         self.launches += 1

@@ -33,6 +33,19 @@ class GemmArgs(C.Structure):
     ]
 
 
+class HcStepArgs(C.Structure):
+    _fields_ = [
+        ("streams_in", C.c_void_p), ("streams_out", C.c_void_p), ("part_bases", C.c_void_p), ("post", C.c_void_p),
+        ("comb", C.c_void_p), ("pre_in", C.c_void_p), ("fn", C.c_void_p), ("scale", C.c_void_p),
+        ("base", C.c_void_p), ("norm_w", C.c_void_p), ("partial", C.c_void_p), ("xc", C.c_void_p),
+        ("next_pre", C.c_void_p), ("post_out", C.c_void_p), ("comb_out", C.c_void_p), ("xn", C.c_void_p),
+        ("tap_mean", C.c_void_p), ("xq", C.c_void_p), ("xq_sf", C.c_void_p), ("tickets", C.c_void_p),
+        ("wait_flags", C.c_void_p), ("wait_epoch", C.c_void_p), ("status", C.c_void_p),
+        ("split_stride", C.c_longlong), ("n_ranks", C.c_int), ("n_splits", C.c_int),
+        ("rows", C.c_int), ("H", C.c_int), ("iters", C.c_int), ("hc_eps", C.c_float), ("norm_eps", C.c_float),
+    ]
+
+
 def _load(name: str, builder: str):
     path = _LIBDIR / name
     if not path.exists() or os.environ.get("DS41_REBUILD"):
@@ -63,7 +76,7 @@ def dir_functions():
         "ds41_gemm_tc", "ds41_embed_streams", "ds41_hc_post_mix", "ds41_hc_finish", "ds41_qkv_post",
         "ds41_compress", "ds41_index_score", "ds41_topk_select", "ds41_attend", "ds41_router_select",
         "ds41_moe_plan", "ds41_moe_combine", "ds41_signal", "ds41_reduce_planes", "ds41_argmax_rows",
-        "ds41_argmax_merge", "ds41_spec_accept", "ds41_act_quant_mx", "ds41_decode_feedback",
+        "ds41_argmax_merge", "ds41_spec_accept", "ds41_act_quant_mx", "ds41_decode_feedback", "ds41_hc_step",
     ]
 
 

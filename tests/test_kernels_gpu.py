@@ -203,3 +203,66 @@ def test_act_quant_mx(group):
     got_e = unpack_sf_atoms(sf.cpu(), rows)
     assert torch.equal(got_e, we)
     assert torch.equal(q.cpu().view(torch.float8_e4m3fn).float(), wq.float())
+
+
+def test_hc_step_matches_unfused_kernels():
+    """The fused hyper-connection step equals post_mix + finish run separately (same inputs)."""
+    from ds41rt_b200.ops import lib
+    k = lib.kernels()
+    torch.manual_seed(1)
+    rows, H = 3, 1024
+    streams = torch.randn(rows, 4, H, device="cuda").bfloat16()
+    sub = torch.randn(2, rows, H, device="cuda")
+    fn = torch.randn(24, 4 * H, device="cuda") * 0.02
+    scale = torch.tensor([1.0, 0.7, 1.3], device="cuda")
+    base = torch.randn(24, device="cuda") * 0.5
+    pre_in = torch.rand(rows, 4, device="cuda")
+    post = torch.rand(rows, 4, device="cuda") * 2
+    comb = torch.rand(rows, 16, device="cuda")
+    norm_w = torch.rand(H, device="cuda") + 0.5
+    st = lib.new_status("cuda")
+    bases = (C.c_void_p * 1)(sub.data_ptr())
+    # unfused
+    s1 = streams.clone()
+    partial = torch.zeros(H // 128, rows, 25, device="cuda")
+    lib.check(k.ds41_hc_post_mix(lib.ptr(s1), lib.ptr(s1), bases, 1, 2, C.c_longlong(rows * H), lib.ptr(post),
+                                 lib.ptr(comb), lib.ptr(fn), lib.ptr(partial), rows, H, lib.ptr(None), lib.ptr(None),
+                                 lib.ptr(st), lib.stream()), "post_mix")
+    np1, po1, co1 = torch.zeros(rows, 4, device="cuda"), torch.zeros(rows, 4, device="cuda"), torch.zeros(rows, 16, device="cuda")
+    xn1 = torch.zeros(rows, H, device="cuda", dtype=torch.bfloat16)
+    lib.check(k.ds41_hc_finish(lib.ptr(partial), H // 128, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
+                               lib.ptr(s1), lib.ptr(norm_w), lib.ptr(np1), lib.ptr(po1), lib.ptr(co1), lib.ptr(xn1),
+                               lib.ptr(None), lib.ptr(None), lib.ptr(None), rows, H, 20, C.c_float(1e-6),
+                               C.c_float(1e-20), lib.stream()), "finish")
+    # fused (run twice: the ticket counters must reset themselves)
+    for _ in range(2):
+        s2 = streams.clone()
+        a = lib.HcStepArgs()
+        np2, po2, co2 = torch.zeros(rows, 4, device="cuda"), torch.zeros(rows, 4, device="cuda"), torch.zeros(rows, 16, device="cuda")
+        xn2 = torch.zeros(rows, H, device="cuda", dtype=torch.bfloat16)
+        xq = torch.zeros(rows, H, device="cuda", dtype=torch.uint8)
+        xq_sf = torch.zeros(1, H // 128, 512, device="cuda", dtype=torch.uint8)
+        if _ == 0:
+            tickets = torch.zeros(rows, dtype=torch.int32, device="cuda")
+        part2 = torch.zeros(H // 128, rows, 26, device="cuda")
+        xc = torch.zeros(rows, H, device="cuda")
+        a.streams_in = a.streams_out = lib.ptr(s2)
+        a.part_bases = C.cast(bases, C.c_void_p)
+        a.post, a.comb, a.pre_in = lib.ptr(post), lib.ptr(comb), lib.ptr(pre_in)
+        a.fn, a.scale, a.base, a.norm_w = lib.ptr(fn), lib.ptr(scale), lib.ptr(base), lib.ptr(norm_w)
+        a.partial, a.xc = lib.ptr(part2), lib.ptr(xc)
+        a.next_pre, a.post_out, a.comb_out, a.xn = lib.ptr(np2), lib.ptr(po2), lib.ptr(co2), lib.ptr(xn2)
+        a.xq, a.xq_sf, a.tickets, a.status = lib.ptr(xq), lib.ptr(xq_sf), lib.ptr(tickets), lib.ptr(st)
+        a.split_stride, a.n_ranks, a.n_splits = rows * H, 1, 2
+        a.rows, a.H, a.iters, a.hc_eps, a.norm_eps = rows, H, 20, 1e-6, 1e-20
+        lib.check(k.ds41_hc_step(C.byref(a), lib.stream()), "hc_step")
+        torch.cuda.synchronize()
+        assert torch.equal(s1, s2)
+        assert (np1 - np2).abs().max() < 1e-5 and (po1 - po2).abs().max() < 1e-5 and (co1 - co2).abs().max() < 1e-5
+        assert (xn1.float() - xn2.float()).abs().max() < 2e-2
+        assert int(tickets.abs().sum()) == 0
+    from ds41rt_b200.ops import quant_ref as Q
+    from ds41rt_b200.ops.mx import unpack_sf_atoms
+    wq, we = Q.quant_act_fp8_ue8m0(xn2.float().cpu(), 128)
+    assert torch.equal(unpack_sf_atoms(xq_sf.cpu(), rows), we)
+    assert torch.equal(xq.cpu().view(torch.float8_e4m3fn).float(), wq.float())
