@@ -443,6 +443,7 @@ class DS41Engine:
         self.inv_idx = torch.tensor(rope_inv_freq(cfg.rope_long, cfg.index_dim // 2), dtype=F32, device=dev)
         self.layer_prefix_plain = False   # drafter blocks use the plain rope
         self.launches = 0
+        self.only = None
         self.debug = None   # set to a list to record per-layer routing / selection decisions
 
     # ------------------------------------------------------------------ helpers
@@ -451,9 +452,14 @@ class DS41Engine:
             return self.inv_plain
         return self.inv_long
 
-    def _ck(self, err, what):
+    def _run(self, tag, fn, *args, **kw):
+        """Launch one kernel; `self.only` (a set of tags) restricts a pass to some kernels for profiling."""
+        if self.only is not None and tag not in self.only:
+            return
         self.launches += 1
-        lib.check(err, what)
+        err = fn(*args, **kw)
+        if err is not None:
+            lib.check(err, tag)
 
     def set_rows(self, tokens, positions, slots, row_hi=None):
         """Host -> device copy of one pass's inputs (lists or CPU tensors)."""
@@ -473,19 +479,19 @@ class DS41Engine:
     def _post_mix(self, rows, part_bases, n_ranks, n_splits, split_stride, fn, sync):
         k, st = self.k, lib.stream()
         wait_flags = lib.ptr(self.flag_ptrs) if (sync and self.world > 1) else lib.ptr(None)
-        self._ck(k.ds41_hc_post_mix(
+        self._run("hc_post_mix", k.ds41_hc_post_mix, 
             lib.ptr(self.streams), lib.ptr(self.streams), part_bases, n_ranks, n_splits, C.c_longlong(split_stride),
             lib.ptr(self.post), lib.ptr(self.comb), lib.ptr(fn), lib.ptr(self.hc_partial), rows, self.cfg.hidden,
-            wait_flags, lib.ptr(self.epoch), lib.ptr(self.status), st), "hc_post_mix")
+            wait_flags, lib.ptr(self.epoch), lib.ptr(self.status), st)
 
     def _finish(self, rows, scale, base, pre_in, norm_w, next_pre, tap=None, quant=False):
         cfg = self.cfg
-        self._ck(self.k.ds41_hc_finish(
+        self._run("hc_finish", self.k.ds41_hc_finish, 
             lib.ptr(self.hc_partial), self.n_slices, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
             lib.ptr(self.streams), lib.ptr(norm_w), lib.ptr(next_pre), lib.ptr(self.post), lib.ptr(self.comb),
             lib.ptr(self.xn), lib.ptr(tap), lib.ptr(self.xq if quant else None),
             lib.ptr(self.xq_sf if quant else None), rows, cfg.hidden, cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps),
-            C.c_float(cfg.norm_eps), lib.stream()), "hc_finish")
+            C.c_float(cfg.norm_eps), lib.stream())
 
     def _step(self, rows, part_bases, n_ranks, n_splits, split_stride, coef_in, pre_in, fn, scale, base, norm_w,
               next_pre, coef_out, tap=None, quant=False, sync=False):
@@ -505,11 +511,11 @@ class DS41Engine:
         a.wait_epoch, a.status = lib.ptr(self.epoch), lib.ptr(self.status)
         a.split_stride, a.n_ranks, a.n_splits = split_stride, n_ranks, n_splits
         a.rows, a.H, a.iters, a.hc_eps, a.norm_eps = rows, cfg.hidden, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.norm_eps
-        self._ck(self.k.ds41_hc_step(C.byref(a), lib.stream()), "hc_step")
+        self._run("hc_step", self.k.ds41_hc_step, C.byref(a), lib.stream())
 
     def _signal(self):
         if self.world > 1:
-            self._ck(self.k.ds41_signal(lib.ptr(self.epoch), lib.ptr(self.flag), lib.stream()), "signal")
+            self._run("signal", self.k.ds41_signal, lib.ptr(self.epoch), lib.ptr(self.flag), lib.stream())
 
     # ------------------------------------------------------------------ one pass over `rows` rows
     def _hc(self, rows, pending, fn, scale, base, norm_w, tap=None, quant=False):
@@ -535,8 +541,8 @@ class DS41Engine:
         last_layer = self.n_layers if last_layer is None else last_layer
         if embed:
             self._cur, self._ccur = 0, 0
-            self._ck(k.ds41_embed_streams(lib.ptr(self.in_tokens), lib.ptr(self.w.embed), lib.ptr(self.streams),
-                                          lib.ptr(self.pre[0]), R, H, cfg.hc_mult, cfg.vocab, st()), "embed")
+            self._run("embed", k.ds41_embed_streams, lib.ptr(self.in_tokens), lib.ptr(self.w.embed), lib.ptr(self.streams),
+                                          lib.ptr(self.pre[0]), R, H, cfg.hc_mult, cfg.vocab, st())
         pending = None
         fused = R <= self.fused_rows
         tap_i = 0
@@ -552,115 +558,107 @@ class DS41Engine:
             self._hc(R, pending, lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, lw.attn_norm, tap=tap)
             ntot = lw.w_qkv.shape[0]
             s_qkv = G.pick_splits(ntot, H, max_splits=self.max_splits)
-            G.linear_planes(self.xn[:R], lw.w_qkv, self.planes_qkv.view(-1)[: s_qkv * R * ntot].view(s_qkv, R, ntot),
+            self._run("gemm_qkv", G.linear_planes, self.xn[:R], lw.w_qkv, self.planes_qkv.view(-1)[: s_qkv * R * ntot].view(s_qkv, R, ntot),
                             s_qkv, status=self.status)
-            self.launches += 1
-            self._ck(k.ds41_qkv_post(
+            self._run("qkv_post", k.ds41_qkv_post, 
                 lib.ptr(self.planes_qkv), s_qkv, R, ntot, Q, D, cfg.rope_dim, lw.extra_cols, lw.index_heads_cols,
                 C.c_float(cfg.index_weight_scale), lib.ptr(lw.q_norm), lib.ptr(lw.kv_norm), lib.ptr(inv),
                 lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.q_lat), lib.ptr(self.cache.win[l]),
-                self.cache.ring, lib.ptr(self.extras), C.c_float(cfg.norm_eps), st()), "qkv_post")
+                self.cache.ring, lib.ptr(self.extras), C.c_float(cfg.norm_eps), st())
             src = None if self.layer_prefix_plain else cfg.source_of(l)
             if lw.ratio:
-                self._ck(k.ds41_compress(
+                self._run("compress", k.ds41_compress, 
                     lib.ptr(self.extras), lw.extra_cols, R, D, cfg.index_dim, cfg.rope_dim, lw.ratio,
                     lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.cache.pending.get(l)),
                     lib.ptr(lw.comp_norm), lib.ptr(lw.wk_idx), lib.ptr(lw.k_norm), lib.ptr(inv), lib.ptr(self.inv_idx),
                     lib.ptr(self.cache.page_table), self.cache.max_pages, self.cache.page_rows[l],
-                    lib.ptr(self.cache.comp[l]), lib.ptr(self.cache.idx[l]), C.c_float(cfg.norm_eps), st()),
-                    "compress")
+                    lib.ptr(self.cache.comp[l]), lib.ptr(self.cache.idx[l]), C.c_float(cfg.norm_eps), st())
             nqb = lw.w_qb.shape[0]
-            G.gemm_raw(lw.w_qb, self.q_lat, self.qb_out, nqb, R, Q, lda=Q, ldb=Q, ldo=self.nqb, out_mode=2,
+            self._run("gemm_qb", G.gemm_raw, lw.w_qb, self.q_lat, self.qb_out, nqb, R, Q, lda=Q, ldb=Q, ldo=self.nqb, out_mode=2,
                        status=self.status, static_operand=1)
-            self.launches += 1
             if lw.index_heads_cols and src is not None:
                 ratio = cfg.source_layers[src]
-                self._ck(k.ds41_index_score(
+                self._run("index_score", k.ds41_index_score, 
                     lib.ptr(self.qb_out), C.c_longlong(self.nqb), self.HL * D, lib.ptr(self.extras), lw.extra_cols,
                     lw.extra_cols - cfg.index_heads, lib.ptr(self.cache.idx[src]), lib.ptr(self.cache.page_table),
                     self.cache.max_pages, self.cache.page_rows[src], lib.ptr(self.row_pos), lib.ptr(self.row_slot),
                     lib.ptr(self.inv_idx), R, cfg.index_heads, cfg.index_dim, ratio, lib.ptr(self.scores),
-                    self.max_keys, st()), "index_score")
-                self._ck(k.ds41_topk_select(lib.ptr(self.scores), self.max_keys, lib.ptr(self.row_pos),
+                    self.max_keys, st())
+                self._run("topk", k.ds41_topk_select, lib.ptr(self.scores), self.max_keys, lib.ptr(self.row_pos),
                                             lib.ptr(self.row_slot), ratio, cfg.index_topk, lib.ptr(self.sel),
-                                            lib.ptr(self.n_sel), R, st()), "topk")
-            self._ck(k.ds41_attend(
+                                            lib.ptr(self.n_sel), R, st())
+            self._run("attend", k.ds41_attend, 
                 lib.ptr(self.qb_out), C.c_longlong(self.nqb), 0, R, self.HL, D, cfg.window, self.cache.ring,
                 lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.cache.win[l]),
                 lib.ptr(self.cache.comp[src]) if src is not None else lib.ptr(None),
                 lib.ptr(self.sel), lib.ptr(self.n_sel), cfg.index_topk, lib.ptr(self.cache.page_table),
                 self.cache.max_pages, self.cache.page_rows[src] if src is not None else 1, lib.ptr(inv), cfg.rope_dim,
                 C.c_float(cfg.softmax_scale), self.n_splits_attn, lib.ptr(self.row_hi), lib.ptr(self.part_o),
-                lib.ptr(self.part_ml), lib.ptr(lw.sink), lib.ptr(self.attn_out), C.c_longlong(self.HL * D), st()),
-                "attend")
-            self.launches += 1
+                lib.ptr(self.part_ml), lib.ptr(lw.sink), lib.ptr(self.attn_out), C.c_longlong(self.HL * D), st())
             # grouped wo_a: batch = local groups
             kg = cfg.heads_per_group * D
-            G.gemm_raw(lw.wo_a, self.attn_out, self.oa, cfg.o_lora, R, kg, lda=kg, ldb=self.HL * D,
+            self._run("gemm_wo_a", G.gemm_raw, lw.wo_a, self.attn_out, self.oa, cfg.o_lora, R, kg, lda=kg, ldb=self.HL * D,
                        ldo=self.GL * cfg.o_lora, out_mode=2, batch=self.GL, a_batch_stride=cfg.o_lora * kg,
                        b_batch_stride=kg, out_batch_stride=cfg.o_lora, status=self.status, static_operand=1)
             ko = self.GL * cfg.o_lora
             s_o = G.pick_splits(H, ko, max_splits=self.max_splits)
-            G.linear_planes(self.oa[:R], lw.wo_b, self.planes_o.view(-1)[: s_o * R * H].view(s_o, R, H), s_o,
+            self._run("gemm_wo_b", G.linear_planes, self.oa[:R], lw.wo_b, self.planes_o.view(-1)[: s_o * R * H].view(s_o, R, H), s_o,
                             status=self.status)
-            self.launches += 2
             self._signal()
             pending = (self._o_bases, self.world, s_o, R * H)
             # ---------------- MoE sublayer
             self._hc(R, pending, lw.hc_ffn_fn, lw.hc_ffn_scale, lw.hc_ffn_base, lw.ffn_norm, quant=self.mx)
             ng = lw.w_gate_sh.shape[0]
             s_g = G.pick_splits(ng, H, max_splits=self.max_splits)
-            G.linear_planes(self.xn[:R], lw.w_gate_sh, self.planes_gate.view(-1)[: s_g * R * ng].view(s_g, R, ng),
+            self._run("gemm_gate", G.linear_planes, self.xn[:R], lw.w_gate_sh, self.planes_gate.view(-1)[: s_g * R * ng].view(s_g, R, ng),
                             s_g, status=self.status)
-            self.launches += 1
-            self._ck(k.ds41_router_select(
+            self._run("router_select", k.ds41_router_select, 
                 lib.ptr(self.planes_gate), s_g, R, ng, lw.n_experts, self.I_sh, lw.topk, lib.ptr(lw.gate_bias),
                 C.c_float(cfg.route_scale), C.c_float(cfg.swiglu_limit), lib.ptr(self.ids), lib.ptr(self.route_w),
-                lib.ptr(self.shared_act), st()), "router_select")
+                lib.ptr(self.shared_act), st())
             if self.debug is not None:
                 self.debug.append({"layer": l, "ids": self.ids[:R].clone(), "sel": self.sel[:R].clone(),
                                    "n_sel": self.n_sel[:R].clone()})
             EL = lw.n_experts // self.world
-            self._ck(k.ds41_moe_plan(
+            self._run("moe_plan", k.ds41_moe_plan, 
                 lib.ptr(self.ids), lib.ptr(self.route_w), lib.ptr(self.row_slot), R, lw.topk, self.rank * EL,
                 (self.rank + 1) * EL, self.max_active, self.max_rows, lib.ptr(self.active), lib.ptr(self.n_active),
-                lib.ptr(self.row_w), lib.ptr(self.slot_of), st()), "moe_plan")
+                lib.ptr(self.row_w), lib.ptr(self.slot_of), st())
             I = cfg.inter
             bn = G.pick_bn(R)
             # FC1: act[slot][row][i] = swiglu(W1 x, W3 x) * route weight;  FC2: fc2[slot][row][h]
             if self.mx:
                 ra = (R + 127) // 128
-                G.gemm_raw(lw.w13, self.xq, self.act, I, R, H, lda=H, ldb=H, ldo=I, kind=2, out_mode=4, bn=bn,
+                self._run("gemm_fc1", G.gemm_raw, lw.w13, self.xq, self.act, I, R, H, lda=H, ldb=H, ldo=I, kind=2, out_mode=4, bn=bn,
                            batch=self.max_active, a_batches=EL, a_batch_stride=2 * I * H, out_batch_stride=R * I,
                            batch_map=self.active, n_active=self.n_active, b_batch_kind=1, up_row_offset=I,
                            row_w=self.row_w, row_w_ld=self.max_rows, act_limit=cfg.swiglu_limit,
                            sfa=lw.w13_sf, sfa_batch_stride=lw.w13_sf[0].numel(), sfb=self.xq_sf, status=self.status)
                 sf_slot = ra * (I // 128) * 512
-                self._ck(k.ds41_act_quant_mx(lib.ptr(self.act), C.c_longlong(I), C.c_longlong(R * I),
+                self._run("act_quant act", k.ds41_act_quant_mx, lib.ptr(self.act), C.c_longlong(I), C.c_longlong(R * I),
                                              lib.ptr(self.actq), C.c_longlong(I), C.c_longlong(R * I),
                                              lib.ptr(self.actq_sf), C.c_longlong(sf_slot), R, I, self.max_active, 128,
-                                             lib.ptr(self.n_active), st()), "act_quant act")
-                G.gemm_raw(lw.w2, self.actq, self.fc2, H, R, I, lda=I, ldb=I, ldo=H, kind=2, out_mode=5, bn=bn,
+                                             lib.ptr(self.n_active), st())
+                self._run("gemm_fc2", G.gemm_raw, lw.w2, self.actq, self.fc2, H, R, I, lda=I, ldb=I, ldo=H, kind=2, out_mode=5, bn=bn,
                            batch=self.max_active, a_batches=EL, a_batch_stride=H * I, b_batch_stride=R * I,
                            out_batch_stride=R * H, batch_map=self.active, n_active=self.n_active, b_batch_kind=2,
                            row_w=self.row_w, row_w_ld=self.max_rows, sfa=lw.w2_sf,
                            sfa_batch_stride=lw.w2_sf[0].numel(), sfb=self.actq_sf, sfb_batch_stride=sf_slot,
                            status=self.status)
             else:
-                G.gemm_raw(lw.w13, self.xn, self.act, I, R, H, lda=H, ldb=H, ldo=I, out_mode=4, bn=bn,
+                self._run("gemm_fc1", G.gemm_raw, lw.w13, self.xn, self.act, I, R, H, lda=H, ldb=H, ldo=I, out_mode=4, bn=bn,
                            batch=self.max_active, a_batches=EL, a_batch_stride=2 * I * H, out_batch_stride=R * I,
                            batch_map=self.active, n_active=self.n_active, b_batch_kind=1, up_row_offset=I,
                            row_w=self.row_w, row_w_ld=self.max_rows, act_limit=cfg.swiglu_limit, status=self.status)
-                G.gemm_raw(lw.w2, self.act, self.fc2, H, R, I, lda=I, ldb=I, ldo=H, out_mode=5, bn=bn,
+                self._run("gemm_fc2", G.gemm_raw, lw.w2, self.act, self.fc2, H, R, I, lda=I, ldb=I, ldo=H, out_mode=5, bn=bn,
                            batch=self.max_active, a_batches=EL, a_batch_stride=H * I, b_batch_stride=R * I,
                            out_batch_stride=R * H, batch_map=self.active, n_active=self.n_active, b_batch_kind=2,
                            row_w=self.row_w, row_w_ld=self.max_rows, status=self.status)
             s_s = G.pick_splits(H, self.I_sh, max_splits=self.max_splits)
-            G.linear_planes(self.shared_act[:R], lw.w2_sh,
+            self._run("gemm_shared_down", G.linear_planes, self.shared_act[:R], lw.w2_sh,
                             self.planes_shared.view(-1)[: s_s * R * H].view(s_s, R, H), s_s, status=self.status)
-            self.launches += 3
-            self._ck(k.ds41_moe_combine(lib.ptr(self.fc2), lib.ptr(self.slot_of), lib.ptr(self.planes_shared), s_s,
-                                        R, lw.topk, H, lib.ptr(self.moe_plane), st()), "moe_combine")
+            self._run("moe_combine", k.ds41_moe_combine, lib.ptr(self.fc2), lib.ptr(self.slot_of), lib.ptr(self.planes_shared), s_s,
+                                        R, lw.topk, H, lib.ptr(self.moe_plane), st())
             self._signal()
             pending = (self._moe_bases, self.world, 1, 0)
         self._pending = pending
@@ -674,17 +672,16 @@ class DS41Engine:
         self._hc(rows, getattr(self, "_pending", None), lw0.hc_attn_fn, lw0.hc_attn_scale, lw0.hc_attn_base,
                  self.w.final_norm)
         self._pending = None
-        G.gemm_raw(self.w.head, self.xn, self.logits, self.V_local, rows, cfg.hidden, lda=cfg.hidden, ldb=cfg.hidden,
+        self._run("gemm_head", G.gemm_raw, self.w.head, self.xn, self.logits, self.V_local, rows, cfg.hidden, lda=cfg.hidden, ldb=cfg.hidden,
                    ldo=self.V_local, out_mode=3, status=self.status, static_operand=1)
-        self.launches += 1
-        self._ck(k.ds41_argmax_rows(
+        self._run("argmax_rows", k.ds41_argmax_rows, 
             lib.ptr(self.logits), C.c_longlong(self.V_local), rows, self.V_local, self.rank * self.V_local,
             lib.ptr(mask), 0 if mask is None else mask.shape[-1], lib.ptr(self.best_val), lib.ptr(self.best_idx),
-            lib.ptr(None), st()), "argmax_rows")
+            lib.ptr(None), st())
         self._signal()
         wait_flags = lib.ptr(self.flag_ptrs) if self.world > 1 else lib.ptr(None)
-        self._ck(k.ds41_argmax_merge(self._val_ptrs, self._idx_ptrs, self.world, rows, lib.ptr(self.chosen),
-                                     wait_flags, lib.ptr(self.epoch), lib.ptr(self.status), st()), "argmax_merge")
+        self._run("argmax_merge", k.ds41_argmax_merge, self._val_ptrs, self._idx_ptrs, self.world, rows, lib.ptr(self.chosen),
+                                     wait_flags, lib.ptr(self.epoch), lib.ptr(self.status), st())
 
     # ------------------------------------------------------------------ convenience drivers
     def prefill(self, slot: int, tokens: List[int], start: int = 0, chunk: Optional[int] = None) -> int:

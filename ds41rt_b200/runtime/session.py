@@ -38,8 +38,8 @@ class DecodeSession:
     def _enqueue(self, rows: int, feedback: bool):
         self.e.forward_rows(rows)
         if feedback:
-            self.e._ck(self.e.k.ds41_decode_feedback(lib.ptr(self.e.chosen), lib.ptr(self.e.in_tokens),
-                                                     lib.ptr(self.e.row_pos), rows, lib.stream()), "feedback")
+            self.e._run("feedback", self.e.k.ds41_decode_feedback, lib.ptr(self.e.chosen), lib.ptr(self.e.in_tokens),
+                        lib.ptr(self.e.row_pos), rows, lib.stream())
 
     def graph(self, rows: int, feedback: bool = False) -> Optional[torch.cuda.CUDAGraph]:
         key = (rows, feedback)
