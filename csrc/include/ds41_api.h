@@ -145,6 +145,19 @@ int ds41_spec_accept(const int* inputs, const int* chosen, const int* first, con
                      int max_emit, int eos, int* accepted, int* emit, int* n_emit, void* stream);
 
 // ---------------------------------------------------------------------------------------------------
+// dSpark drafter support (dspark.cu)
+int ds41_taps_pack(const float* taps, void* out, int n_taps, int rows, int H, long long tap_stride, void* stream);
+int ds41_norm_rows(const float* planes, int splits, long long plane, const float* w, void* out, int rows, int N,
+                   float eps, void* stream);
+int ds41_markov_step(const float* logits, const void* head, const void* embed, const int* prev_token, int v_local,
+                     int v_offset, int rank, int vocab, float* block_val, int* block_idx, int n_blocks,
+                     unsigned int* ticket, float* best_val, int* best_idx, void* stream);
+int ds41_spec_feedback(const int* inputs, const int* chosen, int width, int forced_accept, int eos, int* accepted,
+                       int* emitted, int* n_emitted, int* next_anchor, int* target_pos, int* draft_pos,
+                       int* draft_hi, int* target_tokens, int* draft_tokens, long long* total_emitted, void* stream);
+int ds41_copy_ints(const int* src, int* dst, int n, void* stream);
+
+// ---------------------------------------------------------------------------------------------------
 // Quantisation (quant.cu).  sf: scale atoms [batch][ceil(rows/128)][K/128][512]; group 32 or 128.
 int ds41_act_quant_mx(const void* x, long long ldx, long long x_batch_stride, void* q, long long ldq,
                       long long q_batch_stride, void* sf, long long sf_batch_stride, int rows, int K, int batch,

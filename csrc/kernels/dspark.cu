@@ -1,0 +1,254 @@
+// dSpark drafter support kernels.
+//
+//  taps_pack     : the target's tap means (fp32 [n_taps][rows][H]) -> bf16 rows [rows][n_taps*H] for the main projection
+//  norm_rows     : sum of fp32 split planes -> RMSNorm(weight) -> bf16 rows (main_norm)
+//  markov_step   : one link of the draft chain.  logits'[v] = logits[v] + <markov_head[v,:], markov_embed[prev,:]>,
+//                  greedy argmax with lowest-id ties over this rank's vocabulary shard; the block that finishes
+//                  last (ticket) merges the block candidates and publishes (value, token)
+//                  (behaviour of the reference's draft terminal: native/cuda/kernels/v41_dspark.cu:241-290)
+//  spec_feedback : prepares the next round on the device: next anchor = chosen[accepted], positions advance by
+//                  accepted + 1; `forced_accept` >= 0 pins the accepted count (fixed acceptance schedule used
+//                  for benchmarking with random weights)
+#include "ds41_api.h"
+#include "ds41_launch.cuh"
+#include "ds41_ptx.cuh"
+
+namespace ds41 {
+
+__global__ void taps_pack_kernel(const float* __restrict__ taps, __nv_bfloat16* __restrict__ out, int n_taps, int rows,
+                                 int H, long long tap_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i = 1ll * blockIdx.x * blockDim.x + threadIdx.x;
+  const long long n = 1ll * rows * n_taps * H;
+  if (i >= n) return;
+  const int c = static_cast<int>(i % H);
+  const int t = static_cast<int>((i / H) % n_taps);
+  const int r = static_cast<int>(i / (1ll * H * n_taps));
+  out[i] = __float2bfloat16_rn(taps[t * tap_stride + 1ll * r * H + c]);
+}
+
+// one block (256 threads) per row; N <= 8192
+__global__ void __launch_bounds__(256) norm_rows_kernel(const float* __restrict__ planes, int splits, long long plane,
+                                                        const float* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                                                        int N, float eps) {
+  __shared__ float part[8];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x, tid = threadIdx.x;
+  float vals[32];
+  float sq = 0.f;
+#pragma unroll
+  for (int n = 0; n < 32; ++n) {
+    const int c = tid + 256 * n;
+    float a = 0.f;
+    if (c < N) {
+#pragma unroll 4
+      for (int s = 0; s < splits; ++s) a += planes[s * plane + 1ll * r * N + c];
+      a = bf16_round(a);
+    }
+    vals[n] = a;
+    sq = fmaf(a, a, sq);
+  }
+  sq = warp_sum(sq);
+  if ((tid & 31) == 0) part[tid >> 5] = sq;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += part[i];
+  const float inv = rsqrtf(tot / N + eps);
+#pragma unroll
+  for (int n = 0; n < 32; ++n) {
+    const int c = tid + 256 * n;
+    if (c < N) out[1ll * r * N + c] = __float2bfloat16_rn(vals[n] * inv * (w != nullptr ? w[c] : 1.f));
+  }
+}
+
+struct MarkovParams {
+  const float* logits;            // [V_local] base logits of this draft row
+  const __nv_bfloat16* head;      // [V_local][rank]
+  const __nv_bfloat16* embed;     // [V][rank]
+  const int* prev_token;          // device scalar: token that precedes this draft position
+  int v_local, v_offset, rank, vocab;
+  float* block_val;               // [gridDim.x]
+  int* block_idx;
+  unsigned int* ticket;           // zero before first use; reset by the finishing block
+  float* best_val;                // [1]
+  int* best_idx;                  // [1] global token id
+};
+
+// grid: enough blocks of 256 threads; each warp strides over vocabulary rows. rank <= 256, multiple of 8.
+__global__ void __launch_bounds__(256) markov_step_kernel(MarkovParams p) {
+  __shared__ float e[256];
+  __shared__ float wv[8];
+  __shared__ int wi[8];
+  __shared__ int s_last;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int prev = *p.prev_token;
+  if (prev < 0 || prev >= p.vocab) prev = 0;
+  if (tid < p.rank) e[tid] = __bfloat162float(p.embed[1ll * prev * p.rank + tid]);
+  __syncthreads();
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  const int lanes_per_row = p.rank / 8;             // 8 bf16 (16 B) per lane
+  const int rows_per_warp = 32 / lanes_per_row;     // rank 256 -> 1 row per warp pass; rank 64 -> 4
+  const int sub = lane / lanes_per_row, l = lane % lanes_per_row;
+  for (int v0 = (blockIdx.x * 8 + warp) * rows_per_warp; v0 < p.v_local; v0 += gridDim.x * 8 * rows_per_warp) {
+    const int v = v0 + sub;
+    float acc = 0.f;
+    if (v < p.v_local && sub < rows_per_warp) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(p.head + 1ll * v * p.rank + l * 8);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __bfloat1622float2(h[q]);
+        acc = fmaf(f.x, e[l * 8 + 2 * q], fmaf(f.y, e[l * 8 + 2 * q + 1], acc));
+      }
+    }
+    for (int o = lanes_per_row / 2; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (l == 0 && v < p.v_local && sub < rows_per_warp) {
+      const float x = p.logits[v] + acc;
+      const int tok = p.v_offset + v;
+      if (x > best || (x == best && tok < best_i)) { best = x; best_i = tok; }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+  }
+  if (lane == 0) { wv[warp] = best; wi[warp] = best_i; }
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (wv[w] > best || (wv[w] == best && wi[w] < best_i)) { best = wv[w]; best_i = wi[w]; }
+    p.block_val[blockIdx.x] = best;
+    p.block_idx[blockIdx.x] = best_i;
+    __threadfence();
+    const unsigned int t = atomicAdd(p.ticket, 1u);
+    s_last = (t == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  best = -INFINITY;
+  best_i = 0x7fffffff;
+  for (int b = tid; b < static_cast<int>(gridDim.x); b += 256) {
+    const float ov = __ldcg(p.block_val + b);
+    const int oi = __ldcg(p.block_idx + b);
+    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+  }
+  if (lane == 0) { wv[warp] = best; wi[warp] = best_i; }
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (wv[w] > best || (wv[w] == best && wi[w] < best_i)) { best = wv[w]; best_i = wi[w]; }
+    *p.best_val = best;
+    *p.best_idx = best_i == 0x7fffffff ? -1 : best_i;
+    *p.ticket = 0u;
+  }
+}
+
+struct SpecFeedbackParams {
+  const int* inputs;      // [width] tokens the verification pass consumed (anchor, drafts...)
+  const int* chosen;      // [width] target's choice after each row
+  int width, forced_accept, eos;
+  int* accepted;          // [1]
+  int* emitted;           // [width] tokens emitted this round (chosen[0..accepted])
+  int* n_emitted;         // [1]
+  int* next_anchor;       // [1]
+  int* target_pos;        // [>= width]: verification rows' positions, advanced for the next round
+  int* draft_pos;         // [>= width]: drafter rows' positions
+  int* draft_hi;          // [>= width]: drafter rows' highest visible position
+  int* target_tokens;     // [>= width]: row 0 receives the next anchor
+  int* draft_tokens;      // [>= width]: row 0 receives the next anchor
+  long long* total_emitted;   // running counter
+};
+__global__ void spec_feedback_kernel(SpecFeedbackParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int acc = 0;
+  if (p.forced_accept >= 0) {
+    acc = min(p.forced_accept, p.width - 1);
+  } else {
+    while (acc + 1 < p.width && p.inputs[acc + 1] == p.chosen[acc] && p.chosen[acc] != p.eos) ++acc;
+  }
+  for (int j = 0; j <= acc; ++j) p.emitted[j] = p.chosen[j];
+  *p.accepted = acc;
+  *p.n_emitted = acc + 1;
+  const int anchor = p.chosen[acc];
+  *p.next_anchor = anchor;
+  p.target_tokens[0] = anchor;
+  p.draft_tokens[0] = anchor;
+  const int base = p.target_pos[0] + acc + 1;
+  for (int j = 0; j < p.width; ++j) {
+    p.target_pos[j] = base + j;
+    p.draft_pos[j] = base + j;
+    p.draft_hi[j] = base + p.width - 1;
+  }
+  if (p.total_emitted != nullptr) *p.total_emitted += acc + 1;
+}
+
+// copy `n` ints device-to-device with an element offset (draft tokens -> verification inputs)
+__global__ void copy_ints_kernel(const int* src, int* dst, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = src[i];
+}
+
+}  // namespace ds41
+
+using namespace ds41;
+
+extern "C" int ds41_taps_pack(const float* taps, void* out, int n_taps, int rows, int H, long long tap_stride,
+                              void* stream) {
+  if (n_taps <= 0 || rows <= 0 || H <= 0) return cudaErrorInvalidValue;
+  const long long n = 1ll * rows * n_taps * H;
+  return launch_pdl(taps_pack_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0,
+                    static_cast<cudaStream_t>(stream), taps, static_cast<__nv_bfloat16*>(out), n_taps, rows, H,
+                    tap_stride);
+}
+
+extern "C" int ds41_norm_rows(const float* planes, int splits, long long plane, const float* w, void* out, int rows,
+                              int N, float eps, void* stream) {
+  if (rows <= 0 || N <= 0 || N > 8192 || splits <= 0) return cudaErrorInvalidValue;
+  return launch_pdl(norm_rows_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), planes, splits,
+                    plane, w, static_cast<__nv_bfloat16*>(out), N, eps);
+}
+
+extern "C" int ds41_markov_step(const float* logits, const void* head, const void* embed, const int* prev_token,
+                                int v_local, int v_offset, int rank, int vocab, float* block_val, int* block_idx,
+                                int n_blocks, unsigned int* ticket, float* best_val, int* best_idx, void* stream) {
+  if (v_local <= 0 || rank <= 0 || rank > 256 || (rank & 7) || (32 % (rank / 8)) != 0 || n_blocks <= 0)
+    return cudaErrorInvalidValue;
+  MarkovParams p{logits, static_cast<const __nv_bfloat16*>(head), static_cast<const __nv_bfloat16*>(embed),
+                 prev_token, v_local, v_offset, rank, vocab, block_val, block_idx, ticket, best_val, best_idx};
+  return launch_pdl(markov_step_kernel, dim3(n_blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
+}
+
+extern "C" int ds41_spec_feedback(const int* inputs, const int* chosen, int width, int forced_accept, int eos,
+                                  int* accepted, int* emitted, int* n_emitted, int* next_anchor, int* target_pos,
+                                  int* draft_pos, int* draft_hi, int* target_tokens, int* draft_tokens,
+                                  long long* total_emitted, void* stream) {
+  if (width <= 0) return cudaErrorInvalidValue;
+  SpecFeedbackParams p{inputs, chosen, width, forced_accept, eos, accepted, emitted, n_emitted, next_anchor,
+                       target_pos, draft_pos, draft_hi, target_tokens, draft_tokens, total_emitted};
+  return launch_pdl(spec_feedback_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), p);
+}
+
+extern "C" int ds41_copy_ints(const int* src, int* dst, int n, void* stream) {
+  if (n <= 0) return cudaErrorInvalidValue;
+  return launch_pdl(copy_ints_kernel, dim3((n + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream), src, dst,
+                    n);
+}

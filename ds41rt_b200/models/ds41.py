@@ -114,16 +114,20 @@ class EngineWeights:
     @staticmethod
     def from_fp32(cfg: ModelConfig, w: Dict[str, torch.Tensor], rank: int, world: int, device,
                   prefix: str = "layers", n_layers: Optional[int] = None, n_experts: Optional[int] = None,
-                  topk: Optional[int] = None, expert_dtype: str = "bf16") -> "EngineWeights":
+                  topk: Optional[int] = None, expert_dtype: str = "bf16", share: Optional["EngineWeights"] = None
+                  ) -> "EngineWeights":
         """Build one rank's shard from an fp32 name->tensor dict.  expert_dtype "mxfp8" stores routed
         experts as E4M3 with power-of-two 128x128 block scales (consumed by the block-scaled GEMM)."""
         ew = EngineWeights(cfg, rank, world, device)
         ew.expert_dtype = expert_dtype
         D, H = cfg.head_dim, cfg.hidden
         dev = lambda t, dt=BF16: t.to(device=device, dtype=dt).contiguous()
-        ew.embed = dev(w["embed.weight"])
-        v0 = rank * ew.V_local
-        ew.head = dev(w["head.weight"][v0:v0 + ew.V_local])
+        if share is not None:          # drafter blocks reuse the target's embedding and vocabulary head
+            ew.embed, ew.head = share.embed, share.head
+        else:
+            ew.embed = dev(w["embed.weight"])
+            v0 = rank * ew.V_local
+            ew.head = dev(w["head.weight"][v0:v0 + ew.V_local])
         ew.final_norm = dev(w["norm.weight"], F32)
         n_layers = cfg.n_layers if n_layers is None else n_layers
         E = cfg.n_experts if n_experts is None else n_experts
@@ -190,7 +194,8 @@ class EngineWeights:
 
     @staticmethod
     def random(cfg: ModelConfig, rank: int, world: int, device, seed: int = 0, std: float = 0.02,
-               router_std: Optional[float] = None, expert_dtype: str = "bf16") -> "EngineWeights":
+               router_std: Optional[float] = None, expert_dtype: str = "bf16",
+               share: Optional["EngineWeights"] = None) -> "EngineWeights":
         """Random-init shard generated directly on the device (for models too large to stage on the host).
         expert_dtype "mxfp8": E4M3 payloads ~ N(0, 48^2) with every 128x128 block scale 2^-11 (dequantised
         std 0.0234), the statistics an amax-scaled quantisation of N(0, 0.02) weights produces."""
@@ -210,8 +215,11 @@ class EngineWeights:
             return chunk
 
         ones = lambda n: torch.ones(n, dtype=F32, device=device)
-        ew.embed = rnd((cfg.vocab, H), shared_gen)
-        ew.head = rnd((ew.V_local, H))
+        if share is not None:
+            ew.embed, ew.head = share.embed, share.head
+        else:
+            ew.embed = rnd((cfg.vocab, H), shared_gen)
+            ew.head = rnd((ew.V_local, H))
         ew.final_norm = ones(H)
         EL = cfg.n_experts // world
         nproj = 2 * cfg.hc_mult + cfg.hc_mult ** 2
@@ -682,6 +690,33 @@ class DS41Engine:
         wait_flags = lib.ptr(self.flag_ptrs) if self.world > 1 else lib.ptr(None)
         self._run("argmax_merge", k.ds41_argmax_merge, self._val_ptrs, self._idx_ptrs, self.world, rows, lib.ptr(self.chosen),
                                      wait_flags, lib.ptr(self.epoch), lib.ptr(self.status), st())
+
+    def head_logits(self, rows: int):
+        """collapse -> final norm -> vocabulary shard GEMM; leaves fp32 logits in self.logits (no selection)."""
+        cfg = self.cfg
+        lw0 = self.w.layers[0]
+        self._hc(rows, getattr(self, "_pending", None), lw0.hc_attn_fn, lw0.hc_attn_scale, lw0.hc_attn_base,
+                 self.w.final_norm)
+        self._pending = None
+        self._run("gemm_head", G.gemm_raw, self.w.head, self.xn, self.logits, self.V_local, rows, cfg.hidden,
+                  lda=cfg.hidden, ldb=cfg.hidden, ldo=self.V_local, out_mode=3, status=self.status, static_operand=1)
+
+    def feed_rings(self, rows: int):
+        """Write every layer's window-ring rows from the normalised hidden states currently in self.xn
+        (rows/positions/slots as set by set_rows): the drafter's committed KV comes from the target's taps."""
+        cfg, k, st = self.cfg, self.k, lib.stream
+        H, D, Q = cfg.hidden, cfg.head_dim, cfg.q_lora
+        for l, lw in enumerate(self.w.layers):
+            ntot = lw.w_qkv.shape[0]
+            s_qkv = G.pick_splits(ntot, H, max_splits=self.max_splits)
+            self._run("gemm_qkv_feed", G.linear_planes, self.xn[:rows], lw.w_qkv,
+                      self.planes_qkv.view(-1)[: s_qkv * rows * ntot].view(s_qkv, rows, ntot), s_qkv,
+                      status=self.status)
+            self._run("qkv_post_feed", k.ds41_qkv_post, lib.ptr(self.planes_qkv), s_qkv, rows, ntot, Q, D,
+                      cfg.rope_dim, lw.extra_cols, lw.index_heads_cols, C.c_float(cfg.index_weight_scale),
+                      lib.ptr(lw.q_norm), lib.ptr(lw.kv_norm), lib.ptr(self._inv(l)), lib.ptr(self.row_pos),
+                      lib.ptr(self.row_slot), lib.ptr(self.q_lat), lib.ptr(self.cache.win[l]), self.cache.ring,
+                      lib.ptr(self.extras), C.c_float(cfg.norm_eps), st())
 
     # ------------------------------------------------------------------ convenience drivers
     def prefill(self, slot: int, tokens: List[int], start: int = 0, chunk: Optional[int] = None) -> int:

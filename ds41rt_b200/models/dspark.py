@@ -1,0 +1,132 @@
+"""dSpark drafter: a few DS41 blocks that propose a block of draft tokens per round.
+
+Structure (reference: architecture.md:62-66, rust/crates/ds41rt-daemon/src/v41_experts/dspark/main_context.rs:1-60,
+native/cuda/kernels/v41_dspark.cu:40-58,241-290):
+  * conditioning: the means of the target's residual streams entering its tap layers are concatenated, projected by
+    `mtp.0.main_proj` and normalised (`main_norm`); every drafter stage turns those rows into committed KV
+    (its own wkv / kv_norm / plain RoPE) stored in a position-indexed ring of 128 rows;
+  * a draft pass feeds [anchor token, noise, noise, ...] through the stages; draft rows attend to the ring and to
+    each other without a causal mask; stages have their own mHC, attention and a smaller MoE;
+  * terminal: final norm, the TARGET's vocabulary head, plus a low-rank Markov head whose bias is chained position
+    by position (token j conditions the logits of token j+1); greedy selection.
+The drafter blocks are executed by a second DS41Engine instance that shares the target's embedding/head tensors.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import dataclasses
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config import ModelConfig
+from ..ops import gemm as G
+from ..ops import lib
+from .ds41 import BF16, DS41Engine, EngineWeights, F32, I32
+
+
+def drafter_config(cfg: ModelConfig) -> ModelConfig:
+    d = cfg.dspark
+    return dataclasses.replace(cfg, name=cfg.name + "-dspark", n_layers=d.stages, compress_ratios=[0] * d.stages,
+                               source_layers={}, index_layers=(), n_experts=d.n_experts, topk=d.topk,
+                               window=d.ring_rows, dspark=None, engram=None, vision=None)
+
+
+class DSparkDrafter:
+    def __init__(self, cfg: ModelConfig, target: DS41Engine, weights: Optional[Dict[str, torch.Tensor]] = None,
+                 width: Optional[int] = None, seed: int = 0, expert_dtype: str = "bf16"):
+        assert cfg.dspark is not None
+        d = cfg.dspark
+        self.cfg, self.target, self.d = cfg, target, d
+        self.width = width or d.block_size
+        dev, rank, world = target.device, target.rank, target.world
+        dcfg = drafter_config(cfg)
+        H = cfg.hidden
+        n_taps = len(d.tap_layers)
+        last = d.stages - 1
+        if weights is not None:
+            ew = EngineWeights.from_fp32(dcfg, weights, rank, world, dev, prefix="mtp", n_layers=d.stages,
+                                         n_experts=d.n_experts, topk=d.topk, share=target.w,
+                                         expert_dtype=expert_dtype)
+            to = lambda t, dt=BF16: t.to(device=dev, dtype=dt).contiguous()
+            ew.final_norm = to(weights[f"mtp.{last}.norm.weight"], F32)
+            self.main_proj = to(weights["mtp.0.main_proj.weight"])
+            self.main_norm = to(weights["mtp.0.main_norm.weight"], F32)
+            self.markov_embed = to(weights[f"mtp.{last}.markov_head.embed.weight"])
+            v0 = rank * target.V_local
+            self.markov_head = to(weights[f"mtp.{last}.markov_head.head.weight"][v0:v0 + target.V_local])
+        else:
+            ew = EngineWeights.random(dcfg, rank, world, dev, seed=seed + 77, share=target.w,
+                                      expert_dtype=expert_dtype)
+            gen = torch.Generator(device=dev).manual_seed(seed + 78)
+            rnd = lambda *shape: (torch.randn(*shape, generator=gen, device=dev) * 0.02).to(BF16)
+            self.main_proj = rnd(H, n_taps * H)
+            self.main_norm = torch.ones(H, dtype=F32, device=dev)
+            self.markov_embed = rnd(cfg.vocab, d.markov_rank)
+            self.markov_head = rnd(target.V_local, d.markov_rank)
+        R = max(target.max_rows, self.width)
+        self.eng = DS41Engine(dcfg, ew, target.fabric, max_rows=R, slots=target.cache.slots, max_ctx=64,
+                              row_hi=True)
+        self.eng.layer_prefix_plain = True
+        z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=dev)
+        self.taps_bf16 = z((R, n_taps * H), BF16)
+        self.main_splits = G.pick_splits(H, n_taps * H, max_splits=16)
+        self.main_planes = z((16, R, H), F32)
+        self.n_blocks = 296
+        self.block_val = z((self.n_blocks,), F32)
+        self.block_idx = z((self.n_blocks,), I32)
+        self.ticket = z((1,), I32)
+        self.drafts = z((self.width,), I32)          # drafts[j] = proposed token for position p + 1 + j
+        self.draft_val = z((self.width,), F32)
+        self.launches = 0
+
+    # ------------------------------------------------------------------ conditioning
+    def feed(self, rows: int):
+        """Turn the target's tap means of its last pass (rows/positions/slots as in the target's inputs)
+        into committed ring rows of every drafter stage."""
+        t, e, k = self.target, self.eng, lib.kernels()
+        H = self.cfg.hidden
+        n_taps = t.taps.shape[0]
+        e._run("taps_pack", k.ds41_taps_pack, lib.ptr(t.taps), lib.ptr(self.taps_bf16), n_taps, rows, H,
+               C.c_longlong(t.taps.stride(0)), lib.stream())
+        e._run("gemm_main", G.linear_planes, self.taps_bf16[:rows], self.main_proj,
+               self.main_planes.view(-1)[: self.main_splits * rows * H].view(self.main_splits, rows, H),
+               self.main_splits, status=e.status)
+        e._run("norm_main", k.ds41_norm_rows, lib.ptr(self.main_planes), self.main_splits, C.c_longlong(rows * H),
+               lib.ptr(self.main_norm), lib.ptr(e.xn), rows, H, C.c_float(self.cfg.norm_eps), lib.stream())
+        # the drafter engine's row metadata mirrors the target's
+        e._run("copy_pos", k.ds41_copy_ints, lib.ptr(t.row_pos), lib.ptr(e.row_pos), rows, lib.stream())
+        e._run("copy_slot", k.ds41_copy_ints, lib.ptr(t.row_slot), lib.ptr(e.row_slot), rows, lib.stream())
+        e.feed_rings(rows)
+
+    # ------------------------------------------------------------------ drafting
+    def set_draft_rows(self, anchor: int, pos: int, slot: int):
+        w = self.width
+        toks = [anchor] + [self.d.noise_token_id] * (w - 1)
+        self.eng.set_rows(toks, list(range(pos, pos + w)), [slot] * w, row_hi=[pos + w - 1] * w)
+
+    def draft(self):
+        """One draft pass over the rows prepared in the drafter engine's inputs -> self.drafts (device)."""
+        e, k, t = self.eng, lib.kernels(), self.target
+        w = self.width
+        e.forward_rows(w, head=False)
+        e.head_logits(w)
+        rank = self.d.markov_rank
+        for j in range(w):
+            prev = e.in_tokens[0:1] if j == 0 else self.drafts[j - 1:j]
+            e._run("markov_step", k.ds41_markov_step, lib.ptr(e.logits[j]), lib.ptr(self.markov_head),
+                   lib.ptr(self.markov_embed), lib.ptr(prev), e.V_local, e.rank * e.V_local, rank, self.cfg.vocab,
+                   lib.ptr(self.block_val), lib.ptr(self.block_idx), self.n_blocks, lib.ptr(self.ticket),
+                   lib.ptr(e.best_val[j:j + 1]), lib.ptr(e.best_idx[j:j + 1]), lib.stream())
+            if e.world > 1:
+                e._signal()
+                e._run("draft_merge", k.ds41_argmax_merge, _offset_ptrs(e._val_ptrs, 4 * j, e.world),
+                       _offset_ptrs(e._idx_ptrs, 4 * j, e.world), e.world, 1, lib.ptr(self.drafts[j:j + 1]),
+                       lib.ptr(e.flag_ptrs), lib.ptr(e.epoch), lib.ptr(e.status), lib.stream())
+            else:
+                e._run("draft_take", k.ds41_copy_ints, lib.ptr(e.best_idx[j:j + 1]), lib.ptr(self.drafts[j:j + 1]), 1,
+                       lib.stream())
+
+
+def _offset_ptrs(ptrs, offset_bytes: int, n: int):
+    return (C.c_void_p * n)(*[(p or 0) + offset_bytes for p in ptrs])

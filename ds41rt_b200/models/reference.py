@@ -196,7 +196,8 @@ class ReferenceModel:
 
     def attention(self, p: str, layer: int, xn: torch.Tensor, positions: torch.Tensor,
                   source, select: Optional[torch.Tensor], trace: Optional[LayerTrace] = None,
-                  attend_all_draft: int = 0):
+                  attend_all_draft: int = 0, kv_prefix: Optional[torch.Tensor] = None,
+                  prefix_pos: Optional[torch.Tensor] = None):
         """Sparse latent attention for all T query rows.  `source` = (comp, first_pos, ratio) or None."""
         cfg = self.cfg
         T = xn.shape[0]
@@ -211,13 +212,18 @@ class ReferenceModel:
             kv = Q.qdq_mxfp8(kv, 32)
         if trace is not None:
             trace.q, trace.kv = q, kv
-        # window keys
-        pj = positions[None, :]
+        # window keys (optionally preceded by externally produced rows, e.g. the drafter's committed ring)
+        key_pos = positions
+        if kv_prefix is not None:
+            kv = torch.cat([kv_prefix.float(), kv], 0)
+            key_pos = torch.cat([prefix_pos, positions])
+        pj = key_pos[None, :]
         pt = positions[:, None]
-        wmask = (pj <= pt) & (pj > pt - cfg.window)
+        hi = pt.clone()
         if attend_all_draft:
             # drafter rows: the last `attend_all_draft` rows see each other non-causally
-            wmask[-attend_all_draft:, -attend_all_draft:] = True
+            hi[-attend_all_draft:] = positions[-1]
+        wmask = (pj <= hi) & (pj > pt - cfg.window)
         logits = torch.einsum("thd,jd->thj", q, kv) * cfg.softmax_scale
         logits = logits.masked_fill(~wmask[:, None, :], float("-inf"))
         values = kv
@@ -263,7 +269,7 @@ class ReferenceModel:
         return out
 
     def block(self, p: str, layer: int, streams, pre, positions, source, select, n_experts, topk,
-              trace=None, attend_all_draft: int = 0, produce=None):
+              trace=None, attend_all_draft: int = 0, produce=None, kv_prefix=None, prefix_pos=None):
         """One decoder block on streams [T,m,H] with incoming pre [T,m].
         `produce(xn, q_lat)` lets the caller build sources/selections from this layer's
         normalised input before attention runs; it returns (source, select)."""
@@ -277,7 +283,8 @@ class ReferenceModel:
             trace.x_attn_norm = xn
         if produce is not None:
             source, select = produce(xn)
-        a, _ = self.attention(p, layer, xn, positions, source, select, trace, attend_all_draft)
+        a, _ = self.attention(p, layer, xn, positions, source, select, trace, attend_all_draft, kv_prefix,
+                              prefix_pos)
         streams = hc_expand(streams, a, post, comb)
         pre = next_pre
         next_pre, post, comb = mix(streams, "ffn")
@@ -368,6 +375,48 @@ class ReferenceModel:
         keep = torch.zeros(T, nb, dtype=torch.bool)
         keep.scatter_(1, order, True)
         return keep.repeat_interleave(B, 1)[:, :Tc]
+
+    # ------------------------------------------------------------------ dSpark drafter
+    def dspark_main(self, taps: List[torch.Tensor]) -> torch.Tensor:
+        """Tap means [T,H] of the tap layers -> normalised conditioning rows [T,H]."""
+        x = torch.cat([t.float() for t in taps], -1) @ self._g("mtp.0.main_proj.weight").t()
+        return rmsnorm(x, self._g("mtp.0.main_norm.weight"), self.cfg.norm_eps)
+
+    @torch.no_grad()
+    def dspark_draft(self, main: torch.Tensor, anchor: int, width: int):
+        """Draft `width` tokens following `anchor` given conditioning rows for positions 0..T-1.
+        Returns (draft tokens [width], base logits [width, vocab])."""
+        cfg, d = self.cfg, self.cfg.dspark
+        T = main.shape[0]
+        toks = torch.tensor([anchor] + [d.noise_token_id] * (width - 1))
+        positions = torch.arange(T, T + width)
+        prefix_pos = torch.arange(T)
+        inv = self.inv_freq(cfg.rope_plain, cfg.rope_dim)
+        streams = self._g("embed.weight")[toks][:, None, :].repeat(1, cfg.hc_mult, 1)
+        pre = torch.zeros(width, cfg.hc_mult)
+        pre[:, 0] = 1.0
+        saved_window = cfg.window
+        cfg.window = d.ring_rows
+        try:
+            for s in range(d.stages):
+                p = f"mtp.{s}"
+                kvp = rmsnorm(main @ self._g(f"{p}.attn.wkv.weight").t(), self._g(f"{p}.attn.kv_norm.weight"),
+                              cfg.norm_eps)
+                kvp = apply_rope(kvp, prefix_pos, inv, cfg.rope_dim)
+                streams, pre = self.block(p, -1, streams, pre, positions, None, None, d.n_experts, d.topk,
+                                          attend_all_draft=width, kv_prefix=kvp, prefix_pos=prefix_pos)
+        finally:
+            cfg.window = saved_window
+        last = d.stages - 1
+        x = rmsnorm(hc_collapse(streams, pre), self._g(f"mtp.{last}.norm.weight"), cfg.norm_eps)
+        logits = x @ self._g("head.weight").t()
+        me, mh = self._g(f"mtp.{last}.markov_head.embed.weight"), self._g(f"mtp.{last}.markov_head.head.weight")
+        drafts, prev = [], anchor
+        for j in range(width):
+            lj = logits[j] + mh @ me[prev]
+            prev = int(torch.argmax(lj))
+            drafts.append(prev)
+        return torch.tensor(drafts), logits
 
     @torch.no_grad()
     def generate_greedy(self, prompt: torch.Tensor, n_new: int):

@@ -76,7 +76,8 @@ def dir_functions():
         "ds41_gemm_tc", "ds41_embed_streams", "ds41_hc_post_mix", "ds41_hc_finish", "ds41_qkv_post",
         "ds41_compress", "ds41_index_score", "ds41_topk_select", "ds41_attend", "ds41_router_select",
         "ds41_moe_plan", "ds41_moe_combine", "ds41_signal", "ds41_reduce_planes", "ds41_argmax_rows",
-        "ds41_argmax_merge", "ds41_spec_accept", "ds41_act_quant_mx", "ds41_decode_feedback", "ds41_hc_step",
+        "ds41_argmax_merge", "ds41_spec_accept", "ds41_act_quant_mx", "ds41_decode_feedback", "ds41_hc_step", "ds41_taps_pack", "ds41_norm_rows", "ds41_markov_step", "ds41_spec_feedback",
+        "ds41_copy_ints",
     ]
 
 

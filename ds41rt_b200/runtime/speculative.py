@@ -1,0 +1,121 @@
+"""Speculative decoding rounds: dSpark drafts a block, the target verifies it in one pass.
+
+One round (all on the device, CUDA-graph capturable):
+    draft pass -> drafts become the verification inputs -> target pass over [anchor, d1..d_{w-1}] ->
+    drafter rings are fed from the target's taps -> accept rule + next-round inputs (spec_feedback)
+Accept rule (rust/crates/ds41rt-core/src/dspark_verify.rs:18-52 of the reference): draft j is accepted while it
+equals the target's own choice after draft j-1; the target's choice after the last accepted row is emitted as
+the bonus token and becomes the next anchor.  Because every cache row is addressed by token position, rows of
+rejected drafts are simply rewritten when their position is processed again - there is no separate commit.
+`forced_accept >= 0` pins the accepted count per round (fixed acceptance schedule for benchmarking random
+weights, where real acceptance is meaningless).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional
+
+import torch
+
+from ..models.ds41 import DS41Engine, I32
+from ..models.dspark import DSparkDrafter
+from ..ops import lib
+
+
+class SpecSession:
+    def __init__(self, target: DS41Engine, drafter: DSparkDrafter, forced_accept: int = -1, use_graphs: bool = True):
+        self.t, self.d = target, drafter
+        self.width = drafter.width
+        self.forced = forced_accept
+        self.use_graphs = use_graphs
+        dev = target.device
+        z = lambda n, dt=I32: torch.zeros(n, dtype=dt, device=dev)
+        self.accepted, self.n_emitted, self.next_anchor = z(1), z(1), z(1)
+        self.emitted = z(self.width)
+        self.total = z(1, torch.int64)
+        self.graph = None
+        self.launches_per_round = 0
+        self.h_out = torch.zeros(self.width + 2, dtype=torch.int32).pin_memory()
+        self.h_in = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self.h2d_bytes = self.d2h_bytes = 0
+
+    # ------------------------------------------------------------------ prompt
+    def start(self, slot: int, prompt: List[int], max_new: int, chunk: Optional[int] = None) -> int:
+        """Prefill the target (feeding the drafter's rings chunk by chunk) and prime round 0's inputs.
+        Returns the first generated token (the anchor of round 0)."""
+        t, d = self.t, self.d
+        chunk = chunk or t.max_rows
+        assert t.cache.ensure(slot, len(prompt) + max_new + 2 * self.width + 2), "KV pool exhausted"
+        nxt = -1
+        for c0 in range(0, len(prompt), chunk):
+            part = prompt[c0:c0 + chunk]
+            t.set_rows(part, list(range(c0, c0 + len(part))), [slot] * len(part))
+            last = c0 + chunk >= len(prompt)
+            t.forward_rows(len(part), head=last)
+            d.feed(len(part))
+            if last:
+                nxt = int(t.chosen[len(part) - 1].item())
+        self.prime(slot, nxt, len(prompt))
+        return nxt
+
+    def prime(self, slot: int, anchor: int, pos: int):
+        w = self.width
+        self.t.set_rows([anchor] + [0] * (w - 1), list(range(pos, pos + w)), [slot] * w)
+        self.d.set_draft_rows(anchor, pos, slot)
+        self.total.zero_()
+
+    # ------------------------------------------------------------------ one round
+    def _enqueue_round(self):
+        t, d, k, w = self.t, self.d, lib.kernels(), self.width
+        d.draft()
+        t._run("drafts_to_inputs", k.ds41_copy_ints, lib.ptr(d.drafts), lib.ptr(t.in_tokens[1:]), w - 1, lib.stream())
+        t.forward_rows(w)
+        d.feed(w)
+        t._run("spec_feedback", k.ds41_spec_feedback, lib.ptr(t.in_tokens), lib.ptr(t.chosen), w, self.forced,
+               self.t.cfg.eos if self.forced < 0 else -1, lib.ptr(self.accepted), lib.ptr(self.emitted),
+               lib.ptr(self.n_emitted), lib.ptr(self.next_anchor), lib.ptr(t.row_pos), lib.ptr(d.eng.row_pos),
+               lib.ptr(d.eng.row_hi), lib.ptr(t.in_tokens), lib.ptr(d.eng.in_tokens), lib.ptr(self.total),
+               lib.stream())
+
+    def round(self):
+        if not self.use_graphs:
+            self._enqueue_round()
+            return
+        if self.graph is None:
+            snap = [x.clone() for x in (self.t.in_tokens, self.t.row_pos, self.d.eng.in_tokens, self.d.eng.row_pos,
+                                        self.d.eng.row_hi, self.total)]
+            self._enqueue_round()          # eager warm-up (sets kernel attributes)
+            torch.cuda.synchronize()
+            restore = lambda: [dst.copy_(src) for dst, src in zip(
+                (self.t.in_tokens, self.t.row_pos, self.d.eng.in_tokens, self.d.eng.row_pos, self.d.eng.row_hi,
+                 self.total), snap)]
+            restore()
+            before = self.t.launches + self.d.eng.launches
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._enqueue_round()
+            self.launches_per_round = self.t.launches + self.d.eng.launches - before
+            restore()
+            self.graph = g
+        self.graph.replay()
+
+    def round_host(self) -> List[int]:
+        """One round through the public path: replay, then read the emitted tokens back to pinned host memory."""
+        self.round()
+        self.h_out[: self.width].copy_(self.emitted, non_blocking=True)
+        self.h_out[self.width: self.width + 1].copy_(self.n_emitted, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes += 4 * (self.width + 1)
+        n = int(self.h_out[self.width])
+        return self.h_out[:n].tolist()
+
+    def generate(self, prompt: List[int], max_new_tokens: int, slot: int = 0, eos: Optional[int] = None) -> List[int]:
+        first = self.start(slot, prompt, max_new_tokens)
+        out = [first]
+        while len(out) < max_new_tokens and (eos is None or eos not in out):
+            out.extend(self.round_host())
+        self.t.check_status("speculative generate (target)")
+        self.d.eng.check_status("speculative generate (drafter)")
+        if eos is not None and eos in out:
+            out = out[: out.index(eos) + 1]
+        return out[:max_new_tokens]

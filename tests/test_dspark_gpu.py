@@ -1,0 +1,75 @@
+"""dSpark drafter and speculative rounds on the GPU vs the CPU oracle / plain greedy decoding."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _build(max_rows=8):
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.weights import init_weights
+    from ds41rt_b200.models.reference import ReferenceModel
+    from ds41rt_b200.models.ds41 import EngineWeights, DS41Engine
+    from ds41rt_b200.models.dspark import DSparkDrafter
+    cfg = ModelConfig.tiny()
+    w = init_weights(cfg, seed=0)
+    wr = {k: (v.bfloat16().float() if v.dim() == 2 and not k.endswith("_fn") else v) for k, v in w.items()}
+    ref = ReferenceModel(cfg, wr)
+    dev = torch.device("cuda")
+    eng = DS41Engine(cfg, EngineWeights.from_fp32(cfg, wr, 0, 1, dev), max_rows=max_rows, slots=2, max_ctx=512)
+    drafter = DSparkDrafter(cfg, eng, weights=wr)
+    return cfg, ref, eng, drafter
+
+
+def test_drafter_matches_oracle():
+    from ds41rt_b200.runtime.speculative import SpecSession
+    cfg, ref, eng, drafter = _build()
+    g = torch.Generator().manual_seed(11)
+    prompt = torch.randint(0, cfg.vocab, (40,), generator=g)
+    with torch.no_grad():
+        logits, taps = ref.forward(prompt, return_taps=True)
+    anchor = int(logits[-1].argmax())
+    main = ref.dspark_main(taps)
+    want, want_logits = ref.dspark_draft(main, anchor, drafter.width)
+    sess = SpecSession(eng, drafter, use_graphs=False)
+    first = sess.start(0, prompt.tolist(), 16)
+    drafter.draft()
+    torch.cuda.synchronize()
+    eng.check_status()
+    drafter.eng.check_status()
+    got_logits = drafter.eng.logits[: drafter.width].float().cpu()
+    err = float((got_logits - want_logits).abs().max())
+    scale = float(want_logits.abs().max())
+    print("drafter logits err", err, "scale", scale, "drafts", drafter.drafts.tolist(), want.tolist(), first, anchor)
+    assert first == anchor
+    assert err < 0.08 * scale
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_speculative_decoding_is_lossless(graphs):
+    """Greedy speculative decoding must emit exactly the tokens plain greedy decoding emits."""
+    from ds41rt_b200.runtime.session import DecodeSession
+    from ds41rt_b200.runtime.speculative import SpecSession
+    cfg, ref, eng, drafter = _build()
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, cfg.vocab, (37,), generator=g).tolist()
+    plain = DecodeSession(eng, use_graphs=False).generate(prompt, 24, slot=1)
+    spec = SpecSession(eng, drafter, use_graphs=graphs)
+    out = spec.generate(prompt, 24, slot=0)
+    print("plain", plain)
+    print("spec ", out, "emitted/round", float(spec.total.item()))
+    assert out == plain
+
+
+def test_forced_acceptance_schedule_advances_four_tokens_per_round():
+    from ds41rt_b200.runtime.speculative import SpecSession
+    cfg, ref, eng, drafter = _build()
+    prompt = list(range(10, 40))
+    spec = SpecSession(eng, drafter, forced_accept=3, use_graphs=True)
+    spec.start(0, prompt, 64)
+    for _ in range(6):
+        spec.round()
+    torch.cuda.synchronize()
+    eng.check_status()
+    assert int(spec.total.item()) == 24
+    assert int(eng.row_pos[0].item()) == len(prompt) + 24
