@@ -1,17 +1,21 @@
 #!/usr/bin/env python
-"""Headline benchmark: C1 greedy decode tokens/s of a DeepSeek-V4.1-Flash-shaped model.
+"""Headline benchmark: C1 decode tokens/s of a DeepSeek-V4.1-Flash-shaped model with dSpark speculative decoding.
 
-Config (BASELINE.json config 2): full Flash architecture, random-init weights, routed experts FP8 E4M3 with
+Config (BASELINE.json configs 2 and 5): full Flash architecture, random-init weights, routed experts FP8 E4M3 with
 128x128 power-of-two block scales and 1x128 activation scales, dense/attention weights bf16, EP<N> experts and
-TP<N> attention over N GPUs of one node, a 4096-token random-id prompt and greedy decode.  Where the full model
-does not fit the N GPUs' memory the model is layer-truncated (the JSON line says how many layers ran).
+TP<N> attention over N GPUs of one node, a 4096-token random-id prompt.  A dSpark-shaped one-stage drafter that
+shares the target's embedding and head proposes 4 tokens per round; the target verifies the 5-row chunk; acceptance
+follows the fixed schedule "3 of 4 drafts accepted" (random weights make real acceptance meaningless), so every
+round emits 4 tokens.  Where the full model does not fit the N GPUs' memory the model is layer-truncated (the JSON
+line says how many layers ran).  `--no-spec` times plain one-token-per-step greedy decoding instead.
 
   python bench.py --gpus N --steps K --warmup W          (N > 1: launched by torch.distributed.run)
   python bench.py --impl reference ...                   (prints the reference arm's availability line)
 
-Prints ONE JSON line on rank 0.  `value` is device-timed (CUDA events, max over ranks) with the chosen token
-fed back on the device; `e2e` is the same metric through DecodeSession.step(): per step the inputs are copied
-from pinned host memory and the chosen token is read back.
+Prints ONE JSON line on rank 0.  `value` is device-timed (CUDA events, max over ranks): K rounds replayed as CUDA
+graphs with the accept rule and next-round inputs computed on the device.  `e2e` is the same metric through the
+public SpecSession.round_host() call: per round the inputs come from pinned host memory and the emitted tokens
+are read back to the host.
 """
 from __future__ import annotations
 
@@ -25,7 +29,8 @@ import tempfile
 import time
 
 BASELINE_C1_DECODE = 146.12   # reference README.md:39 (1 RTX PRO 6000 + 4 DGX Spark, dSpark on)
-LAYERS_FOR_GPUS = {1: 11, 2: 22, 4: 40, 8: 40}
+BASELINE_TARGET_ONLY = 60.63  # reference README.md:109 (no drafts)
+LAYERS_FOR_GPUS = {1: 10, 2: 22, 4: 40, 8: 40}
 
 
 def reference_arm():
@@ -89,28 +94,48 @@ class ClockSampler:
         return out
 
 
+def timed(fabric, torch, fn):
+    """Barrier + synchronize on both sides, CUDA events on the launching stream, max over ranks -> ms."""
+    fabric.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    fn()
+    ev1.record()
+    torch.cuda.synchronize()
+    fabric.barrier()
+    return fabric.all_reduce_max(ev0.elapsed_time(ev1))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--steps", type=int, default=64, help="timed rounds (speculative) or decode steps (--no-spec)")
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = fit to memory)")
     ap.add_argument("--prompt", type=int, default=4096)
     ap.add_argument("--model", default="flash", choices=["flash", "small", "tiny"])
     ap.add_argument("--expert-dtype", default="mxfp8", choices=["mxfp8", "bf16"])
-    ap.add_argument("--prefill-chunk", type=int, default=64)
-    ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the host-loop measurement (0 = --steps)")
+    ap.add_argument("--prefill-chunk", type=int, default=32)
+    ap.add_argument("--e2e-steps", type=int, default=0, help="rounds/steps of the host-loop measurement (0 = --steps)")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly (for per-kernel profiling)")
+    ap.add_argument("--no-spec", action="store_true", help="plain greedy decoding, one token per step")
+    ap.add_argument("--accept", type=int, default=3, help="drafts accepted per round in the fixed schedule")
+    ap.add_argument("--draft-stages", type=int, default=1)
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
 
+    import dataclasses
+
     import torch
     from ds41rt_b200.config import ModelConfig
     from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    from ds41rt_b200.models.dspark import DSparkDrafter
     from ds41rt_b200.parallel.fabric import Fabric
     from ds41rt_b200.runtime.session import DecodeSession
+    from ds41rt_b200.runtime.speculative import SpecSession
 
     fabric = Fabric.create()
     world, rank = fabric.world, fabric.rank
@@ -126,81 +151,115 @@ def main():
     else:
         cfg = getattr(ModelConfig, args.model)()
         n_layers = cfg.n_layers
+    spec = not args.no_spec
+    if spec:
+        cfg.dspark = dataclasses.replace(cfg.dspark, stages=args.draft_stages)
+    width = cfg.dspark.block_size if spec else 1
+    per_round = args.accept + 1 if spec else 1
     W, K = max(args.warmup, 3), args.steps
     e2e_steps = args.e2e_steps or K
-    total_new = W + K + W + e2e_steps + 8
+    total_new = (W + K + W + e2e_steps + 4) * per_round + 3 * width + 64
     max_ctx = (args.prompt + total_new + 63) // 64 * 64
 
     t0 = time.time()
     weights = EngineWeights.random(cfg, rank, world, dev, seed=0, expert_dtype=args.expert_dtype)
-    eng = DS41Engine(cfg, weights, fabric, max_rows=args.prefill_chunk, slots=1, max_ctx=max_ctx)
-    sess = DecodeSession(eng, use_graphs=not args.no_graph)
+    eng = DS41Engine(cfg, weights, fabric, max_rows=max(args.prefill_chunk, width), slots=1, max_ctx=max_ctx)
     g = torch.Generator().manual_seed(1234)
     prompt = torch.randint(3, cfg.vocab - 600, (args.prompt,), generator=g).tolist()
     assert eng.cache.ensure(0, max_ctx)
-    first = eng.prefill(0, prompt, chunk=args.prefill_chunk)
+    drafter = None
+    if spec:
+        drafter = DSparkDrafter(cfg, eng, weights=None, seed=0, expert_dtype=args.expert_dtype)
+        sess = SpecSession(eng, drafter, forced_accept=args.accept, use_graphs=not args.no_graph)
+        sess.start(0, prompt, total_new, chunk=args.prefill_chunk)
+    else:
+        sess = DecodeSession(eng, use_graphs=not args.no_graph)
+        first = eng.prefill(0, prompt, chunk=args.prefill_chunk)
+        eng.set_rows([first], [args.prompt], [0])
     torch.cuda.synchronize()
     eng.check_status("prefill")
     setup_s = time.time() - t0
 
-    # ---------------- device-timed decode: K graph replays, token fed back on the device
-    pos = args.prompt
-    eng.set_rows([first], [pos], [0])
-    sess.graph(1, feedback=True)
-    before = eng.launches
-    sess.run_device_loop(1, W)
-    if args.no_graph:
-        sess.launches_per_graph[(1, True)] = (eng.launches - before) // W
-    fabric.barrier()
-    torch.cuda.synchronize()
+    def run(n):
+        if spec:
+            for _ in range(n):
+                sess.round()
+        else:
+            sess.run_device_loop(1, n)
+
+    # ---------------- device-timed: K graph replays, accept rule / token feedback on the device
+    l0 = eng.launches + (drafter.eng.launches if drafter else 0)
+    run(W)
+    per_pass_eager = (eng.launches + (drafter.eng.launches if drafter else 0) - l0) // W
     sampler = ClockSampler(dev.index or 0)
     if rank == 0:
         sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    sess.run_device_loop(1, K)
-    ev1.record()
-    torch.cuda.synchronize()
-    fabric.barrier()
-    ms = fabric.all_reduce_max(ev0.elapsed_time(ev1))
+    ms = timed(fabric, torch, lambda: run(K))
     clocks = sampler.stop() if rank == 0 else {}
     eng.check_status("timed decode")
-    pos += W + K
-    launches = sess.launches_per_graph.get((1, True), 0) * K
+    if drafter:
+        drafter.eng.check_status("timed decode (drafter)")
+    if args.no_graph:
+        per_pass = per_pass_eager
+    else:
+        per_pass = sess.launches_per_round if spec else sess.launches_per_graph.get((1, True), 0)
+    launches = per_pass * K
 
-    # ---------------- end to end through the public stepping API (pinned H2D in, D2H out, every step)
-    tok = int(eng.in_tokens[0].item())
-    for _ in range(W):
-        tok = sess.step([tok], [pos], [0])[0]
-        pos += 1
-    sess.h2d_bytes = sess.d2h_bytes = 0
-    fabric.barrier()
-    torch.cuda.synchronize()
-    t1 = time.perf_counter()
-    for _ in range(e2e_steps):
-        tok = sess.step([tok], [pos], [0])[0]
-        pos += 1
-    torch.cuda.synchronize()
-    e2e_s = fabric.all_reduce_max(time.perf_counter() - t1)
+    # ---------------- end to end through the public API: pinned H2D in, D2H out, every round/step
+    if spec:
+        for _ in range(W):
+            sess.round_host(feed_inputs=True)
+        sess.h2d_bytes = sess.d2h_bytes = 0
+        fabric.barrier()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        emitted = 0
+        for _ in range(e2e_steps):
+            emitted += len(sess.round_host(feed_inputs=True))
+        torch.cuda.synchronize()
+        e2e_s = fabric.all_reduce_max(time.perf_counter() - t1)
+        e2e_tokens = emitted
+    else:
+        pos = int(eng.row_pos[0].item())
+        tok = int(eng.in_tokens[0].item())
+        for _ in range(W):
+            tok = sess.step([tok], [pos], [0])[0]
+            pos += 1
+        sess.h2d_bytes = sess.d2h_bytes = 0
+        fabric.barrier()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        for _ in range(e2e_steps):
+            tok = sess.step([tok], [pos], [0])[0]
+            pos += 1
+        torch.cuda.synchronize()
+        e2e_s = fabric.all_reduce_max(time.perf_counter() - t1)
+        e2e_tokens = e2e_steps
     eng.check_status("e2e decode")
 
     if rank == 0:
-        value = K / (ms / 1e3)
+        value = K * per_round / (ms / 1e3)
+        metric = (f"decode tok/s C1 (dSpark drafter, fixed acceptance {args.accept}/{width - 1})" if spec
+                  else "decode tok/s C1 (greedy, target-only)")
+        base = BASELINE_C1_DECODE if spec else BASELINE_TARGET_ONLY
         line = {
-            "metric": "decode tok/s C1 (greedy, target-only)", "value": round(value, 2), "unit": "tok/s",
+            "metric": metric, "value": round(value, 2), "unit": "tok/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": round(value / BASELINE_C1_DECODE, 3),
+            "scaling": "weak", "vs_baseline": round(value / base, 3),
             "dtype": "bf16 dense / fp8-e4m3 experts (fp32 accumulate)", "data": "synthetic",
             "config": {"model": f"DeepSeek-V4.1-Flash-shaped ({cfg.name})", "layers": n_layers,
                        "layers_full_model": 40, "global_batch": 1, "seq_len": args.prompt,
                        "prompt_tokens": args.prompt, "parallelism": f"tp{world}+ep{world}",
+                       "tokens_per_step": per_round,
+                       "speculative": {"drafter_stages": args.draft_stages, "verify_rows": width,
+                                       "accepted_per_round": args.accept} if spec else None,
                        "experts": "fp8 e4m3, 128x128 ue8m0 block scales, 1x128 activation scales"
                        if args.expert_dtype == "mxfp8" else "bf16",
                        "l2": "no flush: every step streams more weight bytes than the 126 MB L2",
                        "weights_gb_per_gpu": round(weights.nbytes() / 1e9, 2),
                        "kv_gb_per_gpu": round(eng.cache.nbytes() / 1e9, 3), "setup_s": round(setup_s, 1)},
             "clocks": clocks,
-            "e2e": {"value": round(e2e_steps / e2e_s, 2), "unit": "tok/s", "steps": e2e_steps,
+            "e2e": {"value": round(e2e_tokens / e2e_s, 2), "unit": "tok/s", "steps": e2e_steps,
                     "h2d_bytes_per_step": sess.h2d_bytes // max(e2e_steps, 1),
                     "d2h_bytes_per_step": sess.d2h_bytes // max(e2e_steps, 1)},
             "gpu_launches": launches,

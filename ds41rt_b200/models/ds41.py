@@ -382,7 +382,7 @@ class DS41Engine:
         self.xc = z((R, H), F32)
         self.tickets = z((R,), I32)
         self.fused_rows = 16      # passes of at most this many rows use the fused hyper-connection step
-        self.taps = z((3, R, H), F32) if cfg.dspark is not None else None
+        self.taps = z((len(cfg.dspark.tap_layers), R, H), F32) if cfg.dspark is not None else None
         # attention
         max_extra = max([lw.extra_cols for lw in weights.layers] + [0])
         self.ntot_qkv = Q + D + max_extra

@@ -36,7 +36,8 @@ class SpecSession:
         self.graph = None
         self.launches_per_round = 0
         self.h_out = torch.zeros(self.width + 2, dtype=torch.int32).pin_memory()
-        self.h_in = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self.h_in = torch.zeros(1 + 2 * self.width, dtype=torch.int32).pin_memory()
+        self._host_state = None
         self.h2d_bytes = self.d2h_bytes = 0
 
     # ------------------------------------------------------------------ prompt
@@ -99,15 +100,32 @@ class SpecSession:
             self.graph = g
         self.graph.replay()
 
-    def round_host(self) -> List[int]:
-        """One round through the public path: replay, then read the emitted tokens back to pinned host memory."""
+    def round_host(self, feed_inputs: bool = False) -> List[int]:
+        """One round through the public path: (optionally) copy this round's anchor and positions from pinned
+        host memory, replay, then read the emitted tokens back to pinned host memory."""
+        w = self.width
+        if feed_inputs and self._host_state is not None:
+            anchor, pos = self._host_state
+            self.h_in[0] = anchor
+            self.h_in[1: 1 + w] = torch.arange(pos, pos + w, dtype=torch.int32)
+            self.h_in[1 + w: 1 + 2 * w] = pos + w - 1
+            t, e = self.t, self.d.eng
+            t.in_tokens[0:1].copy_(self.h_in[0:1], non_blocking=True)
+            e.in_tokens[0:1].copy_(self.h_in[0:1], non_blocking=True)
+            t.row_pos[:w].copy_(self.h_in[1: 1 + w], non_blocking=True)
+            e.row_pos[:w].copy_(self.h_in[1: 1 + w], non_blocking=True)
+            e.row_hi[:w].copy_(self.h_in[1 + w: 1 + 2 * w], non_blocking=True)
+            self.h2d_bytes += 4 * (2 + 3 * w)
         self.round()
-        self.h_out[: self.width].copy_(self.emitted, non_blocking=True)
-        self.h_out[self.width: self.width + 1].copy_(self.n_emitted, non_blocking=True)
+        self.h_out[:w].copy_(self.emitted, non_blocking=True)
+        self.h_out[w: w + 1].copy_(self.n_emitted, non_blocking=True)
+        self.h_out[w + 1: w + 2].copy_(self.t.row_pos[0:1], non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        self.d2h_bytes += 4 * (self.width + 1)
-        n = int(self.h_out[self.width])
-        return self.h_out[:n].tolist()
+        self.d2h_bytes += 4 * (w + 2)
+        n = int(self.h_out[w])
+        toks = self.h_out[:n].tolist()
+        self._host_state = (toks[-1], int(self.h_out[w + 1]))
+        return toks
 
     def generate(self, prompt: List[int], max_new_tokens: int, slot: int = 0, eos: Optional[int] = None) -> List[int]:
         first = self.start(slot, prompt, max_new_tokens)
