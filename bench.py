@@ -159,7 +159,7 @@ def main():
     W, K = max(args.warmup, 3), args.steps
     e2e_steps = args.e2e_steps or K
     total_new = (W + K + W + e2e_steps + 4) * per_round + 3 * width + 64
-    max_ctx = (args.prompt + total_new + 63) // 64 * 64
+    max_ctx = (args.prompt + total_new + 4 * width + 127) // 64 * 64
 
     t0 = time.time()
     weights = EngineWeights.random(cfg, rank, world, dev, seed=0, expert_dtype=args.expert_dtype)
