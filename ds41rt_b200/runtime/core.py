@@ -1,0 +1,225 @@
+"""Python bindings of the host runtime library (libds41_core.so): sampler oracle, speculative verification,
+Engram hashing/history, prefix radix banks and the paged KV allocator.  Pure CPU; usable without CUDA."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from ..ops import lib as _lib
+
+_c = None
+
+
+def core():
+    global _c
+    if _c is None:
+        c = _lib.core()
+        c.ds41_sample_uniform.restype = C.c_float
+        c.ds41_sample_uniform.argtypes = [C.c_uint64, C.c_uint64]
+        c.ds41_sample_token.restype = C.c_int
+        c.ds41_verify_greedy.restype = C.c_int
+        for name in ("ds41_engram_history_new", "ds41_engram_history_fork", "ds41_prefix_new", "ds41_kv_new"):
+            getattr(c, name).restype = C.c_void_p
+        c.ds41_engram_history_position.restype = C.c_uint64
+        c.ds41_prefix_insert.restype = C.c_int64
+        c.ds41_prefix_lookup.restype = C.c_int64
+        c.ds41_kv_plan_groups.restype = C.c_longlong
+        _c = c
+    return _c
+
+
+SAMPLE_STATUS = {0: "ok", 1: "empty_candidates", 2: "nonfinite_logit", 3: "invalid_temperature", 4: "mask_width",
+                 5: "internal", 6: "invalid_parameter"}
+
+
+class SamplingError(ValueError):
+    pass
+
+
+def sample_uniform(seed: int, position: int) -> float:
+    return float(core().ds41_sample_uniform(seed & (2 ** 64 - 1), position))
+
+
+def sample_token(logits: np.ndarray, mask: Optional[np.ndarray] = None, temperature: float = 0.0, top_k: int = 0,
+                 top_p: float = 1.0, min_p: float = 0.0, uniform: float = 0.0) -> int:
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    tok = C.c_int(-1)
+    mp, mw = None, 0
+    if mask is not None:
+        mask = np.ascontiguousarray(mask, dtype=np.uint32)
+        mp, mw = mask.ctypes.data_as(C.c_void_p), mask.size
+    st = core().ds41_sample_token(logits.ctypes.data_as(C.c_void_p), logits.size, mp, mw, C.c_float(temperature),
+                                  int(top_k), C.c_float(top_p), C.c_float(min_p), C.c_float(uniform), C.byref(tok))
+    if st != 0:
+        raise SamplingError(SAMPLE_STATUS.get(st, str(st)))
+    return tok.value
+
+
+def verify_greedy(inputs: Sequence[int], target_next: Sequence[int], eos: int, remaining: int, vocab: int = 129280):
+    n = len(inputs)
+    a = (C.c_uint32 * n)(*inputs)
+    b = (C.c_uint32 * n)(*target_next)
+    out = (C.c_uint32 * n)()
+    acc, flags = C.c_int(0), C.c_int(0)
+    r = core().ds41_verify_greedy(a, b, n, eos, remaining, vocab, out, C.byref(acc), C.byref(flags))
+    if r < 0:
+        raise ValueError({-1: "verification requires one to eight corresponding target rows",
+                          -2: "completed request cannot verify another anchor",
+                          -3: "verification token outside vocabulary"}[r])
+    return {"emitted": list(out[:r]), "accepted_inputs": acc.value, "eos": bool(flags.value & 1),
+            "length_limit": bool(flags.value & 2)}
+
+
+# ---------------------------------------------------------------------------------------------- Engram
+def engram_primes() -> np.ndarray:
+    out = np.zeros((2, 24), dtype=np.uint64)
+    core().ds41_engram_primes(out.ctypes.data_as(C.c_void_p))
+    return out
+
+
+def engram_hash(tokens4: Sequence[int]) -> np.ndarray:
+    t = (C.c_uint32 * 4)(*tokens4)
+    out = np.zeros((2, 24), dtype=np.uint64)
+    core().ds41_engram_hash(t, out.ctypes.data_as(C.c_void_p))
+    return out
+
+
+class EngramHistory:
+    def __init__(self, pad_id: int = 2, _handle=None):
+        self.pad = pad_id
+        self.h = C.c_void_p(_handle if _handle is not None else core().ds41_engram_history_new(pad_id))
+
+    def __del__(self):
+        try:
+            core().ds41_engram_history_free(self.h)
+        except Exception:
+            pass
+
+    @property
+    def position(self) -> int:
+        return int(core().ds41_engram_history_position(self.h))
+
+    def fork(self) -> "EngramHistory":
+        return EngramHistory(self.pad, core().ds41_engram_history_fork(self.h))
+
+    def prepare(self, tokens: Sequence[int]) -> np.ndarray:
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        out = np.zeros((len(t), 2, 24), dtype=np.uint64)
+        assert core().ds41_engram_prepare(self.h, t.ctypes.data_as(C.c_void_p), len(t),
+                                          out.ctypes.data_as(C.c_void_p)) == 0
+        return out
+
+    def commit(self, tokens: Sequence[int], accepted: int):
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        if core().ds41_engram_commit(self.h, t.ctypes.data_as(C.c_void_p), len(t), accepted) != 0:
+            raise ValueError("accepted count outside the prepared batch")
+
+
+# ---------------------------------------------------------------------------------------------- prefix radix
+class PrefixBanks:
+    PROMPT, TURN = 0, 1
+
+    def __init__(self, prompt_capacity: int = 20, turn_capacity: int = 20, window: int = 128):
+        self.h = C.c_void_p(core().ds41_prefix_new(prompt_capacity, turn_capacity, window))
+
+    def __del__(self):
+        try:
+            core().ds41_prefix_free(self.h)
+        except Exception:
+            pass
+
+    def insert(self, tokens: Sequence[int], bank: int = 0) -> Tuple[int, int]:
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        ev = C.c_int64(-1)
+        sid = core().ds41_prefix_insert(self.h, t.ctypes.data_as(C.c_void_p), len(t), bank, C.byref(ev))
+        return int(sid), int(ev.value)
+
+    def remove(self, sid: int) -> bool:
+        return core().ds41_prefix_remove(self.h, C.c_int64(sid)) == 0
+
+    def lookup(self, tokens: Sequence[int]):
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        common, frontier, skipped = C.c_int(0), C.c_int(0), C.c_int(0)
+        sid = core().ds41_prefix_lookup(self.h, t.ctypes.data_as(C.c_void_p), len(t), C.byref(common),
+                                        C.byref(frontier), C.byref(skipped))
+        if sid < 0:
+            return None
+        return {"id": int(sid), "common": common.value, "frontier": frontier.value, "skipped": skipped.value,
+                "exact": common.value == frontier.value}
+
+    def live(self, bank: int) -> int:
+        return int(core().ds41_prefix_live(self.h, bank))
+
+
+# ---------------------------------------------------------------------------------------------- KV allocator
+class KvAllocator:
+    def __init__(self, n_pages: int, n_slots: int, page_tokens: int = 64):
+        self.h = C.c_void_p(core().ds41_kv_new(n_pages, n_slots, page_tokens))
+        self.page_tokens = page_tokens
+        self.n_pages = n_pages
+
+    def __del__(self):
+        try:
+            core().ds41_kv_free(self.h)
+        except Exception:
+            pass
+
+    @property
+    def free_pages(self) -> int:
+        return int(core().ds41_kv_free_pages(self.h))
+
+    def admit(self) -> Optional[Tuple[int, int]]:
+        gen = C.c_uint32(0)
+        slot = core().ds41_kv_admit(self.h, C.byref(gen))
+        return None if slot < 0 else (slot, gen.value)
+
+    def ensure(self, slot: int, gen: int, n_tokens: int) -> List[Tuple[int, int]]:
+        cap = (n_tokens + self.page_tokens - 1) // self.page_tokens + 1
+        out = (C.c_int32 * (2 * cap))()
+        r = core().ds41_kv_ensure(self.h, slot, gen, n_tokens, out, cap)
+        if r == -1:
+            raise KeyError("stale lease")
+        if r == -2:
+            raise MemoryError("KV pool exhausted")
+        if r < 0:
+            raise ValueError("ensure failed")
+        return [(out[2 * i], out[2 * i + 1]) for i in range(r)]
+
+    def share(self, slot: int, gen: int, pages: Sequence[int]):
+        a = (C.c_int32 * len(pages))(*pages)
+        if core().ds41_kv_share(self.h, slot, gen, a, len(pages)) != 0:
+            raise ValueError("share failed")
+
+    def make_private(self, slot: int, gen: int, index: int):
+        src, dst = C.c_int32(-1), C.c_int32(-1)
+        r = core().ds41_kv_make_private(self.h, slot, gen, index, C.byref(src), C.byref(dst))
+        if r < 0:
+            raise MemoryError("copy-on-write failed") if r == -2 else KeyError("stale lease or bad index")
+        return None if r == 0 else (src.value, dst.value)
+
+    def retain(self, slot: int, gen: int, n_pages: int) -> List[int]:
+        out = (C.c_int32 * max(n_pages, 1))()
+        r = core().ds41_kv_retain(self.h, slot, gen, n_pages, out)
+        if r < 0:
+            raise KeyError("stale lease")
+        return list(out[:r])
+
+    def release_pages(self, pages: Sequence[int]):
+        a = (C.c_int32 * len(pages))(*pages)
+        core().ds41_kv_release_pages(self.h, a, len(pages))
+
+    def retire(self, slot: int, gen: int) -> bool:
+        return core().ds41_kv_retire(self.h, slot, gen) == 0
+
+    def page_count(self, slot: int) -> int:
+        return int(core().ds41_kv_page_count(self.h, slot))
+
+    def page_ref(self, page: int) -> int:
+        return int(core().ds41_kv_page_ref(self.h, page))
+
+
+def plan_kv_groups(ctx: int, group_tokens: int, slots: int, retained: int, bytes_per_group: int, budget: int) -> int:
+    return int(core().ds41_kv_plan_groups(C.c_longlong(ctx), group_tokens, slots, retained,
+                                          C.c_longlong(bytes_per_group), C.c_longlong(budget)))

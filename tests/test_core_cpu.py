@@ -1,0 +1,173 @@
+"""Host runtime (C++ core) unit tests: sampler oracle, verification rule, Engram hashing, prefix banks, KV leases."""
+import numpy as np
+import pytest
+
+from ds41rt_b200.runtime import core as K
+
+
+# ---------------------------------------------------------------------------------------------- sampler
+def test_greedy_lowest_id_tie_and_mask():
+    logits = np.array([1.0, 3.0, 3.0, 2.0], dtype=np.float32)
+    assert K.sample_token(logits) == 1
+    mask = np.array([0b1101], dtype=np.uint32)        # token 1 disallowed
+    assert K.sample_token(logits, mask) == 2
+    assert K.sample_token(logits, temperature=0.7, top_k=1) == 1
+
+
+def test_greedy_rejects_nonfinite_rows_and_empty_masks():
+    with pytest.raises(K.SamplingError, match="nonfinite"):
+        K.sample_token(np.array([0.0, np.nan], dtype=np.float32))
+    with pytest.raises(K.SamplingError, match="empty"):
+        K.sample_token(np.zeros(40, dtype=np.float32), np.zeros(2, dtype=np.uint32))
+    with pytest.raises(K.SamplingError, match="mask_width"):
+        K.sample_token(np.zeros(40, dtype=np.float32), np.zeros(3, dtype=np.uint32))
+    with pytest.raises(K.SamplingError, match="invalid_temperature"):
+        K.sample_token(np.zeros(4, dtype=np.float32), temperature=-1.0)
+
+
+def test_categorical_follows_cdf_in_token_order():
+    logits = np.log(np.array([0.1, 0.2, 0.3, 0.4], dtype=np.float32))
+    picks = [K.sample_token(logits, temperature=1.0, uniform=u) for u in (0.05, 0.15, 0.45, 0.95)]
+    assert picks == [0, 1, 2, 3]
+
+
+def test_top_k_top_p_min_p_filters():
+    logits = np.log(np.array([0.5, 0.25, 0.15, 0.10], dtype=np.float32))
+    # top_k 2 renormalises over {0,1}: cdf 2/3, 1
+    assert K.sample_token(logits, temperature=1.0, top_k=2, uniform=0.6) == 0
+    assert K.sample_token(logits, temperature=1.0, top_k=2, uniform=0.7) == 1
+    # top_p 0.7: nucleus {0,1} with mass 0.75; target = u * 0.75
+    assert K.sample_token(logits, temperature=1.0, top_p=0.7, uniform=0.99) == 1
+    # min_p 0.4: only tokens with p >= 0.4 * pmax = 0.2 survive -> {0,1}
+    assert K.sample_token(logits, temperature=1.0, min_p=0.4, uniform=0.999) == 1
+
+
+def test_distribution_matches_softmax_statistically():
+    rng = np.random.default_rng(0)
+    logits = rng.normal(size=16).astype(np.float32)
+    p = np.exp(logits / 0.8)
+    p /= p.sum()
+    counts = np.zeros(16)
+    for i in range(4000):
+        counts[K.sample_token(logits, temperature=0.8, uniform=K.sample_uniform(1234, i))] += 1
+    assert np.abs(counts / 4000 - p).max() < 0.03
+
+
+def test_uniform_depends_only_on_seed_and_position():
+    a = [K.sample_uniform(7, i) for i in range(8)]
+    assert a == [K.sample_uniform(7, i) for i in range(8)]
+    assert all(0.0 <= u < 1.0 for u in a) and len(set(a)) == 8
+    assert K.sample_uniform(8, 0) != a[0]
+
+
+# ---------------------------------------------------------------------------------------------- verification
+def test_verify_accept_prefix():
+    r = K.verify_greedy([10, 11, 12, 13], [11, 12, 99, 14], eos=1, remaining=100)
+    assert r["emitted"] == [11, 12, 99] and r["accepted_inputs"] == 3 and not r["eos"]
+    r = K.verify_greedy([10, 11], [50, 51], eos=1, remaining=100)
+    assert r["emitted"] == [50] and r["accepted_inputs"] == 1
+    r = K.verify_greedy([10, 11, 12], [11, 12, 13], eos=1, remaining=100)       # all accepted + bonus
+    assert r["emitted"] == [11, 12, 13] and r["accepted_inputs"] == 3
+
+
+def test_verify_stops_at_eos_and_length():
+    r = K.verify_greedy([10, 1, 12], [1, 12, 13], eos=1, remaining=100)
+    assert r["emitted"] == [1] and r["eos"]
+    r = K.verify_greedy([10, 11, 12], [11, 12, 13], eos=1, remaining=2)
+    assert r["emitted"] == [11, 12] and r["length_limit"]
+    with pytest.raises(ValueError):
+        K.verify_greedy([1, 2], [2, 3], eos=1, remaining=5)           # anchor is EOS
+    with pytest.raises(ValueError):
+        K.verify_greedy(list(range(9)), list(range(9)), eos=1000, remaining=5)
+
+
+# ---------------------------------------------------------------------------------------------- Engram
+def test_engram_primes_and_hash_layout():
+    p = K.engram_primes()
+    assert p[0, 0] == 16000057 and (np.diff(p.reshape(-1).astype(np.int64)) > 0).all()
+    h = K.engram_hash([5, 6, 7, 8])
+    offs = np.concatenate([[0], np.cumsum(p[0].astype(np.int64))[:-1]])
+    assert ((h[0].astype(np.int64) - offs) >= 0).all() and ((h[0].astype(np.int64) - offs) < p[0].astype(np.int64)).all()
+    # order-1 columns depend only on the first two tokens
+    h2 = K.engram_hash([5, 6, 70, 80])
+    assert (h[:, :8] == h2[:, :8]).all() and (h[:, 8:] != h2[:, 8:]).any()
+
+
+def test_engram_history_is_transactional_and_chunking_invariant():
+    toks = list(np.random.default_rng(1).integers(0, 99092, size=12))
+    a = K.EngramHistory(pad_id=2)
+    whole = a.prepare(toks)
+    b = K.EngramHistory(pad_id=2)
+    parts = []
+    for i in range(0, 12, 5):
+        chunk = toks[i:i + 5]
+        parts.append(b.prepare(chunk))
+        b.commit(chunk, len(chunk))
+    assert (np.concatenate(parts) == whole).all() and b.position == 12
+    # rejected speculative rows leave no trace
+    c = K.EngramHistory(pad_id=2)
+    c.commit(toks[:4], 4)
+    spec = c.prepare(toks[4:9])
+    c.commit(toks[4:9], 2)
+    again = c.prepare(toks[6:9])
+    assert (again == spec[2:5]).all()
+    # image rows (negative ids) hash to zero and reset the lookback
+    d = K.EngramHistory(pad_id=2)
+    hz = d.prepare([3, -1, 4])
+    assert (hz[1] == 0).all() and (hz[2] == K.engram_hash([4, 2, 2, 2])).all()
+
+
+# ---------------------------------------------------------------------------------------------- prefix banks
+def test_prefix_reuse_rule_and_lru():
+    banks = K.PrefixBanks(prompt_capacity=2, turn_capacity=2, window=128)
+    base = list(range(1000, 1600))
+    sid, _ = banks.insert(base, K.PrefixBanks.PROMPT)
+    hit = banks.lookup(base + [1, 2, 3])                       # exact ancestor
+    assert hit["id"] == sid and hit["exact"] and hit["skipped"] == 600
+    hit = banks.lookup(base[:401] + [7, 7, 7])                 # partial: (401//2*2) - 128
+    assert hit["id"] == sid and not hit["exact"] and hit["common"] == 401 and hit["skipped"] == 272
+    assert banks.lookup(base[:100] + [9]) is None              # too short to pay for the replay window
+    assert banks.lookup([5, 6, 7]) is None
+    s2, ev = banks.insert([1, 2, 3] * 100, K.PrefixBanks.PROMPT)
+    assert ev == -1
+    banks.lookup(base)                                          # touch sid -> s2 becomes LRU
+    s3, ev = banks.insert([4, 5] * 100, K.PrefixBanks.PROMPT)
+    assert ev == s2 and banks.live(0) == 2
+    assert banks.lookup([1, 2, 3] * 100) is None
+    t1, ev = banks.insert(base + [42], K.PrefixBanks.TURN)      # other bank is independent
+    assert ev == -1 and banks.live(1) == 1
+    assert banks.lookup(base + [42, 43])["id"] == t1            # longer exact ancestor wins
+    assert banks.remove(t1) and not banks.remove(t1)
+
+
+# ---------------------------------------------------------------------------------------------- KV allocator
+def test_kv_leases_pages_and_cow():
+    kv = K.KvAllocator(n_pages=8, n_slots=2, page_tokens=64)
+    slot, gen = kv.admit()
+    new = kv.ensure(slot, gen, 130)
+    assert [i for i, _ in new] == [0, 1, 2] and kv.free_pages == 5
+    assert kv.ensure(slot, gen, 100) == []
+    pages = kv.retain(slot, gen, 2)                              # snapshot keeps two pages
+    assert all(kv.page_ref(p) == 2 for p in pages)
+    s2, g2 = kv.admit()
+    kv.share(s2, g2, pages)
+    assert kv.page_count(s2) == 2 and kv.page_ref(pages[0]) == 3
+    moved = kv.make_private(s2, g2, 1)                           # copy-on-write before writing page 1
+    assert moved is not None and moved[0] == pages[1] and kv.page_ref(pages[1]) == 2
+    assert kv.make_private(s2, g2, 1) is None
+    with pytest.raises(MemoryError):
+        kv.ensure(s2, g2, 64 * 20)
+    assert kv.retire(slot, gen) and not kv.retire(slot, gen)     # stale generation rejected
+    with pytest.raises(KeyError):
+        kv.ensure(slot, gen, 10)
+    kv.retire(s2, g2)
+    kv.release_pages(pages)
+    assert kv.free_pages == 8
+    assert kv.admit() is not None and kv.admit() is not None and kv.admit() is None
+
+
+def test_kv_pool_plan():
+    # 64K context, 512-token groups, 16 slots, 20+20 retained snapshots
+    want = K.plan_kv_groups(65536, 512, 16, 40, 455680, 1 << 40)
+    assert want == 128 * 18 + 16 + 80
+    assert K.plan_kv_groups(65536, 512, 16, 40, 455680, 455680 * 100) == 100
