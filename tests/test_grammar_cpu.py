@@ -1,0 +1,136 @@
+"""Grammar engine: JSON-schema / regex matching and token masks vs brute force."""
+import json
+
+import numpy as np
+import pytest
+
+from ds41rt_b200.runtime.grammar import (Grammar, GrammarError, Matcher, TokenConstraint, Vocab, mask_allows)
+
+SCHEMA8 = {
+    "type": "object",
+    "properties": {
+        "name": {"type": "string"},
+        "age": {"type": "integer"},
+        "tier": {"enum": ["free", "pro", "enterprise"]},
+        "active": {"type": "boolean"},
+        "score": {"type": "number"},
+        "tags": {"type": "array", "items": {"type": "string"}, "maxItems": 3},
+        "address": {"type": "object",
+                    "properties": {"city": {"type": "string"}, "zip": {"type": "string", "pattern": "[0-9]{5}"}},
+                    "required": ["city", "zip"]},
+        "note": {"type": ["string", "null"]},
+    },
+    "required": ["name", "age", "tier", "active", "address"],
+}
+
+
+def _ok(g, text):
+    return Matcher(g).accept_bytes(text.encode()) 
+
+
+def _complete(g, text):
+    m = Matcher(g)
+    return m.accept_bytes(text.encode()) and m.can_finish
+
+
+def test_schema_accepts_valid_documents_and_rejects_invalid():
+    g = Grammar.json_schema(SCHEMA8)
+    good = {"name": "Ada", "age": 36, "tier": "pro", "active": True, "score": -1.5e3, "tags": ["a", "b"],
+            "address": {"city": "Paris", "zip": "75001"}, "note": None}
+    assert _complete(g, json.dumps(good))
+    assert _complete(g, json.dumps(good, indent=2))
+    minimal = {"name": "x", "age": 0, "tier": "free", "active": False, "address": {"city": "", "zip": "00000"}}
+    assert _complete(g, json.dumps(minimal))
+    assert not _complete(g, json.dumps({k: v for k, v in minimal.items() if k != "age"}))     # required missing
+    bad = dict(minimal, tier="gold")
+    assert not _complete(g, json.dumps(bad))
+    bad = dict(minimal, age=1.5)
+    assert not _complete(g, json.dumps(bad))
+    bad = dict(minimal, address={"city": "x", "zip": "123"})
+    assert not _complete(g, json.dumps(bad))
+    bad = dict(good, tags=["a", "b", "c", "d"])
+    assert not _complete(g, json.dumps(bad))
+    assert not _complete(g, json.dumps(good)[:-1])            # prefix is accepted but cannot finish
+    assert _ok(g, json.dumps(good)[:-1])
+    assert not _ok(g, '{"age"')                                # declared order: name comes first
+    assert not _ok(g, "{" + " " * 17)                          # whitespace bounded to 16
+
+
+def test_refs_anyof_and_free_form():
+    schema = {"$defs": {"node": {"type": "object", "properties": {"v": {"type": "integer"},
+                                                                    "next": {"anyOf": [{"$ref": "#/$defs/node"},
+                                                                                       {"type": "null"}]}},
+                                 "required": ["v", "next"]}},
+              "$ref": "#/$defs/node"}
+    g = Grammar.json_schema(schema)
+    assert _complete(g, '{"v":1,"next":{"v":2,"next":null}}')
+    assert not _complete(g, '{"v":1,"next":{"v":2}}')
+    any_obj = Grammar.json_object()
+    assert _complete(any_obj, '{"a":[1,2,{"b":"c\\n"}],"d":{}}')
+    assert not _complete(any_obj, '[1]')
+    with pytest.raises(GrammarError):
+        Grammar.json_schema({"type": "frobnicate"})
+    with pytest.raises(GrammarError):
+        Grammar("{not json")
+
+
+def test_regex_and_until():
+    g = Grammar.regex(r"(foo|ba+r)-[0-9]{2,3}\.[a-c]?x")
+    assert _complete(g, "foo-12.x") and _complete(g, "baaar-123.bx")
+    assert not _complete(g, "foo-1.x") and not _complete(g, "bar-1234.x") and not _complete(g, "foo-12.dx")
+    u = Grammar({"seq": [{"until": "</end>"}, {"lit": "!"}]})
+    assert _complete(u, "free <text </en </end>!")
+    assert not _complete(u, "abc</end>?")
+    m = Matcher(u)
+    assert m.accept_bytes(b"abc</end>") and not m.can_finish and m.accept_bytes(b"!") and m.terminated
+
+
+def _toy_vocab():
+    pieces = ['{', '}', '"', ':', ',', ' ', '\n', '{"', '":', '",', 'name', 'age', 'tier', 'active', 'address', 'city',
+              'zip', 'true', 'false', 'null', 'free', 'pro', 'enterprise', 'A', 'da', '0', '1', '23', '75001', '-',
+              '.', 'e', '[', ']', '"}', '"name"', 'x' * 3, 'tru', 'e,', '": "', '{"name": "']
+    toks = [b""] + [p.encode() for p in pieces]          # id 0 = EOS (no bytes)
+    return Vocab(toks), toks
+
+
+def test_token_mask_equals_brute_force_and_fork_is_independent():
+    vocab, toks = _toy_vocab()
+    g = Grammar.json_schema(SCHEMA8)
+    m = Matcher(g)
+    rng = np.random.default_rng(0)
+    steps = 0
+    while steps < 60 and not m.terminated:
+        mask = m.fill_mask(vocab, stop_token=0)
+        brute = [i for i in range(1, vocab.size) if m.fork().accept_bytes(toks[i])]
+        got = [i for i in range(1, vocab.size) if mask_allows(mask, i)]
+        assert got == brute
+        assert mask_allows(mask, 0) == m.can_finish
+        if not brute:
+            break
+        f = m.fork()
+        pick = int(rng.choice(brute))
+        assert m.accept_token(vocab, pick)
+        assert f.fill_mask(vocab, 0).tolist() == mask.tolist()        # the fork did not move
+        steps += 1
+    assert steps > 10
+
+
+def test_token_constraint_thinking_and_proposals():
+    vocab, toks = _toy_vocab()
+    think_end = vocab.size - 1
+    ids = {t: i for i, t in enumerate(toks)}
+    g = Grammar.json_schema({"type": "object", "properties": {"name": {"type": "string"}}, "required": ["name"]})
+    c = TokenConstraint(vocab, g, eos=0, think_end=think_end, thinking=True)
+    m = c.mask()
+    assert not mask_allows(m, 0) and mask_allows(m, 5) and mask_allows(m, think_end)
+    assert c.accept(ids[b"pro"]) and c.accept(think_end) and not c.in_thinking
+    m = c.mask()
+    assert mask_allows(m, ids[b'{']) and mask_allows(m, ids[b'{"']) and not mask_allows(m, ids[b'pro'])
+    seq = [ids[b'{"'], ids[b'name'], ids[b'":'], ids[b'"'], ids[b'A'], ids[b'"}']]
+    assert c.truncate_proposal(seq + [ids[b'pro']]) == seq            # trimmed at the first rejected token only
+    assert c.accept(seq[0])                                            # the anchor is committed first
+    masks = c.row_masks(seq[:3])
+    assert len(masks) == 3 and mask_allows(masks[0], ids[b'name']) and mask_allows(masks[2], ids[b'"'])
+    for t in seq[1:]:
+        assert c.accept(t)
+    assert mask_allows(c.mask(), 0) and c.accept(0) and c.finished
