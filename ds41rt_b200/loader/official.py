@@ -1,0 +1,101 @@
+"""Conversion between the official on-disk layout and the engine's name -> fp32 tensor dict.
+
+`export_official` quantises an fp32 weight dict into the official layout (FP8+UE8M0 32x32 dense, FP4+UE8M0/32 routed
+experts or the NVFP4 variant) and writes sharded safetensors + index; `load_official` reads a validated catalog back
+into fp32 (dequantised) tensors, optionally only one rank's shard.  Used for small models and tests; the large-model
+path streams shards straight into `EngineWeights` tensors.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Dict, Optional
+
+import torch
+
+from ..config import ModelConfig
+from ..ops import quant_ref as Q
+from .catalog import Catalog, expected_tensors
+from .safetensors_io import write_safetensors
+
+
+def _quantise(name: str, spec, w: Dict[str, torch.Tensor], variant: str):
+    dt, shape = spec
+    base, _, leaf = name.rpartition(".")
+    if dt == "F8_E4M3" and leaf == "weight":
+        q, _ = Q.quant_weight_mxfp8_32x32(w[name])
+        return q
+    if dt == "F8_E8M0" and leaf == "scale":
+        src = w[base + ".weight"]
+        if ".ffn.experts." in name:
+            return Q.quant_mxfp4(src, 32)[1]
+        if ".engram.embed" in name:
+            return Q.quant_mxfp8(src, 32)[1]
+        return Q.quant_weight_mxfp8_32x32(src)[1]
+    if dt == "I8":
+        return Q.quant_mxfp4(w[name], 32)[0].view(torch.int8)
+    if dt == "U8" and leaf == "weight":
+        return Q.quant_nvfp4(w[name])[0]
+    if leaf == "weight_scale":
+        return Q.quant_nvfp4(w[base + ".weight"])[1]
+    if leaf == "weight_scale_2":
+        return Q.quant_nvfp4(w[base + ".weight"])[2].reshape(())
+    if leaf == "input_scale":
+        return torch.tensor(1.0)
+    t = w[name]
+    return t.to(torch.bfloat16) if dt == "BF16" else t.to(torch.float32)
+
+
+def export_official(cfg: ModelConfig, w: Dict[str, torch.Tensor], directory: str, variant: str = "mxfp4",
+                    shards: int = 2, with_vision: bool = False, with_engram: bool = False):
+    os.makedirs(directory, exist_ok=True)
+    want = expected_tensors(cfg, variant, with_vision, with_engram)
+    names = list(want)
+    per = (len(names) + shards - 1) // shards
+    weight_map = {}
+    for s in range(shards):
+        part = names[s * per:(s + 1) * per]
+        if not part:
+            continue
+        fname = f"model-{s + 1:05d}-of-{shards:05d}.safetensors"
+        tensors, dts = {}, {}
+        for n in part:
+            if n.endswith("gate.bias_vl") and n not in w:
+                t = torch.zeros(want[n][1])
+            else:
+                t = _quantise(n, want[n], w, variant)
+            assert tuple(t.shape) == tuple(want[n][1]), (n, t.shape, want[n])
+            tensors[n] = t
+            dts[n] = want[n][0]
+            weight_map[n] = fname
+        write_safetensors(os.path.join(directory, fname), tensors, dts)
+    json.dump({"metadata": {}, "weight_map": weight_map},
+              open(os.path.join(directory, "model.safetensors.index.json"), "w"))
+
+
+def load_official(cat: Catalog, rank: Optional[int] = None, world: int = 1) -> Dict[str, torch.Tensor]:
+    """Dequantised fp32 tensors under the engine's names.  With `rank` given only that rank's shard is read
+    (sliced tensors come back at their sliced shape)."""
+    plan = cat.shard_plan(rank, world) if rank is not None else {n: (None, None) for n in cat.expected}
+    out: Dict[str, torch.Tensor] = {}
+    for name, (rows, cols) in plan.items():
+        dt, _ = cat.expected[name]
+        base, _, leaf = name.rpartition(".")
+        if leaf in ("scale", "weight_scale", "weight_scale_2", "input_scale"):
+            continue
+        raw = cat.read(name, rows, cols)
+        if dt == "F8_E4M3" and leaf == "weight":
+            srows, scols = plan[base + ".scale"]
+            e = cat.read(base + ".scale", srows, scols)
+            if ".engram.embed" in name:
+                out[name] = Q.dequant_mxfp8(raw, e, 32)
+            else:
+                out[name] = Q.dequant_weight_mxfp8_32x32(raw, e)
+        elif dt == "I8":
+            out[name] = Q.dequant_mxfp4(raw.view(torch.uint8), cat.read(base + ".scale", rows, None), 32)
+        elif dt == "U8" and leaf == "weight":
+            out[name] = Q.dequant_nvfp4(raw, cat.read(base + ".weight_scale", rows, None),
+                                        cat.read(base + ".weight_scale_2").float())
+        else:
+            out[name] = raw.float()
+    return out

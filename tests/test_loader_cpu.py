@@ -1,0 +1,131 @@
+"""Checkpoint container and catalog: strict validation, sparse-file offsets beyond 4 GiB, official-layout round trip."""
+import json
+import os
+import struct
+
+import pytest
+import torch
+
+from ds41rt_b200.config import ModelConfig
+from ds41rt_b200.loader import Catalog, SafetensorsError, SafetensorsFile, expected_tensors, official_templates, \
+    write_safetensors
+from ds41rt_b200.loader.official import export_official, load_official
+from ds41rt_b200.models.weights import init_weights
+
+
+def _raw(path, header: dict, data_len: int):
+    h = json.dumps(header).encode()
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(h)))
+        f.write(h)
+        f.truncate(8 + len(h) + data_len)
+
+
+def test_roundtrip_and_slices(tmp_path):
+    p = str(tmp_path / "a.safetensors")
+    a = torch.arange(6 * 8, dtype=torch.float32).view(6, 8)
+    b = torch.randn(5, 4).bfloat16()
+    write_safetensors(p, {"a": a, "b": b, "s": torch.tensor(3.5)})
+    f = SafetensorsFile(p)
+    assert torch.equal(f.read("a"), a) and torch.equal(f.read("b"), b) and float(f.read("s")) == 3.5
+    assert torch.equal(f.read("a", rows=(2, 5)), a[2:5])
+    assert torch.equal(f.read("a", cols=(3, 7)), a[:, 3:7])
+    assert torch.equal(f.read("a", rows=(1, 4), cols=(2, 6)), a[1:4, 2:6])
+    with pytest.raises(SafetensorsError):
+        f.read("a", rows=(0, 7))
+
+
+def test_adversarial_headers(tmp_path):
+    p = str(tmp_path / "x.safetensors")
+    ok = {"t": {"dtype": "F32", "shape": [2, 2], "data_offsets": [0, 16]}}
+    _raw(p, ok, 16)
+    SafetensorsFile(p)
+    _raw(p, ok, 20)                                             # trailing bytes
+    with pytest.raises(SafetensorsError, match="trailing"):
+        SafetensorsFile(p)
+    _raw(p, {"t": {"dtype": "F32", "shape": [2, 2], "data_offsets": [0, 12]}}, 12)          # length mismatch
+    with pytest.raises(SafetensorsError, match="does not match"):
+        SafetensorsFile(p)
+    _raw(p, {"t": {"dtype": "F32", "shape": [1], "data_offsets": [0, 4]},
+             "u": {"dtype": "F32", "shape": [1], "data_offsets": [2, 6]}}, 6)               # overlap
+    with pytest.raises(SafetensorsError, match="gap or overlaps"):
+        SafetensorsFile(p)
+    _raw(p, {"t": {"dtype": "F32", "shape": [1], "data_offsets": [4, 8]}}, 8)               # gap at start
+    with pytest.raises(SafetensorsError):
+        SafetensorsFile(p)
+    _raw(p, {"t": {"dtype": "Q4", "shape": [1], "data_offsets": [0, 4]}}, 4)
+    with pytest.raises(SafetensorsError, match="unknown dtype"):
+        SafetensorsFile(p)
+    with open(p, "wb") as fh:
+        fh.write(struct.pack("<Q", 1 << 40))
+    with pytest.raises(SafetensorsError, match="implausible"):
+        SafetensorsFile(p)
+
+
+def test_sparse_file_offsets_beyond_4gib(tmp_path):
+    p = str(tmp_path / "big.safetensors")
+    big = 5 * (1 << 30)
+    hdr = {"pad": {"dtype": "U8", "shape": [big], "data_offsets": [0, big]},
+           "tail": {"dtype": "F32", "shape": [4, 4], "data_offsets": [big, big + 64]}}
+    _raw(p, hdr, big + 64)
+    want = torch.arange(16, dtype=torch.float32).view(4, 4)
+    f = SafetensorsFile(p)
+    with open(p, "r+b") as fh:
+        fh.seek(f.data_start + big)
+        fh.write(want.numpy().tobytes())
+    assert torch.equal(f.read("tail"), want)
+    assert torch.equal(f.read("tail", rows=(1, 3), cols=(1, 4)), want[1:3, 1:4])
+
+
+def test_official_flash_catalog_shape():
+    cfg = ModelConfig.flash()
+    want = expected_tensors(cfg)
+    assert want["layers.0.attn.wq_b.weight"] == ("F8_E4M3", (32768, 1280))
+    assert want["layers.0.attn.wo_a.scale"] == ("F8_E8M0", (256, 128))
+    assert want["layers.5.ffn.experts.383.w2.weight"] == ("I8", (5120, 1152))
+    assert want["layers.1.engram.wkv.weight"] == ("F8_E4M3", (25600, 6144))
+    assert want["mtp.0.main_proj.scale"] == ("F8_E8M0", (160, 480))
+    assert want["aligner.w1.weight"] == ("BF16", (5120, 9216))
+    assert len(want) == 96085                       # tensor count of the official checkpoint
+    assert len(official_templates(cfg)) == 116
+
+
+def test_official_layout_roundtrip_and_strict_catalog(tmp_path):
+    cfg = ModelConfig.tiny()
+    w = init_weights(cfg, seed=0)
+    d = str(tmp_path / "ckpt")
+    export_official(cfg, w, d, shards=3)
+    cat = Catalog(d, cfg, with_vision=False, with_engram=False)
+    got = load_official(cat)
+    for name in ("layers.0.attn.wq_a.weight", "layers.1.ffn.experts.3.w1.weight", "embed.weight", "layers.0.hc_attn_fn"):
+        ref = w[name]
+        err = float((got[name] - ref).abs().max())
+        tol = 0.26 * float(ref.abs().max()) if ".experts." in name else 0.07 * float(ref.abs().max()) + 1e-3
+        assert err <= tol, (name, err)
+    # one rank's shard of two: sliced shapes and only its experts
+    part = load_official(cat, rank=1, world=2)
+    assert part["layers.0.attn.wq_b.weight"].shape == (cfg.n_heads // 2 * cfg.head_dim, cfg.q_lora)
+    assert torch.equal(part["layers.0.attn.wq_b.weight"], got["layers.0.attn.wq_b.weight"][512:])
+    assert part["layers.0.attn.wo_b.weight"].shape == (cfg.hidden, cfg.o_lora)
+    assert "layers.0.ffn.experts.3.w1.weight" not in part and "layers.0.ffn.experts.12.w1.weight" in part
+    assert cat.shard_bytes(0, 2) < sum(e.nbytes for f in cat.files.values() for e in f.entries.values())
+    # strictness: a renamed tensor is both "missing" and "unknown"
+    idx = os.path.join(d, "model.safetensors.index.json")
+    doc = json.load(open(idx))
+    doc["weight_map"]["bogus.weight"] = doc["weight_map"].pop("norm.weight")
+    json.dump(doc, open(idx, "w"))
+    with pytest.raises(SafetensorsError):
+        Catalog(d, cfg, with_vision=False, with_engram=False)
+
+
+def test_nvfp4_variant_catalog(tmp_path):
+    cfg = ModelConfig.tiny()
+    w = init_weights(cfg, seed=1)
+    d = str(tmp_path / "nv")
+    export_official(cfg, w, d, variant="nvfp4", shards=1)
+    cat = Catalog(d, cfg, variant="nvfp4", with_vision=False, with_engram=False)
+    got = load_official(cat)
+    ref = w["layers.0.ffn.experts.0.w2.weight"]
+    assert float((got["layers.0.ffn.experts.0.w2.weight"] - ref).abs().max()) < 0.2 * float(ref.abs().max())
+    with pytest.raises(SafetensorsError):
+        Catalog(d, cfg, variant="mxfp4", with_vision=False, with_engram=False)
