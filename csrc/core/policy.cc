@@ -1,0 +1,126 @@
+// dSpark verification-length policy (host runtime).
+//
+// Chooses how many draft rows to verify per round from an online cost/benefit model:
+//   benefit(w) = expected emitted tokens = 1 + sum_{j=1..w} prod_{i<=j} a_i      (a_i = calibrated acceptance at depth i)
+//   cost(w)    = t_fixed + t_row * (1 + w) + t_draft(w)                          (fitted from device-timed rounds)
+// and picks argmax benefit/cost.  Acceptance per depth is an exponentially weighted frequency, optionally conditioned
+// on the drafter's confidence through a Platt-style logistic calibration.  Until enough rounds are observed the
+// policy verifies everything (warm-up: 12 rounds).  Times come from CUDA events, never host clocks.
+// Behavioural counterpart of rust/crates/ds41rt-core/src/dspark_policy.rs:449-874 and
+// docs/dspark-bandwidth-policy.md:31-140 of the reference (whose cost model is bandwidth balance over RDMA workers;
+// here the cost terms are the NVLink-box step times).
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <vector>
+
+namespace {
+
+struct Policy {
+  int max_width;
+  int warmup_rounds;
+  int rounds = 0;
+  std::vector<double> tried, accepted;   // per depth (1-based index - 1), exponentially decayed
+  // least squares of round time against rows: t = t_fixed + t_row * rows
+  double n = 0, sx = 0, sy = 0, sxx = 0, sxy = 0;
+  double draft_us_per_row = 0, draft_n = 0;
+  double decay = 0.98;
+  // Platt calibration of confidence -> acceptance at depth 1: sigmoid(a*c + b), fitted by SGD
+  double pa = 4.0, pb = -2.0;
+  uint64_t hist[16] = {0};
+};
+
+double sigmoid(double x) { return 1.0 / (1.0 + std::exp(-x)); }
+
+}  // namespace
+
+extern "C" {
+
+void* ds41_policy_new(int max_width, int warmup_rounds) {
+  Policy* p = new Policy();
+  p->max_width = std::max(1, std::min(max_width, 15));
+  p->warmup_rounds = warmup_rounds;
+  p->tried.assign(p->max_width, 0.0);
+  p->accepted.assign(p->max_width, 0.0);
+  return p;
+}
+void ds41_policy_free(void* p) { delete static_cast<Policy*>(p); }
+
+// One verified round: `width` drafts were verified, `n_accepted` of them accepted; device times in microseconds.
+void ds41_policy_observe(void* h, int width, int n_accepted, double verify_us, double draft_us, double confidence) {
+  Policy* p = static_cast<Policy*>(h);
+  width = std::max(0, std::min(width, p->max_width));
+  n_accepted = std::max(0, std::min(n_accepted, width));
+  for (int d = 0; d < p->max_width; ++d) { p->tried[d] *= p->decay; p->accepted[d] *= p->decay; }
+  for (int d = 0; d < width; ++d) {
+    if (d <= n_accepted) p->tried[d] += 1.0;          // depth d+1 was reached only if all shallower drafts matched
+    if (d < n_accepted) p->accepted[d] += 1.0;
+  }
+  if (verify_us > 0) {
+    const double x = 1.0 + width;
+    p->n += 1; p->sx += x; p->sy += verify_us; p->sxx += x * x; p->sxy += x * verify_us;
+  }
+  if (draft_us > 0 && width > 0) {
+    p->draft_us_per_row = (p->draft_us_per_row * p->draft_n + draft_us / width) / (p->draft_n + 1);
+    p->draft_n += 1;
+  }
+  if (confidence >= 0.0 && width > 0) {
+    const double y = n_accepted > 0 ? 1.0 : 0.0;
+    const double pr = sigmoid(p->pa * confidence + p->pb);
+    p->pa += 0.05 * (y - pr) * confidence;
+    p->pb += 0.05 * (y - pr);
+  }
+  ++p->hist[std::min(n_accepted, 15)];
+  ++p->rounds;
+}
+
+double ds41_policy_acceptance(void* h, int depth) {
+  Policy* p = static_cast<Policy*>(h);
+  if (depth < 1 || depth > p->max_width) return 0.0;
+  const double t = p->tried[depth - 1];
+  return t < 1e-9 ? 0.5 : p->accepted[depth - 1] / t;
+}
+
+// Number of drafts to verify next round (0..max_width).  `confidence` < 0 means "unknown".
+int ds41_policy_choose(void* h, double confidence) {
+  Policy* p = static_cast<Policy*>(h);
+  if (p->rounds < p->warmup_rounds) return p->max_width;
+  double t_fixed = 0.0, t_row = 1.0;
+  const double den = p->n * p->sxx - p->sx * p->sx;
+  if (p->n >= 2 && std::fabs(den) > 1e-9) {
+    t_row = std::max(0.0, (p->n * p->sxy - p->sx * p->sy) / den);
+    t_fixed = std::max(0.0, (p->sy - t_row * p->sx) / p->n);
+  } else if (p->n >= 1) {
+    t_fixed = p->sy / p->n;      // one width seen so far: treat the pass as flat in rows
+    t_row = 0.0;
+  }
+  int best_w = 0;
+  double best = -1.0, benefit = 1.0, chain = 1.0;
+  for (int w = 0; w <= p->max_width; ++w) {
+    if (w > 0) {
+      double a = ds41_policy_acceptance(h, w);
+      if (w == 1 && confidence >= 0.0) a = 0.5 * a + 0.5 * sigmoid(p->pa * confidence + p->pb);
+      chain *= a;
+      benefit += chain;
+    }
+    const double cost = t_fixed + t_row * (1.0 + w) + p->draft_us_per_row * w + 1e-9;
+    const double score = benefit / cost;
+    if (score > best * (1.0 + 1e-9)) { best = score; best_w = w; }
+  }
+  return best_w;
+}
+
+void ds41_policy_stats(void* h, double* out /*[8]*/, uint64_t* hist16) {
+  Policy* p = static_cast<Policy*>(h);
+  const double den = p->n * p->sxx - p->sx * p->sx;
+  double t_row = 0, t_fixed = p->n > 0 ? p->sy / p->n : 0;
+  if (p->n >= 2 && std::fabs(den) > 1e-9) {
+    t_row = (p->n * p->sxy - p->sx * p->sy) / den;
+    t_fixed = (p->sy - t_row * p->sx) / p->n;
+  }
+  out[0] = p->rounds; out[1] = t_fixed; out[2] = t_row; out[3] = p->draft_us_per_row;
+  out[4] = p->pa; out[5] = p->pb; out[6] = ds41_policy_acceptance(h, 1); out[7] = ds41_policy_acceptance(h, p->max_width);
+  for (int i = 0; i < 16; ++i) hist16[i] = p->hist[i];
+}
+
+}  // extern "C"

@@ -223,3 +223,146 @@ class KvAllocator:
 def plan_kv_groups(ctx: int, group_tokens: int, slots: int, retained: int, bytes_per_group: int, budget: int) -> int:
     return int(core().ds41_kv_plan_groups(C.c_longlong(ctx), group_tokens, slots, retained,
                                           C.c_longlong(bytes_per_group), C.c_longlong(budget)))
+
+
+# ---------------------------------------------------------------------------------------------- admission / lanes
+def _more():
+    c = core()
+    if not getattr(c, "_ds41_more", False):
+        for name in ("ds41_admission_new", "ds41_lanes_new", "ds41_policy_new", "ds41_hostcache_new",
+                     "ds41_stubcopy_new"):
+            getattr(c, name).restype = C.c_void_p
+        c.ds41_policy_acceptance.restype = C.c_double
+        c.ds41_stubcopy_copy.restype = C.c_double
+        c.ds41_stubcopy_now.restype = C.c_double
+        c._ds41_more = True
+    return c
+
+
+class Admission:
+    def __init__(self, queue_cap: int, waiter_cap: int):
+        self.h = C.c_void_p(_more().ds41_admission_new(queue_cap, waiter_cap))
+
+    def reserve(self) -> int:
+        """0 queued, 1 waiting, -1 rejected (HTTP 429)."""
+        return int(core().ds41_admission_reserve(self.h))
+
+    def release(self):
+        core().ds41_admission_release(self.h)
+
+    def stats(self) -> dict:
+        out = (C.c_uint64 * 4)()
+        core().ds41_admission_stats(self.h, out)
+        return {"queued": out[0], "waiting": out[1], "accepted": out[2], "rejected": out[3]}
+
+
+class Lanes:
+    def __init__(self, n_lanes: int = 2):
+        self.n = n_lanes
+        self.h = C.c_void_p(_more().ds41_lanes_new(n_lanes))
+
+    def add(self, rid: int, remaining: int, history: int) -> int:
+        return int(core().ds41_lanes_add(self.h, C.c_int64(rid), remaining, history))
+
+    def update(self, rid: int, remaining: int, history: int):
+        core().ds41_lanes_update(self.h, C.c_int64(rid), remaining, history)
+
+    def retire(self, rid: int) -> int:
+        return int(core().ds41_lanes_retire(self.h, C.c_int64(rid)))
+
+    def lane_of(self, rid: int) -> int:
+        return int(core().ds41_lanes_lane_of(self.h, C.c_int64(rid)))
+
+    def load(self, lane: int) -> int:
+        return int(core().ds41_lanes_load(self.h, lane))
+
+    def plan_round(self, lane: int, draft_len: int, max_rows: int, min_history: int = 0, cap: int = 64):
+        ids = (C.c_int64 * cap)()
+        rows = (C.c_int * cap)()
+        n = core().ds41_lanes_plan_round(self.h, lane, draft_len, max_rows, min_history, ids, rows, cap)
+        return [(int(ids[i]), int(rows[i])) for i in range(n)]
+
+
+class DSparkPolicy:
+    def __init__(self, max_width: int = 4, warmup_rounds: int = 12):
+        self.h = C.c_void_p(_more().ds41_policy_new(max_width, warmup_rounds))
+
+    def observe(self, width: int, accepted: int, verify_us: float, draft_us: float = 0.0, confidence: float = -1.0):
+        core().ds41_policy_observe(self.h, width, accepted, C.c_double(verify_us), C.c_double(draft_us),
+                                   C.c_double(confidence))
+
+    def choose(self, confidence: float = -1.0) -> int:
+        return int(core().ds41_policy_choose(self.h, C.c_double(confidence)))
+
+    def acceptance(self, depth: int) -> float:
+        return float(core().ds41_policy_acceptance(self.h, depth))
+
+    def stats(self) -> dict:
+        out = (C.c_double * 8)()
+        hist = (C.c_uint64 * 16)()
+        core().ds41_policy_stats(self.h, out, hist)
+        return {"rounds": int(out[0]), "t_fixed_us": out[1], "t_row_us": out[2], "draft_us_per_row": out[3],
+                "platt": [out[4], out[5]], "acceptance_first": out[6], "acceptance_last": out[7],
+                "accepted_histogram": list(hist)}
+
+
+class HostCache:
+    METRICS = ("free_pages", "snapshots", "stored", "shared", "restored", "evictions", "hits", "misses", "deferred",
+               "failed")
+
+    def __init__(self, n_pages: int, page_bytes: int, store_budget: int = 1 << 62, restore_budget: int = 1 << 62):
+        self.h = C.c_void_p(_more().ds41_hostcache_new(n_pages, C.c_uint64(page_bytes), C.c_uint64(store_budget),
+                                                       C.c_uint64(restore_budget)))
+        self.page_bytes = page_bytes
+
+    def tick(self):
+        core().ds41_hostcache_tick(self.h)
+
+    def store(self, sid: int, keys: Sequence[int], tokens: int = 0):
+        n = len(keys)
+        k = (C.c_uint64 * n)(*[x & (2 ** 64 - 1) for x in keys])
+        pages = (C.c_int32 * n)()
+        need = (C.c_uint8 * n)()
+        r = core().ds41_hostcache_store(self.h, C.c_int64(sid), k, n, C.c_uint64(tokens), pages, need)
+        if r <= 0:
+            return r, [], []
+        return r, list(pages), [bool(x) for x in need]
+
+    def abort(self, sid: int):
+        core().ds41_hostcache_abort(self.h, C.c_int64(sid))
+
+    def restore(self, sid: int, cap: int = 4096):
+        pages = (C.c_int32 * cap)()
+        r = core().ds41_hostcache_restore(self.h, C.c_int64(sid), pages, cap)
+        return r, list(pages[:max(r, 0)])
+
+    def contains(self, sid: int) -> bool:
+        return bool(core().ds41_hostcache_contains(self.h, C.c_int64(sid)))
+
+    def drop(self, sid: int) -> bool:
+        return core().ds41_hostcache_drop(self.h, C.c_int64(sid)) == 0
+
+    def metrics(self) -> dict:
+        out = (C.c_uint64 * 10)()
+        core().ds41_hostcache_metrics(self.h, out)
+        return dict(zip(self.METRICS, [int(x) for x in out]))
+
+    def check(self) -> int:
+        return int(core().ds41_hostcache_check(self.h))
+
+
+class StubCopyEngine:
+    """Copy engine on a virtual clock (latency + bytes / bandwidth) with one-shot failure injection."""
+
+    def __init__(self, latency_us: float = 10.0, gb_per_s: float = 25.0):
+        self.h = C.c_void_p(_more().ds41_stubcopy_new(C.c_double(latency_us), C.c_double(gb_per_s)))
+
+    def fail_at(self, op: int):
+        core().ds41_stubcopy_fail_at(self.h, C.c_int64(op))
+
+    def copy(self, nbytes: int) -> float:
+        return float(core().ds41_stubcopy_copy(self.h, C.c_uint64(nbytes)))
+
+    @property
+    def now_us(self) -> float:
+        return float(core().ds41_stubcopy_now(self.h))

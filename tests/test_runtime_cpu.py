@@ -1,0 +1,123 @@
+"""Host runtime: admission, lanes, dSpark policy, host snapshot cache with a stub copy engine (no GPU)."""
+import random
+
+import pytest
+
+from ds41rt_b200.runtime import core as K
+
+
+def test_admission_bounds_queue_and_waiters():
+    a = K.Admission(queue_cap=2, waiter_cap=1)
+    assert [a.reserve() for _ in range(4)] == [0, 0, 1, -1]
+    a.release()                      # the waiter takes the freed place
+    assert a.stats()["waiting"] == 0 and a.stats()["queued"] == 2
+    assert a.reserve() == 1 and a.reserve() == -1
+    assert a.stats()["rejected"] == 2
+
+
+def test_lanes_balance_and_round_plan():
+    l = K.Lanes(2)
+    lanes = [l.add(i, remaining=10, history=500) for i in range(5)]
+    assert lanes == [0, 1, 0, 1, 0] and l.load(0) == 3 and l.load(1) == 2
+    l.retire(1)
+    l.retire(3)                      # lane 1 empty -> one request moves over
+    assert abs(l.load(0) - l.load(1)) <= 1
+    l2 = K.Lanes(1)
+    l2.add(10, remaining=100, history=500)
+    l2.add(11, remaining=1, history=500)       # one token left: anchor only
+    l2.add(12, remaining=100, history=3)       # short history: anchor only
+    l2.add(13, remaining=3, history=500)       # never verify more rows than tokens remain
+    assert l2.plan_round(0, draft_len=4, max_rows=64, min_history=16) == [(10, 5), (11, 1), (12, 1), (13, 3)]
+    assert l2.plan_round(0, draft_len=4, max_rows=7, min_history=16) == [(10, 5), (11, 1), (12, 1)]
+
+
+def test_policy_matches_exhaustive_search_after_warmup():
+    rng = random.Random(0)
+    pol = K.DSparkPolicy(max_width=4, warmup_rounds=12)
+    assert pol.choose() == 4
+    # environment: acceptance 0.9 per depth, pass time 1000 us + 150 us per row, drafting 20 us per row
+    acc = 0.9
+    for _ in range(400):
+        w = rng.randint(0, 4)
+        n = 0
+        while n < w and rng.random() < acc:
+            n += 1
+        pol.observe(w, n, 1000 + 150 * (1 + w), 20.0 * w)
+    best, best_w = -1, 0
+    for w in range(5):
+        benefit = 1 + sum(acc ** j for j in range(1, w + 1))
+        cost = 1000 + 150 * (1 + w) + 20 * w
+        if benefit / cost > best:
+            best, best_w = benefit / cost, w
+    assert pol.choose() == best_w == 4
+    assert abs(pol.acceptance(1) - acc) < 0.1
+    # hopeless drafts: stop verifying them
+    bad = K.DSparkPolicy(max_width=4, warmup_rounds=4)
+    for _ in range(100):
+        bad.observe(4, 0, 1000 + 150 * 5, 80.0)
+        bad.observe(0, 0, 1000 + 150, 0.0)
+    assert bad.choose() == 0
+    s = pol.stats()
+    assert s["rounds"] == 400 and abs(s["t_row_us"] - 150) < 5 and abs(s["t_fixed_us"] - 1000) < 20
+
+
+def test_hostcache_sharing_budgets_eviction_and_failure():
+    hc = K.HostCache(n_pages=8, page_bytes=1000, store_budget=5000, restore_budget=3000)
+    r, pages, need = hc.store(1, [11, 12, 13], tokens=192)
+    assert r == 3 and need == [True, True, True]
+    r, pages2, need2 = hc.store(2, [11, 12, 99])            # shares two pages exactly, uses the remaining budget
+    assert r == 3 and need2 == [False, False, True] and pages2[:2] == pages[:2]
+    assert hc.store(3, [21, 22, 23])[0] == 0                # store budget exhausted this tick -> deferred
+    hc.tick()
+    assert hc.store(3, [21, 22, 23])[0] == 3
+    assert hc.restore(1)[0] == 3
+    assert hc.restore(2)[0] == 0                            # restore budget (3000) used up
+    hc.tick()
+    assert hc.restore(2)[0] == 3 and hc.restore(42)[0] == -1
+    # pool has 8 pages, 7 in use: a 3-page snapshot forces eviction of the least recently used one (id 3)
+    assert hc.store(4, [31, 32, 33])[0] == 3
+    assert not hc.contains(3) and hc.contains(1) and hc.contains(2)
+    assert hc.check() == 0
+    # failed copy: the store is rolled back and leaves no pages behind
+    eng = K.StubCopyEngine(latency_us=5, gb_per_s=10)
+    eng.fail_at(1)
+    hc.tick()
+    r, pages, need = hc.store(5, [41, 42])
+    ok = all(eng.copy(1000) >= 0 for n in need if n)
+    assert not ok
+    hc.abort(5)
+    assert not hc.contains(5) and hc.check() == 0 and hc.metrics()["failed"] == 1
+    assert eng.now_us > 0
+
+
+def test_hostcache_randomised_simulation_keeps_invariants():
+    rng = random.Random(7)
+    hc = K.HostCache(n_pages=32, page_bytes=4096, store_budget=20 * 4096, restore_budget=20 * 4096)
+    eng = K.StubCopyEngine()
+    live = set()
+    for step in range(2000):
+        op = rng.random()
+        sid = rng.randint(0, 40)
+        if op < 0.5:
+            keys = [rng.randint(0, 60) for _ in range(rng.randint(1, 6))]
+            keys = list(dict.fromkeys(keys))
+            r, pages, need = hc.store(sid, keys)
+            if r > 0:
+                if rng.random() < 0.05:
+                    hc.abort(sid)
+                    live.discard(sid)
+                else:
+                    for n in need:
+                        if n:
+                            eng.copy(4096)
+                    live.add(sid)
+        elif op < 0.8:
+            r, pages = hc.restore(sid)
+            assert (r >= 0) == hc.contains(sid)
+        elif op < 0.9:
+            hc.drop(sid)
+        else:
+            hc.tick()
+        assert hc.check() == 0, step
+    m = hc.metrics()
+    assert m["evictions"] > 0 and m["shared"] > 0 and m["hits"] > 0
