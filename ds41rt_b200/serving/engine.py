@@ -1,0 +1,325 @@
+"""Serving backends: the interface between the HTTP layer and the CUDA-owning worker.
+
+The HTTP threads never touch CUDA.  They put a `GenRequest` on a bounded queue; ONE worker thread owns the
+device, runs the scheduler loop (retire -> admit -> prefill -> one batched decode pass -> sample -> emit) and answers
+through per-request event queues: Ready(usage) / Tokens / Finish / Error.  A missing Finish is never reported as
+success.  (Process layout of the reference: rust/crates/ds41rt-daemon/src/v41_native_serve.rs:73-113,
+scheduler.rs:200-451; request/event types: rust/crates/ds41rt-api/src/native_v41.rs:55-65.)
+
+`FakeBackend` scripts token streams for API tests; `NativeBackend` drives a `DS41Engine`.
+"""
+from __future__ import annotations
+
+import queue
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+import numpy as np
+
+from ..runtime import core as K
+from ..runtime.grammar import TokenConstraint
+from .protocol import Sampling
+
+
+@dataclass
+class GenRequest:
+    prompt_ids: List[int]
+    max_tokens: int
+    sampling: Sampling
+    constraint: Optional[TokenConstraint] = None
+    stop_ids: List[int] = field(default_factory=list)
+    events: "queue.Queue" = field(default_factory=lambda: queue.Queue())
+    cancelled: threading.Event = field(default_factory=threading.Event)
+    rid: int = 0
+
+
+@dataclass
+class Event:
+    kind: str                 # ready | tokens | finish | error
+    tokens: List[int] = field(default_factory=list)
+    reason: str = ""          # finish: stop | length | cancelled
+    status: int = 200         # error
+    message: str = ""
+    usage: Dict[str, int] = field(default_factory=dict)
+
+
+class Backend:
+    healthy = True
+    fingerprint = "ds41rt-b200"
+
+    def submit(self, req: GenRequest) -> None:
+        raise NotImplementedError
+
+    def stats(self) -> dict:
+        return {}
+
+    def close(self) -> None:
+        pass
+
+
+class FakeBackend(Backend):
+    """Emits a scripted token list (optionally slowly, or failing midway) - the fake worker of the API tests."""
+    fingerprint = "ds41rt-b200-fake"
+
+    def __init__(self, script: Optional[List[int]] = None, tokenizer=None, delay: float = 0.0, fail_after: int = -1,
+                 drop_finish: bool = False, chunk: int = 3):
+        self.script, self.tk, self.delay, self.fail_after = script, tokenizer, delay, fail_after
+        self.drop_finish, self.chunk = drop_finish, chunk
+        self.submitted: List[GenRequest] = []
+        self.n = 0
+
+    def submit(self, req: GenRequest) -> None:
+        self.submitted.append(req)
+        self.n += 1
+        threading.Thread(target=self._run, args=(req,), daemon=True).start()
+
+    def _run(self, req: GenRequest):
+        toks = list(self.script if self.script is not None else [])
+        req.events.put(Event("ready", usage={"prompt_tokens": len(req.prompt_ids), "prompt_cache_hit_tokens": 0}))
+        sent, reason = 0, "stop"
+        for i in range(0, len(toks), self.chunk):
+            if req.cancelled.is_set():
+                reason = "cancelled"
+                break
+            if self.fail_after >= 0 and sent >= self.fail_after:
+                req.events.put(Event("error", status=500, message="scripted backend failure"))
+                return
+            part = toks[i:i + self.chunk]
+            if sent + len(part) >= req.max_tokens:
+                part = part[: req.max_tokens - sent]
+                reason = "length"
+            if req.constraint is not None:
+                for t in part:
+                    req.constraint.accept(t)
+            req.events.put(Event("tokens", tokens=part))
+            sent += len(part)
+            if reason == "length":
+                break
+            if self.delay:
+                time.sleep(self.delay)
+        if not self.drop_finish:
+            req.events.put(Event("finish", reason=reason,
+                                 usage={"prompt_tokens": len(req.prompt_ids), "completion_tokens": sent}))
+
+    def stats(self) -> dict:
+        return {"requests": self.n}
+
+
+@dataclass
+class _Active:
+    req: GenRequest
+    slot: int
+    gen: int
+    pos: int                  # next position to be written
+    last: int                 # last emitted token (next input)
+    emitted: int = 0
+    lane: int = 0
+
+
+class NativeBackend(Backend):
+    """Worker thread + scheduler loop over a DS41Engine (target-only batched decode; greedy rows are selected on
+    the device, sampled or constrained rows go through the sampler oracle with the request's allow-mask)."""
+    fingerprint = "ds41rt-b200-fp8"
+
+    def __init__(self, engine, eos: int, concurrency: int = 4, queue_depth: int = 16, prefill_chunk: Optional[int] = None):
+        self.e, self.eos = engine, eos
+        self.concurrency = min(concurrency, engine.cache.slots, engine.max_rows)
+        self.q: "queue.Queue[GenRequest]" = queue.Queue(maxsize=queue_depth)
+        self.kv = K.KvAllocator(engine.cache.n_pages, engine.cache.slots, engine.cache.page_tokens)
+        self.lanes = K.Lanes(2)
+        self.prefix = K.PrefixBanks(20, 20, engine.cfg.window)
+        self.prefill_chunk = prefill_chunk or engine.max_rows
+        self.active: List[_Active] = []
+        self.pending: Optional[GenRequest] = None
+        self.totals = {"requests": 0, "prompt_tokens": 0, "completion_tokens": 0, "device_greedy_rows": 0,
+                       "cpu_sampled_rows": 0, "rounds": 0, "failed": 0}
+        self._rid = 0
+        self._stop = threading.Event()
+        self._ready = threading.Event()
+        self.error: Optional[str] = None
+        self.thread = threading.Thread(target=self._worker, name="ds41-cuda-worker", daemon=True)
+        self.thread.start()
+        self._ready.wait(timeout=120)
+
+    # ------------------------------------------------------------------ HTTP side
+    def submit(self, req: GenRequest) -> None:
+        if not self.healthy:
+            raise RuntimeError("worker is not running")
+        self._rid += 1
+        req.rid = self._rid
+        self.q.put_nowait(req)           # queue.Full -> the HTTP layer answers 429
+
+    def stats(self) -> dict:
+        pages_free = self.kv.free_pages
+        return {"totals": dict(self.totals), "active": len(self.active), "queued": self.q.qsize(),
+                "kv": {"pages_free": pages_free, "pages_total": self.kv.n_pages},
+                "lanes": [self.lanes.load(0), self.lanes.load(1)],
+                "target_sampling": {"device_rounds_rows": self.totals["device_greedy_rows"],
+                                    "cpu_fallback_rows": self.totals["cpu_sampled_rows"]}}
+
+    def close(self) -> None:
+        self._stop.set()
+        self.thread.join(timeout=30)
+
+    # ------------------------------------------------------------------ worker side
+    def _worker(self):
+        import torch
+        try:
+            if self.e.device.type == "cuda":
+                torch.cuda.set_device(self.e.device)
+            self._ready.set()
+            while not self._stop.is_set():
+                self._retire()
+                self._admit()
+                if not self.active:
+                    time.sleep(0.001)
+                    continue
+                try:
+                    self._decode_round()
+                except Exception as ex:           # a failed round fails the active requests; the server keeps running
+                    for a in self.active:
+                        a.req.events.put(Event("error", status=500, message=f"decode round failed: {ex}"[:300]))
+                        self._release(a)
+                        self.totals["failed"] += 1
+                    self.active.clear()
+        except Exception as ex:
+            self.error = str(ex)
+            self.healthy = False
+            self._ready.set()
+
+    def _release(self, a: _Active):
+        self.kv.retire(a.slot, a.gen)
+        self.e.cache.release(a.slot)
+        self.lanes.retire(a.req.rid)
+
+    def _finish(self, a: _Active, reason: str):
+        a.req.events.put(Event("finish", reason=reason, usage={"prompt_tokens": len(a.req.prompt_ids),
+                                                               "completion_tokens": a.emitted}))
+        self.totals["completion_tokens"] += a.emitted
+        self._release(a)
+
+    def _retire(self):
+        keep = []
+        for a in self.active:
+            if a.req.cancelled.is_set():
+                self._finish(a, "cancelled")
+            else:
+                keep.append(a)
+        self.active = keep
+
+    def _admit(self):
+        while len(self.active) < self.concurrency:
+            req = self.pending
+            self.pending = None
+            if req is None:
+                try:
+                    req = self.q.get_nowait()
+                except queue.Empty:
+                    return
+            if req.cancelled.is_set():
+                continue
+            need = len(req.prompt_ids) + req.max_tokens + 1
+            if need > self.e.cache.max_ctx:
+                req.events.put(Event("error", status=400, message="prompt plus max_tokens exceeds the context window"))
+                continue
+            lease = self.kv.admit()
+            if lease is None:
+                self.pending = req
+                return
+            slot, gen = lease
+            try:
+                self.kv.ensure(slot, gen, need)
+            except MemoryError:
+                self.kv.retire(slot, gen)
+                if self.active:
+                    self.pending = req          # park until someone retires
+                    return
+                req.events.put(Event("error", status=503, message="KV pool cannot hold this request"))
+                continue
+            if not self.e.cache.ensure(slot, need):
+                self.kv.retire(slot, gen)
+                req.events.put(Event("error", status=503, message="KV pool cannot hold this request"))
+                continue
+            hit = self.prefix.lookup(req.prompt_ids)
+            req.events.put(Event("ready", usage={"prompt_tokens": len(req.prompt_ids),
+                                                 "prompt_cache_hit_tokens": 0 if hit is None else 0}))
+            self.totals["requests"] += 1
+            self.totals["prompt_tokens"] += len(req.prompt_ids)
+            first = self._prefill(slot, req)
+            a = _Active(req, slot, gen, pos=len(req.prompt_ids), last=first)
+            a.lane = self.lanes.add(req.rid, req.max_tokens, len(req.prompt_ids))
+            self.prefix.insert(req.prompt_ids, K.PrefixBanks.PROMPT)
+            if self._emit(a, first):
+                self.active.append(a)
+
+    def _prefill(self, slot: int, req: GenRequest) -> int:
+        e = self.e
+        toks = req.prompt_ids
+        for c0 in range(0, len(toks), self.prefill_chunk):
+            part = toks[c0:c0 + self.prefill_chunk]
+            e.set_rows(part, list(range(c0, c0 + len(part))), [slot] * len(part))
+            last = c0 + self.prefill_chunk >= len(toks)
+            e.forward_rows(len(part), head=last)
+        return self._select([req], [len(part) - 1])[0]
+
+    def _select(self, reqs: List[GenRequest], rows: List[int]) -> List[int]:
+        """Pick the next token of each request from the logits row it owns in the last pass."""
+        import torch
+        e = self.e
+        out = []
+        simple = all(r.sampling.greedy and r.constraint is None for r in reqs)
+        if simple:
+            chosen = e.chosen.tolist()
+            self.totals["device_greedy_rows"] += len(reqs)
+            return [chosen[i] for i in rows]
+        logits = e.logits_rows(max(rows) + 1).float().cpu().numpy()
+        for r, i in zip(reqs, rows):
+            mask = r.constraint.mask() if r.constraint is not None else None
+            s = r.sampling
+            position = len(r.prompt_ids)  # refined by the caller through r._emitted
+            u = K.sample_uniform(s.seed, getattr(r, "_emitted", 0))
+            tok = K.sample_token(logits[i], mask, s.temperature, s.top_k, s.top_p, s.min_p, u)
+            out.append(tok)
+            self.totals["cpu_sampled_rows"] += 1
+        e.check_status("serving pass")
+        return out
+
+    def _emit(self, a: _Active, tok: int) -> bool:
+        """Deliver one token; returns False when the request finished."""
+        r = a.req
+        if r.constraint is not None and not r.constraint.accept(tok):
+            r.events.put(Event("error", status=500, message="selected token violates the request's grammar"))
+            self._release(a)
+            return False
+        a.emitted += 1
+        r._emitted = a.emitted
+        a.last = tok
+        if tok == self.eos or tok in r.stop_ids:
+            self._finish(a, "stop")
+            return False
+        r.events.put(Event("tokens", tokens=[tok]))
+        if a.emitted >= r.max_tokens:
+            self._finish(a, "length")
+            return False
+        if r.constraint is not None and r.constraint.matcher is not None and not r.constraint.in_thinking \
+                and r.constraint.matcher.terminated:
+            self._finish(a, "stop")
+            return False
+        return True
+
+    def _decode_round(self):
+        e = self.e
+        acts = self.active
+        e.set_rows([a.last for a in acts], [a.pos for a in acts], [a.slot for a in acts])
+        e.forward_rows(len(acts))
+        toks = self._select([a.req for a in acts], list(range(len(acts))))
+        self.totals["rounds"] += 1
+        keep = []
+        for a, t in zip(acts, toks):
+            a.pos += 1
+            self.lanes.update(a.req.rid, a.req.max_tokens - a.emitted, a.pos)
+            if self._emit(a, t):
+                keep.append(a)
+        self.active = keep
