@@ -272,3 +272,46 @@ extern "C" int ds41_hc_step(const ds41_hc_step_args* a, void* stream) {
   p.wait_flags = a->wait_flags; p.wait_epoch = a->wait_epoch; p.status = a->status;
   return launch_pdl(hc_step_kernel, dim3(a->H / kSlice, a->rows), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant: same kernel, scratch taken from a fixed array inside the library image.
+#include "ds41_noalloc.h"
+
+namespace {
+constexpr size_t kStaticPartialBytes =
+    sizeof(float) * (DS41_HC_STATIC_MAX_H / ds41::kSlice) * DS41_HC_STATIC_MAX_ROWS * ds41::kStride;
+constexpr size_t kStaticXcBytes = sizeof(float) * DS41_HC_STATIC_MAX_ROWS * DS41_HC_STATIC_MAX_H;
+constexpr size_t kStaticTicketBytes = 256;
+constexpr size_t kStaticBytes = kStaticPartialBytes + kStaticXcBytes + kStaticTicketBytes;
+static_assert(kStaticPartialBytes % 256 == 0 && kStaticXcBytes % 256 == 0, "sub-buffers stay 256-byte aligned");
+static_assert(sizeof(unsigned int) * DS41_HC_STATIC_MAX_ROWS <= kStaticTicketBytes, "ticket area too small");
+}  // namespace
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char g_hc_static_scratch[kStaticBytes];
+
+extern "C" int ds41_hc_step_static(const ds41_hc_step_args* a, void* stream) {
+  if (a == nullptr || a->rows <= 0 || a->rows > DS41_HC_STATIC_MAX_ROWS || a->H <= 0 ||
+      a->H > DS41_HC_STATIC_MAX_H || a->H % ds41::kSlice != 0)
+    return cudaErrorInvalidValue;
+  static unsigned char* device_base[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (device_base[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_hc_static_scratch);     // once per device, with that device current
+    if (e != cudaSuccess) return e;
+    device_base[dev] = static_cast<unsigned char*>(p);
+  }
+  unsigned char* base = device_base[dev];
+  ds41_hc_step_args b = *a;
+  b.partial = reinterpret_cast<float*>(base);
+  b.xc = reinterpret_cast<float*>(base + kStaticPartialBytes);
+  b.tickets = reinterpret_cast<unsigned int*>(base + kStaticPartialBytes + kStaticXcBytes);
+  // the array keeps whatever the previous call left: the ticket counters must start at zero
+  e = cudaMemsetAsync(b.tickets, 0, kStaticTicketBytes, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return e;
+  return ds41_hc_step(&b, stream);
+}
