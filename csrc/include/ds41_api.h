@@ -41,6 +41,17 @@ typedef struct ds41_gemm_args {
   int row_w_ld;
   float act_limit;
   int static_operand;   // 1: A is a weight matrix, 2: B is (prefetched ahead of the stream dependency), 0: neither
+  // Fused collectives over NVLink peer memory (out_mode 0/1, batch 1):
+  //  all-gather -> GEMM: A's rows are sharded by rank (ag_rows each, a multiple of 128); a_peers[r] is rank r's shard
+  //    (symmetric memory), fetched tile by tile with TMA once rank r's flag has reached *ag_epoch (bounded wait).
+  //  GEMM -> reduce-scatter: the output rows owned by rank d (rs_rows each) are stored into rs_out[d] at row
+  //    rs_rank * rs_rows + local_row, i.e. every destination receives one slot per source rank to sum in fixed order.
+  int ag_world, ag_rank, ag_rows;
+  int rs_world, rs_rank, rs_rows;
+  const void* a_peers[8];
+  const void* ag_flags;      // DEVICE array of ag_world flag pointers
+  const void* ag_epoch;      // device word
+  void* rs_out[8];
 } ds41_gemm_args;
 
 int ds41_gemm_tc(const ds41_gemm_args* args, void* stream);
@@ -143,6 +154,11 @@ int ds41_argmax_merge(const float* const* vals, const int* const* idxs, int n_ra
 int ds41_decode_feedback(const int* chosen, int* tokens, int* pos, int rows, void* stream);
 int ds41_spec_accept(const int* inputs, const int* chosen, const int* first, const int* count, int reqs,
                      int max_emit, int eos, int* accepted, int* emit, int* n_emit, void* stream);
+
+// ---------------------------------------------------------------------------------------------------
+// Collective epilogues (comm.cu).  slots: fp32 [world][n] (one slot per source rank), summed in rank order.
+int ds41_rs_reduce(const float* slots, int world, long long slot_stride, void* out, int as_bf16, long long n,
+                   const void* wait_flags, const void* wait_epoch, int* status, void* stream);
 
 // ---------------------------------------------------------------------------------------------------
 // dSpark drafter support (dspark.cu)

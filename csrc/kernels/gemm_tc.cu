@@ -22,6 +22,10 @@ constexpr int kBM = 128;
 constexpr int kTileKBytes = 128;       // one 128-byte swizzle span of K per stage
 constexpr int kGemmThreads = 192;
 
+struct PeerMaps {
+  CUtensorMap m[8];
+};
+
 struct GemmParams {
   int M, N, K;            // K in elements
   int batch;
@@ -45,6 +49,12 @@ struct GemmParams {
   int row_w_ld;
   float act_limit;        // mode 4: SwiGLU clamp
   int static_operand;     // 1: A holds weights, 2: B holds weights (may be fetched before the dependency wait)
+  // fused collectives over peer memory (normal orientation: A = activations, rows sharded by rank)
+  int ag_world, ag_rank, ag_rows;         // all-gather -> GEMM: A rows [r*ag_rows, (r+1)*ag_rows) live on rank r
+  const uint32_t* const* ag_flags;        // device array of peer flag pointers ("my shard is ready")
+  const uint32_t* ag_epoch;
+  int rs_world, rs_rank, rs_rows;         // GEMM -> reduce-scatter: output rows of rank d go to rs_out[d], slot rs_rank
+  void* rs_out[8];
   int* status;
 };
 
@@ -74,7 +84,8 @@ struct GemmCfg {
 
 template <int BN, int KIND, int DUAL>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ PeerMaps peer, GemmParams p) {
   using Cfg = GemmCfg<BN, KIND, DUAL>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -101,6 +112,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     batch_run = min(batch_run, *p.n_active);
   }
   const long long tiles = 1ll * m_tiles * n_tiles * p.k_splits * batch_run;
+  // with a fused collective every rank starts on its own rows and walks the peers in ring order
+  const int rot = p.ag_world > 0 ? p.ag_rank * (p.ag_rows / kBM) : (p.rs_world > 0 ? p.rs_rank * (p.rs_rows / kBM) : 0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -155,6 +168,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
     pdl_wait();
+    uint32_t ag_seen = 0;
     for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
       long long r = t;
       const int mt = static_cast<int>(r % m_tiles); r /= m_tiles;
@@ -163,6 +177,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int b = static_cast<int>(r);
       const int kb0 = sp * kb_per_split;
       const int kb1 = min(kb_total, kb0 + kb_per_split);
+      const int mt_eff = rot ? (mt + rot) % m_tiles : mt;
+      const CUtensorMap* mapA = &tmA;
+      int a_row = mt_eff * kBM;
+      if (p.ag_world > 0) {
+        const int src = a_row / p.ag_rows;
+        a_row -= src * p.ag_rows;
+        mapA = &peer.m[src];
+        if (src != p.ag_rank && !((ag_seen >> src) & 1u)) {
+          // the peer's shard must be complete before its tiles are fetched over NVLink
+          if (!flag_wait_ge(p.ag_flags[src], *p.ag_epoch, p.status, 110 + src)) { ok = false; break; }
+          ag_seen |= 1u << src;
+        }
+      }
       for (int kb = kb0; kb < kb1; ++kb) {
         const bool early = prefetched > 0;      // this stage's barrier is armed and its weight tile is in flight
         if (early) --prefetched;
@@ -173,7 +200,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int ba = p.batch_map != nullptr ? p.batch_map[b] : b;
         const int bb = p.b_batch_kind == 0 ? ba : (p.b_batch_kind == 1 ? 0 : b);
         if (!early || p.static_operand != 1) {
-          tma_load_3d(sa, &tmA, &full[stage], kb * Cfg::kBK, mt * kBM, ba);
+          tma_load_3d(sa, mapA, &full[stage], kb * Cfg::kBK, a_row, ba);
           if constexpr (DUAL)
             tma_load_3d(sa + Cfg::kATile, &tmA, &full[stage], kb * Cfg::kBK, p.up_row_offset + mt * kBM, ba);
         }
@@ -275,7 +302,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int b = static_cast<int>(r);
       if (!mbar_wait(&acc_full[acc], acc_phase, p.status, 300)) { ok = false; break; }
       tc_fence_after();
-      const int m = mt * kBM + quad * 32 + lane;
+      const int m = (rot ? (mt + rot) % m_tiles : mt) * kBM + quad * 32 + lane;
+      // reduce-scatter: rows owned by rank d are stored into d's buffer, in the slot of this (source) rank
+      char* rs_base = nullptr;
+      long long rs_row = 0;
+      if (p.rs_world > 0) {
+        const int dst = m / p.rs_rows;
+        rs_base = static_cast<char*>(p.rs_out[dst < p.rs_world ? dst : 0]);
+        rs_row = 1ll * p.rs_rank * p.rs_rows + (m - dst * p.rs_rows);
+      }
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * Cfg::kAccCols;
       const long long obase = b * p.out_batch_stride + sp * p.out_split_stride;
       constexpr int kChunk = BN >= 32 ? 32 : BN;
@@ -299,7 +334,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int n0 = nt * BN + c;
         if (p.out_mode == 0) {
           if (m < p.M) {
-            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + obase + 1ll * m * p.ldo + n0;
+            __nv_bfloat16* o = rs_base != nullptr ? reinterpret_cast<__nv_bfloat16*>(rs_base) + rs_row * p.ldo + n0
+                                                  : reinterpret_cast<__nv_bfloat16*>(p.out) + obase + 1ll * m * p.ldo + n0;
             if (n0 + kChunk <= p.N && (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
 #pragma unroll
               for (int j = 0; j < kChunk; j += 8) {
@@ -322,7 +358,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         } else if (p.out_mode == 1) {
           if (m < p.M) {
-            float* o = reinterpret_cast<float*>(p.out) + obase + 1ll * m * p.ldo + n0;
+            float* o = rs_base != nullptr ? reinterpret_cast<float*>(rs_base) + rs_row * p.ldo + n0
+                                          : reinterpret_cast<float*>(p.out) + obase + 1ll * m * p.ldo + n0;
             if (n0 + kChunk <= p.N && (p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
 #pragma unroll
               for (int j = 0; j < kChunk; j += 4)
@@ -405,8 +442,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 template <int BN, int KIND, int DUAL = 0>
-static cudaError_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
-                               cudaStream_t stream) {
+static cudaError_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const PeerMaps& peer,
+                               const GemmParams& p, int grid, cudaStream_t stream) {
   using Cfg = GemmCfg<BN, KIND, DUAL>;
   static bool configured[64] = {false};
   int dev = 0;
@@ -417,30 +454,30 @@ static cudaError_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, c
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  return launch_pdl(gemm_tc_kernel<BN, KIND, DUAL>, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, tmA, tmB, p);
+  return launch_pdl(gemm_tc_kernel<BN, KIND, DUAL>, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, tmA, tmB, peer, p);
 }
 
 template <int KIND>
-static cudaError_t dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
-                               cudaStream_t stream) {
+static cudaError_t dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap& tmB, const PeerMaps& peer,
+                               const GemmParams& p, int grid, cudaStream_t stream) {
   if (p.out_mode == 4) {
     switch (bn) {
-      case 16: return launch_gemm<16, KIND, 1>(tmA, tmB, p, grid, stream);
-      case 32: return launch_gemm<32, KIND, 1>(tmA, tmB, p, grid, stream);
-      case 64: return launch_gemm<64, KIND, 1>(tmA, tmB, p, grid, stream);
+      case 16: return launch_gemm<16, KIND, 1>(tmA, tmB, peer, p, grid, stream);
+      case 32: return launch_gemm<32, KIND, 1>(tmA, tmB, peer, p, grid, stream);
+      case 64: return launch_gemm<64, KIND, 1>(tmA, tmB, peer, p, grid, stream);
       case 128:
-        if constexpr (KIND != 2) return launch_gemm<128, KIND, 1>(tmA, tmB, p, grid, stream);
+        if constexpr (KIND != 2) return launch_gemm<128, KIND, 1>(tmA, tmB, peer, p, grid, stream);
         return cudaErrorInvalidValue;
       default: return cudaErrorInvalidValue;
     }
   }
   switch (bn) {
-    case 16: return launch_gemm<16, KIND>(tmA, tmB, p, grid, stream);
-    case 32: return launch_gemm<32, KIND>(tmA, tmB, p, grid, stream);
-    case 64: return launch_gemm<64, KIND>(tmA, tmB, p, grid, stream);
-    case 128: return launch_gemm<128, KIND>(tmA, tmB, p, grid, stream);
+    case 16: return launch_gemm<16, KIND>(tmA, tmB, peer, p, grid, stream);
+    case 32: return launch_gemm<32, KIND>(tmA, tmB, peer, p, grid, stream);
+    case 64: return launch_gemm<64, KIND>(tmA, tmB, peer, p, grid, stream);
+    case 128: return launch_gemm<128, KIND>(tmA, tmB, peer, p, grid, stream);
     case 256:
-      if constexpr (KIND != 2) return launch_gemm<256, KIND>(tmA, tmB, p, grid, stream);
+      if constexpr (KIND != 2) return launch_gemm<256, KIND>(tmA, tmB, peer, p, grid, stream);
       return cudaErrorInvalidValue;
     default: return cudaErrorInvalidValue;
   }
@@ -470,16 +507,38 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   const int a_rows = out_mode == 4 ? a->up_row_offset + M : M;           // dual tiles address gate and up rows
   const int a_batches = a->a_batches > 0 ? a->a_batches : batch;
   const int b_batches = a->b_batch_kind == 1 ? 1 : (a->b_batch_kind == 0 ? a_batches : batch);
-  cudaError_t e = make_tensor_map_3d(&tmA, a->A, dt, K, a_rows, a_batches, a->lda * elem, a->a_batch_stride * elem,
-                                     bk, kBM, true);
+  const void* a_base = a->ag_world > 0 ? a->a_peers[a->ag_rank] : a->A;
+  cudaError_t e = make_tensor_map_3d(&tmA, a_base, dt, K, a->ag_world > 0 ? a->ag_rows : a_rows, a_batches, a->lda * elem,
+                                     a->a_batch_stride * elem, bk, kBM, true);
   if (e != cudaSuccess) return e;
   e = make_tensor_map_3d(&tmB, a->B, dt, K, N, b_batches, a->ldb * elem, a->b_batch_stride * elem, bk, bn, true);
   if (e != cudaSuccess) return e;
+  PeerMaps peer{};
+  if (a->ag_world > 0) {
+    if (a->ag_world > 8 || a->ag_rows <= 0 || a->ag_rows % kBM != 0 || M != a->ag_world * a->ag_rows || batch != 1 ||
+        out_mode > 1 || a->ag_flags == nullptr || a->ag_epoch == nullptr)
+      return cudaErrorInvalidValue;
+    for (int r = 0; r < a->ag_world; ++r) {
+      if (a->a_peers[r] == nullptr) return cudaErrorInvalidValue;
+      e = make_tensor_map_3d(&peer.m[r], a->a_peers[r], dt, K, a->ag_rows, 1, a->lda * elem, 0, bk, kBM, true);
+      if (e != cudaSuccess) return e;
+    }
+  }
+  if (a->rs_world > 0) {
+    if (a->rs_world > 8 || a->rs_rows <= 0 || a->rs_rows % kBM != 0 || M != a->rs_world * a->rs_rows || batch != 1 ||
+        out_mode > 1 || k_splits != 1)
+      return cudaErrorInvalidValue;
+  }
   GemmParams p{};
+  p.ag_world = a->ag_world; p.ag_rank = a->ag_rank; p.ag_rows = a->ag_rows;
+  p.ag_flags = reinterpret_cast<const uint32_t* const*>(a->ag_flags);
+  p.ag_epoch = reinterpret_cast<const uint32_t*>(a->ag_epoch);
+  p.rs_world = a->rs_world; p.rs_rank = a->rs_rank; p.rs_rows = a->rs_rows;
+  for (int r = 0; r < 8; ++r) p.rs_out[r] = r < a->rs_world ? a->rs_out[r] : nullptr;
   p.M = M; p.N = N; p.K = K; p.batch = batch; p.k_splits = k_splits; p.out_mode = out_mode;
   p.ldo = a->ldo; p.out_batch_stride = a->out_batch_stride;
   p.out = k_splits > 1 ? a->split_workspace : a->out;
-  if (p.out == nullptr) return cudaErrorInvalidValue;
+  if (p.out == nullptr && a->rs_world == 0) return cudaErrorInvalidValue;
   // split planes are laid out [split][batch][rows][ldo]
   const long long plane = (out_mode == 1 ? 1ll * M : 1ll * N) * a->ldo;
   p.out_split_stride = k_splits > 1 ? plane * batch : 0;
@@ -501,8 +560,8 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (kind) {
-    case 0: return dispatch_bn<0>(bn, tmA, tmB, p, grid, s);
-    case 1: return dispatch_bn<1>(bn, tmA, tmB, p, grid, s);
-    default: return dispatch_bn<2>(bn, tmA, tmB, p, grid, s);
+    case 0: return dispatch_bn<0>(bn, tmA, tmB, peer, p, grid, s);
+    case 1: return dispatch_bn<1>(bn, tmA, tmB, peer, p, grid, s);
+    default: return dispatch_bn<2>(bn, tmA, tmB, peer, p, grid, s);
   }
 }

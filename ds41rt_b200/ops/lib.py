@@ -30,6 +30,9 @@ class GemmArgs(C.Structure):
         ("kind", C.c_int), ("out_mode", C.c_int), ("k_splits", C.c_int), ("bn", C.c_int),
         ("b_batch_kind", C.c_int), ("up_row_offset", C.c_int), ("row_w_ld", C.c_int), ("act_limit", C.c_float),
         ("static_operand", C.c_int),
+        ("ag_world", C.c_int), ("ag_rank", C.c_int), ("ag_rows", C.c_int),
+        ("rs_world", C.c_int), ("rs_rank", C.c_int), ("rs_rows", C.c_int),
+        ("a_peers", C.c_void_p * 8), ("ag_flags", C.c_void_p), ("ag_epoch", C.c_void_p), ("rs_out", C.c_void_p * 8),
     ]
 
 
@@ -77,7 +80,7 @@ def dir_functions():
         "ds41_compress", "ds41_index_score", "ds41_topk_select", "ds41_attend", "ds41_router_select",
         "ds41_moe_plan", "ds41_moe_combine", "ds41_signal", "ds41_reduce_planes", "ds41_argmax_rows",
         "ds41_argmax_merge", "ds41_spec_accept", "ds41_act_quant_mx", "ds41_decode_feedback", "ds41_hc_step", "ds41_taps_pack", "ds41_norm_rows", "ds41_markov_step", "ds41_spec_feedback",
-        "ds41_copy_ints",
+        "ds41_copy_ints", "ds41_rs_reduce",
     ]
 
 

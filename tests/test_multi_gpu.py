@@ -20,3 +20,15 @@ def test_tp2_engine_matches_oracle():
     sys.stderr.write(r.stderr[-3000:])
     assert r.returncode == 0
     assert "TP_WORKER_OK" in r.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_allgather_gemm_and_gemm_reducescatter():
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TP_ROWS="512", TP_K="1024", TP_N="1024", TP_REPS="3")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29519", os.path.join(here, "multi", "tp_linear_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    sys.stdout.write(r.stdout[-3000:])
+    sys.stderr.write(r.stderr[-3000:])
+    assert r.returncode == 0 and "TP_LINEAR_OK" in r.stdout
