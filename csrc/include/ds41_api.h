@@ -52,6 +52,21 @@ typedef struct ds41_gemm_args {
   const void* ag_flags;      // DEVICE array of ag_world flag pointers
   const void* ag_epoch;      // device word
   void* rs_out[8];
+  // Grouped tokens (expert-parallel prefill; swap-AB, B = flat rows sorted by expert, B batch kind 1):
+  //   device tile table: tile j = rows [tile_row0[j], tile_end[j]) of expert tile_group[j]; *n_tiles_dev live tiles,
+  //   at most max_tiles.  row_w is then indexed by flat row.  out_mode 7 scatters result rows (bf16) to
+  //   scatter_out[meta.x] + meta.y * ldo, meta = scatter_meta[row] (P2P stores: the combine half of the all-to-all).
+  //   wait_flags / wait_epoch / wait_world: peers whose stores this GEMM consumes (bounded wait before the first load).
+  const int* tile_group;
+  const int* tile_row0;
+  const int* tile_end;
+  const int* n_tiles_dev;
+  const void* scatter_meta;
+  const void* wait_flags;
+  const void* wait_epoch;
+  void* scatter_out[8];
+  int max_tiles;
+  int wait_world;
 } ds41_gemm_args;
 
 int ds41_gemm_tc(const ds41_gemm_args* args, void* stream);
@@ -178,6 +193,37 @@ int ds41_copy_ints(const int* src, int* dst, int n, void* stream);
 int ds41_act_quant_mx(const void* x, long long ldx, long long x_batch_stride, void* q, long long ldq,
                       long long q_batch_stride, void* sf, long long sf_batch_stride, int rows, int K, int batch,
                       int group, const int* n_active, void* stream);
+
+// ---------------------------------------------------------------------------------------------------
+// Expert-parallel token exchange over peer memory (ep.cu).  Pointer tables hold one pointer per rank (symmetric memory).
+typedef struct {
+  int world, rank, e_local, topk, tokens, H, cap, bn, max_tiles;
+  const void* x;            // [tokens, H] bf16 rows of this rank
+  const int* ids;           // [tokens, topk] global expert ids (out of range = no route)
+  const float* weights;     // [tokens, topk]
+  uint32_t* epoch;          // rank-local step counter (bumped by ds41_ep_count)
+  int* cursor;              // [world * e_local] scratch
+  int* ticket;              // [1] scratch
+  void* counts[8];          // int [world(src)][e_local] at each rank
+  void* send_base[8];       // int [world(dst)][e_local] at each rank
+  void* recv_x[8];          // bf16 [cap, H] at each rank
+  void* recv_meta[8];       // int2 [cap] {source rank, token*topk+k}
+  void* recv_w[8];          // float [cap]
+  void* flags[8];           // uint32 [4] phase flags at each rank
+  int* tile_group;          // [max_tiles] tile table of the grouped GEMMs (local)
+  int* tile_row0;
+  int* tile_end;
+  int* n_tiles;
+  int* total_rows;
+  int* status;
+} ds41_ep_args;
+int ds41_ep_count(const ds41_ep_args* a, void* stream);
+int ds41_ep_plan(const ds41_ep_args* a, void* stream);
+int ds41_ep_dispatch(const ds41_ep_args* a, int blocks, void* stream);
+int ds41_ep_mark(const ds41_ep_args* a, int phase, void* stream);
+int ds41_ep_wait(const ds41_ep_args* a, int phase, void* stream);
+int ds41_ep_combine(const ds41_ep_args* a, const void* comb, const float* extra, long long extra_ld, void* out,
+                    int as_bf16, void* stream);
 
 #ifdef __cplusplus
 }

@@ -49,6 +49,19 @@ struct GemmParams {
   int row_w_ld;
   float act_limit;        // mode 4: SwiGLU clamp
   int static_operand;     // 1: A holds weights, 2: B holds weights (may be fetched before the dependency wait)
+  // grouped tokens (expert-parallel prefill, swap-AB): the N operand is a flat buffer of rows sorted by expert;
+  // tile j covers rows [tile_row0[j], tile_end[j]) of expert tile_group[j]; *n_tiles_dev tiles are live
+  const int* tile_group;
+  const int* tile_row0;
+  const int* tile_end;
+  const int* n_tiles_dev;
+  // generic dependency on peers (bounded wait by the producer before its first dependent load)
+  const uint32_t* const* wait_flags;
+  const uint32_t* wait_epoch;
+  int wait_world;
+  // mode 7: scatter rows to their source ranks (expert-parallel combine): meta[n] = {source rank, slot}
+  const int2* scatter_meta;
+  void* scatter_out[8];
   // fused collectives over peer memory (normal orientation: A = activations, rows sharded by rank)
   int ag_world, ag_rank, ag_rows;         // all-gather -> GEMM: A rows [r*ag_rows, (r+1)*ag_rows) live on rank r
   const uint32_t* const* ag_flags;        // device array of peer flag pointers ("my shard is ready")
@@ -102,11 +115,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int lane = threadIdx.x & 31;
 
   const int m_tiles = (p.M + kBM - 1) / kBM;
-  const int n_tiles = (p.N + BN - 1) / BN;
+  const bool table = p.tile_group != nullptr;
+  if (table) pdl_wait();              // the tile table is produced by an earlier kernel
+  const int n_tiles = table ? *p.n_tiles_dev : (p.N + BN - 1) / BN;
   const int kb_total = (p.K + Cfg::kBK - 1) / Cfg::kBK;
   const int kb_per_split = (kb_total + p.k_splits - 1) / p.k_splits;
   pdl_launch_dependents();
-  int batch_run = p.batch;
+  int batch_run = table ? 1 : p.batch;
   if (p.n_active != nullptr) {
     pdl_wait();                       // the active-expert count is produced by an earlier kernel
     batch_run = min(batch_run, *p.n_active);
@@ -146,7 +161,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     constexpr uint32_t kStageTx = Cfg::kABytes + Cfg::kBBytes + (KIND == 2 ? 512 * (Cfg::kAtomsA + Cfg::kAtomsB) : 0);
     // Weight tiles of the first stages do not depend on the previous kernel: fetch them before waiting for it.
     int prefetched = 0;
-    if (p.static_operand != 0 && p.n_active == nullptr && p.batch_map == nullptr && blockIdx.x < tiles) {
+    if (p.static_operand != 0 && p.n_active == nullptr && p.batch_map == nullptr && !table && blockIdx.x < tiles) {
       long long r = blockIdx.x;
       const int mt = static_cast<int>(r % m_tiles); r /= m_tiles;
       const int nt = static_cast<int>(r % n_tiles); r /= n_tiles;
@@ -169,12 +184,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     pdl_wait();
     uint32_t ag_seen = 0;
+    if (p.wait_flags != nullptr && p.wait_world > 1) {
+      for (int k = 0; k < p.wait_world && ok; ++k)
+        if (!flag_wait_ge(p.wait_flags[k], *p.wait_epoch, p.status, 120 + k)) ok = false;
+    }
     for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
       long long r = t;
       const int mt = static_cast<int>(r % m_tiles); r /= m_tiles;
       const int nt = static_cast<int>(r % n_tiles); r /= n_tiles;
       const int sp = static_cast<int>(r % p.k_splits); r /= p.k_splits;
-      const int b = static_cast<int>(r);
+      const int b = table ? p.tile_group[nt] : static_cast<int>(r);
+      const int n_base = table ? p.tile_row0[nt] : nt * BN;
       const int kb0 = sp * kb_per_split;
       const int kb1 = min(kb_total, kb0 + kb_per_split);
       const int mt_eff = rot ? (mt + rot) % m_tiles : mt;
@@ -204,7 +224,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if constexpr (DUAL)
             tma_load_3d(sa + Cfg::kATile, &tmA, &full[stage], kb * Cfg::kBK, p.up_row_offset + mt * kBM, ba);
         }
-        if (!early || p.static_operand != 2) tma_load_3d(sb, &tmB, &full[stage], kb * Cfg::kBK, nt * BN, bb);
+        if (!early || p.static_operand != 2) tma_load_3d(sb, &tmB, &full[stage], kb * Cfg::kBK, n_base, bb);
         if constexpr (KIND == 2) {
           // scale-factor atoms: [row_atom][k_atom][512 B]; one k_atom per stage (128 elements of K)
           uint8_t* ssf = sb + Cfg::kBBytes;
@@ -217,7 +237,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
 #pragma unroll
           for (int a = 0; a < Cfg::kAtomsB; ++a) {
-            const long long ra = (1ll * nt * BN) / 128 + a;
+            const long long ra = n_base / 128 + a;
             bulk_load(ssf + 512 * (Cfg::kAtomsA + a), p.sfb + bb * p.sfb_batch_stride + (ra * n_ka + ka) * 512, 512,
                       &full[stage]);
           }
@@ -257,7 +277,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int a = 0; a < Cfg::kAtomsA + Cfg::kAtomsB; ++a)
             tmem_cp_32x128b_warpx4(sf_t + 4 * a, umma_desc_plain(ssf + 512 * a, 16, 128));
           // B scale columns: rows of this n-tile start (nt*BN % 128)/32 columns into the atom
-          const uint32_t sfb_t = sf_t + 4 * Cfg::kAtomsA + ((static_cast<uint32_t>(nt) * BN) & 127u) / 32u;
+          const uint32_t n_base_u = table ? static_cast<uint32_t>(p.tile_row0[nt]) : static_cast<uint32_t>(nt) * BN;
+          const uint32_t sfb_t = sf_t + 4 * Cfg::kAtomsA + (n_base_u & 127u) / 32u;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint32_t id = umma_idesc_bs(kBM, BN, 0, 0, 1, k, k);
@@ -299,7 +320,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int mt = static_cast<int>(r % m_tiles); r /= m_tiles;
       const int nt = static_cast<int>(r % n_tiles); r /= n_tiles;
       const int sp = static_cast<int>(r % p.k_splits); r /= p.k_splits;
-      const int b = static_cast<int>(r);
+      const int b = table ? p.tile_group[nt] : static_cast<int>(r);
+      const int n_base = table ? p.tile_row0[nt] : nt * BN;
+      const int n_lim = table ? p.tile_end[nt] : p.N;
       if (!mbar_wait(&acc_full[acc], acc_phase, p.status, 300)) { ok = false; break; }
       tc_fence_after();
       const int m = (rot ? (mt + rot) % m_tiles : mt) * kBM + quad * 32 + lane;
@@ -312,7 +335,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         rs_row = 1ll * p.rs_rank * p.rs_rows + (m - dst * p.rs_rows);
       }
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * Cfg::kAccCols;
-      const long long obase = b * p.out_batch_stride + sp * p.out_split_stride;
+      const long long obase = (table ? 0ll : b * p.out_batch_stride) + sp * p.out_split_stride;
       constexpr int kChunk = BN >= 32 ? 32 : BN;
 #pragma unroll 1
       for (int c = 0; c < BN; c += kChunk) {
@@ -331,12 +354,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int j = 0; j < 8; ++j) v[j] = v8[j];
         }
         tmem_wait_ld();
-        const int n0 = nt * BN + c;
+        const int n0 = n_base + c;
         if (p.out_mode == 0) {
           if (m < p.M) {
             __nv_bfloat16* o = rs_base != nullptr ? reinterpret_cast<__nv_bfloat16*>(rs_base) + rs_row * p.ldo + n0
                                                   : reinterpret_cast<__nv_bfloat16*>(p.out) + obase + 1ll * m * p.ldo + n0;
-            if (n0 + kChunk <= p.N && (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+            if (n0 + kChunk <= n_lim && (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
 #pragma unroll
               for (int j = 0; j < kChunk; j += 8) {
                 uint4 q;
@@ -353,21 +376,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             } else {
 #pragma unroll
               for (int j = 0; j < kChunk; ++j)
-                if (n0 + j < p.N) o[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                if (n0 + j < n_lim) o[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
             }
           }
         } else if (p.out_mode == 1) {
           if (m < p.M) {
             float* o = rs_base != nullptr ? reinterpret_cast<float*>(rs_base) + rs_row * p.ldo + n0
                                           : reinterpret_cast<float*>(p.out) + obase + 1ll * m * p.ldo + n0;
-            if (n0 + kChunk <= p.N && (p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+            if (n0 + kChunk <= n_lim && (p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
 #pragma unroll
               for (int j = 0; j < kChunk; j += 4)
                 *reinterpret_cast<uint4*>(o + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
             } else {
 #pragma unroll
               for (int j = 0; j < kChunk; ++j)
-                if (n0 + j < p.N) o[j] = __uint_as_float(v[j]);
+                if (n0 + j < n_lim) o[j] = __uint_as_float(v[j]);
             }
           }
         } else if (p.out_mode == 2) {
@@ -375,14 +398,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (m < p.M) {
 #pragma unroll
             for (int j = 0; j < kChunk; ++j)
-              if (n0 + j < p.N) o[1ll * (n0 + j) * p.ldo] = __float2bfloat16_rn(__uint_as_float(v[j]));
+              if (n0 + j < n_lim) o[1ll * (n0 + j) * p.ldo] = __float2bfloat16_rn(__uint_as_float(v[j]));
           }
         } else if (p.out_mode == 3) {
           float* o = reinterpret_cast<float*>(p.out) + obase + m;
           if (m < p.M) {
 #pragma unroll
             for (int j = 0; j < kChunk; ++j)
-              if (n0 + j < p.N) o[1ll * (n0 + j) * p.ldo] = __uint_as_float(v[j]);
+              if (n0 + j < n_lim) o[1ll * (n0 + j) * p.ldo] = __uint_as_float(v[j]);
           }
         } else if (p.out_mode == 4) {
           if constexpr (DUAL) {
@@ -398,26 +421,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             tmem_wait_ld();
             __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + obase + m;
-            const float* rw = p.row_w + 1ll * b * p.row_w_ld;
+            const float* rw = p.row_w + (table ? 0ll : 1ll * b * p.row_w_ld);
             if (m < p.M) {
 #pragma unroll
               for (int j = 0; j < kChunk; ++j) {
-                if (n0 + j < p.N) {
+                if (n0 + j < n_lim) {
                   const float gte = fminf(bf16_round(__uint_as_float(v[j])), p.act_limit);
                   const float upv = fminf(fmaxf(bf16_round(__uint_as_float(u[j])), -p.act_limit), p.act_limit);
-                  const float act = gte / (1.0f + __expf(-gte)) * upv * rw[n0 + j];
+                  const float act = gte / (1.0f + __expf(-gte)) * upv * __ldcg(rw + n0 + j);
                   o[1ll * (n0 + j) * p.ldo] = __float2bfloat16_rn(act);
+                }
+              }
+            }
+          }
+        } else if (p.out_mode == 7) {
+          // expert-parallel combine: column n is a received token row; its result row goes back to the rank it
+          // came from, into that rank's combine buffer at the (token, route) slot - a P2P store from the epilogue
+          if (m < p.M) {
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) {
+              if (n0 + j < n_lim) {
+                const int2 meta = __ldcg(p.scatter_meta + n0 + j);
+                if (meta.x >= 0 && meta.x < 8 && meta.y >= 0) {
+                  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.scatter_out[meta.x]) + 1ll * meta.y * p.ldo + m;
+                  *o = __float2bfloat16_rn(__uint_as_float(v[j]));
                 }
               }
             }
           }
         } else {
           float* o = reinterpret_cast<float*>(p.out) + obase + m;
-          const float* rw = p.row_w + 1ll * b * p.row_w_ld;
+          const float* rw = p.row_w + (table ? 0ll : 1ll * b * p.row_w_ld);
           if (m < p.M) {
 #pragma unroll
             for (int j = 0; j < kChunk; ++j)
-              if (n0 + j < p.N && rw[n0 + j] != 0.f) o[1ll * (n0 + j) * p.ldo] = __uint_as_float(v[j]);
+              if (n0 + j < n_lim && rw[n0 + j] != 0.f) o[1ll * (n0 + j) * p.ldo] = __uint_as_float(v[j]);
           }
         }
       }
@@ -492,7 +530,7 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   const int M = a->M, N = a->N, K = a->K, batch = a->batch, kind = a->kind, out_mode = a->out_mode;
   const int k_splits = a->k_splits, bn = a->bn;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0 || k_splits <= 0 || kind < 0 || kind > 2 || out_mode < 0 ||
-      out_mode > 5)
+      out_mode > 7 || out_mode == 6)
     return cudaErrorInvalidValue;
   const int elem = kind == 0 ? 2 : 1;
   const int bk = kTileKBytes / elem;
@@ -502,6 +540,10 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   if (kind == 2 && bn < 32 && N > bn) return cudaErrorInvalidValue;      // 16-row scale tiles cannot be lane-shifted
   if (k_splits > 1 && out_mode != 1 && out_mode != 3) return cudaErrorInvalidValue;   // partials are fp32
   if ((out_mode == 4 || out_mode == 5) && a->row_w == nullptr) return cudaErrorInvalidValue;
+  if (out_mode == 7 && (a->scatter_meta == nullptr || a->tile_group == nullptr)) return cudaErrorInvalidValue;
+  if (a->tile_group != nullptr && (a->tile_row0 == nullptr || a->tile_end == nullptr || a->n_tiles_dev == nullptr ||
+                                   k_splits != 1 || a->max_tiles <= 0))
+    return cudaErrorInvalidValue;
   CUtensorMap tmA, tmB;
   const TmaDtype dt = kind == 0 ? TmaDtype::kBF16 : TmaDtype::kU8;
   const int a_rows = out_mode == 4 ? a->up_row_offset + M : M;           // dual tiles address gate and up rows
@@ -554,9 +596,16 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   p.row_w = a->row_w;
   p.row_w_ld = a->row_w_ld;
   p.act_limit = a->act_limit;
+  p.tile_group = a->tile_group; p.tile_row0 = a->tile_row0; p.tile_end = a->tile_end; p.n_tiles_dev = a->n_tiles_dev;
+  p.wait_flags = reinterpret_cast<const uint32_t* const*>(a->wait_flags);
+  p.wait_epoch = reinterpret_cast<const uint32_t*>(a->wait_epoch);
+  p.wait_world = a->wait_world;
+  p.scatter_meta = reinterpret_cast<const int2*>(a->scatter_meta);
+  for (int r = 0; r < 8; ++r) p.scatter_out[r] = a->scatter_out[r];
   p.static_operand = a->static_operand;
   p.status = a->status;
-  const long long tiles = 1ll * ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn) * k_splits * batch;
+  const long long n_t = a->tile_group != nullptr ? a->max_tiles : (N + bn - 1) / bn;
+  const long long tiles = 1ll * ((M + kBM - 1) / kBM) * n_t * k_splits * (a->tile_group != nullptr ? 1 : batch);
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (kind) {

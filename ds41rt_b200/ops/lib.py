@@ -33,6 +33,9 @@ class GemmArgs(C.Structure):
         ("ag_world", C.c_int), ("ag_rank", C.c_int), ("ag_rows", C.c_int),
         ("rs_world", C.c_int), ("rs_rank", C.c_int), ("rs_rows", C.c_int),
         ("a_peers", C.c_void_p * 8), ("ag_flags", C.c_void_p), ("ag_epoch", C.c_void_p), ("rs_out", C.c_void_p * 8),
+        ("tile_group", C.c_void_p), ("tile_row0", C.c_void_p), ("tile_end", C.c_void_p), ("n_tiles_dev", C.c_void_p),
+        ("scatter_meta", C.c_void_p), ("wait_flags", C.c_void_p), ("wait_epoch", C.c_void_p),
+        ("scatter_out", C.c_void_p * 8), ("max_tiles", C.c_int), ("wait_world", C.c_int),
     ]
 
 
@@ -46,6 +49,19 @@ class HcStepArgs(C.Structure):
         ("wait_flags", C.c_void_p), ("wait_epoch", C.c_void_p), ("status", C.c_void_p),
         ("split_stride", C.c_longlong), ("n_ranks", C.c_int), ("n_splits", C.c_int),
         ("rows", C.c_int), ("H", C.c_int), ("iters", C.c_int), ("hc_eps", C.c_float), ("norm_eps", C.c_float),
+    ]
+
+
+class EpArgs(C.Structure):
+    _fields_ = [
+        ("world", C.c_int), ("rank", C.c_int), ("e_local", C.c_int), ("topk", C.c_int), ("tokens", C.c_int),
+        ("H", C.c_int), ("cap", C.c_int), ("bn", C.c_int), ("max_tiles", C.c_int),
+        ("x", C.c_void_p), ("ids", C.c_void_p), ("weights", C.c_void_p), ("epoch", C.c_void_p),
+        ("cursor", C.c_void_p), ("ticket", C.c_void_p),
+        ("counts", C.c_void_p * 8), ("send_base", C.c_void_p * 8), ("recv_x", C.c_void_p * 8),
+        ("recv_meta", C.c_void_p * 8), ("recv_w", C.c_void_p * 8), ("flags", C.c_void_p * 8),
+        ("tile_group", C.c_void_p), ("tile_row0", C.c_void_p), ("tile_end", C.c_void_p), ("n_tiles", C.c_void_p),
+        ("total_rows", C.c_void_p), ("status", C.c_void_p),
     ]
 
 
@@ -80,7 +96,8 @@ def dir_functions():
         "ds41_compress", "ds41_index_score", "ds41_topk_select", "ds41_attend", "ds41_router_select",
         "ds41_moe_plan", "ds41_moe_combine", "ds41_signal", "ds41_reduce_planes", "ds41_argmax_rows",
         "ds41_argmax_merge", "ds41_spec_accept", "ds41_act_quant_mx", "ds41_decode_feedback", "ds41_hc_step", "ds41_taps_pack", "ds41_norm_rows", "ds41_markov_step", "ds41_spec_feedback",
-        "ds41_copy_ints", "ds41_rs_reduce",
+        "ds41_copy_ints", "ds41_rs_reduce", "ds41_ep_count", "ds41_ep_plan", "ds41_ep_dispatch", "ds41_ep_mark",
+        "ds41_ep_wait", "ds41_ep_combine",
     ]
 
 
@@ -105,7 +122,8 @@ def stream() -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-STATUS_NAMES = {0: "ok", 1: "mbarrier wait timed out", 2: "flag wait timed out", 3: "bad argument"}
+STATUS_NAMES = {0: "ok", 1: "mbarrier wait timed out", 2: "flag wait timed out", 3: "bad argument",
+                7: "expert-parallel receive buffer too small"}
 
 
 def new_status(device) -> torch.Tensor:

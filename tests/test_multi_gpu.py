@@ -32,3 +32,30 @@ def test_fused_allgather_gemm_and_gemm_reducescatter():
     sys.stdout.write(r.stdout[-3000:])
     sys.stderr.write(r.stderr[-3000:])
     assert r.returncode == 0 and "TP_LINEAR_OK" in r.stdout
+
+
+def _run_ep(nproc: int, port: int, **env_extra):
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **env_extra)
+    worker = os.path.join(here, "multi", "ep_worker.py")
+    if nproc == 1:
+        cmd = [sys.executable, worker]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+               "--master-addr", "127.0.0.1", "--master-port", str(port), worker]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    sys.stdout.write(r.stdout[-3000:])
+    sys.stderr.write(r.stderr[-3000:])
+    assert r.returncode == 0 and "EP_OK" in r.stdout
+
+
+@pytest.mark.parametrize("mx", ["0", "1"])
+def test_grouped_experts_one_rank(mx):
+    """Tile-table grouped GEMMs and the scatter epilogue with every expert local (no peers)."""
+    _run_ep(1, 0, EP_TOKENS="384", EP_H="512", EP_I="256", EP_E="8", EP_TOPK="4", EP_REPS="2", EP_MX=mx)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("mx", ["0", "1"])
+def test_expert_parallel_dispatch_gemm_combine(mx):
+    _run_ep(2, 29521, EP_TOKENS="384", EP_H="512", EP_I="256", EP_E="8", EP_TOPK="4", EP_REPS="2", EP_MX=mx)
