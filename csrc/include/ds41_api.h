@@ -41,15 +41,20 @@ typedef struct ds41_gemm_args {
   int row_w_ld;
   float act_limit;
   int static_operand;   // 1: A is a weight matrix, 2: B is (prefetched ahead of the stream dependency), 0: neither
-  // Fused collectives over NVLink peer memory (out_mode 0/1, batch 1):
-  //  all-gather -> GEMM: A's rows are sharded by rank (ag_rows each, a multiple of 128); a_peers[r] is rank r's shard
-  //    (symmetric memory), fetched tile by tile with TMA once rank r's flag has reached *ag_epoch (bounded wait).
+  // Fused collectives over NVLink peer memory (out_mode 0/1/6, batch 1):
+  //  all-gather -> GEMM (push model): every rank holds a full copy of A (a_peers[r] = rank r's copy, symmetric
+  //    memory); rank r wrote its own rows [r*ag_rows, (r+1)*ag_rows) (ag_rows a multiple of 128).  Copier warps of
+  //    the kernel push those rows into every peer's copy and bump the peer's arrival counters
+  //    ag_arrive[d][src * ag_rows/128 + tile]; the TMA producer loads a remote tile from LOCAL memory once its counter
+  //    has reached *ag_epoch * chunks (bounded wait).  Counters only grow; *ag_epoch is the call count.
   //  GEMM -> reduce-scatter: the output rows owned by rank d (rs_rows each) are stored into rs_out[d] at row
   //    rs_rank * rs_rows + local_row, i.e. every destination receives one slot per source rank to sum in fixed order.
+  //    With out_mode 6 the slots are bf16 and written by TMA stores from shared memory.
+  //  out_mode 6 without rs_world: bf16 [m,n] output through the same TMA-store epilogue (bn >= 64, bf16 kind).
   int ag_world, ag_rank, ag_rows;
   int rs_world, rs_rank, rs_rows;
-  const void* a_peers[8];
-  const void* ag_flags;      // DEVICE array of ag_world flag pointers
+  void* a_peers[8];
+  void* ag_arrive[8];
   const void* ag_epoch;      // device word
   void* rs_out[8];
   // Grouped tokens (expert-parallel prefill; swap-AB, B = flat rows sorted by expert, B batch kind 1):
@@ -197,7 +202,7 @@ int ds41_act_quant_mx(const void* x, long long ldx, long long x_batch_stride, vo
 // ---------------------------------------------------------------------------------------------------
 // Expert-parallel token exchange over peer memory (ep.cu).  Pointer tables hold one pointer per rank (symmetric memory).
 typedef struct {
-  int world, rank, e_local, topk, tokens, H, cap, bn, max_tiles;
+  int world, rank, e_local, topk, tokens, H, cap, bn, bn2, max_tiles;   // bn2 > 0: second tile table of bn2-row tiles
   const void* x;            // [tokens, H] bf16 rows of this rank
   const int* ids;           // [tokens, topk] global expert ids (out of range = no route)
   const float* weights;     // [tokens, topk]
@@ -210,10 +215,10 @@ typedef struct {
   void* recv_meta[8];       // int2 [cap] {source rank, token*topk+k}
   void* recv_w[8];          // float [cap]
   void* flags[8];           // uint32 [4] phase flags at each rank
-  int* tile_group;          // [max_tiles] tile table of the grouped GEMMs (local)
+  int* tile_group;          // [2 * max_tiles] tile tables of the grouped GEMMs (local): bn tiles, then bn2 tiles
   int* tile_row0;
   int* tile_end;
-  int* n_tiles;
+  int* n_tiles;             // [2]
   int* total_rows;
   int* status;
 } ds41_ep_args;

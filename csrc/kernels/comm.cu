@@ -3,6 +3,7 @@
 //  rs_reduce : second half of the fused GEMM -> reduce-scatter.  Every source rank's GEMM epilogue stored its partial
 //              rows for this rank into slot[src] of this rank's symmetric buffer; after a bounded wait on the peers'
 //              epoch flags the slots are summed in rank order (deterministic) into bf16 or fp32 rows.
+//              `as_bf16` bit 0: bf16 output; bit 1: the slots hold bf16 (TMA-store epilogue) instead of fp32.
 //  The flags follow the library-wide protocol: a rank publishes "my stores for this step are complete" by raising its
 //  epoch flag (ds41_signal); waiters spin with a cycle limit and report through the status word instead of hanging.
 #include "ds41_api.h"
@@ -24,9 +25,19 @@ rs_reduce_kernel(const float* __restrict__ slots, int world, long long slot_stri
   const long long i = (1ll * blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i >= n) return;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool slots_bf16 = (as_bf16 & 2) != 0;
+  as_bf16 &= 1;
   for (int s = 0; s < world; ++s) {
-    const float4 v = __ldcg(reinterpret_cast<const float4*>(slots + s * slot_stride + i));
-    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    if (slots_bf16) {
+      const uint2 q = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(slots) +
+                                                            s * slot_stride + i));
+      const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.x));
+      const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.y));
+      acc.x += lo.x; acc.y += lo.y; acc.z += hi.x; acc.w += hi.y;
+    } else {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(slots + s * slot_stride + i));
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
   }
   if (as_bf16) {
     __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y), b = __floats2bfloat162_rn(acc.z, acc.w);

@@ -30,7 +30,7 @@
 namespace ds41 {
 
 struct EpParams {
-  int world, rank, e_local, topk, tokens, H, cap, bn, max_tiles, group_align;
+  int world, rank, e_local, topk, tokens, H, cap, bn, bn2, max_tiles, group_align;
   const __nv_bfloat16* x;
   const int* ids;
   const float* weights;
@@ -104,7 +104,8 @@ __global__ void __launch_bounds__(256) ep_plan_kernel(EpParams p) {
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    int off = 0, nt = 0;
+    // table 0 (tiles of bn rows) at [0, max_tiles), table 1 (tiles of bn2 rows, if bn2 > 0) at [max_tiles, 2*max_tiles)
+    int off = 0, nt = 0, nt2 = 0;
     bool fits = s_ok != 0;
     for (int e = 0; e < p.e_local; ++e) {
       goff[e] = off;
@@ -121,11 +122,23 @@ __global__ void __launch_bounds__(256) ep_plan_kernel(EpParams p) {
             fits = false;
           }
         }
+        if (p.bn2 > 0) {
+          for (int r0 = off; r0 < off + g; r0 += p.bn2) {
+            if (nt2 < p.max_tiles) {
+              p.tile_group[p.max_tiles + nt2] = e;
+              p.tile_row0[p.max_tiles + nt2] = r0;
+              p.tile_end[p.max_tiles + nt2] = min(r0 + p.bn2, off + g);
+              ++nt2;
+            } else {
+              fits = false;
+            }
+          }
+        }
       }
       off += (g + p.group_align - 1) / p.group_align * p.group_align;
     }
     if (!fits) {
-      nt = 0;
+      nt = nt2 = 0;
       if (p.status != nullptr && s_ok != 0 && atomicCAS(p.status, 0, kEpOverflow) == 0) {
         p.status[1] = 710;
         p.status[2] = off;
@@ -133,7 +146,8 @@ __global__ void __launch_bounds__(256) ep_plan_kernel(EpParams p) {
       }
       s_ok = 0;
     }
-    *p.n_tiles = nt;
+    p.n_tiles[0] = nt;
+    p.n_tiles[1] = nt2;
     *p.total_rows = fits ? off : 0;
   }
   __syncthreads();
@@ -250,10 +264,10 @@ ep_combine_kernel(EpParams p, const __nv_bfloat16* __restrict__ comb, const floa
 static bool fill(const ds41_ep_args* a, EpParams& p) {
   if (a == nullptr || a->world < 1 || a->world > 8 || a->rank < 0 || a->rank >= a->world || a->e_local < 1 ||
       a->world * a->e_local > 4096 || a->topk < 1 || a->tokens < 0 || a->H < 8 || (a->H & 7) || a->cap < 1 ||
-      a->bn < 8 || a->max_tiles < 1)
+      a->bn < 8 || a->bn2 < 0 || a->max_tiles < 1)
     return false;
   p.world = a->world; p.rank = a->rank; p.e_local = a->e_local; p.topk = a->topk; p.tokens = a->tokens;
-  p.H = a->H; p.cap = a->cap; p.bn = a->bn; p.max_tiles = a->max_tiles; p.group_align = 128;
+  p.H = a->H; p.cap = a->cap; p.bn = a->bn; p.bn2 = a->bn2; p.max_tiles = a->max_tiles; p.group_align = 128;
   p.x = static_cast<const __nv_bfloat16*>(a->x);
   p.ids = a->ids; p.weights = a->weights;
   p.epoch = a->epoch; p.cursor = a->cursor; p.ticket = reinterpret_cast<unsigned*>(a->ticket);

@@ -20,9 +20,12 @@ namespace ds41 {
 
 constexpr int kBM = 128;
 constexpr int kTileKBytes = 128;       // one 128-byte swizzle span of K per stage
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 256;      // warps: 0 TMA, 1 MMA, 2-5 epilogue, 6-7 all-gather copiers
+constexpr int kStagingBytes = 32768;   // TMA-store staging: 4 epilogue warps x 2 buffers x [32 rows][128 B]
 
-struct PeerMaps {
+// tensor maps of the TMA-store epilogue (mode 6): m[0] = the output, or with reduce-scatter m[d] = this rank's slot
+// in rank d's buffer
+struct StoreMaps {
   CUtensorMap m[8];
 };
 
@@ -31,7 +34,8 @@ struct GemmParams {
   int batch;
   int k_splits;
   int out_mode;           // 0 bf16 [m,n]; 1 f32 [m,n]; 2 bf16 [n,m]; 3 f32 [n,m];
-                          // 4 (DUAL) bf16 [n,m] = swiglu(gate,up)*row_w; 5 f32 [n,m] where row_w != 0
+                          // 4 (DUAL) bf16 [n,m] = swiglu(gate,up)*row_w; 5 f32 [n,m] where row_w != 0;
+                          // 6 bf16 [m,n] staged in shared memory and written by TMA stores; 7 scatter rows
   long long ldo;          // leading dimension of the output in elements
   long long out_batch_stride;
   long long out_split_stride;
@@ -63,11 +67,17 @@ struct GemmParams {
   const int2* scatter_meta;
   void* scatter_out[8];
   // fused collectives over peer memory (normal orientation: A = activations, rows sharded by rank)
-  int ag_world, ag_rank, ag_rows;         // all-gather -> GEMM: A rows [r*ag_rows, (r+1)*ag_rows) live on rank r
-  const uint32_t* const* ag_flags;        // device array of peer flag pointers ("my shard is ready")
+  // all-gather -> GEMM (push model): A is this rank's copy of the gathered matrix; rows [r*ag_rows, (r+1)*ag_rows)
+  // belong to rank r.  The copier warps push this rank's rows into every peer's copy (ag_bufs[d]) in
+  // (128-row tile, K chunk) units and add 1 to the peer's arrival counter [src][tile] per unit; the TMA producer
+  // waits until a remote tile's counter reaches epoch * ag_chunks before loading it from local memory.
+  int ag_world, ag_rank, ag_rows, ag_chunks;
+  long long a_row_bytes;                  // bytes between rows of A
+  void* ag_bufs[8];
+  uint32_t* ag_arrive[8];                 // counters [ag_world][ag_rows / 128] on every rank
   const uint32_t* ag_epoch;
-  int rs_world, rs_rank, rs_rows;         // GEMM -> reduce-scatter: output rows of rank d go to rs_out[d], slot rs_rank
-  void* rs_out[8];
+  int rs_world, rs_rank, rs_rows;         // GEMM -> reduce-scatter: output rows of rank d go to rank d (mode 6 maps
+  void* rs_out[8];                        // or, modes 0/1, rs_out[d] slot rs_rank)
   int* status;
 };
 
@@ -83,14 +93,15 @@ struct GemmCfg {
   // scale-factor atoms (512 B each), padded so every stage keeps its 1024-byte tile alignment
   static constexpr int kSfBytes = (KIND == 2) ? ((512 * (kAtomsA + kAtomsB) + 1023) / 1024 * 1024) : 0;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
-  static constexpr int kStagesRaw = (200 * 1024) / kStageBytes;
+  static constexpr int kStaging = (KIND == 0 && !DUAL && BN >= 64) ? kStagingBytes : 0;
+  static constexpr int kStagesRaw = ((kStaging ? 194 : 200) * 1024) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kSfCols = (KIND == 2) ? 4 * (kAtomsA + kAtomsB) : 0;           // TMEM columns per stage
   static constexpr int kAccCols = (BN < 32 ? 32 : BN) * (DUAL ? 2 : 1);
   static constexpr int kTmemNeeded = 2 * kAccCols + kStages * kSfCols;
   static constexpr int kTmemCols = kTmemNeeded <= 32 ? 32 : kTmemNeeded <= 64 ? 64 : kTmemNeeded <= 128 ? 128
                                    : kTmemNeeded <= 256 ? 256 : 512;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStaging + 1024 /*align*/ + 256 /*barriers*/;
   static_assert(kTmemNeeded <= 512, "TMEM budget exceeded");
   static_assert(kStages >= 2, "not enough shared memory for two stages");
 };
@@ -98,13 +109,14 @@ struct GemmCfg {
 template <int BN, int KIND, int DUAL>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ PeerMaps peer, GemmParams p) {
+               const __grid_constant__ StoreMaps stm, GemmParams p) {
   using Cfg = GemmCfg<BN, KIND, DUAL>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-  uint8_t* bar_base = smem + S * Cfg::kStageBytes;
+  uint8_t* staging = smem + S * Cfg::kStageBytes;
+  uint8_t* bar_base = staging + Cfg::kStaging;
   uint64_t* full = reinterpret_cast<uint64_t*>(bar_base);
   uint64_t* empty = full + S;
   uint64_t* acc_full = empty + S;
@@ -128,7 +140,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
   const long long tiles = 1ll * m_tiles * n_tiles * p.k_splits * batch_run;
   // with a fused collective every rank starts on its own rows and walks the peers in ring order
-  const int rot = p.ag_world > 0 ? p.ag_rank * (p.ag_rows / kBM) : (p.rs_world > 0 ? p.rs_rank * (p.rs_rows / kBM) : 0);
+  // reduce-scatter: the rows of the next rank first (their stores travel while the rest computes), the own rows last
+  const int rot = p.ag_world > 0 ? p.ag_rank * (p.ag_rows / kBM)
+                  : (p.rs_world > 0 ? ((p.rs_rank + 1) % p.rs_world) * (p.rs_rows / kBM) : 0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -183,7 +197,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
     pdl_wait();
-    uint32_t ag_seen = 0;
     if (p.wait_flags != nullptr && p.wait_world > 1) {
       for (int k = 0; k < p.wait_world && ok; ++k)
         if (!flag_wait_ge(p.wait_flags[k], *p.wait_epoch, p.status, 120 + k)) ok = false;
@@ -198,16 +211,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int kb0 = sp * kb_per_split;
       const int kb1 = min(kb_total, kb0 + kb_per_split);
       const int mt_eff = rot ? (mt + rot) % m_tiles : mt;
-      const CUtensorMap* mapA = &tmA;
-      int a_row = mt_eff * kBM;
-      if (p.ag_world > 0) {
+      const int a_row = mt_eff * kBM;
+      if (p.ag_world > 1) {
         const int src = a_row / p.ag_rows;
-        a_row -= src * p.ag_rows;
-        mapA = &peer.m[src];
-        if (src != p.ag_rank && !((ag_seen >> src) & 1u)) {
-          // the peer's shard must be complete before its tiles are fetched over NVLink
-          if (!flag_wait_ge(p.ag_flags[src], *p.ag_epoch, p.status, 110 + src)) { ok = false; break; }
-          ag_seen |= 1u << src;
+        if (src != p.ag_rank) {
+          // the rows were pushed by rank src's copier warps: wait for all K chunks of this 128-row tile
+          const int j = (a_row - src * p.ag_rows) / kBM;
+          const uint32_t need = *p.ag_epoch * static_cast<uint32_t>(p.ag_chunks);
+          if (!flag_wait_ge(p.ag_arrive[p.ag_rank] + src * (p.ag_rows / kBM) + j, need, p.status, 110 + src)) {
+            ok = false;
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");
         }
       }
       for (int kb = kb0; kb < kb1; ++kb) {
@@ -220,7 +235,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int ba = p.batch_map != nullptr ? p.batch_map[b] : b;
         const int bb = p.b_batch_kind == 0 ? ba : (p.b_batch_kind == 1 ? 0 : b);
         if (!early || p.static_operand != 1) {
-          tma_load_3d(sa, mapA, &full[stage], kb * Cfg::kBK, a_row, ba);
+          tma_load_3d(sa, &tmA, &full[stage], kb * Cfg::kBK, a_row, ba);
           if constexpr (DUAL)
             tma_load_3d(sa + Cfg::kATile, &tmA, &full[stage], kb * Cfg::kBK, p.up_row_offset + mt * kBM, ba);
         }
@@ -309,12 +324,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
-  } else if (warp >= 2) {
+  } else if (warp >= 2 && warp < 6) {
     // ------------------------------------------------------------ epilogue (4 warps)
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    uint32_t st_pair = 0;                      // mode 6: staging buffer parity of this warp
     for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
       long long r = t;
       const int mt = static_cast<int>(r % m_tiles); r /= m_tiles;
@@ -422,40 +438,84 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tmem_wait_ld();
             __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + obase + m;
             const float* rw = p.row_w + (table ? 0ll : 1ll * b * p.row_w_ld);
-            if (m < p.M) {
+            // one coalesced load of the chunk's route weights, handed out by shuffle: a load per column would be
+            // ordered behind the previous column's store
+            const float rw_lane = (lane < kChunk && n0 + lane < n_lim) ? __ldcg(rw + n0 + lane) : 0.f;
 #pragma unroll
-              for (int j = 0; j < kChunk; ++j) {
-                if (n0 + j < n_lim) {
-                  const float gte = fminf(bf16_round(__uint_as_float(v[j])), p.act_limit);
-                  const float upv = fminf(fmaxf(bf16_round(__uint_as_float(u[j])), -p.act_limit), p.act_limit);
-                  const float act = gte / (1.0f + __expf(-gte)) * upv * __ldcg(rw + n0 + j);
-                  o[1ll * (n0 + j) * p.ldo] = __float2bfloat16_rn(act);
-                }
+            for (int j = 0; j < kChunk; ++j) {
+              const float rwj = __shfl_sync(0xffffffffu, rw_lane, j);
+              if (m < p.M && n0 + j < n_lim) {
+                const float gte = fminf(bf16_round(__uint_as_float(v[j])), p.act_limit);
+                const float upv = fminf(fmaxf(bf16_round(__uint_as_float(u[j])), -p.act_limit), p.act_limit);
+                const float act = gte / (1.0f + __expf(-gte)) * upv * rwj;
+                o[1ll * (n0 + j) * p.ldo] = __float2bfloat16_rn(act);
               }
+            }
+          }
+        } else if (p.out_mode == 6) {
+          if constexpr (Cfg::kStaging > 0) {
+            // 64 columns (two chunks) per staging buffer: [32 rows][128 B] in the 128-byte swizzle, then one TMA store
+            uint8_t* buf = staging + quad * 8192 + (st_pair & 1u) * 4096;
+            const int half = (c >> 5) & 1;
+            if (half == 0) {
+              if (lane == 0) bulk_wait_group_read<1>();     // the store issued from this buffer two pairs ago has read it
+              __syncwarp();
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 w;
+              __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1]));
+              __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
+              __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+              w.x = *reinterpret_cast<uint32_t*>(&h0);
+              w.y = *reinterpret_cast<uint32_t*>(&h1);
+              w.z = *reinterpret_cast<uint32_t*>(&h2);
+              w.w = *reinterpret_cast<uint32_t*>(&h3);
+              const int chunk16 = half * 4 + q;
+              *reinterpret_cast<uint4*>(buf + lane * 128 + ((chunk16 ^ (lane & 7)) << 4)) = w;
+            }
+            if (half == 1) {
+              fence_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                const int m_tile0 = (rot ? (mt + rot) % m_tiles : mt) * kBM;
+                int row0 = m_tile0 + quad * 32, z = b;
+                const CUtensorMap* map = &stm.m[0];
+                if (p.rs_world > 0) {
+                  const int dst = m_tile0 / p.rs_rows;
+                  map = &stm.m[dst];
+                  row0 -= dst * p.rs_rows;
+                  z = 0;
+                }
+                tma_store_3d(map, buf, n0 - 32, row0, z);
+                bulk_commit_group();
+              }
+              ++st_pair;
             }
           }
         } else if (p.out_mode == 7) {
           // expert-parallel combine: column n is a received token row; its result row goes back to the rank it
           // came from, into that rank's combine buffer at the (token, route) slot - a P2P store from the epilogue
-          if (m < p.M) {
+          int2 meta_lane = make_int2(-1, -1);
+          if (lane < kChunk && n0 + lane < n_lim) meta_lane = __ldcg(p.scatter_meta + n0 + lane);
 #pragma unroll
-            for (int j = 0; j < kChunk; ++j) {
-              if (n0 + j < n_lim) {
-                const int2 meta = __ldcg(p.scatter_meta + n0 + j);
-                if (meta.x >= 0 && meta.x < 8 && meta.y >= 0) {
-                  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.scatter_out[meta.x]) + 1ll * meta.y * p.ldo + m;
-                  *o = __float2bfloat16_rn(__uint_as_float(v[j]));
-                }
-              }
+          for (int j = 0; j < kChunk; ++j) {
+            const int src = __shfl_sync(0xffffffffu, meta_lane.x, j);
+            const int slot = __shfl_sync(0xffffffffu, meta_lane.y, j);
+            if (m < p.M && src >= 0 && src < 8 && slot >= 0) {
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.scatter_out[src]) + 1ll * slot * p.ldo + m;
+              *o = __float2bfloat16_rn(__uint_as_float(v[j]));
             }
           }
         } else {
           float* o = reinterpret_cast<float*>(p.out) + obase + m;
           const float* rw = p.row_w + (table ? 0ll : 1ll * b * p.row_w_ld);
-          if (m < p.M) {
+          const float rw_lane = (lane < kChunk && n0 + lane < n_lim) ? __ldcg(rw + n0 + lane) : 0.f;
 #pragma unroll
-            for (int j = 0; j < kChunk; ++j)
-              if (n0 + j < n_lim && rw[n0 + j] != 0.f) o[1ll * (n0 + j) * p.ldo] = __uint_as_float(v[j]);
+          for (int j = 0; j < kChunk; ++j) {
+            const float rwj = __shfl_sync(0xffffffffu, rw_lane, j);
+            if (m < p.M && rwj != 0.f) o[1ll * (n0 + j) * p.ldo] = __uint_as_float(v[j]);
           }
         }
       }
@@ -464,6 +524,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
+    }
+    if (p.out_mode == 6 && lane == 0) bulk_wait_group<0>();   // every TMA store of this warp has been performed
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------ all-gather copiers (2 warps)
+    if (p.ag_world > 1) {
+      pdl_wait();
+      const int ct = static_cast<int>(threadIdx.x) - 192;
+      const int mt_shard = p.ag_rows / kBM;
+      const int peers = p.ag_world - 1;
+      const int units = mt_shard * peers * p.ag_chunks;
+      const int chunk_bytes = static_cast<int>(1ll * p.K * Cfg::kElemBytes / p.ag_chunks);
+      const int vec_row = chunk_bytes >> 4;
+      const int total = kBM * vec_row;
+      for (int u = blockIdx.x; u < units; u += gridDim.x) {
+        const int j = u % mt_shard;
+        const int rr = u / mt_shard;
+        const int d = (p.ag_rank + 1 + rr % peers) % p.ag_world;
+        const int c = rr / peers;
+        const long long off = (1ll * p.ag_rank * p.ag_rows + 1ll * j * kBM) * p.a_row_bytes + 1ll * c * chunk_bytes;
+        const char* src = static_cast<const char*>(p.ag_bufs[p.ag_rank]) + off;
+        char* dst = static_cast<char*>(p.ag_bufs[d]) + off;
+        for (int i0 = 0; i0 < total; i0 += 64 * 8) {
+          uint4 w[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int i = i0 + q * 64 + ct;
+            if (i < total) w[q] = *reinterpret_cast<const uint4*>(src + (i / vec_row) * p.a_row_bytes + ((i % vec_row) << 4));
+          }
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int i = i0 + q * 64 + ct;
+            if (i < total) *reinterpret_cast<uint4*>(dst + (i / vec_row) * p.a_row_bytes + ((i % vec_row) << 4)) = w[q];
+          }
+        }
+        __threadfence_system();
+        named_barrier(1, 64);
+        if (ct == 0) flag_add_release(p.ag_arrive[d] + p.ag_rank * mt_shard + j, 1u);
+      }
     }
   }
 
@@ -480,7 +578,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 template <int BN, int KIND, int DUAL = 0>
-static cudaError_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const PeerMaps& peer,
+static cudaError_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const StoreMaps& peer,
                                const GemmParams& p, int grid, cudaStream_t stream) {
   using Cfg = GemmCfg<BN, KIND, DUAL>;
   static bool configured[64] = {false};
@@ -496,7 +594,7 @@ static cudaError_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, c
 }
 
 template <int KIND>
-static cudaError_t dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap& tmB, const PeerMaps& peer,
+static cudaError_t dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap& tmB, const StoreMaps& peer,
                                const GemmParams& p, int grid, cudaStream_t stream) {
   if (p.out_mode == 4) {
     switch (bn) {
@@ -530,7 +628,7 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   const int M = a->M, N = a->N, K = a->K, batch = a->batch, kind = a->kind, out_mode = a->out_mode;
   const int k_splits = a->k_splits, bn = a->bn;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0 || k_splits <= 0 || kind < 0 || kind > 2 || out_mode < 0 ||
-      out_mode > 7 || out_mode == 6)
+      out_mode > 7)
     return cudaErrorInvalidValue;
   const int elem = kind == 0 ? 2 : 1;
   const int bk = kTileKBytes / elem;
@@ -550,30 +648,54 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   const int a_batches = a->a_batches > 0 ? a->a_batches : batch;
   const int b_batches = a->b_batch_kind == 1 ? 1 : (a->b_batch_kind == 0 ? a_batches : batch);
   const void* a_base = a->ag_world > 0 ? a->a_peers[a->ag_rank] : a->A;
-  cudaError_t e = make_tensor_map_3d(&tmA, a_base, dt, K, a->ag_world > 0 ? a->ag_rows : a_rows, a_batches, a->lda * elem,
-                                     a->a_batch_stride * elem, bk, kBM, true);
+  cudaError_t e = make_tensor_map_3d(&tmA, a_base, dt, K, a_rows, a_batches, a->lda * elem, a->a_batch_stride * elem, bk,
+                                     kBM, true);
   if (e != cudaSuccess) return e;
   e = make_tensor_map_3d(&tmB, a->B, dt, K, N, b_batches, a->ldb * elem, a->b_batch_stride * elem, bk, bn, true);
   if (e != cudaSuccess) return e;
-  PeerMaps peer{};
+  StoreMaps peer{};
+  int ag_chunks = 1;
   if (a->ag_world > 0) {
     if (a->ag_world > 8 || a->ag_rows <= 0 || a->ag_rows % kBM != 0 || M != a->ag_world * a->ag_rows || batch != 1 ||
-        out_mode > 1 || a->ag_flags == nullptr || a->ag_epoch == nullptr)
+        (out_mode > 1 && out_mode != 6) || a->ag_epoch == nullptr || ((1ll * K * elem) & 15) != 0)
       return cudaErrorInvalidValue;
-    for (int r = 0; r < a->ag_world; ++r) {
-      if (a->a_peers[r] == nullptr) return cudaErrorInvalidValue;
-      e = make_tensor_map_3d(&peer.m[r], a->a_peers[r], dt, K, a->ag_rows, 1, a->lda * elem, 0, bk, kBM, true);
-      if (e != cudaSuccess) return e;
-    }
+    for (int r = 0; r < a->ag_world; ++r)
+      if (a->a_peers[r] == nullptr || a->ag_arrive[r] == nullptr) return cudaErrorInvalidValue;
+    // split every 128-row tile into K chunks so that about two rounds of copy units cover the grid
+    const int base_units = (a->ag_rows / kBM) * (a->ag_world - 1);
+    while (base_units > 0 && base_units * ag_chunks < 2 * sm_count() && ag_chunks < 16 &&
+           (1ll * K * elem) % (ag_chunks * 2 * 16) == 0)
+      ag_chunks *= 2;
   }
   if (a->rs_world > 0) {
     if (a->rs_world > 8 || a->rs_rows <= 0 || a->rs_rows % kBM != 0 || M != a->rs_world * a->rs_rows || batch != 1 ||
-        out_mode > 1 || k_splits != 1)
+        (out_mode > 1 && out_mode != 6) || k_splits != 1)
       return cudaErrorInvalidValue;
   }
+  if (out_mode == 6) {
+    if (kind != 0 || bn < 64 || k_splits != 1 || ((a->ldo * 2) & 15) != 0) return cudaErrorInvalidValue;
+    if (a->rs_world > 0) {
+      // this rank's slot in every destination's buffer: [rs_rows, N] bf16 at slot index rs_rank
+      for (int d = 0; d < a->rs_world; ++d) {
+        if (a->rs_out[d] == nullptr) return cudaErrorInvalidValue;
+        const char* base = static_cast<const char*>(a->rs_out[d]) + 1ll * a->rs_rank * a->rs_rows * a->ldo * 2;
+        e = make_tensor_map_3d(&peer.m[d], base, TmaDtype::kBF16, N, a->rs_rows, 1, a->ldo * 2, 0, 64, 32, true);
+        if (e != cudaSuccess) return e;
+      }
+    } else {
+      if (a->out == nullptr) return cudaErrorInvalidValue;
+      e = make_tensor_map_3d(&peer.m[0], a->out, TmaDtype::kBF16, N, M, batch, a->ldo * 2, a->out_batch_stride * 2, 64,
+                             32, true);
+      if (e != cudaSuccess) return e;
+    }
+  }
   GemmParams p{};
-  p.ag_world = a->ag_world; p.ag_rank = a->ag_rank; p.ag_rows = a->ag_rows;
-  p.ag_flags = reinterpret_cast<const uint32_t* const*>(a->ag_flags);
+  p.ag_world = a->ag_world; p.ag_rank = a->ag_rank; p.ag_rows = a->ag_rows; p.ag_chunks = ag_chunks;
+  p.a_row_bytes = a->lda * elem;
+  for (int r = 0; r < 8; ++r) {
+    p.ag_bufs[r] = r < a->ag_world ? a->a_peers[r] : nullptr;
+    p.ag_arrive[r] = r < a->ag_world ? static_cast<uint32_t*>(a->ag_arrive[r]) : nullptr;
+  }
   p.ag_epoch = reinterpret_cast<const uint32_t*>(a->ag_epoch);
   p.rs_world = a->rs_world; p.rs_rank = a->rs_rank; p.rs_rows = a->rs_rows;
   for (int r = 0; r < 8; ++r) p.rs_out[r] = r < a->rs_world ? a->rs_out[r] : nullptr;

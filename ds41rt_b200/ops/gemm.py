@@ -71,8 +71,11 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         gemm_raw(w, x, out, N, rows, K, lda=w.stride(0), ldb=x.stride(0), ldo=out.stride(0),
                  out_mode=3 if f32 else 2, status=status, static_operand=1)
     else:
+        # bf16 results leave through the TMA-store epilogue when the output rows are 16-byte aligned
+        tma_out = not f32 and N >= 64 and (out.stride(0) * 2) % 16 == 0 and out.data_ptr() % 16 == 0
         gemm_raw(x, w, out, rows, N, K, lda=x.stride(0), ldb=w.stride(0), ldo=out.stride(0),
-                 out_mode=1 if f32 else 0, bn=256 if N >= 256 else 128, status=status, static_operand=2)
+                 out_mode=1 if f32 else (6 if tma_out else 0), bn=256 if N >= 256 else (128 if N >= 128 else 64),
+                 status=status, static_operand=2)
     return out
 
 

@@ -32,7 +32,7 @@ class GemmArgs(C.Structure):
         ("static_operand", C.c_int),
         ("ag_world", C.c_int), ("ag_rank", C.c_int), ("ag_rows", C.c_int),
         ("rs_world", C.c_int), ("rs_rank", C.c_int), ("rs_rows", C.c_int),
-        ("a_peers", C.c_void_p * 8), ("ag_flags", C.c_void_p), ("ag_epoch", C.c_void_p), ("rs_out", C.c_void_p * 8),
+        ("a_peers", C.c_void_p * 8), ("ag_arrive", C.c_void_p * 8), ("ag_epoch", C.c_void_p), ("rs_out", C.c_void_p * 8),
         ("tile_group", C.c_void_p), ("tile_row0", C.c_void_p), ("tile_end", C.c_void_p), ("n_tiles_dev", C.c_void_p),
         ("scatter_meta", C.c_void_p), ("wait_flags", C.c_void_p), ("wait_epoch", C.c_void_p),
         ("scatter_out", C.c_void_p * 8), ("max_tiles", C.c_int), ("wait_world", C.c_int),
@@ -55,7 +55,7 @@ class HcStepArgs(C.Structure):
 class EpArgs(C.Structure):
     _fields_ = [
         ("world", C.c_int), ("rank", C.c_int), ("e_local", C.c_int), ("topk", C.c_int), ("tokens", C.c_int),
-        ("H", C.c_int), ("cap", C.c_int), ("bn", C.c_int), ("max_tiles", C.c_int),
+        ("H", C.c_int), ("cap", C.c_int), ("bn", C.c_int), ("bn2", C.c_int), ("max_tiles", C.c_int),
         ("x", C.c_void_p), ("ids", C.c_void_p), ("weights", C.c_void_p), ("epoch", C.c_void_p),
         ("cursor", C.c_void_p), ("ticket", C.c_void_p),
         ("counts", C.c_void_p * 8), ("send_base", C.c_void_p * 8), ("recv_x", C.c_void_p * 8),

@@ -43,7 +43,8 @@ class ExpertParallelMoE:
         self.topk, self.max_tokens, self.act_limit = topk, max_tokens, act_limit
         W, dev = fabric.world, fabric.device
         assert self.H % 128 == 0 and self.I % 128 == 0 and W <= 8
-        self.bn = 64 if self.mx else 128
+        self.bn = 64 if self.mx else 128          # FC1: gate and up accumulators share tensor memory
+        self.bn2 = 128 if self.mx else 256         # FC2
         worst = W * max_tokens * topk
         self.cap = _round_up(min(worst, capacity) if capacity else worst, 128) + 128 * self.e_local
         self.max_tiles = self.cap // self.bn + self.e_local
@@ -70,10 +71,10 @@ class ExpertParallelMoE:
         self.epoch = torch.zeros(1, **i32)
         self.cursor = torch.zeros(W * self.e_local, **i32)
         self.ticket = torch.zeros(1, **i32)
-        self.tile_group = torch.zeros(self.max_tiles, **i32)
-        self.tile_row0 = torch.zeros(self.max_tiles, **i32)
-        self.tile_end = torch.zeros(self.max_tiles, **i32)
-        self.n_tiles = torch.zeros(1, **i32)
+        self.tile_group = torch.zeros(2 * self.max_tiles, **i32)
+        self.tile_row0 = torch.zeros(2 * self.max_tiles, **i32)
+        self.tile_end = torch.zeros(2 * self.max_tiles, **i32)
+        self.n_tiles = torch.zeros(2, **i32)
         self.total_rows = torch.zeros(1, **i32)
         self.status = lib.new_status(dev)
         self.act = torch.zeros(cap, self.I, dtype=torch.bfloat16, device=dev)
@@ -84,12 +85,13 @@ class ExpertParallelMoE:
             self.actq = torch.zeros(cap, self.I, **u8)
             self.actq_sf = torch.zeros(cap // 128 * (self.I // 128) * 512, **u8)
         self.dispatch_blocks = 4 * 148
+        self.marks = None          # list of (name, event) while phase timing is on
 
     # ------------------------------------------------------------------ argument blocks
     def _ep_args(self, x, ids, weights, tokens) -> lib.EpArgs:
         f, a = self.f, lib.EpArgs()
         a.world, a.rank, a.e_local, a.topk, a.tokens = f.world, f.rank, self.e_local, self.topk, tokens
-        a.H, a.cap, a.bn, a.max_tiles = self.H, self.cap, self.bn, self.max_tiles
+        a.H, a.cap, a.bn, a.bn2, a.max_tiles = self.H, self.cap, self.bn, self.bn2, self.max_tiles
         a.x, a.ids, a.weights = lib.ptr(x), lib.ptr(ids), lib.ptr(weights)
         a.epoch, a.cursor, a.ticket = lib.ptr(self.epoch), lib.ptr(self.cursor), lib.ptr(self.ticket)
         for r, base in enumerate(self.sym.peer_ptrs):
@@ -103,15 +105,17 @@ class ExpertParallelMoE:
         a.n_tiles, a.total_rows, a.status = lib.ptr(self.n_tiles), lib.ptr(self.total_rows), lib.ptr(self.status)
         return a
 
-    def _grouped(self, A, B, out, M, K, *, lda, ldo, out_mode, wait_phase=None, **kw) -> None:
+    def _grouped(self, A, B, out, M, K, *, lda, ldo, out_mode, wait_phase=None, table=0, **kw) -> None:
         a = lib.GemmArgs()
         a.A, a.B, a.out, a.status = lib.ptr(A), lib.ptr(B), lib.ptr(out), lib.ptr(self.status)
         a.lda, a.ldb, a.ldo = lda, K, ldo
         a.M, a.N, a.K, a.batch, a.a_batches = M, self.cap, K, self.e_local, self.e_local
         a.a_batch_stride = A.stride(0)
-        a.kind, a.out_mode, a.k_splits, a.bn, a.b_batch_kind = (2 if self.mx else 0), out_mode, 1, self.bn, 1
-        a.tile_group, a.tile_row0, a.tile_end = lib.ptr(self.tile_group), lib.ptr(self.tile_row0), lib.ptr(self.tile_end)
-        a.n_tiles_dev, a.max_tiles = lib.ptr(self.n_tiles), self.max_tiles
+        a.kind, a.out_mode, a.k_splits, a.b_batch_kind = (2 if self.mx else 0), out_mode, 1, 1
+        a.bn = self.bn2 if table else self.bn
+        t0 = table * self.max_tiles
+        a.tile_group, a.tile_row0 = lib.ptr(self.tile_group[t0:]), lib.ptr(self.tile_row0[t0:])
+        a.tile_end, a.n_tiles_dev, a.max_tiles = lib.ptr(self.tile_end[t0:]), lib.ptr(self.n_tiles[table:]), self.max_tiles
         a.row_w, a.act_limit = lib.ptr(self.recv_w), self.act_limit
         if wait_phase is not None and self.f.world > 1:
             a.wait_flags, a.wait_epoch, a.wait_world = lib.ptr(self.flag_ptrs[wait_phase]), lib.ptr(self.epoch), self.f.world
@@ -122,6 +126,25 @@ class ExpertParallelMoE:
             for r, base in enumerate(self.sym.peer_ptrs):
                 a.scatter_out[r] = base + self.lay["comb"]
         lib.check(lib.kernels().ds41_gemm_tc(C.byref(a), lib.stream()), "grouped gemm")
+
+    def _mark(self, name: str) -> None:
+        if self.marks is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.marks.append((name, ev))
+
+    def phase_times(self, *args, reps: int = 5):
+        """Per-phase device times (ms) of forward(*args), averaged over `reps` calls."""
+        acc = {}
+        for _ in range(reps):
+            self.marks = []
+            self._mark("start")
+            self.forward(*args)
+            torch.cuda.synchronize()
+            for (_, e0), (name, e1) in zip(self.marks[:-1], self.marks[1:]):
+                acc[name] = acc.get(name, 0.0) + e0.elapsed_time(e1) / reps
+        self.marks = None
+        return acc
 
     # ------------------------------------------------------------------ the fused layer
     def forward(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, out: torch.Tensor,
@@ -136,7 +159,9 @@ class ExpertParallelMoE:
         a = self._ep_args(x, ids, weights, T)
         lib.check(k.ds41_ep_count(C.byref(a), st()), "ep_count")
         lib.check(k.ds41_ep_plan(C.byref(a), st()), "ep_plan")
+        self._mark("count+plan")
         lib.check(k.ds41_ep_dispatch(C.byref(a), self.dispatch_blocks, st()), "ep_dispatch")
+        self._mark("dispatch")
         if self.mx:
             lib.check(k.ds41_ep_wait(C.byref(a), 2, st()), "ep_wait")
             cap = self.cap
@@ -145,19 +170,24 @@ class ExpertParallelMoE:
                                           H, 1, 128, None, st()), "act_quant")
             self._grouped(self.w13, self.xq, self.act, I, H, lda=H, ldo=I, out_mode=4, up_row_offset=I,
                           sfa=self.w13_sf, sfa_batch_stride=self.w13_sf[0].numel(), sfb=self.xq_sf)
+            self._mark("wait+quant+fc1")
             lib.check(k.ds41_act_quant_mx(lib.ptr(self.act), C.c_longlong(I), C.c_longlong(0), lib.ptr(self.actq),
                                           C.c_longlong(I), C.c_longlong(0), lib.ptr(self.actq_sf), C.c_longlong(0), cap,
                                           I, 1, 128, None, st()), "act_quant")
-            self._grouped(self.w2, self.actq, self.comb, H, I, lda=I, ldo=H, out_mode=7, sfa=self.w2_sf,
+            self._grouped(self.w2, self.actq, self.comb, H, I, lda=I, ldo=H, out_mode=7, table=1, sfa=self.w2_sf,
                           sfa_batch_stride=self.w2_sf[0].numel(), sfb=self.actq_sf)
+            self._mark("quant+fc2")
         else:
             self._grouped(self.w13, self.recv_x, self.act, I, H, lda=H, ldo=I, out_mode=4, up_row_offset=I,
                           wait_phase=2)
-            self._grouped(self.w2, self.act, self.comb, H, I, lda=I, ldo=H, out_mode=7)
+            self._mark("fc1")
+            self._grouped(self.w2, self.act, self.comb, H, I, lda=I, ldo=H, out_mode=7, table=1)
+            self._mark("fc2")
         lib.check(k.ds41_ep_mark(C.byref(a), 3, st()), "ep_mark")
         lib.check(k.ds41_ep_combine(C.byref(a), lib.ptr(self.comb), lib.ptr(extra),
                                     C.c_longlong(extra.stride(0) if extra is not None else 0), lib.ptr(out),
                                     1 if out.dtype == torch.bfloat16 else 0, st()), "ep_combine")
+        self._mark("mark+combine")
         return out
 
     def check(self):

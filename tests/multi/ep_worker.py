@@ -79,6 +79,7 @@ def main():
     t_fused = timed(f, lambda: moe.forward(x, ids, wts, out, extra), reps)
     t_base = timed(f, lambda: moe.baseline(x, ids, wts, w13_ref, w2_ref, extra), reps)
     moe.check()
+    phases = moe.phase_times(x, ids, wts, out, extra, reps=reps) if int(os.environ.get("EP_PHASES", "0")) else None
     if f.rank == 0:
         routes = T * topk                                       # per rank
         flops = 2.0 * routes * H * (3 * I)                      # per rank when balanced
@@ -90,6 +91,8 @@ def main():
                "fused_ms": t_fused, "nccl_library_ms": t_base,
                "roofline_ms": max(flops / peak, (nv_bytes / 2) / link) * 1e3}
         res["frac_of_roofline"] = res["roofline_ms"] / t_fused
+        if phases:
+            res["phases_ms_rank0"] = {k: round(v, 4) for k, v in phases.items()}
         print("EP " + json.dumps(res))
         print("EP_OK")
     f.barrier()

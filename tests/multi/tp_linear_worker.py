@@ -67,8 +67,8 @@ def main():
     if f.rank == 0:
         flops = 2.0 * W * rows * K * (N // W)
         link = 770e9
-        ag_bytes = (W - 1) * rows * K * 2                  # bytes this GPU must pull over NVLink
-        rs_bytes = (W - 1) * rows * K * 4                  # fp32 slots pushed to the peers
+        ag_bytes = (W - 1) * rows * K * 2                  # bytes this GPU pushes over NVLink (bf16 rows)
+        rs_bytes = (W - 1) * rows * K * 2                  # bf16 partial rows pushed to the peers
         peak = float(os.environ.get("PEAK_TFLOPS", "1430")) * 1e12
         res = {"world": W, "rows_per_rank": rows, "K": K, "N": N,
                "ag_gemm_ms": t_ag, "ag_gemm_nccl_ms": t_ag_base, "gemm_rs_ms": t_rs, "gemm_rs_nccl_ms": t_rs_base,

@@ -14,7 +14,8 @@ def _rel(out, ref):
 
 
 @pytest.mark.parametrize("rows,N,K", [(1, 256, 512), (5, 1280, 5120), (16, 384, 1024), (64, 512, 192),
-                                      (100, 640, 2304), (300, 1024, 512), (1000, 768, 1536)])
+                                      (100, 640, 2304), (300, 1024, 512), (1000, 768, 1536), (300, 200, 512),
+                                      (257, 72, 256)])
 def test_matmul_nt_bf16(rows, N, K):
     from ds41rt_b200.ops import gemm as G, lib
     torch.manual_seed(rows + N)
