@@ -230,6 +230,10 @@ int ds41_ep_wait(const ds41_ep_args* a, int phase, void* stream);
 int ds41_ep_combine(const ds41_ep_args* a, const void* comb, const float* extra, long long extra_ld, void* out,
                     int as_bf16, void* stream);
 
+// Prefill-sized activation quantiser (1x128 scales, one warp per row); rows >= *rows_dev (if given) are skipped.
+int ds41_act_quant_mx_rows(const void* x, long long ldx, void* q, long long ldq, void* sf, int rows, int K,
+                           const int* rows_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

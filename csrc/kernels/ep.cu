@@ -53,7 +53,7 @@ struct EpParams {
 
 constexpr int kEpOverflow = 7;   // status code: received rows exceed the receive buffer
 
-__global__ void __launch_bounds__(256) ep_count_kernel(EpParams p) {
+__global__ void __launch_bounds__(1024) ep_count_kernel(EpParams p) {
   extern __shared__ int hist[];
   pdl_launch_dependents();
   pdl_wait();
@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(256) ep_count_kernel(EpParams p) {
 }
 
 __global__ void __launch_bounds__(256) ep_plan_kernel(EpParams p) {
-  extern __shared__ int sm[];   // [e_local] group sizes, [e_local] group offsets
+  extern __shared__ int sm[];   // [e_local] group sizes, group offsets, first tiles (two tables)
   int* gsize = sm;
   int* goff = sm + p.e_local;
   __shared__ int s_ok;
@@ -103,40 +103,21 @@ __global__ void __launch_bounds__(256) ep_plan_kernel(EpParams p) {
     gsize[e] = g;
   }
   __syncthreads();
+  // table 0 (tiles of bn rows) at [0, max_tiles), table 1 (tiles of bn2 rows, if bn2 > 0) at [max_tiles, 2*max_tiles)
+  int* toff = goff + p.e_local;        // [e_local] first tile of each expert, table 0
+  int* toff2 = toff + p.e_local;       // same for table 1
   if (threadIdx.x == 0) {
-    // table 0 (tiles of bn rows) at [0, max_tiles), table 1 (tiles of bn2 rows, if bn2 > 0) at [max_tiles, 2*max_tiles)
     int off = 0, nt = 0, nt2 = 0;
-    bool fits = s_ok != 0;
     for (int e = 0; e < p.e_local; ++e) {
       goff[e] = off;
+      toff[e] = nt;
+      toff2[e] = nt2;
       const int g = gsize[e];
-      if (off + g > p.cap) fits = false;
-      if (fits) {
-        for (int r0 = off; r0 < off + g; r0 += p.bn) {
-          if (nt < p.max_tiles) {
-            p.tile_group[nt] = e;
-            p.tile_row0[nt] = r0;
-            p.tile_end[nt] = min(r0 + p.bn, off + g);
-            ++nt;
-          } else {
-            fits = false;
-          }
-        }
-        if (p.bn2 > 0) {
-          for (int r0 = off; r0 < off + g; r0 += p.bn2) {
-            if (nt2 < p.max_tiles) {
-              p.tile_group[p.max_tiles + nt2] = e;
-              p.tile_row0[p.max_tiles + nt2] = r0;
-              p.tile_end[p.max_tiles + nt2] = min(r0 + p.bn2, off + g);
-              ++nt2;
-            } else {
-              fits = false;
-            }
-          }
-        }
-      }
+      nt += (g + p.bn - 1) / p.bn;
+      if (p.bn2 > 0) nt2 += (g + p.bn2 - 1) / p.bn2;
       off += (g + p.group_align - 1) / p.group_align * p.group_align;
     }
+    const bool fits = s_ok != 0 && off <= p.cap && nt <= p.max_tiles && nt2 <= p.max_tiles;
     if (!fits) {
       nt = nt2 = 0;
       if (p.status != nullptr && s_ok != 0 && atomicCAS(p.status, 0, kEpOverflow) == 0) {
@@ -149,6 +130,26 @@ __global__ void __launch_bounds__(256) ep_plan_kernel(EpParams p) {
     p.n_tiles[0] = nt;
     p.n_tiles[1] = nt2;
     *p.total_rows = fits ? off : 0;
+  }
+  __syncthreads();
+  if (s_ok) {
+    for (int e = threadIdx.x; e < p.e_local; e += blockDim.x) {
+      const int off = goff[e], g = gsize[e];
+      int t = toff[e];
+      for (int r0 = off; r0 < off + g; r0 += p.bn, ++t) {
+        p.tile_group[t] = e;
+        p.tile_row0[t] = r0;
+        p.tile_end[t] = min(r0 + p.bn, off + g);
+      }
+      if (p.bn2 > 0) {
+        t = p.max_tiles + toff2[e];
+        for (int r0 = off; r0 < off + g; r0 += p.bn2, ++t) {
+          p.tile_group[t] = e;
+          p.tile_row0[t] = r0;
+          p.tile_end[t] = min(r0 + p.bn2, off + g);
+        }
+      }
+    }
   }
   __syncthreads();
   // first row of every (source, expert) run; -1 tells the source to drop the route (receive buffer too small)
@@ -188,7 +189,19 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpParams p) {
     const int tok = i / p.topk;
     const uint4* src = reinterpret_cast<const uint4*>(p.x + 1ll * tok * p.H);
     uint4* out = reinterpret_cast<uint4*>(p.recv_x[dst] + 1ll * row * p.H);
-    for (int v = lane; v < vec; v += 32) out[v] = src[v];
+    for (int v0 = 0; v0 < vec; v0 += 32 * 4) {      // four 16-byte loads in flight per lane
+      uint4 w[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int v = v0 + q * 32 + lane;
+        if (v < vec) w[q] = src[v];
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int v = v0 + q * 32 + lane;
+        if (v < vec) out[v] = w[q];
+      }
+    }
     if (lane == 0) {
       p.recv_meta[dst][row] = make_int2(p.rank, i);
       p.recv_w[dst][row] = p.weights[i];
@@ -292,13 +305,13 @@ extern "C" int ds41_ep_count(const ds41_ep_args* a, void* stream) {
   EpParams p;
   if (!fill(a, p)) return cudaErrorInvalidValue;
   const size_t smem = sizeof(int) * p.world * p.e_local;
-  return launch_pdl(ep_count_kernel, dim3(1), dim3(256), smem, static_cast<cudaStream_t>(stream), p);
+  return launch_pdl(ep_count_kernel, dim3(1), dim3(1024), smem, static_cast<cudaStream_t>(stream), p);
 }
 
 extern "C" int ds41_ep_plan(const ds41_ep_args* a, void* stream) {
   EpParams p;
   if (!fill(a, p)) return cudaErrorInvalidValue;
-  const size_t smem = sizeof(int) * 2 * p.e_local;
+  const size_t smem = sizeof(int) * 4 * p.e_local;
   return launch_pdl(ep_plan_kernel, dim3(1), dim3(256), smem, static_cast<cudaStream_t>(stream), p);
 }
 

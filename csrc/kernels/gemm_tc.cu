@@ -93,7 +93,7 @@ struct GemmCfg {
   // scale-factor atoms (512 B each), padded so every stage keeps its 1024-byte tile alignment
   static constexpr int kSfBytes = (KIND == 2) ? ((512 * (kAtomsA + kAtomsB) + 1023) / 1024 * 1024) : 0;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
-  static constexpr int kStaging = (KIND == 0 && !DUAL && BN >= 64) ? kStagingBytes : 0;
+  static constexpr int kStaging = (!DUAL && BN >= 64) ? kStagingBytes : 0;
   static constexpr int kStagesRaw = ((kStaging ? 194 : 200) * 1024) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kSfCols = (KIND == 2) ? 4 * (kAtomsA + kAtomsB) : 0;           // TMEM columns per stage
@@ -105,6 +105,24 @@ struct GemmCfg {
   static_assert(kTmemNeeded <= 512, "TMEM budget exceeded");
   static_assert(kStages >= 2, "not enough shared memory for two stages");
 };
+
+// Tile order: bands of kBandTiles m-tiles; inside a band the m-tile runs fastest, then the n-tile.  The CTAs of one
+// wave then share a few n-tiles of B and a band of A that stays in L2 while the band sweeps N, instead of streaming all
+// of A from DRAM once per n-tile.  Returns the remaining (split, batch) index.
+constexpr int kBandTiles = 16;
+__device__ __forceinline__ long long decode_tile(long long t, int m_tiles, int n_tiles, int band_tiles, int& mt,
+                                                 int& nt) {
+  const long long per_mn = 1ll * m_tiles * n_tiles;
+  const long long outer = t / per_mn;
+  const int r = static_cast<int>(t - outer * per_mn);
+  const int per_band = band_tiles * n_tiles;
+  const int band = r / per_band;
+  const int rb = r - band * per_band;
+  const int band_rows = min(band_tiles, m_tiles - band * band_tiles);
+  nt = rb / band_rows;
+  mt = band * band_tiles + (rb - nt * band_rows);
+  return outer;
+}
 
 template <int BN, int KIND, int DUAL>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -121,7 +139,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint64_t* empty = full + S;
   uint64_t* acc_full = empty + S;
   uint64_t* acc_empty = acc_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* epi_bar = acc_empty + 2;        // the four epilogue warps meet here when they share a staging buffer
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_bar + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -130,6 +149,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const bool table = p.tile_group != nullptr;
   if (table) pdl_wait();              // the tile table is produced by an earlier kernel
   const int n_tiles = table ? *p.n_tiles_dev : (p.N + BN - 1) / BN;
+  // grouped experts sweep all weight tiles of an expert per token tile; dense GEMMs use bands
+  const int band_tiles = table ? m_tiles : kBandTiles;
   const int kb_total = (p.K + Cfg::kBK - 1) / Cfg::kBK;
   const int kb_per_split = (kb_total + p.k_splits - 1) / p.k_splits;
   pdl_launch_dependents();
@@ -153,6 +174,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 4);
     }
+    mbar_init(epi_bar, 4);
     mbar_init_fence();
   }
   __syncwarp();
@@ -177,8 +199,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int prefetched = 0;
     if (p.static_operand != 0 && p.n_active == nullptr && p.batch_map == nullptr && !table && blockIdx.x < tiles) {
       long long r = blockIdx.x;
-      const int mt = static_cast<int>(r % m_tiles); r /= m_tiles;
-      const int nt = static_cast<int>(r % n_tiles); r /= n_tiles;
+      int mt, nt;
+      r = decode_tile(r, m_tiles, n_tiles, band_tiles, mt, nt);
       const int sp = static_cast<int>(r % p.k_splits); r /= p.k_splits;
       const int b = static_cast<int>(r);
       const int kb0 = sp * kb_per_split;
@@ -203,8 +225,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
       long long r = t;
-      const int mt = static_cast<int>(r % m_tiles); r /= m_tiles;
-      const int nt = static_cast<int>(r % n_tiles); r /= n_tiles;
+      int mt, nt;
+      r = decode_tile(r, m_tiles, n_tiles, band_tiles, mt, nt);
       const int sp = static_cast<int>(r % p.k_splits); r /= p.k_splits;
       const int b = table ? p.tile_group[nt] : static_cast<int>(r);
       const int n_base = table ? p.tile_row0[nt] : nt * BN;
@@ -270,8 +292,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     constexpr uint32_t kFmt = (KIND == 0) ? 1u : 0u;   // bf16 / e4m3
     constexpr uint32_t idesc = umma_idesc(kBM, BN, kFmt, kFmt);
     for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-      const int nt = static_cast<int>((t / m_tiles) % n_tiles);
-      long long r = t / (1ll * m_tiles * n_tiles);
+      int mt_unused, nt;
+      const long long r = decode_tile(t, m_tiles, n_tiles, band_tiles, mt_unused, nt);
       const int sp = static_cast<int>(r % p.k_splits);
       const int kb0 = sp * kb_per_split;
       const int kb1 = min(kb_total, kb0 + kb_per_split);
@@ -331,14 +353,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t acc_phase = 0;
     bool ok = true;
     uint32_t st_pair = 0;                      // mode 6: staging buffer parity of this warp
+    uint32_t epi_count = 0;                    // mode 7: chunks staged so far (buffer = count & 1, barrier phase)
     for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
       long long r = t;
-      const int mt = static_cast<int>(r % m_tiles); r /= m_tiles;
-      const int nt = static_cast<int>(r % n_tiles); r /= n_tiles;
+      int mt, nt;
+      r = decode_tile(r, m_tiles, n_tiles, band_tiles, mt, nt);
       const int sp = static_cast<int>(r % p.k_splits); r /= p.k_splits;
       const int b = table ? p.tile_group[nt] : static_cast<int>(r);
       const int n_base = table ? p.tile_row0[nt] : nt * BN;
       const int n_lim = table ? p.tile_end[nt] : p.N;
+      // per-column metadata (route weight / return address) of the first chunk, fetched while the MMAs still run;
+      // every chunk then fetches the next chunk's before it starts its own stores
+      constexpr int kChunkPre = BN >= 32 ? 32 : BN;
+      const float* rw_base = (p.out_mode == 4 || p.out_mode == 5) ? p.row_w + (table ? 0ll : 1ll * b * p.row_w_ld) : nullptr;
+      float rw_next = 0.f;
+      int2 meta_next = make_int2(-1, -1);
+      if (lane < kChunkPre && n_base + lane < n_lim) {
+        if (rw_base != nullptr) rw_next = __ldcg(rw_base + n_base + lane);
+        if (p.out_mode == 7) meta_next = __ldcg(p.scatter_meta + n_base + lane);
+      }
       if (!mbar_wait(&acc_full[acc], acc_phase, p.status, 300)) { ok = false; break; }
       tc_fence_after();
       const int m = (rot ? (mt + rot) % m_tiles : mt) * kBM + quad * 32 + lane;
@@ -371,6 +404,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         tmem_wait_ld();
         const int n0 = n_base + c;
+        const float rw_lane = rw_next;
+        const int2 meta_lane = meta_next;
+        rw_next = 0.f;
+        meta_next = make_int2(-1, -1);
+        if (c + kChunk < BN && lane < kChunk && n0 + kChunk + lane < n_lim) {
+          if (rw_base != nullptr) rw_next = __ldcg(rw_base + n0 + kChunk + lane);
+          if (p.out_mode == 7) meta_next = __ldcg(p.scatter_meta + n0 + kChunk + lane);
+        }
         if (p.out_mode == 0) {
           if (m < p.M) {
             __nv_bfloat16* o = rs_base != nullptr ? reinterpret_cast<__nv_bfloat16*>(rs_base) + rs_row * p.ldo + n0
@@ -437,10 +478,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             tmem_wait_ld();
             __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + obase + m;
-            const float* rw = p.row_w + (table ? 0ll : 1ll * b * p.row_w_ld);
-            // one coalesced load of the chunk's route weights, handed out by shuffle: a load per column would be
-            // ordered behind the previous column's store
-            const float rw_lane = (lane < kChunk && n0 + lane < n_lim) ? __ldcg(rw + n0 + lane) : 0.f;
+            // the chunk's route weights were fetched with one coalesced load and are handed out by shuffle: a load per
+            // column would be ordered behind the previous column's store
 #pragma unroll
             for (int j = 0; j < kChunk; ++j) {
               const float rwj = __shfl_sync(0xffffffffu, rw_lane, j);
@@ -496,22 +535,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         } else if (p.out_mode == 7) {
           // expert-parallel combine: column n is a received token row; its result row goes back to the rank it
-          // came from, into that rank's combine buffer at the (token, route) slot - a P2P store from the epilogue
-          int2 meta_lane = make_int2(-1, -1);
-          if (lane < kChunk && n0 + lane < n_lim) meta_lane = __ldcg(p.scatter_meta + n0 + lane);
+          // came from, into that rank's combine buffer at the (token, route) slot - P2P stores from the epilogue.
+          if constexpr (Cfg::kStaging > 0) {
+            // The four warps transpose the chunk through shared memory ([32 tokens][128 features] bf16) so that half a
+            // warp writes 256 contiguous bytes of one token: 8x fewer and 4x longer stores than one column per warp.
+            uint8_t* buf = staging + (epi_count & 1u) * 8192;
+            __nv_bfloat16* col = reinterpret_cast<__nv_bfloat16*>(buf) + quad * 32 + lane;
 #pragma unroll
-          for (int j = 0; j < kChunk; ++j) {
-            const int src = __shfl_sync(0xffffffffu, meta_lane.x, j);
-            const int slot = __shfl_sync(0xffffffffu, meta_lane.y, j);
-            if (m < p.M && src >= 0 && src < 8 && slot >= 0) {
-              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.scatter_out[src]) + 1ll * slot * p.ldo + m;
-              *o = __float2bfloat16_rn(__uint_as_float(v[j]));
+            for (int j = 0; j < kChunk; ++j) col[j * 128] = __float2bfloat16_rn(__uint_as_float(v[j]));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(epi_bar);
+            if (!mbar_wait(epi_bar, epi_count & 1u, p.status, 310)) { ok = false; break; }
+            ++epi_count;
+            const int e = quad * 32 + lane;
+            const int m_tile0 = (rot ? (mt + rot) % m_tiles : mt) * kBM;
+            const int piece = e & 15;
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+              const int j = it * 8 + (e >> 4);
+              const int src = __shfl_sync(0xffffffffu, meta_lane.x, j & 31);
+              const int slot = __shfl_sync(0xffffffffu, meta_lane.y, j & 31);
+              const int mm = m_tile0 + piece * 8;
+              if (src >= 0 && src < 8 && slot >= 0 && mm < p.M) {
+                const uint4 w = *reinterpret_cast<const uint4*>(buf + j * 256 + piece * 16);
+                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.scatter_out[src]) + 1ll * slot * p.ldo + mm;
+                if (mm + 8 <= p.M) {
+                  *reinterpret_cast<uint4*>(o) = w;
+                } else {
+                  const __nv_bfloat16* wh = reinterpret_cast<const __nv_bfloat16*>(&w);
+                  for (int q = 0; q < 8 && mm + q < p.M; ++q) o[q] = wh[q];
+                }
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) {
+              const int src = __shfl_sync(0xffffffffu, meta_lane.x, j);
+              const int slot = __shfl_sync(0xffffffffu, meta_lane.y, j);
+              if (m < p.M && src >= 0 && src < 8 && slot >= 0) {
+                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.scatter_out[src]) + 1ll * slot * p.ldo + m;
+                *o = __float2bfloat16_rn(__uint_as_float(v[j]));
+              }
             }
           }
         } else {
           float* o = reinterpret_cast<float*>(p.out) + obase + m;
-          const float* rw = p.row_w + (table ? 0ll : 1ll * b * p.row_w_ld);
-          const float rw_lane = (lane < kChunk && n0 + lane < n_lim) ? __ldcg(rw + n0 + lane) : 0.f;
 #pragma unroll
           for (int j = 0; j < kChunk; ++j) {
             const float rwj = __shfl_sync(0xffffffffu, rw_lane, j);
@@ -638,7 +706,8 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   if (kind == 2 && bn < 32 && N > bn) return cudaErrorInvalidValue;      // 16-row scale tiles cannot be lane-shifted
   if (k_splits > 1 && out_mode != 1 && out_mode != 3) return cudaErrorInvalidValue;   // partials are fp32
   if ((out_mode == 4 || out_mode == 5) && a->row_w == nullptr) return cudaErrorInvalidValue;
-  if (out_mode == 7 && (a->scatter_meta == nullptr || a->tile_group == nullptr)) return cudaErrorInvalidValue;
+  if (out_mode == 7 && (a->scatter_meta == nullptr || a->tile_group == nullptr || (a->ldo & 7) != 0))
+    return cudaErrorInvalidValue;
   if (a->tile_group != nullptr && (a->tile_row0 == nullptr || a->tile_end == nullptr || a->n_tiles_dev == nullptr ||
                                    k_splits != 1 || a->max_tiles <= 0))
     return cudaErrorInvalidValue;

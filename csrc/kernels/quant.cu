@@ -13,6 +13,17 @@
 
 namespace ds41 {
 
+static int sm_count_cached() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
 __device__ __forceinline__ uint32_t ue8m0_ceil_exp(float x) {
   x = fmaxf(x, 1.17549435e-38f);
   const uint32_t bits = __float_as_uint(x);
@@ -68,9 +79,67 @@ __global__ void __launch_bounds__(256) act_quant_mx_kernel(ActQuantParams p) {
   }
 }
 
+// Prefill-sized variant (1x128 scales): one warp per row, 16 bytes per lane, two 128-wide K chunks per step; only rows
+// below *rows_dev (a device count, e.g. the rows an expert-parallel rank received) are touched.
+__global__ void __launch_bounds__(256)
+act_quant_mx_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q, long long ldq,
+                         uint8_t* __restrict__ sf, int rows, int K, const int* __restrict__ rows_dev) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int live = rows_dev != nullptr ? min(rows, *rows_dev) : rows;
+  const int chunks = K / 128;
+  for (int r = blockIdx.x * 8 + warp; r < live; r += gridDim.x * 8) {
+    const __nv_bfloat16* src = x + 1ll * r * ldx;
+    uint8_t* dst = q + 1ll * r * ldq;
+    uint8_t* atom_row = sf + 1ll * (r / 128) * chunks * 512 + (r % 32) * 16 + ((r / 32) % 4) * 4;
+    for (int k0 = 0; k0 < K; k0 += 256) {
+      const int k = k0 + lane * 8;
+      float f[8];
+      float amax = 0.f;
+      if (k < K) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + k);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 v = __bfloat1622float2(h[j]);
+          f[2 * j] = v.x;
+          f[2 * j + 1] = v.y;
+          amax = fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y)));
+        }
+      }
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
+      if (k < K) {
+        const uint32_t e = ue8m0_ceil_exp(amax * (1.0f / 448.0f));
+        const float inv = __uint_as_float((254u - e) << 23);
+        const __nv_fp8x4_e4m3 lo(make_float4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv));
+        const __nv_fp8x4_e4m3 hi(make_float4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv));
+        uint2 o;
+        o.x = *reinterpret_cast<const uint32_t*>(&lo);
+        o.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(dst + k) = o;
+        if ((lane & 15) == 0)
+          *reinterpret_cast<uint32_t*>(atom_row + 1ll * (k / 128) * 512) = e * 0x01010101u;
+      }
+    }
+  }
+}
+
 }  // namespace ds41
 
 using namespace ds41;
+
+extern "C" int ds41_act_quant_mx_rows(const void* x, long long ldx, void* q, long long ldq, void* sf, int rows, int K,
+                                      const int* rows_dev, void* stream) {
+  if (rows <= 0 || K <= 0 || K % 128 != 0 || (ldx & 7) || (ldq & 7)) return cudaErrorInvalidValue;
+  const int blocks = min((rows + 7) / 8, 8 * sm_count_cached());
+  return launch_pdl(act_quant_mx_rows_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(q), ldq, static_cast<uint8_t*>(sf),
+                    rows, K, rows_dev);
+}
 
 extern "C" int ds41_act_quant_mx(const void* x, long long ldx, long long x_batch_stride, void* q, long long ldq,
                                  long long q_batch_stride, void* sf, long long sf_batch_stride, int rows, int K,

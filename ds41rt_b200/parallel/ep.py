@@ -165,15 +165,13 @@ class ExpertParallelMoE:
         if self.mx:
             lib.check(k.ds41_ep_wait(C.byref(a), 2, st()), "ep_wait")
             cap = self.cap
-            lib.check(k.ds41_act_quant_mx(lib.ptr(self.recv_x), C.c_longlong(H), C.c_longlong(0), lib.ptr(self.xq),
-                                          C.c_longlong(H), C.c_longlong(0), lib.ptr(self.xq_sf), C.c_longlong(0), cap,
-                                          H, 1, 128, None, st()), "act_quant")
+            lib.check(k.ds41_act_quant_mx_rows(lib.ptr(self.recv_x), C.c_longlong(H), lib.ptr(self.xq), C.c_longlong(H),
+                                               lib.ptr(self.xq_sf), cap, H, lib.ptr(self.total_rows), st()), "act_quant")
             self._grouped(self.w13, self.xq, self.act, I, H, lda=H, ldo=I, out_mode=4, up_row_offset=I,
                           sfa=self.w13_sf, sfa_batch_stride=self.w13_sf[0].numel(), sfb=self.xq_sf)
             self._mark("wait+quant+fc1")
-            lib.check(k.ds41_act_quant_mx(lib.ptr(self.act), C.c_longlong(I), C.c_longlong(0), lib.ptr(self.actq),
-                                          C.c_longlong(I), C.c_longlong(0), lib.ptr(self.actq_sf), C.c_longlong(0), cap,
-                                          I, 1, 128, None, st()), "act_quant")
+            lib.check(k.ds41_act_quant_mx_rows(lib.ptr(self.act), C.c_longlong(I), lib.ptr(self.actq), C.c_longlong(I),
+                                               lib.ptr(self.actq_sf), cap, I, lib.ptr(self.total_rows), st()), "act_quant")
             self._grouped(self.w2, self.actq, self.comb, H, I, lda=I, ldo=H, out_mode=7, table=1, sfa=self.w2_sf,
                           sfa_batch_stride=self.w2_sf[0].numel(), sfb=self.actq_sf)
             self._mark("quant+fc2")

@@ -43,7 +43,7 @@ def main():
     x = torch.randn(n, n, device=dev).bfloat16()
     w = torch.randn(n, n, device=dev).bfloat16()
     y = torch.empty(n, n, device=dev, dtype=torch.bfloat16)
-    big = lambda: G.gemm_raw(x, w, y, n, n, n, lda=n, ldb=n, ldo=n, out_mode=0, bn=256, status=st, static_operand=2)
+    big = lambda: G.gemm_raw(x, w, y, n, n, n, lda=n, ldb=n, ldo=n, out_mode=6, bn=256, status=st, static_operand=2)
     # ---- bandwidth bound (decode head shard)
     rows, V, H = 8, 16160, 5120
     xs = torch.randn(rows, H, device=dev).bfloat16()
