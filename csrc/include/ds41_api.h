@@ -230,6 +230,22 @@ int ds41_ep_wait(const ds41_ep_args* a, int phase, void* stream);
 int ds41_ep_combine(const ds41_ep_args* a, const void* comb, const float* extra, long long extra_ld, void* out,
                     int as_bf16, void* stream);
 
+// ---------------------------------------------------------------------------------------------------
+// Token sampler (sampler_rows.cu): one 64-byte parameter block per row.  Status per row: 0 ok, 1 no candidate,
+// 2 non-finite logit, 3 bad temperature, 5 internal, 6 bad parameter (same codes as ds41_sample_token on the host).
+typedef struct {
+  float temperature;
+  int top_k;                    // <= 0: off
+  float top_p;                  // >= 1: off
+  float min_p;                  // <= 0: off
+  unsigned long long seed;
+  unsigned long long position;  // absolute index of the emitted token
+  int mask_row;                 // row of the packed allow-mask arena, < 0: no mask
+  int reserved[7];
+} ds41_sample_row;
+int ds41_sample_rows(const float* logits, long long ld, int rows, int vocab, const uint32_t* masks, int mask_words,
+                     const ds41_sample_row* params, int* tokens, int* status, void* stream);
+
 // Prefill-sized activation quantiser (1x128 scales, one warp per row); rows >= *rows_dev (if given) are skipped.
 int ds41_act_quant_mx_rows(const void* x, long long ldx, void* q, long long ldq, void* sf, int rows, int K,
                            const int* rows_dev, void* stream);

@@ -65,6 +65,13 @@ class EpArgs(C.Structure):
     ]
 
 
+class SampleRow(C.Structure):
+    _fields_ = [
+        ("temperature", C.c_float), ("top_k", C.c_int), ("top_p", C.c_float), ("min_p", C.c_float),
+        ("seed", C.c_ulonglong), ("position", C.c_ulonglong), ("mask_row", C.c_int), ("reserved", C.c_int * 7),
+    ]
+
+
 def _load(name: str, builder: str):
     path = _LIBDIR / name
     if not path.exists() or os.environ.get("DS41_REBUILD"):
@@ -97,7 +104,7 @@ def dir_functions():
         "ds41_moe_plan", "ds41_moe_combine", "ds41_signal", "ds41_reduce_planes", "ds41_argmax_rows",
         "ds41_argmax_merge", "ds41_spec_accept", "ds41_act_quant_mx", "ds41_decode_feedback", "ds41_hc_step", "ds41_taps_pack", "ds41_norm_rows", "ds41_markov_step", "ds41_spec_feedback",
         "ds41_copy_ints", "ds41_rs_reduce", "ds41_ep_count", "ds41_ep_plan", "ds41_ep_dispatch", "ds41_ep_mark",
-        "ds41_ep_wait", "ds41_ep_combine", "ds41_act_quant_mx_rows",
+        "ds41_ep_wait", "ds41_ep_combine", "ds41_act_quant_mx_rows", "ds41_sample_rows",
     ]
 
 
