@@ -1,0 +1,112 @@
+"""Command line: `python -m ds41rt_b200 <command>`.
+
+  build                      compile the kernel and host-runtime libraries in-tree
+  serve  [--model ...]       OpenAI-compatible HTTP server over the native engine on this GPU
+  info                       print the model configuration and the per-rank memory plan
+
+The reference's counterparts are its run.sh / build.sh launchers and the `v41-native-serve` daemon command
+(rust/crates/ds41rt-daemon/src/v41_native_serve.rs, rust/crates/ds41rt-daemon/src/cli.rs).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+
+
+def _config(args):
+    from .config import ModelConfig
+    if args.config:
+        with open(args.config) as f:
+            return ModelConfig.from_official_json(json.load(f))
+    if args.model == "flash":
+        return ModelConfig.flash(args.layers or 4)
+    return ModelConfig.small() if args.model == "small" else ModelConfig.tiny()
+
+
+def cmd_build(args) -> int:
+    from . import build
+    build.build_kernels()
+    build.build_core()
+    print("built", flush=True)
+    return 0
+
+
+def cmd_info(args) -> int:
+    from .loader.catalog import expected_tensors
+    cfg = _config(args)
+    n = len(expected_tensors(cfg)) if args.model == "flash" and not args.layers else None
+    expert = 3 * cfg.hidden * cfg.inter
+    print(json.dumps({"model": cfg.name, "layers": cfg.n_layers, "hidden": cfg.hidden, "experts": cfg.n_experts,
+                      "topk": cfg.topk, "vocab": cfg.vocab, "checkpoint_tensors": n,
+                      "expert_bytes_fp8": expert, "experts_gb_per_layer_fp8": round(expert * cfg.n_experts / 2 ** 30, 2)}))
+    return 0
+
+
+def cmd_serve(args) -> int:
+    import torch
+    from .models.ds41 import DS41Engine, EngineWeights
+    from .serving.engine import NativeBackend
+    from .serving.http import ApiServer
+    from .serving.tokenizer import ByteTokenizer, HFTokenizer
+    if not torch.cuda.is_available():
+        print("serve needs a CUDA device", file=sys.stderr)
+        return 2
+    cfg = _config(args)
+    dev = torch.device("cuda", args.device)
+    tk = HFTokenizer(args.tokenizer) if args.tokenizer else ByteTokenizer(vocab_size=cfg.vocab)
+    t0 = time.time()
+    if args.checkpoint:
+        from .loader.official import load_engine_weights
+        weights = load_engine_weights(args.checkpoint, cfg, 0, 1, dev)
+    else:
+        weights = EngineWeights.random(cfg, 0, 1, dev, seed=args.seed, expert_dtype=args.expert_dtype)
+    eng = DS41Engine(cfg, weights, max_rows=max(8, args.concurrency), slots=args.concurrency, max_ctx=args.max_context)
+    backend = NativeBackend(eng, eos=tk.eos, concurrency=args.concurrency, queue_depth=args.queue_depth)
+    srv = ApiServer(backend, tk, host=args.host, port=args.port, queue_depth=args.queue_depth, waiters=args.waiters,
+                    max_context=args.max_context).start()
+    print(json.dumps({"listening": f"http://{args.host}:{srv.port}", "model": cfg.name,
+                      "setup_s": round(time.time() - t0, 1)}), flush=True)
+    try:
+        while True:
+            time.sleep(3600)
+    except KeyboardInterrupt:
+        pass
+    finally:
+        srv.stop()
+        backend.close()
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="ds41rt_b200")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+
+    def model_args(p):
+        p.add_argument("--model", default="tiny", choices=["tiny", "small", "flash"])
+        p.add_argument("--layers", type=int, default=0, help="flash: number of layers to instantiate")
+        p.add_argument("--config", default="", help="official config.json (overrides --model)")
+
+    sub.add_parser("build")
+    pi = sub.add_parser("info")
+    model_args(pi)
+    ps = sub.add_parser("serve")
+    model_args(ps)
+    ps.add_argument("--checkpoint", default="", help="directory with model.safetensors.index.json (official layout)")
+    ps.add_argument("--tokenizer", default="", help="tokenizer.json; default: byte-level tokenizer")
+    ps.add_argument("--expert-dtype", default="mxfp8", choices=["mxfp8", "bf16"])
+    ps.add_argument("--host", default="127.0.0.1")
+    ps.add_argument("--port", type=int, default=8000)
+    ps.add_argument("--device", type=int, default=0)
+    ps.add_argument("--concurrency", type=int, default=4)
+    ps.add_argument("--queue-depth", type=int, default=16)
+    ps.add_argument("--waiters", type=int, default=16)
+    ps.add_argument("--max-context", type=int, default=8192)
+    ps.add_argument("--seed", type=int, default=0)
+    args = ap.parse_args(argv)
+    return {"build": cmd_build, "info": cmd_info, "serve": cmd_serve}[args.cmd](args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

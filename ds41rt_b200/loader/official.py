@@ -99,3 +99,38 @@ def load_official(cat: Catalog, rank: Optional[int] = None, world: int = 1) -> D
         else:
             out[name] = raw.float()
     return out
+
+
+class LazyOfficialWeights:
+    """Mapping view of a validated checkpoint: a tensor is read and dequantised to fp32 when it is indexed, so a
+    consumer that walks the model layer by layer never holds more than the tensors it is converting."""
+
+    def __init__(self, cat: Catalog):
+        self.cat = cat
+
+    def __contains__(self, name: str) -> bool:
+        return name in self.cat.expected
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        cat = self.cat
+        dt, _ = cat.expected[name]
+        base, _, leaf = name.rpartition(".")
+        raw = cat.read(name)
+        if dt == "F8_E4M3" and leaf == "weight":
+            e = cat.read(base + ".scale")
+            return Q.dequant_mxfp8(raw, e, 32) if ".engram.embed" in name else Q.dequant_weight_mxfp8_32x32(raw, e)
+        if dt == "I8":
+            return Q.dequant_mxfp4(raw.view(torch.uint8), cat.read(base + ".scale"), 32)
+        if dt == "U8" and leaf == "weight":
+            return Q.dequant_nvfp4(raw, cat.read(base + ".weight_scale"), cat.read(base + ".weight_scale_2").float())
+        return raw.float()
+
+
+def load_engine_weights(directory: str, cfg: ModelConfig, rank: int, world: int, device, variant: str = "mxfp4",
+                        expert_dtype: str = "mxfp8", with_vision: bool = False, with_engram: bool = False):
+    """Validate the checkpoint under `directory` against the catalog and stream it into one rank's `EngineWeights`
+    (reference: rust/crates/ds41rt-loader/src/v41_catalog.rs:478-637 for validation and range reads,
+    v41_expert_staging for the per-rank expert plan)."""
+    from ..models.ds41 import EngineWeights
+    cat = Catalog(directory, cfg, variant, with_vision=with_vision, with_engram=with_engram)
+    return EngineWeights.from_fp32(cfg, LazyOfficialWeights(cat), rank, world, device, expert_dtype=expert_dtype)

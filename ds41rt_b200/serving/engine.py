@@ -134,7 +134,7 @@ class NativeBackend(Backend):
         self.active: List[_Active] = []
         self.pending: Optional[GenRequest] = None
         self.totals = {"requests": 0, "prompt_tokens": 0, "completion_tokens": 0, "device_greedy_rows": 0,
-                       "cpu_sampled_rows": 0, "rounds": 0, "failed": 0}
+                       "cpu_sampled_rows": 0, "gpu_sampled_rows": 0, "rounds": 0, "failed": 0}
         self._rid = 0
         self._stop = threading.Event()
         self._ready = threading.Event()
@@ -157,7 +157,8 @@ class NativeBackend(Backend):
                 "kv": {"pages_free": pages_free, "pages_total": self.kv.n_pages},
                 "lanes": [self.lanes.load(0), self.lanes.load(1)],
                 "target_sampling": {"device_rounds_rows": self.totals["device_greedy_rows"],
-                                    "cpu_fallback_rows": self.totals["cpu_sampled_rows"]}}
+                                    "cpu_fallback_rows": self.totals["cpu_sampled_rows"],
+                                    "gpu_sampled_rows": self.totals["gpu_sampled_rows"]}}
 
     def close(self) -> None:
         self._stop.set()
@@ -274,15 +275,35 @@ class NativeBackend(Backend):
             chosen = e.chosen.tolist()
             self.totals["device_greedy_rows"] += len(reqs)
             return [chosen[i] for i in rows]
-        logits = e.logits_rows(max(rows) + 1).float().cpu().numpy()
-        for r, i in zip(reqs, rows):
-            mask = r.constraint.mask() if r.constraint is not None else None
+        # sampled or grammar-constrained rows: the GPU sampler reads the logits where they are; only the packed
+        # allow-masks (vocab/8 bytes per constrained row) go up and one token id per row comes back
+        import numpy as np
+        from ..ops.sampling import RowParams, pack_params, sample_rows
+        logits = e.logits_rows(max(rows) + 1)
+        if logits.dtype != torch.float32:
+            logits = logits.float()
+        picked = logits[torch.tensor(rows, device=logits.device)] if rows != list(range(len(rows))) else logits[:len(rows)]
+        params, masks = [], []
+        for r in reqs:
             s = r.sampling
-            position = len(r.prompt_ids)  # refined by the caller through r._emitted
-            u = K.sample_uniform(s.seed, getattr(r, "_emitted", 0))
-            tok = K.sample_token(logits[i], mask, s.temperature, s.top_k, s.top_p, s.min_p, u)
+            mask_row = -1
+            m = r.constraint.mask() if r.constraint is not None else None
+            if m is not None:
+                mask_row = len(masks)
+                masks.append(np.ascontiguousarray(m, dtype=np.uint32))
+            params.append(RowParams(temperature=0.0 if s.greedy else s.temperature, top_k=s.top_k, top_p=s.top_p,
+                                    min_p=s.min_p, seed=s.seed, position=getattr(r, "_emitted", 0), mask_row=mask_row))
+        arena = None
+        if masks:
+            arena = torch.from_numpy(np.stack(masks).view(np.int32)).to(logits.device)
+        toks, status = sample_rows(picked.contiguous(), pack_params(params, logits.device), arena)
+        toks, status = toks.tolist(), status.tolist()
+        for r, tok, st in zip(reqs, toks, status):
+            if st != 0:
+                # the oracle names the failure (no candidate under the mask, non-finite logits, bad parameters)
+                raise K.SamplingError(K.SAMPLE_STATUS.get(st, str(st)))
             out.append(tok)
-            self.totals["cpu_sampled_rows"] += 1
+            self.totals["gpu_sampled_rows"] += 1
         e.check_status("serving pass")
         return out
 

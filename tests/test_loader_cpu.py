@@ -129,3 +129,20 @@ def test_nvfp4_variant_catalog(tmp_path):
     assert float((got["layers.0.ffn.experts.0.w2.weight"] - ref).abs().max()) < 0.2 * float(ref.abs().max())
     with pytest.raises(SafetensorsError):
         Catalog(d, cfg, variant="mxfp4", with_vision=False, with_engram=False)
+
+
+def test_lazy_weights_match_eager_load(tmp_path):
+    """The streaming view used to fill engine shards returns exactly what the eager loader returns."""
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.loader.official import LazyOfficialWeights
+    from ds41rt_b200.models.weights import init_weights
+    cfg = ModelConfig.tiny()
+    w = init_weights(cfg, seed=3)
+    d = str(tmp_path / "ckpt")
+    export_official(cfg, w, d, shards=2)
+    cat = Catalog(d, cfg, with_vision=False, with_engram=False)
+    eager = load_official(cat)
+    lazy = LazyOfficialWeights(cat)
+    for name in ("embed.weight", "layers.0.attn.wq_a.weight", "layers.1.ffn.experts.3.w1.weight", "layers.0.hc_attn_fn"):
+        assert name in lazy
+        assert torch.equal(lazy[name], eager[name])
