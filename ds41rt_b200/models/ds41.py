@@ -348,7 +348,7 @@ class KVCache:
 class DS41Engine:
     def __init__(self, cfg: ModelConfig, weights: EngineWeights, fabric: Optional[Fabric] = None, *,
                  max_rows: int = 8, slots: int = 1, max_ctx: int = 4096, page_tokens: int = 64,
-                 n_pages: Optional[int] = None, row_hi: bool = False):
+                 n_pages: Optional[int] = None, row_hi: bool = False, moe_rows: int = 32):
         self.cfg, self.w = cfg, weights
         self.fabric = fabric or Fabric.single(weights.device)
         self.rank, self.world = self.fabric.rank, self.fabric.world
@@ -357,12 +357,18 @@ class DS41Engine:
         self.n_layers = len(weights.layers)
         H, D, Q = cfg.hidden, cfg.head_dim, cfg.q_lora
         self.k = lib.kernels()
-        self.cache = KVCache(cfg, self.n_layers, slots, max_ctx, dev, page_tokens, n_pages)
+        # the window ring holds one pass of new rows beyond the window: a row still needs the key at pos - window + 1
+        # after the last row of its pass has been written
+        self.cache = KVCache(cfg, self.n_layers, slots, max_ctx, dev, page_tokens, n_pages, spec_slack=max(16, R))
         self.HL, self.GL, self.I_sh, self.V_local = weights.HL, weights.GL, weights.I_sh, weights.V_local
         E = weights.layers[0].n_experts if weights.layers else cfg.n_experts
         self.E, self.topk = E, (weights.layers[0].topk if weights.layers else cfg.topk)
         self.EL = E // self.world
-        self.max_active = min(R * self.topk, self.EL)
+        # passes of at most moe_rows rows run every active expert over all rows (decode); longer passes sort the rows
+        # by expert and go through the expert-parallel tile-table path (prefill)
+        self.moe_rows = Rm = min(R, moe_rows)
+        self.max_active = min(Rm * self.topk, self.EL)
+        self._ep = None
         z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=dev)
         # inputs
         self.in_tokens = z((R,), I32)
@@ -409,18 +415,18 @@ class DS41Engine:
         self.shared_act = z((R, self.I_sh), BF16)
         self.active = z((self.max_active,), I32)
         self.n_active = z((1,), I32)
-        self.row_w = z((self.max_active, R), F32)
+        self.row_w = z((self.max_active, Rm), F32)
         self.slot_of = z((R, self.topk), I32)
-        self.act = z((self.max_active, R, cfg.inter), BF16)
+        self.act = z((self.max_active, Rm, cfg.inter), BF16)
         self.mx = weights.expert_dtype == "mxfp8"
         if self.mx:
             assert H % 128 == 0 and cfg.inter % 128 == 0
-            ra = (R + 127) // 128
+            ra = (Rm + 127) // 128
             self.xq = z((R, H), torch.uint8)
-            self.xq_sf = z((ra, H // 128, 512), torch.uint8)
-            self.actq = z((self.max_active, R, cfg.inter), torch.uint8)
+            self.xq_sf = z(((R + 127) // 128, H // 128, 512), torch.uint8)
+            self.actq = z((self.max_active, Rm, cfg.inter), torch.uint8)
             self.actq_sf = z((self.max_active, ra, cfg.inter // 128, 512), torch.uint8)
-        self.fc2 = z((self.max_active, R, H), F32)
+        self.fc2 = z((self.max_active, Rm, H), F32)
         self.planes_shared = z((self.max_splits, R, H), F32)
         # head
         self.logits = z((R, self.V_local), F32)
@@ -452,6 +458,8 @@ class DS41Engine:
         self.layer_prefix_plain = False   # drafter blocks use the plain rope
         self.launches = 0
         self.only = None
+        if R > self.moe_rows and weights.layers:
+            self._make_ep(weights.layers[0])
         self.debug = None   # set to a list to record per-layer routing / selection decisions
 
     # ------------------------------------------------------------------ helpers
@@ -627,51 +635,80 @@ class DS41Engine:
             if self.debug is not None:
                 self.debug.append({"layer": l, "ids": self.ids[:R].clone(), "sel": self.sel[:R].clone(),
                                    "n_sel": self.n_sel[:R].clone()})
-            EL = lw.n_experts // self.world
-            self._run("moe_plan", k.ds41_moe_plan, 
-                lib.ptr(self.ids), lib.ptr(self.route_w), lib.ptr(self.row_slot), R, lw.topk, self.rank * EL,
-                (self.rank + 1) * EL, self.max_active, self.max_rows, lib.ptr(self.active), lib.ptr(self.n_active),
-                lib.ptr(self.row_w), lib.ptr(self.slot_of), st())
-            I = cfg.inter
-            bn = G.pick_bn(R)
-            # FC1: act[slot][row][i] = swiglu(W1 x, W3 x) * route weight;  FC2: fc2[slot][row][h]
-            if self.mx:
-                ra = (R + 127) // 128
-                self._run("gemm_fc1", G.gemm_raw, lw.w13, self.xq, self.act, I, R, H, lda=H, ldb=H, ldo=I, kind=2, out_mode=4, bn=bn,
-                           batch=self.max_active, a_batches=EL, a_batch_stride=2 * I * H, out_batch_stride=R * I,
-                           batch_map=self.active, n_active=self.n_active, b_batch_kind=1, up_row_offset=I,
-                           row_w=self.row_w, row_w_ld=self.max_rows, act_limit=cfg.swiglu_limit,
-                           sfa=lw.w13_sf, sfa_batch_stride=lw.w13_sf[0].numel(), sfb=self.xq_sf, status=self.status)
-                sf_slot = ra * (I // 128) * 512
-                self._run("act_quant act", k.ds41_act_quant_mx, lib.ptr(self.act), C.c_longlong(I), C.c_longlong(R * I),
-                                             lib.ptr(self.actq), C.c_longlong(I), C.c_longlong(R * I),
-                                             lib.ptr(self.actq_sf), C.c_longlong(sf_slot), R, I, self.max_active, 128,
-                                             lib.ptr(self.n_active), st())
-                self._run("gemm_fc2", G.gemm_raw, lw.w2, self.actq, self.fc2, H, R, I, lda=I, ldb=I, ldo=H, kind=2, out_mode=5, bn=bn,
-                           batch=self.max_active, a_batches=EL, a_batch_stride=H * I, b_batch_stride=R * I,
-                           out_batch_stride=R * H, batch_map=self.active, n_active=self.n_active, b_batch_kind=2,
-                           row_w=self.row_w, row_w_ld=self.max_rows, sfa=lw.w2_sf,
-                           sfa_batch_stride=lw.w2_sf[0].numel(), sfb=self.actq_sf, sfb_batch_stride=sf_slot,
-                           status=self.status)
+            if R > self.moe_rows:
+                self._moe_sorted(R, lw)
             else:
-                self._run("gemm_fc1", G.gemm_raw, lw.w13, self.xn, self.act, I, R, H, lda=H, ldb=H, ldo=I, out_mode=4, bn=bn,
-                           batch=self.max_active, a_batches=EL, a_batch_stride=2 * I * H, out_batch_stride=R * I,
-                           batch_map=self.active, n_active=self.n_active, b_batch_kind=1, up_row_offset=I,
-                           row_w=self.row_w, row_w_ld=self.max_rows, act_limit=cfg.swiglu_limit, status=self.status)
-                self._run("gemm_fc2", G.gemm_raw, lw.w2, self.act, self.fc2, H, R, I, lda=I, ldb=I, ldo=H, out_mode=5, bn=bn,
-                           batch=self.max_active, a_batches=EL, a_batch_stride=H * I, b_batch_stride=R * I,
-                           out_batch_stride=R * H, batch_map=self.active, n_active=self.n_active, b_batch_kind=2,
-                           row_w=self.row_w, row_w_ld=self.max_rows, status=self.status)
-            s_s = G.pick_splits(H, self.I_sh, max_splits=self.max_splits)
-            self._run("gemm_shared_down", G.linear_planes, self.shared_act[:R], lw.w2_sh,
-                            self.planes_shared.view(-1)[: s_s * R * H].view(s_s, R, H), s_s, status=self.status)
-            self._run("moe_combine", k.ds41_moe_combine, lib.ptr(self.fc2), lib.ptr(self.slot_of), lib.ptr(self.planes_shared), s_s,
-                                        R, lw.topk, H, lib.ptr(self.moe_plane), st())
+                EL = lw.n_experts // self.world
+                self._run("moe_plan", k.ds41_moe_plan, 
+                    lib.ptr(self.ids), lib.ptr(self.route_w), lib.ptr(self.row_slot), R, lw.topk, self.rank * EL,
+                    (self.rank + 1) * EL, self.max_active, self.moe_rows, lib.ptr(self.active), lib.ptr(self.n_active),
+                    lib.ptr(self.row_w), lib.ptr(self.slot_of), st())
+                I = cfg.inter
+                bn = G.pick_bn(R)
+                # FC1: act[slot][row][i] = swiglu(W1 x, W3 x) * route weight;  FC2: fc2[slot][row][h]
+                if self.mx:
+                    ra = (R + 127) // 128
+                    self._run("gemm_fc1", G.gemm_raw, lw.w13, self.xq, self.act, I, R, H, lda=H, ldb=H, ldo=I, kind=2, out_mode=4, bn=bn,
+                               batch=self.max_active, a_batches=EL, a_batch_stride=2 * I * H, out_batch_stride=R * I,
+                               batch_map=self.active, n_active=self.n_active, b_batch_kind=1, up_row_offset=I,
+                               row_w=self.row_w, row_w_ld=self.moe_rows, act_limit=cfg.swiglu_limit,
+                               sfa=lw.w13_sf, sfa_batch_stride=lw.w13_sf[0].numel(), sfb=self.xq_sf, status=self.status)
+                    sf_slot = ra * (I // 128) * 512
+                    self._run("act_quant act", k.ds41_act_quant_mx, lib.ptr(self.act), C.c_longlong(I), C.c_longlong(R * I),
+                                                 lib.ptr(self.actq), C.c_longlong(I), C.c_longlong(R * I),
+                                                 lib.ptr(self.actq_sf), C.c_longlong(sf_slot), R, I, self.max_active, 128,
+                                                 lib.ptr(self.n_active), st())
+                    self._run("gemm_fc2", G.gemm_raw, lw.w2, self.actq, self.fc2, H, R, I, lda=I, ldb=I, ldo=H, kind=2, out_mode=5, bn=bn,
+                               batch=self.max_active, a_batches=EL, a_batch_stride=H * I, b_batch_stride=R * I,
+                               out_batch_stride=R * H, batch_map=self.active, n_active=self.n_active, b_batch_kind=2,
+                               row_w=self.row_w, row_w_ld=self.moe_rows, sfa=lw.w2_sf,
+                               sfa_batch_stride=lw.w2_sf[0].numel(), sfb=self.actq_sf, sfb_batch_stride=sf_slot,
+                               status=self.status)
+                else:
+                    self._run("gemm_fc1", G.gemm_raw, lw.w13, self.xn, self.act, I, R, H, lda=H, ldb=H, ldo=I, out_mode=4, bn=bn,
+                               batch=self.max_active, a_batches=EL, a_batch_stride=2 * I * H, out_batch_stride=R * I,
+                               batch_map=self.active, n_active=self.n_active, b_batch_kind=1, up_row_offset=I,
+                               row_w=self.row_w, row_w_ld=self.moe_rows, act_limit=cfg.swiglu_limit, status=self.status)
+                    self._run("gemm_fc2", G.gemm_raw, lw.w2, self.act, self.fc2, H, R, I, lda=I, ldb=I, ldo=H, out_mode=5, bn=bn,
+                               batch=self.max_active, a_batches=EL, a_batch_stride=H * I, b_batch_stride=R * I,
+                               out_batch_stride=R * H, batch_map=self.active, n_active=self.n_active, b_batch_kind=2,
+                               row_w=self.row_w, row_w_ld=self.moe_rows, status=self.status)
+                s_s = G.pick_splits(H, self.I_sh, max_splits=self.max_splits)
+                self._run("gemm_shared_down", G.linear_planes, self.shared_act[:R], lw.w2_sh,
+                                self.planes_shared.view(-1)[: s_s * R * H].view(s_s, R, H), s_s, status=self.status)
+                self._run("moe_combine", k.ds41_moe_combine, lib.ptr(self.fc2), lib.ptr(self.slot_of), lib.ptr(self.planes_shared), s_s,
+                                            R, lw.topk, H, lib.ptr(self.moe_plane), st())
             self._signal()
             pending = (self._moe_bases, self.world, 1, 0)
         self._pending = pending
         if head:
             self.head_rows(R)
+
+    def _make_ep(self, lw: LayerWeights):
+        from ..parallel.ep import ExpertParallelMoE
+        per_rank = (self.max_rows + self.world - 1) // self.world
+        self._ep = ExpertParallelMoE(self.fabric, lw.w13, lw.w2, topk=lw.topk, max_tokens=per_rank,
+                                     act_limit=self.cfg.swiglu_limit, w13_sf=getattr(lw, "w13_sf", None),
+                                     w2_sf=getattr(lw, "w2_sf", None))
+
+    def _moe_sorted(self, R: int, lw: LayerWeights):
+        """Routed + shared experts of a long pass: this rank's slice of the rows is dispatched to the experts' owners,
+        multiplied as expert groups and combined back (parallel/ep.py); the plane every rank publishes holds its
+        partial shared expert for all rows plus the complete routed sum of its own slice."""
+        cfg, k, st, H = self.cfg, self.k, lib.stream, self.cfg.hidden
+        s_s = G.pick_splits(H, self.I_sh, max_splits=self.max_splits)
+        self._run("gemm_shared_down", G.linear_planes, self.shared_act[:R], lw.w2_sh,
+                  self.planes_shared.view(-1)[: s_s * R * H].view(s_s, R, H), s_s, status=self.status)
+        self._run("reduce_planes", k.ds41_reduce_planes, lib.ptr(self.planes_shared), s_s, C.c_longlong(R * H),
+                  lib.ptr(self.moe_plane), 0, C.c_longlong(R * H), st())
+        if self._ep is None:
+            self._make_ep(lw)
+        lo, hi = R * self.rank // self.world, R * (self.rank + 1) // self.world
+        ep = self._ep
+        ep.set_weights(lw.w13, lw.w2, getattr(lw, "w13_sf", None), getattr(lw, "w2_sf", None))
+        if self.only is None or "ep_moe" in self.only:
+            self.launches += 8
+            ep.forward(self.xn[lo:hi], self.ids[lo:hi], self.route_w[lo:hi], self.moe_plane[lo:hi], self.moe_plane[lo:hi])
 
     def head_rows(self, rows: int, mask: Optional[torch.Tensor] = None):
         """collapse -> final norm -> vocabulary shard GEMM -> greedy candidate (+ cross-rank merge)."""

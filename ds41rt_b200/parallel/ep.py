@@ -87,6 +87,11 @@ class ExpertParallelMoE:
         self.dispatch_blocks = 4 * 148
         self.marks = None          # list of (name, event) while phase timing is on
 
+    def set_weights(self, w13, w2, w13_sf=None, w2_sf=None) -> None:
+        """Point the layer at another expert stack of the same shape and kind (one instance serves every MoE layer)."""
+        assert w13.shape == self.w13.shape and w2.shape == self.w2.shape and (w13_sf is not None) == self.mx
+        self.w13, self.w2, self.w13_sf, self.w2_sf = w13, w2, w13_sf, w2_sf
+
     # ------------------------------------------------------------------ argument blocks
     def _ep_args(self, x, ids, weights, tokens) -> lib.EpArgs:
         f, a = self.f, lib.EpArgs()
