@@ -107,6 +107,78 @@ def timed(fabric, torch, fn):
     return fabric.all_reduce_max(ev0.elapsed_time(ev1))
 
 
+BASELINE_PREFILL = 8355.0     # reference README.md:36 (best prefill, 2 RTX PRO 6000, v6 campaign)
+
+
+def prefill_bench(args, fabric, cfg, n_layers):
+    """Prompt throughput: the whole prompt goes through DS41Engine.prefill in passes of --chunk rows (sorted expert
+    path, sparse attention over the window and the selected compressed keys); a step is one whole prompt."""
+    import torch
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    world, rank, dev = fabric.world, fabric.rank, fabric.device
+    W, K = max(args.warmup, 3), args.steps
+    t0 = time.time()
+    weights = EngineWeights.random(cfg, rank, world, dev, seed=0, expert_dtype=args.expert_dtype)
+    P = args.prompt
+    eng = DS41Engine(cfg, weights, fabric, max_rows=args.chunk, slots=1, max_ctx=(P + 127) // 64 * 64)
+    g = torch.Generator().manual_seed(1234)
+    prompt = torch.randint(3, cfg.vocab - 600, (P,), generator=g).tolist()
+    setup_s = time.time() - t0
+    l0 = eng.launches
+    for _ in range(W):
+        eng.prefill(0, prompt, chunk=args.chunk)
+    per_prompt = (eng.launches - l0) // W
+    eng.check_status("prefill warm-up")
+    sampler = ClockSampler(dev.index or 0)
+    if rank == 0:
+        sampler.start()
+    ms = timed(fabric, torch, lambda: [eng.prefill(0, prompt, chunk=args.chunk) for _ in range(K)])
+    clocks = sampler.stop() if rank == 0 else {}
+    eng.check_status("timed prefill")
+    if args.breakdown and rank == 0:
+        eng.timeline = []
+        eng.prefill(0, prompt, chunk=args.chunk)
+        torch.cuda.synchronize()
+        acc = {}
+        for tag, e0, e1 in eng.timeline:
+            acc[tag] = acc.get(tag, 0.0) + e0.elapsed_time(e1)
+        eng.timeline = None
+        total = sum(acc.values())
+        for tag, v in sorted(acc.items(), key=lambda kv: -kv[1]):
+            print(f"  {tag:24s} {v:9.3f} ms  {100 * v / total:5.1f}%", file=sys.stderr)
+    # end to end: the same public call, wall clock around it (token ids go up and the next token comes back per call)
+    fabric.barrier()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    for _ in range(K):
+        eng.prefill(0, prompt, chunk=args.chunk)
+    torch.cuda.synchronize()
+    e2e_s = fabric.all_reduce_max(time.perf_counter() - t1)
+    if rank == 0:
+        value = K * P / (ms / 1e3)
+        chunks = (P + args.chunk - 1) // args.chunk
+        line = {
+            "metric": "prefill tok/s (one prompt, chunked passes)", "value": round(value, 1), "unit": "tok/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 3), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": round(value / BASELINE_PREFILL, 3),
+            "dtype": "bf16 dense / fp8-e4m3 experts (fp32 accumulate)", "data": "synthetic",
+            "config": {"model": f"DeepSeek-V4.1-Flash-shaped ({cfg.name})", "layers": n_layers, "layers_full_model": 40,
+                       "global_batch": 1, "seq_len": P, "chunk_rows": args.chunk,
+                       "parallelism": f"tp{world}+ep{world}",
+                       "experts": "fp8 e4m3, 128x128 ue8m0 block scales, 1x128 activation scales"
+                       if args.expert_dtype == "mxfp8" else "bf16",
+                       "l2": "no flush: every pass streams more weight bytes than the 126 MB L2",
+                       "weights_gb_per_gpu": round(weights.nbytes() / 1e9, 2), "setup_s": round(setup_s, 1)},
+            "clocks": clocks,
+            "e2e": {"value": round(K * P / e2e_s, 1), "unit": "tok/s", "steps": K,
+                    "h2d_bytes_per_step": 12 * P, "d2h_bytes_per_step": 4 * chunks},
+            "gpu_launches": per_prompt * K, "impl": "ours",
+        }
+        print(json.dumps(line))
+    fabric.barrier()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -123,6 +195,10 @@ def main():
     ap.add_argument("--no-spec", action="store_true", help="plain greedy decoding, one token per step")
     ap.add_argument("--accept", type=int, default=3, help="drafts accepted per round in the fixed schedule")
     ap.add_argument("--draft-stages", type=int, default=1)
+    ap.add_argument("--mode", default="decode", choices=["decode", "prefill"],
+                    help="prefill: time whole-prompt passes in --chunk-row chunks (tok/s of prompt tokens)")
+    ap.add_argument("--chunk", type=int, default=1024, help="rows per pass in --mode prefill")
+    ap.add_argument("--breakdown", action="store_true", help="prefill: per-kernel device time of one prompt (stderr)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -151,6 +227,8 @@ def main():
     else:
         cfg = getattr(ModelConfig, args.model)()
         n_layers = cfg.n_layers
+    if args.mode == "prefill":
+        return prefill_bench(args, fabric, cfg, n_layers)
     spec = not args.no_spec
     if spec:
         cfg.dspark = dataclasses.replace(cfg.dspark, stages=args.draft_stages)

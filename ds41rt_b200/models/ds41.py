@@ -458,6 +458,7 @@ class DS41Engine:
         self.layer_prefix_plain = False   # drafter blocks use the plain rope
         self.launches = 0
         self.only = None
+        self.timeline = None   # set to a list to record (tag, start event, end event) per launch of eager passes
         if R > self.moe_rows and weights.layers:
             self._make_ep(weights.layers[0])
         self.debug = None   # set to a list to record per-layer routing / selection decisions
@@ -468,12 +469,24 @@ class DS41Engine:
             return self.inv_plain
         return self.inv_long
 
+    def _splits(self, m: int, k: int, rows: int) -> int:
+        """Split-K factor of a swap-AB projection: fill one wave of CTAs, counting the row tiles of long passes."""
+        n_tiles = (rows + G.pick_bn(rows) - 1) // G.pick_bn(rows)
+        return G.pick_splits(m, k, max_splits=self.max_splits, n_tiles=n_tiles)
+
     def _run(self, tag, fn, *args, **kw):
         """Launch one kernel; `self.only` (a set of tags) restricts a pass to some kernels for profiling."""
         if self.only is not None and tag not in self.only:
             return
         self.launches += 1
-        err = fn(*args, **kw)
+        if self.timeline is not None:           # eager passes only: a CUDA event pair around every launch
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            err = fn(*args, **kw)
+            e1.record()
+            self.timeline.append((tag, e0, e1))
+        else:
+            err = fn(*args, **kw)
         if err is not None:
             lib.check(err, tag)
 
@@ -573,7 +586,7 @@ class DS41Engine:
                 tap_i += 1
             self._hc(R, pending, lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, lw.attn_norm, tap=tap)
             ntot = lw.w_qkv.shape[0]
-            s_qkv = G.pick_splits(ntot, H, max_splits=self.max_splits)
+            s_qkv = self._splits(ntot, H, R)
             self._run("gemm_qkv", G.linear_planes, self.xn[:R], lw.w_qkv, self.planes_qkv.view(-1)[: s_qkv * R * ntot].view(s_qkv, R, ntot),
                             s_qkv, status=self.status)
             self._run("qkv_post", k.ds41_qkv_post, 
@@ -617,7 +630,7 @@ class DS41Engine:
                        ldo=self.GL * cfg.o_lora, out_mode=2, batch=self.GL, a_batch_stride=cfg.o_lora * kg,
                        b_batch_stride=kg, out_batch_stride=cfg.o_lora, status=self.status, static_operand=1)
             ko = self.GL * cfg.o_lora
-            s_o = G.pick_splits(H, ko, max_splits=self.max_splits)
+            s_o = self._splits(H, ko, R)
             self._run("gemm_wo_b", G.linear_planes, self.oa[:R], lw.wo_b, self.planes_o.view(-1)[: s_o * R * H].view(s_o, R, H), s_o,
                             status=self.status)
             self._signal()
@@ -625,7 +638,7 @@ class DS41Engine:
             # ---------------- MoE sublayer
             self._hc(R, pending, lw.hc_ffn_fn, lw.hc_ffn_scale, lw.hc_ffn_base, lw.ffn_norm, quant=self.mx)
             ng = lw.w_gate_sh.shape[0]
-            s_g = G.pick_splits(ng, H, max_splits=self.max_splits)
+            s_g = self._splits(ng, H, R)
             self._run("gemm_gate", G.linear_planes, self.xn[:R], lw.w_gate_sh, self.planes_gate.view(-1)[: s_g * R * ng].view(s_g, R, ng),
                             s_g, status=self.status)
             self._run("router_select", k.ds41_router_select, 
@@ -673,7 +686,7 @@ class DS41Engine:
                                batch=self.max_active, a_batches=EL, a_batch_stride=H * I, b_batch_stride=R * I,
                                out_batch_stride=R * H, batch_map=self.active, n_active=self.n_active, b_batch_kind=2,
                                row_w=self.row_w, row_w_ld=self.moe_rows, status=self.status)
-                s_s = G.pick_splits(H, self.I_sh, max_splits=self.max_splits)
+                s_s = self._splits(H, self.I_sh, R)
                 self._run("gemm_shared_down", G.linear_planes, self.shared_act[:R], lw.w2_sh,
                                 self.planes_shared.view(-1)[: s_s * R * H].view(s_s, R, H), s_s, status=self.status)
                 self._run("moe_combine", k.ds41_moe_combine, lib.ptr(self.fc2), lib.ptr(self.slot_of), lib.ptr(self.planes_shared), s_s,
@@ -696,7 +709,7 @@ class DS41Engine:
         multiplied as expert groups and combined back (parallel/ep.py); the plane every rank publishes holds its
         partial shared expert for all rows plus the complete routed sum of its own slice."""
         cfg, k, st, H = self.cfg, self.k, lib.stream, self.cfg.hidden
-        s_s = G.pick_splits(H, self.I_sh, max_splits=self.max_splits)
+        s_s = self._splits(H, self.I_sh, R)
         self._run("gemm_shared_down", G.linear_planes, self.shared_act[:R], lw.w2_sh,
                   self.planes_shared.view(-1)[: s_s * R * H].view(s_s, R, H), s_s, status=self.status)
         self._run("reduce_planes", k.ds41_reduce_planes, lib.ptr(self.planes_shared), s_s, C.c_longlong(R * H),
@@ -707,8 +720,9 @@ class DS41Engine:
         ep = self._ep
         ep.set_weights(lw.w13, lw.w2, getattr(lw, "w13_sf", None), getattr(lw, "w2_sf", None))
         if self.only is None or "ep_moe" in self.only:
-            self.launches += 8
-            ep.forward(self.xn[lo:hi], self.ids[lo:hi], self.route_w[lo:hi], self.moe_plane[lo:hi], self.moe_plane[lo:hi])
+            self.launches += 7
+            self._run("ep_moe", ep.forward, self.xn[lo:hi], self.ids[lo:hi], self.route_w[lo:hi], self.moe_plane[lo:hi],
+                      self.moe_plane[lo:hi])
 
     def head_rows(self, rows: int, mask: Optional[torch.Tensor] = None):
         """collapse -> final norm -> vocabulary shard GEMM -> greedy candidate (+ cross-rank merge)."""
@@ -745,7 +759,7 @@ class DS41Engine:
         H, D, Q = cfg.hidden, cfg.head_dim, cfg.q_lora
         for l, lw in enumerate(self.w.layers):
             ntot = lw.w_qkv.shape[0]
-            s_qkv = G.pick_splits(ntot, H, max_splits=self.max_splits)
+            s_qkv = self._splits(ntot, H, rows)
             self._run("gemm_qkv_feed", G.linear_planes, self.xn[:rows], lw.w_qkv,
                       self.planes_qkv.view(-1)[: s_qkv * rows * ntot].view(s_qkv, rows, ntot), s_qkv,
                       status=self.status)

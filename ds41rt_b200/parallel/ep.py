@@ -153,7 +153,7 @@ class ExpertParallelMoE:
 
     # ------------------------------------------------------------------ the fused layer
     def forward(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, out: torch.Tensor,
-                extra: Optional[torch.Tensor] = None) -> torch.Tensor:
+                extra: Optional[torch.Tensor] = None) -> None:
         """x [T,H] bf16, ids [T,topk] int32 (global expert ids), weights [T,topk] fp32 -> out [T,H] (bf16 or fp32).
 
         `extra` ([T,H] fp32, e.g. the shared expert's output) is added before the routed rows, in a fixed order."""
@@ -191,7 +191,7 @@ class ExpertParallelMoE:
                                     C.c_longlong(extra.stride(0) if extra is not None else 0), lib.ptr(out),
                                     1 if out.dtype == torch.bfloat16 else 0, st()), "ep_combine")
         self._mark("mark+combine")
-        return out
+        return None
 
     def check(self):
         lib.raise_on_status(self.status, "expert-parallel layer")
