@@ -259,7 +259,9 @@ __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
 
-// grid (n_splits, rows, ceil(heads/16)), 128 threads: one CTA = 64 keys x 16 heads.
+// grid (n_splits, rows, ceil(heads/16)), 128 threads: one CTA = 16 heads x the 64-key tiles split, split + n_splits, ...
+// of one row, folded with a running softmax; n_splits = number of tiles gives one tile per CTA (decode), a small
+// n_splits keeps the partial outputs of long passes small (prefill).
 template <int D>
 __global__ void __launch_bounds__(128) attend_kernel(AttendParams p) {
   constexpr int LD = D + 8;                                // padded row (bf16 elements)
@@ -271,6 +273,9 @@ __global__ void __launch_bounds__(128) attend_kernel(AttendParams p) {
   float* sCos = reinterpret_cast<float*>(sP + kHeadsPerCta * 72);                    // [64]
   float* sSin = sCos + 64;
   const __nv_bfloat16** sPtr = reinterpret_cast<const __nv_bfloat16**>(sSin + 64);   // [64]
+  float* sM = reinterpret_cast<float*>(sPtr + 64);                                    // [16] running max
+  float* sL = sM + kHeadsPerCta;                                                      // [16] running sum
+  float* sScale = sL + kHeadsPerCta;                                                  // [16] rescale of this tile
 
   const int split = blockIdx.x, r = blockIdx.y, h_base = blockIdx.z * kHeadsPerCta;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -291,44 +296,21 @@ __global__ void __launch_bounds__(128) attend_kernel(AttendParams p) {
     n_s = (p.comp_pool != nullptr && p.n_sel != nullptr) ? p.n_sel[r] : 0;
   }
   const int n_keys = n_w + n_s;
-  const int k0 = split * kKeysPerCta;
-  const int k_cnt = max(0, min(kKeysPerCta, n_keys - k0));
-  if (k_cnt == 0) {
+  const int n_tiles = (n_keys + kKeysPerCta - 1) / kKeysPerCta;
+  if (split >= n_tiles) {
     if (tid < n_heads) {
       ml_out[2 * tid] = -INFINITY;
       ml_out[2 * tid + 1] = 0.f;
     }
     return;
   }
-  // ---- key pointers + rope table
-  if (tid < kKeysPerCta) {
-    const __nv_bfloat16* ptr = nullptr;
-    const int j = k0 + tid;
-    if (tid < k_cnt) {
-      if (j < n_w) {
-        const int kp = lo_pos + j;
-        ptr = p.win + (1ll * slot * p.ring + (kp % p.ring)) * D;
-      } else {
-        const int id = p.sel[1ll * r * p.k + (j - n_w)];
-        const long long phys = id < 0 ? -1 : pool_row(p.page_table, p.max_pages, p.page_rows, slot, id);
-        if (phys >= 0) ptr = p.comp_pool + phys * D;
-      }
-    }
-    sPtr[tid] = ptr;
-  } else if (tid - kKeysPerCta < p.rope_dim / 2) {
-    rope_cs2(pos, p.inv_freq[tid - kKeysPerCta], &sCos[tid - kKeysPerCta], &sSin[tid - kKeysPerCta]);
+  // ---- rope table and the Q tile with RoPE on the tail (zero rows for padding heads), once per CTA
+  if (tid < p.rope_dim / 2) rope_cs2(pos, p.inv_freq[tid], &sCos[tid], &sSin[tid]);
+  if (tid < kHeadsPerCta) {
+    sM[tid] = -INFINITY;
+    sL[tid] = 0.f;
   }
   __syncthreads();
-  // ---- K tile: asynchronous 16-byte copies straight into shared memory (zero-filled beyond k_cnt)
-#pragma unroll 8
-  for (int idx = tid; idx < kKeysPerCta * (D / 8); idx += 128) {
-    const int key = idx / (D / 8), ch = idx % (D / 8);
-    const __nv_bfloat16* src = sPtr[key];
-    __nv_bfloat16* dst = sK + key * LD + ch * 8;
-    if (src != nullptr) cp_async_16(dst, src + ch * 8);
-    else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-  }
-  // ---- Q tile with RoPE on the tail (zero rows for padding heads)
   const int rope0 = D - p.rope_dim;
 #pragma unroll 4
   for (int idx = tid; idx < kHeadsPerCta * (D / 8); idx += 128) {
@@ -348,81 +330,130 @@ __global__ void __launch_bounds__(128) attend_kernel(AttendParams p) {
     }
     *reinterpret_cast<uint4*>(sQ + h * LD + ch * 8) = raw;
   }
-  cp_async_wait_all();
-  __syncthreads();
-  // ---- S = Q K^T: warp w owns keys [16w, 16w+16)
-  {
-    float c[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    const __nv_bfloat16* qa = sQ + g * LD + 2 * t4;
-    const __nv_bfloat16* kb = sK + (warp * 16 + g) * LD + 2 * t4;
+  constexpr int NT = D / 32;
+  float acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[nt][j] = 0.f;
+  const int d_base = warp * (D / 4);
+
+  // ---- this CTA's key tiles: split, split + n_splits, ... with a running (max, sum, output) per head
+  for (int tile = split; tile < n_tiles; tile += p.n_splits) {
+    const int k0 = tile * kKeysPerCta;
+    const int k_cnt = min(kKeysPerCta, n_keys - k0);
+    if (tid < kKeysPerCta) {
+      const __nv_bfloat16* ptr = nullptr;
+      const int j = k0 + tid;
+      if (tid < k_cnt) {
+        if (j < n_w) {
+          const int kp = lo_pos + j;
+          ptr = p.win + (1ll * slot * p.ring + (kp % p.ring)) * D;
+        } else {
+          const int id = p.sel[1ll * r * p.k + (j - n_w)];
+          const long long phys = id < 0 ? -1 : pool_row(p.page_table, p.max_pages, p.page_rows, slot, id);
+          if (phys >= 0) ptr = p.comp_pool + phys * D;
+        }
+      }
+      sPtr[tid] = ptr;
+    }
+    __syncthreads();          // also: the previous tile's P.V reads of sK / sP are complete
+    // K tile: asynchronous 16-byte copies straight into shared memory (zero-filled beyond k_cnt)
 #pragma unroll 8
-    for (int kk = 0; kk < D; kk += 16) {
-      uint32_t a[4];
-      a[0] = *reinterpret_cast<const uint32_t*>(qa + kk);
-      a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + kk);
-      a[2] = *reinterpret_cast<const uint32_t*>(qa + kk + 8);
-      a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + kk + 8);
+    for (int idx = tid; idx < kKeysPerCta * (D / 8); idx += 128) {
+      const int key = idx / (D / 8), ch = idx % (D / 8);
+      const __nv_bfloat16* src = sPtr[key];
+      __nv_bfloat16* dst = sK + key * LD + ch * 8;
+      if (src != nullptr) cp_async_16(dst, src + ch * 8);
+      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    // S = Q K^T: warp w owns keys [16w, 16w+16)
+    {
+      float c[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      const __nv_bfloat16* qa = sQ + g * LD + 2 * t4;
+      const __nv_bfloat16* kb = sK + (warp * 16 + g) * LD + 2 * t4;
+#pragma unroll 8
+      for (int kk = 0; kk < D; kk += 16) {
+        uint32_t a[4];
+        a[0] = *reinterpret_cast<const uint32_t*>(qa + kk);
+        a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + kk);
+        a[2] = *reinterpret_cast<const uint32_t*>(qa + kk + 8);
+        a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + kk + 8);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb + nt * 8 * LD + kk);
+          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kb + nt * 8 * LD + kk + 8);
+          mma_bf16_16816(c[nt], a, b0, b1);
+        }
+      }
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb + nt * 8 * LD + kk);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kb + nt * 8 * LD + kk + 8);
-        mma_bf16_16816(c[nt], a, b0, b1);
+        const int key = warp * 16 + nt * 8 + 2 * t4;
+        float* s0 = sS + g * 65 + key;
+        float* s1 = sS + (g + 8) * 65 + key;
+        s0[0] = key < k_cnt ? c[nt][0] * p.scale : -INFINITY;
+        s0[1] = key + 1 < k_cnt ? c[nt][1] * p.scale : -INFINITY;
+        s1[0] = key < k_cnt ? c[nt][2] * p.scale : -INFINITY;
+        s1[1] = key + 1 < k_cnt ? c[nt][3] * p.scale : -INFINITY;
       }
     }
+    __syncthreads();
+    // per-head running softmax statistics; P in bf16 (4 head rows per warp)
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      const int key = warp * 16 + nt * 8 + 2 * t4;
-      float* s0 = sS + g * 65 + key;
-      float* s1 = sS + (g + 8) * 65 + key;
-      s0[0] = key < k_cnt ? c[nt][0] * p.scale : -INFINITY;
-      s0[1] = key + 1 < k_cnt ? c[nt][1] * p.scale : -INFINITY;
-      s1[0] = key < k_cnt ? c[nt][2] * p.scale : -INFINITY;
-      s1[1] = key + 1 < k_cnt ? c[nt][3] * p.scale : -INFINITY;
+    for (int i = 0; i < 4; ++i) {
+      const int row = warp * 4 + i;
+      const float v0 = sS[row * 65 + lane], v1 = sS[row * 65 + lane + 32];
+      const float m_old = sM[row];
+      const float m = fmaxf(m_old, warp_max(fmaxf(v0, v1)));
+      const float e0 = __expf(v0 - m), e1 = __expf(v1 - m);
+      const __nv_bfloat16 b0 = __float2bfloat16_rn(e0), b1 = __float2bfloat16_rn(e1);
+      const float l = warp_sum(__bfloat162float(b0) + __bfloat162float(b1));
+      sP[row * 72 + lane] = b0;
+      sP[row * 72 + lane + 32] = b1;
+      if (lane == 0) {
+        const float keep = m_old == -INFINITY ? 0.f : __expf(m_old - m);
+        sScale[row] = keep;
+        sL[row] = sL[row] * keep + l;
+        sM[row] = m;
+      }
     }
-  }
-  __syncthreads();
-  // ---- per-head softmax statistics over this CTA's keys; P in bf16 (4 head rows per warp)
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int row = warp * 4 + i;
-    const float v0 = sS[row * 65 + lane], v1 = sS[row * 65 + lane + 32];
-    const float m = warp_max(fmaxf(v0, v1));
-    const float e0 = __expf(v0 - m), e1 = __expf(v1 - m);
-    const __nv_bfloat16 b0 = __float2bfloat16_rn(e0), b1 = __float2bfloat16_rn(e1);
-    const float l = warp_sum(__bfloat162float(b0) + __bfloat162float(b1));
-    sP[row * 72 + lane] = b0;
-    sP[row * 72 + lane + 32] = b1;
-    if (lane == 0 && row < n_heads) {
-      ml_out[2 * row] = m;
-      ml_out[2 * row + 1] = l;
-    }
-  }
-  __syncthreads();
-  // ---- O = P V : warp w owns dims [w*D/4, (w+1)*D/4)
-  {
-    constexpr int NT = D / 32;
-    float acc[NT][4];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) acc[nt][j] = 0.f;
-    const int d_base = warp * (D / 4);
-#pragma unroll
-    for (int kk = 0; kk < kKeysPerCta; kk += 16) {
-      uint32_t a[4];
-      const __nv_bfloat16* pa = sP + g * 72 + kk + 2 * t4;
-      a[0] = *reinterpret_cast<const uint32_t*>(pa);
-      a[1] = *reinterpret_cast<const uint32_t*>(pa + 8 * 72);
-      a[2] = *reinterpret_cast<const uint32_t*>(pa + 8);
-      a[3] = *reinterpret_cast<const uint32_t*>(pa + 8 * 72 + 8);
-      const __nv_bfloat16* vrow = sK + (kk + (lane & 15)) * LD + d_base;
+    __syncthreads();
+    // O = O * keep + P V : warp w owns dims [w*D/4, (w+1)*D/4)
+    {
+      const float keep0 = sScale[g], keep1 = sScale[g + 8];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        uint32_t b0, b1;
-        ldmatrix_x2_trans(b0, b1, vrow + nt * 8);
-        mma_bf16_16816(acc[nt], a, b0, b1);
+        acc[nt][0] *= keep0;
+        acc[nt][1] *= keep0;
+        acc[nt][2] *= keep1;
+        acc[nt][3] *= keep1;
+      }
+#pragma unroll
+      for (int kk = 0; kk < kKeysPerCta; kk += 16) {
+        uint32_t a[4];
+        const __nv_bfloat16* pa = sP + g * 72 + kk + 2 * t4;
+        a[0] = *reinterpret_cast<const uint32_t*>(pa);
+        a[1] = *reinterpret_cast<const uint32_t*>(pa + 8 * 72);
+        a[2] = *reinterpret_cast<const uint32_t*>(pa + 8);
+        a[3] = *reinterpret_cast<const uint32_t*>(pa + 8 * 72 + 8);
+        const __nv_bfloat16* vrow = sK + (kk + (lane & 15)) * LD + d_base;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          uint32_t b0, b1;
+          ldmatrix_x2_trans(b0, b1, vrow + nt * 8);
+          mma_bf16_16816(acc[nt], a, b0, b1);
+        }
       }
     }
+  }
+  __syncthreads();
+  if (tid < n_heads) {
+    ml_out[2 * tid] = sM[tid];
+    ml_out[2 * tid + 1] = sL[tid];
+  }
+  {
     const int h0 = g, h1 = g + 8;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -501,7 +532,7 @@ template <int D>
 static cudaError_t launch_attend(const AttendParams& p, cudaStream_t stream) {
   constexpr int LD = D + 8;
   constexpr size_t smem = size_t(kKeysPerCta) * LD * 2 + size_t(kHeadsPerCta) * LD * 2 + size_t(kHeadsPerCta) * 65 * 4 +
-                          size_t(kHeadsPerCta) * 72 * 2 + 128 * 4 + 64 * 8 + 64;
+                          size_t(kHeadsPerCta) * 72 * 2 + 128 * 4 + 64 * 8 + 3 * kHeadsPerCta * 4 + 64;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);

@@ -403,8 +403,9 @@ class DS41Engine:
         self.sel = z((R, cfg.index_topk), I32)
         self.n_sel = z((R,), I32)
         self.n_splits_attn = (cfg.window + 16 + cfg.index_topk + 63) // 64
-        self.part_o = z((R, self.n_splits_attn, self.HL, D), F32)
-        self.part_ml = z((R, self.n_splits_attn, self.HL, 2), F32)
+        cells = max(r * self._attn_splits(r) for r in range(1, R + 1))      # (row, split) partial outputs
+        self.part_o = z((cells, self.HL, D), F32)
+        self.part_ml = z((cells, self.HL, 2), F32)
         self.attn_out = z((R, self.HL * D), BF16)
         self.oa = z((R, self.GL * cfg.o_lora), BF16)
         # MoE
@@ -468,6 +469,13 @@ class DS41Engine:
         if self.layer_prefix_plain or self.cfg.compress_ratios[layer] == 0:
             return self.inv_plain
         return self.inv_long
+
+    def _attn_splits(self, rows: int) -> int:
+        """Key-tile splits per (row, head group): one tile per CTA for a few rows (decode), fewer and longer CTAs once
+        the rows alone fill the GPU about three CTAs deep (prefill)."""
+        groups = (self.HL + 15) // 16
+        want = -(-3 * 148 // (rows * groups))
+        return max(1, min(self.n_splits_attn, want))
 
     def _splits(self, m: int, k: int, rows: int) -> int:
         """Split-K factor of a swap-AB projection: fill one wave of CTAs, counting the row tiles of long passes."""
@@ -622,7 +630,7 @@ class DS41Engine:
                 lib.ptr(self.cache.comp[src]) if src is not None else lib.ptr(None),
                 lib.ptr(self.sel), lib.ptr(self.n_sel), cfg.index_topk, lib.ptr(self.cache.page_table),
                 self.cache.max_pages, self.cache.page_rows[src] if src is not None else 1, lib.ptr(inv), cfg.rope_dim,
-                C.c_float(cfg.softmax_scale), self.n_splits_attn, lib.ptr(self.row_hi), lib.ptr(self.part_o),
+                C.c_float(cfg.softmax_scale), self._attn_splits(R), lib.ptr(self.row_hi), lib.ptr(self.part_o),
                 lib.ptr(self.part_ml), lib.ptr(lw.sink), lib.ptr(self.attn_out), C.c_longlong(self.HL * D), st())
             # grouped wo_a: batch = local groups
             kg = cfg.heads_per_group * D
