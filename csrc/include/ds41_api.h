@@ -72,6 +72,9 @@ typedef struct ds41_gemm_args {
   void* scatter_out[8];
   int max_tiles;
   int wait_world;
+  // kind 2 only: 1 = A holds e2m1 (FP4) values, two per byte in memory (even element in the low nibble), with UE8M0
+  // scales per 32 elements; lda / a_batch_stride then count elements.  B stays e4m3.
+  int a_format;
 } ds41_gemm_args;
 
 int ds41_gemm_tc(const ds41_gemm_args* args, void* stream);

@@ -53,6 +53,7 @@ struct GemmParams {
   int row_w_ld;
   float act_limit;        // mode 4: SwiGLU clamp
   int static_operand;     // 1: A holds weights, 2: B holds weights (may be fetched before the dependency wait)
+  int a_fp4;              // MX kind: A holds e2m1 values (packed in global memory, one per byte in shared memory)
   // grouped tokens (expert-parallel prefill, swap-AB): the N operand is a flat buffer of rows sorted by expert;
   // tile j covers rows [tile_row0[j], tile_end[j]) of expert tile_group[j]; *n_tiles_dev tiles are live
   const int* tile_group;
@@ -318,7 +319,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t sfb_t = sf_t + 4 * Cfg::kAtomsA + (n_base_u & 127u) / 32u;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint32_t id = umma_idesc_bs(kBM, BN, 0, 0, 1, k, k);
+            const uint32_t id = umma_idesc_bs(kBM, BN, p.a_fp4 ? 5u : 0u, 0, 1, k, k);   // e2m1 = 5, e4m3 = 0
             const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
             umma_mxf8(d_tmem, adesc + 2 * k, bdesc + 2 * k, id, accum, sf_t, sfb_t);
             if constexpr (DUAL) {
@@ -713,12 +714,17 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
     return cudaErrorInvalidValue;
   CUtensorMap tmA, tmB;
   const TmaDtype dt = kind == 0 ? TmaDtype::kBF16 : TmaDtype::kU8;
+  const bool a_fp4 = a->a_format == 1;
+  if (a_fp4 && (kind != 2 || a->ag_world > 0)) return cudaErrorInvalidValue;
   const int a_rows = out_mode == 4 ? a->up_row_offset + M : M;           // dual tiles address gate and up rows
   const int a_batches = a->a_batches > 0 ? a->a_batches : batch;
   const int b_batches = a->b_batch_kind == 1 ? 1 : (a->b_batch_kind == 0 ? a_batches : batch);
   const void* a_base = a->ag_world > 0 ? a->a_peers[a->ag_rank] : a->A;
-  cudaError_t e = make_tensor_map_3d(&tmA, a_base, dt, K, a_rows, a_batches, a->lda * elem, a->a_batch_stride * elem, bk,
-                                     kBM, true);
+  // e2m1 operands: lda and a_batch_stride count elements, two per byte
+  cudaError_t e = a_fp4 ? make_tensor_map_3d(&tmA, a_base, TmaDtype::kU4x16Align16, K, a_rows, a_batches, a->lda / 2,
+                                             a->a_batch_stride / 2, bk, kBM, true)
+                        : make_tensor_map_3d(&tmA, a_base, dt, K, a_rows, a_batches, a->lda * elem,
+                                             a->a_batch_stride * elem, bk, kBM, true);
   if (e != cudaSuccess) return e;
   e = make_tensor_map_3d(&tmB, a->B, dt, K, N, b_batches, a->ldb * elem, a->b_batch_stride * elem, bk, bn, true);
   if (e != cudaSuccess) return e;
@@ -794,6 +800,7 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   p.scatter_meta = reinterpret_cast<const int2*>(a->scatter_meta);
   for (int r = 0; r < 8; ++r) p.scatter_out[r] = a->scatter_out[r];
   p.static_operand = a->static_operand;
+  p.a_fp4 = a_fp4 ? 1 : 0;
   p.status = a->status;
   const long long n_t = a->tile_group != nullptr ? a->max_tiles : (N + bn - 1) / bn;
   const long long tiles = 1ll * ((M + kBM - 1) / kBM) * n_t * k_splits * (a->tile_group != nullptr ? 1 : batch);

@@ -36,15 +36,20 @@ cudaError_t make_tensor_map_3d(CUtensorMap* out, const void* base, TmaDtype dtyp
     case TmaDtype::kU4x16Align16: dt = CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B; elem_bits = 4; break;
     default: return cudaErrorInvalidValue;
   }
-  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_stride_bytes & 15) != 0 ||
-      (batch > 1 && (batch_stride_bytes & 15) != 0) || ((uint64_t(box_cols) * elem_bits / 8) & 15) != 0 ||
-      box_rows == 0 || box_rows > 256 || box_cols == 0 || box_cols > 256) {
+  // 4-bit elements packed two per byte in global memory land one per byte in shared memory (16 values per 16 bytes):
+  // the box must be 128 elements wide and addresses / strides need 32-byte alignment
+  const bool padded4 = dtype == TmaDtype::kU4x16Align16;
+  const uint64_t box_smem_bytes = padded4 ? box_cols : uint64_t(box_cols) * elem_bits / 8;
+  const uint64_t align = padded4 ? 31 : 15;
+  if ((reinterpret_cast<uintptr_t>(base) & align) != 0 || (row_stride_bytes & align) != 0 ||
+      (batch > 1 && (batch_stride_bytes & align) != 0) || (box_smem_bytes & 15) != 0 ||
+      box_rows == 0 || box_rows > 256 || box_cols == 0 || box_cols > 256 || (padded4 && (box_cols != 128 || cols % 128))) {
     return cudaErrorInvalidValue;
   }
-  if (swizzle128 && uint64_t(box_cols) * elem_bits / 8 != 128) return cudaErrorInvalidValue;
+  if (swizzle128 && box_smem_bytes != 128) return cudaErrorInvalidValue;
   cuuint64_t dims[3] = {cols, rows, batch == 0 ? 1 : batch};
   cuuint64_t strides[2] = {row_stride_bytes, batch > 1 ? batch_stride_bytes : row_stride_bytes * rows};
-  if ((strides[1] & 15) != 0) strides[1] = (strides[1] + 15) & ~uint64_t(15);
+  if ((strides[1] & align) != 0) strides[1] = (strides[1] + align) & ~align;
   cuuint32_t box[3] = {box_cols, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = g_encode(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,

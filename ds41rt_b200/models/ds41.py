@@ -86,6 +86,25 @@ def quantize_expert_stack(w: torch.Tensor, device):
     return torch.stack(qs).to(device).contiguous(), torch.stack(sfs).to(device).contiguous()
 
 
+def quantize_expert_stack_fp4(w: torch.Tensor, device):
+    """[E, n, k] fp32 -> (E2M1 codes two per byte [E, n, k/2], scale atoms [E, n/128, k/128, 512]): the official routed
+    expert format (UE8M0 scale per 32 elements), consumed directly by the block-scaled GEMM with FP4 weights."""
+    from ..ops import quant_ref as Q
+    from ..ops.mx import pack_sf_atoms
+    qs, sfs = [], []
+    for e in range(w.shape[0]):
+        q, ex = Q.quant_mxfp4(w[e], 32)
+        qs.append(q)
+        sfs.append(pack_sf_atoms(ex))
+    return torch.stack(qs).to(device).contiguous(), torch.stack(sfs).to(device).contiguous()
+
+
+def dequantize_expert_fp4(q: torch.Tensor, sf_atoms: torch.Tensor) -> torch.Tensor:
+    from ..ops import quant_ref as Q
+    from ..ops.mx import unpack_sf_atoms
+    return Q.dequant_mxfp4(q.cpu(), unpack_sf_atoms(sf_atoms.cpu(), q.shape[0]), 32)
+
+
 def dequantize_expert(q: torch.Tensor, sf_atoms: torch.Tensor) -> torch.Tensor:
     """Inverse of quantize_expert_stack for one expert (used by tests to feed the oracle)."""
     from ..ops import quant_ref as Q
@@ -187,6 +206,9 @@ class EngineWeights:
             if expert_dtype == "mxfp8":
                 lw.w13, lw.w13_sf = quantize_expert_stack(w13, device)
                 lw.w2, lw.w2_sf = quantize_expert_stack(w2, device)
+            elif expert_dtype == "mxfp4":
+                lw.w13, lw.w13_sf = quantize_expert_stack_fp4(w13, device)
+                lw.w2, lw.w2_sf = quantize_expert_stack_fp4(w2, device)
             else:
                 lw.w13, lw.w2 = dev(w13), dev(w2)
             ew.layers.append(lw)
@@ -268,6 +290,21 @@ class EngineWeights:
                 lw.w2 = rnd8((EL, H, I))
                 lw.w13_sf = torch.full((EL, 2 * I // 128, H // 128, 512), 127 - 11, dtype=torch.uint8, device=device)
                 lw.w2_sf = torch.full((EL, H // 128, I // 128, 512), 127 - 11, dtype=torch.uint8, device=device)
+            elif expert_dtype == "mxfp4":
+                # uniform random E2M1 codes (two per byte) with every 1x32 scale 2^-7: dequantised std about 0.024
+                def rnd4(shape):
+                    out = torch.empty(shape, dtype=torch.uint8, device=device)
+                    flat = out.view(-1)
+                    step = 1 << 27
+                    for i in range(0, flat.numel(), step):
+                        n = min(step, flat.numel() - i)
+                        flat[i:i + n] = torch.randint(0, 256, (n,), generator=gen, device=device, dtype=torch.uint8)
+                    return out
+                I = cfg.inter
+                lw.w13 = rnd4((EL, 2 * I, H // 2))
+                lw.w2 = rnd4((EL, H, I // 2))
+                lw.w13_sf = torch.full((EL, 2 * I // 128, H // 128, 512), 127 - 7, dtype=torch.uint8, device=device)
+                lw.w2_sf = torch.full((EL, H // 128, I // 128, 512), 127 - 7, dtype=torch.uint8, device=device)
             else:
                 lw.w13 = rnd((EL, 2 * cfg.inter, H))
                 lw.w2 = rnd((EL, H, cfg.inter))
@@ -419,7 +456,8 @@ class DS41Engine:
         self.row_w = z((self.max_active, Rm), F32)
         self.slot_of = z((R, self.topk), I32)
         self.act = z((self.max_active, Rm, cfg.inter), BF16)
-        self.mx = weights.expert_dtype == "mxfp8"
+        self.mx = weights.expert_dtype in ("mxfp8", "mxfp4")
+        self.a_fmt = 1 if weights.expert_dtype == "mxfp4" else 0     # routed expert weights in E2M1 (two per byte)
         if self.mx:
             assert H % 128 == 0 and cfg.inter % 128 == 0
             ra = (Rm + 127) // 128
@@ -673,7 +711,8 @@ class DS41Engine:
                                batch=self.max_active, a_batches=EL, a_batch_stride=2 * I * H, out_batch_stride=R * I,
                                batch_map=self.active, n_active=self.n_active, b_batch_kind=1, up_row_offset=I,
                                row_w=self.row_w, row_w_ld=self.moe_rows, act_limit=cfg.swiglu_limit,
-                               sfa=lw.w13_sf, sfa_batch_stride=lw.w13_sf[0].numel(), sfb=self.xq_sf, status=self.status)
+                               sfa=lw.w13_sf, sfa_batch_stride=lw.w13_sf[0].numel(), sfb=self.xq_sf, status=self.status,
+                               a_format=self.a_fmt)
                     sf_slot = ra * (I // 128) * 512
                     self._run("act_quant act", k.ds41_act_quant_mx, lib.ptr(self.act), C.c_longlong(I), C.c_longlong(R * I),
                                                  lib.ptr(self.actq), C.c_longlong(I), C.c_longlong(R * I),
@@ -684,7 +723,7 @@ class DS41Engine:
                                out_batch_stride=R * H, batch_map=self.active, n_active=self.n_active, b_batch_kind=2,
                                row_w=self.row_w, row_w_ld=self.moe_rows, sfa=lw.w2_sf,
                                sfa_batch_stride=lw.w2_sf[0].numel(), sfb=self.actq_sf, sfb_batch_stride=sf_slot,
-                               status=self.status)
+                               status=self.status, a_format=self.a_fmt)
                 else:
                     self._run("gemm_fc1", G.gemm_raw, lw.w13, self.xn, self.act, I, R, H, lda=H, ldb=H, ldo=I, out_mode=4, bn=bn,
                                batch=self.max_active, a_batches=EL, a_batch_stride=2 * I * H, out_batch_stride=R * I,
@@ -710,7 +749,7 @@ class DS41Engine:
         per_rank = (self.max_rows + self.world - 1) // self.world
         self._ep = ExpertParallelMoE(self.fabric, lw.w13, lw.w2, topk=lw.topk, max_tokens=per_rank,
                                      act_limit=self.cfg.swiglu_limit, w13_sf=getattr(lw, "w13_sf", None),
-                                     w2_sf=getattr(lw, "w2_sf", None))
+                                     w2_sf=getattr(lw, "w2_sf", None), fp4=self.a_fmt == 1)
 
     def _moe_sorted(self, R: int, lw: LayerWeights):
         """Routed + shared experts of a long pass: this rank's slice of the rows is dispatched to the experts' owners,

@@ -41,7 +41,7 @@ def gemm_raw(A, B, out, M, N, K, *, lda, ldb, ldo, kind=0, out_mode=0, k_splits=
              a_batch_stride=0, b_batch_stride=0, out_batch_stride=0, a_batches=0, split_workspace=None,
              sfa=None, sfb=None, sfa_batch_stride=0, sfb_batch_stride=0, batch_map=None, n_active=None,
              b_batch_kind=0, up_row_offset=0, row_w=None, row_w_ld=0, act_limit=10.0, status=None,
-             static_operand=0):
+             static_operand=0, a_format=0):
     a = lib.GemmArgs()
     a.A, a.B, a.out = lib.ptr(A), lib.ptr(B), lib.ptr(out)
     a.split_workspace = lib.ptr(split_workspace)
@@ -54,6 +54,7 @@ def gemm_raw(A, B, out, M, N, K, *, lda, ldb, ldo, kind=0, out_mode=0, k_splits=
     a.kind, a.out_mode, a.k_splits, a.bn = kind, out_mode, k_splits, bn or pick_bn(N)
     a.b_batch_kind, a.up_row_offset, a.row_w_ld, a.act_limit = b_batch_kind, up_row_offset, row_w_ld, act_limit
     a.static_operand = static_operand
+    a.a_format = a_format
     lib.check(lib.kernels().ds41_gemm_tc(C.byref(a), lib.stream()), "ds41_gemm_tc")
 
 

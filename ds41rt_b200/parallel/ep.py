@@ -33,12 +33,16 @@ def _round_up(x: int, m: int) -> int:
 class ExpertParallelMoE:
     def __init__(self, fabric: Fabric, w13: torch.Tensor, w2: torch.Tensor, *, topk: int, max_tokens: int,
                  act_limit: float = 10.0, capacity: Optional[int] = None, w13_sf: Optional[torch.Tensor] = None,
-                 w2_sf: Optional[torch.Tensor] = None):
-        """w13: [E_local, 2*I, H] (gate rows then up rows), w2: [E_local, H, I]; bf16, or e4m3 with UE8M0 scale atoms."""
+                 w2_sf: Optional[torch.Tensor] = None, fp4: bool = False):
+        """w13: [E_local, 2*I, H] (gate rows then up rows), w2: [E_local, H, I]; bf16, or e4m3 with UE8M0 scale atoms,
+        or (fp4) E2M1 codes two per byte ([.., H/2] / [.., I/2] uint8) with UE8M0 scale atoms."""
         self.f = fabric
         self.w13, self.w2, self.w13_sf, self.w2_sf = w13, w2, w13_sf, w2_sf
         self.mx = w13_sf is not None
+        self.fp4 = fp4
         self.e_local, two_i, self.H = w13.shape
+        if fp4:
+            self.H *= 2
         self.I = two_i // 2
         self.topk, self.max_tokens, self.act_limit = topk, max_tokens, act_limit
         W, dev = fabric.world, fabric.device
@@ -115,7 +119,8 @@ class ExpertParallelMoE:
         a.A, a.B, a.out, a.status = lib.ptr(A), lib.ptr(B), lib.ptr(out), lib.ptr(self.status)
         a.lda, a.ldb, a.ldo = lda, K, ldo
         a.M, a.N, a.K, a.batch, a.a_batches = M, self.cap, K, self.e_local, self.e_local
-        a.a_batch_stride = A.stride(0)
+        a.a_batch_stride = A.stride(0) * (2 if self.fp4 else 1)      # counted in elements
+        a.a_format = 1 if self.fp4 else 0
         a.kind, a.out_mode, a.k_splits, a.b_batch_kind = (2 if self.mx else 0), out_mode, 1, 1
         a.bn = self.bn2 if table else self.bn
         t0 = table * self.max_tiles

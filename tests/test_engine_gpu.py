@@ -128,18 +128,20 @@ def test_verify_rows_equal_single_steps():
     assert chunk == seq[1:6]
 
 
-@pytest.mark.parametrize("chunk", [8, 40])
-def test_mxfp8_experts_match_oracle(chunk):
+@pytest.mark.parametrize("dtype,chunk", [("mxfp8", 8), ("mxfp8", 40), ("mxfp4", 8), ("mxfp4", 40)])
+def test_block_scaled_experts_match_oracle(dtype, chunk):
     """Routed experts stored as FP8 E4M3 + 128x128 power-of-two block scales, run through the block-scaled
     tcgen05 path, vs the oracle evaluated on the dequantised weights (chunk 40: the sorted expert path)."""
     from ds41rt_b200.config import ModelConfig
     from ds41rt_b200.models.weights import init_weights
     from ds41rt_b200.models.reference import ReferenceModel
-    from ds41rt_b200.models.ds41 import EngineWeights, DS41Engine, dequantize_expert
+    from ds41rt_b200.models.ds41 import EngineWeights, DS41Engine, dequantize_expert, dequantize_expert_fp4
     cfg = ModelConfig.tiny()
     w = init_weights(cfg, seed=0)
     wr = {k: (v.bfloat16().float() if v.dim() == 2 and not k.endswith("_fn") else v) for k, v in w.items()}
-    ew = EngineWeights.from_fp32(cfg, wr, 0, 1, torch.device("cuda"), expert_dtype="mxfp8")
+    ew = EngineWeights.from_fp32(cfg, wr, 0, 1, torch.device("cuda"), expert_dtype=dtype)
+    if dtype == "mxfp4":
+        dequantize_expert = dequantize_expert_fp4
     I = cfg.inter
     for l, lw in enumerate(ew.layers):
         for e in range(cfg.n_experts):

@@ -95,3 +95,23 @@ def test_mxfp8_block_scaled(rows, N, K):
     torch.cuda.synchronize()
     lib.raise_on_status(st, "gemm mx")
     assert _rel(out, ref) < 2e-3
+
+
+@pytest.mark.parametrize("rows,N,K", [(5, 256, 512), (40, 384, 1024), (16, 4608, 5120)])
+def test_mxfp4_weights_times_mxfp8_rows(rows, N, K):
+    """E2M1 weights (two per byte, UE8M0 per 32) as the M operand of the block-scaled kind, E4M3 rows as N."""
+    from ds41rt_b200.ops import gemm as G, lib, quant_ref as Q
+    from ds41rt_b200.ops.mx import pack_sf_atoms
+    torch.manual_seed(2)
+    x = torch.randn(rows, K, device="cuda") * torch.exp(torch.randn(rows, 1, device="cuda"))
+    w = torch.randn(N, K, device="cuda") * 0.1 * torch.exp(torch.randn(N, 1, device="cuda"))
+    xq, xe = Q.quant_mxfp8(x)
+    wq, we = Q.quant_mxfp4(w)
+    ref = Q.dequant_mxfp8(xq, xe) @ Q.dequant_mxfp4(wq, we).t()
+    st = lib.new_status("cuda")
+    out = torch.zeros(rows, N, device="cuda")
+    G.gemm_raw(wq.contiguous(), xq, out, N, rows, K, lda=K, ldb=K, ldo=N, kind=2, out_mode=3, sfa=pack_sf_atoms(we),
+               sfb=pack_sf_atoms(xe), bn=max(32, G.pick_bn(rows)), status=st, a_format=1)
+    torch.cuda.synchronize()
+    lib.raise_on_status(st, "gemm mxfp4")
+    assert _rel(out, ref) < 2e-3

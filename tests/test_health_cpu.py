@@ -1,0 +1,91 @@
+"""Rank failure detection on the host: fake clock on an in-process store, and real gloo ranks where one leaves with
+a note or goes silent.  No GPU is involved; a peer learns of the loss from the store before its next collective, or -
+if that collective was already posted - from the collective's error, and then names the rank from the store."""
+import multiprocessing as mp
+import os
+import time
+
+import pytest
+
+from ds41rt_b200.parallel.health import DictStore, Heartbeat, RankFailure
+
+
+def test_silent_left_and_missing_ranks_with_a_fake_clock():
+    now = [100.0]
+    store = DictStore()
+    hb = [Heartbeat(store, r, 4, max_age=2.0, clock=lambda: now[0]) for r in range(3)]   # rank 3 never joins
+    assert hb[0].peers_down() == {3: "never joined"}
+    now[0] += 1.5
+    hb[0].beat(); hb[1].beat()                       # rank 2 goes silent
+    now[0] += 1.0
+    down = hb[0].peers_down()
+    assert set(down) == {2, 3} and down[2].startswith("silent")
+    hb[1].leave("cuda status 2 at site 110")
+    with pytest.raises(RankFailure) as e:
+        hb[0].guard()
+    assert e.value.ranks == [1, 2, 3] and "site 110" in e.value.reasons[1]
+
+
+def _rank(rank, world, port, mode, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    store = dist.TCPStore("127.0.0.1", port + 1, world, is_master=(rank == 0), wait_for_workers=False)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=__import__("datetime").timedelta(seconds=20))
+    import torch
+    hb = Heartbeat(store, rank, world, interval=0.05, max_age=0.6).start()
+    steps, failure = 0, None
+    try:
+        for step in range(60):
+            hb.guard()                               # between steps: nothing in flight
+            if rank == world - 1 and step == 3:
+                if mode == "leave":
+                    hb.leave("leaving after step 3")
+                    break
+                if mode == "die":
+                    hb.stop()                        # goes silent without a note; stays out of further collectives
+                    time.sleep(2.0)
+                    break
+            t = torch.ones(4)
+            try:
+                dist.all_reduce(t)
+            except RuntimeError:
+                # the peer left while this collective was already posted: the store says who and why
+                deadline = time.time() + 3.0
+                while time.time() < deadline and not hb.peers_down():
+                    time.sleep(0.05)
+                hb.guard()
+                raise
+            steps += 1
+            time.sleep(0.05)
+    except RankFailure as e:
+        failure = (e.ranks, dict(e.reasons))
+    q.put((rank, steps, failure))
+    hb.stop()
+    time.sleep(0.3)
+    os._exit(0)                                      # no collective teardown with a missing peer
+
+
+@pytest.mark.parametrize("mode", ["leave", "die"])
+def test_gloo_ranks_detect_a_lost_peer_before_the_next_collective(mode):
+    world, port = 3, 29650 + (0 if mode == "leave" else 10)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank, args=(r, world, port, mode, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = {}
+    for _ in range(world):
+        rank, steps, failure = q.get(timeout=60)
+        results[rank] = (steps, failure)
+    for p in procs:
+        p.join(timeout=20)
+    lost = world - 1
+    assert results[lost][0] == 3
+    for r in range(world - 1):
+        steps, failure = results[r]
+        assert failure is not None and lost in failure[0], results
+        assert steps >= 3
+        if mode == "leave":
+            assert "leaving after step 3" in failure[1][lost]
+        else:
+            assert failure[1][lost].startswith("silent")
