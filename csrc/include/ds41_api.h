@@ -130,14 +130,17 @@ int ds41_hc_step(const ds41_hc_step_args* args, void* stream);
 
 // ---------------------------------------------------------------------------------------------------
 // Attention-side projections' epilogues and cache writes (attn_ops.cu)
+// kv_row_bytes (qkv_post, compress, attend): 0 = latent rows are bf16 [D]; otherwise FP8 rows of that many bytes:
+// D e4m3 values, then D/32 UE8M0 scales (ceil_pow2(amax/448) per 32 elements), padded to a multiple of 16 bytes.
 int ds41_qkv_post(const float* planes, int splits, int rows, int ntot, int Q, int D, int rope_dim, int extra_f32,
                   int index_heads, float index_scale, const float* q_norm_w, const float* kv_norm_w,
                   const float* inv_freq, const int* row_pos, const int* row_slot, void* q_lat, void* win, int ring,
-                  float* extras, float eps, void* stream);
+                  float* extras, float eps, int kv_row_bytes, void* stream);
 int ds41_compress(const float* extras, int extra_stride, int rows, int D, int ID, int rope_dim, int ratio,
                   const int* row_pos, const int* row_slot, float* pending, const float* comp_norm_w, const void* wk,
                   const float* k_norm_w, const float* inv_freq, const float* inv_freq_idx, const int* page_table,
-                  int max_pages, int page_rows, void* comp_pool, void* idx_pool, float eps, void* stream);
+                  int max_pages, int page_rows, void* comp_pool, void* idx_pool, float eps, int kv_row_bytes,
+                  void* stream);
 
 // ---------------------------------------------------------------------------------------------------
 // Indexer, top-k and sparse attention (sparse_attn.cu)
@@ -151,7 +154,7 @@ int ds41_attend(const void* q, long long ldq, int q_off, int rows, int heads, in
                 const int* row_pos, const int* row_slot, const void* win, const void* comp_pool, const int* sel,
                 const int* n_sel, int k, const int* page_table, int max_pages, int page_rows, const float* inv_freq,
                 int rope_dim, float scale, int n_splits, const int* row_hi, float* part_o, float* part_ml,
-                const float* sink, void* out, long long ldo, void* stream);
+                const float* sink, void* out, long long ldo, int kv_row_bytes, void* stream);
 
 // ---------------------------------------------------------------------------------------------------
 // Router / experts (moe.cu)

@@ -290,5 +290,13 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+// Biased exponent of the smallest power of two >= x (UE8M0 scale, clamped to the finite range).
+__device__ __forceinline__ uint32_t ue8m0_ceil_exp(float x) {
+  x = fmaxf(x, 1.17549435e-38f);
+  const uint32_t bits = __float_as_uint(x);
+  uint32_t e = (bits >> 23) & 0xFF;
+  if (bits & 0x7FFFFF) ++e;
+  return e > 254 ? 254 : e;
+}
 
 }  // namespace ds41

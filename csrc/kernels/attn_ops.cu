@@ -14,6 +14,24 @@
 
 namespace ds41 {
 
+// FP8 cache row: D e4m3 bytes, then D/32 UE8M0 scale bytes (scale = ceil_pow2(amax / 448) per 32 elements), padded to a
+// multiple of 16 bytes.  The calling thread holds elements (2i, 2i+1); 16 consecutive lanes form one 32-element group.
+// Every lane of the warp must call (inactive lanes pass zeros and active = false).
+__device__ __forceinline__ void store_kv_fp8_pair(uint8_t* row, int D, int i, float a, float b, bool active) {
+  float amax = fmaxf(fabsf(a), fabsf(b));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
+  if (!active) return;
+  const uint32_t e = ue8m0_ceil_exp(amax * (1.0f / 448.0f));
+  const float inv = __uint_as_float((254u - e) << 23);
+  const __nv_fp8x2_e4m3 q(make_float2(a * inv, b * inv));
+  *reinterpret_cast<uint16_t*>(row + 2 * i) = *reinterpret_cast<const uint16_t*>(&q);
+  if ((i & 15) == 0) row[D + (i >> 4)] = static_cast<uint8_t>(e);
+}
+
+
 __device__ __forceinline__ void rope_cs(int pos, float inv_freq, float* c, float* s) {
   // reduce the angle in double so positions up to 2^20 keep fp32-accurate sin/cos
   const double a = static_cast<double>(pos) * static_cast<double>(inv_freq);
@@ -46,8 +64,9 @@ struct QkvPostParams {
   const int* row_pos;
   const int* row_slot;
   __nv_bfloat16* q_lat;     // [rows][Q]
-  __nv_bfloat16* win;       // [slots][ring][D]
+  __nv_bfloat16* win;       // [slots][ring][D] bf16, or FP8 rows of kv_row_bytes bytes (see store_kv_fp8_pair)
   int ring;
+  int kv_row_bytes;         // 0: bf16 rows
   float* extras;            // [rows][extra_f32]
   float eps;
 };
@@ -109,23 +128,34 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostParams p) {
   const float inv = rsqrtf(tot / p.D + p.eps);
   const int pos = p.row_pos[r];
   const int slot = p.row_slot[r];
-  __nv_bfloat16* dst = p.win + (1ll * slot * p.ring + (pos % p.ring)) * p.D;
+  const long long ring_row = 1ll * slot * p.ring + (pos % p.ring);
+  __nv_bfloat16* dst = p.win + ring_row * p.D;
+  uint8_t* dst8 = reinterpret_cast<uint8_t*>(p.win) + ring_row * p.kv_row_bytes;
 #pragma unroll
   for (int n = 0; n < 4; ++n) {
     const int i = tid + 256 * n;
-    if (i >= p.D / 2) continue;
-    float a = bf16_round(kvv[n].x * inv * p.kv_norm_w[2 * i]);
-    float b = bf16_round(kvv[n].y * inv * p.kv_norm_w[2 * i + 1]);
-    const int t = 2 * i - (p.D - p.rope_dim);
-    if (t >= 0) {
-      float c, s;
-      rope_cs(pos, p.inv_freq[t / 2], &c, &s);
-      const float ra = a * c - b * s;
-      const float rb = b * c + a * s;
-      a = ra;
-      b = rb;
+    if (256 * n >= p.D / 2) break;                      // uniform over the block
+    const bool active = i < p.D / 2;
+    float a = 0.f, b = 0.f;
+    if (active) {
+      a = bf16_round(kvv[n].x * inv * p.kv_norm_w[2 * i]);
+      b = bf16_round(kvv[n].y * inv * p.kv_norm_w[2 * i + 1]);
+      const int t = 2 * i - (p.D - p.rope_dim);
+      if (t >= 0) {
+        float c, s;
+        rope_cs(pos, p.inv_freq[t / 2], &c, &s);
+        const float ra = a * c - b * s;
+        const float rb = b * c + a * s;
+        a = ra;
+        b = rb;
+      }
     }
-    if (slot >= 0) reinterpret_cast<__nv_bfloat162*>(dst)[i] = __floats2bfloat162_rn(a, b);
+    if (p.kv_row_bytes > 0) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);      // the cache holds the FP8 image of the bf16 row
+      store_kv_fp8_pair(dst8, p.D, i, __low2float(h), __high2float(h), active && slot >= 0);
+    } else if (active && slot >= 0) {
+      reinterpret_cast<__nv_bfloat162*>(dst)[i] = __floats2bfloat162_rn(a, b);
+    }
   }
   // ---- extras (fp32 pass-through; index weights scaled)
   for (int c = tid; c < p.extra_f32; c += 256) {
@@ -150,7 +180,8 @@ struct CompressParams {
   const float* inv_freq_idx; // [ID/4]
   const int* page_table;     // [slots][max_pages]
   int max_pages, page_rows;
-  __nv_bfloat16* comp_pool;  // [pool_rows][D]
+  __nv_bfloat16* comp_pool;  // [pool_rows][D] bf16, or FP8 rows of kv_row_bytes bytes
+  int kv_row_bytes;
   __nv_bfloat16* idx_pool;   // [pool_rows][ID]
   float eps;
 };
@@ -226,17 +257,28 @@ __global__ void __launch_bounds__(256) compress_kernel(CompressParams p) {
     }
     reinterpret_cast<__nv_bfloat162*>(p.idx_pool + phys * p.ID)[i] = __floats2bfloat162_rn(a, b);
   }
-  for (int i = tid; i < p.D / 2; i += 256) {
-    float a = latent[2 * i], b = latent[2 * i + 1];
-    const int t = 2 * i - (p.D - p.rope_dim);
-    if (t >= 0) {
-      float c, s;
-      rope_cs(first_pos, p.inv_freq[t / 2], &c, &s);
-      const float ra = a * c - b * s, rb = b * c + a * s;
-      a = ra;
-      b = rb;
+  for (int i0 = 0; i0 < p.D / 2; i0 += 256) {
+    const int i = i0 + tid;
+    const bool active = i < p.D / 2;
+    float a = 0.f, b = 0.f;
+    if (active) {
+      a = latent[2 * i];
+      b = latent[2 * i + 1];
+      const int t = 2 * i - (p.D - p.rope_dim);
+      if (t >= 0) {
+        float c, s;
+        rope_cs(first_pos, p.inv_freq[t / 2], &c, &s);
+        const float ra = a * c - b * s, rb = b * c + a * s;
+        a = ra;
+        b = rb;
+      }
     }
-    reinterpret_cast<__nv_bfloat162*>(p.comp_pool + phys * p.D)[i] = __floats2bfloat162_rn(a, b);
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    if (p.kv_row_bytes > 0)
+      store_kv_fp8_pair(reinterpret_cast<uint8_t*>(p.comp_pool) + phys * p.kv_row_bytes, p.D, i, __low2float(h),
+                        __high2float(h), active);
+    else if (active)
+      reinterpret_cast<__nv_bfloat162*>(p.comp_pool + phys * p.D)[i] = h;
   }
 }
 
@@ -247,12 +289,14 @@ using namespace ds41;
 extern "C" int ds41_qkv_post(const float* planes, int splits, int rows, int ntot, int Q, int D, int rope_dim,
                              int extra_f32, int index_heads, float index_scale, const float* q_norm_w,
                              const float* kv_norm_w, const float* inv_freq, const int* row_pos, const int* row_slot,
-                             void* q_lat, void* win, int ring, float* extras, float eps, void* stream) {
+                             void* q_lat, void* win, int ring, float* extras, float eps, int kv_row_bytes,
+                             void* stream) {
   if (rows <= 0 || Q > 2048 || D > 2048 || (D & 1) || (rope_dim & 1) || Q + D + extra_f32 > ntot)
     return cudaErrorInvalidValue;
+  if (kv_row_bytes != 0 && (kv_row_bytes < D + D / 32 || (D & 31) || (kv_row_bytes & 15))) return cudaErrorInvalidValue;
   QkvPostParams p{planes, splits, rows, ntot, Q, D, rope_dim, extra_f32, index_heads, index_scale, q_norm_w,
                   kv_norm_w, inv_freq, row_pos, row_slot, static_cast<__nv_bfloat16*>(q_lat),
-                  static_cast<__nv_bfloat16*>(win), ring, extras, eps};
+                  static_cast<__nv_bfloat16*>(win), ring, kv_row_bytes, extras, eps};
   if ((Q + D) & 1) return cudaErrorInvalidValue;   // kv columns are read as aligned float2
   return launch_pdl(qkv_post_kernel, dim3(rows, 2), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
 }
@@ -261,11 +305,13 @@ extern "C" int ds41_compress(const float* extras, int extra_stride, int rows, in
                              const int* row_pos, const int* row_slot, float* pending, const float* comp_norm_w,
                              const void* wk, const float* k_norm_w, const float* inv_freq, const float* inv_freq_idx,
                              const int* page_table, int max_pages, int page_rows, void* comp_pool, void* idx_pool,
-                             float eps, void* stream) {
+                             float eps, int kv_row_bytes, void* stream) {
+  if (kv_row_bytes != 0 && (kv_row_bytes < D + D / 32 || (D & 31) || (kv_row_bytes & 15))) return cudaErrorInvalidValue;
   if (rows <= 0 || D > 1024 || ID > 256 || (ratio != 1 && ratio != 2) || (D & 1) || (ID & 3))
     return cudaErrorInvalidValue;
   CompressParams p{extras, extra_stride, rows, D, ID, rope_dim, ratio, row_pos, row_slot, pending, comp_norm_w,
                    static_cast<const __nv_bfloat16*>(wk), k_norm_w, inv_freq, inv_freq_idx, page_table, max_pages,
-                   page_rows, static_cast<__nv_bfloat16*>(comp_pool), static_cast<__nv_bfloat16*>(idx_pool), eps};
+                   page_rows, static_cast<__nv_bfloat16*>(comp_pool), kv_row_bytes,
+                   static_cast<__nv_bfloat16*>(idx_pool), eps};
   return launch_pdl(compress_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
 }

@@ -24,14 +24,6 @@ static int sm_count_cached() {
   return n;
 }
 
-__device__ __forceinline__ uint32_t ue8m0_ceil_exp(float x) {
-  x = fmaxf(x, 1.17549435e-38f);
-  const uint32_t bits = __float_as_uint(x);
-  uint32_t e = (bits >> 23) & 0xFF;
-  if (bits & 0x7FFFFF) ++e;
-  return e > 254 ? 254 : e;
-}
-
 struct ActQuantParams {
   const __nv_bfloat16* x;
   long long ldx, x_batch_stride;

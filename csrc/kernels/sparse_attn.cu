@@ -247,6 +247,7 @@ struct AttendParams {
   const int* row_hi;           // optional [rows]: highest visible window position (>= pos); null = causal
   float* part_o;               // [rows][n_splits][heads][D]
   float* part_ml;              // [rows][n_splits][heads][2]
+  int kv_row_bytes;            // 0: win / comp_pool rows are bf16 [D]; else FP8 rows (D e4m3 + D/32 UE8M0, padded)
 };
 
 constexpr int kKeysPerCta = 64;
@@ -276,6 +277,7 @@ __global__ void __launch_bounds__(128) attend_kernel(AttendParams p) {
   float* sM = reinterpret_cast<float*>(sPtr + 64);                                    // [16] running max
   float* sL = sM + kHeadsPerCta;                                                      // [16] running sum
   float* sScale = sL + kHeadsPerCta;                                                  // [16] rescale of this tile
+  uint8_t* sK8 = reinterpret_cast<uint8_t*>(sScale + kHeadsPerCta);                   // FP8 rows: [64][kv_row_bytes]
 
   const int split = blockIdx.x, r = blockIdx.y, h_base = blockIdx.z * kHeadsPerCta;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -345,30 +347,64 @@ __global__ void __launch_bounds__(128) attend_kernel(AttendParams p) {
     if (tid < kKeysPerCta) {
       const __nv_bfloat16* ptr = nullptr;
       const int j = k0 + tid;
+      const long long row_bytes = p.kv_row_bytes > 0 ? p.kv_row_bytes : 2ll * D;
       if (tid < k_cnt) {
         if (j < n_w) {
           const int kp = lo_pos + j;
-          ptr = p.win + (1ll * slot * p.ring + (kp % p.ring)) * D;
+          ptr = reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const uint8_t*>(p.win) +
+                                                       (1ll * slot * p.ring + (kp % p.ring)) * row_bytes);
         } else {
           const int id = p.sel[1ll * r * p.k + (j - n_w)];
           const long long phys = id < 0 ? -1 : pool_row(p.page_table, p.max_pages, p.page_rows, slot, id);
-          if (phys >= 0) ptr = p.comp_pool + phys * D;
+          if (phys >= 0)
+            ptr = reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const uint8_t*>(p.comp_pool) + phys * row_bytes);
         }
       }
       sPtr[tid] = ptr;
     }
     __syncthreads();          // also: the previous tile's P.V reads of sK / sP are complete
     // K tile: asynchronous 16-byte copies straight into shared memory (zero-filled beyond k_cnt)
+    if (p.kv_row_bytes == 0) {
 #pragma unroll 8
-    for (int idx = tid; idx < kKeysPerCta * (D / 8); idx += 128) {
-      const int key = idx / (D / 8), ch = idx % (D / 8);
-      const __nv_bfloat16* src = sPtr[key];
-      __nv_bfloat16* dst = sK + key * LD + ch * 8;
-      if (src != nullptr) cp_async_16(dst, src + ch * 8);
-      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      for (int idx = tid; idx < kKeysPerCta * (D / 8); idx += 128) {
+        const int key = idx / (D / 8), ch = idx % (D / 8);
+        const __nv_bfloat16* src = sPtr[key];
+        __nv_bfloat16* dst = sK + key * LD + ch * 8;
+        if (src != nullptr) cp_async_16(dst, src + ch * 8);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+      cp_async_wait_all();
+      __syncthreads();
+    } else {
+      // FP8 rows: copy payload + scales as they are, then expand to bf16 (exact: e4m3 value times a power of two)
+      const int chunks = p.kv_row_bytes / 16;
+      for (int idx = tid; idx < kKeysPerCta * chunks; idx += 128) {
+        const int key = idx / chunks, ch = idx - key * chunks;
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(sPtr[key]);
+        uint8_t* dst = sK8 + key * p.kv_row_bytes + ch * 16;
+        if (src != nullptr) cp_async_16(dst, src + ch * 16);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+      cp_async_wait_all();
+      __syncthreads();
+#pragma unroll 4
+      for (int idx = tid; idx < kKeysPerCta * (D / 8); idx += 128) {
+        const int key = idx / (D / 8), ch = idx % (D / 8);
+        const uint8_t* row8 = sK8 + key * p.kv_row_bytes;
+        const uint2 raw = *reinterpret_cast<const uint2*>(row8 + ch * 8);
+        const float sc = __uint_as_float(static_cast<uint32_t>(row8[D + (ch >> 2)]) << 23);
+        const __nv_fp8x2_storage_t* q2 = reinterpret_cast<const __nv_fp8x2_storage_t*>(&raw);
+        uint4 out;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(q2[q], __NV_E4M3)));
+          o2[q] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+        }
+        *reinterpret_cast<uint4*>(sK + key * LD + ch * 8) = out;
+      }
+      __syncthreads();
     }
-    cp_async_wait_all();
-    __syncthreads();
     // S = Q K^T: warp w owns keys [16w, 16w+16)
     {
       float c[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -531,13 +567,17 @@ __global__ void __launch_bounds__(128) attend_merge_kernel(MergeParams p) {
 template <int D>
 static cudaError_t launch_attend(const AttendParams& p, cudaStream_t stream) {
   constexpr int LD = D + 8;
-  constexpr size_t smem = size_t(kKeysPerCta) * LD * 2 + size_t(kHeadsPerCta) * LD * 2 + size_t(kHeadsPerCta) * 65 * 4 +
+  constexpr size_t base = size_t(kKeysPerCta) * LD * 2 + size_t(kHeadsPerCta) * LD * 2 + size_t(kHeadsPerCta) * 65 * 4 +
                           size_t(kHeadsPerCta) * 72 * 2 + 128 * 4 + 64 * 8 + 3 * kHeadsPerCta * 4 + 64;
+  constexpr size_t smem_max = base + size_t(kKeysPerCta) * ((D + D / 32 + 15) / 16 * 16);
+  const size_t smem = base + size_t(kKeysPerCta) * p.kv_row_bytes;
+  if (p.kv_row_bytes != 0 && (p.kv_row_bytes < D + D / 32 || (p.kv_row_bytes & 15) || smem > smem_max))
+    return cudaErrorInvalidValue;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(attend_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    cudaError_t e = cudaFuncSetAttribute(attend_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_max));
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
@@ -574,12 +614,13 @@ extern "C" int ds41_attend(const void* q, long long ldq, int q_off, int rows, in
                            const int* sel, const int* n_sel, int k, const int* page_table, int max_pages,
                            int page_rows, const float* inv_freq, int rope_dim, float scale, int n_splits,
                            const int* row_hi, float* part_o, float* part_ml, const float* sink, void* out,
-                           long long ldo, void* stream) {
+                           long long ldo, int kv_row_bytes, void* stream) {
   if (rows <= 0 || heads <= 0 || rope_dim > 128 || (rope_dim & 7) || n_splits <= 0 || n_splits > 32)
     return cudaErrorInvalidValue;
   AttendParams p{static_cast<const __nv_bfloat16*>(q), ldq, q_off, rows, heads, window, ring, row_pos, row_slot,
                  static_cast<const __nv_bfloat16*>(win), static_cast<const __nv_bfloat16*>(comp_pool), sel, n_sel, k,
-                 page_table, max_pages, page_rows, inv_freq, rope_dim, scale, n_splits, row_hi, part_o, part_ml};
+                 page_table, max_pages, page_rows, inv_freq, rope_dim, scale, n_splits, row_hi, part_o, part_ml,
+                 kv_row_bytes};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   if (D == 512) e = launch_attend<512>(p, s);

@@ -330,14 +330,19 @@ class KVCache:
     (sizing rule: native counterpart rust/crates/ds41rt-daemon/src/v41_native_serve/memory.rs:9-13,137)."""
 
     def __init__(self, cfg: ModelConfig, n_layers: int, slots: int, max_ctx: int, device, page_tokens: int = 64,
-                 n_pages: Optional[int] = None, spec_slack: int = 16):
+                 n_pages: Optional[int] = None, spec_slack: int = 16, kv_dtype: str = "bf16"):
         self.cfg, self.slots, self.max_ctx, self.page_tokens = cfg, slots, max_ctx, page_tokens
+        assert kv_dtype in ("bf16", "fp8")
+        self.kv_dtype = kv_dtype
+        # FP8 rows: D e4m3 values + D/32 UE8M0 scales (per 32 elements), padded to 16 bytes; 0 = bf16 rows
+        self.row_bytes = 0 if kv_dtype == "bf16" else (cfg.head_dim + cfg.head_dim // 32 + 15) // 16 * 16
         D = cfg.head_dim
         ring = cfg.window + spec_slack
         self.ring = ring
         self.max_pages = (max_ctx + page_tokens - 1) // page_tokens
         self.n_pages = n_pages if n_pages is not None else self.max_pages * slots
-        self.win = torch.zeros(n_layers, slots, ring, D, dtype=BF16, device=device)
+        kv_shape, kv_dt = ((D,), BF16) if self.row_bytes == 0 else ((self.row_bytes,), torch.uint8)
+        self.win = torch.zeros(n_layers, slots, ring, *kv_shape, dtype=kv_dt, device=device)
         self.comp: Dict[int, torch.Tensor] = {}
         self.idx: Dict[int, torch.Tensor] = {}
         self.pending: Dict[int, torch.Tensor] = {}
@@ -347,7 +352,7 @@ class KVCache:
                 continue
             pr = page_tokens // ratio
             self.page_rows[src] = pr
-            self.comp[src] = torch.zeros(self.n_pages * pr, D, dtype=BF16, device=device)
+            self.comp[src] = torch.zeros(self.n_pages * pr, *kv_shape, dtype=kv_dt, device=device)
             self.idx[src] = torch.zeros(self.n_pages * pr, cfg.index_dim, dtype=BF16, device=device)
             if ratio == 2:
                 self.pending[src] = torch.zeros(slots, 4, 2 * D, dtype=F32, device=device)
@@ -385,7 +390,7 @@ class KVCache:
 class DS41Engine:
     def __init__(self, cfg: ModelConfig, weights: EngineWeights, fabric: Optional[Fabric] = None, *,
                  max_rows: int = 8, slots: int = 1, max_ctx: int = 4096, page_tokens: int = 64,
-                 n_pages: Optional[int] = None, row_hi: bool = False, moe_rows: int = 32):
+                 n_pages: Optional[int] = None, row_hi: bool = False, moe_rows: int = 32, kv_dtype: str = "bf16"):
         self.cfg, self.w = cfg, weights
         self.fabric = fabric or Fabric.single(weights.device)
         self.rank, self.world = self.fabric.rank, self.fabric.world
@@ -396,7 +401,8 @@ class DS41Engine:
         self.k = lib.kernels()
         # the window ring holds one pass of new rows beyond the window: a row still needs the key at pos - window + 1
         # after the last row of its pass has been written
-        self.cache = KVCache(cfg, self.n_layers, slots, max_ctx, dev, page_tokens, n_pages, spec_slack=max(16, R))
+        self.cache = KVCache(cfg, self.n_layers, slots, max_ctx, dev, page_tokens, n_pages, spec_slack=max(16, R),
+                             kv_dtype=kv_dtype)
         self.HL, self.GL, self.I_sh, self.V_local = weights.HL, weights.GL, weights.I_sh, weights.V_local
         E = weights.layers[0].n_experts if weights.layers else cfg.n_experts
         self.E, self.topk = E, (weights.layers[0].topk if weights.layers else cfg.topk)
@@ -639,7 +645,7 @@ class DS41Engine:
                 lib.ptr(self.planes_qkv), s_qkv, R, ntot, Q, D, cfg.rope_dim, lw.extra_cols, lw.index_heads_cols,
                 C.c_float(cfg.index_weight_scale), lib.ptr(lw.q_norm), lib.ptr(lw.kv_norm), lib.ptr(inv),
                 lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.q_lat), lib.ptr(self.cache.win[l]),
-                self.cache.ring, lib.ptr(self.extras), C.c_float(cfg.norm_eps), st())
+                self.cache.ring, lib.ptr(self.extras), C.c_float(cfg.norm_eps), self.cache.row_bytes, st())
             src = None if self.layer_prefix_plain else cfg.source_of(l)
             if lw.ratio:
                 self._run("compress", k.ds41_compress, 
@@ -647,7 +653,8 @@ class DS41Engine:
                     lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.cache.pending.get(l)),
                     lib.ptr(lw.comp_norm), lib.ptr(lw.wk_idx), lib.ptr(lw.k_norm), lib.ptr(inv), lib.ptr(self.inv_idx),
                     lib.ptr(self.cache.page_table), self.cache.max_pages, self.cache.page_rows[l],
-                    lib.ptr(self.cache.comp[l]), lib.ptr(self.cache.idx[l]), C.c_float(cfg.norm_eps), st())
+                    lib.ptr(self.cache.comp[l]), lib.ptr(self.cache.idx[l]), C.c_float(cfg.norm_eps),
+                    self.cache.row_bytes, st())
             nqb = lw.w_qb.shape[0]
             self._run("gemm_qb", G.gemm_raw, lw.w_qb, self.q_lat, self.qb_out, nqb, R, Q, lda=Q, ldb=Q, ldo=self.nqb, out_mode=2,
                        status=self.status, static_operand=1)
@@ -669,7 +676,8 @@ class DS41Engine:
                 lib.ptr(self.sel), lib.ptr(self.n_sel), cfg.index_topk, lib.ptr(self.cache.page_table),
                 self.cache.max_pages, self.cache.page_rows[src] if src is not None else 1, lib.ptr(inv), cfg.rope_dim,
                 C.c_float(cfg.softmax_scale), self._attn_splits(R), lib.ptr(self.row_hi), lib.ptr(self.part_o),
-                lib.ptr(self.part_ml), lib.ptr(lw.sink), lib.ptr(self.attn_out), C.c_longlong(self.HL * D), st())
+                lib.ptr(self.part_ml), lib.ptr(lw.sink), lib.ptr(self.attn_out), C.c_longlong(self.HL * D),
+                self.cache.row_bytes, st())
             # grouped wo_a: batch = local groups
             kg = cfg.heads_per_group * D
             self._run("gemm_wo_a", G.gemm_raw, lw.wo_a, self.attn_out, self.oa, cfg.o_lora, R, kg, lda=kg, ldb=self.HL * D,
@@ -814,7 +822,7 @@ class DS41Engine:
                       cfg.rope_dim, lw.extra_cols, lw.index_heads_cols, C.c_float(cfg.index_weight_scale),
                       lib.ptr(lw.q_norm), lib.ptr(lw.kv_norm), lib.ptr(self._inv(l)), lib.ptr(self.row_pos),
                       lib.ptr(self.row_slot), lib.ptr(self.q_lat), lib.ptr(self.cache.win[l]), self.cache.ring,
-                      lib.ptr(self.extras), C.c_float(cfg.norm_eps), st())
+                      lib.ptr(self.extras), C.c_float(cfg.norm_eps), self.cache.row_bytes, st())
 
     # ------------------------------------------------------------------ convenience drivers
     def prefill(self, slot: int, tokens: List[int], start: int = 0, chunk: Optional[int] = None) -> int:

@@ -193,3 +193,47 @@ def test_cuda_graph_decode_matches_eager():
     torch.cuda.synchronize()
     assert int(eng.row_pos[0]) == len(prompt) + 5
     assert int(eng.in_tokens[0]) == out_graph[5]
+
+
+def test_fp8_kv_cache_rows_and_logits():
+    """FP8 cache rows are exactly the MX-FP8 (1x32, ceil-pow2 scale) image of the bf16 rows, and the model's logits
+    move only by the quantisation noise."""
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    from ds41rt_b200.ops import quant_ref as Q
+    cfg = ModelConfig.tiny()
+    dev = torch.device("cuda")
+    ew = EngineWeights.random(cfg, 0, 1, dev, seed=3)
+    engines = {kv: DS41Engine(cfg, ew, max_rows=16, slots=1, max_ctx=256, kv_dtype=kv) for kv in ("bf16", "fp8")}
+    g = torch.Generator().manual_seed(11)
+    toks = torch.randint(3, cfg.vocab, (48,), generator=g).tolist()
+    logits = {}
+    for kv, eng in engines.items():
+        eng.cache.ensure(0, 128)
+        for c0 in range(0, len(toks), 16):
+            part = toks[c0:c0 + 16]
+            eng.set_rows(part, list(range(c0, c0 + len(part))), [0] * len(part))
+            eng.forward_rows(len(part))
+        logits[kv] = eng.logits_rows(16).float().cpu()
+        eng.check_status()
+    D = cfg.head_dim
+    # layer 0 sees identical inputs in both engines: its window rows must be the exact FP8 image
+    ref_rows = engines["bf16"].cache.win[0][0]                      # [ring, D] bf16
+    got = engines["fp8"].cache.win[0][0]                             # [ring, row_bytes] uint8
+    q, e = Q.quant_mxfp8(ref_rows.float(), 32)
+    live = [p % engines["bf16"].cache.ring for p in range(len(toks))]
+    assert torch.equal(got[live, :D], q.view(torch.uint8)[live])
+    assert torch.equal(got[live, D:D + D // 32], e.to(torch.uint8)[live])
+    src = next(iter(engines["bf16"].cache.comp))
+    rows = len(toks) // cfg.source_layers[src]
+    qc, ec = Q.quant_mxfp8(engines["bf16"].cache.comp[src].float(), 32)
+    if src == 0:
+        pages = engines["bf16"].cache.pages_of[0]
+        pr = engines["bf16"].cache.page_rows[src]
+        phys = [pages[i // pr] * pr + i % pr for i in range(rows)]
+        assert torch.equal(engines["fp8"].cache.comp[src][phys, :D], qc.view(torch.uint8)[phys])
+    scale = float(logits["bf16"].abs().max())
+    err = float((logits["fp8"] - logits["bf16"]).abs().max())
+    agree = float((logits["fp8"].argmax(-1) == logits["bf16"].argmax(-1)).float().mean())
+    print("fp8 kv: max logit drift", err, "scale", scale, "argmax agreement", agree)
+    assert err < 0.15 * scale and agree >= 0.75

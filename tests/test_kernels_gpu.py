@@ -42,8 +42,20 @@ def _attend_ref(q, keys, sink, scale):
     return (e / (e.sum(-1, keepdim=True) + torch.exp(sink[:, None] - m))) @ keys
 
 
+def _pack_fp8_rows(x, row_bytes):
+    """bf16 rows -> (FP8 cache rows [.., row_bytes] uint8, the dequantised values the kernel must see)."""
+    from ds41rt_b200.ops import quant_ref as Q
+    D = x.shape[-1]
+    q, e = Q.quant_mxfp8(x.float(), 32)
+    rows = torch.zeros(*x.shape[:-1], row_bytes, dtype=torch.uint8, device=x.device)
+    rows[..., :D] = q.view(torch.uint8)
+    rows[..., D:D + D // 32] = e.to(torch.uint8)
+    return rows.contiguous(), Q.dequant_mxfp8(q, e, 32).bfloat16()
+
+
+@pytest.mark.parametrize("kv", ["bf16", "fp8"])
 @pytest.mark.parametrize("D,heads,rope", [(128, 8, 32), (512, 16, 64), (512, 64, 64)])
-def test_sparse_attention(D, heads, rope):
+def test_sparse_attention(D, heads, rope, kv):
     from ds41rt_b200.ops import lib
     from ds41rt_b200.config import RopeConfig, rope_inv_freq
     from ds41rt_b200.models.reference import apply_rope
@@ -54,6 +66,11 @@ def test_sparse_attention(D, heads, rope):
     slots = [0, 0, 1]
     win = torch.randn(2, ring, D, device="cuda").bfloat16()
     pool = torch.randn(max_pages * 2 * page_rows, D, device="cuda").bfloat16()
+    row_bytes = 0 if kv == "bf16" else (D + D // 32 + 15) // 16 * 16
+    win_dev, pool_dev = win, pool
+    if row_bytes:
+        win_dev, win = _pack_fp8_rows(win, row_bytes)          # the reference below sees the dequantised rows
+        pool_dev, pool = _pack_fp8_rows(pool, row_bytes)
     page_table = torch.arange(2 * max_pages, dtype=torch.int32, device="cuda").view(2, max_pages).flip(1).contiguous()
     sel = torch.full((rows, topk), -1, dtype=torch.int32, device="cuda")
     n_sel = torch.tensor([64, 40, 0], dtype=torch.int32, device="cuda")
@@ -70,10 +87,10 @@ def test_sparse_attention(D, heads, rope):
     slot_t = torch.tensor(slots, dtype=torch.int32, device="cuda")
     scale = D ** -0.5
     lib.check(k.ds41_attend(lib.ptr(q), C.c_longlong(heads * D), 0, rows, heads, D, window, ring, lib.ptr(pos_t),
-                            lib.ptr(slot_t), lib.ptr(win), lib.ptr(pool), lib.ptr(sel), lib.ptr(n_sel), topk,
+                            lib.ptr(slot_t), lib.ptr(win_dev), lib.ptr(pool_dev), lib.ptr(sel), lib.ptr(n_sel), topk,
                             lib.ptr(page_table), max_pages, page_rows, lib.ptr(inv), rope, C.c_float(scale), n_splits,
                             lib.ptr(None), lib.ptr(part_o), lib.ptr(part_ml), lib.ptr(sink), lib.ptr(out),
-                            C.c_longlong(heads * D), lib.stream()), "attend")
+                            C.c_longlong(heads * D), row_bytes, lib.stream()), "attend")
     torch.cuda.synchronize()
     for r in range(rows):
         pos, slot = positions[r], slots[r]
