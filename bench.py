@@ -34,9 +34,9 @@ LAYERS_FOR_GPUS = {1: 10, 2: 22, 4: 40, 8: 40}
 
 
 def reference_arm():
-    why = ("reference is a Rust/CMake engine whose kernels are AOT-exported for SM120/SM121 only and whose "
-           "sparkinfer/xgrammar submodules and Rust toolchain are absent; pip install of /root/reference finds no "
-           "Python project to build")
+    why = ("pip install of /root/reference fails: \"Directory '/root/reference' is not installable. Neither 'setup.py' "
+           "nor 'pyproject.toml' found.\" - the reference is a Rust/CMake engine whose kernels are AOT-exported for "
+           "SM120/SM121 by absent submodules, and the image has no Rust toolchain")
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
