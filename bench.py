@@ -135,7 +135,10 @@ def prefill_bench(args, fabric, cfg, n_layers):
     ms = timed(fabric, torch, lambda: [eng.prefill(0, prompt, chunk=args.chunk) for _ in range(K)])
     clocks = sampler.stop() if rank == 0 else {}
     eng.check_status("timed prefill")
-    if args.breakdown and rank == 0:
+    if args.breakdown:
+        # every rank runs the pass (its kernels wait on the peers'); rank 0 prints its own event times, which include
+        # the time its kernels spend waiting for slower peers
+        fabric.barrier()
         eng.timeline = []
         eng.prefill(0, prompt, chunk=args.chunk)
         torch.cuda.synchronize()
@@ -143,9 +146,11 @@ def prefill_bench(args, fabric, cfg, n_layers):
         for tag, e0, e1 in eng.timeline:
             acc[tag] = acc.get(tag, 0.0) + e0.elapsed_time(e1)
         eng.timeline = None
+        eng.check_status("breakdown pass")
         total = sum(acc.values())
-        for tag, v in sorted(acc.items(), key=lambda kv: -kv[1]):
-            print(f"  {tag:24s} {v:9.3f} ms  {100 * v / total:5.1f}%", file=sys.stderr)
+        if rank == 0:
+            for tag, v in sorted(acc.items(), key=lambda kv: -kv[1]):
+                print(f"  {tag:24s} {v:9.3f} ms  {100 * v / total:5.1f}%", file=sys.stderr)
     # end to end: the same public call, wall clock around it (token ids go up and the next token comes back per call)
     fabric.barrier()
     torch.cuda.synchronize()

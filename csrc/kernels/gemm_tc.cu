@@ -195,7 +195,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    constexpr uint32_t kStageTx = Cfg::kABytes + Cfg::kBBytes + (KIND == 2 ? 512 * (Cfg::kAtomsA + Cfg::kAtomsB) : 0);
+    // 4-bit A tiles occupy one byte per element in shared memory but the copy engine accounts the packed bytes
+    const uint32_t kStageTx = (p.a_fp4 ? Cfg::kABytes / 2 : Cfg::kABytes) + Cfg::kBBytes +
+                              (KIND == 2 ? 512 * (Cfg::kAtomsA + Cfg::kAtomsB) : 0);
     // Weight tiles of the first stages do not depend on the previous kernel: fetch them before waiting for it.
     int prefetched = 0;
     if (p.static_operand != 0 && p.n_active == nullptr && p.batch_map == nullptr && !table && blockIdx.x < tiles) {

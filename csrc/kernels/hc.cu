@@ -24,7 +24,7 @@ namespace ds41 {
 constexpr int kHcMaxMult = 4;
 constexpr int kHcProj = 2 * kHcMaxMult + kHcMaxMult * kHcMaxMult;   // 24
 constexpr int kHcSlice = 128;                                       // columns of H per block
-constexpr int kHcRowsPerBlock = 4;
+constexpr int kHcRowsPerBlock = 8;                                  // 8 rows x 32 four-column groups = one item per thread
 constexpr int kHcPartialStride = kHcProj + 1;                       // 24 dots + sum of squares
 
 struct PartList {
@@ -57,7 +57,7 @@ hc_post_mix_kernel(const __nv_bfloat16* __restrict__ streams_in, __nv_bfloat16* 
                    PartList parts, const float* __restrict__ post, const float* __restrict__ comb,
                    const float* __restrict__ fn, float* __restrict__ partial, int rows, int H,
                    const uint32_t* const* __restrict__ wait_flags, const uint32_t* __restrict__ wait_epoch, int* status) {
-  __shared__ float xs[kHcRowsPerBlock][kHcMaxMult][kHcSlice];
+  __shared__ __align__(16) float xs[kHcRowsPerBlock][kHcMaxMult][kHcSlice];
   const int c0 = blockIdx.x * kHcSlice;
   const int r0 = blockIdx.y * kHcRowsPerBlock;
   const int tid = threadIdx.x;
@@ -70,39 +70,68 @@ hc_post_mix_kernel(const __nv_bfloat16* __restrict__ streams_in, __nv_bfloat16* 
     if (tid < parts.n_ranks) flag_wait_ge(wait_flags[tid], *wait_epoch, status, 400 + tid);
     __syncthreads();
   }
-  // ---- expand (or plain load) into shared memory, bf16-rounded like the stored streams
-  for (int idx = tid; idx < kHcRowsPerBlock * kHcSlice; idx += blockDim.x) {
-    const int rr = idx / kHcSlice, c = idx % kHcSlice;
+  // ---- expand (or plain load) into shared memory, bf16-rounded like the stored streams.  One item = one row x four
+  // adjacent columns: 8-byte stream loads and 16-byte plane loads, all issued before the first use.
+  for (int idx = tid; idx < kHcRowsPerBlock * (kHcSlice / 4); idx += blockDim.x) {
+    const int rr = idx / (kHcSlice / 4), c = (idx % (kHcSlice / 4)) * 4;
     const int r = r0 + rr;
-    float out[kHcMaxMult] = {0.f, 0.f, 0.f, 0.f};
+    float out[kHcMaxMult][4];
+#pragma unroll
+    for (int d = 0; d < kHcMaxMult; ++d)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) out[d][j] = 0.f;
     if (r < rows) {
-      float s_in[kHcMaxMult];
+      float s_in[kHcMaxMult][4];
 #pragma unroll
-      for (int s = 0; s < kHcMaxMult; ++s)
-        s_in[s] = __bfloat162float(streams_in[(1ll * r * kHcMaxMult + s) * H + c0 + c]);
+      for (int s = 0; s < kHcMaxMult; ++s) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(streams_in + (1ll * r * kHcMaxMult + s) * H + c0 + c);
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        s_in[s][0] = lo.x; s_in[s][1] = lo.y; s_in[s][2] = hi.x; s_in[s][3] = hi.y;
+      }
       if (parts.n_ranks > 0) {
-        float sub = 0.f;
+        float sub[4] = {0.f, 0.f, 0.f, 0.f};
         for (int k = 0; k < parts.n_ranks; ++k)
-          for (int sp = 0; sp < parts.n_splits; ++sp)
-            sub += parts.base[k][sp * parts.split_stride + 1ll * r * H + c0 + c];
-        sub = bf16_round(sub);
+          for (int sp = 0; sp < parts.n_splits; ++sp) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(parts.base[k] + sp * parts.split_stride +
+                                                                    1ll * r * H + c0 + c));
+            sub[0] += v.x; sub[1] += v.y; sub[2] += v.z; sub[3] += v.w;
+          }
+        float cm[16], pw[4];
 #pragma unroll
-        for (int d = 0; d < kHcMaxMult; ++d) {
-          float acc = 0.f;
+        for (int q = 0; q < 16; ++q) cm[q] = comb[r * 16 + q];
 #pragma unroll
-          for (int s = 0; s < kHcMaxMult; ++s) acc = fmaf(comb[r * 16 + s * 4 + d], s_in[s], acc);
-          out[d] = bf16_round(fmaf(post[r * 4 + d], sub, acc));
+        for (int q = 0; q < 4; ++q) pw[q] = post[r * 4 + q];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float sb = bf16_round(sub[j]);
+#pragma unroll
+          for (int d = 0; d < kHcMaxMult; ++d) {
+            float acc = 0.f;
+#pragma unroll
+            for (int s = 0; s < kHcMaxMult; ++s) acc = fmaf(cm[s * 4 + d], s_in[s][j], acc);
+            out[d][j] = bf16_round(fmaf(pw[d], sb, acc));
+          }
         }
 #pragma unroll
-        for (int d = 0; d < kHcMaxMult; ++d)
-          streams_out[(1ll * r * kHcMaxMult + d) * H + c0 + c] = __float2bfloat16_rn(out[d]);
+        for (int d = 0; d < kHcMaxMult; ++d) {
+          const __nv_bfloat162 a = __floats2bfloat162_rn(out[d][0], out[d][1]);
+          const __nv_bfloat162 b = __floats2bfloat162_rn(out[d][2], out[d][3]);
+          uint2 w;
+          w.x = *reinterpret_cast<const uint32_t*>(&a);
+          w.y = *reinterpret_cast<const uint32_t*>(&b);
+          *reinterpret_cast<uint2*>(streams_out + (1ll * r * kHcMaxMult + d) * H + c0 + c) = w;
+        }
       } else {
 #pragma unroll
-        for (int d = 0; d < kHcMaxMult; ++d) out[d] = s_in[d];
+        for (int d = 0; d < kHcMaxMult; ++d)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) out[d][j] = s_in[d][j];
       }
     }
 #pragma unroll
-    for (int d = 0; d < kHcMaxMult; ++d) xs[rr][d][c] = out[d];
+    for (int d = 0; d < kHcMaxMult; ++d)
+      *reinterpret_cast<float4*>(&xs[rr][d][c]) = make_float4(out[d][0], out[d][1], out[d][2], out[d][3]);
   }
   __syncthreads();
   // ---- partial mixes: warp w owns projections w, w+8, w+16
