@@ -185,6 +185,80 @@ def prefill_bench(args, fabric, cfg, n_layers):
     return 0
 
 
+def concurrent_bench(args, fabric, cfg, n_layers):
+    """Concurrent greedy decode: C requests, one row each per step, all in one pass (paged KV, one slot per request).
+    Prompts share their first half (the shared-prefix workload); this build recomputes the shared half per request."""
+    import torch
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    from ds41rt_b200.runtime.session import DecodeSession
+    world, rank, dev = fabric.world, fabric.rank, fabric.device
+    C, P = args.concurrency, args.prompt
+    W, K = max(args.warmup, 3), args.steps
+    new_tokens = 2 * (W + K) + 8
+    t0 = time.time()
+    weights = EngineWeights.random(cfg, rank, world, dev, seed=0, expert_dtype=args.expert_dtype)
+    eng = DS41Engine(cfg, weights, fabric, max_rows=max(C, args.chunk), slots=C,
+                     max_ctx=(P + new_tokens + 127) // 64 * 64, kv_dtype=args.kv_dtype)
+    g = torch.Generator().manual_seed(1234)
+    shared = torch.randint(3, cfg.vocab - 600, (P // 2,), generator=g).tolist()
+    first = []
+    for s in range(C):
+        own = torch.randint(3, cfg.vocab - 600, (P - P // 2,), generator=g).tolist()
+        first.append(eng.prefill(s, shared + own, chunk=args.chunk))
+    eng.check_status("prefill")
+    setup_s = time.time() - t0
+    sess = DecodeSession(eng, use_graphs=not args.no_graph)
+    eng.set_rows(first, [P] * C, list(range(C)))
+    sess.run_device_loop(C, W)
+    sampler = ClockSampler(dev.index or 0)
+    if rank == 0:
+        sampler.start()
+    ms = timed(fabric, torch, lambda: sess.run_device_loop(C, K))
+    clocks = sampler.stop() if rank == 0 else {}
+    eng.check_status("timed decode")
+    per_pass = sess.launches_per_graph.get((C, True), 0) if not args.no_graph else 0
+    # end to end: inputs from pinned host memory and the chosen tokens back to the host, every step
+    toks = eng.in_tokens[:C].tolist()
+    pos = eng.row_pos[:C].tolist()
+    slots = list(range(C))
+    for _ in range(3):
+        toks = sess.step(toks, pos, slots)
+        pos = [p + 1 for p in pos]
+    sess.h2d_bytes = sess.d2h_bytes = 0
+    fabric.barrier()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    for _ in range(K):
+        toks = sess.step(toks, pos, slots)
+        pos = [p + 1 for p in pos]
+    torch.cuda.synchronize()
+    e2e_s = fabric.all_reduce_max(time.perf_counter() - t1)
+    eng.check_status("e2e decode")
+    if rank == 0:
+        value = C * K / (ms / 1e3)
+        line = {
+            "metric": f"decode tok/s C{C} (greedy, target-only)", "value": round(value, 1), "unit": "tok/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 dense / fp8-e4m3 experts (fp32 accumulate)", "data": "synthetic",
+            "config": {"model": f"DeepSeek-V4.1-Flash-shaped ({cfg.name})", "layers": n_layers, "layers_full_model": 40,
+                       "global_batch": C, "seq_len": P, "prompt_tokens": P, "parallelism": f"tp{world}+ep{world}",
+                       "tokens_per_step": C, "kv_cache": f"paged, 64-token pages, {args.kv_dtype} rows",
+                       "shared_prefix": "first half of every prompt identical; recomputed per request",
+                       "experts": args.expert_dtype,
+                       "l2": "no flush: every step streams more weight bytes than the 126 MB L2",
+                       "weights_gb_per_gpu": round(weights.nbytes() / 1e9, 2),
+                       "kv_gb_per_gpu": round(eng.cache.nbytes() / 1e9, 3), "setup_s": round(setup_s, 1)},
+            "clocks": clocks,
+            "e2e": {"value": round(C * K / e2e_s, 1), "unit": "tok/s", "steps": K,
+                    "h2d_bytes_per_step": sess.h2d_bytes // max(K, 1), "d2h_bytes_per_step": sess.d2h_bytes // max(K, 1)},
+            "gpu_launches": per_pass * K, "impl": "ours",
+        }
+        print(json.dumps(line))
+    fabric.barrier()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -204,6 +278,8 @@ def main():
     ap.add_argument("--mode", default="decode", choices=["decode", "prefill"],
                     help="prefill: time whole-prompt passes in --chunk-row chunks (tok/s of prompt tokens)")
     ap.add_argument("--chunk", type=int, default=1024, help="rows per pass in --mode prefill")
+    ap.add_argument("--concurrency", type=int, default=1, help="decode: number of concurrent requests (greedy, no drafter)")
+    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8"], help="latent KV rows in the cache")
     ap.add_argument("--breakdown", action="store_true", help="prefill: per-kernel device time of one prompt (stderr)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -235,6 +311,8 @@ def main():
         n_layers = cfg.n_layers
     if args.mode == "prefill":
         return prefill_bench(args, fabric, cfg, n_layers)
+    if args.concurrency > 1:
+        return concurrent_bench(args, fabric, cfg, n_layers)
     spec = not args.no_spec
     if spec:
         cfg.dspark = dataclasses.replace(cfg.dspark, stages=args.draft_stages)
@@ -247,7 +325,8 @@ def main():
 
     t0 = time.time()
     weights = EngineWeights.random(cfg, rank, world, dev, seed=0, expert_dtype=args.expert_dtype)
-    eng = DS41Engine(cfg, weights, fabric, max_rows=max(args.prefill_chunk, width), slots=1, max_ctx=max_ctx)
+    eng = DS41Engine(cfg, weights, fabric, max_rows=max(args.prefill_chunk, width), slots=1, max_ctx=max_ctx,
+                     kv_dtype=args.kv_dtype)
     g = torch.Generator().manual_seed(1234)
     prompt = torch.randint(3, cfg.vocab - 600, (args.prompt,), generator=g).tolist()
     assert eng.cache.ensure(0, max_ctx)
