@@ -252,6 +252,13 @@ typedef struct {
 int ds41_sample_rows(const float* logits, long long ld, int rows, int vocab, const uint32_t* masks, int mask_words,
                      const ds41_sample_row* params, int* tokens, int* status, void* stream);
 
+// ---------------------------------------------------------------------------------------------------
+// Engram memory (engram.cu): table rows (dim e4m3 values + dim/32 UE8M0 scales, row_bytes apart) -> bf16 [n_rows, dim];
+// gated residual update of the 4 streams from kv = [rows][4 keys + 1 value][H] (bf16); text_mask 0 = pass through.
+int ds41_engram_dequant(const void* rows_q, int row_bytes, int dim, void* out, int n_rows, void* stream);
+int ds41_engram_gate(const void* x, const void* kv, const void* q_w, const void* k_w, const uint8_t* text_mask,
+                     void* out, int rows, int H, float eps, void* stream);
+
 // Prefill-sized activation quantiser (1x128 scales, one warp per row); rows >= *rows_dev (if given) are skipped.
 int ds41_act_quant_mx_rows(const void* x, long long ldx, void* q, long long ldq, void* sf, int rows, int K,
                            const int* rows_dev, void* stream);
