@@ -259,6 +259,24 @@ int ds41_engram_dequant(const void* rows_q, int row_bytes, int dim, void* out, i
 int ds41_engram_gate(const void* x, const void* kv, const void* q_w, const void* k_w, const uint8_t* text_mask,
                      void* out, int rows, int H, float eps, void* stream);
 
+// ---------------------------------------------------------------------------------------------------
+// Candidate blocks of the long-context indexer (candidates.cu).
+int ds41_block_max(const float* scores, long long ld, int rows, int n_keys, int block, float* out, void* stream);
+int ds41_expand_blocks(const int* blocks, int rows, int k, int block, const int* limit, int* pos, int* count,
+                       void* stream);
+
+// ---------------------------------------------------------------------------------------------------
+// Vision tower elementwise kernels (vision.cu); all tensors bf16 unless noted.
+int ds41_vis_rmsnorm(const void* x, const void* w, void* out, int rows, int W, float eps, void* stream);
+int ds41_vis_bias_act(const void* x, const void* bias, const void* residual, void* out, long long rows, int cols,
+                      int act, void* stream);
+int ds41_vis_silu_mul(const void* gu, void* out, int rows, int I, void* stream);
+int ds41_vis_rope2d(void* qkv, const int* pos_hw, int rows, int W, int heads, float theta, void* stream);
+int ds41_vis_softmax(const float* s, long long ld, long long rows, int n_valid, float scale, void* p, long long ldp,
+                     int n_pad, void* stream);
+int ds41_vis_merge(const void* x, void* out, int gh, int gw, int m, int W, void* stream);
+int ds41_vis_scatter(const void* src, const int* rows, void* dst, int n, int H, int copies, void* stream);
+
 // Prefill-sized activation quantiser (1x128 scales, one warp per row); rows >= *rows_dev (if given) are skipped.
 int ds41_act_quant_mx_rows(const void* x, long long ldx, void* q, long long ldq, void* sf, int rows, int K,
                            const int* rows_dev, void* stream);
