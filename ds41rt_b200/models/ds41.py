@@ -503,6 +503,7 @@ class DS41Engine:
         self.layer_prefix_plain = False   # drafter blocks use the plain rope
         self.launches = 0
         self.only = None
+        self.image_patch = None   # (image rows, pass-row ids) applied after the embedding lookup of the next pass
         self.timeline = None   # set to a list to record (tag, start event, end event) per launch of eager passes
         if R > self.moe_rows and weights.layers:
             self._make_ep(weights.layers[0])
@@ -624,6 +625,12 @@ class DS41Engine:
             self._cur, self._ccur = 0, 0
             self._run("embed", k.ds41_embed_streams, lib.ptr(self.in_tokens), lib.ptr(self.w.embed), lib.ptr(self.streams),
                                           lib.ptr(self.pre[0]), R, H, cfg.hc_mult, cfg.vocab, st())
+            if self.image_patch is not None:
+                # rows of this pass that stand for image placeholders take the vision tower's output instead of the
+                # placeholder token's embedding: (image_rows [n, H] bf16, row_ids [n] int32, -1 = not in this pass)
+                img_rows, img_ids = self.image_patch
+                self._run("image_rows", k.ds41_vis_scatter, lib.ptr(img_rows), lib.ptr(img_ids), lib.ptr(self.streams),
+                          img_rows.shape[0], H, cfg.hc_mult, st())
         pending = None
         fused = R <= self.fused_rows
         tap_i = 0

@@ -32,3 +32,29 @@ def test_vision_tower_matches_reference(grid, layers, tile):
     tower.scatter(tower.out[: got.shape[0]], ids, streams)
     torch.cuda.synchronize()
     assert torch.equal(streams[3, 2].cpu(), tower.out[0].cpu()) and float(streams[4].abs().sum()) == 0.0
+
+
+def test_image_rows_replace_placeholder_embeddings():
+    """Placeholder rows of a pass get the tower's rows: the logits of those positions change, other rows do not when
+    the image rows equal the placeholder's own embedding."""
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    cfg = ModelConfig.tiny()
+    dev = torch.device("cuda")
+    eng = DS41Engine(cfg, EngineWeights.random(cfg, 0, 1, dev, seed=0), max_rows=8, slots=1, max_ctx=128)
+    eng.cache.ensure(0, 64)
+    toks = [5, 9, 9, 9, 7, 8]
+    def run(patch):
+        eng.image_patch = patch
+        eng.set_rows(toks, list(range(len(toks))), [0] * len(toks))
+        eng.forward_rows(len(toks))
+        eng.image_patch = None
+        return eng.logits_rows(len(toks)).clone()
+    base = run(None)
+    same_rows = eng.w.embed[9].view(1, -1).repeat(3, 1).contiguous()
+    ids = torch.tensor([1, 2, 3], dtype=torch.int32, device=dev)
+    assert torch.equal(run((same_rows, ids)), base)
+    other = (torch.randn(3, cfg.hidden, device=dev) * 0.02).bfloat16()
+    changed = run((other, ids))
+    assert not torch.equal(changed[1:4], base[1:4]) and torch.equal(changed[0], base[0])
+    eng.check_status()
