@@ -1,7 +1,8 @@
 """Command line: `python -m ds41rt_b200 <command>`.
 
   build                      compile the kernel and host-runtime libraries in-tree
-  serve  [--model ...]       OpenAI-compatible HTTP server over the native engine on this GPU
+  serve  [--model ...]       OpenAI-compatible HTTP server over the native engine; under torch.distributed.run rank 0
+                             serves and the other ranks mirror its engine calls (tensor + expert parallel)
   info                       print the model configuration and the per-rank memory plan
 
 The reference's counterparts are its run.sh / build.sh launchers and the `v41-native-serve` daemon command
@@ -11,6 +12,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 import time
 
@@ -53,20 +55,30 @@ def cmd_serve(args) -> int:
     if not torch.cuda.is_available():
         print("serve needs a CUDA device", file=sys.stderr)
         return 2
+    from .parallel.fabric import Fabric
+    from .serving.distributed import LeaderEngine, follower_loop, make_control_group
     cfg = _config(args)
-    dev = torch.device("cuda", args.device)
+    fabric = Fabric.create() if "WORLD_SIZE" in os.environ else Fabric.single(torch.device("cuda", args.device))
+    rank, world, dev = fabric.rank, fabric.world, fabric.device
+    ctl = make_control_group(fabric)
     tk = HFTokenizer(args.tokenizer) if args.tokenizer else ByteTokenizer(vocab_size=cfg.vocab)
     t0 = time.time()
     if args.checkpoint:
         from .loader.official import load_engine_weights
-        weights = load_engine_weights(args.checkpoint, cfg, 0, 1, dev)
+        weights = load_engine_weights(args.checkpoint, cfg, rank, world, dev, expert_dtype=args.expert_dtype)
     else:
-        weights = EngineWeights.random(cfg, 0, 1, dev, seed=args.seed, expert_dtype=args.expert_dtype)
-    eng = DS41Engine(cfg, weights, max_rows=max(8, args.concurrency), slots=args.concurrency, max_ctx=args.max_context)
-    backend = NativeBackend(eng, eos=tk.eos, concurrency=args.concurrency, queue_depth=args.queue_depth)
+        weights = EngineWeights.random(cfg, rank, world, dev, seed=args.seed, expert_dtype=args.expert_dtype)
+    eng = DS41Engine(cfg, weights, fabric, max_rows=max(8, args.concurrency), slots=args.concurrency,
+                     max_ctx=args.max_context, kv_dtype=args.kv_dtype)
+    if rank != 0:
+        # every other rank mirrors the leader's engine calls until it is told to stop
+        follower_loop(eng, ctl, on_error=lambda e: print(f"rank {rank}: {e}", file=sys.stderr, flush=True))
+        return 0
+    lead = LeaderEngine(eng, ctl)
+    backend = NativeBackend(lead, eos=tk.eos, concurrency=args.concurrency, queue_depth=args.queue_depth)
     srv = ApiServer(backend, tk, host=args.host, port=args.port, queue_depth=args.queue_depth, waiters=args.waiters,
                     max_context=args.max_context).start()
-    print(json.dumps({"listening": f"http://{args.host}:{srv.port}", "model": cfg.name,
+    print(json.dumps({"listening": f"http://{args.host}:{srv.port}", "model": cfg.name, "ranks": world,
                       "setup_s": round(time.time() - t0, 1)}), flush=True)
     try:
         while True:
@@ -76,6 +88,7 @@ def cmd_serve(args) -> int:
     finally:
         srv.stop()
         backend.close()
+        lead.stop_followers()
     return 0
 
 
@@ -95,7 +108,7 @@ def main(argv=None) -> int:
     model_args(ps)
     ps.add_argument("--checkpoint", default="", help="directory with model.safetensors.index.json (official layout)")
     ps.add_argument("--tokenizer", default="", help="tokenizer.json; default: byte-level tokenizer")
-    ps.add_argument("--expert-dtype", default="mxfp8", choices=["mxfp8", "bf16"])
+    ps.add_argument("--expert-dtype", default="mxfp8", choices=["mxfp8", "mxfp4", "bf16"])
     ps.add_argument("--host", default="127.0.0.1")
     ps.add_argument("--port", type=int, default=8000)
     ps.add_argument("--device", type=int, default=0)
@@ -104,6 +117,7 @@ def main(argv=None) -> int:
     ps.add_argument("--waiters", type=int, default=16)
     ps.add_argument("--max-context", type=int, default=8192)
     ps.add_argument("--seed", type=int, default=0)
+    ps.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8"])
     args = ap.parse_args(argv)
     return {"build": cmd_build, "info": cmd_info, "serve": cmd_serve}[args.cmd](args)
 

@@ -1,0 +1,103 @@
+"""Serving on several GPUs: rank 0 owns the HTTP server and the scheduler, the other ranks mirror its engine calls.
+
+Every rank holds its shard of the model and runs the same launch sequence (the kernels meet in peer memory), so the
+only thing the followers need is the sequence of engine calls with their host-side arguments.  `LeaderEngine` wraps the
+rank-0 engine: each call that launches work (or changes the page tables) is first broadcast as a small message over a
+CPU process group, then executed locally; `follower_loop` executes the same calls on the other ranks until it is told
+to stop.  Collectives inside those calls (e.g. the vocabulary-shard gather of `logits_rows`) therefore line up.
+
+The reference's counterpart is its coordinator / expert-worker split over TCP and RoCE
+(rust/crates/ds41rt-daemon/src/v41_experts/coordinator.rs, service.rs:12-44); here all ranks are peers of one program.
+"""
+from __future__ import annotations
+
+from typing import Any, List, Optional, Tuple
+
+
+def make_control_group(fabric):
+    """A gloo group over the same ranks for host-side control messages (None on one rank)."""
+    if fabric.world == 1:
+        return None
+    import torch.distributed as dist
+    return dist.new_group(backend="gloo")
+
+
+def _bcast(group, obj: Any, src: int = 0) -> Any:
+    import torch.distributed as dist
+    box = [obj]
+    dist.broadcast_object_list(box, src=src, group=group)
+    return box[0]
+
+
+class _CacheMirror:
+    def __init__(self, leader: "LeaderEngine"):
+        self._l = leader
+
+    def __getattr__(self, name):
+        return getattr(self._l.eng.cache, name)
+
+    def ensure(self, slot: int, n_tokens: int) -> bool:
+        self._l._send(("ensure", slot, n_tokens))
+        return self._l.eng.cache.ensure(slot, n_tokens)
+
+    def release(self, slot: int) -> None:
+        self._l._send(("release", slot))
+        self._l.eng.cache.release(slot)
+
+
+class LeaderEngine:
+    """Drop-in for DS41Engine on rank 0 (the subset the serving backend uses)."""
+
+    def __init__(self, engine, group):
+        self.eng, self.group = engine, group
+        self.cache = _CacheMirror(self)
+
+    def __getattr__(self, name):
+        return getattr(self.eng, name)
+
+    def _send(self, msg: Tuple) -> None:
+        if self.group is not None:
+            _bcast(self.group, msg)
+
+    def set_rows(self, tokens: List[int], positions: List[int], slots: List[int]) -> None:
+        self._send(("set_rows", list(tokens), list(positions), list(slots)))
+        self.eng.set_rows(tokens, positions, slots)
+
+    def forward_rows(self, rows: int, **kw) -> None:
+        self._send(("forward", rows, kw))
+        self.eng.forward_rows(rows, **kw)
+
+    def logits_rows(self, rows: int):
+        self._send(("logits", rows))
+        return self.eng.logits_rows(rows)
+
+    def check_status(self, what: str = "engine pass") -> None:
+        self.eng.check_status(what)
+
+    def stop_followers(self) -> None:
+        self._send(("stop",))
+
+
+def follower_loop(engine, group, on_error=None) -> int:
+    """Run on ranks > 0 until the leader says stop; returns the number of passes executed."""
+    passes = 0
+    while True:
+        msg = _bcast(group, None)
+        op = msg[0]
+        if op == "stop":
+            return passes
+        try:
+            if op == "set_rows":
+                engine.set_rows(msg[1], msg[2], msg[3])
+            elif op == "forward":
+                engine.forward_rows(msg[1], **msg[2])
+                passes += 1
+            elif op == "logits":
+                engine.logits_rows(msg[1])
+            elif op == "ensure":
+                engine.cache.ensure(msg[1], msg[2])
+            elif op == "release":
+                engine.cache.release(msg[1])
+        except Exception as e:          # keep the launch sequences aligned; the leader sees the status word / timeout
+            if on_error is not None:
+                on_error(e)

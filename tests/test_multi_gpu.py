@@ -59,3 +59,16 @@ def test_grouped_experts_one_rank(mx):
 @pytest.mark.parametrize("mx", ["0", "1"])
 def test_expert_parallel_dispatch_gemm_combine(mx):
     _run_ep(2, 29521, EP_TOKENS="384", EP_H="512", EP_I="256", EP_E="8", EP_TOPK="4", EP_REPS="2", EP_MX=mx)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_serving_backend_with_mirrored_ranks():
+    """Rank 0 schedules and samples; rank 1 mirrors every engine call (set_rows / forward / logits gather / pages)."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29523", os.path.join(here, "multi", "serve_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    sys.stdout.write(r.stdout[-3000:])
+    sys.stderr.write(r.stderr[-3000:])
+    assert r.returncode == 0 and "SERVE_WORKER_OK" in r.stdout
