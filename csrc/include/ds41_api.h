@@ -75,6 +75,9 @@ typedef struct ds41_gemm_args {
   // kind 2 only: 1 = A holds e2m1 (FP4) values, two per byte in memory (even element in the low nibble), with UE8M0
   // scales per 32 elements; lda / a_batch_stride then count elements.  B stays e4m3.
   int a_format;
+  // out_mode 8 (indexer scores): M rows are (query, head) pairs with 32 heads per query; out is fp32 [M/32, ldo];
+  // row_w[query * row_w_ld + head] weights relu(acc); columns >= col_limit[query] (if given) are written as -inf.
+  const int* col_limit;
 } ds41_gemm_args;
 
 int ds41_gemm_tc(const ds41_gemm_args* args, void* stream);
@@ -148,6 +151,12 @@ int ds41_index_score(const void* q, long long ldq, int q_off, const float* w, in
                      const void* idx_pool, const int* page_table, int max_pages, int page_rows, const int* row_pos,
                      const int* row_slot, const float* inv_freq_idx, int rows, int IH, int ID, int ratio,
                      float* scores, int max_keys, void* stream);
+// Operands of the tensor-core indexer (one request per pass): RoPE'd queries [rows*IH, ID], the request's keys gathered
+// into [n_keys, ID], visible keys per row.  The scores then come from ds41_gemm_tc with out_mode 8.
+int ds41_index_prepare(const void* q, long long ldq, int q_off, const void* idx_pool, const int* page_table,
+                       int max_pages, int page_rows, const int* row_pos, const int* row_slot,
+                       const float* inv_freq_idx, int rows, int IH, int ID, int ratio, int n_keys, int max_keys,
+                       void* qr, void* kc, int* n_vis, void* stream);
 int ds41_topk_select(const float* scores, int max_keys, const int* row_pos, const int* row_slot, int ratio, int k,
                      int* sel, int* n_sel, int rows, void* stream);
 int ds41_attend(const void* q, long long ldq, int q_off, int rows, int heads, int D, int window, int ring,

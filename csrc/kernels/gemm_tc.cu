@@ -35,7 +35,9 @@ struct GemmParams {
   int k_splits;
   int out_mode;           // 0 bf16 [m,n]; 1 f32 [m,n]; 2 bf16 [n,m]; 3 f32 [n,m];
                           // 4 (DUAL) bf16 [n,m] = swiglu(gate,up)*row_w; 5 f32 [n,m] where row_w != 0;
-                          // 6 bf16 [m,n] staged in shared memory and written by TMA stores; 7 scatter rows
+                          // 6 bf16 [m,n] staged in shared memory and written by TMA stores; 7 scatter rows;
+                          // 8 indexer scores: rows of M are (query, head) pairs, 32 heads per query; out[query][n] =
+                          //   sum_head relu(acc) * row_w[query][head], -inf at n >= col_limit[query]
   long long ldo;          // leading dimension of the output in elements
   long long out_batch_stride;
   long long out_split_stride;
@@ -67,6 +69,7 @@ struct GemmParams {
   // mode 7: scatter rows to their source ranks (expert-parallel combine): meta[n] = {source rank, slot}
   const int2* scatter_meta;
   void* scatter_out[8];
+  const int* col_limit;   // mode 8: visible keys per query row
   // fused collectives over peer memory (normal orientation: A = activations, rows sharded by rank)
   // all-gather -> GEMM (push model): A is this rank's copy of the gathered matrix; rows [r*ag_rows, (r+1)*ag_rows)
   // belong to rank r.  The copier warps push this rank's rows into every peer's copy (ag_bufs[d]) in
@@ -536,6 +539,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               ++st_pair;
             }
           }
+        } else if (p.out_mode == 8) {
+          // One epilogue warp = the 32 heads of one query row.  relu x head weight, then a butterfly that leaves the
+          // sum over heads of column l on lane l (31 shuffles for 32 columns), then one coalesced row store.
+          if constexpr (kChunk == 32) {
+            const int qrow = m >> 5;
+            const float wgt = m < p.M ? __ldg(p.row_w + 1ll * qrow * p.row_w_ld + lane) : 0.f;
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = fmaxf(__uint_as_float(v[j]), 0.f) * wgt;
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) {
+              const bool upper = (lane & off) != 0;
+#pragma unroll
+              for (int i = 0; i < off; ++i) {
+                const float send = upper ? f[i] : f[i + off];
+                const float keep = upper ? f[i + off] : f[i];
+                f[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+              }
+            }
+            if (m < p.M && n0 + lane < n_lim) {
+              const int lim = p.col_limit != nullptr ? __ldg(p.col_limit + qrow) : n_lim;
+              reinterpret_cast<float*>(p.out)[obase + 1ll * qrow * p.ldo + n0 + lane] = n0 + lane < lim ? f[0] : -INFINITY;
+            }
+          }
         } else if (p.out_mode == 7) {
           // expert-parallel combine: column n is a received token row; its result row goes back to the rank it
           // came from, into that rank's combine buffer at the (token, route) slot - P2P stores from the epilogue.
@@ -699,7 +726,7 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   const int M = a->M, N = a->N, K = a->K, batch = a->batch, kind = a->kind, out_mode = a->out_mode;
   const int k_splits = a->k_splits, bn = a->bn;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0 || k_splits <= 0 || kind < 0 || kind > 2 || out_mode < 0 ||
-      out_mode > 7)
+      out_mode > 8)
     return cudaErrorInvalidValue;
   const int elem = kind == 0 ? 2 : 1;
   const int bk = kTileKBytes / elem;
@@ -708,7 +735,8 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   if (kind == 2 && (K % 128 != 0 || a->sfa == nullptr || a->sfb == nullptr)) return cudaErrorInvalidValue;
   if (kind == 2 && bn < 32 && N > bn) return cudaErrorInvalidValue;      // 16-row scale tiles cannot be lane-shifted
   if (k_splits > 1 && out_mode != 1 && out_mode != 3) return cudaErrorInvalidValue;   // partials are fp32
-  if ((out_mode == 4 || out_mode == 5) && a->row_w == nullptr) return cudaErrorInvalidValue;
+  if ((out_mode == 4 || out_mode == 5 || out_mode == 8) && a->row_w == nullptr) return cudaErrorInvalidValue;
+  if (out_mode == 8 && (bn < 32 || (M & 31) != 0 || k_splits != 1)) return cudaErrorInvalidValue;
   if (out_mode == 7 && (a->scatter_meta == nullptr || a->tile_group == nullptr || (a->ldo & 7) != 0))
     return cudaErrorInvalidValue;
   if (a->tile_group != nullptr && (a->tile_row0 == nullptr || a->tile_end == nullptr || a->n_tiles_dev == nullptr ||
@@ -800,6 +828,7 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   p.wait_epoch = reinterpret_cast<const uint32_t*>(a->wait_epoch);
   p.wait_world = a->wait_world;
   p.scatter_meta = reinterpret_cast<const int2*>(a->scatter_meta);
+  p.col_limit = a->col_limit;
   for (int r = 0; r < 8; ++r) p.scatter_out[r] = a->scatter_out[r];
   p.static_operand = a->static_operand;
   p.a_fp4 = a_fp4 ? 1 : 0;

@@ -97,6 +97,50 @@ __global__ void __launch_bounds__(256) index_score_kernel(IndexScoreParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------- index score on tensor cores
+// Long passes over one request: the scores are a GEMM [rows*IH, ID] x [keys, ID]^T whose epilogue applies relu, the head
+// weights and the sum over heads (gemm_tc.cu out_mode 8).  This kernel lays out its operands: blocks [0, rows) write the
+// RoPE'd, bf16-rounded queries and the number of visible keys per row; the remaining blocks copy the request's index
+// keys from the paged pool into one contiguous matrix (8 keys per block, zero rows where a page is missing).
+__global__ void __launch_bounds__(256) index_prepare_kernel(IndexScoreParams p, int n_keys, __nv_bfloat16* qr,
+                                                            __nv_bfloat16* kc, int* n_vis) {
+  const int tid = threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (static_cast<int>(blockIdx.x) < p.rows) {
+    const int r = blockIdx.x;
+    const int pos = p.row_pos[r], slot = p.row_slot[r];
+    if (tid == 0) n_vis[r] = slot < 0 ? 0 : min(min((pos + 1) / p.ratio, p.max_keys), n_keys);
+    const int rope0 = p.ID - p.ID / 2;
+    for (int idx = tid; idx < p.IH * p.ID / 2; idx += 256) {
+      const int h = idx / (p.ID / 2), i = idx % (p.ID / 2);
+      const float2 v = __bfloat1622float2(
+          *reinterpret_cast<const __nv_bfloat162*>(p.q + 1ll * r * p.ldq + p.q_off + h * p.ID + 2 * i));
+      float a = v.x, b = v.y;
+      const int t = 2 * i - rope0;
+      if (t >= 0) {
+        float c, s;
+        rope_cs2(pos, p.inv_freq_idx[t / 2], &c, &s);
+        const float ra = a * c - b * s, rb = b * c + a * s;
+        a = ra;
+        b = rb;
+      }
+      *reinterpret_cast<__nv_bfloat162*>(qr + (1ll * r * p.IH + h) * p.ID + 2 * i) = __floats2bfloat162_rn(a, b);
+    }
+    return;
+  }
+  const int slot = p.row_slot[0];
+  const int vec = p.ID / 8;
+  for (int idx = tid; idx < 8 * vec; idx += 256) {
+    const int c = (blockIdx.x - p.rows) * 8 + idx / vec, v = idx % vec;
+    if (c >= n_keys) continue;
+    const long long phys = slot < 0 ? -1 : pool_row(p.page_table, p.max_pages, p.page_rows, slot, c);
+    uint4 w = make_uint4(0, 0, 0, 0);
+    if (phys >= 0) w = *reinterpret_cast<const uint4*>(p.idx_pool + phys * p.ID + v * 8);
+    *reinterpret_cast<uint4*>(kc + 1ll * c * p.ID + v * 8) = w;
+  }
+}
+
 // ---------------------------------------------------------------------------------------- top-k
 __device__ __forceinline__ uint32_t orderable(float f) {
   const uint32_t u = __float_as_uint(f);
@@ -600,6 +644,19 @@ extern "C" int ds41_index_score(const void* q, long long ldq, int q_off, const f
   int bx = (max_keys + 7) / 8;
   if (bx > 256) bx = 256;
   return launch_pdl(index_score_kernel, dim3(bx, rows), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
+}
+
+extern "C" int ds41_index_prepare(const void* q, long long ldq, int q_off, const void* idx_pool, const int* page_table,
+                                  int max_pages, int page_rows, const int* row_pos, const int* row_slot,
+                                  const float* inv_freq_idx, int rows, int IH, int ID, int ratio, int n_keys,
+                                  int max_keys, void* qr, void* kc, int* n_vis, void* stream) {
+  if (rows <= 0 || n_keys <= 0 || IH <= 0 || ID <= 0 || (ID & 7)) return cudaErrorInvalidValue;
+  IndexScoreParams p{static_cast<const __nv_bfloat16*>(q), ldq, q_off, nullptr, 0, 0,
+                     static_cast<const __nv_bfloat16*>(idx_pool), page_table, max_pages, page_rows, row_pos,
+                     row_slot, inv_freq_idx, rows, IH, ID, ratio, nullptr, max_keys};
+  return launch_pdl(index_prepare_kernel, dim3(rows + (n_keys + 7) / 8), dim3(256), 0,
+                    static_cast<cudaStream_t>(stream), p, n_keys, static_cast<__nv_bfloat16*>(qr),
+                    static_cast<__nv_bfloat16*>(kc), n_vis);
 }
 
 extern "C" int ds41_topk_select(const float* scores, int max_keys, const int* row_pos, const int* row_slot,

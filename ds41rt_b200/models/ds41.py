@@ -443,6 +443,10 @@ class DS41Engine:
         self.qb_out = z((R, self.nqb), BF16)
         self.max_keys = max_ctx
         self.scores = z((R, self.max_keys), F32)
+        if R > self.moe_rows and cfg.index_layers:
+            self.idx_q = z((R * cfg.index_heads, cfg.index_dim), BF16)      # RoPE'd index queries, (row, head) major
+            self.idx_k = z((self.max_keys, cfg.index_dim), BF16)            # one request's index keys, contiguous
+            self.idx_vis = z((R,), I32)
         self.sel = z((R, cfg.index_topk), I32)
         self.n_sel = z((R,), I32)
         self.n_splits_attn = (cfg.window + 16 + cfg.index_topk + 63) // 64
@@ -503,6 +507,7 @@ class DS41Engine:
         self.layer_prefix_plain = False   # drafter blocks use the plain rope
         self.launches = 0
         self.only = None
+        self._pass_hint = None    # (rows, highest position) of a single-request pass described by the last set_rows
         self.image_patch = None   # (image rows, pass-row ids) applied after the embedding lookup of the next pass
         self.timeline = None   # set to a list to record (tag, start event, end event) per launch of eager passes
         if R > self.moe_rows and weights.layers:
@@ -554,6 +559,11 @@ class DS41Engine:
         self.in_tokens.copy_(t, non_blocking=True)
         self.row_pos.copy_(p, non_blocking=True)
         self.row_slot.copy_(s, non_blocking=True)
+        # what the host knows about the pass it just described (used by the next forward_rows only): a long pass over
+        # one request lets the indexer run as a tensor-core GEMM over that request's keys
+        slot_list = list(slots)
+        one = n > self.moe_rows and len(set(slot_list)) == 1 and slot_list[0] >= 0
+        self._pass_hint = (n, int(max(positions)) if n else 0) if one else None
         if self.row_hi is not None:
             h = torch.tensor(list(row_hi if row_hi is not None else positions) + [0] * pad, dtype=I32)
             self.row_hi.copy_(h, non_blocking=True)
@@ -667,12 +677,26 @@ class DS41Engine:
                        status=self.status, static_operand=1)
             if lw.index_heads_cols and src is not None:
                 ratio = cfg.source_layers[src]
-                self._run("index_score", k.ds41_index_score, 
-                    lib.ptr(self.qb_out), C.c_longlong(self.nqb), self.HL * D, lib.ptr(self.extras), lw.extra_cols,
-                    lw.extra_cols - cfg.index_heads, lib.ptr(self.cache.idx[src]), lib.ptr(self.cache.page_table),
-                    self.cache.max_pages, self.cache.page_rows[src], lib.ptr(self.row_pos), lib.ptr(self.row_slot),
-                    lib.ptr(self.inv_idx), R, cfg.index_heads, cfg.index_dim, ratio, lib.ptr(self.scores),
-                    self.max_keys, st())
+                hint = self._pass_hint
+                n_keys = min((hint[1] + 1) // ratio, self.max_keys) if hint is not None and hint[0] == R else 0
+                if n_keys >= 64 and cfg.index_heads == 32 and cfg.index_dim % 64 == 0:
+                    self._run("index_prepare", k.ds41_index_prepare, lib.ptr(self.qb_out), C.c_longlong(self.nqb),
+                              self.HL * D, lib.ptr(self.cache.idx[src]), lib.ptr(self.cache.page_table),
+                              self.cache.max_pages, self.cache.page_rows[src], lib.ptr(self.row_pos),
+                              lib.ptr(self.row_slot), lib.ptr(self.inv_idx), R, cfg.index_heads, cfg.index_dim, ratio,
+                              n_keys, self.max_keys, lib.ptr(self.idx_q), lib.ptr(self.idx_k), lib.ptr(self.idx_vis), st())
+                    w_off = lw.extra_cols - cfg.index_heads
+                    self._run("index_score_gemm", G.gemm_raw, self.idx_q, self.idx_k, self.scores, R * cfg.index_heads,
+                              n_keys, cfg.index_dim, lda=cfg.index_dim, ldb=cfg.index_dim, ldo=self.max_keys, out_mode=8,
+                              bn=256 if n_keys >= 256 else 64, row_w=self.extras[:, w_off:], row_w_ld=lw.extra_cols,
+                              col_limit=self.idx_vis, status=self.status)
+                else:
+                    self._run("index_score", k.ds41_index_score,
+                        lib.ptr(self.qb_out), C.c_longlong(self.nqb), self.HL * D, lib.ptr(self.extras), lw.extra_cols,
+                        lw.extra_cols - cfg.index_heads, lib.ptr(self.cache.idx[src]), lib.ptr(self.cache.page_table),
+                        self.cache.max_pages, self.cache.page_rows[src], lib.ptr(self.row_pos), lib.ptr(self.row_slot),
+                        lib.ptr(self.inv_idx), R, cfg.index_heads, cfg.index_dim, ratio, lib.ptr(self.scores),
+                        self.max_keys, st())
                 self._run("topk", k.ds41_topk_select, lib.ptr(self.scores), self.max_keys, lib.ptr(self.row_pos),
                                             lib.ptr(self.row_slot), ratio, cfg.index_topk, lib.ptr(self.sel),
                                             lib.ptr(self.n_sel), R, st())
@@ -756,6 +780,7 @@ class DS41Engine:
             self._signal()
             pending = (self._moe_bases, self.world, 1, 0)
         self._pending = pending
+        self._pass_hint = None
         if head:
             self.head_rows(R)
 

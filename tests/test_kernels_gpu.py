@@ -311,3 +311,46 @@ def test_candidate_blocks():
     ref = torch.where(ref >= limit[:, None], torch.full_like(ref, -1), ref)
     assert torch.equal(pos.long(), ref)
     assert torch.equal(count.long(), (ref >= 0).sum(1))
+
+
+def test_index_scores_on_tensor_cores_match_the_scalar_kernel():
+    """One request, a long pass: RoPE'd queries x gathered keys as a GEMM with the relu / head-weight / head-sum
+    epilogue gives the scores of the per-key kernel (same bf16 operands, fp32 accumulation)."""
+    from ds41rt_b200.config import RopeConfig, rope_inv_freq
+    from ds41rt_b200.ops import gemm as G, lib
+    k = lib.kernels()
+    torch.manual_seed(7)
+    rows, IH, ID, ratio, page_rows, max_pages, max_keys = 200, 32, 128, 2, 32, 80, 2560
+    pos0 = 3000
+    positions = torch.arange(pos0, pos0 + rows, dtype=torch.int32, device="cuda")
+    slots = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    ldq = IH * ID + 64
+    q = torch.randn(rows, ldq, device="cuda").bfloat16()
+    w_stride, w_off = 40, 8
+    w = torch.randn(rows, w_stride, device="cuda")
+    pool = torch.randn(max_pages * page_rows, ID, device="cuda").bfloat16()
+    page_table = torch.randperm(max_pages, device="cuda").int().view(1, max_pages).contiguous()
+    inv = torch.tensor(rope_inv_freq(RopeConfig(), ID // 2), device="cuda")
+    ref = torch.full((rows, max_keys), float("nan"), device="cuda")
+    lib.check(k.ds41_index_score(lib.ptr(q), C.c_longlong(ldq), 64, lib.ptr(w), w_stride, w_off, lib.ptr(pool),
+                                 lib.ptr(page_table), max_pages, page_rows, lib.ptr(positions), lib.ptr(slots),
+                                 lib.ptr(inv), rows, IH, ID, ratio, lib.ptr(ref), max_keys, lib.stream()), "score")
+    n_keys = (pos0 + rows) // ratio
+    qr = torch.zeros(rows * IH, ID, device="cuda", dtype=torch.bfloat16)
+    kc = torch.zeros(max_keys, ID, device="cuda", dtype=torch.bfloat16)
+    vis = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    got = torch.full((rows, max_keys), float("nan"), device="cuda")
+    st = lib.new_status("cuda")
+    lib.check(k.ds41_index_prepare(lib.ptr(q), C.c_longlong(ldq), 64, lib.ptr(pool), lib.ptr(page_table), max_pages,
+                                   page_rows, lib.ptr(positions), lib.ptr(slots), lib.ptr(inv), rows, IH, ID, ratio,
+                                   n_keys, max_keys, lib.ptr(qr), lib.ptr(kc), lib.ptr(vis), lib.stream()), "prepare")
+    G.gemm_raw(qr, kc, got, rows * IH, n_keys, ID, lda=ID, ldb=ID, ldo=max_keys, out_mode=8, bn=256,
+               row_w=w[:, w_off:], row_w_ld=w_stride, col_limit=vis, status=st)
+    torch.cuda.synchronize()
+    lib.raise_on_status(st, "index gemm")
+    for r in (0, 57, rows - 1):
+        nv = (pos0 + r + 1) // ratio
+        assert int(vis[r]) == nv
+        a, b = got[r, :nv], ref[r, :nv]
+        assert float((a - b).abs().max()) < 2e-3 * float(b.abs().max())
+        assert torch.isinf(got[r, nv:n_keys]).all()
