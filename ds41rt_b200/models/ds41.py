@@ -322,6 +322,25 @@ class EngineWeights:
         return total
 
 
+@dataclass
+class KVSnapshot:
+    """State of one request after `n_tokens` positions: enough to continue it in another slot.
+
+    Full pages of the compressed / index pools are shared by reference (they are never written again); the rows of the
+    last, partly filled page, the window rings of every layer and the ratio-2 pair carry are copied."""
+    n_tokens: int
+    pages: List[int]
+    partial: Dict[int, tuple]
+    rings: torch.Tensor
+    pending: Dict[int, torch.Tensor]
+
+    def nbytes(self) -> int:
+        n = self.rings.numel() * self.rings.element_size()
+        for a, b in self.partial.values():
+            n += a.numel() * a.element_size() + b.numel() * b.element_size()
+        return n + sum(t.numel() * t.element_size() for t in self.pending.values())
+
+
 class KVCache:
     """Window rings, paged compressed pools and the page table for `slots` concurrent requests.
 
@@ -359,6 +378,7 @@ class KVCache:
         self.page_table_host = torch.full((slots, self.max_pages), -1, dtype=I32)
         self.page_table = self.page_table_host.to(device)
         self.free_pages = list(range(self.n_pages - 1, -1, -1))
+        self.page_ref = [0] * self.n_pages          # slots and snapshots holding each page
         self.pages_of: Dict[int, List[int]] = {s: [] for s in range(slots)}
 
     def ensure(self, slot: int, n_tokens: int) -> bool:
@@ -371,16 +391,71 @@ class KVCache:
             return False
         for i in range(have, need):
             pg = self.free_pages.pop()
+            self.page_ref[pg] = 1
             self.pages_of[slot].append(pg)
             self.page_table_host[slot, i] = pg
         self.page_table[slot, :need].copy_(self.page_table_host[slot, :need], non_blocking=True)
         return True
 
+    def _unref(self, pages: List[int]):
+        for pg in reversed(pages):
+            self.page_ref[pg] -= 1
+            if self.page_ref[pg] == 0:
+                self.free_pages.append(pg)
+
     def release(self, slot: int):
-        self.free_pages.extend(reversed(self.pages_of[slot]))
+        self._unref(self.pages_of[slot])
         self.pages_of[slot] = []
         self.page_table_host[slot].fill_(-1)
         self.page_table[slot].fill_(-1)
+
+    # ------------------------------------------------------------------ prefix snapshots
+    def snapshot(self, slot: int, n_tokens: int) -> KVSnapshot:
+        """Capture `slot` after positions [0, n_tokens) (call it between passes, on the engine's stream)."""
+        full = n_tokens // self.page_tokens
+        pages = list(self.pages_of[slot][:full])
+        for pg in pages:
+            self.page_ref[pg] += 1
+        partial = {}
+        rem = n_tokens - full * self.page_tokens
+        if rem and full < len(self.pages_of[slot]):
+            pg = self.pages_of[slot][full]
+            for src, pr in self.page_rows.items():
+                rows = (rem * pr + self.page_tokens - 1) // self.page_tokens
+                partial[src] = (self.comp[src][pg * pr: pg * pr + rows].clone(), self.idx[src][pg * pr: pg * pr + rows].clone())
+        return KVSnapshot(n_tokens, pages, partial, self.win[:, slot].clone(),
+                          {src: t[slot].clone() for src, t in self.pending.items()})
+
+    def restore(self, slot: int, snap: KVSnapshot) -> bool:
+        """Continue a snapshot in an empty `slot`: shared full pages, a private copy of the partial page, rings and
+        carry.  Returns False when no page is free for the partial page."""
+        assert not self.pages_of[slot], "restore needs an empty slot"
+        if snap.partial and not self.free_pages:
+            return False
+        for i, pg in enumerate(snap.pages):
+            self.page_ref[pg] += 1
+            self.pages_of[slot].append(pg)
+            self.page_table_host[slot, i] = pg
+        if snap.partial:
+            pg = self.free_pages.pop()
+            self.page_ref[pg] = 1
+            self.pages_of[slot].append(pg)
+            self.page_table_host[slot, len(snap.pages)] = pg
+            for src, (c, ix) in snap.partial.items():
+                pr = self.page_rows[src]
+                self.comp[src][pg * pr: pg * pr + c.shape[0]].copy_(c)
+                self.idx[src][pg * pr: pg * pr + ix.shape[0]].copy_(ix)
+        n = len(self.pages_of[slot])
+        if n:
+            self.page_table[slot, :n].copy_(self.page_table_host[slot, :n], non_blocking=True)
+        self.win[:, slot].copy_(snap.rings)
+        for src, t in snap.pending.items():
+            self.pending[src][slot].copy_(t)
+        return True
+
+    def drop_snapshot(self, snap: KVSnapshot):
+        self._unref(snap.pages)
+        snap.pages = []
 
     def nbytes(self) -> int:
         ts = [self.win] + list(self.comp.values()) + list(self.idx.values()) + list(self.pending.values())

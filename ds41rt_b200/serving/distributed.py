@@ -44,12 +44,28 @@ class _CacheMirror:
         self._l._send(("release", slot))
         self._l.eng.cache.release(slot)
 
+    def snapshot(self, slot: int, n_tokens: int):
+        self._l._sid += 1
+        self._l._send(("snapshot", slot, n_tokens, self._l._sid))
+        snap = self._l.eng.cache.snapshot(slot, n_tokens)
+        snap.sid = self._l._sid
+        return snap
+
+    def restore(self, slot: int, snap) -> bool:
+        self._l._send(("restore", slot, snap.sid))
+        return self._l.eng.cache.restore(slot, snap)
+
+    def drop_snapshot(self, snap) -> None:
+        self._l._send(("drop", snap.sid))
+        self._l.eng.cache.drop_snapshot(snap)
+
 
 class LeaderEngine:
     """Drop-in for DS41Engine on rank 0 (the subset the serving backend uses)."""
 
     def __init__(self, engine, group):
         self.eng, self.group = engine, group
+        self._sid = 0
         self.cache = _CacheMirror(self)
 
     def __getattr__(self, name):
@@ -81,6 +97,7 @@ class LeaderEngine:
 def follower_loop(engine, group, on_error=None) -> int:
     """Run on ranks > 0 until the leader says stop; returns the number of passes executed."""
     passes = 0
+    snaps = {}
     while True:
         msg = _bcast(group, None)
         op = msg[0]
@@ -98,6 +115,12 @@ def follower_loop(engine, group, on_error=None) -> int:
                 engine.cache.ensure(msg[1], msg[2])
             elif op == "release":
                 engine.cache.release(msg[1])
+            elif op == "snapshot":
+                snaps[msg[3]] = engine.cache.snapshot(msg[1], msg[2])
+            elif op == "restore":
+                engine.cache.restore(msg[1], snaps[msg[2]])
+            elif op == "drop":
+                engine.cache.drop_snapshot(snaps.pop(msg[2]))
         except Exception as e:          # keep the launch sequences aligned; the leader sees the status word / timeout
             if on_error is not None:
                 on_error(e)

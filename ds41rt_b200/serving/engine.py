@@ -116,6 +116,7 @@ class _Active:
     last: int                 # last emitted token (next input)
     emitted: int = 0
     lane: int = 0
+    tokens: List[int] = field(default_factory=list)     # emitted token ids
 
 
 class NativeBackend(Backend):
@@ -130,11 +131,15 @@ class NativeBackend(Backend):
         self.kv = K.KvAllocator(engine.cache.n_pages, engine.cache.slots, engine.cache.page_tokens)
         self.lanes = K.Lanes(2)
         self.prefix = K.PrefixBanks(20, 20, engine.cfg.window)
+        # KV snapshots at prompt ends and turn ends, newest last: (token tuple, KVSnapshot, logits after the last token)
+        self.snapshots: List[tuple] = []
+        self.snapshot_capacity = 40
         self.prefill_chunk = prefill_chunk or engine.max_rows
         self.active: List[_Active] = []
         self.pending: Optional[GenRequest] = None
         self.totals = {"requests": 0, "prompt_tokens": 0, "completion_tokens": 0, "device_greedy_rows": 0,
-                       "cpu_sampled_rows": 0, "gpu_sampled_rows": 0, "rounds": 0, "failed": 0}
+                       "cpu_sampled_rows": 0, "gpu_sampled_rows": 0, "rounds": 0, "failed": 0,
+                       "prompt_cache_hit_tokens": 0, "snapshots": 0}
         self._rid = 0
         self._stop = threading.Event()
         self._ready = threading.Event()
@@ -199,6 +204,12 @@ class NativeBackend(Backend):
         a.req.events.put(Event("finish", reason=reason, usage={"prompt_tokens": len(a.req.prompt_ids),
                                                                "completion_tokens": a.emitted}))
         self.totals["completion_tokens"] += a.emitted
+        if reason in ("stop", "length") and a.emitted > 1:
+            # turn bank: the cache holds the prompt and every emitted token but the last one
+            try:
+                self._store_snapshot(a.slot, list(a.req.prompt_ids) + a.tokens[:-1], None)
+            except Exception:
+                pass
         self._release(a)
 
     def _retire(self):
@@ -243,34 +254,72 @@ class NativeBackend(Backend):
                 self.kv.retire(slot, gen)
                 req.events.put(Event("error", status=503, message="KV pool cannot hold this request"))
                 continue
-            hit = self.prefix.lookup(req.prompt_ids)
+            self.prefix.lookup(req.prompt_ids)
+            reused, snap_logits = self._restore_prefix(slot, req.prompt_ids)
             req.events.put(Event("ready", usage={"prompt_tokens": len(req.prompt_ids),
-                                                 "prompt_cache_hit_tokens": 0 if hit is None else 0}))
+                                                 "prompt_cache_hit_tokens": reused}))
             self.totals["requests"] += 1
             self.totals["prompt_tokens"] += len(req.prompt_ids)
-            first = self._prefill(slot, req)
+            self.totals["prompt_cache_hit_tokens"] += reused
+            first = self._prefill(slot, req, start=reused, logits=snap_logits)
             a = _Active(req, slot, gen, pos=len(req.prompt_ids), last=first)
             a.lane = self.lanes.add(req.rid, req.max_tokens, len(req.prompt_ids))
             self.prefix.insert(req.prompt_ids, K.PrefixBanks.PROMPT)
             if self._emit(a, first):
                 self.active.append(a)
 
-    def _prefill(self, slot: int, req: GenRequest) -> int:
+    # ------------------------------------------------------------------ prefix reuse (exact snapshot boundaries)
+    def _restore_prefix(self, slot: int, prompt: List[int]):
+        """Longest stored snapshot whose tokens are a prefix of `prompt` -> (tokens reused, logits after them or None).
+        A snapshot can only be continued from its own end, so the hit is all of its tokens or nothing."""
+        best = None
+        for i, (toks, snap, logits) in enumerate(self.snapshots):
+            n = len(toks)
+            if n == len(prompt) and logits is None:
+                continue                                   # nothing to continue from without the last logits
+            if n <= len(prompt) and (best is None or n > len(self.snapshots[best][0])) and tuple(prompt[:n]) == toks:
+                best = i
+        if best is None:
+            return 0, None
+        toks, snap, logits = self.snapshots[best]
+        self.e.cache.release(slot)                     # the slot was given fresh pages by the admission path
+        if not self.e.cache.restore(slot, snap):
+            self.e.cache.ensure(slot, len(prompt) + 1)
+            return 0, None
+        self.snapshots.append(self.snapshots.pop(best))   # most recently used last
+        return len(toks), (logits if len(toks) == len(prompt) else None)
+
+    def _store_snapshot(self, slot: int, tokens: List[int], logits):
+        key = tuple(tokens)
+        if not key or any(t == key for t, _, _ in self.snapshots):
+            return
+        self.snapshots.append((key, self.e.cache.snapshot(slot, len(key)), logits))
+        self.totals["snapshots"] += 1
+        while len(self.snapshots) > self.snapshot_capacity:
+            _, old, _ = self.snapshots.pop(0)
+            self.e.cache.drop_snapshot(old)
+
+    def _prefill(self, slot: int, req: GenRequest, start: int = 0, logits=None) -> int:
         e = self.e
         toks = req.prompt_ids
-        for c0 in range(0, len(toks), self.prefill_chunk):
-            part = toks[c0:c0 + self.prefill_chunk]
-            e.set_rows(part, list(range(c0, c0 + len(part))), [slot] * len(part))
-            last = c0 + self.prefill_chunk >= len(toks)
-            e.forward_rows(len(part), head=last)
-        return self._select([req], [len(part) - 1])[0]
+        if not e.cache.ensure(slot, len(toks) + req.max_tokens + 1):
+            raise MemoryError("KV pool cannot hold this request")
+        if start < len(toks):
+            for c0 in range(start, len(toks), self.prefill_chunk):
+                part = toks[c0:c0 + self.prefill_chunk]
+                e.set_rows(part, list(range(c0, c0 + len(part))), [slot] * len(part))
+                last = c0 + self.prefill_chunk >= len(toks)
+                e.forward_rows(len(part), head=last)
+            logits = e.logits_rows(len(part))[len(part) - 1].clone()
+            self._store_snapshot(slot, toks, logits)          # prompt bank
+        return self._select([req], [0], logits=logits.view(1, -1))[0]
 
-    def _select(self, reqs: List[GenRequest], rows: List[int]) -> List[int]:
-        """Pick the next token of each request from the logits row it owns in the last pass."""
+    def _select(self, reqs: List[GenRequest], rows: List[int], logits=None) -> List[int]:
+        """Pick the next token of each request from the logits row it owns in the last pass (or in `logits`)."""
         import torch
         e = self.e
         out = []
-        simple = all(r.sampling.greedy and r.constraint is None for r in reqs)
+        simple = logits is None and all(r.sampling.greedy and r.constraint is None for r in reqs)
         if simple:
             chosen = e.chosen.tolist()
             self.totals["device_greedy_rows"] += len(reqs)
@@ -279,7 +328,8 @@ class NativeBackend(Backend):
         # allow-masks (vocab/8 bytes per constrained row) go up and one token id per row comes back
         import numpy as np
         from ..ops.sampling import RowParams, pack_params, sample_rows
-        logits = e.logits_rows(max(rows) + 1)
+        if logits is None:
+            logits = e.logits_rows(max(rows) + 1)
         if logits.dtype != torch.float32:
             logits = logits.float()
         picked = logits[torch.tensor(rows, device=logits.device)] if rows != list(range(len(rows))) else logits[:len(rows)]
@@ -315,6 +365,7 @@ class NativeBackend(Backend):
             self._release(a)
             return False
         a.emitted += 1
+        a.tokens.append(tok)
         r._emitted = a.emitted
         a.last = tok
         if tok == self.eos or tok in r.stop_ids:

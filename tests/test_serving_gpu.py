@@ -100,3 +100,43 @@ def test_official_checkpoint_streams_into_the_engine(tmp_path):
         outs.append(eng.logits_rows(len(toks)).clone())
         eng.check_status()
     assert torch.equal(outs[0], outs[1])
+
+
+def test_prefix_snapshots_reuse_prompt_and_turn(server):
+    """A second request that extends an earlier prompt (or an earlier whole turn) restarts from the stored snapshot:
+    usage reports the reused tokens and the continuation is what a cold run produces."""
+    srv, backend = server
+    from ds41rt_b200.serving.engine import GenRequest
+    from ds41rt_b200.serving.protocol import Sampling
+    g = torch.Generator().manual_seed(9)
+    base = torch.randint(3, 2000, (70,), generator=g).tolist()
+    ext = base + torch.randint(3, 2000, (25,), generator=g).tolist()
+
+    def run(prompt, n=10):
+        r = GenRequest(prompt_ids=prompt, max_tokens=n, sampling=Sampling(temperature=0.0))
+        backend.submit(r)
+        toks, usage = [], None
+        while True:
+            ev = r.events.get(timeout=120)
+            if ev.kind == "ready":
+                usage = ev.usage
+            elif ev.kind == "tokens":
+                toks += ev.tokens
+            elif ev.kind == "finish":
+                return toks, usage
+            elif ev.kind == "error":
+                raise RuntimeError(ev.message)
+
+    backend.snapshots.clear()
+    cold, u0 = run(ext)                                  # nothing stored yet
+    assert u0["prompt_cache_hit_tokens"] == 0
+    backend.snapshots.clear()
+    first, _ = run(base)                                 # stores a prompt snapshot (70) and a turn snapshot (70 + 9)
+    warm, u1 = run(ext)                                  # continues from the 70-token prompt snapshot
+    assert u1["prompt_cache_hit_tokens"] == len(base)
+    assert warm == cold
+    again, u2 = run(base)                                # exact prompt hit: no prefill at all, first token from stored logits
+    assert u2["prompt_cache_hit_tokens"] == len(base) and again == first
+    turn = base + first[:-1] + [77, 78, 79]
+    _, u3 = run(turn)                                    # previous turn + new tokens: continues from the turn snapshot
+    assert u3["prompt_cache_hit_tokens"] == len(base) + len(first) - 1
