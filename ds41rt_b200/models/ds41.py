@@ -582,6 +582,9 @@ class DS41Engine:
         self.layer_prefix_plain = False   # drafter blocks use the plain rope
         self.launches = 0
         self.only = None
+        from ..utils.trace import ActivationTrace
+        self.layer_timer = None   # utils.trace.LayerTimer: device time per layer of eager passes
+        self.activation_trace = ActivationTrace.from_env()
         self._pass_hint = None    # (rows, highest position) of a single-request pass described by the last set_rows
         self.image_patch = None   # (image rows, pass-row ids) applied after the embedding lookup of the next pass
         self.timeline = None   # set to a list to record (tag, start event, end event) per launch of eager passes
@@ -719,6 +722,8 @@ class DS41Engine:
         pending = None
         fused = R <= self.fused_rows
         tap_i = 0
+        if self.layer_timer is not None:
+            self.layer_timer.begin()
         for l in range(first_layer, last_layer):
             lw = self.w.layers[l]
             inv = self._inv(l)
@@ -854,6 +859,12 @@ class DS41Engine:
                                             R, lw.topk, H, lib.ptr(self.moe_plane), st())
             self._signal()
             pending = (self._moe_bases, self.world, 1, 0)
+            if self.layer_timer is not None:
+                self.layer_timer.mark()
+            if self.activation_trace is not None:
+                # the layer's output is merged into the streams by the next sublayer; the dump shows the streams as
+                # they stand plus the pending expert plane of this rank
+                self.activation_trace.dump(l, self.streams, self.row_pos, R)
         self._pending = pending
         self._pass_hint = None
         if head:

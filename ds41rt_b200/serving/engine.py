@@ -33,6 +33,7 @@ class GenRequest:
     events: "queue.Queue" = field(default_factory=lambda: queue.Queue())
     cancelled: threading.Event = field(default_factory=threading.Event)
     rid: int = 0
+    images: List[Any] = field(default_factory=list)     # (PreparedImage, [prompt positions of its rows]) in order
 
 
 @dataclass
@@ -124,8 +125,11 @@ class NativeBackend(Backend):
     the device, sampled or constrained rows go through the sampler oracle with the request's allow-mask)."""
     fingerprint = "ds41rt-b200-fp8"
 
-    def __init__(self, engine, eos: int, concurrency: int = 4, queue_depth: int = 16, prefill_chunk: Optional[int] = None):
+    def __init__(self, engine, eos: int, concurrency: int = 4, queue_depth: int = 16, prefill_chunk: Optional[int] = None,
+                 vision=None):
         self.e, self.eos = engine, eos
+        self.vision = vision                     # models.vision.VisionTower on the engine's device, or None
+        self.supports_images = vision is not None
         self.concurrency = min(concurrency, engine.cache.slots, engine.max_rows)
         self.q: "queue.Queue[GenRequest]" = queue.Queue(maxsize=queue_depth)
         self.kv = K.KvAllocator(engine.cache.n_pages, engine.cache.slots, engine.cache.page_tokens)
@@ -204,7 +208,7 @@ class NativeBackend(Backend):
         a.req.events.put(Event("finish", reason=reason, usage={"prompt_tokens": len(a.req.prompt_ids),
                                                                "completion_tokens": a.emitted}))
         self.totals["completion_tokens"] += a.emitted
-        if reason in ("stop", "length") and a.emitted > 1:
+        if reason in ("stop", "length") and a.emitted > 1 and not a.req.images:
             # turn bank: the cache holds the prompt and every emitted token but the last one
             try:
                 self._store_snapshot(a.slot, list(a.req.prompt_ids) + a.tokens[:-1], None)
@@ -255,7 +259,7 @@ class NativeBackend(Backend):
                 req.events.put(Event("error", status=503, message="KV pool cannot hold this request"))
                 continue
             self.prefix.lookup(req.prompt_ids)
-            reused, snap_logits = self._restore_prefix(slot, req.prompt_ids)
+            reused, snap_logits = (0, None) if req.images else self._restore_prefix(slot, req.prompt_ids)
             req.events.put(Event("ready", usage={"prompt_tokens": len(req.prompt_ids),
                                                  "prompt_cache_hit_tokens": reused}))
             self.totals["requests"] += 1
@@ -299,9 +303,27 @@ class NativeBackend(Backend):
             _, old, _ = self.snapshots.pop(0)
             self.e.cache.drop_snapshot(old)
 
+    def _image_rows(self, req: GenRequest):
+        """Run the vision tower over the request's images -> (rows [n, H] bf16, prompt position of every row)."""
+        import torch
+        rows, positions = [], []
+        for image, pos in req.images:
+            out = self.vision.encode(torch.from_numpy(image.patches), image.grid)
+            if out.shape[0] != len(pos):
+                raise ValueError("image placeholders do not match the image grid")
+            rows.append(out.clone())
+            positions += list(pos)
+        return torch.cat(rows, 0).contiguous(), positions
+
     def _prefill(self, slot: int, req: GenRequest, start: int = 0, logits=None) -> int:
+        import torch
         e = self.e
         toks = req.prompt_ids
+        img_rows = img_pos = None
+        if req.images:
+            if self.vision is None:
+                raise ValueError("this server has no vision tower")
+            img_rows, img_pos = self._image_rows(req)
         if not e.cache.ensure(slot, len(toks) + req.max_tokens + 1):
             raise MemoryError("KV pool cannot hold this request")
         if start < len(toks):
@@ -309,9 +331,15 @@ class NativeBackend(Backend):
                 part = toks[c0:c0 + self.prefill_chunk]
                 e.set_rows(part, list(range(c0, c0 + len(part))), [slot] * len(part))
                 last = c0 + self.prefill_chunk >= len(toks)
+                if img_rows is not None:
+                    ids = [p - c0 if c0 <= p < c0 + len(part) else -1 for p in img_pos]
+                    if any(i >= 0 for i in ids):
+                        e.image_patch = (img_rows, torch.tensor(ids, dtype=torch.int32, device=img_rows.device))
                 e.forward_rows(len(part), head=last)
+                e.image_patch = None
             logits = e.logits_rows(len(part))[len(part) - 1].clone()
-            self._store_snapshot(slot, toks, logits)          # prompt bank
+            if not req.images:                                # placeholders look alike: image prompts are not banked
+                self._store_snapshot(slot, toks, logits)      # prompt bank
         return self._select([req], [0], logits=logits.view(1, -1))[0]
 
     def _select(self, reqs: List[GenRequest], rows: List[int], logits=None) -> List[int]:

@@ -38,10 +38,11 @@ s.onmessage=e=>{o.textContent=JSON.stringify(JSON.parse(e.data),null,2)};</scrip
 class ApiServer:
     def __init__(self, backend: Backend, tokenizer, host: str = "127.0.0.1", port: int = 0, model_id: str = MODEL_ID,
                  max_context: int = MAX_CONTEXT, max_output: int = MAX_OUTPUT, queue_depth: int = 16, waiters: int = 16,
-                 default_max_tokens: int = 4096, first_event_timeout: float = 600.0):
+                 default_max_tokens: int = 4096, first_event_timeout: float = 600.0, vision_cfg=None):
         self.backend, self.tk, self.model_id = backend, tokenizer, model_id
         self.max_context, self.max_output, self.default_max_tokens = max_context, max_output, default_max_tokens
         self.first_event_timeout = first_event_timeout
+        self.vision_cfg = vision_cfg             # config.VisionConfig when the backend has a vision tower
         self.admission = K.Admission(queue_depth, waiters)
         self.vocab: Optional[Vocab] = None
         self.counters = {"requests": 0, "rejected_429": 0, "bad_request": 0, "errors": 0, "streams": 0}
@@ -157,7 +158,7 @@ class ApiServer:
                                                        req.thinking, req.reasoning_effort)
             except C.ChatError as e:
                 raise ApiError(400, str(e))
-            ids = self.tk.encode(prompt)
+            ids, image_refs = self._encode_with_images(prompt, images)
             if len(ids) >= self.max_context:
                 raise ApiError(400, f"prompt of {len(ids)} tokens exceeds the context window")
             max_tokens = min(req.max_tokens or self.default_max_tokens, self.max_output, self.max_context - len(ids))
@@ -165,7 +166,8 @@ class ApiServer:
             slot = self.admission.reserve()
             if slot < 0:
                 raise ApiError(429, "server is at capacity, retry shortly", retry_after=1)
-            gen = GenRequest(prompt_ids=ids, max_tokens=max_tokens, sampling=req.sampling, constraint=constraint)
+            gen = GenRequest(prompt_ids=ids, max_tokens=max_tokens, sampling=req.sampling, constraint=constraint,
+                             images=image_refs)
             try:
                 try:
                     self.backend.submit(gen)
@@ -192,6 +194,35 @@ class ApiServer:
                 self._fail(h, e)
             except (BrokenPipeError, ConnectionResetError):
                 pass
+
+    def _encode_with_images(self, prompt: str, images):
+        """Token ids of the rendered prompt; every "<image>" mark becomes the span of its image (start, one placeholder
+        per merged patch row group with a newline after each grid row, end).  Images are decoded and resized here, on
+        the HTTP thread; the vision tower runs on the worker."""
+        if not images:
+            return self.tk.encode(prompt), []
+        from . import images as IM
+        if self.vision_cfg is None or not getattr(self.backend, "supports_images", False):
+            raise ApiError(400, "this model does not accept images")
+        special = getattr(self.tk, "special", {})
+        try:
+            tok, start, end, newline = (special[n] for n in ("<image>", "<image_start>", "<image_end>", "<image_newline>"))
+        except KeyError:
+            raise ApiError(400, "the tokenizer has no image tokens")
+        pieces = prompt.split("<image>")
+        if len(pieces) != len(images) + 1:
+            raise ApiError(400, "image marks and image parts do not match")
+        ids, refs = self.tk.encode(pieces[0]), []
+        for url, text in zip(images, pieces[1:]):
+            try:
+                prepared = IM.prepare_image(IM.decode_data_url(url), self.vision_cfg)
+            except IM.ImageError as e:
+                raise ApiError(400, str(e))
+            span = IM.image_span(prepared, self.vision_cfg, tok, start, end, newline)
+            refs.append((prepared, [len(ids) + i for i, t in enumerate(span) if t == tok]))
+            ids += span
+            ids += self.tk.encode(text)
+        return ids, refs
 
     def _constraint(self, req) -> Optional[TokenConstraint]:
         rf = req.response_format

@@ -121,3 +121,17 @@ def test_hostcache_randomised_simulation_keeps_invariants():
         assert hc.check() == 0, step
     m = hc.metrics()
     assert m["evictions"] > 0 and m["shared"] > 0 and m["hits"] > 0
+
+
+def test_trace_targets_follow_the_env_filter(monkeypatch):
+    import importlib
+    import logging
+    from ds41rt_b200.utils import trace
+    monkeypatch.setenv("DS41_LOG", "timing,sampling=debug")
+    importlib.reload(trace)
+    assert trace.enabled("timing") and not trace.enabled("timing", logging.DEBUG)
+    assert trace.enabled("sampling", logging.DEBUG)
+    assert not trace.enabled("host_cache")
+    monkeypatch.delenv("DS41_LOG")
+    importlib.reload(trace)
+    assert not trace.enabled("timing")

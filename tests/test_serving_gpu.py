@@ -140,3 +140,53 @@ def test_prefix_snapshots_reuse_prompt_and_turn(server):
     turn = base + first[:-1] + [77, 78, 79]
     _, u3 = run(turn)                                    # previous turn + new tokens: continues from the turn snapshot
     assert u3["prompt_cache_hit_tokens"] == len(base) + len(first) - 1
+
+
+def test_image_parts_reach_the_vision_tower():
+    """A chat request with an image: decoded and gridded on the HTTP thread, encoded by the tower on the worker, its
+    rows replace the placeholder embeddings; a different image changes the answer, a bad image is a 400."""
+    import base64
+    import io
+
+    import numpy as np
+    from PIL import Image
+
+    from ds41rt_b200.config import ModelConfig, VisionConfig
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    from ds41rt_b200.models.vision import VisionTower, init_vision_weights
+    from ds41rt_b200.serving.engine import NativeBackend
+    from ds41rt_b200.serving.http import ApiServer
+    from ds41rt_b200.serving.tokenizer import ByteTokenizer
+    cfg = ModelConfig.tiny()
+    v = VisionConfig(layers=2, hidden=256, heads=4, intermediate=384, min_pixels=42 * 42 * 4, max_image_tokens=16)
+    dev = torch.device("cuda", 0)
+    tk = ByteTokenizer(vocab_size=cfg.vocab, extra_specials=["<image>", "<image_start>", "<image_end>", "<image_newline>"])
+    eng = DS41Engine(cfg, EngineWeights.random(cfg, 0, 1, dev, seed=0), max_rows=16, slots=2, max_ctx=1024)
+    tower = VisionTower(v, init_vision_weights(v, cfg.hidden, 2, seed=4, std=0.05), cfg.hidden, 2, dev, max_patches=144)
+    backend = NativeBackend(eng, eos=tk.eos, concurrency=2, vision=tower)
+    srv = ApiServer(backend, tk, queue_depth=4, waiters=2, first_event_timeout=60.0, vision_cfg=v).start()
+
+    def data_url(seed):
+        rng = np.random.default_rng(seed)
+        buf = io.BytesIO()
+        Image.fromarray(rng.integers(0, 256, size=(90, 120, 3), dtype=np.uint8)).save(buf, format="PNG")
+        return "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+
+    def ask(url):
+        body = _body(temperature=0, max_tokens=8, thinking={"type": "disabled"})
+        body["messages"] = [{"role": "user", "content": [{"type": "text", "text": "what is this "},
+                                                         {"type": "image_url", "image_url": {"url": url}}]}]
+        return _call(srv, body)
+
+    try:
+        a, b, c = ask(data_url(1)), ask(data_url(1)), ask(data_url(2))
+        assert a[0] == 200 and b[0] == 200 and c[0] == 200, (a, c)
+        ma, mb, mc = (json.loads(x[1])["choices"][0]["message"]["content"] for x in (a, b, c))
+        assert ma == mb
+        assert json.loads(a[1])["usage"]["prompt_tokens"] > 20          # the span is part of the prompt
+        bad = ask("data:image/png;base64," + base64.b64encode(b"nope").decode())
+        assert bad[0] == 400
+        print("image answers differ:", ma != mc)
+    finally:
+        srv.stop()
+        backend.close()
