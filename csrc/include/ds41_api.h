@@ -78,6 +78,11 @@ typedef struct ds41_gemm_args {
   // out_mode 8 (indexer scores): M rows are (query, head) pairs with 32 heads per query; out is fp32 [M/32, ldo];
   // row_w[query * row_w_ld + head] weights relu(acc); columns >= col_limit[query] (if given) are written as -inf.
   const int* col_limit;
+  // kind 3 (NVFP4 x NVFP4): A and B hold e2m1 values two per byte, sfa / sfb hold E4M3 scales per 16 elements in
+  // 512-byte atoms of (128 rows, 64 K elements): byte = (row%32)*16 + ((row/32)%4)*4 + (k/16)%4, atoms [row/128][K/64].
+  // K must be a multiple of 256; lda / ldb / batch strides count elements; alpha (the product of the two global
+  // scales, 0 = 1) multiplies the accumulators.
+  float alpha;
 } ds41_gemm_args;
 
 int ds41_gemm_tc(const ds41_gemm_args* args, void* stream);
@@ -289,6 +294,11 @@ int ds41_vis_scatter(const void* src, const int* rows, void* dst, int n, int H, 
 // Prefill-sized activation quantiser (1x128 scales, one warp per row); rows >= *rows_dev (if given) are skipped.
 int ds41_act_quant_mx_rows(const void* x, long long ldx, void* q, long long ldq, void* sf, int rows, int K,
                            const int* rows_dev, void* stream);
+
+// NVFP4 activation rows (e2m1 two per byte + E4M3 scale atoms per 16 elements, relative to global_scale); ldq counts
+// elements; rows >= *rows_dev (if given) are skipped.
+int ds41_act_quant_nvfp4_rows(const void* x, long long ldx, void* q, long long ldq, void* sf, int rows, int K,
+                              float global_scale, const int* rows_dev, void* stream);
 
 #ifdef __cplusplus
 }

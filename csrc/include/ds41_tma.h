@@ -7,7 +7,7 @@
 
 namespace ds41 {
 
-enum class TmaDtype : int { kBF16 = 0, kU8 = 1, kF32 = 2, kU4x16Align16 = 3 };
+enum class TmaDtype : int { kBF16 = 0, kU8 = 1, kF32 = 2, kU4x16Align16 = 3, kU4x16Align8 = 4 };
 
 // 3-D row-major view {batch, rows, cols}: cols contiguous, `row_stride_bytes` between rows and
 // `batch_stride_bytes` between batches.  The box is {1, box_rows, box_cols}.  `swizzle128` selects

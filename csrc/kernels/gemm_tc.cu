@@ -55,6 +55,7 @@ struct GemmParams {
   int row_w_ld;
   float act_limit;        // mode 4: SwiGLU clamp
   int static_operand;     // 1: A holds weights, 2: B holds weights (may be fetched before the dependency wait)
+  float alpha;            // kind 3: product of the two tensors' global scales, applied to the accumulators
   int a_fp4;              // MX kind: A holds e2m1 values (packed in global memory, one per byte in shared memory)
   // grouped tokens (expert-parallel prefill, swap-AB): the N operand is a flat buffer of rows sorted by expert;
   // tile j covers rows [tile_row0[j], tile_end[j]) of expert tile_group[j]; *n_tiles_dev tiles are live
@@ -88,19 +89,24 @@ struct GemmParams {
 template <int BN, int KIND, int DUAL = 0>
 struct GemmCfg {
   static constexpr int kElemBytes = (KIND == 0) ? 2 : 1;
-  static constexpr int kBK = kTileKBytes / kElemBytes;                 // elements of K per stage
+  // elements of K per stage: one 128-byte swizzle span (kind 3 packs two e2m1 values per byte)
+  static constexpr int kBK = (KIND == 3) ? 2 * kTileKBytes : kTileKBytes / kElemBytes;
+  static constexpr int kSfPerTile = (KIND == 3) ? 4 : 1;               // 512-byte scale atoms per 128 rows per stage
+  static constexpr bool kScaled = (KIND == 2 || KIND == 3);
   static constexpr int kATile = kBM * kTileKBytes;                     // 16 KiB
   static constexpr int kABytes = kATile * (DUAL ? 2 : 1);
   static constexpr int kBBytes = BN * kTileKBytes;
-  static constexpr int kAtomsA = DUAL ? 2 : 1;
-  static constexpr int kAtomsB = (BN + 127) / 128;
+  static constexpr int kTilesA = DUAL ? 2 : 1;
+  static constexpr int kTilesB = (BN + 127) / 128;
+  static constexpr int kAtomsA = kTilesA * kSfPerTile;
+  static constexpr int kAtomsB = kTilesB * kSfPerTile;
   // scale-factor atoms (512 B each), padded so every stage keeps its 1024-byte tile alignment
-  static constexpr int kSfBytes = (KIND == 2) ? ((512 * (kAtomsA + kAtomsB) + 1023) / 1024 * 1024) : 0;
+  static constexpr int kSfBytes = kScaled ? ((512 * (kAtomsA + kAtomsB) + 1023) / 1024 * 1024) : 0;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
   static constexpr int kStaging = (!DUAL && BN >= 64) ? kStagingBytes : 0;
   static constexpr int kStagesRaw = ((kStaging ? 194 : 200) * 1024) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kSfCols = (KIND == 2) ? 4 * (kAtomsA + kAtomsB) : 0;           // TMEM columns per stage
+  static constexpr int kSfCols = kScaled ? 4 * (kAtomsA + kAtomsB) : 0;               // TMEM columns per stage
   static constexpr int kAccCols = (BN < 32 ? 32 : BN) * (DUAL ? 2 : 1);
   static constexpr int kTmemNeeded = 2 * kAccCols + kStages * kSfCols;
   static constexpr int kTmemCols = kTmemNeeded <= 32 ? 32 : kTmemNeeded <= 64 ? 64 : kTmemNeeded <= 128 ? 128
@@ -200,7 +206,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     bool ok = true;
     // 4-bit A tiles occupy one byte per element in shared memory but the copy engine accounts the packed bytes
     const uint32_t kStageTx = (p.a_fp4 ? Cfg::kABytes / 2 : Cfg::kABytes) + Cfg::kBBytes +
-                              (KIND == 2 ? 512 * (Cfg::kAtomsA + Cfg::kAtomsB) : 0);
+                              (Cfg::kScaled ? 512 * (Cfg::kAtomsA + Cfg::kAtomsB) : 0);
     // Weight tiles of the first stages do not depend on the previous kernel: fetch them before waiting for it.
     int prefetched = 0;
     if (p.static_operand != 0 && p.n_active == nullptr && p.batch_map == nullptr && !table && blockIdx.x < tiles) {
@@ -268,21 +274,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tma_load_3d(sa + Cfg::kATile, &tmA, &full[stage], kb * Cfg::kBK, p.up_row_offset + mt * kBM, ba);
         }
         if (!early || p.static_operand != 2) tma_load_3d(sb, &tmB, &full[stage], kb * Cfg::kBK, n_base, bb);
-        if constexpr (KIND == 2) {
-          // scale-factor atoms: [row_atom][k_atom][512 B]; one k_atom per stage (128 elements of K)
+        if constexpr (Cfg::kScaled) {
+          // scale-factor atoms: [row_atom][k_atom][512 B]; kSfPerTile consecutive k_atoms per stage and 128 rows
+          // (MX: one atom = 128 K elements with a UE8M0 scale per 32; NVFP4: four atoms of 64 K elements, E4M3 per 16)
+          constexpr int kSf = Cfg::kSfPerTile;
           uint8_t* ssf = sb + Cfg::kBBytes;
-          const long long ka = kb;
-          const long long n_ka = kb_total;
-          bulk_load(ssf, p.sfa + ba * p.sfa_batch_stride + (1ll * mt * n_ka + ka) * 512, 512, &full[stage]);
+          const long long ka = 1ll * kb * kSf;
+          const long long n_ka = 1ll * kb_total * kSf;
+          bulk_load(ssf, p.sfa + ba * p.sfa_batch_stride + (1ll * mt * n_ka + ka) * 512, 512 * kSf, &full[stage]);
           if constexpr (DUAL) {
             const long long mt_up = p.up_row_offset / 128 + mt;
-            bulk_load(ssf + 512, p.sfa + ba * p.sfa_batch_stride + (mt_up * n_ka + ka) * 512, 512, &full[stage]);
+            bulk_load(ssf + 512 * kSf, p.sfa + ba * p.sfa_batch_stride + (mt_up * n_ka + ka) * 512, 512 * kSf, &full[stage]);
           }
 #pragma unroll
-          for (int a = 0; a < Cfg::kAtomsB; ++a) {
+          for (int a = 0; a < Cfg::kTilesB; ++a) {
             const long long ra = n_base / 128 + a;
-            bulk_load(ssf + 512 * (Cfg::kAtomsA + a), p.sfb + bb * p.sfb_batch_stride + (ra * n_ka + ka) * 512, 512,
-                      &full[stage]);
+            bulk_load(ssf + 512 * (Cfg::kAtomsA + a * kSf), p.sfb + bb * p.sfb_batch_stride + (ra * n_ka + ka) * 512,
+                      512 * kSf, &full[stage]);
           }
         }
         if (++stage == S) { stage = 0; phase ^= 1; }
@@ -313,7 +321,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t sb = sa + Cfg::kABytes;
         const uint64_t adesc = umma_desc_sw128(sa);
         const uint64_t bdesc = umma_desc_sw128(sb);
-        if constexpr (KIND == 2) {
+        if constexpr (Cfg::kScaled) {
           const uint32_t ssf = sb + Cfg::kBBytes;
           const uint32_t sf_t = tmem_base + 2 * Cfg::kAccCols + stage * Cfg::kSfCols;
 #pragma unroll
@@ -324,12 +332,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t sfb_t = sf_t + 4 * Cfg::kAtomsA + (n_base_u & 127u) / 32u;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint32_t id = umma_idesc_bs(kBM, BN, p.a_fp4 ? 5u : 0u, 0, 1, k, k);   // e2m1 = 5, e4m3 = 0
             const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
-            umma_mxf8(d_tmem, adesc + 2 * k, bdesc + 2 * k, id, accum, sf_t, sfb_t);
-            if constexpr (DUAL) {
-              const uint64_t adesc2 = umma_desc_sw128(sa + Cfg::kATile);
-              umma_mxf8(d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, id, accum, sf_t + 4, sfb_t);
+            if constexpr (KIND == 2) {
+              // one atom per stage; instruction k uses byte k of every 32-bit scale cell
+              const uint32_t id = umma_idesc_bs(kBM, BN, p.a_fp4 ? 5u : 0u, 0, 1, k, k);   // e2m1 = 5, e4m3 = 0
+              umma_mxf8(d_tmem, adesc + 2 * k, bdesc + 2 * k, id, accum, sf_t, sfb_t);
+              if constexpr (DUAL) {
+                const uint64_t adesc2 = umma_desc_sw128(sa + Cfg::kATile);
+                umma_mxf8(d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, id, accum, sf_t + 4, sfb_t);
+              }
+            } else {
+              // NVFP4: instruction k (64 K elements) uses atom k: four E4M3 scales per row fill one 32-bit cell
+              const uint32_t id = umma_idesc_bs(kBM, BN, 1u, 1u, 0, 0, 0);                 // e2m1 x e2m1, UE4M3 scales
+              umma_nvf4(d_tmem, adesc + 2 * k, bdesc + 2 * k, id, accum, sf_t + 4 * k, sfb_t + 4 * k);
+              if constexpr (DUAL) {
+                const uint64_t adesc2 = umma_desc_sw128(sa + Cfg::kATile);
+                umma_nvf4(d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, id, accum, sf_t + 16 + 4 * k,
+                          sfb_t + 4 * k);
+              }
             }
           }
         } else {
@@ -409,6 +429,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int j = 0; j < 8; ++j) v[j] = v8[j];
         }
         tmem_wait_ld();
+        if constexpr (KIND == 3) {
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * p.alpha);
+        }
         const int n0 = n_base + c;
         const float rw_lane = rw_next;
         const int2 meta_lane = meta_next;
@@ -483,6 +507,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               for (int j = 0; j < 16; ++j) u[j] = u16[j];
             }
             tmem_wait_ld();
+            if constexpr (KIND == 3) {
+#pragma unroll
+              for (int j = 0; j < kChunk; ++j) u[j] = __float_as_uint(__uint_as_float(u[j]) * p.alpha);
+            }
             __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + obase + m;
             // the chunk's route weights were fetched with one coalesced load and are handed out by shuffle: a load per
             // column would be ordered behind the previous column's store
@@ -700,7 +728,7 @@ static cudaError_t dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap
       case 32: return launch_gemm<32, KIND, 1>(tmA, tmB, peer, p, grid, stream);
       case 64: return launch_gemm<64, KIND, 1>(tmA, tmB, peer, p, grid, stream);
       case 128:
-        if constexpr (KIND != 2) return launch_gemm<128, KIND, 1>(tmA, tmB, peer, p, grid, stream);
+        if constexpr (KIND < 2) return launch_gemm<128, KIND, 1>(tmA, tmB, peer, p, grid, stream);
         return cudaErrorInvalidValue;
       default: return cudaErrorInvalidValue;
     }
@@ -711,7 +739,7 @@ static cudaError_t dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap
     case 64: return launch_gemm<64, KIND>(tmA, tmB, peer, p, grid, stream);
     case 128: return launch_gemm<128, KIND>(tmA, tmB, peer, p, grid, stream);
     case 256:
-      if constexpr (KIND != 2) return launch_gemm<256, KIND>(tmA, tmB, peer, p, grid, stream);
+      if constexpr (KIND < 2) return launch_gemm<256, KIND>(tmA, tmB, peer, p, grid, stream);
       return cudaErrorInvalidValue;
     default: return cudaErrorInvalidValue;
   }
@@ -725,14 +753,17 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   if (a == nullptr) return cudaErrorInvalidValue;
   const int M = a->M, N = a->N, K = a->K, batch = a->batch, kind = a->kind, out_mode = a->out_mode;
   const int k_splits = a->k_splits, bn = a->bn;
-  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0 || k_splits <= 0 || kind < 0 || kind > 2 || out_mode < 0 ||
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0 || k_splits <= 0 || kind < 0 || kind > 3 || out_mode < 0 ||
       out_mode > 8)
     return cudaErrorInvalidValue;
   const int elem = kind == 0 ? 2 : 1;
-  const int bk = kTileKBytes / elem;
+  const int bk = kind == 3 ? 2 * kTileKBytes : kTileKBytes / elem;     // kind 3: two e2m1 values per byte
   const int kb_total = (K + bk - 1) / bk;
   if (1ll * (k_splits - 1) * ((kb_total + k_splits - 1) / k_splits) >= kb_total) return cudaErrorInvalidValue;   // no empty split
   if (kind == 2 && (K % 128 != 0 || a->sfa == nullptr || a->sfb == nullptr)) return cudaErrorInvalidValue;
+  if (kind == 3 && (K % 256 != 0 || a->sfa == nullptr || a->sfb == nullptr || a->ag_world > 0 || a->rs_world > 0 ||
+                    out_mode == 6 || out_mode == 8 || (bn < 32 && N > bn)))
+    return cudaErrorInvalidValue;
   if (kind == 2 && bn < 32 && N > bn) return cudaErrorInvalidValue;      // 16-row scale tiles cannot be lane-shifted
   if (k_splits > 1 && out_mode != 1 && out_mode != 3) return cudaErrorInvalidValue;   // partials are fp32
   if ((out_mode == 4 || out_mode == 5 || out_mode == 8) && a->row_w == nullptr) return cudaErrorInvalidValue;
@@ -756,7 +787,16 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
                         : make_tensor_map_3d(&tmA, a_base, dt, K, a_rows, a_batches, a->lda * elem,
                                              a->a_batch_stride * elem, bk, kBM, true);
   if (e != cudaSuccess) return e;
-  e = make_tensor_map_3d(&tmB, a->B, dt, K, N, b_batches, a->ldb * elem, a->b_batch_stride * elem, bk, bn, true);
+  if (kind == 3) {
+    // both operands e2m1, two per byte in memory and in shared memory; strides count elements
+    e = make_tensor_map_3d(&tmA, a_base, TmaDtype::kU4x16Align8, K, a_rows, a_batches, a->lda / 2, a->a_batch_stride / 2,
+                           bk, kBM, true);
+    if (e != cudaSuccess) return e;
+    e = make_tensor_map_3d(&tmB, a->B, TmaDtype::kU4x16Align8, K, N, b_batches, a->ldb / 2, a->b_batch_stride / 2, bk, bn,
+                           true);
+  } else {
+    e = make_tensor_map_3d(&tmB, a->B, dt, K, N, b_batches, a->ldb * elem, a->b_batch_stride * elem, bk, bn, true);
+  }
   if (e != cudaSuccess) return e;
   StoreMaps peer{};
   int ag_chunks = 1;
@@ -832,6 +872,7 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   for (int r = 0; r < 8; ++r) p.scatter_out[r] = a->scatter_out[r];
   p.static_operand = a->static_operand;
   p.a_fp4 = a_fp4 ? 1 : 0;
+  p.alpha = a->alpha != 0.f ? a->alpha : 1.f;
   p.status = a->status;
   const long long n_t = a->tile_group != nullptr ? a->max_tiles : (N + bn - 1) / bn;
   const long long tiles = 1ll * ((M + kBM - 1) / kBM) * n_t * k_splits * (a->tile_group != nullptr ? 1 : batch);
@@ -840,6 +881,7 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   switch (kind) {
     case 0: return dispatch_bn<0>(bn, tmA, tmB, peer, p, grid, s);
     case 1: return dispatch_bn<1>(bn, tmA, tmB, peer, p, grid, s);
-    default: return dispatch_bn<2>(bn, tmA, tmB, peer, p, grid, s);
+    case 2: return dispatch_bn<2>(bn, tmA, tmB, peer, p, grid, s);
+    default: return dispatch_bn<3>(bn, tmA, tmB, peer, p, grid, s);
   }
 }

@@ -120,9 +120,82 @@ act_quant_mx_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uin
   }
 }
 
+// NVFP4 activation rows: e2m1 values (two per byte, even element in the low nibble) with one E4M3 scale per 16
+// elements, relative to a fixed per-tensor scale `global_scale` (value = code * block_scale * global_scale).
+// block_scale = e4m3(amax / 6 / global_scale); codes round to nearest (ties to even) on the e2m1 grid.
+// One warp per row, 8 elements per lane per step (two lanes share a 16-element block).  Scales go straight into the
+// 512-byte atoms of the tensor-core kind: atom [row/128][k/64], byte (row%32)*16 + ((row/32)%4)*4 + (k/16)%4.
+__device__ __forceinline__ uint32_t e2m1_code(float v) {
+  const float a = fabsf(v);
+  uint32_t c;
+  // midpoints between representable magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6; ties go to the even mantissa
+  if (a <= 0.25f) c = 0;
+  else if (a < 0.75f) c = 1;
+  else if (a <= 1.25f) c = 2;
+  else if (a < 1.75f) c = 3;
+  else if (a <= 2.5f) c = 4;
+  else if (a < 3.5f) c = 5;
+  else if (a <= 5.0f) c = 6;
+  else c = 7;
+  return c | (v < 0.f ? 8u : 0u);
+}
+
+__global__ void __launch_bounds__(256)
+act_quant_nvfp4_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q, long long ldq,
+                            uint8_t* __restrict__ sf, int rows, int K, float global_scale,
+                            const int* __restrict__ rows_dev) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int live = rows_dev != nullptr ? min(rows, *rows_dev) : rows;
+  const int k_atoms = K / 64;
+  for (int r = blockIdx.x * 8 + warp; r < live; r += gridDim.x * 8) {
+    const __nv_bfloat16* src = x + 1ll * r * ldx;
+    uint8_t* dst = q + 1ll * r * (ldq / 2);
+    uint8_t* atom_row = sf + 1ll * (r / 128) * k_atoms * 512 + (r % 32) * 16 + ((r / 32) % 4) * 4;
+    for (int k0 = 0; k0 < K; k0 += 256) {
+      const int k = k0 + lane * 8;
+      float f[8];
+      float amax = 0.f;
+      if (k < K) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + k);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 v = __bfloat1622float2(h[j]);
+          f[2 * j] = v.x;
+          f[2 * j + 1] = v.y;
+          amax = fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y)));
+        }
+      }
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));       // 16-element block = two lanes
+      if (k < K) {
+        // IEEE divisions in this order, so that scales and codes are bit-identical to the host oracle
+        const __nv_fp8_e4m3 bs(__fdiv_rn(__fdiv_rn(amax, 6.0f), global_scale));
+        const float bsf = __fmul_rn(static_cast<float>(bs), global_scale);
+        const float den = bsf == 0.f ? 1.0f : bsf;
+        uint32_t packed = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) packed |= e2m1_code(__fdiv_rn(f[j], den)) << (4 * j);
+        *reinterpret_cast<uint32_t*>(dst + k / 2) = packed;
+        if ((lane & 1) == 0) atom_row[1ll * (k / 64) * 512 + ((k / 16) & 3)] = bs.__x;
+      }
+    }
+  }
+}
+
 }  // namespace ds41
 
 using namespace ds41;
+
+extern "C" int ds41_act_quant_nvfp4_rows(const void* x, long long ldx, void* q, long long ldq, void* sf, int rows,
+                                         int K, float global_scale, const int* rows_dev, void* stream) {
+  if (rows <= 0 || K <= 0 || K % 64 != 0 || (ldx & 7) || (ldq & 7) || !(global_scale > 0.f)) return cudaErrorInvalidValue;
+  const int blocks = min((rows + 7) / 8, 8 * sm_count_cached());
+  return launch_pdl(act_quant_nvfp4_rows_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(q), ldq, static_cast<uint8_t*>(sf),
+                    rows, K, global_scale, rows_dev);
+}
 
 extern "C" int ds41_act_quant_mx_rows(const void* x, long long ldx, void* q, long long ldq, void* sf, int rows, int K,
                                       const int* rows_dev, void* stream) {

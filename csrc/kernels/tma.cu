@@ -34,6 +34,7 @@ cudaError_t make_tensor_map_3d(CUtensorMap* out, const void* base, TmaDtype dtyp
     case TmaDtype::kU8: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; elem_bits = 8; break;
     case TmaDtype::kF32: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; elem_bits = 32; break;
     case TmaDtype::kU4x16Align16: dt = CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B; elem_bits = 4; break;
+    case TmaDtype::kU4x16Align8: dt = CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B; elem_bits = 4; break;   // packed in smem too
     default: return cudaErrorInvalidValue;
   }
   // 4-bit elements packed two per byte in global memory land one per byte in shared memory (16 values per 16 bytes):

@@ -35,7 +35,7 @@ class GemmArgs(C.Structure):
         ("a_peers", C.c_void_p * 8), ("ag_arrive", C.c_void_p * 8), ("ag_epoch", C.c_void_p), ("rs_out", C.c_void_p * 8),
         ("tile_group", C.c_void_p), ("tile_row0", C.c_void_p), ("tile_end", C.c_void_p), ("n_tiles_dev", C.c_void_p),
         ("scatter_meta", C.c_void_p), ("wait_flags", C.c_void_p), ("wait_epoch", C.c_void_p),
-        ("scatter_out", C.c_void_p * 8), ("max_tiles", C.c_int), ("wait_world", C.c_int), ("a_format", C.c_int), ("col_limit", C.c_void_p),
+        ("scatter_out", C.c_void_p * 8), ("max_tiles", C.c_int), ("wait_world", C.c_int), ("a_format", C.c_int), ("col_limit", C.c_void_p), ("alpha", C.c_float),
     ]
 
 
@@ -105,7 +105,7 @@ def dir_functions():
         "ds41_argmax_merge", "ds41_spec_accept", "ds41_act_quant_mx", "ds41_decode_feedback", "ds41_hc_step", "ds41_taps_pack", "ds41_norm_rows", "ds41_markov_step", "ds41_spec_feedback",
         "ds41_copy_ints", "ds41_rs_reduce", "ds41_ep_count", "ds41_ep_plan", "ds41_ep_dispatch", "ds41_ep_mark",
         "ds41_ep_wait", "ds41_ep_combine", "ds41_act_quant_mx_rows", "ds41_sample_rows", "ds41_engram_dequant", "ds41_engram_gate", "ds41_block_max", "ds41_expand_blocks", "ds41_vis_rmsnorm", "ds41_vis_bias_act", "ds41_vis_silu_mul",
-        "ds41_index_prepare", "ds41_vis_rope2d", "ds41_vis_softmax", "ds41_vis_merge", "ds41_vis_scatter",
+        "ds41_index_prepare", "ds41_act_quant_nvfp4_rows", "ds41_vis_rope2d", "ds41_vis_softmax", "ds41_vis_merge", "ds41_vis_scatter",
     ]
 
 

@@ -115,3 +115,31 @@ def test_mxfp4_weights_times_mxfp8_rows(rows, N, K):
     torch.cuda.synchronize()
     lib.raise_on_status(st, "gemm mxfp4")
     assert _rel(out, ref) < 2e-3
+
+
+@pytest.mark.parametrize("rows,N,K", [(5, 256, 512), (40, 384, 1024), (16, 4608, 5120), (300, 256, 768)])
+def test_nvfp4_both_operands(rows, N, K):
+    """E2M1 values with an E4M3 scale per 16 elements and one fp32 scale per tensor (NVFP4) on both operands:
+    tcgen05 kind::mxf4nvf4, scale_vec 4X, global scales folded into the epilogue."""
+    from ds41rt_b200.ops import gemm as G, lib, quant_ref as Q
+    from ds41rt_b200.ops.mx import pack_sf_atoms
+    torch.manual_seed(3)
+    x = torch.randn(rows, K, device="cuda") * torch.exp(0.5 * torch.randn(rows, 1, device="cuda"))
+    w = torch.randn(N, K, device="cuda") * 0.1 * torch.exp(0.5 * torch.randn(N, 1, device="cuda"))
+    xq, xs, xg = Q.quant_nvfp4(x)
+    wq, ws, wg = Q.quant_nvfp4(w)
+    ref = Q.dequant_nvfp4(xq, xs, xg) @ Q.dequant_nvfp4(wq, ws, wg).t()
+    st = lib.new_status("cuda")
+    out = torch.zeros(rows, N, device="cuda")
+    sfx = pack_sf_atoms(xs.view(torch.uint8))
+    sfw = pack_sf_atoms(ws.view(torch.uint8))
+    alpha = float(xg) * float(wg)
+    if rows <= 128:
+        G.gemm_raw(wq.contiguous(), xq.contiguous(), out, N, rows, K, lda=K, ldb=K, ldo=N, kind=3, out_mode=3, sfa=sfw,
+                   sfb=sfx, bn=max(32, G.pick_bn(rows)), status=st, alpha=alpha)
+    else:
+        G.gemm_raw(xq.contiguous(), wq.contiguous(), out, rows, N, K, lda=K, ldb=K, ldo=N, kind=3, out_mode=1, sfa=sfx,
+                   sfb=sfw, bn=128, status=st, alpha=alpha)
+    torch.cuda.synchronize()
+    lib.raise_on_status(st, "gemm nvfp4")
+    assert _rel(out, ref) < 2e-3

@@ -354,3 +354,23 @@ def test_index_scores_on_tensor_cores_match_the_scalar_kernel():
         a, b = got[r, :nv], ref[r, :nv]
         assert float((a - b).abs().max()) < 2e-3 * float(b.abs().max())
         assert torch.isinf(got[r, nv:n_keys]).all()
+
+
+def test_nvfp4_activation_quantiser_matches_oracle():
+    from ds41rt_b200.ops import lib, quant_ref as Q
+    from ds41rt_b200.ops.mx import pack_sf_atoms
+    k = lib.kernels()
+    torch.manual_seed(5)
+    rows, K = 70, 768
+    x = (torch.randn(rows, K, device="cuda") * torch.exp(torch.randn(rows, 1, device="cuda"))).bfloat16()
+    gs = float(x.float().abs().amax() / (448 * 6))
+    want_q, want_s, _ = Q.quant_nvfp4(x.float(), gs)
+    q = torch.zeros(rows, K // 2, dtype=torch.uint8, device="cuda")
+    sf = torch.zeros((rows + 127) // 128, K // 64, 512, dtype=torch.uint8, device="cuda")
+    lib.check(k.ds41_act_quant_nvfp4_rows(lib.ptr(x), C.c_longlong(K), lib.ptr(q), C.c_longlong(K), lib.ptr(sf), rows,
+                                          K, C.c_float(gs), None, lib.stream()), "quant")
+    torch.cuda.synchronize()
+    assert torch.equal(q, want_q)
+    want_atoms = pack_sf_atoms(want_s.view(torch.uint8))
+    from ds41rt_b200.ops.mx import unpack_sf_atoms
+    assert torch.equal(unpack_sf_atoms(sf.cpu(), rows), unpack_sf_atoms(want_atoms.cpu(), rows))
