@@ -205,9 +205,15 @@ int ds41_rs_reduce(const float* slots, int world, long long slot_stride, void* o
 int ds41_taps_pack(const float* taps, void* out, int n_taps, int rows, int H, long long tap_stride, void* stream);
 int ds41_norm_rows(const float* planes, int splits, long long plane, const float* w, void* out, int rows, int N,
                    float eps, void* stream);
+// Draft sampling parameters of ds41_markov_step (null = greedy): Gumbel-max over x / temperature with Philox uniforms
+// addressed by (seed, subsequence, offset + token / 4, token % 4).
+typedef struct {
+  float temperature;
+  unsigned long long seed, subsequence, offset;
+} ds41_draft_rng;
 int ds41_markov_step(const float* logits, const void* head, const void* embed, const int* prev_token, int v_local,
                      int v_offset, int rank, int vocab, float* block_val, int* block_idx, int n_blocks,
-                     unsigned int* ticket, float* best_val, int* best_idx, void* stream);
+                     unsigned int* ticket, float* best_val, int* best_idx, const ds41_draft_rng* rng, void* stream);
 int ds41_spec_feedback(const int* inputs, const int* chosen, int width, int forced_accept, int eos, int* accepted,
                        int* emitted, int* n_emitted, int* next_anchor, int* target_pos, int* draft_pos,
                        int* draft_hi, int* target_tokens, int* draft_tokens, long long* total_emitted, void* stream);

@@ -11,6 +11,7 @@
 //                  for benchmarking with random weights)
 #include "ds41_api.h"
 #include "ds41_launch.cuh"
+#include "ds41_philox.h"
 #include "ds41_ptx.cuh"
 
 namespace ds41 {
@@ -75,6 +76,10 @@ struct MarkovParams {
   unsigned int* ticket;           // zero before first use; reset by the finishing block
   float* best_val;                // [1]
   int* best_idx;                  // [1] global token id
+  // draft sampling: temperature > 0 turns the arg max into a Gumbel-max draw, key = x / T - log(-log(u)), with
+  // u = Philox(seed, subsequence, offset + token / 4)[token % 4]; temperature <= 0 is greedy
+  float temperature;
+  unsigned long long seed, subsequence, offset;
 };
 
 // grid: enough blocks of 256 threads; each warp strides over vocabulary rows. rank <= 256, multiple of 8.
@@ -109,8 +114,13 @@ __global__ void __launch_bounds__(256) markov_step_kernel(MarkovParams p) {
     }
     for (int o = lanes_per_row / 2; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     if (l == 0 && v < p.v_local && sub < rows_per_warp) {
-      const float x = p.logits[v] + acc;
+      float x = p.logits[v] + acc;
       const int tok = p.v_offset + v;
+      if (p.temperature > 0.f) {
+        const Philox4 rnd = philox4x32_10(p.seed, p.subsequence, p.offset + static_cast<unsigned long long>(tok >> 2));
+        const float u = philox_uniform(rnd.v[tok & 3]);
+        x = x / p.temperature - __logf(-__logf(u));
+      }
       if (x > best || (x == best && tok < best_i)) { best = x; best_i = tok; }
     }
   }
@@ -229,11 +239,14 @@ extern "C" int ds41_norm_rows(const float* planes, int splits, long long plane, 
 
 extern "C" int ds41_markov_step(const float* logits, const void* head, const void* embed, const int* prev_token,
                                 int v_local, int v_offset, int rank, int vocab, float* block_val, int* block_idx,
-                                int n_blocks, unsigned int* ticket, float* best_val, int* best_idx, void* stream) {
+                                int n_blocks, unsigned int* ticket, float* best_val, int* best_idx,
+                                const ds41_draft_rng* rng, void* stream) {
   if (v_local <= 0 || rank <= 0 || rank > 256 || (rank & 7) || (32 % (rank / 8)) != 0 || n_blocks <= 0)
     return cudaErrorInvalidValue;
   MarkovParams p{logits, static_cast<const __nv_bfloat16*>(head), static_cast<const __nv_bfloat16*>(embed),
-                 prev_token, v_local, v_offset, rank, vocab, block_val, block_idx, ticket, best_val, best_idx};
+                 prev_token, v_local, v_offset, rank, vocab, block_val, block_idx, ticket, best_val, best_idx,
+                 rng != nullptr ? rng->temperature : 0.f, rng != nullptr ? rng->seed : 0ull,
+                 rng != nullptr ? rng->subsequence : 0ull, rng != nullptr ? rng->offset : 0ull};
   return launch_pdl(markov_step_kernel, dim3(n_blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
 }
 

@@ -105,6 +105,21 @@ class DSparkDrafter:
         toks = [anchor] + [self.d.noise_token_id] * (w - 1)
         self.eng.set_rows(toks, list(range(pos, pos + w)), [slot] * w, row_hi=[pos + w - 1] * w)
 
+    def set_sampling(self, temperature: float = 0.0, seed: int = 0, subsequence: int = 0, offset: int = 0):
+        """Draft tokens are sampled (Gumbel-max with Philox numbers) when temperature > 0, greedy otherwise.  `offset`
+        is the first Philox counter of this draft pass; row j uses the block starting at offset + j * ceil(vocab/4)
+        (reserve width * ceil(vocab/4) counters per pass, e.g. with runtime.core.DraftRng)."""
+        self.sampling = (float(temperature), int(seed), int(subsequence), int(offset))
+
+    def _draft_rng(self, j: int):
+        import ctypes as C
+        t, seed, sub, off = getattr(self, "sampling", (0.0, 0, 0, 0))
+        if t <= 0.0:
+            return None
+        r = lib.DraftRng(t, seed & (2 ** 64 - 1), sub, off + j * ((self.cfg.vocab + 3) // 4))
+        self._rng_keep = getattr(self, "_rng_keep", [])[-16:] + [r]
+        return C.byref(r)
+
     def draft(self):
         """One draft pass over the rows prepared in the drafter engine's inputs -> self.drafts (device)."""
         e, k, t = self.eng, lib.kernels(), self.target
@@ -117,7 +132,7 @@ class DSparkDrafter:
             e._run("markov_step", k.ds41_markov_step, lib.ptr(e.logits[j]), lib.ptr(self.markov_head),
                    lib.ptr(self.markov_embed), lib.ptr(prev), e.V_local, e.rank * e.V_local, rank, self.cfg.vocab,
                    lib.ptr(self.block_val), lib.ptr(self.block_idx), self.n_blocks, lib.ptr(self.ticket),
-                   lib.ptr(e.best_val[j:j + 1]), lib.ptr(e.best_idx[j:j + 1]), lib.stream())
+                   lib.ptr(e.best_val[j:j + 1]), lib.ptr(e.best_idx[j:j + 1]), self._draft_rng(j), lib.stream())
             if e.world > 1:
                 e._signal()
                 e._run("draft_merge", k.ds41_argmax_merge, _offset_ptrs(e._val_ptrs, 4 * j, e.world),

@@ -65,6 +65,11 @@ class EpArgs(C.Structure):
     ]
 
 
+class DraftRng(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("seed", C.c_ulonglong), ("subsequence", C.c_ulonglong),
+                ("offset", C.c_ulonglong)]
+
+
 class SampleRow(C.Structure):
     _fields_ = [
         ("temperature", C.c_float), ("top_k", C.c_int), ("top_p", C.c_float), ("min_p", C.c_float),

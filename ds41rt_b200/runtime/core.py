@@ -366,3 +366,42 @@ class StubCopyEngine:
     @property
     def now_us(self) -> float:
         return float(core().ds41_stubcopy_now(self.h))
+
+
+def philox_uniform(seed: int, subsequence: int, offset: int, lane: int) -> float:
+    """The uniform in (0, 1) that draft sampling uses for token 4 * (offset - base) + lane."""
+    c = core()
+    c.ds41_philox_uniform.restype = C.c_float
+    c.ds41_philox_uniform.argtypes = [C.c_uint64, C.c_uint64, C.c_uint64, C.c_int]
+    return float(c.ds41_philox_uniform(seed & (2 ** 64 - 1), subsequence, offset, lane))
+
+
+class DraftRng:
+    """Per-request Philox subsequences with forward-only counter reservations (csrc/core/rng.cc)."""
+
+    def __init__(self):
+        c = core()
+        c.ds41_rng_create.restype = C.c_void_p
+        c.ds41_rng_destroy.argtypes = [C.c_void_p]
+        c.ds41_rng_reserve.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+        c.ds41_rng_fork.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64]
+        c.ds41_rng_release.argtypes = [C.c_void_p, C.c_uint64]
+        self._c, self.h = c, c.ds41_rng_create()
+
+    def reserve(self, request: int, counters: int):
+        sub, off = C.c_uint64(0), C.c_uint64(0)
+        if self._c.ds41_rng_reserve(self.h, request, counters, C.byref(sub), C.byref(off)) != 0:
+            raise ValueError("bad reservation")
+        return sub.value, off.value
+
+    def fork(self, parent: int, child: int):
+        if self._c.ds41_rng_fork(self.h, parent, child) != 0:
+            raise KeyError("unknown parent or existing child")
+
+    def release(self, request: int) -> bool:
+        return self._c.ds41_rng_release(self.h, request) == 0
+
+    def close(self):
+        if self.h:
+            self._c.ds41_rng_destroy(self.h)
+            self.h = None

@@ -171,3 +171,23 @@ def test_kv_pool_plan():
     want = K.plan_kv_groups(65536, 512, 16, 40, 455680, 1 << 40)
     assert want == 128 * 18 + 16 + 80
     assert K.plan_kv_groups(65536, 512, 16, 40, 455680, 455680 * 100) == 100
+
+
+def test_philox_vectors_and_reservations():
+    """Philox4x32-10 against the published known-answer vector, and forward-only per-request reservations."""
+    from ds41rt_b200.runtime import core as K
+    # Random123 KAT: counter = key = all ones -> 408f276d 41c83b0e a20bc7c6 6d5451fd
+    ones64 = 0xFFFFFFFFFFFFFFFF
+    got = [K.philox_uniform(ones64, ones64, ones64, lane) for lane in range(4)]
+    want_bits = [0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd]
+    for g, b in zip(got, want_bits):
+        assert g == ((b >> 9) + 0.5) / 8388608.0
+    rng = K.DraftRng()
+    a = rng.reserve(7, 100)
+    b = rng.reserve(7, 50)
+    c = rng.reserve(9, 10)
+    assert a == (1, 0) and b == (1, 100) and c == (2, 0)
+    rng.fork(7, 8)
+    assert rng.reserve(8, 5) == (3, 0) and rng.reserve(7, 1) == (1, 150)
+    assert rng.release(9) and not rng.release(9)
+    rng.close()

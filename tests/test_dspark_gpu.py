@@ -74,3 +74,40 @@ def test_forced_acceptance_schedule_advances_four_tokens_per_round():
     eng.check_status()
     assert int(spec.total.item()) == 24
     assert int(eng.row_pos[0].item()) == len(prompt) + 24
+
+
+def test_sampled_draft_step_follows_the_philox_gumbel_rule():
+    """markov_step with a temperature: the chosen token maximises x / T - log(-log(u)) with the host Philox oracle's
+    u for (seed, subsequence, offset + token / 4, token % 4); greedy when no rng is given."""
+    import ctypes as C
+    import math
+    from ds41rt_b200.ops import lib
+    from ds41rt_b200.runtime import core as K
+    k = lib.kernels()
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    V, rank = 1000, 64
+    logits = torch.randn(V, device=dev)
+    head = (torch.randn(V, rank, device=dev) * 0.3).bfloat16()
+    embed = (torch.randn(V, rank, device=dev) * 0.3).bfloat16()
+    prev = torch.tensor([17], dtype=torch.int32, device=dev)
+    nb = 16
+    bv, bi = torch.zeros(nb, device=dev), torch.zeros(nb, dtype=torch.int32, device=dev)
+    ticket = torch.zeros(1, dtype=torch.int32, device=dev)
+    out_v, out_i = torch.zeros(1, device=dev), torch.zeros(1, dtype=torch.int32, device=dev)
+    x = logits + head.float() @ embed[17].float()
+
+    def run(rng):
+        lib.check(k.ds41_markov_step(lib.ptr(logits), lib.ptr(head), lib.ptr(embed), lib.ptr(prev), V, 0, rank, V,
+                                     lib.ptr(bv), lib.ptr(bi), nb, lib.ptr(ticket), lib.ptr(out_v), lib.ptr(out_i),
+                                     C.byref(rng) if rng is not None else None, lib.stream()), "markov")
+        torch.cuda.synchronize()
+        return int(out_i[0])
+
+    assert run(None) == int(x.argmax())
+    T, seed, sub, off = 0.8, 1234, 5, 1000
+    u = torch.tensor([K.philox_uniform(seed, sub, off + t // 4, t % 4) for t in range(V)])
+    keys = x.cpu() / T - torch.log(-torch.log(u))
+    got = run(lib.DraftRng(T, seed, sub, off))
+    assert float(keys.max() - keys[got]) < 1e-3
+    assert got != run(lib.DraftRng(T, seed, sub + 1, off)) or got != run(lib.DraftRng(T, seed + 1, sub, off))
