@@ -18,5 +18,6 @@ cudaError_t make_tensor_map_3d(CUtensorMap* out, const void* base, TmaDtype dtyp
                                uint32_t box_cols, uint32_t box_rows, bool swizzle128);
 
 int sm_count();
+int last_tensor_map_result();   // CUresult of the most recent cuTensorMapEncodeTiled call (0 = success)
 
 }  // namespace ds41

@@ -749,6 +749,8 @@ static cudaError_t dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap
 
 using namespace ds41;
 
+extern "C" int ds41_last_tensor_map_result() { return ds41::last_tensor_map_result(); }
+
 extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   if (a == nullptr) return cudaErrorInvalidValue;
   const int M = a->M, N = a->N, K = a->K, batch = a->batch, kind = a->kind, out_mode = a->out_mode;

@@ -22,6 +22,8 @@ void resolve() {
 }
 }  // namespace
 
+static int g_last_result = 0;     // driver result of the most recent encode (diagnostics)
+
 cudaError_t make_tensor_map_3d(CUtensorMap* out, const void* base, TmaDtype dtype, uint64_t cols, uint64_t rows,
                                uint64_t batch, uint64_t row_stride_bytes, uint64_t batch_stride_bytes,
                                uint32_t box_cols, uint32_t box_rows, bool swizzle128) {
@@ -56,8 +58,11 @@ cudaError_t make_tensor_map_3d(CUtensorMap* out, const void* base, TmaDtype dtyp
   CUresult r = g_encode(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  g_last_result = static_cast<int>(r);
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
+
+int last_tensor_map_result() { return g_last_result; }
 
 int sm_count() {
   static int cached[64] = {0};
