@@ -783,20 +783,21 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   const int a_batches = a->a_batches > 0 ? a->a_batches : batch;
   const int b_batches = a->b_batch_kind == 1 ? 1 : (a->b_batch_kind == 0 ? a_batches : batch);
   const void* a_base = a->ag_world > 0 ? a->a_peers[a->ag_rank] : a->A;
-  // e2m1 operands: lda and a_batch_stride count elements, two per byte
-  cudaError_t e = a_fp4 ? make_tensor_map_3d(&tmA, a_base, TmaDtype::kU4x16Align16, K, a_rows, a_batches, a->lda / 2,
-                                             a->a_batch_stride / 2, bk, kBM, true)
-                        : make_tensor_map_3d(&tmA, a_base, dt, K, a_rows, a_batches, a->lda * elem,
-                                             a->a_batch_stride * elem, bk, kBM, true);
-  if (e != cudaSuccess) return e;
+  // e2m1 operands: strides count elements, two per byte in memory
+  cudaError_t e;
   if (kind == 3) {
-    // both operands e2m1, two per byte in memory and in shared memory; strides count elements
+    // both operands e2m1, packed in memory and in shared memory
     e = make_tensor_map_3d(&tmA, a_base, TmaDtype::kU4x16Align8, K, a_rows, a_batches, a->lda / 2, a->a_batch_stride / 2,
                            bk, kBM, true);
     if (e != cudaSuccess) return e;
     e = make_tensor_map_3d(&tmB, a->B, TmaDtype::kU4x16Align8, K, N, b_batches, a->ldb / 2, a->b_batch_stride / 2, bk, bn,
                            true);
   } else {
+    e = a_fp4 ? make_tensor_map_3d(&tmA, a_base, TmaDtype::kU4x16Align16, K, a_rows, a_batches, a->lda / 2,
+                                   a->a_batch_stride / 2, bk, kBM, true)
+              : make_tensor_map_3d(&tmA, a_base, dt, K, a_rows, a_batches, a->lda * elem, a->a_batch_stride * elem, bk,
+                                   kBM, true);
+    if (e != cudaSuccess) return e;
     e = make_tensor_map_3d(&tmB, a->B, dt, K, N, b_batches, a->ldb * elem, a->b_batch_stride * elem, bk, bn, true);
   }
   if (e != cudaSuccess) return e;
