@@ -172,7 +172,9 @@ def prefill_bench(args, fabric, cfg, n_layers):
                        "parallelism": f"tp{world}+ep{world}",
                        "experts": {"mxfp8": "fp8 e4m3, 128x128 ue8m0 block scales, 1x128 activation scales",
                                    "mxfp4": "fp4 e2m1 weights, 1x32 ue8m0 scales (official layout), fp8 e4m3 activations "
-                                            "with 1x128 scales", "bf16": "bf16"}[args.expert_dtype],
+                                            "with 1x128 scales", "bf16": "bf16",
+                                   "nvfp4": "NVFP4 W4A4: e2m1 weights and activations, e4m3 scale per 16, fp32 scale per "
+                                            "tensor"}[args.expert_dtype],
                        "l2": "no flush: every pass streams more weight bytes than the 126 MB L2",
                        "weights_gb_per_gpu": round(weights.nbytes() / 1e9, 2), "setup_s": round(setup_s, 1)},
             "clocks": clocks,
@@ -268,7 +270,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = fit to memory)")
     ap.add_argument("--prompt", type=int, default=4096)
     ap.add_argument("--model", default="flash", choices=["flash", "small", "tiny"])
-    ap.add_argument("--expert-dtype", default="mxfp8", choices=["mxfp8", "mxfp4", "bf16"])
+    ap.add_argument("--expert-dtype", default="mxfp8", choices=["mxfp8", "mxfp4", "nvfp4", "bf16"])
     ap.add_argument("--prefill-chunk", type=int, default=32)
     ap.add_argument("--e2e-steps", type=int, default=0, help="rounds/steps of the host-loop measurement (0 = --steps)")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly (for per-kernel profiling)")
@@ -418,7 +420,9 @@ def main():
                                        "accepted_per_round": args.accept} if spec else None,
                        "experts": {"mxfp8": "fp8 e4m3, 128x128 ue8m0 block scales, 1x128 activation scales",
                                    "mxfp4": "fp4 e2m1 weights, 1x32 ue8m0 scales (official layout), fp8 e4m3 activations "
-                                            "with 1x128 scales", "bf16": "bf16"}[args.expert_dtype],
+                                            "with 1x128 scales", "bf16": "bf16",
+                                   "nvfp4": "NVFP4 W4A4: e2m1 weights and activations, e4m3 scale per 16, fp32 scale per "
+                                            "tensor"}[args.expert_dtype],
                        "l2": "no flush: every step streams more weight bytes than the 126 MB L2",
                        "weights_gb_per_gpu": round(weights.nbytes() / 1e9, 2),
                        "kv_gb_per_gpu": round(eng.cache.nbytes() / 1e9, 3), "setup_s": round(setup_s, 1)},

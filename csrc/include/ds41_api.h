@@ -83,6 +83,7 @@ typedef struct ds41_gemm_args {
   // K must be a multiple of 256; lda / ldb / batch strides count elements; alpha (the product of the two global
   // scales, 0 = 1) multiplies the accumulators.
   float alpha;
+  const float* alpha_batch;   // optional: one more factor per A batch (a global scale per expert)
 } ds41_gemm_args;
 
 int ds41_gemm_tc(const ds41_gemm_args* args, void* stream);
@@ -302,9 +303,11 @@ int ds41_act_quant_mx_rows(const void* x, long long ldx, void* q, long long ldq,
                            const int* rows_dev, void* stream);
 
 // NVFP4 activation rows (e2m1 two per byte + E4M3 scale atoms per 16 elements, relative to global_scale); ldq counts
-// elements; rows >= *rows_dev (if given) are skipped.
+// elements; rows >= *rows_dev (if given) are skipped; `batch` row blocks of `rows` rows each (strides in elements of x / q
+// and bytes of sf), of which only the first *n_active (if given) are processed.
 int ds41_act_quant_nvfp4_rows(const void* x, long long ldx, void* q, long long ldq, void* sf, int rows, int K,
-                              float global_scale, const int* rows_dev, void* stream);
+                              float global_scale, const int* rows_dev, int batch, long long x_batch_stride,
+                              long long q_batch_stride, long long sf_batch_stride, const int* n_active, void* stream);
 
 #ifdef __cplusplus
 }

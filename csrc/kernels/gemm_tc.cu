@@ -56,6 +56,7 @@ struct GemmParams {
   float act_limit;        // mode 4: SwiGLU clamp
   int static_operand;     // 1: A holds weights, 2: B holds weights (may be fetched before the dependency wait)
   float alpha;            // kind 3: product of the two tensors' global scales, applied to the accumulators
+  const float* alpha_batch;   // optional extra factor per A batch (one global scale per expert)
   int a_fp4;              // MX kind: A holds e2m1 values (packed in global memory, one per byte in shared memory)
   // grouped tokens (expert-parallel prefill, swap-AB): the N operand is a flat buffer of rows sorted by expert;
   // tile j covers rows [tile_row0[j], tile_end[j]) of expert tile_group[j]; *n_tiles_dev tiles are live
@@ -412,6 +413,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * Cfg::kAccCols;
       const long long obase = (table ? 0ll : b * p.out_batch_stride) + sp * p.out_split_stride;
       constexpr int kChunk = BN >= 32 ? 32 : BN;
+      float alpha = p.alpha;
+      if (KIND == 3 && p.alpha_batch != nullptr) alpha *= __ldg(p.alpha_batch + (p.batch_map != nullptr ? p.batch_map[b] : b));
 #pragma unroll 1
       for (int c = 0; c < BN; c += kChunk) {
         uint32_t v[32];
@@ -431,7 +434,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tmem_wait_ld();
         if constexpr (KIND == 3) {
 #pragma unroll
-          for (int j = 0; j < kChunk; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * p.alpha);
+          for (int j = 0; j < kChunk; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
         }
         const int n0 = n_base + c;
         const float rw_lane = rw_next;
@@ -509,7 +512,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tmem_wait_ld();
             if constexpr (KIND == 3) {
 #pragma unroll
-              for (int j = 0; j < kChunk; ++j) u[j] = __float_as_uint(__uint_as_float(u[j]) * p.alpha);
+              for (int j = 0; j < kChunk; ++j) u[j] = __float_as_uint(__uint_as_float(u[j]) * alpha);
             }
             __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + obase + m;
             // the chunk's route weights were fetched with one coalesced load and are handed out by shuffle: a load per
@@ -876,6 +879,7 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   p.static_operand = a->static_operand;
   p.a_fp4 = a_fp4 ? 1 : 0;
   p.alpha = a->alpha != 0.f ? a->alpha : 1.f;
+  p.alpha_batch = a->alpha_batch;
   p.status = a->status;
   const long long n_t = a->tile_group != nullptr ? a->max_tiles : (N + bn - 1) / bn;
   const long long tiles = 1ll * ((M + kBM - 1) / kBM) * n_t * k_splits * (a->tile_group != nullptr ? 1 : batch);

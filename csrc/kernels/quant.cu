@@ -143,12 +143,18 @@ __device__ __forceinline__ uint32_t e2m1_code(float v) {
 __global__ void __launch_bounds__(256)
 act_quant_nvfp4_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q, long long ldq,
                             uint8_t* __restrict__ sf, int rows, int K, float global_scale,
-                            const int* __restrict__ rows_dev) {
+                            const int* __restrict__ rows_dev, long long x_bs, long long q_bs, long long sf_bs,
+                            const int* __restrict__ n_active) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   pdl_launch_dependents();
   pdl_wait();
+  const int b = blockIdx.y;
+  if (n_active != nullptr && b >= *n_active) return;
   const int live = rows_dev != nullptr ? min(rows, *rows_dev) : rows;
   const int k_atoms = K / 64;
+  x += b * x_bs;
+  q += b * (q_bs / 2);
+  sf += b * sf_bs;
   for (int r = blockIdx.x * 8 + warp; r < live; r += gridDim.x * 8) {
     const __nv_bfloat16* src = x + 1ll * r * ldx;
     uint8_t* dst = q + 1ll * r * (ldq / 2);
@@ -189,12 +195,16 @@ act_quant_nvfp4_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, 
 using namespace ds41;
 
 extern "C" int ds41_act_quant_nvfp4_rows(const void* x, long long ldx, void* q, long long ldq, void* sf, int rows,
-                                         int K, float global_scale, const int* rows_dev, void* stream) {
-  if (rows <= 0 || K <= 0 || K % 64 != 0 || (ldx & 7) || (ldq & 7) || !(global_scale > 0.f)) return cudaErrorInvalidValue;
+                                         int K, float global_scale, const int* rows_dev, int batch,
+                                         long long x_batch_stride, long long q_batch_stride, long long sf_batch_stride,
+                                         const int* n_active, void* stream) {
+  if (rows <= 0 || K <= 0 || K % 64 != 0 || (ldx & 7) || (ldq & 7) || !(global_scale > 0.f) || batch <= 0 ||
+      (q_batch_stride & 1))
+    return cudaErrorInvalidValue;
   const int blocks = min((rows + 7) / 8, 8 * sm_count_cached());
-  return launch_pdl(act_quant_nvfp4_rows_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
+  return launch_pdl(act_quant_nvfp4_rows_kernel, dim3(blocks, batch), dim3(256), 0, static_cast<cudaStream_t>(stream),
                     static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(q), ldq, static_cast<uint8_t*>(sf),
-                    rows, K, global_scale, rows_dev);
+                    rows, K, global_scale, rows_dev, x_batch_stride, q_batch_stride, sf_batch_stride, n_active);
 }
 
 extern "C" int ds41_act_quant_mx_rows(const void* x, long long ldx, void* q, long long ldq, void* sf, int rows, int K,

@@ -108,7 +108,7 @@ def main(argv=None) -> int:
     model_args(ps)
     ps.add_argument("--checkpoint", default="", help="directory with model.safetensors.index.json (official layout)")
     ps.add_argument("--tokenizer", default="", help="tokenizer.json; default: byte-level tokenizer")
-    ps.add_argument("--expert-dtype", default="mxfp8", choices=["mxfp8", "mxfp4", "bf16"])
+    ps.add_argument("--expert-dtype", default="mxfp8", choices=["mxfp8", "mxfp4", "nvfp4", "bf16"])
     ps.add_argument("--host", default="127.0.0.1")
     ps.add_argument("--port", type=int, default=8000)
     ps.add_argument("--device", type=int, default=0)

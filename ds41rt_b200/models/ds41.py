@@ -105,6 +105,34 @@ def dequantize_expert_fp4(q: torch.Tensor, sf_atoms: torch.Tensor) -> torch.Tens
     return Q.dequant_mxfp4(q.cpu(), unpack_sf_atoms(sf_atoms.cpu(), q.shape[0]), 32)
 
 
+def quantize_expert_stack_nvfp4(w: torch.Tensor, device):
+    """[E, n, k] fp32 -> (e2m1 codes two per byte [E, n, k/2], E4M3 scale atoms [E, n/128, k/64, 512], global scales [E]):
+    the NVFP4 W4A4 expert variant (one E4M3 scale per 16 elements and one fp32 scale per tensor)."""
+    from ..ops import quant_ref as Q
+    from ..ops.mx import pack_sf_atoms
+    qs, sfs, gs = [], [], []
+    for e in range(w.shape[0]):
+        q, bs, g = Q.quant_nvfp4(w[e])
+        qs.append(q)
+        sfs.append(pack_sf_atoms(bs.view(torch.uint8)))
+        gs.append(float(g))
+    return (torch.stack(qs).to(device).contiguous(), torch.stack(sfs).to(device).contiguous(),
+            torch.tensor(gs, dtype=torch.float32, device=device))
+
+
+def dequantize_expert_nvfp4(q: torch.Tensor, sf_atoms: torch.Tensor, gs: float) -> torch.Tensor:
+    from ..ops import quant_ref as Q
+    from ..ops.mx import unpack_sf_atoms
+    bs = unpack_sf_atoms(sf_atoms.cpu(), q.shape[0]).view(torch.float8_e4m3fn)
+    return Q.dequant_nvfp4(q.cpu(), bs, gs)
+
+
+# fixed per-tensor scales of the NVFP4 activations (ModelOpt's input_scale): FC1 sees normalised hidden rows, FC2 the
+# clamped SwiGLU output times the route weight
+NVFP4_IN_SCALE_FC1 = 16.0 / (448.0 * 6.0)
+NVFP4_IN_SCALE_FC2 = 8.0 / (448.0 * 6.0)
+
+
 def dequantize_expert(q: torch.Tensor, sf_atoms: torch.Tensor) -> torch.Tensor:
     """Inverse of quantize_expert_stack for one expert (used by tests to feed the oracle)."""
     from ..ops import quant_ref as Q
@@ -209,6 +237,9 @@ class EngineWeights:
             elif expert_dtype == "mxfp4":
                 lw.w13, lw.w13_sf = quantize_expert_stack_fp4(w13, device)
                 lw.w2, lw.w2_sf = quantize_expert_stack_fp4(w2, device)
+            elif expert_dtype == "nvfp4":
+                lw.w13, lw.w13_sf, lw.w13_gs = quantize_expert_stack_nvfp4(w13, device)
+                lw.w2, lw.w2_sf, lw.w2_gs = quantize_expert_stack_nvfp4(w2, device)
             else:
                 lw.w13, lw.w2 = dev(w13), dev(w2)
             ew.layers.append(lw)
@@ -290,6 +321,24 @@ class EngineWeights:
                 lw.w2 = rnd8((EL, H, I))
                 lw.w13_sf = torch.full((EL, 2 * I // 128, H // 128, 512), 127 - 11, dtype=torch.uint8, device=device)
                 lw.w2_sf = torch.full((EL, H // 128, I // 128, 512), 127 - 11, dtype=torch.uint8, device=device)
+            elif expert_dtype == "nvfp4":
+                # uniform random E2M1 codes, every 1x16 scale 1.0 (E4M3 0x38) and a global scale of 0.008 per expert:
+                # dequantised std about 0.02
+                def rnd4n(shape):
+                    out = torch.empty(shape, dtype=torch.uint8, device=device)
+                    flat = out.view(-1)
+                    step = 1 << 27
+                    for i in range(0, flat.numel(), step):
+                        n = min(step, flat.numel() - i)
+                        flat[i:i + n] = torch.randint(0, 256, (n,), generator=gen, device=device, dtype=torch.uint8)
+                    return out
+                I = cfg.inter
+                lw.w13 = rnd4n((EL, 2 * I, H // 2))
+                lw.w2 = rnd4n((EL, H, I // 2))
+                lw.w13_sf = torch.full((EL, 2 * I // 128, H // 64, 512), 0x38, dtype=torch.uint8, device=device)
+                lw.w2_sf = torch.full((EL, H // 128, I // 64, 512), 0x38, dtype=torch.uint8, device=device)
+                lw.w13_gs = torch.full((EL,), 0.008, dtype=F32, device=device)
+                lw.w2_gs = torch.full((EL,), 0.008, dtype=F32, device=device)
             elif expert_dtype == "mxfp4":
                 # uniform random E2M1 codes (two per byte) with every 1x32 scale 2^-7: dequantised std about 0.024
                 def rnd4(shape):
@@ -541,6 +590,7 @@ class DS41Engine:
         self.row_w = z((self.max_active, Rm), F32)
         self.slot_of = z((R, self.topk), I32)
         self.act = z((self.max_active, Rm, cfg.inter), BF16)
+        self.nv = weights.expert_dtype == "nvfp4"         # W4A4: e2m1 weights and activations, E4M3 scales per 16
         self.mx = weights.expert_dtype in ("mxfp8", "mxfp4")
         self.a_fmt = 1 if weights.expert_dtype == "mxfp4" else 0     # routed expert weights in E2M1 (two per byte)
         if self.mx:
@@ -550,6 +600,13 @@ class DS41Engine:
             self.xq_sf = z(((R + 127) // 128, H // 128, 512), torch.uint8)
             self.actq = z((self.max_active, Rm, cfg.inter), torch.uint8)
             self.actq_sf = z((self.max_active, ra, cfg.inter // 128, 512), torch.uint8)
+        if self.nv:
+            assert H % 256 == 0 and cfg.inter % 256 == 0
+            ra = (Rm + 127) // 128
+            self.xq4 = z((R, H // 2), torch.uint8)
+            self.xq4_sf = z(((R + 127) // 128, H // 64, 512), torch.uint8)
+            self.actq4 = z((self.max_active, Rm, cfg.inter // 2), torch.uint8)
+            self.actq4_sf = z((self.max_active, ra, cfg.inter // 64, 512), torch.uint8)
         self.fc2 = z((self.max_active, Rm, H), F32)
         self.planes_shared = z((self.max_splits, R, H), F32)
         # head
@@ -824,7 +881,31 @@ class DS41Engine:
                 I = cfg.inter
                 bn = G.pick_bn(R)
                 # FC1: act[slot][row][i] = swiglu(W1 x, W3 x) * route weight;  FC2: fc2[slot][row][h]
-                if self.mx:
+                if self.nv:
+                    ra = (R + 127) // 128
+                    zero = C.c_longlong(0)
+                    self._run("act_quant x", k.ds41_act_quant_nvfp4_rows, lib.ptr(self.xn), C.c_longlong(H),
+                              lib.ptr(self.xq4), C.c_longlong(H), lib.ptr(self.xq4_sf), R, H,
+                              C.c_float(NVFP4_IN_SCALE_FC1), None, 1, zero, zero, zero, None, st())
+                    self._run("gemm_fc1", G.gemm_raw, lw.w13, self.xq4, self.act, I, R, H, lda=H, ldb=H, ldo=I, kind=3,
+                              out_mode=4, bn=max(bn, 32), batch=self.max_active, a_batches=EL, a_batch_stride=2 * I * H,
+                              out_batch_stride=R * I, batch_map=self.active, n_active=self.n_active, b_batch_kind=1,
+                              up_row_offset=I, row_w=self.row_w, row_w_ld=self.moe_rows, act_limit=cfg.swiglu_limit,
+                              sfa=lw.w13_sf, sfa_batch_stride=lw.w13_sf[0].numel(), sfb=self.xq4_sf, status=self.status,
+                              alpha=NVFP4_IN_SCALE_FC1, alpha_batch=lw.w13_gs)
+                    sf_slot = ra * (I // 64) * 512
+                    self._run("act_quant act", k.ds41_act_quant_nvfp4_rows, lib.ptr(self.act), C.c_longlong(I),
+                              lib.ptr(self.actq4), C.c_longlong(I), lib.ptr(self.actq4_sf), R, I,
+                              C.c_float(NVFP4_IN_SCALE_FC2), None, self.max_active, C.c_longlong(R * I),
+                              C.c_longlong(R * I), C.c_longlong(sf_slot), lib.ptr(self.n_active), st())
+                    self._run("gemm_fc2", G.gemm_raw, lw.w2, self.actq4, self.fc2, H, R, I, lda=I, ldb=I, ldo=H, kind=3,
+                              out_mode=5, bn=max(bn, 32), batch=self.max_active, a_batches=EL, a_batch_stride=H * I,
+                              b_batch_stride=R * I, out_batch_stride=R * H, batch_map=self.active,
+                              n_active=self.n_active, b_batch_kind=2, row_w=self.row_w, row_w_ld=self.moe_rows,
+                              sfa=lw.w2_sf, sfa_batch_stride=lw.w2_sf[0].numel(), sfb=self.actq4_sf,
+                              sfb_batch_stride=sf_slot, status=self.status, alpha=NVFP4_IN_SCALE_FC2,
+                              alpha_batch=lw.w2_gs)
+                elif self.mx:
                     ra = (R + 127) // 128
                     self._run("gemm_fc1", G.gemm_raw, lw.w13, self.xq, self.act, I, R, H, lda=H, ldb=H, ldo=I, kind=2, out_mode=4, bn=bn,
                                batch=self.max_active, a_batches=EL, a_batch_stride=2 * I * H, out_batch_stride=R * I,
@@ -875,7 +956,9 @@ class DS41Engine:
         per_rank = (self.max_rows + self.world - 1) // self.world
         self._ep = ExpertParallelMoE(self.fabric, lw.w13, lw.w2, topk=lw.topk, max_tokens=per_rank,
                                      act_limit=self.cfg.swiglu_limit, w13_sf=getattr(lw, "w13_sf", None),
-                                     w2_sf=getattr(lw, "w2_sf", None), fp4=self.a_fmt == 1)
+                                     w2_sf=getattr(lw, "w2_sf", None), fp4=self.a_fmt == 1,
+                                     nvfp4=(NVFP4_IN_SCALE_FC1, NVFP4_IN_SCALE_FC2) if self.nv else None,
+                                     w13_gs=getattr(lw, "w13_gs", None), w2_gs=getattr(lw, "w2_gs", None))
 
     def _moe_sorted(self, R: int, lw: LayerWeights):
         """Routed + shared experts of a long pass: this rank's slice of the rows is dispatched to the experts' owners,
@@ -891,7 +974,8 @@ class DS41Engine:
             self._make_ep(lw)
         lo, hi = R * self.rank // self.world, R * (self.rank + 1) // self.world
         ep = self._ep
-        ep.set_weights(lw.w13, lw.w2, getattr(lw, "w13_sf", None), getattr(lw, "w2_sf", None))
+        ep.set_weights(lw.w13, lw.w2, getattr(lw, "w13_sf", None), getattr(lw, "w2_sf", None),
+                       getattr(lw, "w13_gs", None), getattr(lw, "w2_gs", None))
         if self.only is None or "ep_moe" in self.only:
             self.launches += 7
             self._run("ep_moe", ep.forward, self.xn[lo:hi], self.ids[lo:hi], self.route_w[lo:hi], self.moe_plane[lo:hi],

@@ -97,10 +97,15 @@ def swiglu_clamped(gate: torch.Tensor, up: torch.Tensor, limit: float) -> torch.
     return F.silu(gate) * up
 
 
-def expert_ffn(x, w1, w3, w2, limit, route_w=None):
+def expert_ffn(x, w1, w3, w2, limit, route_w=None, act_qdq=None):
+    """act_qdq = (f_in, f_mid): optional quantise-dequantise of the FC1 and FC2 inputs (W4A4 / W8A8 expert variants)."""
+    if act_qdq is not None:
+        x = act_qdq[0](x)
     act = swiglu_clamped(x @ w1.float().t(), x @ w3.float().t(), limit)
     if route_w is not None:
         act = act * route_w[:, None]          # route weight is applied before FC2
+    if act_qdq is not None:
+        act = act_qdq[1](act.bfloat16().float())
     return act @ w2.float().t()
 
 
@@ -260,7 +265,8 @@ class ReferenceModel:
             rw = (wts * hit)[rows].sum(-1)
             out[rows] += expert_ffn(xn[rows], self._g(f"{p}.ffn.experts.{e}.w1.weight"),
                                     self._g(f"{p}.ffn.experts.{e}.w3.weight"),
-                                    self._g(f"{p}.ffn.experts.{e}.w2.weight"), cfg.swiglu_limit, rw)
+                                    self._g(f"{p}.ffn.experts.{e}.w2.weight"), cfg.swiglu_limit, rw,
+                                    getattr(self, "expert_act_qdq", None))
         out = out + expert_ffn(xn, self._g(f"{p}.ffn.shared_experts.w1.weight"),
                                self._g(f"{p}.ffn.shared_experts.w3.weight"),
                                self._g(f"{p}.ffn.shared_experts.w2.weight"), cfg.swiglu_limit)

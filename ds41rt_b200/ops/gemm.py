@@ -41,7 +41,7 @@ def gemm_raw(A, B, out, M, N, K, *, lda, ldb, ldo, kind=0, out_mode=0, k_splits=
              a_batch_stride=0, b_batch_stride=0, out_batch_stride=0, a_batches=0, split_workspace=None,
              sfa=None, sfb=None, sfa_batch_stride=0, sfb_batch_stride=0, batch_map=None, n_active=None,
              b_batch_kind=0, up_row_offset=0, row_w=None, row_w_ld=0, act_limit=10.0, status=None,
-             static_operand=0, a_format=0, col_limit=None, alpha=0.0):
+             static_operand=0, a_format=0, col_limit=None, alpha=0.0, alpha_batch=None):
     a = lib.GemmArgs()
     a.A, a.B, a.out = lib.ptr(A), lib.ptr(B), lib.ptr(out)
     a.split_workspace = lib.ptr(split_workspace)
@@ -57,6 +57,7 @@ def gemm_raw(A, B, out, M, N, K, *, lda, ldb, ldo, kind=0, out_mode=0, k_splits=
     a.a_format = a_format
     a.col_limit = lib.ptr(col_limit)
     a.alpha = alpha
+    a.alpha_batch = lib.ptr(alpha_batch)
     lib.check(lib.kernels().ds41_gemm_tc(C.byref(a), lib.stream()), "ds41_gemm_tc")
 
 

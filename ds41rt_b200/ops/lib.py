@@ -35,7 +35,7 @@ class GemmArgs(C.Structure):
         ("a_peers", C.c_void_p * 8), ("ag_arrive", C.c_void_p * 8), ("ag_epoch", C.c_void_p), ("rs_out", C.c_void_p * 8),
         ("tile_group", C.c_void_p), ("tile_row0", C.c_void_p), ("tile_end", C.c_void_p), ("n_tiles_dev", C.c_void_p),
         ("scatter_meta", C.c_void_p), ("wait_flags", C.c_void_p), ("wait_epoch", C.c_void_p),
-        ("scatter_out", C.c_void_p * 8), ("max_tiles", C.c_int), ("wait_world", C.c_int), ("a_format", C.c_int), ("col_limit", C.c_void_p), ("alpha", C.c_float),
+        ("scatter_out", C.c_void_p * 8), ("max_tiles", C.c_int), ("wait_world", C.c_int), ("a_format", C.c_int), ("col_limit", C.c_void_p), ("alpha", C.c_float), ("alpha_batch", C.c_void_p),
     ]
 
 

@@ -33,22 +33,28 @@ def _round_up(x: int, m: int) -> int:
 class ExpertParallelMoE:
     def __init__(self, fabric: Fabric, w13: torch.Tensor, w2: torch.Tensor, *, topk: int, max_tokens: int,
                  act_limit: float = 10.0, capacity: Optional[int] = None, w13_sf: Optional[torch.Tensor] = None,
-                 w2_sf: Optional[torch.Tensor] = None, fp4: bool = False):
+                 w2_sf: Optional[torch.Tensor] = None, fp4: bool = False, nvfp4=None,
+                 w13_gs: Optional[torch.Tensor] = None, w2_gs: Optional[torch.Tensor] = None):
         """w13: [E_local, 2*I, H] (gate rows then up rows), w2: [E_local, H, I]; bf16, or e4m3 with UE8M0 scale atoms,
-        or (fp4) E2M1 codes two per byte ([.., H/2] / [.., I/2] uint8) with UE8M0 scale atoms."""
+        or (fp4) E2M1 codes two per byte ([.., H/2] / [.., I/2] uint8) with UE8M0 scale atoms, or (nvfp4 = the two
+        activation scales) E2M1 codes with E4M3 scale atoms per 16 and one global scale per expert (w13_gs / w2_gs):
+        then the received rows and the FC1 output are quantised to NVFP4 too (W4A4)."""
         self.f = fabric
         self.w13, self.w2, self.w13_sf, self.w2_sf = w13, w2, w13_sf, w2_sf
-        self.mx = w13_sf is not None
-        self.fp4 = fp4
+        self.mx = w13_sf is not None and nvfp4 is None
+        self.fp4 = fp4 or nvfp4 is not None
+        self.nv = nvfp4
+        self.w13_gs, self.w2_gs = w13_gs, w2_gs
         self.e_local, two_i, self.H = w13.shape
-        if fp4:
+        if self.fp4:
             self.H *= 2
         self.I = two_i // 2
         self.topk, self.max_tokens, self.act_limit = topk, max_tokens, act_limit
         W, dev = fabric.world, fabric.device
         assert self.H % 128 == 0 and self.I % 128 == 0 and W <= 8
-        self.bn = 64 if self.mx else 128          # FC1: gate and up accumulators share tensor memory
-        self.bn2 = 128 if self.mx else 256         # FC2
+        scaled = self.mx or self.nv is not None
+        self.bn = 64 if scaled else 128           # FC1: gate and up accumulators share tensor memory
+        self.bn2 = 128 if scaled else 256          # FC2
         worst = W * max_tokens * topk
         self.cap = _round_up(min(worst, capacity) if capacity else worst, 128) + 128 * self.e_local
         self.max_tiles = self.cap // self.bn + self.e_local
@@ -82,6 +88,13 @@ class ExpertParallelMoE:
         self.total_rows = torch.zeros(1, **i32)
         self.status = lib.new_status(dev)
         self.act = torch.zeros(cap, self.I, dtype=torch.bfloat16, device=dev)
+        if self.nv is not None:
+            u8 = dict(dtype=torch.uint8, device=dev)
+            assert H % 256 == 0 and self.I % 256 == 0
+            self.xq = torch.zeros(cap, H // 2, **u8)
+            self.xq_sf = torch.zeros(cap // 128 * (H // 64) * 512, **u8)
+            self.actq = torch.zeros(cap, self.I // 2, **u8)
+            self.actq_sf = torch.zeros(cap // 128 * (self.I // 64) * 512, **u8)
         if self.mx:
             u8 = dict(dtype=torch.uint8, device=dev)
             self.xq = torch.zeros(cap, H, **u8)
@@ -91,10 +104,12 @@ class ExpertParallelMoE:
         self.dispatch_blocks = 4 * 148
         self.marks = None          # list of (name, event) while phase timing is on
 
-    def set_weights(self, w13, w2, w13_sf=None, w2_sf=None) -> None:
+    def set_weights(self, w13, w2, w13_sf=None, w2_sf=None, w13_gs=None, w2_gs=None) -> None:
         """Point the layer at another expert stack of the same shape and kind (one instance serves every MoE layer)."""
-        assert w13.shape == self.w13.shape and w2.shape == self.w2.shape and (w13_sf is not None) == self.mx
+        assert w13.shape == self.w13.shape and w2.shape == self.w2.shape
+        assert (w13_sf is not None) == (self.mx or self.nv is not None)
         self.w13, self.w2, self.w13_sf, self.w2_sf = w13, w2, w13_sf, w2_sf
+        self.w13_gs, self.w2_gs = w13_gs, w2_gs
 
     # ------------------------------------------------------------------ argument blocks
     def _ep_args(self, x, ids, weights, tokens) -> lib.EpArgs:
@@ -120,8 +135,8 @@ class ExpertParallelMoE:
         a.lda, a.ldb, a.ldo = lda, K, ldo
         a.M, a.N, a.K, a.batch, a.a_batches = M, self.cap, K, self.e_local, self.e_local
         a.a_batch_stride = A.stride(0) * (2 if self.fp4 else 1)      # counted in elements
-        a.a_format = 1 if self.fp4 else 0
-        a.kind, a.out_mode, a.k_splits, a.b_batch_kind = (2 if self.mx else 0), out_mode, 1, 1
+        a.a_format = 1 if (self.fp4 and self.nv is None) else 0
+        a.kind, a.out_mode, a.k_splits, a.b_batch_kind = (3 if self.nv is not None else 2 if self.mx else 0), out_mode, 1, 1
         a.bn = self.bn2 if table else self.bn
         t0 = table * self.max_tiles
         a.tile_group, a.tile_row0 = lib.ptr(self.tile_group[t0:]), lib.ptr(self.tile_row0[t0:])
@@ -172,7 +187,24 @@ class ExpertParallelMoE:
         self._mark("count+plan")
         lib.check(k.ds41_ep_dispatch(C.byref(a), self.dispatch_blocks, st()), "ep_dispatch")
         self._mark("dispatch")
-        if self.mx:
+        if self.nv is not None:
+            lib.check(k.ds41_ep_wait(C.byref(a), 2, st()), "ep_wait")
+            cap, zero = self.cap, C.c_longlong(0)
+            lib.check(k.ds41_act_quant_nvfp4_rows(lib.ptr(self.recv_x), C.c_longlong(H), lib.ptr(self.xq), C.c_longlong(H),
+                                                  lib.ptr(self.xq_sf), cap, H, C.c_float(self.nv[0]),
+                                                  lib.ptr(self.total_rows), 1, zero, zero, zero, None, st()), "quant")
+            self._grouped(self.w13, self.xq, self.act, I, H, lda=H, ldo=I, out_mode=4, up_row_offset=I,
+                          sfa=self.w13_sf, sfa_batch_stride=self.w13_sf[0].numel(), sfb=self.xq_sf, alpha=self.nv[0],
+                          alpha_batch=self.w13_gs)
+            self._mark("wait+quant+fc1")
+            lib.check(k.ds41_act_quant_nvfp4_rows(lib.ptr(self.act), C.c_longlong(I), lib.ptr(self.actq), C.c_longlong(I),
+                                                  lib.ptr(self.actq_sf), cap, I, C.c_float(self.nv[1]),
+                                                  lib.ptr(self.total_rows), 1, zero, zero, zero, None, st()), "quant")
+            self._grouped(self.w2, self.actq, self.comb, H, I, lda=I, ldo=H, out_mode=7, table=1, sfa=self.w2_sf,
+                          sfa_batch_stride=self.w2_sf[0].numel(), sfb=self.actq_sf, alpha=self.nv[1],
+                          alpha_batch=self.w2_gs)
+            self._mark("quant+fc2")
+        elif self.mx:
             lib.check(k.ds41_ep_wait(C.byref(a), 2, st()), "ep_wait")
             cap = self.cap
             lib.check(k.ds41_act_quant_mx_rows(lib.ptr(self.recv_x), C.c_longlong(H), lib.ptr(self.xq), C.c_longlong(H),

@@ -128,7 +128,8 @@ def test_verify_rows_equal_single_steps():
     assert chunk == seq[1:6]
 
 
-@pytest.mark.parametrize("dtype,chunk", [("mxfp8", 8), ("mxfp8", 40), ("mxfp4", 8), ("mxfp4", 40)])
+@pytest.mark.parametrize("dtype,chunk", [("mxfp8", 8), ("mxfp8", 40), ("mxfp4", 8), ("mxfp4", 40), ("nvfp4", 8),
+                                         ("nvfp4", 40)])
 def test_block_scaled_experts_match_oracle(dtype, chunk):
     """Routed experts stored as FP8 E4M3 + 128x128 power-of-two block scales, run through the block-scaled
     tcgen05 path, vs the oracle evaluated on the dequantised weights (chunk 40: the sorted expert path)."""
@@ -142,14 +143,29 @@ def test_block_scaled_experts_match_oracle(dtype, chunk):
     ew = EngineWeights.from_fp32(cfg, wr, 0, 1, torch.device("cuda"), expert_dtype=dtype)
     if dtype == "mxfp4":
         dequantize_expert = dequantize_expert_fp4
+    if dtype == "nvfp4":
+        from ds41rt_b200.models.ds41 import dequantize_expert_nvfp4
     I = cfg.inter
     for l, lw in enumerate(ew.layers):
         for e in range(cfg.n_experts):
+            if dtype == "nvfp4":
+                w13 = dequantize_expert_nvfp4(lw.w13[e], lw.w13_sf[e], float(lw.w13_gs[e]))
+                wr[f"layers.{l}.ffn.experts.{e}.w1.weight"] = w13[:I]
+                wr[f"layers.{l}.ffn.experts.{e}.w3.weight"] = w13[I:]
+                wr[f"layers.{l}.ffn.experts.{e}.w2.weight"] = dequantize_expert_nvfp4(lw.w2[e], lw.w2_sf[e],
+                                                                                      float(lw.w2_gs[e]))
+                continue
             w13 = dequantize_expert(lw.w13[e], lw.w13_sf[e])
             wr[f"layers.{l}.ffn.experts.{e}.w1.weight"] = w13[:I]
             wr[f"layers.{l}.ffn.experts.{e}.w3.weight"] = w13[I:]
             wr[f"layers.{l}.ffn.experts.{e}.w2.weight"] = dequantize_expert(lw.w2[e], lw.w2_sf[e])
     ref = ReferenceModel(cfg, wr)
+    if dtype == "nvfp4":
+        # W4A4: the oracle quantises the expert inputs the same way (fixed per-tensor scales, E4M3 scale per 16)
+        from ds41rt_b200.models.ds41 import NVFP4_IN_SCALE_FC1, NVFP4_IN_SCALE_FC2
+        from ds41rt_b200.ops import quant_ref as Q
+        qdq = lambda gs: (lambda t: Q.dequant_nvfp4(*Q.quant_nvfp4(t.bfloat16().float(), gs)[:2], gs))
+        ref.expert_act_qdq = (qdq(NVFP4_IN_SCALE_FC1), qdq(NVFP4_IN_SCALE_FC2))
     eng = DS41Engine(cfg, ew, max_rows=chunk, slots=1, max_ctx=256)
     g = torch.Generator().manual_seed(5)
     prompt = torch.randint(0, cfg.vocab, (40,), generator=g)

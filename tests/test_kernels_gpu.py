@@ -368,7 +368,8 @@ def test_nvfp4_activation_quantiser_matches_oracle():
     q = torch.zeros(rows, K // 2, dtype=torch.uint8, device="cuda")
     sf = torch.zeros((rows + 127) // 128, K // 64, 512, dtype=torch.uint8, device="cuda")
     lib.check(k.ds41_act_quant_nvfp4_rows(lib.ptr(x), C.c_longlong(K), lib.ptr(q), C.c_longlong(K), lib.ptr(sf), rows,
-                                          K, C.c_float(gs), None, lib.stream()), "quant")
+                                          K, C.c_float(gs), None, 1, C.c_longlong(0), C.c_longlong(0), C.c_longlong(0), None,
+                                          lib.stream()), "quant")
     torch.cuda.synchronize()
     assert torch.equal(q, want_q)
     want_atoms = pack_sf_atoms(want_s.view(torch.uint8))
