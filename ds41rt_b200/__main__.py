@@ -75,7 +75,15 @@ def cmd_serve(args) -> int:
         follower_loop(eng, ctl, on_error=lambda e: print(f"rank {rank}: {e}", file=sys.stderr, flush=True))
         return 0
     lead = LeaderEngine(eng, ctl)
-    backend = NativeBackend(lead, eos=tk.eos, concurrency=args.concurrency, queue_depth=args.queue_depth)
+    drafter = None
+    if args.speculative:
+        if world > 1:
+            print("--speculative serves from one rank only in this build; ignoring it", file=sys.stderr)
+        else:
+            from .models.dspark import DSparkDrafter
+            drafter = DSparkDrafter(cfg, eng, weights=None, seed=args.seed, expert_dtype=args.expert_dtype)
+    backend = NativeBackend(lead if world > 1 else eng, eos=tk.eos, concurrency=args.concurrency,
+                            queue_depth=args.queue_depth, drafter=drafter)
     srv = ApiServer(backend, tk, host=args.host, port=args.port, queue_depth=args.queue_depth, waiters=args.waiters,
                     max_context=args.max_context).start()
     print(json.dumps({"listening": f"http://{args.host}:{srv.port}", "model": cfg.name, "ranks": world,
@@ -118,6 +126,9 @@ def main(argv=None) -> int:
     ps.add_argument("--max-context", type=int, default=8192)
     ps.add_argument("--seed", type=int, default=0)
     ps.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8"])
+    ps.add_argument("--speculative", action="store_true",
+                    help="decode a lone greedy request with dSpark draft + verify rounds (random-init drafter unless the "
+                         "checkpoint provides one)")
     args = ap.parse_args(argv)
     return {"build": cmd_build, "info": cmd_info, "serve": cmd_serve}[args.cmd](args)
 

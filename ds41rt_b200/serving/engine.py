@@ -118,16 +118,23 @@ class _Active:
     emitted: int = 0
     lane: int = 0
     tokens: List[int] = field(default_factory=list)     # emitted token ids
+    spec: bool = False        # decoded by speculative rounds (drafter + verify) while it is the only active request
 
 
 class NativeBackend(Backend):
     """Worker thread + scheduler loop over a DS41Engine (target-only batched decode; greedy rows are selected on
-    the device, sampled or constrained rows go through the sampler oracle with the request's allow-mask)."""
+    the device, sampled or constrained rows go through the GPU sampler with the request's allow-mask).  With a
+    drafter, a greedy unconstrained request that is alone on the engine is decoded by speculative rounds (dSpark drafts,
+    one verification pass, device-side accept rule); it drops to plain decoding when a second request joins."""
     fingerprint = "ds41rt-b200-fp8"
 
     def __init__(self, engine, eos: int, concurrency: int = 4, queue_depth: int = 16, prefill_chunk: Optional[int] = None,
-                 vision=None):
+                 vision=None, drafter=None):
         self.e, self.eos = engine, eos
+        self.spec = None
+        if drafter is not None:
+            from ..runtime.speculative import SpecSession
+            self.spec = SpecSession(engine, drafter)
         self.vision = vision                     # models.vision.VisionTower on the engine's device, or None
         self.supports_images = vision is not None
         self.concurrency = min(concurrency, engine.cache.slots, engine.max_rows)
@@ -143,7 +150,7 @@ class NativeBackend(Backend):
         self.pending: Optional[GenRequest] = None
         self.totals = {"requests": 0, "prompt_tokens": 0, "completion_tokens": 0, "device_greedy_rows": 0,
                        "cpu_sampled_rows": 0, "gpu_sampled_rows": 0, "rounds": 0, "failed": 0,
-                       "prompt_cache_hit_tokens": 0, "snapshots": 0}
+                       "prompt_cache_hit_tokens": 0, "snapshots": 0, "spec_rounds": 0, "spec_tokens": 0}
         self._rid = 0
         self._stop = threading.Event()
         self._ready = threading.Event()
@@ -265,8 +272,12 @@ class NativeBackend(Backend):
             self.totals["requests"] += 1
             self.totals["prompt_tokens"] += len(req.prompt_ids)
             self.totals["prompt_cache_hit_tokens"] += reused
-            first = self._prefill(slot, req, start=reused, logits=snap_logits)
-            a = _Active(req, slot, gen, pos=len(req.prompt_ids), last=first)
+            solo = (self.spec is not None and not self.active and req.sampling.greedy and req.constraint is None
+                    and not req.images and req.max_tokens > 1)
+            first = self._prefill(slot, req, start=reused, logits=snap_logits, feed_drafter=solo)
+            a = _Active(req, slot, gen, pos=len(req.prompt_ids), last=first, spec=solo)
+            if solo:
+                self.spec.prime(slot, first, len(req.prompt_ids))
             a.lane = self.lanes.add(req.rid, req.max_tokens, len(req.prompt_ids))
             self.prefix.insert(req.prompt_ids, K.PrefixBanks.PROMPT)
             if self._emit(a, first):
@@ -315,7 +326,7 @@ class NativeBackend(Backend):
             positions += list(pos)
         return torch.cat(rows, 0).contiguous(), positions
 
-    def _prefill(self, slot: int, req: GenRequest, start: int = 0, logits=None) -> int:
+    def _prefill(self, slot: int, req: GenRequest, start: int = 0, logits=None, feed_drafter: bool = False) -> int:
         import torch
         e = self.e
         toks = req.prompt_ids
@@ -324,7 +335,8 @@ class NativeBackend(Backend):
             if self.vision is None:
                 raise ValueError("this server has no vision tower")
             img_rows, img_pos = self._image_rows(req)
-        if not e.cache.ensure(slot, len(toks) + req.max_tokens + 1):
+        slack = 2 * self.spec.width + 2 if self.spec is not None else 1
+        if not e.cache.ensure(slot, len(toks) + req.max_tokens + slack):
             raise MemoryError("KV pool cannot hold this request")
         if start < len(toks):
             for c0 in range(start, len(toks), self.prefill_chunk):
@@ -337,6 +349,8 @@ class NativeBackend(Backend):
                         e.image_patch = (img_rows, torch.tensor(ids, dtype=torch.int32, device=img_rows.device))
                 e.forward_rows(len(part), head=last)
                 e.image_patch = None
+                if feed_drafter:
+                    self.spec.d.feed(len(part))       # the drafter's rings follow the target's taps
             logits = e.logits_rows(len(part))[len(part) - 1].clone()
             if not req.images:                                # placeholders look alike: image prompts are not banked
                 self._store_snapshot(slot, toks, logits)      # prompt bank
@@ -409,9 +423,29 @@ class NativeBackend(Backend):
             return False
         return True
 
+    def _spec_round(self, a: _Active):
+        """One speculative round for the only active request: up to `width` tokens come back."""
+        toks = self.spec.round_host()
+        self.totals["rounds"] += 1
+        self.totals["spec_rounds"] += 1
+        self.totals["spec_tokens"] += len(toks)
+        keep = True
+        for t in toks:
+            a.pos += 1
+            if not self._emit(a, t):
+                keep = False
+                break
+        if keep:
+            self.lanes.update(a.req.rid, a.req.max_tokens - a.emitted, a.pos)
+        self.active = [a] if keep else []
+
     def _decode_round(self):
         e = self.e
         acts = self.active
+        if len(acts) == 1 and acts[0].spec:
+            return self._spec_round(acts[0])
+        for a in acts:
+            a.spec = False             # a request that shared a pass stays on plain decoding
         e.set_rows([a.last for a in acts], [a.pos for a in acts], [a.slot for a in acts])
         e.forward_rows(len(acts))
         toks = self._select([a.req for a in acts], list(range(len(acts))))

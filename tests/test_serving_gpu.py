@@ -190,3 +190,53 @@ def test_image_parts_reach_the_vision_tower():
     finally:
         srv.stop()
         backend.close()
+
+
+def test_solo_request_is_served_by_speculative_rounds():
+    """With a drafter, a lone greedy request runs draft + verify rounds and produces exactly the tokens plain decoding
+    produces; when a second request joins mid-way both continue on plain decoding and still match."""
+    import threading
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    from ds41rt_b200.models.dspark import DSparkDrafter
+    from ds41rt_b200.serving.engine import GenRequest, NativeBackend
+    from ds41rt_b200.serving.protocol import Sampling
+    cfg = ModelConfig.tiny()
+    dev = torch.device("cuda", 0)
+    w = EngineWeights.random(cfg, 0, 1, dev, seed=0)
+
+    def backend(with_drafter):
+        eng = DS41Engine(cfg, w, max_rows=8, slots=4, max_ctx=512)
+        drafter = DSparkDrafter(cfg, eng, weights=None, seed=0) if with_drafter else None
+        return NativeBackend(eng, eos=1, concurrency=4, drafter=drafter)
+
+    def collect(r):
+        toks = []
+        while True:
+            ev = r.events.get(timeout=120)
+            if ev.kind == "tokens":
+                toks += ev.tokens
+            elif ev.kind == "finish":
+                return toks
+            elif ev.kind == "error":
+                raise RuntimeError(ev.message)
+
+    g = torch.Generator().manual_seed(21)
+    p1 = torch.randint(3, 2000, (40,), generator=g).tolist()
+    p2 = torch.randint(3, 2000, (33,), generator=g).tolist()
+    req = lambda p, n: GenRequest(prompt_ids=p, max_tokens=n, sampling=Sampling(temperature=0.0))
+    plain = backend(False)
+    r = req(p1, 40); plain.submit(r); want1 = collect(r)
+    r = req(p2, 12); plain.submit(r); want2 = collect(r)
+    plain.close()
+    spec = backend(True)
+    r = req(p1, 40); spec.submit(r)
+    assert collect(r) == want1
+    assert spec.totals["spec_rounds"] > 0 and spec.totals["spec_tokens"] >= spec.totals["spec_rounds"]
+    spec.snapshots.clear()
+    a, b = req(p1, 40), req(p2, 12)
+    spec.submit(a)
+    threading.Timer(0.05, lambda: spec.submit(b)).start()
+    assert collect(a) == want1 and collect(b) == want2
+    assert spec.healthy, spec.error
+    spec.close()
