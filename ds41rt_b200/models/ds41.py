@@ -560,7 +560,7 @@ class DS41Engine:
         max_extra = max([lw.extra_cols for lw in weights.layers] + [0])
         self.ntot_qkv = Q + D + max_extra
         self.max_splits = 16
-        self.planes_qkv = z((self.max_splits, R, self.ntot_qkv), F32)
+        self.planes_qkv = z((self._plane_rows(self.ntot_qkv), self.ntot_qkv), F32)
         self.q_lat = z((R, Q), BF16)
         self.extras = z((R, max(max_extra, 1)), F32)
         self.nqb = self.HL * D + cfg.index_heads * cfg.index_dim
@@ -581,7 +581,7 @@ class DS41Engine:
         self.oa = z((R, self.GL * cfg.o_lora), BF16)
         # MoE
         self.ntot_gate = E + 2 * self.I_sh
-        self.planes_gate = z((self.max_splits, R, self.ntot_gate), F32)
+        self.planes_gate = z((self._plane_rows(self.ntot_gate), self.ntot_gate), F32)
         self.ids = z((R, self.topk), I32)
         self.route_w = z((R, self.topk), F32)
         self.shared_act = z((R, self.I_sh), BF16)
@@ -608,19 +608,23 @@ class DS41Engine:
             self.actq4 = z((self.max_active, Rm, cfg.inter // 2), torch.uint8)
             self.actq4_sf = z((self.max_active, ra, cfg.inter // 64, 512), torch.uint8)
         self.fc2 = z((self.max_active, Rm, H), F32)
-        self.planes_shared = z((self.max_splits, R, H), F32)
+        self.planes_shared = z((self._plane_rows(H), H), F32)
         # head
-        self.logits = z((R, self.V_local), F32)
+        # long passes (prefill) only need the last row's logits: the head runs on at most head_cap rows
+        self.head_cap = 64
+        self.last_head_row = 0
+        self.logits = z((min(R, self.head_cap), self.V_local), F32)
         self.chosen = z((R,), I32)
         self.status = lib.new_status(dev)
         # symmetric buffers: [attn planes | moe plane | flag | best_val | best_idx]
-        self.o_plane_bytes = self.max_splits * R * H * 4
+        o_rows = self._plane_rows(H)
+        self.o_plane_bytes = o_rows * H * 4
         self.moe_plane_bytes = R * H * 4
         off_flag = self.o_plane_bytes + self.moe_plane_bytes
         off_best = off_flag + 256
         total = off_best + 2 * R * 4 + 256
         self.sym: SymBuffer = self.fabric.alloc(total)
-        self.planes_o = self.sym.view(F32, (self.max_splits, R, H), 0)
+        self.planes_o = self.sym.view(F32, (o_rows, H), 0)
         self.moe_plane = self.sym.view(F32, (R, H), self.o_plane_bytes)
         self.flag = self.sym.view(torch.int32, (1,), off_flag)
         self.best_val = self.sym.view(F32, (R,), off_best)
@@ -654,6 +658,14 @@ class DS41Engine:
         if self.layer_prefix_plain or self.cfg.compress_ratios[layer] == 0:
             return self.inv_plain
         return self.inv_long
+
+    def _plane_rows(self, m: int) -> int:
+        """Rows of split-K plane storage a projection with `m` outputs can need: max over pass sizes of splits x rows."""
+        best = 0
+        for r in range(1, self.max_rows + 1):
+            bn = G.pick_bn(r)
+            best = max(best, r * G.pick_splits(m, 1 << 20, max_splits=self.max_splits, n_tiles=(r + bn - 1) // bn))
+        return best
 
     def _attn_splits(self, rows: int) -> int:
         """Key-tile splits per (row, head group): one tile per CTA for a few rows (decode), fewer and longer CTAs once
@@ -988,7 +1000,12 @@ class DS41Engine:
         self._hc(rows, getattr(self, "_pending", None), lw0.hc_attn_fn, lw0.hc_attn_scale, lw0.hc_attn_base,
                  self.w.final_norm)
         self._pending = None
-        self._run("gemm_head", G.gemm_raw, self.w.head, self.xn, self.logits, self.V_local, rows, cfg.hidden, lda=cfg.hidden, ldb=cfg.hidden,
+        xn = self.xn
+        self.last_head_row = rows - 1
+        if rows > self.head_cap:
+            # a long pass: only its last row continues the sequence; its logits land in row 0
+            xn, rows, self.last_head_row = self.xn[rows - 1:rows], 1, 0
+        self._run("gemm_head", G.gemm_raw, self.w.head, xn, self.logits, self.V_local, rows, cfg.hidden, lda=cfg.hidden, ldb=cfg.hidden,
                    ldo=self.V_local, out_mode=3, status=self.status, static_operand=1)
         self._run("argmax_rows", k.ds41_argmax_rows, 
             lib.ptr(self.logits), C.c_longlong(self.V_local), rows, self.V_local, self.rank * self.V_local,
@@ -1039,7 +1056,7 @@ class DS41Engine:
             last = c0 + chunk >= len(tokens)
             self.forward_rows(self.max_rows if len(part) == self.max_rows else len(part), head=last)
             if last:
-                nxt = int(self.chosen[len(part) - 1].item())
+                nxt = int(self.chosen[self.last_head_row].item())
         return nxt
 
     def logits_rows(self, rows: int) -> torch.Tensor:

@@ -55,7 +55,7 @@ class SpecSession:
             t.forward_rows(len(part), head=last)
             d.feed(len(part))
             if last:
-                nxt = int(t.chosen[len(part) - 1].item())
+                nxt = int(t.chosen[t.last_head_row].item())
         self.prime(slot, nxt, len(prompt))
         return nxt
 

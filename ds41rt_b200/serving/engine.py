@@ -351,7 +351,7 @@ class NativeBackend(Backend):
                 e.image_patch = None
                 if feed_drafter:
                     self.spec.d.feed(len(part))       # the drafter's rings follow the target's taps
-            logits = e.logits_rows(len(part))[len(part) - 1].clone()
+            logits = e.logits_rows(e.last_head_row + 1)[e.last_head_row].clone()
             if not req.images:                                # placeholders look alike: image prompts are not banked
                 self._store_snapshot(slot, toks, logits)      # prompt bank
         return self._select([req], [0], logits=logits.view(1, -1))[0]
