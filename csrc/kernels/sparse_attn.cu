@@ -544,6 +544,257 @@ __global__ void __launch_bounds__(128) attend_kernel(AttendParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------- wide variant (long passes)
+// grid (n_splits, rows, heads/64), 512 threads: one CTA = all 64 heads of a head block x this split's keys of one row.
+// The gathered latent rows are shared by the four 16-head groups (a quarter of the gather traffic of attend_kernel), in
+// half tiles of 32 keys that are double buffered: the copies of half tile i+1 are in flight while half tile i is used.
+// Warp w: head group w & 3, part w >> 2.  S = Q K^T: 16 heads x 8 keys per warp; softmax: 4 heads per warp (lane =
+// key); O += P V: 16 heads x D/4 dims per warp.  Split partials and the merge kernel are the same as attend_kernel's.
+constexpr int kWideHeads = 64;
+constexpr int kWideKeys = 32;
+
+template <int D>
+__global__ void __launch_bounds__(512) attend_wide_kernel(AttendParams p) {
+  constexpr int LD = D + 8;
+  extern __shared__ __align__(16) uint8_t smem_attn[];
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_attn);                    // [64][LD]
+  __nv_bfloat16* sK = sQ + kWideHeads * LD;                                           // [2][32][LD]
+  float* sS = reinterpret_cast<float*>(sK + 2 * kWideKeys * LD);                      // [64][33]
+  __nv_bfloat16* sP = reinterpret_cast<__nv_bfloat16*>(sS + kWideHeads * 33);         // [64][40]
+  float* sCos = reinterpret_cast<float*>(sP + kWideHeads * 40);                       // [64]
+  float* sSin = sCos + 64;
+  const __nv_bfloat16** sPtr = reinterpret_cast<const __nv_bfloat16**>(sSin + 64);    // [2][32]
+  float* sM = reinterpret_cast<float*>(sPtr + 2 * kWideKeys);                         // [64]
+  float* sL = sM + kWideHeads;
+  float* sScale = sL + kWideHeads;
+  uint8_t* sK8 = reinterpret_cast<uint8_t*>(sScale + kWideHeads);                     // FP8 rows: [2][32][kv_row_bytes]
+
+  const int split = blockIdx.x, r = blockIdx.y, h_base = blockIdx.z * kWideHeads;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int hg = warp & 3, part = warp >> 2;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pos = p.row_pos[r], slot = p.row_slot[r];
+  float* ml_out = p.part_ml + ((1ll * r * p.n_splits + split) * p.heads + h_base) * 2;
+  float* o_out = p.part_o + ((1ll * r * p.n_splits + split) * p.heads + h_base) * D;
+
+  int n_w = 0, n_s = 0, hi_pos = pos, lo_pos = 0;
+  if (slot >= 0) {
+    if (p.row_hi != nullptr) hi_pos = max(pos, p.row_hi[r]);
+    lo_pos = max(0, pos - p.window + 1);
+    n_w = hi_pos - lo_pos + 1;
+    n_s = (p.comp_pool != nullptr && p.n_sel != nullptr) ? p.n_sel[r] : 0;
+  }
+  const int n_keys = n_w + n_s;
+  const int n_half = (n_keys + kWideKeys - 1) / kWideKeys;      // half tiles of this row
+  // split s takes half tiles s, s + n_splits, ...
+  if (split >= n_half) {
+    if (tid < kWideHeads) {
+      ml_out[2 * tid] = -INFINITY;
+      ml_out[2 * tid + 1] = 0.f;
+    }
+    return;
+  }
+  if (tid < p.rope_dim / 2) rope_cs2(pos, p.inv_freq[tid], &sCos[tid], &sSin[tid]);
+  if (tid < kWideHeads) {
+    sM[tid] = -INFINITY;
+    sL[tid] = 0.f;
+  }
+  const long long row_bytes = p.kv_row_bytes > 0 ? p.kv_row_bytes : 2ll * D;
+
+  // pointer table + copies of one half tile into buffer b (every thread commits one group per call)
+  auto issue = [&](int half, int b) {
+    const int k0 = half * kWideKeys;
+    const int k_cnt = min(kWideKeys, n_keys - k0);
+    if (tid < kWideKeys) {
+      const __nv_bfloat16* ptr = nullptr;
+      const int j = k0 + tid;
+      if (tid < k_cnt) {
+        if (j < n_w) {
+          const int kp = lo_pos + j;
+          ptr = reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const uint8_t*>(p.win) +
+                                                       (1ll * slot * p.ring + (kp % p.ring)) * row_bytes);
+        } else {
+          const int id = p.sel[1ll * r * p.k + (j - n_w)];
+          const long long phys = id < 0 ? -1 : pool_row(p.page_table, p.max_pages, p.page_rows, slot, id);
+          if (phys >= 0)
+            ptr = reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const uint8_t*>(p.comp_pool) + phys * row_bytes);
+        }
+      }
+      sPtr[b * kWideKeys + tid] = ptr;
+    }
+    __syncthreads();
+    if (p.kv_row_bytes == 0) {
+      for (int idx = tid; idx < kWideKeys * (D / 8); idx += 512) {
+        const int key = idx / (D / 8), ch = idx % (D / 8);
+        const __nv_bfloat16* src = sPtr[b * kWideKeys + key];
+        __nv_bfloat16* dst = sK + (b * kWideKeys + key) * LD + ch * 8;
+        if (src != nullptr) cp_async_16(dst, src + ch * 8);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+    } else {
+      const int chunks = p.kv_row_bytes / 16;
+      for (int idx = tid; idx < kWideKeys * chunks; idx += 512) {
+        const int key = idx / chunks, ch = idx - key * chunks;
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(sPtr[b * kWideKeys + key]);
+        uint8_t* dst = sK8 + (b * kWideKeys + key) * p.kv_row_bytes + ch * 16;
+        if (src != nullptr) cp_async_16(dst, src + ch * 16);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  issue(split, 0);
+  // Q tile with RoPE on the tail (zero rows for heads beyond this rank's count), while the first copies fly
+  const int rope0 = D - p.rope_dim;
+  const int n_heads = min(kWideHeads, p.heads - h_base);
+  for (int idx = tid; idx < kWideHeads * (D / 8); idx += 512) {
+    const int h = idx / (D / 8), ch = idx % (D / 8);
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (h < n_heads)
+      raw = *reinterpret_cast<const uint4*>(p.q + 1ll * r * p.ldq + p.q_off + 1ll * (h_base + h) * D + ch * 8);
+    if (ch * 8 >= rope0 && h < n_heads) {
+      __nv_bfloat162* v = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __bfloat1622float2(v[q]);
+        const int t = (ch * 8 + 2 * q - rope0) / 2;
+        const float c = sCos[t], sn = sSin[t];
+        v[q] = __floats2bfloat162_rn(f.x * c - f.y * sn, f.y * c + f.x * sn);
+      }
+    }
+    *reinterpret_cast<uint4*>(sQ + h * LD + ch * 8) = raw;
+  }
+  constexpr int NT = D / 32;                 // n8 tiles of this warp's D/4 output dims
+  float acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[nt][j] = 0.f;
+  const int d_base = part * (D / 4);
+
+  int buf = 0;
+  for (int half = split; half < n_half; half += p.n_splits, buf ^= 1) {
+    const int k0 = half * kWideKeys;
+    const int k_cnt = min(kWideKeys, n_keys - k0);
+    const int next = half + p.n_splits;
+    if (next < n_half) {
+      issue(next, buf ^ 1);                  // its buffer was last read two iterations ago (sync at the loop's end)
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    __nv_bfloat16* kt = sK + buf * kWideKeys * LD;
+    if (p.kv_row_bytes != 0) {
+      // FP8 rows -> bf16 (exact: e4m3 value times a power of two)
+      for (int idx = tid; idx < kWideKeys * (D / 8); idx += 512) {
+        const int key = idx / (D / 8), ch = idx % (D / 8);
+        const uint8_t* row8 = sK8 + (buf * kWideKeys + key) * p.kv_row_bytes;
+        const uint2 raw = *reinterpret_cast<const uint2*>(row8 + ch * 8);
+        const float sc = __uint_as_float(static_cast<uint32_t>(row8[D + (ch >> 2)]) << 23);
+        const __nv_fp8x2_storage_t* q2 = reinterpret_cast<const __nv_fp8x2_storage_t*>(&raw);
+        uint4 out;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(q2[q], __NV_E4M3)));
+          o2[q] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+        }
+        *reinterpret_cast<uint4*>(kt + key * LD + ch * 8) = out;
+      }
+      __syncthreads();
+    }
+    // ---- S = Q K^T: this warp's 16 heads x 8 keys
+    {
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      const __nv_bfloat16* qa = sQ + (hg * 16 + g) * LD + 2 * t4;
+      const __nv_bfloat16* kb = kt + (part * 8 + g) * LD + 2 * t4;
+#pragma unroll 8
+      for (int kk = 0; kk < D; kk += 16) {
+        uint32_t a[4];
+        a[0] = *reinterpret_cast<const uint32_t*>(qa + kk);
+        a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + kk);
+        a[2] = *reinterpret_cast<const uint32_t*>(qa + kk + 8);
+        a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + kk + 8);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb + kk);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kb + kk + 8);
+        mma_bf16_16816(c, a, b0, b1);
+      }
+      const int key = part * 8 + 2 * t4;
+      float* s0 = sS + (hg * 16 + g) * 33 + key;
+      float* s1 = sS + (hg * 16 + g + 8) * 33 + key;
+      s0[0] = key < k_cnt ? c[0] * p.scale : -INFINITY;
+      s0[1] = key + 1 < k_cnt ? c[1] * p.scale : -INFINITY;
+      s1[0] = key < k_cnt ? c[2] * p.scale : -INFINITY;
+      s1[1] = key + 1 < k_cnt ? c[3] * p.scale : -INFINITY;
+    }
+    __syncthreads();
+    // ---- running softmax statistics, 4 heads per warp, lane = key
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = warp * 4 + i;
+      const float v0 = sS[row * 33 + lane];
+      const float m_old = sM[row];
+      const float m = fmaxf(m_old, warp_max(v0));
+      const float e0 = __expf(v0 - m);
+      const __nv_bfloat16 b0 = __float2bfloat16_rn(e0);
+      const float l = warp_sum(__bfloat162float(b0));
+      sP[row * 40 + lane] = b0;
+      if (lane == 0) {
+        const float keep = m_old == -INFINITY ? 0.f : __expf(m_old - m);
+        sScale[row] = keep;
+        sL[row] = sL[row] * keep + l;
+        sM[row] = m;
+      }
+    }
+    __syncthreads();
+    // ---- O = O * keep + P V: this warp's 16 heads x D/4 dims
+    {
+      const float keep0 = sScale[hg * 16 + g], keep1 = sScale[hg * 16 + g + 8];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        acc[nt][0] *= keep0;
+        acc[nt][1] *= keep0;
+        acc[nt][2] *= keep1;
+        acc[nt][3] *= keep1;
+      }
+#pragma unroll
+      for (int kk = 0; kk < kWideKeys; kk += 16) {
+        uint32_t a[4];
+        const __nv_bfloat16* pa = sP + (hg * 16 + g) * 40 + kk + 2 * t4;
+        a[0] = *reinterpret_cast<const uint32_t*>(pa);
+        a[1] = *reinterpret_cast<const uint32_t*>(pa + 8 * 40);
+        a[2] = *reinterpret_cast<const uint32_t*>(pa + 8);
+        a[3] = *reinterpret_cast<const uint32_t*>(pa + 8 * 40 + 8);
+        const __nv_bfloat16* vrow = kt + (kk + (lane & 15)) * LD + d_base;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          uint32_t b0, b1;
+          ldmatrix_x2_trans(b0, b1, vrow + nt * 8);
+          mma_bf16_16816(acc[nt], a, b0, b1);
+        }
+      }
+    }
+    __syncthreads();     // everyone is done with this buffer, sS and sP
+  }
+  if (tid < n_heads) {
+    ml_out[2 * tid] = sM[tid];
+    ml_out[2 * tid + 1] = sL[tid];
+  }
+  {
+    const int h0 = hg * 16 + g, h1 = h0 + 8;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int d = d_base + nt * 8 + 2 * t4;
+      if (h0 < n_heads) *reinterpret_cast<float2*>(o_out + 1ll * h0 * D + d) = make_float2(acc[nt][0], acc[nt][1]);
+      if (h1 < n_heads) *reinterpret_cast<float2*>(o_out + 1ll * h1 * D + d) = make_float2(acc[nt][2], acc[nt][3]);
+    }
+  }
+}
+
 struct MergeParams {
   const float* part_o;
   const float* part_ml;
@@ -624,6 +875,23 @@ static cudaError_t launch_attend(const AttendParams& p, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(attend_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_max));
     if (e != cudaSuccess) return e;
     configured[dev] = true;
+  }
+  if (p.rows >= 64 && p.heads % kWideHeads == 0 && D % 128 == 0) {
+    // long pass: all 64 heads of a block share every gathered key row
+    const size_t wide = size_t(kWideHeads) * LD * 2 + 2 * size_t(kWideKeys) * LD * 2 + size_t(kWideHeads) * 33 * 4 +
+                        size_t(kWideHeads) * 40 * 2 + 128 * 4 + 2 * kWideKeys * 8 + 3 * kWideHeads * 4 + 64 +
+                        2 * size_t(kWideKeys) * p.kv_row_bytes;
+    static bool wide_configured[64] = {false};
+    if (dev >= 0 && dev < 64 && !wide_configured[dev]) {
+      const size_t wide_max = wide - 2 * size_t(kWideKeys) * p.kv_row_bytes +
+                              2 * size_t(kWideKeys) * ((D + D / 32 + 15) / 16 * 16);
+      cudaError_t e = cudaFuncSetAttribute(attend_wide_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           int(wide_max));
+      if (e != cudaSuccess) return e;
+      wide_configured[dev] = true;
+    }
+    dim3 wgrid(p.n_splits, p.rows, p.heads / kWideHeads);
+    return launch_pdl(attend_wide_kernel<D>, wgrid, dim3(512), wide, stream, p);
   }
   dim3 grid(p.n_splits, p.rows, (p.heads + kHeadsPerCta - 1) / kHeadsPerCta);
   return launch_pdl(attend_kernel<D>, grid, dim3(128), smem, stream, p);

@@ -54,16 +54,18 @@ def _pack_fp8_rows(x, row_bytes):
 
 
 @pytest.mark.parametrize("kv", ["bf16", "fp8"])
-@pytest.mark.parametrize("D,heads,rope", [(128, 8, 32), (512, 16, 64), (512, 64, 64)])
-def test_sparse_attention(D, heads, rope, kv):
+@pytest.mark.parametrize("D,heads,rope,rows,n_splits", [(128, 8, 32, 3, 0), (512, 16, 64, 3, 0), (512, 64, 64, 3, 0),
+                                                         (512, 64, 64, 70, 1), (512, 64, 64, 66, 3), (128, 64, 32, 64, 2)])
+def test_sparse_attention(D, heads, rope, rows, n_splits, kv):
+    """rows >= 64 with 64 heads runs the wide kernel (all heads share the gathered keys, double-buffered half tiles)."""
     from ds41rt_b200.ops import lib
     from ds41rt_b200.config import RopeConfig, rope_inv_freq
     from ds41rt_b200.models.reference import apply_rope
     k = lib.kernels()
     torch.manual_seed(0)
-    rows, window, ring, topk, page_rows, max_pages = 3, 128, 144, 64, 32, 16
-    positions = [700, 701, 50]
-    slots = [0, 0, 1]
+    window, ring, topk, page_rows, max_pages = 128, 144 + rows, 64, 32, 16
+    positions = ([700, 701, 50] + [300 + 3 * i for i in range(rows)])[:rows]
+    slots = ([0, 0, 1] + [i % 2 for i in range(rows)])[:rows]
     win = torch.randn(2, ring, D, device="cuda").bfloat16()
     pool = torch.randn(max_pages * 2 * page_rows, D, device="cuda").bfloat16()
     row_bytes = 0 if kv == "bf16" else (D + D // 32 + 15) // 16 * 16
@@ -73,13 +75,15 @@ def test_sparse_attention(D, heads, rope, kv):
         pool_dev, pool = _pack_fp8_rows(pool, row_bytes)
     page_table = torch.arange(2 * max_pages, dtype=torch.int32, device="cuda").view(2, max_pages).flip(1).contiguous()
     sel = torch.full((rows, topk), -1, dtype=torch.int32, device="cuda")
-    n_sel = torch.tensor([64, 40, 0], dtype=torch.int32, device="cuda")
-    sel[0] = torch.sort(torch.randperm(300)[:64]).values.int().cuda()
-    sel[1, :40] = torch.sort(torch.randperm(300)[:40]).values.int().cuda()
+    counts = ([64, 40, 0] + [(7 * i) % 65 for i in range(rows)])[:rows]
+    n_sel = torch.tensor(counts, dtype=torch.int32, device="cuda")
+    for i, c in enumerate(counts):
+        if c:
+            sel[i, :c] = torch.sort(torch.randperm(300)[:c]).values.int().cuda()
     q = torch.randn(rows, heads * D, device="cuda").bfloat16()
     sink = torch.randn(heads, device="cuda")
     inv = torch.tensor(rope_inv_freq(RopeConfig(), rope), device="cuda")
-    n_splits = (window + 16 + topk + 63) // 64
+    n_splits = n_splits or (window + 16 + topk + 63) // 64
     part_o = torch.zeros(rows, n_splits, heads, D, device="cuda")
     part_ml = torch.zeros(rows, n_splits, heads, 2, device="cuda")
     out = torch.zeros(rows, heads * D, device="cuda", dtype=torch.bfloat16)
