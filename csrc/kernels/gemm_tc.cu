@@ -18,6 +18,10 @@
 
 namespace ds41 {
 
+#ifndef DS41_SKINNY_STAGES
+#define DS41_SKINNY_STAGES 8
+#endif
+
 constexpr int kBM = 128;
 constexpr int kTileKBytes = 128;       // one 128-byte swizzle span of K per stage
 constexpr int kGemmThreads = 256;      // warps: 0 TMA, 1 MMA, 2-5 epilogue, 6-7 all-gather copiers
@@ -106,7 +110,10 @@ struct GemmCfg {
   static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
   static constexpr int kStaging = (!DUAL && BN >= 64) ? kStagingBytes : 0;
   static constexpr int kStagesRaw = ((kStaging ? 194 : 200) * 1024) / kStageBytes;
-  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  // Skinny decode tiles (BN <= 32) keep the ring short enough for two CTAs of consecutive launches to share an SM: the
+  // next kernel's set-up and its weight prefetch then overlap the tail of the previous one (programmatic launch).
+  static constexpr int kStageCap = (BN <= 32) ? DS41_SKINNY_STAGES : 8;
+  static constexpr int kStages = kStagesRaw > kStageCap ? kStageCap : kStagesRaw;
   static constexpr int kSfCols = kScaled ? 4 * (kAtomsA + kAtomsB) : 0;               // TMEM columns per stage
   static constexpr int kAccCols = (BN < 32 ? 32 : BN) * (DUAL ? 2 : 1);
   static constexpr int kTmemNeeded = 2 * kAccCols + kStages * kSfCols;

@@ -560,7 +560,9 @@ class DS41Engine:
         max_extra = max([lw.extra_cols for lw in weights.layers] + [0])
         self.ntot_qkv = Q + D + max_extra
         self.max_splits = 16
-        self.planes_qkv = z((self._plane_rows(self.ntot_qkv), self.ntot_qkv), F32)
+        # layers differ in their extra columns; fewer columns can mean more splits, so size for every distinct width
+        widths = sorted({lw.w_qkv.shape[0] for lw in weights.layers} | {self.ntot_qkv})
+        self.planes_qkv = z((max(self._plane_rows(n) * n for n in widths),), F32)
         self.q_lat = z((R, Q), BF16)
         self.extras = z((R, max(max_extra, 1)), F32)
         self.nqb = self.HL * D + cfg.index_heads * cfg.index_dim

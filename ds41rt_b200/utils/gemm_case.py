@@ -69,8 +69,17 @@ def main():
                                  a_batches=E, a_batch_stride=2 * I * H, out_batch_stride=rows * I, batch_map=active,
                                  n_active=n_active, b_batch_kind=1, up_row_offset=I, row_w=row_w, row_w_ld=rows,
                                  sfa=w13_sf, sfa_batch_stride=w13_sf[0].numel(), sfb=xq_sf, status=st, a_format=1)
+    # NVFP4 W4A4: both operands e2m1, E4M3 scale per 16, 64 K elements per instruction
+    xq4 = torch.randint(0, 256, (rows, H // 2), dtype=torch.uint8, device=dev)
+    xq4_sf = torch.full((1, H // 64, 512), 0x38, dtype=torch.uint8, device=dev)
+    w13_sf4 = torch.full((E, 2 * I // 128, H // 64, 512), 0x38, dtype=torch.uint8, device=dev)
+    fc1_nv = lambda: G.gemm_raw(w13_4, xq4, act, I, rows, H, lda=H, ldb=H, ldo=I, kind=3, out_mode=4, bn=32, batch=6,
+                                a_batches=E, a_batch_stride=2 * I * H, out_batch_stride=rows * I, batch_map=active,
+                                n_active=n_active, b_batch_kind=1, up_row_offset=I, row_w=row_w, row_w_ld=rows,
+                                sfa=w13_sf4, sfa_batch_stride=w13_sf4[0].numel(), sfb=xq4_sf, status=st, alpha=0.01)
     cases = [("bf16_gemm_%d" % n, big, 2.0 * n ** 3, None), ("decode_head_shard", skinny, None, V * H * 2),
-             ("mxfp8_expert_fc1", fc1, None, 6 * 2 * I * H), ("mxfp4_expert_fc1", fc1_fp4, None, 6 * 2 * I * H // 2)]
+             ("mxfp8_expert_fc1", fc1, None, 6 * 2 * I * H), ("mxfp4_expert_fc1", fc1_fp4, None, 6 * 2 * I * H // 2),
+             ("nvfp4_expert_fc1", fc1_nv, None, 6 * 2 * I * H // 2)]
     for name, fn, flops, nbytes in cases:
         if args.once:
             for _ in range(2):
