@@ -46,6 +46,47 @@ def cmd_info(args) -> int:
     return 0
 
 
+def _attach_engram(args, cfg, eng, dev):
+    """Every rank: give the engine its Engram layers (checkpoint weights, or random ones for a random-init model).
+    Returns the decoder layers that have one, in hash-family order."""
+    if cfg.engram is None or not (args.engram_table or args.engram_random_rows):
+        return []
+    import torch
+    from .models.engram import EngramLayer, init_engram_weights
+    layers = [l for l in cfg.engram.layers if l < eng.n_layers]
+    for i, l in enumerate(layers):
+        if args.checkpoint:
+            from .loader.official import load_engram_layer
+            mod = load_engram_layer(args.checkpoint, cfg, l, dev)
+        else:
+            wkv, q_w, k_w = init_engram_weights(cfg.hidden, seed=args.seed + 31 * i, std=0.002)
+            bf = lambda t: t.to(device=dev, dtype=torch.bfloat16)
+            mod = EngramLayer(bf(wkv), bf(q_w), bf(k_w), cfg.hidden)
+        eng.attach_engram(l, mod)
+    return layers
+
+
+def _engram_pipeline(args, cfg, eng, layers, tokenizer):
+    """Rank 0: the tables and the gather threads behind the engine's Engram layers."""
+    if not layers:
+        return None
+    import tempfile
+    from .models.engram import random_table_rows
+    from .runtime.engram import EngramPipeline, compressed_token_ids
+    from .runtime.engram_io import EngramTable
+    tables = []
+    for i, l in enumerate(layers):
+        if args.engram_table:
+            n_rows = cfg.engram.num_embeddings[cfg.engram.layers.index(l)]
+            tables.append(EngramTable(args.engram_table[i], n_rows, 264))
+        else:                                        # a small random table, row ids folded into it
+            path = os.path.join(tempfile.mkdtemp(prefix="ds41-engram-"), f"layer{l}.bin")
+            random_table_rows(args.engram_random_rows, seed=args.seed + i).numpy().tofile(path)
+            tables.append(EngramTable(path, args.engram_random_rows, 264))
+    return EngramPipeline(layers, tables, token_map=compressed_token_ids(tokenizer.token_bytes()),
+                          pad_id=cfg.engram.pad_token_id, max_rows=eng.max_rows, fold=not args.engram_table)
+
+
 def cmd_serve(args) -> int:
     import torch
     from .models.ds41 import DS41Engine, EngineWeights
@@ -70,6 +111,7 @@ def cmd_serve(args) -> int:
         weights = EngineWeights.random(cfg, rank, world, dev, seed=args.seed, expert_dtype=args.expert_dtype)
     eng = DS41Engine(cfg, weights, fabric, max_rows=max(8, args.concurrency), slots=args.concurrency,
                      max_ctx=args.max_context, kv_dtype=args.kv_dtype)
+    engram_layers = _attach_engram(args, cfg, eng, dev)
     if rank != 0:
         # every other rank mirrors the leader's engine calls until it is told to stop
         follower_loop(eng, ctl, on_error=lambda e: print(f"rank {rank}: {e}", file=sys.stderr, flush=True))
@@ -83,7 +125,8 @@ def cmd_serve(args) -> int:
             from .models.dspark import DSparkDrafter
             drafter = DSparkDrafter(cfg, eng, weights=None, seed=args.seed, expert_dtype=args.expert_dtype)
     backend = NativeBackend(lead if world > 1 else eng, eos=tk.eos, concurrency=args.concurrency,
-                            queue_depth=args.queue_depth, drafter=drafter)
+                            queue_depth=args.queue_depth, drafter=drafter,
+                            engram=_engram_pipeline(args, cfg, eng, engram_layers, tk))
     srv = ApiServer(backend, tk, host=args.host, port=args.port, queue_depth=args.queue_depth, waiters=args.waiters,
                     max_context=args.max_context).start()
     print(json.dumps({"listening": f"http://{args.host}:{srv.port}", "model": cfg.name, "ranks": world,
@@ -126,6 +169,11 @@ def main(argv=None) -> int:
     ps.add_argument("--max-context", type=int, default=8192)
     ps.add_argument("--seed", type=int, default=0)
     ps.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8"])
+    ps.add_argument("--engram-table", action="append", default=[],
+                    help="flat Engram table file (loader.official.export_engram_table), once per Engram layer in layer "
+                         "order; enables the Engram memory layers")
+    ps.add_argument("--engram-random-rows", type=int, default=0,
+                    help="random-init models: enable the Engram layers over random tables of this many rows")
     ps.add_argument("--speculative", action="store_true",
                     help="decode a lone greedy request with dSpark draft + verify rounds (random-init drafter unless the "
                          "checkpoint provides one)")

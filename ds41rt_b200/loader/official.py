@@ -23,6 +23,8 @@ def _quantise(name: str, spec, w: Dict[str, torch.Tensor], variant: str):
     dt, shape = spec
     base, _, leaf = name.rpartition(".")
     if dt == "F8_E4M3" and leaf == "weight":
+        if ".engram.embed" in name:                       # table rows carry one scale per 32 values of the row
+            return Q.quant_mxfp8(w[name], 32)[0]
         q, _ = Q.quant_weight_mxfp8_32x32(w[name])
         return q
     if dt == "F8_E8M0" and leaf == "scale":
@@ -134,3 +136,35 @@ def load_engine_weights(directory: str, cfg: ModelConfig, rank: int, world: int,
     from ..models.ds41 import EngineWeights
     cat = Catalog(directory, cfg, variant, with_vision=with_vision, with_engram=with_engram)
     return EngineWeights.from_fp32(cfg, LazyOfficialWeights(cat), rank, world, device, expert_dtype=expert_dtype)
+
+
+# ------------------------------------------------------------------------------------------------- Engram memory
+def export_engram_table(cat: Catalog, layer: int, path: str, row_bytes: int = 264, chunk_rows: int = 1 << 20) -> int:
+    """Write layer `layer`'s Engram table as the flat file the host gather maps: one record per table row,
+    `head_dim` e4m3 bytes followed by head_dim/32 UE8M0 scale bytes, zero padded to `row_bytes`.  Streams the
+    checkpoint in chunks of `chunk_rows` rows; returns the number of rows written.
+    (Reference: rust/crates/ds41rt-loader/src/mapped_rows.rs:15 maps the same records.)"""
+    name = f"layers.{layer}.engram.embed"
+    _, (n_rows, dim) = cat.expected[name + ".weight"]
+    assert dim + dim // 32 <= row_bytes
+    with open(path, "wb") as f:
+        for r0 in range(0, n_rows, chunk_rows):
+            r1 = min(n_rows, r0 + chunk_rows)
+            rec = torch.zeros(r1 - r0, row_bytes, dtype=torch.uint8)
+            rec[:, :dim] = cat.read(name + ".weight", (r0, r1), None).view(torch.uint8)
+            rec[:, dim:dim + dim // 32] = cat.read(name + ".scale", (r0, r1), None).view(torch.uint8)
+            f.write(rec.numpy().tobytes())
+    return n_rows
+
+
+def load_engram_layer(directory: str, cfg: ModelConfig, layer: int, device, variant: str = "mxfp4"):
+    """The projection and gate weights of one Engram layer of an official checkpoint -> models.engram.EngramLayer
+    (the table itself stays on the host: export_engram_table + runtime.engram.EngramPipeline)."""
+    from ..models.engram import EngramLayer
+    cat = Catalog(directory, cfg, variant, with_vision=False, with_engram=True)
+    w = LazyOfficialWeights(cat)
+    p = f"layers.{layer}.engram"
+    bf = lambda t: t.to(device=device, dtype=torch.bfloat16).contiguous()
+    g = cfg.engram
+    return EngramLayer(bf(w[p + ".wkv.weight"]), bf(w[p + ".q_weight"]), bf(w[p + ".k_weight"]), cfg.hidden,
+                       rows_per_token=g.n_heads * (g.max_ngram - 1), row_dim=g.head_dim)

@@ -651,6 +651,12 @@ class DS41Engine:
         self._pass_hint = None    # (rows, highest position) of a single-request pass described by the last set_rows
         self.image_patch = None   # (image rows, pass-row ids) applied after the embedding lookup of the next pass
         self.timeline = None   # set to a list to record (tag, start event, end event) per launch of eager passes
+        # Engram memory layers: layer -> (EngramLayer, pinned host rows [max_rows * rows_per_token, row_bytes], device
+        # text mask [max_rows] uint8).  A layer takes part in a pass only after set_engram_rows() filled its host rows.
+        self.engram: Dict[int, tuple] = {}
+        self._engram_live: set = set()
+        self._engram_copied: Dict[int, object] = {}      # layer -> event after the last upload of its host rows
+        self._engram_layer_of: Dict[int, int] = {}
         if R > self.moe_rows and weights.layers:
             self._make_ep(weights.layers[0])
         self.debug = None   # set to a list to record per-layer routing / selection decisions
@@ -717,19 +723,57 @@ class DS41Engine:
             h = torch.tensor(list(row_hi if row_hi is not None else positions) + [0] * pad, dtype=I32)
             self.row_hi.copy_(h, non_blocking=True)
 
-    def _post_mix(self, rows, part_bases, n_ranks, n_splits, split_stride, fn, sync):
+    # ------------------------------------------------------------------ Engram memory layers
+    def attach_engram(self, layer: int, module) -> None:
+        """Give decoder layer `layer` an Engram update of the streams it receives (models/engram.py EngramLayer;
+        reference: rust/crates/ds41rt-daemon/src/v41_target_pass.rs:403-442)."""
+        assert 0 <= layer < self.n_layers and module.H == self.cfg.hidden
+        n = self.max_rows * module.rpt
+        module.reserve(self.max_rows)
+        module.status = self.status        # one status word for the whole pass
+        host = torch.zeros(n, module.row_bytes, dtype=torch.uint8)
+        if self.device.type == "cuda":
+            host = host.pin_memory()
+        self._engram_layer_of[id(module)] = layer
+        self.engram[layer] = (module, host, torch.ones(self.max_rows, dtype=torch.uint8, device=self.device))
+
+    def set_engram_rows(self, layer: int, rows_q, text_mask=None) -> None:
+        """Table rows of the next pass for one Engram layer: uint8 [pass rows * rows_per_token, row_bytes] (numpy or a
+        CPU tensor, e.g. a gather slot), `text_mask` one flag per pass row (0 = image row, streams pass through).
+        The rows are copied into the engine's pinned buffer, so the caller's buffer is free on return and a captured
+        pass replays against the same host address."""
+        module, host, mask = self.engram[layer]
+        src = rows_q if isinstance(rows_q, torch.Tensor) else torch.from_numpy(rows_q)
+        n = src.shape[0]
+        assert n % module.rpt == 0 and n <= host.shape[0] and src.shape[1] == module.row_bytes
+        ev = self._engram_copied.get(layer)
+        if ev is not None:
+            ev.synchronize()          # the previous pass's upload reads the same pinned buffer
+        host[:n].copy_(src)
+        m = torch.ones(self.max_rows, dtype=torch.uint8)
+        if text_mask is not None:
+            m[: len(text_mask)] = torch.as_tensor(text_mask, dtype=torch.uint8)
+        mask.copy_(m, non_blocking=True)
+        self._engram_live.add(layer)
+
+    def clear_engram_rows(self) -> None:
+        self._engram_live.clear()
+
+    def _post_mix(self, rows, part_bases, n_ranks, n_splits, split_stride, fn, sync, coef=None):
         k, st = self.k, lib.stream()
+        post, comb = coef if coef is not None else (self.post, self.comb)
         wait_flags = lib.ptr(self.flag_ptrs) if (sync and self.world > 1) else lib.ptr(None)
         self._run("hc_post_mix", k.ds41_hc_post_mix, 
             lib.ptr(self.streams), lib.ptr(self.streams), part_bases, n_ranks, n_splits, C.c_longlong(split_stride),
-            lib.ptr(self.post), lib.ptr(self.comb), lib.ptr(fn), lib.ptr(self.hc_partial), rows, self.cfg.hidden,
+            lib.ptr(post), lib.ptr(comb), lib.ptr(fn), lib.ptr(self.hc_partial), rows, self.cfg.hidden,
             wait_flags, lib.ptr(self.epoch), lib.ptr(self.status), st)
 
-    def _finish(self, rows, scale, base, pre_in, norm_w, next_pre, tap=None, quant=False):
+    def _finish(self, rows, scale, base, pre_in, norm_w, next_pre, tap=None, quant=False, coef=None):
         cfg = self.cfg
+        post, comb = coef if coef is not None else (self.post, self.comb)
         self._run("hc_finish", self.k.ds41_hc_finish, 
             lib.ptr(self.hc_partial), self.n_slices, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
-            lib.ptr(self.streams), lib.ptr(norm_w), lib.ptr(next_pre), lib.ptr(self.post), lib.ptr(self.comb),
+            lib.ptr(self.streams), lib.ptr(norm_w), lib.ptr(next_pre), lib.ptr(post), lib.ptr(comb),
             lib.ptr(self.xn), lib.ptr(tap), lib.ptr(self.xq if quant else None),
             lib.ptr(self.xq_sf if quant else None), rows, cfg.hidden, cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps),
             C.c_float(cfg.norm_eps), lib.stream())
@@ -759,12 +803,30 @@ class DS41Engine:
             self._run("signal", self.k.ds41_signal, lib.ptr(self.epoch), lib.ptr(self.flag), lib.stream())
 
     # ------------------------------------------------------------------ one pass over `rows` rows
-    def _hc(self, rows, pending, fn, scale, base, norm_w, tap=None, quant=False):
+    def _hc(self, rows, pending, fn, scale, base, norm_w, tap=None, quant=False, engram=None):
         """Close the pending sublayer (expand with its partial planes) and open the next one
-        (mixes -> collapse -> RMSNorm into self.xn).  One fused launch for small passes, two otherwise."""
+        (mixes -> collapse -> RMSNorm into self.xn).  One fused launch for small passes, two otherwise.
+        With `engram` (a layer that receives an Engram update) the step is split: expand, gated update of the
+        streams, mixes recomputed on the updated streams, then collapse + norm."""
         cur = self._cur
         bases, n_ranks, n_splits, stride = pending if pending is not None else (None, 0, 0, 0)
-        if rows <= self.fused_rows:
+        if engram is not None:
+            module, host, mask = engram
+            small = rows <= self.fused_rows
+            cin = self.coef[self._ccur] if small else None
+            cout = self.coef[self._ccur ^ 1] if small else None
+            if pending is not None:
+                self._post_mix(rows, bases, n_ranks, n_splits, stride, fn, sync=True, coef=cin)
+            self._run("engram", module.apply, self.streams[:rows], host, mask)
+            if self.device.type == "cuda" and not torch.cuda.is_current_stream_capturing():
+                ev = torch.cuda.Event()
+                ev.record()
+                self._engram_copied[self._engram_layer_of[id(module)]] = ev
+            self._post_mix(rows, None, 0, 0, 0, fn, sync=False, coef=cin)
+            self._finish(rows, scale, base, self.pre[cur], norm_w, self.pre[cur ^ 1], tap, quant, coef=cout)
+            if small:
+                self._ccur ^= 1
+        elif rows <= self.fused_rows:
             cc = self._ccur
             self._step(rows, bases, n_ranks, n_splits, stride, self.coef[cc], self.pre[cur], fn, scale, base, norm_w,
                        self.pre[cur ^ 1], self.coef[cc ^ 1], tap=tap, quant=quant, sync=pending is not None)
@@ -804,7 +866,8 @@ class DS41Engine:
                     and l in cfg.dspark.tap_layers and tap_i < self.taps.shape[0]:
                 tap = self.taps[tap_i]
                 tap_i += 1
-            self._hc(R, pending, lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, lw.attn_norm, tap=tap)
+            self._hc(R, pending, lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, lw.attn_norm, tap=tap,
+                     engram=self.engram[l] if l in self._engram_live else None)
             ntot = lw.w_qkv.shape[0]
             s_qkv = self._splits(ntot, H, R)
             self._run("gemm_qkv", G.linear_planes, self.xn[:R], lw.w_qkv, self.planes_qkv.view(-1)[: s_qkv * R * ntot].view(s_qkv, R, ntot),

@@ -53,16 +53,26 @@ class EngramLayer:
         dev = wkv.device
         assert wkv.shape == (5 * hidden, rows_per_token * row_dim) and wkv.dtype == torch.bfloat16
         self.wkv, self.q_w, self.k_w = wkv.contiguous(), q_weight.contiguous(), k_weight.contiguous()
-        self.H, self.rpt, self.dim, self.row_bytes, self.eps = hidden, rows_per_token, row_dim, row_bytes, eps
-        self.max_tokens = max_tokens
-        self.staging = torch.zeros(max_tokens * rows_per_token, row_bytes, dtype=torch.uint8, device=dev)
-        self.rows = torch.zeros(max_tokens, rows_per_token * row_dim, dtype=torch.bfloat16, device=dev)
-        self.kv = torch.zeros(max_tokens, 5 * hidden, dtype=torch.bfloat16, device=dev)
+        self.H, self.rpt, self.dim, self.row_bytes = hidden, rows_per_token, row_dim, row_bytes
+        self.eps = eps
+        self.max_tokens = 0
         self.status = lib.new_status(dev)
+        self.reserve(max_tokens)
+
+    def reserve(self, max_tokens: int) -> None:
+        """Size the device buffers for passes of up to `max_tokens` rows (no allocation happens in forward)."""
+        if max_tokens <= self.max_tokens:
+            return
+        dev = self.wkv.device
+        self.max_tokens = max_tokens
+        self.staging = torch.zeros(max_tokens * self.rpt, self.row_bytes, dtype=torch.uint8, device=dev)
+        self.rows = torch.zeros(max_tokens, self.rpt * self.dim, dtype=torch.bfloat16, device=dev)
+        self.kv = torch.zeros(max_tokens, 5 * self.H, dtype=torch.bfloat16, device=dev)
 
     def forward(self, streams: torch.Tensor, rows_q_host, text_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """streams [T, 4, H] bf16 (updated in place), rows_q_host: uint8 [T * rows_per_token, row_bytes] (numpy or a
-        pinned tensor, e.g. a gather slot).  Asynchronous on the current stream after the upload."""
+        """streams [T, 4, H] bf16 (updated in place), rows_q_host: uint8 [>= T * rows_per_token, row_bytes] (numpy or a
+        pinned tensor, e.g. a gather slot), text_mask: device uint8 [>= T] or None.  Asynchronous on the current
+        stream after the upload."""
         T = streams.shape[0]
         assert T <= self.max_tokens and streams.dtype == torch.bfloat16 and streams.is_contiguous()
         k, st = lib.kernels(), lib.stream
@@ -76,3 +86,30 @@ class EngramLayer:
                                      lib.ptr(text_mask), lib.ptr(streams), T, self.H, C.c_float(self.eps), st()),
                   "engram_gate")
         return streams
+
+    def apply(self, streams: torch.Tensor, rows_q_host, text_mask: Optional[torch.Tensor] = None) -> None:
+        """forward() for callers that expect no return value (the engine's launch wrapper); the projection's device
+        status word is `self.status`."""
+        self.forward(streams, rows_q_host, text_mask)
+
+
+def init_engram_weights(hidden: int, rows_per_token: int = 24, row_dim: int = 256, seed: int = 0, std: float = 0.02):
+    """Random Engram projection for tests and random-init models: (wkv [5H, rows_per_token * row_dim], q_weight [4, H],
+    k_weight [4, H]) as fp32 CPU tensors."""
+    g = torch.Generator().manual_seed(seed)
+    wkv = torch.randn(5 * hidden, rows_per_token * row_dim, generator=g) * std
+    q_w = 1.0 + 0.1 * torch.randn(4, hidden, generator=g)
+    k_w = 1.0 + 0.1 * torch.randn(4, hidden, generator=g)
+    return wkv, q_w, k_w
+
+
+def random_table_rows(n_rows: int, row_dim: int = 256, row_bytes: int = 264, seed: int = 0) -> torch.Tensor:
+    """A table of `n_rows` records in the checkpoint's row format (e4m3 payload + UE8M0 scale per 32, padded to
+    `row_bytes`) with values of order one: uint8 [n_rows, row_bytes]."""
+    g = torch.Generator().manual_seed(seed)
+    vals = (torch.randn(n_rows, row_dim, generator=g)).clamp(-3, 3)
+    out = torch.zeros(n_rows, row_bytes, dtype=torch.uint8)
+    out[:, :row_dim] = vals.to(torch.float8_e4m3fn).view(torch.uint8)
+    out[:, row_dim:row_dim + row_dim // 32] = torch.randint(125, 129, (n_rows, row_dim // 32), generator=g,
+                                                            dtype=torch.int32).to(torch.uint8)
+    return out

@@ -135,6 +135,8 @@ class ReferenceModel:
         self._inv = {}
 
     # ------------------------------------------------------------------ helpers
+    engram_hook = None   # optional callable (layer, streams [T, m, H]) -> streams, applied on entry to each layer
+
     def inv_freq(self, rope: RopeConfig, dim: int) -> torch.Tensor:
         key = (rope.theta, rope.factor, dim)
         if key not in self._inv:
@@ -321,6 +323,9 @@ class ReferenceModel:
         for l in range(cfg.n_layers):
             p = f"layers.{l}"
             tr = LayerTrace() if return_trace else None
+            if self.engram_hook is not None:
+                # Engram memory: layers that have one update the streams they receive (bf16 rounding as the kernel)
+                streams = self.engram_hook(l, streams)
             if cfg.dspark is not None and l in cfg.dspark.tap_layers:
                 taps.append(streams.mean(1))
             src_layer = cfg.source_of(l)

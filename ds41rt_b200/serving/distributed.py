@@ -83,6 +83,19 @@ class LeaderEngine:
         self._send(("forward", rows, kw))
         self.eng.forward_rows(rows, **kw)
 
+    def set_engram_rows(self, layer: int, rows_q, text_mask=None) -> None:
+        """The leader's gathered table rows travel with the pass: every rank applies the same Engram update to its
+        replicated streams."""
+        import numpy as np
+        arr = np.ascontiguousarray(rows_q.numpy() if hasattr(rows_q, "numpy") else rows_q)
+        mask = None if text_mask is None else [int(m) for m in text_mask]
+        self._send(("engram", layer, arr, mask))
+        self.eng.set_engram_rows(layer, arr, mask)
+
+    def clear_engram_rows(self) -> None:
+        self._send(("engram_clear",))
+        self.eng.clear_engram_rows()
+
     def logits_rows(self, rows: int):
         self._send(("logits", rows))
         return self.eng.logits_rows(rows)
@@ -111,6 +124,10 @@ def follower_loop(engine, group, on_error=None) -> int:
                 passes += 1
             elif op == "logits":
                 engine.logits_rows(msg[1])
+            elif op == "engram":
+                engine.set_engram_rows(msg[1], msg[2], msg[3])
+            elif op == "engram_clear":
+                engine.clear_engram_rows()
             elif op == "ensure":
                 engine.cache.ensure(msg[1], msg[2])
             elif op == "release":

@@ -129,9 +129,15 @@ class NativeBackend(Backend):
     fingerprint = "ds41rt-b200-fp8"
 
     def __init__(self, engine, eos: int, concurrency: int = 4, queue_depth: int = 16, prefill_chunk: Optional[int] = None,
-                 vision=None, drafter=None):
+                 vision=None, drafter=None, engram=None):
         self.e, self.eos = engine, eos
         self.spec = None
+        # runtime.engram.EngramPipeline or None.  Every pass hands its token ids to the pipeline first (hashes, page
+        # advice, gather requests), runs, and commits the rows it kept.  Speculative rounds keep their draft tokens on
+        # the device, so a backend with Engram layers decodes without the drafter.
+        self.engram = engram
+        if engram is not None:
+            drafter = None
         if drafter is not None:
             from ..runtime.speculative import SpecSession
             self.spec = SpecSession(engine, drafter)
@@ -206,9 +212,19 @@ class NativeBackend(Backend):
             self.healthy = False
             self._ready.set()
 
+    def _engram_pass(self, tokens: List[int], slots: List[int], is_image=None):
+        """Start the table reads for one pass and hand the rows to the engine -> pass record to commit afterwards."""
+        if self.engram is None:
+            return None
+        p = self.engram.begin(tokens, slots, is_image)
+        self.engram.apply(p, self.e)
+        return p
+
     def _release(self, a: _Active):
         self.kv.retire(a.slot, a.gen)
         self.e.cache.release(a.slot)
+        if self.engram is not None:
+            self.engram.release(a.slot)
         self.lanes.retire(a.req.rid)
 
     def _finish(self, a: _Active, reason: str):
@@ -338,10 +354,14 @@ class NativeBackend(Backend):
         slack = 2 * self.spec.width + 2 if self.spec is not None else 1
         if not e.cache.ensure(slot, len(toks) + req.max_tokens + slack):
             raise MemoryError("KV pool cannot hold this request")
+        if self.engram is not None:
+            self.engram.reset(slot, toks[:start])
+        image_at = set(img_pos) if img_pos is not None else set()
         if start < len(toks):
             for c0 in range(start, len(toks), self.prefill_chunk):
                 part = toks[c0:c0 + self.prefill_chunk]
                 e.set_rows(part, list(range(c0, c0 + len(part))), [slot] * len(part))
+                ep = self._engram_pass(part, [slot] * len(part), [c0 + i in image_at for i in range(len(part))])
                 last = c0 + self.prefill_chunk >= len(toks)
                 if img_rows is not None:
                     ids = [p - c0 if c0 <= p < c0 + len(part) else -1 for p in img_pos]
@@ -349,6 +369,8 @@ class NativeBackend(Backend):
                         e.image_patch = (img_rows, torch.tensor(ids, dtype=torch.int32, device=img_rows.device))
                 e.forward_rows(len(part), head=last)
                 e.image_patch = None
+                if ep is not None:
+                    self.engram.commit(ep)
                 if feed_drafter:
                     self.spec.d.feed(len(part))       # the drafter's rings follow the target's taps
             logits = e.logits_rows(e.last_head_row + 1)[e.last_head_row].clone()
@@ -447,7 +469,10 @@ class NativeBackend(Backend):
         for a in acts:
             a.spec = False             # a request that shared a pass stays on plain decoding
         e.set_rows([a.last for a in acts], [a.pos for a in acts], [a.slot for a in acts])
+        ep = self._engram_pass([a.last for a in acts], [a.slot for a in acts])
         e.forward_rows(len(acts))
+        if ep is not None:
+            self.engram.commit(ep)
         toks = self._select([a.req for a in acts], list(range(len(acts))))
         self.totals["rounds"] += 1
         keep = []

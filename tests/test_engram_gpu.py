@@ -34,3 +34,57 @@ def test_engram_layer_matches_reference(T, H):
     err = float((got.float().cpu() - want).abs().max())
     assert err < 3e-2 * float(want.abs().max()), err
     assert torch.equal(got[1].cpu(), x[1].cpu())
+
+
+@pytest.mark.parametrize("rows", [5, 40])
+def test_engine_pass_with_engram_layer_matches_oracle(rows):
+    """A decoder layer that has an Engram memory: the engine's split hyper-connection step (expand, gated update,
+    mixes recomputed, collapse) against the fp32 oracle with the same update on entry to that layer."""
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    from ds41rt_b200.models.engram import (EngramLayer, dequant_rows_reference, engram_reference,
+                                            init_engram_weights, random_table_rows)
+    from ds41rt_b200.models.reference import ReferenceModel
+    from ds41rt_b200.models.weights import init_weights
+    cfg = ModelConfig.tiny()
+    w = init_weights(cfg, seed=3)
+    dev = torch.device("cuda", 0)
+    H, rpt, dim = cfg.hidden, 24, 256
+    wkv, q_w, k_w = init_engram_weights(H, seed=5, std=0.002)
+    bf = lambda t: t.bfloat16()
+    table = random_table_rows(rows * rpt, seed=7)
+    mask = torch.ones(rows, dtype=torch.uint8)
+    mask[2] = 0
+    tokens = torch.randint(0, cfg.vocab - 8, (rows,), generator=torch.Generator().manual_seed(rows))
+
+    ref = ReferenceModel(cfg, w)
+    deq = dequant_rows_reference(table, dim).bfloat16().view(rows, rpt * dim)
+    ref.engram_hook = lambda l, s: engram_reference(s.bfloat16(), deq, bf(wkv), bf(q_w), bf(k_w), mask) if l == 1 else s
+    want = ref.forward(tokens)
+    plain = ReferenceModel(cfg, w).forward(tokens)
+    assert float((want - plain).abs().max()) > 1e-2            # the update matters in this setup
+
+    eng = DS41Engine(cfg, EngineWeights.from_fp32(cfg, w, 0, 1, dev), max_rows=max(rows, 8), slots=1, max_ctx=256)
+    eng.attach_engram(1, EngramLayer(bf(wkv).to(dev), bf(q_w).to(dev), bf(k_w).to(dev), H))
+    assert eng.cache.ensure(0, rows)
+    eng.set_rows(tokens.tolist(), list(range(rows)), [0] * rows)
+    eng.set_engram_rows(1, table.numpy(), mask)
+    eng.forward_rows(rows)
+    torch.cuda.synchronize()
+    eng.check_status("engram pass")
+    got = eng.logits_rows(rows).float().cpu()
+    # bf16 activations may flip near-tied expert / key selections in single rows, so judge the bulk of the rows
+    scale = float(want.abs().max())
+    err = (got - want).abs().max(dim=1).values
+    off = (got - plain).abs().max(dim=1).values
+    assert float(err.median()) < 0.05 * scale, (float(err.median()), scale)
+    assert int((err < off).sum()) >= 0.8 * rows, (err, off)
+    # and without rows for this pass the layer is skipped
+    eng.clear_engram_rows()
+    eng.cache.release(0)
+    assert eng.cache.ensure(0, rows)
+    eng.set_rows(tokens.tolist(), list(range(rows)), [0] * rows)
+    eng.forward_rows(rows)
+    torch.cuda.synchronize()
+    got2 = eng.logits_rows(rows).float().cpu()
+    assert float((got2 - plain).abs().max(dim=1).values.median()) < 0.05 * float(plain.abs().max())

@@ -146,3 +146,33 @@ def test_lazy_weights_match_eager_load(tmp_path):
     for name in ("embed.weight", "layers.0.attn.wq_a.weight", "layers.1.ffn.experts.3.w1.weight", "layers.0.hc_attn_fn"):
         assert name in lazy
         assert torch.equal(lazy[name], eager[name])
+
+
+def test_engram_table_export_matches_checkpoint_rows(tmp_path):
+    """An Engram layer of an official-layout checkpoint: the exported flat table holds the checkpoint's e4m3 payload and
+    UE8M0 scales record by record, and dequantises to the stored values."""
+    import dataclasses
+    import numpy as np
+    from ds41rt_b200.config import EngramConfig
+    from ds41rt_b200.loader.official import export_engram_table
+    from ds41rt_b200.models.engram import dequant_rows_reference
+    from ds41rt_b200.runtime.engram_io import EngramTable
+    cfg = dataclasses.replace(ModelConfig.tiny(), engram=EngramConfig(layers=(1,), num_embeddings=(3000,)))
+    w = init_weights(cfg, seed=0)
+    g = torch.Generator().manual_seed(1)
+    H, width = cfg.hidden, 24 * 256
+    w["layers.1.engram.embed.weight"] = torch.randn(3000, 256, generator=g)
+    w["layers.1.engram.k_weight"] = torch.randn(cfg.hc_mult, H, generator=g)
+    w["layers.1.engram.q_weight"] = torch.randn(cfg.hc_mult, H, generator=g)
+    w["layers.1.engram.wkv.weight"] = torch.randn((cfg.hc_mult + 1) * H, width, generator=g) * 0.02
+    d = str(tmp_path / "ckpt")
+    export_official(cfg, w, d, shards=2, with_engram=True)
+    cat = Catalog(d, cfg, with_vision=False, with_engram=True)
+    path = str(tmp_path / "engram1.bin")
+    assert export_engram_table(cat, 1, path, chunk_rows=1024) == 3000
+    table = EngramTable(path, 3000, 264)
+    rec = torch.from_numpy(np.fromfile(path, dtype=np.uint8).reshape(3000, 264))
+    deq = dequant_rows_reference(rec, 256)
+    ref = w["layers.1.engram.embed.weight"]
+    assert float((deq - ref).abs().max()) <= 0.07 * float(ref.abs().max())
+    table.close()

@@ -240,3 +240,74 @@ def test_solo_request_is_served_by_speculative_rounds():
     assert collect(a) == want1 and collect(b) == want2
     assert spec.healthy, spec.error
     spec.close()
+
+
+def test_engram_pipeline_serves_requests(tmp_path):
+    """A backend whose engine has an Engram layer: every pass hashes its tokens, gathers table rows on the I/O thread and
+    applies the gated update.  The emitted tokens are what the fp32 oracle picks when it is given the same rows
+    (teacher forced over the emitted sequence), and a request continued from a prompt snapshot emits the same tokens as
+    a cold run (the slot's n-gram history is rebuilt from the reused tokens)."""
+    import numpy as np
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    from ds41rt_b200.models.engram import (EngramLayer, dequant_rows_reference, engram_reference,
+                                            init_engram_weights, random_table_rows)
+    from ds41rt_b200.models.reference import ReferenceModel
+    from ds41rt_b200.models.weights import init_weights
+    from ds41rt_b200.runtime.core import EngramHistory
+    from ds41rt_b200.runtime.engram import EngramPipeline
+    from ds41rt_b200.runtime.engram_io import EngramTable
+    from ds41rt_b200.serving.engine import GenRequest, NativeBackend
+    from ds41rt_b200.serving.protocol import Sampling
+    cfg = ModelConfig.tiny()
+    w = init_weights(cfg, seed=11)
+    dev = torch.device("cuda", 0)
+    n_rows = 4096
+    rec = random_table_rows(n_rows, seed=2)
+    path = str(tmp_path / "engram.bin")
+    rec.numpy().tofile(path)
+    wkv, q_w, k_w = init_engram_weights(cfg.hidden, seed=4, std=0.002)
+    bf = lambda t: t.bfloat16()
+    eng = DS41Engine(cfg, EngineWeights.from_fp32(cfg, w, 0, 1, dev), max_rows=16, slots=2, max_ctx=512)
+    eng.attach_engram(1, EngramLayer(bf(wkv).to(dev), bf(q_w).to(dev), bf(k_w).to(dev), cfg.hidden))
+    pipe = EngramPipeline([1], [EngramTable(path, n_rows, 264)], pad_id=2, max_rows=16, fold=True)
+    backend = NativeBackend(eng, eos=cfg.vocab - 1, concurrency=2, engram=pipe)
+
+    def run(prompt, n=8):
+        r = GenRequest(prompt_ids=prompt, max_tokens=n, sampling=Sampling(temperature=0.0))
+        backend.submit(r)
+        toks, usage = [], None
+        while True:
+            ev = r.events.get(timeout=120)
+            if ev.kind == "ready":
+                usage = ev.usage
+            elif ev.kind == "tokens":
+                toks += ev.tokens
+            elif ev.kind == "finish":
+                return toks, usage
+            elif ev.kind == "error":
+                raise RuntimeError(ev.message)
+
+    try:
+        g = torch.Generator().manual_seed(3)
+        prompt = torch.randint(3, 2000, (40,), generator=g).tolist()
+        cold, _ = run(prompt + [5, 6, 7])
+        backend.snapshots.clear()
+        got, _ = run(prompt)
+        warm, usage = run(prompt + [5, 6, 7])
+        assert usage["prompt_cache_hit_tokens"] == len(prompt) and warm == cold
+        assert pipe.stats()["gather"][0]["requests"] > 0
+    finally:
+        backend.close()
+    # teacher-forced oracle over prompt + emitted tokens with the same table rows
+    full = prompt + got
+    ids = (EngramHistory(2).prepare(full)[:, 0, :].reshape(-1) % np.uint64(n_rows)).astype(np.int64)
+    deq = dequant_rows_reference(rec[torch.from_numpy(ids)], 256).bfloat16().view(len(full), 24 * 256)
+    ref = ReferenceModel(cfg, w)
+    ref.engram_hook = lambda l, s: engram_reference(s.bfloat16(), deq[: s.shape[0]], bf(wkv), bf(q_w), bf(k_w)) if l == 1 else s
+    logits = ref.forward(torch.tensor(full))
+    want = logits[len(prompt) - 1:-1].argmax(-1).tolist()
+    agree = sum(int(a == b) for a, b in zip(want, got))
+    assert agree >= len(got) - 2, (want, got)
+    plain = ReferenceModel(cfg, w).forward(torch.tensor(full))[len(prompt) - 1:-1].argmax(-1).tolist()
+    assert plain != want                                  # the memory layer changes what is generated
