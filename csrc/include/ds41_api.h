@@ -165,6 +165,21 @@ int ds41_index_prepare(const void* q, long long ldq, int q_off, const void* idx_
                        void* qr, void* kc, int* n_vis, void* stream);
 int ds41_topk_select(const float* scores, int max_keys, const int* row_pos, const int* row_slot, int ratio, int k,
                      int* sel, int* n_sel, int rows, void* stream);
+// Candidate blocks of the long-context indexer: ds41_candidate_select reduces one layer's scores to block maxima (blocks
+// of `block` keys, the newest visible block pinned), keeps the best `k_blocks` blocks per row and publishes them as a list
+// [rows, k_blocks] and a bit mask [rows, words] (32 * words * block >= max_keys).  The *_cand variants of the score and
+// top-k kernels skip / exclude keys whose block bit is 0 (cand_mask null = unrestricted).
+int ds41_candidate_select(const float* scores, int max_keys, const int* row_pos, const int* row_slot, int ratio,
+                          int block, int k_blocks, int* blocks, int* n_blocks, void* mask, int words, int rows,
+                          void* stream);
+int ds41_index_score_cand(const void* q, long long ldq, int q_off, const float* w, int w_stride, int w_off,
+                          const void* idx_pool, const int* page_table, int max_pages, int page_rows,
+                          const int* row_pos, const int* row_slot, const float* inv_freq_idx, int rows, int IH, int ID,
+                          int ratio, float* scores, int max_keys, const void* cand_mask, int cand_words,
+                          int cand_block, void* stream);
+int ds41_topk_select_cand(const float* scores, int max_keys, const int* row_pos, const int* row_slot, int ratio, int k,
+                          int* sel, int* n_sel, int rows, const void* cand_mask, int cand_words, int cand_block,
+                          void* stream);
 int ds41_attend(const void* q, long long ldq, int q_off, int rows, int heads, int D, int window, int ring,
                 const int* row_pos, const int* row_slot, const void* win, const void* comp_pool, const int* sel,
                 const int* n_sel, int k, const int* page_table, int max_pages, int page_rows, const float* inv_freq,

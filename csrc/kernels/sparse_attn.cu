@@ -44,7 +44,15 @@ struct IndexScoreParams {
   int rows, IH, ID, ratio;
   float* scores;              // [rows][max_keys]
   int max_keys;
+  const uint32_t* cand_mask;  // optional [rows][cand_words]: one bit per block of cand_block keys; 0 = not scored
+  int cand_words, cand_block;
 };
+
+__device__ __forceinline__ bool cand_allowed(const uint32_t* mask, int words, int block, int r, int key) {
+  if (mask == nullptr) return true;
+  const int b = key / block;
+  return (mask[1ll * r * words + (b >> 5)] >> (b & 31)) & 1u;
+}
 
 // grid (blocks_x, rows), 256 threads; IH <= 32, ID <= 128
 __global__ void __launch_bounds__(256) index_score_kernel(IndexScoreParams p) {
@@ -78,6 +86,10 @@ __global__ void __launch_bounds__(256) index_score_kernel(IndexScoreParams p) {
   if (tid < 32) ws[tid] = tid < p.IH ? p.w[1ll * r * p.w_stride + p.w_off + tid] : 0.f;
   __syncthreads();
   for (int c = blockIdx.x * 8 + warp; c < n_vis; c += gridDim.x * 8) {
+    if (!cand_allowed(p.cand_mask, p.cand_words, p.cand_block, r, c)) {      // warp-uniform: c is per warp
+      if (lane == 0) p.scores[1ll * r * p.max_keys + c] = -INFINITY;
+      continue;
+    }
     const long long phys = pool_row(p.page_table, p.max_pages, p.page_rows, slot, c);
     __syncwarp();
     for (int d = lane * 2; d < p.ID; d += 64) {
@@ -174,6 +186,80 @@ __device__ __forceinline__ int block_excl_scan_1024(int v, int* warp_tot /*[32]*
   return warp_tot[warp] + incl - v;
 }
 
+// Exact top-k of one row by a block of 1024 threads.  key(i) is the order-preserving 32-bit key of element i, 0 for an
+// element that must never be chosen.  Writes the chosen ids in ascending order (-1 padded) and their count.  With at most
+// k eligible elements all of them are chosen; otherwise a 4-pass radix select finds the k-th largest key and ties on it
+// go to the lowest ids.
+template <class Key>
+__device__ void select_topk_row(Key key, int n, int k, int* out, int* n_out) {
+  __shared__ int hist[256];
+  __shared__ int warp_tot[32];
+  __shared__ int s_total;
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_need;
+  __shared__ int s_valid;
+  const int tid = threadIdx.x;
+  if (tid == 0) s_valid = 0;
+  __syncthreads();
+  int mine = 0;
+  for (int i = tid; i < n; i += 1024) mine += key(i) != 0u;
+  if (mine) atomicAdd(&s_valid, mine);
+  __syncthreads();
+  const int valid = s_valid;
+  for (int i = valid + tid; i < k; i += 1024) out[i] = -1;
+  uint32_t thr = 0;
+  int need = 0;
+  if (valid > k) {
+    uint32_t prefix = 0, mask = 0;
+    need = k;
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      if (tid < 256) hist[tid] = 0;
+      __syncthreads();
+      for (int i = tid; i < n; i += 1024) {
+        const uint32_t u = key(i);
+        if (u != 0u && (u & mask) == prefix) atomicAdd(&hist[(u >> shift) & 255], 1);
+      }
+      __syncthreads();
+      if (tid == 0) {
+        int cum = 0, d = 255;
+        for (; d > 0; --d) {
+          if (cum + hist[d] >= need) break;
+          cum += hist[d];
+        }
+        s_prefix = prefix | (static_cast<uint32_t>(d) << shift);
+        s_need = need - cum;
+      }
+      __syncthreads();
+      prefix = s_prefix;
+      need = s_need;
+      mask |= 0xFFu << shift;
+      __syncthreads();
+    }
+    thr = prefix;                   // exact key of the k-th largest element; `need` of the equal ones are kept
+  }
+  // ---- ordered compaction (ascending id): keep key > thr, and the first `need` keys == thr
+  int base = 0, eq_base = 0;
+  for (int c0 = 0; c0 < n; c0 += 1024) {
+    const int i = c0 + tid;
+    uint32_t u = 0;
+    if (i < n) u = key(i);
+    const int is_eq = (i < n && u != 0u && u == thr) ? 1 : 0;
+    int eq_total;
+    const int eq_rank = eq_base + block_excl_scan_1024(is_eq, warp_tot, &s_total);
+    __syncthreads();
+    eq_total = s_total;
+    const int keep = (i < n && u != 0u && (u > thr || (is_eq && eq_rank < need))) ? 1 : 0;
+    const int at = base + block_excl_scan_1024(keep, warp_tot, &s_total);
+    __syncthreads();
+    if (keep && at < k) out[at] = i;
+    base += s_total;
+    eq_base += eq_total;
+    __syncthreads();
+  }
+  if (tid == 0) *n_out = min(base, k);
+}
+
 struct TopkParams {
   const float* scores;   // [rows][max_keys]
   int max_keys;
@@ -182,14 +268,11 @@ struct TopkParams {
   int ratio, k;
   int* sel;              // [rows][k]  ascending ids, -1 padded
   int* n_sel;            // [rows]
+  const uint32_t* cand_mask;   // optional [rows][cand_words]: keys of blocks whose bit is 0 are not eligible
+  int cand_words, cand_block;
 };
 
 __global__ void __launch_bounds__(1024) topk_select_kernel(TopkParams p) {
-  __shared__ int hist[256];
-  __shared__ int warp_tot[32];
-  __shared__ int s_total;
-  __shared__ uint32_t s_prefix;
-  __shared__ int s_need;
   const int r = blockIdx.x, tid = threadIdx.x;
   pdl_launch_dependents();
   pdl_wait();
@@ -201,60 +284,70 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(TopkParams p) {
     return;
   }
   const int n = min((pos + 1) / p.ratio, p.max_keys);
-  if (n <= p.k) {
+  if (n <= p.k && p.cand_mask == nullptr) {
     for (int i = tid; i < p.k; i += 1024) out[i] = i < n ? i : -1;
     if (tid == 0) p.n_sel[r] = n;
     return;
   }
   const float* sc = p.scores + 1ll * r * p.max_keys;
-  // ---- radix select of the k-th largest key (4 passes of 8 bits)
-  uint32_t prefix = 0, mask = 0;
-  int need = p.k;
-  for (int pass = 0; pass < 4; ++pass) {
-    const int shift = 24 - 8 * pass;
-    if (tid < 256) hist[tid] = 0;
-    __syncthreads();
-    for (int i = tid; i < n; i += 1024) {
-      const uint32_t u = orderable(sc[i]);
-      if ((u & mask) == prefix) atomicAdd(&hist[(u >> shift) & 255], 1);
-    }
-    __syncthreads();
-    if (tid == 0) {
-      int cum = 0, d = 255;
-      for (; d > 0; --d) {
-        if (cum + hist[d] >= need) break;
-        cum += hist[d];
-      }
-      s_prefix = prefix | (static_cast<uint32_t>(d) << shift);
-      s_need = need - cum;
-    }
-    __syncthreads();
-    prefix = s_prefix;
-    need = s_need;
-    mask |= 0xFFu << shift;
-    __syncthreads();
+  const uint32_t* cm = p.cand_mask;
+  const int words = p.cand_words, blk = p.cand_block;
+  select_topk_row(
+      [=](int i) -> uint32_t {
+        if (!cand_allowed(cm, words, blk, r, i)) return 0u;
+        const uint32_t u = orderable(sc[i]);
+        return u == 0u ? 1u : u;
+      },
+      n, p.k, out, p.n_sel + r);
+}
+
+// Candidate blocks: the scores of one index layer are reduced to one score per block of `block` consecutive keys (the
+// maximum), the newest visible block is pinned, the best `k_blocks` blocks are chosen and published both as a list
+// (ascending block ids) and as a bit mask that the later index layers use to restrict scoring and selection.
+struct CandParams {
+  const float* scores;   // [rows][max_keys]
+  int max_keys;
+  const int* row_pos;
+  const int* row_slot;
+  int ratio, block, k_blocks;
+  int* blocks;           // [rows][k_blocks]
+  int* n_blocks;         // [rows]
+  uint32_t* mask;        // [rows][words]
+  int words;
+};
+
+__global__ void __launch_bounds__(1024) candidate_select_kernel(CandParams p) {
+  const int r = blockIdx.x, tid = threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
+  uint32_t* mask = p.mask + 1ll * r * p.words;
+  int* out = p.blocks + 1ll * r * p.k_blocks;
+  for (int i = tid; i < p.words; i += 1024) mask[i] = 0u;
+  const int n_vis = p.row_slot[r] < 0 ? 0 : min((p.row_pos[r] + 1) / p.ratio, p.max_keys);
+  const int nb = (n_vis + p.block - 1) / p.block;
+  if (nb == 0) {
+    for (int i = tid; i < p.k_blocks; i += 1024) out[i] = -1;
+    if (tid == 0) p.n_blocks[r] = 0;
+    return;
   }
-  const uint32_t thr = prefix;      // exact key of the k-th largest element; `need` of the equal ones are kept
-  // ---- ordered compaction (ascending row id): keep key > thr, and the first `need` keys == thr
-  int base = 0, eq_base = 0;
-  for (int c0 = 0; c0 < n; c0 += 1024) {
-    const int i = c0 + tid;
-    uint32_t u = 0;
-    if (i < n) u = orderable(sc[i]);
-    const int is_eq = (i < n && u == thr) ? 1 : 0;
-    int eq_total;
-    const int eq_rank = eq_base + block_excl_scan_1024(is_eq, warp_tot, &s_total);
-    __syncthreads();
-    eq_total = s_total;
-    const int keep = (i < n && (u > thr || (is_eq && eq_rank < need))) ? 1 : 0;
-    const int at = base + block_excl_scan_1024(keep, warp_tot, &s_total);
-    __syncthreads();
-    if (keep && at < p.k) out[at] = i;
-    base += s_total;
-    eq_base += eq_total;
-    __syncthreads();
+  const float* sc = p.scores + 1ll * r * p.max_keys;
+  const int B = p.block, newest = (n_vis - 1) / B;
+  select_topk_row(
+      [=](int b) -> uint32_t {
+        if (b == newest) return 0xFFFFFFFFu;
+        float m = -INFINITY;
+        const int hi = min(B, n_vis - b * B);
+        for (int j = 0; j < hi; ++j) m = fmaxf(m, sc[b * B + j]);
+        const uint32_t u = orderable(m);
+        return u == 0u ? 1u : u;
+      },
+      nb, p.k_blocks, out, p.n_blocks + r);
+  __syncthreads();                    // the list and its count (written by this block) are visible to all threads
+  const int n = p.n_blocks[r];
+  for (int i = tid; i < n; i += 1024) {
+    const int b = out[i];
+    atomicOr(&mask[b >> 5], 1u << (b & 31));
   }
-  if (tid == 0) p.n_sel[r] = min(base, p.k);
 }
 
 // ---------------------------------------------------------------------------------------- attention
@@ -901,17 +994,28 @@ static cudaError_t launch_attend(const AttendParams& p, cudaStream_t stream) {
 
 using namespace ds41;
 
+extern "C" int ds41_index_score_cand(const void* q, long long ldq, int q_off, const float* w, int w_stride, int w_off,
+                                     const void* idx_pool, const int* page_table, int max_pages, int page_rows,
+                                     const int* row_pos, const int* row_slot, const float* inv_freq_idx, int rows,
+                                     int IH, int ID, int ratio, float* scores, int max_keys, const void* cand_mask,
+                                     int cand_words, int cand_block, void* stream) {
+  if (rows <= 0 || IH > 32 || ID > 128 || (ID & 3)) return cudaErrorInvalidValue;
+  if (cand_mask != nullptr && (cand_words <= 0 || cand_block <= 0)) return cudaErrorInvalidValue;
+  IndexScoreParams p{static_cast<const __nv_bfloat16*>(q), ldq, q_off, w, w_stride, w_off,
+                     static_cast<const __nv_bfloat16*>(idx_pool), page_table, max_pages, page_rows, row_pos,
+                     row_slot, inv_freq_idx, rows, IH, ID, ratio, scores, max_keys,
+                     static_cast<const uint32_t*>(cand_mask), cand_words, cand_block};
+  int bx = (max_keys + 7) / 8;
+  if (bx > 256) bx = 256;
+  return launch_pdl(index_score_kernel, dim3(bx, rows), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
+}
+
 extern "C" int ds41_index_score(const void* q, long long ldq, int q_off, const float* w, int w_stride, int w_off,
                                 const void* idx_pool, const int* page_table, int max_pages, int page_rows,
                                 const int* row_pos, const int* row_slot, const float* inv_freq_idx, int rows, int IH,
                                 int ID, int ratio, float* scores, int max_keys, void* stream) {
-  if (rows <= 0 || IH > 32 || ID > 128 || (ID & 3)) return cudaErrorInvalidValue;
-  IndexScoreParams p{static_cast<const __nv_bfloat16*>(q), ldq, q_off, w, w_stride, w_off,
-                     static_cast<const __nv_bfloat16*>(idx_pool), page_table, max_pages, page_rows, row_pos,
-                     row_slot, inv_freq_idx, rows, IH, ID, ratio, scores, max_keys};
-  int bx = (max_keys + 7) / 8;
-  if (bx > 256) bx = 256;
-  return launch_pdl(index_score_kernel, dim3(bx, rows), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
+  return ds41_index_score_cand(q, ldq, q_off, w, w_stride, w_off, idx_pool, page_table, max_pages, page_rows, row_pos,
+                               row_slot, inv_freq_idx, rows, IH, ID, ratio, scores, max_keys, nullptr, 0, 0, stream);
 }
 
 extern "C" int ds41_index_prepare(const void* q, long long ldq, int q_off, const void* idx_pool, const int* page_table,
@@ -921,17 +1025,36 @@ extern "C" int ds41_index_prepare(const void* q, long long ldq, int q_off, const
   if (rows <= 0 || n_keys <= 0 || IH <= 0 || ID <= 0 || (ID & 7)) return cudaErrorInvalidValue;
   IndexScoreParams p{static_cast<const __nv_bfloat16*>(q), ldq, q_off, nullptr, 0, 0,
                      static_cast<const __nv_bfloat16*>(idx_pool), page_table, max_pages, page_rows, row_pos,
-                     row_slot, inv_freq_idx, rows, IH, ID, ratio, nullptr, max_keys};
+                     row_slot, inv_freq_idx, rows, IH, ID, ratio, nullptr, max_keys, nullptr, 0, 0};
   return launch_pdl(index_prepare_kernel, dim3(rows + (n_keys + 7) / 8), dim3(256), 0,
                     static_cast<cudaStream_t>(stream), p, n_keys, static_cast<__nv_bfloat16*>(qr),
                     static_cast<__nv_bfloat16*>(kc), n_vis);
 }
 
+extern "C" int ds41_topk_select_cand(const float* scores, int max_keys, const int* row_pos, const int* row_slot,
+                                     int ratio, int k, int* sel, int* n_sel, int rows, const void* cand_mask,
+                                     int cand_words, int cand_block, void* stream) {
+  if (rows <= 0 || k <= 0) return cudaErrorInvalidValue;
+  if (cand_mask != nullptr && (cand_words <= 0 || cand_block <= 0)) return cudaErrorInvalidValue;
+  TopkParams p{scores, max_keys, row_pos, row_slot, ratio, k, sel, n_sel,
+               static_cast<const uint32_t*>(cand_mask), cand_words, cand_block};
+  return launch_pdl(topk_select_kernel, dim3(rows), dim3(1024), 0, static_cast<cudaStream_t>(stream), p);
+}
+
 extern "C" int ds41_topk_select(const float* scores, int max_keys, const int* row_pos, const int* row_slot,
                                 int ratio, int k, int* sel, int* n_sel, int rows, void* stream) {
-  if (rows <= 0 || k <= 0) return cudaErrorInvalidValue;
-  TopkParams p{scores, max_keys, row_pos, row_slot, ratio, k, sel, n_sel};
-  return launch_pdl(topk_select_kernel, dim3(rows), dim3(1024), 0, static_cast<cudaStream_t>(stream), p);
+  return ds41_topk_select_cand(scores, max_keys, row_pos, row_slot, ratio, k, sel, n_sel, rows, nullptr, 0, 0, stream);
+}
+
+extern "C" int ds41_candidate_select(const float* scores, int max_keys, const int* row_pos, const int* row_slot,
+                                     int ratio, int block, int k_blocks, int* blocks, int* n_blocks, void* mask,
+                                     int words, int rows, void* stream) {
+  if (rows <= 0 || block <= 0 || k_blocks <= 0 || ratio <= 0 || scores == nullptr || blocks == nullptr ||
+      n_blocks == nullptr || mask == nullptr || 32ll * words * block < max_keys)
+    return cudaErrorInvalidValue;
+  CandParams p{scores, max_keys, row_pos, row_slot, ratio, block, k_blocks, blocks, n_blocks,
+               static_cast<uint32_t*>(mask), words};
+  return launch_pdl(candidate_select_kernel, dim3(rows), dim3(1024), 0, static_cast<cudaStream_t>(stream), p);
 }
 
 extern "C" int ds41_attend(const void* q, long long ldq, int q_off, int rows, int heads, int D, int window, int ring,

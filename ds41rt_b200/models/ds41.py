@@ -575,6 +575,16 @@ class DS41Engine:
             self.idx_vis = z((R,), I32)
         self.sel = z((R, cfg.index_topk), I32)
         self.n_sel = z((R,), I32)
+        # candidate blocks: the candidate layer's block selection (list + bit mask per row) restricts the index layers
+        # above it (reference: native/cuda/kernels/v41_candidate_blocks.cu:18-44)
+        self.cand_on = cfg.candidate_layer >= 0 and cfg.candidate_topk_blocks > 0 and cfg.candidate_layer < self.n_layers
+        if self.cand_on:
+            nb = (self.max_keys + cfg.candidate_block - 1) // cfg.candidate_block
+            self.cand_words = (nb + 31) // 32
+            self.cand_mask = z((R, self.cand_words), I32)
+            self.cand_blocks = z((R, cfg.candidate_topk_blocks), I32)
+            self.cand_count = z((R,), I32)
+        self._cand_ratio = None     # ratio of the source the live candidate mask was computed on (None = no mask)
         self.n_splits_attn = (cfg.window + 16 + cfg.index_topk + 63) // 64
         cells = max(r * self._attn_splits(r) for r in range(1, R + 1))      # (row, split) partial outputs
         self.part_o = z((cells, self.HL, D), F32)
@@ -842,6 +852,8 @@ class DS41Engine:
         H, D, Q = cfg.hidden, cfg.head_dim, cfg.q_lora
         R = rows
         last_layer = self.n_layers if last_layer is None else last_layer
+        if first_layer == 0:
+            self._cand_ratio = None
         if embed:
             self._cur, self._ccur = 0, 0
             self._run("embed", k.ds41_embed_streams, lib.ptr(self.in_tokens), lib.ptr(self.w.embed), lib.ptr(self.streams),
@@ -891,6 +903,10 @@ class DS41Engine:
                        status=self.status, static_operand=1)
             if lw.index_heads_cols and src is not None:
                 ratio = cfg.source_layers[src]
+                # index layers above the candidate layer score and select only inside its candidate blocks
+                restrict = self.cand_on and l > cfg.candidate_layer and self._cand_ratio == ratio
+                cand = (lib.ptr(self.cand_mask), self.cand_words, cfg.candidate_block) if restrict \
+                    else (lib.ptr(None), 0, 0)
                 hint = self._pass_hint
                 n_keys = min((hint[1] + 1) // ratio, self.max_keys) if hint is not None and hint[0] == R else 0
                 if n_keys >= 64 and cfg.index_heads == 32 and cfg.index_dim % 64 == 0:
@@ -905,15 +921,21 @@ class DS41Engine:
                               bn=256 if n_keys >= 256 else 64, row_w=self.extras[:, w_off:], row_w_ld=lw.extra_cols,
                               col_limit=self.idx_vis, status=self.status)
                 else:
-                    self._run("index_score", k.ds41_index_score,
+                    self._run("index_score", k.ds41_index_score_cand,
                         lib.ptr(self.qb_out), C.c_longlong(self.nqb), self.HL * D, lib.ptr(self.extras), lw.extra_cols,
                         lw.extra_cols - cfg.index_heads, lib.ptr(self.cache.idx[src]), lib.ptr(self.cache.page_table),
                         self.cache.max_pages, self.cache.page_rows[src], lib.ptr(self.row_pos), lib.ptr(self.row_slot),
                         lib.ptr(self.inv_idx), R, cfg.index_heads, cfg.index_dim, ratio, lib.ptr(self.scores),
-                        self.max_keys, st())
-                self._run("topk", k.ds41_topk_select, lib.ptr(self.scores), self.max_keys, lib.ptr(self.row_pos),
+                        self.max_keys, *cand, st())
+                if self.cand_on and l == cfg.candidate_layer:
+                    self._run("candidate_select", k.ds41_candidate_select, lib.ptr(self.scores), self.max_keys,
+                              lib.ptr(self.row_pos), lib.ptr(self.row_slot), ratio, cfg.candidate_block,
+                              cfg.candidate_topk_blocks, lib.ptr(self.cand_blocks), lib.ptr(self.cand_count),
+                              lib.ptr(self.cand_mask), self.cand_words, R, st())
+                    self._cand_ratio = ratio
+                self._run("topk", k.ds41_topk_select_cand, lib.ptr(self.scores), self.max_keys, lib.ptr(self.row_pos),
                                             lib.ptr(self.row_slot), ratio, cfg.index_topk, lib.ptr(self.sel),
-                                            lib.ptr(self.n_sel), R, st())
+                                            lib.ptr(self.n_sel), R, *cand, st())
             self._run("attend", k.ds41_attend, 
                 lib.ptr(self.qb_out), C.c_longlong(self.nqb), 0, R, self.HL, D, cfg.window, self.cache.ring,
                 lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.cache.win[l]),

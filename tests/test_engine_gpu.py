@@ -257,3 +257,49 @@ def test_fp8_kv_cache_rows_and_logits():
     agree = float((logits["fp8"].argmax(-1) == logits["bf16"].argmax(-1)).float().mean())
     print("fp8 kv: median / max logit drift", float(err.median()), float(err.max()), "scale", scale, "agreement", agree)
     assert float(err.median()) < 0.1 * scale and agree >= 0.5
+
+
+def test_candidate_blocks_restrict_later_index_layers():
+    """Three index layers over one compressed source; the first is the candidate layer (top-2 blocks of 8 keys), so the
+    two above it select their keys inside 16 candidates.  Rows whose discrete decisions agree with the oracle must have
+    matching logits, and the restriction must actually bite (the oracle's selections differ from unrestricted ones)."""
+    import dataclasses
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    from ds41rt_b200.models.reference import ReferenceModel
+    from ds41rt_b200.models.weights import init_weights
+    base = ModelConfig.tiny()
+    cfg = dataclasses.replace(base, name="tiny-cand", n_layers=3, source_layers={0: 2}, compress_ratios=[2, 2, 2],
+                              index_layers=(0, 1, 2), index_topk=8, candidate_layer=0, candidate_topk_blocks=2,
+                              candidate_block=8,
+                              dspark=dataclasses.replace(base.dspark, tap_layers=(0, 1)))
+    cfg.validate()
+    w = init_weights(cfg, seed=2)
+    wr = {k: (v.bfloat16().float() if v.dim() == 2 and not k.endswith("_fn") else v) for k, v in w.items()}
+    ref = ReferenceModel(cfg, wr)
+    free = ReferenceModel(dataclasses.replace(cfg, candidate_layer=-1, candidate_topk_blocks=0), wr)
+    eng = DS41Engine(cfg, EngineWeights.from_fp32(cfg, wr, 0, 1, torch.device("cuda")), max_rows=8, slots=1,
+                     max_ctx=256)
+    prompt = torch.randint(0, cfg.vocab, (96,), generator=torch.Generator().manual_seed(4))
+    with torch.no_grad():
+        want, traces = ref.forward(prompt, return_trace=True)
+        _, free_traces = free.forward(prompt, return_trace=True)
+    assert any(not torch.equal(a.select, b.select) for a, b in zip(traces[1:], free_traces[1:]))
+    assert eng.cache.ensure(0, 128)
+    got, same = [], []
+    toks = prompt.tolist()
+    for c0 in range(0, len(toks), 8):
+        part = toks[c0:c0 + 8]
+        eng.debug = []
+        eng.set_rows(part, list(range(c0, c0 + len(part))), [0] * len(part))
+        eng.forward_rows(len(part))
+        got.append(eng.logits_rows(len(part)).cpu())
+        same.append(_decisions_match(cfg, traces, eng.debug, c0, len(part), None))
+    eng.debug = None
+    torch.cuda.synchronize()
+    eng.check_status()
+    got, same = torch.cat(got, 0), torch.cat(same, 0)
+    err = (got - want).abs().max(dim=1).values
+    scale = float(want.abs().max())
+    assert int(same.sum()) >= 0.5 * len(same), int(same.sum())
+    assert float(err[same].max()) < 0.05 * scale, (float(err[same].max()), scale)

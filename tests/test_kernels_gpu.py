@@ -379,3 +379,51 @@ def test_nvfp4_activation_quantiser_matches_oracle():
     want_atoms = pack_sf_atoms(want_s.view(torch.uint8))
     from ds41rt_b200.ops.mx import unpack_sf_atoms
     assert torch.equal(unpack_sf_atoms(sf.cpu(), rows), unpack_sf_atoms(want_atoms.cpu(), rows))
+
+
+def test_candidate_blocks_select_and_restrict():
+    """Candidate layer: block maxima, newest block pinned, best blocks kept (ties to the lowest block id) -> list + mask;
+    the masked top-k then only sees keys of those blocks."""
+    from ds41rt_b200.ops import lib
+    k = lib.kernels()
+    rows, max_keys, B, KB, topk = 5, 3000, 8, 40, 64
+    torch.manual_seed(1)
+    scores = torch.randn(rows, max_keys, device="cuda")
+    scores[1] = scores[1].round()                                  # ties between block maxima
+    pos = torch.tensor([2999, 2500, 100, 1203, 9], dtype=torch.int32, device="cuda")   # row 2: fewer blocks than KB
+    slot = torch.tensor([0, 0, 0, 0, -1], dtype=torch.int32, device="cuda")
+    nb = (max_keys + B - 1) // B
+    words = (nb + 31) // 32
+    blocks = torch.zeros(rows, KB, dtype=torch.int32, device="cuda")
+    n_blocks = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    mask = torch.full((rows, words), -1, dtype=torch.int32, device="cuda")
+    lib.check(k.ds41_candidate_select(lib.ptr(scores), max_keys, lib.ptr(pos), lib.ptr(slot), 1, B, KB, lib.ptr(blocks),
+                                      lib.ptr(n_blocks), lib.ptr(mask), words, rows, lib.stream()), "candidate_select")
+    sel = torch.zeros(rows, topk, dtype=torch.int32, device="cuda")
+    n_sel = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    scores2 = torch.randn(rows, max_keys, device="cuda")           # a later layer's scores
+    lib.check(k.ds41_topk_select_cand(lib.ptr(scores2), max_keys, lib.ptr(pos), lib.ptr(slot), 1, topk, lib.ptr(sel),
+                                      lib.ptr(n_sel), rows, lib.ptr(mask), words, B, lib.stream()), "topk_cand")
+    torch.cuda.synchronize()
+    bits = mask.cpu().numpy().view("uint32")
+    for r in range(4):
+        n = int(pos[r]) + 1
+        nbv = (n + B - 1) // B
+        s = scores[r, :n].cpu()
+        s = torch.nn.functional.pad(s, (0, nbv * B - n), value=float("-inf")).view(nbv, B).amax(-1)
+        s[(n - 1) // B] = float("inf")
+        want = sorted(torch.sort(s, descending=True, stable=True).indices[:KB].tolist())
+        got = blocks[r, : int(n_blocks[r])].tolist()
+        assert got == want, r
+        on = [b for b in range(nb) if (int(bits[r, b >> 5]) >> (b & 31)) & 1]
+        assert on == want
+        # restricted selection of the later layer
+        allowed = torch.zeros(n, dtype=torch.bool)
+        for b in want:
+            allowed[b * B: (b + 1) * B] = True
+        s2 = scores2[r, :n].cpu().masked_fill(~allowed, float("-inf"))
+        n_ok = int(allowed.sum())
+        order = torch.sort(s2, descending=True, stable=True).indices[: min(topk, n_ok)]
+        assert sel[r, : int(n_sel[r])].tolist() == sorted(order.tolist()), r
+        assert int(n_sel[r]) == min(topk, n_ok)
+    assert int(n_blocks[4]) == 0 and int(n_sel[4]) == 0 and not bits[4].any()
