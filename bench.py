@@ -120,19 +120,28 @@ def prefill_bench(args, fabric, cfg, n_layers):
     t0 = time.time()
     weights = EngineWeights.random(cfg, rank, world, dev, seed=0, expert_dtype=args.expert_dtype)
     P = args.prompt
+    if args.ced:
+        # encoder / decoder-replay prompt passes: the boundary is the model's own (layer 20 of 40); a truncated stack
+        # keeps the same half-and-half split if it still has no compressed source above it
+        import dataclasses
+        if not cfg.ced_on:
+            cfg = dataclasses.replace(cfg, ced_boundary=args.ced_boundary or max(cfg.source_layers, default=0))
+        if not cfg.ced_on:
+            raise SystemExit("--ced: this layer count has no usable encoder/decoder boundary")
     eng = DS41Engine(cfg, weights, fabric, max_rows=args.chunk, slots=1, max_ctx=(P + 127) // 64 * 64)
+    run_prompt = eng.prefill_ced if args.ced else eng.prefill
     g = torch.Generator().manual_seed(1234)
     prompt = torch.randint(3, cfg.vocab - 600, (P,), generator=g).tolist()
     setup_s = time.time() - t0
     l0 = eng.launches
     for _ in range(W):
-        eng.prefill(0, prompt, chunk=args.chunk)
+        run_prompt(0, prompt, chunk=args.chunk)
     per_prompt = (eng.launches - l0) // W
     eng.check_status("prefill warm-up")
     sampler = ClockSampler(dev.index or 0)
     if rank == 0:
         sampler.start()
-    ms = timed(fabric, torch, lambda: [eng.prefill(0, prompt, chunk=args.chunk) for _ in range(K)])
+    ms = timed(fabric, torch, lambda: [run_prompt(0, prompt, chunk=args.chunk) for _ in range(K)])
     clocks = sampler.stop() if rank == 0 else {}
     eng.check_status("timed prefill")
     if args.breakdown:
@@ -140,7 +149,7 @@ def prefill_bench(args, fabric, cfg, n_layers):
         # the time its kernels spend waiting for slower peers
         fabric.barrier()
         eng.timeline = []
-        eng.prefill(0, prompt, chunk=args.chunk)
+        run_prompt(0, prompt, chunk=args.chunk)
         torch.cuda.synchronize()
         acc = {}
         for tag, e0, e1 in eng.timeline:
@@ -156,14 +165,16 @@ def prefill_bench(args, fabric, cfg, n_layers):
     torch.cuda.synchronize()
     t1 = time.perf_counter()
     for _ in range(K):
-        eng.prefill(0, prompt, chunk=args.chunk)
+        run_prompt(0, prompt, chunk=args.chunk)
     torch.cuda.synchronize()
     e2e_s = fabric.all_reduce_max(time.perf_counter() - t1)
     if rank == 0:
         value = K * P / (ms / 1e3)
         chunks = (P + args.chunk - 1) // args.chunk
         line = {
-            "metric": "prefill tok/s (one prompt, chunked passes)", "value": round(value, 1), "unit": "tok/s",
+            "metric": "prefill tok/s (one prompt, chunked passes)" if not args.ced else
+                      f"prefill tok/s (one prompt, layers below {cfg.ced_boundary} over all tokens, layers from it "
+                      f"upwards over the last {cfg.ced_replay})", "value": round(value, 1), "unit": "tok/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 3), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": round(value / BASELINE_PREFILL, 3),
             "dtype": "bf16 dense / fp8-e4m3 experts (fp32 accumulate)", "data": "synthetic",
@@ -282,6 +293,10 @@ def main():
     ap.add_argument("--chunk", type=int, default=1024, help="rows per pass in --mode prefill")
     ap.add_argument("--concurrency", type=int, default=1, help="decode: number of concurrent requests (greedy, no drafter)")
     ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8"], help="latent KV rows in the cache")
+    ap.add_argument("--ced", action="store_true",
+                    help="prefill: the decoder layers run over the last 128 prompt tokens only (the reference's prompt "
+                         "scheme); default is every layer over every token")
+    ap.add_argument("--ced-boundary", type=int, default=0, help="first decoder layer for --ced on a truncated stack")
     ap.add_argument("--breakdown", action="store_true", help="prefill: per-kernel device time of one prompt (stderr)")
     args = ap.parse_args()
     if args.impl == "reference":

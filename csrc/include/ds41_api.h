@@ -288,6 +288,15 @@ typedef struct {
 int ds41_sample_rows(const float* logits, long long ld, int rows, int vocab, const uint32_t* masks, int mask_words,
                      const ds41_sample_row* params, int* tokens, int* status, void* stream);
 
+// ds41_attend with a per-row floor on the window: positions below row_lo[r] are not attended (a window that was
+// rebuilt from that position on, e.g. the decoder layers after a prompt's tail replay); row_lo null = no floor.
+int ds41_attend_floor(const void* q, long long ldq, int q_off, int rows, int heads, int D, int window, int ring,
+                      const int* row_pos, const int* row_slot, const void* win, const void* comp_pool, const int* sel,
+                      const int* n_sel, int k, const int* page_table, int max_pages, int page_rows,
+                      const float* inv_freq, int rope_dim, float scale, int n_splits, const int* row_hi, float* part_o,
+                      float* part_ml, const float* sink, void* out, long long ldo, int kv_row_bytes, const int* row_lo,
+                      void* stream);
+
 // ---------------------------------------------------------------------------------------------------
 // Engram memory (engram.cu): table rows (dim e4m3 values + dim/32 UE8M0 scales, row_bytes apart) -> bf16 [n_rows, dim];
 // gated residual update of the 4 streams from kv = [rows][4 keys + 1 value][H] (bf16); text_mask 0 = pass through.

@@ -385,6 +385,7 @@ struct AttendParams {
   float* part_o;               // [rows][n_splits][heads][D]
   float* part_ml;              // [rows][n_splits][heads][2]
   int kv_row_bytes;            // 0: win / comp_pool rows are bf16 [D]; else FP8 rows (D e4m3 + D/32 UE8M0, padded)
+  const int* row_lo;           // optional [rows]: lowest visible window position (a window rebuilt from there on)
 };
 
 constexpr int kKeysPerCta = 64;
@@ -431,6 +432,7 @@ __global__ void __launch_bounds__(128) attend_kernel(AttendParams p) {
     // drafter rows may see later rows of their own block: row_hi gives the highest visible position
     if (p.row_hi != nullptr) hi_pos = max(pos, p.row_hi[r]);
     lo_pos = max(0, pos - p.window + 1);
+    if (p.row_lo != nullptr) lo_pos = max(lo_pos, p.row_lo[r]);
     n_w = hi_pos - lo_pos + 1;
     n_s = (p.comp_pool != nullptr && p.n_sel != nullptr) ? p.n_sel[r] : 0;
   }
@@ -676,6 +678,7 @@ __global__ void __launch_bounds__(512) attend_wide_kernel(AttendParams p) {
   if (slot >= 0) {
     if (p.row_hi != nullptr) hi_pos = max(pos, p.row_hi[r]);
     lo_pos = max(0, pos - p.window + 1);
+    if (p.row_lo != nullptr) lo_pos = max(lo_pos, p.row_lo[r]);
     n_w = hi_pos - lo_pos + 1;
     n_s = (p.comp_pool != nullptr && p.n_sel != nullptr) ? p.n_sel[r] : 0;
   }
@@ -1063,12 +1066,23 @@ extern "C" int ds41_attend(const void* q, long long ldq, int q_off, int rows, in
                            int page_rows, const float* inv_freq, int rope_dim, float scale, int n_splits,
                            const int* row_hi, float* part_o, float* part_ml, const float* sink, void* out,
                            long long ldo, int kv_row_bytes, void* stream) {
+  return ds41_attend_floor(q, ldq, q_off, rows, heads, D, window, ring, row_pos, row_slot, win, comp_pool, sel, n_sel, k,
+                           page_table, max_pages, page_rows, inv_freq, rope_dim, scale, n_splits, row_hi, part_o,
+                           part_ml, sink, out, ldo, kv_row_bytes, nullptr, stream);
+}
+
+extern "C" int ds41_attend_floor(const void* q, long long ldq, int q_off, int rows, int heads, int D, int window,
+                                 int ring, const int* row_pos, const int* row_slot, const void* win,
+                                 const void* comp_pool, const int* sel, const int* n_sel, int k, const int* page_table,
+                                 int max_pages, int page_rows, const float* inv_freq, int rope_dim, float scale,
+                                 int n_splits, const int* row_hi, float* part_o, float* part_ml, const float* sink,
+                                 void* out, long long ldo, int kv_row_bytes, const int* row_lo, void* stream) {
   if (rows <= 0 || heads <= 0 || rope_dim > 128 || (rope_dim & 7) || n_splits <= 0 || n_splits > 32)
     return cudaErrorInvalidValue;
   AttendParams p{static_cast<const __nv_bfloat16*>(q), ldq, q_off, rows, heads, window, ring, row_pos, row_slot,
                  static_cast<const __nv_bfloat16*>(win), static_cast<const __nv_bfloat16*>(comp_pool), sel, n_sel, k,
                  page_table, max_pages, page_rows, inv_freq, rope_dim, scale, n_splits, row_hi, part_o, part_ml,
-                 kv_row_bytes};
+                 kv_row_bytes, row_lo};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   if (D == 512) e = launch_attend<512>(p, s);

@@ -88,6 +88,11 @@ class ModelConfig:
     candidate_layer: int = 20
     candidate_topk_blocks: int = 2048
     candidate_block: int = 8
+    # prompt passes: layers below the boundary ("encoder") run over the whole prompt, the layers from it upwards
+    # ("decoder") only over the last `ced_replay` prompt tokens; the boundary layer still produces its compressed source
+    # for every token.  Inactive unless 0 < ced_boundary < n_layers.
+    ced_boundary: int = 20
+    ced_replay: int = 128
     # hyper-connections
     hc_mult: int = 4
     hc_sinkhorn_iters: int = 20
@@ -146,6 +151,13 @@ class ModelConfig:
             if s <= layer:
                 best = s
         return best
+
+    @property
+    def ced_on(self) -> bool:
+        """True when this model can prefill with the decoder layers replayed for the prompt's tail only: a boundary
+        inside the stack and no compressed source produced above it."""
+        b = self.ced_boundary
+        return 0 < b < self.n_layers and all(s <= b for s in self.source_layers if s < self.n_layers)
 
     def rope_for(self, layer: int) -> RopeConfig:
         return self.rope_plain if self.compress_ratios[layer] == 0 else self.rope_long

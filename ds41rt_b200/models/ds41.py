@@ -575,6 +575,8 @@ class DS41Engine:
             self.idx_vis = z((R,), I32)
         self.sel = z((R, cfg.index_topk), I32)
         self.n_sel = z((R,), I32)
+        self.row_lo = z((R,), I32)      # window floor per row (set_rows(row_lo=...)); used only while _floor_on
+        self._floor_on = False
         # candidate blocks: the candidate layer's block selection (list + bit mask per row) restricts the index layers
         # above it (reference: native/cuda/kernels/v41_candidate_blocks.cu:18-44)
         self.cand_on = cfg.candidate_layer >= 0 and cfg.candidate_topk_blocks > 0 and cfg.candidate_layer < self.n_layers
@@ -713,9 +715,13 @@ class DS41Engine:
         if err is not None:
             lib.check(err, tag)
 
-    def set_rows(self, tokens, positions, slots, row_hi=None):
-        """Host -> device copy of one pass's inputs (lists or CPU tensors)."""
+    def set_rows(self, tokens, positions, slots, row_hi=None, row_lo=None):
+        """Host -> device copy of one pass's inputs (lists or CPU tensors).  `row_lo` (one position per row) puts a
+        floor under the attention windows of the pass: positions below it are not attended."""
         n = len(tokens)
+        self._floor_on = row_lo is not None
+        if row_lo is not None:
+            self.row_lo.copy_(torch.tensor(list(row_lo) + [0] * (self.max_rows - n), dtype=I32), non_blocking=True)
         assert n <= self.max_rows
         pad = self.max_rows - n
         t = torch.tensor(list(tokens) + [0] * pad, dtype=I32)
@@ -846,8 +852,34 @@ class DS41Engine:
             self._finish(rows, scale, base, self.pre[cur], norm_w, self.pre[cur ^ 1], tap, quant)
         self._cur = cur ^ 1
 
+    def _qkv(self, l: int, lw: LayerWeights, R: int, inv, sources: bool = True):
+        """Fused q_a / kv / extras projection of layer `l` from self.xn, its post-processing (norms, RoPE, window-ring
+        rows) and, for a layer that produces a compressed source, the compressor (skipped with sources=False)."""
+        cfg, k, st = self.cfg, self.k, lib.stream
+        H, D, Q = cfg.hidden, cfg.head_dim, cfg.q_lora
+        ntot = lw.w_qkv.shape[0]
+        s_qkv = self._splits(ntot, H, R)
+        self._run("gemm_qkv", G.linear_planes, self.xn[:R], lw.w_qkv,
+                  self.planes_qkv.view(-1)[: s_qkv * R * ntot].view(s_qkv, R, ntot), s_qkv, status=self.status)
+        self._run("qkv_post", k.ds41_qkv_post,
+            lib.ptr(self.planes_qkv), s_qkv, R, ntot, Q, D, cfg.rope_dim, lw.extra_cols, lw.index_heads_cols,
+            C.c_float(cfg.index_weight_scale), lib.ptr(lw.q_norm), lib.ptr(lw.kv_norm), lib.ptr(inv),
+            lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.q_lat), lib.ptr(self.cache.win[l]),
+            self.cache.ring, lib.ptr(self.extras), C.c_float(cfg.norm_eps), self.cache.row_bytes, st())
+        if lw.ratio and sources:
+            self._run("compress", k.ds41_compress,
+                lib.ptr(self.extras), lw.extra_cols, R, D, cfg.index_dim, cfg.rope_dim, lw.ratio,
+                lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.cache.pending.get(l)),
+                lib.ptr(lw.comp_norm), lib.ptr(lw.wk_idx), lib.ptr(lw.k_norm), lib.ptr(inv), lib.ptr(self.inv_idx),
+                lib.ptr(self.cache.page_table), self.cache.max_pages, self.cache.page_rows[l],
+                lib.ptr(self.cache.comp[l]), lib.ptr(self.cache.idx[l]), C.c_float(cfg.norm_eps),
+                self.cache.row_bytes, st())
+
     def forward_rows(self, rows: int, *, embed: bool = True, head: bool = True, first_layer: int = 0,
-                     last_layer: Optional[int] = None):
+                     last_layer: Optional[int] = None, sources: bool = True):
+        """One pass over `rows` rows described by set_rows().  `first_layer` / `last_layer` run a slice of the stack
+        (the streams and the pending sublayer carry over between slices); `sources=False` leaves the compressed
+        sources untouched (decoder replay of a prompt's tail)."""
         cfg, k, st = self.cfg, self.k, lib.stream
         H, D, Q = cfg.hidden, cfg.head_dim, cfg.q_lora
         R = rows
@@ -866,7 +898,6 @@ class DS41Engine:
                           img_rows.shape[0], H, cfg.hc_mult, st())
         pending = None
         fused = R <= self.fused_rows
-        tap_i = 0
         if self.layer_timer is not None:
             self.layer_timer.begin()
         for l in range(first_layer, last_layer):
@@ -875,29 +906,13 @@ class DS41Engine:
             # ---------------- attention sublayer
             tap = None
             if self.taps is not None and cfg.dspark is not None and not self.layer_prefix_plain \
-                    and l in cfg.dspark.tap_layers and tap_i < self.taps.shape[0]:
-                tap = self.taps[tap_i]
-                tap_i += 1
+                    and l in cfg.dspark.tap_layers:
+                tap_i = cfg.dspark.tap_layers.index(l)
+                tap = self.taps[tap_i] if tap_i < self.taps.shape[0] else None
             self._hc(R, pending, lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, lw.attn_norm, tap=tap,
                      engram=self.engram[l] if l in self._engram_live else None)
-            ntot = lw.w_qkv.shape[0]
-            s_qkv = self._splits(ntot, H, R)
-            self._run("gemm_qkv", G.linear_planes, self.xn[:R], lw.w_qkv, self.planes_qkv.view(-1)[: s_qkv * R * ntot].view(s_qkv, R, ntot),
-                            s_qkv, status=self.status)
-            self._run("qkv_post", k.ds41_qkv_post, 
-                lib.ptr(self.planes_qkv), s_qkv, R, ntot, Q, D, cfg.rope_dim, lw.extra_cols, lw.index_heads_cols,
-                C.c_float(cfg.index_weight_scale), lib.ptr(lw.q_norm), lib.ptr(lw.kv_norm), lib.ptr(inv),
-                lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.q_lat), lib.ptr(self.cache.win[l]),
-                self.cache.ring, lib.ptr(self.extras), C.c_float(cfg.norm_eps), self.cache.row_bytes, st())
+            self._qkv(l, lw, R, inv, sources)
             src = None if self.layer_prefix_plain else cfg.source_of(l)
-            if lw.ratio:
-                self._run("compress", k.ds41_compress, 
-                    lib.ptr(self.extras), lw.extra_cols, R, D, cfg.index_dim, cfg.rope_dim, lw.ratio,
-                    lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.cache.pending.get(l)),
-                    lib.ptr(lw.comp_norm), lib.ptr(lw.wk_idx), lib.ptr(lw.k_norm), lib.ptr(inv), lib.ptr(self.inv_idx),
-                    lib.ptr(self.cache.page_table), self.cache.max_pages, self.cache.page_rows[l],
-                    lib.ptr(self.cache.comp[l]), lib.ptr(self.cache.idx[l]), C.c_float(cfg.norm_eps),
-                    self.cache.row_bytes, st())
             nqb = lw.w_qb.shape[0]
             self._run("gemm_qb", G.gemm_raw, lw.w_qb, self.q_lat, self.qb_out, nqb, R, Q, lda=Q, ldb=Q, ldo=self.nqb, out_mode=2,
                        status=self.status, static_operand=1)
@@ -936,7 +951,7 @@ class DS41Engine:
                 self._run("topk", k.ds41_topk_select_cand, lib.ptr(self.scores), self.max_keys, lib.ptr(self.row_pos),
                                             lib.ptr(self.row_slot), ratio, cfg.index_topk, lib.ptr(self.sel),
                                             lib.ptr(self.n_sel), R, *cand, st())
-            self._run("attend", k.ds41_attend, 
+            self._run("attend", k.ds41_attend_floor, 
                 lib.ptr(self.qb_out), C.c_longlong(self.nqb), 0, R, self.HL, D, cfg.window, self.cache.ring,
                 lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.cache.win[l]),
                 lib.ptr(self.cache.comp[src]) if src is not None else lib.ptr(None),
@@ -944,7 +959,7 @@ class DS41Engine:
                 self.cache.max_pages, self.cache.page_rows[src] if src is not None else 1, lib.ptr(inv), cfg.rope_dim,
                 C.c_float(cfg.softmax_scale), self._attn_splits(R), lib.ptr(self.row_hi), lib.ptr(self.part_o),
                 lib.ptr(self.part_ml), lib.ptr(lw.sink), lib.ptr(self.attn_out), C.c_longlong(self.HL * D),
-                self.cache.row_bytes, st())
+                self.cache.row_bytes, lib.ptr(self.row_lo if self._floor_on else None), st())
             # grouped wo_a: batch = local groups
             kg = cfg.heads_per_group * D
             self._run("gemm_wo_a", G.gemm_raw, lw.wo_a, self.attn_out, self.oa, cfg.o_lora, R, kg, lda=kg, ldb=self.HL * D,
@@ -1145,6 +1160,83 @@ class DS41Engine:
             if last:
                 nxt = int(self.chosen[self.last_head_row].item())
         return nxt
+
+    def boundary_source(self, rows: int, layer: int):
+        """Finish an encoder slice at `layer`: merge the pending sublayer into the streams, normalise layer `layer`'s
+        input and run only its projection + compressor, so that its compressed source covers these rows.  Afterwards
+        self.streams holds the complete streams entering `layer`; returns the index of the self.pre buffer that holds
+        the collapse weights they go with."""
+        lw = self.w.layers[layer]
+        pre_idx = self._cur
+        self._hc(rows, getattr(self, "_pending", None), lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, lw.attn_norm)
+        self._pending = None
+        if lw.ratio:
+            self._qkv(layer, lw, rows, self._inv(layer), True)
+        return pre_idx
+
+    def prefill_ced(self, slot: int, tokens: List[int], start: int = 0, chunk: Optional[int] = None) -> int:
+        """Prompt pass with the decoder layers replayed for the tail only: layers below cfg.ced_boundary run over every
+        chunk and the boundary layer produces its compressed source for every token; the layers from the boundary
+        upwards then run over the last cfg.ced_replay tokens, whose streams were kept at the boundary.  Falls back to
+        prefill() when the model has no usable boundary or when a continuation is shorter than the replay span (its
+        decoder windows must then be continued, not rebuilt).  Returns the greedy next token.
+        Reference: rust/crates/ds41rt-daemon/src/v41_backbone_cache/ced.rs:3-34,
+        rust/crates/ds41rt-daemon/src/v41_native_serve.rs:620-738."""
+        cfg = self.cfg
+        n = len(tokens)
+        if not self.ced_usable(start, n):
+            return self.prefill(slot, tokens, start, chunk)
+        chunk = chunk or self.max_rows
+        end = start + n
+        assert self.cache.ensure(slot, end + 1)
+        r0 = self.ced_replay_start(start, end)
+        for c0 in range(start, end, chunk):
+            c1 = min(end, c0 + chunk)
+            self.set_rows(tokens[c0 - start:c1 - start], list(range(c0, c1)), [slot] * (c1 - c0))
+            self.ced_encoder_slice(c0, c1, r0)
+        nxt = -1
+        for c0 in range(r0, end, chunk):
+            c1 = min(end, c0 + chunk)
+            self.set_rows(tokens[c0 - start:c1 - start], list(range(c0, c1)), [slot] * (c1 - c0),
+                          row_lo=[r0] * (c1 - c0))
+            self.ced_replay_slice(c0, c1, r0, head=c1 >= end)
+            if c1 >= end:
+                nxt = int(self.chosen[self.last_head_row].item())
+        return nxt
+
+    def ced_usable(self, start: int, n_new: int) -> bool:
+        """Can a prompt pass of `n_new` tokens from position `start` use the encoder / replay split?  A continuation
+        shorter than the replay span must continue the decoder windows instead of rebuilding them."""
+        cfg = self.cfg
+        return cfg.ced_on and n_new > 0 and (start == 0 or n_new >= cfg.ced_replay) \
+            and not any(l >= cfg.ced_boundary for l in self.engram)
+
+    def ced_replay_start(self, start: int, end: int) -> int:
+        return max(start, end - self.cfg.ced_replay)
+
+    def ced_encoder_slice(self, c0: int, c1: int, r0: int):
+        """Rows set by set_rows() are prompt positions [c0, c1): run the layers below the boundary, produce the boundary
+        layer's compressed source, and keep the boundary streams of the positions >= r0 for the replay."""
+        cfg = self.cfg
+        B, m = cfg.ced_boundary, c1 - c0
+        if getattr(self, "ced_streams", None) is None:
+            self.ced_streams = torch.zeros(cfg.ced_replay, cfg.hc_mult, cfg.hidden, dtype=BF16, device=self.device)
+            self.ced_pre = torch.zeros(cfg.ced_replay, cfg.hc_mult, dtype=F32, device=self.device)
+        self.forward_rows(m, head=False, last_layer=B)
+        pre_idx = self.boundary_source(m, B)
+        lo = max(c0, r0)
+        if lo < c1:
+            self.ced_streams[lo - r0:c1 - r0].copy_(self.streams[lo - c0:m])
+            self.ced_pre[lo - r0:c1 - r0].copy_(self.pre[pre_idx][lo - c0:m])
+
+    def ced_replay_slice(self, c0: int, c1: int, r0: int, head: bool):
+        """Rows set by set_rows() are prompt positions [c0, c1) of the replayed tail: continue them from the kept
+        boundary streams through the layers from the boundary upwards (compressed sources stay as they are)."""
+        m = c1 - c0
+        self._cur, self._ccur, self._pending, self._cand_ratio = 0, 0, None, None
+        self.streams[:m].copy_(self.ced_streams[c0 - r0:c1 - r0])
+        self.pre[0][:m].copy_(self.ced_pre[c0 - r0:c1 - r0])
+        self.forward_rows(m, embed=False, head=head, first_layer=self.cfg.ced_boundary, sources=False)
 
     def logits_rows(self, rows: int) -> torch.Tensor:
         """Full-vocabulary fp32 logits of the last pass (gathers vocabulary shards over the process group)."""

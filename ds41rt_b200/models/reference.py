@@ -370,6 +370,69 @@ class ReferenceModel:
             out.append(taps)
         return out[0] if len(out) == 1 else tuple(out)
 
+    def forward_ced(self, tokens: torch.Tensor, boundary: int, replay: int = 128) -> torch.Tensor:
+        """Prefill with the decoder layers replayed only for the prompt's tail (reference:
+        rust/crates/ds41rt-daemon/src/v41_backbone_cache/ced.rs:3-34, docs/ds41-ced-cache-transactions.md:8-20).
+        Layers [0, boundary) run over all tokens and layer `boundary` produces its compressed source from all of them;
+        layers [boundary, n_layers) then run only over the last `replay` tokens: their windows hold those tokens only,
+        the compressed sources are complete.  Returns the logits of the replayed rows [min(replay, T), vocab]."""
+        cfg = self.cfg
+        T = tokens.shape[0]
+        assert 0 < boundary < cfg.n_layers and all(s <= boundary for s in cfg.source_layers if s < cfg.n_layers)
+        positions = torch.arange(T)
+        streams = self._g("embed.weight")[tokens][:, None, :].repeat(1, cfg.hc_mult, 1)
+        pre = torch.zeros(T, cfg.hc_mult)
+        pre[:, 0] = 1.0
+        sources: Dict[int, tuple] = {}
+        selections: Dict[int, torch.Tensor] = {}
+        candidates: Optional[torch.Tensor] = None
+
+        def make_produce(l, pos, recompute):
+            p = f"layers.{l}"
+            src_layer = cfg.source_of(l)
+
+            def produce(xn):
+                nonlocal candidates
+                if src_layer is None:
+                    return None, None
+                if l in cfg.source_layers and recompute:
+                    comp, ik, first = self.compress_source(p, l, xn, pos)
+                    sources[l] = (comp, first, cfg.source_layers[l], ik)
+                comp, first, ratio, ik = sources[src_layer]
+                visible = torch.arange(comp.shape[0])[None, :] < ((pos + 1) // ratio)[:, None]
+                if l in cfg.index_layers:
+                    q_lat = rmsnorm(xn @ self._g(f"{p}.attn.wq_a.weight").t(), self._g(f"{p}.attn.q_norm.weight"),
+                                    cfg.norm_eps)
+                    sc = self.index_scores(p, l, q_lat, xn, pos, ik)
+                    vis = visible
+                    if cfg.candidate_layer >= 0 and cfg.candidate_topk_blocks > 0:
+                        if l == cfg.candidate_layer:
+                            candidates = self._candidate_blocks(sc, visible)
+                        elif l > cfg.candidate_layer and candidates is not None:
+                            vis = visible & candidates
+                    selections[l] = self.select_topk(sc, vis, cfg.index_topk)
+                return (comp, first, ratio), selections[cfg.index_producer_of(l)]
+            return produce
+
+        for l in range(boundary):
+            if self.engram_hook is not None:
+                streams = self.engram_hook(l, streams)
+            streams, pre = self.block(f"layers.{l}", l, streams, pre, positions, None, None, cfg.n_experts, cfg.topk,
+                                      None, produce=make_produce(l, positions, True))
+        pb = f"layers.{boundary}"
+        if boundary in cfg.source_layers:
+            xn = rmsnorm(hc_collapse(streams, pre), self._g(f"{pb}.attn_norm.weight"), cfg.norm_eps)
+            comp, ik, first = self.compress_source(pb, boundary, xn, positions)
+            sources[boundary] = (comp, first, cfg.source_layers[boundary], ik)
+        s0 = max(0, T - replay)
+        streams, pre, pos = streams[s0:], pre[s0:], positions[s0:]
+        candidates = None
+        for l in range(boundary, cfg.n_layers):
+            streams, pre = self.block(f"layers.{l}", l, streams, pre, pos, None, None, cfg.n_experts, cfg.topk,
+                                      None, produce=make_produce(l, pos, False))
+        x = rmsnorm(hc_collapse(streams, pre), self._g("norm.weight"), cfg.norm_eps)
+        return x @ self._g("head.weight").t()
+
     def _candidate_blocks(self, scores: torch.Tensor, visible: torch.Tensor) -> torch.Tensor:
         """Top candidate blocks of `candidate_block` rows by block-max score; the newest
         visible block is always kept (native/cuda/kernels/v41_candidate_blocks.cu:18-44)."""

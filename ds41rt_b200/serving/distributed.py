@@ -75,13 +75,21 @@ class LeaderEngine:
         if self.group is not None:
             _bcast(self.group, msg)
 
-    def set_rows(self, tokens: List[int], positions: List[int], slots: List[int]) -> None:
-        self._send(("set_rows", list(tokens), list(positions), list(slots)))
-        self.eng.set_rows(tokens, positions, slots)
+    def set_rows(self, tokens: List[int], positions: List[int], slots: List[int], row_lo=None) -> None:
+        self._send(("set_rows", list(tokens), list(positions), list(slots), None if row_lo is None else list(row_lo)))
+        self.eng.set_rows(tokens, positions, slots, row_lo=row_lo)
 
     def forward_rows(self, rows: int, **kw) -> None:
         self._send(("forward", rows, kw))
         self.eng.forward_rows(rows, **kw)
+
+    def ced_encoder_slice(self, c0: int, c1: int, r0: int) -> None:
+        self._send(("ced_enc", c0, c1, r0))
+        self.eng.ced_encoder_slice(c0, c1, r0)
+
+    def ced_replay_slice(self, c0: int, c1: int, r0: int, head: bool) -> None:
+        self._send(("ced_replay", c0, c1, r0, head))
+        self.eng.ced_replay_slice(c0, c1, r0, head)
 
     def set_engram_rows(self, layer: int, rows_q, text_mask=None) -> None:
         """The leader's gathered table rows travel with the pass: every rank applies the same Engram update to its
@@ -118,12 +126,18 @@ def follower_loop(engine, group, on_error=None) -> int:
             return passes
         try:
             if op == "set_rows":
-                engine.set_rows(msg[1], msg[2], msg[3])
+                engine.set_rows(msg[1], msg[2], msg[3], row_lo=msg[4])
             elif op == "forward":
                 engine.forward_rows(msg[1], **msg[2])
                 passes += 1
             elif op == "logits":
                 engine.logits_rows(msg[1])
+            elif op == "ced_enc":
+                engine.ced_encoder_slice(msg[1], msg[2], msg[3])
+                passes += 1
+            elif op == "ced_replay":
+                engine.ced_replay_slice(msg[1], msg[2], msg[3], msg[4])
+                passes += 1
             elif op == "engram":
                 engine.set_engram_rows(msg[1], msg[2], msg[3])
             elif op == "engram_clear":

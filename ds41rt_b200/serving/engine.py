@@ -129,8 +129,10 @@ class NativeBackend(Backend):
     fingerprint = "ds41rt-b200-fp8"
 
     def __init__(self, engine, eos: int, concurrency: int = 4, queue_depth: int = 16, prefill_chunk: Optional[int] = None,
-                 vision=None, drafter=None, engram=None):
+                 vision=None, drafter=None, engram=None, ced: bool = True):
         self.e, self.eos = engine, eos
+        # prompt passes use the encoder / decoder-replay split when the model has a boundary (config.ced_on)
+        self.ced = ced
         self.spec = None
         # runtime.engram.EngramPipeline or None.  Every pass hands its token ids to the pipeline first (hashes, page
         # advice, gather requests), runs, and commits the rows it kept.  Speculative rounds keep their draft tokens on
@@ -156,7 +158,8 @@ class NativeBackend(Backend):
         self.pending: Optional[GenRequest] = None
         self.totals = {"requests": 0, "prompt_tokens": 0, "completion_tokens": 0, "device_greedy_rows": 0,
                        "cpu_sampled_rows": 0, "gpu_sampled_rows": 0, "rounds": 0, "failed": 0,
-                       "prompt_cache_hit_tokens": 0, "snapshots": 0, "spec_rounds": 0, "spec_tokens": 0}
+                       "prompt_cache_hit_tokens": 0, "snapshots": 0, "spec_rounds": 0, "spec_tokens": 0,
+                       "ced_prefills": 0}
         self._rid = 0
         self._stop = threading.Event()
         self._ready = threading.Event()
@@ -357,7 +360,30 @@ class NativeBackend(Backend):
         if self.engram is not None:
             self.engram.reset(slot, toks[:start])
         image_at = set(img_pos) if img_pos is not None else set()
-        if start < len(toks):
+        taps_above = (self.spec is None or min(e.cfg.dspark.tap_layers) >= e.cfg.ced_boundary) \
+            and e.cfg.ced_replay >= e.cfg.window        # stored snapshots must hold complete decoder windows
+        if self.ced and start < len(toks) and not req.images and taps_above \
+                and e.ced_usable(start, len(toks) - start):
+            # encoder slices over the new tokens, then the decoder layers over the tail only
+            end, step = len(toks), self.prefill_chunk
+            r0 = e.ced_replay_start(start, end)
+            for c0 in range(start, end, step):
+                c1 = min(end, c0 + step)
+                e.set_rows(toks[c0:c1], list(range(c0, c1)), [slot] * (c1 - c0))
+                ep = self._engram_pass(toks[c0:c1], [slot] * (c1 - c0))
+                e.ced_encoder_slice(c0, c1, r0)
+                if ep is not None:
+                    self.engram.commit(ep)
+            for c0 in range(r0, end, step):
+                c1 = min(end, c0 + step)
+                e.set_rows(toks[c0:c1], list(range(c0, c1)), [slot] * (c1 - c0), row_lo=[r0] * (c1 - c0))
+                e.ced_replay_slice(c0, c1, r0, c1 >= end)
+                if feed_drafter:
+                    self.spec.d.feed(c1 - c0)
+            self.totals["ced_prefills"] += 1
+            logits = e.logits_rows(e.last_head_row + 1)[e.last_head_row].clone()
+            self._store_snapshot(slot, toks, logits)
+        elif start < len(toks):
             for c0 in range(start, len(toks), self.prefill_chunk):
                 part = toks[c0:c0 + self.prefill_chunk]
                 e.set_rows(part, list(range(c0, c0 + len(part))), [slot] * len(part))

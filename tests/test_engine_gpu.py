@@ -303,3 +303,59 @@ def test_candidate_blocks_restrict_later_index_layers():
     scale = float(want.abs().max())
     assert int(same.sum()) >= 0.5 * len(same), int(same.sum())
     assert float(err[same].max()) < 0.05 * scale, (float(err[same].max()), scale)
+
+
+@pytest.mark.parametrize("deep", [False, True])
+def test_ced_prefill_matches_full_prefill_and_oracle(deep):
+    """Prompt passes with the decoder layers replayed for the tail only.  (a) A prompt that fits the replay span takes
+    exactly the computations of the ordinary prefill: same logits bit for bit.  (b) A longer prompt follows the fp32
+    oracle of the same scheme (complete compressed sources, decoder windows from the tail only)."""
+    import dataclasses
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    from ds41rt_b200.models.reference import ReferenceModel
+    from ds41rt_b200.models.weights import init_weights
+    cfg = dataclasses.replace(ModelConfig.tiny(), ced_boundary=1, ced_replay=24)
+    if deep:      # two decoder layers above the boundary, all three layers read the source of layer 0
+        cfg = dataclasses.replace(cfg, name="tiny-ced3", n_layers=3, source_layers={0: 2}, compress_ratios=[2, 2, 2],
+                                  index_layers=(0, 1, 2), index_topk=16,
+                                  dspark=dataclasses.replace(cfg.dspark, tap_layers=(1, 2)))
+        cfg.validate()
+    assert cfg.ced_on
+    w = init_weights(cfg, seed=0)
+    wr = {k: (v.bfloat16().float() if v.dim() == 2 and not k.endswith("_fn") else v) for k, v in w.items()}
+    ref = ReferenceModel(cfg, wr)
+    dev = torch.device("cuda")
+    eng = DS41Engine(cfg, EngineWeights.from_fp32(cfg, wr, 0, 1, dev), max_rows=8, slots=2, max_ctx=512)
+    g = torch.Generator().manual_seed(5)
+    short = torch.randint(0, cfg.vocab, (21,), generator=g).tolist()
+    t_full = eng.prefill(0, short)
+    l_full = eng.logits_rows(eng.last_head_row + 1)[eng.last_head_row].clone()
+    t_ced = eng.prefill_ced(1, short)
+    l_ced = eng.logits_rows(eng.last_head_row + 1)[eng.last_head_row].clone()
+    eng.check_status("ced short")
+    assert t_full == t_ced and torch.equal(l_full, l_ced)
+    eng.cache.release(0)
+    eng.cache.release(1)
+    # (b) 100 tokens, replay 24: chunks of 8 cross the replay start (76) inside a chunk
+    prompt = torch.randint(0, cfg.vocab, (100,), generator=g)
+    with torch.no_grad():
+        want = ref.forward_ced(prompt, 1, replay=24)[-4:]
+        full = ref.forward(prompt)[-4:]
+    eng.prefill_ced(0, prompt.tolist())
+    got = eng.logits_rows(eng.last_head_row + 1).float().cpu()       # the last replay slice: positions 92..99
+    eng.check_status("ced long")
+    assert got.shape[0] == 8
+    got = got[-4:]
+    scale = float(want.abs().max())
+    # single rows can flip a near-tied expert or key selection under bf16: judge the typical row
+    err_ced = (got - want).abs().max(dim=1).values.median()
+    err_full = (got - full).abs().max(dim=1).values.median()
+    assert float((want - full).abs().max()) > 0.02 * scale          # the scheme differs from the full pass here
+    assert float(err_ced) < 0.1 * scale and float(err_ced) < 0.5 * float(err_full), (err_ced, err_full, scale)
+    # decoding continues from the replayed windows
+    nxt = int(eng.chosen[eng.last_head_row].item())
+    eng.set_rows([nxt], [100], [0])
+    eng.forward_rows(1)
+    torch.cuda.synchronize()
+    eng.check_status("ced decode")
