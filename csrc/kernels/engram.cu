@@ -44,9 +44,13 @@ engram_dequant_kernel(const uint8_t* __restrict__ rows_q, int row_bytes, int dim
 }
 
 __global__ void __launch_bounds__(256)
-engram_gate_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ kv,
+engram_gate_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ kv,
                    const __nv_bfloat16* __restrict__ q_w, const __nv_bfloat16* __restrict__ k_w,
-                   const uint8_t* __restrict__ text_mask, __nv_bfloat16* __restrict__ out, int H, float eps) {
+                   const uint8_t* __restrict__ text_mask, __nv_bfloat16* out, int H, float eps) {
+  // x and out are the same buffer in the engine (streams updated in place): they are not declared __restrict__, so
+  // that x is read with ordinary coherent loads.  A read-only-path load would leave lines in this SM's cache that the
+  // stores below do not refresh, and a dependent kernel that was launched early (its cache flush already done) could
+  // read those stale lines.
   __shared__ float part[3][8];
   __shared__ float gate_s[4];
   const int row = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;

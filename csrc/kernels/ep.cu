@@ -236,8 +236,8 @@ __global__ void ep_wait_kernel(EpParams p, int phase) {
 
 // out[t] = sum_k comb[t*topk + k] (+ extra[t]); routes whose id is out of range contributed nothing
 __global__ void __launch_bounds__(256)
-ep_combine_kernel(EpParams p, const __nv_bfloat16* __restrict__ comb, const float* __restrict__ extra,
-                  long long extra_ld, void* __restrict__ out, int as_bf16) {
+ep_combine_kernel(EpParams p, const __nv_bfloat16* __restrict__ comb, const float* extra,
+                  long long extra_ld, void* out, int as_bf16) {   // extra may be the output plane: coherent loads
   pdl_launch_dependents();
   pdl_wait();
   if (threadIdx.x < p.world && p.world > 1) flag_wait_ge(p.flags[threadIdx.x] + 3, *p.epoch, p.status, 730 + threadIdx.x);

@@ -53,7 +53,7 @@ __global__ void embed_streams_kernel(const int* __restrict__ tokens, const __nv_
 // grid (H / kHcSlice, ceil(rows / kHcRowsPerBlock)), 256 threads.
 // parts.n_ranks == 0: no expand, mixes are computed on `streams_in` as they are.
 __global__ void __launch_bounds__(256)
-hc_post_mix_kernel(const __nv_bfloat16* __restrict__ streams_in, __nv_bfloat16* __restrict__ streams_out,
+hc_post_mix_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out,   // same buffer in the engine: coherent loads
                    PartList parts, const float* __restrict__ post, const float* __restrict__ comb,
                    const float* __restrict__ fn, float* __restrict__ partial, int rows, int H,
                    const uint32_t* const* __restrict__ wait_flags, const uint32_t* __restrict__ wait_epoch, int* status) {

@@ -46,9 +46,10 @@ vis_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 __device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f)); }
 
 __global__ void __launch_bounds__(256)
-vis_bias_act_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ bias,
-                    const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out, long long n, int cols,
+vis_bias_act_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ bias,
+                    const __nv_bfloat16* residual, __nv_bfloat16* out, long long n, int cols,
                     int act) {
+  // x or residual may be the output buffer (in-place calls): no __restrict__, so they are read with coherent loads
   pdl_launch_dependents();
   pdl_wait();
   const long long i = (1ll * blockIdx.x * blockDim.x + threadIdx.x) * 2;
