@@ -201,7 +201,12 @@ __global__ void __launch_bounds__(256) compress_kernel(CompressParams p) {
   if (p.ratio == 2) {
     float* pend = p.pending + (1ll * slot * 4 + ((pos >> 1) & 3)) * 2 * p.D;
     if ((pos & 1) == 0) {
-      for (int c = tid; c < 2 * p.D; c += 256) pend[c] = cur[c];
+      // The carry has four places per request, indexed by (pos / 2) & 3, so that a rejected speculative row leaves
+      // the carry of the accepted ones intact.  In a pass longer than 8 positions two even rows 8 apart share a
+      // place: only the later one may write it (its block can run before or after the earlier row's block).
+      const bool later_writer = r + 8 < p.rows && p.row_slot[r + 8] == slot && p.row_pos[r + 8] == pos + 8;
+      if (!later_writer)
+        for (int c = tid; c < 2 * p.D; c += 256) pend[c] = cur[c];
       return;
     }
     const float* prev = pend;

@@ -475,6 +475,40 @@ class KVCache:
         return KVSnapshot(n_tokens, pages, partial, self.win[:, slot].clone(),
                           {src: t[slot].clone() for src, t in self.pending.items()})
 
+    def restore_prefix(self, slot: int, snap: KVSnapshot, n_tokens: int) -> bool:
+        """Give an empty `slot` the compressed / index rows of the snapshot's first `n_tokens` positions (an even
+        count below the snapshot's length): whole pages below the cut are shared, the page the cut falls into is copied
+        up to the cut.  Window rings and the pair carry are NOT restored: the caller replays the tokens from the cut on
+        with a window floor at the cut.  Returns False when no page is free for the copied page."""
+        assert not self.pages_of[slot], "restore needs an empty slot"
+        assert 0 < n_tokens <= snap.n_tokens and n_tokens % 2 == 0
+        full = n_tokens // self.page_tokens
+        rem = n_tokens - full * self.page_tokens
+        if rem and not self.free_pages:
+            return False
+        for i, pg in enumerate(snap.pages[:full]):
+            self.page_ref[pg] += 1
+            self.pages_of[slot].append(pg)
+            self.page_table_host[slot, i] = pg
+        if rem:
+            pg = self.free_pages.pop()
+            self.page_ref[pg] = 1
+            self.pages_of[slot].append(pg)
+            self.page_table_host[slot, full] = pg
+            for src, pr in self.page_rows.items():
+                rows = (rem * pr + self.page_tokens - 1) // self.page_tokens
+                if full < len(snap.pages):                  # the cut falls into one of the snapshot's whole pages
+                    sp = snap.pages[full]
+                    c, ix = self.comp[src][sp * pr: sp * pr + rows], self.idx[src][sp * pr: sp * pr + rows]
+                else:                                       # ... or into its partly filled last page
+                    c, ix = snap.partial[src][0][:rows], snap.partial[src][1][:rows]
+                self.comp[src][pg * pr: pg * pr + rows].copy_(c)
+                self.idx[src][pg * pr: pg * pr + rows].copy_(ix)
+        n = len(self.pages_of[slot])
+        if n:
+            self.page_table[slot, :n].copy_(self.page_table_host[slot, :n], non_blocking=True)
+        return True
+
     def restore(self, slot: int, snap: KVSnapshot) -> bool:
         """Continue a snapshot in an empty `slot`: shared full pages, a private copy of the partial page, rings and
         carry.  Returns False when no page is free for the partial page."""
@@ -1161,7 +1195,7 @@ class DS41Engine:
                 nxt = int(self.chosen[self.last_head_row].item())
         return nxt
 
-    def boundary_source(self, rows: int, layer: int):
+    def boundary_source(self, rows: int, layer: int, sources: bool = True):
         """Finish an encoder slice at `layer`: merge the pending sublayer into the streams, normalise layer `layer`'s
         input and run only its projection + compressor, so that its compressed source covers these rows.  Afterwards
         self.streams holds the complete streams entering `layer`; returns the index of the self.pre buffer that holds
@@ -1170,7 +1204,7 @@ class DS41Engine:
         pre_idx = self._cur
         self._hc(rows, getattr(self, "_pending", None), lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, lw.attn_norm)
         self._pending = None
-        if lw.ratio:
+        if lw.ratio and sources:
             self._qkv(layer, lw, rows, self._inv(layer), True)
         return pre_idx
 
@@ -1214,16 +1248,17 @@ class DS41Engine:
     def ced_replay_start(self, start: int, end: int) -> int:
         return max(start, end - self.cfg.ced_replay)
 
-    def ced_encoder_slice(self, c0: int, c1: int, r0: int):
+    def ced_encoder_slice(self, c0: int, c1: int, r0: int, sources: bool = True):
         """Rows set by set_rows() are prompt positions [c0, c1): run the layers below the boundary, produce the boundary
-        layer's compressed source, and keep the boundary streams of the positions >= r0 for the replay."""
+        layer's compressed source, and keep the boundary streams of the positions >= r0 for the replay.
+        sources=False: the compressed rows of these positions are already in the cache (restored pages)."""
         cfg = self.cfg
         B, m = cfg.ced_boundary, c1 - c0
         if getattr(self, "ced_streams", None) is None:
             self.ced_streams = torch.zeros(cfg.ced_replay, cfg.hc_mult, cfg.hidden, dtype=BF16, device=self.device)
             self.ced_pre = torch.zeros(cfg.ced_replay, cfg.hc_mult, dtype=F32, device=self.device)
-        self.forward_rows(m, head=False, last_layer=B)
-        pre_idx = self.boundary_source(m, B)
+        self.forward_rows(m, head=False, last_layer=B, sources=sources)
+        pre_idx = self.boundary_source(m, B, sources)
         lo = max(c0, r0)
         if lo < c1:
             self.ced_streams[lo - r0:c1 - r0].copy_(self.streams[lo - c0:m])

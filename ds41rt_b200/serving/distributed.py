@@ -51,6 +51,10 @@ class _CacheMirror:
         snap.sid = self._l._sid
         return snap
 
+    def restore_prefix(self, slot: int, snap, n_tokens: int) -> bool:
+        self._l._send(("restore_prefix", slot, snap.sid, n_tokens))
+        return self._l.eng.cache.restore_prefix(slot, snap, n_tokens)
+
     def restore(self, slot: int, snap) -> bool:
         self._l._send(("restore", slot, snap.sid))
         return self._l.eng.cache.restore(slot, snap)
@@ -83,9 +87,9 @@ class LeaderEngine:
         self._send(("forward", rows, kw))
         self.eng.forward_rows(rows, **kw)
 
-    def ced_encoder_slice(self, c0: int, c1: int, r0: int) -> None:
-        self._send(("ced_enc", c0, c1, r0))
-        self.eng.ced_encoder_slice(c0, c1, r0)
+    def ced_encoder_slice(self, c0: int, c1: int, r0: int, sources: bool = True) -> None:
+        self._send(("ced_enc", c0, c1, r0, sources))
+        self.eng.ced_encoder_slice(c0, c1, r0, sources)
 
     def ced_replay_slice(self, c0: int, c1: int, r0: int, head: bool) -> None:
         self._send(("ced_replay", c0, c1, r0, head))
@@ -133,7 +137,7 @@ def follower_loop(engine, group, on_error=None) -> int:
             elif op == "logits":
                 engine.logits_rows(msg[1])
             elif op == "ced_enc":
-                engine.ced_encoder_slice(msg[1], msg[2], msg[3])
+                engine.ced_encoder_slice(msg[1], msg[2], msg[3], msg[4])
                 passes += 1
             elif op == "ced_replay":
                 engine.ced_replay_slice(msg[1], msg[2], msg[3], msg[4])
@@ -150,6 +154,8 @@ def follower_loop(engine, group, on_error=None) -> int:
                 snaps[msg[3]] = engine.cache.snapshot(msg[1], msg[2])
             elif op == "restore":
                 engine.cache.restore(msg[1], snaps[msg[2]])
+            elif op == "restore_prefix":
+                engine.cache.restore_prefix(msg[1], snaps[msg[2]], msg[3])
             elif op == "drop":
                 engine.cache.drop_snapshot(snaps.pop(msg[2]))
         except Exception as e:          # keep the launch sequences aligned; the leader sees the status word / timeout

@@ -133,6 +133,7 @@ class NativeBackend(Backend):
         self.e, self.eos = engine, eos
         # prompt passes use the encoder / decoder-replay split when the model has a boundary (config.ced_on)
         self.ced = ced
+        self.partial_reuse = True     # snapshots that share only a leading part with a prompt contribute that part
         self.spec = None
         # runtime.engram.EngramPipeline or None.  Every pass hands its token ids to the pipeline first (hashes, page
         # advice, gather requests), runs, and commits the rows it kept.  Speculative rounds keep their draft tokens on
@@ -159,7 +160,7 @@ class NativeBackend(Backend):
         self.totals = {"requests": 0, "prompt_tokens": 0, "completion_tokens": 0, "device_greedy_rows": 0,
                        "cpu_sampled_rows": 0, "gpu_sampled_rows": 0, "rounds": 0, "failed": 0,
                        "prompt_cache_hit_tokens": 0, "snapshots": 0, "spec_rounds": 0, "spec_tokens": 0,
-                       "ced_prefills": 0}
+                       "ced_prefills": 0, "partial_prefix_hits": 0}
         self._rid = 0
         self._stop = threading.Event()
         self._ready = threading.Event()
@@ -285,7 +286,12 @@ class NativeBackend(Backend):
                 req.events.put(Event("error", status=503, message="KV pool cannot hold this request"))
                 continue
             self.prefix.lookup(req.prompt_ids)
-            reused, snap_logits = (0, None) if req.images else self._restore_prefix(slot, req.prompt_ids)
+            reused, snap_logits, replay_from = (0, None, None) if req.images \
+                else self._restore_prefix(slot, req.prompt_ids)
+            first_new = reused
+            if replay_from is not None:
+                # a truncated snapshot: its compressed rows reach up to the common prefix's even boundary
+                first_new = replay_from + self.e.cfg.window
             req.events.put(Event("ready", usage={"prompt_tokens": len(req.prompt_ids),
                                                  "prompt_cache_hit_tokens": reused}))
             self.totals["requests"] += 1
@@ -293,7 +299,8 @@ class NativeBackend(Backend):
             self.totals["prompt_cache_hit_tokens"] += reused
             solo = (self.spec is not None and not self.active and req.sampling.greedy and req.constraint is None
                     and not req.images and req.max_tokens > 1)
-            first = self._prefill(slot, req, start=reused, logits=snap_logits, feed_drafter=solo)
+            first = self._prefill(slot, req, start=first_new, logits=snap_logits, feed_drafter=solo,
+                                  replay_from=replay_from)
             a = _Active(req, slot, gen, pos=len(req.prompt_ids), last=first, spec=solo)
             if solo:
                 self.spec.prime(slot, first, len(req.prompt_ids))
@@ -304,24 +311,48 @@ class NativeBackend(Backend):
 
     # ------------------------------------------------------------------ prefix reuse (exact snapshot boundaries)
     def _restore_prefix(self, slot: int, prompt: List[int]):
-        """Longest stored snapshot whose tokens are a prefix of `prompt` -> (tokens reused, logits after them or None).
-        A snapshot can only be continued from its own end, so the hit is all of its tokens or nothing."""
-        best = None
+        """Best stored snapshot for `prompt` -> (tokens reused, logits after them or None, replay start or None).
+
+        A snapshot whose tokens are a prefix of the prompt is continued from its own end (all of its tokens count).  A
+        snapshot that only shares `common` leading tokens with the prompt contributes its compressed rows up to
+        skipped = common / 2 * 2 - window: the windows are rebuilt by running the tokens from `skipped` again (third
+        value), so only `skipped` tokens count as reused.  The higher count wins (reference:
+        rust/crates/ds41rt-core/src/prefix.rs:23-30, rust/crates/ds41rt-daemon/src/v41_native_serve/prefix.rs:258-294)."""
+        window = self.e.cfg.window
+        best, best_score, best_exact = None, 0, False
         for i, (toks, snap, logits) in enumerate(self.snapshots):
             n = len(toks)
-            if n == len(prompt) and logits is None:
-                continue                                   # nothing to continue from without the last logits
-            if n <= len(prompt) and (best is None or n > len(self.snapshots[best][0])) and tuple(prompt[:n]) == toks:
-                best = i
+            common = 0
+            for a, b in zip(toks, prompt):
+                if a != b:
+                    break
+                common += 1
+            if common == n and n <= len(prompt):
+                if n == len(prompt) and logits is None:
+                    continue                               # nothing to continue from without the last logits
+                score, exact = n, True
+            else:
+                score, exact = common // 2 * 2 - window, False
+                if not self.partial_reuse or score <= 0 or common >= len(prompt):
+                    continue
+            if score > best_score:
+                best, best_score, best_exact = i, score, exact
         if best is None:
-            return 0, None
+            return 0, None, None
         toks, snap, logits = self.snapshots[best]
         self.e.cache.release(slot)                     # the slot was given fresh pages by the admission path
-        if not self.e.cache.restore(slot, snap):
+        if best_exact:
+            if not self.e.cache.restore(slot, snap):
+                self.e.cache.ensure(slot, len(prompt) + 1)
+                return 0, None, None
+            self.snapshots.append(self.snapshots.pop(best))   # most recently used last
+            return len(toks), (logits if len(toks) == len(prompt) else None), None
+        if not self.e.cache.restore_prefix(slot, snap, best_score):
             self.e.cache.ensure(slot, len(prompt) + 1)
-            return 0, None
-        self.snapshots.append(self.snapshots.pop(best))   # most recently used last
-        return len(toks), (logits if len(toks) == len(prompt) else None)
+            return 0, None, None
+        self.snapshots.append(self.snapshots.pop(best))
+        self.totals["partial_prefix_hits"] += 1
+        return best_score, None, best_score
 
     def _store_snapshot(self, slot: int, tokens: List[int], logits):
         key = tuple(tokens)
@@ -345,7 +376,11 @@ class NativeBackend(Backend):
             positions += list(pos)
         return torch.cat(rows, 0).contiguous(), positions
 
-    def _prefill(self, slot: int, req: GenRequest, start: int = 0, logits=None, feed_drafter: bool = False) -> int:
+    def _prefill(self, slot: int, req: GenRequest, start: int = 0, logits=None, feed_drafter: bool = False,
+                 replay_from: Optional[int] = None) -> int:
+        """Run the prompt from position `start` on.  With `replay_from` (< start, after a truncated snapshot restore)
+        the positions [replay_from, start) are run again to rebuild the windows: their compressed rows are already in
+        the cache, and every pass of this prompt carries a window floor at `replay_from`."""
         import torch
         e = self.e
         toks = req.prompt_ids
@@ -357,21 +392,24 @@ class NativeBackend(Backend):
         slack = 2 * self.spec.width + 2 if self.spec is not None else 1
         if not e.cache.ensure(slot, len(toks) + req.max_tokens + slack):
             raise MemoryError("KV pool cannot hold this request")
+        first = start if replay_from is None else replay_from
         if self.engram is not None:
-            self.engram.reset(slot, toks[:start])
+            self.engram.reset(slot, toks[:first])
         image_at = set(img_pos) if img_pos is not None else set()
+        end, step = len(toks), self.prefill_chunk
+        # passes never straddle `start`: below it the compressed sources are kept, from it on they are produced
+        cuts = [(c0, min(hi, c0 + step), hi == end) for lo, hi in ((first, start), (start, end))
+                for c0 in range(lo, hi, step)]
+        floor = (lambda m: [replay_from] * m) if replay_from is not None else (lambda m: None)
         taps_above = (self.spec is None or min(e.cfg.dspark.tap_layers) >= e.cfg.ced_boundary) \
             and e.cfg.ced_replay >= e.cfg.window        # stored snapshots must hold complete decoder windows
-        if self.ced and start < len(toks) and not req.images and taps_above \
-                and e.ced_usable(start, len(toks) - start):
+        if self.ced and first < end and not req.images and taps_above and e.ced_usable(first, end - first):
             # encoder slices over the new tokens, then the decoder layers over the tail only
-            end, step = len(toks), self.prefill_chunk
-            r0 = e.ced_replay_start(start, end)
-            for c0 in range(start, end, step):
-                c1 = min(end, c0 + step)
-                e.set_rows(toks[c0:c1], list(range(c0, c1)), [slot] * (c1 - c0))
+            r0 = e.ced_replay_start(first, end)
+            for c0, c1, fresh in cuts:
+                e.set_rows(toks[c0:c1], list(range(c0, c1)), [slot] * (c1 - c0), row_lo=floor(c1 - c0))
                 ep = self._engram_pass(toks[c0:c1], [slot] * (c1 - c0))
-                e.ced_encoder_slice(c0, c1, r0)
+                e.ced_encoder_slice(c0, c1, r0, fresh)
                 if ep is not None:
                     self.engram.commit(ep)
             for c0 in range(r0, end, step):
@@ -383,17 +421,17 @@ class NativeBackend(Backend):
             self.totals["ced_prefills"] += 1
             logits = e.logits_rows(e.last_head_row + 1)[e.last_head_row].clone()
             self._store_snapshot(slot, toks, logits)
-        elif start < len(toks):
-            for c0 in range(start, len(toks), self.prefill_chunk):
-                part = toks[c0:c0 + self.prefill_chunk]
-                e.set_rows(part, list(range(c0, c0 + len(part))), [slot] * len(part))
+        elif first < end:
+            for c0, c1, fresh in cuts:
+                part = toks[c0:c1]
+                e.set_rows(part, list(range(c0, c1)), [slot] * len(part), row_lo=floor(len(part)))
                 ep = self._engram_pass(part, [slot] * len(part), [c0 + i in image_at for i in range(len(part))])
-                last = c0 + self.prefill_chunk >= len(toks)
+                last = c1 >= end
                 if img_rows is not None:
-                    ids = [p - c0 if c0 <= p < c0 + len(part) else -1 for p in img_pos]
+                    ids = [p - c0 if c0 <= p < c1 else -1 for p in img_pos]
                     if any(i >= 0 for i in ids):
                         e.image_patch = (img_rows, torch.tensor(ids, dtype=torch.int32, device=img_rows.device))
-                e.forward_rows(len(part), head=last)
+                e.forward_rows(len(part), head=last, sources=fresh)
                 e.image_patch = None
                 if ep is not None:
                     self.engram.commit(ep)

@@ -359,3 +359,28 @@ def test_ced_prefill_matches_full_prefill_and_oracle(deep):
     eng.forward_rows(1)
     torch.cuda.synchronize()
     eng.check_status("ced decode")
+
+
+def test_long_chunks_leave_the_same_state_as_short_ones():
+    """A 43-token prompt run in passes of 16 rows (two even rows of one pass share a pair-carry place) and in passes of
+    8 rows: the ratio-2 pair carry and the following decode steps are bit-identical."""
+    cfg, ref, eng = _setup(max_rows=16)
+    prompt = torch.randint(3, cfg.vocab - 8, (43,), generator=torch.Generator().manual_seed(21)).tolist()
+    outs = []
+    for slot, chunk in ((0, 16), (1, 8)):
+        tok = eng.prefill(slot, prompt, chunk=chunk)
+        carry = {k: v[slot].clone() for k, v in eng.cache.pending.items()}
+        steps = []
+        assert eng.cache.ensure(slot, len(prompt) + 8)
+        for i in range(4):
+            eng.set_rows([tok], [len(prompt) + i], [slot])
+            eng.forward_rows(1)
+            steps.append(eng.logits[:1].clone())
+            tok = int(eng.chosen[0].item())
+        outs.append((carry, steps))
+    eng.check_status()
+    place = (42 >> 1) & 3
+    for k in outs[0][0]:
+        assert torch.equal(outs[0][0][k][place], outs[1][0][k][place]), k
+    for a, b in zip(outs[0][1], outs[1][1]):
+        assert torch.equal(a, b)
