@@ -51,7 +51,61 @@ __device__ __forceinline__ float uniform01(unsigned long long seed, unsigned lon
   return static_cast<float>(static_cast<uint32_t>(x >> 40)) * (1.0f / 16777216.0f);
 }
 
+// Walk the row with several independent 16-byte loads in flight per thread (one CTA owns a whole row, so the walk is
+// bound by load latency).  Every thread still sees its tokens in ascending order, and every lane of a warp calls
+// f(i, value, valid) together, so f may use warp collectives.
+template <class F>
+__device__ __forceinline__ void for_vocab4(const float* lg, int vocab, F f) {
+  const int lane = threadIdx.x & 31, wbase = threadIdx.x - lane, B = blockDim.x;
+  constexpr int U = 4;
+  if ((reinterpret_cast<uintptr_t>(lg) & 15) == 0) {
+    const int n4 = vocab >> 2;
+    const float4* lg4 = reinterpret_cast<const float4*>(lg);
+    for (int base = wbase; base < n4; base += U * B) {
+      float4 v[U];
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+        const int q = base + j * B + lane;
+        v[j] = q < n4 ? lg4[q] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+        if (base + j * B >= n4) break;
+        const int q = base + j * B + lane;
+        const bool ok = q < n4;
+        f(4 * q, v[j].x, ok);
+        f(4 * q + 1, v[j].y, ok);
+        f(4 * q + 2, v[j].z, ok);
+        f(4 * q + 3, v[j].w, ok);
+      }
+    }
+    if (wbase == 0 && 4 * n4 < vocab) {          // up to three trailing tokens, warp 0
+      const int i = 4 * n4 + lane;
+      f(i, i < vocab ? lg[i] : 0.f, i < vocab);
+    }
+    return;
+  }
+  for (int base = wbase; base < vocab; base += U * B) {
+    float v[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      const int i = base + j * B + lane;
+      v[j] = i < vocab ? lg[i] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      const int i = base + j * B + lane;
+      if (base + j * B < vocab) f(i, v[j], i < vocab);
+    }
+  }
+}
+
+constexpr int kSampleListCap = 2048;   // survivors of a top-k cut are kept in shared memory up to this many
+
 struct SampleShared {
+  float list_val[kSampleListCap];       // raw logits of the tokens above the top-k cut key (any order)
+  int list_id[kSampleListCap];
+  int list_n;
   unsigned int cnt[256];
   unsigned long long mass[256];
   unsigned long long scan[kSampleThreads];
@@ -62,6 +116,30 @@ struct SampleShared {
   float fmax;
   int imax;
 };
+
+// What a selection walks: the whole row, or (n_list >= 0) the compact list of the tokens above the top-k cut key.
+struct RowView {
+  const float* lg;
+  int vocab;
+  const uint32_t* mask;
+  const float* list_val;
+  const int* list_id;
+  int n_list;
+};
+
+template <class F>
+__device__ __forceinline__ void for_view(const RowView& v, F f) {
+  if (v.n_list < 0) {
+    for_vocab4(v.lg, v.vocab, [&](int i, float x, bool valid) { f(i, x, valid && mask_allows(v.mask, i)); });
+    return;
+  }
+  const int lane = threadIdx.x & 31, wbase = threadIdx.x - lane;
+  for (int base = wbase; base < v.n_list; base += blockDim.x) {
+    const int j = base + lane;
+    const bool valid = j < v.n_list;
+    f(valid ? v.list_id[j] : 0, valid ? v.list_val[j] : 0.f, valid);
+  }
+}
 
 // The candidate set of a selection: allowed tokens with key > excl, plus `tie_mult` tokens of key `tie_key`
 // (the admitted part of a tie group cut by an earlier selection; tie_key <= excl whenever tie_mult > 0).
@@ -74,8 +152,8 @@ struct CandSet {
 // Radix selection, high keys first.  by_mass: find the key at which the running weight reaches `target`; else the key
 // at which the running count reaches it.  On return sh.remaining is what the ties at the returned key must still
 // supply and sh.tie_count how many candidates carry that key.
-__device__ uint32_t radix_select(SampleShared& sh, const float* lg, int vocab, const uint32_t* mask, float inv_t,
-                                 float max_scaled, CandSet set, bool by_mass, double target) {
+__device__ uint32_t radix_select(SampleShared& sh, const RowView& view, float inv_t, float max_scaled, CandSet set,
+                                 bool by_mass, double target) {
   uint32_t prefix = 0, prefix_mask = 0;
   if (threadIdx.x == 0) sh.remaining = target;
   for (int shift = 24; shift >= 0; shift -= 8) {
@@ -84,15 +162,31 @@ __device__ uint32_t radix_select(SampleShared& sh, const float* lg, int vocab, c
       sh.mass[d] = 0;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-      if (!mask_allows(mask, i)) continue;
-      const float s = __fmul_rn(lg[i], inv_t);
+    // lanes of a warp that hit the same digit add once: logits of one row share their top key bytes, so unaggregated
+    // shared-memory atomics would serialise on a handful of counters.  Integer sums: the result does not depend on
+    // the grouping.
+    for_view(view, [&](int i, float v, bool valid) {
+      const float s = __fmul_rn(v, inv_t);
       const uint32_t k = order_key(s);
-      if (k <= set.excl || (k & prefix_mask) != prefix) continue;
+      const bool act = valid && k > set.excl && (k & prefix_mask) == prefix;
       const uint32_t d = (k >> shift) & 255u;
-      atomicAdd(&sh.cnt[d], 1u);
-      if (by_mass) atomicAdd(&sh.mass[d], weight_fx(s, max_scaled));
-    }
+      const unsigned peers = __match_any_sync(0xffffffffu, act ? d : 256u);
+      if (act) {
+        const int leader = __ffs(peers) - 1;
+        const int lane = threadIdx.x & 31;
+        unsigned long long wsum = 0;
+        if (by_mass) {
+          const unsigned long long w = weight_fx(s, max_scaled);           // <= 2^40: two 20/21-bit halves
+          const unsigned lo = __reduce_add_sync(peers, static_cast<unsigned>(w & 0xFFFFFu));
+          const unsigned hi = __reduce_add_sync(peers, static_cast<unsigned>(w >> 20));
+          wsum = (static_cast<unsigned long long>(hi) << 20) + lo;
+        }
+        if (lane == leader) {
+          atomicAdd(&sh.cnt[d], static_cast<unsigned>(__popc(peers)));
+          if (by_mass) atomicAdd(&sh.mass[d], wsum);
+        }
+      }
+    });
     if (threadIdx.x == 0 && set.tie_mult > 0 && (set.tie_key & prefix_mask) == prefix) {
       const uint32_t d = (set.tie_key >> shift) & 255u;
       atomicAdd(&sh.cnt[d], static_cast<unsigned int>(set.tie_mult));
@@ -171,19 +265,19 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, co
   // ---- prepare: finiteness, allowed count, maximum (greedy: arg max with the lowest id on ties)
   float best = -INFINITY;
   int best_i = -1, n_allowed = 0, bad = 0;
-  for (int i = tid; i < vocab; i += blockDim.x) {
-    const float v = lg[i];
+  for_vocab4(lg, vocab, [&](int i, float v, bool valid) {
+    if (!valid) return;
     const bool ok = mask_allows(mask, i);
     if (greedy) {
       if (!isfinite(v)) bad = 1;
     } else if (ok && (isnan(v) || v == INFINITY)) {
       bad = 1;
     }
-    if (!ok) continue;
+    if (!ok) return;
     ++n_allowed;
     const float s = __fmul_rn(v, inv_t);
     if (best_i < 0 || s > best) { best = s; best_i = i; }      // ascending i per thread: first maximum kept
-  }
+  });
   for (int off = 16; off > 0; off >>= 1) {
     const float ob = __shfl_xor_sync(0xffffffffu, best, off);
     const int oi = __shfl_xor_sync(0xffffffffu, best_i, off);
@@ -266,37 +360,64 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, co
 
   // ---- ranked path
   CandSet set{excl0, 0u, 0ull};
+  RowView view{lg, vocab, mask, sh.list_val, sh.list_id, -1};
   // survivor count
   int mine_n = 0;
-  for (int i = tid; i < vocab; i += blockDim.x)
-    if (mask_allows(mask, i) && order_key(__fmul_rn(lg[i], inv_t)) > excl0) ++mine_n;
+  for_view(view, [&](int i, float v, bool valid) {
+    if (valid && order_key(__fmul_rn(v, inv_t)) > excl0) ++mine_n;
+  });
   block_scan(sh, static_cast<unsigned long long>(mine_n));
   const unsigned long long survivors = sh.total;
   __syncthreads();
   if (survivors == 0) return finish(kSampleEmpty, 0);
+  uint32_t list_key = 0xFFFFFFFFu;      // keys above this one live in the compact list (when view.n_list >= 0)
   if (p.top_k > 0 && static_cast<unsigned long long>(p.top_k) < survivors) {
-    const uint32_t pk = radix_select(sh, lg, vocab, mask, inv_t, max_scaled, set, false, static_cast<double>(p.top_k));
+    const uint32_t pk = radix_select(sh, view, inv_t, max_scaled, set, false, static_cast<double>(p.top_k));
     const double need = sh.remaining;
     const unsigned long long ties = sh.tie_count;
     __syncthreads();
     set.excl = pk;
     set.tie_key = pk;
     set.tie_mult = static_cast<unsigned long long>(fmin(fmax(need, 1.0), static_cast<double>(ties)));
+    if (p.top_k <= kSampleListCap) {
+      // fewer than top_k tokens lie above the cut key: gather them once; every later selection walks this list
+      // instead of the row (the admitted ties of the cut key stay described by set.tie_key / set.tie_mult)
+      if (tid == 0) sh.list_n = 0;
+      __syncthreads();
+      for_view(view, [&](int i, float v, bool valid) {
+        const bool keep = valid && order_key(__fmul_rn(v, inv_t)) > pk;
+        const unsigned m = __ballot_sync(0xffffffffu, keep);
+        if (m == 0) return;
+        const int lane = threadIdx.x & 31;
+        int at = 0;
+        if (lane == __ffs(m) - 1) at = atomicAdd(&sh.list_n, __popc(m));
+        at = __shfl_sync(0xffffffffu, at, __ffs(m) - 1) + __popc(m & ((1u << lane) - 1u));
+        if (keep && at < kSampleListCap) {
+          sh.list_val[at] = v;
+          sh.list_id[at] = i;
+        }
+      });
+      __syncthreads();
+      if (sh.list_n <= kSampleListCap) {
+        view.n_list = sh.list_n;
+        list_key = pk;
+      }
+    }
   }
   // total weight of the kept set
   unsigned long long mine_w = 0;
-  for (int i = tid; i < vocab; i += blockDim.x) {
-    if (!mask_allows(mask, i)) continue;
-    const float s = __fmul_rn(lg[i], inv_t);
+  for_view(view, [&](int i, float v, bool valid) {
+    if (!valid) return;
+    const float s = __fmul_rn(v, inv_t);
     if (order_key(s) > set.excl) mine_w += weight_fx(s, max_scaled);
-  }
+  });
   block_scan(sh, mine_w);
   unsigned long long total = sh.total + set.tie_mult * (set.tie_mult ? weight_fx(key_value(set.tie_key), max_scaled) : 0ull);
   __syncthreads();
   double mass = static_cast<double>(total);
   if (p.top_p < 1.0f) {
     const double target = static_cast<double>(p.top_p) * mass;
-    const uint32_t pp = radix_select(sh, lg, vocab, mask, inv_t, max_scaled, set, true, target);
+    const uint32_t pp = radix_select(sh, view, inv_t, max_scaled, set, true, target);
     const double need = sh.remaining;
     const unsigned long long ties = sh.tie_count;
     __syncthreads();
@@ -311,7 +432,7 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, co
   }
   // ---- the draw
   const double target = static_cast<double>(u) * mass;
-  const uint32_t dk = radix_select(sh, lg, vocab, mask, inv_t, max_scaled, set, true, target);
+  const uint32_t dk = radix_select(sh, view, inv_t, max_scaled, set, true, target);
   const double need = sh.remaining;
   const unsigned long long ties = sh.tie_count;
   __syncthreads();
@@ -320,6 +441,20 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, co
   if (tie_index < 0) tie_index = 0;
   if (tie_index > static_cast<long long>(ties) - 1) tie_index = static_cast<long long>(ties) - 1;
   // the tie_index-th allowed token with key == dk in id order
+  if (view.n_list >= 0 && dk > list_key) {
+    // all tokens of that key are in the list: the one with exactly tie_index smaller ids among them
+    if (tid == 0) sh.token = -1;
+    __syncthreads();
+    for (int j = tid; j < view.n_list; j += blockDim.x) {
+      if (order_key(__fmul_rn(sh.list_val[j], inv_t)) != dk) continue;
+      long long rank = 0;
+      for (int q = 0; q < view.n_list; ++q)
+        if (sh.list_id[q] < sh.list_id[j] && order_key(__fmul_rn(sh.list_val[q], inv_t)) == dk) ++rank;
+      if (rank == tie_index) sh.token = sh.list_id[j];
+    }
+    __syncthreads();
+    return finish(sh.token >= 0 ? kSampleOk : kSampleInternal, sh.token);
+  }
   const int seg = (vocab + kSampleThreads - 1) / kSampleThreads;
   const int i0 = min(vocab, tid * seg), i1 = min(vocab, i0 + seg);
   unsigned long long eq = 0;
