@@ -298,6 +298,14 @@ int ds41_attend_floor(const void* q, long long ldq, int q_off, int rows, int hea
                       void* stream);
 
 // ---------------------------------------------------------------------------------------------------
+// Pipeline-stage handoff over peer memory (pp.cu).  Counters are 32-bit words in symmetric memory; every wait is bounded
+// and reports {flag timeout, site} in the status word.
+int ds41_pp_signal(void* flag, unsigned value, void* stream);
+int ds41_pp_wait(const void* flag, unsigned value, int* status, int site, void* stream);
+int ds41_pp_pull(const void* src, void* dst, long long nbytes, const void* flag, unsigned value, int* status, int site,
+                 void* stream);
+
+// ---------------------------------------------------------------------------------------------------
 // Engram memory (engram.cu): table rows (dim e4m3 values + dim/32 UE8M0 scales, row_bytes apart) -> bf16 [n_rows, dim];
 // gated residual update of the 4 streams from kv = [rows][4 keys + 1 value][H] (bf16); text_mask 0 = pass through.
 int ds41_engram_dequant(const void* rows_q, int row_bytes, int dim, void* out, int n_rows, void* stream);

@@ -161,8 +161,8 @@ class EngineWeights:
     @staticmethod
     def from_fp32(cfg: ModelConfig, w: Dict[str, torch.Tensor], rank: int, world: int, device,
                   prefix: str = "layers", n_layers: Optional[int] = None, n_experts: Optional[int] = None,
-                  topk: Optional[int] = None, expert_dtype: str = "bf16", share: Optional["EngineWeights"] = None
-                  ) -> "EngineWeights":
+                  topk: Optional[int] = None, expert_dtype: str = "bf16", share: Optional["EngineWeights"] = None,
+                  layer_range: Optional[tuple] = None) -> "EngineWeights":
         """Build one rank's shard from an fp32 name->tensor dict.  expert_dtype "mxfp8" stores routed
         experts as E4M3 with power-of-two 128x128 block scales (consumed by the block-scaled GEMM)."""
         ew = EngineWeights(cfg, rank, world, device)
@@ -184,6 +184,9 @@ class EngineWeights:
         h0, h1 = rank * ew.HL, (rank + 1) * ew.HL
         g0, g1 = rank * ew.GL, (rank + 1) * ew.GL
         for l in range(n_layers):
+            if layer_range is not None and not (layer_range[0] <= l < layer_range[1]):
+                ew.layers.append(None)        # a pipeline stage holds only its own layers
+                continue
             p = f"{prefix}.{l}"
             lw = LayerWeights(n_experts=E, topk=k)
             for kind in ("attn", "ffn"):
@@ -248,7 +251,7 @@ class EngineWeights:
     @staticmethod
     def random(cfg: ModelConfig, rank: int, world: int, device, seed: int = 0, std: float = 0.02,
                router_std: Optional[float] = None, expert_dtype: str = "bf16",
-               share: Optional["EngineWeights"] = None) -> "EngineWeights":
+               share: Optional["EngineWeights"] = None, layer_range: Optional[tuple] = None) -> "EngineWeights":
         """Random-init shard generated directly on the device (for models too large to stage on the host).
         expert_dtype "mxfp8": E4M3 payloads ~ N(0, 48^2) with every 128x128 block scale 2^-11 (dequantised
         std 0.0234), the statistics an amax-scaled quantisation of N(0, 0.02) weights produces."""
@@ -277,6 +280,9 @@ class EngineWeights:
         EL = cfg.n_experts // world
         nproj = 2 * cfg.hc_mult + cfg.hc_mult ** 2
         for l in range(cfg.n_layers):
+            if layer_range is not None and not (layer_range[0] <= l < layer_range[1]):
+                ew.layers.append(None)        # a pipeline stage holds only its own layers
+                continue
             lw = LayerWeights(n_experts=cfg.n_experts, topk=cfg.topk)
             for kind in ("attn", "ffn"):
                 setattr(lw, f"hc_{kind}_fn", rnd((nproj, cfg.hc_mult * H), shared_gen, std, F32))
@@ -365,6 +371,8 @@ class EngineWeights:
         for t in [self.embed, self.head, self.final_norm]:
             total += t.numel() * t.element_size()
         for lw in self.layers:
+            if lw is None:
+                continue
             for v in vars(lw).values():
                 if isinstance(v, torch.Tensor):
                     total += v.numel() * v.element_size()
@@ -562,8 +570,10 @@ class DS41Engine:
         self.cache = KVCache(cfg, self.n_layers, slots, max_ctx, dev, page_tokens, n_pages, spec_slack=max(16, R),
                              kv_dtype=kv_dtype)
         self.HL, self.GL, self.I_sh, self.V_local = weights.HL, weights.GL, weights.I_sh, weights.V_local
-        E = weights.layers[0].n_experts if weights.layers else cfg.n_experts
-        self.E, self.topk = E, (weights.layers[0].topk if weights.layers else cfg.topk)
+        live = [lw for lw in weights.layers if lw is not None]      # a pipeline stage holds a slice of the stack
+        self._lw_any = live[0] if live else None
+        E = live[0].n_experts if live else cfg.n_experts
+        self.E, self.topk = E, (live[0].topk if live else cfg.topk)
         self.EL = E // self.world
         # passes of at most moe_rows rows run every active expert over all rows (decode); longer passes sort the rows
         # by expert and go through the expert-parallel tile-table path (prefill)
@@ -591,11 +601,11 @@ class DS41Engine:
         self.fused_rows = 16      # passes of at most this many rows use the fused hyper-connection step
         self.taps = z((len(cfg.dspark.tap_layers), R, H), F32) if cfg.dspark is not None else None
         # attention
-        max_extra = max([lw.extra_cols for lw in weights.layers] + [0])
+        max_extra = max([lw.extra_cols for lw in live] + [0])
         self.ntot_qkv = Q + D + max_extra
         self.max_splits = 16
         # layers differ in their extra columns; fewer columns can mean more splits, so size for every distinct width
-        widths = sorted({lw.w_qkv.shape[0] for lw in weights.layers} | {self.ntot_qkv})
+        widths = sorted({lw.w_qkv.shape[0] for lw in live} | {self.ntot_qkv})
         self.planes_qkv = z((max(self._plane_rows(n) * n for n in widths),), F32)
         self.q_lat = z((R, Q), BF16)
         self.extras = z((R, max(max_extra, 1)), F32)
@@ -703,8 +713,8 @@ class DS41Engine:
         self._engram_live: set = set()
         self._engram_copied: Dict[int, object] = {}      # layer -> event after the last upload of its host rows
         self._engram_layer_of: Dict[int, int] = {}
-        if R > self.moe_rows and weights.layers:
-            self._make_ep(weights.layers[0])
+        if R > self.moe_rows and live:
+            self._make_ep(live[0])
         self.debug = None   # set to a list to record per-layer routing / selection decisions
 
     # ------------------------------------------------------------------ helpers
@@ -752,16 +762,17 @@ class DS41Engine:
     def set_rows(self, tokens, positions, slots, row_hi=None, row_lo=None):
         """Host -> device copy of one pass's inputs (lists or CPU tensors).  `row_lo` (one position per row) puts a
         floor under the attention windows of the pass: positions below it are not attended."""
-        n = len(tokens)
+        n = len(positions)
         self._floor_on = row_lo is not None
         if row_lo is not None:
             self.row_lo.copy_(torch.tensor(list(row_lo) + [0] * (self.max_rows - n), dtype=I32), non_blocking=True)
         assert n <= self.max_rows
         pad = self.max_rows - n
-        t = torch.tensor(list(tokens) + [0] * pad, dtype=I32)
         p = torch.tensor(list(positions) + [0] * pad, dtype=I32)
         s = torch.tensor(list(slots) + [-1] * pad, dtype=I32)
-        self.in_tokens.copy_(t, non_blocking=True)
+        if tokens is not None:        # None: the token ids are already on the device (fed by a kernel)
+            assert len(tokens) == n
+            self.in_tokens.copy_(torch.tensor(list(tokens) + [0] * pad, dtype=I32), non_blocking=True)
         self.row_pos.copy_(p, non_blocking=True)
         self.row_slot.copy_(s, non_blocking=True)
         # what the host knows about the pass it just described (used by the next forward_rows only): a long pass over
@@ -910,7 +921,7 @@ class DS41Engine:
                 self.cache.row_bytes, st())
 
     def forward_rows(self, rows: int, *, embed: bool = True, head: bool = True, first_layer: int = 0,
-                     last_layer: Optional[int] = None, sources: bool = True):
+                     last_layer: Optional[int] = None, sources: bool = True, pending=None):
         """One pass over `rows` rows described by set_rows().  `first_layer` / `last_layer` run a slice of the stack
         (the streams and the pending sublayer carry over between slices); `sources=False` leaves the compressed
         sources untouched (decoder replay of a prompt's tail)."""
@@ -930,7 +941,8 @@ class DS41Engine:
                 img_rows, img_ids = self.image_patch
                 self._run("image_rows", k.ds41_vis_scatter, lib.ptr(img_rows), lib.ptr(img_ids), lib.ptr(self.streams),
                           img_rows.shape[0], H, cfg.hc_mult, st())
-        pending = None
+        # `pending`: an unmerged sublayer handed in by the caller (bases, ranks, splits, stride), e.g. a pipeline stage
+        # that continues another stage's stack
         fused = R <= self.fused_rows
         if self.layer_timer is not None:
             self.layer_timer.begin()
@@ -1132,7 +1144,7 @@ class DS41Engine:
     def head_rows(self, rows: int, mask: Optional[torch.Tensor] = None):
         """collapse -> final norm -> vocabulary shard GEMM -> greedy candidate (+ cross-rank merge)."""
         cfg, k, st = self.cfg, self.k, lib.stream
-        lw0 = self.w.layers[0]
+        lw0 = self._lw_any
         self._hc(rows, getattr(self, "_pending", None), lw0.hc_attn_fn, lw0.hc_attn_scale, lw0.hc_attn_base,
                  self.w.final_norm)
         self._pending = None
@@ -1155,7 +1167,7 @@ class DS41Engine:
     def head_logits(self, rows: int):
         """collapse -> final norm -> vocabulary shard GEMM; leaves fp32 logits in self.logits (no selection)."""
         cfg = self.cfg
-        lw0 = self.w.layers[0]
+        lw0 = self._lw_any
         self._hc(rows, getattr(self, "_pending", None), lw0.hc_attn_fn, lw0.hc_attn_scale, lw0.hc_attn_base,
                  self.w.final_norm)
         self._pending = None
