@@ -363,6 +363,19 @@ __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, co
                : "r"(smem_u32(smem_row)));
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3,
+                                            const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(smem_u32(smem_row)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3,
+                                                  const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(smem_u32(smem_row)));
+}
+
 struct AttendParams {
   const __nv_bfloat16* q;      // [rows][ldq]; local head h at column q_off + h*D
   long long ldq;
@@ -805,19 +818,19 @@ __global__ void __launch_bounds__(512) attend_wide_kernel(AttendParams p) {
     }
     // ---- S = Q K^T: this warp's 16 heads x 8 keys
     {
+      // fragments come from ldmatrix: one x4 per 16 x 16 block of Q and one x4 per two k-steps of the 8 key rows
+      // (three shared-memory instructions per two MMAs instead of twelve 32-bit loads)
       float c[4] = {0.f, 0.f, 0.f, 0.f};
-      const __nv_bfloat16* qa = sQ + (hg * 16 + g) * LD + 2 * t4;
-      const __nv_bfloat16* kb = kt + (part * 8 + g) * LD + 2 * t4;
-#pragma unroll 8
-      for (int kk = 0; kk < D; kk += 16) {
-        uint32_t a[4];
-        a[0] = *reinterpret_cast<const uint32_t*>(qa + kk);
-        a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + kk);
-        a[2] = *reinterpret_cast<const uint32_t*>(qa + kk + 8);
-        a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + kk + 8);
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb + kk);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kb + kk + 8);
-        mma_bf16_16816(c, a, b0, b1);
+      const __nv_bfloat16* qa = sQ + (hg * 16 + (lane & 15)) * LD + (lane >> 4) * 8;
+      const __nv_bfloat16* kb = kt + (part * 8 + (lane & 7)) * LD + (lane >> 3) * 8;
+#pragma unroll 4
+      for (int kk = 0; kk < D; kk += 32) {
+        uint32_t a[4], a2[4], b[4];
+        ldmatrix_x4(a[0], a[1], a[2], a[3], qa + kk);
+        ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], qa + kk + 16);
+        ldmatrix_x4(b[0], b[1], b[2], b[3], kb + kk);
+        mma_bf16_16816(c, a, b[0], b[1]);
+        mma_bf16_16816(c, a2, b[2], b[3]);
       }
       const int key = part * 8 + 2 * t4;
       float* s0 = sS + (hg * 16 + g) * 33 + key;
@@ -865,12 +878,13 @@ __global__ void __launch_bounds__(512) attend_wide_kernel(AttendParams p) {
         a[1] = *reinterpret_cast<const uint32_t*>(pa + 8 * 40);
         a[2] = *reinterpret_cast<const uint32_t*>(pa + 8);
         a[3] = *reinterpret_cast<const uint32_t*>(pa + 8 * 40 + 8);
-        const __nv_bfloat16* vrow = kt + (kk + (lane & 15)) * LD + d_base;
+        const __nv_bfloat16* vrow = kt + (kk + (lane & 15)) * LD + d_base + (lane >> 4) * 8;
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          uint32_t b0, b1;
-          ldmatrix_x2_trans(b0, b1, vrow + nt * 8);
+        for (int nt = 0; nt < NT; nt += 2) {
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4_trans(b0, b1, b2, b3, vrow + nt * 8);      // two 8-column tiles of V per instruction
           mma_bf16_16816(acc[nt], a, b0, b1);
+          mma_bf16_16816(acc[nt + 1], a, b2, b3);
         }
       }
     }
