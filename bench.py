@@ -292,7 +292,7 @@ def main():
                     help="prefill: time whole-prompt passes in --chunk-row chunks (tok/s of prompt tokens)")
     ap.add_argument("--chunk", type=int, default=1024, help="rows per pass in --mode prefill")
     ap.add_argument("--concurrency", type=int, default=1, help="decode: number of concurrent requests (greedy, no drafter)")
-    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8"], help="latent KV rows in the cache")
+    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8", "fp4"], help="latent KV rows in the cache")
     ap.add_argument("--ced", action="store_true",
                     help="prefill: the decoder layers run over the last 128 prompt tokens only (the reference's prompt "
                          "scheme); default is every layer over every token")

@@ -297,6 +297,15 @@ int ds41_attend_floor(const void* q, long long ldq, int q_off, int rows, int hea
                       float* part_ml, const float* sink, void* out, long long ldo, int kv_row_bytes, const int* row_lo,
                       void* stream);
 
+// ds41_attend_floor with FP4 compressed rows: comp_row_bytes > 0 says that comp_pool holds FP4 rows (D/2 e2m1 bytes, then
+// D/16 E4M3 scales, padded to comp_row_bytes) while the window rows are FP8 rows of kv_row_bytes; 0 = one format.
+int ds41_attend_kv(const void* q, long long ldq, int q_off, int rows, int heads, int D, int window, int ring,
+                   const int* row_pos, const int* row_slot, const void* win, const void* comp_pool, const int* sel,
+                   const int* n_sel, int k, const int* page_table, int max_pages, int page_rows, const float* inv_freq,
+                   int rope_dim, float scale, int n_splits, const int* row_hi, float* part_o, float* part_ml,
+                   const float* sink, void* out, long long ldo, int kv_row_bytes, int comp_row_bytes, const int* row_lo,
+                   void* stream);
+
 // ---------------------------------------------------------------------------------------------------
 // Pipeline-stage handoff over peer memory (pp.cu).  Counters are 32-bit words in symmetric memory; every wait is bounded
 // and reports {flag timeout, site} in the status word.

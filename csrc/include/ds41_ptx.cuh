@@ -106,6 +106,28 @@ __device__ __forceinline__ bool flag_wait_ge(const uint32_t* flag, uint32_t targ
     }
   }
 }
+// E2M1 (FP4) code of a value: magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6, round to nearest with ties to the even mantissa.
+__device__ __forceinline__ uint32_t e2m1_code(float v) {
+  const float a = fabsf(v);
+  uint32_t c;
+  // midpoints between representable magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6; ties go to the even mantissa
+  if (a <= 0.25f) c = 0;
+  else if (a < 0.75f) c = 1;
+  else if (a <= 1.25f) c = 2;
+  else if (a < 1.75f) c = 3;
+  else if (a <= 2.5f) c = 4;
+  else if (a < 3.5f) c = 5;
+  else if (a <= 5.0f) c = 6;
+  else c = 7;
+  return c | (v < 0.f ? 8u : 0u);
+}
+
+__device__ __forceinline__ float e2m1_value(uint32_t code) {
+  const uint32_t m = code & 7u;
+  const float a = m < 2u ? 0.5f * m : (m & 1u ? 1.5f : 1.0f) * static_cast<float>(1u << ((m >> 1) - 1u));
+  return (code & 8u) ? -a : a;
+}
+
 __device__ __forceinline__ void flag_store_release(uint32_t* flag, uint32_t value) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(value) : "memory");
 }

@@ -32,6 +32,24 @@ __device__ __forceinline__ void store_kv_fp8_pair(uint8_t* row, int D, int i, fl
 }
 
 
+// Compressed-cache row in FP4: D/2 bytes of e2m1 pairs (even element in the low nibble), then D/16 E4M3 scales, one per
+// 16 values: scale = e4m3(max(amax, 6 * 2^-9) / 6), code = e2m1(value / scale).  Thread i owns elements 2i, 2i+1; the
+// eight threads of a 16-value group share the scale.  All lanes of a warp call it (shuffles); `active` gates the stores.
+// Format parity: native/cuda/kernels/v41_kv.cu:29-39 of the reference.
+__device__ __forceinline__ void store_kv_fp4_pair(uint8_t* row, int D, int i, float a, float b, bool active) {
+  float amax = fmaxf(fabsf(a), fabsf(b));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+  if (!active) return;
+  amax = fmaxf(amax, 6.0f * 0.001953125f);
+  const __nv_fp8_e4m3 sc(__fdiv_rn(amax, 6.0f));
+  const float scf = static_cast<float>(sc);
+  const uint32_t ca = e2m1_code(__fdiv_rn(a, scf)), cb = e2m1_code(__fdiv_rn(b, scf));
+  row[i] = static_cast<uint8_t>(ca | (cb << 4));
+  if ((i & 7) == 0) row[D / 2 + (i >> 3)] = *reinterpret_cast<const uint8_t*>(&sc);
+}
+
 __device__ __forceinline__ void rope_cs(int pos, float inv_freq, float* c, float* s) {
   // reduce the angle in double so positions up to 2^20 keep fp32-accurate sin/cos
   const double a = static_cast<double>(pos) * static_cast<double>(inv_freq);
@@ -180,7 +198,7 @@ struct CompressParams {
   const float* inv_freq_idx; // [ID/4]
   const int* page_table;     // [slots][max_pages]
   int max_pages, page_rows;
-  __nv_bfloat16* comp_pool;  // [pool_rows][D] bf16, or FP8 rows of kv_row_bytes bytes
+  __nv_bfloat16* comp_pool;  // [pool_rows][D] bf16, FP8 rows of kv_row_bytes bytes, or FP4 rows of -kv_row_bytes bytes
   int kv_row_bytes;
   __nv_bfloat16* idx_pool;   // [pool_rows][ID]
   float eps;
@@ -279,7 +297,10 @@ __global__ void __launch_bounds__(256) compress_kernel(CompressParams p) {
       }
     }
     const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    if (p.kv_row_bytes > 0)
+    if (p.kv_row_bytes < 0)        // FP4 rows of -kv_row_bytes bytes
+      store_kv_fp4_pair(reinterpret_cast<uint8_t*>(p.comp_pool) + phys * (-p.kv_row_bytes), p.D, i, __low2float(h),
+                        __high2float(h), active);
+    else if (p.kv_row_bytes > 0)
       store_kv_fp8_pair(reinterpret_cast<uint8_t*>(p.comp_pool) + phys * p.kv_row_bytes, p.D, i, __low2float(h),
                         __high2float(h), active);
     else if (active)
@@ -311,7 +332,10 @@ extern "C" int ds41_compress(const float* extras, int extra_stride, int rows, in
                              const void* wk, const float* k_norm_w, const float* inv_freq, const float* inv_freq_idx,
                              const int* page_table, int max_pages, int page_rows, void* comp_pool, void* idx_pool,
                              float eps, int kv_row_bytes, void* stream) {
-  if (kv_row_bytes != 0 && (kv_row_bytes < D + D / 32 || (D & 31) || (kv_row_bytes & 15))) return cudaErrorInvalidValue;
+  // kv_row_bytes: 0 bf16 rows, > 0 FP8 rows (D + D/32 bytes, padded), < 0 FP4 rows of -kv_row_bytes (D/2 + D/16 bytes)
+  if (kv_row_bytes > 0 && (kv_row_bytes < D + D / 32 || (D & 31) || (kv_row_bytes & 15))) return cudaErrorInvalidValue;
+  if (kv_row_bytes < 0 && (-kv_row_bytes < D / 2 + D / 16 || (D & 15) || ((-kv_row_bytes) & 15)))
+    return cudaErrorInvalidValue;
   if (rows <= 0 || D > 1024 || ID > 256 || (ratio != 1 && ratio != 2) || (D & 1) || (ID & 3))
     return cudaErrorInvalidValue;
   CompressParams p{extras, extra_stride, rows, D, ID, rope_dim, ratio, row_pos, row_slot, pending, comp_norm_w,

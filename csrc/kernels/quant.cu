@@ -125,21 +125,6 @@ act_quant_mx_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uin
 // block_scale = e4m3(amax / 6 / global_scale); codes round to nearest (ties to even) on the e2m1 grid.
 // One warp per row, 8 elements per lane per step (two lanes share a 16-element block).  Scales go straight into the
 // 512-byte atoms of the tensor-core kind: atom [row/128][k/64], byte (row%32)*16 + ((row/32)%4)*4 + (k/16)%4.
-__device__ __forceinline__ uint32_t e2m1_code(float v) {
-  const float a = fabsf(v);
-  uint32_t c;
-  // midpoints between representable magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6; ties go to the even mantissa
-  if (a <= 0.25f) c = 0;
-  else if (a < 0.75f) c = 1;
-  else if (a <= 1.25f) c = 2;
-  else if (a < 1.75f) c = 3;
-  else if (a <= 2.5f) c = 4;
-  else if (a < 3.5f) c = 5;
-  else if (a <= 5.0f) c = 6;
-  else c = 7;
-  return c | (v < 0.f ? 8u : 0u);
-}
-
 __global__ void __launch_bounds__(256)
 act_quant_nvfp4_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q, long long ldq,
                             uint8_t* __restrict__ sf, int rows, int K, float global_scale,

@@ -399,7 +399,22 @@ struct AttendParams {
   float* part_ml;              // [rows][n_splits][heads][2]
   int kv_row_bytes;            // 0: win / comp_pool rows are bf16 [D]; else FP8 rows (D e4m3 + D/32 UE8M0, padded)
   const int* row_lo;           // optional [rows]: lowest visible window position (a window rebuilt from there on)
+  int comp_row_bytes;          // > 0: comp_pool rows are FP4 (D/2 e2m1 bytes + D/16 E4M3 scales) of this many bytes;
+                               // the window rows must then be FP8 rows (kv_row_bytes > 0)
 };
+
+// Eight values of an FP4 cache row -> bf16 (exact: a 2-bit-mantissa value times a 4-bit-mantissa scale).
+__device__ __forceinline__ uint4 expand_fp4_chunk(const uint8_t* row8, int D, int ch) {
+  const uint32_t packed = *reinterpret_cast<const uint32_t*>(row8 + ch * 4);
+  const __half_raw hs = __nv_cvt_fp8_to_halfraw(row8[D / 2 + (ch >> 1)], __NV_E4M3);
+  const float sc = __half2float(__half(hs));
+  uint4 out;
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    o2[q] = __floats2bfloat162_rn(e2m1_value((packed >> (8 * q)) & 15u) * sc, e2m1_value((packed >> (8 * q + 4)) & 15u) * sc);
+  return out;
+}
 
 constexpr int kKeysPerCta = 64;
 constexpr int kHeadsPerCta = 16;
@@ -509,7 +524,8 @@ __global__ void __launch_bounds__(128) attend_kernel(AttendParams p) {
           const int id = p.sel[1ll * r * p.k + (j - n_w)];
           const long long phys = id < 0 ? -1 : pool_row(p.page_table, p.max_pages, p.page_rows, slot, id);
           if (phys >= 0)
-            ptr = reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const uint8_t*>(p.comp_pool) + phys * row_bytes);
+            ptr = reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const uint8_t*>(p.comp_pool) +
+                                                         phys * (p.comp_row_bytes > 0 ? p.comp_row_bytes : row_bytes));
         }
       }
       sPtr[tid] = ptr;
@@ -530,12 +546,13 @@ __global__ void __launch_bounds__(128) attend_kernel(AttendParams p) {
     } else {
       // FP8 rows: copy payload + scales as they are, then expand to bf16 (exact: e4m3 value times a power of two)
       const int chunks = p.kv_row_bytes / 16;
+      const int comp_chunks = p.comp_row_bytes > 0 ? p.comp_row_bytes / 16 : chunks;
       for (int idx = tid; idx < kKeysPerCta * chunks; idx += 128) {
         const int key = idx / chunks, ch = idx - key * chunks;
         const uint8_t* src = reinterpret_cast<const uint8_t*>(sPtr[key]);
         uint8_t* dst = sK8 + key * p.kv_row_bytes + ch * 16;
-        if (src != nullptr) cp_async_16(dst, src + ch * 16);
-        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        if (src == nullptr) *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        else if (ch < (k0 + key >= n_w ? comp_chunks : chunks)) cp_async_16(dst, src + ch * 16);   // FP4 rows are shorter
       }
       cp_async_wait_all();
       __syncthreads();
@@ -543,6 +560,10 @@ __global__ void __launch_bounds__(128) attend_kernel(AttendParams p) {
       for (int idx = tid; idx < kKeysPerCta * (D / 8); idx += 128) {
         const int key = idx / (D / 8), ch = idx % (D / 8);
         const uint8_t* row8 = sK8 + key * p.kv_row_bytes;
+        if (p.comp_row_bytes > 0 && k0 + key >= n_w) {
+          *reinterpret_cast<uint4*>(sK + key * LD + ch * 8) = expand_fp4_chunk(row8, D, ch);
+          continue;
+        }
         const uint2 raw = *reinterpret_cast<const uint2*>(row8 + ch * 8);
         const float sc = __uint_as_float(static_cast<uint32_t>(row8[D + (ch >> 2)]) << 23);
         const __nv_fp8x2_storage_t* q2 = reinterpret_cast<const __nv_fp8x2_storage_t*>(&raw);
@@ -728,7 +749,8 @@ __global__ void __launch_bounds__(512) attend_wide_kernel(AttendParams p) {
           const int id = p.sel[1ll * r * p.k + (j - n_w)];
           const long long phys = id < 0 ? -1 : pool_row(p.page_table, p.max_pages, p.page_rows, slot, id);
           if (phys >= 0)
-            ptr = reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const uint8_t*>(p.comp_pool) + phys * row_bytes);
+            ptr = reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const uint8_t*>(p.comp_pool) +
+                                                         phys * (p.comp_row_bytes > 0 ? p.comp_row_bytes : row_bytes));
         }
       }
       sPtr[b * kWideKeys + tid] = ptr;
@@ -744,12 +766,13 @@ __global__ void __launch_bounds__(512) attend_wide_kernel(AttendParams p) {
       }
     } else {
       const int chunks = p.kv_row_bytes / 16;
+      const int comp_chunks = p.comp_row_bytes > 0 ? p.comp_row_bytes / 16 : chunks;
       for (int idx = tid; idx < kWideKeys * chunks; idx += 512) {
         const int key = idx / chunks, ch = idx - key * chunks;
         const uint8_t* src = reinterpret_cast<const uint8_t*>(sPtr[b * kWideKeys + key]);
         uint8_t* dst = sK8 + (b * kWideKeys + key) * p.kv_row_bytes + ch * 16;
-        if (src != nullptr) cp_async_16(dst, src + ch * 16);
-        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        if (src == nullptr) *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        else if (ch < (k0 + key >= n_w ? comp_chunks : chunks)) cp_async_16(dst, src + ch * 16);   // FP4 rows are shorter
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -802,6 +825,10 @@ __global__ void __launch_bounds__(512) attend_wide_kernel(AttendParams p) {
       for (int idx = tid; idx < kWideKeys * (D / 8); idx += 512) {
         const int key = idx / (D / 8), ch = idx % (D / 8);
         const uint8_t* row8 = sK8 + (buf * kWideKeys + key) * p.kv_row_bytes;
+        if (p.comp_row_bytes > 0 && k0 + key >= n_w) {
+          *reinterpret_cast<uint4*>(kt + key * LD + ch * 8) = expand_fp4_chunk(row8, D, ch);
+          continue;
+        }
         const uint2 raw = *reinterpret_cast<const uint2*>(row8 + ch * 8);
         const float sc = __uint_as_float(static_cast<uint32_t>(row8[D + (ch >> 2)]) << 23);
         const __nv_fp8x2_storage_t* q2 = reinterpret_cast<const __nv_fp8x2_storage_t*>(&raw);
@@ -1091,12 +1118,27 @@ extern "C" int ds41_attend_floor(const void* q, long long ldq, int q_off, int ro
                                  int max_pages, int page_rows, const float* inv_freq, int rope_dim, float scale,
                                  int n_splits, const int* row_hi, float* part_o, float* part_ml, const float* sink,
                                  void* out, long long ldo, int kv_row_bytes, const int* row_lo, void* stream) {
+  return ds41_attend_kv(q, ldq, q_off, rows, heads, D, window, ring, row_pos, row_slot, win, comp_pool, sel, n_sel, k,
+                        page_table, max_pages, page_rows, inv_freq, rope_dim, scale, n_splits, row_hi, part_o, part_ml,
+                        sink, out, ldo, kv_row_bytes, 0, row_lo, stream);
+}
+
+extern "C" int ds41_attend_kv(const void* q, long long ldq, int q_off, int rows, int heads, int D, int window,
+                              int ring, const int* row_pos, const int* row_slot, const void* win,
+                              const void* comp_pool, const int* sel, const int* n_sel, int k, const int* page_table,
+                              int max_pages, int page_rows, const float* inv_freq, int rope_dim, float scale,
+                              int n_splits, const int* row_hi, float* part_o, float* part_ml, const float* sink,
+                              void* out, long long ldo, int kv_row_bytes, int comp_row_bytes, const int* row_lo,
+                              void* stream) {
+  if (comp_row_bytes != 0 && (kv_row_bytes <= 0 || comp_row_bytes < D / 2 + D / 16 || (comp_row_bytes & 15) ||
+                              comp_row_bytes > kv_row_bytes))
+    return cudaErrorInvalidValue;
   if (rows <= 0 || heads <= 0 || rope_dim > 128 || (rope_dim & 7) || n_splits <= 0 || n_splits > 32)
     return cudaErrorInvalidValue;
   AttendParams p{static_cast<const __nv_bfloat16*>(q), ldq, q_off, rows, heads, window, ring, row_pos, row_slot,
                  static_cast<const __nv_bfloat16*>(win), static_cast<const __nv_bfloat16*>(comp_pool), sel, n_sel, k,
                  page_table, max_pages, page_rows, inv_freq, rope_dim, scale, n_splits, row_hi, part_o, part_ml,
-                 kv_row_bytes, row_lo};
+                 kv_row_bytes, row_lo, comp_row_bytes};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   if (D == 512) e = launch_attend<512>(p, s);

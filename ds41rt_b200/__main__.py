@@ -168,7 +168,7 @@ def main(argv=None) -> int:
     ps.add_argument("--waiters", type=int, default=16)
     ps.add_argument("--max-context", type=int, default=8192)
     ps.add_argument("--seed", type=int, default=0)
-    ps.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8"])
+    ps.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8", "fp4"])
     ps.add_argument("--engram-table", action="append", default=[],
                     help="flat Engram table file (loader.official.export_engram_table), once per Engram layer in layer "
                          "order; enables the Engram memory layers")

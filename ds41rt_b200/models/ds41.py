@@ -408,10 +408,13 @@ class KVCache:
     def __init__(self, cfg: ModelConfig, n_layers: int, slots: int, max_ctx: int, device, page_tokens: int = 64,
                  n_pages: Optional[int] = None, spec_slack: int = 16, kv_dtype: str = "bf16"):
         self.cfg, self.slots, self.max_ctx, self.page_tokens = cfg, slots, max_ctx, page_tokens
-        assert kv_dtype in ("bf16", "fp8")
+        assert kv_dtype in ("bf16", "fp8", "fp4")
         self.kv_dtype = kv_dtype
         # FP8 rows: D e4m3 values + D/32 UE8M0 scales (per 32 elements), padded to 16 bytes; 0 = bf16 rows
         self.row_bytes = 0 if kv_dtype == "bf16" else (cfg.head_dim + cfg.head_dim // 32 + 15) // 16 * 16
+        # "fp4": the window rings stay FP8, the compressed rows are FP4 (D/2 e2m1 bytes + D/16 E4M3 scales, the
+        # reference's 288-byte rows for D = 512); 0 = compressed rows in the window's format
+        self.comp_row_bytes = (cfg.head_dim // 2 + cfg.head_dim // 16 + 15) // 16 * 16 if kv_dtype == "fp4" else 0
         D = cfg.head_dim
         ring = cfg.window + spec_slack
         self.ring = ring
@@ -428,7 +431,8 @@ class KVCache:
                 continue
             pr = page_tokens // ratio
             self.page_rows[src] = pr
-            self.comp[src] = torch.zeros(self.n_pages * pr, *kv_shape, dtype=kv_dt, device=device)
+            comp_shape = (self.comp_row_bytes,) if self.comp_row_bytes else kv_shape
+            self.comp[src] = torch.zeros(self.n_pages * pr, *comp_shape, dtype=kv_dt, device=device)
             self.idx[src] = torch.zeros(self.n_pages * pr, cfg.index_dim, dtype=BF16, device=device)
             if ratio == 2:
                 self.pending[src] = torch.zeros(slots, 4, 2 * D, dtype=F32, device=device)
@@ -918,7 +922,7 @@ class DS41Engine:
                 lib.ptr(lw.comp_norm), lib.ptr(lw.wk_idx), lib.ptr(lw.k_norm), lib.ptr(inv), lib.ptr(self.inv_idx),
                 lib.ptr(self.cache.page_table), self.cache.max_pages, self.cache.page_rows[l],
                 lib.ptr(self.cache.comp[l]), lib.ptr(self.cache.idx[l]), C.c_float(cfg.norm_eps),
-                self.cache.row_bytes, st())
+                -self.cache.comp_row_bytes if self.cache.comp_row_bytes else self.cache.row_bytes, st())
 
     def forward_rows(self, rows: int, *, embed: bool = True, head: bool = True, first_layer: int = 0,
                      last_layer: Optional[int] = None, sources: bool = True, pending=None):
@@ -997,7 +1001,7 @@ class DS41Engine:
                 self._run("topk", k.ds41_topk_select_cand, lib.ptr(self.scores), self.max_keys, lib.ptr(self.row_pos),
                                             lib.ptr(self.row_slot), ratio, cfg.index_topk, lib.ptr(self.sel),
                                             lib.ptr(self.n_sel), R, *cand, st())
-            self._run("attend", k.ds41_attend_floor, 
+            self._run("attend", k.ds41_attend_kv, 
                 lib.ptr(self.qb_out), C.c_longlong(self.nqb), 0, R, self.HL, D, cfg.window, self.cache.ring,
                 lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.cache.win[l]),
                 lib.ptr(self.cache.comp[src]) if src is not None else lib.ptr(None),
@@ -1005,7 +1009,7 @@ class DS41Engine:
                 self.cache.max_pages, self.cache.page_rows[src] if src is not None else 1, lib.ptr(inv), cfg.rope_dim,
                 C.c_float(cfg.softmax_scale), self._attn_splits(R), lib.ptr(self.row_hi), lib.ptr(self.part_o),
                 lib.ptr(self.part_ml), lib.ptr(lw.sink), lib.ptr(self.attn_out), C.c_longlong(self.HL * D),
-                self.cache.row_bytes, lib.ptr(self.row_lo if self._floor_on else None), st())
+                self.cache.row_bytes, self.cache.comp_row_bytes, lib.ptr(self.row_lo if self._floor_on else None), st())
             # grouped wo_a: batch = local groups
             kg = cfg.heads_per_group * D
             self._run("gemm_wo_a", G.gemm_raw, lw.wo_a, self.attn_out, self.oa, cfg.o_lora, R, kg, lda=kg, ldb=self.HL * D,

@@ -384,3 +384,44 @@ def test_long_chunks_leave_the_same_state_as_short_ones():
         assert torch.equal(outs[0][0][k][place], outs[1][0][k][place]), k
     for a, b in zip(outs[0][1], outs[1][1]):
         assert torch.equal(a, b)
+
+
+def test_fp4_compressed_rows_and_logits():
+    """kv_dtype "fp4": window rings FP8, compressed rows FP4 (e2m1 + E4M3 scale per 16).  The compressed rows of the
+    first source layer are the exact FP4 image of the bf16 engine's rows (same inputs there), and the logits move only
+    by quantisation noise."""
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    from ds41rt_b200.ops import quant_ref as Q
+    cfg = ModelConfig.tiny()
+    dev = torch.device("cuda")
+    ew = EngineWeights.random(cfg, 0, 1, dev, seed=3)
+    engines = {kv: DS41Engine(cfg, ew, max_rows=16, slots=1, max_ctx=256, kv_dtype=kv) for kv in ("bf16", "fp4")}
+    toks = torch.randint(3, cfg.vocab, (48,), generator=torch.Generator().manual_seed(11)).tolist()
+    logits = {}
+    for kv, eng in engines.items():
+        eng.cache.ensure(0, 128)
+        for c0 in range(0, len(toks), 16):
+            part = toks[c0:c0 + 16]
+            eng.set_rows(part, list(range(c0, c0 + len(part))), [0] * len(part))
+            eng.forward_rows(len(part))
+        logits[kv] = eng.logits_rows(16).float().cpu()
+        eng.check_status()
+    D = cfg.head_dim
+    assert D // 2 + D // 16 <= engines["fp4"].cache.comp_row_bytes < engines["fp4"].cache.row_bytes
+    src = 0                                                    # layer 0: identical inputs in both engines
+    assert src in engines["bf16"].cache.comp
+    n = len(toks) // cfg.source_layers[src]
+    pr = engines["bf16"].cache.page_rows[src]
+    rows = [engines["bf16"].cache.pages_of[0][i // pr] * pr + i % pr for i in range(n)]
+    ref = engines["bf16"].cache.comp[src][rows].float().cpu()
+    rows4 = [engines["fp4"].cache.pages_of[0][i // pr] * pr + i % pr for i in range(n)]
+    got = engines["fp4"].cache.comp[src][rows4].cpu()
+    packed, bs = Q.quant_kv_fp4_e4m3_16(ref)
+    assert torch.equal(got[:, :D // 2], packed.view(torch.uint8).reshape(n, D // 2))
+    assert torch.equal(got[:, D // 2:D // 2 + D // 16], bs.view(torch.uint8).reshape(n, D // 16))
+    a, b = logits["bf16"], logits["fp4"]
+    scale = float(a.abs().max())
+    drift = (a - b).abs().max(dim=1).values
+    assert float(drift.median()) < 0.15 * scale, (float(drift.median()), scale)
+    assert float((a.argmax(-1) == b.argmax(-1)).float().mean()) >= 0.5

@@ -53,7 +53,18 @@ def _pack_fp8_rows(x, row_bytes):
     return rows.contiguous(), Q.dequant_mxfp8(q, e, 32).bfloat16()
 
 
-@pytest.mark.parametrize("kv", ["bf16", "fp8"])
+def _pack_fp4_rows(x, row_bytes):
+    """bf16 rows -> (FP4 cache rows [.., row_bytes] uint8, the dequantised values the kernel must see)."""
+    from ds41rt_b200.ops import quant_ref as Q
+    D = x.shape[-1]
+    packed, bs = Q.quant_kv_fp4_e4m3_16(x.float())
+    rows = torch.zeros(*x.shape[:-1], row_bytes, dtype=torch.uint8, device=x.device)
+    rows[..., :D // 2] = packed.view(torch.uint8).reshape(*x.shape[:-1], D // 2)
+    rows[..., D // 2:D // 2 + D // 16] = bs.view(torch.uint8).reshape(*x.shape[:-1], D // 16)
+    return rows.contiguous(), Q.dequant_kv_fp4_e4m3_16(packed, bs).reshape(x.shape).bfloat16()
+
+
+@pytest.mark.parametrize("kv", ["bf16", "fp8", "fp4"])
 @pytest.mark.parametrize("D,heads,rope,rows,n_splits", [(128, 8, 32, 3, 0), (512, 16, 64, 3, 0), (512, 64, 64, 3, 0),
                                                          (512, 64, 64, 70, 1), (512, 64, 64, 66, 3), (128, 64, 32, 64, 2)])
 def test_sparse_attention(D, heads, rope, rows, n_splits, kv):
@@ -68,11 +79,16 @@ def test_sparse_attention(D, heads, rope, rows, n_splits, kv):
     slots = ([0, 0, 1] + [i % 2 for i in range(rows)])[:rows]
     win = torch.randn(2, ring, D, device="cuda").bfloat16()
     pool = torch.randn(max_pages * 2 * page_rows, D, device="cuda").bfloat16()
-    row_bytes = 0 if kv == "bf16" else (D + D // 32 + 15) // 16 * 16
+    row_bytes = 0 if kv == "bf16" else (D + D // 32 + 15) // 16 * 16      # "fp4" keeps FP8 window rows
     win_dev, pool_dev = win, pool
+    comp_bytes = 0
     if row_bytes:
         win_dev, win = _pack_fp8_rows(win, row_bytes)          # the reference below sees the dequantised rows
-        pool_dev, pool = _pack_fp8_rows(pool, row_bytes)
+        if kv == "fp4":                                        # FP8 window rows, FP4 compressed rows
+            comp_bytes = (D // 2 + D // 16 + 15) // 16 * 16
+            pool_dev, pool = _pack_fp4_rows(pool, comp_bytes)
+        else:
+            pool_dev, pool = _pack_fp8_rows(pool, row_bytes)
     page_table = torch.arange(2 * max_pages, dtype=torch.int32, device="cuda").view(2, max_pages).flip(1).contiguous()
     sel = torch.full((rows, topk), -1, dtype=torch.int32, device="cuda")
     counts = ([64, 40, 0] + [(7 * i) % 65 for i in range(rows)])[:rows]
@@ -90,11 +106,11 @@ def test_sparse_attention(D, heads, rope, rows, n_splits, kv):
     pos_t = torch.tensor(positions, dtype=torch.int32, device="cuda")
     slot_t = torch.tensor(slots, dtype=torch.int32, device="cuda")
     scale = D ** -0.5
-    lib.check(k.ds41_attend(lib.ptr(q), C.c_longlong(heads * D), 0, rows, heads, D, window, ring, lib.ptr(pos_t),
-                            lib.ptr(slot_t), lib.ptr(win_dev), lib.ptr(pool_dev), lib.ptr(sel), lib.ptr(n_sel), topk,
-                            lib.ptr(page_table), max_pages, page_rows, lib.ptr(inv), rope, C.c_float(scale), n_splits,
-                            lib.ptr(None), lib.ptr(part_o), lib.ptr(part_ml), lib.ptr(sink), lib.ptr(out),
-                            C.c_longlong(heads * D), row_bytes, lib.stream()), "attend")
+    lib.check(k.ds41_attend_kv(lib.ptr(q), C.c_longlong(heads * D), 0, rows, heads, D, window, ring, lib.ptr(pos_t),
+                               lib.ptr(slot_t), lib.ptr(win_dev), lib.ptr(pool_dev), lib.ptr(sel), lib.ptr(n_sel), topk,
+                               lib.ptr(page_table), max_pages, page_rows, lib.ptr(inv), rope, C.c_float(scale), n_splits,
+                               lib.ptr(None), lib.ptr(part_o), lib.ptr(part_ml), lib.ptr(sink), lib.ptr(out),
+                               C.c_longlong(heads * D), row_bytes, comp_bytes, lib.ptr(None), lib.stream()), "attend")
     torch.cuda.synchronize()
     for r in range(rows):
         pos, slot = positions[r], slots[r]
