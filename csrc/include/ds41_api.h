@@ -306,6 +306,47 @@ int ds41_attend_kv(const void* q, long long ldq, int q_off, int rows, int heads,
                    const float* sink, void* out, long long ldo, int kv_row_bytes, int comp_row_bytes, const int* row_lo,
                    void* stream);
 
+// Sparse attention on the tcgen05 tensor cores (attend_tc.cu): same semantics as ds41_attend_kv for D = 512 or 128 and at
+// most 64 heads.  One CTA per (row, key split) multiplies every head against each gathered 64-key tile; with
+// n_splits == 1 the kernel writes the final bf16 rows itself (sink, normalisation, inverse RoPE), otherwise partials go
+// to part_o / part_ml and ds41_attend_merge finishes them.  split_d = 1 runs two CTAs per (row, split), one per half of
+// D, instead of keeping both halves in lane-interleaved accumulators.  Waits are bounded; `status` receives
+// {code, site, row, detail}.
+typedef struct {
+  const void* q;
+  long long ldq;
+  int q_off;
+  int rows, heads, D, window, ring;
+  const int* row_pos;
+  const int* row_slot;
+  const int* row_hi;
+  const int* row_lo;
+  const void* win;
+  const void* comp_pool;
+  const int* sel;
+  const int* n_sel;
+  int k;
+  const int* page_table;
+  int max_pages, page_rows;
+  const float* inv_freq;
+  int rope_dim;
+  float scale;
+  int n_splits;
+  float* part_o;
+  float* part_ml;
+  const float* sink;
+  void* out;
+  long long ldo;
+  int kv_row_bytes, comp_row_bytes;
+  int split_d;
+  int* status;
+} ds41_attend_args;
+int ds41_attend_tc(const ds41_attend_args* args, void* stream);
+// Merge of split-key partials: part_o [rows][n_splits][heads][D] fp32, part_ml [rows][n_splits][heads][2] = (max, sum).
+int ds41_attend_merge(const float* part_o, const float* part_ml, const float* sink, const int* row_pos,
+                      const int* row_slot, const float* inv_freq, int rope_dim, int heads, int D, int n_splits, int rows,
+                      void* out, long long ldo, void* stream);
+
 // ---------------------------------------------------------------------------------------------------
 // Pipeline-stage handoff over peer memory (pp.cu).  Counters are 32-bit words in symmetric memory; every wait is bounded
 // and reports {flag timeout, site} in the status word.

@@ -225,10 +225,29 @@ __device__ __forceinline__ uint64_t umma_desc_plain(uint32_t smem_addr, uint32_t
   return d;
 }
 
+// MN-major operand (the dimension that is NOT contracted is contiguous) in the 128-byte swizzle: 128-byte spans of 64
+// bf16 along M/N, rows of the contracted dimension 128 bytes apart inside an 8-row atom; `mn_group_bytes` separates
+// consecutive 64-element groups along M/N (leading byte offset), `k_group_bytes` consecutive 8-row groups along K
+// (stride byte offset).
+__device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t smem_addr, uint32_t mn_group_bytes,
+                                                       uint32_t k_group_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(mn_group_bytes >> 4) << 16;
+  d |= static_cast<uint64_t>(k_group_bytes >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
 // Instruction descriptor for kind::f16 / kind::tf32 / kind::f8f6f4 (dense, fp32 accumulate).
 // a_fmt/b_fmt: f16 kinds 0=F16 1=BF16 2=TF32; f8f6f4 kinds 0=E4M3 1=E5M2 3=E2M3 4=E3M2 5=E2M1.
 __host__ __device__ constexpr uint32_t umma_idesc(uint32_t m, uint32_t n, uint32_t a_fmt, uint32_t b_fmt) {
   return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+// Same with the B operand MN-major (bit 16), e.g. P x V where V is stored [key][dim] and the keys are contracted.
+__host__ __device__ constexpr uint32_t umma_idesc_bmn(uint32_t m, uint32_t n, uint32_t a_fmt, uint32_t b_fmt) {
+  return umma_idesc(m, n, a_fmt, b_fmt) | (1u << 16);
 }
 // Block-scaled kinds (mxf8f6f4 / mxf4 / mxf4nvf4): scale_fmt 0=E4M3 1=UE8M0; sf ids select the
 // byte (scale_vec 1X) within the 32-bit TMEM scale column.
@@ -293,6 +312,20 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
       : "r"(taddr)
       : "memory");
 }
+// registers -> TMEM: the mirror image of tmem_ld_32x32 (complete after tmem_wait_st)
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "

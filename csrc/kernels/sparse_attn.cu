@@ -1101,6 +1101,15 @@ extern "C" int ds41_candidate_select(const float* scores, int max_keys, const in
   return launch_pdl(candidate_select_kernel, dim3(rows), dim3(1024), 0, static_cast<cudaStream_t>(stream), p);
 }
 
+extern "C" int ds41_attend_merge(const float* part_o, const float* part_ml, const float* sink, const int* row_pos,
+                                 const int* row_slot, const float* inv_freq, int rope_dim, int heads, int D, int n_splits,
+                                 int rows, void* out, long long ldo, void* stream) {
+  if (rows <= 0 || heads <= 0 || n_splits <= 0 || n_splits > 32 || (D & 1)) return cudaErrorInvalidValue;
+  MergeParams m{part_o, part_ml, sink, row_pos, row_slot, inv_freq, rope_dim, heads, D, n_splits,
+                static_cast<__nv_bfloat16*>(out), ldo};
+  return launch_pdl(attend_merge_kernel, dim3(heads, rows), dim3(128), 0, static_cast<cudaStream_t>(stream), m);
+}
+
 extern "C" int ds41_attend(const void* q, long long ldq, int q_off, int rows, int heads, int D, int window, int ring,
                            const int* row_pos, const int* row_slot, const void* win, const void* comp_pool,
                            const int* sel, const int* n_sel, int k, const int* page_table, int max_pages,

@@ -26,6 +26,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..config import ModelConfig, rope_inv_freq
+from ..ops import attention as A
 from ..ops import gemm as G
 from ..ops import lib
 from ..parallel.fabric import Fabric, SymBuffer
@@ -736,10 +737,12 @@ class DS41Engine:
         return best
 
     def _attn_splits(self, rows: int) -> int:
-        """Key-tile splits per (row, head group): one tile per CTA for a few rows (decode), fewer and longer CTAs once
-        the rows alone fill the GPU about three CTAs deep (prefill)."""
-        groups = (self.HL + 15) // 16
-        want = -(-3 * 148 // (rows * groups))
+        """Key-tile splits per row: one tile per CTA for a few rows (decode), fewer and longer CTAs once the rows
+        alone fill the GPU about two to three CTAs deep (prefill; one split lets the kernel write final rows)."""
+        if A.tc_usable(self.cfg.head_dim, self.HL):
+            want = -(-2 * 148 // rows)           # one CTA covers every head of a row
+        else:
+            want = -(-3 * 148 // (rows * ((self.HL + 15) // 16)))
         return max(1, min(self.n_splits_attn, want))
 
     def _splits(self, m: int, k: int, rows: int) -> int:
@@ -1001,15 +1004,15 @@ class DS41Engine:
                 self._run("topk", k.ds41_topk_select_cand, lib.ptr(self.scores), self.max_keys, lib.ptr(self.row_pos),
                                             lib.ptr(self.row_slot), ratio, cfg.index_topk, lib.ptr(self.sel),
                                             lib.ptr(self.n_sel), R, *cand, st())
-            self._run("attend", k.ds41_attend_kv, 
-                lib.ptr(self.qb_out), C.c_longlong(self.nqb), 0, R, self.HL, D, cfg.window, self.cache.ring,
-                lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.cache.win[l]),
-                lib.ptr(self.cache.comp[src]) if src is not None else lib.ptr(None),
-                lib.ptr(self.sel), lib.ptr(self.n_sel), cfg.index_topk, lib.ptr(self.cache.page_table),
-                self.cache.max_pages, self.cache.page_rows[src] if src is not None else 1, lib.ptr(inv), cfg.rope_dim,
-                C.c_float(cfg.softmax_scale), self._attn_splits(R), lib.ptr(self.row_hi), lib.ptr(self.part_o),
-                lib.ptr(self.part_ml), lib.ptr(lw.sink), lib.ptr(self.attn_out), C.c_longlong(self.HL * D),
-                self.cache.row_bytes, self.cache.comp_row_bytes, lib.ptr(self.row_lo if self._floor_on else None), st())
+            self._run("attend", A.attend, q=self.qb_out, ldq=self.nqb, q_off=0, rows=R, heads=self.HL, D=D,
+                      window=cfg.window, ring=self.cache.ring, row_pos=self.row_pos, row_slot=self.row_slot,
+                      win=self.cache.win[l], comp_pool=self.cache.comp[src] if src is not None else None,
+                      sel=self.sel, n_sel=self.n_sel, k=cfg.index_topk, page_table=self.cache.page_table,
+                      max_pages=self.cache.max_pages, page_rows=self.cache.page_rows[src] if src is not None else 1,
+                      inv_freq=inv, rope_dim=cfg.rope_dim, scale=cfg.softmax_scale, n_splits=self._attn_splits(R),
+                      part_o=self.part_o, part_ml=self.part_ml, sink=lw.sink, out=self.attn_out, ldo=self.HL * D,
+                      kv_row_bytes=self.cache.row_bytes, comp_row_bytes=self.cache.comp_row_bytes,
+                      row_hi=self.row_hi, row_lo=self.row_lo if self._floor_on else None, status=self.status)
             # grouped wo_a: batch = local groups
             kg = cfg.heads_per_group * D
             self._run("gemm_wo_a", G.gemm_raw, lw.wo_a, self.attn_out, self.oa, cfg.o_lora, R, kg, lda=kg, ldb=self.HL * D,

@@ -52,6 +52,20 @@ class HcStepArgs(C.Structure):
     ]
 
 
+class AttendArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("ldq", C.c_longlong), ("q_off", C.c_int),
+        ("rows", C.c_int), ("heads", C.c_int), ("D", C.c_int), ("window", C.c_int), ("ring", C.c_int),
+        ("row_pos", C.c_void_p), ("row_slot", C.c_void_p), ("row_hi", C.c_void_p), ("row_lo", C.c_void_p),
+        ("win", C.c_void_p), ("comp_pool", C.c_void_p), ("sel", C.c_void_p), ("n_sel", C.c_void_p), ("k", C.c_int),
+        ("page_table", C.c_void_p), ("max_pages", C.c_int), ("page_rows", C.c_int),
+        ("inv_freq", C.c_void_p), ("rope_dim", C.c_int), ("scale", C.c_float),
+        ("n_splits", C.c_int), ("part_o", C.c_void_p), ("part_ml", C.c_void_p), ("sink", C.c_void_p),
+        ("out", C.c_void_p), ("ldo", C.c_longlong), ("kv_row_bytes", C.c_int), ("comp_row_bytes", C.c_int),
+        ("split_d", C.c_int), ("status", C.c_void_p),
+    ]
+
+
 class EpArgs(C.Structure):
     _fields_ = [
         ("world", C.c_int), ("rank", C.c_int), ("e_local", C.c_int), ("topk", C.c_int), ("tokens", C.c_int),
@@ -111,6 +125,7 @@ def dir_functions():
         "ds41_copy_ints", "ds41_rs_reduce", "ds41_ep_count", "ds41_ep_plan", "ds41_ep_dispatch", "ds41_ep_mark",
         "ds41_ep_wait", "ds41_ep_combine", "ds41_act_quant_mx_rows", "ds41_sample_rows", "ds41_engram_dequant", "ds41_engram_gate", "ds41_block_max", "ds41_expand_blocks", "ds41_vis_rmsnorm", "ds41_vis_bias_act", "ds41_vis_silu_mul",
         "ds41_index_prepare", "ds41_candidate_select", "ds41_pp_signal", "ds41_pp_wait", "ds41_pp_pull", "ds41_attend_floor", "ds41_attend_kv", "ds41_index_score_cand", "ds41_topk_select_cand", "ds41_act_quant_nvfp4_rows", "ds41_vis_rope2d", "ds41_vis_softmax", "ds41_vis_merge", "ds41_vis_scatter",
+        "ds41_attend_tc", "ds41_attend_merge",
     ]
 
 

@@ -76,25 +76,35 @@ class Heartbeat:
 
     def leave(self, reason: str) -> None:
         """Announce that this rank stops launching (call it between steps, then stop)."""
-        self.store.set(f"{self.prefix}/left/{self.rank}", reason)
-        self.stop()
+        try:
+            self.store.set(f"{self.prefix}/left/{self.rank}", reason)
+        finally:
+            self.stop()
 
     # ------------------------------------------------------------------ checking
     def peers_down(self) -> Dict[int, str]:
+        """Peers that left, never joined or went silent.  A store that cannot be reached counts as a failure too: the
+        rank that hosts it is gone (or the network to it is), so every peer is reported with that reason."""
         now, down = self.clock(), {}
-        for r in range(self.world):
-            if r == self.rank:
-                continue
-            if self.store.check([f"{self.prefix}/left/{r}"]):
-                down[r] = self.store.get(f"{self.prefix}/left/{r}").decode()
-                continue
-            key = f"{self.prefix}/{r}"
-            if not self.store.check([key]):
-                down[r] = "never joined"
-                continue
-            age = now - float(self.store.get(key).decode())
-            if age > self.max_age:
-                down[r] = f"silent for {age:.1f} s"
+        try:
+            for r in range(self.world):
+                if r == self.rank:
+                    continue
+                if self.store.check([f"{self.prefix}/left/{r}"]):
+                    down[r] = self.store.get(f"{self.prefix}/left/{r}").decode()
+                    continue
+                key = f"{self.prefix}/{r}"
+                if not self.store.check([key]):
+                    down[r] = "never joined"
+                    continue
+                age = now - float(self.store.get(key).decode())
+                if age > self.max_age:
+                    down[r] = f"silent for {age:.1f} s"
+        except Exception as e:           # TCPStore raises DistNetworkError / RuntimeError when its host is gone
+            why = f"store unreachable: {type(e).__name__}"
+            for r in range(self.world):
+                if r != self.rank:
+                    down.setdefault(r, why)
         return down
 
     def guard(self) -> None:

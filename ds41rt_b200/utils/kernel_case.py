@@ -5,7 +5,7 @@
 
 Cases (model-sized rows, working sets of a few hundred MB at most):
   attend_wide    sparse attention of a long pass: 256 rows x 64 heads x D 512, window 128 + 512 selected keys (bf16 rows)
-  attend_decode  the same attention for 5 rows (16 heads per CTA, key tiles split over CTAs)
+  attend_decode  the same attention for 5 rows (key tiles split over CTAs); --attn-impl picks the kernel
   index_gemm     lightning-indexer scores on tensor cores: 1024 rows x 32 heads x 128 dims against 16384 keys
   topk           exact top-512 of 16384 scores for 1024 rows
   candidates     candidate-block selection: top 2048 blocks of 8 from 131072 scores for 64 rows
@@ -38,7 +38,8 @@ def _time(fn, reps: int) -> float:
     return e0.elapsed_time(e1) / reps
 
 
-def attend_case(rows: int, heads: int = 64, D: int = 512, window: int = 128, topk: int = 512, ctx: int = 16384):
+def attend_case(rows: int, heads: int = 64, D: int = 512, window: int = 128, topk: int = 512, ctx: int = 16384,
+                impl: str = "tc"):
     k, dev = lib.kernels(), torch.device("cuda")
     g = torch.Generator(device=dev).manual_seed(0)
     ring, page_rows = window + max(16, rows), 64
@@ -55,22 +56,27 @@ def attend_case(rows: int, heads: int = 64, D: int = 512, window: int = 128, top
     q = torch.randn(rows, heads * D, device=dev, generator=g).bfloat16()
     sink = torch.zeros(heads, device=dev)
     inv = torch.tensor(rope_inv_freq(RopeConfig(), 64), device=dev)
-    groups = (heads + 15) // 16
-    n_splits = max(1, min(16, -(-3 * 148 // (rows * groups))))
+    from ..ops import attention as A
+    if impl == "legacy":
+        n_splits = max(1, min(16, -(-3 * 148 // (rows * ((heads + 15) // 16)))))
+    else:
+        n_splits = max(1, min((window + 16 + topk + 63) // 64, -(-2 * 148 // rows)))
     part_o = torch.zeros(rows, n_splits, heads, D, device=dev)
     part_ml = torch.zeros(rows, n_splits, heads, 2, device=dev)
     out = torch.zeros(rows, heads * D, device=dev, dtype=torch.bfloat16)
+    status = lib.new_status(dev)
 
     def run():
-        lib.check(k.ds41_attend(lib.ptr(q), C.c_longlong(heads * D), 0, rows, heads, D, window, ring, lib.ptr(pos),
-                                lib.ptr(slot), lib.ptr(win), lib.ptr(pool), lib.ptr(sel), lib.ptr(n_sel), topk,
-                                lib.ptr(page_table), max_pages, page_rows, lib.ptr(inv), 64, C.c_float(D ** -0.5),
-                                n_splits, lib.ptr(None), lib.ptr(part_o), lib.ptr(part_ml), lib.ptr(sink), lib.ptr(out),
-                                C.c_longlong(heads * D), 0, lib.stream()), "attend")
+        lib.check(A.attend(q=q, ldq=heads * D, q_off=0, rows=rows, heads=heads, D=D, window=window, ring=ring,
+                           row_pos=pos, row_slot=slot, win=win, comp_pool=pool, sel=sel, n_sel=n_sel, k=topk,
+                           page_table=page_table, max_pages=max_pages, page_rows=page_rows, inv_freq=inv, rope_dim=64,
+                           scale=D ** -0.5, n_splits=n_splits, part_o=part_o, part_ml=part_ml, sink=sink, out=out,
+                           ldo=heads * D, status=status, impl=impl), "attend")
     keys = window + topk
     flops = 2.0 * 2.0 * rows * heads * keys * D
     gathered = 2.0 * rows * keys * D          # each row's keys read once if all its heads share them
-    return run, {"flops": flops, "bytes_min": gathered, "rows": rows, "keys_per_row": keys, "splits": n_splits}
+    return run, {"flops": flops, "bytes_min": gathered, "rows": rows, "keys_per_row": keys, "splits": n_splits,
+                 "status": status}
 
 
 def index_gemm_case(rows: int = 1024, n_keys: int = 16384, heads: int = 32, dim: int = 128):
@@ -136,18 +142,25 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="")
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--attn-impl", default="tc", choices=["tc", "tc_split_d", "legacy"],
+                    help="attention cases: tcgen05 kernel (default), its one-CTA-per-half-of-D form, or the warp-MMA kernels")
+    ap.add_argument("--attn-rows", type=int, default=256, help="rows of the attend_wide case")
     args = ap.parse_args(argv)
     want = lambda name: not args.only or name in args.only.split(",")
     out = {}
     idx = None
     if want("attend_wide"):
-        run, info = attend_case(256)
+        run, info = attend_case(args.attn_rows, impl=args.attn_impl)
         ms = _time(run, args.reps)
-        out["attend_wide"] = {"ms": ms, "tflops": info["flops"] / ms / 1e9, **{k: v for k, v in info.items() if k != "flops"}}
+        lib.raise_on_status(info.pop("status"), "attend_wide")
+        out["attend_wide"] = {"ms": ms, "tflops": info["flops"] / ms / 1e9, "impl": args.attn_impl,
+                              "gb_s_keys": info["bytes_min"] / ms / 1e6, **{k: v for k, v in info.items() if k != "flops"}}
     if want("attend_decode"):
-        run, info = attend_case(5)
+        run, info = attend_case(5, impl=args.attn_impl)
         ms = _time(run, args.reps)
-        out["attend_decode"] = {"ms": ms, "gb_s_keys": info["bytes_min"] / ms / 1e6, "splits": info["splits"]}
+        lib.raise_on_status(info.pop("status"), "attend_decode")
+        out["attend_decode"] = {"ms": ms, "gb_s_keys": info["bytes_min"] / ms / 1e6, "splits": info["splits"],
+                                "impl": args.attn_impl}
     if want("index_gemm") or want("topk"):
         run, idx = index_gemm_case()
         ms = _time(run, args.reps)

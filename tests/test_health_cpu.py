@@ -26,10 +26,38 @@ def test_silent_left_and_missing_ranks_with_a_fake_clock():
     assert e.value.ranks == [1, 2, 3] and "site 110" in e.value.reasons[1]
 
 
-def _rank(rank, world, port, mode, q):
+def _free_port_below_ephemeral():
+    """A free port outside the range the kernel hands to outgoing connections: a client that retries against a port
+    nobody listens on yet can otherwise be given that very port as its source and connect to itself."""
+    import random
+    import socket
+    for _ in range(200):
+        port = random.randint(20000, 29999)
+        with socket.socket() as s:
+            try:
+                s.bind(("127.0.0.1", port))
+            except OSError:
+                continue
+        return port
+    raise RuntimeError("no free port")
+
+
+def test_an_unreachable_store_reports_every_peer():
+    class Broken(DictStore):
+        def check(self, keys):
+            raise ConnectionError("Broken pipe")
+    store = Broken()
+    hb = Heartbeat(store, 0, 3)
+    down = hb.peers_down()
+    assert set(down) == {1, 2} and all(v.startswith("store unreachable") for v in down.values())
+    with pytest.raises(RankFailure):
+        hb.guard()
+
+
+def _rank(rank, world, port, store_port, mode, q):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
-    store = dist.TCPStore("127.0.0.1", port + 1, world, is_master=(rank == 0), wait_for_workers=False)
+    store = dist.TCPStore("127.0.0.1", store_port, world, is_master=False)      # hosted by the launcher
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=__import__("datetime").timedelta(seconds=20))
     import torch
     hb = Heartbeat(store, rank, world, interval=0.05, max_age=0.6).start()
@@ -59,6 +87,8 @@ def _rank(rank, world, port, mode, q):
             time.sleep(0.05)
     except RankFailure as e:
         failure = (e.ranks, dict(e.reasons))
+    except Exception as e:                           # anything else is reported, not left to hang the parent
+        failure = ([], {"error": f"{type(e).__name__}: {e}"})
     q.put((rank, steps, failure))
     hb.stop()
     time.sleep(0.3)
@@ -67,10 +97,15 @@ def _rank(rank, world, port, mode, q):
 
 @pytest.mark.parametrize("mode", ["leave", "die"])
 def test_gloo_ranks_detect_a_lost_peer_before_the_next_collective(mode):
-    world, port = 3, 29650 + (0 if mode == "leave" else 10)
+    import torch.distributed as dist
+    world = 3
+    port = _free_port_below_ephemeral()
+    # the heartbeat store lives in the launcher: it listens before any rank starts and outlives all of them
+    host = dist.TCPStore("127.0.0.1", 0, None, is_master=True, wait_for_workers=False)
+    store_port = host.port
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_rank, args=(r, world, port, mode, q)) for r in range(world)]
+    procs = [ctx.Process(target=_rank, args=(r, world, port, store_port, mode, q)) for r in range(world)]
     for p in procs:
         p.start()
     results = {}

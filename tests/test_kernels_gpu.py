@@ -64,12 +64,18 @@ def _pack_fp4_rows(x, row_bytes):
     return rows.contiguous(), Q.dequant_kv_fp4_e4m3_16(packed, bs).reshape(x.shape).bfloat16()
 
 
+@pytest.mark.parametrize("impl", ["tc", "tc_split_d", "legacy"])
 @pytest.mark.parametrize("kv", ["bf16", "fp8", "fp4"])
 @pytest.mark.parametrize("D,heads,rope,rows,n_splits", [(128, 8, 32, 3, 0), (512, 16, 64, 3, 0), (512, 64, 64, 3, 0),
                                                          (512, 64, 64, 70, 1), (512, 64, 64, 66, 3), (128, 64, 32, 64, 2)])
-def test_sparse_attention(D, heads, rope, rows, n_splits, kv):
-    """rows >= 64 with 64 heads runs the wide kernel (all heads share the gathered keys, double-buffered half tiles)."""
+def test_sparse_attention(D, heads, rope, rows, n_splits, kv, impl):
+    """impl "tc": tcgen05 kernel (one CTA per row and key split, accumulators in tensor memory, final rows written by
+    the kernel when there is one split); "tc_split_d": the same with one CTA per half of D; "legacy": warp-MMA kernels
+    (rows >= 64 with 64 heads runs their wide form)."""
     from ds41rt_b200.ops import lib
+    from ds41rt_b200.ops import attention as A
+    if impl == "tc_split_d" and D != 512:
+        pytest.skip("one accumulator already holds a 128-wide row")
     from ds41rt_b200.config import RopeConfig, rope_inv_freq
     from ds41rt_b200.models.reference import apply_rope
     k = lib.kernels()
@@ -106,11 +112,15 @@ def test_sparse_attention(D, heads, rope, rows, n_splits, kv):
     pos_t = torch.tensor(positions, dtype=torch.int32, device="cuda")
     slot_t = torch.tensor(slots, dtype=torch.int32, device="cuda")
     scale = D ** -0.5
-    lib.check(k.ds41_attend_kv(lib.ptr(q), C.c_longlong(heads * D), 0, rows, heads, D, window, ring, lib.ptr(pos_t),
-                               lib.ptr(slot_t), lib.ptr(win_dev), lib.ptr(pool_dev), lib.ptr(sel), lib.ptr(n_sel), topk,
-                               lib.ptr(page_table), max_pages, page_rows, lib.ptr(inv), rope, C.c_float(scale), n_splits,
-                               lib.ptr(None), lib.ptr(part_o), lib.ptr(part_ml), lib.ptr(sink), lib.ptr(out),
-                               C.c_longlong(heads * D), row_bytes, comp_bytes, lib.ptr(None), lib.stream()), "attend")
+    status = lib.new_status(q.device)
+    lib.check(A.attend(q=q, ldq=heads * D, q_off=0, rows=rows, heads=heads, D=D, window=window, ring=ring, row_pos=pos_t,
+                       row_slot=slot_t, win=win_dev, comp_pool=pool_dev, sel=sel, n_sel=n_sel, k=topk,
+                       page_table=page_table, max_pages=max_pages, page_rows=page_rows, inv_freq=inv, rope_dim=rope,
+                       scale=scale, n_splits=n_splits, part_o=part_o, part_ml=part_ml, sink=sink, out=out,
+                       ldo=heads * D, kv_row_bytes=row_bytes, comp_row_bytes=comp_bytes, status=status, impl=impl),
+              "attend")
+    torch.cuda.synchronize()
+    lib.raise_on_status(status, "attend")
     torch.cuda.synchronize()
     for r in range(rows):
         pos, slot = positions[r], slots[r]
