@@ -56,6 +56,29 @@ int ds41_kv_admit(void* p, uint32_t* generation) {
   return -1;
 }
 
+// Admit a request into one particular slot: 0 and its generation, -1 when the slot is taken or out of range.
+int ds41_kv_admit_slot(void* p, int slot, uint32_t* generation) {
+  Alloc* a = static_cast<Alloc*>(p);
+  if (slot < 0 || slot >= static_cast<int>(a->slots.size()) || a->slots[slot].active) return -1;
+  a->slots[slot].active = true;
+  if (generation) *generation = a->slots[slot].generation;
+  return 0;
+}
+// Generation of an active slot, 0 when the slot is free (generations start at 1).
+uint32_t ds41_kv_slot_generation(const void* p, int slot) {
+  const Alloc* a = static_cast<const Alloc*>(p);
+  if (slot < 0 || slot >= static_cast<int>(a->slots.size()) || !a->slots[slot].active) return 0;
+  return a->slots[slot].generation;
+}
+// Page list of a slot (up to cap entries); returns the number of pages the slot holds.
+int ds41_kv_slot_pages(const void* p, int slot, int32_t* out, int cap) {
+  const Alloc* a = static_cast<const Alloc*>(p);
+  if (slot < 0 || slot >= static_cast<int>(a->slots.size())) return -1;
+  const std::vector<int32_t>& pg = a->slots[slot].pages;
+  for (int i = 0; i < static_cast<int>(pg.size()) && i < cap; ++i) out[i] = pg[i];
+  return static_cast<int>(pg.size());
+}
+
 // Ensure pages for positions [0, n_tokens).  Writes newly mapped (index, page) pairs into out (capacity `cap`
 // pairs).  Returns the number of new pages, -1 stale lease, -2 pool exhausted (nothing changes), -3 cap too small.
 int ds41_kv_ensure(void* p, int slot, uint32_t gen, int n_tokens, int32_t* out, int cap) {

@@ -307,11 +307,10 @@ int ds41_attend_kv(const void* q, long long ldq, int q_off, int rows, int heads,
                    void* stream);
 
 // Sparse attention on the tcgen05 tensor cores (attend_tc.cu): same semantics as ds41_attend_kv for D = 512 or 128 and at
-// most 64 heads.  One CTA per (row, key split) multiplies every head against each gathered 64-key tile; with
-// n_splits == 1 the kernel writes the final bf16 rows itself (sink, normalisation, inverse RoPE), otherwise partials go
-// to part_o / part_ml and ds41_attend_merge finishes them.  split_d = 1 runs two CTAs per (row, split), one per half of
-// D, instead of keeping both halves in lane-interleaved accumulators.  Waits are bounded; `status` receives
-// {code, site, row, detail}.
+// most 64 heads.  A persistent grid walks the (row, key split) items; each item multiplies every head against each
+// gathered 64-key tile.  With n_splits == 1 the kernel writes the final bf16 rows itself (sink, normalisation, inverse
+// RoPE), otherwise partials go to part_o / part_ml and ds41_attend_merge finishes them.  Waits are bounded; `status`
+// receives {code, site, row, detail}.
 typedef struct {
   const void* q;
   long long ldq;
@@ -338,7 +337,6 @@ typedef struct {
   void* out;
   long long ldo;
   int kv_row_bytes, comp_row_bytes;
-  int split_d;
   int* status;
 } ds41_attend_args;
 int ds41_attend_tc(const ds41_attend_args* args, void* stream);

@@ -439,35 +439,58 @@ class KVCache:
                 self.pending[src] = torch.zeros(slots, 4, 2 * D, dtype=F32, device=device)
         self.page_table_host = torch.full((slots, self.max_pages), -1, dtype=I32)
         self.page_table = self.page_table_host.to(device)
-        self.free_pages = list(range(self.n_pages - 1, -1, -1))
-        self.page_ref = [0] * self.n_pages          # slots and snapshots holding each page
-        self.pages_of: Dict[int, List[int]] = {s: [] for s in range(slots)}
+        # Pages, reference counts and slot leases live in the host runtime's allocator (csrc/core/kvalloc.cc); this
+        # class only mirrors each slot's page list into the device page table.
+        from ..runtime import core as K
+        self.alloc = K.KvAllocator(self.n_pages, slots, page_tokens)
+
+    # ------------------------------------------------------------------ slots and pages
+    @property
+    def free_pages(self) -> int:
+        return self.alloc.free_pages
+
+    def pages_of(self, slot: int) -> List[int]:
+        return self.alloc.pages(slot)
+
+    def admit(self):
+        """Lease a free slot -> (slot, generation), or None when every slot is taken."""
+        return self.alloc.admit()
+
+    def _gen(self, slot: int) -> int:
+        """Generation of the slot's lease; a slot used without admit() (single-request drivers) is leased here."""
+        g = self.alloc.generation(slot)
+        if g == 0:
+            g = self.alloc.admit_slot(slot)
+            assert g is not None
+        return g
+
+    def _publish(self, slot: int, first: int = 0):
+        pages = self.alloc.pages(slot)
+        n = len(pages)
+        if n > first:
+            self.page_table_host[slot, first:n] = torch.tensor(pages[first:], dtype=I32)
+            self.page_table[slot, first:n].copy_(self.page_table_host[slot, first:n], non_blocking=True)
 
     def ensure(self, slot: int, n_tokens: int) -> bool:
         """Make sure `slot` has pages for positions [0, n_tokens).  Returns False when the pool is exhausted."""
         need = (n_tokens + self.page_tokens - 1) // self.page_tokens
-        have = len(self.pages_of[slot])
+        if need > self.max_pages:
+            return False
+        gen = self._gen(slot)
+        have = self.alloc.page_count(slot)
         if need <= have:
             return True
-        if need > self.max_pages or need - have > len(self.free_pages):
+        try:
+            self.alloc.ensure(slot, gen, n_tokens)
+        except MemoryError:
             return False
-        for i in range(have, need):
-            pg = self.free_pages.pop()
-            self.page_ref[pg] = 1
-            self.pages_of[slot].append(pg)
-            self.page_table_host[slot, i] = pg
-        self.page_table[slot, :need].copy_(self.page_table_host[slot, :need], non_blocking=True)
+        self._publish(slot, have)
         return True
 
-    def _unref(self, pages: List[int]):
-        for pg in reversed(pages):
-            self.page_ref[pg] -= 1
-            if self.page_ref[pg] == 0:
-                self.free_pages.append(pg)
-
     def release(self, slot: int):
-        self._unref(self.pages_of[slot])
-        self.pages_of[slot] = []
+        g = self.alloc.generation(slot)
+        if g:
+            self.alloc.retire(slot, g)
         self.page_table_host[slot].fill_(-1)
         self.page_table[slot].fill_(-1)
 
@@ -475,13 +498,12 @@ class KVCache:
     def snapshot(self, slot: int, n_tokens: int) -> KVSnapshot:
         """Capture `slot` after positions [0, n_tokens) (call it between passes, on the engine's stream)."""
         full = n_tokens // self.page_tokens
-        pages = list(self.pages_of[slot][:full])
-        for pg in pages:
-            self.page_ref[pg] += 1
+        mine = self.alloc.pages(slot)
+        pages = self.alloc.retain(slot, self._gen(slot), min(full, len(mine)))
         partial = {}
         rem = n_tokens - full * self.page_tokens
-        if rem and full < len(self.pages_of[slot]):
-            pg = self.pages_of[slot][full]
+        if rem and full < len(mine):
+            pg = mine[full]
             for src, pr in self.page_rows.items():
                 rows = (rem * pr + self.page_tokens - 1) // self.page_tokens
                 partial[src] = (self.comp[src][pg * pr: pg * pr + rows].clone(), self.idx[src][pg * pr: pg * pr + rows].clone())
@@ -493,21 +515,17 @@ class KVCache:
         count below the snapshot's length): whole pages below the cut are shared, the page the cut falls into is copied
         up to the cut.  Window rings and the pair carry are NOT restored: the caller replays the tokens from the cut on
         with a window floor at the cut.  Returns False when no page is free for the copied page."""
-        assert not self.pages_of[slot], "restore needs an empty slot"
+        gen = self._gen(slot)
+        assert self.alloc.page_count(slot) == 0, "restore needs an empty slot"
         assert 0 < n_tokens <= snap.n_tokens and n_tokens % 2 == 0
         full = n_tokens // self.page_tokens
         rem = n_tokens - full * self.page_tokens
-        if rem and not self.free_pages:
+        if rem and self.alloc.free_pages == 0:
             return False
-        for i, pg in enumerate(snap.pages[:full]):
-            self.page_ref[pg] += 1
-            self.pages_of[slot].append(pg)
-            self.page_table_host[slot, i] = pg
+        self.alloc.share(slot, gen, snap.pages[:full])
         if rem:
-            pg = self.free_pages.pop()
-            self.page_ref[pg] = 1
-            self.pages_of[slot].append(pg)
-            self.page_table_host[slot, full] = pg
+            self.alloc.ensure(slot, gen, n_tokens)
+            pg = self.alloc.pages(slot)[full]
             for src, pr in self.page_rows.items():
                 rows = (rem * pr + self.page_tokens - 1) // self.page_tokens
                 if full < len(snap.pages):                  # the cut falls into one of the snapshot's whole pages
@@ -517,40 +535,33 @@ class KVCache:
                     c, ix = snap.partial[src][0][:rows], snap.partial[src][1][:rows]
                 self.comp[src][pg * pr: pg * pr + rows].copy_(c)
                 self.idx[src][pg * pr: pg * pr + rows].copy_(ix)
-        n = len(self.pages_of[slot])
-        if n:
-            self.page_table[slot, :n].copy_(self.page_table_host[slot, :n], non_blocking=True)
+        self._publish(slot)
         return True
 
     def restore(self, slot: int, snap: KVSnapshot) -> bool:
         """Continue a snapshot in an empty `slot`: shared full pages, a private copy of the partial page, rings and
         carry.  Returns False when no page is free for the partial page."""
-        assert not self.pages_of[slot], "restore needs an empty slot"
-        if snap.partial and not self.free_pages:
+        gen = self._gen(slot)
+        assert self.alloc.page_count(slot) == 0, "restore needs an empty slot"
+        if snap.partial and self.alloc.free_pages == 0:
             return False
-        for i, pg in enumerate(snap.pages):
-            self.page_ref[pg] += 1
-            self.pages_of[slot].append(pg)
-            self.page_table_host[slot, i] = pg
+        self.alloc.share(slot, gen, snap.pages)
         if snap.partial:
-            pg = self.free_pages.pop()
-            self.page_ref[pg] = 1
-            self.pages_of[slot].append(pg)
-            self.page_table_host[slot, len(snap.pages)] = pg
+            self.alloc.ensure(slot, gen, (len(snap.pages) + 1) * self.page_tokens)
+            pg = self.alloc.pages(slot)[len(snap.pages)]
             for src, (c, ix) in snap.partial.items():
                 pr = self.page_rows[src]
                 self.comp[src][pg * pr: pg * pr + c.shape[0]].copy_(c)
                 self.idx[src][pg * pr: pg * pr + ix.shape[0]].copy_(ix)
-        n = len(self.pages_of[slot])
-        if n:
-            self.page_table[slot, :n].copy_(self.page_table_host[slot, :n], non_blocking=True)
+        self._publish(slot)
         self.win[:, slot].copy_(snap.rings)
         for src, t in snap.pending.items():
             self.pending[src][slot].copy_(t)
         return True
 
     def drop_snapshot(self, snap: KVSnapshot):
-        self._unref(snap.pages)
+        if snap.pages:
+            self.alloc.release_pages(snap.pages)
         snap.pages = []
 
     def nbytes(self) -> int:
@@ -739,7 +750,7 @@ class DS41Engine:
     def _attn_splits(self, rows: int) -> int:
         """Key-tile splits per row: one tile per CTA for a few rows (decode), fewer and longer CTAs once the rows
         alone fill the GPU about two to three CTAs deep (prefill; one split lets the kernel write final rows)."""
-        if A.tc_usable(self.cfg.head_dim, self.HL):
+        if A.tc_usable(self.cfg.head_dim, self.HL, rows):
             want = -(-2 * 148 // rows)           # one CTA covers every head of a row
         else:
             want = -(-3 * 148 // (rows * ((self.HL + 15) // 16)))

@@ -16,19 +16,24 @@ from . import lib
 KEYS_PER_TILE = 64
 
 
-def tc_usable(D: int, heads: int) -> bool:
-    return D in (128, 512) and heads <= 64 and os.environ.get("DS41_ATTN", "tc") != "legacy"
+TC_MIN_ROWS = 17      # decode-sized passes (a handful of rows, one key tile per CTA) stay on the warp-MMA kernel
+
+
+def tc_usable(D: int, heads: int, rows: int = TC_MIN_ROWS) -> bool:
+    """Does the tensor-core kernel serve this pass?  DS41_ATTN=legacy / tc forces one kernel for every pass."""
+    mode = os.environ.get("DS41_ATTN", "")
+    if D not in (128, 512) or heads > 64 or mode == "legacy":
+        return False
+    return mode == "tc" or rows >= TC_MIN_ROWS
 
 
 def attend(*, q, ldq, q_off, rows, heads, D, window, ring, row_pos, row_slot, win, comp_pool, sel, n_sel, k,
            page_table, max_pages, page_rows, inv_freq, rope_dim, scale, n_splits, part_o, part_ml, sink, out, ldo,
            kv_row_bytes=0, comp_row_bytes=0, row_hi=None, row_lo=None, status=None, impl=None):
-    """Enqueue the attention of one pass on the current stream.  `impl`: None (pick), "tc", "tc_split_d", "legacy"."""
+    """Enqueue the attention of one pass on the current stream.  `impl`: None (pick), "tc" or "legacy"."""
     kern = lib.kernels()
     if impl is None:
-        impl = "tc" if tc_usable(D, heads) else "legacy"
-        if impl == "tc" and os.environ.get("DS41_ATTN_SPLIT_D") == "1":
-            impl = "tc_split_d"
+        impl = "tc" if tc_usable(D, heads, rows) else "legacy"
     if impl == "legacy":
         return kern.ds41_attend_kv(
             lib.ptr(q), C.c_longlong(ldq), q_off, rows, heads, D, window, ring, lib.ptr(row_pos), lib.ptr(row_slot),
@@ -45,6 +50,5 @@ def attend(*, q, ldq, q_off, rows, heads, D, window, ring, row_pos, row_slot, wi
     a.inv_freq, a.rope_dim, a.scale = lib.ptr(inv_freq), rope_dim, scale
     a.n_splits, a.part_o, a.part_ml, a.sink = n_splits, lib.ptr(part_o), lib.ptr(part_ml), lib.ptr(sink)
     a.out, a.ldo, a.kv_row_bytes, a.comp_row_bytes = lib.ptr(out), ldo, kv_row_bytes, comp_row_bytes
-    a.split_d = 1 if impl == "tc_split_d" else 0
     a.status = lib.ptr(status)
     return kern.ds41_attend_tc(C.byref(a), lib.stream())

@@ -62,7 +62,7 @@ class AttendArgs(C.Structure):
         ("inv_freq", C.c_void_p), ("rope_dim", C.c_int), ("scale", C.c_float),
         ("n_splits", C.c_int), ("part_o", C.c_void_p), ("part_ml", C.c_void_p), ("sink", C.c_void_p),
         ("out", C.c_void_p), ("ldo", C.c_longlong), ("kv_row_bytes", C.c_int), ("comp_row_bytes", C.c_int),
-        ("split_d", C.c_int), ("status", C.c_void_p),
+        ("status", C.c_void_p),
     ]
 
 

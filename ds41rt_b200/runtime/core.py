@@ -175,6 +175,24 @@ class KvAllocator:
         slot = core().ds41_kv_admit(self.h, C.byref(gen))
         return None if slot < 0 else (slot, gen.value)
 
+    def admit_slot(self, slot: int) -> Optional[int]:
+        """Take one particular slot -> its generation, or None when it is in use."""
+        gen = C.c_uint32(0)
+        return gen.value if core().ds41_kv_admit_slot(self.h, slot, C.byref(gen)) == 0 else None
+
+    def generation(self, slot: int) -> int:
+        """Generation of an active slot, 0 when the slot is free."""
+        core().ds41_kv_slot_generation.restype = C.c_uint32
+        return int(core().ds41_kv_slot_generation(self.h, slot))
+
+    def pages(self, slot: int) -> List[int]:
+        n = self.page_count(slot)
+        if n <= 0:
+            return []
+        out = (C.c_int32 * n)()
+        core().ds41_kv_slot_pages(self.h, slot, out, n)
+        return list(out)
+
     def ensure(self, slot: int, gen: int, n_tokens: int) -> List[Tuple[int, int]]:
         cap = (n_tokens + self.page_tokens - 1) // self.page_tokens + 1
         out = (C.c_int32 * (2 * cap))()

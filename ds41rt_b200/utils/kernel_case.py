@@ -142,8 +142,8 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="")
     ap.add_argument("--reps", type=int, default=20)
-    ap.add_argument("--attn-impl", default="tc", choices=["tc", "tc_split_d", "legacy"],
-                    help="attention cases: tcgen05 kernel (default), its one-CTA-per-half-of-D form, or the warp-MMA kernels")
+    ap.add_argument("--attn-impl", default="tc", choices=["tc", "legacy"],
+                    help="attention cases: tcgen05 kernel (default) or the warp-MMA kernels")
     ap.add_argument("--attn-rows", type=int, default=256, help="rows of the attend_wide case")
     args = ap.parse_args(argv)
     want = lambda name: not args.only or name in args.only.split(",")

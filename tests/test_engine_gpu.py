@@ -246,7 +246,7 @@ def test_fp8_kv_cache_rows_and_logits():
     rows = len(toks) // cfg.source_layers[src]
     qc, ec = Q.quant_mxfp8(engines["bf16"].cache.comp[src].float(), 32)
     if src == 0:
-        pages = engines["bf16"].cache.pages_of[0]
+        pages = engines["bf16"].cache.pages_of(0)
         pr = engines["bf16"].cache.page_rows[src]
         phys = [pages[i // pr] * pr + i % pr for i in range(rows)]
         assert torch.equal(engines["fp8"].cache.comp[src][phys, :D], qc.view(torch.uint8)[phys])
@@ -413,9 +413,9 @@ def test_fp4_compressed_rows_and_logits():
     assert src in engines["bf16"].cache.comp
     n = len(toks) // cfg.source_layers[src]
     pr = engines["bf16"].cache.page_rows[src]
-    rows = [engines["bf16"].cache.pages_of[0][i // pr] * pr + i % pr for i in range(n)]
+    rows = [engines["bf16"].cache.pages_of(0)[i // pr] * pr + i % pr for i in range(n)]
     ref = engines["bf16"].cache.comp[src][rows].float().cpu()
-    rows4 = [engines["fp4"].cache.pages_of[0][i // pr] * pr + i % pr for i in range(n)]
+    rows4 = [engines["fp4"].cache.pages_of(0)[i // pr] * pr + i % pr for i in range(n)]
     got = engines["fp4"].cache.comp[src][rows4].cpu()
     packed, bs = Q.quant_kv_fp4_e4m3_16(ref)
     assert torch.equal(got[:, :D // 2], packed.view(torch.uint8).reshape(n, D // 2))

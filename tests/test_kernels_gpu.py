@@ -64,18 +64,17 @@ def _pack_fp4_rows(x, row_bytes):
     return rows.contiguous(), Q.dequant_kv_fp4_e4m3_16(packed, bs).reshape(x.shape).bfloat16()
 
 
-@pytest.mark.parametrize("impl", ["tc", "tc_split_d", "legacy"])
+@pytest.mark.parametrize("impl", ["tc", "legacy"])
 @pytest.mark.parametrize("kv", ["bf16", "fp8", "fp4"])
 @pytest.mark.parametrize("D,heads,rope,rows,n_splits", [(128, 8, 32, 3, 0), (512, 16, 64, 3, 0), (512, 64, 64, 3, 0),
-                                                         (512, 64, 64, 70, 1), (512, 64, 64, 66, 3), (128, 64, 32, 64, 2)])
+                                                         (512, 64, 64, 70, 1), (512, 64, 64, 66, 3), (128, 64, 32, 64, 2),
+                                                         (512, 64, 64, 330, 1), (512, 8, 64, 180, 2)])
 def test_sparse_attention(D, heads, rope, rows, n_splits, kv, impl):
-    """impl "tc": tcgen05 kernel (one CTA per row and key split, accumulators in tensor memory, final rows written by
-    the kernel when there is one split); "tc_split_d": the same with one CTA per half of D; "legacy": warp-MMA kernels
-    (rows >= 64 with 64 heads runs their wide form)."""
+    """impl "tc": tcgen05 kernel (persistent grid over (row, key split) items, accumulators in tensor memory, final rows
+    written by the kernel when there is one split); "legacy": warp-MMA kernels (rows >= 64 with 64 heads runs their wide
+    form)."""
     from ds41rt_b200.ops import lib
     from ds41rt_b200.ops import attention as A
-    if impl == "tc_split_d" and D != 512:
-        pytest.skip("one accumulator already holds a 128-wide row")
     from ds41rt_b200.config import RopeConfig, rope_inv_freq
     from ds41rt_b200.models.reference import apply_rope
     k = lib.kernels()
