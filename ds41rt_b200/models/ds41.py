@@ -67,6 +67,14 @@ class LayerWeights:
     w2: torch.Tensor = None             # [E_local, H, I]
     w13_sf: Optional[torch.Tensor] = None   # MX experts: scale atoms [E_local, 2I/128, H/128, 512]
     w2_sf: Optional[torch.Tensor] = None    # [E_local, H/128, I/128, 512]
+    # unsharded attention / shared-expert weights for sequence-parallel long passes (world > 1); where the layouts
+    # allow it the rank's shards above are views of these
+    w_qb_full: Optional[torch.Tensor] = None       # [n_heads*D (+IH*ID), Q]
+    wo_a_full: Optional[torch.Tensor] = None       # [o_groups, o_lora, hpg*D]
+    wo_b_full: Optional[torch.Tensor] = None       # [H, o_groups*o_lora]
+    sink_full: Optional[torch.Tensor] = None       # [n_heads]
+    w_gate_full: Optional[torch.Tensor] = None     # [E + 2*I, H]
+    w2_sh_full: Optional[torch.Tensor] = None      # [H, I]
     n_experts: int = 0
     topk: int = 0
     extra_cols: int = 0
@@ -163,9 +171,11 @@ class EngineWeights:
     def from_fp32(cfg: ModelConfig, w: Dict[str, torch.Tensor], rank: int, world: int, device,
                   prefix: str = "layers", n_layers: Optional[int] = None, n_experts: Optional[int] = None,
                   topk: Optional[int] = None, expert_dtype: str = "bf16", share: Optional["EngineWeights"] = None,
-                  layer_range: Optional[tuple] = None) -> "EngineWeights":
+                  layer_range: Optional[tuple] = None, full_dense: bool = True) -> "EngineWeights":
         """Build one rank's shard from an fp32 name->tensor dict.  expert_dtype "mxfp8" stores routed
-        experts as E4M3 with power-of-two 128x128 block scales (consumed by the block-scaled GEMM)."""
+        experts as E4M3 with power-of-two 128x128 block scales (consumed by the block-scaled GEMM).
+        full_dense (world > 1): also keep the unsharded attention / shared-expert weights, which the sequence-parallel
+        long pass multiplies against its own rows (about 0.3 GB per Flash layer in bf16)."""
         ew = EngineWeights(cfg, rank, world, device)
         ew.expert_dtype = expert_dtype
         D, H = cfg.head_dim, cfg.hidden
@@ -223,14 +233,30 @@ class EngineWeights:
                 qb.append(w[f"{p}.attn.indexer.wq_b.weight"])
             lw.w_qb = dev(torch.cat(qb, 0))
             wo_a = w[f"{p}.attn.wo_a.weight"].view(cfg.o_groups, cfg.o_lora, cfg.heads_per_group * D)
-            lw.wo_a = dev(wo_a[g0:g1])
-            lw.wo_b = dev(w[f"{p}.attn.wo_b.weight"][:, g0 * cfg.o_lora:g1 * cfg.o_lora])
-            lw.sink = dev(w[f"{p}.attn.attn_sink"][h0:h1], F32)
             i0, i1 = rank * ew.I_sh, (rank + 1) * ew.I_sh
+            if world > 1 and full_dense:
+                lw.w_qb_full = dev(torch.cat([w[f"{p}.attn.wq_b.weight"]] + qb[1:], 0))
+                lw.wo_a_full = dev(wo_a)
+                lw.wo_b_full = dev(w[f"{p}.attn.wo_b.weight"])
+                lw.sink_full = dev(w[f"{p}.attn.attn_sink"], F32)
+                lw.w_gate_full = dev(torch.cat([w[f"{p}.ffn.gate.weight"], w[f"{p}.ffn.shared_experts.w1.weight"],
+                                                w[f"{p}.ffn.shared_experts.w3.weight"]], 0))
+                lw.w2_sh_full = dev(w[f"{p}.ffn.shared_experts.w2.weight"])
+                lw.wo_a = lw.wo_a_full[g0:g1]
+                lw.wo_b = lw.wo_b_full[:, g0 * cfg.o_lora:g1 * cfg.o_lora]
+                lw.sink = lw.sink_full[h0:h1]
+                lw.w2_sh = lw.w2_sh_full[:, i0:i1]
+            else:
+                lw.wo_a = dev(wo_a[g0:g1])
+                lw.wo_b = dev(w[f"{p}.attn.wo_b.weight"][:, g0 * cfg.o_lora:g1 * cfg.o_lora])
+                lw.sink = dev(w[f"{p}.attn.attn_sink"][h0:h1], F32)
+                lw.w2_sh = dev(w[f"{p}.ffn.shared_experts.w2.weight"][:, i0:i1])
             lw.w_gate_sh = dev(torch.cat([w[f"{p}.ffn.gate.weight"], w[f"{p}.ffn.shared_experts.w1.weight"][i0:i1],
                                           w[f"{p}.ffn.shared_experts.w3.weight"][i0:i1]], 0))
             lw.gate_bias = dev(w[f"{p}.ffn.gate.bias"], F32)
-            lw.w2_sh = dev(w[f"{p}.ffn.shared_experts.w2.weight"][:, i0:i1])
+            if world == 1:
+                lw.w_qb_full, lw.wo_a_full, lw.wo_b_full, lw.sink_full = lw.w_qb, lw.wo_a, lw.wo_b, lw.sink
+                lw.w_gate_full, lw.w2_sh_full = lw.w_gate_sh, lw.w2_sh
             e0 = rank * EL
             w13 = torch.stack([torch.cat([w[f"{p}.ffn.experts.{e}.w1.weight"],
                                           w[f"{p}.ffn.experts.{e}.w3.weight"]], 0) for e in range(e0, e0 + EL)], 0)
@@ -252,7 +278,8 @@ class EngineWeights:
     @staticmethod
     def random(cfg: ModelConfig, rank: int, world: int, device, seed: int = 0, std: float = 0.02,
                router_std: Optional[float] = None, expert_dtype: str = "bf16",
-               share: Optional["EngineWeights"] = None, layer_range: Optional[tuple] = None) -> "EngineWeights":
+               share: Optional["EngineWeights"] = None, layer_range: Optional[tuple] = None,
+               full_dense: bool = True) -> "EngineWeights":
         """Random-init shard generated directly on the device (for models too large to stage on the host).
         expert_dtype "mxfp8": E4M3 payloads ~ N(0, 48^2) with every 128x128 block scale 2^-11 (dequantised
         std 0.0234), the statistics an amax-scaled quantisation of N(0, 0.02) weights produces."""
@@ -303,16 +330,40 @@ class EngineWeights:
             lw.extra_cols = extra
             lw.w_qkv = rnd((Q + D + extra, H), shared_gen)
             lw.q_norm, lw.kv_norm = ones(Q), ones(D)
-            nqb = ew.HL * D + (cfg.index_heads * cfg.index_dim if l in cfg.index_layers else 0)
-            lw.w_qb = rnd((nqb, Q))
-            lw.wo_a = rnd((ew.GL, cfg.o_lora, cfg.heads_per_group * D))
-            lw.wo_b = rnd((H, ew.GL * cfg.o_lora))
-            lw.sink = rnd((ew.HL,), gen, 0.5, F32)
-            lw.w_gate_sh = rnd((cfg.n_experts + 2 * ew.I_sh, H), shared_gen)
-            if router_std is not None:
-                lw.w_gate_sh[:cfg.n_experts] = rnd((cfg.n_experts, H), shared_gen, router_std / math.sqrt(H) * 1.0)
+            n_idx = cfg.index_heads * cfg.index_dim if l in cfg.index_layers else 0
+            E_g, I_all = cfg.n_experts, cfg.inter
+            if world > 1 and full_dense:
+                # the same unsharded tensors on every rank (replicated generator); the rank's shards are slices of them
+                lw.w_qb_full = rnd((cfg.n_heads * D + n_idx, Q), shared_gen)
+                lw.w_qb = torch.cat([lw.w_qb_full[rank * ew.HL * D:(rank + 1) * ew.HL * D],
+                                     lw.w_qb_full[cfg.n_heads * D:]], 0).contiguous()
+                lw.wo_a_full = rnd((cfg.o_groups, cfg.o_lora, cfg.heads_per_group * D), shared_gen)
+                lw.wo_b_full = rnd((H, cfg.o_groups * cfg.o_lora), shared_gen)
+                lw.sink_full = rnd((cfg.n_heads,), shared_gen, 0.5, F32)
+                lw.w_gate_full = rnd((E_g + 2 * I_all, H), shared_gen)
+                if router_std is not None:
+                    lw.w_gate_full[:E_g] = rnd((E_g, H), shared_gen, router_std / math.sqrt(H) * 1.0)
+                lw.w2_sh_full = rnd((H, I_all), shared_gen)
+                i0, i1 = rank * ew.I_sh, (rank + 1) * ew.I_sh
+                lw.wo_a = lw.wo_a_full[rank * ew.GL:(rank + 1) * ew.GL]
+                lw.wo_b = lw.wo_b_full[:, rank * ew.GL * cfg.o_lora:(rank + 1) * ew.GL * cfg.o_lora]
+                lw.sink = lw.sink_full[rank * ew.HL:(rank + 1) * ew.HL]
+                lw.w_gate_sh = torch.cat([lw.w_gate_full[:E_g], lw.w_gate_full[E_g + i0:E_g + i1],
+                                          lw.w_gate_full[E_g + I_all + i0:E_g + I_all + i1]], 0).contiguous()
+                lw.w2_sh = lw.w2_sh_full[:, i0:i1]
+            else:
+                lw.w_qb = rnd((ew.HL * D + n_idx, Q))
+                lw.wo_a = rnd((ew.GL, cfg.o_lora, cfg.heads_per_group * D))
+                lw.wo_b = rnd((H, ew.GL * cfg.o_lora))
+                lw.sink = rnd((ew.HL,), gen, 0.5, F32)
+                lw.w_gate_sh = rnd((cfg.n_experts + 2 * ew.I_sh, H), shared_gen)
+                if router_std is not None:
+                    lw.w_gate_sh[:cfg.n_experts] = rnd((cfg.n_experts, H), shared_gen, router_std / math.sqrt(H) * 1.0)
+                lw.w2_sh = rnd((H, ew.I_sh))
+                if world == 1:
+                    lw.w_qb_full, lw.wo_a_full, lw.wo_b_full, lw.sink_full = lw.w_qb, lw.wo_a, lw.wo_b, lw.sink
+                    lw.w_gate_full, lw.w2_sh_full = lw.w_gate_sh, lw.w2_sh
             lw.gate_bias = rnd((cfg.n_experts,), shared_gen, 0.01, F32)
-            lw.w2_sh = rnd((H, ew.I_sh))
             if expert_dtype == "mxfp8":
                 def rnd8(shape):
                     out = torch.empty(shape, dtype=torch.float8_e4m3fn, device=device)
@@ -368,15 +419,17 @@ class EngineWeights:
         return ew
 
     def nbytes(self) -> int:
-        total = 0
-        for t in [self.embed, self.head, self.final_norm]:
-            total += t.numel() * t.element_size()
+        """Bytes held by this rank (a storage shared by a tensor and its views counts once)."""
+        seen, total = set(), 0
+        ts = [self.embed, self.head, self.final_norm]
         for lw in self.layers:
-            if lw is None:
-                continue
-            for v in vars(lw).values():
-                if isinstance(v, torch.Tensor):
-                    total += v.numel() * v.element_size()
+            if lw is not None:
+                ts += [v for v in vars(lw).values() if isinstance(v, torch.Tensor)]
+        for t in ts:
+            st = t.untyped_storage()
+            if st.data_ptr() not in seen:
+                seen.add(st.data_ptr())
+                total += st.nbytes()
         return total
 
 
@@ -572,7 +625,17 @@ class KVCache:
 class DS41Engine:
     def __init__(self, cfg: ModelConfig, weights: EngineWeights, fabric: Optional[Fabric] = None, *,
                  max_rows: int = 8, slots: int = 1, max_ctx: int = 4096, page_tokens: int = 64,
-                 n_pages: Optional[int] = None, row_hi: bool = False, moe_rows: int = 32, kv_dtype: str = "bf16"):
+                 n_pages: Optional[int] = None, row_hi: bool = False, moe_rows: int = 32, kv_dtype: str = "bf16",
+                 long_pass: str = "auto"):
+        """long_pass: how passes longer than `moe_rows` rows run on several ranks.  "sp" (sequence parallel): every rank
+        owns rows/world rows of the residual streams; hyper-connections, q_b, indexer, attention over all heads, wo_a /
+        wo_b, router and shared expert run on the own rows against unsharded weights, the normalised rows are
+        all-gathered inside the q_a / kv projection (every rank writes every cache row) and the routed experts go
+        through the all-to-all.  "replicated": every rank holds all rows, heads and shared expert are sharded and the
+        partial planes are summed by peer reads.  "auto": "sp" where a pass allows it (rows a multiple of 128 x world,
+        unsharded weights present, no Engram layer live), else "replicated"."""
+        assert long_pass in ("auto", "sp", "replicated")
+        self.long_pass = long_pass
         self.cfg, self.w = cfg, weights
         self.fabric = fabric or Fabric.single(weights.device)
         self.rank, self.world = self.fabric.rank, self.fabric.world
@@ -732,6 +795,10 @@ class DS41Engine:
         if R > self.moe_rows and live:
             self._make_ep(live[0])
         self.debug = None   # set to a list to record per-layer routing / selection decisions
+        self._sp = None           # buffers of the sequence-parallel long pass (made on first use)
+        self._sp_ag = {}          # rows per rank -> all-gather context of the q_a / kv projection
+        self._sp_active = None    # (first own row, own rows, rows) while the streams are row-sharded
+        self._sp_pending = None   # (plane address, splits, split stride) of the own rows' unmerged sublayer
 
     # ------------------------------------------------------------------ helpers
     def _inv(self, layer: int) -> torch.Tensor:
@@ -939,7 +1006,8 @@ class DS41Engine:
                 -self.cache.comp_row_bytes if self.cache.comp_row_bytes else self.cache.row_bytes, st())
 
     def forward_rows(self, rows: int, *, embed: bool = True, head: bool = True, first_layer: int = 0,
-                     last_layer: Optional[int] = None, sources: bool = True, pending=None):
+                     last_layer: Optional[int] = None, sources: bool = True, pending=None,
+                     head_row: Optional[int] = None):
         """One pass over `rows` rows described by set_rows().  `first_layer` / `last_layer` run a slice of the stack
         (the streams and the pending sublayer carry over between slices); `sources=False` leaves the compressed
         sources untouched (decoder replay of a prompt's tail)."""
@@ -949,6 +1017,11 @@ class DS41Engine:
         last_layer = self.n_layers if last_layer is None else last_layer
         if first_layer == 0:
             self._cand_ratio = None
+        if pending is None and self.sp_ready(R) and (embed or self._sp_active is not None):
+            return self._forward_rows_sp(R, embed=embed, head=head, first_layer=first_layer, last_layer=last_layer,
+                                         sources=sources, head_row=head_row)
+        assert self._sp_active is None or embed, "a row-sharded pass cannot continue replicated"
+        self._sp_active = None
         if embed:
             self._cur, self._ccur = 0, 0
             self._run("embed", k.ds41_embed_streams, lib.ptr(self.in_tokens), lib.ptr(self.w.embed), lib.ptr(self.streams),
@@ -1127,7 +1200,273 @@ class DS41Engine:
         self._pending = pending
         self._pass_hint = None
         if head:
-            self.head_rows(R)
+            self.head_rows(R if head_row is None else head_row + 1)
+
+
+    # ------------------------------------------------------------------ sequence-parallel long passes
+    def sp_ready(self, rows: int) -> bool:
+        """Can a pass of `rows` rows run row-sharded (see `long_pass` in the constructor)?"""
+        if self.long_pass == "replicated" or rows <= self.moe_rows or self._engram_live:
+            return False
+        if self.world == 1 and self.long_pass != "sp":
+            return False
+        lw = self._lw_any
+        return rows % (128 * self.world) == 0 and lw is not None and lw.w_qb_full is not None \
+            and self.cfg.n_heads <= 64
+
+    def sp_rows(self, n: int) -> int:
+        """Rows to run for a chunk of n real rows: padded up to the row-sharded granularity when that fits."""
+        g = 128 * self.world
+        padded = (n + g - 1) // g * g
+        return padded if padded <= self.max_rows and self.sp_ready(padded) else n
+
+    def _sp_buffers(self, Rl: int):
+        cfg, dev = self.cfg, self.device
+        if self._sp is not None and self._sp["Rl"] >= Rl:
+            return self._sp
+        z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=dev)
+        D, NH = cfg.head_dim, cfg.n_heads
+        nqb = NH * D + cfg.index_heads * cfg.index_dim
+        splits = max(1, min(self.n_splits_attn, -(-2 * 148 // Rl)))
+        ng = self.E + 2 * cfg.inter
+        self._sp = dict(
+            Rl=Rl, nqb=nqb, qb=z((Rl, nqb), BF16), attn=z((Rl, NH * D), BF16), oa=z((Rl, cfg.o_groups * cfg.o_lora), BF16),
+            # the tensor-core kernel writes final rows when it has one split; the warp-MMA kernels always go through
+            # partials
+            part_o=z((Rl * splits if splits > 1 or not A.tc_usable(D, NH, Rl) else 1, NH, D), F32),
+            part_ml=z((Rl * splits, NH, 2), F32),
+            planes_o=z((self.max_splits * Rl * cfg.hidden,), F32), planes_gate=z((self.max_splits * Rl * ng,), F32),
+            shared_act=z((Rl, cfg.inter), BF16), planes_shared=z((self.max_splits * Rl * cfg.hidden,), F32),
+            xn_last=z((1, cfg.hidden), BF16))
+        return self._sp
+
+    def _sp_gather_ctx(self, Rl: int):
+        """Symmetric buffers of the fused all-gather -> GEMM for `Rl` rows per rank: two alternating copies of the
+        gathered [world * Rl, H] matrix, arrival counters per (source, 128-row tile) and a private call counter."""
+        ctx = self._sp_ag.get(Rl)
+        if ctx is None:
+            from ..parallel.tp import SyncFlags
+            W, H = self.world, self.cfg.hidden
+            full = W * Rl * H * 2
+            x_sym = self.fabric.alloc(2 * full)
+            ctx = dict(x_sym=x_sym, full=full, parity=0, calls=SyncFlags(self.fabric),
+                       arrive=self.fabric.alloc(4 * W * (Rl // 128)),
+                       views=[x_sym.view(BF16, (W * Rl, H), i * full) for i in range(2)])
+            self._sp_ag[Rl] = ctx
+        return ctx
+
+    def _sp_hc(self, lo, Rl, pending, fn, scale, base, norm_w, xn_out, tap=None):
+        """Own rows [lo, lo + Rl): close the pending sublayer (its planes are local and complete) and open the next
+        one; the normalised rows go to `xn_out` ([Rl, H] bf16)."""
+        cfg, cur = self.cfg, self._cur
+        bases, n_splits, stride = pending if pending is not None else (None, 0, 0)
+        ptrs = (C.c_void_p * 1)(bases) if bases is not None else None
+        streams = self.streams[lo:]
+        self._run("hc_post_mix", self.k.ds41_hc_post_mix, lib.ptr(streams), lib.ptr(streams), ptrs,
+                  1 if bases is not None else 0, n_splits, C.c_longlong(stride), lib.ptr(self.post[lo:]),
+                  lib.ptr(self.comb[lo:]), lib.ptr(fn), lib.ptr(self.hc_partial), Rl, cfg.hidden, lib.ptr(None),
+                  lib.ptr(self.epoch), lib.ptr(self.status), lib.stream())
+        self._run("hc_finish", self.k.ds41_hc_finish, lib.ptr(self.hc_partial), self.n_slices, lib.ptr(scale),
+                  lib.ptr(base), lib.ptr(self.pre[cur][lo:]), lib.ptr(streams), lib.ptr(norm_w),
+                  lib.ptr(self.pre[cur ^ 1][lo:]), lib.ptr(self.post[lo:]), lib.ptr(self.comb[lo:]), lib.ptr(xn_out),
+                  lib.ptr(tap[lo:] if tap is not None else None), lib.ptr(None), lib.ptr(None), Rl, cfg.hidden,
+                  cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps), C.c_float(cfg.norm_eps), lib.stream())
+        self._cur = cur ^ 1
+
+    def _sp_qkv(self, l, lw, R, Rl, inv, sources, ctx):
+        """q_a / kv / extras of every row on every rank: the own normalised rows (already written into the gathered
+        matrix) are pushed to the peers inside the GEMM kernel, which multiplies remote row tiles as they arrive."""
+        cfg, k, W = self.cfg, self.k, self.world
+        H, D, Q = cfg.hidden, cfg.head_dim, cfg.q_lora
+        ntot = lw.w_qkv.shape[0]
+        planes = self.planes_qkv.view(-1)[: R * ntot].view(R, ntot)
+        xfull = ctx["views"][ctx["parity"]]
+        if W == 1:
+            self._run("gemm_qkv", G.gemm_raw, xfull, lw.w_qkv, planes, R, ntot, H, lda=H, ldb=H, ldo=ntot, out_mode=1,
+                      bn=256, status=self.status, static_operand=2)
+        else:
+            ctx["calls"].signal()
+            a = lib.GemmArgs()
+            a.B, a.out, a.status = lib.ptr(lw.w_qkv), lib.ptr(planes), lib.ptr(self.status)
+            a.lda, a.ldb, a.ldo = H, lw.w_qkv.stride(0), ntot
+            a.M, a.N, a.K, a.batch = R, ntot, H, 1
+            a.kind, a.out_mode, a.k_splits, a.bn = 0, 1, 1, 256
+            a.static_operand = 2
+            a.ag_world, a.ag_rank, a.ag_rows = W, self.rank, Rl
+            for r in range(W):
+                a.a_peers[r] = ctx["x_sym"].peer_ptrs[r] + ctx["parity"] * ctx["full"]
+                a.ag_arrive[r] = ctx["arrive"].peer_ptrs[r]
+            a.ag_epoch = lib.ptr(ctx["calls"].epoch)
+            self._run("gemm_qkv", lambda: lib.kernels().ds41_gemm_tc(C.byref(a), lib.stream()))
+        ctx["parity"] ^= 1
+        self._run("qkv_post", k.ds41_qkv_post, lib.ptr(planes), 1, R, ntot, Q, D, cfg.rope_dim, lw.extra_cols,
+                  lw.index_heads_cols, C.c_float(cfg.index_weight_scale), lib.ptr(lw.q_norm), lib.ptr(lw.kv_norm),
+                  lib.ptr(inv), lib.ptr(self.row_pos), lib.ptr(self.row_slot), lib.ptr(self.q_lat),
+                  lib.ptr(self.cache.win[l]), self.cache.ring, lib.ptr(self.extras), C.c_float(cfg.norm_eps),
+                  self.cache.row_bytes, lib.stream())
+        if lw.ratio and sources:
+            self._run("compress", k.ds41_compress, lib.ptr(self.extras), lw.extra_cols, R, D, cfg.index_dim,
+                      cfg.rope_dim, lw.ratio, lib.ptr(self.row_pos), lib.ptr(self.row_slot),
+                      lib.ptr(self.cache.pending.get(l)), lib.ptr(lw.comp_norm), lib.ptr(lw.wk_idx), lib.ptr(lw.k_norm),
+                      lib.ptr(inv), lib.ptr(self.inv_idx), lib.ptr(self.cache.page_table), self.cache.max_pages,
+                      self.cache.page_rows[l], lib.ptr(self.cache.comp[l]), lib.ptr(self.cache.idx[l]),
+                      C.c_float(cfg.norm_eps),
+                      -self.cache.comp_row_bytes if self.cache.comp_row_bytes else self.cache.row_bytes, lib.stream())
+
+    def _forward_rows_sp(self, R, *, embed, head, first_layer, last_layer, sources, head_row):
+        cfg, k, st = self.cfg, self.k, lib.stream
+        H, D, Q, W = cfg.hidden, cfg.head_dim, cfg.q_lora, self.world
+        Rl = R // W
+        lo = self.rank * Rl
+        sp = self._sp_buffers(Rl)
+        ctx = self._sp_gather_ctx(Rl)
+        NH, nqb = cfg.n_heads, sp["nqb"]
+        pos, slot = self.row_pos[lo:], self.row_slot[lo:]
+        if embed:
+            self._cur, self._ccur = 0, 0
+            self._run("embed", k.ds41_embed_streams, lib.ptr(self.in_tokens), lib.ptr(self.w.embed),
+                      lib.ptr(self.streams), lib.ptr(self.pre[0]), R, H, cfg.hc_mult, cfg.vocab, st())
+            if self.image_patch is not None:
+                img_rows, img_ids = self.image_patch
+                self._run("image_rows", k.ds41_vis_scatter, lib.ptr(img_rows), lib.ptr(img_ids), lib.ptr(self.streams),
+                          img_rows.shape[0], H, cfg.hc_mult, st())
+            self._sp_pending = None
+        self._sp_active = (lo, Rl, R)
+        pending = self._sp_pending
+        if self.layer_timer is not None:
+            self.layer_timer.begin()
+        attn_splits = max(1, min(self.n_splits_attn, -(-2 * 148 // Rl)))
+        for l in range(first_layer, last_layer):
+            lw = self.w.layers[l]
+            inv = self._inv(l)
+            tap = None
+            if self.taps is not None and cfg.dspark is not None and not self.layer_prefix_plain \
+                    and l in cfg.dspark.tap_layers:
+                tap_i = cfg.dspark.tap_layers.index(l)
+                tap = self.taps[tap_i] if tap_i < self.taps.shape[0] else None
+            # ---------------- attention sublayer
+            xfull = ctx["views"][ctx["parity"]]
+            self._sp_hc(lo, Rl, pending, lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, lw.attn_norm, xfull[lo:],
+                        tap=tap)
+            self._sp_qkv(l, lw, R, Rl, inv, sources, ctx)
+            src = None if self.layer_prefix_plain else cfg.source_of(l)
+            nq = lw.w_qb_full.shape[0]
+            self._run("gemm_qb", G.gemm_raw, lw.w_qb_full, self.q_lat[lo:], sp["qb"], nq, Rl, Q, lda=Q, ldb=Q, ldo=nqb,
+                      out_mode=2, status=self.status, static_operand=1)
+            if lw.index_heads_cols and src is not None:
+                ratio = cfg.source_layers[src]
+                restrict = self.cand_on and l > cfg.candidate_layer and self._cand_ratio == ratio
+                cand = (lib.ptr(self.cand_mask[lo:]), self.cand_words, cfg.candidate_block) if restrict \
+                    else (lib.ptr(None), 0, 0)
+                hint = self._pass_hint        # rows beyond the hinted count are padding (slot -1: no visible key)
+                n_keys = min((hint[1] + 1) // ratio, self.max_keys) if hint is not None and hint[0] <= R else 0
+                scores = self.scores[lo:]
+                if n_keys >= 64 and cfg.index_heads == 32 and cfg.index_dim % 64 == 0:
+                    self._run("index_prepare", k.ds41_index_prepare, lib.ptr(sp["qb"]), C.c_longlong(nqb), NH * D,
+                              lib.ptr(self.cache.idx[src]), lib.ptr(self.cache.page_table), self.cache.max_pages,
+                              self.cache.page_rows[src], lib.ptr(pos), lib.ptr(slot), lib.ptr(self.inv_idx), Rl,
+                              cfg.index_heads, cfg.index_dim, ratio, n_keys, self.max_keys, lib.ptr(self.idx_q),
+                              lib.ptr(self.idx_k), lib.ptr(self.idx_vis), st())
+                    w_off = lw.extra_cols - cfg.index_heads
+                    self._run("index_score_gemm", G.gemm_raw, self.idx_q, self.idx_k, scores, Rl * cfg.index_heads,
+                              n_keys, cfg.index_dim, lda=cfg.index_dim, ldb=cfg.index_dim, ldo=self.max_keys,
+                              out_mode=8, bn=256 if n_keys >= 256 else 64, row_w=self.extras[lo:, w_off:],
+                              row_w_ld=lw.extra_cols, col_limit=self.idx_vis, status=self.status)
+                else:
+                    self._run("index_score", k.ds41_index_score_cand, lib.ptr(sp["qb"]), C.c_longlong(nqb), NH * D,
+                              lib.ptr(self.extras[lo:]), lw.extra_cols, lw.extra_cols - cfg.index_heads,
+                              lib.ptr(self.cache.idx[src]), lib.ptr(self.cache.page_table), self.cache.max_pages,
+                              self.cache.page_rows[src], lib.ptr(pos), lib.ptr(slot), lib.ptr(self.inv_idx), Rl,
+                              cfg.index_heads, cfg.index_dim, ratio, lib.ptr(scores), self.max_keys, *cand, st())
+                if self.cand_on and l == cfg.candidate_layer:
+                    self._run("candidate_select", k.ds41_candidate_select, lib.ptr(scores), self.max_keys, lib.ptr(pos),
+                              lib.ptr(slot), ratio, cfg.candidate_block, cfg.candidate_topk_blocks,
+                              lib.ptr(self.cand_blocks[lo:]), lib.ptr(self.cand_count[lo:]),
+                              lib.ptr(self.cand_mask[lo:]), self.cand_words, Rl, st())
+                    self._cand_ratio = ratio
+                self._run("topk", k.ds41_topk_select_cand, lib.ptr(scores), self.max_keys, lib.ptr(pos), lib.ptr(slot),
+                          ratio, cfg.index_topk, lib.ptr(self.sel[lo:]), lib.ptr(self.n_sel[lo:]), Rl, *cand, st())
+            self._run("attend", A.attend, q=sp["qb"], ldq=nqb, q_off=0, rows=Rl, heads=NH, D=D, window=cfg.window,
+                      ring=self.cache.ring, row_pos=pos, row_slot=slot, win=self.cache.win[l],
+                      comp_pool=self.cache.comp[src] if src is not None else None, sel=self.sel[lo:],
+                      n_sel=self.n_sel[lo:], k=cfg.index_topk, page_table=self.cache.page_table,
+                      max_pages=self.cache.max_pages, page_rows=self.cache.page_rows[src] if src is not None else 1,
+                      inv_freq=inv, rope_dim=cfg.rope_dim, scale=cfg.softmax_scale, n_splits=attn_splits,
+                      part_o=sp["part_o"], part_ml=sp["part_ml"], sink=lw.sink_full, out=sp["attn"], ldo=NH * D,
+                      kv_row_bytes=self.cache.row_bytes, comp_row_bytes=self.cache.comp_row_bytes,
+                      row_hi=self.row_hi[lo:] if self.row_hi is not None else None,
+                      row_lo=self.row_lo[lo:] if self._floor_on else None, status=self.status)
+            kg = cfg.heads_per_group * D
+            ko = cfg.o_groups * cfg.o_lora
+            self._run("gemm_wo_a", G.gemm_raw, lw.wo_a_full, sp["attn"], sp["oa"], cfg.o_lora, Rl, kg, lda=kg,
+                      ldb=NH * D, ldo=ko, out_mode=2, batch=cfg.o_groups, a_batch_stride=cfg.o_lora * kg,
+                      b_batch_stride=kg, out_batch_stride=cfg.o_lora, status=self.status, static_operand=1)
+            s_o = self._splits(H, ko, Rl)
+            planes_o = sp["planes_o"][: s_o * Rl * H].view(s_o, Rl, H)
+            self._run("gemm_wo_b", G.linear_planes, sp["oa"][:Rl], lw.wo_b_full, planes_o, s_o, status=self.status)
+            pending = (planes_o.data_ptr(), s_o, Rl * H)
+            # ---------------- MoE sublayer: router and shared expert on the own rows, routed experts by all-to-all
+            xn = self.xn[lo:lo + Rl]
+            self._sp_hc(lo, Rl, pending, lw.hc_ffn_fn, lw.hc_ffn_scale, lw.hc_ffn_base, lw.ffn_norm, xn)
+            ng = lw.w_gate_full.shape[0]
+            I_all = (ng - lw.n_experts) // 2
+            s_g = self._splits(ng, H, Rl)
+            planes_g = sp["planes_gate"][: s_g * Rl * ng].view(s_g, Rl, ng)
+            self._run("gemm_gate", G.linear_planes, xn, lw.w_gate_full, planes_g, s_g, status=self.status)
+            self._run("router_select", k.ds41_router_select, lib.ptr(planes_g), s_g, Rl, ng, lw.n_experts, I_all,
+                      lw.topk, lib.ptr(lw.gate_bias), C.c_float(cfg.route_scale), C.c_float(cfg.swiglu_limit),
+                      lib.ptr(self.ids[lo:]), lib.ptr(self.route_w[lo:]), lib.ptr(sp["shared_act"]), st())
+            if self.debug is not None:
+                self.debug.append({"layer": l, "ids": self.ids[lo:lo + Rl].clone(), "sel": self.sel[lo:lo + Rl].clone(),
+                                   "n_sel": self.n_sel[lo:lo + Rl].clone(), "rows": (lo, lo + Rl)})
+            s_s = self._splits(H, I_all, Rl)
+            planes_s = sp["planes_shared"][: s_s * Rl * H].view(s_s, Rl, H)
+            self._run("gemm_shared_down", G.linear_planes, sp["shared_act"][:Rl], lw.w2_sh_full, planes_s, s_s,
+                      status=self.status)
+            moe_rows = self.moe_plane[lo:lo + Rl]
+            self._run("reduce_planes", k.ds41_reduce_planes, lib.ptr(planes_s), s_s, C.c_longlong(Rl * H),
+                      lib.ptr(moe_rows), 0, C.c_longlong(Rl * H), st())
+            if self._ep is None:
+                self._make_ep(lw)
+            ep = self._ep
+            ep.set_weights(lw.w13, lw.w2, getattr(lw, "w13_sf", None), getattr(lw, "w2_sf", None),
+                           getattr(lw, "w13_gs", None), getattr(lw, "w2_gs", None))
+            if self.only is None or "ep_moe" in self.only:
+                self.launches += 7
+                self._run("ep_moe", ep.forward, xn, self.ids[lo:lo + Rl], self.route_w[lo:lo + Rl], moe_rows, moe_rows)
+            pending = (moe_rows.data_ptr(), 1, 0)
+            if self.layer_timer is not None:
+                self.layer_timer.mark()
+            if self.activation_trace is not None:
+                self.activation_trace.dump(l, self.streams, self.row_pos, R)
+        self._sp_pending = pending
+        self._pending = None
+        self._pass_hint = None
+        if head:
+            self.head_rows(R if head_row is None else head_row + 1)
+
+    def _sp_close(self, fn, scale, base, norm_w):
+        """Merge the pending sublayer of a row-sharded pass and normalise: own rows of self.xn are valid afterwards."""
+        lo, Rl, R = self._sp_active
+        self._sp_hc(lo, Rl, self._sp_pending, fn, scale, base, norm_w, self.xn[lo:lo + Rl])
+        self._sp_pending = None
+
+    def _sp_head(self, rows: int):
+        """Head of a row-sharded pass: the owner of row rows - 1 hands its normalised row to every rank (one H-wide
+        broadcast), then the vocabulary shards are multiplied as usual; the logits land in row 0."""
+        lo, Rl, R = self._sp_active
+        lw0 = self._lw_any
+        self._sp_close(lw0.hc_attn_fn, lw0.hc_attn_scale, lw0.hc_attn_base, self.w.final_norm)
+        last = rows - 1
+        row = self._sp["xn_last"]
+        owner = last // Rl
+        if owner == self.rank:
+            row.copy_(self.xn[last:last + 1])
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.broadcast(row, src=owner, group=self.fabric.group)
+        self._sp_active = None
+        return row
 
     def _make_ep(self, lw: LayerWeights):
         from ..parallel.ep import ExpertParallelMoE
@@ -1163,10 +1502,13 @@ class DS41Engine:
         """collapse -> final norm -> vocabulary shard GEMM -> greedy candidate (+ cross-rank merge)."""
         cfg, k, st = self.cfg, self.k, lib.stream
         lw0 = self._lw_any
-        self._hc(rows, getattr(self, "_pending", None), lw0.hc_attn_fn, lw0.hc_attn_scale, lw0.hc_attn_base,
-                 self.w.final_norm)
-        self._pending = None
-        xn = self.xn
+        if self._sp_active is not None:
+            xn, rows = self._sp_head(rows), 1
+        else:
+            self._hc(rows, getattr(self, "_pending", None), lw0.hc_attn_fn, lw0.hc_attn_scale, lw0.hc_attn_base,
+                     self.w.final_norm)
+            self._pending = None
+            xn = self.xn
         self.last_head_row = rows - 1
         if rows > self.head_cap:
             # a long pass: only its last row continues the sequence; its logits land in row 0
@@ -1220,7 +1562,8 @@ class DS41Engine:
             pos = list(range(start + c0, start + c0 + len(part)))
             self.set_rows(part, pos, [slot] * len(part))
             last = c0 + chunk >= len(tokens)
-            self.forward_rows(self.max_rows if len(part) == self.max_rows else len(part), head=last)
+            # a chunk may run padded up to the row-sharded granularity (the padding rows have no slot)
+            self.forward_rows(self.sp_rows(len(part)), head=last, head_row=len(part) - 1)
             if last:
                 nxt = int(self.chosen[self.last_head_row].item())
         return nxt
@@ -1232,6 +1575,15 @@ class DS41Engine:
         the collapse weights they go with."""
         lw = self.w.layers[layer]
         pre_idx = self._cur
+        if self._sp_active is not None:
+            lo, Rl, R = self._sp_active
+            ctx = self._sp_gather_ctx(Rl)
+            self._sp_hc(lo, Rl, self._sp_pending, lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, lw.attn_norm,
+                        ctx["views"][ctx["parity"]][lo:])
+            self._sp_pending = None
+            if lw.ratio and sources:
+                self._sp_qkv(layer, lw, R, Rl, self._inv(layer), True, ctx)
+            return pre_idx
         self._hc(rows, getattr(self, "_pending", None), lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, lw.attn_norm)
         self._pending = None
         if lw.ratio and sources:
@@ -1287,10 +1639,26 @@ class DS41Engine:
         if getattr(self, "ced_streams", None) is None:
             self.ced_streams = torch.zeros(cfg.ced_replay, cfg.hc_mult, cfg.hidden, dtype=BF16, device=self.device)
             self.ced_pre = torch.zeros(cfg.ced_replay, cfg.hc_mult, dtype=F32, device=self.device)
-        self.forward_rows(m, head=False, last_layer=B, sources=sources)
+        self.forward_rows(self.sp_rows(m), head=False, last_layer=B, sources=sources)
         pre_idx = self.boundary_source(m, B, sources)
         lo = max(c0, r0)
-        if lo < c1:
+        if self._sp_active is not None:
+            # the streams are row-sharded: every rank contributes the kept rows it owns, the sum assembles them
+            own0, Rl, _ = self._sp_active
+            self._sp_active = None
+            if lo < c1:
+                ks, kp = self.ced_streams[lo - r0:c1 - r0], self.ced_pre[lo - r0:c1 - r0]
+                ks.zero_()
+                kp.zero_()
+                a, b = max(lo - c0, own0), min(m, own0 + Rl)
+                if a < b:
+                    ks[a - (lo - c0):b - (lo - c0)].copy_(self.streams[a:b])
+                    kp[a - (lo - c0):b - (lo - c0)].copy_(self.pre[pre_idx][a:b])
+                if self.world > 1:
+                    import torch.distributed as dist
+                    dist.all_reduce(ks, group=self.fabric.group)
+                    dist.all_reduce(kp, group=self.fabric.group)
+        elif lo < c1:
             self.ced_streams[lo - r0:c1 - r0].copy_(self.streams[lo - c0:m])
             self.ced_pre[lo - r0:c1 - r0].copy_(self.pre[pre_idx][lo - c0:m])
 
@@ -1298,7 +1666,7 @@ class DS41Engine:
         """Rows set by set_rows() are prompt positions [c0, c1) of the replayed tail: continue them from the kept
         boundary streams through the layers from the boundary upwards (compressed sources stay as they are)."""
         m = c1 - c0
-        self._cur, self._ccur, self._pending, self._cand_ratio = 0, 0, None, None
+        self._cur, self._ccur, self._pending, self._cand_ratio, self._sp_active = 0, 0, None, None, None
         self.streams[:m].copy_(self.ced_streams[c0 - r0:c1 - r0])
         self.pre[0][:m].copy_(self.ced_pre[c0 - r0:c1 - r0])
         self.forward_rows(m, embed=False, head=head, first_layer=self.cfg.ced_boundary, sources=False)
