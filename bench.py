@@ -1,21 +1,31 @@
 #!/usr/bin/env python
-"""Headline benchmark: C1 decode tokens/s of a DeepSeek-V4.1-Flash-shaped model with dSpark speculative decoding.
+"""Benchmarks of the DeepSeek-V4.1-Flash-shaped engine: C1 decode with dSpark speculative decoding (the default and the
+reference's headline), plain decode, concurrent decode and prompt throughput.
 
-Config (BASELINE.json configs 2 and 5): full Flash architecture, random-init weights, routed experts FP8 E4M3 with
-128x128 power-of-two block scales and 1x128 activation scales, dense/attention weights bf16, EP<N> experts and
-TP<N> attention over N GPUs of one node, a 4096-token random-id prompt.  A dSpark-shaped one-stage drafter that
-shares the target's embedding and head proposes 4 tokens per round; the target verifies the 5-row chunk; acceptance
-follows the fixed schedule "3 of 4 drafts accepted" (random weights make real acceptance meaningless), so every
-round emits 4 tokens.  Where the full model does not fit the N GPUs' memory the model is layer-truncated (the JSON
-line says how many layers ran).  `--no-spec` times plain one-token-per-step greedy decoding instead.
+Default run: full Flash architecture, random-init weights, routed experts FP8 E4M3 with 128x128 power-of-two block
+scales and 1x128 activation scales, dense / attention weights bf16, EP<N> experts and TP<N> attention over N GPUs of
+one node, a 4096-token random-id prompt.  A dSpark-shaped drafter that shares the target's embedding and head proposes
+4 tokens per round; the target verifies the 5-row chunk; acceptance follows the fixed schedule "3 of 4 drafts accepted"
+(random weights make real acceptance meaningless), so every round emits 4 tokens.  Where the 40-layer model does not
+fit the N GPUs' memory the stack is truncated: the metric names the layer count and `vs_baseline` (a ratio against
+the reference's published 40-layer numbers) is then null; `vs_baseline_depth_scaled` is the same ratio with the
+measured tokens/s multiplied by layers / 40.
+
+Presets (`--config`): 2 = target-only C1 decode, 4096-token prompt, 512 greedy tokens; 3 = prompt throughput, 8 prompts
+of 8192 tokens, router logits ~ N(0, 1) (`--skew`: two experts take about a quarter of the routed tokens); 4 = NVFP4
+W4A4 experts, 64 concurrent requests, 2048-token prompts whose first 1024 tokens are one shared prefix restored from a
+snapshot, 1024 output tokens, paged FP8 KV rows; 5 = speculative C1 decode over a 32 K-token context with a per-step
+vocabulary mask on the target's choices.
 
   python bench.py --gpus N --steps K --warmup W          (N > 1: launched by torch.distributed.run)
   python bench.py --impl reference ...                   (prints the reference arm's availability line)
 
-Prints ONE JSON line on rank 0.  `value` is device-timed (CUDA events, max over ranks): K rounds replayed as CUDA
-graphs with the accept rule and next-round inputs computed on the device.  `e2e` is the same metric through the
-public SpecSession.round_host() call: per round the inputs come from pinned host memory and the emitted tokens
-are read back to the host.
+Prints ONE JSON line on rank 0.  `value` is device-timed (CUDA events on the launching stream, barrier and
+synchronize on both sides, max over ranks): K steps replayed as CUDA graphs with the accept rule and the next inputs
+computed on the device.  The K-step measurement is repeated until about two seconds have been timed and the median
+repeat is reported; clocks are sampled over the whole region.  `e2e` is the same metric through the public
+SpecSession.round_host() / DecodeSession.step() call: per step the inputs come from pinned host memory and the
+emitted tokens are read back to the host.
 """
 from __future__ import annotations
 
@@ -33,12 +43,40 @@ BASELINE_TARGET_ONLY = 60.63  # reference README.md:109 (no drafts)
 LAYERS_FOR_GPUS = {1: 10, 2: 22, 4: 40, 8: 40}
 
 
+LAYERS_FULL = 40
+MIN_TIMED_S = 2.0          # the K-step measurement is repeated until this much device time has been measured
+MAX_REPEATS = 64
+
+
 def reference_arm():
-    why = ("pip install of /root/reference fails: \"Directory '/root/reference' is not installable. Neither 'setup.py' "
-           "nor 'pyproject.toml' found.\" - the reference is a Rust/CMake engine whose kernels are AOT-exported for "
+    why = ("pip install of the reference tree fails: \"Directory is not installable. Neither 'setup.py' nor "
+           "'pyproject.toml' found.\" - the reference is a Rust/CMake engine whose kernels are AOT-exported for "
            "SM120/SM121 by absent submodules, and the image has no Rust toolchain")
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
+
+
+def baseline_fields(value: float, base, n_layers: int) -> dict:
+    """Ratios against a published 40-layer number: the plain ratio only for the full stack."""
+    if base is None:
+        return {"vs_baseline": None}
+    full = n_layers >= LAYERS_FULL
+    return {"vs_baseline": round(value / base, 3) if full else None,
+            "vs_baseline_depth_scaled": round(value * min(n_layers, LAYERS_FULL) / LAYERS_FULL / base, 3),
+            "baseline": {"value": base, "layers": LAYERS_FULL,
+                         "note": "vs_baseline_depth_scaled = value x layers / 40 / baseline (per-layer cost taken as "
+                                 "uniform; the head and the drafter are scaled down with it, so it understates)"}}
+
+
+def layers_tag(n_layers: int) -> str:
+    return "" if n_layers >= LAYERS_FULL else f", {n_layers} of {LAYERS_FULL} layers"
+
+
+def timed_repeats(fabric, torch, run_k, est_ms: float, max_repeats: int = MAX_REPEATS):
+    """Repeat the K-step measurement until about MIN_TIMED_S have been timed -> (median ms, all ms)."""
+    reps = max(1, min(max_repeats, int(MIN_TIMED_S * 1e3 / max(est_ms, 1e-3)) + 1))
+    times = [timed(fabric, torch, run_k) for _ in range(reps)]
+    return statistics.median(times), times
 
 
 class ClockSampler:
@@ -110,16 +148,33 @@ def timed(fabric, torch, fn):
 BASELINE_PREFILL = 8355.0     # reference README.md:36 (best prefill, 2 RTX PRO 6000, v6 campaign)
 
 
+def expert_note(dtype: str) -> str:
+    return {"mxfp8": "fp8 e4m3, 128x128 ue8m0 block scales, 1x128 activation scales",
+            "mxfp4": "fp4 e2m1 weights, 1x32 ue8m0 scales (official layout), fp8 e4m3 activations with 1x128 scales",
+            "bf16": "bf16",
+            "nvfp4": "NVFP4 W4A4: e2m1 weights and activations, e4m3 scale per 16, fp32 scale per tensor"}[dtype]
+
+
+def skew_router(weights, cfg, hot: int = 2, bias: float = 0.94):
+    """Push `hot` experts' selection bias up so that they are picked for most tokens (the skewed-load run)."""
+    for lw in weights.layers:
+        if lw is not None:
+            lw.gate_bias[:hot] += bias
+
+
 def prefill_bench(args, fabric, cfg, n_layers):
-    """Prompt throughput: the whole prompt goes through DS41Engine.prefill in passes of --chunk rows (sorted expert
-    path, sparse attention over the window and the selected compressed keys); a step is one whole prompt."""
+    """Prompt throughput: --prompts prompts, each run through DS41Engine.prefill in passes of --chunk rows (sorted expert
+    path, sparse attention over the window and the selected compressed keys); a step is the whole batch of prompts."""
     import torch
     from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
     world, rank, dev = fabric.world, fabric.rank, fabric.device
     W, K = max(args.warmup, 3), args.steps
     t0 = time.time()
-    weights = EngineWeights.random(cfg, rank, world, dev, seed=0, expert_dtype=args.expert_dtype)
-    P = args.prompt
+    weights = EngineWeights.random(cfg, rank, world, dev, seed=0, expert_dtype=args.expert_dtype,
+                                   router_std=args.router_std)
+    if args.skew:
+        skew_router(weights, cfg)
+    P, NP = args.prompt, args.prompts
     if args.ced:
         # encoder / decoder-replay prompt passes: the boundary is the model's own (layer 20 of 40); a truncated stack
         # keeps the same half-and-half split if it still has no compressed source above it
@@ -128,20 +183,38 @@ def prefill_bench(args, fabric, cfg, n_layers):
             cfg = dataclasses.replace(cfg, ced_boundary=args.ced_boundary or max(cfg.source_layers, default=0))
         if not cfg.ced_on:
             raise SystemExit("--ced: this layer count has no usable encoder/decoder boundary")
-    eng = DS41Engine(cfg, weights, fabric, max_rows=args.chunk, slots=1, max_ctx=(P + 127) // 64 * 64)
+    eng = DS41Engine(cfg, weights, fabric, max_rows=args.chunk, slots=1, max_ctx=(P + 127) // 64 * 64,
+                     long_pass=args.long_pass)
     run_prompt = eng.prefill_ced if args.ced else eng.prefill
     g = torch.Generator().manual_seed(1234)
-    prompt = torch.randint(3, cfg.vocab - 600, (P,), generator=g).tolist()
+    prompts = [torch.randint(3, cfg.vocab - 600, (P,), generator=g).tolist() for _ in range(NP)]
     setup_s = time.time() - t0
+
+    def step():
+        for pr in prompts:           # one request slot, reused: every prompt starts from an empty context
+            run_prompt(0, pr, chunk=args.chunk)
+
     l0 = eng.launches
+    est_ms = float("inf")
     for _ in range(W):
-        run_prompt(0, prompt, chunk=args.chunk)
-    per_prompt = (eng.launches - l0) // W
+        torch.cuda.synchronize()
+        tw = time.perf_counter()
+        step()
+        torch.cuda.synchronize()
+        est_ms = min(est_ms, (time.perf_counter() - tw) * 1e3)
+    per_step = (eng.launches - l0) // W
     eng.check_status("prefill warm-up")
+    hot_share = None
+    if args.skew:
+        eng.debug = []
+        run_prompt(0, prompts[0], chunk=args.chunk)
+        ids = torch.cat([d["ids"].flatten() for d in eng.debug])
+        hot_share = round(float((ids < 2).float().mean()), 4)
+        eng.debug = None
     sampler = ClockSampler(dev.index or 0)
     if rank == 0:
         sampler.start()
-    ms = timed(fabric, torch, lambda: [run_prompt(0, prompt, chunk=args.chunk) for _ in range(K)])
+    ms, all_ms = timed_repeats(fabric, torch, lambda: [step() for _ in range(K)], est_ms * K)
     clocks = sampler.stop() if rank == 0 else {}
     eng.check_status("timed prefill")
     if args.breakdown:
@@ -149,7 +222,7 @@ def prefill_bench(args, fabric, cfg, n_layers):
         # the time its kernels spend waiting for slower peers
         fabric.barrier()
         eng.timeline = []
-        run_prompt(0, prompt, chunk=args.chunk)
+        run_prompt(0, prompts[0], chunk=args.chunk)
         torch.cuda.synchronize()
         acc = {}
         for tag, e0, e1 in eng.timeline:
@@ -165,33 +238,35 @@ def prefill_bench(args, fabric, cfg, n_layers):
     torch.cuda.synchronize()
     t1 = time.perf_counter()
     for _ in range(K):
-        run_prompt(0, prompt, chunk=args.chunk)
+        step()
     torch.cuda.synchronize()
     e2e_s = fabric.all_reduce_max(time.perf_counter() - t1)
     if rank == 0:
-        value = K * P / (ms / 1e3)
+        value = K * NP * P / (ms / 1e3)
         chunks = (P + args.chunk - 1) // args.chunk
+        sp = eng._sp is not None
+        scheme = "every layer over every token" if not args.ced else \
+            f"layers below {cfg.ced_boundary} over all tokens, layers from it upwards over the last {cfg.ced_replay}"
         line = {
-            "metric": "prefill tok/s (one prompt, chunked passes)" if not args.ced else
-                      f"prefill tok/s (one prompt, layers below {cfg.ced_boundary} over all tokens, layers from it "
-                      f"upwards over the last {cfg.ced_replay})", "value": round(value, 1), "unit": "tok/s",
+            "metric": f"prefill tok/s ({NP} prompt{'s' if NP > 1 else ''} of {P} tokens, {scheme}{layers_tag(n_layers)})",
+            "value": round(value, 1), "unit": "tok/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 3), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": round(value / BASELINE_PREFILL, 3),
+            "scaling": "strong", **baseline_fields(value, BASELINE_PREFILL, n_layers),
+            "repeats": len(all_ms), "timed_s": round(sum(all_ms) / 1e3, 3),
             "dtype": "bf16 dense / fp8-e4m3 experts (fp32 accumulate)", "data": "synthetic",
-            "config": {"model": f"DeepSeek-V4.1-Flash-shaped ({cfg.name})", "layers": n_layers, "layers_full_model": 40,
-                       "global_batch": 1, "seq_len": P, "chunk_rows": args.chunk,
-                       "parallelism": f"tp{world}+ep{world}",
-                       "experts": {"mxfp8": "fp8 e4m3, 128x128 ue8m0 block scales, 1x128 activation scales",
-                                   "mxfp4": "fp4 e2m1 weights, 1x32 ue8m0 scales (official layout), fp8 e4m3 activations "
-                                            "with 1x128 scales", "bf16": "bf16",
-                                   "nvfp4": "NVFP4 W4A4: e2m1 weights and activations, e4m3 scale per 16, fp32 scale per "
-                                            "tensor"}[args.expert_dtype],
+            "config": {"model": f"DeepSeek-V4.1-Flash-shaped ({cfg.name})", "layers": n_layers,
+                       "layers_full_model": LAYERS_FULL, "global_batch": NP, "seq_len": P, "chunk_rows": args.chunk,
+                       "parallelism": (f"sp{world} (row-sharded streams, unsharded dense weights) + ep{world}" if sp
+                                       else f"tp{world}+ep{world}"),
+                       "router": f"logits ~ N(0, {args.router_std}^2)" if args.router_std else "weights ~ N(0, 0.02^2)",
+                       "skew": {"hot_experts": 2, "share_of_routed_tokens": hot_share} if args.skew else None,
+                       "experts": expert_note(args.expert_dtype),
                        "l2": "no flush: every pass streams more weight bytes than the 126 MB L2",
                        "weights_gb_per_gpu": round(weights.nbytes() / 1e9, 2), "setup_s": round(setup_s, 1)},
             "clocks": clocks,
-            "e2e": {"value": round(K * P / e2e_s, 1), "unit": "tok/s", "steps": K,
-                    "h2d_bytes_per_step": 12 * P, "d2h_bytes_per_step": 4 * chunks},
-            "gpu_launches": per_prompt * K, "impl": "ours",
+            "e2e": {"value": round(K * NP * P / e2e_s, 1), "unit": "tok/s", "steps": K,
+                    "h2d_bytes_per_step": 12 * P * NP, "d2h_bytes_per_step": 4 * chunks * NP},
+            "gpu_launches": per_step * K * len(all_ms), "impl": "ours",
         }
         print(json.dumps(line))
     fabric.barrier()
@@ -200,33 +275,49 @@ def prefill_bench(args, fabric, cfg, n_layers):
 
 def concurrent_bench(args, fabric, cfg, n_layers):
     """Concurrent greedy decode: C requests, one row each per step, all in one pass (paged KV, one slot per request).
-    Prompts share their first half (the shared-prefix workload); this build recomputes the shared half per request."""
+    The prompts share their first half: it is run once, snapshotted, and restored into every other slot (whole pages
+    shared by reference, the cut page, window rings and pair carry copied); each request then runs only its own half."""
     import torch
     from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
     from ds41rt_b200.runtime.session import DecodeSession
     world, rank, dev = fabric.world, fabric.rank, fabric.device
     C, P = args.concurrency, args.prompt
     W, K = max(args.warmup, 3), args.steps
-    new_tokens = 2 * (W + K) + 8
+    reps_max = max(1, min(MAX_REPEATS, 2048 // max(K, 1)))
+    new_tokens = W + K * (reps_max + 1) + 16
     t0 = time.time()
     weights = EngineWeights.random(cfg, rank, world, dev, seed=0, expert_dtype=args.expert_dtype)
-    eng = DS41Engine(cfg, weights, fabric, max_rows=max(C, args.chunk), slots=C,
-                     max_ctx=(P + new_tokens + 127) // 64 * 64, kv_dtype=args.kv_dtype)
+    max_ctx = (P + new_tokens + 127) // 64 * 64
+    n_pages = C * ((max_ctx + 63) // 64) + 8
+    eng = DS41Engine(cfg, weights, fabric, max_rows=max(C, args.chunk), slots=C, max_ctx=max_ctx, n_pages=n_pages,
+                     kv_dtype=args.kv_dtype)
     g = torch.Generator().manual_seed(1234)
-    shared = torch.randint(3, cfg.vocab - 600, (P // 2,), generator=g).tolist()
+    n_shared = P // 2
+    shared = torch.randint(3, cfg.vocab - 600, (n_shared,), generator=g).tolist()
+    tp0 = time.time()
+    eng.prefill(0, shared, chunk=args.chunk)
+    snap = eng.cache.snapshot(0, n_shared)
     first = []
     for s in range(C):
-        own = torch.randint(3, cfg.vocab - 600, (P - P // 2,), generator=g).tolist()
-        first.append(eng.prefill(s, shared + own, chunk=args.chunk))
+        own = torch.randint(3, cfg.vocab - 600, (P - n_shared,), generator=g).tolist()
+        if s > 0:
+            assert eng.cache.restore(s, snap), "KV pool exhausted while restoring the shared prefix"
+        first.append(eng.prefill(s, own, start=n_shared, chunk=args.chunk))
+    torch.cuda.synchronize()
+    prefill_s = time.time() - tp0
     eng.check_status("prefill")
     setup_s = time.time() - t0
     sess = DecodeSession(eng, use_graphs=not args.no_graph)
     eng.set_rows(first, [P] * C, list(range(C)))
+    torch.cuda.synchronize()
+    tw = time.perf_counter()
     sess.run_device_loop(C, W)
+    torch.cuda.synchronize()
+    est_ms = (time.perf_counter() - tw) * 1e3 / W
     sampler = ClockSampler(dev.index or 0)
     if rank == 0:
         sampler.start()
-    ms = timed(fabric, torch, lambda: sess.run_device_loop(C, K))
+    ms, all_ms = timed_repeats(fabric, torch, lambda: sess.run_device_loop(C, K), est_ms * K, reps_max)
     clocks = sampler.stop() if rank == 0 else {}
     eng.check_status("timed decode")
     per_pass = sess.launches_per_graph.get((C, True), 0) if not args.no_graph else 0
@@ -238,10 +329,11 @@ def concurrent_bench(args, fabric, cfg, n_layers):
         toks = sess.step(toks, pos, slots)
         pos = [p + 1 for p in pos]
     sess.h2d_bytes = sess.d2h_bytes = 0
+    e2e_steps = min(K, 64)
     fabric.barrier()
     torch.cuda.synchronize()
     t1 = time.perf_counter()
-    for _ in range(K):
+    for _ in range(e2e_steps):
         toks = sess.step(toks, pos, slots)
         pos = [p + 1 for p in pos]
     torch.cuda.synchronize()
@@ -250,49 +342,73 @@ def concurrent_bench(args, fabric, cfg, n_layers):
     if rank == 0:
         value = C * K / (ms / 1e3)
         line = {
-            "metric": f"decode tok/s C{C} (greedy, target-only)", "value": round(value, 1), "unit": "tok/s",
+            "metric": f"decode tok/s C{C} (greedy, target-only{layers_tag(n_layers)})", "value": round(value, 1),
+            "unit": "tok/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16 dense / fp8-e4m3 experts (fp32 accumulate)", "data": "synthetic",
-            "config": {"model": f"DeepSeek-V4.1-Flash-shaped ({cfg.name})", "layers": n_layers, "layers_full_model": 40,
+            "scaling": "strong", "vs_baseline": None, "repeats": len(all_ms), "timed_s": round(sum(all_ms) / 1e3, 3),
+            "dtype": "bf16 dense / " + args.expert_dtype + " experts (fp32 accumulate)", "data": "synthetic",
+            "config": {"model": f"DeepSeek-V4.1-Flash-shaped ({cfg.name})", "layers": n_layers,
+                       "layers_full_model": LAYERS_FULL,
                        "global_batch": C, "seq_len": P, "prompt_tokens": P, "parallelism": f"tp{world}+ep{world}",
                        "tokens_per_step": C, "kv_cache": f"paged, 64-token pages, {args.kv_dtype} rows",
-                       "shared_prefix": "first half of every prompt identical; recomputed per request",
-                       "experts": args.expert_dtype,
+                       "shared_prefix": {"tokens": n_shared, "reuse": "run once, snapshot restored into every other slot "
+                                         "(pages shared by reference)", "pages_shared": len(snap.pages),
+                                         "prompt_phase_s": round(prefill_s, 2)},
+                       "experts": expert_note(args.expert_dtype),
+                       "reference_concurrency_cap": 16,
                        "l2": "no flush: every step streams more weight bytes than the 126 MB L2",
                        "weights_gb_per_gpu": round(weights.nbytes() / 1e9, 2),
                        "kv_gb_per_gpu": round(eng.cache.nbytes() / 1e9, 3), "setup_s": round(setup_s, 1)},
             "clocks": clocks,
-            "e2e": {"value": round(C * K / e2e_s, 1), "unit": "tok/s", "steps": K,
-                    "h2d_bytes_per_step": sess.h2d_bytes // max(K, 1), "d2h_bytes_per_step": sess.d2h_bytes // max(K, 1)},
-            "gpu_launches": per_pass * K, "impl": "ours",
+            "e2e": {"value": round(C * e2e_steps / e2e_s, 1), "unit": "tok/s", "steps": e2e_steps,
+                    "h2d_bytes_per_step": sess.h2d_bytes // max(e2e_steps, 1),
+                    "d2h_bytes_per_step": sess.d2h_bytes // max(e2e_steps, 1)},
+            "gpu_launches": per_pass * K * len(all_ms), "impl": "ours",
         }
         print(json.dumps(line))
     fabric.barrier()
     return 0
 
 
+PRESETS = {
+    2: dict(no_spec=True, prompt=4096, steps=512),
+    3: dict(mode="prefill", prompts=8, prompt=8192, chunk=8192, router_std=1.0, steps=2),
+    4: dict(concurrency=64, prompt=2048, steps=1024, expert_dtype="nvfp4", kv_dtype="fp8"),
+    5: dict(prompt=32768, prefill_chunk=2048, mask=True),
+}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64, help="timed rounds (speculative) or decode steps (--no-spec)")
+    ap.add_argument("--steps", type=int, default=None, help="timed rounds (speculative) or decode steps / prompt batches")
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours")
+    ap.add_argument("--config", type=int, default=0, choices=[0, 2, 3, 4, 5],
+                    help="preset of one of the named benchmark configurations (explicit flags still win)")
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = fit to memory)")
-    ap.add_argument("--prompt", type=int, default=4096)
+    ap.add_argument("--prompt", type=int, default=None)
+    ap.add_argument("--prompts", type=int, default=None, help="prefill: prompts per step")
     ap.add_argument("--model", default="flash", choices=["flash", "small", "tiny"])
-    ap.add_argument("--expert-dtype", default="mxfp8", choices=["mxfp8", "mxfp4", "nvfp4", "bf16"])
-    ap.add_argument("--prefill-chunk", type=int, default=32)
+    ap.add_argument("--expert-dtype", default=None, choices=["mxfp8", "mxfp4", "nvfp4", "bf16"])
+    ap.add_argument("--prefill-chunk", type=int, default=None)
     ap.add_argument("--e2e-steps", type=int, default=0, help="rounds/steps of the host-loop measurement (0 = --steps)")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly (for per-kernel profiling)")
-    ap.add_argument("--no-spec", action="store_true", help="plain greedy decoding, one token per step")
+    ap.add_argument("--no-spec", action="store_true", default=None, help="plain greedy decoding, one token per step")
     ap.add_argument("--accept", type=int, default=3, help="drafts accepted per round in the fixed schedule")
     ap.add_argument("--draft-stages", type=int, default=1)
-    ap.add_argument("--mode", default="decode", choices=["decode", "prefill"],
+    ap.add_argument("--mode", default=None, choices=["decode", "prefill"],
                     help="prefill: time whole-prompt passes in --chunk-row chunks (tok/s of prompt tokens)")
-    ap.add_argument("--chunk", type=int, default=1024, help="rows per pass in --mode prefill")
-    ap.add_argument("--concurrency", type=int, default=1, help="decode: number of concurrent requests (greedy, no drafter)")
-    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8", "fp4"], help="latent KV rows in the cache")
+    ap.add_argument("--chunk", type=int, default=None, help="rows per pass in --mode prefill")
+    ap.add_argument("--concurrency", type=int, default=None, help="decode: number of concurrent requests (greedy, no drafter)")
+    ap.add_argument("--kv-dtype", default=None, choices=["bf16", "fp8", "fp4"], help="latent KV rows in the cache")
+    ap.add_argument("--router-std", type=float, default=None, help="standard deviation of the router logits (prefill)")
+    ap.add_argument("--skew", action="store_true", help="prefill: two experts take about a quarter of the routed tokens")
+    ap.add_argument("--mask", action="store_true", default=None,
+                    help="speculative decode: a vocabulary allow-mask (synthetic, 1 token in 4 allowed) on every "
+                         "verification row, applied in the target's selection kernel")
+    ap.add_argument("--long-pass", default="auto", choices=["auto", "sp", "replicated"],
+                    help="multi-GPU long passes: row-sharded (sp) or replicated rows with sharded heads")
     ap.add_argument("--ced", action="store_true",
                     help="prefill: the decoder layers run over the last 128 prompt tokens only (the reference's prompt "
                          "scheme); default is every layer over every token")
@@ -301,6 +417,12 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
+    defaults = dict(steps=64, prompt=4096, prompts=1, expert_dtype="mxfp8", prefill_chunk=32, no_spec=False,
+                    mode="decode", chunk=1024, concurrency=1, kv_dtype="bf16", router_std=None, mask=False)
+    defaults.update(PRESETS.get(args.config, {}))
+    for key, val in defaults.items():
+        if getattr(args, key) is None:
+            setattr(args, key, val)
 
     import dataclasses
 
@@ -321,7 +443,7 @@ def main():
         return 2
     dev = fabric.device
     if args.model == "flash":
-        n_layers = args.layers or LAYERS_FOR_GPUS.get(world, 40)
+        n_layers = args.layers or LAYERS_FOR_GPUS.get(world, LAYERS_FULL)
         cfg = ModelConfig.flash(n_layers)
     else:
         cfg = getattr(ModelConfig, args.model)()
@@ -336,8 +458,9 @@ def main():
     width = cfg.dspark.block_size if spec else 1
     per_round = args.accept + 1 if spec else 1
     W, K = max(args.warmup, 3), args.steps
-    e2e_steps = args.e2e_steps or K
-    total_new = (W + K + W + e2e_steps + 4) * per_round + 3 * width + 64
+    e2e_steps = args.e2e_steps or min(K, 256)
+    reps_max = max(1, min(MAX_REPEATS, 2048 // max(K, 1)))
+    total_new = (2 * W + K * (reps_max + 1) + e2e_steps + 4) * per_round + 3 * width + 64
     max_ctx = (args.prompt + total_new + 4 * width + 127) // 64 * 64
 
     t0 = time.time()
@@ -347,6 +470,14 @@ def main():
     g = torch.Generator().manual_seed(1234)
     prompt = torch.randint(3, cfg.vocab - 600, (args.prompt,), generator=g).tolist()
     assert eng.cache.ensure(0, max_ctx)
+    if args.mask:
+        # one allow-mask row per verification row: a fixed pseudo-random quarter of the vocabulary (the stand-in for
+        # the per-step masks a grammar matcher produces; real constraints come from runtime/grammar.py)
+        words = (cfg.vocab + 31) // 32
+        gm = torch.Generator().manual_seed(99)
+        m = torch.randint(0, 2 ** 31 - 1, (width, words), generator=gm, dtype=torch.int64) & \
+            torch.randint(0, 2 ** 31 - 1, (width, words), generator=gm, dtype=torch.int64)
+        eng.head_mask = m.to(torch.int32).to(dev)
     drafter = None
     if spec:
         drafter = DSparkDrafter(cfg, eng, weights=None, seed=0, expert_dtype=args.expert_dtype)
@@ -369,12 +500,17 @@ def main():
 
     # ---------------- device-timed: K graph replays, accept rule / token feedback on the device
     l0 = eng.launches + (drafter.eng.launches if drafter else 0)
+    run(3)                                  # graph capture and first replays
+    torch.cuda.synchronize()
+    tw = time.perf_counter()
     run(W)
-    per_pass_eager = (eng.launches + (drafter.eng.launches if drafter else 0) - l0) // W
+    torch.cuda.synchronize()
+    est_ms = (time.perf_counter() - tw) * 1e3 / W
+    per_pass_eager = (eng.launches + (drafter.eng.launches if drafter else 0) - l0) // (W + 3)
     sampler = ClockSampler(dev.index or 0)
     if rank == 0:
         sampler.start()
-    ms = timed(fabric, torch, lambda: run(K))
+    ms, all_ms = timed_repeats(fabric, torch, lambda: run(K), est_ms * K, reps_max)
     clocks = sampler.stop() if rank == 0 else {}
     eng.check_status("timed decode")
     if drafter:
@@ -383,7 +519,7 @@ def main():
         per_pass = per_pass_eager
     else:
         per_pass = sess.launches_per_round if spec else sess.launches_per_graph.get((1, True), 0)
-    launches = per_pass * K
+    launches = per_pass * K * len(all_ms)
 
     # ---------------- end to end through the public API: pinned H2D in, D2H out, every round/step
     if spec:
@@ -419,25 +555,23 @@ def main():
 
     if rank == 0:
         value = K * per_round / (ms / 1e3)
-        metric = (f"decode tok/s C1 (dSpark drafter, fixed acceptance {args.accept}/{width - 1})" if spec
-                  else "decode tok/s C1 (greedy, target-only)")
+        tag = layers_tag(n_layers) + (", vocabulary mask on every verification row" if args.mask else "")
+        metric = (f"decode tok/s C1 (dSpark drafter, fixed acceptance {args.accept}/{width - 1}{tag})" if spec
+                  else f"decode tok/s C1 (greedy, target-only{tag})")
         base = BASELINE_C1_DECODE if spec else BASELINE_TARGET_ONLY
         line = {
             "metric": metric, "value": round(value, 2), "unit": "tok/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": round(value / base, 3),
+            "scaling": "strong", **baseline_fields(value, base, n_layers),
+            "repeats": len(all_ms), "timed_s": round(sum(all_ms) / 1e3, 3),
             "dtype": "bf16 dense / fp8-e4m3 experts (fp32 accumulate)", "data": "synthetic",
             "config": {"model": f"DeepSeek-V4.1-Flash-shaped ({cfg.name})", "layers": n_layers,
-                       "layers_full_model": 40, "global_batch": 1, "seq_len": args.prompt,
-                       "prompt_tokens": args.prompt, "parallelism": f"tp{world}+ep{world}",
-                       "tokens_per_step": per_round,
+                       "layers_full_model": LAYERS_FULL, "global_batch": 1, "seq_len": args.prompt,
+                       "prompt_tokens": args.prompt, "context_at_end": int(eng.row_pos[0].item()),
+                       "parallelism": f"tp{world}+ep{world}", "tokens_per_step": per_round,
                        "speculative": {"drafter_stages": args.draft_stages, "verify_rows": width,
                                        "accepted_per_round": args.accept} if spec else None,
-                       "experts": {"mxfp8": "fp8 e4m3, 128x128 ue8m0 block scales, 1x128 activation scales",
-                                   "mxfp4": "fp4 e2m1 weights, 1x32 ue8m0 scales (official layout), fp8 e4m3 activations "
-                                            "with 1x128 scales", "bf16": "bf16",
-                                   "nvfp4": "NVFP4 W4A4: e2m1 weights and activations, e4m3 scale per 16, fp32 scale per "
-                                            "tensor"}[args.expert_dtype],
+                       "experts": expert_note(args.expert_dtype),
                        "l2": "no flush: every step streams more weight bytes than the 126 MB L2",
                        "weights_gb_per_gpu": round(weights.nbytes() / 1e9, 2),
                        "kv_gb_per_gpu": round(eng.cache.nbytes() / 1e9, 3), "setup_s": round(setup_s, 1)},

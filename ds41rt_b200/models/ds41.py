@@ -795,6 +795,7 @@ class DS41Engine:
         if R > self.moe_rows and live:
             self._make_ep(live[0])
         self.debug = None   # set to a list to record per-layer routing / selection decisions
+        self.head_mask = None     # optional allow-mask rows for the greedy selection of every pass (see head_rows)
         self._sp = None           # buffers of the sequence-parallel long pass (made on first use)
         self._sp_ag = {}          # rows per rank -> all-gather context of the q_a / kv projection
         self._sp_active = None    # (first own row, own rows, rows) while the streams are row-sharded
@@ -1361,6 +1362,8 @@ class DS41Engine:
                 hint = self._pass_hint        # rows beyond the hinted count are padding (slot -1: no visible key)
                 n_keys = min((hint[1] + 1) // ratio, self.max_keys) if hint is not None and hint[0] <= R else 0
                 scores = self.scores[lo:]
+                # qkv_post packs the extras rows with this layer's own width, not the buffer's
+                extras_own = self.extras.view(-1)[lo * lw.extra_cols:]
                 if n_keys >= 64 and cfg.index_heads == 32 and cfg.index_dim % 64 == 0:
                     self._run("index_prepare", k.ds41_index_prepare, lib.ptr(sp["qb"]), C.c_longlong(nqb), NH * D,
                               lib.ptr(self.cache.idx[src]), lib.ptr(self.cache.page_table), self.cache.max_pages,
@@ -1370,11 +1373,11 @@ class DS41Engine:
                     w_off = lw.extra_cols - cfg.index_heads
                     self._run("index_score_gemm", G.gemm_raw, self.idx_q, self.idx_k, scores, Rl * cfg.index_heads,
                               n_keys, cfg.index_dim, lda=cfg.index_dim, ldb=cfg.index_dim, ldo=self.max_keys,
-                              out_mode=8, bn=256 if n_keys >= 256 else 64, row_w=self.extras[lo:, w_off:],
+                              out_mode=8, bn=256 if n_keys >= 256 else 64, row_w=extras_own[w_off:],
                               row_w_ld=lw.extra_cols, col_limit=self.idx_vis, status=self.status)
                 else:
                     self._run("index_score", k.ds41_index_score_cand, lib.ptr(sp["qb"]), C.c_longlong(nqb), NH * D,
-                              lib.ptr(self.extras[lo:]), lw.extra_cols, lw.extra_cols - cfg.index_heads,
+                              lib.ptr(extras_own), lw.extra_cols, lw.extra_cols - cfg.index_heads,
                               lib.ptr(self.cache.idx[src]), lib.ptr(self.cache.page_table), self.cache.max_pages,
                               self.cache.page_rows[src], lib.ptr(pos), lib.ptr(slot), lib.ptr(self.inv_idx), Rl,
                               cfg.index_heads, cfg.index_dim, ratio, lib.ptr(scores), self.max_keys, *cand, st())
@@ -1502,6 +1505,8 @@ class DS41Engine:
         """collapse -> final norm -> vocabulary shard GEMM -> greedy candidate (+ cross-rank merge)."""
         cfg, k, st = self.cfg, self.k, lib.stream
         lw0 = self._lw_any
+        if mask is None:
+            mask = self.head_mask      # [rows, ceil(vocab / 32)] int32 allow-bits applied by the selection kernel
         if self._sp_active is not None:
             xn, rows = self._sp_head(rows), 1
         else:
