@@ -111,6 +111,15 @@ int64_t ds41_prefix_insert(void* p, const uint32_t* tokens, int n, int bank, int
   return id;
 }
 
+// Least recently used live snapshot of either bank (-1 when none): the one to drop when the page pool runs short.
+int64_t ds41_prefix_oldest(const void* p) {
+  const Radix* r = static_cast<const Radix*>(p);
+  int64_t victim = -1;
+  for (size_t i = 0; i < r->snaps.size(); ++i)
+    if (r->snaps[i].live && (victim < 0 || r->snaps[i].clock < r->snaps[victim].clock)) victim = static_cast<int64_t>(i);
+  return victim;
+}
+
 int ds41_prefix_remove(void* p, int64_t id) {
   Radix* r = static_cast<Radix*>(p);
   if (id < 0 || id >= static_cast<int64_t>(r->snaps.size()) || !r->snaps[id].live) return -1;

@@ -4,6 +4,14 @@
   serve  [--model ...]       OpenAI-compatible HTTP server over the native engine; under torch.distributed.run rank 0
                              serves and the other ranks mirror its engine calls (tensor + expert parallel)
   info                       print the model configuration and the per-rank memory plan
+  doctor                     check the machine: toolchain, built libraries, GPUs, peer access, settings tiers
+  inspect-model              tensor catalog of a configuration or a checkpoint directory (counts, bytes, placement)
+  tokenize                   text -> token ids with the server's tokenizer
+  load-tensors               read (and validate) tensors of a checkpoint, with timing
+  plan-memory                KV page pool that fits a device next to the weights
+
+`serve` reads its options in three tiers: a KEY=VALUE settings file (`--settings`, default ./ds41rt.config), the
+environment (DS41RT_<KEY>) and the command line, later tiers overriding earlier ones (ds41rt_b200/settings.py).
 
 The reference's counterparts are its run.sh / build.sh launchers and the `v41-native-serve` daemon command
 (rust/crates/ds41rt-daemon/src/v41_native_serve.rs, rust/crates/ds41rt-daemon/src/cli.rs).
@@ -43,6 +51,124 @@ def cmd_info(args) -> int:
     print(json.dumps({"model": cfg.name, "layers": cfg.n_layers, "hidden": cfg.hidden, "experts": cfg.n_experts,
                       "topk": cfg.topk, "vocab": cfg.vocab, "checkpoint_tensors": n,
                       "expert_bytes_fp8": expert, "experts_gb_per_layer_fp8": round(expert * cfg.n_experts / 2 ** 30, 2)}))
+    return 0
+
+
+def cmd_doctor(args) -> int:
+    """Machine check-up (reference: `ds41rt doctor`, rust/crates/ds41rt-daemon/src/cli.rs:15-35, scripts/doctor.sh)."""
+    import shutil
+    import subprocess
+    from . import build
+    rep = {"python": sys.version.split()[0]}
+    try:
+        import torch
+        rep["torch"] = torch.__version__
+        rep["cuda_available"] = torch.cuda.is_available()
+        rep["gpus"] = []
+        if torch.cuda.is_available():
+            n = torch.cuda.device_count()
+            for i in range(n):
+                p = torch.cuda.get_device_properties(i)
+                free, total = torch.cuda.mem_get_info(i)
+                rep["gpus"].append({"index": i, "name": p.name, "sm": f"{p.major}.{p.minor}", "sms": p.multi_processor_count,
+                                    "memory_gb": round(total / 2 ** 30, 1), "free_gb": round(free / 2 ** 30, 1)})
+            rep["peer_access"] = [[bool(i == j or torch.cuda.can_device_access_peer(i, j)) for j in range(n)]
+                                  for i in range(n)]
+            rep["sm_100"] = all(g["sm"] == "10.0" for g in rep["gpus"])
+        rep["nccl"] = ".".join(map(str, torch.cuda.nccl.version())) if torch.cuda.is_available() else None
+    except Exception as e:                                   # pragma: no cover - depends on the machine
+        rep["torch_error"] = str(e)
+    nvcc = shutil.which("nvcc") or ("/usr/local/cuda/bin/nvcc" if os.path.exists("/usr/local/cuda/bin/nvcc") else None)
+    rep["nvcc"] = None
+    if nvcc:
+        out = subprocess.run([nvcc, "--version"], capture_output=True, text=True).stdout
+        rep["nvcc"] = out.strip().splitlines()[-1] if out else nvcc
+    rep["libraries"] = {n: (build.LIBDIR / n).exists() for n in ("libds41_kernels.so", "libds41_core.so")}
+    try:
+        from .runtime import core as K
+        K.core()
+        rep["core_loads"] = True
+    except Exception as e:
+        rep["core_loads"] = f"{type(e).__name__}: {e}"
+    from . import settings as S
+    try:
+        rep["settings_file"] = {"path": args.settings or (S.DEFAULT_FILE if os.path.exists(S.DEFAULT_FILE) else None),
+                                "values": S.load_settings_file(args.settings or None)}
+    except Exception as e:
+        rep["settings_file"] = f"{type(e).__name__}: {e}"
+    rep["environment"] = {k: v for k, v in os.environ.items() if k.startswith(S.ENV_PREFIX) or k.startswith("DS41_")}
+    ok = bool(rep.get("cuda_available")) and all(rep["libraries"].values()) and rep.get("core_loads") is True
+    rep["ok"] = ok
+    print(json.dumps(rep, indent=1))
+    return 0 if ok or args.lenient else 1
+
+
+def cmd_inspect_model(args) -> int:
+    """Catalog summary (reference: `ds41rt inspect-model`, rust/crates/ds41rt-loader/src/v41_catalog.rs:478-637)."""
+    from .loader.catalog import Catalog, expected_tensors, official_templates
+    cfg = _config(args)
+    specs = expected_tensors(cfg, variant=args.variant)
+    by_dtype, by_class = {}, {}
+    import math
+    sizes = {"BF16": 2, "F32": 4, "F8_E4M3": 1, "F8_E8M0": 1, "I8": 1, "U8": 1}
+    for name, sp in specs.items():
+        dt, shape = sp[0], sp[1]
+        nbytes = math.prod(shape) * sizes.get(dt, 1)
+        by_dtype[dt] = by_dtype.get(dt, 0) + nbytes
+        cls = ("experts" if ".experts." in name else "shared_expert" if "shared_experts" in name else "attention"
+               if ".attn." in name else "engram" if "engram" in name else "vision" if name.startswith("vision") else
+               "drafter" if name.startswith("mtp.") else "other")
+        by_class[cls] = by_class.get(cls, 0) + nbytes
+    rep = {"model": cfg.name, "variant": args.variant, "tensors": len(specs),
+           "templates": len(official_templates(cfg, args.variant)),
+           "bytes_by_dtype": by_dtype, "gb_by_class": {k: round(v / 2 ** 30, 3) for k, v in by_class.items()},
+           "total_gb": round(sum(by_dtype.values()) / 2 ** 30, 2)}
+    if args.checkpoint:
+        cat = Catalog(args.checkpoint, cfg, variant=args.variant)
+        rep["checkpoint"] = {"directory": args.checkpoint, "shards": len(cat.files), "validated_tensors": len(cat.where)}
+    if args.world > 1:
+        per_rank = by_class.get("experts", 0) / args.world + sum(v for k, v in by_class.items() if k != "experts")
+        rep["per_rank_gb_expert_parallel"] = round(per_rank / 2 ** 30, 2)
+    print(json.dumps(rep, indent=1))
+    return 0
+
+
+def cmd_tokenize(args) -> int:
+    from .serving.tokenizer import ByteTokenizer, HFTokenizer
+    cfg = _config(args)
+    tk = HFTokenizer(args.tokenizer) if args.tokenizer else ByteTokenizer(vocab_size=cfg.vocab)
+    text = args.text if args.text is not None else sys.stdin.read()
+    ids = tk.encode(text)
+    print(json.dumps({"tokens": len(ids), "ids": ids, "round_trip": tk.decode(ids) == text}))
+    return 0
+
+
+def cmd_load_tensors(args) -> int:
+    """Read tensors of a checkpoint through the strict catalog (reference: `ds41rt load-tensors`)."""
+    import fnmatch
+    from .loader.catalog import Catalog
+    cfg = _config(args)
+    t0 = time.time()
+    cat = Catalog(args.checkpoint, cfg, variant=args.variant)
+    t_open = time.time() - t0
+    names = [n for n in cat.where if fnmatch.fnmatch(n, args.pattern)][: args.limit or None]
+    nbytes, t1 = 0, time.time()
+    for n in names:
+        t = cat.read(n)
+        nbytes += t.numel() * t.element_size()
+    dt = time.time() - t1
+    print(json.dumps({"opened_s": round(t_open, 3), "tensors_read": len(names), "bytes": nbytes,
+                      "read_s": round(dt, 3), "gb_per_s": round(nbytes / max(dt, 1e-9) / 1e9, 3)}))
+    return 0
+
+
+def cmd_plan_memory(args) -> int:
+    from .runtime.memory import plan_pool
+    cfg = _config(args)
+    free = int(args.free_gb * 2 ** 30)
+    plan = plan_pool(cfg, n_layers=cfg.n_layers, slots=args.concurrency, max_context=args.max_context,
+                     free_bytes=free, kv_dtype=args.kv_dtype, retained=args.retained)
+    print(json.dumps(plan.as_dict()))
     return 0
 
 
@@ -109,14 +235,34 @@ def cmd_serve(args) -> int:
         weights = load_engine_weights(args.checkpoint, cfg, rank, world, dev, expert_dtype=args.expert_dtype)
     else:
         weights = EngineWeights.random(cfg, rank, world, dev, seed=args.seed, expert_dtype=args.expert_dtype)
-    eng = DS41Engine(cfg, weights, fabric, max_rows=max(8, args.concurrency), slots=args.concurrency,
-                     max_ctx=args.max_context, kv_dtype=args.kv_dtype)
+    # KV pool: what the request slots want at full context, cut to what is free beside the weights
+    from .runtime.memory import plan_pool
+    torch.cuda.synchronize()
+    free_now = torch.cuda.mem_get_info(dev)[0]
+    plan = plan_pool(cfg, n_layers=cfg.n_layers, slots=args.concurrency, max_context=args.max_context,
+                     free_bytes=free_now, kv_dtype=args.kv_dtype, retained=args.prompt_snapshots + args.turn_snapshots,
+                     ring_rows=cfg.window + max(16, args.prefill_chunk), reserve_bytes=args.reserve_gb << 30)
+    n_pages = int(fabric.all_reduce_max(-plan.pages) * -1) if world > 1 else plan.pages     # the smallest rank decides
+    if n_pages < (args.max_context + 63) // 64 + 1:
+        print(f"rank {rank}: only {n_pages} KV pages fit; lower --max-context or --concurrency", file=sys.stderr)
+        return 2
+    eng = DS41Engine(cfg, weights, fabric, max_rows=max(8, args.concurrency, args.prefill_chunk), slots=args.concurrency,
+                     max_ctx=args.max_context, kv_dtype=args.kv_dtype, n_pages=n_pages)
     engram_layers = _attach_engram(args, cfg, eng, dev)
+    hb = None
+    if world > 1:
+        # liveness over a TCP store next to the rendezvous port: heartbeats from every rank, a guard on the leader
+        import torch.distributed as dist
+        from .parallel.health import Heartbeat
+        port = int(os.environ.get("MASTER_PORT", "29500")) + 7
+        store = dist.TCPStore(os.environ.get("MASTER_ADDR", "127.0.0.1"), port, world, is_master=(rank == 0),
+                              wait_for_workers=False)
+        hb = Heartbeat(store, rank, world, interval=0.5, max_age=args.peer_timeout).start()
     if rank != 0:
         # every other rank mirrors the leader's engine calls until it is told to stop
-        follower_loop(eng, ctl, on_error=lambda e: print(f"rank {rank}: {e}", file=sys.stderr, flush=True))
+        follower_loop(eng, ctl, on_error=lambda e: print(f"rank {rank}: {e}", file=sys.stderr, flush=True), heartbeat=hb)
         return 0
-    lead = LeaderEngine(eng, ctl)
+    lead = LeaderEngine(eng, ctl, heartbeat=hb)
     drafter = None
     if args.speculative:
         if world > 1:
@@ -125,12 +271,14 @@ def cmd_serve(args) -> int:
             from .models.dspark import DSparkDrafter
             drafter = DSparkDrafter(cfg, eng, weights=None, seed=args.seed, expert_dtype=args.expert_dtype)
     backend = NativeBackend(lead if world > 1 else eng, eos=tk.eos, concurrency=args.concurrency,
-                            queue_depth=args.queue_depth, drafter=drafter,
+                            queue_depth=args.queue_depth, drafter=drafter, prefill_chunk=args.prefill_chunk,
+                            prompt_snapshots=args.prompt_snapshots, turn_snapshots=args.turn_snapshots,
                             engram=_engram_pipeline(args, cfg, eng, engram_layers, tk))
     srv = ApiServer(backend, tk, host=args.host, port=args.port, queue_depth=args.queue_depth, waiters=args.waiters,
                     max_context=args.max_context).start()
     print(json.dumps({"listening": f"http://{args.host}:{srv.port}", "model": cfg.name, "ranks": world,
-                      "setup_s": round(time.time() - t0, 1)}), flush=True)
+                      "setup_s": round(time.time() - t0, 1), "kv_pool": plan.as_dict() | {"pages": n_pages},
+                      "settings": {k: v for k, v in getattr(args, "_origin", {}).items() if v != "default"}}), flush=True)
     try:
         while True:
             time.sleep(3600)
@@ -155,8 +303,39 @@ def main(argv=None) -> int:
     sub.add_parser("build")
     pi = sub.add_parser("info")
     model_args(pi)
+    pd = sub.add_parser("doctor")
+    pd.add_argument("--settings", default="", help="settings file to check (default ./ds41rt.config when present)")
+    pd.add_argument("--lenient", action="store_true", help="exit 0 even when a check fails (report only)")
+    pm = sub.add_parser("inspect-model")
+    model_args(pm)
+    pm.add_argument("--variant", default="mxfp4", choices=["mxfp4", "nvfp4"])
+    pm.add_argument("--checkpoint", default="", help="validate this checkpoint directory against the catalog")
+    pm.add_argument("--world", type=int, default=1, help="ranks: also print the per-rank share under expert parallelism")
+    pt = sub.add_parser("tokenize")
+    model_args(pt)
+    pt.add_argument("--tokenizer", default="")
+    pt.add_argument("--text", default=None, help="text to encode (default: standard input)")
+    pl = sub.add_parser("load-tensors")
+    model_args(pl)
+    pl.add_argument("--checkpoint", required=True)
+    pl.add_argument("--variant", default="mxfp4", choices=["mxfp4", "nvfp4"])
+    pl.add_argument("--pattern", default="*", help="shell pattern over tensor names")
+    pl.add_argument("--limit", type=int, default=0)
+    pp = sub.add_parser("plan-memory")
+    model_args(pp)
+    pp.add_argument("--free-gb", type=float, required=True, help="device memory left after the weights")
+    pp.add_argument("--concurrency", type=int, default=4)
+    pp.add_argument("--max-context", type=int, default=8192)
+    pp.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8", "fp4"])
+    pp.add_argument("--retained", type=int, default=40)
     ps = sub.add_parser("serve")
     model_args(ps)
+    ps.add_argument("--settings", default="", help="KEY=VALUE settings file (default ./ds41rt.config when present)")
+    ps.add_argument("--prefill-chunk", type=int, default=2048, help="rows per prompt pass (80-4096)")
+    ps.add_argument("--prompt-snapshots", type=int, default=20, help="prompt-bank capacity (LRU)")
+    ps.add_argument("--turn-snapshots", type=int, default=20, help="turn-bank capacity (LRU)")
+    ps.add_argument("--reserve-gb", type=int, default=0, help="device memory to leave untouched by the KV pool")
+    ps.add_argument("--peer-timeout", type=float, default=10.0, help="seconds without a heartbeat before a rank counts as gone")
     ps.add_argument("--checkpoint", default="", help="directory with model.safetensors.index.json (official layout)")
     ps.add_argument("--tokenizer", default="", help="tokenizer.json; default: byte-level tokenizer")
     ps.add_argument("--expert-dtype", default="mxfp8", choices=["mxfp8", "mxfp4", "nvfp4", "bf16"])
@@ -177,8 +356,21 @@ def main(argv=None) -> int:
     ps.add_argument("--speculative", action="store_true",
                     help="decode a lone greedy request with dSpark draft + verify rounds (random-init drafter unless the "
                          "checkpoint provides one)")
+    argv = list(sys.argv[1:] if argv is None else argv)
     args = ap.parse_args(argv)
-    return {"build": cmd_build, "info": cmd_info, "serve": cmd_serve}[args.cmd](args)
+    if args.cmd == "serve":
+        # settings tiers: file < environment < command line
+        from . import settings as S
+        file_values = S.load_settings_file(args.settings or None)
+        args = S.apply_tiers(ps, argv[argv.index("serve") + 1:], file_values)
+        args.cmd = "serve"
+        if not 80 <= args.prefill_chunk <= 4096:
+            ap.error("--prefill-chunk must be within 80..4096")
+        if not 1 <= args.concurrency <= 64:
+            ap.error("--concurrency must be within 1..64")
+    return {"build": cmd_build, "info": cmd_info, "serve": cmd_serve, "doctor": cmd_doctor,
+            "inspect-model": cmd_inspect_model, "tokenize": cmd_tokenize, "load-tensors": cmd_load_tensors,
+            "plan-memory": cmd_plan_memory}[args.cmd](args)
 
 
 if __name__ == "__main__":

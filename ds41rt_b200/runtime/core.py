@@ -152,6 +152,11 @@ class PrefixBanks:
     def live(self, bank: int) -> int:
         return int(core().ds41_prefix_live(self.h, bank))
 
+    def oldest(self) -> int:
+        """Least recently used live snapshot of either bank, -1 when there is none."""
+        core().ds41_prefix_oldest.restype = C.c_int64
+        return int(core().ds41_prefix_oldest(self.h))
+
 
 # ---------------------------------------------------------------------------------------------- KV allocator
 class KvAllocator:

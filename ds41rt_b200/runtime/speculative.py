@@ -127,6 +127,28 @@ class SpecSession:
         self._host_state = (toks[-1], int(self.h_out[w + 1]))
         return toks
 
+    # ------------------------------------------------------------------ host-selected rounds
+    def draft_host(self, slot: int, anchor: int, pos: int) -> List[int]:
+        """Draft pass alone: [anchor, noise...] at positions pos.. -> the width - 1 proposed tokens, on the host.
+        For rounds whose verification rows are selected under masks or drawn by the sampler (the caller cuts the
+        proposal, builds the row masks and then calls verify_host)."""
+        w = self.width
+        self.d.set_draft_rows(anchor, pos, slot)
+        self.d.draft()
+        self.h_out[: w - 1].copy_(self.d.drafts[: w - 1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes += 4 * (w - 1)
+        return self.h_out[: w - 1].tolist()
+
+    def verify_host(self, slot: int, inputs: List[int], pos: int) -> None:
+        """Target pass over [anchor, drafts...] at positions pos..; the logits of every row stay in the engine and the
+        drafter's rings are fed from the target's taps of these rows (a rejected row is rewritten when its position
+        comes again)."""
+        n = len(inputs)
+        self.t.set_rows(inputs, list(range(pos, pos + n)), [slot] * n)
+        self.t.forward_rows(n)
+        self.d.feed(n)
+
     def generate(self, prompt: List[int], max_new_tokens: int, slot: int = 0, eos: Optional[int] = None) -> List[int]:
         first = self.start(slot, prompt, max_new_tokens)
         out = [first]

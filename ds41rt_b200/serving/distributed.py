@@ -14,12 +14,14 @@ from __future__ import annotations
 from typing import Any, List, Optional, Tuple
 
 
-def make_control_group(fabric):
-    """A gloo group over the same ranks for host-side control messages (None on one rank)."""
+def make_control_group(fabric, timeout_s: float = 600.0):
+    """A gloo group over the same ranks for host-side control messages (None on one rank).  Its collectives give up
+    after `timeout_s`, so a leader whose follower vanished does not wait for ever."""
     if fabric.world == 1:
         return None
+    import datetime
     import torch.distributed as dist
-    return dist.new_group(backend="gloo")
+    return dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=timeout_s))
 
 
 def _bcast(group, obj: Any, src: int = 0) -> Any:
@@ -35,6 +37,10 @@ class _CacheMirror:
 
     def __getattr__(self, name):
         return getattr(self._l.eng.cache, name)
+
+    def admit(self):
+        self._l._send(("admit",))
+        return self._l.eng.cache.admit()
 
     def ensure(self, slot: int, n_tokens: int) -> bool:
         self._l._send(("ensure", slot, n_tokens))
@@ -67,8 +73,10 @@ class _CacheMirror:
 class LeaderEngine:
     """Drop-in for DS41Engine on rank 0 (the subset the serving backend uses)."""
 
-    def __init__(self, engine, group):
-        self.eng, self.group = engine, group
+    def __init__(self, engine, group, heartbeat=None):
+        """heartbeat: parallel.health.Heartbeat of this rank (optional).  Its guard runs before every mirrored call -
+        between passes, with nothing in flight - and raises RankFailure when a follower left or went silent."""
+        self.eng, self.group, self.heartbeat = engine, group, heartbeat
         self._sid = 0
         self.cache = _CacheMirror(self)
 
@@ -76,6 +84,8 @@ class LeaderEngine:
         return getattr(self.eng, name)
 
     def _send(self, msg: Tuple) -> None:
+        if self.heartbeat is not None:
+            self.heartbeat.guard()
         if self.group is not None:
             _bcast(self.group, msg)
 
@@ -119,8 +129,10 @@ class LeaderEngine:
         self._send(("stop",))
 
 
-def follower_loop(engine, group, on_error=None) -> int:
-    """Run on ranks > 0 until the leader says stop; returns the number of passes executed."""
+def follower_loop(engine, group, on_error=None, heartbeat=None) -> int:
+    """Run on ranks > 0 until the leader says stop; returns the number of passes executed.  A call that raises is
+    reported (on_error) and, with a heartbeat, announced as this rank leaving: the leader's guard then fails its
+    requests instead of waiting on kernels that never meet their peer."""
     passes = 0
     snaps = {}
     while True:
@@ -129,6 +141,9 @@ def follower_loop(engine, group, on_error=None) -> int:
         if op == "stop":
             return passes
         try:
+            if op == "admit":
+                engine.cache.admit()
+                continue
             if op == "set_rows":
                 engine.set_rows(msg[1], msg[2], msg[3], row_lo=msg[4])
             elif op == "forward":
@@ -161,3 +176,6 @@ def follower_loop(engine, group, on_error=None) -> int:
         except Exception as e:          # keep the launch sequences aligned; the leader sees the status word / timeout
             if on_error is not None:
                 on_error(e)
+            if heartbeat is not None:
+                heartbeat.leave(f"follower call {op} failed: {type(e).__name__}: {e}"[:200])
+                return passes

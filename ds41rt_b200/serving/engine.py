@@ -121,20 +121,48 @@ class _Active:
     spec: bool = False        # decoded by speculative rounds (drafter + verify) while it is the only active request
 
 
+@dataclass
+class _Prefill:
+    """A prompt on its way through the engine, one pass per scheduler iteration (decode rounds of the active requests
+    run in between; cancellation is looked at before every pass)."""
+    req: GenRequest
+    slot: int
+    gen: int
+    passes: List[tuple]                      # (kind, c0, c1, extra) still to run
+    reused: int = 0
+    solo: bool = False
+    logits: Any = None                       # logits of the prompt's last token once known
+    r0: int = 0
+    ced: bool = False
+    img_rows: Any = None
+    img_pos: Any = None
+    floor: Optional[int] = None
+
+
 class NativeBackend(Backend):
-    """Worker thread + scheduler loop over a DS41Engine (target-only batched decode; greedy rows are selected on
-    the device, sampled or constrained rows go through the GPU sampler with the request's allow-mask).  With a
-    drafter, a greedy unconstrained request that is alone on the engine is decoded by speculative rounds (dSpark drafts,
-    one verification pass, device-side accept rule); it drops to plain decoding when a second request joins."""
+    """Worker thread + scheduler loop over a DS41Engine.
+
+    One iteration: retire cancelled requests -> admit queued requests (slot lease, KV pages with snapshot eviction under
+    pressure, prefix restore) -> ONE prompt pass of the request being prefilled -> ONE decode round of the active
+    requests (captured as a CUDA graph per batch size; greedy rows are selected on the device, sampled or constrained
+    rows go through the GPU sampler with the request's allow-mask) -> emit.  With a drafter, a request that is alone on
+    the engine is decoded by speculative rounds: greedy unconstrained requests by the all-device round, constrained or
+    stochastic ones by a round whose verification rows are selected under per-row grammar masks (a fork of the matcher
+    per draft row) or drawn with the request's own (seed, position) numbers and compared with the drafts
+    (sample-and-match); the verification-length policy decides per round whether drafting pays.
+    Reference behaviour: rust/crates/ds41rt-daemon/src/v41_native_serve/scheduler.rs:200-451, scheduler/independent.rs,
+    constraints.rs:48-68, speculative.rs:121-163."""
     fingerprint = "ds41rt-b200-fp8"
 
     def __init__(self, engine, eos: int, concurrency: int = 4, queue_depth: int = 16, prefill_chunk: Optional[int] = None,
-                 vision=None, drafter=None, engram=None, ced: bool = True):
+                 vision=None, drafter=None, engram=None, ced: bool = True, use_graphs: bool = True,
+                 prompt_snapshots: int = 20, turn_snapshots: int = 20):
         self.e, self.eos = engine, eos
         # prompt passes use the encoder / decoder-replay split when the model has a boundary (config.ced_on)
         self.ced = ced
         self.partial_reuse = True     # snapshots that share only a leading part with a prompt contribute that part
         self.spec = None
+        self.policy = None
         # runtime.engram.EngramPipeline or None.  Every pass hands its token ids to the pipeline first (hashes, page
         # advice, gather requests), runs, and commits the rows it kept.  Speculative rounds keep their draft tokens on
         # the device, so a backend with Engram layers decodes without the drafter.
@@ -144,23 +172,32 @@ class NativeBackend(Backend):
         if drafter is not None:
             from ..runtime.speculative import SpecSession
             self.spec = SpecSession(engine, drafter)
+            self.policy = K.DSparkPolicy(max_width=self.spec.width - 1)
         self.vision = vision                     # models.vision.VisionTower on the engine's device, or None
         self.supports_images = vision is not None
         self.concurrency = min(concurrency, engine.cache.slots, engine.max_rows)
         self.q: "queue.Queue[GenRequest]" = queue.Queue(maxsize=queue_depth)
-        self.kv = K.KvAllocator(engine.cache.n_pages, engine.cache.slots, engine.cache.page_tokens)
         self.lanes = K.Lanes(2)
-        self.prefix = K.PrefixBanks(20, 20, engine.cfg.window)
-        # KV snapshots at prompt ends and turn ends, newest last: (token tuple, KVSnapshot, logits after the last token)
-        self.snapshots: List[tuple] = []
-        self.snapshot_capacity = 40
+        # Prompt and turn banks: the radix (csrc/core/prefix.cc) owns ids, reuse scores and the per-bank LRU; this map
+        # holds what an id stands for: (token tuple, KVSnapshot, logits after the last token or None)
+        self.prefix = K.PrefixBanks(prompt_snapshots, turn_snapshots, engine.cfg.window)
+        self.snapshots: Dict[int, tuple] = {}
         self.prefill_chunk = prefill_chunk or engine.max_rows
         self.active: List[_Active] = []
+        self.prefilling: Optional[_Prefill] = None
         self.pending: Optional[GenRequest] = None
+        # decode rounds replay one captured graph per batch size; eager when the pass depends on host data per step
+        # (Engram rows) or when the engine is a multi-rank mirror (its launches are broadcast call by call)
+        self.use_graphs = use_graphs and engram is None and getattr(engine, "group", None) is None \
+            and engine.device.type == "cuda"
+        self._graphs: Dict[int, Any] = {}
+        self._spec_dirty = False
         self.totals = {"requests": 0, "prompt_tokens": 0, "completion_tokens": 0, "device_greedy_rows": 0,
                        "cpu_sampled_rows": 0, "gpu_sampled_rows": 0, "rounds": 0, "failed": 0,
                        "prompt_cache_hit_tokens": 0, "snapshots": 0, "spec_rounds": 0, "spec_tokens": 0,
-                       "ced_prefills": 0, "partial_prefix_hits": 0}
+                       "ced_prefills": 0, "partial_prefix_hits": 0, "snapshots_evicted_for_pages": 0,
+                       "graph_rounds": 0, "prefill_passes": 0, "spec_masked_rounds": 0, "policy_plain_rounds": 0,
+                       "cancelled_in_prefill": 0}
         self._rid = 0
         self._stop = threading.Event()
         self._ready = threading.Event()
@@ -178,13 +215,20 @@ class NativeBackend(Backend):
         self.q.put_nowait(req)           # queue.Full -> the HTTP layer answers 429
 
     def stats(self) -> dict:
-        pages_free = self.kv.free_pages
-        return {"totals": dict(self.totals), "active": len(self.active), "queued": self.q.qsize(),
-                "kv": {"pages_free": pages_free, "pages_total": self.kv.n_pages},
-                "lanes": [self.lanes.load(0), self.lanes.load(1)],
-                "target_sampling": {"device_rounds_rows": self.totals["device_greedy_rows"],
-                                    "cpu_fallback_rows": self.totals["cpu_sampled_rows"],
-                                    "gpu_sampled_rows": self.totals["gpu_sampled_rows"]}}
+        cache = self.e.cache
+        out = {"totals": dict(self.totals), "active": len(self.active), "queued": self.q.qsize(),
+               "prefilling": self.prefilling is not None,
+               "kv": {"pages_free": cache.free_pages, "pages_total": cache.n_pages,
+                      "snapshots": len(self.snapshots),
+                      "prompt_bank": self.prefix.live(K.PrefixBanks.PROMPT),
+                      "turn_bank": self.prefix.live(K.PrefixBanks.TURN)},
+               "lanes": [self.lanes.load(0), self.lanes.load(1)],
+               "target_sampling": {"device_rounds_rows": self.totals["device_greedy_rows"],
+                                   "cpu_fallback_rows": self.totals["cpu_sampled_rows"],
+                                   "gpu_sampled_rows": self.totals["gpu_sampled_rows"]}}
+        if self.policy is not None:
+            out["dspark_policy"] = self.policy.stats()
+        return out
 
     def close(self) -> None:
         self._stop.set()
@@ -200,21 +244,35 @@ class NativeBackend(Backend):
             while not self._stop.is_set():
                 self._retire()
                 self._admit()
+                self._prefill_step()
                 if not self.active:
-                    time.sleep(0.001)
+                    if self.prefilling is None:
+                        time.sleep(0.001)
                     continue
                 try:
                     self._decode_round()
                 except Exception as ex:           # a failed round fails the active requests; the server keeps running
+                    from ..parallel.health import RankFailure
+                    if isinstance(ex, RankFailure):
+                        for a in self.active:
+                            a.req.events.put(Event("error", status=503, message=str(ex)[:300]))
+                        raise                     # a rank is gone: this backend cannot launch any more
+                    self._device_alive()
                     for a in self.active:
                         a.req.events.put(Event("error", status=500, message=f"decode round failed: {ex}"[:300]))
-                        self._release(a)
+                        self._release(a.slot, a.req)
                         self.totals["failed"] += 1
                     self.active.clear()
         except Exception as ex:
             self.error = str(ex)
             self.healthy = False
             self._ready.set()
+
+    def _device_alive(self):
+        """After a failed pass: a lost CUDA context ends the worker (everything else is the request's problem)."""
+        if self.e.device.type == "cuda":
+            import torch
+            torch.cuda.synchronize(self.e.device)        # raises when the context is gone
 
     def _engram_pass(self, tokens: List[int], slots: List[int], is_image=None):
         """Start the table reads for one pass and hand the rows to the engine -> pass record to commit afterwards."""
@@ -224,12 +282,17 @@ class NativeBackend(Backend):
         self.engram.apply(p, self.e)
         return p
 
-    def _release(self, a: _Active):
-        self.kv.retire(a.slot, a.gen)
-        self.e.cache.release(a.slot)
+    def _release(self, slot: int, req: GenRequest):
+        self.e.cache.release(slot)
         if self.engram is not None:
-            self.engram.release(a.slot)
-        self.lanes.retire(a.req.rid)
+            self.engram.release(slot)
+        self.lanes.retire(req.rid)
+
+    def _fail(self, req: GenRequest, slot: Optional[int], status: int, message: str):
+        req.events.put(Event("error", status=status, message=message[:300]))
+        if slot is not None:
+            self._release(slot, req)
+        self.totals["failed"] += 1
 
     def _finish(self, a: _Active, reason: str):
         a.req.events.put(Event("finish", reason=reason, usage={"prompt_tokens": len(a.req.prompt_ids),
@@ -238,10 +301,10 @@ class NativeBackend(Backend):
         if reason in ("stop", "length") and a.emitted > 1 and not a.req.images:
             # turn bank: the cache holds the prompt and every emitted token but the last one
             try:
-                self._store_snapshot(a.slot, list(a.req.prompt_ids) + a.tokens[:-1], None)
+                self._store_snapshot(a.slot, list(a.req.prompt_ids) + a.tokens[:-1], None, K.PrefixBanks.TURN)
             except Exception:
                 pass
-        self._release(a)
+        self._release(a.slot, a.req)
 
     def _retire(self):
         keep = []
@@ -252,8 +315,38 @@ class NativeBackend(Backend):
                 keep.append(a)
         self.active = keep
 
+    # ------------------------------------------------------------------ admission
+    def _slack(self) -> int:
+        """Positions a request may touch beyond prompt + max_tokens (speculative rows run ahead of the accepted ones)."""
+        return 2 * self.spec.width + 2 if self.spec is not None else 1
+
+    def _ensure_pages(self, slot: int, n_tokens: int) -> bool:
+        """Pages for positions [0, n_tokens) of `slot`, dropping least recently used snapshots while the pool is short."""
+        while not self.e.cache.ensure(slot, n_tokens):
+            if not self._evict_one():
+                return False
+        return True
+
+    def _evict_one(self) -> bool:
+        """Drop the least recently used snapshot (either bank) to free its pages."""
+        if not self.snapshots:
+            return False
+        sid = self.prefix.oldest()
+        if sid < 0 or sid not in self.snapshots:
+            sid = next(iter(self.snapshots))
+        self._drop_snapshot(sid)
+        self.totals["snapshots_evicted_for_pages"] += 1
+        return True
+
+    def _drop_snapshot(self, sid: int):
+        ent = self.snapshots.pop(sid, None)
+        self.prefix.remove(sid)
+        if ent is not None:
+            self.e.cache.drop_snapshot(ent[1])
+
     def _admit(self):
-        while len(self.active) < self.concurrency:
+        while len(self.active) + (1 if self.prefilling is not None else 0) < self.concurrency \
+                and self.prefilling is None:
             req = self.pending
             self.pending = None
             if req is None:
@@ -263,106 +356,104 @@ class NativeBackend(Backend):
                     return
             if req.cancelled.is_set():
                 continue
-            need = len(req.prompt_ids) + req.max_tokens + 1
+            need = len(req.prompt_ids) + req.max_tokens + self._slack()
             if need > self.e.cache.max_ctx:
                 req.events.put(Event("error", status=400, message="prompt plus max_tokens exceeds the context window"))
                 continue
-            lease = self.kv.admit()
+            lease = self.e.cache.admit()
             if lease is None:
                 self.pending = req
                 return
             slot, gen = lease
             try:
-                self.kv.ensure(slot, gen, need)
-            except MemoryError:
-                self.kv.retire(slot, gen)
-                if self.active:
-                    self.pending = req          # park until someone retires
-                    return
-                req.events.put(Event("error", status=503, message="KV pool cannot hold this request"))
+                parked = self._admit_one(req, slot, gen, need)
+            except Exception as ex:
+                # the request fails, its slot and pages go back, the worker goes on (unless the device is gone)
+                self._fail(req, slot, 503 if isinstance(ex, MemoryError) else 500, f"admission failed: {ex}")
+                self._device_alive()
                 continue
-            if not self.e.cache.ensure(slot, need):
-                self.kv.retire(slot, gen)
-                req.events.put(Event("error", status=503, message="KV pool cannot hold this request"))
-                continue
-            self.prefix.lookup(req.prompt_ids)
-            reused, snap_logits, replay_from = (0, None, None) if req.images \
-                else self._restore_prefix(slot, req.prompt_ids)
-            first_new = reused
-            if replay_from is not None:
-                # a truncated snapshot: its compressed rows reach up to the common prefix's even boundary
-                first_new = replay_from + self.e.cfg.window
-            req.events.put(Event("ready", usage={"prompt_tokens": len(req.prompt_ids),
-                                                 "prompt_cache_hit_tokens": reused}))
-            self.totals["requests"] += 1
-            self.totals["prompt_tokens"] += len(req.prompt_ids)
-            self.totals["prompt_cache_hit_tokens"] += reused
-            solo = (self.spec is not None and not self.active and req.sampling.greedy and req.constraint is None
-                    and not req.images and req.max_tokens > 1)
-            first = self._prefill(slot, req, start=first_new, logits=snap_logits, feed_drafter=solo,
-                                  replay_from=replay_from)
-            a = _Active(req, slot, gen, pos=len(req.prompt_ids), last=first, spec=solo)
-            if solo:
-                self.spec.prime(slot, first, len(req.prompt_ids))
-            a.lane = self.lanes.add(req.rid, req.max_tokens, len(req.prompt_ids))
-            self.prefix.insert(req.prompt_ids, K.PrefixBanks.PROMPT)
-            if self._emit(a, first):
-                self.active.append(a)
+            if parked:
+                return
 
-    # ------------------------------------------------------------------ prefix reuse (exact snapshot boundaries)
-    def _restore_prefix(self, slot: int, prompt: List[int]):
+    def _admit_one(self, req: GenRequest, slot: int, gen: int, need: int) -> bool:
+        """Lease pages, restore the best prefix and queue the prompt's passes.  True = parked until a request retires."""
+        e = self.e
+        if not self._ensure_pages(slot, need):
+            e.cache.release(slot)
+            if self.active:
+                self.pending = req              # park until someone retires
+                return True
+            req.events.put(Event("error", status=503, message="KV pool cannot hold this request"))
+            self.totals["failed"] += 1
+            return False
+        reused, snap_logits, replay_from = (0, None, None) if req.images \
+            else self._restore_prefix(slot, req.prompt_ids, need)
+        first_new = reused
+        if replay_from is not None:
+            # a truncated snapshot: its compressed rows reach up to the common prefix's even boundary
+            first_new = replay_from + e.cfg.window
+        req.events.put(Event("ready", usage={"prompt_tokens": len(req.prompt_ids), "prompt_cache_hit_tokens": reused}))
+        self.totals["requests"] += 1
+        self.totals["prompt_tokens"] += len(req.prompt_ids)
+        self.totals["prompt_cache_hit_tokens"] += reused
+        solo = self.spec is not None and not self.active and not req.images and req.max_tokens > 1
+        self.prefilling = self._plan_prefill(slot, gen, req, first_new, snap_logits, solo, replay_from)
+        self.prefilling.reused = reused
+        return False
+
+    # ------------------------------------------------------------------ prefix reuse (radix-driven snapshot banks)
+    def _restore_prefix(self, slot: int, prompt: List[int], need: int):
         """Best stored snapshot for `prompt` -> (tokens reused, logits after them or None, replay start or None).
 
-        A snapshot whose tokens are a prefix of the prompt is continued from its own end (all of its tokens count).  A
-        snapshot that only shares `common` leading tokens with the prompt contributes its compressed rows up to
-        skipped = common / 2 * 2 - window: the windows are rebuilt by running the tokens from `skipped` again (third
-        value), so only `skipped` tokens count as reused.  The higher count wins (reference:
+        The radix names the snapshot and its reuse score.  A snapshot whose tokens are a prefix of the prompt is
+        continued from its own end (all of its tokens count).  A snapshot that only shares `common` leading tokens with
+        the prompt contributes its compressed rows up to skipped = common / 2 * 2 - window: the windows are rebuilt by
+        running the tokens from `skipped` again (third value), so only `skipped` tokens count as reused (reference:
         rust/crates/ds41rt-core/src/prefix.rs:23-30, rust/crates/ds41rt-daemon/src/v41_native_serve/prefix.rs:258-294)."""
-        window = self.e.cfg.window
-        best, best_score, best_exact = None, 0, False
-        for i, (toks, snap, logits) in enumerate(self.snapshots):
-            n = len(toks)
-            common = 0
-            for a, b in zip(toks, prompt):
-                if a != b:
-                    break
-                common += 1
-            if common == n and n <= len(prompt):
-                if n == len(prompt) and logits is None:
-                    continue                               # nothing to continue from without the last logits
-                score, exact = n, True
-            else:
-                score, exact = common // 2 * 2 - window, False
-                if not self.partial_reuse or score <= 0 or common >= len(prompt):
-                    continue
-            if score > best_score:
-                best, best_score, best_exact = i, score, exact
-        if best is None:
+        e = self.e
+        hit = self.prefix.lookup(prompt)
+        if hit is None:
             return 0, None, None
-        toks, snap, logits = self.snapshots[best]
-        self.e.cache.release(slot)                     # the slot was given fresh pages by the admission path
-        if best_exact:
-            if not self.e.cache.restore(slot, snap):
-                self.e.cache.ensure(slot, len(prompt) + 1)
-                return 0, None, None
-            self.snapshots.append(self.snapshots.pop(best))   # most recently used last
-            return len(toks), (logits if len(toks) == len(prompt) else None), None
-        if not self.e.cache.restore_prefix(slot, snap, best_score):
-            self.e.cache.ensure(slot, len(prompt) + 1)
+        ent = self.snapshots.get(hit["id"])
+        if ent is None:                                   # the map was cleared behind the radix: forget the id
+            self.prefix.remove(hit["id"])
             return 0, None, None
-        self.snapshots.append(self.snapshots.pop(best))
+        toks, snap, logits = ent
+        window = e.cfg.window
+        n = len(toks)
+        exact = hit["exact"] and n <= len(prompt) and not (n == len(prompt) and logits is None)
+        score = n if exact else min(hit["common"], len(prompt) - 1) // 2 * 2 - window
+        if not exact and (not self.partial_reuse or score <= 0):
+            return 0, None, None
+        e.cache.release(slot)                             # the slot was given fresh pages by the admission path
+        ok = e.cache.restore(slot, snap) if exact else e.cache.restore_prefix(slot, snap, score)
+        if not ok:
+            # no page for the copied partial page: make room once, else run the whole prompt
+            ok = self._evict_one() and (e.cache.restore(slot, snap) if exact
+                                        else e.cache.restore_prefix(slot, snap, score))
+        if not ok or not self._ensure_pages(slot, need):
+            e.cache.release(slot)
+            if not self._ensure_pages(slot, need):
+                raise MemoryError("KV pool cannot hold this request")
+            return 0, None, None
+        if exact:
+            return n, (logits if n == len(prompt) else None), None
         self.totals["partial_prefix_hits"] += 1
-        return best_score, None, best_score
+        return score, None, score
 
-    def _store_snapshot(self, slot: int, tokens: List[int], logits):
+    def _store_snapshot(self, slot: int, tokens: List[int], logits, bank: int = 0):
         key = tuple(tokens)
-        if not key or any(t == key for t, _, _ in self.snapshots):
+        if not key or any(t == key for t, _, _ in self.snapshots.values()):
             return
-        self.snapshots.append((key, self.e.cache.snapshot(slot, len(key)), logits))
+        sid, evicted = self.prefix.insert(key, bank)
+        if evicted >= 0:
+            ent = self.snapshots.pop(evicted, None)
+            if ent is not None:
+                self.e.cache.drop_snapshot(ent[1])
+        if sid < 0:
+            return
+        self.snapshots[sid] = (key, self.e.cache.snapshot(slot, len(key)), logits)
         self.totals["snapshots"] += 1
-        while len(self.snapshots) > self.snapshot_capacity:
-            _, old, _ = self.snapshots.pop(0)
-            self.e.cache.drop_snapshot(old)
 
     def _image_rows(self, req: GenRequest):
         """Run the vision tower over the request's images -> (rows [n, H] bf16, prompt position of every row)."""
@@ -376,104 +467,148 @@ class NativeBackend(Backend):
             positions += list(pos)
         return torch.cat(rows, 0).contiguous(), positions
 
-    def _prefill(self, slot: int, req: GenRequest, start: int = 0, logits=None, feed_drafter: bool = False,
-                 replay_from: Optional[int] = None) -> int:
-        """Run the prompt from position `start` on.  With `replay_from` (< start, after a truncated snapshot restore)
-        the positions [replay_from, start) are run again to rebuild the windows: their compressed rows are already in
-        the cache, and every pass of this prompt carries a window floor at `replay_from`."""
-        import torch
+    # ------------------------------------------------------------------ prompt passes, one per scheduler iteration
+    def _plan_prefill(self, slot, gen, req, start, logits, solo, replay_from) -> _Prefill:
+        """List the passes of a prompt from position `start` on.  With `replay_from` (< start, after a truncated
+        snapshot restore) the positions [replay_from, start) run again to rebuild the windows: their compressed rows
+        are already in the cache, and every pass of this prompt carries a window floor at `replay_from`."""
         e = self.e
         toks = req.prompt_ids
-        img_rows = img_pos = None
+        pf = _Prefill(req, slot, gen, [], solo=solo, logits=logits, floor=replay_from)
         if req.images:
             if self.vision is None:
                 raise ValueError("this server has no vision tower")
-            img_rows, img_pos = self._image_rows(req)
-        slack = 2 * self.spec.width + 2 if self.spec is not None else 1
-        if not e.cache.ensure(slot, len(toks) + req.max_tokens + slack):
-            raise MemoryError("KV pool cannot hold this request")
+            pf.img_rows, pf.img_pos = self._image_rows(req)
         first = start if replay_from is None else replay_from
         if self.engram is not None:
             self.engram.reset(slot, toks[:first])
-        image_at = set(img_pos) if img_pos is not None else set()
         end, step = len(toks), self.prefill_chunk
         # passes never straddle `start`: below it the compressed sources are kept, from it on they are produced
         cuts = [(c0, min(hi, c0 + step), hi == end) for lo, hi in ((first, start), (start, end))
                 for c0 in range(lo, hi, step)]
-        floor = (lambda m: [replay_from] * m) if replay_from is not None else (lambda m: None)
         taps_above = (self.spec is None or min(e.cfg.dspark.tap_layers) >= e.cfg.ced_boundary) \
             and e.cfg.ced_replay >= e.cfg.window        # stored snapshots must hold complete decoder windows
         if self.ced and first < end and not req.images and taps_above and e.ced_usable(first, end - first):
-            # encoder slices over the new tokens, then the decoder layers over the tail only
-            r0 = e.ced_replay_start(first, end)
-            for c0, c1, fresh in cuts:
-                e.set_rows(toks[c0:c1], list(range(c0, c1)), [slot] * (c1 - c0), row_lo=floor(c1 - c0))
-                ep = self._engram_pass(toks[c0:c1], [slot] * (c1 - c0))
-                e.ced_encoder_slice(c0, c1, r0, fresh)
-                if ep is not None:
-                    self.engram.commit(ep)
-            for c0 in range(r0, end, step):
-                c1 = min(end, c0 + step)
-                e.set_rows(toks[c0:c1], list(range(c0, c1)), [slot] * (c1 - c0), row_lo=[r0] * (c1 - c0))
-                e.ced_replay_slice(c0, c1, r0, c1 >= end)
-                if feed_drafter:
-                    self.spec.d.feed(c1 - c0)
-            self.totals["ced_prefills"] += 1
-            logits = e.logits_rows(e.last_head_row + 1)[e.last_head_row].clone()
-            self._store_snapshot(slot, toks, logits)
+            pf.ced, pf.r0 = True, e.ced_replay_start(first, end)
+            pf.passes = [("enc", c0, c1, fresh) for c0, c1, fresh in cuts]
+            pf.passes += [("replay", c0, min(end, c0 + step), None) for c0 in range(pf.r0, end, step)]
         elif first < end:
-            for c0, c1, fresh in cuts:
-                part = toks[c0:c1]
-                e.set_rows(part, list(range(c0, c1)), [slot] * len(part), row_lo=floor(len(part)))
-                ep = self._engram_pass(part, [slot] * len(part), [c0 + i in image_at for i in range(len(part))])
-                last = c1 >= end
-                if img_rows is not None:
-                    ids = [p - c0 if c0 <= p < c1 else -1 for p in img_pos]
-                    if any(i >= 0 for i in ids):
-                        e.image_patch = (img_rows, torch.tensor(ids, dtype=torch.int32, device=img_rows.device))
-                e.forward_rows(len(part), head=last, sources=fresh)
-                e.image_patch = None
-                if ep is not None:
-                    self.engram.commit(ep)
-                if feed_drafter:
-                    self.spec.d.feed(len(part))       # the drafter's rings follow the target's taps
-            logits = e.logits_rows(e.last_head_row + 1)[e.last_head_row].clone()
-            if not req.images:                                # placeholders look alike: image prompts are not banked
-                self._store_snapshot(slot, toks, logits)      # prompt bank
-        return self._select([req], [0], logits=logits.view(1, -1))[0]
+            pf.passes = [("full", c0, c1, fresh) for c0, c1, fresh in cuts]
+        return pf
 
-    def _select(self, reqs: List[GenRequest], rows: List[int], logits=None) -> List[int]:
-        """Pick the next token of each request from the logits row it owns in the last pass (or in `logits`)."""
+    def _prefill_step(self):
+        """Run the next pass of the prompt in flight; after its last pass the request joins the decode rounds."""
+        pf = self.prefilling
+        if pf is None:
+            return
+        if pf.req.cancelled.is_set():
+            self.prefilling = None
+            self.totals["cancelled_in_prefill"] += 1
+            pf.req.events.put(Event("finish", reason="cancelled",
+                                    usage={"prompt_tokens": len(pf.req.prompt_ids), "completion_tokens": 0}))
+            self._release(pf.slot, pf.req)
+            return
+        try:
+            if pf.passes:
+                self._run_pass(pf, pf.passes.pop(0))
+                self.totals["prefill_passes"] += 1
+                if pf.passes:
+                    return
+            self._finish_prefill(pf)
+        except Exception as ex:
+            self.prefilling = None
+            self._fail(pf.req, pf.slot, 503 if isinstance(ex, MemoryError) else 500, f"prompt pass failed: {ex}")
+            self._device_alive()
+
+    def _run_pass(self, pf: _Prefill, step):
+        import torch
+        e, toks, slot = self.e, pf.req.prompt_ids, pf.slot
+        kind, c0, c1, extra = step
+        self._spec_dirty = True
+        m = c1 - c0
+        end = len(toks)
+        if kind == "enc":
+            e.set_rows(toks[c0:c1], list(range(c0, c1)), [slot] * m, row_lo=[pf.floor] * m if pf.floor is not None else None)
+            ep = self._engram_pass(toks[c0:c1], [slot] * m)
+            e.ced_encoder_slice(c0, c1, pf.r0, extra)
+            if ep is not None:
+                self.engram.commit(ep)
+        elif kind == "replay":
+            e.set_rows(toks[c0:c1], list(range(c0, c1)), [slot] * m, row_lo=[pf.r0] * m)
+            e.ced_replay_slice(c0, c1, pf.r0, c1 >= end)
+            if pf.solo:
+                self.spec.d.feed(m)
+        else:
+            part = toks[c0:c1]
+            image_at = set(pf.img_pos) if pf.img_pos is not None else set()
+            e.set_rows(part, list(range(c0, c1)), [slot] * m, row_lo=[pf.floor] * m if pf.floor is not None else None)
+            ep = self._engram_pass(part, [slot] * m, [c0 + i in image_at for i in range(m)])
+            if pf.img_rows is not None:
+                ids = [p - c0 if c0 <= p < c1 else -1 for p in pf.img_pos]
+                if any(i >= 0 for i in ids):
+                    e.image_patch = (pf.img_rows, torch.tensor(ids, dtype=torch.int32, device=pf.img_rows.device))
+            try:
+                e.forward_rows(m, head=c1 >= end, sources=extra)
+            finally:
+                e.image_patch = None
+            if ep is not None:
+                self.engram.commit(ep)
+            if pf.solo:
+                self.spec.d.feed(m)           # the drafter's rings follow the target's taps
+
+    def _finish_prefill(self, pf: _Prefill):
+        e, req, slot = self.e, pf.req, pf.slot
+        self.prefilling = None
+        if pf.logits is None:
+            pf.logits = e.logits_rows(e.last_head_row + 1)[e.last_head_row].clone()
+            if pf.ced:
+                self.totals["ced_prefills"] += 1
+            if not req.images:                                # placeholders look alike: image prompts are not banked
+                self._store_snapshot(slot, req.prompt_ids, pf.logits, K.PrefixBanks.PROMPT)
+        first = self._select([req], [0], logits=pf.logits.view(1, -1))[0]
+        solo = pf.solo and not self.active
+        a = _Active(req, slot, pf.gen, pos=len(req.prompt_ids), last=first, spec=solo)
+        if solo and req.sampling.greedy and req.constraint is None:
+            self.spec.prime(slot, first, len(req.prompt_ids))
+        a.lane = self.lanes.add(req.rid, req.max_tokens, len(req.prompt_ids))
+        if self._emit(a, first):
+            self.active.append(a)
+
+    # ------------------------------------------------------------------ selection
+    def _select(self, reqs: List[GenRequest], rows: List[int], logits=None, positions=None, masks=None) -> List[int]:
+        """Pick the next token of each request from the logits row it owns in the last pass (or in `logits`).
+        `positions`: sampling position per row (default: the request's emitted count); `masks`: allow-mask per row
+        (default: the request's constraint as it stands)."""
         import torch
         e = self.e
         out = []
-        simple = logits is None and all(r.sampling.greedy and r.constraint is None for r in reqs)
+        simple = logits is None and masks is None and all(r.sampling.greedy and r.constraint is None for r in reqs)
         if simple:
             chosen = e.chosen.tolist()
             self.totals["device_greedy_rows"] += len(reqs)
             return [chosen[i] for i in rows]
         # sampled or grammar-constrained rows: the GPU sampler reads the logits where they are; only the packed
         # allow-masks (vocab/8 bytes per constrained row) go up and one token id per row comes back
-        import numpy as np
         from ..ops.sampling import RowParams, pack_params, sample_rows
         if logits is None:
             logits = e.logits_rows(max(rows) + 1)
         if logits.dtype != torch.float32:
             logits = logits.float()
         picked = logits[torch.tensor(rows, device=logits.device)] if rows != list(range(len(rows))) else logits[:len(rows)]
-        params, masks = [], []
-        for r in reqs:
+        params, arena_rows = [], []
+        for i, r in enumerate(reqs):
             s = r.sampling
             mask_row = -1
-            m = r.constraint.mask() if r.constraint is not None else None
+            m = masks[i] if masks is not None else (r.constraint.mask() if r.constraint is not None else None)
             if m is not None:
-                mask_row = len(masks)
-                masks.append(np.ascontiguousarray(m, dtype=np.uint32))
+                mask_row = len(arena_rows)
+                arena_rows.append(np.ascontiguousarray(m, dtype=np.uint32))
+            position = positions[i] if positions is not None else getattr(r, "_emitted", 0)
             params.append(RowParams(temperature=0.0 if s.greedy else s.temperature, top_k=s.top_k, top_p=s.top_p,
-                                    min_p=s.min_p, seed=s.seed, position=getattr(r, "_emitted", 0), mask_row=mask_row))
+                                    min_p=s.min_p, seed=s.seed, position=position, mask_row=mask_row))
         arena = None
-        if masks:
-            arena = torch.from_numpy(np.stack(masks).view(np.int32)).to(logits.device)
+        if arena_rows:
+            arena = torch.from_numpy(np.stack(arena_rows).view(np.int32)).to(logits.device)
         toks, status = sample_rows(picked.contiguous(), pack_params(params, logits.device), arena)
         toks, status = toks.tolist(), status.tolist()
         for r, tok, st in zip(reqs, toks, status):
@@ -490,7 +625,7 @@ class NativeBackend(Backend):
         r = a.req
         if r.constraint is not None and not r.constraint.accept(tok):
             r.events.put(Event("error", status=500, message="selected token violates the request's grammar"))
-            self._release(a)
+            self._release(a.slot, r)
             return False
         a.emitted += 1
         a.tokens.append(tok)
@@ -509,9 +644,29 @@ class NativeBackend(Backend):
             return False
         return True
 
+    # ------------------------------------------------------------------ speculative rounds (one request on the engine)
     def _spec_round(self, a: _Active):
         """One speculative round for the only active request: up to `width` tokens come back."""
-        toks = self.spec.round_host()
+        import torch
+        r = a.req
+        plain = r.sampling.greedy and r.constraint is None
+        timed = self.e.device.type == "cuda"
+        if timed:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+        if plain:
+            if self._spec_dirty:                   # another request's prompt pass used the engine's input rows
+                self.spec.prime(a.slot, a.last, a.pos)
+                self._spec_dirty = False
+            toks = self.spec.round_host()
+            drafts_checked = self.spec.width - 1
+        else:
+            toks, drafts_checked = self._spec_round_selected(a)
+            self.totals["spec_masked_rounds"] += 1
+        if timed:
+            ev1.record()
+            ev1.synchronize()
+            self.policy.observe(drafts_checked, max(0, len(toks) - 1), ev0.elapsed_time(ev1) * 1e3)
         self.totals["rounds"] += 1
         self.totals["spec_rounds"] += 1
         self.totals["spec_tokens"] += len(toks)
@@ -525,24 +680,78 @@ class NativeBackend(Backend):
             self.lanes.update(a.req.rid, a.req.max_tokens - a.emitted, a.pos)
         self.active = [a] if keep else []
 
+    def _spec_round_selected(self, a: _Active):
+        """Speculative round whose verification rows are selected on the host's terms: drafts come back first, the
+        proposal is cut at the first token the grammar rejects, every verification row gets the mask of a matcher fork
+        advanced over the drafts before it, and the rows are drawn by the GPU sampler with the request's own
+        (seed, position) numbers - a draft counts while it equals the target's own draw (sample-and-match)."""
+        r, sp, e = a.req, self.spec, self.e
+        w = sp.width
+        drafts = sp.draft_host(a.slot, a.last, a.pos)                    # w - 1 proposed tokens
+        if r.constraint is not None:
+            drafts = r.constraint.truncate_proposal(drafts)
+        remaining = r.max_tokens - a.emitted
+        drafts = drafts[: max(0, min(len(drafts), remaining - 1))]
+        inputs = [a.last] + drafts
+        n = len(inputs)
+        masks = r.constraint.row_masks(inputs) if r.constraint is not None else None
+        sp.verify_host(a.slot, inputs, a.pos)                            # target pass over the n rows, rings fed
+        picked = self._select([r] * n, list(range(n)), positions=[a.emitted + i for i in range(n)], masks=masks)
+        accepted = 0
+        while accepted < n - 1 and picked[accepted] == drafts[accepted] and picked[accepted] != self.eos \
+                and picked[accepted] not in r.stop_ids:
+            accepted += 1
+        return picked[: accepted + 1], len(drafts)
+
+    # ------------------------------------------------------------------ decode rounds
+    def _graph_for(self, rows: int):
+        """Captured launch sequence of one `rows`-row decode pass (made on first use of a batch size)."""
+        import torch
+        g = self._graphs.get(rows)
+        if g is None:
+            e = self.e
+            keep = (e.in_tokens.clone(), e.row_pos.clone(), e.row_slot.clone())
+            e.forward_rows(rows)                      # eager pass first: kernel attributes, every code path warm
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                e.forward_rows(rows)
+            e.in_tokens.copy_(keep[0])
+            e.row_pos.copy_(keep[1])
+            e.row_slot.copy_(keep[2])
+            self._graphs[rows] = g
+        return g
+
     def _decode_round(self):
         e = self.e
         acts = self.active
         if len(acts) == 1 and acts[0].spec:
-            return self._spec_round(acts[0])
-        for a in acts:
-            a.spec = False             # a request that shared a pass stays on plain decoding
+            a = acts[0]
+            if a.req.max_tokens - a.emitted > 1 and self.policy.choose() > 0:
+                return self._spec_round(a)
+            self.totals["policy_plain_rounds"] += 1
         e.set_rows([a.last for a in acts], [a.pos for a in acts], [a.slot for a in acts])
-        ep = self._engram_pass([a.last for a in acts], [a.slot for a in acts])
-        e.forward_rows(len(acts))
-        if ep is not None:
-            self.engram.commit(ep)
+        if self.use_graphs:
+            self._graph_for(len(acts)).replay()
+            self.totals["graph_rounds"] += 1
+        else:
+            ep = self._engram_pass([a.last for a in acts], [a.slot for a in acts])
+            e.forward_rows(len(acts))
+            if ep is not None:
+                self.engram.commit(ep)
+        for a in acts:
+            if a.spec and len(acts) == 1:
+                self.spec.d.feed(1)                 # the drafter's rings follow a plain step too
         toks = self._select([a.req for a in acts], list(range(len(acts))))
         self.totals["rounds"] += 1
         keep = []
         for a, t in zip(acts, toks):
             a.pos += 1
+            if len(acts) > 1:
+                a.spec = False         # a request that shared a pass stays on plain decoding
             self.lanes.update(a.req.rid, a.req.max_tokens - a.emitted, a.pos)
             if self._emit(a, t):
                 keep.append(a)
         self.active = keep
+        if len(keep) == 1 and keep[0].spec and keep[0].req.sampling.greedy and keep[0].req.constraint is None:
+            self.spec.prime(keep[0].slot, keep[0].last, keep[0].pos)      # the all-device round starts from here
