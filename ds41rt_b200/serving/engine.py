@@ -295,16 +295,17 @@ class NativeBackend(Backend):
         self.totals["failed"] += 1
 
     def _finish(self, a: _Active, reason: str):
-        a.req.events.put(Event("finish", reason=reason, usage={"prompt_tokens": len(a.req.prompt_ids),
-                                                               "completion_tokens": a.emitted}))
         self.totals["completion_tokens"] += a.emitted
         if reason in ("stop", "length") and a.emitted > 1 and not a.req.images:
-            # turn bank: the cache holds the prompt and every emitted token but the last one
+            # turn bank: the cache holds the prompt and every emitted token but the last one.  Stored before the
+            # finish event leaves, so a client that reacts to the event finds the bank as it will stay.
             try:
                 self._store_snapshot(a.slot, list(a.req.prompt_ids) + a.tokens[:-1], None, K.PrefixBanks.TURN)
             except Exception:
                 pass
         self._release(a.slot, a.req)
+        a.req.events.put(Event("finish", reason=reason, usage={"prompt_tokens": len(a.req.prompt_ids),
+                                                               "completion_tokens": a.emitted}))
 
     def _retire(self):
         keep = []
@@ -411,13 +412,14 @@ class NativeBackend(Backend):
         running the tokens from `skipped` again (third value), so only `skipped` tokens count as reused (reference:
         rust/crates/ds41rt-core/src/prefix.rs:23-30, rust/crates/ds41rt-daemon/src/v41_native_serve/prefix.rs:258-294)."""
         e = self.e
-        hit = self.prefix.lookup(prompt)
-        if hit is None:
-            return 0, None, None
-        ent = self.snapshots.get(hit["id"])
-        if ent is None:                                   # the map was cleared behind the radix: forget the id
-            self.prefix.remove(hit["id"])
-            return 0, None, None
+        while True:
+            hit = self.prefix.lookup(prompt)
+            if hit is None:
+                return 0, None, None
+            ent = self.snapshots.get(hit["id"])
+            if ent is not None:
+                break
+            self.prefix.remove(hit["id"])                 # the map was cleared behind the radix: forget the id, look again
         toks, snap, logits = ent
         window = e.cfg.window
         n = len(toks)

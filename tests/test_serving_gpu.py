@@ -242,6 +242,72 @@ def test_solo_request_is_served_by_speculative_rounds():
     spec.close()
 
 
+def test_speculative_rounds_serve_constrained_and_sampled_requests_losslessly():
+    """A lone request decodes by draft + verify rounds also when it is grammar-constrained (verification rows selected
+    under the masks of a matcher fork per draft row, proposals cut at the first rejected token) or stochastic (rows drawn
+    with the request's own (seed, position) numbers; a draft counts while it equals the draw).  Both produce exactly the
+    tokens of a backend without a drafter; decode rounds of that backend replay captured graphs and agree with eager
+    launches; the verification policy reports its fit."""
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    from ds41rt_b200.models.dspark import DSparkDrafter
+    from ds41rt_b200.runtime.grammar import Grammar, TokenConstraint, Vocab
+    from ds41rt_b200.serving.engine import GenRequest, NativeBackend
+    from ds41rt_b200.serving.protocol import Sampling
+    from ds41rt_b200.serving.tokenizer import ByteTokenizer
+    cfg = ModelConfig.tiny()
+    dev = torch.device("cuda", 0)
+    w = EngineWeights.random(cfg, 0, 1, dev, seed=0)
+    tk = ByteTokenizer(vocab_size=cfg.vocab)
+    vocab = Vocab(tk.token_bytes())
+    schema = {"type": "object", "properties": {"name": {"type": "string"}, "n": {"type": "integer"},
+                                               "kind": {"enum": ["a", "b"]}}, "required": ["name", "n", "kind"]}
+
+    def backend(with_drafter, graphs=True):
+        eng = DS41Engine(cfg, w, max_rows=8, slots=4, max_ctx=512)
+        drafter = DSparkDrafter(cfg, eng, weights=None, seed=0) if with_drafter else None
+        return NativeBackend(eng, eos=tk.eos, concurrency=4, drafter=drafter, use_graphs=graphs)
+
+    def collect(r):
+        toks = []
+        while True:
+            ev = r.events.get(timeout=120)
+            if ev.kind == "tokens":
+                toks += ev.tokens
+            elif ev.kind == "finish":
+                return toks
+            elif ev.kind == "error":
+                raise RuntimeError(ev.message)
+
+    g = torch.Generator().manual_seed(33)
+    prompt = torch.randint(3, 250, (40,), generator=g).tolist()
+
+    def requests():
+        con = TokenConstraint(vocab, Grammar.json_schema(schema), eos=tk.eos)
+        return [GenRequest(prompt_ids=prompt, max_tokens=48, sampling=Sampling(temperature=0.0), constraint=con),
+                GenRequest(prompt_ids=prompt, max_tokens=32, sampling=Sampling(temperature=0.8, top_p=0.95, top_k=40,
+                                                                               seed=5))]
+
+    out = {}
+    for name, be in (("plain", backend(False)), ("eager", backend(False, graphs=False)), ("spec", backend(True))):
+        res = []
+        for r in requests():
+            be.snapshots.clear()
+            be.submit(r)
+            res.append(collect(r))
+        out[name] = (res, dict(be.totals), be.stats())
+        assert be.healthy, be.error
+        be.close()
+    assert out["plain"][0] == out["eager"][0] == out["spec"][0]
+    assert out["plain"][1]["graph_rounds"] > 0 and out["eager"][1]["graph_rounds"] == 0
+    tot = out["spec"][1]
+    assert tot["spec_masked_rounds"] > 0 and tot["spec_rounds"] >= tot["spec_masked_rounds"]
+    pol = out["spec"][2]["dspark_policy"]
+    assert pol["rounds"] > 0 and len(pol["accepted_histogram"]) == 16
+    text = tk.decode(out["spec"][0][0])
+    assert text.lstrip().startswith("{")
+
+
 def test_engram_pipeline_serves_requests(tmp_path):
     """A backend whose engine has an Engram layer: every pass hashes its tokens, gathers table rows on the I/O thread and
     applies the gated update.  The emitted tokens are what the fp32 oracle picks when it is given the same rows
