@@ -50,8 +50,10 @@ MAX_REPEATS = 64
 
 def reference_arm():
     why = ("pip install of the reference tree fails: \"Directory is not installable. Neither 'setup.py' nor "
-           "'pyproject.toml' found.\" - the reference is a Rust/CMake engine whose kernels are AOT-exported for "
-           "SM120/SM121 by absent submodules, and the image has no Rust toolchain")
+           "'pyproject.toml' found.\" - the reference's serving engine is a Rust daemon (no Rust toolchain in the image) "
+           "whose expert and projection GEMMs are AOT-exported for SM120/SM121 by absent submodules; its in-tree CUDA "
+           "kernels do build (baseline/build_ref.py) and are timed one by one with "
+           "`python -m ds41rt_b200.utils.kernel_case --impl reference`")
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 

@@ -361,12 +361,6 @@ int ds41_engram_gate(const void* x, const void* kv, const void* q_w, const void*
                      void* out, int rows, int H, float eps, void* stream);
 
 // ---------------------------------------------------------------------------------------------------
-// Candidate blocks of the long-context indexer (candidates.cu).
-int ds41_block_max(const float* scores, long long ld, int rows, int n_keys, int block, float* out, void* stream);
-int ds41_expand_blocks(const int* blocks, int rows, int k, int block, const int* limit, int* pos, int* count,
-                       void* stream);
-
-// ---------------------------------------------------------------------------------------------------
 // Vision tower elementwise kernels (vision.cu); all tensors bf16 unless noted.
 int ds41_vis_rmsnorm(const void* x, const void* w, void* out, int rows, int W, float eps, void* stream);
 int ds41_vis_bias_act(const void* x, const void* bias, const void* residual, void* out, long long rows, int cols,

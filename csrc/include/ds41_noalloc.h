@@ -9,9 +9,12 @@
 //
 //  * Limits: rows <= DS41_HC_STATIC_MAX_ROWS and H <= DS41_HC_STATIC_MAX_H (H a multiple of 128).  Larger sizes are
 //    refused with cudaErrorInvalidValue before anything is launched.
-//  * The array (about 0.8 MB) is part of every GPU context that loads the library and stays until the process exits.
+//  * The array (631,040 bytes: 106,496 of slice partials, 524,288 of collapsed rows, 256 of ticket counters) is
+//    part of every GPU context that loads the library and stays until the process exits.
 //  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
-//    current).  Make that first call before starting any stream capture.
+//    current) and caches it per device; concurrent first calls are safe (they store the same value through an
+//    atomic).  Make that first call before starting any stream capture.  The cached address is not refreshed: after
+//    cudaDeviceReset on a device the entry point must not be used on it again in the same process.
 //  * No cudaMalloc / cudaFree / allocating library routine is called.  The fields `partial`, `xc` and `tickets` of
 //    the argument struct are ignored; inputs and outputs are still the caller's.
 //  * Every call uses the same array and the array keeps the previous call's contents; the ticket counters are

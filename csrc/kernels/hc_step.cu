@@ -275,6 +275,8 @@ extern "C" int ds41_hc_step(const ds41_hc_step_args* a, void* stream) {
 
 // ---------------------------------------------------------------------------------------------------
 // Allocation-free variant: same kernel, scratch taken from a fixed array inside the library image.
+#include <atomic>
+
 #include "ds41_noalloc.h"
 
 namespace {
@@ -294,18 +296,22 @@ extern "C" int ds41_hc_step_static(const ds41_hc_step_args* a, void* stream) {
   if (a == nullptr || a->rows <= 0 || a->rows > DS41_HC_STATIC_MAX_ROWS || a->H <= 0 ||
       a->H > DS41_HC_STATIC_MAX_H || a->H % ds41::kSlice != 0)
     return cudaErrorInvalidValue;
-  static unsigned char* device_base[64] = {nullptr};
+  // Per-device address cache.  Threads may race to fill an entry: each looks the same symbol up with the same
+  // device current and stores the same value, and the atomic makes the store and the loads well defined.  The entry
+  // is never refreshed, so it goes stale if the device is reset (cudaDeviceReset) while the library stays loaded.
+  static std::atomic<unsigned char*> device_base[64];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  if (device_base[dev] == nullptr) {
+  unsigned char* base = device_base[dev].load(std::memory_order_acquire);
+  if (base == nullptr) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_hc_static_scratch);     // once per device, with that device current
     if (e != cudaSuccess) return e;
-    device_base[dev] = static_cast<unsigned char*>(p);
+    base = static_cast<unsigned char*>(p);
+    device_base[dev].store(base, std::memory_order_release);
   }
-  unsigned char* base = device_base[dev];
   ds41_hc_step_args b = *a;
   b.partial = reinterpret_cast<float*>(base);
   b.xc = reinterpret_cast<float*>(base + kStaticPartialBytes);

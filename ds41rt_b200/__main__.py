@@ -258,6 +258,7 @@ def cmd_serve(args) -> int:
         store = dist.TCPStore(os.environ.get("MASTER_ADDR", "127.0.0.1"), port, world, is_master=(rank == 0),
                               wait_for_workers=False)
         hb = Heartbeat(store, rank, world, interval=0.5, max_age=args.peer_timeout).start()
+        hb.wait_joined(60.0)
     if rank != 0:
         # every other rank mirrors the leader's engine calls until it is told to stop
         follower_loop(eng, ctl, on_error=lambda e: print(f"rank {rank}: {e}", file=sys.stderr, flush=True), heartbeat=hb)

@@ -47,9 +47,13 @@ class Heartbeat:
     """`store` needs set/get/check (torch.distributed.TCPStore, FileStore, or DictStore)."""
 
     def __init__(self, store, rank: int, world: int, interval: float = 0.2, max_age: float = 2.0,
-                 clock=time.time, prefix: str = "ds41/hb"):
+                 clock=time.time, prefix: str = "ds41/hb", join_grace: float = 10.0):
+        """`join_grace`: how long after this rank's own start a peer may still be without its first beat before it
+        counts as "never joined" (ranks leave their rendezvous at slightly different times)."""
         self.store, self.rank, self.world = store, rank, world
         self.interval, self.max_age, self.clock, self.prefix = interval, max_age, clock, prefix
+        self.join_grace = join_grace
+        self._born = clock()
         self._stop = threading.Event()
         self._thread: Optional[threading.Thread] = None
         self.beat()
@@ -68,6 +72,19 @@ class Heartbeat:
         self._thread = threading.Thread(target=loop, name="ds41-heartbeat", daemon=True)
         self._thread.start()
         return self
+
+    def wait_joined(self, timeout: float = 30.0) -> bool:
+        """Block until every peer has posted its first beat (or `timeout` real seconds pass)."""
+        keys = [f"{self.prefix}/{r}" for r in range(self.world) if r != self.rank]
+        deadline = time.time() + timeout
+        while time.time() < deadline:
+            try:
+                if self.store.check(keys):
+                    return True
+            except Exception:
+                return False
+            time.sleep(min(0.05, self.interval))
+        return False
 
     def stop(self) -> None:
         self._stop.set()
@@ -95,7 +112,8 @@ class Heartbeat:
                     continue
                 key = f"{self.prefix}/{r}"
                 if not self.store.check([key]):
-                    down[r] = "never joined"
+                    if now - self._born >= self.join_grace:
+                        down[r] = "never joined"
                     continue
                 age = now - float(self.store.get(key).decode())
                 if age > self.max_age:

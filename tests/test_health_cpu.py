@@ -13,9 +13,11 @@ from ds41rt_b200.parallel.health import DictStore, Heartbeat, RankFailure
 def test_silent_left_and_missing_ranks_with_a_fake_clock():
     now = [100.0]
     store = DictStore()
-    hb = [Heartbeat(store, r, 4, max_age=2.0, clock=lambda: now[0]) for r in range(3)]   # rank 3 never joins
+    hb = [Heartbeat(store, r, 4, max_age=2.0, clock=lambda: now[0], join_grace=1.0) for r in range(3)]   # rank 3 never joins
+    assert hb[0].peers_down() == {}                  # still within the joining grace
+    now[0] += 1.0
     assert hb[0].peers_down() == {3: "never joined"}
-    now[0] += 1.5
+    now[0] += 0.5
     hb[0].beat(); hb[1].beat()                       # rank 2 goes silent
     now[0] += 1.0
     down = hb[0].peers_down()
@@ -60,7 +62,8 @@ def _rank(rank, world, port, store_port, mode, q):
     store = dist.TCPStore("127.0.0.1", store_port, world, is_master=False)      # hosted by the launcher
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=__import__("datetime").timedelta(seconds=20))
     import torch
-    hb = Heartbeat(store, rank, world, interval=0.05, max_age=0.6).start()
+    hb = Heartbeat(store, rank, world, interval=0.05, max_age=1.5).start()
+    hb.wait_joined(30.0)                             # ranks leave the rendezvous at slightly different times
     steps, failure = 0, None
     try:
         for step in range(60):
@@ -71,14 +74,14 @@ def _rank(rank, world, port, store_port, mode, q):
                     break
                 if mode == "die":
                     hb.stop()                        # goes silent without a note; stays out of further collectives
-                    time.sleep(2.0)
+                    time.sleep(4.0)
                     break
             t = torch.ones(4)
             try:
                 dist.all_reduce(t)
             except RuntimeError:
                 # the peer left while this collective was already posted: the store says who and why
-                deadline = time.time() + 3.0
+                deadline = time.time() + 5.0
                 while time.time() < deadline and not hb.peers_down():
                     time.sleep(0.05)
                 hb.guard()

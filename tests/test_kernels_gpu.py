@@ -314,34 +314,6 @@ def test_hc_step_matches_unfused_kernels():
     assert torch.equal(xq.cpu().view(torch.float8_e4m3fn).float(), wq.float())
 
 
-def test_candidate_blocks():
-    """block-max over 8-position blocks and expansion of selected blocks into causal position lists."""
-    from ds41rt_b200.ops import lib
-    k = lib.kernels()
-    torch.manual_seed(4)
-    rows, n_keys, block, topk = 3, 1000, 8, 16
-    scores = torch.randn(rows, 1024, device="cuda")
-    scores[:, n_keys:] = float("-inf")
-    scores[1, 500:] = float("-inf")
-    n_blocks = (n_keys + block - 1) // block
-    out = torch.zeros(rows, n_blocks, device="cuda")
-    lib.check(k.ds41_block_max(lib.ptr(scores), C.c_longlong(1024), rows, n_keys, block, lib.ptr(out), lib.stream()), "bm")
-    want = scores[:, :n_blocks * block].reshape(rows, n_blocks, block).amax(-1)
-    assert torch.equal(out, want)
-    blocks = out.topk(topk, dim=1).indices.int().contiguous()
-    blocks[2, 10:] = -1
-    limit = torch.tensor([n_keys, 500, 77], dtype=torch.int32, device="cuda")
-    pos = torch.zeros(rows, topk * block, dtype=torch.int32, device="cuda")
-    count = torch.zeros(rows, dtype=torch.int32, device="cuda")
-    lib.check(k.ds41_expand_blocks(lib.ptr(blocks), rows, topk, block, lib.ptr(limit), lib.ptr(pos), lib.ptr(count),
-                                   lib.stream()), "expand")
-    ref = blocks.long()[:, :, None] * block + torch.arange(block, device="cuda")
-    ref = torch.where(blocks[:, :, None] < 0, torch.full_like(ref, -1), ref).reshape(rows, -1)
-    ref = torch.where(ref >= limit[:, None], torch.full_like(ref, -1), ref)
-    assert torch.equal(pos.long(), ref)
-    assert torch.equal(count.long(), (ref >= 0).sum(1))
-
-
 def test_index_scores_on_tensor_cores_match_the_scalar_kernel():
     """One request, a long pass: RoPE'd queries x gathered keys as a GEMM with the relu / head-weight / head-sum
     epilogue gives the scores of the per-key kernel (same bf16 operands, fp32 accumulation)."""
