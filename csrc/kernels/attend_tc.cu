@@ -81,6 +81,51 @@ __device__ __forceinline__ void st_shared16(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 // byte offset of 16-byte chunk `ch` (8 bf16) of row `row` inside a tile stored as D/64 panels of [64 rows][128 B]
+// 16 E4M3 values (one UE8M0 scale: a power of two, so the products are exact) -> 16 bf16 in two 16-byte chunks.
+__device__ __forceinline__ void expand_fp8x16(const uint4& raw, uint32_t scale_e8m0, uint4& o0, uint4& o1) {
+  const float sc = __uint_as_float(scale_e8m0 ? scale_e8m0 << 23 : 0x00400000u);     // 2^(e - 127); e = 0 is 2^-127
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const __nv_fp8x2_storage_t pair = static_cast<__nv_fp8x2_storage_t>((w[i >> 1] >> (16 * (i & 1))) & 0xffffu);
+    const float2 f = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3)));
+    const __nv_bfloat162 v = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+    o[i] = *reinterpret_cast<const uint32_t*>(&v);
+  }
+  o0 = make_uint4(o[0], o[1], o[2], o[3]);
+  o1 = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+// 16 E2M1 values (8 bytes, low nibble first; one E4M3 scale) -> 16 bf16.  Magnitudes come from two byte tables through
+// the byte-permute unit (the three magnitude bits of four values select four table bytes at once), the signs from its
+// sign-replication mode; a value has at most 2 significant bits and the scale 4, so the bf16 products are exact.
+__device__ __forceinline__ void expand_fp4x16(uint32_t x, uint32_t y, uint32_t scale_e4m3, uint4& o0, uint4& o1) {
+  const __half_raw hs = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(scale_e4m3 & 0xffu), __NV_E4M3);
+  const __nv_bfloat162 sc2 = __float2bfloat162_rn(__half2float(__half(hs)));
+  const uint32_t in[2] = {x, y};
+  uint32_t o[8];
+#pragma unroll
+  for (int h = 0; h < 4; ++h) {
+    const uint32_t word = in[h >> 1], word4 = word << 4;
+    const uint32_t sel = ((h & 1) ? word >> 16 : word) & 0x7777u;
+    const uint32_t lo = __byte_perm(0xC0800000u, 0xC0804000u, sel);     // low bytes of bf16 {0, .5, 1, 1.5, 2, 3, 4, 6}
+    const uint32_t hi = __byte_perm(0x3F3F3F00u, 0x40404040u, sel);     // high bytes
+    uint32_t w0 = __byte_perm(lo, hi, 0x5140u), w1 = __byte_perm(lo, hi, 0x7362u);
+    // bit 15 / 31 of a pair <- sign nibble bits of its two values (most significant bit of a byte of word << 4 / word)
+    const uint32_t m0 = __byte_perm(word4, word, (h & 1) ? 0xE0A0u : 0xC080u);
+    const uint32_t m1 = __byte_perm(word4, word, (h & 1) ? 0xF0B0u : 0xD090u);
+    w0 ^= m0 & 0x80008000u;
+    w1 ^= m1 & 0x80008000u;
+    const __nv_bfloat162 v0 = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&w0), sc2);
+    const __nv_bfloat162 v1 = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&w1), sc2);
+    o[2 * h] = *reinterpret_cast<const uint32_t*>(&v0);
+    o[2 * h + 1] = *reinterpret_cast<const uint32_t*>(&v1);
+  }
+  o0 = make_uint4(o[0], o[1], o[2], o[3]);
+  o1 = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
 __device__ __forceinline__ uint32_t tile_off(int row, int ch) {
   return static_cast<uint32_t>((ch >> 3) * kPanelBytes + row * 128 + (((ch & 7) ^ (row & 7)) << 4));
 }
@@ -319,57 +364,54 @@ __global__ void __launch_bounds__(kTcThreads, 1) attend_tc_kernel(AttendTcParams
           }
         }
       } else {
-        // quantised rows: every load of the warp's 16 keys is issued before the first conversion.
-        //   FP8 row: D e4m3 values, then one UE8M0 scale per 32 values; lane u expands values [16u, 16u+16)
-        //   FP4 row: D/2 bytes of e2m1 pairs, then one E4M3 scale per 16 values; lane u expands values [32u, 32u+32)
-        uint4 raw[16];
-        uint32_t scs[16];
+        // quantised rows.  Lane u expands values [16u, 16u + 16) of every key - 16 bytes of an FP8 row (one UE8M0
+        // scale per 32 values behind the D values) or 8 bytes of an FP4 row (one E4M3 scale per 16 values behind the
+        // D/2 bytes) - into the two 16-byte chunks 2u, 2u + 1 of the key's tile row.  Keys pass through registers four
+        // at a time, the next four loads in flight while the current four are expanded.  The loop over the groups
+        // stays rolled: unrolled over 16 keys its code does not fit the instruction cache and every tile refetches it.
+        const bool act = lane < D / 16;
+        uint4 nxt[4];
+        uint32_t nsc[4];
+        auto load4 = [&](int grp) {
 #pragma unroll
-        for (int kk = 0; kk < 16; ++kk) {
-          const uint8_t* src = reinterpret_cast<const uint8_t*>(
-              __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_ptr), kk));
-          const bool fp4 = (fp4_mask >> kk) & 1u;
-          raw[kk] = make_uint4(0, 0, 0, 0);
-          scs[kk] = 0;
-          if (src != nullptr && lane < (fp4 ? D / 32 : D / 16)) {
-            raw[kk] = __ldg(reinterpret_cast<const uint4*>(src + lane * 16));
-            scs[kk] = fp4 ? static_cast<uint32_t>(__ldg(reinterpret_cast<const unsigned short*>(src + D / 2 + 2 * lane)))
-                          : static_cast<uint32_t>(__ldg(src + D + (lane >> 1)));
-          }
-        }
-#pragma unroll
-        for (int kk = 0; kk < 16; ++kk) {
-          const int key = lw * 16 + kk;
-          if ((null_mask >> kk) & 1u) {
-            for (int ch = lane; ch < CH; ch += 32) st_shared16(kb + tile_off(key, ch), make_uint4(0, 0, 0, 0));
-          } else if (!((fp4_mask >> kk) & 1u)) {
-            if (lane < D / 16) {
-              const float sc = __uint_as_float(scs[kk] << 23);            // exact: e4m3 value times a power of two
-              const __nv_fp8x2_storage_t* q2 = reinterpret_cast<const __nv_fp8x2_storage_t*>(&raw[kk]);
-              uint4 o[2];
-              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(o);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const float2 f = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(q2[i], __NV_E4M3)));
-                o2[i] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+          for (int u = 0; u < 4; ++u) {
+            const int kk = 4 * grp + u;
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(
+                __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_ptr), kk));
+            nxt[u] = make_uint4(0, 0, 0, 0);
+            nsc[u] = 0;
+            if (src != nullptr && act) {
+              if ((fp4_mask >> kk) & 1u) {
+                const uint2 t = __ldg(reinterpret_cast<const uint2*>(src + lane * 8));
+                nxt[u].x = t.x;
+                nxt[u].y = t.y;
+                nsc[u] = __ldg(src + D / 2 + lane);
+              } else {
+                nxt[u] = __ldg(reinterpret_cast<const uint4*>(src + lane * 16));
+                nsc[u] = __ldg(src + D + (lane >> 1));
               }
-              st_shared16(kb + tile_off(key, 2 * lane), o[0]);
-              st_shared16(kb + tile_off(key, 2 * lane + 1), o[1]);
             }
-          } else if (lane < D / 32) {
-            const uint32_t w4[4] = {raw[kk].x, raw[kk].y, raw[kk].z, raw[kk].w};
+          }
+        };
+        load4(0);
+#pragma unroll 1
+        for (int grp = 0; grp < 4; ++grp) {
+          uint4 cur[4];
+          uint32_t csc[4];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const __half_raw hs = __nv_cvt_fp8_to_halfraw(
-                  static_cast<__nv_fp8_storage_t>((scs[kk] >> (8 * (c >> 1))) & 0xff), __NV_E4M3);
-              const float sc = __half2float(__half(hs));                  // exact: 2-bit mantissa times 4-bit mantissa
-              uint4 o;
-              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+          for (int u = 0; u < 4; ++u) { cur[u] = nxt[u]; csc[u] = nsc[u]; }
+          if (grp < 3) load4(grp + 1);
 #pragma unroll
-              for (int i = 0; i < 4; ++i)
-                o2[i] = __floats2bfloat162_rn(e2m1_value((w4[c] >> (8 * i)) & 15u) * sc,
-                                              e2m1_value((w4[c] >> (8 * i + 4)) & 15u) * sc);
-              st_shared16(kb + tile_off(key, 4 * lane + c), o);
+          for (int u = 0; u < 4; ++u) {
+            const int kk = 4 * grp + u, key = lw * 16 + kk;
+            uint4 o0 = make_uint4(0, 0, 0, 0), o1 = o0;
+            if (!((null_mask >> kk) & 1u)) {
+              if ((fp4_mask >> kk) & 1u) expand_fp4x16(cur[u].x, cur[u].y, csc[u], o0, o1);
+              else expand_fp8x16(cur[u], csc[u], o0, o1);
+            }
+            if (act) {
+              st_shared16(kb + tile_off(key, 2 * lane), o0);
+              st_shared16(kb + tile_off(key, 2 * lane + 1), o1);
             }
           }
         }

@@ -818,7 +818,7 @@ class DS41Engine:
     def _attn_splits(self, rows: int) -> int:
         """Key-tile splits per row: one tile per CTA for a few rows (decode), fewer and longer CTAs once the rows
         alone fill the GPU about two to three CTAs deep (prefill; one split lets the kernel write final rows)."""
-        if A.tc_usable(self.cfg.head_dim, self.HL, rows):
+        if A.tc_usable(self.cfg.head_dim, self.HL, rows, self.cache.row_bytes > 0):
             want = -(-2 * 148 // rows)           # one CTA covers every head of a row
         else:
             want = -(-3 * 148 // (rows * ((self.HL + 15) // 16)))
@@ -1234,7 +1234,7 @@ class DS41Engine:
             Rl=Rl, nqb=nqb, qb=z((Rl, nqb), BF16), attn=z((Rl, NH * D), BF16), oa=z((Rl, cfg.o_groups * cfg.o_lora), BF16),
             # the tensor-core kernel writes final rows when it has one split; the warp-MMA kernels always go through
             # partials
-            part_o=z((Rl * splits if splits > 1 or not A.tc_usable(D, NH, Rl) else 1, NH, D), F32),
+            part_o=z((Rl * splits if splits > 1 or not A.tc_usable(D, NH, Rl, self.cache.row_bytes > 0) else 1, NH, D), F32),
             part_ml=z((Rl * splits, NH, 2), F32),
             planes_o=z((self.max_splits * Rl * cfg.hidden,), F32), planes_gate=z((self.max_splits * Rl * ng,), F32),
             shared_act=z((Rl, cfg.inter), BF16), planes_shared=z((self.max_splits * Rl * cfg.hidden,), F32),

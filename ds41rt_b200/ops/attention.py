@@ -16,15 +16,17 @@ from . import lib
 KEYS_PER_TILE = 64
 
 
-TC_MIN_ROWS = 17      # decode-sized passes (a handful of rows, one key tile per CTA) stay on the warp-MMA kernel
+TC_MIN_ROWS = 17      # decode-sized passes over bf16 rows (a handful of rows, one key tile per CTA) stay on the warp-MMA kernel
 
 
-def tc_usable(D: int, heads: int, rows: int = TC_MIN_ROWS) -> bool:
-    """Does the tensor-core kernel serve this pass?  DS41_ATTN=legacy / tc forces one kernel for every pass."""
+def tc_usable(D: int, heads: int, rows: int = TC_MIN_ROWS, quantised: bool = False) -> bool:
+    """Does the tensor-core kernel serve this pass?  DS41_ATTN=legacy / tc forces one kernel for every pass.
+    Passes over FP8 / FP4 cache rows take it at every size: its gather warps expand a key tile once for all heads
+    (5 rows x 640 keys: 0.023 ms against 0.055 ms)."""
     mode = os.environ.get("DS41_ATTN", "")
     if D not in (128, 512) or heads > 64 or mode == "legacy":
         return False
-    return mode == "tc" or rows >= TC_MIN_ROWS
+    return mode == "tc" or quantised or rows >= TC_MIN_ROWS
 
 
 def attend(*, q, ldq, q_off, rows, heads, D, window, ring, row_pos, row_slot, win, comp_pool, sel, n_sel, k,
@@ -33,7 +35,7 @@ def attend(*, q, ldq, q_off, rows, heads, D, window, ring, row_pos, row_slot, wi
     """Enqueue the attention of one pass on the current stream.  `impl`: None (pick), "tc" or "legacy"."""
     kern = lib.kernels()
     if impl is None:
-        impl = "tc" if tc_usable(D, heads, rows) else "legacy"
+        impl = "tc" if tc_usable(D, heads, rows, kv_row_bytes > 0) else "legacy"
     if impl == "legacy":
         return kern.ds41_attend_kv(
             lib.ptr(q), C.c_longlong(ldq), q_off, rows, heads, D, window, ring, lib.ptr(row_pos), lib.ptr(row_slot),
