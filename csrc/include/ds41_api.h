@@ -199,6 +199,10 @@ int ds41_moe_combine(const float* fc2, const int* slot_of, const float* shared, 
 int ds41_signal(uint32_t* epoch, uint32_t* flag, void* stream);
 int ds41_reduce_planes(const float* planes, int splits, long long plane, void* out, int as_bf16, long long n,
                        void* stream);
+// planes [split][group][rows][width] fp32 (split-K partials of a grouped projection) -> bf16 out [rows][ld_out],
+// group g in columns [g * width, (g + 1) * width)
+int ds41_reduce_groups(const float* planes, int splits, int groups, int rows, int width, void* out, long long ld_out,
+                       void* stream);
 
 // ---------------------------------------------------------------------------------------------------
 // Head epilogues (sampler.cu)

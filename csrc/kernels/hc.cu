@@ -91,12 +91,23 @@ hc_post_mix_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, 
       }
       if (parts.n_ranks > 0) {
         float sub[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int k = 0; k < parts.n_ranks; ++k)
-          for (int sp = 0; sp < parts.n_splits; ++sp) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(parts.base[k] + sp * parts.split_stride +
-                                                                    1ll * r * H + c0 + c));
-            sub[0] += v.x; sub[1] += v.y; sub[2] += v.z; sub[3] += v.w;
+        // rank-major, split-minor order; eight plane loads in flight before the first add (peer loads are slow)
+        const int n_sp = parts.n_splits, total = parts.n_ranks * n_sp;
+        for (int j0 = 0; j0 < total; j0 += 8) {
+          float4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int j = j0 + u;
+            v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (j < total) {
+              const int k = j / n_sp, sp = j - k * n_sp;
+              v[u] = __ldcg(reinterpret_cast<const float4*>(parts.base[k] + sp * parts.split_stride +
+                                                            1ll * r * H + c0 + c));
+            }
           }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) { sub[0] += v[u].x; sub[1] += v[u].y; sub[2] += v[u].z; sub[3] += v[u].w; }
+        }
         float cm[16], pw[4];
 #pragma unroll
         for (int q = 0; q < 16; ++q) cm[q] = comb[r * 16 + q];

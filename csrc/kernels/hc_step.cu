@@ -82,11 +82,24 @@ __global__ void __launch_bounds__(256) hc_step_kernel(HcStepParams p) {
 #pragma unroll
     for (int s = 0; s < kMult; ++s) s_in[s] = __bfloat162float(p.streams_in[(1ll * r * kMult + s) * H + c]);
     if (p.parts.n_ranks > 0) {
+      // Partial planes of every rank, summed in rank-major, split-minor order.  The loads of 32 planes are issued
+      // before the first add: a load from a peer takes a few microseconds, and one at a time they were most of this
+      // kernel's time on 8 GPUs.
       float sub = 0.f;
-      for (int k = 0; k < p.parts.n_ranks; ++k) {
-        const float* src = p.parts.base[k] + 1ll * r * H + c;
-#pragma unroll 4
-        for (int sp = 0; sp < p.parts.n_splits; ++sp) sub += src[sp * p.parts.split_stride];
+      const int n_sp = p.parts.n_splits, total = p.parts.n_ranks * n_sp;
+      for (int j0 = 0; j0 < total; j0 += 32) {
+        float v[32];
+#pragma unroll
+        for (int u = 0; u < 32; ++u) {
+          const int j = j0 + u;
+          v[u] = 0.f;
+          if (j < total) {
+            const int k = j / n_sp, sp = j - k * n_sp;
+            v[u] = p.parts.base[k][1ll * r * H + c + sp * p.parts.split_stride];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 32; ++u) sub += v[u];
       }
       sub = bf16_round(sub);
 #pragma unroll

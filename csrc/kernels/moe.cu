@@ -222,9 +222,40 @@ __global__ void reduce_planes_kernel(const float* planes, int splits, long long 
   }
 }
 
+// ---- split-K planes of a grouped projection, [split][group][rows][width] fp32 -> bf16 [rows][ld_out] with group g in
+// columns [g * width, (g + 1) * width); the splits are summed in order
+__global__ void reduce_groups_kernel(const float* planes, int splits, int groups, int rows, int width,
+                                     __nv_bfloat16* out, long long ld_out) {
+  const long long i = (1ll * blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long per_split = 1ll * groups * rows * width;
+  if (i >= per_split) return;
+  float a = 0.f, b = 0.f;
+#pragma unroll 4
+  for (int s = 0; s < splits; ++s) {
+    const float2 v = *reinterpret_cast<const float2*>(planes + s * per_split + i);
+    a += v.x;
+    b += v.y;
+  }
+  const int c = static_cast<int>(i % width);
+  const long long gr = i / width;
+  const int r = static_cast<int>(gr % rows), g = static_cast<int>(gr / rows);
+  *reinterpret_cast<__nv_bfloat162*>(out + r * ld_out + 1ll * g * width + c) = __floats2bfloat162_rn(a, b);
+}
+
 }  // namespace ds41
 
 using namespace ds41;
+
+extern "C" int ds41_reduce_groups(const float* planes, int splits, int groups, int rows, int width, void* out,
+                                  long long ld_out, void* stream) {
+  if (splits <= 0 || groups <= 0 || rows <= 0 || width <= 0 || (width & 1) || (ld_out & 1)) return cudaErrorInvalidValue;
+  const long long threads = 1ll * groups * rows * width / 2;
+  return launch_pdl(reduce_groups_kernel, dim3(static_cast<unsigned>((threads + 255) / 256)), dim3(256), 0,
+                    static_cast<cudaStream_t>(stream), planes, splits, groups, rows, width,
+                    static_cast<__nv_bfloat16*>(out), ld_out);
+}
 
 extern "C" int ds41_router_select(const float* planes, int splits, int rows, int ntot, int E, int I_sh, int topk,
                                   const float* bias, float route_scale, float limit, int* ids, float* weights,

@@ -84,10 +84,22 @@ __global__ void argmax_merge_kernel(MergeArgs p) {
   if (r >= p.rows) return;
   float v = -INFINITY;
   int idx = -1;
-  for (int k = 0; k < p.n_ranks; ++k) {
-    const float ov = p.vals[k][r];
-    const int oi = p.idxs[k][r];
-    if (oi >= 0 && (idx < 0 || ov > v || (ov == v && oi < idx))) { v = ov; idx = oi; }
+  // every rank's candidate is requested before the first comparison: a peer load takes a few microseconds
+  for (int k0 = 0; k0 < p.n_ranks; k0 += 8) {
+    float ovs[8];
+    int ois[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      ovs[u] = -INFINITY;
+      ois[u] = -1;
+      if (k0 + u < p.n_ranks) { ovs[u] = p.vals[k0 + u][r]; ois[u] = p.idxs[k0 + u][r]; }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const float ov = ovs[u];
+      const int oi = ois[u];
+      if (oi >= 0 && (idx < 0 || ov > v || (ov == v && oi < idx))) { v = ov; idx = oi; }
+    }
   }
   p.out[r] = idx;
 }

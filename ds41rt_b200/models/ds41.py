@@ -716,6 +716,7 @@ class DS41Engine:
         self.part_ml = z((cells, self.HL, 2), F32)
         self.attn_out = z((R, self.HL * D), BF16)
         self.oa = z((R, self.GL * cfg.o_lora), BF16)
+        self.planes_oa = z((self.max_splits * self.GL * min(R, 16) * cfg.o_lora,), F32)    # split-K partials of wo_a
         # MoE
         self.ntot_gate = E + 2 * self.I_sh
         self.planes_gate = z((self._plane_rows(self.ntot_gate), self.ntot_gate), F32)
@@ -814,6 +815,13 @@ class DS41Engine:
             bn = G.pick_bn(r)
             best = max(best, r * G.pick_splits(m, 1 << 20, max_splits=self.max_splits, n_tiles=(r + bn - 1) // bn))
         return best
+
+    def _wo_a_splits(self, rows: int) -> int:
+        """Split-K factor of the grouped wo_a projection (one batch entry per local head group)."""
+        if rows > self.fused_rows:
+            return 1
+        kg = self.cfg.heads_per_group * self.cfg.head_dim
+        return G.pick_splits(self.cfg.o_lora, kg, max_splits=self.max_splits, batch=self.GL)
 
     def _attn_splits(self, rows: int) -> int:
         """Key-tile splits per row: one tile per CTA for a few rows (decode), fewer and longer CTAs once the rows
@@ -1100,9 +1108,21 @@ class DS41Engine:
                       row_hi=self.row_hi, row_lo=self.row_lo if self._floor_on else None, status=self.status)
             # grouped wo_a: batch = local groups
             kg = cfg.heads_per_group * D
-            self._run("gemm_wo_a", G.gemm_raw, lw.wo_a, self.attn_out, self.oa, cfg.o_lora, R, kg, lda=kg, ldb=self.HL * D,
-                       ldo=self.GL * cfg.o_lora, out_mode=2, batch=self.GL, a_batch_stride=cfg.o_lora * kg,
-                       b_batch_stride=kg, out_batch_stride=cfg.o_lora, status=self.status, static_operand=1)
+            s_a = self._wo_a_splits(R)
+            if s_a > 1:
+                # few rows: the K loop of one CTA per (group, 128 outputs) is a latency chain, so it is split over
+                # CTAs and the fp32 partials are summed into the bf16 rows by one small kernel
+                self._run("gemm_wo_a", G.gemm_raw, lw.wo_a, self.attn_out, None, cfg.o_lora, R, kg, lda=kg,
+                          ldb=self.HL * D, ldo=cfg.o_lora, out_mode=3, k_splits=s_a, split_workspace=self.planes_oa,
+                          batch=self.GL, a_batch_stride=cfg.o_lora * kg, b_batch_stride=kg, status=self.status,
+                          static_operand=1)
+                self._run("reduce_groups", k.ds41_reduce_groups, lib.ptr(self.planes_oa), s_a, self.GL, R, cfg.o_lora,
+                          lib.ptr(self.oa), C.c_longlong(self.GL * cfg.o_lora), st())
+            else:
+                self._run("gemm_wo_a", G.gemm_raw, lw.wo_a, self.attn_out, self.oa, cfg.o_lora, R, kg, lda=kg,
+                          ldb=self.HL * D, ldo=self.GL * cfg.o_lora, out_mode=2, batch=self.GL,
+                          a_batch_stride=cfg.o_lora * kg, b_batch_stride=kg, out_batch_stride=cfg.o_lora,
+                          status=self.status, static_operand=1)
             ko = self.GL * cfg.o_lora
             s_o = self._splits(H, ko, R)
             self._run("gemm_wo_b", G.linear_planes, self.oa[:R], lw.wo_b, self.planes_o.view(-1)[: s_o * R * H].view(s_o, R, H), s_o,
