@@ -234,6 +234,10 @@ typedef struct {
 int ds41_markov_step(const float* logits, const void* head, const void* embed, const int* prev_token, int v_local,
                      int v_offset, int rank, int vocab, float* block_val, int* block_idx, int n_blocks,
                      unsigned int* ticket, float* best_val, int* best_idx, const ds41_draft_rng* rng, void* stream);
+// Confidence head of the drafter: out[j] = weight . [hidden[j] (fp32, H) | embed[prev_j] (bf16, rank)], raw (no sigmoid);
+// prev_0 = anchor[0], prev_j = drafts[j - 1].
+int ds41_dspark_confidence(const float* hidden, long long ld_hidden, const void* embed, int rank, const int* anchor,
+                           const int* drafts, const void* weight, float* out, int rows, int H, int vocab, void* stream);
 int ds41_spec_feedback(const int* inputs, const int* chosen, int width, int forced_accept, int eos, int* accepted,
                        int* emitted, int* n_emitted, int* next_anchor, int* target_pos, int* draft_pos,
                        int* draft_hi, int* target_tokens, int* draft_tokens, long long* total_emitted, void* stream);

@@ -217,9 +217,46 @@ __global__ void copy_ints_kernel(const int* src, int* dst, int n) {
   if (i < n) dst[i] = src[i];
 }
 
+// ---- confidence head: raw projection of [collapsed hidden row | Markov embedding of the previous token] per draft row.
+// Row j's previous token is the anchor (j = 0) or draft j - 1.  The consumer applies the sigmoid.
+// Reference: native/cuda/kernels/v41_dspark.cu:40-58 (same inputs, promoted to fp32, one block per row).
+__global__ void __launch_bounds__(256) confidence_kernel(const float* __restrict__ hidden, long long ld_hidden,
+                                                         const __nv_bfloat16* __restrict__ embed, int rank,
+                                                         const int* __restrict__ anchor, const int* __restrict__ drafts,
+                                                         const __nv_bfloat16* __restrict__ weight, float* __restrict__ out,
+                                                         int H, int vocab) {
+  __shared__ float partial[8];
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
+  int prev = row == 0 ? anchor[0] : drafts[row - 1];
+  prev = min(max(prev, 0), vocab - 1);
+  float sum = 0.f;
+  for (int c = tid; c < H + rank; c += 256) {
+    const float x = c < H ? hidden[row * ld_hidden + c] : __bfloat162float(embed[1ll * prev * rank + (c - H)]);
+    sum = fmaf(x, __bfloat162float(weight[c]), sum);
+  }
+  sum = warp_sum(sum);
+  if (lane == 0) partial[warp] = sum;
+  __syncthreads();
+  if (warp == 0) {
+    sum = warp_sum(lane < 8 ? partial[lane] : 0.f);
+    if (lane == 0) out[row] = sum;
+  }
+}
+
 }  // namespace ds41
 
 using namespace ds41;
+
+extern "C" int ds41_dspark_confidence(const float* hidden, long long ld_hidden, const void* embed, int rank,
+                                      const int* anchor, const int* drafts, const void* weight, float* out, int rows,
+                                      int H, int vocab, void* stream) {
+  if (rows <= 0 || H <= 0 || rank <= 0 || vocab <= 0) return cudaErrorInvalidValue;
+  return launch_pdl(confidence_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), hidden, ld_hidden,
+                    static_cast<const __nv_bfloat16*>(embed), rank, anchor, drafts,
+                    static_cast<const __nv_bfloat16*>(weight), out, H, vocab);
+}
 
 extern "C" int ds41_taps_pack(const float* taps, void* out, int n_taps, int rows, int H, long long tap_stride,
                               void* stream) {

@@ -55,6 +55,8 @@ class DSparkDrafter:
             self.markov_embed = to(weights[f"mtp.{last}.markov_head.embed.weight"])
             v0 = rank * target.V_local
             self.markov_head = to(weights[f"mtp.{last}.markov_head.head.weight"][v0:v0 + target.V_local])
+            conf = weights.get(f"mtp.{last}.confidence_head.proj.weight")
+            self.conf_w = to(conf.reshape(-1)) if conf is not None else None
         else:
             ew = EngineWeights.random(dcfg, rank, world, dev, seed=seed + 77, share=target.w,
                                       expert_dtype=expert_dtype)
@@ -64,6 +66,7 @@ class DSparkDrafter:
             self.main_norm = torch.ones(H, dtype=F32, device=dev)
             self.markov_embed = rnd(cfg.vocab, d.markov_rank)
             self.markov_head = rnd(target.V_local, d.markov_rank)
+            self.conf_w = rnd(H + d.markov_rank)
         R = max(target.max_rows, self.width)
         self.eng = DS41Engine(dcfg, ew, target.fabric, max_rows=R, slots=target.cache.slots, max_ctx=64,
                               row_hi=True)
@@ -78,6 +81,7 @@ class DSparkDrafter:
         self.ticket = z((1,), I32)
         self.drafts = z((self.width,), I32)          # drafts[j] = proposed token for position p + 1 + j
         self.draft_val = z((self.width,), F32)
+        self.confidence = z((self.width,), F32)      # raw confidence-head output per draft row (sigmoid on the host)
         self.launches = 0
 
     # ------------------------------------------------------------------ conditioning
@@ -141,6 +145,11 @@ class DSparkDrafter:
             else:
                 e._run("draft_take", k.ds41_copy_ints, lib.ptr(e.best_idx[j:j + 1]), lib.ptr(self.drafts[j:j + 1]), 1,
                        lib.stream())
+        if self.conf_w is not None:
+            # collapsed (pre-norm) rows of the last stage and the Markov embedding each position was conditioned on
+            e._run("confidence", k.ds41_dspark_confidence, lib.ptr(e.xc), C.c_longlong(self.cfg.hidden),
+                   lib.ptr(self.markov_embed), rank, lib.ptr(e.in_tokens[0:1]), lib.ptr(self.drafts),
+                   lib.ptr(self.conf_w), lib.ptr(self.confidence), w, self.cfg.hidden, self.cfg.vocab, lib.stream())
 
 
 def _offset_ptrs(ptrs, offset_bytes: int, n: int):

@@ -36,6 +36,8 @@ class SpecSession:
         self.graph = None
         self.launches_per_round = 0
         self.h_out = torch.zeros(self.width + 2, dtype=torch.int32).pin_memory()
+        self.h_conf = torch.zeros(self.width, dtype=torch.float32).pin_memory()
+        self.last_confidence: List[float] = []      # sigmoid of the drafter's confidence head, one per draft row
         self.h_in = torch.zeros(1 + 2 * self.width, dtype=torch.int32).pin_memory()
         self._host_state = None
         self.h2d_bytes = self.d2h_bytes = 0
@@ -120,8 +122,10 @@ class SpecSession:
         self.h_out[:w].copy_(self.emitted, non_blocking=True)
         self.h_out[w: w + 1].copy_(self.n_emitted, non_blocking=True)
         self.h_out[w + 1: w + 2].copy_(self.t.row_pos[0:1], non_blocking=True)
+        self._read_confidence()
         torch.cuda.current_stream().synchronize()
         self.d2h_bytes += 4 * (w + 2)
+        self._publish_confidence()
         n = int(self.h_out[w])
         toks = self.h_out[:n].tolist()
         self._host_state = (toks[-1], int(self.h_out[w + 1]))
@@ -136,9 +140,20 @@ class SpecSession:
         self.d.set_draft_rows(anchor, pos, slot)
         self.d.draft()
         self.h_out[: w - 1].copy_(self.d.drafts[: w - 1], non_blocking=True)
+        self._read_confidence()
         torch.cuda.current_stream().synchronize()
         self.d2h_bytes += 4 * (w - 1)
+        self._publish_confidence()
         return self.h_out[: w - 1].tolist()
+
+    def _read_confidence(self):
+        if self.d.conf_w is not None:
+            self.h_conf.copy_(self.d.confidence, non_blocking=True)
+            self.d2h_bytes += 4 * self.width
+
+    def _publish_confidence(self):
+        if self.d.conf_w is not None:
+            self.last_confidence = torch.sigmoid(self.h_conf).tolist()
 
     def verify_host(self, slot: int, inputs: List[int], pos: int) -> None:
         """Target pass over [anchor, drafts...] at positions pos..; the logits of every row stay in the engine and the

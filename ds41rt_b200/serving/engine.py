@@ -164,11 +164,10 @@ class NativeBackend(Backend):
         self.spec = None
         self.policy = None
         # runtime.engram.EngramPipeline or None.  Every pass hands its token ids to the pipeline first (hashes, page
-        # advice, gather requests), runs, and commits the rows it kept.  Speculative rounds keep their draft tokens on
-        # the device, so a backend with Engram layers decodes without the drafter.
+        # advice, gather requests), runs, and commits the rows it kept.  With Engram layers a speculative round reads
+        # its drafts back before the target pass (the n-gram hashes of the verification rows need them) and commits
+        # only the accepted rows to the slot's history.
         self.engram = engram
-        if engram is not None:
-            drafter = None
         if drafter is not None:
             from ..runtime.speculative import SpecSession
             self.spec = SpecSession(engine, drafter)
@@ -651,7 +650,7 @@ class NativeBackend(Backend):
         """One speculative round for the only active request: up to `width` tokens come back."""
         import torch
         r = a.req
-        plain = r.sampling.greedy and r.constraint is None
+        plain = r.sampling.greedy and r.constraint is None and self.engram is None
         timed = self.e.device.type == "cuda"
         if timed:
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -668,7 +667,9 @@ class NativeBackend(Backend):
         if timed:
             ev1.record()
             ev1.synchronize()
-            self.policy.observe(drafts_checked, max(0, len(toks) - 1), ev0.elapsed_time(ev1) * 1e3)
+            conf = self.spec.last_confidence
+            self.policy.observe(drafts_checked, max(0, len(toks) - 1), ev0.elapsed_time(ev1) * 1e3,
+                                confidence=conf[0] if conf else -1.0)
         self.totals["rounds"] += 1
         self.totals["spec_rounds"] += 1
         self.totals["spec_tokens"] += len(toks)
@@ -690,6 +691,9 @@ class NativeBackend(Backend):
         r, sp, e = a.req, self.spec, self.e
         w = sp.width
         drafts = sp.draft_host(a.slot, a.last, a.pos)                    # w - 1 proposed tokens
+        if sp.last_confidence:
+            # verification length from the policy, given how sure the drafter is of its first token
+            drafts = drafts[: max(0, self.policy.choose(sp.last_confidence[0]))]
         if r.constraint is not None:
             drafts = r.constraint.truncate_proposal(drafts)
         remaining = r.max_tokens - a.emitted
@@ -697,12 +701,15 @@ class NativeBackend(Backend):
         inputs = [a.last] + drafts
         n = len(inputs)
         masks = r.constraint.row_masks(inputs) if r.constraint is not None else None
+        ep = self._engram_pass(inputs, [a.slot] * n)                     # table rows of the n verification rows
         sp.verify_host(a.slot, inputs, a.pos)                            # target pass over the n rows, rings fed
         picked = self._select([r] * n, list(range(n)), positions=[a.emitted + i for i in range(n)], masks=masks)
         accepted = 0
         while accepted < n - 1 and picked[accepted] == drafts[accepted] and picked[accepted] != self.eos \
                 and picked[accepted] not in r.stop_ids:
             accepted += 1
+        if ep is not None:
+            self.engram.commit(ep, {a.slot: accepted + 1})               # the anchor and the accepted drafts
         return picked[: accepted + 1], len(drafts)
 
     # ------------------------------------------------------------------ decode rounds

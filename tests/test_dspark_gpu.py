@@ -5,13 +5,16 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _build(max_rows=8):
+def _build(max_rows=8, stages=None):
+    import dataclasses
     from ds41rt_b200.config import ModelConfig
     from ds41rt_b200.models.weights import init_weights
     from ds41rt_b200.models.reference import ReferenceModel
     from ds41rt_b200.models.ds41 import EngineWeights, DS41Engine
     from ds41rt_b200.models.dspark import DSparkDrafter
     cfg = ModelConfig.tiny()
+    if stages is not None:
+        cfg = dataclasses.replace(cfg, dspark=dataclasses.replace(cfg.dspark, stages=stages))
     w = init_weights(cfg, seed=0)
     wr = {k: (v.bfloat16().float() if v.dim() == 2 and not k.endswith("_fn") else v) for k, v in w.items()}
     ref = ReferenceModel(cfg, wr)
@@ -111,3 +114,51 @@ def test_sampled_draft_step_follows_the_philox_gumbel_rule():
     got = run(lib.DraftRng(T, seed, sub, off))
     assert float(keys.max() - keys[got]) < 1e-3
     assert got != run(lib.DraftRng(T, seed, sub + 1, off)) or got != run(lib.DraftRng(T, seed + 1, sub, off))
+
+
+def test_three_stage_drafter_matches_oracle_and_stays_lossless():
+    """The release drafter has three stages (the tiny preset has one): logits against the oracle, then greedy
+    speculative decoding against plain greedy decoding, eagerly and through the captured round."""
+    from ds41rt_b200.runtime.session import DecodeSession
+    from ds41rt_b200.runtime.speculative import SpecSession
+    cfg, ref, eng, drafter = _build(stages=3)
+    assert drafter.eng.n_layers == 3
+    g = torch.Generator().manual_seed(11)
+    prompt = torch.randint(0, cfg.vocab, (40,), generator=g)
+    with torch.no_grad():
+        _, taps = ref.forward(prompt, return_taps=True)
+    main = ref.dspark_main(taps)
+    sess = SpecSession(eng, drafter, use_graphs=False)
+    first = sess.start(0, prompt.tolist(), 16)
+    _, want_logits = ref.dspark_draft(main, first, drafter.width)
+    drafter.draft()
+    torch.cuda.synchronize()
+    drafter.eng.check_status()
+    got = drafter.eng.logits[: drafter.width].float().cpu()
+    assert float((got - want_logits).abs().max()) < 0.08 * float(want_logits.abs().max())
+    prompt2 = torch.randint(0, cfg.vocab, (37,), generator=torch.Generator().manual_seed(5)).tolist()
+    plain = DecodeSession(eng, use_graphs=False).generate(prompt2, 24, slot=1)
+    for graphs in (False, True):
+        out = SpecSession(eng, drafter, use_graphs=graphs).generate(prompt2, 24, slot=0)
+        assert out == plain, graphs
+
+
+def test_confidence_head_projects_collapsed_rows_and_markov_embeddings():
+    """confidence[j] = w . [collapsed hidden row j of the last stage | Markov embedding of the token before draft j]
+    (raw, fp32), read back with the drafts as probabilities."""
+    from ds41rt_b200.runtime.speculative import SpecSession
+    cfg, ref, eng, drafter = _build()
+    assert drafter.conf_w is not None
+    sess = SpecSession(eng, drafter, use_graphs=False)
+    anchor = sess.start(0, list(range(20, 60)), 16)
+    drafts = sess.draft_host(0, anchor, 40)
+    torch.cuda.synchronize()
+    w, H = drafter.width, cfg.hidden
+    prev = torch.tensor([anchor] + drafter.drafts[: w - 1].tolist(), device="cuda")
+    x = torch.cat([drafter.eng.xc[:w].float(), drafter.markov_embed[prev].float()], dim=1)
+    want = x.double() @ drafter.conf_w.double()
+    got = drafter.confidence[:w].double()
+    assert float((got - want).abs().max()) < 1e-3 * (1.0 + float(want.abs().max()))
+    assert len(sess.last_confidence) == w and all(0.0 <= c <= 1.0 for c in sess.last_confidence)
+    assert abs(sess.last_confidence[0] - float(torch.sigmoid(want[0]))) < 1e-3
+    assert len(drafts) == w - 1

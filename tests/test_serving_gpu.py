@@ -379,6 +379,63 @@ def test_engram_pipeline_serves_requests(tmp_path):
     assert plain != want                                  # the memory layer changes what is generated
 
 
+def test_engram_backend_speculates_losslessly(tmp_path):
+    """An engine with an Engram layer and a drafter: the drafts come back to the host before the verification pass (the
+    n-gram hashes of its rows need them), only the accepted rows advance the slot's history, and the request emits what
+    the same engine emits without the drafter."""
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    from ds41rt_b200.models.dspark import DSparkDrafter
+    from ds41rt_b200.models.engram import EngramLayer, init_engram_weights, random_table_rows
+    from ds41rt_b200.runtime.engram import EngramPipeline
+    from ds41rt_b200.runtime.engram_io import EngramTable
+    from ds41rt_b200.serving.engine import GenRequest, NativeBackend
+    from ds41rt_b200.serving.protocol import Sampling
+    cfg = ModelConfig.tiny()
+    dev = torch.device("cuda", 0)
+    w = EngineWeights.random(cfg, 0, 1, dev, seed=0)
+    n_rows = 4096
+    path = str(tmp_path / "engram.bin")
+    random_table_rows(n_rows, seed=2).numpy().tofile(path)
+    wkv, q_w, k_w = init_engram_weights(cfg.hidden, seed=4, std=0.002)
+    bf = lambda t: t.bfloat16().to(dev)
+
+    def backend(with_drafter):
+        eng = DS41Engine(cfg, w, max_rows=8, slots=2, max_ctx=512)
+        eng.attach_engram(1, EngramLayer(bf(wkv), bf(q_w), bf(k_w), cfg.hidden))
+        pipe = EngramPipeline([1], [EngramTable(path, n_rows, 264)], pad_id=2, max_rows=8, fold=True)
+        drafter = DSparkDrafter(cfg, eng, weights=None, seed=0) if with_drafter else None
+        return NativeBackend(eng, eos=1, concurrency=2, engram=pipe, drafter=drafter)
+
+    def run(b, prompt, n):
+        r = GenRequest(prompt_ids=prompt, max_tokens=n, sampling=Sampling(temperature=0.0))
+        b.submit(r)
+        toks = []
+        while True:
+            ev = r.events.get(timeout=120)
+            if ev.kind == "tokens":
+                toks += ev.tokens
+            elif ev.kind == "finish":
+                return toks
+            elif ev.kind == "error":
+                raise RuntimeError(ev.message)
+
+    prompt = torch.randint(3, 2000, (40,), generator=torch.Generator().manual_seed(9)).tolist()
+    plain = backend(False)
+    try:
+        want = run(plain, prompt, 24)
+    finally:
+        plain.close()
+    spec = backend(True)
+    try:
+        got = run(spec, prompt, 24)
+        assert got == want
+        assert spec.totals["spec_rounds"] > 0 and spec.totals["spec_masked_rounds"] == spec.totals["spec_rounds"]
+        assert spec.healthy, spec.error
+    finally:
+        spec.close()
+
+
 def test_partial_prefix_overlap_reuses_compressed_rows(server):
     """A prompt that shares only its first 100 tokens with a stored one: the compressed rows below
     skipped = 100 / 2 * 2 - window are taken from the snapshot, the tokens from there on are run again to rebuild the
