@@ -474,3 +474,54 @@ def test_row_sharded_long_pass_matches_replicated(cfg_name, n, ced):
     for s_ in ca:
         assert close(ca[s_], cb[s_])
     assert ta[:2] == tb[:2]
+
+
+def test_flash_width_layers_match_oracle():
+    """The release model's widths - hidden 5120, 64 heads x 512, 8 output groups, 384 experts top-6 stored as FP8 with
+    block scales, a 32 x 128 indexer over ratio-2 compressed rows - on a 2-layer stack with a shortened expert width
+    and vocabulary (so the fp32 oracle fits in host memory): 8-row passes against the oracle on the dequantised
+    weights."""
+    import dataclasses
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.weights import init_weights
+    from ds41rt_b200.models.reference import ReferenceModel
+    from ds41rt_b200.models.ds41 import EngineWeights, DS41Engine, dequantize_expert
+    cfg = dataclasses.replace(ModelConfig.flash(2), name="flash-width-L2", vocab=8192, inter=128,
+                              source_layers={1: 2}, compress_ratios=[0, 2], index_layers=(1,), candidate_layer=-1,
+                              candidate_topk_blocks=0, dspark=None, engram=None, image_token=8191,
+                              think_end_token=8190)
+    cfg.validate()
+    assert cfg.hidden == 5120 and cfg.n_experts == 384 and cfg.n_heads == 64 and cfg.head_dim == 512
+    w = init_weights(cfg, seed=0)
+    wr = {k: (v.bfloat16().float() if v.dim() == 2 and not k.endswith("_fn") else v) for k, v in w.items()}
+    del w
+    ew = EngineWeights.from_fp32(cfg, wr, 0, 1, torch.device("cuda"), expert_dtype="mxfp8")
+    I = cfg.inter
+    for l, lw in enumerate(ew.layers):
+        for e in range(cfg.n_experts):
+            w13 = dequantize_expert(lw.w13[e], lw.w13_sf[e])
+            wr[f"layers.{l}.ffn.experts.{e}.w1.weight"] = w13[:I]
+            wr[f"layers.{l}.ffn.experts.{e}.w3.weight"] = w13[I:]
+            wr[f"layers.{l}.ffn.experts.{e}.w2.weight"] = dequantize_expert(lw.w2[e], lw.w2_sf[e])
+    ref = ReferenceModel(cfg, wr)
+    eng = DS41Engine(cfg, ew, max_rows=8, slots=1, max_ctx=256)
+    prompt = torch.randint(0, cfg.vocab, (48,), generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        want, traces = ref.forward(prompt, return_trace=True)
+    eng.cache.ensure(0, 64)
+    got, same = [], []
+    toks = prompt.tolist()
+    for c0 in range(0, len(toks), 8):
+        part = toks[c0:c0 + 8]
+        eng.debug = []
+        eng.set_rows(part, list(range(c0, c0 + len(part))), [0] * len(part))
+        eng.forward_rows(len(part))
+        got.append(eng.logits_rows(len(part)).cpu())
+        same.append(_decisions_match(cfg, traces, eng.debug, c0, len(part), None))
+    eng.check_status()
+    got, same = torch.cat(got, 0), torch.cat(same, 0)
+    err = (got - want).abs().max(dim=1).values
+    scale = float(want.abs().max())
+    print("flash width: same", int(same.sum()), "of", len(same), "max err", float(err[same].max()), "scale", scale)
+    assert int(same.sum()) >= 0.6 * len(same)
+    assert float(err[same].max()) < 0.08 * scale
