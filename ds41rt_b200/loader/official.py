@@ -110,6 +110,28 @@ class LazyOfficialWeights:
     def __init__(self, cat: Catalog):
         self.cat = cat
 
+    def expert_stack_fp4(self, prefix: str, e0: int, e1: int, device):
+        """Routed experts [e0, e1) of the layer `prefix` ("layers.7", "mtp.0") in the engine's MX-FP4 layout, taken
+        byte for byte from an FP4 + UE8M0/32 checkpoint: the E2M1 payloads are the checkpoint's bytes (w1 rows, then
+        w3 rows), only the scales are re-tiled into the tensor cores' 128 x 4 atoms, on the device and for all experts
+        at once.  No value is dequantised.  Returns (w13, w13 atoms, w2, w2 atoms), or None when the checkpoint holds
+        another expert format.  (The reference re-tiles on the GPU too: native/cuda/kernels/v41_expert_pack.cu:10-107.)"""
+        from ..ops.mx import pack_sf_atoms_batched
+        cat = self.cat
+        probe = f"{prefix}.ffn.experts.{e0}.w1.weight"
+        if probe not in cat.expected or cat.expected[probe][0] != "I8":
+            return None
+        u8 = lambda name: cat.read(name).view(torch.uint8)
+        w13, s13, w2, s2 = [], [], [], []
+        for e in range(e0, e1):
+            b = f"{prefix}.ffn.experts.{e}"
+            w13.append(torch.cat([u8(f"{b}.w1.weight"), u8(f"{b}.w3.weight")], 0))
+            s13.append(torch.cat([u8(f"{b}.w1.scale"), u8(f"{b}.w3.scale")], 0))
+            w2.append(u8(f"{b}.w2.weight"))
+            s2.append(u8(f"{b}.w2.scale"))
+        up = lambda ts: torch.stack(ts).to(device, non_blocking=True).contiguous()
+        return (up(w13), pack_sf_atoms_batched(up(s13)), up(w2), pack_sf_atoms_batched(up(s2)))
+
     def __contains__(self, name: str) -> bool:
         return name in self.cat.expected
 

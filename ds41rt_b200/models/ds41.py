@@ -258,6 +258,13 @@ class EngineWeights:
                 lw.w_qb_full, lw.wo_a_full, lw.wo_b_full, lw.sink_full = lw.w_qb, lw.wo_a, lw.wo_b, lw.sink
                 lw.w_gate_full, lw.w2_sh_full = lw.w_gate_sh, lw.w2_sh
             e0 = rank * EL
+            raw = w.expert_stack_fp4(p, e0, e0 + EL, device) \
+                if expert_dtype == "mxfp4" and hasattr(w, "expert_stack_fp4") else None
+            if raw is not None:
+                # an FP4 checkpoint into FP4 engine experts: bytes are copied, only the scales are re-tiled
+                lw.w13, lw.w13_sf, lw.w2, lw.w2_sf = raw
+                ew.layers.append(lw)
+                continue
             w13 = torch.stack([torch.cat([w[f"{p}.ffn.experts.{e}.w1.weight"],
                                           w[f"{p}.ffn.experts.{e}.w3.weight"]], 0) for e in range(e0, e0 + EL)], 0)
             w2 = torch.stack([w[f"{p}.ffn.experts.{e}.w2.weight"] for e in range(e0, e0 + EL)], 0)

@@ -176,3 +176,39 @@ def test_engram_table_export_matches_checkpoint_rows(tmp_path):
     ref = w["layers.1.engram.embed.weight"]
     assert float((deq - ref).abs().max()) <= 0.07 * float(ref.abs().max())
     table.close()
+
+
+def test_fp4_experts_import_byte_for_byte(tmp_path):
+    """An FP4 + UE8M0/32 checkpoint becomes the engine's MX-FP4 expert stacks without dequantising a value: payload
+    bytes are the checkpoint's, the scales are only re-tiled into 128 x 4 atoms; the stacks expand to exactly the
+    values the dequantising loader reads."""
+    from ds41rt_b200.loader.official import LazyOfficialWeights
+    from ds41rt_b200.models.ds41 import EngineWeights, dequantize_expert_fp4
+    from ds41rt_b200.ops.mx import pack_sf_atoms, pack_sf_atoms_batched
+    cfg = ModelConfig.tiny()
+    w = init_weights(cfg, seed=3)
+    d = str(tmp_path / "ckpt")
+    export_official(cfg, w, d, variant="mxfp4", shards=3)
+    cat = Catalog(d, cfg, "mxfp4", with_vision=False, with_engram=False)
+    lazy = LazyOfficialWeights(cat)
+    w13, sf13, w2, sf2 = lazy.expert_stack_fp4("layers.1", 4, 9, torch.device("cpu"))
+    I = cfg.inter
+    assert w13.shape == (5, 2 * I, cfg.hidden // 2) and w2.shape == (5, cfg.hidden, I // 2)
+    eager = load_official(cat)
+    for i, e in enumerate(range(4, 9)):
+        raw1 = cat.read(f"layers.1.ffn.experts.{e}.w1.weight").view(torch.uint8)
+        assert torch.equal(w13[i, :I], raw1)                                     # the checkpoint's bytes
+        got13 = dequantize_expert_fp4(w13[i], sf13[i])
+        assert torch.equal(got13[:I], eager[f"layers.1.ffn.experts.{e}.w1.weight"])
+        assert torch.equal(got13[I:], eager[f"layers.1.ffn.experts.{e}.w3.weight"])
+        assert torch.equal(dequantize_expert_fp4(w2[i], sf2[i]), eager[f"layers.1.ffn.experts.{e}.w2.weight"])
+    s = torch.randint(0, 255, (3, 200, 16), dtype=torch.uint8)
+    assert torch.equal(pack_sf_atoms_batched(s), torch.stack([pack_sf_atoms(x) for x in s]))
+    # the engine takes this path for mxfp4 experts and ends with the same stacks
+    ew = EngineWeights.from_fp32(cfg, lazy, 0, 1, torch.device("cpu"), expert_dtype="mxfp4")
+    assert torch.equal(ew.layers[1].w13[4:9], w13) and torch.equal(ew.layers[1].w13_sf[4:9], sf13)
+    assert lazy.expert_stack_fp4("layers.1", 0, 2, torch.device("cpu")) is not None
+    nv = str(tmp_path / "nv")
+    export_official(cfg, w, nv, variant="nvfp4", shards=2)
+    other = LazyOfficialWeights(Catalog(nv, cfg, "nvfp4", with_vision=False, with_engram=False))
+    assert other.expert_stack_fp4("layers.1", 0, 2, torch.device("cpu")) is None     # another expert format
