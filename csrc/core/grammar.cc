@@ -4,7 +4,9 @@
 // It is built from a JSON description:
 //   {"lit": "text"} {"chars": "[a-z0-9_]"} {"seq": [...]} {"alt": [...]} {"repeat": [node, min, max]} (max < 0: unbounded)
 //   {"schema": <JSON schema>}   {"regex": "pattern"}   {"json": true} (any JSON value)   {"until": "stop"} (free text
-//   that ends at the first occurrence of the stop string, which is consumed)
+//   that ends at the first occurrence of the stop string, which is consumed)   {"text_without": "stop"} (free text
+//   that may end anywhere and never contains the stop string: with {"until": stop} beside it in an "alt" this is the
+//   triggered form used for optional tool calls - plain text, or text up to a trigger tag and then a structure)
 // The matcher simulates the graph with a set of continuation stacks (the grammars used here are near-deterministic,
 // so the set stays small), can be forked cheaply for per-draft-row verification masks, and fills a packed allow-mask
 // by walking a byte trie of the vocabulary so tokens sharing a prefix share the work.
@@ -19,6 +21,7 @@
 #include <cstring>
 #include <map>
 #include <memory>
+#include <mutex>
 #include <set>
 #include <string>
 #include <vector>
@@ -198,16 +201,19 @@ struct CharSet {
 };
 
 struct Node {
-  enum Kind { Lit, Chars, Seq, Alt, Repeat, Ref, Until } kind = Lit;
-  std::string lit;            // Lit / Until (stop string)
+  enum Kind { Lit, Chars, Seq, Alt, Repeat, Ref, Until, Free } kind = Lit;
+  std::string lit;            // Lit / Until / Free (stop string)
   CharSet cs;                 // Chars
   std::vector<int> kids;      // Seq / Alt / Repeat[0] / Ref[0]
   int rmin = 0, rmax = -1;
 };
 
+struct MaskCache;
+
 struct Grammar {
   std::vector<Node> nodes;
   int root = -1;
+  std::shared_ptr<MaskCache> masks;      // allow-masks by matcher state (free text sits in one state for long)
   std::string error;
   std::map<std::string, int> defs;       // $defs name -> node
   const JVal* schema_root = nullptr;
@@ -544,9 +550,9 @@ int Grammar::build(const JVal& d) {
   }
   if (k == "regex") return regex(v.str);
   if (k == "json") return any_json();
-  if (k == "until") {
-    if (v.str.empty()) { error = "until needs a stop string"; return lit(""); }
-    Node n; n.kind = Node::Until; n.lit = v.str;
+  if (k == "until" || k == "text_without") {
+    if (v.str.empty()) { error = k + " needs a stop string"; return lit(""); }
+    Node n; n.kind = k == "until" ? Node::Until : Node::Free; n.lit = v.str;
     return add(n);
   }
   error = "unknown grammar node '" + k + "'";
@@ -584,6 +590,14 @@ struct Matcher {
           if (f.pos >= static_cast<int>(n.lit.size())) { t.pop_back(); continue; }
           out.push_back(std::move(t));
           return;
+        case Node::Free: {
+          // may stop here (the continuation is settled on its own) or consume another byte
+          Thread c = t;
+          c.pop_back();
+          settle(std::move(c), out, depth + 1);
+          out.push_back(std::move(t));
+          return;
+        }
         case Node::Chars:
           if (f.pos >= 1) { t.pop_back(); continue; }
           out.push_back(std::move(t));
@@ -663,16 +677,17 @@ struct Matcher {
         Thread c = t;
         c.back().pos = 1;
         settle(std::move(c), next);
-      } else if (n.kind == Node::Until) {
+      } else if (n.kind == Node::Until || n.kind == Node::Free) {
         // KMP-free fallback on the stop string: longest suffix of (matched + b) that is a prefix of stop
         const std::string& stop = n.lit;
         std::string cur = stop.substr(0, f.pos);
         cur.push_back(static_cast<char>(b));
         int k = static_cast<int>(std::min(cur.size(), stop.size()));
         while (k > 0 && stop.compare(0, k, cur, cur.size() - k, k) != 0) --k;
+        if (n.kind == Node::Free && k == static_cast<int>(stop.size())) continue;   // the text would contain the stop
         Thread c = t;
         c.back().pos = k;
-        settle(std::move(c), next);
+        settle(std::move(c), next);          // a Free frame settles into "stop here" and "one more byte" again
       }
       if (next.size() >= kMaxThreads) break;
     }
@@ -700,6 +715,15 @@ struct Vocab {
   std::vector<TNode> nodes;
   std::vector<std::string> bytes;
   int size = 0;
+};
+
+// Masks of recent matcher states of one grammar, for one vocabulary at a time.  Free text ("until" / "text_without")
+// stays in the same state token after token, and its mask costs a walk over the whole vocabulary trie.
+struct MaskCache {
+  std::mutex mu;
+  const void* vocab = nullptr;
+  std::map<std::vector<Thread>, std::vector<uint32_t>> by_state;
+  static constexpr size_t kMaxStates = 64;
 };
 
 void fill_rec(const Vocab& v, int tn, const Matcher& m, uint32_t* mask) {
@@ -750,6 +774,7 @@ void* ds41_grammar_compile(const char* description, char* error, int error_cap) 
   if (!jp.ok || jp.p != jp.end) g->error = "grammar description is not valid JSON";
   else g->root = g->build(d);
   g->schema_root = nullptr;
+  g->masks = std::make_shared<MaskCache>();
   if (!g->error.empty() || g->root < 0) {
     if (error != nullptr && error_cap > 0) std::snprintf(error, static_cast<size_t>(error_cap), "%s", g->error.c_str());
     delete g;
@@ -795,8 +820,26 @@ int ds41_matcher_fill_mask(const void* m, const void* vocab, uint32_t* mask, int
   const Matcher* mm = static_cast<const Matcher*>(m);
   const int words = (v->size + 31) / 32;
   std::memset(mask, 0, sizeof(uint32_t) * static_cast<size_t>(words));
-  // bytes may only be consumed by non-accepting threads; the trie walk ignores finished threads
-  fill_rec(*v, 0, *mm, mask);
+  MaskCache* cache = mm->g->masks.get();
+  bool hit = false;
+  if (cache != nullptr) {
+    std::lock_guard<std::mutex> lock(cache->mu);
+    if (cache->vocab != vocab) { cache->by_state.clear(); cache->vocab = vocab; }
+    auto it = cache->by_state.find(mm->threads);
+    if (it != cache->by_state.end()) {
+      std::memcpy(mask, it->second.data(), sizeof(uint32_t) * static_cast<size_t>(words));
+      hit = true;
+    }
+  }
+  if (!hit) {
+    // bytes may only be consumed by non-accepting threads; the trie walk ignores finished threads
+    fill_rec(*v, 0, *mm, mask);
+    if (cache != nullptr) {
+      std::lock_guard<std::mutex> lock(cache->mu);
+      if (cache->by_state.size() >= MaskCache::kMaxStates) cache->by_state.clear();
+      cache->by_state.emplace(mm->threads, std::vector<uint32_t>(mask, mask + words));
+    }
+  }
   // the trie root has no tokens, so nothing was set for the empty string
   if (stop_token >= 0 && stop_token < v->size && mm->can_finish()) mask[stop_token >> 5] |= 1u << (stop_token & 31);
   int count = 0;

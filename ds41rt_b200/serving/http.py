@@ -235,6 +235,8 @@ class ApiServer:
             grammar = Grammar.regex(rf["regex"])
         elif req.tools and (req.tool_choice == "required" or isinstance(req.tool_choice, dict)):
             grammar = Grammar(tool_call_grammar(req.tools, req.tool_choice, req.parallel_tool_calls))
+        elif req.tools and req.tool_choice == "auto":
+            grammar = Grammar(tool_call_grammar(req.tools, "auto", req.parallel_tool_calls, triggered=True))
         if grammar is None:
             return None
         return TokenConstraint(self._vocab(), grammar, eos=self.tk.eos, think_end=self.tk.think_end,
@@ -368,8 +370,11 @@ class ApiServer:
             gen.cancelled.set()              # client went away: stop generating
 
 
-def tool_call_grammar(tools, tool_choice, parallel: bool) -> dict:
-    """Grammar description of a DSML calls block for the declared tools (string parameters raw, others JSON)."""
+def tool_call_grammar(tools, tool_choice, parallel: bool, triggered: bool = False) -> dict:
+    """Grammar description of a DSML calls block for the declared tools (string parameters raw, others JSON).
+    `triggered` (tool_choice "auto"): the answer is plain text, or text up to the tag that opens a calls block and
+    then a block that must be well formed - the model is free until it writes the tag
+    (reference: rust/crates/ds41rt-api/src/native_v41/constraints.rs:35, the triggered-tag structural grammar)."""
     names = [t["function"]["name"] for t in tools]
     if isinstance(tool_choice, dict):
         names = [tool_choice["function"]["name"]]
@@ -395,4 +400,7 @@ def tool_call_grammar(tools, tool_choice, parallel: bool) -> dict:
                                [{"lit": f"{C.DSML_CLOSE} invoke>\n"}]})
     one = {"alt": invokes}
     body = {"repeat": [one, 1, -1 if parallel else 1]}
+    if triggered:
+        return {"alt": [{"text_without": C.CALLS_OPEN},
+                        {"seq": [{"until": C.CALLS_OPEN}, {"lit": "\n"}, body, {"lit": C.CALLS_CLOSE}]}]}
     return {"seq": [{"lit": C.CALLS_OPEN + "\n"}, body, {"lit": C.CALLS_CLOSE}]}

@@ -134,3 +134,43 @@ def test_token_constraint_thinking_and_proposals():
     for t in seq[1:]:
         assert c.accept(t)
     assert mask_allows(c.mask(), 0) and c.accept(0) and c.finished
+
+
+def test_triggered_tool_grammar_leaves_text_free_until_the_tag():
+    """tool_choice "auto": plain text of any kind completes; once the opening tag of a calls block is written, only a
+    well-formed block for a declared tool completes; masks along the way equal brute force (and repeat from the cache)."""
+    from ds41rt_b200.serving import chat as C
+    from ds41rt_b200.serving.http import tool_call_grammar
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+        "type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "integer"}},
+        "required": ["city"]}}}]
+    g = Grammar(tool_call_grammar(tools, "auto", parallel=False, triggered=True))
+    assert _complete(g, "") and _complete(g, "It is sunny. <not a tag> 1 < 2")
+    assert _complete(g, "partial tag " + C.CALLS_OPEN[:-1])            # a prefix of the tag is still just text
+    call = (f'{C.CALLS_OPEN}\n{C.DSML_OPEN} invoke name="get_weather">\n'
+            f'{C.DSML_OPEN} parameter name="city" string="true">Paris{C.DSML_CLOSE} parameter>\n'
+            f'{C.DSML_OPEN} parameter name="days" string="false">3{C.DSML_CLOSE} parameter>\n'
+            f'{C.DSML_CLOSE} invoke>\n{C.CALLS_CLOSE}')
+    assert _complete(g, "Let me check. " + call)
+    m = Matcher(g)
+    assert m.accept_bytes(("text " + C.CALLS_OPEN).encode()) and not m.can_finish          # the block must now be finished
+    assert not _ok(g, "x " + C.CALLS_OPEN + "\n" + f'{C.DSML_OPEN} invoke name="unknown_tool">')
+    assert not _complete(g, call + " trailing text")
+    # token masks: a vocabulary with text pieces, tag pieces and a token that spans the tag boundary
+    pieces = ["It", " is", " sunny", ".", C.CALLS_OPEN, C.CALLS_OPEN[:3], C.CALLS_OPEN[3:], "\n", "x" + C.CALLS_OPEN + "y",
+              f'{C.DSML_OPEN} invoke name="get_weather">\n', f'{C.DSML_OPEN} invoke name="nope">\n', "Paris", " parameter>\n"]
+    toks = [b""] + [p.encode() for p in pieces]
+    vocab = Vocab(toks)
+    m = Matcher(g)
+    for text in ("It", " is", C.CALLS_OPEN[:3], C.CALLS_OPEN[3:], "\n"):
+        for _ in range(2):                                            # second fill comes from the state cache
+            mask = m.fill_mask(vocab, stop_token=0)
+            brute = [i for i in range(1, vocab.size) if m.fork().accept_bytes(toks[i])]
+            assert [i for i in range(1, vocab.size) if mask_allows(mask, i)] == brute
+            assert mask_allows(mask, 0) == m.can_finish
+        assert m.accept_bytes(text.encode())
+    mask = m.fill_mask(vocab, stop_token=0)
+    allowed = [pieces[i - 1] for i in range(1, vocab.size) if mask_allows(mask, i)]
+    # inside the block only the declared tool's invoke line can follow (or a piece that is a prefix of it)
+    assert f'{C.DSML_OPEN} invoke name="get_weather">\n' in allowed and not mask_allows(mask, 0)
+    assert all(f'{C.DSML_OPEN} invoke name="get_weather">\n'.startswith(p) for p in allowed)
