@@ -5,8 +5,10 @@ Routes (reference: rust/crates/ds41rt-api/src/native_v41.rs:90-126,202-437):
   GET  /v1/models              the served model with max_context_tokens / max_output_tokens
   GET  /v1/stats               backend counters, HTTP queue counters
   POST /v1/chat/completions    JSON or SSE ("data: {...}\\n\\n" ... "data: [DONE]")
-  GET  /  and /v1/console/snapshot   a small live console page and its JSON feed; /v1/console streams the same
-                                     snapshots as server-sent events
+  GET  /  and /v1/console/snapshot   a small live console page and its JSON feed; /v1/console pushes the same
+                                     snapshots once a second over a WebSocket (RFC 6455 text frames; reference:
+                                     native_v41.rs:94-106, v41_native_serve/console.rs:71-260), or as server-sent events
+                                     to a client that does not ask for the upgrade
 Errors: {"error":{"message","type":"native_v41_error"}}; 400 bad request, 429 + Retry-After: 1 when the bounded
 admission queue is full, 500, 503.  A stream that ends without a Finish event is reported as an error, never as a
 successful completion.
@@ -31,8 +33,54 @@ from .tokenizer import StreamingDecoder
 CONSOLE_HTML = """<!doctype html><meta charset=utf-8><title>ds41rt-b200 console</title>
 <style>body{font:14px monospace;background:#111;color:#ddd;margin:2em}pre{background:#1b1b1b;padding:1em}</style>
 <h3>ds41rt-b200 live console</h3><pre id=o>connecting...</pre>
-<script>const o=document.getElementById('o');const s=new EventSource('/v1/console');
-s.onmessage=e=>{o.textContent=JSON.stringify(JSON.parse(e.data),null,2)};</script>"""
+<script>const o=document.getElementById('o');const show=d=>{o.textContent=JSON.stringify(JSON.parse(d),null,2)};
+let w;try{w=new WebSocket((location.protocol=='https:'?'wss://':'ws://')+location.host+'/v1/console');
+w.onmessage=e=>show(e.data);w.onerror=()=>{const s=new EventSource('/v1/console');s.onmessage=e=>show(e.data)}}
+catch(e){const s=new EventSource('/v1/console');s.onmessage=e=>show(e.data)}</script>"""
+
+WS_GUID = "258EAFA5-E914-47DA-95CA-C5AB0DC85B11"
+
+
+def ws_frame(payload: bytes, opcode: int = 1) -> bytes:
+    """One unmasked server-to-client frame (FIN set)."""
+    n = len(payload)
+    head = bytes([0x80 | opcode])
+    if n < 126:
+        head += bytes([n])
+    elif n < 65536:
+        head += bytes([126]) + n.to_bytes(2, "big")
+    else:
+        head += bytes([127]) + n.to_bytes(8, "big")
+    return head + payload
+
+
+def ws_read_frame(sock):
+    """One client-to-server frame -> (opcode, payload), or None when the peer closed the connection."""
+    def need(k):
+        buf = b""
+        while len(buf) < k:
+            part = sock.recv(k - len(buf))
+            if not part:
+                return None
+            buf += part
+        return buf
+    h = need(2)
+    if h is None:
+        return None
+    n = h[1] & 0x7F
+    if n == 126:
+        ext = need(2)
+        n = int.from_bytes(ext, "big") if ext else 0
+    elif n == 127:
+        ext = need(8)
+        n = int.from_bytes(ext, "big") if ext else 0
+    if n > 1 << 20:
+        return None
+    mask = need(4) if h[1] & 0x80 else b"\0\0\0\0"
+    data = need(n) if n else b""
+    if mask is None or data is None:
+        return None
+    return h[0] & 0x0F, bytes(b ^ mask[i & 3] for i, b in enumerate(data))
 
 
 class ApiServer:
@@ -114,6 +162,8 @@ class ApiServer:
             return self._send_json(h, 200, self.snapshot())
         if path == "/v1/console/snapshot":
             return self._send_json(h, 200, self.snapshot())
+        if path == "/v1/console" and "websocket" in (h.headers.get("Upgrade") or "").lower():
+            return self._console_socket(h)
         if path == "/v1/console":
             h.send_response(200)
             h.send_header("Content-Type", "text/event-stream")
@@ -136,6 +186,47 @@ class ApiServer:
             h.wfile.write(data)
             return
         self._fail(h, ApiError(404, "no such route"))
+
+    def _console_socket(self, h, period: float = 1.0, max_frames: int = 86400):
+        """WebSocket feed of the console: handshake, then one JSON text frame per `period`; pings are answered, a
+        close frame (or a vanished peer) ends the feed."""
+        import base64
+        import hashlib
+        import select
+        key = h.headers.get("Sec-WebSocket-Key")
+        if not key:
+            return self._fail(h, ApiError(400, "missing Sec-WebSocket-Key"))
+        accept = base64.b64encode(hashlib.sha1((key + WS_GUID).encode()).digest()).decode()
+        h.send_response(101, "Switching Protocols")
+        h.send_header("Upgrade", "websocket")
+        h.send_header("Connection", "Upgrade")
+        h.send_header("Sec-WebSocket-Accept", accept)
+        h.end_headers()
+        h.wfile.flush()
+        h.close_connection = True
+        sock = h.connection
+        try:
+            for _ in range(max_frames):
+                sock.sendall(ws_frame(json.dumps(self.snapshot()).encode()))
+                deadline = time.time() + period
+                while True:
+                    left = deadline - time.time()
+                    if left <= 0:
+                        break
+                    ready, _, _ = select.select([sock], [], [], left)
+                    if not ready:
+                        break
+                    frame = ws_read_frame(sock)
+                    if frame is None:
+                        return
+                    op, data = frame
+                    if op == 0x8:                                  # close: echo and stop
+                        sock.sendall(ws_frame(data[:2], 0x8))
+                        return
+                    if op == 0x9:                                  # ping -> pong
+                        sock.sendall(ws_frame(data, 0xA))
+        except (BrokenPipeError, ConnectionResetError, OSError):
+            pass
 
     # ------------------------------------------------------------------ POST
     def handle_post(self, h):

@@ -215,3 +215,53 @@ def test_streaming_decoder_holds_incomplete_utf8():
     ids = TK.encode("a✓b")
     out = [d.push([t]) for t in ids]
     assert "".join(out) == "a✓b" and out[1] == "" and out[2] == ""
+
+
+def test_console_websocket_feed_pushes_snapshots():
+    """GET /v1/console with an upgrade request: RFC 6455 handshake, JSON text frames, ping answered, close echoed."""
+    import base64
+    import hashlib
+    import os
+    import socket
+    from ds41rt_b200.serving.http import WS_GUID, ws_read_frame
+    srv, be = serve("x")
+    try:
+        s = socket.create_connection(("127.0.0.1", srv.port), timeout=10)
+        key = base64.b64encode(os.urandom(16)).decode()
+        s.sendall((f"GET /v1/console HTTP/1.1\r\nHost: x\r\nUpgrade: websocket\r\nConnection: Upgrade\r\n"
+                   f"Sec-WebSocket-Key: {key}\r\nSec-WebSocket-Version: 13\r\n\r\n").encode())
+        head = b""
+        while b"\r\n\r\n" not in head:
+            head += s.recv(1)
+        want = base64.b64encode(hashlib.sha1((key + WS_GUID).encode()).digest()).decode()
+        assert head.startswith(b"HTTP/1.1 101") and f"Sec-WebSocket-Accept: {want}".encode() in head
+        op, data = ws_read_frame(s)                              # server frames are unmasked: same parser
+        assert op == 1 and "admission" in json.loads(data)
+
+        def send(opcode, payload):
+            mask = os.urandom(4)
+            s.sendall(bytes([0x80 | opcode, 0x80 | len(payload)]) + mask +
+                      bytes(b ^ mask[i & 3] for i, b in enumerate(payload)))
+        send(0x9, b"hello")
+        seen = []
+        while 0xA not in [o for o, _ in seen]:
+            seen.append(ws_read_frame(s))
+        assert (0xA, b"hello") in seen
+        op, data = ws_read_frame(s)                              # the next periodic snapshot
+        assert op == 1 and json.loads(data)["http"]["requests"] >= 0
+        send(0x8, (1000).to_bytes(2, "big"))
+        while True:
+            f = ws_read_frame(s)
+            if f is None or f[0] == 0x8:
+                break
+        assert f is not None and f[0] == 0x8
+        s.close()
+        # a client that does not ask for the upgrade still gets the event stream
+        c = http.client.HTTPConnection("127.0.0.1", srv.port, timeout=10)
+        c.request("GET", "/v1/console")
+        r = c.getresponse()
+        assert r.status == 200 and r.getheader("Content-Type") == "text/event-stream"
+        assert r.fp.readline().startswith(b"data: ")
+        c.close()
+    finally:
+        srv.stop()
