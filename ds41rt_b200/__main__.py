@@ -274,6 +274,7 @@ def cmd_serve(args) -> int:
     backend = NativeBackend(lead if world > 1 else eng, eos=tk.eos, concurrency=args.concurrency,
                             queue_depth=args.queue_depth, drafter=drafter, prefill_chunk=args.prefill_chunk,
                             prompt_snapshots=args.prompt_snapshots, turn_snapshots=args.turn_snapshots,
+                            host_cache_bytes=int(args.host_cache_gb * (1 << 30)) if world == 1 else 0,
                             engram=_engram_pipeline(args, cfg, eng, engram_layers, tk))
     srv = ApiServer(backend, tk, host=args.host, port=args.port, queue_depth=args.queue_depth, waiters=args.waiters,
                     max_context=args.max_context).start()
@@ -335,6 +336,8 @@ def main(argv=None) -> int:
     ps.add_argument("--prefill-chunk", type=int, default=2048, help="rows per prompt pass (80-4096)")
     ps.add_argument("--prompt-snapshots", type=int, default=20, help="prompt-bank capacity (LRU)")
     ps.add_argument("--turn-snapshots", type=int, default=20, help="turn-bank capacity (LRU)")
+    ps.add_argument("--host-cache-gb", type=float, default=0.0,
+                    help="pinned host memory for snapshots that leave the device banks (0 = off; one-rank serving)")
     ps.add_argument("--reserve-gb", type=int, default=0, help="device memory to leave untouched by the KV pool")
     ps.add_argument("--peer-timeout", type=float, default=10.0, help="seconds without a heartbeat before a rank counts as gone")
     ps.add_argument("--checkpoint", default="", help="directory with model.safetensors.index.json (official layout)")

@@ -156,7 +156,7 @@ class NativeBackend(Backend):
 
     def __init__(self, engine, eos: int, concurrency: int = 4, queue_depth: int = 16, prefill_chunk: Optional[int] = None,
                  vision=None, drafter=None, engram=None, ced: bool = True, use_graphs: bool = True,
-                 prompt_snapshots: int = 20, turn_snapshots: int = 20):
+                 prompt_snapshots: int = 20, turn_snapshots: int = 20, host_cache_bytes: int = 0):
         self.e, self.eos = engine, eos
         # prompt passes use the encoder / decoder-replay split when the model has a boundary (config.ced_on)
         self.ced = ced
@@ -181,6 +181,12 @@ class NativeBackend(Backend):
         # holds what an id stands for: (token tuple, KVSnapshot, logits after the last token or None)
         self.prefix = K.PrefixBanks(prompt_snapshots, turn_snapshots, engine.cfg.window)
         self.snapshots: Dict[int, tuple] = {}
+        # pinned-host tier behind the banks: a snapshot that leaves the device (bank eviction, page pressure) is copied
+        # there and comes back when a prompt extends it (runtime/hosttier.py)
+        self.host_tier = None
+        if host_cache_bytes > 0:
+            from ..runtime.hosttier import HostSnapshotTier
+            self.host_tier = HostSnapshotTier(engine.cache, host_cache_bytes)
         self.prefill_chunk = prefill_chunk or engine.max_rows
         self.active: List[_Active] = []
         self.prefilling: Optional[_Prefill] = None
@@ -196,7 +202,7 @@ class NativeBackend(Backend):
                        "prompt_cache_hit_tokens": 0, "snapshots": 0, "spec_rounds": 0, "spec_tokens": 0,
                        "ced_prefills": 0, "partial_prefix_hits": 0, "snapshots_evicted_for_pages": 0,
                        "graph_rounds": 0, "prefill_passes": 0, "spec_masked_rounds": 0, "policy_plain_rounds": 0,
-                       "cancelled_in_prefill": 0}
+                       "cancelled_in_prefill": 0, "snapshots_demoted": 0, "host_tier_hits": 0}
         self._rid = 0
         self._stop = threading.Event()
         self._ready = threading.Event()
@@ -227,6 +233,8 @@ class NativeBackend(Backend):
                                    "gpu_sampled_rows": self.totals["gpu_sampled_rows"]}}
         if self.policy is not None:
             out["dspark_policy"] = self.policy.stats()
+        if self.host_tier is not None:
+            out["host_cache"] = self.host_tier.stats()
         return out
 
     def close(self) -> None:
@@ -241,6 +249,8 @@ class NativeBackend(Backend):
                 torch.cuda.set_device(self.e.device)
             self._ready.set()
             while not self._stop.is_set():
+                if self.host_tier is not None:
+                    self.host_tier.tick()             # a new scheduler iteration: fresh store / restore budgets
                 self._retire()
                 self._admit()
                 self._prefill_step()
@@ -342,7 +352,18 @@ class NativeBackend(Backend):
         ent = self.snapshots.pop(sid, None)
         self.prefix.remove(sid)
         if ent is not None:
+            self._demote(ent)
             self.e.cache.drop_snapshot(ent[1])
+
+    def _demote(self, ent):
+        """A snapshot is leaving the device: keep it in host memory when there is a host tier."""
+        if self.host_tier is not None:
+            toks, snap, logits = ent
+            try:
+                if self.host_tier.demote(toks, snap, logits):
+                    self.totals["snapshots_demoted"] += 1
+            except Exception:
+                pass                                      # the tier is an optimisation: a failed copy only loses the entry
 
     def _admit(self):
         while len(self.active) + (1 if self.prefilling is not None else 0) < self.concurrency \
@@ -403,6 +424,28 @@ class NativeBackend(Backend):
 
     # ------------------------------------------------------------------ prefix reuse (radix-driven snapshot banks)
     def _restore_prefix(self, slot: int, prompt: List[int], need: int):
+        """Device banks first; a demoted snapshot in the host tier is taken when it reuses more tokens."""
+        tier = self.host_tier
+        hit = tier.lookup(prompt) if tier is not None else None
+        if hit is not None:
+            sid, n, has_logits = hit
+            dev = self.prefix.lookup(prompt)
+            dev_n = 0
+            if dev is not None and dev["id"] in self.snapshots:
+                dev_n = dev["frontier"] if dev["exact"] else max(0, dev["common"] // 2 * 2 - self.e.cfg.window)
+            usable = n < len(prompt) or (n == len(prompt) and has_logits)
+            if usable and n > dev_n:
+                self.e.cache.release(slot)
+                got = tier.restore_into(slot, sid) if self._ensure_pages(slot, n) else None
+                if got is not None and self._ensure_pages(slot, need):
+                    self.totals["host_tier_hits"] += 1
+                    return n, (got[1] if n == len(prompt) else None), None
+                self.e.cache.release(slot)
+                if not self._ensure_pages(slot, need):
+                    raise MemoryError("KV pool cannot hold this request")
+        return self._restore_prefix_device(slot, prompt, need)
+
+    def _restore_prefix_device(self, slot: int, prompt: List[int], need: int):
         """Best stored snapshot for `prompt` -> (tokens reused, logits after them or None, replay start or None).
 
         The radix names the snapshot and its reuse score.  A snapshot whose tokens are a prefix of the prompt is
@@ -450,6 +493,7 @@ class NativeBackend(Backend):
         if evicted >= 0:
             ent = self.snapshots.pop(evicted, None)
             if ent is not None:
+                self._demote(ent)
                 self.e.cache.drop_snapshot(ent[1])
         if sid < 0:
             return

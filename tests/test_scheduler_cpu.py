@@ -178,3 +178,57 @@ def test_prefix_banks_drive_reuse_and_decode_interleaves_with_prompt_passes(cpu_
         assert st["kv"]["prompt_bank"] >= 1 and st["active"] == 0
     finally:
         be.close()
+
+
+def test_demoted_snapshots_come_back_from_the_host_tier(cpu_sampler):
+    """A snapshot pushed out of the device banks by page pressure is copied into host pages; a prompt that extends it
+    gets fresh device pages filled from them (rows, rings and carry intact) and counts its tokens as cache hits; two
+    snapshots with a common first page share that host page."""
+    eng = FakeEngine(slots=2, max_ctx=512, n_pages=10)
+    be = NativeBackend(eng, eos=1, concurrency=2, prefill_chunk=64, host_cache_bytes=4 << 20)
+    cache, tier = eng.cache, be.host_tier
+    try:
+        first = [1000 + i for i in range(130)]                       # 2 full pages + 2 tokens
+        r = _req(first, max_tokens=3)
+        be.submit(r)
+        assert _run(be, [r])[0][1] == "length"
+        _idle(be)
+        (sid, (toks, snap, _)), = [(k, v) for k, v in be.snapshots.items() if len(v[0]) == 130]
+        stamp = {}
+        for n, pg in enumerate(snap.pages):                          # recognisable rows in the snapshot's pages
+            for src, pr in cache.page_rows.items():
+                cache.comp[src][pg * pr:(pg + 1) * pr] = 0.5 + n + 10 * src
+                cache.idx[src][pg * pr:(pg + 1) * pr] = -1.5 - n - 10 * src
+                stamp[(n, src)] = (cache.comp[src][pg * pr].clone(), cache.idx[src][pg * pr].clone())
+        snap.rings.fill_(3.25)
+        sibling = first[:64] + [5000 + i for i in range(66)]          # same first page, different second page
+        r = _req(sibling, max_tokens=3)
+        be.submit(r)
+        assert _run(be, [r])[0][1] == "length"
+        big = _req([7 + i for i in range(440)], max_tokens=60)       # needs 8 of the 10 pages: the snapshots must go
+        be.submit(big)
+        assert _run(be, [big])[0][1] == "length"
+        _idle(be)
+        assert be.totals["snapshots_demoted"] >= 2 and sid not in be.snapshots
+        m = tier.stats()
+        assert m["shared"] >= 1 and m["entries"] >= 2                # the common first page is stored once
+        for pool in list(cache.comp.values()) + list(cache.idx.values()):
+            pool.zero_()                                             # nothing of the old rows is left on the "device"
+        hits0 = be.totals["prompt_cache_hit_tokens"]
+        again = _req(first + [77, 78, 79], max_tokens=2)
+        be.submit(again)
+        # look at the slot while the request is still active: restore happened at admission
+        assert _run(be, [again])[0][1] == "length"
+        assert be.totals["host_tier_hits"] == 1 and be.totals["prompt_cache_hit_tokens"] - hits0 == 130
+        assert tier.stats()["promoted_tokens"] == 130
+        # the turn snapshot of the finished request shares the restored pages: its first two pages carry the stamps
+        ent = [v for v in be.snapshots.values() if tuple(v[0][:130]) == tuple(first)]
+        assert ent
+        pages = ent[0][1].pages
+        for n in range(2):
+            for src, pr in cache.page_rows.items():
+                assert torch.equal(cache.comp[src][pages[n] * pr], stamp[(n, src)][0])
+                assert torch.equal(cache.idx[src][pages[n] * pr], stamp[(n, src)][1])
+        assert "host_cache" in be.stats()
+    finally:
+        be.close()

@@ -436,6 +436,55 @@ def test_engram_backend_speculates_losslessly(tmp_path):
         spec.close()
 
 
+def test_host_tier_restore_continues_like_a_cold_run():
+    """Page pressure pushes a prompt snapshot out of the device pool into pinned host pages; a prompt that extends it
+    is restored from them (H2D page copies, rings, carry) and generates exactly what a backend without any cache
+    generates."""
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    from ds41rt_b200.serving.engine import GenRequest, NativeBackend
+    from ds41rt_b200.serving.protocol import Sampling
+    cfg = ModelConfig.tiny()
+    dev = torch.device("cuda", 0)
+    w = EngineWeights.random(cfg, 0, 1, dev, seed=0)
+
+    def run(b, prompt, n):
+        r = GenRequest(prompt_ids=prompt, max_tokens=n, sampling=Sampling(temperature=0.0))
+        b.submit(r)
+        toks, usage = [], None
+        while True:
+            ev = r.events.get(timeout=120)
+            if ev.kind == "ready":
+                usage = ev.usage
+            elif ev.kind == "tokens":
+                toks += ev.tokens
+            elif ev.kind == "finish":
+                return toks, usage
+            elif ev.kind == "error":
+                raise RuntimeError(ev.message)
+
+    g = torch.Generator().manual_seed(4)
+    first = torch.randint(3, 2000, (130,), generator=g).tolist()
+    big = torch.randint(3, 2000, (440,), generator=g).tolist()
+    tail = [11, 12, 13]
+    cold = NativeBackend(DS41Engine(cfg, w, max_rows=16, slots=2, max_ctx=512), eos=1, concurrency=2)
+    try:
+        want, _ = run(cold, first + tail, 12)
+    finally:
+        cold.close()
+    be = NativeBackend(DS41Engine(cfg, w, max_rows=16, slots=2, max_ctx=512, n_pages=10), eos=1, concurrency=2,
+                       host_cache_bytes=64 << 20)
+    try:
+        run(be, first, 3)
+        run(be, big, 60)                                   # 8 of the 10 pages: the first prompt's snapshot leaves the device
+        assert be.totals["snapshots_demoted"] >= 1
+        got, usage = run(be, first + tail, 12)
+        assert be.totals["host_tier_hits"] == 1 and usage["prompt_cache_hit_tokens"] == len(first)
+        assert got == want
+    finally:
+        be.close()
+
+
 def test_partial_prefix_overlap_reuses_compressed_rows(server):
     """A prompt that shares only its first 100 tokens with a stored one: the compressed rows below
     skipped = 100 / 2 * 2 - window are taken from the snapshot, the tokens from there on are run again to rebuild the
