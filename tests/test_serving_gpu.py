@@ -472,11 +472,11 @@ def test_host_tier_restore_continues_like_a_cold_run():
         want, _ = run(cold, first + tail, 12)
     finally:
         cold.close()
-    be = NativeBackend(DS41Engine(cfg, w, max_rows=16, slots=2, max_ctx=512, n_pages=10), eos=1, concurrency=2,
+    be = NativeBackend(DS41Engine(cfg, w, max_rows=16, slots=2, max_ctx=512, n_pages=9), eos=1, concurrency=2,
                        host_cache_bytes=64 << 20)
     try:
         run(be, first, 3)
-        run(be, big, 60)                                   # 8 of the 10 pages: the first prompt's snapshot leaves the device
+        run(be, big, 60)                                   # 8 of the 9 pages: the first prompt's snapshot leaves the device
         assert be.totals["snapshots_demoted"] >= 1
         got, usage = run(be, first + tail, 12)
         assert be.totals["host_tier_hits"] == 1 and usage["prompt_cache_hit_tokens"] == len(first)
