@@ -84,6 +84,13 @@ typedef struct ds41_gemm_args {
   // scales, 0 = 1) multiplies the accumulators.
   float alpha;
   const float* alpha_batch;   // optional: one more factor per A batch (a global scale per expert)
+  // Completion signal folded into the kernel (multi-rank decode): the CTA that finishes last bumps *sig_epoch and
+  // stores the new value to sig_flags[0 .. sig_world) (device array of flag addresses, one slot in every rank's
+  // memory), with release semantics at system scope.  sig_counter is a zeroed device word, left at zero again.
+  unsigned int* sig_counter;
+  unsigned int* sig_epoch;
+  unsigned int* const* sig_flags;
+  int sig_world;
 } ds41_gemm_args;
 
 int ds41_gemm_tc(const ds41_gemm_args* args, void* stream);
@@ -197,6 +204,14 @@ int ds41_moe_plan(const int* ids, const float* weights, const int* row_slot, int
 int ds41_moe_combine(const float* fc2, const int* slot_of, const float* shared, int shared_splits, int rows,
                      int topk, int H, float* out, void* stream);
 int ds41_signal(uint32_t* epoch, uint32_t* flag, void* stream);
+// bump *epoch and store it to flags[0 .. n) (a device array of flag addresses in this and the peers' memory): every
+// rank then polls flags in its own memory
+int ds41_signal_all(uint32_t* epoch, uint32_t* const* flags, int n, void* stream);
+// ds41_moe_combine with the completion signal of ds41_signal_all folded in (done by the block that finishes last;
+// `counter` is a zeroed device word, left at zero again)
+int ds41_moe_combine_signal(const float* fc2, const int* slot_of, const float* shared, int shared_splits, int rows,
+                            int topk, int H, float* out, unsigned int* counter, uint32_t* epoch,
+                            uint32_t* const* flags, int n_flags, void* stream);
 int ds41_reduce_planes(const float* planes, int splits, long long plane, void* out, int as_bf16, long long n,
                        void* stream);
 // planes [split][group][rows][width] fp32 (split-K partials of a grouped projection) -> bf16 out [rows][ld_out],

@@ -61,6 +61,11 @@ struct GemmParams {
   int static_operand;     // 1: A holds weights, 2: B holds weights (may be fetched before the dependency wait)
   float alpha;            // kind 3: product of the two tensors' global scales, applied to the accumulators
   const float* alpha_batch;   // optional extra factor per A batch (one global scale per expert)
+  // completion signal folded into the kernel: the CTA that finishes last bumps *sig_epoch and stores it to sig_flags[..]
+  unsigned int* sig_counter;
+  unsigned int* sig_epoch;
+  unsigned int* const* sig_flags;
+  int sig_world;
   int a_fp4;              // MX kind: A holds e2m1 values (packed in global memory, one per byte in shared memory)
   // grouped tokens (expert-parallel prefill, swap-AB): the N operand is a flat buffer of rows sorted by expert;
   // tile j covers rows [tile_row0[j], tile_end[j]) of expert tile_group[j]; *n_tiles_dev tiles are live
@@ -703,7 +708,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
+  if (p.sig_counter != nullptr) __threadfence();          // this CTA's output stores, before it is counted as done
   __syncthreads();
+  if (p.sig_counter != nullptr && warp == 0) {
+    unsigned int last = 0;
+    if (lane == 0) last = atomicAdd(p.sig_counter, 1u) == gridDim.x - 1 ? 1u : 0u;
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      __threadfence();
+      uint32_t e = 0;
+      if (lane == 0) {
+        e = *p.sig_epoch + 1;
+        *p.sig_epoch = e;
+        *p.sig_counter = 0u;
+      }
+      e = __shfl_sync(0xffffffffu, e, 0);
+      __threadfence_system();
+      if (lane < p.sig_world) flag_store_release(const_cast<uint32_t*>(p.sig_flags[lane]), e);
+    }
+  }
   if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != kStatusOk) {
     // A wait gave up: let copies that may still be in flight land before the CTA's memory goes away.
     const long long start = clock64();
@@ -887,6 +910,9 @@ extern "C" int ds41_gemm_tc(const ds41_gemm_args* a, void* stream) {
   p.a_fp4 = a_fp4 ? 1 : 0;
   p.alpha = a->alpha != 0.f ? a->alpha : 1.f;
   p.alpha_batch = a->alpha_batch;
+  p.sig_counter = a->sig_counter; p.sig_epoch = a->sig_epoch; p.sig_flags = a->sig_flags; p.sig_world = a->sig_world;
+  if (p.sig_counter != nullptr && (p.sig_epoch == nullptr || p.sig_flags == nullptr || p.sig_world <= 0 || p.sig_world > 32))
+    return cudaErrorInvalidValue;
   p.status = a->status;
   const long long n_t = a->tile_group != nullptr ? a->max_tiles : (N + bn - 1) / bn;
   const long long tiles = 1ll * ((M + kBM - 1) / kBM) * n_t * k_splits * (a->tile_group != nullptr ? 1 : batch);

@@ -165,28 +165,73 @@ struct CombineParams {
   int shared_splits;
   int rows, topk, H;
   float* out;               // [rows][H]
+  unsigned int* counter;    // optional: completion signal (see publish_all)
+  uint32_t* epoch;
+  uint32_t* const* flags;
+  int n_flags;
 };
+
+// The block that arrives last publishes "this rank's planes are complete": it bumps the rank's epoch and stores the
+// new value into its slot of every rank's flag array (so that every rank polls its own memory).  Call it after the
+// block's stores, from every thread.
+__device__ __forceinline__ void publish_all(unsigned int* counter, uint32_t* epoch, uint32_t* const* flags,
+                                            int n_flags, unsigned int n_blocks) {
+  __shared__ unsigned int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(counter, 1u) == n_blocks - 1 ? 1u : 0u;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (threadIdx.x < 32) {
+    uint32_t e = 0;
+    if (threadIdx.x == 0) {
+      e = *epoch + 1;
+      *epoch = e;
+      *counter = 0u;
+    }
+    e = __shfl_sync(0xffffffffu, e, 0);
+    __threadfence_system();
+    if (static_cast<int>(threadIdx.x) < n_flags) flag_store_release(flags[threadIdx.x], e);
+  }
+}
 
 __global__ void __launch_bounds__(256) moe_combine_kernel(CombineParams p) {
   const int r = blockIdx.y;
   const int c = (blockIdx.x * 256 + threadIdx.x) * 4;
   pdl_launch_dependents();
   pdl_wait();
-  if (c >= p.H) return;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int k = 0; k < p.topk; ++k) {
-    const int s = p.slot_of[r * p.topk + k];
-    if (s >= 0) {
-      const float4 v = *reinterpret_cast<const float4*>(p.fc2 + (1ll * s * p.rows + r) * p.H + c);
-      // per-route bf16 boundary, then fp32 accumulation in route order
-      acc.x += bf16_round(v.x); acc.y += bf16_round(v.y); acc.z += bf16_round(v.z); acc.w += bf16_round(v.w);
+  if (c < p.H) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < p.topk; ++k) {
+      const int s = p.slot_of[r * p.topk + k];
+      if (s >= 0) {
+        const float4 v = *reinterpret_cast<const float4*>(p.fc2 + (1ll * s * p.rows + r) * p.H + c);
+        // per-route bf16 boundary, then fp32 accumulation in route order
+        acc.x += bf16_round(v.x); acc.y += bf16_round(v.y); acc.z += bf16_round(v.z); acc.w += bf16_round(v.w);
+      }
     }
+    for (int s = 0; s < p.shared_splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(p.shared + (1ll * s * p.rows + r) * p.H + c);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4*>(p.out + 1ll * r * p.H + c) = acc;
   }
-  for (int s = 0; s < p.shared_splits; ++s) {
-    const float4 v = *reinterpret_cast<const float4*>(p.shared + (1ll * s * p.rows + r) * p.H + c);
-    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  if (p.counter != nullptr) publish_all(p.counter, p.epoch, p.flags, p.n_flags, gridDim.x * gridDim.y);
+}
+
+// ---- the same publication as a kernel of its own (after kernels that do not fold it in)
+__global__ void signal_all_kernel(unsigned int* epoch, uint32_t* const* flags, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  uint32_t e = 0;
+  if (threadIdx.x == 0) {
+    e = *epoch + 1;
+    *epoch = e;
   }
-  *reinterpret_cast<float4*>(p.out + 1ll * r * p.H + c) = acc;
+  e = __shfl_sync(0xffffffffu, e, 0);
+  __threadfence_system();
+  if (static_cast<int>(threadIdx.x) < n) flag_store_release(flags[threadIdx.x], e);
 }
 
 // ---- publish "this rank's partial planes are complete": bump the rank-local epoch and store it to the flag
@@ -277,9 +322,24 @@ extern "C" int ds41_moe_plan(const int* ids, const float* weights, const int* ro
 extern "C" int ds41_moe_combine(const float* fc2, const int* slot_of, const float* shared, int shared_splits,
                                 int rows, int topk, int H, float* out, void* stream) {
   if (rows <= 0 || (H & 3)) return cudaErrorInvalidValue;
-  CombineParams p{fc2, slot_of, shared, shared_splits, rows, topk, H, out};
+  CombineParams p{fc2, slot_of, shared, shared_splits, rows, topk, H, out, nullptr, nullptr, nullptr, 0};
   dim3 grid((H / 4 + 255) / 256, rows);
   return launch_pdl(moe_combine_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), p);
+}
+
+extern "C" int ds41_moe_combine_signal(const float* fc2, const int* slot_of, const float* shared, int shared_splits,
+                                       int rows, int topk, int H, float* out, unsigned int* counter, uint32_t* epoch,
+                                       uint32_t* const* flags, int n_flags, void* stream) {
+  if (rows <= 0 || (H & 3) || counter == nullptr || epoch == nullptr || flags == nullptr || n_flags <= 0 || n_flags > 32)
+    return cudaErrorInvalidValue;
+  CombineParams p{fc2, slot_of, shared, shared_splits, rows, topk, H, out, counter, epoch, flags, n_flags};
+  dim3 grid((H / 4 + 255) / 256, rows);
+  return launch_pdl(moe_combine_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), p);
+}
+
+extern "C" int ds41_signal_all(uint32_t* epoch, uint32_t* const* flags, int n, void* stream) {
+  if (epoch == nullptr || flags == nullptr || n <= 0 || n > 32) return cudaErrorInvalidValue;
+  return launch_pdl(signal_all_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), epoch, flags, n);
 }
 
 extern "C" int ds41_signal(uint32_t* epoch, uint32_t* flag, void* stream) {

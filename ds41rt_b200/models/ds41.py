@@ -771,7 +771,8 @@ class DS41Engine:
         self.sym: SymBuffer = self.fabric.alloc(total)
         self.planes_o = self.sym.view(F32, (o_rows, H), 0)
         self.moe_plane = self.sym.view(F32, (R, H), self.o_plane_bytes)
-        self.flag = self.sym.view(torch.int32, (1,), off_flag)
+        # flag area: one slot per rank; rank r publishes into slot r of EVERY rank's area, so waits poll local memory
+        self.flag = self.sym.view(torch.int32, (max(self.world, 1),), off_flag)
         self.best_val = self.sym.view(F32, (R,), off_best)
         self.best_idx = self.sym.view(I32, (R,), off_best + R * 4)
         self.epoch = z((1,), I32)
@@ -780,7 +781,11 @@ class DS41Engine:
         self._moe_bases = (C.c_void_p * self.world)(*[p + self.o_plane_bytes for p in peers])
         self._val_ptrs = (C.c_void_p * self.world)(*[p + off_best for p in peers])
         self._idx_ptrs = (C.c_void_p * self.world)(*[p + off_best + R * 4 for p in peers])
-        self.flag_ptrs = torch.tensor([p + off_flag for p in peers], dtype=torch.int64, device=dev)
+        self.flag_ptrs = torch.tensor([peers[self.rank] + off_flag + 4 * r for r in range(self.world)],
+                                      dtype=torch.int64, device=dev)           # where this rank waits: its own area
+        self.flag_out = torch.tensor([p + off_flag + 4 * self.rank for p in peers], dtype=torch.int64, device=dev)
+        self.sig_counters = z((2,), I32)          # arrival counters of the kernels that fold the publication in
+        self._sig_attn = (self.sig_counters[0:1], self.epoch, self.flag_out, self.world) if self.world > 1 else None
         # rope tables
         self.inv_plain = torch.tensor(rope_inv_freq(cfg.rope_plain, cfg.rope_dim), dtype=F32, device=dev)
         self.inv_long = torch.tensor(rope_inv_freq(cfg.rope_long, cfg.rope_dim), dtype=F32, device=dev)
@@ -962,7 +967,8 @@ class DS41Engine:
 
     def _signal(self):
         if self.world > 1:
-            self._run("signal", self.k.ds41_signal, lib.ptr(self.epoch), lib.ptr(self.flag), lib.stream())
+            self._run("signal", self.k.ds41_signal_all, lib.ptr(self.epoch), lib.ptr(self.flag_out), self.world,
+                      lib.stream())
 
     # ------------------------------------------------------------------ one pass over `rows` rows
     def _hc(self, rows, pending, fn, scale, base, norm_w, tap=None, quant=False, engram=None):
@@ -1132,9 +1138,9 @@ class DS41Engine:
                           status=self.status, static_operand=1)
             ko = self.GL * cfg.o_lora
             s_o = self._splits(H, ko, R)
+            # the CTA of wo_b that finishes last publishes "this rank's attention planes are complete"
             self._run("gemm_wo_b", G.linear_planes, self.oa[:R], lw.wo_b, self.planes_o.view(-1)[: s_o * R * H].view(s_o, R, H), s_o,
-                            status=self.status)
-            self._signal()
+                            status=self.status, signal=self._sig_attn)
             pending = (self._o_bases, self.world, s_o, R * H)
             # ---------------- MoE sublayer
             self._hc(R, pending, lw.hc_ffn_fn, lw.hc_ffn_scale, lw.hc_ffn_base, lw.ffn_norm, quant=self.mx)
@@ -1149,6 +1155,7 @@ class DS41Engine:
             if self.debug is not None:
                 self.debug.append({"layer": l, "ids": self.ids[:R].clone(), "sel": self.sel[:R].clone(),
                                    "n_sel": self.n_sel[:R].clone()})
+            folded = False           # did the sublayer's last kernel publish the plane itself?
             if R > self.moe_rows:
                 self._moe_sorted(R, lw)
             else:
@@ -1215,9 +1222,16 @@ class DS41Engine:
                 s_s = self._splits(H, self.I_sh, R)
                 self._run("gemm_shared_down", G.linear_planes, self.shared_act[:R], lw.w2_sh,
                                 self.planes_shared.view(-1)[: s_s * R * H].view(s_s, R, H), s_s, status=self.status)
-                self._run("moe_combine", k.ds41_moe_combine, lib.ptr(self.fc2), lib.ptr(self.slot_of), lib.ptr(self.planes_shared), s_s,
-                                            R, lw.topk, H, lib.ptr(self.moe_plane), st())
-            self._signal()
+                if self.world > 1:       # the block that finishes last publishes the expert plane
+                    self._run("moe_combine", k.ds41_moe_combine_signal, lib.ptr(self.fc2), lib.ptr(self.slot_of),
+                              lib.ptr(self.planes_shared), s_s, R, lw.topk, H, lib.ptr(self.moe_plane),
+                              lib.ptr(self.sig_counters[1:2]), lib.ptr(self.epoch), lib.ptr(self.flag_out), self.world, st())
+                else:
+                    self._run("moe_combine", k.ds41_moe_combine, lib.ptr(self.fc2), lib.ptr(self.slot_of), lib.ptr(self.planes_shared), s_s,
+                                                R, lw.topk, H, lib.ptr(self.moe_plane), st())
+                folded = True
+            if not folded:
+                self._signal()
             pending = (self._moe_bases, self.world, 1, 0)
             if self.layer_timer is not None:
                 self.layer_timer.mark()

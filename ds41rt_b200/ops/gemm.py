@@ -41,7 +41,7 @@ def gemm_raw(A, B, out, M, N, K, *, lda, ldb, ldo, kind=0, out_mode=0, k_splits=
              a_batch_stride=0, b_batch_stride=0, out_batch_stride=0, a_batches=0, split_workspace=None,
              sfa=None, sfb=None, sfa_batch_stride=0, sfb_batch_stride=0, batch_map=None, n_active=None,
              b_batch_kind=0, up_row_offset=0, row_w=None, row_w_ld=0, act_limit=10.0, status=None,
-             static_operand=0, a_format=0, col_limit=None, alpha=0.0, alpha_batch=None):
+             static_operand=0, a_format=0, col_limit=None, alpha=0.0, alpha_batch=None, signal=None):
     a = lib.GemmArgs()
     a.A, a.B, a.out = lib.ptr(A), lib.ptr(B), lib.ptr(out)
     a.split_workspace = lib.ptr(split_workspace)
@@ -58,6 +58,9 @@ def gemm_raw(A, B, out, M, N, K, *, lda, ldb, ldo, kind=0, out_mode=0, k_splits=
     a.col_limit = lib.ptr(col_limit)
     a.alpha = alpha
     a.alpha_batch = lib.ptr(alpha_batch)
+    if signal is not None:          # (zeroed counter word, epoch word, device array of flag addresses, number of flags)
+        a.sig_counter, a.sig_epoch, a.sig_flags, a.sig_world = (lib.ptr(signal[0]), lib.ptr(signal[1]),
+                                                                lib.ptr(signal[2]), signal[3])
     lib.check(lib.kernels().ds41_gemm_tc(C.byref(a), lib.stream()), "ds41_gemm_tc")
 
 
@@ -83,14 +86,14 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     return out
 
 
-def linear_planes(x: torch.Tensor, w: torch.Tensor, planes: torch.Tensor, splits: int, *, status=None):
-    """Swap-AB split-K projection: planes[s, rows, N] (fp32) partial sums of x @ w.T."""
+def linear_planes(x: torch.Tensor, w: torch.Tensor, planes: torch.Tensor, splits: int, *, status=None, signal=None):
+    """Swap-AB split-K projection: planes[s, rows, N] (fp32) partial sums of x @ w.T.  `signal`: see gemm_raw."""
     rows, K = x.shape
     N = w.shape[0]
     assert planes.dtype == torch.float32 and planes.is_contiguous()
     if splits == 1:
         gemm_raw(w, x, planes, N, rows, K, lda=w.stride(0), ldb=x.stride(0), ldo=N, out_mode=3, status=status,
-                 static_operand=1)
+                 static_operand=1, signal=signal)
     else:
         gemm_raw(w, x, None, N, rows, K, lda=w.stride(0), ldb=x.stride(0), ldo=N, out_mode=3, k_splits=splits,
-                 split_workspace=planes, status=status, static_operand=1)
+                 split_workspace=planes, status=status, static_operand=1, signal=signal)

@@ -36,6 +36,7 @@ class GemmArgs(C.Structure):
         ("tile_group", C.c_void_p), ("tile_row0", C.c_void_p), ("tile_end", C.c_void_p), ("n_tiles_dev", C.c_void_p),
         ("scatter_meta", C.c_void_p), ("wait_flags", C.c_void_p), ("wait_epoch", C.c_void_p),
         ("scatter_out", C.c_void_p * 8), ("max_tiles", C.c_int), ("wait_world", C.c_int), ("a_format", C.c_int), ("col_limit", C.c_void_p), ("alpha", C.c_float), ("alpha_batch", C.c_void_p),
+        ("sig_counter", C.c_void_p), ("sig_epoch", C.c_void_p), ("sig_flags", C.c_void_p), ("sig_world", C.c_int),
     ]
 
 
@@ -120,7 +121,7 @@ def dir_functions():
     return [
         "ds41_gemm_tc", "ds41_embed_streams", "ds41_hc_post_mix", "ds41_hc_finish", "ds41_qkv_post",
         "ds41_compress", "ds41_index_score", "ds41_topk_select", "ds41_attend", "ds41_router_select",
-        "ds41_moe_plan", "ds41_moe_combine", "ds41_signal", "ds41_reduce_planes", "ds41_reduce_groups", "ds41_argmax_rows",
+        "ds41_moe_plan", "ds41_moe_combine", "ds41_signal", "ds41_signal_all", "ds41_moe_combine_signal", "ds41_reduce_planes", "ds41_reduce_groups", "ds41_argmax_rows",
         "ds41_argmax_merge", "ds41_spec_accept", "ds41_act_quant_mx", "ds41_decode_feedback", "ds41_hc_step", "ds41_taps_pack", "ds41_norm_rows", "ds41_markov_step", "ds41_dspark_confidence", "ds41_spec_feedback",
         "ds41_copy_ints", "ds41_rs_reduce", "ds41_ep_count", "ds41_ep_plan", "ds41_ep_dispatch", "ds41_ep_mark",
         "ds41_ep_wait", "ds41_ep_combine", "ds41_act_quant_mx_rows", "ds41_sample_rows", "ds41_engram_dequant", "ds41_engram_gate", "ds41_vis_rmsnorm", "ds41_vis_bias_act", "ds41_vis_silu_mul",
