@@ -714,6 +714,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     unsigned int last = 0;
     if (lane == 0) last = atomicAdd(p.sig_counter, 1u) == gridDim.x - 1 ? 1u : 0u;
     last = __shfl_sync(0xffffffffu, last, 0);
+    __syncwarp();                              // the other lanes order themselves after lane 0's view of the counter
     if (last) {
       __threadfence();
       uint32_t e = 0;
@@ -723,8 +724,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         *p.sig_counter = 0u;
       }
       e = __shfl_sync(0xffffffffu, e, 0);
-      __threadfence_system();
-      if (lane < p.sig_world) flag_store_release(const_cast<uint32_t*>(p.sig_flags[lane]), e);
+      if (lane < p.sig_world) flag_store_release(const_cast<uint32_t*>(p.sig_flags[lane]), e);   // release at system scope
     }
   }
   if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != kStatusOk) {

@@ -191,7 +191,8 @@ __device__ __forceinline__ void publish_all(unsigned int* counter, uint32_t* epo
       *counter = 0u;
     }
     e = __shfl_sync(0xffffffffu, e, 0);
-    __threadfence_system();
+    // one release store per flag: it orders this rank's earlier plane writes (observed through the counter and the
+    // fence above) before the flag at system scope; no separate system fence is needed in front of it
     if (static_cast<int>(threadIdx.x) < n_flags) flag_store_release(flags[threadIdx.x], e);
   }
 }
@@ -230,7 +231,6 @@ __global__ void signal_all_kernel(unsigned int* epoch, uint32_t* const* flags, i
     *epoch = e;
   }
   e = __shfl_sync(0xffffffffu, e, 0);
-  __threadfence_system();
   if (static_cast<int>(threadIdx.x) < n) flag_store_release(flags[threadIdx.x], e);
 }
 
