@@ -286,6 +286,12 @@ typedef struct {
   int* n_tiles;             // [2]
   int* total_rows;
   int* status;
+  // FP8 rows on the wire (optional, all three set or none): ds41_ep_dispatch quantises every row it sends (E4M3 values,
+  // one UE8M0 scale per 128 values) and stores values and scales straight into the destination's operand buffers of
+  // the block-scaled FC1 - 5280 bytes per row of 5120 values instead of 10240 - and recv_x is not written.
+  void* recv_q[8];          // uint8 [cap, H] at each rank
+  void* recv_sf[8];         // scale atoms [cap/128][H/128][512] at each rank
+  int wire_fp8;
 } ds41_ep_args;
 int ds41_ep_count(const ds41_ep_args* a, void* stream);
 int ds41_ep_plan(const ds41_ep_args* a, void* stream);

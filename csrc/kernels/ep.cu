@@ -23,6 +23,8 @@
 // and sums partial planes (rust/crates/ds41rt-transport/src/v41_expert.rs:27-111, dispatch/collect/reduce wave in
 // rust/crates/ds41rt-daemon/src/v41_experts/coordinator.rs; counting sort by expert in ds4_flash_aot.cu).  This file
 // is the NVLink counterpart: tokens travel only to the rank that owns their expert and come back once.
+#include <cuda_fp8.h>
+
 #include "ds41_api.h"
 #include "ds41_launch.cuh"
 #include "ds41_ptx.cuh"
@@ -49,6 +51,9 @@ struct EpParams {
   int* n_tiles;
   int* total_rows;
   int* status;
+  uint8_t* recv_q[8];
+  uint8_t* recv_sf[8];
+  int wire_fp8;
 };
 
 constexpr int kEpOverflow = 7;   // status code: received rows exceed the receive buffer
@@ -187,6 +192,55 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpParams p) {
     row = __shfl_sync(0xffffffffu, row, 0);
     if (row < 0 || row >= p.cap) continue;
     const int tok = i / p.topk;
+    if (p.wire_fp8) {
+      // FP8 on the wire: 8 values per lane and step, one scale per 128 values (16 lanes); values and scale bytes go
+      // straight into the destination's FC1 operand buffers (scale atoms of the tensor cores' block-scaled kind)
+      const __nv_bfloat16* srow = p.x + 1ll * tok * p.H;
+      uint8_t* qrow = p.recv_q[dst] + 1ll * row * p.H;
+      uint8_t* atom_row = p.recv_sf[dst] + 1ll * (row / 128) * (p.H / 128) * 512 + (row % 32) * 16 + ((row / 32) % 4) * 4;
+      for (int k0 = 0; k0 < p.H; k0 += 512) {       // two steps of 256 values in flight
+        uint4 raw[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int k = k0 + u * 256 + lane * 8;
+          raw[u] = k < p.H ? *reinterpret_cast<const uint4*>(srow + k) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int k = k0 + u * 256 + lane * 8;
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+          float f[8];
+          float amax = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 v = __bfloat1622float2(h[j]);
+            f[2 * j] = v.x;
+            f[2 * j + 1] = v.y;
+            amax = fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y)));
+          }
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
+          if (k < p.H) {
+            const uint32_t e = ue8m0_ceil_exp(amax * (1.0f / 448.0f));
+            const float inv = __uint_as_float((254u - e) << 23);
+            const __nv_fp8x4_e4m3 lo(make_float4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv));
+            const __nv_fp8x4_e4m3 hi(make_float4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv));
+            uint2 o;
+            o.x = *reinterpret_cast<const uint32_t*>(&lo);
+            o.y = *reinterpret_cast<const uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(qrow + k) = o;
+            if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(atom_row + 1ll * (k / 128) * 512) = e * 0x01010101u;
+          }
+        }
+      }
+      if (lane == 0) {
+        p.recv_meta[dst][row] = make_int2(p.rank, i);
+        p.recv_w[dst][row] = p.weights[i];
+      }
+      continue;
+    }
     const uint4* src = reinterpret_cast<const uint4*>(p.x + 1ll * tok * p.H);
     uint4* out = reinterpret_cast<uint4*>(p.recv_x[dst] + 1ll * row * p.H);
     for (int v0 = 0; v0 < vec; v0 += 32 * 4) {      // four 16-byte loads in flight per lane
@@ -294,6 +348,13 @@ static bool fill(const ds41_ep_args* a, EpParams& p) {
   }
   p.tile_group = a->tile_group; p.tile_row0 = a->tile_row0; p.tile_end = a->tile_end;
   p.n_tiles = a->n_tiles; p.total_rows = a->total_rows; p.status = a->status;
+  p.wire_fp8 = a->wire_fp8;
+  for (int r = 0; r < 8; ++r) {
+    p.recv_q[r] = static_cast<uint8_t*>(a->recv_q[r]);
+    p.recv_sf[r] = static_cast<uint8_t*>(a->recv_sf[r]);
+    if (p.wire_fp8 && r < p.world && (p.recv_q[r] == nullptr || p.recv_sf[r] == nullptr)) return false;
+  }
+  if (p.wire_fp8 && (p.H % 256) != 0) return false;
   return true;
 }
 

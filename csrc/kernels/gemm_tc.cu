@@ -121,7 +121,11 @@ struct GemmCfg {
   static constexpr int kStages = kStagesRaw > kStageCap ? kStageCap : kStagesRaw;
   static constexpr int kSfCols = kScaled ? 4 * (kAtomsA + kAtomsB) : 0;               // TMEM columns per stage
   static constexpr int kAccCols = (BN < 32 ? 32 : BN) * (DUAL ? 2 : 1);
-  static constexpr int kTmemNeeded = 2 * kAccCols + kStages * kSfCols;
+  // Two accumulator sets let the epilogue of one tile overlap the MMAs of the next.  The widest block-scaled dual tile
+  // (128 tokens x gate + up) leaves room for only one beside its scale columns; it is still the better trade there:
+  // each weight byte fetched from L2 serves twice the tokens of a 64-wide tile.
+  static constexpr int kAccStages = (2 * kAccCols + kStages * kSfCols <= 512) ? 2 : 1;
+  static constexpr int kTmemNeeded = kAccStages * kAccCols + kStages * kSfCols;
   static constexpr int kTmemCols = kTmemNeeded <= 32 ? 32 : kTmemNeeded <= 64 ? 64 : kTmemNeeded <= 128 ? 128
                                    : kTmemNeeded <= 256 ? 256 : 512;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStaging + 1024 /*align*/ + 256 /*barriers*/;
@@ -336,7 +340,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint64_t bdesc = umma_desc_sw128(sb);
         if constexpr (Cfg::kScaled) {
           const uint32_t ssf = sb + Cfg::kBBytes;
-          const uint32_t sf_t = tmem_base + 2 * Cfg::kAccCols + stage * Cfg::kSfCols;
+          const uint32_t sf_t = tmem_base + Cfg::kAccStages * Cfg::kAccCols + stage * Cfg::kSfCols;
 #pragma unroll
           for (int a = 0; a < Cfg::kAtomsA + Cfg::kAtomsB; ++a)
             tmem_cp_32x128b_warpx4(sf_t + 4 * a, umma_desc_plain(ssf + 512 * a, 16, 128));
@@ -382,7 +386,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (++stage == S) { stage = 0; phase ^= 1; }
       }
       if (ok) tc_commit(&acc_full[acc]);
-      acc ^= 1;
+      acc = (acc + 1 == Cfg::kAccStages) ? 0 : acc + 1;
       if (acc == 0) acc_phase ^= 1;
     }
   } else if (warp >= 2 && warp < 6) {
@@ -663,7 +667,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
-      acc ^= 1;
+      acc = (acc + 1 == Cfg::kAccStages) ? 0 : acc + 1;
       if (acc == 0) acc_phase ^= 1;
     }
     if (p.out_mode == 6 && lane == 0) bulk_wait_group<0>();   // every TMA store of this warp has been performed
@@ -761,7 +765,7 @@ static cudaError_t dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap
       case 32: return launch_gemm<32, KIND, 1>(tmA, tmB, peer, p, grid, stream);
       case 64: return launch_gemm<64, KIND, 1>(tmA, tmB, peer, p, grid, stream);
       case 128:
-        if constexpr (KIND < 2) return launch_gemm<128, KIND, 1>(tmA, tmB, peer, p, grid, stream);
+        if constexpr (KIND < 3) return launch_gemm<128, KIND, 1>(tmA, tmB, peer, p, grid, stream);
         return cudaErrorInvalidValue;
       default: return cudaErrorInvalidValue;
     }

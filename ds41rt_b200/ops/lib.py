@@ -77,6 +77,7 @@ class EpArgs(C.Structure):
         ("recv_meta", C.c_void_p * 8), ("recv_w", C.c_void_p * 8), ("flags", C.c_void_p * 8),
         ("tile_group", C.c_void_p), ("tile_row0", C.c_void_p), ("tile_end", C.c_void_p), ("n_tiles", C.c_void_p),
         ("total_rows", C.c_void_p), ("status", C.c_void_p),
+        ("recv_q", C.c_void_p * 8), ("recv_sf", C.c_void_p * 8), ("wire_fp8", C.c_int),
     ]
 
 

@@ -34,11 +34,17 @@ class ExpertParallelMoE:
     def __init__(self, fabric: Fabric, w13: torch.Tensor, w2: torch.Tensor, *, topk: int, max_tokens: int,
                  act_limit: float = 10.0, capacity: Optional[int] = None, w13_sf: Optional[torch.Tensor] = None,
                  w2_sf: Optional[torch.Tensor] = None, fp4: bool = False, nvfp4=None,
-                 w13_gs: Optional[torch.Tensor] = None, w2_gs: Optional[torch.Tensor] = None):
+                 w13_gs: Optional[torch.Tensor] = None, w2_gs: Optional[torch.Tensor] = None,
+                 wire: str = "auto"):
         """w13: [E_local, 2*I, H] (gate rows then up rows), w2: [E_local, H, I]; bf16, or e4m3 with UE8M0 scale atoms,
         or (fp4) E2M1 codes two per byte ([.., H/2] / [.., I/2] uint8) with UE8M0 scale atoms, or (nvfp4 = the two
         activation scales) E2M1 codes with E4M3 scale atoms per 16 and one global scale per expert (w13_gs / w2_gs):
-        then the received rows and the FC1 output are quantised to NVFP4 too (W4A4)."""
+        then the received rows and the FC1 output are quantised to NVFP4 too (W4A4).
+        wire: what a token row looks like on NVLink.  "fp8" (the default for block-scaled FP8 / FP4 experts): the
+        sender quantises the row inside the dispatch kernel (E4M3 + one UE8M0 scale per 128 values, 5280 bytes for 5120
+        values - the reference's wire format, docs/dspark-bandwidth-policy.md:19-20) and stores it straight into the
+        owner's FC1 operand buffers, so no receive-side wait or quantisation kernel runs; "bf16": rows travel as bf16
+        and the owner quantises what it received."""
         self.f = fabric
         self.w13, self.w2, self.w13_sf, self.w2_sf = w13, w2, w13_sf, w2_sf
         self.mx = w13_sf is not None and nvfp4 is None
@@ -50,10 +56,15 @@ class ExpertParallelMoE:
             self.H *= 2
         self.I = two_i // 2
         self.topk, self.max_tokens, self.act_limit = topk, max_tokens, act_limit
+        assert wire in ("auto", "fp8", "bf16")
+        self.wire_fp8 = self.mx and wire != "bf16"
         W, dev = fabric.world, fabric.device
         assert self.H % 128 == 0 and self.I % 128 == 0 and W <= 8
         scaled = self.mx or self.nv is not None
-        self.bn = 64 if scaled else 128           # FC1: gate and up accumulators share tensor memory
+        # FC1 tile width in tokens.  Gate and up accumulators share tensor memory with the scale columns: the block-scaled
+        # FP8 kind still takes 128 tokens with a single accumulator set (half the weight bytes per token from L2, which
+        # is what bounds it); NVFP4 carries four times the scale columns and stays at 64
+        self.bn = 128 if (not scaled or self.mx) else 64
         self.bn2 = 128 if scaled else 256          # FC2
         worst = W * max_tokens * topk
         self.cap = _round_up(min(worst, capacity) if capacity else worst, 128) + 128 * self.e_local
@@ -62,13 +73,16 @@ class ExpertParallelMoE:
         # symmetric memory: [counts | send_base | flags | recv_meta | recv_w | recv_x | comb]
         off, lay = 0, {}
         for name, nbytes in (("counts", 4 * W * self.e_local), ("send_base", 4 * W * self.e_local), ("flags", 64),
-                             ("recv_meta", 8 * cap), ("recv_w", 4 * cap), ("recv_x", 2 * cap * H),
+                             ("recv_meta", 8 * cap), ("recv_w", 4 * cap),
+                             ("recv_x", 0 if self.wire_fp8 else 2 * cap * H),
+                             ("recv_q", cap * H if self.wire_fp8 else 0),
+                             ("recv_sf", cap // 128 * (H // 128) * 512 if self.wire_fp8 else 0),
                              ("comb", 2 * max_tokens * topk * H)):
             lay[name] = off
             off += _round_up(nbytes, 256)
         self.sym = fabric.alloc(off)
         self.lay = lay
-        self.recv_x = self.sym.view(torch.bfloat16, (cap, H), lay["recv_x"])
+        self.recv_x = None if self.wire_fp8 else self.sym.view(torch.bfloat16, (cap, H), lay["recv_x"])
         self.recv_w = self.sym.view(torch.float32, (cap,), lay["recv_w"])
         self.recv_meta = self.sym.view(torch.int32, (cap, 2), lay["recv_meta"])
         self.comb = self.sym.view(torch.bfloat16, (max_tokens * topk, H), lay["comb"])
@@ -97,8 +111,12 @@ class ExpertParallelMoE:
             self.actq_sf = torch.zeros(cap // 128 * (self.I // 64) * 512, **u8)
         if self.mx:
             u8 = dict(dtype=torch.uint8, device=dev)
-            self.xq = torch.zeros(cap, H, **u8)
-            self.xq_sf = torch.zeros(cap // 128 * (H // 128) * 512, **u8)
+            if self.wire_fp8:           # the FC1 operand buffers are the receive buffers: peers write them directly
+                self.xq = self.sym.view(torch.uint8, (cap, H), lay["recv_q"])
+                self.xq_sf = self.sym.view(torch.uint8, (cap // 128 * (H // 128) * 512,), lay["recv_sf"])
+            else:
+                self.xq = torch.zeros(cap, H, **u8)
+                self.xq_sf = torch.zeros(cap // 128 * (H // 128) * 512, **u8)
             self.actq = torch.zeros(cap, self.I, **u8)
             self.actq_sf = torch.zeros(cap // 128 * (self.I // 128) * 512, **u8)
         self.dispatch_blocks = 4 * 148
@@ -125,6 +143,10 @@ class ExpertParallelMoE:
             a.recv_meta[r] = base + self.lay["recv_meta"]
             a.recv_w[r] = base + self.lay["recv_w"]
             a.flags[r] = base + self.lay["flags"]
+            if self.wire_fp8:
+                a.recv_q[r] = base + self.lay["recv_q"]
+                a.recv_sf[r] = base + self.lay["recv_sf"]
+        a.wire_fp8 = 1 if self.wire_fp8 else 0
         a.tile_group, a.tile_row0, a.tile_end = lib.ptr(self.tile_group), lib.ptr(self.tile_row0), lib.ptr(self.tile_end)
         a.n_tiles, a.total_rows, a.status = lib.ptr(self.n_tiles), lib.ptr(self.total_rows), lib.ptr(self.status)
         return a
@@ -205,12 +227,18 @@ class ExpertParallelMoE:
                           alpha_batch=self.w2_gs)
             self._mark("quant+fc2")
         elif self.mx:
-            lib.check(k.ds41_ep_wait(C.byref(a), 2, st()), "ep_wait")
             cap = self.cap
-            lib.check(k.ds41_act_quant_mx_rows(lib.ptr(self.recv_x), C.c_longlong(H), lib.ptr(self.xq), C.c_longlong(H),
-                                               lib.ptr(self.xq_sf), cap, H, lib.ptr(self.total_rows), st()), "act_quant")
-            self._grouped(self.w13, self.xq, self.act, I, H, lda=H, ldo=I, out_mode=4, up_row_offset=I,
-                          sfa=self.w13_sf, sfa_batch_stride=self.w13_sf[0].numel(), sfb=self.xq_sf)
+            if self.wire_fp8:
+                # the rows arrived quantised, in place: FC1 waits for the peers' dispatch flags inside the kernel
+                self._grouped(self.w13, self.xq, self.act, I, H, lda=H, ldo=I, out_mode=4, up_row_offset=I,
+                              sfa=self.w13_sf, sfa_batch_stride=self.w13_sf[0].numel(), sfb=self.xq_sf, wait_phase=2)
+            else:
+                lib.check(k.ds41_ep_wait(C.byref(a), 2, st()), "ep_wait")
+                lib.check(k.ds41_act_quant_mx_rows(lib.ptr(self.recv_x), C.c_longlong(H), lib.ptr(self.xq),
+                                                   C.c_longlong(H), lib.ptr(self.xq_sf), cap, H,
+                                                   lib.ptr(self.total_rows), st()), "act_quant")
+                self._grouped(self.w13, self.xq, self.act, I, H, lda=H, ldo=I, out_mode=4, up_row_offset=I,
+                              sfa=self.w13_sf, sfa_batch_stride=self.w13_sf[0].numel(), sfb=self.xq_sf)
             self._mark("wait+quant+fc1")
             lib.check(k.ds41_act_quant_mx_rows(lib.ptr(self.act), C.c_longlong(I), lib.ptr(self.actq), C.c_longlong(I),
                                                lib.ptr(self.actq_sf), cap, I, lib.ptr(self.total_rows), st()), "act_quant")

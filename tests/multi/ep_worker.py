@@ -44,6 +44,7 @@ def main():
     E, topk = int(os.environ.get("EP_E", "16")), int(os.environ.get("EP_TOPK", "4"))
     reps, skew = int(os.environ.get("EP_REPS", "5")), int(os.environ.get("EP_SKEW", "0"))
     mx = int(os.environ.get("EP_MX", "0"))
+    wire = os.environ.get("EP_WIRE", "auto")       # block-scaled experts: "fp8" (sender quantises) or "bf16" rows on NVLink
     EL = E // W
     g = torch.Generator(device=dev).manual_seed(7 + f.rank)
     w13 = (torch.randn(EL, 2 * I, H, device=dev, generator=g) * 0.04)
@@ -52,7 +53,7 @@ def main():
         from ds41rt_b200.models.ds41 import dequantize_expert, quantize_expert_stack
         q13, s13 = quantize_expert_stack(w13.cpu(), dev)
         q2, s2 = quantize_expert_stack(w2.cpu(), dev)
-        moe = ExpertParallelMoE(f, q13, q2, topk=topk, max_tokens=T, w13_sf=s13, w2_sf=s2)
+        moe = ExpertParallelMoE(f, q13, q2, topk=topk, max_tokens=T, w13_sf=s13, w2_sf=s2, wire=wire)
         w13_ref = torch.stack([dequantize_expert(q13[e], s13[e]) for e in range(EL)]).to(dev).bfloat16()
         w2_ref = torch.stack([dequantize_expert(q2[e], s2[e]) for e in range(EL)]).to(dev).bfloat16()
     else:
@@ -86,8 +87,10 @@ def main():
         peak = float(os.environ.get("PEAK_TFLOPS", "1430")) * 1e12 * (2 if mx else 1)
         link = 770e9
         remote = routes * (W - 1) / W
-        nv_bytes = remote * H * 2 * 2                           # bf16 out and bf16 back, per direction: H*2 each
+        out_row = (H + H // 32) if (mx and wire != "bf16") else 2 * H     # FP8 + scales on the way out, bf16 back
+        nv_bytes = remote * (out_row + H * 2)
         res = {"world": W, "tokens_per_rank": T, "H": H, "I": I, "E": E, "topk": topk, "skew": skew, "mx": mx,
+               "wire": ("fp8" if (mx and wire != "bf16") else "bf16"),
                "fused_ms": t_fused, "nccl_library_ms": t_base,
                "roofline_ms": max(flops / peak, (nv_bytes / 2) / link) * 1e3}
         res["frac_of_roofline"] = res["roofline_ms"] / t_fused

@@ -53,12 +53,18 @@ def _run_ep(nproc: int, port: int, **env_extra):
 def test_grouped_experts_one_rank(mx):
     """Tile-table grouped GEMMs and the scatter epilogue with every expert local (no peers)."""
     _run_ep(1, 0, EP_TOKENS="384", EP_H="512", EP_I="256", EP_E="8", EP_TOPK="4", EP_REPS="2", EP_MX=mx)
+    if mx == "1":
+        _run_ep(1, 0, EP_TOKENS="384", EP_H="512", EP_I="256", EP_E="8", EP_TOPK="4", EP_REPS="2", EP_MX=mx,
+                EP_WIRE="bf16")
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("mx", ["0", "1"])
-def test_expert_parallel_dispatch_gemm_combine(mx):
-    _run_ep(2, 29521, EP_TOKENS="384", EP_H="512", EP_I="256", EP_E="8", EP_TOPK="4", EP_REPS="2", EP_MX=mx)
+@pytest.mark.parametrize("mx,wire", [("0", "auto"), ("1", "fp8"), ("1", "bf16")])
+def test_expert_parallel_dispatch_gemm_combine(mx, wire):
+    """wire "fp8": the sender quantises each row inside the dispatch kernel and stores it into the owner's FC1 operand
+    buffers; "bf16": bf16 rows travel and the owner quantises what it received."""
+    _run_ep(2, 29521, EP_TOKENS="384", EP_H="512", EP_I="256", EP_E="8", EP_TOPK="4", EP_REPS="2", EP_MX=mx,
+            EP_WIRE=wire)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
