@@ -156,10 +156,13 @@ int ds41_compress(const float* extras, int extra_stride, int rows, int D, int ID
                   const int* row_pos, const int* row_slot, float* pending, const float* comp_norm_w, const void* wk,
                   const float* k_norm_w, const float* inv_freq, const float* inv_freq_idx, const int* page_table,
                   int max_pages, int page_rows, void* comp_pool, void* idx_pool, float eps, int kv_row_bytes,
-                  void* stream);
+                  int idx_row_bytes, void* stream);
 
 // ---------------------------------------------------------------------------------------------------
 // Indexer, top-k and sparse attention (sparse_attn.cu)
+// idx_row_bytes (ds41_compress, ds41_index_score_cand, ds41_index_prepare): 0 = index keys are bf16 rows of ID values;
+// > 0 = FP4 rows that many bytes apart: ID/2 bytes of E2M1 pairs (even value in the low nibble), then ID/32 UE8M0
+// scales (68 bytes for ID = 128).  With FP4 keys the queries are quantised to the same format before the dot.
 int ds41_index_score(const void* q, long long ldq, int q_off, const float* w, int w_stride, int w_off,
                      const void* idx_pool, const int* page_table, int max_pages, int page_rows, const int* row_pos,
                      const int* row_slot, const float* inv_freq_idx, int rows, int IH, int ID, int ratio,
@@ -169,7 +172,7 @@ int ds41_index_score(const void* q, long long ldq, int q_off, const float* w, in
 int ds41_index_prepare(const void* q, long long ldq, int q_off, const void* idx_pool, const int* page_table,
                        int max_pages, int page_rows, const int* row_pos, const int* row_slot,
                        const float* inv_freq_idx, int rows, int IH, int ID, int ratio, int n_keys, int max_keys,
-                       void* qr, void* kc, int* n_vis, void* stream);
+                       void* qr, void* kc, int* n_vis, int idx_row_bytes, void* stream);
 int ds41_topk_select(const float* scores, int max_keys, const int* row_pos, const int* row_slot, int ratio, int k,
                      int* sel, int* n_sel, int rows, void* stream);
 // Candidate blocks of the long-context indexer: ds41_candidate_select reduces one layer's scores to block maxima (blocks
@@ -183,7 +186,7 @@ int ds41_index_score_cand(const void* q, long long ldq, int q_off, const float* 
                           const void* idx_pool, const int* page_table, int max_pages, int page_rows,
                           const int* row_pos, const int* row_slot, const float* inv_freq_idx, int rows, int IH, int ID,
                           int ratio, float* scores, int max_keys, const void* cand_mask, int cand_words,
-                          int cand_block, void* stream);
+                          int cand_block, int idx_row_bytes, void* stream);
 int ds41_topk_select_cand(const float* scores, int max_keys, const int* row_pos, const int* row_slot, int ratio, int k,
                           int* sel, int* n_sel, int rows, const void* cand_mask, int cand_words, int cand_block,
                           void* stream);

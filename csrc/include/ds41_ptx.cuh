@@ -6,6 +6,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
+#include <cuda_fp4.h>
 #include <cuda_fp8.h>
 #include <stdint.h>
 
@@ -139,6 +140,32 @@ __device__ __forceinline__ float e2m1_value(uint32_t code) {
   const uint32_t m = code & 7u;
   const float a = m < 2u ? 0.5f * m : (m & 1u ? 1.5f : 1.0f) * static_cast<float>(1u << ((m >> 1) - 1u));
   return (code & 8u) ? -a : a;
+}
+
+// ------------------------------------------------------------------ FP4 index rows (E2M1 pairs + one UE8M0 scale per 32)
+// A thread holds one pair of adjacent values; the 16 threads of a 32-value group (16 consecutive lanes, all active)
+// agree on the scale ceil_pow2(max(amax, 6 * 2^-126) / 6) and each returns its packed byte (even value in the low
+// nibble; saturating round-to-nearest-even on the E2M1 grid).  `mask` names the lanes that take part (taken with
+// __activemask() where they are known to be converged, i.e. before any branch that splits a group).
+// Reference: native/cuda/kernels/v41_compressor.cu:25-41.
+__device__ __forceinline__ uint32_t fp4_group_pack(float a, float b, uint32_t* exponent_out, unsigned mask) {
+  float m = fmaxf(fabsf(a), fabsf(b));
+#pragma unroll
+  for (int delta = 8; delta; delta >>= 1) m = fmaxf(m, __shfl_xor_sync(mask, m, delta, 16));
+  m = fmaxf(m, 6.0f * 0x1p-126f);
+  const uint32_t bits = __float_as_uint(m / 6.0f);
+  const uint32_t exponent = (bits >> 23) + ((bits & 0x7fffffu) != 0 ? 1u : 0u);
+  const float scale = __uint_as_float(exponent << 23);
+  *exponent_out = exponent;
+  return static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(make_float2(a / scale, b / scale), __NV_E2M1, cudaRoundNearest));
+}
+// quantise and dequantise in place (the values an FP4 operand would carry)
+__device__ __forceinline__ void fp4_group_qdq(float& a, float& b, unsigned mask) {
+  uint32_t e;
+  const uint32_t byte = fp4_group_pack(a, b, &e, mask);
+  const float scale = __uint_as_float(e << 23);
+  a = e2m1_value(byte & 15u) * scale;
+  b = e2m1_value((byte >> 4) & 15u) * scale;
 }
 
 __device__ __forceinline__ void flag_store_release(uint32_t* flag, uint32_t value) {

@@ -200,8 +200,9 @@ struct CompressParams {
   int max_pages, page_rows;
   __nv_bfloat16* comp_pool;  // [pool_rows][D] bf16, FP8 rows of kv_row_bytes bytes, or FP4 rows of -kv_row_bytes bytes
   int kv_row_bytes;
-  __nv_bfloat16* idx_pool;   // [pool_rows][ID]
+  __nv_bfloat16* idx_pool;   // [pool_rows][ID] bf16, or FP4 rows of idx_row_bytes bytes (ID/2 E2M1 bytes + ID/32 UE8M0)
   float eps;
+  int idx_row_bytes;
 };
 
 // One block (256 threads) per row.  D <= 1024, ID <= 256.
@@ -268,6 +269,7 @@ __global__ void __launch_bounds__(256) compress_kernel(CompressParams p) {
   const long long phys = 1ll * page * p.page_rows + crow % p.page_rows;
   const int idx_rope = p.ID / 2;
   for (int i = tid; i < p.ID / 2; i += 256) {
+    const unsigned lanes = __activemask();          // whole 16-lane groups: ID / 2 is a multiple of 16
     float a = bf16_round(ikey[2 * i] * inv * p.k_norm_w[2 * i]);
     float b = bf16_round(ikey[2 * i + 1] * inv * p.k_norm_w[2 * i + 1]);
     const int t = 2 * i - (p.ID - idx_rope);
@@ -278,7 +280,17 @@ __global__ void __launch_bounds__(256) compress_kernel(CompressParams p) {
       a = ra;
       b = rb;
     }
-    reinterpret_cast<__nv_bfloat162*>(p.idx_pool + phys * p.ID)[i] = __floats2bfloat162_rn(a, b);
+    if (p.idx_row_bytes == 0) {
+      reinterpret_cast<__nv_bfloat162*>(p.idx_pool + phys * p.ID)[i] = __floats2bfloat162_rn(a, b);
+    } else {
+      // FP4 key row: the 16 threads of a 32-value group share one scale (ID / 2 is a multiple of 16, so the groups
+      // are whole in every active warp)
+      uint8_t* row = reinterpret_cast<uint8_t*>(p.idx_pool) + phys * p.idx_row_bytes;
+      uint32_t e;
+      const uint32_t byte = fp4_group_pack(bf16_round(a), bf16_round(b), &e, lanes);
+      row[i] = static_cast<uint8_t>(byte);
+      if ((i & 15) == 0) row[p.ID / 2 + (i >> 4)] = static_cast<uint8_t>(e);
+    }
   }
   for (int i0 = 0; i0 < p.D / 2; i0 += 256) {
     const int i = i0 + tid;
@@ -331,7 +343,9 @@ extern "C" int ds41_compress(const float* extras, int extra_stride, int rows, in
                              const int* row_pos, const int* row_slot, float* pending, const float* comp_norm_w,
                              const void* wk, const float* k_norm_w, const float* inv_freq, const float* inv_freq_idx,
                              const int* page_table, int max_pages, int page_rows, void* comp_pool, void* idx_pool,
-                             float eps, int kv_row_bytes, void* stream) {
+                             float eps, int kv_row_bytes, int idx_row_bytes, void* stream) {
+  if (idx_row_bytes != 0 && (idx_row_bytes < ID / 2 + ID / 32 || (ID & 31) || (idx_row_bytes & 3)))
+    return cudaErrorInvalidValue;
   // kv_row_bytes: 0 bf16 rows, > 0 FP8 rows (D + D/32 bytes, padded), < 0 FP4 rows of -kv_row_bytes (D/2 + D/16 bytes)
   if (kv_row_bytes > 0 && (kv_row_bytes < D + D / 32 || (D & 31) || (kv_row_bytes & 15))) return cudaErrorInvalidValue;
   if (kv_row_bytes < 0 && (-kv_row_bytes < D / 2 + D / 16 || (D & 15) || ((-kv_row_bytes) & 15)))
@@ -341,6 +355,6 @@ extern "C" int ds41_compress(const float* extras, int extra_stride, int rows, in
   CompressParams p{extras, extra_stride, rows, D, ID, rope_dim, ratio, row_pos, row_slot, pending, comp_norm_w,
                    static_cast<const __nv_bfloat16*>(wk), k_norm_w, inv_freq, inv_freq_idx, page_table, max_pages,
                    page_rows, static_cast<__nv_bfloat16*>(comp_pool), kv_row_bytes,
-                   static_cast<__nv_bfloat16*>(idx_pool), eps};
+                   static_cast<__nv_bfloat16*>(idx_pool), eps, idx_row_bytes};
   return launch_pdl(compress_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
 }

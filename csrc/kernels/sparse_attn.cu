@@ -46,7 +46,18 @@ struct IndexScoreParams {
   int max_keys;
   const uint32_t* cand_mask;  // optional [rows][cand_words]: one bit per block of cand_block keys; 0 = not scored
   int cand_words, cand_block;
+  // > 0: key rows are FP4 (ID/2 bytes of E2M1 pairs, then ID/32 UE8M0 scales; idx_row_bytes apart) and the queries are
+  // quantised to the same format before the dot; products are rounded to bf16 where the reference rounds them
+  // (native/cuda/kernels/v41_index_scores.cu:36-103).  0: bf16 rows of ID values.
+  int idx_row_bytes;
 };
+
+// two adjacent values of an FP4 key row
+__device__ __forceinline__ float2 fp4_key_pair(const uint8_t* row, int ID, int d) {
+  const uint32_t byte = row[d >> 1];
+  const float scale = __uint_as_float(static_cast<uint32_t>(row[ID / 2 + (d >> 5)]) << 23);
+  return make_float2(e2m1_value(byte & 15u) * scale, e2m1_value(byte >> 4) * scale);
+}
 
 __device__ __forceinline__ bool cand_allowed(const uint32_t* mask, int words, int block, int r, int key) {
   if (mask == nullptr) return true;
@@ -68,6 +79,7 @@ __global__ void __launch_bounds__(256) index_score_kernel(IndexScoreParams p) {
   if (blockIdx.x * 8 >= n_vis) return;
   const int rope0 = p.ID - p.ID / 2;
   for (int idx = tid; idx < p.IH * p.ID / 2; idx += 256) {
+    const unsigned lanes = __activemask();
     const int h = idx / (p.ID / 2), i = idx % (p.ID / 2);
     const float2 v = __bfloat1622float2(
         *reinterpret_cast<const __nv_bfloat162*>(p.q + 1ll * r * p.ldq + p.q_off + h * p.ID + 2 * i));
@@ -80,6 +92,7 @@ __global__ void __launch_bounds__(256) index_score_kernel(IndexScoreParams p) {
       a = bf16_round(ra);
       b = bf16_round(rb);
     }
+    if (p.idx_row_bytes > 0) fp4_group_qdq(a, b, lanes);   // 16 consecutive threads hold one 32-value group of a head
     qs[h][2 * i] = a;
     qs[h][2 * i + 1] = b;
   }
@@ -94,7 +107,10 @@ __global__ void __launch_bounds__(256) index_score_kernel(IndexScoreParams p) {
     __syncwarp();
     for (int d = lane * 2; d < p.ID; d += 64) {
       float2 v = make_float2(0.f, 0.f);
-      if (phys >= 0) v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p.idx_pool + phys * p.ID + d));
+      if (phys >= 0)
+        v = p.idx_row_bytes > 0
+                ? fp4_key_pair(reinterpret_cast<const uint8_t*>(p.idx_pool) + phys * p.idx_row_bytes, p.ID, d)
+                : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p.idx_pool + phys * p.ID + d));
       kbuf[warp][d] = v.x;
       kbuf[warp][d + 1] = v.y;
     }
@@ -102,9 +118,11 @@ __global__ void __launch_bounds__(256) index_score_kernel(IndexScoreParams p) {
     float acc = 0.f;
     if (lane < p.IH) {
       for (int d = 0; d < p.ID; ++d) acc = fmaf(qs[lane][d], kbuf[warp][d], acc);
-      acc = fmaxf(acc, 0.f) * ws[lane];
+      if (p.idx_row_bytes > 0) acc = bf16_round(fmaxf(bf16_round(acc), 0.f) * ws[lane]);   // the reference's rounding points
+      else acc = fmaxf(acc, 0.f) * ws[lane];
     }
     acc = warp_sum(acc);
+    if (p.idx_row_bytes > 0) acc = bf16_round(acc);
     if (lane == 0) p.scores[1ll * r * p.max_keys + c] = phys >= 0 ? acc : -INFINITY;
   }
 }
@@ -125,6 +143,7 @@ __global__ void __launch_bounds__(256) index_prepare_kernel(IndexScoreParams p, 
     if (tid == 0) n_vis[r] = slot < 0 ? 0 : min(min((pos + 1) / p.ratio, p.max_keys), n_keys);
     const int rope0 = p.ID - p.ID / 2;
     for (int idx = tid; idx < p.IH * p.ID / 2; idx += 256) {
+      const unsigned lanes = __activemask();
       const int h = idx / (p.ID / 2), i = idx % (p.ID / 2);
       const float2 v = __bfloat1622float2(
           *reinterpret_cast<const __nv_bfloat162*>(p.q + 1ll * r * p.ldq + p.q_off + h * p.ID + 2 * i));
@@ -137,6 +156,11 @@ __global__ void __launch_bounds__(256) index_prepare_kernel(IndexScoreParams p, 
         a = ra;
         b = rb;
       }
+      if (p.idx_row_bytes > 0) {
+        a = bf16_round(a);
+        b = bf16_round(b);
+        fp4_group_qdq(a, b, lanes);
+      }
       *reinterpret_cast<__nv_bfloat162*>(qr + (1ll * r * p.IH + h) * p.ID + 2 * i) = __floats2bfloat162_rn(a, b);
     }
     return;
@@ -148,7 +172,18 @@ __global__ void __launch_bounds__(256) index_prepare_kernel(IndexScoreParams p, 
     if (c >= n_keys) continue;
     const long long phys = slot < 0 ? -1 : pool_row(p.page_table, p.max_pages, p.page_rows, slot, c);
     uint4 w = make_uint4(0, 0, 0, 0);
-    if (phys >= 0) w = *reinterpret_cast<const uint4*>(p.idx_pool + phys * p.ID + v * 8);
+    if (phys >= 0 && p.idx_row_bytes > 0) {
+      // FP4 key row -> eight bf16 values (every product of an E2M1 level and a power of two is a bf16 value)
+      const uint8_t* row = reinterpret_cast<const uint8_t*>(p.idx_pool) + phys * p.idx_row_bytes;
+      __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = fp4_key_pair(row, p.ID, v * 8 + 2 * j);
+        o[j] = __floats2bfloat162_rn(f.x, f.y);
+      }
+    } else if (phys >= 0) {
+      w = *reinterpret_cast<const uint4*>(p.idx_pool + phys * p.ID + v * 8);
+    }
     *reinterpret_cast<uint4*>(kc + 1ll * c * p.ID + v * 8) = w;
   }
 }
@@ -1042,13 +1077,14 @@ extern "C" int ds41_index_score_cand(const void* q, long long ldq, int q_off, co
                                      const void* idx_pool, const int* page_table, int max_pages, int page_rows,
                                      const int* row_pos, const int* row_slot, const float* inv_freq_idx, int rows,
                                      int IH, int ID, int ratio, float* scores, int max_keys, const void* cand_mask,
-                                     int cand_words, int cand_block, void* stream) {
+                                     int cand_words, int cand_block, int idx_row_bytes, void* stream) {
   if (rows <= 0 || IH > 32 || ID > 128 || (ID & 3)) return cudaErrorInvalidValue;
+  if (idx_row_bytes != 0 && (idx_row_bytes < ID / 2 + ID / 32 || (ID & 31))) return cudaErrorInvalidValue;
   if (cand_mask != nullptr && (cand_words <= 0 || cand_block <= 0)) return cudaErrorInvalidValue;
   IndexScoreParams p{static_cast<const __nv_bfloat16*>(q), ldq, q_off, w, w_stride, w_off,
                      static_cast<const __nv_bfloat16*>(idx_pool), page_table, max_pages, page_rows, row_pos,
                      row_slot, inv_freq_idx, rows, IH, ID, ratio, scores, max_keys,
-                     static_cast<const uint32_t*>(cand_mask), cand_words, cand_block};
+                     static_cast<const uint32_t*>(cand_mask), cand_words, cand_block, idx_row_bytes};
   int bx = (max_keys + 7) / 8;
   if (bx > 256) bx = 256;
   return launch_pdl(index_score_kernel, dim3(bx, rows), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
@@ -1059,17 +1095,18 @@ extern "C" int ds41_index_score(const void* q, long long ldq, int q_off, const f
                                 const int* row_pos, const int* row_slot, const float* inv_freq_idx, int rows, int IH,
                                 int ID, int ratio, float* scores, int max_keys, void* stream) {
   return ds41_index_score_cand(q, ldq, q_off, w, w_stride, w_off, idx_pool, page_table, max_pages, page_rows, row_pos,
-                               row_slot, inv_freq_idx, rows, IH, ID, ratio, scores, max_keys, nullptr, 0, 0, stream);
+                               row_slot, inv_freq_idx, rows, IH, ID, ratio, scores, max_keys, nullptr, 0, 0, 0, stream);
 }
 
 extern "C" int ds41_index_prepare(const void* q, long long ldq, int q_off, const void* idx_pool, const int* page_table,
                                   int max_pages, int page_rows, const int* row_pos, const int* row_slot,
                                   const float* inv_freq_idx, int rows, int IH, int ID, int ratio, int n_keys,
-                                  int max_keys, void* qr, void* kc, int* n_vis, void* stream) {
+                                  int max_keys, void* qr, void* kc, int* n_vis, int idx_row_bytes, void* stream) {
   if (rows <= 0 || n_keys <= 0 || IH <= 0 || ID <= 0 || (ID & 7)) return cudaErrorInvalidValue;
+  if (idx_row_bytes != 0 && (idx_row_bytes < ID / 2 + ID / 32 || (ID & 31))) return cudaErrorInvalidValue;
   IndexScoreParams p{static_cast<const __nv_bfloat16*>(q), ldq, q_off, nullptr, 0, 0,
                      static_cast<const __nv_bfloat16*>(idx_pool), page_table, max_pages, page_rows, row_pos,
-                     row_slot, inv_freq_idx, rows, IH, ID, ratio, nullptr, max_keys, nullptr, 0, 0};
+                     row_slot, inv_freq_idx, rows, IH, ID, ratio, nullptr, max_keys, nullptr, 0, 0, idx_row_bytes};
   return launch_pdl(index_prepare_kernel, dim3(rows + (n_keys + 7) / 8), dim3(256), 0,
                     static_cast<cudaStream_t>(stream), p, n_keys, static_cast<__nv_bfloat16*>(qr),
                     static_cast<__nv_bfloat16*>(kc), n_vis);

@@ -467,10 +467,19 @@ class KVCache:
     (sizing rule: native counterpart rust/crates/ds41rt-daemon/src/v41_native_serve/memory.rs:9-13,137)."""
 
     def __init__(self, cfg: ModelConfig, n_layers: int, slots: int, max_ctx: int, device, page_tokens: int = 64,
-                 n_pages: Optional[int] = None, spec_slack: int = 16, kv_dtype: str = "bf16"):
+                 n_pages: Optional[int] = None, spec_slack: int = 16, kv_dtype: str = "bf16",
+                 index_dtype: Optional[str] = None):
         self.cfg, self.slots, self.max_ctx, self.page_tokens = cfg, slots, max_ctx, page_tokens
         assert kv_dtype in ("bf16", "fp8", "fp4")
         self.kv_dtype = kv_dtype
+        # index keys: "fp4" = E2M1 pairs + one UE8M0 scale per 32 values (68 bytes per key of 128 values instead of
+        # 256; the queries are then quantised the same way before the dot - the reference's FP4 x FP4 contract,
+        # native/cuda/kernels/v41_index_scores.cu:36-103, v41_compressor.cu:25-57).  Default: FP4 with the FP4 cache.
+        if index_dtype is None:
+            index_dtype = "fp4" if kv_dtype == "fp4" and cfg.index_dim % 32 == 0 else "bf16"
+        assert index_dtype in ("bf16", "fp4") and (index_dtype == "bf16" or cfg.index_dim % 32 == 0)
+        self.index_dtype = index_dtype
+        self.idx_row_bytes = (cfg.index_dim // 2 + cfg.index_dim // 32 + 3) // 4 * 4 if index_dtype == "fp4" else 0
         # FP8 rows: D e4m3 values + D/32 UE8M0 scales (per 32 elements), padded to 16 bytes; 0 = bf16 rows
         self.row_bytes = 0 if kv_dtype == "bf16" else (cfg.head_dim + cfg.head_dim // 32 + 15) // 16 * 16
         # "fp4": the window rings stay FP8, the compressed rows are FP4 (D/2 e2m1 bytes + D/16 E4M3 scales, the
@@ -494,7 +503,9 @@ class KVCache:
             self.page_rows[src] = pr
             comp_shape = (self.comp_row_bytes,) if self.comp_row_bytes else kv_shape
             self.comp[src] = torch.zeros(self.n_pages * pr, *comp_shape, dtype=kv_dt, device=device)
-            self.idx[src] = torch.zeros(self.n_pages * pr, cfg.index_dim, dtype=BF16, device=device)
+            self.idx[src] = (torch.zeros(self.n_pages * pr, self.idx_row_bytes, dtype=torch.uint8, device=device)
+                             if self.idx_row_bytes else
+                             torch.zeros(self.n_pages * pr, cfg.index_dim, dtype=BF16, device=device))
             if ratio == 2:
                 self.pending[src] = torch.zeros(slots, 4, 2 * D, dtype=F32, device=device)
         self.page_table_host = torch.full((slots, self.max_pages), -1, dtype=I32)
@@ -633,7 +644,7 @@ class DS41Engine:
     def __init__(self, cfg: ModelConfig, weights: EngineWeights, fabric: Optional[Fabric] = None, *,
                  max_rows: int = 8, slots: int = 1, max_ctx: int = 4096, page_tokens: int = 64,
                  n_pages: Optional[int] = None, row_hi: bool = False, moe_rows: int = 32, kv_dtype: str = "bf16",
-                 long_pass: str = "auto"):
+                 long_pass: str = "auto", index_dtype: Optional[str] = None):
         """long_pass: how passes longer than `moe_rows` rows run on several ranks.  "sp" (sequence parallel): every rank
         owns rows/world rows of the residual streams; hyper-connections, q_b, indexer, attention over all heads, wo_a /
         wo_b, router and shared expert run on the own rows against unsharded weights, the normalised rows are
@@ -654,7 +665,7 @@ class DS41Engine:
         # the window ring holds one pass of new rows beyond the window: a row still needs the key at pos - window + 1
         # after the last row of its pass has been written
         self.cache = KVCache(cfg, self.n_layers, slots, max_ctx, dev, page_tokens, n_pages, spec_slack=max(16, R),
-                             kv_dtype=kv_dtype)
+                             kv_dtype=kv_dtype, index_dtype=index_dtype)
         self.HL, self.GL, self.I_sh, self.V_local = weights.HL, weights.GL, weights.I_sh, weights.V_local
         live = [lw for lw in weights.layers if lw is not None]      # a pipeline stage holds a slice of the stack
         self._lw_any = live[0] if live else None
@@ -1025,7 +1036,8 @@ class DS41Engine:
                 lib.ptr(lw.comp_norm), lib.ptr(lw.wk_idx), lib.ptr(lw.k_norm), lib.ptr(inv), lib.ptr(self.inv_idx),
                 lib.ptr(self.cache.page_table), self.cache.max_pages, self.cache.page_rows[l],
                 lib.ptr(self.cache.comp[l]), lib.ptr(self.cache.idx[l]), C.c_float(cfg.norm_eps),
-                -self.cache.comp_row_bytes if self.cache.comp_row_bytes else self.cache.row_bytes, st())
+                -self.cache.comp_row_bytes if self.cache.comp_row_bytes else self.cache.row_bytes,
+                self.cache.idx_row_bytes, st())
 
     def forward_rows(self, rows: int, *, embed: bool = True, head: bool = True, first_layer: int = 0,
                      last_layer: Optional[int] = None, sources: bool = True, pending=None,
@@ -1088,7 +1100,8 @@ class DS41Engine:
                               self.HL * D, lib.ptr(self.cache.idx[src]), lib.ptr(self.cache.page_table),
                               self.cache.max_pages, self.cache.page_rows[src], lib.ptr(self.row_pos),
                               lib.ptr(self.row_slot), lib.ptr(self.inv_idx), R, cfg.index_heads, cfg.index_dim, ratio,
-                              n_keys, self.max_keys, lib.ptr(self.idx_q), lib.ptr(self.idx_k), lib.ptr(self.idx_vis), st())
+                              n_keys, self.max_keys, lib.ptr(self.idx_q), lib.ptr(self.idx_k), lib.ptr(self.idx_vis),
+                              self.cache.idx_row_bytes, st())
                     w_off = lw.extra_cols - cfg.index_heads
                     self._run("index_score_gemm", G.gemm_raw, self.idx_q, self.idx_k, self.scores, R * cfg.index_heads,
                               n_keys, cfg.index_dim, lda=cfg.index_dim, ldb=cfg.index_dim, ldo=self.max_keys, out_mode=8,
@@ -1100,7 +1113,7 @@ class DS41Engine:
                         lw.extra_cols - cfg.index_heads, lib.ptr(self.cache.idx[src]), lib.ptr(self.cache.page_table),
                         self.cache.max_pages, self.cache.page_rows[src], lib.ptr(self.row_pos), lib.ptr(self.row_slot),
                         lib.ptr(self.inv_idx), R, cfg.index_heads, cfg.index_dim, ratio, lib.ptr(self.scores),
-                        self.max_keys, *cand, st())
+                        self.max_keys, *cand, self.cache.idx_row_bytes, st())
                 if self.cand_on and l == cfg.candidate_layer:
                     self._run("candidate_select", k.ds41_candidate_select, lib.ptr(self.scores), self.max_keys,
                               lib.ptr(self.row_pos), lib.ptr(self.row_slot), ratio, cfg.candidate_block,
@@ -1353,7 +1366,8 @@ class DS41Engine:
                       lib.ptr(inv), lib.ptr(self.inv_idx), lib.ptr(self.cache.page_table), self.cache.max_pages,
                       self.cache.page_rows[l], lib.ptr(self.cache.comp[l]), lib.ptr(self.cache.idx[l]),
                       C.c_float(cfg.norm_eps),
-                      -self.cache.comp_row_bytes if self.cache.comp_row_bytes else self.cache.row_bytes, lib.stream())
+                      -self.cache.comp_row_bytes if self.cache.comp_row_bytes else self.cache.row_bytes,
+                      self.cache.idx_row_bytes, lib.stream())
 
     def _forward_rows_sp(self, R, *, embed, head, first_layer, last_layer, sources, head_row):
         cfg, k, st = self.cfg, self.k, lib.stream
@@ -1410,7 +1424,7 @@ class DS41Engine:
                               lib.ptr(self.cache.idx[src]), lib.ptr(self.cache.page_table), self.cache.max_pages,
                               self.cache.page_rows[src], lib.ptr(pos), lib.ptr(slot), lib.ptr(self.inv_idx), Rl,
                               cfg.index_heads, cfg.index_dim, ratio, n_keys, self.max_keys, lib.ptr(self.idx_q),
-                              lib.ptr(self.idx_k), lib.ptr(self.idx_vis), st())
+                              lib.ptr(self.idx_k), lib.ptr(self.idx_vis), self.cache.idx_row_bytes, st())
                     w_off = lw.extra_cols - cfg.index_heads
                     self._run("index_score_gemm", G.gemm_raw, self.idx_q, self.idx_k, scores, Rl * cfg.index_heads,
                               n_keys, cfg.index_dim, lda=cfg.index_dim, ldb=cfg.index_dim, ldo=self.max_keys,
@@ -1421,7 +1435,8 @@ class DS41Engine:
                               lib.ptr(extras_own), lw.extra_cols, lw.extra_cols - cfg.index_heads,
                               lib.ptr(self.cache.idx[src]), lib.ptr(self.cache.page_table), self.cache.max_pages,
                               self.cache.page_rows[src], lib.ptr(pos), lib.ptr(slot), lib.ptr(self.inv_idx), Rl,
-                              cfg.index_heads, cfg.index_dim, ratio, lib.ptr(scores), self.max_keys, *cand, st())
+                              cfg.index_heads, cfg.index_dim, ratio, lib.ptr(scores), self.max_keys, *cand,
+                              self.cache.idx_row_bytes, st())
                 if self.cand_on and l == cfg.candidate_layer:
                     self._run("candidate_select", k.ds41_candidate_select, lib.ptr(scores), self.max_keys, lib.ptr(pos),
                               lib.ptr(slot), ratio, cfg.candidate_block, cfg.candidate_topk_blocks,

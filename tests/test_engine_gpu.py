@@ -420,6 +420,16 @@ def test_fp4_compressed_rows_and_logits():
     packed, bs = Q.quant_kv_fp4_e4m3_16(ref)
     assert torch.equal(got[:, :D // 2], packed.view(torch.uint8).reshape(n, D // 2))
     assert torch.equal(got[:, D // 2:D // 2 + D // 16], bs.view(torch.uint8).reshape(n, D // 16))
+    # the index keys of that layer are FP4 rows too (E2M1 pairs + one UE8M0 scale per 32 values): the exact image of the
+    # bf16 engine's keys
+    ID = cfg.index_dim
+    c4 = engines["fp4"].cache
+    assert c4.index_dtype == "fp4" and c4.idx_row_bytes >= ID // 2 + ID // 32 and engines["bf16"].cache.idx_row_bytes == 0
+    ikeys = engines["bf16"].cache.idx[src][rows].float().cpu()
+    p4, e4 = Q.quant_mxfp4(ikeys, 32)
+    got_i = c4.idx[src][rows4].cpu()
+    assert torch.equal(got_i[:, :ID // 2], p4.view(torch.uint8).reshape(n, ID // 2))
+    assert torch.equal(got_i[:, ID // 2:ID // 2 + ID // 32], e4.to(torch.uint8).reshape(n, ID // 32))
     a, b = logits["bf16"], logits["fp4"]
     scale = float(a.abs().max())
     drift = (a - b).abs().max(dim=1).values

@@ -344,7 +344,7 @@ def test_index_scores_on_tensor_cores_match_the_scalar_kernel():
     st = lib.new_status("cuda")
     lib.check(k.ds41_index_prepare(lib.ptr(q), C.c_longlong(ldq), 64, lib.ptr(pool), lib.ptr(page_table), max_pages,
                                    page_rows, lib.ptr(positions), lib.ptr(slots), lib.ptr(inv), rows, IH, ID, ratio,
-                                   n_keys, max_keys, lib.ptr(qr), lib.ptr(kc), lib.ptr(vis), lib.stream()), "prepare")
+                                   n_keys, max_keys, lib.ptr(qr), lib.ptr(kc), lib.ptr(vis), 0, lib.stream()), "prepare")
     G.gemm_raw(qr, kc, got, rows * IH, n_keys, ID, lda=ID, ldb=ID, ldo=max_keys, out_mode=8, bn=256,
                row_w=w[:, w_off:], row_w_ld=w_stride, col_limit=vis, status=st)
     torch.cuda.synchronize()
@@ -355,6 +355,78 @@ def test_index_scores_on_tensor_cores_match_the_scalar_kernel():
         a, b = got[r, :nv], ref[r, :nv]
         assert float((a - b).abs().max()) < 2e-3 * float(b.abs().max())
         assert torch.isinf(got[r, nv:n_keys]).all()
+
+
+def test_fp4_index_keys_and_queries_follow_the_quantisation_oracle():
+    """Index keys stored as FP4 rows (E2M1 pairs + UE8M0 per 32 values, 68 bytes for 128 values): the per-key kernel and
+    the tensor-core path both score the dequantised keys against queries quantised the same way; the per-key kernel
+    also rounds to bf16 where the reference does (dot, weighted relu, head sum)."""
+    from ds41rt_b200.config import RopeConfig, rope_inv_freq
+    from ds41rt_b200.models.reference import apply_rope
+    from ds41rt_b200.ops import gemm as G, lib, quant_ref as Q
+    k = lib.kernels()
+    torch.manual_seed(9)
+    rows, IH, ID, ratio, page_rows, max_pages, max_keys = 70, 32, 128, 2, 32, 40, 1280
+    pos0 = 2000
+    positions = torch.arange(pos0, pos0 + rows, dtype=torch.int32, device="cuda")
+    slots = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    ldq = IH * ID
+    q = torch.randn(rows, ldq, device="cuda").bfloat16()
+    w = torch.rand(rows, IH, device="cuda")
+    keys = (torch.randn(max_pages * page_rows, ID, device="cuda") * torch.exp(torch.randn(max_pages * page_rows, 1,
+                                                                                             device="cuda"))).bfloat16()
+    packed, e = Q.quant_mxfp4(keys.float().cpu(), 32)
+    row_bytes = 68
+    pool = torch.zeros(max_pages * page_rows, row_bytes, dtype=torch.uint8)
+    pool[:, :ID // 2] = packed.view(torch.uint8)
+    pool[:, ID // 2:ID // 2 + ID // 32] = e.to(torch.uint8)
+    pool = pool.cuda()
+    keys_dq = Q.dequant_mxfp4(packed, e, 32).cuda()
+    page_table = torch.randperm(max_pages, device="cuda").int().view(1, max_pages).contiguous()
+    inv = torch.tensor(rope_inv_freq(RopeConfig(), ID // 2), device="cuda")
+    got = torch.full((rows, max_keys), float("nan"), device="cuda")
+    lib.check(k.ds41_index_score_cand(lib.ptr(q), C.c_longlong(ldq), 0, lib.ptr(w), IH, 0, lib.ptr(pool),
+                                      lib.ptr(page_table), max_pages, page_rows, lib.ptr(positions), lib.ptr(slots),
+                                      lib.ptr(inv), rows, IH, ID, ratio, lib.ptr(got), max_keys, None, 0, 0, row_bytes,
+                                      lib.stream()), "score")
+    n_keys = (pos0 + rows) // ratio
+    qr = torch.zeros(rows * IH, ID, device="cuda", dtype=torch.bfloat16)
+    kc = torch.zeros(max_keys, ID, device="cuda", dtype=torch.bfloat16)
+    vis = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    gemm = torch.full((rows, max_keys), float("nan"), device="cuda")
+    st = lib.new_status("cuda")
+    lib.check(k.ds41_index_prepare(lib.ptr(q), C.c_longlong(ldq), 0, lib.ptr(pool), lib.ptr(page_table), max_pages,
+                                   page_rows, lib.ptr(positions), lib.ptr(slots), lib.ptr(inv), rows, IH, ID, ratio,
+                                   n_keys, max_keys, lib.ptr(qr), lib.ptr(kc), lib.ptr(vis), row_bytes, lib.stream()),
+              "prepare")
+    G.gemm_raw(qr, kc, gemm, rows * IH, n_keys, ID, lda=ID, ldb=ID, ldo=max_keys, out_mode=8, bn=256, row_w=w,
+               row_w_ld=IH, col_limit=vis, status=st)
+    torch.cuda.synchronize()
+    lib.raise_on_status(st, "index gemm")
+    # oracle: RoPE, bf16, FP4 round trip of the queries; keys as dequantised; logical key c lives in page_table[c / page_rows]
+    qh = q.float().view(rows, IH, ID).cpu()
+    qh = apply_rope(qh, positions.cpu().long(), inv.cpu(), ID // 2).bfloat16().float()
+    qh = Q.qdq_mxfp4(qh, 32).cuda()
+    logical = torch.arange(n_keys, device="cuda")
+    phys = page_table[0, logical // page_rows].long() * page_rows + logical % page_rows
+    kd = keys_dq[phys]
+    assert torch.equal(kc[:n_keys].float(), kd)                                  # gathered keys are the dequantised rows
+    # the queries are FP4 values (a fixed point of the round trip) and the round trip of the oracle's RoPE'd queries, up to
+    # the few elements where the kernel's and torch's sine differ by an ulp of bf16 before quantisation
+    qk = qr.float().view(rows, IH, ID)
+    assert torch.equal(Q.qdq_mxfp4(qk.cpu(), 32).cuda(), qk)
+    assert float((qk == qh).float().mean()) > 0.97 and float((qk - qh).abs().max()) <= 0.5 * float(qh.abs().max())
+    qh = qk
+    bf = lambda t: t.bfloat16().float()
+    dots = bf(torch.einsum("rhd,cd->rhc", qh, kd))
+    want = bf((bf(torch.relu(dots) * w[:, :, None])).sum(1))
+    for r in (0, 33, rows - 1):
+        nv = (pos0 + r + 1) // ratio
+        a, b = got[r, :nv], want[r, :nv]
+        assert float((a - b).abs().max()) <= 0.02 * float(b.abs().max())        # bf16 rounding points: one ulp apart at most
+        g = gemm[r, :nv]
+        assert float((g - b).abs().max()) < 0.02 * float(b.abs().max())
+        assert torch.isinf(gemm[r, nv:n_keys]).all()
 
 
 def test_nvfp4_activation_quantiser_matches_oracle():
