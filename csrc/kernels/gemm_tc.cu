@@ -313,8 +313,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (++stage == S) { stage = 0; phase ^= 1; }
       }
     }
-  } else if (warp == 1 && lane == 0) {
+  } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
+    // The whole warp walks the loop with uniform control flow; `leader` predicates the tensor-core instructions
+    // themselves.  Issued from inside a one-lane branch, every instruction's descriptors took a detour through the
+    // divergent path that cost more than a K = 32 FP8 instruction takes to execute (tensor pipe 30 % busy in the
+    // block-scaled expert GEMMs).
+    const bool leader = elect_one();
     int stage = 0;
     uint32_t phase = 0;
     int acc = 0;
@@ -328,11 +333,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int sp = static_cast<int>(r % p.k_splits);
       const int kb0 = sp * kb_per_split;
       const int kb1 = min(kb_total, kb0 + kb_per_split);
-      if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, p.status, 200)) { ok = false; break; }
+      ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1, p.status, 200);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * Cfg::kAccCols;
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait(&full[stage], phase, p.status, 201)) { ok = false; break; }
+        ok = mbar_wait(&full[stage], phase, p.status, 201);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
         const uint32_t sb = sa + Cfg::kABytes;
@@ -343,7 +352,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t sf_t = tmem_base + Cfg::kAccStages * Cfg::kAccCols + stage * Cfg::kSfCols;
 #pragma unroll
           for (int a = 0; a < Cfg::kAtomsA + Cfg::kAtomsB; ++a)
-            tmem_cp_32x128b_warpx4(sf_t + 4 * a, umma_desc_plain(ssf + 512 * a, 16, 128));
+            tmem_cp_32x128b_warpx4_if(leader, sf_t + 4 * a, umma_desc_plain(ssf + 512 * a, 16, 128));
           // B scale columns: rows of this n-tile start (nt*BN % 128)/32 columns into the atom
           const uint32_t n_base_u = table ? static_cast<uint32_t>(p.tile_row0[nt]) : static_cast<uint32_t>(nt) * BN;
           const uint32_t sfb_t = sf_t + 4 * Cfg::kAtomsA + (n_base_u & 127u) / 32u;
@@ -353,18 +362,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if constexpr (KIND == 2) {
               // one atom per stage; instruction k uses byte k of every 32-bit scale cell
               const uint32_t id = umma_idesc_bs(kBM, BN, p.a_fp4 ? 5u : 0u, 0, 1, k, k);   // e2m1 = 5, e4m3 = 0
-              umma_mxf8(d_tmem, adesc + 2 * k, bdesc + 2 * k, id, accum, sf_t, sfb_t);
+              umma_mxf8_if(leader, d_tmem, adesc + 2 * k, bdesc + 2 * k, id, accum, sf_t, sfb_t);
               if constexpr (DUAL) {
                 const uint64_t adesc2 = umma_desc_sw128(sa + Cfg::kATile);
-                umma_mxf8(d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, id, accum, sf_t + 4, sfb_t);
+                umma_mxf8_if(leader, d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, id, accum, sf_t + 4, sfb_t);
               }
             } else {
               // NVFP4: instruction k (64 K elements) uses atom k: four E4M3 scales per row fill one 32-bit cell
               const uint32_t id = umma_idesc_bs(kBM, BN, 1u, 1u, 0, 0, 0);                 // e2m1 x e2m1, UE4M3 scales
-              umma_nvf4(d_tmem, adesc + 2 * k, bdesc + 2 * k, id, accum, sf_t + 4 * k, sfb_t + 4 * k);
+              umma_nvf4_if(leader, d_tmem, adesc + 2 * k, bdesc + 2 * k, id, accum, sf_t + 4 * k, sfb_t + 4 * k);
               if constexpr (DUAL) {
                 const uint64_t adesc2 = umma_desc_sw128(sa + Cfg::kATile);
-                umma_nvf4(d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, id, accum, sf_t + 16 + 4 * k,
+                umma_nvf4_if(leader, d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, id, accum, sf_t + 16 + 4 * k,
                           sfb_t + 4 * k);
               }
             }
@@ -373,19 +382,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int k = 0; k < kTileKBytes / 32; ++k) {
             const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
-            if constexpr (KIND == 0) umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
-            else umma_f8(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
+            if constexpr (KIND == 0) umma_bf16_if(leader, d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
+            else umma_f8_if(leader, d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
             if constexpr (DUAL) {
               const uint64_t adesc2 = umma_desc_sw128(sa + Cfg::kATile);
-              if constexpr (KIND == 0) umma_bf16(d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, idesc, accum);
-              else umma_f8(d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, idesc, accum);
+              if constexpr (KIND == 0) umma_bf16_if(leader, d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, idesc, accum);
+              else umma_f8_if(leader, d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, idesc, accum);
             }
           }
         }
-        tc_commit(&empty[stage]);       // frees the smem stage when these MMAs retire
+        tc_commit_if(leader, &empty[stage]);       // frees the smem stage when these MMAs retire
         if (++stage == S) { stage = 0; phase ^= 1; }
       }
-      if (ok) tc_commit(&acc_full[acc]);
+      tc_commit_if(leader && ok, &acc_full[acc]);
       acc = (acc + 1 == Cfg::kAccStages) ? 0 : acc + 1;
       if (acc == 0) acc_phase ^= 1;
     }
