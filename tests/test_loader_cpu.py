@@ -212,3 +212,37 @@ def test_fp4_experts_import_byte_for_byte(tmp_path):
     export_official(cfg, w, nv, variant="nvfp4", shards=2)
     other = LazyOfficialWeights(Catalog(nv, cfg, "nvfp4", with_vision=False, with_engram=False))
     assert other.expert_stack_fp4("layers.1", 0, 2, torch.device("cpu")) is None     # another expert format
+
+
+def test_full_size_layer_loads_from_a_sparse_checkpoint(tmp_path):
+    """One layer of the release model at its real tensor shapes (384 experts of 4608 x 5120 + 5120 x 2304 FP4 values, FP8
+    dense projections, the 129280-row embedding and head), stored as a sparse file: the catalog validates all 2337
+    tensors and rank 0 of 8 streams its shard into engine tensors - expert payloads byte for byte - in seconds."""
+    import dataclasses
+    import time
+    from ds41rt_b200.loader.official import load_engine_weights
+    cfg = dataclasses.replace(ModelConfig.flash(1), dspark=None, engram=None)
+    want = expected_tensors(cfg, "mxfp4", False, False)
+    size = {"BF16": 2, "F32": 4, "F8_E4M3": 1, "F8_E8M0": 1, "I8": 1, "U8": 1}
+    hdr, cur = {}, 0
+    for name, (dt, shape) in want.items():
+        nb = size[dt]
+        for s in shape:
+            nb *= s
+        hdr[name] = {"dtype": dt, "shape": list(shape), "data_offsets": [cur, cur + nb]}
+        cur += nb
+    d = str(tmp_path)
+    fname = "model-00001-of-00001.safetensors"
+    _raw(os.path.join(d, fname), hdr, cur)                       # header + a hole of `cur` bytes
+    json.dump({"metadata": {}, "weight_map": {n: fname for n in want}},
+              open(os.path.join(d, "model.safetensors.index.json"), "w"))
+    assert cur > 9 * (1 << 30) and os.stat(os.path.join(d, fname)).st_blocks * 512 < (64 << 20)
+    t0 = time.time()
+    ew = load_engine_weights(d, cfg, 0, 8, torch.device("cpu"), variant="mxfp4", expert_dtype="mxfp4")
+    took = time.time() - t0
+    lw = ew.layers[0]
+    assert lw.w13.shape == (48, 4608, 2560) and lw.w13.dtype == torch.uint8          # 48 experts per rank, E2M1 pairs
+    assert lw.w2.shape == (48, 5120, 1152) and lw.w13_sf.shape == (48, 36, 40, 512)
+    assert ew.head.shape[0] == 129280 // 8
+    print(f"one full-size layer, rank 0 of 8: {took:.1f} s")
+    assert took < 120
