@@ -274,6 +274,18 @@ def reference_main(args) -> int:
         run, info = REF.topk_case()
         ms = _time(run, args.reps)
         out["topk"] = {"ms": ms, "gb_s_one_pass": info["bytes_min"] / ms / 1e6}
+    if want("sampler"):
+        # same logits, seeds and filters as this package's `sampler` case; both samplers implement the same host oracle,
+        # so their tokens can be compared
+        from ..runtime import core
+        run, info = REF.sampler_case()
+        ms = _time(run, args.reps)
+        tok, st = info["tokens"].cpu().tolist(), info["status"].cpu().tolist()
+        lg = info["logits"].cpu().numpy()
+        agree = sum(int(st[r] == 0 and tok[r] == core.sample_token(lg[r], None, 0.8, 50, 0.9, 0.0,
+                                                                    core.sample_uniform(r, 0))) for r in range(len(tok)))
+        out["sampler"] = {"ms": ms, "gb_s_one_pass": info["bytes_min"] / ms / 1e6, "kernels": "K1 + K2, K3 + K4, K5",
+                          "status_ok_rows": sum(int(x == 0) for x in st), "tokens_equal_to_host_oracle": f"{agree}/{len(tok)}"}
     for name, rows in (("router_decode", 5), ("router_wide", 2048)):
         if want(name) or want("router"):
             run, info = REF.router_case(rows)

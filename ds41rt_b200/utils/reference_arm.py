@@ -10,6 +10,8 @@ on the host and returns an error code before it launches anything):
   router      ds41rt_v41_router                          native/include/ds41rt_v41_router.h:6-14
   hc          ds41rt_v41_hc_post + _mixes + _pre         native/include/ds41rt_v41_hc.h:6-20
   index       ds41rt_v41_index_scores                    native/include/ds41rt_v41_index_scores.h:10-22
+  sampler     ds41rt_cuda_v41_target_sample_async + _topk_select_async + _nucleus_async (K1/K2, K3/K4, K5)
+                                                         native/cuda/kernels/v41_sampling_gpu.h:286-420
 
 The shapes are those of `kernel_case` (window 128 + 512 selected keys, 64 heads x 512, FP8 window rows and FP4
 compressed rows; 384 experts over a 5120-wide hidden row; 4 residual streams).  Each case returns a closure that
@@ -48,6 +50,9 @@ def library() -> Optional[C.CDLL]:
     except OSError as exc:
         _WHY = f"cannot load the reference kernel library: {exc}"
         return None
+    for name in ("ds41rt_cuda_v41_target_sample_async", "ds41rt_cuda_v41_topk_select_async",
+                 "ds41rt_cuda_v41_nucleus_async"):
+        getattr(_LIB, name).restype = C.c_int32
     for name in ("ds41rt_v41_sparse_attention", "ds41rt_v41_sparse_attention_split", "ds41rt_v41_index_top512",
                  "ds41rt_v41_router", "ds41rt_v41_hc_pre", "ds41rt_v41_hc_post", "ds41rt_v41_hc_mixes",
                  "ds41rt_v41_index_scores", "ds41rt_v41_sparse_attention_initialize", "ds41rt_v41_router_initialize"):
@@ -251,3 +256,48 @@ def index_case(queries: int = 256, candidates: int = 16384):
                                            C.c_uint64(candidates), _stream()), "index_scores")
     return run, {"flops": 2.0 * queries * 32 * candidates * 128, "queries": queries, "candidates": candidates,
                  "keep": (q, qs, weights, keys, ks, pages, lengths, meta, positions, out), "out": out}
+
+
+def sampler_case(rows: int = 8, vocab: int = 129280, top_k: int = 50, top_p: float = 0.9, temperature: float = 0.8):
+    """The reference's GPU target sampler for `rows` unconstrained rows: K1 (mask / finiteness / scaled maximum) + K2, then
+    K3 / K4 (exact top-k membership in rank order), then K5 (top-p nucleus and the (seed, position) draw).  Row r uses
+    seed r and position 0, as the `sampler` case of kernel_case does."""
+    import numpy as np
+    lib = library()
+    dev = torch.device("cuda")
+    logits = torch.randn(rows, vocab, device=dev, generator=torch.Generator(device=dev).manual_seed(3)) * 3
+    row_t = np.dtype([("seed", "<u8"), ("position", "<u8"), ("temperature", "<f4"), ("top_p", "<f4"), ("min_p", "<f4"),
+                      ("top_k", "<u4"), ("mask_row", "<u4"), ("flags", "<u4"), ("output_row", "<u4"), ("ln_min_p", "<f4"),
+                      ("reserved0", "<u4"), ("reserved1", "<u4"), ("reserved2", "<u8")])
+    assert row_t.itemsize == 64
+    host = np.zeros(rows, dtype=row_t)
+    host["seed"], host["position"] = np.arange(rows), 0
+    host["temperature"], host["top_p"], host["min_p"], host["top_k"] = temperature, top_p, 0.0, top_k
+    host["mask_row"], host["flags"], host["output_row"] = 0xFFFFFFFF, 0x4, np.arange(rows)     # unconstrained rows
+    host["ln_min_p"] = -np.inf
+    params = torch.from_numpy(host.view(np.uint8).reshape(rows, 64).copy()).to(dev)
+    u32 = lambda n: torch.zeros(n, dtype=torch.int32, device=dev)
+    f32 = lambda n: torch.zeros(n, dtype=torch.float32, device=dev)
+    out_idx, out_status, out_detail, retained, passes, nucleus = u32(rows), u32(rows), u32(rows), u32(rows), u32(rows), u32(rows)
+    out_scores, out_total = f32(rows), f32(rows)
+    scratch = torch.zeros(rows * 64, dtype=torch.uint8, device=dev)
+    cap = 256
+    assert top_k <= cap
+    rank_ids = u32(rows * cap)
+    rank_scratch = torch.zeros(rows * cap, dtype=torch.int64, device=dev)
+    z = C.c_size_t
+
+    def run():
+        s = _stream()
+        _check(lib.ds41rt_cuda_v41_target_sample_async(_p(logits), z(rows), z(vocab), z(vocab), _p(params), _p(None), z(0),
+                                                       _p(out_idx), _p(out_status), _p(out_detail), _p(out_scores),
+                                                       _p(out_total), _p(nucleus), _p(scratch), s), "target_sample")
+        _check(lib.ds41rt_cuda_v41_topk_select_async(_p(logits), z(rows), z(vocab), z(vocab), _p(params), _p(None), z(0),
+                                                     _p(rank_ids), _p(rank_scratch), z(cap), _p(retained), _p(passes),
+                                                     _p(scratch), s), "topk_select")
+        _check(lib.ds41rt_cuda_v41_nucleus_async(_p(logits), z(rows), z(vocab), z(vocab), _p(params), _p(None), z(0),
+                                                 _p(rank_ids), z(cap), _p(retained), _p(out_idx), _p(out_status),
+                                                 _p(out_total), _p(nucleus), _p(scratch), s), "nucleus")
+    return run, {"bytes_min": 4.0 * rows * vocab, "logits": logits, "tokens": out_idx, "status": out_status,
+                 "keep": (params, out_detail, retained, passes, nucleus, out_scores, out_total, scratch, rank_ids,
+                          rank_scratch)}
