@@ -15,6 +15,8 @@
 //                  streams, and accumulate this column slice's contribution to the NEXT mixes projection.
 //   hc_finish    : reduce the slice partials in fixed order, compute pre/post/comb, collapse with the
 //                  incoming pre and apply the RMSNorm weight -> normalised bf16 rows for the GEMMs.
+#include <atomic>
+
 #include "ds41_api.h"
 #include "ds41_launch.cuh"
 #include "ds41_ptx.cuh"
@@ -56,12 +58,23 @@ __global__ void __launch_bounds__(256)
 hc_post_mix_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out,   // same buffer in the engine: coherent loads
                    PartList parts, const float* __restrict__ post, const float* __restrict__ comb,
                    const float* __restrict__ fn, float* __restrict__ partial, int rows, int H,
-                   const uint32_t* const* __restrict__ wait_flags, const uint32_t* __restrict__ wait_epoch, int* status) {
-  __shared__ __align__(16) float xs[kHcRowsPerBlock][kHcMaxMult][kHcSlice];
+                   const uint32_t* const* __restrict__ wait_flags, const uint32_t* __restrict__ wait_epoch, int* status,
+                   int rows_per_block) {
+  // The block's slice of the mixing matrix (24 projections x 4 streams x 128 columns, 48 KB) stays in shared memory
+  // while the block walks `rows_per_block` rows in groups of eight: fetched per group it was four times the stream
+  // bytes the group itself moves, and the kernel ran at a sixth of the copy bandwidth.
+  extern __shared__ __align__(16) float hc_smem[];
+  float (*xs)[kHcMaxMult][kHcSlice] = reinterpret_cast<float (*)[kHcMaxMult][kHcSlice]>(hc_smem);
+  float* fs = hc_smem + kHcRowsPerBlock * kHcMaxMult * kHcSlice;      // [24][4 * 128]
   const int c0 = blockIdx.x * kHcSlice;
-  const int r0 = blockIdx.y * kHcRowsPerBlock;
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
+  for (int i = tid; i < kHcProj * kHcMaxMult * (kHcSlice / 4); i += blockDim.x) {     // weights: before the dependency wait
+    const int j = i / (kHcMaxMult * (kHcSlice / 4)), rem = i % (kHcMaxMult * (kHcSlice / 4));
+    const int d = rem / (kHcSlice / 4), c4 = (rem % (kHcSlice / 4)) * 4;
+    *reinterpret_cast<float4*>(fs + j * (kHcMaxMult * kHcSlice) + d * kHcSlice + c4) =
+        *reinterpret_cast<const float4*>(fn + 1ll * j * (kHcMaxMult * H) + 1ll * d * H + c0 + c4);
+  }
   pdl_launch_dependents();
   pdl_wait();
 
@@ -70,6 +83,9 @@ hc_post_mix_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, 
     if (tid < parts.n_ranks) flag_wait_ge(wait_flags[tid], *wait_epoch, status, 400 + tid);
     __syncthreads();
   }
+  const int r_begin = blockIdx.y * rows_per_block, r_end = min(rows, r_begin + rows_per_block);
+  for (int r0 = r_begin; r0 < r_end; r0 += kHcRowsPerBlock) {
+  if (r0 > r_begin) __syncthreads();                  // the previous group's rows have been read by every warp
   // ---- expand (or plain load) into shared memory, bf16-rounded like the stored streams.  One item = one row x four
   // adjacent columns: 8-byte stream loads and 16-byte plane loads, all issued before the first use.
   for (int idx = tid; idx < kHcRowsPerBlock * (kHcSlice / 4); idx += blockDim.x) {
@@ -157,10 +173,9 @@ hc_post_mix_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, 
 #pragma unroll 8
   for (int idx = lane; idx < kHcMaxMult * kHcSlice; idx += 32) {
     const int d = idx / kHcSlice, c = idx % kHcSlice;
-    const long long kcol = 1ll * d * H + c0 + c;
     float f[3];
 #pragma unroll
-    for (int j = 0; j < 3; ++j) f[j] = fn[1ll * (warp + 8 * j) * (kHcMaxMult * H) + kcol];
+    for (int j = 0; j < 3; ++j) f[j] = fs[(warp + 8 * j) * (kHcMaxMult * kHcSlice) + idx];
 #pragma unroll
     for (int rr = 0; rr < kHcRowsPerBlock; ++rr) {
       const float x = xs[rr][d][c];
@@ -182,6 +197,7 @@ hc_post_mix_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, 
       if (lane == 0 && r0 + rr < rows) partial[(1ll * blockIdx.x * rows + r0 + rr) * kHcPartialStride + kHcProj] = v;
     }
   }
+  }   // row groups of this block
 }
 
 // One block per row.  Produces next_pre/post/comb from the slice partials, then the collapsed,
@@ -354,10 +370,24 @@ extern "C" int ds41_hc_post_mix(const void* streams_in, void* streams_out, const
   parts.n_splits = n_splits;
   parts.split_stride = split_stride;
   for (int i = 0; i < n_ranks; ++i) parts.base[i] = part_bases[i];
-  dim3 grid(H / kHcSlice, (rows + kHcRowsPerBlock - 1) / kHcRowsPerBlock);
-  return launch_pdl(hc_post_mix_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream),
+  // rows per block: as many eight-row groups as still leave about two blocks per SM
+  const int slices = H / kHcSlice;
+  int rpb = rows * slices / (2 * 148) / kHcRowsPerBlock * kHcRowsPerBlock;
+  rpb = rpb < kHcRowsPerBlock ? kHcRowsPerBlock : (rpb > 64 ? 64 : rpb);
+  constexpr size_t kSmem = sizeof(float) * (kHcRowsPerBlock * kHcMaxMult * kHcSlice + kHcProj * kHcMaxMult * kHcSlice);
+  static std::atomic<bool> configured[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
+    cudaError_t e = cudaFuncSetAttribute(hc_post_mix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kSmem));
+    if (e != cudaSuccess) return e;
+    configured[dev].store(true, std::memory_order_release);
+  }
+  dim3 grid(slices, (rows + rpb - 1) / rpb);
+  return launch_pdl(hc_post_mix_kernel, grid, dim3(256), kSmem, static_cast<cudaStream_t>(stream),
                     static_cast<const __nv_bfloat16*>(streams_in), static_cast<__nv_bfloat16*>(streams_out), parts,
-                    post, comb, fn, partial, rows, H, wait_flags, wait_epoch, status);
+                    post, comb, fn, partial, rows, H, wait_flags, wait_epoch, status, rpb);
 }
 
 extern "C" int ds41_hc_finish(const float* partial, int n_slices, const float* scale, const float* base,
