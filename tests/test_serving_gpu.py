@@ -527,3 +527,24 @@ def test_partial_prefix_overlap_reuses_compressed_rows(server):
     print("agreement with the cold run:", sum(int(x == y) for x, y in zip(warm, cold)), "of", len(cold))
     again, u2 = run(b)                                   # now an exact hit on b's own prompt snapshot
     assert u2["prompt_cache_hit_tokens"] == len(b) and again == warm
+
+
+def test_http_campaign_runs_mixed_traffic_through_the_real_server():
+    """The campaign tool against an in-process server on the tiny model: greedy, sampled, schema-constrained and
+    follow-up requests from four clients all complete, schema answers are valid (or valid prefixes when cut by
+    max_tokens), and the follow-up turns hit the prefix banks."""
+    import argparse
+    from ds41rt_b200.utils import http_campaign as HC
+    args = argparse.Namespace(model="tiny", layers=0, expert_dtype="bf16", kv_dtype="bf16", max_context=1024,
+                              prefill_chunk=64, clients=4, no_drafter=False)
+    srv, backend, cfg = HC._local_server(args)
+    try:
+        out = HC.run_campaign("127.0.0.1", srv.port, 4, 12, 24)
+        assert out["completed"] == 12 and out["failed"] == 0 and out["rejected_429"] == 0
+        assert out["by_kind"]["schema"] >= 2 and out["by_kind"]["sampled"] >= 2
+        ok, total = map(int, out["schema_answers_valid_or_valid_prefix"].split("/"))
+        assert ok == total
+        assert out["completion_tokens"] > 0 and backend.healthy, backend.error
+    finally:
+        srv.stop()
+        backend.close()
