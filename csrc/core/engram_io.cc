@@ -7,14 +7,25 @@
 // owner uploads the slot when it reaches that layer.  Slots are a fixed pool: submit() refuses (-1) when none is free,
 // so the producer can never run ahead of the consumer by more than the pool.  A pending request can be cancelled
 // (speculative rows that were rejected); the thread checks the flag between records.
-// Capability reference: rust/crates/ds41rt-loader/src/mapped_rows.rs:15, engram_prefetch.rs:143, engram_gather.rs:126,
+//
+// Two measuring aids sit beside the pipeline.  ds41_engram_table_evict drops this one file's pages from the page cache
+// (unmap-level advice, then file-level advice; nothing system-wide is touched) and ds41_engram_table_resident reports the
+// fraction that is resident, so a cold-cache measurement can be set up and checked without privileges.
+// ds41_engram_io_bench times the delivery of the records of synthetic passes (tokens x rows_per_token uniformly hashed
+// ids, sorted and de-duplicated as the gather does) by four routes: page faults on the mapping, page advice followed by
+// the copy, one pread per record, and preads spread over threads.
+// Capability reference: scripts/native/bench-engram-io.cpp and scripts/native/drop-page-cache.c of the reference (the
+// reference's dropper writes the system-wide drop_caches control; this one is scoped to the table's file);
+// rust/crates/ds41rt-loader/src/mapped_rows.rs:15, engram_prefetch.rs:143, engram_gather.rs:126,
 // engram_pipeline.rs:69 of the reference.
 #include <fcntl.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <atomic>
+#include <chrono>
 #include <condition_variable>
 #include <cstdint>
 #include <cstdlib>
@@ -133,6 +144,108 @@ int ds41_engram_prefetch(void* table, const uint64_t* ids, int n) {
     if (madvise(t->map + start, std::min<uint64_t>(end, t->bytes) - start, MADV_WILLNEED) == 0) ++advised;
   }
   return advised;
+}
+
+// Drop the table's pages from the page cache.  0 = ok, -1 = bad handle, otherwise the errno-style code of the advice.
+int ds41_engram_table_evict(void* table) {
+  Table* t = static_cast<Table*>(table);
+  if (t == nullptr) return -1;
+  fsync(t->fd);                                                        // a freshly written file: dirty pages cannot be dropped
+  if (madvise(t->map, t->bytes, MADV_DONTNEED) != 0) return 1;        // page-table entries of this mapping
+  const int rc = posix_fadvise(t->fd, 0, 0, POSIX_FADV_DONTNEED);      // then the now unmapped cache pages
+  madvise(t->map, t->bytes, MADV_RANDOM);
+  return rc;
+}
+
+// Fraction of the table's pages that are in memory (-1 on error).
+double ds41_engram_table_resident(void* table) {
+  Table* t = static_cast<Table*>(table);
+  if (t == nullptr) return -1.0;
+  const size_t page = static_cast<size_t>(sysconf(_SC_PAGESIZE));
+  const size_t n = (t->bytes + page - 1) / page;
+  std::vector<unsigned char> vec(n);
+  if (mincore(t->map, t->bytes, vec.data()) != 0) return -1.0;
+  size_t in = 0;
+  for (unsigned char v : vec) in += v & 1;
+  return n ? static_cast<double>(in) / static_cast<double>(n) : 0.0;
+}
+
+// Time `iters` synthetic passes.  mode 0 = copy from the mapping (page faults on demand), 1 = page advice for every
+// record, then the copy, 2 = one pread per record, 3 = preads over `threads` threads.  `evict_each` drops the table
+// from the page cache before every pass (cold measurements).  out: {mean us, min us, max us, records per pass (mean),
+// checksum}.  0 = ok, -1 = bad arguments, -2 = read error.
+int ds41_engram_io_bench(void* table, int tokens, int rows_per_token, int mode, int threads, int iters, int evict_each,
+                         uint64_t seed, double* out5) {
+  Table* t = static_cast<Table*>(table);
+  if (t == nullptr || tokens <= 0 || tokens > 65536 || rows_per_token <= 0 || rows_per_token > 256 || mode < 0 ||
+      mode > 3 || iters <= 0 || threads <= 0 || threads > 64 || out5 == nullptr)
+    return -1;
+  const uint32_t rb = t->row_bytes;
+  const long page = sysconf(_SC_PAGESIZE);
+  std::vector<uint8_t> sink(static_cast<size_t>(tokens) * rows_per_token * rb);
+  uint64_t state = seed * 0x9E3779B97F4A7C15ull + 0xD1B54A32D192ED03ull;
+  auto next = [&state] {                                   // splitmix64
+    uint64_t z = (state += 0x9E3779B97F4A7C15ull);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+  };
+  double sum = 0, lo = 1e300, hi = 0, records = 0;
+  uint64_t checksum = 0;
+  std::atomic<int> failed{0};
+  for (int it = 0; it < iters; ++it) {
+    std::vector<uint64_t> ids(static_cast<size_t>(tokens) * rows_per_token);
+    for (auto& id : ids) id = next() % t->rows;
+    std::sort(ids.begin(), ids.end());
+    ids.erase(std::unique(ids.begin(), ids.end()), ids.end());
+    if (evict_each) ds41_engram_table_evict(t);
+    const auto t0 = std::chrono::steady_clock::now();
+    if (mode == 0 || mode == 1) {
+      if (mode == 1) {
+        for (uint64_t id : ids) {
+          const uint64_t off = id * rb, start = off / page * page;
+          const uint64_t end = std::min<uint64_t>((off + rb + page - 1) / page * page, t->bytes);
+          madvise(t->map + start, end - start, MADV_WILLNEED);
+        }
+      }
+      for (size_t i = 0; i < ids.size(); ++i) std::memcpy(sink.data() + i * rb, t->map + ids[i] * rb, rb);
+    } else {
+      auto read_range = [&](size_t a, size_t b) {
+        for (size_t i = a; i < b; ++i) {
+          size_t done = 0;
+          while (done < rb) {
+            const ssize_t n = pread(t->fd, sink.data() + i * rb + done, rb - done, ids[i] * rb + done);
+            if (n <= 0) { failed = 1; return; }
+            done += static_cast<size_t>(n);
+          }
+        }
+      };
+      if (mode == 2 || threads == 1) {
+        read_range(0, ids.size());
+      } else {
+        std::vector<std::thread> pool;
+        const size_t per = (ids.size() + threads - 1) / threads;
+        for (int w = 0; w < threads; ++w) {
+          const size_t a = std::min(ids.size(), per * w), b = std::min(ids.size(), a + per);
+          if (a < b) pool.emplace_back(read_range, a, b);
+        }
+        for (auto& th : pool) th.join();
+      }
+    }
+    const double us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
+    if (failed) return -2;
+    for (size_t i = 0; i < ids.size(); ++i) checksum += sink[i * rb] + sink[i * rb + rb - 1];
+    sum += us;
+    lo = std::min(lo, us);
+    hi = std::max(hi, us);
+    records += static_cast<double>(ids.size());
+  }
+  out5[0] = sum / iters;
+  out5[1] = lo;
+  out5[2] = hi;
+  out5[3] = records / iters;
+  out5[4] = static_cast<double>(checksum);
+  return 0;
 }
 
 void* ds41_engram_gather_create(void* table, int n_slots, int max_rows) {

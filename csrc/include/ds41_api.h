@@ -391,6 +391,16 @@ int ds41_pp_pull(const void* src, void* dst, long long nbytes, const void* flag,
 int ds41_engram_dequant(const void* rows_q, int row_bytes, int dim, void* out, int n_rows, void* stream);
 int ds41_engram_gate(const void* x, const void* kv, const void* q_w, const void* k_w, const uint8_t* text_mask,
                      void* out, int rows, int H, float eps, void* stream);
+// Rows of a table converted to NVFP4 (dim/2 bytes of E2M1 pairs + dim/16 E4M3 scales per record, one fp32 scale per
+// table) -> bf16((code * scale) * table_scale).
+int ds41_engram_dequant_nvfp4(const void* rows_q, int row_bytes, int dim, float table_scale, void* out, int n_rows,
+                              void* stream);
+
+// ---------------------------------------------------------------------------------------------------
+// Hidden-state rows as wire records (wire.cu): H E4M3 values + H/32 UE8M0 scales per row, `row_bytes` apart
+// (multiple of 8, >= H + H/32); bf16 side with leading dimension ld (multiple of 8).  Both pointers 16-byte aligned.
+int ds41_wire_encode(const void* x, long long ldx, void* out, long long row_bytes, int rows, int H, void* stream);
+int ds41_wire_decode(const void* in, long long row_bytes, void* y, long long ldy, int rows, int H, void* stream);
 
 // ---------------------------------------------------------------------------------------------------
 // Vision tower elementwise kernels (vision.cu); all tensors bf16 unless noted.

@@ -1,6 +1,8 @@
 // Engram memory on the GPU: row dequantisation and the gated residual update.
 //
 //  engram_dequant : hashed table rows as stored (256 e4m3 values + 8 UE8M0 scales, one per 32 values) -> bf16
+//  engram_dequant_nvfp4 : rows of a converted table (128 bytes of E2M1 pairs, even element in the low nibble, + 16
+//                   E4M3 scales, one per 16 values; one fp32 scale per table) -> bf16((code * scale) * table scale)
 //  engram_gate    : for every token row and residual stream s (4 streams):
 //                     dot  = sum_c x[s,c] * (q_w[s,c] * k_w[s,c]) * key[s,c]
 //                     dot *= rsqrt(mean x^2 + eps) * rsqrt(mean key^2 + eps) / sqrt(H)
@@ -38,6 +40,32 @@ engram_dequant_kernel(const uint8_t* __restrict__ rows_q, int row_bytes, int dim
     for (int q = 0; q < 4; ++q) {
       const float2 f = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(q2[q], __NV_E4M3)));
       o2[q] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+    }
+    *reinterpret_cast<uint4*>(out + 1ll * warp * dim + c) = o;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+engram_dequant_nvfp4_kernel(const uint8_t* __restrict__ rows_q, int row_bytes, int dim, float table_scale,
+                            __nv_bfloat16* __restrict__ out, int n_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  // one warp per row: 8 values (4 payload bytes, half a scale group) per lane per step
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= n_rows) return;
+  const uint8_t* src = rows_q + 1ll * warp * row_bytes;
+  for (int c = lane * 8; c < dim; c += 256) {
+    const uint32_t raw = *reinterpret_cast<const uint32_t*>(src + (c >> 1));
+    __nv_fp8_e4m3 s8;
+    s8.__x = src[(dim >> 1) + (c >> 4)];
+    const float sc = static_cast<float>(s8);
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const __nv_fp4x2_storage_t pair = static_cast<__nv_fp4x2_storage_t>((raw >> (8 * q)) & 0xffu);
+      const float2 f = __half22float2(__half2(__nv_cvt_fp4x2_to_halfraw2(pair, __NV_E2M1)));
+      o2[q] = __floats2bfloat162_rn(__fmul_rn(__fmul_rn(f.x, sc), table_scale), __fmul_rn(__fmul_rn(f.y, sc), table_scale));
     }
     *reinterpret_cast<uint4*>(out + 1ll * warp * dim + c) = o;
   }
@@ -131,6 +159,17 @@ extern "C" int ds41_engram_dequant(const void* rows_q, int row_bytes, int dim, v
   const int blocks = (n_rows + 7) / 8;
   return launch_pdl(engram_dequant_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
                     static_cast<const uint8_t*>(rows_q), row_bytes, dim, static_cast<__nv_bfloat16*>(out), n_rows);
+}
+
+extern "C" int ds41_engram_dequant_nvfp4(const void* rows_q, int row_bytes, int dim, float table_scale, void* out,
+                                         int n_rows, void* stream) {
+  if (rows_q == nullptr || out == nullptr || n_rows <= 0 || dim <= 0 || (dim & 31) ||
+      row_bytes < dim / 2 + dim / 16 || (row_bytes & 3) || !(table_scale > 0.0f) || !isfinite(table_scale))
+    return cudaErrorInvalidValue;
+  const int blocks = (n_rows + 7) / 8;
+  return launch_pdl(engram_dequant_nvfp4_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const uint8_t*>(rows_q), row_bytes, dim, table_scale,
+                    static_cast<__nv_bfloat16*>(out), n_rows);
 }
 
 extern "C" int ds41_engram_gate(const void* x, const void* kv, const void* q_w, const void* k_w,

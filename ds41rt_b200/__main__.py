@@ -180,35 +180,68 @@ def _attach_engram(args, cfg, eng, dev):
     import torch
     from .models.engram import EngramLayer, init_engram_weights
     layers = [l for l in cfg.engram.layers if l < eng.n_layers]
+    fmt = args.engram_format
     for i, l in enumerate(layers):
+        scale = _engram_table_meta(args, i)["global_scale"]
         if args.checkpoint:
             from .loader.official import load_engram_layer
-            mod = load_engram_layer(args.checkpoint, cfg, l, dev)
+            mod = load_engram_layer(args.checkpoint, cfg, l, dev, table_format=fmt, table_scale=scale)
         else:
             wkv, q_w, k_w = init_engram_weights(cfg.hidden, seed=args.seed + 31 * i, std=0.002)
             bf = lambda t: t.to(device=dev, dtype=torch.bfloat16)
-            mod = EngramLayer(bf(wkv), bf(q_w), bf(k_w), cfg.hidden)
+            mod = EngramLayer(bf(wkv), bf(q_w), bf(k_w), cfg.hidden, table_format=fmt, table_scale=scale)
         eng.attach_engram(l, mod)
     return layers
+
+
+_random_tables: dict = {}
+
+
+def _random_engram_table(args, i: int) -> dict:
+    """A small random table for a random-init model, written once per process (and converted when the format asks for
+    it): {"path", "row_bytes", "global_scale"}.  Every rank derives the same scale from the same seed."""
+    key = (args.seed, i, args.engram_random_rows, args.engram_format)
+    if key not in _random_tables:
+        import tempfile
+        from .models.engram import random_table_rows
+        path = os.path.join(tempfile.mkdtemp(prefix="ds41-engram-"), f"table{i}.bin")
+        random_table_rows(args.engram_random_rows, seed=args.seed + i).numpy().tofile(path)
+        meta = {"path": path, "row_bytes": 264, "global_scale": 1.0}
+        if args.engram_format == "nvfp4":
+            from .runtime.ple_convert import convert_table
+            done = convert_table(path, path + ".nvfp4", args.engram_random_rows)
+            meta = {"path": path + ".nvfp4", "row_bytes": done["row_bytes"], "global_scale": done["global_scale"]}
+        _random_tables[key] = meta
+    return _random_tables[key]
+
+
+def _engram_table_meta(args, i: int) -> dict:
+    """Record size and table scale of the i-th table: from the `.json` that runtime.ple_convert wrote beside a converted
+    table, the fixed 264-byte FP8 record otherwise."""
+    if not args.engram_table:
+        return _random_engram_table(args, i)
+    if args.engram_format != "nvfp4":
+        return {"path": args.engram_table[i], "row_bytes": 264, "global_scale": 1.0}
+    with open(args.engram_table[i] + ".json") as f:
+        meta = json.load(f)
+    if meta.get("format") != "nvfp4" or not meta.get("complete"):
+        raise SystemExit(f"{args.engram_table[i]}: not a finished NVFP4 conversion")
+    return {"path": args.engram_table[i], "row_bytes": meta["row_bytes"], "global_scale": meta["global_scale"]}
 
 
 def _engram_pipeline(args, cfg, eng, layers, tokenizer):
     """Rank 0: the tables and the gather threads behind the engine's Engram layers."""
     if not layers:
         return None
-    import tempfile
-    from .models.engram import random_table_rows
     from .runtime.engram import EngramPipeline, compressed_token_ids
     from .runtime.engram_io import EngramTable
     tables = []
     for i, l in enumerate(layers):
-        if args.engram_table:
-            n_rows = cfg.engram.num_embeddings[cfg.engram.layers.index(l)]
-            tables.append(EngramTable(args.engram_table[i], n_rows, 264))
-        else:                                        # a small random table, row ids folded into it
-            path = os.path.join(tempfile.mkdtemp(prefix="ds41-engram-"), f"layer{l}.bin")
-            random_table_rows(args.engram_random_rows, seed=args.seed + i).numpy().tofile(path)
-            tables.append(EngramTable(path, args.engram_random_rows, 264))
+        meta = _engram_table_meta(args, i)
+        # a checkpoint's table has the configured row count; a random table is small and row ids are folded into it
+        n_rows = (cfg.engram.num_embeddings[cfg.engram.layers.index(l)] if args.engram_table
+                  else args.engram_random_rows)
+        tables.append(EngramTable(meta["path"], n_rows, meta["row_bytes"]))
     return EngramPipeline(layers, tables, token_map=compressed_token_ids(tokenizer.token_bytes()),
                           pad_id=cfg.engram.pad_token_id, max_rows=eng.max_rows, fold=not args.engram_table)
 
@@ -355,6 +388,10 @@ def main(argv=None) -> int:
     ps.add_argument("--engram-table", action="append", default=[],
                     help="flat Engram table file (loader.official.export_engram_table), once per Engram layer in layer "
                          "order; enables the Engram memory layers")
+    ps.add_argument("--engram-format", default="fp8", choices=["fp8", "nvfp4"],
+                    help="record format of the --engram-table files: fp8 (264-byte records as exported) or nvfp4 "
+                         "(144-byte records written by `python -m ds41rt_b200.runtime.ple_convert`, with the table "
+                         "scale read from FILE.json)")
     ps.add_argument("--engram-random-rows", type=int, default=0,
                     help="random-init models: enable the Engram layers over random tables of this many rows")
     ps.add_argument("--speculative", action="store_true",

@@ -179,7 +179,8 @@ def export_engram_table(cat: Catalog, layer: int, path: str, row_bytes: int = 26
     return n_rows
 
 
-def load_engram_layer(directory: str, cfg: ModelConfig, layer: int, device, variant: str = "mxfp4"):
+def load_engram_layer(directory: str, cfg: ModelConfig, layer: int, device, variant: str = "mxfp4",
+                      table_format: str = "fp8", table_scale: float = 1.0):
     """The projection and gate weights of one Engram layer of an official checkpoint -> models.engram.EngramLayer
     (the table itself stays on the host: export_engram_table + runtime.engram.EngramPipeline)."""
     from ..models.engram import EngramLayer
@@ -189,4 +190,5 @@ def load_engram_layer(directory: str, cfg: ModelConfig, layer: int, device, vari
     bf = lambda t: t.to(device=device, dtype=torch.bfloat16).contiguous()
     g = cfg.engram
     return EngramLayer(bf(w[p + ".wkv.weight"]), bf(w[p + ".q_weight"]), bf(w[p + ".k_weight"]), cfg.hidden,
-                       rows_per_token=g.n_heads * (g.max_ngram - 1), row_dim=g.head_dim)
+                       rows_per_token=g.n_heads * (g.max_ngram - 1), row_dim=g.head_dim, table_format=table_format,
+                       table_scale=table_scale)

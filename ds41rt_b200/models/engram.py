@@ -2,7 +2,7 @@
 
 Per token: the (2,3,4)-gram hashes of its history give `n_heads * 3` row ids into the layer's table (csrc/core/engram.cc
 computes them, `runtime/engram_io.py` gathers the rows on a host thread).  On the GPU the rows are dequantised
-(`ds41_engram_dequant`), multiplied by `engram.wkv` ([(4 + 1) * H, 24 * 256], tcgen05 GEMM) into four keys and one
+(`ds41_engram_dequant`; `ds41_engram_dequant_nvfp4` for a table converted by `runtime/ple_convert.py`), multiplied by `engram.wkv` ([(4 + 1) * H, 24 * 256], tcgen05 GEMM) into four keys and one
 value per token, and `ds41_engram_gate` adds gate * value to each of the four streams.
 
 `engram_reference` is the plain PyTorch fp32 statement of the same update used by the tests.
@@ -47,13 +47,20 @@ def engram_reference(x: torch.Tensor, rows_deq: torch.Tensor, wkv: torch.Tensor,
 
 class EngramLayer:
     def __init__(self, wkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor, hidden: int,
-                 rows_per_token: int = 24, row_dim: int = 256, row_bytes: int = 264, max_tokens: int = 64,
-                 eps: float = 1e-20):
-        """wkv [5 * hidden, rows_per_token * row_dim] bf16, q_weight / k_weight [4, hidden] bf16."""
+                 rows_per_token: int = 24, row_dim: int = 256, row_bytes: Optional[int] = None, max_tokens: int = 64,
+                 eps: float = 1e-20, table_format: str = "fp8", table_scale: float = 1.0):
+        """wkv [5 * hidden, rows_per_token * row_dim] bf16, q_weight / k_weight [4, hidden] bf16.
+        table_format "fp8": records of row_dim E4M3 values + row_dim/32 UE8M0 scales (264 bytes for 256);
+        "nvfp4": records of row_dim/2 E2M1 pair bytes + row_dim/16 E4M3 scales (144 bytes) with the table's fp32
+        scale `table_scale` (runtime/ple_convert.py writes both)."""
         dev = wkv.device
         assert wkv.shape == (5 * hidden, rows_per_token * row_dim) and wkv.dtype == torch.bfloat16
+        assert table_format in ("fp8", "nvfp4")
+        if row_bytes is None:
+            row_bytes = row_dim + row_dim // 32 if table_format == "fp8" else row_dim // 2 + row_dim // 16
         self.wkv, self.q_w, self.k_w = wkv.contiguous(), q_weight.contiguous(), k_weight.contiguous()
         self.H, self.rpt, self.dim, self.row_bytes = hidden, rows_per_token, row_dim, row_bytes
+        self.table_format, self.table_scale = table_format, float(table_scale)
         self.eps = eps
         self.max_tokens = 0
         self.status = lib.new_status(dev)
@@ -79,8 +86,13 @@ class EngramLayer:
         src = rows_q_host if isinstance(rows_q_host, torch.Tensor) else torch.from_numpy(rows_q_host)
         n = T * self.rpt
         self.staging[:n].copy_(src[:n], non_blocking=True)
-        lib.check(k.ds41_engram_dequant(lib.ptr(self.staging), self.row_bytes, self.dim, lib.ptr(self.rows), n, st()),
-                  "engram_dequant")
+        if self.table_format == "nvfp4":
+            lib.check(k.ds41_engram_dequant_nvfp4(lib.ptr(self.staging), self.row_bytes, self.dim,
+                                                  C.c_float(self.table_scale), lib.ptr(self.rows), n, st()),
+                      "engram_dequant_nvfp4")
+        else:
+            lib.check(k.ds41_engram_dequant(lib.ptr(self.staging), self.row_bytes, self.dim, lib.ptr(self.rows), n,
+                                            st()), "engram_dequant")
         G.matmul_nt(self.rows[:T], self.wkv, self.kv[:T], status=self.status)
         lib.check(k.ds41_engram_gate(lib.ptr(streams), lib.ptr(self.kv), lib.ptr(self.q_w), lib.ptr(self.k_w),
                                      lib.ptr(text_mask), lib.ptr(streams), T, self.H, C.c_float(self.eps), st()),

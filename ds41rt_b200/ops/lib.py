@@ -127,7 +127,7 @@ def dir_functions():
         "ds41_copy_ints", "ds41_rs_reduce", "ds41_ep_count", "ds41_ep_plan", "ds41_ep_dispatch", "ds41_ep_mark",
         "ds41_ep_wait", "ds41_ep_combine", "ds41_act_quant_mx_rows", "ds41_sample_rows", "ds41_engram_dequant", "ds41_engram_gate", "ds41_vis_rmsnorm", "ds41_vis_bias_act", "ds41_vis_silu_mul",
         "ds41_index_prepare", "ds41_candidate_select", "ds41_pp_signal", "ds41_pp_wait", "ds41_pp_pull", "ds41_attend_floor", "ds41_attend_kv", "ds41_index_score_cand", "ds41_topk_select_cand", "ds41_act_quant_nvfp4_rows", "ds41_vis_rope2d", "ds41_vis_softmax", "ds41_vis_merge", "ds41_vis_scatter",
-        "ds41_attend_tc", "ds41_attend_merge",
+        "ds41_attend_tc", "ds41_attend_merge", "ds41_engram_dequant_nvfp4", "ds41_wire_encode", "ds41_wire_decode",
     ]
 
 

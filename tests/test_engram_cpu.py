@@ -114,3 +114,24 @@ def test_pipeline_hashes_gathers_and_commits_only_accepted(table):
     assert pipe.stats()["gather"][0]["requests"] >= 3
     for g in pipe.gathers:
         g.close()
+
+
+def test_row_delivery_bench_runs_every_route_and_eviction_is_scoped_to_the_file(table, capsys):
+    t, rows, path = table
+    warm = t.bench(tokens=8, mode="mmap", iters=2)
+    assert warm["records_per_pass"] <= 8 * 24 and warm["mean_us"] > 0 and t.resident() > 0
+    for mode in ("willneed", "pread", "pread-mt"):
+        out = t.bench(tokens=8, mode=mode, iters=2, threads=3, cold=(mode == "pread"))
+        assert out["mode"] == mode and out["min_us"] <= out["mean_us"] <= out["max_us"]
+    t.evict()                                        # advice only: the file system may keep some pages
+    assert 0.0 <= t.resident() <= 1.0
+    g = EngramGather(t, slots=1, max_rows=8)         # the mapping still reads correctly afterwards
+    ticket = g.submit([1, 4998])
+    assert np.array_equal(g.wait(ticket), rows[[1, 4998]])
+    g.release(ticket)
+    g.close()
+    with pytest.raises(OSError):
+        t.bench(tokens=0)
+    from ds41rt_b200.runtime.engram_io import main
+    assert main([str(path), "--rows", "5000", "--tokens", "4", "--iters", "2", "--cache", "cold", "--mode", "pread"]) == 0
+    assert '"cache": "cold"' in capsys.readouterr().out
