@@ -246,3 +246,39 @@ def test_full_size_layer_loads_from_a_sparse_checkpoint(tmp_path):
     assert ew.head.shape[0] == 129280 // 8
     print(f"one full-size layer, rank 0 of 8: {took:.1f} s")
     assert took < 120
+
+
+def test_offline_conversion_to_the_nvfp4_variant_resumes_and_validates(tmp_path):
+    """mxfp4 checkpoint -> NVFP4 variant shard by shard: experts re-quantised by the reference recipe, everything else
+    byte for byte, an interrupted run continues from its receipts, and the result opens as a strict nvfp4 catalog."""
+    from ds41rt_b200.loader.convert import convert_checkpoint
+    from ds41rt_b200.ops import quant_ref as Q
+    cfg = ModelConfig.tiny()
+    w = init_weights(cfg, seed=2)
+    src, dst = str(tmp_path / "src"), str(tmp_path / "dst")
+    export_official(cfg, w, src, variant="mxfp4", shards=4)
+    part = convert_checkpoint(src, dst, cfg, with_vision=False, with_engram=False, stop_after_shards=2)
+    assert part["complete"] is False and part["written"] == 2
+    assert not os.path.exists(os.path.join(dst, "model.safetensors.index.json"))
+    full = convert_checkpoint(src, dst, cfg, with_vision=False, with_engram=False, link_unchanged=True)
+    assert full["complete"] and full["already_done"] == 2 and full["written"] == 2
+    again = convert_checkpoint(src, dst, cfg, with_vision=False, with_engram=False)
+    assert again["already_done"] == 4 and again["written"] == 0
+    a = Catalog(src, cfg, "mxfp4", with_vision=False, with_engram=False)
+    b = Catalog(dst, cfg, "nvfp4", with_vision=False, with_engram=False)
+    n_exp = sum(1 for n in a.expected if ".ffn.experts." in n and n.endswith(".weight"))
+    assert part["expert_matrices"] + full["expert_matrices"] == n_exp
+    name = "layers.1.ffn.experts.5.w1"
+    vals = Q.dequant_mxfp4(a.read(name + ".weight").view(torch.uint8), a.read(name + ".scale").view(torch.uint8), 32)
+    q, bs, gs = Q.quant_nvfp4(vals)
+    assert torch.equal(b.read(name + ".weight").view(torch.uint8), q.view(torch.uint8))
+    assert torch.equal(b.read(name + ".weight_scale").view(torch.uint8), bs.view(torch.uint8))
+    assert float(b.read(name + ".weight_scale_2")) == float(gs) and float(b.read(name + ".input_scale")) == 1.0
+    back = Q.dequant_nvfp4(b.read(name + ".weight").view(torch.uint8), b.read(name + ".weight_scale"),
+                           b.read(name + ".weight_scale_2").float())
+    assert float((back - vals).norm() / vals.norm()) < 0.1     # FP4 codes re-rounded onto a finer scale grid
+    for n in ("embed.weight", "layers.0.attn.wq_a.weight", "layers.0.attn.wq_a.scale", "norm.weight"):
+        assert torch.equal(a.read(n).view(torch.uint8), b.read(n).view(torch.uint8)), n
+    eager = load_official(b)
+    ref = w[name + ".weight"]
+    assert float((eager[name + ".weight"] - ref).abs().max()) < 0.3 * float(ref.abs().max())
