@@ -34,11 +34,14 @@ def drafter_config(cfg: ModelConfig) -> ModelConfig:
 
 class DSparkDrafter:
     def __init__(self, cfg: ModelConfig, target: DS41Engine, weights: Optional[Dict[str, torch.Tensor]] = None,
-                 width: Optional[int] = None, seed: int = 0, expert_dtype: str = "bf16"):
+                 width: Optional[int] = None, seed: int = 0, expert_dtype: str = "bf16", max_groups: int = 4):
+        """`max_groups`: how many sequences one draft pass can serve (each gets its own block of `width` rows, its own
+        slot's rings and its own Markov chain)."""
         assert cfg.dspark is not None
         d = cfg.dspark
         self.cfg, self.target, self.d = cfg, target, d
         self.width = width or d.block_size
+        self.max_groups = max(1, min(max_groups, target.max_rows // self.width, target.cache.slots))
         dev, rank, world = target.device, target.rank, target.world
         dcfg = drafter_config(cfg)
         H = cfg.hidden
@@ -79,9 +82,11 @@ class DSparkDrafter:
         self.block_val = z((self.n_blocks,), F32)
         self.block_idx = z((self.n_blocks,), I32)
         self.ticket = z((1,), I32)
-        self.drafts = z((self.width,), I32)          # drafts[j] = proposed token for position p + 1 + j
-        self.draft_val = z((self.width,), F32)
-        self.confidence = z((self.width,), F32)      # raw confidence-head output per draft row (sigmoid on the host)
+        # group g owns entries [g * width, (g + 1) * width): drafts[g * width + j] = proposed token for position p_g + 1 + j
+        self.drafts = z((self.max_groups * self.width,), I32)
+        self.draft_val = z((self.max_groups * self.width,), F32)
+        # raw confidence-head output per draft row (sigmoid on the host)
+        self.confidence = z((self.max_groups * self.width,), F32)
         self.launches = 0
 
     # ------------------------------------------------------------------ conditioning
@@ -109,6 +114,18 @@ class DSparkDrafter:
         toks = [anchor] + [self.d.noise_token_id] * (w - 1)
         self.eng.set_rows(toks, list(range(pos, pos + w)), [slot] * w, row_hi=[pos + w - 1] * w)
 
+    def set_draft_rows_groups(self, anchors: List[int], positions: List[int], slots: List[int]):
+        """One block of `width` rows per sequence, back to back: [anchor, noise, ...] at positions pos.. in its slot."""
+        w = self.width
+        assert 1 <= len(anchors) <= self.max_groups and len(set(slots)) == len(slots)
+        toks, pos, sl, hi = [], [], [], []
+        for a, p, s in zip(anchors, positions, slots):
+            toks += [a] + [self.d.noise_token_id] * (w - 1)
+            pos += list(range(p, p + w))
+            sl += [s] * w
+            hi += [p + w - 1] * w
+        self.eng.set_rows(toks, pos, sl, row_hi=hi)
+
     def set_sampling(self, temperature: float = 0.0, seed: int = 0, subsequence: int = 0, offset: int = 0):
         """Draft tokens are sampled (Gumbel-max with Philox numbers) when temperature > 0, greedy otherwise.  `offset`
         is the first Philox counter of this draft pass; row j uses the block starting at offset + j * ceil(vocab/4)
@@ -124,32 +141,39 @@ class DSparkDrafter:
         self._rng_keep = getattr(self, "_rng_keep", [])[-16:] + [r]
         return C.byref(r)
 
-    def draft(self):
-        """One draft pass over the rows prepared in the drafter engine's inputs -> self.drafts (device)."""
+    def draft(self, groups: int = 1):
+        """One draft pass over the rows prepared in the drafter engine's inputs (`groups` blocks of `width` rows) ->
+        self.drafts (device).  The Markov chain runs position by position inside every block."""
         e, k, t = self.eng, lib.kernels(), self.target
         w = self.width
-        e.forward_rows(w, head=False)
-        e.head_logits(w)
+        assert 1 <= groups <= self.max_groups
+        e.forward_rows(groups * w, head=False)
+        e.head_logits(groups * w)
         rank = self.d.markov_rank
         for j in range(w):
-            prev = e.in_tokens[0:1] if j == 0 else self.drafts[j - 1:j]
-            e._run("markov_step", k.ds41_markov_step, lib.ptr(e.logits[j]), lib.ptr(self.markov_head),
-                   lib.ptr(self.markov_embed), lib.ptr(prev), e.V_local, e.rank * e.V_local, rank, self.cfg.vocab,
-                   lib.ptr(self.block_val), lib.ptr(self.block_idx), self.n_blocks, lib.ptr(self.ticket),
-                   lib.ptr(e.best_val[j:j + 1]), lib.ptr(e.best_idx[j:j + 1]), self._draft_rng(j), lib.stream())
-            if e.world > 1:
-                e._signal()
-                e._run("draft_merge", k.ds41_argmax_merge, _offset_ptrs(e._val_ptrs, 4 * j, e.world),
-                       _offset_ptrs(e._idx_ptrs, 4 * j, e.world), e.world, 1, lib.ptr(self.drafts[j:j + 1]),
-                       lib.ptr(e.flag_ptrs), lib.ptr(e.epoch), lib.ptr(e.status), lib.stream())
-            else:
-                e._run("draft_take", k.ds41_copy_ints, lib.ptr(e.best_idx[j:j + 1]), lib.ptr(self.drafts[j:j + 1]), 1,
-                       lib.stream())
+            for g in range(groups):
+                r = g * w + j                                    # row of the pass, entry of drafts
+                prev = e.in_tokens[r:r + 1] if j == 0 else self.drafts[r - 1:r]
+                e._run("markov_step", k.ds41_markov_step, lib.ptr(e.logits[r]), lib.ptr(self.markov_head),
+                       lib.ptr(self.markov_embed), lib.ptr(prev), e.V_local, e.rank * e.V_local, rank, self.cfg.vocab,
+                       lib.ptr(self.block_val), lib.ptr(self.block_idx), self.n_blocks, lib.ptr(self.ticket),
+                       lib.ptr(e.best_val[r:r + 1]), lib.ptr(e.best_idx[r:r + 1]), self._draft_rng(r), lib.stream())
+                if e.world > 1:
+                    e._signal()
+                    e._run("draft_merge", k.ds41_argmax_merge, _offset_ptrs(e._val_ptrs, 4 * r, e.world),
+                           _offset_ptrs(e._idx_ptrs, 4 * r, e.world), e.world, 1, lib.ptr(self.drafts[r:r + 1]),
+                           lib.ptr(e.flag_ptrs), lib.ptr(e.epoch), lib.ptr(e.status), lib.stream())
+                else:
+                    e._run("draft_take", k.ds41_copy_ints, lib.ptr(e.best_idx[r:r + 1]), lib.ptr(self.drafts[r:r + 1]),
+                           1, lib.stream())
         if self.conf_w is not None:
             # collapsed (pre-norm) rows of the last stage and the Markov embedding each position was conditioned on
-            e._run("confidence", k.ds41_dspark_confidence, lib.ptr(e.xc), C.c_longlong(self.cfg.hidden),
-                   lib.ptr(self.markov_embed), rank, lib.ptr(e.in_tokens[0:1]), lib.ptr(self.drafts),
-                   lib.ptr(self.conf_w), lib.ptr(self.confidence), w, self.cfg.hidden, self.cfg.vocab, lib.stream())
+            for g in range(groups):
+                r = g * w
+                e._run("confidence", k.ds41_dspark_confidence, lib.ptr(e.xc[r:]), C.c_longlong(self.cfg.hidden),
+                       lib.ptr(self.markov_embed), rank, lib.ptr(e.in_tokens[r:r + 1]), lib.ptr(self.drafts[r:]),
+                       lib.ptr(self.conf_w), lib.ptr(self.confidence[r:]), w, self.cfg.hidden, self.cfg.vocab,
+                       lib.stream())
 
 
 def _offset_ptrs(ptrs, offset_bytes: int, n: int):

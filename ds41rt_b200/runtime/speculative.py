@@ -39,6 +39,9 @@ class SpecSession:
         self.h_conf = torch.zeros(self.width, dtype=torch.float32).pin_memory()
         self.last_confidence: List[float] = []      # sigmoid of the drafter's confidence head, one per draft row
         self.h_in = torch.zeros(1 + 2 * self.width, dtype=torch.int32).pin_memory()
+        g = drafter.max_groups
+        self.h_out_groups = torch.zeros(g * self.width, dtype=torch.int32).pin_memory()
+        self.h_conf_groups = torch.zeros(g * self.width, dtype=torch.float32).pin_memory()
         self._host_state = None
         self.h2d_bytes = self.d2h_bytes = 0
 
@@ -146,9 +149,40 @@ class SpecSession:
         self._publish_confidence()
         return self.h_out[: w - 1].tolist()
 
+    def draft_host_groups(self, slots: List[int], anchors: List[int], positions: List[int]):
+        """One draft pass for several sequences -> (proposals, confidences): per sequence the width - 1 proposed tokens
+        and the sigmoid of the confidence head per draft row ([] without a confidence head)."""
+        w, g = self.width, len(slots)
+        self.d.set_draft_rows_groups(anchors, positions, slots)
+        self.d.draft(g)
+        self.h_out_groups[: g * w].copy_(self.d.drafts[: g * w], non_blocking=True)
+        if self.d.conf_w is not None:
+            self.h_conf_groups[: g * w].copy_(self.d.confidence[: g * w], non_blocking=True)
+            self.d2h_bytes += 4 * g * w
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes += 4 * g * w
+        toks = self.h_out_groups[: g * w].tolist()
+        conf = torch.sigmoid(self.h_conf_groups[: g * w]).tolist() if self.d.conf_w is not None else []
+        return ([toks[i * w: i * w + w - 1] for i in range(g)],
+                [conf[i * w: (i + 1) * w] if conf else [] for i in range(g)])
+
+    def verify_host_groups(self, slots: List[int], inputs: List[List[int]], positions: List[int]) -> List[int]:
+        """One target pass over the verification rows of several sequences, back to back; returns the first row of
+        each sequence in the pass.  The drafter's rings of every slot are fed from the target's taps."""
+        toks, pos, sl, first = [], [], [], []
+        for s, inp, p in zip(slots, inputs, positions):
+            first.append(len(toks))
+            toks += inp
+            pos += list(range(p, p + len(inp)))
+            sl += [s] * len(inp)
+        self.t.set_rows(toks, pos, sl)
+        self.t.forward_rows(len(toks))
+        self.d.feed(len(toks))
+        return first
+
     def _read_confidence(self):
         if self.d.conf_w is not None:
-            self.h_conf.copy_(self.d.confidence, non_blocking=True)
+            self.h_conf.copy_(self.d.confidence[: self.width], non_blocking=True)
             self.d2h_bytes += 4 * self.width
 
     def _publish_confidence(self):

@@ -118,7 +118,7 @@ class _Active:
     emitted: int = 0
     lane: int = 0
     tokens: List[int] = field(default_factory=list)     # emitted token ids
-    spec: bool = False        # decoded by speculative rounds (drafter + verify) while it is the only active request
+    spec: bool = False        # the drafter's rings follow this request: it can take part in speculative rounds
 
 
 @dataclass
@@ -149,14 +149,16 @@ class NativeBackend(Backend):
     the engine is decoded by speculative rounds: greedy unconstrained requests by the all-device round, constrained or
     stochastic ones by a round whose verification rows are selected under per-row grammar masks (a fork of the matcher
     per draft row) or drawn with the request's own (seed, position) numbers and compared with the drafts
-    (sample-and-match); the verification-length policy decides per round whether drafting pays.
+    (sample-and-match); the verification-length policy decides per round whether drafting pays.  Up to `spec_lanes`
+    active requests share a speculative round: one draft pass proposes a block per request (own slot, rings and Markov
+    chain), one target pass verifies all blocks, and each request accepts under its own masks and draws.
     Reference behaviour: rust/crates/ds41rt-daemon/src/v41_native_serve/scheduler.rs:200-451, scheduler/independent.rs,
     constraints.rs:48-68, speculative.rs:121-163."""
     fingerprint = "ds41rt-b200-fp8"
 
     def __init__(self, engine, eos: int, concurrency: int = 4, queue_depth: int = 16, prefill_chunk: Optional[int] = None,
                  vision=None, drafter=None, engram=None, ced: bool = True, use_graphs: bool = True,
-                 prompt_snapshots: int = 20, turn_snapshots: int = 20, host_cache_bytes: int = 0):
+                 prompt_snapshots: int = 20, turn_snapshots: int = 20, host_cache_bytes: int = 0, spec_lanes: int = 4):
         self.e, self.eos = engine, eos
         # prompt passes use the encoder / decoder-replay split when the model has a boundary (config.ced_on)
         self.ced = ced
@@ -172,6 +174,10 @@ class NativeBackend(Backend):
             from ..runtime.speculative import SpecSession
             self.spec = SpecSession(engine, drafter)
             self.policy = K.DSparkPolicy(max_width=self.spec.width - 1)
+            # rounds shared by several requests have their own cost model (more rows per pass, one pass for all)
+            self.policy_lanes = K.DSparkPolicy(max_width=self.spec.width - 1)
+        # how many requests one speculative round can serve (each drafts and verifies its own block in the shared passes)
+        self.spec_lanes = max(1, min(spec_lanes, drafter.max_groups)) if drafter is not None else 0
         self.vision = vision                     # models.vision.VisionTower on the engine's device, or None
         self.supports_images = vision is not None
         self.concurrency = min(concurrency, engine.cache.slots, engine.max_rows)
@@ -202,7 +208,7 @@ class NativeBackend(Backend):
                        "prompt_cache_hit_tokens": 0, "snapshots": 0, "spec_rounds": 0, "spec_tokens": 0,
                        "ced_prefills": 0, "partial_prefix_hits": 0, "snapshots_evicted_for_pages": 0,
                        "graph_rounds": 0, "prefill_passes": 0, "spec_masked_rounds": 0, "policy_plain_rounds": 0,
-                       "cancelled_in_prefill": 0, "snapshots_demoted": 0, "host_tier_hits": 0}
+                       "cancelled_in_prefill": 0, "snapshots_demoted": 0, "host_tier_hits": 0, "spec_lane_rounds": 0}
         self._rid = 0
         self._stop = threading.Event()
         self._ready = threading.Event()
@@ -233,6 +239,7 @@ class NativeBackend(Backend):
                                    "gpu_sampled_rows": self.totals["gpu_sampled_rows"]}}
         if self.policy is not None:
             out["dspark_policy"] = self.policy.stats()
+            out["dspark_policy_shared_rounds"] = self.policy_lanes.stats()
         if self.host_tier is not None:
             out["host_cache"] = self.host_tier.stats()
         return out
@@ -417,7 +424,8 @@ class NativeBackend(Backend):
         self.totals["requests"] += 1
         self.totals["prompt_tokens"] += len(req.prompt_ids)
         self.totals["prompt_cache_hit_tokens"] += reused
-        solo = self.spec is not None and not self.active and not req.images and req.max_tokens > 1
+        # the drafter's rings are fed from this prompt's passes (and from every later pass of the request)
+        solo = self.spec is not None and not req.images and req.max_tokens > 1
         self.prefilling = self._plan_prefill(slot, gen, req, first_new, snap_logits, solo, replay_from)
         self.prefilling.reused = reused
         return False
@@ -611,9 +619,8 @@ class NativeBackend(Backend):
             if not req.images:                                # placeholders look alike: image prompts are not banked
                 self._store_snapshot(slot, req.prompt_ids, pf.logits, K.PrefixBanks.PROMPT)
         first = self._select([req], [0], logits=pf.logits.view(1, -1))[0]
-        solo = pf.solo and not self.active
-        a = _Active(req, slot, pf.gen, pos=len(req.prompt_ids), last=first, spec=solo)
-        if solo and req.sampling.greedy and req.constraint is None:
+        a = _Active(req, slot, pf.gen, pos=len(req.prompt_ids), last=first, spec=pf.solo)
+        if pf.solo and not self.active and req.sampling.greedy and req.constraint is None:
             self.spec.prime(slot, first, len(req.prompt_ids))
         a.lane = self.lanes.add(req.rid, req.max_tokens, len(req.prompt_ids))
         if self._emit(a, first):
@@ -756,6 +763,72 @@ class NativeBackend(Backend):
             self.engram.commit(ep, {a.slot: accepted + 1})               # the anchor and the accepted drafts
         return picked[: accepted + 1], len(drafts)
 
+    def _spec_round_lanes(self, acts: List[_Active]):
+        """One speculative round shared by several requests: one draft pass proposes a block per request, each proposal
+        is cut by the policy (given the drafter's confidence in it), by the request's grammar and by its token budget,
+        one target pass verifies all blocks, and every request keeps the drafts that equal the target's own selection
+        under its own sampling parameters and row masks, plus the bonus token."""
+        import torch
+        sp = self.spec
+        timed = self.e.device.type == "cuda"
+        if timed:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+        proposals, confs = sp.draft_host_groups([a.slot for a in acts], [a.last for a in acts], [a.pos for a in acts])
+        inputs, masks, reqs, positions, slots_rows, toks_rows = [], [], [], [], [], []
+        for a, drafts, conf in zip(acts, proposals, confs):
+            r = a.req
+            if conf:
+                drafts = drafts[: max(0, self.policy_lanes.choose(conf[0]))]
+            if r.constraint is not None:
+                drafts = r.constraint.truncate_proposal(drafts)
+            drafts = drafts[: max(0, min(len(drafts), r.max_tokens - a.emitted - 1))]
+            inp = [a.last] + drafts
+            inputs.append(inp)
+            row_masks = r.constraint.row_masks(inp) if r.constraint is not None else [None] * len(inp)
+            masks += row_masks
+            reqs += [r] * len(inp)
+            positions += [a.emitted + i for i in range(len(inp))]
+            slots_rows += [a.slot] * len(inp)
+            toks_rows += inp
+        ep = self._engram_pass(toks_rows, slots_rows)
+        first = sp.verify_host_groups([a.slot for a in acts], inputs, [a.pos for a in acts])
+        n_rows = len(toks_rows)
+        picked = self._select(reqs, list(range(n_rows)), positions=positions,
+                              masks=masks if any(m is not None for m in masks) else None)
+        accepted = []
+        for a, inp, f in zip(acts, inputs, first):
+            r, k = a.req, 0
+            while k < len(inp) - 1 and picked[f + k] == inp[k + 1] and picked[f + k] != self.eos \
+                    and picked[f + k] not in r.stop_ids:
+                k += 1
+            accepted.append(k)
+        if ep is not None:
+            self.engram.commit(ep, {a.slot: k + 1 for a, k in zip(acts, accepted)})
+        if timed:
+            ev1.record()
+            ev1.synchronize()
+            share = ev0.elapsed_time(ev1) * 1e3 / len(acts)
+            for inp, k, conf in zip(inputs, accepted, confs):
+                self.policy_lanes.observe(len(inp) - 1, k, share, confidence=conf[0] if conf else -1.0)
+        self.totals["rounds"] += 1
+        self.totals["spec_rounds"] += 1
+        self.totals["spec_lane_rounds"] += 1
+        self._spec_dirty = True                      # the all-device round of a lone request starts from fresh inputs
+        keep = []
+        for a, f, k in zip(acts, first, accepted):
+            alive = True
+            self.totals["spec_tokens"] += k + 1
+            for t in picked[f: f + k + 1]:
+                a.pos += 1
+                if not self._emit(a, t):
+                    alive = False
+                    break
+            if alive:
+                self.lanes.update(a.req.rid, a.req.max_tokens - a.emitted, a.pos)
+                keep.append(a)
+        self.active = keep
+
     # ------------------------------------------------------------------ decode rounds
     def _graph_for(self, rows: int):
         """Captured launch sequence of one `rows`-row decode pass (made on first use of a batch size)."""
@@ -783,6 +856,11 @@ class NativeBackend(Backend):
             if a.req.max_tokens - a.emitted > 1 and self.policy.choose() > 0:
                 return self._spec_round(a)
             self.totals["policy_plain_rounds"] += 1
+        elif 1 < len(acts) <= self.spec_lanes and all(a.spec for a in acts) \
+                and (len(acts) + 1) * self.spec.width <= e.max_rows:
+            if self.policy_lanes.choose() > 0:
+                return self._spec_round_lanes(acts)
+            self.totals["policy_plain_rounds"] += 1
         e.set_rows([a.last for a in acts], [a.pos for a in acts], [a.slot for a in acts])
         if self.use_graphs:
             self._graph_for(len(acts)).replay()
@@ -792,16 +870,14 @@ class NativeBackend(Backend):
             e.forward_rows(len(acts))
             if ep is not None:
                 self.engram.commit(ep)
-        for a in acts:
-            if a.spec and len(acts) == 1:
-                self.spec.d.feed(1)                 # the drafter's rings follow a plain step too
+        if self.spec is not None and any(a.spec for a in acts):
+            self.spec.d.feed(len(acts))             # the drafter's rings follow a plain step too
+            self._spec_dirty = self._spec_dirty or len(acts) > 1
         toks = self._select([a.req for a in acts], list(range(len(acts))))
         self.totals["rounds"] += 1
         keep = []
         for a, t in zip(acts, toks):
             a.pos += 1
-            if len(acts) > 1:
-                a.spec = False         # a request that shared a pass stays on plain decoding
             self.lanes.update(a.req.rid, a.req.max_tokens - a.emitted, a.pos)
             if self._emit(a, t):
                 keep.append(a)

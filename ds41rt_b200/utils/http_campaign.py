@@ -6,7 +6,7 @@
 Without --url the tool builds the engine (random-init weights of the named architecture, byte-level tokenizer), starts
 `serving.http.ApiServer` over `NativeBackend` in this process and talks to it over a real socket, so every request goes
 through admission, chat templating, tokenisation, the scheduler (prompt chunks interleaved with decode rounds, graph
-replays, speculative rounds when a request is alone), sampling and SSE framing.  Traffic mix per client, round robin:
+replays, speculative rounds for up to four active requests), sampling and SSE framing.  Traffic mix per client, round robin:
 greedy streaming, seeded sampling (temperature / top-p), a JSON-schema-constrained answer, and a follow-up turn that
 extends an earlier prompt (prefix reuse).  Reported: completed requests, aggregate completion tokens per second over
 the wall clock of the campaign, time to first streamed token (median / p95), and the server's own counters.

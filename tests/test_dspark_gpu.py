@@ -162,3 +162,36 @@ def test_confidence_head_projects_collapsed_rows_and_markov_embeddings():
     assert len(sess.last_confidence) == w and all(0.0 <= c <= 1.0 for c in sess.last_confidence)
     assert abs(sess.last_confidence[0] - float(torch.sigmoid(want[0]))) < 1e-3
     assert len(drafts) == w - 1
+
+
+def test_one_draft_pass_serves_two_sequences_like_two_single_passes():
+    """Blocks of two sequences drafted in one pass (own slot, own rings, own Markov chain each) give the logits, drafts
+    and confidences that each sequence gets from a pass of its own."""
+    from ds41rt_b200.runtime.speculative import SpecSession
+    cfg, ref, eng, drafter = _build(max_rows=16)
+    assert drafter.max_groups == 2
+    w = drafter.width
+    g = torch.Generator().manual_seed(17)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (40, 29)]
+    sess = SpecSession(eng, drafter, use_graphs=False)
+    anchors = [sess.start(s, p, 16) for s, p in enumerate(prompts)]
+    single = []
+    for s in (0, 1):
+        toks = sess.draft_host(s, anchors[s], len(prompts[s]))
+        single.append((toks, drafter.eng.logits[:w].float().clone(), drafter.confidence[:w].clone()))
+    both, conf = sess.draft_host_groups([0, 1], anchors, [len(p) for p in prompts])
+    eng.check_status()
+    drafter.eng.check_status()
+    for s in (0, 1):
+        logits = drafter.eng.logits[s * w:(s + 1) * w].float()
+        scale = float(single[s][1].abs().max())
+        assert float((logits - single[s][1]).abs().max()) < 2e-2 * scale
+        assert both[s] == single[s][0]
+        want_conf = torch.sigmoid(single[s][2]).cpu()
+        assert float((torch.tensor(conf[s]) - want_conf).abs().max()) < 2e-2
+    # the verification pass of both sequences in one target pass feeds both slots' rings
+    inputs = [[anchors[s]] + both[s] for s in (0, 1)]
+    first = sess.verify_host_groups([0, 1], inputs, [len(p) for p in prompts])
+    assert first == [0, w]
+    torch.cuda.synchronize()
+    eng.check_status()

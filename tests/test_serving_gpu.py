@@ -194,7 +194,7 @@ def test_image_parts_reach_the_vision_tower():
 
 def test_solo_request_is_served_by_speculative_rounds():
     """With a drafter, a lone greedy request runs draft + verify rounds and produces exactly the tokens plain decoding
-    produces; when a second request joins mid-way both continue on plain decoding and still match."""
+    produces; when a second request joins mid-way both still receive exactly those tokens."""
     import threading
     from ds41rt_b200.config import ModelConfig
     from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
@@ -306,6 +306,69 @@ def test_speculative_rounds_serve_constrained_and_sampled_requests_losslessly():
     assert pol["rounds"] > 0 and len(pol["accepted_histogram"]) == 16
     text = tk.decode(out["spec"][0][0])
     assert text.lstrip().startswith("{")
+
+
+def test_concurrent_requests_share_speculative_rounds_losslessly():
+    """Several active requests - greedy, grammar-constrained and seeded-stochastic - decode by shared draft + verify
+    rounds (one draft pass and one target pass for all of them) and each receives exactly the tokens that a backend
+    without a drafter gives it when it runs alone."""
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    from ds41rt_b200.models.dspark import DSparkDrafter
+    from ds41rt_b200.runtime.grammar import Grammar, TokenConstraint, Vocab
+    from ds41rt_b200.serving.engine import GenRequest, NativeBackend
+    from ds41rt_b200.serving.protocol import Sampling
+    from ds41rt_b200.serving.tokenizer import ByteTokenizer
+    cfg = ModelConfig.tiny()
+    dev = torch.device("cuda", 0)
+    w = EngineWeights.random(cfg, 0, 1, dev, seed=0)
+    tk = ByteTokenizer(vocab_size=cfg.vocab)
+    vocab = Vocab(tk.token_bytes())
+    schema = {"type": "object", "properties": {"name": {"type": "string"}, "n": {"type": "integer"}},
+              "required": ["name", "n"]}
+
+    def backend(with_drafter):
+        eng = DS41Engine(cfg, w, max_rows=32, slots=4, max_ctx=512)
+        drafter = DSparkDrafter(cfg, eng, weights=None, seed=0) if with_drafter else None
+        return NativeBackend(eng, eos=tk.eos, concurrency=4, drafter=drafter)
+
+    def collect(r):
+        toks = []
+        while True:
+            ev = r.events.get(timeout=120)
+            if ev.kind == "tokens":
+                toks += ev.tokens
+            elif ev.kind == "finish":
+                return toks
+            elif ev.kind == "error":
+                raise RuntimeError(ev.message)
+
+    g = torch.Generator().manual_seed(44)
+    prompts = [torch.randint(3, 250, (n,), generator=g).tolist() for n in (40, 33, 47)]
+
+    def requests():
+        con = TokenConstraint(vocab, Grammar.json_schema(schema), eos=tk.eos)
+        return [GenRequest(prompt_ids=prompts[0], max_tokens=60, sampling=Sampling(temperature=0.0)),
+                GenRequest(prompt_ids=prompts[1], max_tokens=56, sampling=Sampling(temperature=0.0), constraint=con),
+                GenRequest(prompt_ids=prompts[2], max_tokens=52, sampling=Sampling(temperature=0.7, top_p=0.9, seed=9))]
+
+    plain = backend(False)
+    want = []
+    for r in requests():
+        plain.submit(r)
+        want.append(collect(r))
+    plain.close()
+    spec = backend(True)
+    assert spec.spec_lanes >= 3
+    reqs = requests()
+    for r in reqs:
+        spec.submit(r)
+    got = [collect(r) for r in reqs]
+    tot = dict(spec.totals)
+    assert spec.healthy, spec.error
+    spec.close()
+    assert got == want
+    assert tot["spec_lane_rounds"] > 0 and tot["spec_tokens"] >= tot["spec_rounds"]
 
 
 def test_engram_pipeline_serves_requests(tmp_path):
