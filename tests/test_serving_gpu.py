@@ -463,10 +463,10 @@ def test_engram_backend_speculates_losslessly(tmp_path):
     wkv, q_w, k_w = init_engram_weights(cfg.hidden, seed=4, std=0.002)
     bf = lambda t: t.bfloat16().to(dev)
 
-    def backend(with_drafter):
-        eng = DS41Engine(cfg, w, max_rows=8, slots=2, max_ctx=512)
-        eng.attach_engram(1, EngramLayer(bf(wkv), bf(q_w), bf(k_w), cfg.hidden))
-        pipe = EngramPipeline([1], [EngramTable(path, n_rows, 264)], pad_id=2, max_rows=8, fold=True)
+    def backend(with_drafter, rows=8):
+        eng = DS41Engine(cfg, w, max_rows=rows, slots=2, max_ctx=512)
+        eng.attach_engram(1, EngramLayer(bf(wkv), bf(q_w), bf(k_w), cfg.hidden, max_tokens=rows))
+        pipe = EngramPipeline([1], [EngramTable(path, n_rows, 264)], pad_id=2, max_rows=rows, fold=True)
         drafter = DSparkDrafter(cfg, eng, weights=None, seed=0) if with_drafter else None
         return NativeBackend(eng, eos=1, concurrency=2, engram=pipe, drafter=drafter)
 
@@ -495,6 +495,35 @@ def test_engram_backend_speculates_losslessly(tmp_path):
         assert got == want
         assert spec.totals["spec_rounds"] > 0 and spec.totals["spec_masked_rounds"] == spec.totals["spec_rounds"]
         assert spec.healthy, spec.error
+    finally:
+        spec.close()
+    # two requests at once share draft + verify rounds; each slot's n-gram history advances by its accepted rows only
+    prompt2 = torch.randint(3, 2000, (31,), generator=torch.Generator().manual_seed(10)).tolist()
+    plain = backend(False, rows=16)
+    try:
+        want2 = run(plain, prompt2, 20)
+    finally:
+        plain.close()
+    spec = backend(True, rows=16)
+    try:
+        ra = GenRequest(prompt_ids=prompt, max_tokens=24, sampling=Sampling(temperature=0.0))
+        rb = GenRequest(prompt_ids=prompt2, max_tokens=20, sampling=Sampling(temperature=0.0))
+        spec.submit(ra)
+        spec.submit(rb)
+        outs = []
+        for r in (ra, rb):
+            toks = []
+            while True:
+                ev = r.events.get(timeout=120)
+                if ev.kind == "tokens":
+                    toks += ev.tokens
+                elif ev.kind == "finish":
+                    break
+                elif ev.kind == "error":
+                    raise RuntimeError(ev.message)
+            outs.append(toks)
+        assert outs == [want, want2]
+        assert spec.totals["spec_lane_rounds"] > 0 and spec.healthy, spec.error
     finally:
         spec.close()
 
@@ -611,3 +640,29 @@ def test_http_campaign_runs_mixed_traffic_through_the_real_server():
     finally:
         srv.stop()
         backend.close()
+
+
+def test_prefill_matrix_reports_cold_and_retained_rows():
+    """The matrix tool drives the backend like the HTTP layer does: a retained row restores the base from the prompt
+    snapshot an earlier request left and computes only the rest; a cold row computes everything."""
+    from ds41rt_b200.config import ModelConfig
+    from ds41rt_b200.models.ds41 import DS41Engine, EngineWeights
+    from ds41rt_b200.serving.engine import NativeBackend
+    from ds41rt_b200.utils.prefill_matrix import run_matrix
+    cfg = ModelConfig.tiny()
+    dev = torch.device("cuda", 0)
+    eng = DS41Engine(cfg, EngineWeights.random(cfg, 0, 1, dev, seed=0), max_rows=32, slots=2, max_ctx=512)
+    be = NativeBackend(eng, eos=-1, concurrency=1, prefill_chunk=32)
+    try:
+        rows = run_matrix(be, cfg.vocab, [0, 96], [16, 48])
+        assert be.healthy, be.error
+    finally:
+        be.close()
+    assert [(r["base"], r["suffix"], r["mode"]) for r in rows] == [
+        (0, 16, "cold"), (0, 48, "cold"), (96, 16, "cold"), (96, 16, "retained"), (96, 48, "cold"), (96, 48, "retained")]
+    for r in rows:
+        assert r["seconds"] > 0 and r["tok_per_s"] > 0
+        if r["mode"] == "cold":
+            assert r["cache_hit_tokens"] == 0 and r["computed_tokens"] == r["base"] + r["suffix"]
+        else:
+            assert 0 < r["cache_hit_tokens"] <= r["base"] and r["computed_tokens"] < r["base"] + r["suffix"]
