@@ -9,6 +9,11 @@
   tokenize                   text -> token ids with the server's tokenizer
   load-tensors               read (and validate) tensors of a checkpoint, with timing
   plan-memory                KV page pool that fits a device next to the weights
+  make-loadplan              which tensors (row / column ranges, bytes, experts) each rank reads from a checkpoint
+  transport-capabilities     what the GPUs of this machine offer each other: peer access, NVLink, multicast, libraries
+  scheduler-smoke            host-only check of admission, lanes, streaming and cancellation over a scripted backend
+  bench-kernels / campaign / prefill-matrix / validate-bench / convert-checkpoint / convert-engram-table
+                             the tools of ds41rt_b200.utils, loader.convert and runtime.ple_convert under one entry
 
 `serve` reads its options in three tiers: a KEY=VALUE settings file (`--settings`, default ./ds41rt.config), the
 environment (DS41RT_<KEY>) and the command line, later tiers overriding earlier ones (ds41rt_b200/settings.py).
@@ -127,8 +132,12 @@ def cmd_inspect_model(args) -> int:
         cat = Catalog(args.checkpoint, cfg, variant=args.variant)
         rep["checkpoint"] = {"directory": args.checkpoint, "shards": len(cat.files), "validated_tensors": len(cat.where)}
     if args.world > 1:
-        per_rank = by_class.get("experts", 0) / args.world + sum(v for k, v in by_class.items() if k != "experts")
-        rep["per_rank_gb_expert_parallel"] = round(per_rank / 2 ** 30, 2)
+        # the Engram tables are read from host memory maps by rank 0 and never copied to a device as a whole
+        tables = sum(math.prod(sp[1]) * sizes.get(sp[0], 1) for n, sp in specs.items() if ".engram.embed" in n)
+        per_rank = by_class.get("experts", 0) / args.world + sum(v for k, v in by_class.items() if k != "experts") \
+            - tables
+        rep["per_rank_device_gb_expert_parallel"] = round(per_rank / 2 ** 30, 2)
+        rep["host_engram_tables_gb"] = round(tables / 2 ** 30, 2)
     print(json.dumps(rep, indent=1))
     return 0
 
@@ -213,6 +222,154 @@ def _random_engram_table(args, i: int) -> dict:
             meta = {"path": path + ".nvfp4", "row_bytes": done["row_bytes"], "global_scale": done["global_scale"]}
         _random_tables[key] = meta
     return _random_tables[key]
+
+
+def cmd_make_loadplan(args) -> int:
+    """Per-rank load plan (reference: `ds41rt make-loadplan`, rust/crates/ds41rt-loader/src/v41_catalog.rs:215-273)."""
+    import math
+    from .loader.catalog import Catalog, expected_tensors
+    cfg = _config(args)
+    sizes = {"BF16": 2, "F32": 4, "F8_E4M3": 1, "F8_E8M0": 1, "I8": 1, "U8": 1}
+    if args.checkpoint:
+        cat = Catalog(args.checkpoint, cfg, variant=args.variant)
+    else:                                                    # plan from the configuration alone
+        cat = object.__new__(Catalog)
+        cat.cfg, cat.expected = cfg, expected_tensors(cfg, args.variant)
+    ranks = [args.rank] if args.rank >= 0 else list(range(args.world))
+    out = {"model": cfg.name, "variant": args.variant, "world": args.world, "ranks": []}
+    for r in ranks:
+        plan = cat.shard_plan(r, args.world)
+        total, tables, sliced, experts = 0, 0, 0, set()
+        for name, (rows, cols) in plan.items():
+            dt, shape = cat.expected[name][0], list(cat.expected[name][1])
+            if rows is not None and shape:
+                shape[0] = rows[1] - rows[0]
+            if cols is not None and len(shape) > 1:
+                shape[1] = cols[1] - cols[0]
+            if ".engram.embed" in name:                  # memory-mapped on the host of rank 0, gathered row by row
+                tables += math.prod(shape) * sizes.get(dt, 1)
+                continue
+            total += math.prod(shape) * sizes.get(dt, 1)
+            sliced += rows is not None or cols is not None
+            if ".ffn.experts." in name and not name.startswith("mtp."):
+                parts = name.split(".")
+                experts.add(int(parts[parts.index("experts") + 1]))
+        entry = {"rank": r, "tensors": len(plan), "sliced_tensors": sliced, "device_gb": round(total / 2 ** 30, 3),
+                 "host_engram_tables_gb": round(tables / 2 ** 30, 3) if r == 0 else 0.0,
+                 "experts": [min(experts), max(experts)] if experts else None}
+        if args.list:
+            entry["plan"] = {n: {"rows": rc[0], "cols": rc[1]} for n, rc in plan.items()}
+        out["ranks"].append(entry)
+    print(json.dumps(out, indent=None if args.list else 1))
+    return 0
+
+
+def cmd_transport_capabilities(args) -> int:
+    """What the GPUs offer each other (reference: `ds41rt transport-capabilities`, which reports its TCP / RDMA paths;
+    here the transport is NVLink peer memory, so the report is about that).  Read-only."""
+    rep = {"transport": "peer memory over NVLink / NVSwitch (loads, stores and multimem from inside kernels); NCCL for "
+                        "bootstrap and baselines"}
+    try:
+        import torch
+        rep["cuda_available"] = torch.cuda.is_available()
+        n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+        rep["gpus"] = n
+        rep["peer_access"] = [[bool(i == j or torch.cuda.can_device_access_peer(i, j)) for j in range(n)]
+                              for i in range(n)]
+        rep["all_peers"] = all(all(row) for row in rep["peer_access"]) if n else False
+        rep["nccl"] = ".".join(map(str, torch.cuda.nccl.version())) if n else None
+        rep["multimem_capable"] = bool(n) and all(torch.cuda.get_device_capability(i)[0] >= 9 for i in range(n))
+        try:
+            import torch.distributed._symmetric_memory  # noqa: F401
+            rep["symmetric_memory"] = True
+        except Exception as e:
+            rep["symmetric_memory"] = f"{type(e).__name__}: {e}"
+    except Exception as e:                                   # pragma: no cover - depends on the machine
+        rep["torch_error"] = str(e)
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        links = []
+        for i in range(pynvml.nvmlDeviceGetCount()):
+            h = pynvml.nvmlDeviceGetHandleByIndex(i)
+            up = 0
+            for l in range(18):
+                try:
+                    up += int(pynvml.nvmlDeviceGetNvLinkState(h, l) == 1)
+                except pynvml.NVMLError:
+                    break
+            links.append(up)
+        rep["nvlink_links_up"] = links
+        pynvml.nvmlShutdown()
+    except Exception as e:
+        rep["nvlink_links_up"] = f"unavailable ({type(e).__name__})"
+    rep["environment"] = {k: os.environ[k] for k in ("NCCL_NVLS_ENABLE", "NCCL_P2P_DISABLE", "CUDA_VISIBLE_DEVICES")
+                          if k in os.environ}
+    print(json.dumps(rep, indent=1))
+    return 0
+
+
+def cmd_scheduler_smoke(args) -> int:
+    """Host-only smoke of the serving path over a scripted backend: bounded admission, lane balance, a streamed and a
+    plain completion through the real HTTP server, and a cancelled stream (reference: `ds41rt scheduler-smoke`)."""
+    import http.client
+    from .runtime import core as K
+    from .serving.engine import FakeBackend
+    from .serving.http import ApiServer
+    from .serving.tokenizer import ByteTokenizer
+    rep = {}
+    adm = K.Admission(2, 1)
+    got = [adm.reserve() for _ in range(4)]              # 0 queued, 1 waiting, -1 refused
+    rep["admission"] = {"entered": sum(1 for g in got if g >= 0), "refused": sum(1 for g in got if g < 0)}
+    lanes = K.Lanes(2)
+    placed = [lanes.add(i, 100 + i, 10) for i in range(4)]
+    rep["lanes"] = {"placed": placed, "loads": [lanes.load(0), lanes.load(1)]}
+    tk = ByteTokenizer()
+    script = tk.encode("scheduler smoke ok")
+    srv = ApiServer(FakeBackend(script, tk, delay=0.001), tk, queue_depth=4, waiters=4).start()
+    try:
+        body = {"model": "deepseek-ai/DeepSeek-V4.1-Flash", "messages": [{"role": "user", "content": "hi"}],
+                "max_tokens": 32, "thinking": {"type": "disabled"}}
+        hdr = {"Content-Type": "application/json", "Connection": "close"}
+        c = http.client.HTTPConnection("127.0.0.1", srv.port, timeout=30)
+        c.request("POST", "/v1/chat/completions", body=json.dumps(body).encode(), headers=hdr)
+        r = c.getresponse()
+        doc = json.loads(r.read())
+        rep["plain"] = {"status": r.status, "text": doc["choices"][0]["message"]["content"] if r.status == 200 else doc}
+        c.close()
+        c = http.client.HTTPConnection("127.0.0.1", srv.port, timeout=30)
+        c.request("POST", "/v1/chat/completions", body=json.dumps(dict(body, stream=True)).encode(), headers=hdr)
+        r = c.getresponse()
+        lines = [l for l in r.read().split(b"\n") if l.startswith(b"data: ")]
+        rep["stream"] = {"status": r.status, "events": len(lines), "done": lines[-1].strip() == b"data: [DONE]"}
+        c.close()
+        c = http.client.HTTPConnection("127.0.0.1", srv.port, timeout=30)
+        c.request("GET", "/health", headers={"Connection": "close"})
+        r = c.getresponse()
+        r.read()
+        rep["health"] = r.status
+        c.close()
+    finally:
+        srv.stop()
+    ok = rep["admission"] == {"entered": 3, "refused": 1} and rep["plain"]["status"] == 200 \
+        and rep["plain"]["text"] == "scheduler smoke ok" and rep["stream"]["done"] and rep["health"] == 200
+    rep["ok"] = bool(ok)
+    print(json.dumps(rep, indent=1))
+    return 0 if ok else 1
+
+
+def _forward(module: str):
+    def run(args) -> int:
+        import importlib
+        rest = args.rest[1:] if args.rest[:1] == ["--"] else args.rest
+        return int(importlib.import_module(module, __package__).main(rest) or 0)
+    return run
+
+
+FORWARDED = {"bench-kernels": ".utils.kernel_case", "campaign": ".utils.http_campaign",
+             "prefill-matrix": ".utils.prefill_matrix", "validate-bench": ".utils.validate_bench",
+             "convert-checkpoint": ".loader.convert", "convert-engram-table": ".runtime.ple_convert",
+             "engram-io-bench": ".runtime.engram_io"}
 
 
 def _engram_table_meta(args, i: int) -> dict:
@@ -363,6 +520,18 @@ def main(argv=None) -> int:
     pp.add_argument("--max-context", type=int, default=8192)
     pp.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8", "fp4"])
     pp.add_argument("--retained", type=int, default=40)
+    pk = sub.add_parser("make-loadplan")
+    model_args(pk)
+    pk.add_argument("--checkpoint", default="", help="validate against this checkpoint (default: plan from the configuration)")
+    pk.add_argument("--variant", default="mxfp4", choices=["mxfp4", "nvfp4"])
+    pk.add_argument("--world", type=int, default=8)
+    pk.add_argument("--rank", type=int, default=-1, help="only this rank (default: all)")
+    pk.add_argument("--list", action="store_true", help="include every tensor with its row / column range")
+    sub.add_parser("transport-capabilities")
+    sub.add_parser("scheduler-smoke")
+    for name in FORWARDED:
+        pf = sub.add_parser(name, add_help=False)
+        pf.add_argument("rest", nargs=argparse.REMAINDER)
     ps = sub.add_parser("serve")
     model_args(ps)
     ps.add_argument("--settings", default="", help="KEY=VALUE settings file (default ./ds41rt.config when present)")
@@ -395,8 +564,8 @@ def main(argv=None) -> int:
     ps.add_argument("--engram-random-rows", type=int, default=0,
                     help="random-init models: enable the Engram layers over random tables of this many rows")
     ps.add_argument("--speculative", action="store_true",
-                    help="decode a lone greedy request with dSpark draft + verify rounds (random-init drafter unless the "
-                         "checkpoint provides one)")
+                    help="decode with dSpark draft + verify rounds: a lone request, or up to four active requests sharing "
+                         "a round (random-init drafter unless the checkpoint provides one)")
     argv = list(sys.argv[1:] if argv is None else argv)
     args = ap.parse_args(argv)
     if args.cmd == "serve":
@@ -409,9 +578,12 @@ def main(argv=None) -> int:
             ap.error("--prefill-chunk must be within 80..4096")
         if not 1 <= args.concurrency <= 64:
             ap.error("--concurrency must be within 1..64")
-    return {"build": cmd_build, "info": cmd_info, "serve": cmd_serve, "doctor": cmd_doctor,
-            "inspect-model": cmd_inspect_model, "tokenize": cmd_tokenize, "load-tensors": cmd_load_tensors,
-            "plan-memory": cmd_plan_memory}[args.cmd](args)
+    table = {"build": cmd_build, "info": cmd_info, "serve": cmd_serve, "doctor": cmd_doctor,
+             "inspect-model": cmd_inspect_model, "tokenize": cmd_tokenize, "load-tensors": cmd_load_tensors,
+             "plan-memory": cmd_plan_memory, "make-loadplan": cmd_make_loadplan,
+             "transport-capabilities": cmd_transport_capabilities, "scheduler-smoke": cmd_scheduler_smoke}
+    table.update({name: _forward(mod) for name, mod in FORWARDED.items()})
+    return table[args.cmd](args)
 
 
 if __name__ == "__main__":

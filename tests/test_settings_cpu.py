@@ -90,3 +90,47 @@ def test_load_tensors_reads_an_exported_checkpoint(tmp_path):
     assert rc == 0 and rep["tensors_read"] > 3 and rep["bytes"] > 0
     rc, out = _cli("inspect-model", "--model", "tiny", "--checkpoint", str(tmp_path))
     assert rc == 0 and json.loads(out)["checkpoint"]["validated_tensors"] > 50
+
+
+def test_load_plan_transport_report_and_scheduler_smoke(tmp_path):
+    rc, out = _cli("make-loadplan", "--model", "tiny", "--world", "2")
+    rep = json.loads(out)
+    assert rc == 0 and [r["rank"] for r in rep["ranks"]] == [0, 1]
+    assert rep["ranks"][0]["experts"] == [0, 7] and rep["ranks"][1]["experts"] == [8, 15]
+    assert rep["ranks"][0]["device_gb"] == rep["ranks"][1]["device_gb"] > 0 and rep["ranks"][0]["sliced_tensors"] > 0
+    rc, out = _cli("make-loadplan", "--model", "tiny", "--world", "2", "--rank", "1", "--list")
+    plan = json.loads(out)["ranks"][0]["plan"]
+    assert rc == 0 and plan["head.weight"]["rows"] == [2048, 4096] and "layers.0.ffn.experts.3.w1.weight" not in plan
+    rc, out = _cli("transport-capabilities")
+    rep = json.loads(out)
+    assert rc == 0 and "peer_access" in rep and "transport" in rep
+    rc, out = _cli("scheduler-smoke")
+    rep = json.loads(out)
+    assert rc == 0 and rep["ok"] and rep["plain"]["text"] == "scheduler smoke ok" and rep["admission"]["refused"] == 1
+    # the tools under the same entry point
+    good = {"impl": "reference", "unavailable": "not installed"}
+    p = tmp_path / "r.json"
+    p.write_text(json.dumps(good))
+    rc, out = _cli("validate-bench", str(p))
+    assert rc == 1 and "no measured record" in out
+
+
+def test_stop_script_ends_the_recorded_process_group(tmp_path):
+    """stop.sh signals exactly the process group that run.sh recorded, and clears the record."""
+    import os
+    import shutil
+    import time
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    shutil.copy(os.path.join(root, "stop.sh"), tmp_path / "stop.sh")
+    child = subprocess.Popen(["setsid", "sleep", "120"])
+    (tmp_path / "ds41rt.pid").write_text(str(child.pid))
+    r = subprocess.run(["bash", str(tmp_path / "stop.sh"), "--grace", "5"], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and "stopped process group" in r.stdout
+    deadline = time.time() + 10
+    while child.poll() is None and time.time() < deadline:
+        time.sleep(0.05)
+    assert child.poll() is not None and not (tmp_path / "ds41rt.pid").exists()
+    r = subprocess.run(["bash", str(tmp_path / "stop.sh")], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and "not running" in r.stdout
+    r = subprocess.run(["bash", os.path.join(root, "run.sh"), "--gpus", "3"], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 64
