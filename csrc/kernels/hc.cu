@@ -15,6 +15,11 @@
 //                  streams, and accumulate this column slice's contribution to the NEXT mixes projection.
 //   hc_finish    : reduce the slice partials in fixed order, compute pre/post/comb, collapse with the
 //                  incoming pre and apply the RMSNorm weight -> normalised bf16 rows for the GEMMs.
+// Long passes put the mixes projection on the tensor cores instead: hc_post_mix runs without `fn` (expand, store and
+// the row's sum of squares only), a tcgen05 GEMM multiplies the stored streams [rows, 4H] by the mixing matrix given as
+// bf16 high and low parts ([24 high | 24 low | pad] x 4H, so the sum carries about 16 mantissa bits of the fp32
+// matrix), and hc_finish adds the two parts of every split-K plane.  24 dot products of length 4H per row are
+// 4 GFMA for 8192 rows: as SIMT work they made this the second largest kernel of a prompt pass.
 #include <atomic>
 
 #include "ds41_api.h"
@@ -69,7 +74,8 @@ hc_post_mix_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, 
   const int c0 = blockIdx.x * kHcSlice;
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  for (int i = tid; i < kHcProj * kHcMaxMult * (kHcSlice / 4); i += blockDim.x) {     // weights: before the dependency wait
+  const bool dots = fn != nullptr;        // without the matrix: expand, store and sum of squares only (no shared memory)
+  for (int i = tid; dots && i < kHcProj * kHcMaxMult * (kHcSlice / 4); i += blockDim.x) {     // weights: before the dependency wait
     const int j = i / (kHcMaxMult * (kHcSlice / 4)), rem = i % (kHcMaxMult * (kHcSlice / 4));
     const int d = rem / (kHcSlice / 4), c4 = (rem % (kHcSlice / 4)) * 4;
     *reinterpret_cast<float4*>(fs + j * (kHcMaxMult * kHcSlice) + d * kHcSlice + c4) =
@@ -85,7 +91,7 @@ hc_post_mix_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, 
   }
   const int r_begin = blockIdx.y * rows_per_block, r_end = min(rows, r_begin + rows_per_block);
   for (int r0 = r_begin; r0 < r_end; r0 += kHcRowsPerBlock) {
-  if (r0 > r_begin) __syncthreads();                  // the previous group's rows have been read by every warp
+  if (dots && r0 > r_begin) __syncthreads();          // the previous group's rows have been read by every warp
   // ---- expand (or plain load) into shared memory, bf16-rounded like the stored streams.  One item = one row x four
   // adjacent columns: 8-byte stream loads and 16-byte plane loads, all issued before the first use.
   for (int idx = tid; idx < kHcRowsPerBlock * (kHcSlice / 4); idx += blockDim.x) {
@@ -156,10 +162,22 @@ hc_post_mix_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, 
           for (int j = 0; j < 4; ++j) out[d][j] = s_in[d][j];
       }
     }
+    if (!dots) {
+      // one warp holds one whole row of the slice (32 four-column groups): its sum of squares needs no shared memory
+      float sq = 0.f;
+#pragma unroll
+      for (int d = 0; d < kHcMaxMult; ++d)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sq = fmaf(out[d][j], out[d][j], sq);
+      sq = warp_sum(sq);
+      if (lane == 0 && r < rows) partial[(1ll * blockIdx.x * rows + r) * kHcPartialStride + kHcProj] = sq;
+      continue;
+    }
 #pragma unroll
     for (int d = 0; d < kHcMaxMult; ++d)
       *reinterpret_cast<float4*>(&xs[rr][d][c]) = make_float4(out[d][0], out[d][1], out[d][2], out[d][3]);
   }
+  if (!dots) continue;
   __syncthreads();
   // ---- partial mixes: warp w owns projections w, w+8, w+16
   float dot[3][kHcRowsPerBlock];
@@ -209,7 +227,8 @@ hc_finish_kernel(const float* __restrict__ partial, int n_slices, const float* _
                  const __nv_bfloat16* __restrict__ streams, const float* __restrict__ norm_w,
                  float* __restrict__ next_pre, float* __restrict__ post, float* __restrict__ comb,
                  __nv_bfloat16* __restrict__ xn, float* __restrict__ tap_mean, uint8_t* __restrict__ xq,
-                 uint8_t* __restrict__ xq_sf, int rows, int H, int iters, float hc_eps, float norm_eps) {
+                 uint8_t* __restrict__ xq_sf, int rows, int H, int iters, float hc_eps, float norm_eps,
+                 const float* __restrict__ mix_planes, int mix_splits, long long mix_split_stride, int mix_ld) {
   __shared__ float proj[kHcProj + 1];
   __shared__ float warp_part[8];
   __shared__ float inv_rms;
@@ -220,7 +239,15 @@ hc_finish_kernel(const float* __restrict__ partial, int n_slices, const float* _
   // ---- slice partials: warp w reduces values w, w+8, w+16 (+24); fixed shuffle tree -> deterministic
   for (int j = warp; j <= kHcProj; j += 8) {
     float acc = 0.f;
-    for (int s = lane; s < n_slices; s += 32) acc += partial[(1ll * s * rows + r) * kHcPartialStride + j];
+    if (mix_planes != nullptr && j < kHcProj) {
+      // tensor-core projection: split-K planes [split][rows][mix_ld], columns j (high part) and 24 + j (low part)
+      for (int s = lane; s < mix_splits; s += 32) {
+        const float* p = mix_planes + s * mix_split_stride + 1ll * r * mix_ld;
+        acc += p[j] + p[kHcProj + j];
+      }
+    } else {
+      for (int s = lane; s < n_slices; s += 32) acc += partial[(1ll * s * rows + r) * kHcPartialStride + j];
+    }
     acc = warp_sum(acc);
     if (lane == 0) proj[j] = acc;
   }
@@ -374,6 +401,13 @@ extern "C" int ds41_hc_post_mix(const void* streams_in, void* streams_out, const
   const int slices = H / kHcSlice;
   int rpb = rows * slices / (2 * 148) / kHcRowsPerBlock * kHcRowsPerBlock;
   rpb = rpb < kHcRowsPerBlock ? kHcRowsPerBlock : (rpb > 64 ? 64 : rpb);
+  if (fn == nullptr) {
+    // expand only: nothing is kept across row groups, so small blocks and no dynamic shared memory
+    dim3 grid(slices, (rows + kHcRowsPerBlock - 1) / kHcRowsPerBlock);
+    return launch_pdl(hc_post_mix_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream),
+                      static_cast<const __nv_bfloat16*>(streams_in), static_cast<__nv_bfloat16*>(streams_out), parts,
+                      post, comb, fn, partial, rows, H, wait_flags, wait_epoch, status, kHcRowsPerBlock);
+  }
   constexpr size_t kSmem = sizeof(float) * (kHcRowsPerBlock * kHcMaxMult * kHcSlice + kHcProj * kHcMaxMult * kHcSlice);
   static std::atomic<bool> configured[64];
   int dev = 0;
@@ -393,11 +427,14 @@ extern "C" int ds41_hc_post_mix(const void* streams_in, void* streams_out, const
 extern "C" int ds41_hc_finish(const float* partial, int n_slices, const float* scale, const float* base,
                               const float* pre_in, const void* streams, const float* norm_w, float* next_pre,
                               float* post, float* comb, void* xn, float* tap_mean, void* xq, void* xq_sf, int rows,
-                              int H, int iters, float hc_eps, float norm_eps, void* stream) {
-  if (rows <= 0 || H % 8 != 0 || H > 256 * 3 * 8 || (xq != nullptr && (H % 128 != 0 || xq_sf == nullptr)))
+                              int H, int iters, float hc_eps, float norm_eps, const float* mix_planes, int mix_splits,
+                              long long mix_split_stride, int mix_ld, void* stream) {
+  if (rows <= 0 || H % 8 != 0 || H > 256 * 3 * 8 || (xq != nullptr && (H % 128 != 0 || xq_sf == nullptr)) ||
+      (mix_planes != nullptr && (mix_splits <= 0 || mix_ld < 2 * kHcProj)))
     return cudaErrorInvalidValue;
   return launch_pdl(hc_finish_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), partial, n_slices,
                     scale, base, pre_in, static_cast<const __nv_bfloat16*>(streams), norm_w, next_pre, post, comb,
                     static_cast<__nv_bfloat16*>(xn), tap_mean, static_cast<uint8_t*>(xq),
-                    static_cast<uint8_t*>(xq_sf), rows, H, iters, hc_eps, norm_eps);
+                    static_cast<uint8_t*>(xq_sf), rows, H, iters, hc_eps, norm_eps, mix_planes, mix_splits,
+                    mix_split_stride, mix_ld);
 }

@@ -696,6 +696,12 @@ class DS41Engine:
         self.xc = z((R, H), F32)
         self.tickets = z((R,), I32)
         self.fused_rows = 16      # passes of at most this many rows use the fused hyper-connection step
+        # Passes of at least `mix_tc_rows` rows take the 24 mixes projections of a hyper-connection step from a
+        # tensor-core GEMM over the stored streams (mixing matrix as bf16 high + low parts) instead of SIMT dot products.
+        self.mix_tc_rows = 128
+        self._mix_w: Dict[int, torch.Tensor] = {}          # data_ptr of an fp32 mixing matrix -> [64, 4H] bf16 split
+        self.mix_planes = z((max(R, 148 * 128) * 64,), F32) if R >= self.mix_tc_rows else None
+        self._mix_state = None                             # (splits, rows) of the projection that hc_finish reads next
         self.taps = z((len(cfg.dspark.tap_layers), R, H), F32) if cfg.dspark is not None else None
         # attention
         max_extra = max([lw.extra_cols for lw in live] + [0])
@@ -937,14 +943,47 @@ class DS41Engine:
     def clear_engram_rows(self) -> None:
         self._engram_live.clear()
 
+    def _mix_weight(self, fn: torch.Tensor) -> torch.Tensor:
+        """[64, 4H] bf16 for the mixes GEMM: rows 0-23 the bf16 rounding of `fn`, rows 24-47 the bf16 rounding of what
+        that left (together about 16 mantissa bits of the fp32 matrix), the rest zero."""
+        w = self._mix_w.get(fn.data_ptr())
+        if w is None:
+            hi = fn.to(BF16)
+            w = torch.zeros(64, fn.shape[1], dtype=BF16, device=fn.device)
+            w[:24] = hi
+            w[24:48] = (fn - hi.float()).to(BF16)
+            self._mix_w[fn.data_ptr()] = w
+        return w
+
+    def _mix_gemm(self, streams: torch.Tensor, rows: int, fn: torch.Tensor) -> None:
+        """mix_planes[split][rows][64] = streams[rows, 4H] x (high | low parts of fn)^T on the tensor cores."""
+        K = self.cfg.hc_mult * self.cfg.hidden
+        splits = G.pick_splits(rows, K, max_splits=16)
+        planes = self.mix_planes[: splits * rows * 64]
+        self._run("gemm_mix", G.gemm_raw, streams.view(-1, K)[:rows], self._mix_weight(fn), planes if splits == 1 else None,
+                  rows, 64, K, lda=K, ldb=K, ldo=64, out_mode=1, k_splits=splits,
+                  split_workspace=planes if splits > 1 else None, bn=64, status=self.status, static_operand=2)
+        self._mix_state = (splits, rows)
+
+    def _mix_args(self, rows: int):
+        """The four projection arguments of hc_finish: the planes of the GEMM that just ran, or none."""
+        st, self._mix_state = self._mix_state, None
+        if st is None:
+            return lib.ptr(None), 0, C.c_longlong(0), 0
+        assert st[1] == rows
+        return lib.ptr(self.mix_planes), st[0], C.c_longlong(rows * 64), 64
+
     def _post_mix(self, rows, part_bases, n_ranks, n_splits, split_stride, fn, sync, coef=None):
         k, st = self.k, lib.stream()
         post, comb = coef if coef is not None else (self.post, self.comb)
         wait_flags = lib.ptr(self.flag_ptrs) if (sync and self.world > 1) else lib.ptr(None)
+        tc = self.mix_planes is not None and rows >= self.mix_tc_rows
         self._run("hc_post_mix", k.ds41_hc_post_mix, 
             lib.ptr(self.streams), lib.ptr(self.streams), part_bases, n_ranks, n_splits, C.c_longlong(split_stride),
-            lib.ptr(post), lib.ptr(comb), lib.ptr(fn), lib.ptr(self.hc_partial), rows, self.cfg.hidden,
+            lib.ptr(post), lib.ptr(comb), lib.ptr(None if tc else fn), lib.ptr(self.hc_partial), rows, self.cfg.hidden,
             wait_flags, lib.ptr(self.epoch), lib.ptr(self.status), st)
+        if tc:
+            self._mix_gemm(self.streams, rows, fn)
 
     def _finish(self, rows, scale, base, pre_in, norm_w, next_pre, tap=None, quant=False, coef=None):
         cfg = self.cfg
@@ -954,7 +993,7 @@ class DS41Engine:
             lib.ptr(self.streams), lib.ptr(norm_w), lib.ptr(next_pre), lib.ptr(post), lib.ptr(comb),
             lib.ptr(self.xn), lib.ptr(tap), lib.ptr(self.xq if quant else None),
             lib.ptr(self.xq_sf if quant else None), rows, cfg.hidden, cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps),
-            C.c_float(cfg.norm_eps), lib.stream())
+            C.c_float(cfg.norm_eps), *self._mix_args(rows), lib.stream())
 
     def _step(self, rows, part_bases, n_ranks, n_splits, split_stride, coef_in, pre_in, fn, scale, base, norm_w,
               next_pre, coef_out, tap=None, quant=False, sync=False):
@@ -1317,15 +1356,19 @@ class DS41Engine:
         bases, n_splits, stride = pending if pending is not None else (None, 0, 0)
         ptrs = (C.c_void_p * 1)(bases) if bases is not None else None
         streams = self.streams[lo:]
+        tc = self.mix_planes is not None and Rl >= self.mix_tc_rows
         self._run("hc_post_mix", self.k.ds41_hc_post_mix, lib.ptr(streams), lib.ptr(streams), ptrs,
                   1 if bases is not None else 0, n_splits, C.c_longlong(stride), lib.ptr(self.post[lo:]),
-                  lib.ptr(self.comb[lo:]), lib.ptr(fn), lib.ptr(self.hc_partial), Rl, cfg.hidden, lib.ptr(None),
-                  lib.ptr(self.epoch), lib.ptr(self.status), lib.stream())
+                  lib.ptr(self.comb[lo:]), lib.ptr(None if tc else fn), lib.ptr(self.hc_partial), Rl, cfg.hidden,
+                  lib.ptr(None), lib.ptr(self.epoch), lib.ptr(self.status), lib.stream())
+        if tc:
+            self._mix_gemm(streams, Rl, fn)
         self._run("hc_finish", self.k.ds41_hc_finish, lib.ptr(self.hc_partial), self.n_slices, lib.ptr(scale),
                   lib.ptr(base), lib.ptr(self.pre[cur][lo:]), lib.ptr(streams), lib.ptr(norm_w),
                   lib.ptr(self.pre[cur ^ 1][lo:]), lib.ptr(self.post[lo:]), lib.ptr(self.comb[lo:]), lib.ptr(xn_out),
                   lib.ptr(tap[lo:] if tap is not None else None), lib.ptr(None), lib.ptr(None), Rl, cfg.hidden,
-                  cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps), C.c_float(cfg.norm_eps), lib.stream())
+                  cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps), C.c_float(cfg.norm_eps), *self._mix_args(Rl),
+                  lib.stream())
         self._cur = cur ^ 1
 
     def _sp_qkv(self, l, lw, R, Rl, inv, sources, ctx):

@@ -241,7 +241,8 @@ def hc_case(rows: int, H: int = 5120):
             lib.check(k.ds41_hc_finish(lib.ptr(partial), H // 128, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
                                        lib.ptr(out_streams), lib.ptr(norm_w), lib.ptr(next_pre), lib.ptr(post2),
                                        lib.ptr(comb2), lib.ptr(xn), lib.ptr(None), lib.ptr(None), lib.ptr(None), rows, H,
-                                       20, C.c_float(1e-6), C.c_float(1e-20), lib.stream()), "hc_finish")
+                                       20, C.c_float(1e-6), C.c_float(1e-20), lib.ptr(None), 0, C.c_longlong(0), 0,
+                                       lib.stream()), "hc_finish")
     streams_bytes = 2.0 * rows * 4 * H
     return run, {"bytes_min": 2 * streams_bytes + 4.0 * rows * H + 2.0 * rows * H + 4.0 * 24 * 4 * H, "status": st,
                  "keep": (keep, streams, sub, fn, scale, base, pre_in, post, comb, norm_w, out_streams, next_pre, post2,

@@ -174,7 +174,7 @@ def test_hc_kernels_match_oracle():
     lib.check(k.ds41_hc_finish(lib.ptr(partial), H // 128, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
                                lib.ptr(s_dev), lib.ptr(norm_w), lib.ptr(next_pre), lib.ptr(post), lib.ptr(comb),
                                lib.ptr(xn_d), lib.ptr(None), lib.ptr(None), lib.ptr(None), rows, H, 20, C.c_float(1e-6), C.c_float(1e-20),
-                               lib.stream()), "finish")
+                               lib.ptr(None), 0, C.c_longlong(0), 0, lib.stream()), "finish")
     torch.cuda.synchronize()
     assert (s_dev.float().cpu() - new_streams).abs().max() < 0.05
     assert (next_pre.cpu() - pre1).abs().max() < 2e-2
@@ -279,7 +279,7 @@ def test_hc_step_matches_unfused_kernels():
     lib.check(k.ds41_hc_finish(lib.ptr(partial), H // 128, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
                                lib.ptr(s1), lib.ptr(norm_w), lib.ptr(np1), lib.ptr(po1), lib.ptr(co1), lib.ptr(xn1),
                                lib.ptr(None), lib.ptr(None), lib.ptr(None), rows, H, 20, C.c_float(1e-6),
-                               C.c_float(1e-20), lib.stream()), "finish")
+                               C.c_float(1e-20), lib.ptr(None), 0, C.c_longlong(0), 0, lib.stream()), "finish")
     # fused (run twice: the ticket counters must reset themselves)
     for _ in range(2):
         s2 = streams.clone()
@@ -496,3 +496,69 @@ def test_candidate_blocks_select_and_restrict():
         assert sel[r, : int(n_sel[r])].tolist() == sorted(order.tolist()), r
         assert int(n_sel[r]) == min(topk, n_ok)
     assert int(n_blocks[4]) == 0 and int(n_sel[4]) == 0 and not bits[4].any()
+
+
+@pytest.mark.parametrize("rows,H", [(300, 512), (1024, 1024)])
+def test_hc_mixes_on_the_tensor_cores_match_the_dot_product_kernel(rows, H):
+    """Long-pass form of the hyper-connection step: expand without the mixing matrix, the 24 projections from a
+    tcgen05 GEMM over the stored streams with the matrix as bf16 high + low parts, hc_finish reading the split-K
+    planes.  Streams are identical to the dot-product kernel's; pre / post / comb and the normalised rows agree to
+    fp32 rounding of a 4H-long sum, and with the fp32 oracle as closely as the dot-product kernel does."""
+    from ds41rt_b200.models import reference as R
+    from ds41rt_b200.ops import gemm as G
+    from ds41rt_b200.ops import lib
+    k = lib.kernels()
+    torch.manual_seed(rows)
+    K = 4 * H
+    streams = torch.randn(rows, 4, H, device="cuda").bfloat16()
+    sub = torch.randn(2, rows, H, device="cuda")
+    fn = torch.randn(24, K, device="cuda") * 0.5
+    scale = torch.tensor([1.0, 0.7, 1.3], device="cuda")
+    base = torch.randn(24, device="cuda") * 0.5
+    pre_in = torch.rand(rows, 4, device="cuda")
+    norm_w = torch.rand(H, device="cuda") + 0.5
+    post = torch.rand(rows, 4, device="cuda") * 2
+    comb = torch.rand(rows, 16, device="cuda") / 4
+    st = lib.new_status("cuda")
+    bases = (C.c_void_p * 1)(sub.data_ptr())
+
+    def run(tc):
+        s = streams.clone()
+        partial = torch.zeros(H // 128, rows, 25, device="cuda")
+        lib.check(k.ds41_hc_post_mix(lib.ptr(s), lib.ptr(s), bases, 1, 2, C.c_longlong(rows * H), lib.ptr(post),
+                                     lib.ptr(comb), lib.ptr(None if tc else fn), lib.ptr(partial), rows, H,
+                                     lib.ptr(None), lib.ptr(None), lib.ptr(st), lib.stream()), "post_mix")
+        mix = (lib.ptr(None), 0, C.c_longlong(0), 0)
+        keep = None
+        if tc:
+            hi = fn.bfloat16()
+            w = torch.zeros(64, K, device="cuda", dtype=torch.bfloat16)
+            w[:24], w[24:48] = hi, (fn - hi.float()).bfloat16()
+            splits = G.pick_splits(rows, K, max_splits=16)
+            assert splits > 1
+            planes = torch.zeros(splits, rows, 64, device="cuda")
+            G.gemm_raw(s.view(rows, K), w, None, rows, 64, K, lda=K, ldb=K, ldo=64, out_mode=1, k_splits=splits,
+                       split_workspace=planes, bn=64, status=st, static_operand=2)
+            mix = (lib.ptr(planes), splits, C.c_longlong(rows * 64), 64)
+            keep = (w, planes)
+        outs = [torch.zeros(rows, 4, device="cuda"), torch.zeros(rows, 4, device="cuda"),
+                torch.zeros(rows, 16, device="cuda"), torch.zeros(rows, H, device="cuda", dtype=torch.bfloat16)]
+        lib.check(k.ds41_hc_finish(lib.ptr(partial), H // 128, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
+                                   lib.ptr(s), lib.ptr(norm_w), lib.ptr(outs[0]), lib.ptr(outs[1]), lib.ptr(outs[2]),
+                                   lib.ptr(outs[3]), lib.ptr(None), lib.ptr(None), lib.ptr(None), rows, H, 20,
+                                   C.c_float(1e-6), C.c_float(1e-20), *mix, lib.stream()), "finish")
+        torch.cuda.synchronize()
+        lib.raise_on_status(st, "hc mixes")
+        return s, outs, partial, keep
+
+    s_a, a, part_a, _ = run(False)
+    s_b, b, part_b, _ = run(True)
+    assert torch.equal(s_a, s_b)
+    assert torch.allclose(part_a[:, :, 24], part_b[:, :, 24], rtol=1e-5, atol=1e-5)      # sums of squares
+    assert torch.equal(a[3], b[3])                                                       # collapse + norm: same inputs
+    for x, y in zip(a[:3], b[:3]):
+        assert float((x - y).abs().max()) < 2e-4
+    pre1, post1, comb1 = R.hc_mixes(s_b.float().cpu(), fn.cpu(), scale.cpu(), base.cpu(), 4, 20, 1e-6, 1e-20)
+    assert float((b[0].cpu() - pre1).abs().max()) < 1e-3
+    assert float((b[1].cpu() - post1).abs().max()) < 1e-3
+    assert float((b[2].cpu().view(rows, 4, 4) - comb1).abs().max()) < 1e-3
