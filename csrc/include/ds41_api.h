@@ -109,7 +109,8 @@ int ds41_hc_finish(const float* partial, int n_slices, const float* scale, const
                    const void* streams, const float* norm_w, float* next_pre, float* post, float* comb, void* xn,
                    float* tap_mean, void* xq, void* xq_sf, int rows, int H, int iters, float hc_eps, float norm_eps,
                    const float* mix_planes, int mix_splits, long long mix_split_stride, int mix_ld, void* stream);
-// hc_post_mix with fn == NULL only expands, stores and leaves each row's sum of squares in `partial`; the 24 mixes
+// hc_post_mix with fn == NULL only expands, stores and leaves row r's sum of squares in partial[r * 25 + 24] (a
+// single slice: hc_finish is then called with n_slices = 1); the 24 mixes
 // projections then come from a GEMM of the stored streams [rows, 4H] with the matrix as bf16 high and low parts
 // (columns j and 24 + j of fp32 split-K planes [mix_splits][rows][mix_ld]), which hc_finish reads as `mix_planes`
 // (NULL: the projections are in `partial`).

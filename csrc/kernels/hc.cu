@@ -74,8 +74,7 @@ hc_post_mix_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, 
   const int c0 = blockIdx.x * kHcSlice;
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  const bool dots = fn != nullptr;        // without the matrix: expand, store and sum of squares only (no shared memory)
-  for (int i = tid; dots && i < kHcProj * kHcMaxMult * (kHcSlice / 4); i += blockDim.x) {     // weights: before the dependency wait
+  for (int i = tid; i < kHcProj * kHcMaxMult * (kHcSlice / 4); i += blockDim.x) {     // weights: before the dependency wait
     const int j = i / (kHcMaxMult * (kHcSlice / 4)), rem = i % (kHcMaxMult * (kHcSlice / 4));
     const int d = rem / (kHcSlice / 4), c4 = (rem % (kHcSlice / 4)) * 4;
     *reinterpret_cast<float4*>(fs + j * (kHcMaxMult * kHcSlice) + d * kHcSlice + c4) =
@@ -91,7 +90,7 @@ hc_post_mix_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, 
   }
   const int r_begin = blockIdx.y * rows_per_block, r_end = min(rows, r_begin + rows_per_block);
   for (int r0 = r_begin; r0 < r_end; r0 += kHcRowsPerBlock) {
-  if (dots && r0 > r_begin) __syncthreads();          // the previous group's rows have been read by every warp
+  if (r0 > r_begin) __syncthreads();                  // the previous group's rows have been read by every warp
   // ---- expand (or plain load) into shared memory, bf16-rounded like the stored streams.  One item = one row x four
   // adjacent columns: 8-byte stream loads and 16-byte plane loads, all issued before the first use.
   for (int idx = tid; idx < kHcRowsPerBlock * (kHcSlice / 4); idx += blockDim.x) {
@@ -162,22 +161,10 @@ hc_post_mix_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, 
           for (int j = 0; j < 4; ++j) out[d][j] = s_in[d][j];
       }
     }
-    if (!dots) {
-      // one warp holds one whole row of the slice (32 four-column groups): its sum of squares needs no shared memory
-      float sq = 0.f;
-#pragma unroll
-      for (int d = 0; d < kHcMaxMult; ++d)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) sq = fmaf(out[d][j], out[d][j], sq);
-      sq = warp_sum(sq);
-      if (lane == 0 && r < rows) partial[(1ll * blockIdx.x * rows + r) * kHcPartialStride + kHcProj] = sq;
-      continue;
-    }
 #pragma unroll
     for (int d = 0; d < kHcMaxMult; ++d)
       *reinterpret_cast<float4*>(&xs[rr][d][c]) = make_float4(out[d][0], out[d][1], out[d][2], out[d][3]);
   }
-  if (!dots) continue;
   __syncthreads();
   // ---- partial mixes: warp w owns projections w, w+8, w+16
   float dot[3][kHcRowsPerBlock];
@@ -216,6 +203,112 @@ hc_post_mix_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, 
     }
   }
   }   // row groups of this block
+}
+
+// Expand alone, for passes whose mixes projection runs as a GEMM afterwards: one block per row walks the row's H
+// columns in groups of eight (16-byte stream loads and stores, two 16-byte loads per partial plane), with the row's
+// 4 + 16 mixing coefficients in registers, and leaves the sum of squares of the new streams in
+// partial[row * kHcPartialStride + kHcProj] (one slice).  parts.n_ranks == 0: the streams stay as they are and only the
+// sum of squares is produced.
+__global__ void __launch_bounds__(256)
+hc_expand_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, PartList parts,
+                 const float* __restrict__ post, const float* __restrict__ comb, float* __restrict__ partial, int rows,
+                 int H, const uint32_t* const* __restrict__ wait_flags, const uint32_t* __restrict__ wait_epoch,
+                 int* status) {
+  __shared__ float warp_sq[8];
+  const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (wait_flags != nullptr && parts.n_ranks > 1) {
+    if (tid < parts.n_ranks) flag_wait_ge(wait_flags[tid], *wait_epoch, status, 400 + tid);
+    __syncthreads();
+  }
+  const bool expand = parts.n_ranks > 0;
+  float cm[16], pw[4];
+  if (expand) {
+#pragma unroll
+    for (int q = 0; q < 16; ++q) cm[q] = comb[r * 16 + q];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) pw[q] = post[r * 4 + q];
+  }
+  const int n_sp = parts.n_splits, total = parts.n_ranks * n_sp;
+  float sq = 0.f;
+  for (int g = tid; g < H / 8; g += 256) {
+    const int c = g * 8;
+    uint4 raw[kHcMaxMult];
+#pragma unroll
+    for (int s = 0; s < kHcMaxMult; ++s)
+      raw[s] = *reinterpret_cast<const uint4*>(streams_in + (1ll * r * kHcMaxMult + s) * H + c);
+    float s_in[kHcMaxMult][8];
+#pragma unroll
+    for (int s = 0; s < kHcMaxMult; ++s) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[s]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 v = __bfloat1622float2(h[q]);
+        s_in[s][2 * q] = v.x;
+        s_in[s][2 * q + 1] = v.y;
+      }
+    }
+    if (!expand) {
+#pragma unroll
+      for (int s = 0; s < kHcMaxMult; ++s)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sq = fmaf(s_in[s][j], s_in[s][j], sq);
+      continue;
+    }
+    float sub[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    // rank-major, split-minor order; four planes (eight 16-byte loads) in flight before the first add
+    for (int j0 = 0; j0 < total; j0 += 4) {
+      float4 v[4][2];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int j = j0 + u;
+        v[u][0] = v[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (j < total) {
+          const int k = j / n_sp, sp = j - k * n_sp;
+          const float4* src = reinterpret_cast<const float4*>(parts.base[k] + sp * parts.split_stride + 1ll * r * H + c);
+          v[u][0] = __ldcg(src);
+          v[u][1] = __ldcg(src + 1);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        sub[0] += v[u][0].x; sub[1] += v[u][0].y; sub[2] += v[u][0].z; sub[3] += v[u][0].w;
+        sub[4] += v[u][1].x; sub[5] += v[u][1].y; sub[6] += v[u][1].z; sub[7] += v[u][1].w;
+      }
+    }
+    float out[kHcMaxMult][8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sb = bf16_round(sub[j]);
+#pragma unroll
+      for (int d = 0; d < kHcMaxMult; ++d) {
+        float acc = 0.f;
+#pragma unroll
+        for (int s = 0; s < kHcMaxMult; ++s) acc = fmaf(cm[s * 4 + d], s_in[s][j], acc);
+        out[d][j] = bf16_round(fmaf(pw[d], sb, acc));
+        sq = fmaf(out[d][j], out[d][j], sq);
+      }
+    }
+#pragma unroll
+    for (int d = 0; d < kHcMaxMult; ++d) {
+      uint4 w;
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(out[d][2 * q], out[d][2 * q + 1]);
+      *reinterpret_cast<uint4*>(streams_out + (1ll * r * kHcMaxMult + d) * H + c) = w;
+    }
+  }
+  sq = warp_sum(sq);
+  if (lane == 0) warp_sq[warp] = sq;
+  __syncthreads();
+  if (tid == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += warp_sq[w];
+    partial[1ll * r * kHcPartialStride + kHcProj] = t;
+  }
 }
 
 // One block per row.  Produces next_pre/post/comb from the slice partials, then the collapsed,
@@ -401,13 +494,10 @@ extern "C" int ds41_hc_post_mix(const void* streams_in, void* streams_out, const
   const int slices = H / kHcSlice;
   int rpb = rows * slices / (2 * 148) / kHcRowsPerBlock * kHcRowsPerBlock;
   rpb = rpb < kHcRowsPerBlock ? kHcRowsPerBlock : (rpb > 64 ? 64 : rpb);
-  if (fn == nullptr) {
-    // expand only: nothing is kept across row groups, so small blocks and no dynamic shared memory
-    dim3 grid(slices, (rows + kHcRowsPerBlock - 1) / kHcRowsPerBlock);
-    return launch_pdl(hc_post_mix_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream),
+  if (fn == nullptr)      // expand only; the sum of squares of row r lands in partial[r * 25 + 24] (one slice)
+    return launch_pdl(hc_expand_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream),
                       static_cast<const __nv_bfloat16*>(streams_in), static_cast<__nv_bfloat16*>(streams_out), parts,
-                      post, comb, fn, partial, rows, H, wait_flags, wait_epoch, status, kHcRowsPerBlock);
-  }
+                      post, comb, partial, rows, H, wait_flags, wait_epoch, status);
   constexpr size_t kSmem = sizeof(float) * (kHcRowsPerBlock * kHcMaxMult * kHcSlice + kHcProj * kHcMaxMult * kHcSlice);
   static std::atomic<bool> configured[64];
   int dev = 0;

@@ -966,12 +966,13 @@ class DS41Engine:
         self._mix_state = (splits, rows)
 
     def _mix_args(self, rows: int):
-        """The four projection arguments of hc_finish: the planes of the GEMM that just ran, or none."""
+        """(slices of hc_partial to sum, the four projection arguments of hc_finish): the planes of the GEMM that just
+        ran and the single slice the expand kernel wrote, or the dot-product kernel's slices and no planes."""
         st, self._mix_state = self._mix_state, None
         if st is None:
-            return lib.ptr(None), 0, C.c_longlong(0), 0
+            return self.n_slices, (lib.ptr(None), 0, C.c_longlong(0), 0)
         assert st[1] == rows
-        return lib.ptr(self.mix_planes), st[0], C.c_longlong(rows * 64), 64
+        return 1, (lib.ptr(self.mix_planes), st[0], C.c_longlong(rows * 64), 64)
 
     def _post_mix(self, rows, part_bases, n_ranks, n_splits, split_stride, fn, sync, coef=None):
         k, st = self.k, lib.stream()
@@ -988,12 +989,13 @@ class DS41Engine:
     def _finish(self, rows, scale, base, pre_in, norm_w, next_pre, tap=None, quant=False, coef=None):
         cfg = self.cfg
         post, comb = coef if coef is not None else (self.post, self.comb)
+        n_slices, mix = self._mix_args(rows)
         self._run("hc_finish", self.k.ds41_hc_finish, 
-            lib.ptr(self.hc_partial), self.n_slices, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
+            lib.ptr(self.hc_partial), n_slices, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
             lib.ptr(self.streams), lib.ptr(norm_w), lib.ptr(next_pre), lib.ptr(post), lib.ptr(comb),
             lib.ptr(self.xn), lib.ptr(tap), lib.ptr(self.xq if quant else None),
             lib.ptr(self.xq_sf if quant else None), rows, cfg.hidden, cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps),
-            C.c_float(cfg.norm_eps), *self._mix_args(rows), lib.stream())
+            C.c_float(cfg.norm_eps), *mix, lib.stream())
 
     def _step(self, rows, part_bases, n_ranks, n_splits, split_stride, coef_in, pre_in, fn, scale, base, norm_w,
               next_pre, coef_out, tap=None, quant=False, sync=False):
@@ -1363,12 +1365,12 @@ class DS41Engine:
                   lib.ptr(None), lib.ptr(self.epoch), lib.ptr(self.status), lib.stream())
         if tc:
             self._mix_gemm(streams, Rl, fn)
-        self._run("hc_finish", self.k.ds41_hc_finish, lib.ptr(self.hc_partial), self.n_slices, lib.ptr(scale),
+        n_slices, mix = self._mix_args(Rl)
+        self._run("hc_finish", self.k.ds41_hc_finish, lib.ptr(self.hc_partial), n_slices, lib.ptr(scale),
                   lib.ptr(base), lib.ptr(self.pre[cur][lo:]), lib.ptr(streams), lib.ptr(norm_w),
                   lib.ptr(self.pre[cur ^ 1][lo:]), lib.ptr(self.post[lo:]), lib.ptr(self.comb[lo:]), lib.ptr(xn_out),
                   lib.ptr(tap[lo:] if tap is not None else None), lib.ptr(None), lib.ptr(None), Rl, cfg.hidden,
-                  cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps), C.c_float(cfg.norm_eps), *self._mix_args(Rl),
-                  lib.stream())
+                  cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps), C.c_float(cfg.norm_eps), *mix, lib.stream())
         self._cur = cur ^ 1
 
     def _sp_qkv(self, l, lw, R, Rl, inv, sources, ctx):

@@ -543,7 +543,7 @@ def test_hc_mixes_on_the_tensor_cores_match_the_dot_product_kernel(rows, H):
             keep = (w, planes)
         outs = [torch.zeros(rows, 4, device="cuda"), torch.zeros(rows, 4, device="cuda"),
                 torch.zeros(rows, 16, device="cuda"), torch.zeros(rows, H, device="cuda", dtype=torch.bfloat16)]
-        lib.check(k.ds41_hc_finish(lib.ptr(partial), H // 128, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
+        lib.check(k.ds41_hc_finish(lib.ptr(partial), 1 if tc else H // 128, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
                                    lib.ptr(s), lib.ptr(norm_w), lib.ptr(outs[0]), lib.ptr(outs[1]), lib.ptr(outs[2]),
                                    lib.ptr(outs[3]), lib.ptr(None), lib.ptr(None), lib.ptr(None), rows, H, 20,
                                    C.c_float(1e-6), C.c_float(1e-20), *mix, lib.stream()), "finish")
@@ -554,7 +554,7 @@ def test_hc_mixes_on_the_tensor_cores_match_the_dot_product_kernel(rows, H):
     s_a, a, part_a, _ = run(False)
     s_b, b, part_b, _ = run(True)
     assert torch.equal(s_a, s_b)
-    assert torch.allclose(part_a[:, :, 24], part_b[:, :, 24], rtol=1e-5, atol=1e-5)      # sums of squares
+    assert torch.allclose(part_a[:, :, 24].sum(0), part_b[0, :, 24], rtol=1e-5, atol=1e-4)   # sums of squares
     assert torch.equal(a[3], b[3])                                                       # collapse + norm: same inputs
     for x, y in zip(a[:3], b[:3]):
         assert float((x - y).abs().max()) < 2e-4
