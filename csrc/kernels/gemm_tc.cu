@@ -326,7 +326,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t acc_phase = 0;
     bool ok = true;
     constexpr uint32_t kFmt = (KIND == 0) ? 1u : 0u;   // bf16 / e4m3
-    constexpr uint32_t idesc = umma_idesc(kBM, BN, kFmt, kFmt);
     for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
       int mt_unused, nt;
       const long long r = decode_tile(t, m_tiles, n_tiles, band_tiles, mt_unused, nt);
@@ -338,6 +337,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * Cfg::kAccCols;
+      // A tile of the expert table that holds fewer than BN token rows multiplies only as many columns as it has
+      // (rounded up to the instruction's granularity of 16): the last tile of an expert is mostly padding otherwise.
+      uint32_t n_mma = BN;
+      if (table) {
+        const int valid = p.tile_end[nt] - p.tile_row0[nt];
+        if (valid < BN) n_mma = static_cast<uint32_t>(max(16, (valid + 15) & ~15));
+      }
+      [[maybe_unused]] const uint32_t idesc_t = umma_idesc(kBM, n_mma, kFmt, kFmt);
       for (int kb = kb0; kb < kb1; ++kb) {
         ok = mbar_wait(&full[stage], phase, p.status, 201);
         ok = __all_sync(0xffffffffu, ok);
@@ -361,7 +368,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
             if constexpr (KIND == 2) {
               // one atom per stage; instruction k uses byte k of every 32-bit scale cell
-              const uint32_t id = umma_idesc_bs(kBM, BN, p.a_fp4 ? 5u : 0u, 0, 1, k, k);   // e2m1 = 5, e4m3 = 0
+              const uint32_t id = umma_idesc_bs(kBM, n_mma, p.a_fp4 ? 5u : 0u, 0, 1, k, k);   // e2m1 = 5, e4m3 = 0
               umma_mxf8_if(leader, d_tmem, adesc + 2 * k, bdesc + 2 * k, id, accum, sf_t, sfb_t);
               if constexpr (DUAL) {
                 const uint64_t adesc2 = umma_desc_sw128(sa + Cfg::kATile);
@@ -369,7 +376,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               }
             } else {
               // NVFP4: instruction k (64 K elements) uses atom k: four E4M3 scales per row fill one 32-bit cell
-              const uint32_t id = umma_idesc_bs(kBM, BN, 1u, 1u, 0, 0, 0);                 // e2m1 x e2m1, UE4M3 scales
+              const uint32_t id = umma_idesc_bs(kBM, n_mma, 1u, 1u, 0, 0, 0);                // e2m1 x e2m1, UE4M3 scales
               umma_nvf4_if(leader, d_tmem, adesc + 2 * k, bdesc + 2 * k, id, accum, sf_t + 4 * k, sfb_t + 4 * k);
               if constexpr (DUAL) {
                 const uint64_t adesc2 = umma_desc_sw128(sa + Cfg::kATile);
@@ -382,12 +389,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int k = 0; k < kTileKBytes / 32; ++k) {
             const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
-            if constexpr (KIND == 0) umma_bf16_if(leader, d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
-            else umma_f8_if(leader, d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
+            if constexpr (KIND == 0) umma_bf16_if(leader, d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc_t, accum);
+            else umma_f8_if(leader, d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc_t, accum);
             if constexpr (DUAL) {
               const uint64_t adesc2 = umma_desc_sw128(sa + Cfg::kATile);
-              if constexpr (KIND == 0) umma_bf16_if(leader, d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, idesc, accum);
-              else umma_f8_if(leader, d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, idesc, accum);
+              if constexpr (KIND == 0) umma_bf16_if(leader, d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, idesc_t, accum);
+              else umma_f8_if(leader, d_tmem + Cfg::kAccCols / 2, adesc2 + 2 * k, bdesc + 2 * k, idesc_t, accum);
             }
           }
         }
@@ -440,8 +447,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       constexpr int kChunk = BN >= 32 ? 32 : BN;
       float alpha = p.alpha;
       if (KIND == 3 && p.alpha_batch != nullptr) alpha *= __ldg(p.alpha_batch + (p.batch_map != nullptr ? p.batch_map[b] : b));
+      // columns the tensor cores wrote for this tile (see n_mma in the issuer), in whole chunks
+      const int n_cols = (table && p.out_mode != 6) ? min(BN, (max(n_lim - n_base, 0) + kChunk - 1) / kChunk * kChunk) : BN;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += kChunk) {
+      for (int c = 0; c < n_cols; c += kChunk) {
         uint32_t v[32];
         if constexpr (kChunk == 32) {
           tmem_ld_32x32(t_row + c, v);
