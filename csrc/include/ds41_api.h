@@ -104,7 +104,8 @@ int ds41_embed_streams(const int* tokens, const void* embed, void* streams, floa
 int ds41_hc_post_mix(const void* streams_in, void* streams_out, const float* const* part_bases, int n_ranks,
                      int n_splits, long long split_stride, const float* post, const float* comb, const float* fn,
                      float* partial, int rows, int H, const uint32_t* const* wait_flags, const uint32_t* wait_epoch,
-                     int* status, void* stream);
+                     int* status, const float* pre_in, const float* norm_w, void* xn, float* tap_mean, float norm_eps,
+                     void* stream);
 int ds41_hc_finish(const float* partial, int n_slices, const float* scale, const float* base, const float* pre_in,
                    const void* streams, const float* norm_w, float* next_pre, float* post, float* comb, void* xn,
                    float* tap_mean, void* xq, void* xq_sf, int rows, int H, int iters, float hc_eps, float norm_eps,
@@ -113,7 +114,9 @@ int ds41_hc_finish(const float* partial, int n_slices, const float* scale, const
 // single slice: hc_finish is then called with n_slices = 1); the 24 mixes
 // projections then come from a GEMM of the stored streams [rows, 4H] with the matrix as bf16 high and low parts
 // (columns j and 24 + j of fp32 split-K planes [mix_splits][rows][mix_ld]), which hc_finish reads as `mix_planes`
-// (NULL: the projections are in `partial`).
+// (NULL: the projections are in `partial`).  In that form hc_post_mix can also collapse and normalise the row it holds
+// (xn != NULL with pre_in, optional norm_w / tap_mean): hc_finish is then called with xn == NULL and only turns the
+// projections into next_pre / post / comb.
 
 // Fused small-batch step (hc_step.cu): expand with the sublayer's partial planes, next mixes, collapse with the
 // known `pre_in`, RMSNorm (+ optional E4M3/scale-atom output) in one launch.  part_bases: HOST array of device

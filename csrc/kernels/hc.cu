@@ -210,12 +210,23 @@ hc_post_mix_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, 
 // 4 + 16 mixing coefficients in registers, and leaves the sum of squares of the new streams in
 // partial[row * kHcPartialStride + kHcProj] (one slice).  parts.n_ranks == 0: the streams stay as they are and only the
 // sum of squares is produced.
+// With `xn` the block also collapses the new streams with the incoming weights `pre_in` and normalises the row
+// (what hc_finish does from a second read of the streams): x = sum_s pre_in[s] * streams'[s], xn = x * rsqrt(mean x^2 +
+// eps) * norm_w, and the drafter's tap mean if asked for.  The collapsed values of a thread's groups stay in registers
+// across the block-wide sum (H <= 6144).
 __global__ void __launch_bounds__(256)
 hc_expand_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, PartList parts,
                  const float* __restrict__ post, const float* __restrict__ comb, float* __restrict__ partial, int rows,
                  int H, const uint32_t* const* __restrict__ wait_flags, const uint32_t* __restrict__ wait_epoch,
-                 int* status) {
+                 int* status, const float* __restrict__ pre_in, const float* __restrict__ norm_w,
+                 __nv_bfloat16* __restrict__ xn, float* __restrict__ tap_mean, float norm_eps) {
   __shared__ float warp_sq[8];
+  __shared__ float warp_xsq[8];
+  __shared__ float inv_rms;
+  constexpr int kMaxItems = 3;
+  float keep[kMaxItems][8];
+  float x_sq = 0.f;
+  float p_in[kHcMaxMult] = {0.f, 0.f, 0.f, 0.f};
   const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   pdl_launch_dependents();
   pdl_wait();
@@ -231,9 +242,16 @@ hc_expand_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, Pa
 #pragma unroll
     for (int q = 0; q < 4; ++q) pw[q] = post[r * 4 + q];
   }
+  if (xn != nullptr) {
+#pragma unroll
+    for (int q = 0; q < kHcMaxMult; ++q) p_in[q] = pre_in[r * 4 + q];
+  }
   const int n_sp = parts.n_splits, total = parts.n_ranks * n_sp;
   float sq = 0.f;
-  for (int g = tid; g < H / 8; g += 256) {
+#pragma unroll
+  for (int n = 0; n < kMaxItems; ++n) {
+    const int g = tid + 256 * n;
+    if (g >= H / 8) continue;
     const int c = g * 8;
     uint4 raw[kHcMaxMult];
 #pragma unroll
@@ -250,13 +268,16 @@ hc_expand_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, Pa
         s_in[s][2 * q + 1] = v.y;
       }
     }
+    float out[kHcMaxMult][8];
     if (!expand) {
 #pragma unroll
       for (int s = 0; s < kHcMaxMult; ++s)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) sq = fmaf(s_in[s][j], s_in[s][j], sq);
-      continue;
-    }
+        for (int j = 0; j < 8; ++j) {
+          out[s][j] = s_in[s][j];
+          sq = fmaf(s_in[s][j], s_in[s][j], sq);
+        }
+    } else {
     float sub[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     // rank-major, split-minor order; four planes (eight 16-byte loads) in flight before the first add
     for (int j0 = 0; j0 < total; j0 += 4) {
@@ -278,7 +299,6 @@ hc_expand_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, Pa
         sub[4] += v[u][1].x; sub[5] += v[u][1].y; sub[6] += v[u][1].z; sub[7] += v[u][1].w;
       }
     }
-    float out[kHcMaxMult][8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float sb = bf16_round(sub[j]);
@@ -299,15 +319,55 @@ hc_expand_kernel(const __nv_bfloat16* streams_in, __nv_bfloat16* streams_out, Pa
       for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(out[d][2 * q], out[d][2 * q + 1]);
       *reinterpret_cast<uint4*>(streams_out + (1ll * r * kHcMaxMult + d) * H + c) = w;
     }
+    }   // expand
+    if (xn != nullptr) {
+      // same arithmetic and summation order as hc_finish, so that both forms give identical rows
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float x = bf16_round(fmaf(p_in[3], out[3][2 * q], fmaf(p_in[2], out[2][2 * q],
+                                   fmaf(p_in[1], out[1][2 * q], p_in[0] * out[0][2 * q]))));
+        const float y = bf16_round(fmaf(p_in[3], out[3][2 * q + 1], fmaf(p_in[2], out[2][2 * q + 1],
+                                   fmaf(p_in[1], out[1][2 * q + 1], p_in[0] * out[0][2 * q + 1]))));
+        keep[n][2 * q] = x;
+        keep[n][2 * q + 1] = y;
+        x_sq = fmaf(x, x, fmaf(y, y, x_sq));
+      }
+      if (tap_mean != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          tap_mean[1ll * r * H + c + j] = 0.25f * (out[0][j] + out[1][j] + out[2][j] + out[3][j]);
+      }
+    }
   }
   sq = warp_sum(sq);
-  if (lane == 0) warp_sq[warp] = sq;
+  x_sq = warp_sum(x_sq);
+  if (lane == 0) {
+    warp_sq[warp] = sq;
+    warp_xsq[warp] = x_sq;
+  }
   __syncthreads();
   if (tid == 0) {
-    float t = 0.f;
+    float t = 0.f, u = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) t += warp_sq[w];
+    for (int w = 0; w < 8; ++w) { t += warp_sq[w]; u += warp_xsq[w]; }
     partial[1ll * r * kHcPartialStride + kHcProj] = t;
+    inv_rms = rsqrtf(u / H + norm_eps);
+  }
+  if (xn == nullptr) return;
+  __syncthreads();
+  const float inv = inv_rms;
+#pragma unroll
+  for (int n = 0; n < kMaxItems; ++n) {
+    const int g = tid + 256 * n;
+    if (g >= H / 8) continue;
+    float y[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) y[q] = bf16_round(keep[n][q] * inv * (norm_w != nullptr ? norm_w[8 * g + q] : 1.f));
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(y[2 * q], y[2 * q + 1]);
+    *reinterpret_cast<uint4*>(xn + 1ll * r * H + 8 * g) = o;
   }
 }
 
@@ -374,6 +434,7 @@ hc_finish_kernel(const float* __restrict__ partial, int n_slices, const float* _
     }
     if (lane < 16) comb[r * 16 + lane] = v;
   }
+  if (xn == nullptr) return;        // the expand kernel already collapsed and normalised the row
   // ---- collapse with the incoming pre + RMSNorm; each thread owns up to 3 groups of 8 columns
   const float p0 = pre_in[r * 4 + 0], p1 = pre_in[r * 4 + 1], p2 = pre_in[r * 4 + 2], p3 = pre_in[r * 4 + 3];
   const __nv_bfloat16* s0 = streams + 1ll * r * 4 * H;
@@ -468,6 +529,57 @@ hc_finish_kernel(const float* __restrict__ partial, int n_slices, const float* _
   }
 }
 
+// Coefficients alone, one warp per row: the 24 projections come from the GEMM's split-K planes (high + low part per
+// split, splits in order), the sum of squares from the expand kernel; the rest is hc_finish's first phase.
+__global__ void __launch_bounds__(256)
+hc_mixes_kernel(const float* __restrict__ partial, const float* __restrict__ scale, const float* __restrict__ base,
+                float* __restrict__ next_pre, float* __restrict__ post, float* __restrict__ comb, int rows, int H,
+                int iters, float hc_eps, float norm_eps, const float* __restrict__ mix_planes, int mix_splits,
+                long long mix_split_stride, int mix_ld) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  float acc = 0.f;
+  if (lane < kHcProj) {
+    for (int s = 0; s < mix_splits; ++s) {
+      const float* p = mix_planes + s * mix_split_stride + 1ll * r * mix_ld;
+      acc += p[lane] + p[kHcProj + lane];
+    }
+  }
+  const float inv = rsqrtf(partial[1ll * r * kHcPartialStride + kHcProj] / (4.0f * H) + norm_eps);
+  const float proj = acc * inv;
+  const float p_post = __shfl_sync(0xffffffffu, proj, (lane + 4) & 31);
+  const float p_comb = __shfl_sync(0xffffffffu, proj, (lane + 8) & 31);
+  if (lane < 4) {
+    const float a = fmaf(proj, scale[0], base[lane]);
+    const float b = fmaf(p_post, scale[1], base[lane + 4]);
+    next_pre[r * 4 + lane] = 1.0f / (1.0f + __expf(-a)) + hc_eps;
+    post[r * 4 + lane] = 2.0f / (1.0f + __expf(-b));
+  }
+  // comb: lane = s*4 + d for lanes < 16
+  float v = lane < 16 ? fmaf(p_comb, scale[2], base[8 + lane]) : 0.f;
+  float mx = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+  v = __expf(v - mx);
+  float sum = v + __shfl_xor_sync(0xffffffffu, v, 1);
+  sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+  v = v / sum + hc_eps;
+  sum = v + __shfl_xor_sync(0xffffffffu, v, 4);
+  sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+  v /= sum + hc_eps;
+  for (int it = 1; it < iters; ++it) {
+    sum = v + __shfl_xor_sync(0xffffffffu, v, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    v /= sum + hc_eps;
+    sum = v + __shfl_xor_sync(0xffffffffu, v, 4);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+    v /= sum + hc_eps;
+  }
+  if (lane < 16) comb[r * 16 + lane] = v;
+}
+
 }  // namespace ds41
 
 using namespace ds41;
@@ -483,8 +595,11 @@ extern "C" int ds41_embed_streams(const int* tokens, const void* embed, void* st
 extern "C" int ds41_hc_post_mix(const void* streams_in, void* streams_out, const float* const* part_bases,
                                 int n_ranks, int n_splits, long long split_stride, const float* post,
                                 const float* comb, const float* fn, float* partial, int rows, int H,
-                                const uint32_t* const* wait_flags, const uint32_t* wait_epoch, int* status, void* stream) {
+                                const uint32_t* const* wait_flags, const uint32_t* wait_epoch, int* status,
+                                const float* pre_in, const float* norm_w, void* xn, float* tap_mean, float norm_eps,
+                                void* stream) {
   if (rows <= 0 || H % kHcSlice != 0 || n_ranks < 0 || n_ranks > 8) return cudaErrorInvalidValue;
+  if (xn != nullptr && (fn != nullptr || pre_in == nullptr || H > 256 * 3 * 8)) return cudaErrorInvalidValue;
   PartList parts{};
   parts.n_ranks = n_ranks;
   parts.n_splits = n_splits;
@@ -497,7 +612,8 @@ extern "C" int ds41_hc_post_mix(const void* streams_in, void* streams_out, const
   if (fn == nullptr)      // expand only; the sum of squares of row r lands in partial[r * 25 + 24] (one slice)
     return launch_pdl(hc_expand_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream),
                       static_cast<const __nv_bfloat16*>(streams_in), static_cast<__nv_bfloat16*>(streams_out), parts,
-                      post, comb, partial, rows, H, wait_flags, wait_epoch, status);
+                      post, comb, partial, rows, H, wait_flags, wait_epoch, status, pre_in, norm_w,
+                      static_cast<__nv_bfloat16*>(xn), tap_mean, norm_eps);
   constexpr size_t kSmem = sizeof(float) * (kHcRowsPerBlock * kHcMaxMult * kHcSlice + kHcProj * kHcMaxMult * kHcSlice);
   static std::atomic<bool> configured[64];
   int dev = 0;
@@ -522,6 +638,10 @@ extern "C" int ds41_hc_finish(const float* partial, int n_slices, const float* s
   if (rows <= 0 || H % 8 != 0 || H > 256 * 3 * 8 || (xq != nullptr && (H % 128 != 0 || xq_sf == nullptr)) ||
       (mix_planes != nullptr && (mix_splits <= 0 || mix_ld < 2 * kHcProj)))
     return cudaErrorInvalidValue;
+  if (xn == nullptr && mix_planes != nullptr)           // coefficients only: one warp per row
+    return launch_pdl(hc_mixes_kernel, dim3((rows + 7) / 8), dim3(256), 0, static_cast<cudaStream_t>(stream), partial,
+                      scale, base, next_pre, post, comb, rows, H, iters, hc_eps, norm_eps, mix_planes, mix_splits,
+                      mix_split_stride, mix_ld);
   return launch_pdl(hc_finish_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), partial, n_slices,
                     scale, base, pre_in, static_cast<const __nv_bfloat16*>(streams), norm_w, next_pre, post, comb,
                     static_cast<__nv_bfloat16*>(xn), tap_mean, static_cast<uint8_t*>(xq),

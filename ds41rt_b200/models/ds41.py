@@ -974,28 +974,42 @@ class DS41Engine:
         assert st[1] == rows
         return 1, (lib.ptr(self.mix_planes), st[0], C.c_longlong(rows * 64), 64)
 
-    def _post_mix(self, rows, part_bases, n_ranks, n_splits, split_stride, fn, sync, coef=None):
+    def _mix_tc(self, rows: int) -> bool:
+        """Long passes (whose routed experts take bf16 rows through the all-to-all, so nothing reads the quantised rows
+        of the fused step) run the mixes projection on the tensor cores and collapse inside the expand kernel."""
+        return self.mix_planes is not None and rows >= self.mix_tc_rows and rows > self.moe_rows
+
+    def _post_mix(self, rows, part_bases, n_ranks, n_splits, split_stride, fn, sync, coef=None, collapse=None):
+        """`collapse` = (pre_in, norm_w, tap) asks the tensor-core form to collapse and normalise the rows into self.xn
+        in the same launch (hc_finish then only turns the projections into the next coefficients)."""
         k, st = self.k, lib.stream()
         post, comb = coef if coef is not None else (self.post, self.comb)
         wait_flags = lib.ptr(self.flag_ptrs) if (sync and self.world > 1) else lib.ptr(None)
-        tc = self.mix_planes is not None and rows >= self.mix_tc_rows
+        tc = self._mix_tc(rows)
+        if tc and collapse is not None:
+            extra = (lib.ptr(collapse[0]), lib.ptr(collapse[1]), lib.ptr(self.xn), lib.ptr(collapse[2]),
+                     C.c_float(self.cfg.norm_eps))
+        else:
+            extra = (lib.ptr(None), lib.ptr(None), lib.ptr(None), lib.ptr(None), C.c_float(0.0))
         self._run("hc_post_mix", k.ds41_hc_post_mix, 
             lib.ptr(self.streams), lib.ptr(self.streams), part_bases, n_ranks, n_splits, C.c_longlong(split_stride),
             lib.ptr(post), lib.ptr(comb), lib.ptr(None if tc else fn), lib.ptr(self.hc_partial), rows, self.cfg.hidden,
-            wait_flags, lib.ptr(self.epoch), lib.ptr(self.status), st)
+            wait_flags, lib.ptr(self.epoch), lib.ptr(self.status), *extra, st)
         if tc:
             self._mix_gemm(self.streams, rows, fn)
 
-    def _finish(self, rows, scale, base, pre_in, norm_w, next_pre, tap=None, quant=False, coef=None):
+    def _finish(self, rows, scale, base, pre_in, norm_w, next_pre, tap=None, quant=False, coef=None, collapsed=False):
+        """`collapsed`: self.xn (and the tap) were written by the expand kernel already."""
         cfg = self.cfg
         post, comb = coef if coef is not None else (self.post, self.comb)
         n_slices, mix = self._mix_args(rows)
+        quant = quant and not collapsed
         self._run("hc_finish", self.k.ds41_hc_finish, 
             lib.ptr(self.hc_partial), n_slices, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
             lib.ptr(self.streams), lib.ptr(norm_w), lib.ptr(next_pre), lib.ptr(post), lib.ptr(comb),
-            lib.ptr(self.xn), lib.ptr(tap), lib.ptr(self.xq if quant else None),
-            lib.ptr(self.xq_sf if quant else None), rows, cfg.hidden, cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps),
-            C.c_float(cfg.norm_eps), *mix, lib.stream())
+            lib.ptr(None if collapsed else self.xn), lib.ptr(None if collapsed else tap),
+            lib.ptr(self.xq if quant else None), lib.ptr(self.xq_sf if quant else None), rows, cfg.hidden,
+            cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps), C.c_float(cfg.norm_eps), *mix, lib.stream())
 
     def _step(self, rows, part_bases, n_ranks, n_splits, split_stride, coef_in, pre_in, fn, scale, base, norm_w,
               next_pre, coef_out, tap=None, quant=False, sync=False):
@@ -1042,8 +1056,11 @@ class DS41Engine:
                 ev = torch.cuda.Event()
                 ev.record()
                 self._engram_copied[self._engram_layer_of[id(module)]] = ev
-            self._post_mix(rows, None, 0, 0, 0, fn, sync=False, coef=cin)
-            self._finish(rows, scale, base, self.pre[cur], norm_w, self.pre[cur ^ 1], tap, quant, coef=cout)
+            fuse = self._mix_tc(rows)
+            self._post_mix(rows, None, 0, 0, 0, fn, sync=False, coef=cin,
+                           collapse=(self.pre[cur], norm_w, tap) if fuse else None)
+            self._finish(rows, scale, base, self.pre[cur], norm_w, self.pre[cur ^ 1], tap, quant, coef=cout,
+                         collapsed=fuse)
             if small:
                 self._ccur ^= 1
         elif rows <= self.fused_rows:
@@ -1052,8 +1069,10 @@ class DS41Engine:
                        self.pre[cur ^ 1], self.coef[cc ^ 1], tap=tap, quant=quant, sync=pending is not None)
             self._ccur = cc ^ 1
         else:
-            self._post_mix(rows, bases, n_ranks, n_splits, stride, fn, sync=pending is not None)
-            self._finish(rows, scale, base, self.pre[cur], norm_w, self.pre[cur ^ 1], tap, quant)
+            fuse = self._mix_tc(rows)
+            self._post_mix(rows, bases, n_ranks, n_splits, stride, fn, sync=pending is not None,
+                           collapse=(self.pre[cur], norm_w, tap) if fuse else None)
+            self._finish(rows, scale, base, self.pre[cur], norm_w, self.pre[cur ^ 1], tap, quant, collapsed=fuse)
         self._cur = cur ^ 1
 
     def _qkv(self, l: int, lw: LayerWeights, R: int, inv, sources: bool = True):
@@ -1358,19 +1377,23 @@ class DS41Engine:
         bases, n_splits, stride = pending if pending is not None else (None, 0, 0)
         ptrs = (C.c_void_p * 1)(bases) if bases is not None else None
         streams = self.streams[lo:]
-        tc = self.mix_planes is not None and Rl >= self.mix_tc_rows
+        tc = self._mix_tc(Rl)
+        tap_lo = tap[lo:] if tap is not None else None
+        extra = (lib.ptr(self.pre[cur][lo:]), lib.ptr(norm_w), lib.ptr(xn_out), lib.ptr(tap_lo),
+                 C.c_float(cfg.norm_eps)) if tc else \
+            (lib.ptr(None), lib.ptr(None), lib.ptr(None), lib.ptr(None), C.c_float(0.0))
         self._run("hc_post_mix", self.k.ds41_hc_post_mix, lib.ptr(streams), lib.ptr(streams), ptrs,
                   1 if bases is not None else 0, n_splits, C.c_longlong(stride), lib.ptr(self.post[lo:]),
                   lib.ptr(self.comb[lo:]), lib.ptr(None if tc else fn), lib.ptr(self.hc_partial), Rl, cfg.hidden,
-                  lib.ptr(None), lib.ptr(self.epoch), lib.ptr(self.status), lib.stream())
+                  lib.ptr(None), lib.ptr(self.epoch), lib.ptr(self.status), *extra, lib.stream())
         if tc:
             self._mix_gemm(streams, Rl, fn)
         n_slices, mix = self._mix_args(Rl)
         self._run("hc_finish", self.k.ds41_hc_finish, lib.ptr(self.hc_partial), n_slices, lib.ptr(scale),
                   lib.ptr(base), lib.ptr(self.pre[cur][lo:]), lib.ptr(streams), lib.ptr(norm_w),
-                  lib.ptr(self.pre[cur ^ 1][lo:]), lib.ptr(self.post[lo:]), lib.ptr(self.comb[lo:]), lib.ptr(xn_out),
-                  lib.ptr(tap[lo:] if tap is not None else None), lib.ptr(None), lib.ptr(None), Rl, cfg.hidden,
-                  cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps), C.c_float(cfg.norm_eps), *mix, lib.stream())
+                  lib.ptr(self.pre[cur ^ 1][lo:]), lib.ptr(self.post[lo:]), lib.ptr(self.comb[lo:]),
+                  lib.ptr(None if tc else xn_out), lib.ptr(None if tc else tap_lo), lib.ptr(None), lib.ptr(None), Rl,
+                  cfg.hidden, cfg.hc_sinkhorn_iters, C.c_float(cfg.hc_eps), C.c_float(cfg.norm_eps), *mix, lib.stream())
         self._cur = cur ^ 1
 
     def _sp_qkv(self, l, lw, R, Rl, inv, sources, ctx):

@@ -237,7 +237,8 @@ def hc_case(rows: int, H: int = 5120):
         def run():
             lib.check(k.ds41_hc_post_mix(lib.ptr(streams), lib.ptr(out_streams), bases, 1, 1, C.c_longlong(rows * H),
                                          lib.ptr(post), lib.ptr(comb), lib.ptr(fn), lib.ptr(partial), rows, H,
-                                         lib.ptr(None), lib.ptr(None), lib.ptr(st), lib.stream()), "hc_post_mix")
+                                         lib.ptr(None), lib.ptr(None), lib.ptr(st), lib.ptr(None), lib.ptr(None), lib.ptr(None), lib.ptr(None), C.c_float(0.0), lib.stream()),
+                      "hc_post_mix")
             lib.check(k.ds41_hc_finish(lib.ptr(partial), H // 128, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
                                        lib.ptr(out_streams), lib.ptr(norm_w), lib.ptr(next_pre), lib.ptr(post2),
                                        lib.ptr(comb2), lib.ptr(xn), lib.ptr(None), lib.ptr(None), lib.ptr(None), rows, H,

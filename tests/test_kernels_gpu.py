@@ -166,7 +166,7 @@ def test_hc_kernels_match_oracle():
     post_d, comb_d = post0.cuda().contiguous(), comb0.reshape(rows, 16).cuda().contiguous()
     lib.check(k.ds41_hc_post_mix(lib.ptr(s_dev), lib.ptr(s_dev), bases, 1, 2, C.c_longlong(rows * H), lib.ptr(post_d),
                                  lib.ptr(comb_d), lib.ptr(fn), lib.ptr(partial), rows, H, lib.ptr(None), lib.ptr(None),
-                                 lib.ptr(st), lib.stream()), "post_mix")
+                                 lib.ptr(st), lib.ptr(None), lib.ptr(None), lib.ptr(None), lib.ptr(None), C.c_float(0.0), lib.stream()), "post_mix")
     next_pre = torch.zeros(rows, 4, device="cuda")
     post = torch.zeros(rows, 4, device="cuda")
     comb = torch.zeros(rows, 16, device="cuda")
@@ -273,7 +273,7 @@ def test_hc_step_matches_unfused_kernels():
     partial = torch.zeros(H // 128, rows, 25, device="cuda")
     lib.check(k.ds41_hc_post_mix(lib.ptr(s1), lib.ptr(s1), bases, 1, 2, C.c_longlong(rows * H), lib.ptr(post),
                                  lib.ptr(comb), lib.ptr(fn), lib.ptr(partial), rows, H, lib.ptr(None), lib.ptr(None),
-                                 lib.ptr(st), lib.stream()), "post_mix")
+                                 lib.ptr(st), lib.ptr(None), lib.ptr(None), lib.ptr(None), lib.ptr(None), C.c_float(0.0), lib.stream()), "post_mix")
     np1, po1, co1 = torch.zeros(rows, 4, device="cuda"), torch.zeros(rows, 4, device="cuda"), torch.zeros(rows, 16, device="cuda")
     xn1 = torch.zeros(rows, H, device="cuda", dtype=torch.bfloat16)
     lib.check(k.ds41_hc_finish(lib.ptr(partial), H // 128, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
@@ -522,12 +522,17 @@ def test_hc_mixes_on_the_tensor_cores_match_the_dot_product_kernel(rows, H):
     st = lib.new_status("cuda")
     bases = (C.c_void_p * 1)(sub.data_ptr())
 
-    def run(tc):
+    def run(tc, fused=False):
         s = streams.clone()
         partial = torch.zeros(H // 128, rows, 25, device="cuda")
+        outs = [torch.zeros(rows, 4, device="cuda"), torch.zeros(rows, 4, device="cuda"),
+                torch.zeros(rows, 16, device="cuda"), torch.zeros(rows, H, device="cuda", dtype=torch.bfloat16)]
+        tap = torch.zeros(rows, H, device="cuda")
+        collapse = (lib.ptr(pre_in), lib.ptr(norm_w), lib.ptr(outs[3]), lib.ptr(tap), C.c_float(1e-20)) if fused else \
+            (lib.ptr(None), lib.ptr(None), lib.ptr(None), lib.ptr(None), C.c_float(0.0))
         lib.check(k.ds41_hc_post_mix(lib.ptr(s), lib.ptr(s), bases, 1, 2, C.c_longlong(rows * H), lib.ptr(post),
                                      lib.ptr(comb), lib.ptr(None if tc else fn), lib.ptr(partial), rows, H,
-                                     lib.ptr(None), lib.ptr(None), lib.ptr(st), lib.stream()), "post_mix")
+                                     lib.ptr(None), lib.ptr(None), lib.ptr(st), *collapse, lib.stream()), "post_mix")
         mix = (lib.ptr(None), 0, C.c_longlong(0), 0)
         keep = None
         if tc:
@@ -541,19 +546,22 @@ def test_hc_mixes_on_the_tensor_cores_match_the_dot_product_kernel(rows, H):
                        split_workspace=planes, bn=64, status=st, static_operand=2)
             mix = (lib.ptr(planes), splits, C.c_longlong(rows * 64), 64)
             keep = (w, planes)
-        outs = [torch.zeros(rows, 4, device="cuda"), torch.zeros(rows, 4, device="cuda"),
-                torch.zeros(rows, 16, device="cuda"), torch.zeros(rows, H, device="cuda", dtype=torch.bfloat16)]
         lib.check(k.ds41_hc_finish(lib.ptr(partial), 1 if tc else H // 128, lib.ptr(scale), lib.ptr(base), lib.ptr(pre_in),
                                    lib.ptr(s), lib.ptr(norm_w), lib.ptr(outs[0]), lib.ptr(outs[1]), lib.ptr(outs[2]),
-                                   lib.ptr(outs[3]), lib.ptr(None), lib.ptr(None), lib.ptr(None), rows, H, 20,
-                                   C.c_float(1e-6), C.c_float(1e-20), *mix, lib.stream()), "finish")
+                                   lib.ptr(None if fused else outs[3]), lib.ptr(None if fused else tap), lib.ptr(None),
+                                   lib.ptr(None), rows, H, 20, C.c_float(1e-6), C.c_float(1e-20), *mix, lib.stream()),
+                  "finish")
         torch.cuda.synchronize()
         lib.raise_on_status(st, "hc mixes")
-        return s, outs, partial, keep
+        return s, outs + [tap], partial, keep
 
     s_a, a, part_a, _ = run(False)
     s_b, b, part_b, _ = run(True)
-    assert torch.equal(s_a, s_b)
+    s_c, c, part_c, _ = run(True, fused=True)       # expand kernel also collapses and normalises; finish: mixes only
+    assert torch.equal(s_a, s_b) and torch.equal(s_b, s_c)
+    assert torch.equal(b[3], c[3]) and torch.equal(b[4], c[4]) and torch.equal(part_b[0, :, 24], part_c[0, :, 24])
+    for x, y in zip(b[:3], c[:3]):
+        assert float((x - y).abs().max()) < 1e-5          # the split-K planes are summed in another order
     assert torch.allclose(part_a[:, :, 24].sum(0), part_b[0, :, 24], rtol=1e-5, atol=1e-4)   # sums of squares
     assert torch.equal(a[3], b[3])                                                       # collapse + norm: same inputs
     for x, y in zip(a[:3], b[:3]):
