@@ -78,7 +78,7 @@ class DSparkDrafter:
         self.taps_bf16 = z((R, n_taps * H), BF16)
         self.main_splits = G.pick_splits(H, n_taps * H, max_splits=16)
         self.main_planes = z((16, R, H), F32)
-        self.n_blocks = 296
+        self.n_blocks = 444          # three resident blocks per SM (markov_step is sized for it)
         self.block_val = z((self.n_blocks,), F32)
         self.block_idx = z((self.n_blocks,), I32)
         self.ticket = z((1,), I32)
