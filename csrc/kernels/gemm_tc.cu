@@ -785,6 +785,9 @@ static cudaError_t dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap
       case 128:
         if constexpr (KIND < 3) return launch_gemm<128, KIND, 1>(tmA, tmB, peer, p, grid, stream);
         return cudaErrorInvalidValue;
+      case 192:      // expert tiles of the block-scaled FP8 kind: one tile holds a whole expert of a typical pass
+        if constexpr (KIND == 2) return launch_gemm<192, KIND, 1>(tmA, tmB, peer, p, grid, stream);
+        return cudaErrorInvalidValue;
       default: return cudaErrorInvalidValue;
     }
   }
@@ -793,6 +796,9 @@ static cudaError_t dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap
     case 32: return launch_gemm<32, KIND>(tmA, tmB, peer, p, grid, stream);
     case 64: return launch_gemm<64, KIND>(tmA, tmB, peer, p, grid, stream);
     case 128: return launch_gemm<128, KIND>(tmA, tmB, peer, p, grid, stream);
+    case 192:
+      if constexpr (KIND == 2) return launch_gemm<192, KIND>(tmA, tmB, peer, p, grid, stream);
+      return cudaErrorInvalidValue;
     case 256:
       if constexpr (KIND < 2) return launch_gemm<256, KIND>(tmA, tmB, peer, p, grid, stream);
       return cudaErrorInvalidValue;

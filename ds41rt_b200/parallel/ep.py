@@ -35,7 +35,7 @@ class ExpertParallelMoE:
                  act_limit: float = 10.0, capacity: Optional[int] = None, w13_sf: Optional[torch.Tensor] = None,
                  w2_sf: Optional[torch.Tensor] = None, fp4: bool = False, nvfp4=None,
                  w13_gs: Optional[torch.Tensor] = None, w2_gs: Optional[torch.Tensor] = None,
-                 wire: str = "auto"):
+                 wire: str = "auto", tile_tokens: Optional[int] = None):
         """w13: [E_local, 2*I, H] (gate rows then up rows), w2: [E_local, H, I]; bf16, or e4m3 with UE8M0 scale atoms,
         or (fp4) E2M1 codes two per byte ([.., H/2] / [.., I/2] uint8) with UE8M0 scale atoms, or (nvfp4 = the two
         activation scales) E2M1 codes with E4M3 scale atoms per 16 and one global scale per expert (w13_gs / w2_gs):
@@ -66,6 +66,13 @@ class ExpertParallelMoE:
         # is what bounds it); NVFP4 carries four times the scale columns and stays at 64
         self.bn = 128 if (not scaled or self.mx) else 64
         self.bn2 = 128 if scaled else 256          # FC2
+        # `tile_tokens` overrides both for the block-scaled FP8 kind (128 or 192).  With hundreds of experts a pass gives
+        # each about 128 rows: 128-token tiles then leave every second expert with a nearly empty second tile that still
+        # streams the expert's weights, while a 192-token tile holds the whole expert and multiplies only the columns
+        # it has
+        if tile_tokens is not None and self.mx and not self.fp4:
+            assert tile_tokens in (128, 192)
+            self.bn = self.bn2 = tile_tokens
         worst = W * max_tokens * topk
         self.cap = _round_up(min(worst, capacity) if capacity else worst, 128) + 128 * self.e_local
         self.max_tiles = self.cap // self.bn + self.e_local

@@ -53,7 +53,8 @@ def main():
         from ds41rt_b200.models.ds41 import dequantize_expert, quantize_expert_stack
         q13, s13 = quantize_expert_stack(w13.cpu(), dev)
         q2, s2 = quantize_expert_stack(w2.cpu(), dev)
-        moe = ExpertParallelMoE(f, q13, q2, topk=topk, max_tokens=T, w13_sf=s13, w2_sf=s2, wire=wire)
+        moe = ExpertParallelMoE(f, q13, q2, topk=topk, max_tokens=T, w13_sf=s13, w2_sf=s2, wire=wire,
+                                tile_tokens=int(os.environ["EP_TILE"]) if os.environ.get("EP_TILE") else None)
         w13_ref = torch.stack([dequantize_expert(q13[e], s13[e]) for e in range(EL)]).to(dev).bfloat16()
         w2_ref = torch.stack([dequantize_expert(q2[e], s2[e]) for e in range(EL)]).to(dev).bfloat16()
     else:

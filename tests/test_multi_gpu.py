@@ -56,6 +56,10 @@ def test_grouped_experts_one_rank(mx):
     if mx == "1":
         _run_ep(1, 0, EP_TOKENS="384", EP_H="512", EP_I="256", EP_E="8", EP_TOPK="4", EP_REPS="2", EP_MX=mx,
                 EP_WIRE="bf16")
+        # 192-token expert tiles: block-scaled MMAs of N = 192 (and narrower ones for partly filled tiles) whose token
+        # scales span two scale atoms
+        _run_ep(1, 0, EP_TOKENS="1000", EP_H="1024", EP_I="512", EP_E="16", EP_TOPK="6", EP_REPS="2", EP_MX=mx,
+                EP_TILE="192")
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
