@@ -900,9 +900,16 @@ class DS41Engine:
         self.row_slot.copy_(s, non_blocking=True)
         # what the host knows about the pass it just described (used by the next forward_rows only): a long pass over
         # one request lets the indexer run as a tensor-core GEMM over that request's keys
+        # A decode-sized pass over one request (a speculative verification, a lone request's step) scores on the tensor
+        # cores too; its launches may be replayed from a graph while the context grows, so the key count is the static
+        # bound (-1) and the visible count per row is worked out on the device.
         slot_list = list(slots)
-        one = n > self.moe_rows and len(set(slot_list)) == 1 and slot_list[0] >= 0
-        self._pass_hint = (n, int(max(positions)) if n else 0) if one else None
+        one = n > 0 and len(set(slot_list)) == 1 and slot_list[0] >= 0
+        self._pass_hint = None
+        if one and n > self.moe_rows:
+            self._pass_hint = (n, int(max(positions)))
+        elif one and getattr(self, "idx_q", None) is not None and self.max_keys <= 32768:
+            self._pass_hint = (n, -1)
         if self.row_hi is not None:
             h = torch.tensor(list(row_hi if row_hi is not None else positions) + [0] * pad, dtype=I32)
             self.row_hi.copy_(h, non_blocking=True)
@@ -1154,7 +1161,12 @@ class DS41Engine:
                 cand = (lib.ptr(self.cand_mask), self.cand_words, cfg.candidate_block) if restrict \
                     else (lib.ptr(None), 0, 0)
                 hint = self._pass_hint
-                n_keys = min((hint[1] + 1) // ratio, self.max_keys) if hint is not None and hint[0] == R else 0
+                n_keys = 0
+                if hint is not None and hint[0] == R:
+                    # static bound: every key row the slot's page table can address (rows of pages that are not
+                    # leased read as zeros and lie beyond every row's visible count)
+                    n_keys = min((self.max_keys + ratio - 1) // ratio, self.cache.max_pages * self.cache.page_rows[src],
+                                 self.max_keys) if hint[1] < 0 else min((hint[1] + 1) // ratio, self.max_keys)
                 if n_keys >= 64 and cfg.index_heads == 32 and cfg.index_dim % 64 == 0:
                     self._run("index_prepare", k.ds41_index_prepare, lib.ptr(self.qb_out), C.c_longlong(self.nqb),
                               self.HL * D, lib.ptr(self.cache.idx[src]), lib.ptr(self.cache.page_table),
@@ -1313,7 +1325,9 @@ class DS41Engine:
                 # they stand plus the pending expert plane of this rank
                 self.activation_trace.dump(l, self.streams, self.row_pos, R)
         self._pending = pending
-        self._pass_hint = None
+        if self._pass_hint is not None and self._pass_hint[1] >= 0:
+            self._pass_hint = None        # a long pass's key count holds for that pass only; the static form stays until
+                                          # the rows are described again (device-fed steps keep their slot)
         if head:
             self.head_rows(R if head_row is None else head_row + 1)
 
