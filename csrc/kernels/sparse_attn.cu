@@ -194,6 +194,41 @@ __device__ __forceinline__ uint32_t orderable(float f) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+// One radix digit of the selection: given the 256-bin histogram of the keys that share the prefix found so far, find the
+// highest bin d whose keys together with all keys in higher bins reach `need`, and how many keys of bin d are still
+// needed.  Warp 0 does it: lane l sums bins 255 - 8l .. 248 - 8l, a shuffle scan gives the count above each lane's bins,
+// and the one lane whose bins contain the answer walks its eight bins.  (One thread walking up to 255 bins, a dependent
+// shared-memory load each, was most of the kernel's time: four digits per row.)
+__device__ __forceinline__ void radix_pick(const int* hist, int need, uint32_t prefix, int shift, uint32_t* s_prefix,
+                                           int* s_need) {
+  if (threadIdx.x >= 32) return;
+  const int lane = threadIdx.x;
+  int local[8], sum = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    local[j] = hist[255 - 8 * lane - j];
+    sum += local[j];
+  }
+  int incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  const unsigned reach = __ballot_sync(0xffffffffu, incl >= need);
+  const int owner = reach ? __ffs(reach) - 1 : 31;      // no lane reaches it: bin 0 takes what is left
+  if (lane != owner) return;
+  int cum = incl - sum, d = 255 - 8 * lane;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    d = 255 - 8 * lane - j;
+    if (d == 0 || cum + local[j] >= need) break;
+    cum += local[j];
+  }
+  *s_prefix = prefix | (static_cast<uint32_t>(d) << shift);
+  *s_need = need - cum;
+}
+
 // exclusive scan over 1024 threads; returns this thread's exclusive prefix, *total gets the block sum
 __device__ __forceinline__ int block_excl_scan_1024(int v, int* warp_tot /*[32]*/, int* total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -225,8 +260,84 @@ __device__ __forceinline__ int block_excl_scan_1024(int v, int* warp_tot /*[32]*
 // element that must never be chosen.  Writes the chosen ids in ascending order (-1 padded) and their count.  With at most
 // k eligible elements all of them are chosen; otherwise a 4-pass radix select finds the k-th largest key and ties on it
 // go to the lowest ids.
+// Rows of at most 1024 * M elements: every thread keeps its M consecutive keys in registers, so the scores are read
+// once, the four radix passes build their histograms from registers, and the ordered compaction needs two block scans
+// in all (one block scan per 1024 elements and six reads of the row made the streaming form below take 30-43 us for 2 K
+// to 16 K keys).
+template <int M, class Key>
+__device__ void select_topk_row_reg(Key key, int n, int k, int* out, int* n_out) {
+  __shared__ int hist[256];
+  __shared__ int warp_tot[32];
+  __shared__ int s_total;
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_need;
+  __shared__ int s_valid;
+  const int tid = threadIdx.x;
+  const int i0 = tid * M;
+  uint32_t u[M];
+  int mine = 0;
+#pragma unroll
+  for (int j = 0; j < M; ++j) {
+    u[j] = i0 + j < n ? key(i0 + j) : 0u;
+    mine += u[j] != 0u;
+  }
+  if (tid == 0) s_valid = 0;
+  __syncthreads();
+  if (mine) atomicAdd(&s_valid, mine);
+  __syncthreads();
+  const int valid = s_valid;
+  for (int i = valid + tid; i < k; i += 1024) out[i] = -1;
+  uint32_t thr = 0;
+  int need = 0;
+  if (valid > k) {
+    uint32_t prefix = 0, mask = 0;
+    need = k;
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      if (tid < 256) hist[tid] = 0;
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < M; ++j)
+        if (u[j] != 0u && (u[j] & mask) == prefix) atomicAdd(&hist[(u[j] >> shift) & 255], 1);
+      __syncthreads();
+      radix_pick(hist, need, prefix, shift, &s_prefix, &s_need);
+      __syncthreads();
+      prefix = s_prefix;
+      need = s_need;
+      mask |= 0xFFu << shift;
+      __syncthreads();
+    }
+    thr = prefix;
+  }
+  // ordered compaction: ids ascend with the thread index, so one scan of the per-thread counts places every element
+  int n_eq = 0;
+#pragma unroll
+  for (int j = 0; j < M; ++j) n_eq += (u[j] != 0u && u[j] == thr) ? 1 : 0;
+  int eq_rank = block_excl_scan_1024(n_eq, warp_tot, &s_total);
+  __syncthreads();
+  int n_keep = 0;
+  uint32_t keep_bits = 0;
+#pragma unroll
+  for (int j = 0; j < M; ++j) {
+    const bool eq = u[j] != 0u && u[j] == thr;
+    const bool keep = u[j] != 0u && (u[j] > thr || (eq && eq_rank < need));
+    eq_rank += eq ? 1 : 0;
+    keep_bits |= keep ? (1u << j) : 0u;
+    n_keep += keep ? 1 : 0;
+  }
+  int at = block_excl_scan_1024(n_keep, warp_tot, &s_total);
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < M; ++j)
+    if ((keep_bits >> j) & 1u) {
+      if (at < k) out[at] = i0 + j;
+      ++at;
+    }
+  if (tid == 0) *n_out = min(s_total, k);
+}
+
 template <class Key>
-__device__ void select_topk_row(Key key, int n, int k, int* out, int* n_out) {
+__device__ void select_topk_row_stream(Key key, int n, int k, int* out, int* n_out) {
   __shared__ int hist[256];
   __shared__ int warp_tot[32];
   __shared__ int s_total;
@@ -256,15 +367,7 @@ __device__ void select_topk_row(Key key, int n, int k, int* out, int* n_out) {
         if (u != 0u && (u & mask) == prefix) atomicAdd(&hist[(u >> shift) & 255], 1);
       }
       __syncthreads();
-      if (tid == 0) {
-        int cum = 0, d = 255;
-        for (; d > 0; --d) {
-          if (cum + hist[d] >= need) break;
-          cum += hist[d];
-        }
-        s_prefix = prefix | (static_cast<uint32_t>(d) << shift);
-        s_need = need - cum;
-      }
+      radix_pick(hist, need, prefix, shift, &s_prefix, &s_need);
       __syncthreads();
       prefix = s_prefix;
       need = s_need;
@@ -293,6 +396,15 @@ __device__ void select_topk_row(Key key, int n, int k, int* out, int* n_out) {
     __syncthreads();
   }
   if (tid == 0) *n_out = min(base, k);
+}
+
+template <class Key>
+__device__ void select_topk_row(Key key, int n, int k, int* out, int* n_out) {
+  if (n <= 4 * 1024) select_topk_row_reg<4>(key, n, k, out, n_out);
+  else if (n <= 8 * 1024) select_topk_row_reg<8>(key, n, k, out, n_out);
+  else if (n <= 16 * 1024) select_topk_row_reg<16>(key, n, k, out, n_out);
+  else if (n <= 24 * 1024) select_topk_row_reg<24>(key, n, k, out, n_out);
+  else select_topk_row_stream(key, n, k, out, n_out);
 }
 
 struct TopkParams {

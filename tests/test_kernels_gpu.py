@@ -7,14 +7,18 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def test_topk_select_exact():
+@pytest.mark.parametrize("max_keys,positions", [(5000, [4999, 2999, 300, 4000]),        # register forms (8 / 4 keys a thread)
+                                                (20000, [15999, 19999, 2047, 9000]),    # 16 a thread; streaming form
+                                                (1024, [1023, 700, 511, 600])])
+def test_topk_select_exact(max_keys, positions):
     from ds41rt_b200.ops import lib
     k = lib.kernels()
-    rows, max_keys, topk = 4, 5000, 512
+    rows, topk = 4, 512
     torch.manual_seed(0)
     scores = torch.randn(rows, max_keys, device="cuda")
     scores[1, :3000] = scores[1, :3000].round()            # many ties
-    pos = torch.tensor([4999, 2999, 300, 4000], dtype=torch.int32, device="cuda")
+    scores[0, 17] = float("-inf")
+    pos = torch.tensor(positions, dtype=torch.int32, device="cuda")
     slot = torch.tensor([0, 0, 0, -1], dtype=torch.int32, device="cuda")
     sel = torch.zeros(rows, topk, dtype=torch.int32, device="cuda")
     n_sel = torch.zeros(rows, dtype=torch.int32, device="cuda")
