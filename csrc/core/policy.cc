@@ -6,6 +6,9 @@
 // and picks argmax benefit/cost.  Acceptance per depth is an exponentially weighted frequency, optionally conditioned
 // on the drafter's confidence through a Platt-style logistic calibration.  Until enough rounds are observed the
 // policy verifies everything (warm-up: 12 rounds).  Times come from CUDA events, never host clocks.
+// A policy that has settled on plain decoding (width 0) observes nothing any more, so it would never notice that the
+// text became predictable again: every `probe_every`-th such decision (64 by default) is answered with a short probe
+// of two drafts, whose outcome feeds the acceptance estimate like any other round.
 // Behavioural counterpart of rust/crates/ds41rt-core/src/dspark_policy.rs:449-874 and
 // docs/dspark-bandwidth-policy.md:31-140 of the reference (whose cost model is bandwidth balance over RDMA workers;
 // here the cost terms are the NVLink-box step times).
@@ -28,6 +31,8 @@ struct Policy {
   // Platt calibration of confidence -> acceptance at depth 1: sigmoid(a*c + b), fitted by SGD
   double pa = 4.0, pb = -2.0;
   uint64_t hist[16] = {0};
+  int probe_every = 64, idle = 0;
+  uint64_t probes = 0;
 };
 
 double sigmoid(double x) { return 1.0 / (1.0 + std::exp(-x)); }
@@ -107,7 +112,21 @@ int ds41_policy_choose(void* h, double confidence) {
     const double score = benefit / cost;
     if (score > best * (1.0 + 1e-9)) { best = score; best_w = w; }
   }
+  if (best_w > 0) {
+    p->idle = 0;
+  } else if (p->probe_every > 0 && ++p->idle >= p->probe_every) {
+    p->idle = 0;
+    ++p->probes;
+    return std::min(2, p->max_width);
+  }
   return best_w;
+}
+
+// Probe cadence while the policy chooses plain decoding (0 = never probe); returns the number of probes so far.
+uint64_t ds41_policy_probe(void* h, int every) {
+  Policy* p = static_cast<Policy*>(h);
+  if (every >= 0) p->probe_every = every;
+  return p->probes;
 }
 
 void ds41_policy_stats(void* h, double* out /*[8]*/, uint64_t* hist16) {

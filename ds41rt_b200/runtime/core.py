@@ -320,6 +320,13 @@ class DSparkPolicy:
     def acceptance(self, depth: int) -> float:
         return float(core().ds41_policy_acceptance(self.h, depth))
 
+    def probe(self, every: int = -1) -> int:
+        """Set how often a policy that chose plain decoding answers with a two-draft probe instead (0 = never; -1 leaves
+        the cadence as it is); returns the number of probes so far."""
+        c = core()
+        c.ds41_policy_probe.restype = C.c_uint64
+        return int(c.ds41_policy_probe(self.h, every))
+
     def stats(self) -> dict:
         out = (C.c_double * 8)()
         hist = (C.c_uint64 * 16)()

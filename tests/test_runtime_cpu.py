@@ -57,6 +57,23 @@ def test_policy_matches_exhaustive_search_after_warmup():
         bad.observe(4, 0, 1000 + 150 * 5, 80.0)
         bad.observe(0, 0, 1000 + 150, 0.0)
     assert bad.choose() == 0
+    # ... but keep probing: every 8th plain decision is a two-draft probe, and once the probes are accepted the policy
+    # returns to speculation
+    bad.probe(8)
+    picks = [bad.choose() for _ in range(16)]
+    assert picks.count(2) == 2 and picks.count(0) == 14 and picks[6] == 2 and bad.probe() == 2
+    for _ in range(200):
+        w = bad.choose()
+        if w > 0:
+            bad.observe(w, w, 1000 + 150 * (1 + w), 20.0 * w)       # the text became predictable
+    assert bad.choose() == 4
+    bad.probe(0)                                                    # probing can be switched off
+    never = K.DSparkPolicy(max_width=4, warmup_rounds=2)
+    never.probe(0)
+    for _ in range(50):
+        never.observe(4, 0, 1750, 80.0)
+        never.observe(0, 0, 1150, 0.0)
+    assert [never.choose() for _ in range(200)].count(0) == 200
     s = pol.stats()
     assert s["rounds"] == 400 and abs(s["t_row_us"] - 150) < 5 and abs(s["t_fixed_us"] - 1000) < 20
 
