@@ -812,6 +812,9 @@ class DS41Engine:
         self.only = None
         from ..utils.trace import ActivationTrace
         self.layer_timer = None   # utils.trace.LayerTimer: device time per layer of eager passes
+        # DS41_NVTX=1: every launch sits in an NVTX range named after its kernel class (for timeline tools)
+        import os
+        self.nvtx = os.environ.get("DS41_NVTX", "") == "1"
         self.activation_trace = ActivationTrace.from_env()
         self._pass_hint = None    # (rows, highest position) of a single-request pass described by the last set_rows
         self.image_patch = None   # (image rows, pass-row ids) applied after the embedding lookup of the next pass
@@ -871,6 +874,15 @@ class DS41Engine:
         if self.only is not None and tag not in self.only:
             return
         self.launches += 1
+        if self.nvtx:
+            torch.cuda.nvtx.range_push(tag)
+            try:
+                err = fn(*args, **kw)
+            finally:
+                torch.cuda.nvtx.range_pop()
+            if err is not None:
+                lib.check(err, tag)
+            return
         if self.timeline is not None:           # eager passes only: a CUDA event pair around every launch
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()

@@ -4,6 +4,7 @@
 Targets used in this package: timing, sampling, lane_schedule, draft_policy, host_cache, graph_capture, logit_trace,
 activation_trace.  `DS41_ACTIVATION_TRACE_DIR` (+ optional `DS41_ACTIVATION_TRACE_POSITION`) makes the engine write the
 residual streams after every layer for the rows at that position (all rows when no position is given).
+`DS41_NVTX=1` puts every kernel launch of the engine into an NVTX range named after its kernel class.
 Counterpart in the reference: the `tracing` targets and env filter (rust/crates/ds41rt-daemon/src/main.rs:66-68), per
 layer CUDA events (`v41_target_pass.rs:142-146`) and the activation dump (`v41_target_pass.rs:348-357,482-484`).
 """

@@ -209,6 +209,11 @@ def test_cuda_graph_decode_matches_eager():
     torch.cuda.synchronize()
     assert int(eng.row_pos[0]) == len(prompt) + 5
     assert int(eng.in_tokens[0]) == out_graph[5]
+    # NVTX ranges around every launch (DS41_NVTX=1) change nothing but the timeline a profiler sees
+    eng.nvtx = True
+    out_ranges = DecodeSession(eng, use_graphs=False).generate(prompt, 12, slot=1)
+    eng.nvtx = False
+    assert out_ranges == out_eager
 
 
 def test_fp8_kv_cache_rows_and_logits():
