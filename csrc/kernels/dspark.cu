@@ -29,7 +29,9 @@ __global__ void taps_pack_kernel(const float* __restrict__ taps, __nv_bfloat16* 
   out[i] = __float2bfloat16_rn(taps[t * tap_stride + 1ll * r * H + c]);
 }
 
-// one block (256 threads) per row; N <= 8192
+// one block (256 threads) per row; N <= 8192 and a multiple of 4.  A thread owns groups of four consecutive columns, so
+// the split planes are summed with 16-byte loads (one scalar load per plane and column made the kernel a chain of 320
+// dependent-latency loads per thread for 16 planes of 5120 columns).
 __global__ void __launch_bounds__(256) norm_rows_kernel(const float* __restrict__ planes, int splits, long long plane,
                                                         const float* __restrict__ w, __nv_bfloat16* __restrict__ out,
                                                         int N, float eps) {
@@ -37,19 +39,22 @@ __global__ void __launch_bounds__(256) norm_rows_kernel(const float* __restrict_
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x, tid = threadIdx.x;
-  float vals[32];
+  float4 vals[8];
   float sq = 0.f;
 #pragma unroll
-  for (int n = 0; n < 32; ++n) {
-    const int c = tid + 256 * n;
-    float a = 0.f;
+  for (int n = 0; n < 8; ++n) {
+    const int c = 4 * (tid + 256 * n);
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c < N) {
 #pragma unroll 4
-      for (int s = 0; s < splits; ++s) a += planes[s * plane + 1ll * r * N + c];
-      a = bf16_round(a);
+      for (int s = 0; s < splits; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(planes + s * plane + 1ll * r * N + c);
+        a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+      }
+      a = make_float4(bf16_round(a.x), bf16_round(a.y), bf16_round(a.z), bf16_round(a.w));
     }
     vals[n] = a;
-    sq = fmaf(a, a, sq);
+    sq = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(a.z, a.z, fmaf(a.w, a.w, sq))));
   }
   sq = warp_sum(sq);
   if ((tid & 31) == 0) part[tid >> 5] = sq;
@@ -59,9 +64,17 @@ __global__ void __launch_bounds__(256) norm_rows_kernel(const float* __restrict_
   for (int i = 0; i < 8; ++i) tot += part[i];
   const float inv = rsqrtf(tot / N + eps);
 #pragma unroll
-  for (int n = 0; n < 32; ++n) {
-    const int c = tid + 256 * n;
-    if (c < N) out[1ll * r * N + c] = __float2bfloat16_rn(vals[n] * inv * (w != nullptr ? w[c] : 1.f));
+  for (int n = 0; n < 8; ++n) {
+    const int c = 4 * (tid + 256 * n);
+    if (c < N) {
+      const float4 g = w != nullptr ? *reinterpret_cast<const float4*>(w + c) : make_float4(1.f, 1.f, 1.f, 1.f);
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(vals[n].x * inv * g.x, vals[n].y * inv * g.y);
+      const __nv_bfloat162 hi = __floats2bfloat162_rn(vals[n].z * inv * g.z, vals[n].w * inv * g.w);
+      uint2 o;
+      o.x = *reinterpret_cast<const uint32_t*>(&lo);
+      o.y = *reinterpret_cast<const uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(out + 1ll * r * N + c) = o;
+    }
   }
 }
 
@@ -289,7 +302,7 @@ extern "C" int ds41_taps_pack(const float* taps, void* out, int n_taps, int rows
 
 extern "C" int ds41_norm_rows(const float* planes, int splits, long long plane, const float* w, void* out, int rows,
                               int N, float eps, void* stream) {
-  if (rows <= 0 || N <= 0 || N > 8192 || splits <= 0) return cudaErrorInvalidValue;
+  if (rows <= 0 || N <= 0 || N > 8192 || (N & 3) || (plane & 3) || splits <= 0) return cudaErrorInvalidValue;
   return launch_pdl(norm_rows_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), planes, splits,
                     plane, w, static_cast<__nv_bfloat16*>(out), N, eps);
 }

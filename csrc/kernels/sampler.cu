@@ -37,13 +37,31 @@ __global__ void __launch_bounds__(1024) argmax_rows_kernel(ArgmaxParams p) {
   float v = -INFINITY;
   int idx = 0x7fffffff;
   int nonfinite = 0;
-  for (int i = tid; i < p.vocab_local; i += 1024) {
+  const float* row = p.logits + 1ll * r * p.ld;
+  const uint32_t* mrow = p.mask != nullptr ? p.mask + 1ll * r * p.mask_words : nullptr;
+  auto take = [&](int i, float x) {
     const int tok = p.vocab_offset + i;
-    const float x = p.logits[1ll * r * p.ld + i];
     if (!isfinite(x)) nonfinite = 1;
     bool ok = true;
-    if (p.mask != nullptr) ok = (p.mask[1ll * r * p.mask_words + (tok >> 5)] >> (tok & 31)) & 1u;
+    if (mrow != nullptr) ok = (mrow[tok >> 5] >> (tok & 31)) & 1u;
     if (ok && (x > v || (x == v && tok < idx))) { v = x; idx = tok; }
+  };
+  if ((p.ld & 3) == 0 && (reinterpret_cast<uintptr_t>(p.logits) & 15) == 0) {
+    // 16-byte loads, two of them in flight per thread: a row is half a megabyte read by one block
+    const int n4 = p.vocab_local >> 2;
+    for (int g = tid; g < n4; g += 2048) {
+      const float4 a = *reinterpret_cast<const float4*>(row + 4 * g);
+      const bool second = g + 1024 < n4;
+      const float4 b = second ? *reinterpret_cast<const float4*>(row + 4 * (g + 1024)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      take(4 * g, a.x); take(4 * g + 1, a.y); take(4 * g + 2, a.z); take(4 * g + 3, a.w);
+      if (second) {
+        const int h = 4 * (g + 1024);
+        take(h, b.x); take(h + 1, b.y); take(h + 2, b.z); take(h + 3, b.w);
+      }
+    }
+    for (int i = 4 * n4 + tid; i < p.vocab_local; i += 1024) take(i, row[i]);
+  } else {
+    for (int i = tid; i < p.vocab_local; i += 1024) take(i, row[i]);
   }
   if (nonfinite) bad = 1;
 #pragma unroll
