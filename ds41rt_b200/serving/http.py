@@ -327,7 +327,12 @@ class ApiServer:
         elif req.tools and (req.tool_choice == "required" or isinstance(req.tool_choice, dict)):
             grammar = Grammar(tool_call_grammar(req.tools, req.tool_choice, req.parallel_tool_calls))
         elif req.tools and req.tool_choice == "auto":
-            grammar = Grammar(tool_call_grammar(req.tools, "auto", req.parallel_tool_calls, triggered=True))
+            # A client may switch the decoding assistance off for automatic selection; tools declared strict keep their
+            # grammar (reference: rust/crates/ds41rt-api/src/constrained.rs:40-45).  The calls block is still parsed and
+            # validated when the answer completes.
+            strict = any(t.get("function", {}).get("strict") for t in req.tools)
+            if req.tool_decoding_assistance or strict:
+                grammar = Grammar(tool_call_grammar(req.tools, "auto", req.parallel_tool_calls, triggered=True))
         if grammar is None:
             return None
         return TokenConstraint(self._vocab(), grammar, eos=self.tk.eos, think_end=self.tk.think_end,

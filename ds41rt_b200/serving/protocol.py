@@ -3,7 +3,8 @@
 Field handling follows the reference router (rust/crates/ds41rt-api/src/native_v41.rs:162-437, limits.rs:4-58):
 temperature defaults to 0 (greedy); top_k 0 or -1 disables top-k; seed is a signed 64-bit integer; the model name
 must match the served model; `response_format` is text | json_object | json_schema{strict} | regex; `thinking.type`
-enabled/disabled (default enabled, effort "high"); `tool_choice` auto | none | required | {function:{name}}.
+enabled/disabled (default enabled, effort "high"); `tool_choice` auto | none | required | {function:{name}}; `tool_decoding_assistance` (false: automatic selection over
+non-strict tools decodes without the tool grammar).
 Errors are {"error": {"message", "type": "native_v41_error"}} with a bounded message.
 """
 from __future__ import annotations
@@ -50,6 +51,7 @@ class ChatRequest:
     tools: List[dict] = field(default_factory=list)
     tool_choice: Any = "auto"
     parallel_tool_calls: bool = True
+    tool_decoding_assistance: bool = True        # false: automatic selection over non-strict tools decodes unconstrained
     response_format: Dict[str, Any] = field(default_factory=lambda: {"type": "text"})
     thinking: bool = True
     reasoning_effort: Optional[str] = "high"
@@ -124,6 +126,10 @@ def parse_chat_request(body: Any, model_id: str = MODEL_ID, max_output: int = MA
         raise ApiError(400, "'tool_choice' required needs tools")
     req.tool_choice = tc
     req.parallel_tool_calls = bool(body.get("parallel_tool_calls", True))
+    assistance = body.get("tool_decoding_assistance")
+    if assistance is not None and not isinstance(assistance, bool):
+        raise ApiError(400, "'tool_decoding_assistance' must be boolean")
+    req.tool_decoding_assistance = True if assistance is None else assistance
     rf = body.get("response_format") or {"type": "text"}
     if not isinstance(rf, dict) or rf.get("type") not in ("text", "json_object", "json_schema", "regex"):
         raise ApiError(400, "'response_format.type' must be text, json_object, json_schema or regex")

@@ -68,6 +68,7 @@ def test_health_models_stats_and_console():
     ({"tool_choice": "required"}, "tools"), ({"thinking": {"type": "maybe"}}, "thinking"),
     ({"response_format": {"type": "json_schema", "json_schema": {"schema": {"type": "frob"}}}}, "unsupported"),
     ({"messages": [{"role": "wizard", "content": "x"}]}, "role"), ({"stop": [1]}, "stop"),
+    ({"tool_decoding_assistance": "no"}, "tool_decoding_assistance"),
 ])
 def test_bad_requests_are_400_with_error_shape(patch, needle):
     srv, _ = serve("x")
@@ -156,6 +157,21 @@ def test_tool_calls_are_parsed_validated_and_streamed():
     try:
         st, _, raw = call(srv, req(tools=tools, tool_choice="required"))
         assert st == 500                                      # the grammar rejects it / validation catches it
+    finally:
+        srv.stop()
+    # decoding assistance: automatic selection carries the triggered grammar unless the client switches it off; a tool
+    # declared strict keeps it; the completed block is validated either way
+    srv, be = serve("</think>Let me check.\n" + block)
+    try:
+        assert call(srv, req(tools=tools))[0] == 200 and be.submitted[-1].constraint is not None
+        st, _, raw = call(srv, req(tools=tools, tool_decoding_assistance=False))
+        assert st == 200 and be.submitted[-1].constraint is None
+        assert json.loads(raw)["choices"][0]["finish_reason"] == "tool_calls"
+        strict = [dict(tools[0], function=dict(tools[0]["function"], strict=True))]
+        assert call(srv, req(tools=strict, tool_decoding_assistance=False))[0] == 200
+        assert be.submitted[-1].constraint is not None
+        assert call(srv, req(tools=tools, tool_choice="required", tool_decoding_assistance=False))[0] == 200
+        assert be.submitted[-1].constraint is not None
     finally:
         srv.stop()
 
