@@ -135,6 +135,20 @@ _PARAM = re.compile(re.escape(DSML_OPEN) + r' parameter name="([^"]*)" string="(
                     re.escape(DSML_CLOSE) + r" parameter>", re.S)
 
 
+def loads_strict(text: str):
+    """json.loads that refuses an object with the same property twice (compared after unescaping, so "a" and "\\u0061"
+    collide) instead of keeping the last value - the reader the reference uses for completed arguments and answers
+    (docs/release-v1-tool-serving.md of the reference, "rejects duplicate properties, including escaped aliases")."""
+    def pairs(items):
+        out = {}
+        for k, v in items:
+            if k in out:
+                raise ValueError(f"duplicate property {k!r}")
+            out[k] = v
+        return out
+    return json.loads(text, object_pairs_hook=pairs)
+
+
 def parse_tool_calls(block: str) -> List[dict]:
     """DSML calls block -> OpenAI tool_calls entries.  Raises ChatError on malformed blocks."""
     if CALLS_OPEN not in block or CALLS_CLOSE not in block:
@@ -144,12 +158,14 @@ def parse_tool_calls(block: str) -> List[dict]:
     for name, body in _INVOKE.findall(inner):
         args = {}
         for key, is_str, val in _PARAM.findall(body):
+            if key in args:
+                raise ChatError(f"parameter {key!r} of {name!r} is given twice")
             if is_str == "true":
                 args[key] = val
             else:
                 try:
-                    args[key] = json.loads(val)
-                except json.JSONDecodeError as e:
+                    args[key] = loads_strict(val)
+                except ValueError as e:                   # JSONDecodeError is a ValueError; so is a duplicate property
                     raise ChatError(f"parameter {key!r} of {name!r} is not valid JSON: {e}")
         calls.append({"id": "call_" + uuid.uuid4().hex[:24], "type": "function",
                       "function": {"name": name, "arguments": json.dumps(args, ensure_ascii=False)}})
@@ -185,8 +201,8 @@ def validate_tool_calls(calls: List[dict], tools: List[dict]) -> Optional[str]:
 def validate_json_output(text: str, schema: Optional[dict]) -> Optional[str]:
     from ..runtime.grammar import Grammar, Matcher
     try:
-        json.loads(text)
-    except json.JSONDecodeError as e:
+        loads_strict(text)
+    except ValueError as e:
         return f"output is not valid JSON: {e}"
     if schema is not None:
         m = Matcher(Grammar.json_schema(schema))

@@ -191,6 +191,24 @@ def test_json_schema_outputs_are_revalidated():
         assert call(srv, req(response_format=rf))[0] == 500
     finally:
         srv.stop()
+    # the same property twice - also through an escaped alias - is an error, not "last value wins"
+    for text in ('{"n": 1, "n": 2}', '{"n": 1, "\\u006e": 2}'):
+        srv, _ = serve("</think>" + text)
+        try:
+            st, _, raw = call(srv, req(response_format={"type": "json_object"}))
+            assert st == 500 and "duplicate" in json.loads(raw)["error"]["message"], text
+        finally:
+            srv.stop()
+    assert C.loads_strict('{"a": {"b": 1}, "c": [{"b": 2}, {"b": 3}]}') == {"a": {"b": 1}, "c": [{"b": 2}, {"b": 3}]}
+    twice = C.CALLS_OPEN + "\n" + f'{C.DSML_OPEN} invoke name="f">\n' + \
+        f'{C.DSML_OPEN} parameter name="x" string="true">1{C.DSML_CLOSE} parameter>\n' * 2 + \
+        f"{C.DSML_CLOSE} invoke>\n" + C.CALLS_CLOSE
+    with pytest.raises(C.ChatError, match="twice"):
+        C.parse_tool_calls(twice)
+    nested = twice.replace('string="true">1', 'string="false">{"k": 1, "k": 2}', 1).replace(
+        f'{C.DSML_OPEN} parameter name="x" string="true">1{C.DSML_CLOSE} parameter>\n', "", 1)
+    with pytest.raises(C.ChatError, match="duplicate"):
+        C.parse_tool_calls(nested)
 
 
 def test_bounded_admission_answers_429_with_retry_after():
