@@ -86,8 +86,20 @@ class LeaderEngine:
     def _send(self, msg: Tuple) -> None:
         if self.heartbeat is not None:
             self.heartbeat.guard()
-        if self.group is not None:
+        if self.group is None:
+            return
+        try:
             _bcast(self.group, msg)
+        except RuntimeError:
+            # A follower that left between the guard and this message closes its end of the control group.  The store
+            # says who and why a moment later: report that (RankFailure) rather than the transport's error.
+            if self.heartbeat is not None:
+                import time
+                deadline = time.time() + 5.0
+                while time.time() < deadline and not self.heartbeat.peers_down():
+                    time.sleep(0.05)
+                self.heartbeat.guard()
+            raise
 
     def set_rows(self, tokens: List[int], positions: List[int], slots: List[int], row_lo=None) -> None:
         self._send(("set_rows", list(tokens), list(positions), list(slots), None if row_lo is None else list(row_lo)))
@@ -172,7 +184,7 @@ def follower_loop(engine, group, on_error=None, heartbeat=None) -> int:
             elif op == "restore_prefix":
                 engine.cache.restore_prefix(msg[1], snaps[msg[2]], msg[3])
             elif op == "drop":
-                engine.cache.drop_snapshot(snaps.pop(msg[2]))
+                engine.cache.drop_snapshot(snaps.pop(msg[1]))
         except Exception as e:          # keep the launch sequences aligned; the leader sees the status word / timeout
             if on_error is not None:
                 on_error(e)
