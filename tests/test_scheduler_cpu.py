@@ -232,3 +232,112 @@ def test_demoted_snapshots_come_back_from_the_host_tier(cpu_sampler):
         assert "host_cache" in be.stats()
     finally:
         be.close()
+
+
+class FakeSpec:
+    """Stand-in for runtime.speculative.SpecSession over the CPU engine above: the "drafter" knows the engine's token
+    rule and proposes the true continuation, except that every `wrong_every`-th proposed token is off by one."""
+
+    def __init__(self, eng, width=5, wrong_every=3):
+        self.e, self.width, self.wrong_every = eng, width, wrong_every
+        self.last_confidence = []
+        self.proposed = 0
+        self.calls = {"draft_groups": 0, "verify_groups": 0, "draft": 0, "verify": 0, "feed": 0}
+
+        class _D:
+            max_groups = 4
+
+            def feed(_self, n):
+                self.calls["feed"] += 1
+        self.d = _D()
+
+    @staticmethod
+    def rule(tok, pos):
+        return (tok * 31 + pos * 7 + 3) % 1000 + 2
+
+    def _propose(self, anchor, pos):
+        out, tok = [], anchor
+        for j in range(self.width - 1):
+            tok = self.rule(tok, pos + j)
+            self.proposed += 1
+            out.append(tok + 1 if self.proposed % self.wrong_every == 0 else tok)
+            tok = out[-1]
+        return out
+
+    def draft_host_groups(self, slots, anchors, positions):
+        self.calls["draft_groups"] += 1
+        return [self._propose(a, p) for a, p in zip(anchors, positions)], [[] for _ in slots]
+
+    def verify_host_groups(self, slots, inputs, positions):
+        self.calls["verify_groups"] += 1
+        toks, pos, first = [], [], []
+        for inp, p in zip(inputs, positions):
+            first.append(len(toks))
+            toks += inp
+            pos += list(range(p, p + len(inp)))
+        self.e.set_rows(toks, pos, [0] * len(toks))
+        self.e.forward_rows(len(toks))
+        return first
+
+    def draft_host(self, slot, anchor, pos):
+        self.calls["draft"] += 1
+        return self._propose(anchor, pos)
+
+    def verify_host(self, slot, inputs, pos):
+        self.calls["verify"] += 1
+        self.e.set_rows(inputs, list(range(pos, pos + len(inputs))), [slot] * len(inputs))
+        self.e.forward_rows(len(inputs))
+
+    def prime(self, slot, anchor, pos):
+        self.state = [slot, anchor, pos]
+
+    def round_host(self):
+        """The all-device round of a lone greedy request, done on the host here."""
+        slot, anchor, pos = self.state
+        drafts = self._propose(anchor, pos)
+        self.verify_host(slot, [anchor] + drafts, pos)
+        chosen = self.e.chosen[: len(drafts) + 1].tolist()
+        k = 0
+        while k < len(drafts) and chosen[k] == drafts[k]:
+            k += 1
+        self.state = [slot, chosen[k], pos + k + 1]
+        return chosen[: k + 1]
+
+
+def test_shared_speculative_rounds_emit_exactly_the_plain_tokens(cpu_sampler):
+    """Scheduler side of the rounds that several requests share: proposals are cut at each request's budget, every
+    request keeps the drafts that equal the verification rows' own tokens plus one more, a request that finishes
+    inside a round leaves the others running - and everyone receives what plain decoding would have given."""
+    from ds41rt_b200.runtime import core as K
+
+    def expected(prompt, n):
+        tok, pos, out = FakeSpec.rule(prompt[-1], len(prompt) - 1), len(prompt), []
+        out.append(tok)
+        while len(out) < n:
+            tok = FakeSpec.rule(tok, pos)
+            pos += 1
+            out.append(tok)
+        return out
+
+    eng = FakeEngine(slots=4, max_rows=64)
+    be = NativeBackend(eng, eos=1, concurrency=4, prefill_chunk=64, use_graphs=False)
+    try:
+        spec = FakeSpec(eng)
+        be.policy, be.policy_lanes = K.DSparkPolicy(max_width=4), K.DSparkPolicy(max_width=4)
+        be.spec_lanes = 4
+        be.spec = spec                                     # from here on admitted requests are followed by the drafter
+        prompts = [list(range(10, 50)), list(range(60, 93)), list(range(200, 247))]
+        budgets = [23, 9, 16]
+        reqs = [_req(p, n) for p, n in zip(prompts, budgets)]
+        for r in reqs:
+            be.submit(r)
+        got = _run(be, reqs)
+        for (toks, status), p, n in zip(got, prompts, budgets):
+            assert status == "length" and toks == expected(p, n)
+        assert be.healthy, be.error
+        t = be.totals
+        assert t["spec_lane_rounds"] > 0 and spec.calls["draft_groups"] == spec.calls["verify_groups"] > 0
+        assert t["spec_tokens"] > t["spec_rounds"]          # drafts were accepted (two of three proposals are right)
+        _idle(be)
+    finally:
+        be.close()
