@@ -403,6 +403,22 @@ def _engram_pipeline(args, cfg, eng, layers, tokenizer):
                           pad_id=cfg.engram.pad_token_id, max_rows=eng.max_rows, fold=not args.engram_table)
 
 
+def _vision_tower(args, cfg, dev):
+    """(VisionTower, VisionConfig) for `serve --vision`: the checkpoint's `vision.*` / `aligner.*` tensors, or random
+    weights of a small tower for a random-init model."""
+    from .config import VisionConfig
+    from .models.vision import VisionTower, init_vision_weights
+    if args.checkpoint:
+        from .loader.catalog import Catalog
+        v = cfg.vision or VisionConfig()
+        cat = Catalog(args.checkpoint, cfg, with_vision=True, with_engram=cfg.engram is not None)
+        weights = {n: cat.read(n).float() for n in cat.where if n.startswith(("vision.", "aligner."))}
+        return VisionTower(v, weights, cfg.hidden, v.layers, dev), v
+    v = VisionConfig(layers=2, hidden=256, heads=4, intermediate=384, min_pixels=42 * 42 * 4, max_image_tokens=64)
+    weights = init_vision_weights(v, cfg.hidden, v.layers, seed=args.seed + 5, std=0.05)
+    return VisionTower(v, weights, cfg.hidden, v.layers, dev, max_patches=(v.max_image_tokens * v.downsample ** 2)), v
+
+
 def cmd_serve(args) -> int:
     import torch
     from .models.ds41 import DS41Engine, EngineWeights
@@ -418,7 +434,9 @@ def cmd_serve(args) -> int:
     fabric = Fabric.create() if "WORLD_SIZE" in os.environ else Fabric.single(torch.device("cuda", args.device))
     rank, world, dev = fabric.rank, fabric.world, fabric.device
     ctl = make_control_group(fabric)
-    tk = HFTokenizer(args.tokenizer) if args.tokenizer else ByteTokenizer(vocab_size=cfg.vocab)
+    image_marks = ["<image>", "<image_start>", "<image_end>", "<image_newline>"]
+    tk = HFTokenizer(args.tokenizer) if args.tokenizer else \
+        ByteTokenizer(vocab_size=cfg.vocab, extra_specials=image_marks if args.vision else ())
     t0 = time.time()
     if args.checkpoint:
         from .loader.official import load_engine_weights
@@ -454,6 +472,13 @@ def cmd_serve(args) -> int:
         follower_loop(eng, ctl, on_error=lambda e: print(f"rank {rank}: {e}", file=sys.stderr, flush=True), heartbeat=hb)
         return 0
     lead = LeaderEngine(eng, ctl, heartbeat=hb)
+    tower = vision_cfg = None
+    if args.vision:
+        # image parts of chat messages: the tower runs on the serving rank and its rows replace placeholder embeddings
+        if world > 1:
+            print("--vision serves from one rank only in this build; ignoring it", file=sys.stderr)
+        else:
+            tower, vision_cfg = _vision_tower(args, cfg, dev)
     drafter = None
     if args.speculative:
         if world > 1:
@@ -465,9 +490,9 @@ def cmd_serve(args) -> int:
                             queue_depth=args.queue_depth, drafter=drafter, prefill_chunk=args.prefill_chunk,
                             prompt_snapshots=args.prompt_snapshots, turn_snapshots=args.turn_snapshots,
                             host_cache_bytes=int(args.host_cache_gb * (1 << 30)) if world == 1 else 0,
-                            engram=_engram_pipeline(args, cfg, eng, engram_layers, tk))
+                            engram=_engram_pipeline(args, cfg, eng, engram_layers, tk), vision=tower)
     srv = ApiServer(backend, tk, host=args.host, port=args.port, queue_depth=args.queue_depth, waiters=args.waiters,
-                    max_context=args.max_context).start()
+                    max_context=args.max_context, vision_cfg=vision_cfg).start()
     print(json.dumps({"listening": f"http://{args.host}:{srv.port}", "model": cfg.name, "ranks": world,
                       "setup_s": round(time.time() - t0, 1), "kv_pool": plan.as_dict() | {"pages": n_pages},
                       "settings": {k: v for k, v in getattr(args, "_origin", {}).items() if v != "default"}}), flush=True)
@@ -563,6 +588,9 @@ def main(argv=None) -> int:
                          "scale read from FILE.json)")
     ps.add_argument("--engram-random-rows", type=int, default=0,
                     help="random-init models: enable the Engram layers over random tables of this many rows")
+    ps.add_argument("--vision", action="store_true",
+                    help="accept image parts in chat messages: vision tower from the checkpoint (or a small random one "
+                         "for a random-init model); one-rank serving")
     ps.add_argument("--speculative", action="store_true",
                     help="decode with dSpark draft + verify rounds: a lone request, or up to four active requests sharing "
                          "a round (random-init drafter unless the checkpoint provides one)")
