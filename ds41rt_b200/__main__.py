@@ -12,6 +12,7 @@
   make-loadplan              which tensors (row / column ranges, bytes, experts) each rank reads from a checkpoint
   transport-capabilities     what the GPUs of this machine offer each other: peer access, NVLink, multicast, libraries
   scheduler-smoke            host-only check of admission, lanes, streaming and cancellation over a scripted backend
+  selftest                   build and run the native self-test of the host runtime library (C ABI, no Python between)
   bench-kernels / campaign / prefill-matrix / validate-bench / convert-checkpoint / convert-engram-table
                              the tools of ds41rt_b200.utils, loader.convert and runtime.ple_convert under one entry
 
@@ -358,6 +359,14 @@ def cmd_scheduler_smoke(args) -> int:
     return 0 if ok else 1
 
 
+def cmd_selftest(args) -> int:
+    """Native self-test of libds41_core.so (csrc/tests/core_selftest.cc); exit status = failed checks."""
+    import subprocess
+    from . import build
+    exe = build.build_selftest()
+    return subprocess.run([str(exe)]).returncode
+
+
 def _forward(module: str):
     def run(args) -> int:
         import importlib
@@ -554,6 +563,7 @@ def main(argv=None) -> int:
     pk.add_argument("--list", action="store_true", help="include every tensor with its row / column range")
     sub.add_parser("transport-capabilities")
     sub.add_parser("scheduler-smoke")
+    sub.add_parser("selftest")
     for name in FORWARDED:
         pf = sub.add_parser(name, add_help=False)
         pf.add_argument("rest", nargs=argparse.REMAINDER)
@@ -609,7 +619,8 @@ def main(argv=None) -> int:
     table = {"build": cmd_build, "info": cmd_info, "serve": cmd_serve, "doctor": cmd_doctor,
              "inspect-model": cmd_inspect_model, "tokenize": cmd_tokenize, "load-tensors": cmd_load_tensors,
              "plan-memory": cmd_plan_memory, "make-loadplan": cmd_make_loadplan,
-             "transport-capabilities": cmd_transport_capabilities, "scheduler-smoke": cmd_scheduler_smoke}
+             "transport-capabilities": cmd_transport_capabilities, "scheduler-smoke": cmd_scheduler_smoke,
+             "selftest": cmd_selftest}
     table.update({name: _forward(mod) for name, mod in FORWARDED.items()})
     return table[args.cmd](args)
 

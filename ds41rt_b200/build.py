@@ -92,6 +92,18 @@ def build_core(verbose: bool = False) -> Path:
     return _build_lib("libds41_core.so", sources, [cxx] + CXX_FLAGS, [cxx, "-shared", "-pthread"], verbose)
 
 
+def build_selftest() -> Path:
+    """csrc/tests/core_selftest.cc -> _lib/ds41_core_selftest, linked against the host runtime library beside it."""
+    cxx = shutil.which("g++") or "g++"
+    core = build_core()
+    out = LIBDIR / "ds41_core_selftest"
+    src = CSRC / "tests" / "core_selftest.cc"
+    if not out.exists() or out.stat().st_mtime < max(src.stat().st_mtime, core.stat().st_mtime):
+        subprocess.run([cxx, "-std=c++17", "-O1", "-Wall", str(src), "-L", str(LIBDIR), "-lds41_core",
+                        "-Wl,-rpath,$ORIGIN", "-o", str(out)], check=True)
+    return out
+
+
 def build_all(verbose: bool = False):
     return build_core(verbose), build_kernels(verbose)
 

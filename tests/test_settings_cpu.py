@@ -134,3 +134,8 @@ def test_stop_script_ends_the_recorded_process_group(tmp_path):
     assert r.returncode == 0 and "not running" in r.stdout
     r = subprocess.run(["bash", os.path.join(root, "run.sh"), "--gpus", "3"], capture_output=True, text=True, timeout=60)
     assert r.returncode == 64
+
+
+def test_native_selftest_of_the_host_runtime_passes():
+    rc, out = _cli("selftest")
+    assert rc == 0 and "ok 48 checks" in out and "FAILED" not in out
