@@ -299,3 +299,20 @@ def test_console_websocket_feed_pushes_snapshots():
         c.close()
     finally:
         srv.stop()
+
+
+def test_campaign_tool_drives_mixed_traffic_through_the_server():
+    """The concurrency campaign tool against the fake backend: every request kind completes, follow-up turns extend an
+    earlier conversation, schema answers are checked, tokens and first-token times are reported."""
+    from ds41rt_b200.utils.http_campaign import run_campaign
+    srv, be = serve('{"city": "Paris", "days": 3, "metric": true}', queue_depth=16, waiters=16)
+    try:
+        out = run_campaign("127.0.0.1", srv.port, clients=4, requests=12, max_tokens=64)
+    finally:
+        srv.stop()
+    assert out["completed"] == 12 and out["failed"] == 0 and out["rejected_429"] == 0
+    assert sum(out["by_kind"].values()) == 12 and out["by_kind"]["sampled"] >= 2 and out["by_kind"]["followup"] >= 1
+    assert out["schema_answers_valid_or_valid_prefix"] == "3/3"
+    assert out["completion_tokens"] > 0 and out["tok_per_s"] > 0 and out["ttft_s"]["median"] is not None
+    follow = [g for g in be.submitted if "Now shorter" in TK.decode(g.prompt_ids) and "Request" in TK.decode(g.prompt_ids)]
+    assert follow, "a follow-up turn carries the earlier exchange in its prompt"
