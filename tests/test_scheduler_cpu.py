@@ -341,3 +341,23 @@ def test_shared_speculative_rounds_emit_exactly_the_plain_tokens(cpu_sampler):
         _idle(be)
     finally:
         be.close()
+
+
+def test_prefill_matrix_tool_reports_cold_and_retained_rows(cpu_sampler):
+    """utils.prefill_matrix over the CPU stand-in: a retained row restores the base from the snapshot an earlier request
+    left and computes only what follows, a cold row computes everything."""
+    from ds41rt_b200.utils.prefill_matrix import run_matrix
+    eng = FakeEngine(slots=2, max_ctx=1024, max_rows=64)
+    be = NativeBackend(eng, eos=1, concurrency=1, prefill_chunk=64)
+    try:
+        rows = run_matrix(be, eng.cfg.vocab, [0, 192], [32, 96], warm=False)
+        assert be.healthy, be.error
+    finally:
+        be.close()
+    assert [(r["base"], r["suffix"], r["mode"]) for r in rows] == [
+        (0, 32, "cold"), (0, 96, "cold"), (192, 32, "cold"), (192, 32, "retained"), (192, 96, "cold"), (192, 96, "retained")]
+    for r in rows:
+        if r["mode"] == "cold":
+            assert r["cache_hit_tokens"] == 0 and r["computed_tokens"] == r["base"] + r["suffix"]
+        else:
+            assert 0 < r["cache_hit_tokens"] <= r["base"] and r["computed_tokens"] < r["base"] + r["suffix"]
