@@ -45,6 +45,29 @@ void* ds41_prefix_new(int prompt_capacity, int turn_capacity, int window);
 void ds41_prefix_free(void* p);
 int64_t ds41_prefix_insert(void* p, const uint32_t* tokens, int n, int bank, int64_t* evicted);
 int64_t ds41_prefix_lookup(void* p, const uint32_t* tokens, int n, int* common, int* frontier, int* skipped);
+void* ds41_vocab_new(const uint8_t* data, const int64_t* offsets, int n);
+void ds41_vocab_free(void* v);
+void* ds41_grammar_compile(const char* description, char* error, int error_cap);
+void ds41_grammar_free(void* g);
+void* ds41_matcher_new(const void* grammar);
+void* ds41_matcher_fork(const void* m);
+void ds41_matcher_free(void* m);
+int ds41_matcher_can_finish(const void* m);
+int ds41_matcher_accept_bytes(void* m, const uint8_t* bytes, int n);
+int ds41_matcher_accept_token(void* m, const void* vocab, int token);
+int ds41_matcher_fill_mask(const void* m, const void* vocab, uint32_t* mask, int stop_token);
+void* ds41_hostcache_new(int n_pages, uint64_t page_bytes, uint64_t store_budget, uint64_t restore_budget);
+void ds41_hostcache_free(void* p);
+int ds41_hostcache_store(void* p, int64_t id, const uint64_t* keys, int n, uint64_t tokens, int32_t* host_pages,
+                         uint8_t* need_copy);
+int ds41_hostcache_restore(void* p, int64_t id, int32_t* host_pages, int cap);
+int ds41_hostcache_contains(void* p, int64_t id);
+int ds41_hostcache_check(void* p);
+void* ds41_engram_history_new(uint32_t pad_id);
+void ds41_engram_history_free(void* h);
+uint64_t ds41_engram_history_position(const void* h);
+int ds41_engram_prepare(const void* hist, const int32_t* tokens, int n, uint64_t* hashes);
+int ds41_engram_commit(void* hist, const int32_t* tokens, int n, int accepted);
 }
 
 static int g_checks = 0, g_failed = 0;
@@ -186,6 +209,72 @@ static void prefix_banks() {
   std::printf("prefix banks ok\n");
 }
 
+static bool feed(void* m, const char* text) {
+  return ds41_matcher_accept_bytes(m, reinterpret_cast<const uint8_t*>(text), static_cast<int>(std::strlen(text))) == 1;
+}
+
+static void grammar_engine() {
+  char err[256] = {0};
+  void* g = ds41_grammar_compile(
+      "{\"schema\": {\"type\": \"object\", \"properties\": {\"n\": {\"type\": \"integer\"}, \"ok\": {\"type\": "
+      "\"boolean\"}}, \"required\": [\"n\", \"ok\"]}}", err, sizeof(err));
+  CHECK(g != nullptr);
+  void* m = ds41_matcher_new(g);
+  CHECK(feed(m, "{\"n\": 12") && !ds41_matcher_can_finish(m));
+  void* fork = ds41_matcher_fork(m);                              // a probe for draft rows: the original does not move
+  CHECK(!feed(fork, "x") && feed(m, ", \"ok\": true}") && ds41_matcher_can_finish(m));
+  ds41_matcher_free(fork);
+  void* bad = ds41_matcher_new(g);
+  CHECK(!feed(bad, "{\"n\": \"twelve\"") );
+  ds41_matcher_free(bad);
+  // token masks over a tiny vocabulary: "{", "}", "\"n\"", "1", "x", " "
+  const char* toks[6] = {"{", "}", "\"n\"", "1", "x", " "};
+  std::vector<uint8_t> data;
+  std::vector<int64_t> off = {0};
+  for (const char* t : toks) {
+    data.insert(data.end(), t, t + std::strlen(t));
+    off.push_back(static_cast<int64_t>(data.size()));
+  }
+  void* v = ds41_vocab_new(data.data(), off.data(), 6);
+  void* fresh = ds41_matcher_new(g);
+  uint32_t mask = 0;
+  CHECK(ds41_matcher_fill_mask(fresh, v, &mask, -1) >= 1 && (mask & 1u) && !(mask & (1u << 4)));   // "{" yes, "x" no
+  CHECK(ds41_matcher_accept_token(fresh, v, 0) == 1 && ds41_matcher_accept_token(fresh, v, 4) == 0);
+  ds41_matcher_fill_mask(fresh, v, &mask, -1);
+  CHECK((mask & (1u << 2)) && !(mask & (1u << 3)));               // after "{": the key "n" may follow, a digit may not
+  ds41_matcher_free(fresh);
+  ds41_matcher_free(m);
+  ds41_vocab_free(v);
+  ds41_grammar_free(g);
+  CHECK(ds41_grammar_compile("{\"schema\": {\"type\": \"frob\"}}", err, sizeof(err)) == nullptr && err[0] != 0);
+  std::printf("grammar engine ok\n");
+}
+
+static void host_cache_and_engram_history() {
+  void* c = ds41_hostcache_new(4, 4096, 1ull << 40, 1ull << 40);
+  const uint64_t ka[3] = {11, 12, 13}, kb[3] = {11, 12, 99};      // two snapshots share two pages by content
+  int32_t pages[4];
+  uint8_t need[4];
+  CHECK(ds41_hostcache_store(c, 1, ka, 3, 192, pages, need) == 3 && need[0] && need[1] && need[2]);
+  CHECK(ds41_hostcache_store(c, 2, kb, 3, 192, pages, need) == 3 && !need[0] && !need[1] && need[2]);
+  CHECK(ds41_hostcache_contains(c, 1) && ds41_hostcache_restore(c, 2, pages, 4) == 3 && ds41_hostcache_check(c) == 0);
+  const uint64_t kc[3] = {21, 22, 23};                            // no room beside both: the older snapshot goes
+  CHECK(ds41_hostcache_store(c, 3, kc, 3, 192, pages, need) == 3 && ds41_hostcache_check(c) == 0);
+  CHECK(!ds41_hostcache_contains(c, 1) || !ds41_hostcache_contains(c, 2));
+  CHECK(ds41_hostcache_restore(c, 77, pages, 4) == -1);
+  ds41_hostcache_free(c);
+  void* h = ds41_engram_history_new(2);
+  const int32_t toks[4] = {5, 6, 7, 8};
+  uint64_t first[4 * 48], again[4 * 48];
+  CHECK(ds41_engram_prepare(h, toks, 4, first) == 0 && ds41_engram_history_position(h) == 0);
+  CHECK(ds41_engram_commit(h, toks, 4, 2) == 0 && ds41_engram_history_position(h) == 2);      // two rows accepted
+  CHECK(ds41_engram_prepare(h, toks + 2, 2, again) == 0);
+  CHECK(std::memcmp(first + 2 * 48, again, sizeof(uint64_t) * 2 * 48) == 0);    // same history, same hashes
+  CHECK(ds41_engram_commit(h, toks, 4, 5) != 0);                  // more than was prepared
+  ds41_engram_history_free(h);
+  std::printf("host cache and n-gram history ok\n");
+}
+
 int main() {
   CHECK(ds41_core_version() >= 1);
   kv_pages();
@@ -195,6 +284,8 @@ int main() {
   policy();
   table_conversion();
   prefix_banks();
+  grammar_engine();
+  host_cache_and_engram_history();
   if (g_failed == 0) std::printf("ok %d checks\n", g_checks);
   else std::printf("%d of %d checks FAILED\n", g_failed, g_checks);
   return g_failed;

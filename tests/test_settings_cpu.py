@@ -138,4 +138,4 @@ def test_stop_script_ends_the_recorded_process_group(tmp_path):
 
 def test_native_selftest_of_the_host_runtime_passes():
     rc, out = _cli("selftest")
-    assert rc == 0 and "ok 48 checks" in out and "FAILED" not in out
+    assert rc == 0 and "ok 67 checks" in out and "FAILED" not in out
