@@ -505,6 +505,14 @@ def cmd_serve(args) -> int:
     print(json.dumps({"listening": f"http://{args.host}:{srv.port}", "model": cfg.name, "ranks": world,
                       "setup_s": round(time.time() - t0, 1), "kv_pool": plan.as_dict() | {"pages": n_pages},
                       "settings": {k: v for k, v in getattr(args, "_origin", {}).items() if v != "default"}}), flush=True)
+    # SIGTERM (./stop.sh, a container runtime) ends the server the way Ctrl-C does: the listener closes, the worker
+    # drains, and the mirroring ranks are told to stop instead of waiting for a leader that vanished
+    import signal
+
+    def _terminate(signum, frame):
+        raise KeyboardInterrupt
+
+    signal.signal(signal.SIGTERM, _terminate)
     try:
         while True:
             time.sleep(3600)
