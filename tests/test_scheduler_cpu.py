@@ -361,3 +361,41 @@ def test_prefill_matrix_tool_reports_cold_and_retained_rows(cpu_sampler):
             assert r["cache_hit_tokens"] == 0 and r["computed_tokens"] == r["base"] + r["suffix"]
         else:
             assert 0 < r["cache_hit_tokens"] <= r["base"] and r["computed_tokens"] < r["base"] + r["suffix"]
+
+
+def test_a_request_cancelled_between_shared_rounds_leaves_the_others_exact(cpu_sampler):
+    """Cancellation is looked at between rounds: the cancelled request retires, its slot and pages come back, and the
+    requests that shared its speculative rounds still receive exactly the plain tokens."""
+    from ds41rt_b200.runtime import core as K
+    eng = FakeEngine(slots=4, max_rows=64)
+    be = NativeBackend(eng, eos=1, concurrency=4, prefill_chunk=64, use_graphs=False)
+    try:
+        be.policy, be.policy_lanes = K.DSparkPolicy(max_width=4), K.DSparkPolicy(max_width=4)
+        be.spec_lanes = 4
+        be.spec = FakeSpec(eng, wrong_every=4)
+        prompts = [list(range(10, 50)), list(range(60, 93)), list(range(200, 247))]
+        reqs = [_req(prompts[0], 400), _req(prompts[1], 30), _req(prompts[2], 26)]
+        for r in reqs:
+            be.submit(r)
+        # wait for the long request's first tokens, then cancel it
+        first = reqs[0].events.get(timeout=10)
+        while first.kind != "tokens":
+            first = reqs[0].events.get(timeout=10)
+        reqs[0].cancelled.set()
+        got = _run(be, reqs[1:])
+        for (toks, status), p, n in zip(got, prompts[1:], (30, 26)):
+            tok, pos, want = FakeSpec.rule(p[-1], len(p) - 1), len(p), []
+            want.append(tok)
+            while len(want) < n:
+                tok = FakeSpec.rule(tok, pos)
+                pos += 1
+                want.append(tok)
+            assert status == "length" and toks == want
+        tail = _run(be, [reqs[0]])[0]
+        assert tail[1] == "cancelled" and be.healthy
+        _idle(be)
+        assert not be.active and eng.cache.free_pages == eng.cache.n_pages - sum(
+            len(s[1].pages) for s in be.snapshots.values())
+        assert be.totals["spec_lane_rounds"] > 0
+    finally:
+        be.close()
