@@ -697,7 +697,7 @@ class NativeBackend(Backend):
         return True
 
     # ------------------------------------------------------------------ speculative rounds (one request on the engine)
-    def _spec_round(self, a: _Active):
+    def _spec_round(self, a: _Active, gate: int = 0):
         """One speculative round for the only active request: up to `width` tokens come back."""
         import torch
         r = a.req
@@ -713,14 +713,15 @@ class NativeBackend(Backend):
             toks = self.spec.round_host()
             drafts_checked = self.spec.width - 1
         else:
-            toks, drafts_checked = self._spec_round_selected(a)
+            toks, drafts_checked = self._spec_round_selected(a, gate)
             self.totals["spec_masked_rounds"] += 1
+        us = -1.0                                  # no device clock (a CPU engine): only the acceptance is observed
         if timed:
             ev1.record()
             ev1.synchronize()
-            conf = self.spec.last_confidence
-            self.policy.observe(drafts_checked, max(0, len(toks) - 1), ev0.elapsed_time(ev1) * 1e3,
-                                confidence=conf[0] if conf else -1.0)
+            us = ev0.elapsed_time(ev1) * 1e3
+        conf = self.spec.last_confidence
+        self.policy.observe(drafts_checked, max(0, len(toks) - 1), us, confidence=conf[0] if conf else -1.0)
         self.totals["rounds"] += 1
         self.totals["spec_rounds"] += 1
         self.totals["spec_tokens"] += len(toks)
@@ -734,7 +735,7 @@ class NativeBackend(Backend):
             self.lanes.update(a.req.rid, a.req.max_tokens - a.emitted, a.pos)
         self.active = [a] if keep else []
 
-    def _spec_round_selected(self, a: _Active):
+    def _spec_round_selected(self, a: _Active, gate: int = 0):
         """Speculative round whose verification rows are selected on the host's terms: drafts come back first, the
         proposal is cut at the first token the grammar rejects, every verification row gets the mask of a matcher fork
         advanced over the drafts before it, and the rows are drawn by the GPU sampler with the request's own
@@ -744,7 +745,8 @@ class NativeBackend(Backend):
         drafts = sp.draft_host(a.slot, a.last, a.pos)                    # w - 1 proposed tokens
         if sp.last_confidence:
             # verification length from the policy, given how sure the drafter is of its first token
-            drafts = drafts[: max(0, self.policy.choose(sp.last_confidence[0]))]
+            # (`gate` > 0: the policy opened this round as a probe, whose width is kept)
+            drafts = drafts[: max(self.policy.choose(sp.last_confidence[0]), gate, 0)]
         if r.constraint is not None:
             drafts = r.constraint.truncate_proposal(drafts)
         remaining = r.max_tokens - a.emitted
@@ -763,7 +765,7 @@ class NativeBackend(Backend):
             self.engram.commit(ep, {a.slot: accepted + 1})               # the anchor and the accepted drafts
         return picked[: accepted + 1], len(drafts)
 
-    def _spec_round_lanes(self, acts: List[_Active]):
+    def _spec_round_lanes(self, acts: List[_Active], gate: int = 0):
         """One speculative round shared by several requests: one draft pass proposes a block per request, each proposal
         is cut by the policy (given the drafter's confidence in it), by the request's grammar and by its token budget,
         one target pass verifies all blocks, and every request keeps the drafts that equal the target's own selection
@@ -779,7 +781,7 @@ class NativeBackend(Backend):
         for a, drafts, conf in zip(acts, proposals, confs):
             r = a.req
             if conf:
-                drafts = drafts[: max(0, self.policy_lanes.choose(conf[0]))]
+                drafts = drafts[: max(self.policy_lanes.choose(conf[0]), gate, 0)]
             if r.constraint is not None:
                 drafts = r.constraint.truncate_proposal(drafts)
             drafts = drafts[: max(0, min(len(drafts), r.max_tokens - a.emitted - 1))]
@@ -805,12 +807,13 @@ class NativeBackend(Backend):
             accepted.append(k)
         if ep is not None:
             self.engram.commit(ep, {a.slot: k + 1 for a, k in zip(acts, accepted)})
+        share = -1.0
         if timed:
             ev1.record()
             ev1.synchronize()
             share = ev0.elapsed_time(ev1) * 1e3 / len(acts)
-            for inp, k, conf in zip(inputs, accepted, confs):
-                self.policy_lanes.observe(len(inp) - 1, k, share, confidence=conf[0] if conf else -1.0)
+        for inp, k, conf in zip(inputs, accepted, confs):
+            self.policy_lanes.observe(len(inp) - 1, k, share, confidence=conf[0] if conf else -1.0)
         self.totals["rounds"] += 1
         self.totals["spec_rounds"] += 1
         self.totals["spec_lane_rounds"] += 1
@@ -828,6 +831,15 @@ class NativeBackend(Backend):
                 self.lanes.update(a.req.rid, a.req.max_tokens - a.emitted, a.pos)
                 keep.append(a)
         self.active = keep
+
+    @staticmethod
+    def _gate(policy):
+        """(verification width the policy wants before drafting, whether that answer is one of its periodic probes).  A
+        probe's width is handed to the round, whose second look at the policy - with the drafter's confidence - would
+        otherwise cut the proposal to nothing and leave the probe without an observation."""
+        before = policy.probe()
+        width = policy.choose()
+        return width, policy.probe() > before
 
     # ------------------------------------------------------------------ decode rounds
     def _graph_for(self, rows: int):
@@ -853,13 +865,15 @@ class NativeBackend(Backend):
         acts = self.active
         if len(acts) == 1 and acts[0].spec:
             a = acts[0]
-            if a.req.max_tokens - a.emitted > 1 and self.policy.choose() > 0:
-                return self._spec_round(a)
+            gate, probe = self._gate(self.policy) if a.req.max_tokens - a.emitted > 1 else (0, False)
+            if gate > 0:
+                return self._spec_round(a, gate if probe else 0)
             self.totals["policy_plain_rounds"] += 1
         elif 1 < len(acts) <= self.spec_lanes and all(a.spec for a in acts) \
                 and (len(acts) + 1) * self.spec.width <= e.max_rows:
-            if self.policy_lanes.choose() > 0:
-                return self._spec_round_lanes(acts)
+            gate, probe = self._gate(self.policy_lanes)
+            if gate > 0:
+                return self._spec_round_lanes(acts, gate if probe else 0)
             self.totals["policy_plain_rounds"] += 1
         e.set_rows([a.last for a in acts], [a.pos for a in acts], [a.slot for a in acts])
         if self.use_graphs:

@@ -399,3 +399,41 @@ def test_a_request_cancelled_between_shared_rounds_leaves_the_others_exact(cpu_s
         assert be.totals["spec_lane_rounds"] > 0
     finally:
         be.close()
+
+
+def test_probe_rounds_bring_speculation_back_when_drafts_become_right(cpu_sampler):
+    """A policy that gave up on drafting answers every few decisions with a probe; the probe round keeps its width through
+    the second, confidence-conditioned look, so its outcome is observed and speculation resumes once drafts are accepted."""
+    from ds41rt_b200.runtime import core as K
+    eng = FakeEngine(slots=2, max_rows=64)
+    be = NativeBackend(eng, eos=1, concurrency=2, prefill_chunk=64, use_graphs=False)
+    try:
+        spec = FakeSpec(eng, wrong_every=1)               # every proposed token is wrong
+        spec.last_confidence = [0.5] * spec.width         # a confidence head: the round asks the policy a second time
+        be.policy, be.policy_lanes = K.DSparkPolicy(max_width=4, warmup_rounds=4), K.DSparkPolicy(max_width=4)
+        be.policy.probe(8)
+        for w in (4, 0, 2, 4, 0, 2):                      # the cost side of the model: 1000 us + 150 us per row (a CPU
+            be.policy.observe(w, 0, 1000 + 150 * (1 + w), 20.0 * w)       # engine has no device clock to learn it from)
+        be.spec = spec
+        sampled = Sampling(temperature=0.7, seed=11)      # not the all-device round: drafts are read back and cut
+        r = GenRequest(prompt_ids=list(range(10, 50)), max_tokens=120, sampling=sampled)
+        be.submit(r)
+        toks, status = _run(be, [r])[0]
+        assert status == "length" and len(toks) == 120
+        t1 = dict(be.totals)
+        assert t1["policy_plain_rounds"] > 20 and be.policy.probe() >= 2      # it gave up, then probed
+        verified_while_wrong = spec.calls["verify"]
+        spec.wrong_every = 10 ** 9                        # from now on every draft is right
+        _idle(be)
+        be.snapshots.clear()
+        r2 = GenRequest(prompt_ids=list(range(60, 100)), max_tokens=200, sampling=sampled)
+        be.submit(r2)
+        toks2, status2 = _run(be, [r2])[0]
+        assert status2 == "length" and len(toks2) == 200
+        t2 = be.totals
+        # accepted probes switched speculation back on: far fewer rounds than tokens for the second request
+        assert t2["spec_tokens"] - t1["spec_tokens"] > 100
+        assert (t2["rounds"] - t1["rounds"]) < 150 and spec.calls["verify"] > verified_while_wrong
+        assert be.policy.choose() > 0
+    finally:
+        be.close()
