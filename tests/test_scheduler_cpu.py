@@ -437,3 +437,25 @@ def test_probe_rounds_bring_speculation_back_when_drafts_become_right(cpu_sample
         assert be.policy.choose() > 0
     finally:
         be.close()
+
+
+def test_a_request_that_does_not_fit_waits_for_a_retirement(cpu_sampler):
+    """With requests active and the page pool short, a new request is parked, not refused: it is admitted when an
+    earlier request retires and then runs to completion.  A cancelled parked request never starts."""
+    eng = FakeEngine(slots=3, max_ctx=512, n_pages=7)        # 64-token pages: room for two of the requests below
+    be = NativeBackend(eng, eos=1, concurrency=3, prefill_chunk=64, prompt_snapshots=0, turn_snapshots=0)
+    try:
+        a, b, c = _req(range(10, 150), 40), _req(range(200, 340), 40), _req(range(400, 540), 12)
+        for r in (a, b, c):
+            be.submit(r)
+        d = _req(range(600, 740), 12)
+        be.submit(d)
+        d.cancelled.set()                                     # queued behind the parked one and cancelled before it starts
+        got = _run(be, [a, b, c])
+        assert [s for _, s in got] == ["length"] * 3 and [len(t) for t, _ in got] == [40, 40, 12]
+        assert be.healthy and be.totals["failed"] == 0
+        _idle(be)
+        assert eng.cache.free_pages == eng.cache.n_pages and be.pending is None
+        assert d.events.empty() or all(ev.kind != "tokens" for ev in list(d.events.queue))
+    finally:
+        be.close()
