@@ -459,3 +459,47 @@ def test_a_request_that_does_not_fit_waits_for_a_retirement(cpu_sampler):
         assert d.events.empty() or all(ev.kind != "tokens" for ev in list(d.events.queue))
     finally:
         be.close()
+
+
+def test_stop_tokens_end_a_request_inside_a_shared_round_like_in_plain_decoding(cpu_sampler):
+    """A stop token that the drafter proposed correctly must not be 'accepted and walked past': the request ends at it,
+    in a shared speculative round exactly as in a plain step."""
+    from ds41rt_b200.runtime import core as K
+
+    def chain(prompt, n):
+        tok, pos, out = FakeSpec.rule(prompt[-1], len(prompt) - 1), len(prompt), []
+        out.append(tok)
+        while len(out) < n:
+            tok = FakeSpec.rule(tok, pos)
+            pos += 1
+            out.append(tok)
+        return out
+
+    prompts = [list(range(10, 50)), list(range(60, 93)), list(range(200, 247))]
+    stops = [chain(prompts[0], 40)[6], chain(prompts[1], 40)[11], chain(prompts[2], 40)[1]]
+
+    def run(with_spec):
+        eng = FakeEngine(slots=4, max_rows=64)
+        be = NativeBackend(eng, eos=1, concurrency=4, prefill_chunk=64, use_graphs=False)
+        try:
+            if with_spec:
+                be.policy, be.policy_lanes = K.DSparkPolicy(max_width=4), K.DSparkPolicy(max_width=4)
+                be.spec_lanes = 4
+                be.spec = FakeSpec(eng, wrong_every=10 ** 9)          # every draft is right: stops sit inside accepted runs
+            reqs = [GenRequest(prompt_ids=p, max_tokens=40, sampling=Sampling(), stop_ids=[s])
+                    for p, s in zip(prompts, stops)]
+            for r in reqs:
+                be.submit(r)
+            out = _run(be, reqs)
+            assert be.healthy, be.error
+            return out, dict(be.totals)
+        finally:
+            be.close()
+
+    plain, _ = run(False)
+    spec, totals = run(True)
+    assert plain == spec and totals["spec_lane_rounds"] > 0
+    for (toks, status), p, s in zip(spec, prompts, stops):
+        want = chain(p, 40)
+        cut = want.index(s)
+        assert status == "stop" and toks == want[:cut]               # the stop token itself is not delivered
