@@ -15,6 +15,9 @@
   selftest                   build and run the native self-test of the host runtime library (C ABI, no Python between)
   bench-kernels / campaign / prefill-matrix / validate-bench / convert-checkpoint / convert-engram-table
                              the tools of ds41rt_b200.utils, loader.convert and runtime.ple_convert under one entry
+  select-gpus                which GPUs of this node have room for an N-rank launch (reads nvidia-smi only)
+  source-manifest            write / verify the sha256 manifest of the source tree; identity of tree and toolchain
+  release-report             results report (tables, scaling, clocks, provenance) recomputed from raw bench records
 
 `serve` reads its options in three tiers: a KEY=VALUE settings file (`--settings`, default ./ds41rt.config), the
 environment (DS41RT_<KEY>) and the command line, later tiers overriding earlier ones (ds41rt_b200/settings.py).
@@ -90,6 +93,8 @@ def cmd_doctor(args) -> int:
         out = subprocess.run([nvcc, "--version"], capture_output=True, text=True).stdout
         rep["nvcc"] = out.strip().splitlines()[-1] if out else nvcc
     rep["libraries"] = {n: (build.LIBDIR / n).exists() for n in ("libds41_kernels.so", "libds41_core.so")}
+    rep["libraries_match_sources"] = {n: st["current"] for n, st in build.library_status().items()}
+    rep["stale_sources"] = sorted(s for st in build.library_status().values() for s in st.get("stale", []))
     try:
         from .runtime import core as K
         K.core()
@@ -378,7 +383,8 @@ def _forward(module: str):
 FORWARDED = {"bench-kernels": ".utils.kernel_case", "campaign": ".utils.http_campaign",
              "prefill-matrix": ".utils.prefill_matrix", "validate-bench": ".utils.validate_bench",
              "convert-checkpoint": ".loader.convert", "convert-engram-table": ".runtime.ple_convert",
-             "engram-io-bench": ".runtime.engram_io"}
+             "engram-io-bench": ".runtime.engram_io", "select-gpus": ".utils.select_gpus",
+             "source-manifest": ".utils.source_manifest", "release-report": ".utils.release_report"}
 
 
 def _engram_table_meta(args, i: int) -> dict:
@@ -526,6 +532,11 @@ def cmd_serve(args) -> int:
 
 
 def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] in FORWARDED:                         # a tool parses its own options, leading flags included
+        import importlib
+        rest = argv[2:] if argv[1:2] == ["--"] else argv[1:]
+        return int(importlib.import_module(FORWARDED[argv[0]], __package__).main(rest) or 0)
     ap = argparse.ArgumentParser(prog="ds41rt_b200")
     sub = ap.add_subparsers(dest="cmd", required=True)
 

@@ -27,6 +27,9 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-I", str(CSRC / "include"),
 ]
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-pthread", "-I", str(CSRC / "include")]
+# the same flags without the checkout's own path, for identities that must agree between two checkouts of one tree
+NVCC_FLAGS_PORTABLE = NVCC_FLAGS[:-1] + ["csrc/include"]
+CXX_FLAGS_PORTABLE = CXX_FLAGS[:-1] + ["csrc/include"]
 
 
 def _nvcc() -> str:
@@ -60,10 +63,10 @@ def _build_lib(name: str, sources, compiler_cmd, link_cmd, verbose: bool) -> Pat
     objs = []
     for src in sources:
         tag = _digest(src, " ".join(compiler_cmd))
-        obj = OBJDIR / f"{src.stem}.{tag}.o"
+        obj = OBJDIR / f"{src.name}.{tag}.o"                 # full file name: engram.cu and engram.cc are two sources
         objs.append(obj)
         if not obj.exists():
-            for old in OBJDIR.glob(f"{src.stem}.*.o"):
+            for old in OBJDIR.glob(f"{src.name}.*.o"):
                 old.unlink()
             jobs.append((compiler_cmd + ["-c", str(src), "-o", str(obj)], src, obj))
     out = LIBDIR / name
@@ -78,18 +81,47 @@ def _build_lib(name: str, sources, compiler_cmd, link_cmd, verbose: bool) -> Pat
     return out
 
 
-def build_kernels(verbose: bool = False) -> Path:
+def _kernel_recipe(verbose: bool = False):
     nvcc = _nvcc()
-    sources = sorted((CSRC / "kernels").glob("*.cu"))
     flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if verbose else [])
-    return _build_lib("libds41_kernels.so", sources, [nvcc] + flags,
-                      [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"], verbose)
+    return sorted((CSRC / "kernels").glob("*.cu")), [nvcc] + flags
+
+
+def _core_recipe():
+    cxx = shutil.which("g++") or "g++"
+    return sorted((CSRC / "core").glob("*.cc")), [cxx] + CXX_FLAGS
+
+
+def build_kernels(verbose: bool = False) -> Path:
+    sources, cmd = _kernel_recipe(verbose)
+    return _build_lib("libds41_kernels.so", sources, cmd,
+                      [cmd[0], "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"], verbose)
 
 
 def build_core(verbose: bool = False) -> Path:
-    cxx = shutil.which("g++") or "g++"
-    sources = sorted((CSRC / "core").glob("*.cc"))
-    return _build_lib("libds41_core.so", sources, [cxx] + CXX_FLAGS, [cxx, "-shared", "-pthread"], verbose)
+    sources, cmd = _core_recipe()
+    return _build_lib("libds41_core.so", sources, cmd, [cmd[0], "-shared", "-pthread"], verbose)
+
+
+def library_status() -> dict:
+    """Whether each built library matches the sources beside it, without compiling anything: a library is `current`
+    when it exists, an object named by the digest of (source, headers, compile command) exists for every source, and
+    the library is not older than any of them.  `stale` lists the sources whose object is missing (edited since the
+    build, or built with other flags or another compiler)."""
+    out = {}
+    for name, recipe in (("libds41_kernels.so", _kernel_recipe), ("libds41_core.so", _core_recipe)):
+        lib = LIBDIR / name
+        try:
+            sources, cmd = recipe()
+        except RuntimeError as e:                            # no compiler here: the digests cannot be formed
+            out[name] = {"exists": lib.exists(), "current": None, "reason": str(e)}
+            continue
+        objs = {src.name: OBJDIR / f"{src.name}.{_digest(src, ' '.join(cmd))}.o" for src in sources}
+        stale = sorted(n for n, o in objs.items() if not o.exists())
+        newest = max((o.stat().st_mtime for o in objs.values() if o.exists()), default=0.0)
+        current = lib.exists() and not stale and lib.stat().st_mtime >= newest
+        out[name] = {"exists": lib.exists(), "current": current, "sources": len(sources), "stale": stale}
+    return out
 
 
 def build_selftest() -> Path:

@@ -33,6 +33,13 @@ REQUIRED = {"metric": str, "value": (int, float), "unit": str, "n_gpus": int, "s
             "ms_per_step": (int, float), "higher_is_better": bool, "scaling": str, "dtype": str, "data": str,
             "config": dict, "clocks": dict, "e2e": dict, "gpu_launches": int}
 BAD_REASONS = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown")
+VOLATILE_CONFIG = ("setup_s", "context_at_end")             # differ between two runs of one configuration (set-up time;
+                                                            # where the context stood after a time-boxed repeat count)
+
+
+def stable_config(cfg: dict) -> dict:
+    """The part of a record's `config` that identifies the workload (run-to-run timings of the set-up removed)."""
+    return {k: v for k, v in cfg.items() if k not in VOLATILE_CONFIG}
 
 
 def check_record(r: dict) -> Tuple[List[str], List[str]]:
@@ -125,9 +132,13 @@ def check_set(records: List[dict], tolerance: float = 0.05, expect_gpus: int = 0
     if full:
         head = full[0]
         for i, r in enumerate(full[1:], 1):
-            for k in ("metric", "unit", "n_gpus", "config", "dtype", "higher_is_better"):
+            for k in ("metric", "unit", "n_gpus", "dtype", "higher_is_better"):
                 if r[k] != head[k]:
                     errors.append(f"record {i}: `{k}` differs from record 0")
+            a, b = stable_config(r["config"]), stable_config(head["config"])
+            if a != b:
+                keys = sorted(k for k in set(a) | set(b) if a.get(k) != b.get(k))
+                errors.append(f"record {i}: `config` differs from record 0 in {', '.join(keys)}")
         if expect_gpus and head["n_gpus"] != expect_gpus:
             errors.append(f"n_gpus {head['n_gpus']} != expected {expect_gpus}")
         vals = [r["value"] for r in full]
