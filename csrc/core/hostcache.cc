@@ -159,6 +159,22 @@ int ds41_hostcache_restore(void* p, int64_t id, int32_t* host_pages, int cap) {
   return n;
 }
 
+// The first `n_first` pages of a snapshot, for a prompt that shares only a leading part with it.  Only those pages are
+// charged to the restore budget.  Returns n_first, 0 when deferred, -1 when absent or shorter than asked.
+int ds41_hostcache_restore_prefix(void* p, int64_t id, int n_first, int32_t* host_pages, int cap) {
+  HostCache* c = static_cast<HostCache*>(p);
+  auto it = c->snaps.find(id);
+  if (it == c->snaps.end()) { ++c->misses; return -1; }
+  if (n_first < 0 || n_first > cap || n_first > static_cast<int>(it->second.pages.size())) return -1;
+  if (c->restore_used + static_cast<uint64_t>(n_first) * c->page_bytes > c->restore_budget) { ++c->deferred; return 0; }
+  c->restore_used += static_cast<uint64_t>(n_first) * c->page_bytes;
+  for (int i = 0; i < n_first; ++i) host_pages[i] = it->second.pages[i];
+  it->second.clock = ++c->clock;
+  c->restored_pages += static_cast<uint64_t>(n_first);
+  ++c->hits;
+  return n_first;
+}
+
 int ds41_hostcache_contains(void* p, int64_t id) { return static_cast<HostCache*>(p)->snaps.count(id) ? 1 : 0; }
 int ds41_hostcache_drop(void* p, int64_t id) {
   HostCache* c = static_cast<HostCache*>(p);

@@ -61,6 +61,7 @@ void ds41_hostcache_free(void* p);
 int ds41_hostcache_store(void* p, int64_t id, const uint64_t* keys, int n, uint64_t tokens, int32_t* host_pages,
                          uint8_t* need_copy);
 int ds41_hostcache_restore(void* p, int64_t id, int32_t* host_pages, int cap);
+int ds41_hostcache_restore_prefix(void* p, int64_t id, int n_first, int32_t* host_pages, int cap);
 int ds41_hostcache_contains(void* p, int64_t id);
 int ds41_hostcache_check(void* p);
 void* ds41_engram_history_new(uint32_t pad_id);
@@ -262,6 +263,14 @@ static void host_cache_and_engram_history() {
   CHECK(ds41_hostcache_store(c, 3, kc, 3, 192, pages, need) == 3 && ds41_hostcache_check(c) == 0);
   CHECK(!ds41_hostcache_contains(c, 1) || !ds41_hostcache_contains(c, 2));
   CHECK(ds41_hostcache_restore(c, 77, pages, 4) == -1);
+  CHECK(ds41_hostcache_restore_prefix(c, 3, 2, pages, 4) == 2 && ds41_hostcache_restore_prefix(c, 3, 4, pages, 4) == -1);
+  CHECK(ds41_hostcache_restore_prefix(c, 77, 1, pages, 4) == -1 && ds41_hostcache_check(c) == 0);
+  ds41_hostcache_free(c);
+  // the restore budget is charged for the pages asked for, not for the whole snapshot
+  c = ds41_hostcache_new(4, 4096, 1ull << 40, 2 * 4096);
+  CHECK(ds41_hostcache_store(c, 1, ka, 3, 192, pages, need) == 3);
+  CHECK(ds41_hostcache_restore(c, 1, pages, 4) == 0 && ds41_hostcache_restore_prefix(c, 1, 2, pages, 4) == 2);
+  CHECK(ds41_hostcache_restore_prefix(c, 1, 1, pages, 4) == 0);
   ds41_hostcache_free(c);
   void* h = ds41_engram_history_new(2);
   const int32_t toks[4] = {5, 6, 7, 8};

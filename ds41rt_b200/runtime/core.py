@@ -366,6 +366,12 @@ class HostCache:
         r = core().ds41_hostcache_restore(self.h, C.c_int64(sid), pages, cap)
         return r, list(pages[:max(r, 0)])
 
+    def restore_prefix(self, sid: int, n_first: int):
+        """The first `n_first` host pages of a snapshot; only they are charged to the restore budget."""
+        pages = (C.c_int32 * max(n_first, 1))()
+        r = core().ds41_hostcache_restore_prefix(self.h, C.c_int64(sid), n_first, pages, max(n_first, 1))
+        return r, list(pages[:max(r, 0)])
+
     def contains(self, sid: int) -> bool:
         return bool(core().ds41_hostcache_contains(self.h, C.c_int64(sid)))
 

@@ -432,15 +432,29 @@ class NativeBackend(Backend):
 
     # ------------------------------------------------------------------ prefix reuse (radix-driven snapshot banks)
     def _restore_prefix(self, slot: int, prompt: List[int], need: int):
-        """Device banks first; a demoted snapshot in the host tier is taken when it reuses more tokens."""
+        """Device banks first; a demoted snapshot in the host tier is taken when it reuses more tokens, whether the
+        prompt extends it (continued from its end) or only shares a leading part with it (rows up to the cut)."""
         tier = self.host_tier
         hit = tier.lookup(prompt) if tier is not None else None
-        if hit is not None:
-            sid, n, has_logits = hit
+        part = tier.lookup_partial(prompt) if tier is not None and hit is None and self.partial_reuse else None
+        dev_n = 0
+        if hit is not None or part is not None:
             dev = self.prefix.lookup(prompt)
-            dev_n = 0
             if dev is not None and dev["id"] in self.snapshots:
                 dev_n = dev["frontier"] if dev["exact"] else max(0, dev["common"] // 2 * 2 - self.e.cfg.window)
+        if part is not None and part[1] > dev_n:
+            # only a leading part is shared: its rows come back from the host, the last window before the cut is replayed
+            sid, n = part
+            self.e.cache.release(slot)
+            if self._ensure_pages(slot, n) and tier.restore_prefix_into(slot, sid, n) and self._ensure_pages(slot, need):
+                self.totals["host_tier_hits"] += 1
+                self.totals["partial_prefix_hits"] += 1
+                return n, None, n
+            self.e.cache.release(slot)
+            if not self._ensure_pages(slot, need):
+                raise MemoryError("KV pool cannot hold this request")
+        if hit is not None:
+            sid, n, has_logits = hit
             usable = n < len(prompt) or (n == len(prompt) and has_logits)
             if usable and n > dev_n:
                 self.e.cache.release(slot)

@@ -234,6 +234,93 @@ def test_demoted_snapshots_come_back_from_the_host_tier(cpu_sampler):
         be.close()
 
 
+def test_a_prompt_that_shares_only_a_leading_part_reuses_host_pages_up_to_the_cut(cpu_sampler):
+    """Demoted snapshots also serve prompts that diverge from them: the rows of the shared part minus one window come
+    back from the host (whole pages below the cut, the cut page only up to the cut - out of a host page, or out of the
+    snapshot's partly filled last page), the window before the cut is replayed, and only the pages read are budgeted."""
+    eng = FakeEngine(slots=2, max_ctx=512, n_pages=10)
+    be = NativeBackend(eng, eos=1, concurrency=2, prefill_chunk=64, host_cache_bytes=4 << 20)
+    cache, tier = eng.cache, be.host_tier
+    W, P = eng.cfg.window, cache.page_tokens
+    assert (W, P) == (32, 64)
+    try:
+        long_, short = [1000 + i for i in range(130)], [3000 + i for i in range(114)]     # 2 pages + 2; 1 page + 50
+        stamps = {}
+        for name, prompt in (("long", long_), ("short", short)):
+            r = _req(prompt, max_tokens=3)
+            be.submit(r)
+            assert _run(be, [r])[0][1] == "length"
+            _idle(be)
+            (toks, snap, _), = [v for v in be.snapshots.values() if len(v[0]) == len(prompt)]
+            for src, pr in cache.page_rows.items():
+                for n, pg in enumerate(snap.pages):
+                    rows = cache.comp[src][pg * pr:(pg + 1) * pr]
+                    rows.copy_((torch.arange(pr).float()[:, None] + 100 * n + 1000 * src + 7).expand_as(rows))
+                    cache.idx[src][pg * pr:(pg + 1) * pr] = -cache.comp[src][pg * pr:(pg + 1) * pr, :cache.idx[src].shape[1]]
+                c, ix = snap.partial[src]
+                c.copy_((torch.arange(c.shape[0]).float()[:, None] + 5000 + 1000 * src).expand_as(c))
+                ix.copy_(-c[:, :ix.shape[1]])
+                stamps[(name, src)] = ([cache.comp[src][pg * pr:(pg + 1) * pr].clone() for pg in snap.pages], c.clone())
+        big = _req([7 + i for i in range(440)], max_tokens=60)           # page pressure: both snapshots are demoted
+        be.submit(big)
+        assert _run(be, [big])[0][1] == "length"
+        _idle(be)
+        assert be.totals["snapshots_demoted"] >= 2
+        for sid in list(be.snapshots):                                   # nothing on the "device" can serve the prompts
+            be._drop_snapshot(sid)
+        for pool in list(cache.comp.values()) + list(cache.idx.values()):
+            pool.zero_()
+        restored0 = tier.stats()["restored"]
+
+        def diverging(base, common, tag):
+            prompt = base[:common] + [9000 + tag * 100 + i for i in range(30)]
+            hits0, partial0, passes0 = be.totals["prompt_cache_hit_tokens"], be.totals["partial_prefix_hits"], eng.passes
+            r = _req(prompt, max_tokens=2)
+            be.submit(r)
+            assert _run(be, [r])[0][1] == "length"
+            _idle(be)
+            cut = common // 2 * 2 - W
+            assert be.totals["prompt_cache_hit_tokens"] - hits0 == cut
+            assert be.totals["partial_prefix_hits"] - partial0 == 1
+            # the prompt snapshot and the turn snapshot of the finished request share the restored pages
+            snap = [v[1] for v in be.snapshots.values() if tuple(v[0][:len(prompt)]) == tuple(prompt)][0]
+            return cut, snap, eng.passes - passes0
+
+        # 1) the cut (78) falls into the long snapshot's second whole page: page 0 whole, 14 positions of page 1
+        cut, snap, passes = diverging(long_, 110, 1)
+        assert cut == 78 and be.totals["host_tier_hits"] == 1
+        for src, pr in cache.page_rows.items():
+            whole, _ = stamps[("long", src)]
+            rows = (14 * pr + P - 1) // P
+            p0, p1 = snap.pages[0], snap.pages[1]
+            assert torch.equal(cache.comp[src][p0 * pr:(p0 + 1) * pr], whole[0])
+            assert torch.equal(cache.idx[src][p0 * pr:(p0 + 1) * pr], -whole[0][:, :cache.idx[src].shape[1]])
+            assert torch.equal(cache.comp[src][p1 * pr:p1 * pr + rows], whole[1][:rows])
+            assert not cache.comp[src][p1 * pr + rows:(p1 + 1) * pr].any()            # nothing beyond the cut came along
+        assert tier.stats()["restored"] - restored0 == 2 and tier.stats()["promoted_partial"] == 1
+        assert passes >= 2                                               # replay of [78, 110) + the new tokens + decode
+        # 2) the cut (80) falls into the short snapshot's partly filled last page: one host page + 16 kept positions
+        restored1 = tier.stats()["restored"]
+        cut, snap, _ = diverging(short, 112, 2)
+        assert cut == 80 and be.totals["host_tier_hits"] == 2
+        for src, pr in cache.page_rows.items():
+            whole, part = stamps[("short", src)]
+            rows = (16 * pr + P - 1) // P
+            p0, p1 = snap.pages[0], snap.pages[1]
+            assert torch.equal(cache.comp[src][p0 * pr:(p0 + 1) * pr], whole[0])
+            assert torch.equal(cache.comp[src][p1 * pr:p1 * pr + rows], part[:rows])
+            assert not cache.comp[src][p1 * pr + rows:(p1 + 1) * pr].any()
+        assert tier.stats()["restored"] - restored1 == 1
+        # 3) a shared part shorter than one window is not worth a restore
+        hits0 = be.totals["host_tier_hits"]
+        r = _req(long_[:30] + [8000 + i for i in range(20)], max_tokens=2)
+        be.submit(r)
+        assert _run(be, [r])[0][1] == "length"
+        assert be.totals["host_tier_hits"] == hits0 and tier.hc.check() == 0
+    finally:
+        be.close()
+
+
 class FakeSpec:
     """Stand-in for runtime.speculative.SpecSession over the CPU engine above: the "drafter" knows the engine's token
     rule and proposes the true continuation, except that every `wrong_every`-th proposed token is off by one."""

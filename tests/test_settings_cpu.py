@@ -1,6 +1,7 @@
 """Settings tiers, the KV pool plan and the operator commands (no GPU)."""
 import argparse
 import json
+import re
 import subprocess
 import sys
 
@@ -138,4 +139,5 @@ def test_stop_script_ends_the_recorded_process_group(tmp_path):
 
 def test_native_selftest_of_the_host_runtime_passes():
     rc, out = _cli("selftest")
-    assert rc == 0 and "ok 67 checks" in out and "FAILED" not in out
+    done = re.search(r"ok (\d+) checks", out)
+    assert rc == 0 and done and int(done.group(1)) >= 72 and "FAILED" not in out
