@@ -98,11 +98,11 @@ class EngramPipeline:
         """Continue `slot` from a stored history (the counterpart of a KV snapshot restore)."""
         self.hist[slot] = hist.fork()
 
-    def reset(self, slot: int, tokens: Sequence[int]) -> None:
-        """Start `slot` from a history that has seen `tokens` (text only): used when a request continues from a
-        stored KV snapshot of those tokens."""
+    def reset(self, slot: int, tokens: Sequence[int], is_image: Optional[Sequence[bool]] = None) -> None:
+        """Start `slot` from a history that has seen `tokens` (`is_image` marks image rows among them): used when a
+        request continues from a stored KV snapshot of those tokens."""
         h = EngramHistory(self.pad)
-        comp = [self.compress(t) for t in tokens]
+        comp = [self.compress(t, bool(is_image[i]) if is_image is not None else False) for i, t in enumerate(tokens)]
         h.commit(comp, len(comp))
         self.hist[slot] = h
 

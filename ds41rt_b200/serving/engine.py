@@ -20,6 +20,7 @@ import numpy as np
 
 from ..runtime import core as K
 from ..runtime.grammar import TokenConstraint
+from .imagekeys import ImageKeySpace
 from .protocol import Sampling
 
 
@@ -34,6 +35,7 @@ class GenRequest:
     cancelled: threading.Event = field(default_factory=threading.Event)
     rid: int = 0
     images: List[Any] = field(default_factory=list)     # (PreparedImage, [prompt positions of its rows]) in order
+    image_keys: Any = None    # set at admission: what the prefix banks compare at the image positions (None: not banked)
 
 
 @dataclass
@@ -189,6 +191,7 @@ class NativeBackend(Backend):
         self.snapshots: Dict[int, tuple] = {}
         # pinned-host tier behind the banks: a snapshot that leaves the device (bank eviction, page pressure) is copied
         # there and comes back when a prompt extends it (runtime/hosttier.py)
+        self.image_keys = ImageKeySpace()
         self.host_tier = None
         if host_cache_bytes > 0:
             from ..runtime.hosttier import HostSnapshotTier
@@ -208,7 +211,7 @@ class NativeBackend(Backend):
                        "prompt_cache_hit_tokens": 0, "snapshots": 0, "spec_rounds": 0, "spec_tokens": 0,
                        "ced_prefills": 0, "partial_prefix_hits": 0, "snapshots_evicted_for_pages": 0,
                        "graph_rounds": 0, "prefill_passes": 0, "spec_masked_rounds": 0, "policy_plain_rounds": 0,
-                       "cancelled_in_prefill": 0, "snapshots_demoted": 0, "host_tier_hits": 0, "spec_lane_rounds": 0}
+                       "cancelled_in_prefill": 0, "snapshots_demoted": 0, "host_tier_hits": 0, "image_encodes_skipped": 0, "spec_lane_rounds": 0}
         self._rid = 0
         self._stop = threading.Event()
         self._ready = threading.Event()
@@ -242,6 +245,8 @@ class NativeBackend(Backend):
             out["dspark_policy_shared_rounds"] = self.policy_lanes.stats()
         if self.host_tier is not None:
             out["host_cache"] = self.host_tier.stats()
+        if self.supports_images:
+            out["image_keys"] = self.image_keys.stats()
         return out
 
     def close(self) -> None:
@@ -312,11 +317,12 @@ class NativeBackend(Backend):
 
     def _finish(self, a: _Active, reason: str):
         self.totals["completion_tokens"] += a.emitted
-        if reason in ("stop", "length") and a.emitted > 1 and not a.req.images:
+        if reason in ("stop", "length") and a.emitted > 1 and (not a.req.images or a.req.image_keys is not None):
             # turn bank: the cache holds the prompt and every emitted token but the last one.  Stored before the
             # finish event leaves, so a client that reacts to the event finds the bank as it will stay.
             try:
-                self._store_snapshot(a.slot, list(a.req.prompt_ids) + a.tokens[:-1], None, K.PrefixBanks.TURN)
+                self._store_snapshot(a.slot, self._match_ids(a.req, list(a.req.prompt_ids) + a.tokens[:-1]), None,
+                                     K.PrefixBanks.TURN)
             except Exception:
                 pass
         self._release(a.slot, a.req)
@@ -414,8 +420,10 @@ class NativeBackend(Backend):
             req.events.put(Event("error", status=503, message="KV pool cannot hold this request"))
             self.totals["failed"] += 1
             return False
-        reused, snap_logits, replay_from = (0, None, None) if req.images \
-            else self._restore_prefix(slot, req.prompt_ids, need)
+        if req.images:
+            req.image_keys = self.image_keys.prepare(req.prompt_ids, req.images)
+        reused, snap_logits, replay_from = (0, None, None) if req.images and req.image_keys is None \
+            else self._restore_prefix(slot, self._match_ids(req, req.prompt_ids), need)
         first_new = reused
         if replay_from is not None:
             # a truncated snapshot: its compressed rows reach up to the common prefix's even boundary
@@ -431,6 +439,12 @@ class NativeBackend(Backend):
         return False
 
     # ------------------------------------------------------------------ prefix reuse (radix-driven snapshot banks)
+    @staticmethod
+    def _match_ids(req: GenRequest, tokens: List[int]) -> List[int]:
+        """What the banks compare for `tokens` of this request: the tokens themselves, with the placeholder positions of
+        every image replaced by that image's key (serving/imagekeys.py).  The model always gets the real tokens."""
+        return req.image_keys.encode(tokens) if req.image_keys else tokens
+
     def _restore_prefix(self, slot: int, prompt: List[int], need: int):
         """Device banks first; a demoted snapshot in the host tier is taken when it reuses more tokens, whether the
         prompt extends it (continued from its end) or only shares a leading part with it (rows up to the cut)."""
@@ -522,16 +536,22 @@ class NativeBackend(Backend):
         self.snapshots[sid] = (key, self.e.cache.snapshot(slot, len(key)), logits)
         self.totals["snapshots"] += 1
 
-    def _image_rows(self, req: GenRequest):
-        """Run the vision tower over the request's images -> (rows [n, H] bf16, prompt position of every row)."""
+    def _image_rows(self, req: GenRequest, first: int = 0):
+        """Run the vision tower over the request's images -> (rows [n, H] bf16, prompt position of every row), or
+        (None, None) when no image reaches into the positions from `first` on (all of them restored from a snapshot)."""
         import torch
         rows, positions = [], []
         for image, pos in req.images:
+            if pos and max(pos) < first:                      # its rows are in the restored cache already
+                self.totals["image_encodes_skipped"] += 1
+                continue
             out = self.vision.encode(torch.from_numpy(image.patches), image.grid)
             if out.shape[0] != len(pos):
                 raise ValueError("image placeholders do not match the image grid")
             rows.append(out.clone())
             positions += list(pos)
+        if not rows:
+            return None, None
         return torch.cat(rows, 0).contiguous(), positions
 
     # ------------------------------------------------------------------ prompt passes, one per scheduler iteration
@@ -542,13 +562,14 @@ class NativeBackend(Backend):
         e = self.e
         toks = req.prompt_ids
         pf = _Prefill(req, slot, gen, [], solo=solo, logits=logits, floor=replay_from)
+        first = start if replay_from is None else replay_from
         if req.images:
             if self.vision is None:
                 raise ValueError("this server has no vision tower")
-            pf.img_rows, pf.img_pos = self._image_rows(req)
-        first = start if replay_from is None else replay_from
+            pf.img_rows, pf.img_pos = self._image_rows(req, first)     # images below `first` are not encoded again
         if self.engram is not None:
-            self.engram.reset(slot, toks[:first])
+            at = {p for _, pos in req.images for p in pos if p < first}
+            self.engram.reset(slot, toks[:first], [i in at for i in range(first)] if at else None)
         end, step = len(toks), self.prefill_chunk
         # passes never straddle `start`: below it the compressed sources are kept, from it on they are produced
         cuts = [(c0, min(hi, c0 + step), hi == end) for lo, hi in ((first, start), (start, end))
@@ -630,8 +651,8 @@ class NativeBackend(Backend):
             pf.logits = e.logits_rows(e.last_head_row + 1)[e.last_head_row].clone()
             if pf.ced:
                 self.totals["ced_prefills"] += 1
-            if not req.images:                                # placeholders look alike: image prompts are not banked
-                self._store_snapshot(slot, req.prompt_ids, pf.logits, K.PrefixBanks.PROMPT)
+            if not req.images or req.image_keys is not None:  # image prompts are banked under their image keys
+                self._store_snapshot(slot, self._match_ids(req, req.prompt_ids), pf.logits, K.PrefixBanks.PROMPT)
         first = self._select([req], [0], logits=pf.logits.view(1, -1))[0]
         a = _Active(req, slot, pf.gen, pos=len(req.prompt_ids), last=first, spec=pf.solo)
         if pf.solo and not self.active and req.sampling.greedy and req.constraint is None:

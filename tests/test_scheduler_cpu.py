@@ -321,6 +321,89 @@ def test_a_prompt_that_shares_only_a_leading_part_reuses_host_pages_up_to_the_cu
         be.close()
 
 
+class FakeVision:
+    """Stand-in for the vision tower: one row per placeholder, counted."""
+
+    def __init__(self, hidden):
+        self.hidden, self.encodes = hidden, 0
+
+    def encode(self, patches, grid):
+        self.encodes += 1
+        return torch.zeros(grid[0] * grid[1], self.hidden)
+
+
+def _image(tag, rows=40):
+    from ds41rt_b200.serving.images import PreparedImage
+    import numpy as np
+    return PreparedImage(patches=np.full((rows, 12), float(tag), dtype=np.float32), grid=(rows, 1), rows=rows,
+                         identity=f"picture-{tag}")
+
+
+def test_prompts_with_images_are_banked_under_the_identity_of_their_pictures(cpu_sampler):
+    """Placeholder tokens look alike, so the banks compare image keys at their positions: the same picture under the
+    same text is a cache hit (and is not encoded again when all of its rows were restored), another picture at the same
+    place shares only the text before it, and a text prompt with the bare placeholder token matches neither."""
+    from ds41rt_b200.serving.imagekeys import FIRST_IMAGE_KEY, ImageKeySpace
+    eng = FakeEngine(slots=2, max_ctx=512)
+    vis = FakeVision(eng.cfg.hidden)
+    be = NativeBackend(eng, eos=1, concurrency=2, prefill_chunk=64, vision=vis)
+    IMG, W = 5, eng.cfg.window
+    head, tail = [100 + i for i in range(50)], [300 + i for i in range(30)]
+
+    def ask(image, extra=(), first=50, text_only=False):
+        prompt = head + [IMG] * 40 + tail + list(extra)
+        r = _req(prompt, max_tokens=3)
+        if not text_only:
+            r.images = [(image, list(range(first, first + 40)))]
+        hits0, enc0 = be.totals["prompt_cache_hit_tokens"], vis.encodes
+        be.submit(r)
+        toks, status = _run(be, [r])[0]
+        assert status == "length"
+        _idle(be)
+        return toks, be.totals["prompt_cache_hit_tokens"] - hits0, vis.encodes - enc0
+
+    try:
+        cat, dog = _image(1), _image(2)
+        cold, hit, enc = ask(cat)
+        assert hit == 0 and enc == 1 and be.stats()["image_keys"] == {"live": 1, "issued": 1, "forgotten": 0}
+        # the stored keys carry the image key at the picture's positions and real tokens elsewhere
+        key, = {v[0][50] for v in be.snapshots.values()}
+        assert key >= FIRST_IMAGE_KEY and all(v[0][49] == 149 and v[0][90] == 300 for v in be.snapshots.values())
+        # same picture, longer text: everything up to the end of the stored turn is reused, nothing is encoded
+        again, hit, enc = ask(cat, extra=cold[:2] + [777, 778])
+        assert hit == 120 + 2 and enc == 0 and be.totals["image_encodes_skipped"] == 1
+        # another picture at the same place: only the text before it (minus one window, replayed) is shared
+        other, hit, enc = ask(dog)
+        assert hit == 50 // 2 * 2 - W and enc == 1 and be.totals["partial_prefix_hits"] == 1
+        assert other == cold                                              # the stand-in engine ignores pixels
+        # the same picture again after the other one: full hit on its own snapshot (logits included: no pass at all)
+        same, hit, enc = ask(cat)
+        assert same == cold and hit == 120 and enc == 0
+        # the bare placeholder token in a text prompt is not an image: it shares the text before the picture only
+        _, hit, enc = ask(None, text_only=True)
+        assert hit == 50 // 2 * 2 - W and enc == 0
+        assert be.stats()["image_keys"]["issued"] == 2
+    finally:
+        be.close()
+    # the key space: keys are single-use, a forgotten picture comes back under a new key, bad spans are not keyed
+    ks = ImageKeySpace(capacity=2)
+    toks = [9] * 8
+    k1 = ks.prepare(toks, [(_image(1), [0, 1])]).bindings[0][1]
+    k2 = ks.prepare(toks, [(_image(2), [2, 3])]).bindings[0][1]
+    assert ks.prepare(toks, [(_image(1), [4])]).bindings == [(4, k1)]
+    ks.prepare(toks, [(_image(3), [5])])                                    # capacity 2: picture 2 is forgotten
+    k2b = ks.prepare(toks, [(_image(2), [2])]).bindings[0][1]
+    assert len({k1, k2, k2b}) == 3 and k2b > k2 and ks.stats()["forgotten"] >= 1
+    both = ks.prepare(toks, [(_image(1), [0, 1]), (_image(1), [4, 5])])
+    assert both.encode(toks)[:6] == [both.bindings[0][1]] * 2 + [9, 9] + [both.bindings[0][1]] * 2
+    assert both.encode(toks[:1]) == [both.bindings[0][1]]
+    assert ks.prepare(toks, [(_image(1), [7, 8])]) is None                  # outside the prompt
+    assert ks.prepare(toks, [(_image(1), [0]), (_image(2), [0])]) is None   # one position, two pictures
+    assert ks.prepare([9, 8], [(_image(1), [0, 1])]) is None                # different placeholder tokens
+    ks.next = (1 << 32)
+    assert ks.prepare(toks, [(_image(7), [0])]) is None                     # key range used up: not banked
+
+
 class FakeSpec:
     """Stand-in for runtime.speculative.SpecSession over the CPU engine above: the "drafter" knows the engine's token
     rule and proposes the true continuation, except that every `wrong_every`-th proposed token is off by one."""
