@@ -37,6 +37,9 @@ void ds41_policy_free(void* p);
 void ds41_policy_observe(void* h, int width, int n_accepted, double verify_us, double draft_us, double confidence);
 int ds41_policy_choose(void* h, double confidence);
 uint64_t ds41_policy_probe(void* h, int every);
+void ds41_policy_observe_round(void* h, int total_rows, int n_requests, double round_us);
+void ds41_policy_observe_positions(void* h, const float* conf, int width, int n_accepted);
+int ds41_policy_choose_joint(void* h, const float* conf, const int* offsets, int n_req, int* widths);
 int ds41_ple_scan(const uint8_t* src, uint64_t rows, int dim, int src_row_bytes, int threads, float* amax);
 float ds41_ple_global_scale(float amax);
 int ds41_ple_convert(const uint8_t* src, uint64_t rows, int dim, int src_row_bytes, float global, uint8_t* dst,
@@ -167,6 +170,22 @@ static void policy() {
   int probes = 0;
   for (int i = 0; i < 12; ++i) probes += ds41_policy_choose(p, -1.0) > 0;
   CHECK(probes == 3 && ds41_policy_probe(p, -1) == 3);
+  ds41_policy_free(p);
+  // a shared round: rows go to the request whose drafts are likely to be kept; a round with cheap rows takes them all
+  p = ds41_policy_new(4, 0);
+  const float sure[4] = {0.95f, 0.95f, 0.95f, 0.95f}, doubt[4] = {0.05f, 0.05f, 0.05f, 0.05f};
+  for (int i = 0; i < 200; ++i) {
+    ds41_policy_observe(p, 4, 4, -1.0, 0.0, 0.95);
+    ds41_policy_observe_positions(p, sure, 4, 4);
+    ds41_policy_observe(p, 4, 0, -1.0, 0.0, 0.05);
+    ds41_policy_observe_positions(p, doubt, 4, 0);
+    ds41_policy_observe_round(p, 2 + (i % 5) * 2, 2, 1000.0 + 400.0 * (2 + (i % 5) * 2));
+  }
+  const float conf[8] = {0.95f, 0.95f, 0.95f, 0.95f, 0.05f, 0.05f, 0.05f, 0.05f};
+  const int offs[3] = {0, 4, 8};
+  int widths[2] = {-1, -1};
+  CHECK(ds41_policy_choose_joint(p, conf, offs, 2, widths) == widths[0] + widths[1]);
+  CHECK(widths[0] >= 3 && widths[1] == 0);
   ds41_policy_free(p);
   std::printf("verification policy ok\n");
 }

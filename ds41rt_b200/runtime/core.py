@@ -320,6 +320,31 @@ class DSparkPolicy:
     def acceptance(self, depth: int) -> float:
         return float(core().ds41_policy_acceptance(self.h, depth))
 
+    # ---- rounds shared by several requests
+    def choose_joint(self, confidences: Sequence[Sequence[float]]) -> List[int]:
+        """Verification length of every request of one shared round, from the drafter's confidence in each proposed
+        token: maximises expected committed tokens per predicted round time over all requests together."""
+        n = len(confidences)
+        offs, flat = [0], []
+        for c in confidences:
+            flat += [float(x) for x in c]
+            offs.append(len(flat))
+        conf = (C.c_float * max(len(flat), 1))(*flat)
+        offsets = (C.c_int * (n + 1))(*offs)
+        widths = (C.c_int * max(n, 1))()
+        core().ds41_policy_choose_joint(self.h, conf, offsets, n, widths)
+        return [int(widths[i]) for i in range(n)]
+
+    def observe_round(self, total_rows: int, n_requests: int, round_us: float):
+        core().ds41_policy_observe_round(self.h, total_rows, n_requests, C.c_double(round_us))
+
+    def observe_positions(self, confidence: Sequence[float], width: int, accepted: int):
+        """Calibrate the confidence head on every position a verification reached."""
+        w = min(width, len(confidence))
+        if w > 0:
+            core().ds41_policy_observe_positions(self.h, (C.c_float * w)(*[float(x) for x in confidence[:w]]), w,
+                                                 min(accepted, w))
+
     def probe(self, every: int = -1) -> int:
         """Set how often a policy that chose plain decoding answers with a two-draft probe instead (0 = never; -1 leaves
         the cadence as it is); returns the number of probes so far."""
@@ -331,9 +356,15 @@ class DSparkPolicy:
         out = (C.c_double * 8)()
         hist = (C.c_uint64 * 16)()
         core().ds41_policy_stats(self.h, out, hist)
+        j = (C.c_double * 6)()
+        jc = (C.c_uint64 * 2)()
+        core().ds41_policy_joint_stats(self.h, j, jc)
         return {"rounds": int(out[0]), "t_fixed_us": out[1], "t_row_us": out[2], "draft_us_per_row": out[3],
                 "platt": [out[4], out[5]], "acceptance_first": out[6], "acceptance_last": out[7],
-                "accepted_histogram": list(hist)}
+                "accepted_histogram": list(hist),
+                "joint": {"rounds": int(j[5]), "round_fixed_us": j[0], "round_us_per_row": j[1], "fit_weight": j[2],
+                          "platt_positions": [j[3], j[4]], "draft_rows_offered": int(jc[0]),
+                          "draft_rows_taken": int(jc[1])}}
 
 
 class HostCache:

@@ -813,10 +813,13 @@ class NativeBackend(Backend):
             ev0.record()
         proposals, confs = sp.draft_host_groups([a.slot for a in acts], [a.last for a in acts], [a.pos for a in acts])
         inputs, masks, reqs, positions, slots_rows, toks_rows = [], [], [], [], [], []
-        for a, drafts, conf in zip(acts, proposals, confs):
+        # with a confidence head the lengths of all requests are chosen together (one pass pays for all rows)
+        widths = self.policy_lanes.choose_joint([c[: len(d)] for d, c in zip(proposals, confs)]) \
+            if confs and all(confs) else None
+        for i, (a, drafts, conf) in enumerate(zip(acts, proposals, confs)):
             r = a.req
-            if conf:
-                drafts = drafts[: max(self.policy_lanes.choose(conf[0]), gate, 0)]
+            if widths is not None:
+                drafts = drafts[: max(widths[i], gate, 0)]
             if r.constraint is not None:
                 drafts = r.constraint.truncate_proposal(drafts)
             drafts = drafts[: max(0, min(len(drafts), r.max_tokens - a.emitted - 1))]
@@ -849,6 +852,10 @@ class NativeBackend(Backend):
             share = ev0.elapsed_time(ev1) * 1e3 / len(acts)
         for inp, k, conf in zip(inputs, accepted, confs):
             self.policy_lanes.observe(len(inp) - 1, k, share, confidence=conf[0] if conf else -1.0)
+            if conf:
+                self.policy_lanes.observe_positions(conf, len(inp) - 1, k)
+        if timed:
+            self.policy_lanes.observe_round(n_rows, len(acts), share * len(acts))
         self.totals["rounds"] += 1
         self.totals["spec_rounds"] += 1
         self.totals["spec_lane_rounds"] += 1

@@ -1,4 +1,5 @@
 """Host runtime: admission, lanes, dSpark policy, host snapshot cache with a stub copy engine (no GPU)."""
+import math
 import random
 
 import pytest
@@ -29,6 +30,65 @@ def test_lanes_balance_and_round_plan():
     l2.add(13, remaining=3, history=500)       # never verify more rows than tokens remain
     assert l2.plan_round(0, draft_len=4, max_rows=64, min_history=16) == [(10, 5), (11, 1), (12, 1), (13, 3)]
     assert l2.plan_round(0, draft_len=4, max_rows=7, min_history=16) == [(10, 5), (11, 1), (12, 1)]
+
+
+def test_joint_policy_spends_rows_where_they_are_likely_to_be_kept():
+    """Lengths of a shared round are chosen together: the round costs A + B x rows, so rows go to the positions most
+    likely to be committed, and the choice equals an exhaustive search over all length combinations."""
+    import itertools
+    rng = random.Random(1)
+    pol = K.DSparkPolicy(max_width=4, warmup_rounds=8)
+    assert pol.choose_joint([[0.9] * 4, [0.1] * 3]) == [4, 3]                   # warm-up: verify everything offered
+    # world: a draft with confidence c is right with probability c (chains stop at the first wrong one);
+    # a shared round of R rows takes 2000 + 400 R microseconds
+    def play(confs, widths):
+        out = []
+        for c, w in zip(confs, widths):
+            k = 0
+            while k < w and rng.random() < c[k]:
+                k += 1
+            out.append(k)
+        return out
+    for _ in range(600):
+        confs = [[rng.choice([0.15, 0.5, 0.95])] * 4 for _ in range(rng.randint(2, 4))]
+        widths = [rng.randint(0, 4) for _ in confs]
+        rows = sum(1 + w for w in widths)
+        for c, w, k in zip(confs, widths, play(confs, widths)):
+            pol.observe(w, k, -1.0, confidence=c[0] if w else -1.0)
+            pol.observe_positions(c, w, k)
+        pol.observe_round(rows, len(confs), 2000.0 + 400.0 * rows)
+    st = pol.stats()["joint"]
+    assert abs(st["round_fixed_us"] - 2000.0) < 1.0 and abs(st["round_us_per_row"] - 400.0) < 0.5 and st["rounds"] == 600
+    # calibration: the fitted curve orders and roughly places the three confidence levels
+    a, b = st["platt_positions"]
+    cal = lambda c: 1.0 / (1.0 + math.exp(-(a * c + b)))
+    assert cal(0.15) < 0.35 and 0.3 < cal(0.5) < 0.7 and cal(0.95) > 0.8
+    sure, unsure = [0.95] * 4, [0.15] * 4
+    got = pol.choose_joint([sure, unsure, [0.5] * 4])
+    assert got[0] >= 3 and got[1] == 0 and got[0] >= got[2] >= got[1]
+    # the same objective by brute force, with the policy's own probabilities
+    def prob(c, depth):
+        return 0.5 * pol.acceptance(depth) + 0.5 * cal(c)
+    def value(confs, widths):
+        tokens = sum(1 + sum(math.prod(prob(c[j], j + 1) for j in range(k + 1)) for k in range(w))
+                     for c, w in zip(confs, widths))
+        return tokens / (st["round_fixed_us"] + st["round_us_per_row"] * sum(1 + w for w in widths))
+    for confs in ([sure, unsure, [0.5] * 4], [[0.95, 0.5, 0.5, 0.15], [0.5, 0.95, 0.95, 0.95]], [unsure, unsure]):
+        best = max(itertools.product(range(5), repeat=len(confs)), key=lambda ws: value(confs, ws))
+        got = pol.choose_joint(confs)
+        assert value(confs, got) >= value(confs, best) * (1 - 1e-6), (confs, got, best)
+    # a chain is only as good as its weakest earlier link: sure drafts behind an unlikely one count for little
+    weak_first, strong = pol.choose_joint([[0.05, 0.99, 0.99, 0.99], [0.95] * 4] * 2)[:2]
+    assert weak_first < strong
+    # expensive rows (a pass dominated by per-row work) make the policy stingy, cheap rows generous
+    dear, cheap = K.DSparkPolicy(max_width=4, warmup_rounds=0), K.DSparkPolicy(max_width=4, warmup_rounds=0)
+    for rows in (2, 4, 6, 8, 10):
+        dear.observe_round(rows, 2, 10.0 + 1000.0 * rows)
+        cheap.observe_round(rows, 2, 5000.0 + 1.0 * rows)
+    mid = [[0.6] * 4, [0.6] * 4]
+    assert sum(cheap.choose_joint(mid)) == 8 and sum(dear.choose_joint(mid)) < 8
+    assert pol.stats()["joint"]["draft_rows_taken"] <= pol.stats()["joint"]["draft_rows_offered"]
+    assert pol.choose_joint([]) == [] and pol.choose_joint([[]]) == [0]
 
 
 def test_policy_matches_exhaustive_search_after_warmup():

@@ -1,5 +1,6 @@
 """The serving scheduler on a CPU stand-in for the engine: real page allocator, prefix banks and scheduler loop, a pass
 that only derives a token from its inputs.  Failures are injected on the host (a pass that raises, a pool too small)."""
+import math
 import queue
 import time
 
@@ -408,8 +409,8 @@ class FakeSpec:
     """Stand-in for runtime.speculative.SpecSession over the CPU engine above: the "drafter" knows the engine's token
     rule and proposes the true continuation, except that every `wrong_every`-th proposed token is off by one."""
 
-    def __init__(self, eng, width=5, wrong_every=3):
-        self.e, self.width, self.wrong_every = eng, width, wrong_every
+    def __init__(self, eng, width=5, wrong_every=3, confident=False):
+        self.e, self.width, self.wrong_every, self.confident = eng, width, wrong_every, confident
         self.last_confidence = []
         self.proposed = 0
         self.calls = {"draft_groups": 0, "verify_groups": 0, "draft": 0, "verify": 0, "feed": 0}
@@ -436,7 +437,18 @@ class FakeSpec:
 
     def draft_host_groups(self, slots, anchors, positions):
         self.calls["draft_groups"] += 1
-        return [self._propose(a, p) for a, p in zip(anchors, positions)], [[] for _ in slots]
+        props = [self._propose(a, p) for a, p in zip(anchors, positions)]
+        if not self.confident:
+            return props, [[] for _ in slots]
+        # a confidence head that knows: high where the proposal is the true continuation, low where it is off
+        confs = []
+        for a, p, prop in zip(anchors, positions, props):
+            tok, c = a, []
+            for j, t in enumerate(prop):
+                c.append(0.95 if t == self.rule(tok, p + j) else 0.05)
+                tok = t
+            confs.append(c + [0.5])
+        return props, confs
 
     def verify_host_groups(self, slots, inputs, positions):
         self.calls["verify_groups"] += 1
@@ -511,6 +523,52 @@ def test_shared_speculative_rounds_emit_exactly_the_plain_tokens(cpu_sampler):
         _idle(be)
     finally:
         be.close()
+
+
+def test_shared_rounds_verify_fewer_rows_when_the_drafter_says_where_it_is_unsure(cpu_sampler):
+    """With a confidence head the lengths of a shared round are chosen together from the per-position confidences:
+    rows behind a draft the head doubts are not verified, the tokens stay exactly the plain ones, and a larger share of
+    the verified drafts is kept than without the head."""
+    from ds41rt_b200.runtime import core as K
+
+    def serve(confident):
+        eng = FakeEngine(slots=4, max_rows=64)
+        be = NativeBackend(eng, eos=1, concurrency=4, prefill_chunk=64, use_graphs=False)
+        try:
+            spec = FakeSpec(eng, confident=confident)
+            be.policy = K.DSparkPolicy(max_width=4)
+            be.policy_lanes = pol = K.DSparkPolicy(max_width=4, warmup_rounds=4)
+            # what a timed engine would have taught the policy (the CPU stand-in has no device clock): a request's
+            # share of a round is dominated by its fixed part, a shared round costs 1000 + 300 us per row
+            for w in (0, 1, 2, 3, 4, 4, 2):
+                pol.observe(w, w, 1000.0 + 10.0 * (1 + w))
+            for rows in (3, 6, 9, 12, 15):
+                pol.observe_round(rows, 3, 1000.0 + 300.0 * rows)
+            be.spec_lanes = 4
+            be.spec = spec
+            prompts = [list(range(10, 50)), list(range(60, 93)), list(range(200, 247))]
+            reqs = [_req(p, 60) for p in prompts]
+            for r in reqs:
+                be.submit(r)
+            got = _run(be, reqs)
+            assert be.healthy, be.error
+            _idle(be)
+            return [g[0] for g in got], be.policy_lanes.stats(), dict(be.totals)
+        finally:
+            be.close()
+
+    plain_toks, plain_stats, plain_totals = serve(False)
+    toks, stats, totals = serve(True)
+    assert toks == plain_toks and all(len(t) == 60 for t in toks)
+    j = stats["joint"]
+    assert j["draft_rows_offered"] > 0 and j["draft_rows_taken"] < j["draft_rows_offered"]
+    assert plain_stats["joint"]["draft_rows_offered"] == 0            # no head: the joint choice is never asked
+    assert totals["spec_lane_rounds"] > 0 and j["draft_rows_taken"] > 0
+    # rows the head doubted were not verified: of the draft rows that were, a larger share was kept than with no head
+    accepted = lambda st: sum(i * n for i, n in enumerate(st["accepted_histogram"]))
+    assert (accepted(stats) - 16) / j["draft_rows_taken"] > 0.7      # 16: the accepted drafts of the taught rounds
+    a, b = stats["joint"]["platt_positions"]
+    assert 1 / (1 + math.exp(-(a * 0.95 + b))) > 1 / (1 + math.exp(-(a * 0.05 + b)))    # the calibration learnt the head
 
 
 def test_prefill_matrix_tool_reports_cold_and_retained_rows(cpu_sampler):

@@ -140,4 +140,4 @@ def test_stop_script_ends_the_recorded_process_group(tmp_path):
 def test_native_selftest_of_the_host_runtime_passes():
     rc, out = _cli("selftest")
     done = re.search(r"ok (\d+) checks", out)
-    assert rc == 0 and done and int(done.group(1)) >= 72 and "FAILED" not in out
+    assert rc == 0 and done and int(done.group(1)) >= 74 and "FAILED" not in out
