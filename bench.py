@@ -58,6 +58,19 @@ def reference_arm():
     return 0
 
 
+def _provenance():
+    """Digests of the sources this record was measured from (whole tree, kernel sources, host runtime, package), so a
+    report can say which code a number belongs to.  Never fails the run: None when the tree cannot be read."""
+    try:
+        from ds41rt_b200.utils import source_manifest as sm
+        d = sm.digests(sm.Path(__file__).resolve().parent)
+        part = lambda prefix: sm.tree_digest({k: h for k, h in d.items() if k.startswith(prefix)})[:16]
+        return {"tree": sm.tree_digest(d)[:16], "kernels": part("./csrc/kernels/"), "core": part("./csrc/core/"),
+                "headers": part("./csrc/include/"), "python": part("./ds41rt_b200/")}
+    except Exception:
+        return None
+
+
 def baseline_fields(value: float, base, n_layers: int) -> dict:
     """Ratios against a published 40-layer number: the plain ratio only for the full stack."""
     if base is None:
@@ -270,6 +283,7 @@ def prefill_bench(args, fabric, cfg, n_layers):
                     "h2d_bytes_per_step": 12 * P * NP, "d2h_bytes_per_step": 4 * chunks * NP},
             "gpu_launches": per_step * K * len(all_ms), "impl": "ours",
         }
+        line["source"] = _provenance()
         print(json.dumps(line))
     fabric.barrier()
     return 0
@@ -367,6 +381,7 @@ def concurrent_bench(args, fabric, cfg, n_layers):
                     "d2h_bytes_per_step": sess.d2h_bytes // max(e2e_steps, 1)},
             "gpu_launches": per_pass * K * len(all_ms), "impl": "ours",
         }
+        line["source"] = _provenance()
         print(json.dumps(line))
     fabric.barrier()
     return 0
@@ -584,6 +599,7 @@ def main():
             "gpu_launches": launches,
             "impl": "ours",
         }
+        line["source"] = _provenance()
         print(json.dumps(line))
     fabric.barrier()
     return 0

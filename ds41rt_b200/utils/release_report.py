@@ -15,8 +15,9 @@ over from an earlier report.  What is rendered:
 * scaling      for a workload measured at several GPU counts with the same model: speed-up over the smallest count
                and efficiency (speed-up / GPU ratio), recomputed here from the per-count medians;
 * clocks       median SM clock under load, its maximum and the active reasons per group;
-* provenance   sha256 of every record file, and the identity of the tree that renders the report (source digest, git
-               commit, compilers; `source_manifest.identity`).
+* provenance   sha256 of every record file, the source digests the records carry (`bench.py` writes them under
+               `source`; a group measured from more than one tree is called out), and the identity of the tree that
+               renders the report (source digest, git commit, compilers; `source_manifest.identity`).
 
 Counterpart of the reference's release renderers and provenance scripts (scripts/render-ds41-v7-headline.py: cells from
 raw records, "-" instead of estimates, disclosure notes; scripts/summarize-ds41-upstream-release.py;
@@ -114,7 +115,11 @@ def summarise(recs: List[dict], tolerance: float = 0.05) -> List[dict]:
                    "ok": gate["ok"], "errors": gate["errors"], "warnings": gate["warnings"],
                    "files": sorted({r["_file"] for r in arms["ours"]}), "_key": key,
                    "value": None, "ms_per_step": None, "e2e": None, "spread": None, "vs_baseline": None,
-                   "clocks": None, "reference": None, "reference_note": None}
+                   "clocks": None, "reference": None, "reference_note": None,
+                   "sources": sorted({json.dumps(r["source"], sort_keys=True) for r in arms["ours"]
+                                      if isinstance(r.get("source"), dict)})}
+            if len(row["sources"]) > 1:
+                row["warnings"] = row["warnings"] + ["records of this group were measured from different source trees"]
             if gate["ok"]:
                 good = arms["ours"]
                 row.update(value=gate["median"], spread=gate["spread"], e2e=gate["e2e_median"],
@@ -206,6 +211,17 @@ def render(rows: List[dict], shas: Dict[str, str], identity: Optional[dict] = No
                      f"{', '.join(c['reasons']) or 'none'} |")
     L += ["", "## Provenance", "", "| record file | sha256 |", "|---|---|"]
     L += [f"| {Path(p).name} | `{h}` |" for p, h in sorted(shas.items())]
+    srcs = sorted({s for r in rows for s in r.get("sources", [])})
+    if srcs:
+        L += ["", "Source digests carried by the records (whole tree / kernel sources / host runtime / headers / package):", ""]
+        for s in srcs:
+            d = json.loads(s)
+            used = sorted({f"{r['metric']} at {r['n_gpus']} GPU(s)" for r in rows if s in r.get("sources", [])})
+            L.append(f"* `{d.get('tree')}` / `{d.get('kernels')}` / `{d.get('core')}` / `{d.get('headers')}` / "
+                     f"`{d.get('python')}`: " + "; ".join(used))
+        mixed = [f"{r['metric']} at {r['n_gpus']} GPU(s)" for r in rows if len(r.get("sources", [])) > 1]
+        if mixed:
+            L += ["", "Measured from more than one source tree: " + "; ".join(mixed) + "."]
     if identity:
         git = identity.get("git") or {}
         L += ["", f"Rendered from source tree `{identity.get('tree')}` ({identity.get('files')} files)"

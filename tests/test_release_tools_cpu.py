@@ -241,6 +241,28 @@ def test_report_recomputes_medians_scaling_and_ratios(tmp_path):
     assert "| 400.0 | tok/s |" in text and "| 100.0 | 4.00x |" in text and "2.00x over 1 | 25 %" in text
     assert "reference arm unavailable: needs RTX workers" in text and "with uncommitted changes" in text
     assert "n1.log" in text and shas[str(f1)] in text and "sw_power_cap" in text
+    assert "Source digests" not in text                                          # these records carry none
+
+
+def test_report_names_the_source_digests_the_records_carry(tmp_path):
+    a, b, c = record(1, 400.0), record(1, 401.0), record(8, 800.0)
+    src = {"tree": "t1", "kernels": "k1", "core": "c1", "headers": "h1", "python": "p1"}
+    a["source"], b["source"], c["source"] = src, dict(src, kernels="k2", tree="t2"), src
+    rows = R.summarise(R.load([write_lines(tmp_path / "r.log", [a, b, c])])[0])
+    assert len(rows[0]["sources"]) == 2 and len(rows[1]["sources"]) == 1
+    assert any("different source trees" in w for w in rows[0]["warnings"])
+    text = R.render(rows, {})
+    assert "`t1` / `k1` / `c1` / `h1` / `p1`" in text and "`t2` / `k2`" in text
+    assert "Measured from more than one source tree: decode tok/s C1 at 1 GPU(s)." in text
+    # bench.py's own helper: digests of this checkout, stable between two calls
+    sys.path.insert(0, str(ROOT))
+    try:
+        import bench
+        got = bench._provenance()
+    finally:
+        sys.path.remove(str(ROOT))
+    assert got == bench._provenance() and set(got) == {"tree", "kernels", "core", "headers", "python"}
+    assert got["kernels"] == M.identity(ROOT)["kernels"]["sources"][:16]
 
 
 def test_report_leaves_a_cell_empty_when_the_gate_rejects_its_records(tmp_path):
