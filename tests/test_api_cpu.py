@@ -316,3 +316,44 @@ def test_campaign_tool_drives_mixed_traffic_through_the_server():
     assert out["completion_tokens"] > 0 and out["tok_per_s"] > 0 and out["ttft_s"]["median"] is not None
     follow = [g for g in be.submitted if "Now shorter" in TK.decode(g.prompt_ids) and "Request" in TK.decode(g.prompt_ids)]
     assert follow, "a follow-up turn carries the earlier exchange in its prompt"
+
+
+def test_api_smoke_battery_passes_on_a_conforming_server_and_names_what_fails():
+    """The operator's protocol battery over scripted servers: every check passes where the server's answer fits it, a
+    check whose promise the answer breaks is reported by name and fails the run."""
+    from ds41rt_b200.utils import api_smoke as S
+    general = ["health", "stats", "chat", "stream", "length", "stop", "seed", "bad_request", "prefix"]
+    srv, _ = serve("one two three four five six seven", queue_depth=8, waiters=4)
+    try:
+        url = f"http://127.0.0.1:{srv.port}"
+        out = S.run(url, max_tokens=48, only=general)
+        assert out["ok"] and out["passed"] == len(general) + 1, out          # + models, which always runs
+        notes = {r["check"]: r["note"] for r in out["checks"]}
+        assert "cut at 16 of 33" in notes["stop"] and notes["length"] == "1 token" and "5 malformed" in notes["bad_request"]
+        # the whole battery against this server: the plain text breaks the JSON and tool promises, and only those
+        out = S.run(url, max_tokens=48)
+        assert not out["ok"] and out["failed"] == ["json_object", "json_schema", "tools"]
+        assert S.main(["--url", url, "--only", "chat,stream", "--json"]) == 0
+        assert S.main(["--url", url, "--only", "tools"]) == 1
+    finally:
+        srv.stop()
+    srv, _ = serve('{"city": "Paris", "days": 3, "metric": true}', queue_depth=8, waiters=4)
+    try:
+        out = S.run(f"http://127.0.0.1:{srv.port}", only=["json_object", "json_schema"])
+        assert out["ok"] and out["passed"] == 3
+    finally:
+        srv.stop()
+    srv, _ = serve('{"city": "Paris", "days": "three"}', queue_depth=8, waiters=4)      # wrong type: the server refuses
+    try:
+        out = S.run(f"http://127.0.0.1:{srv.port}", only=["json_schema"])
+        assert out["failed"] == ["json_schema"] and "status 500" in out["checks"][-1]["note"]
+    finally:
+        srv.stop()
+    srv, _ = serve("Let me check.\n" + C.render_tool_call("get_weather", {"city": "Paris", "days": 3}),
+                   queue_depth=8, waiters=4)
+    try:
+        out = S.run(f"http://127.0.0.1:{srv.port}", only=["tools"], max_tokens=400)
+        assert out["ok"] and '"city": "Paris"' in out["checks"][-1]["note"]
+    finally:
+        srv.stop()
+    assert S.run("http://127.0.0.1:9", only=["health"], timeout=2.0)["failed"] == ["health", "models"]   # nobody listens
