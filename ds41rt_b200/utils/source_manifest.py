@@ -5,10 +5,10 @@
     python -m ds41rt_b200.utils.source_manifest identity [--root DIR]
 
 `write` lists every build-relevant file under the root as `<sha256>  ./<path>` (sorted, the format `sha256sum -c`
-reads).  Left out: version control, caches, built artefacts (`*.so`, `*.o`, the object cache), working folders, the
-launcher's pid and log files, and the installed reference arm.  `verify` recomputes the inventory and fails on any file
-that is missing, changed, or present but not listed, on a malformed or duplicate line and on a path that leaves the
-root; a symlink is followed only when it stays inside the root and names a regular file.  `identity` prints one JSON
+reads).  Left out: version control, caches, built artefacts (`*.so`, `*.o`, the object cache) and whatever the tree's
+own `.gitignore` leaves out of the repository (working folders, the launcher's pid and log files, fetched outputs).
+`verify` recomputes the inventory and fails on any file that is missing, changed, or present but not listed, on a
+malformed or duplicate line and on a path that leaves the root; a symlink is followed only when it stays inside the root and names a regular file.  `identity` prints one JSON
 document: the digest of the whole inventory, the digests of the kernel and host-runtime source sets together with the
 compile commands that turn them into the two libraries, the compiler versions, the git commit when there is one, and
 whether the built libraries match the sources (`build.library_status`).  Two trees with the same `tree` digest build the
@@ -30,12 +30,40 @@ from pathlib import Path, PurePosixPath
 from typing import Dict, List, Optional, Tuple
 
 LINE = re.compile(r"^([0-9a-f]{64})  (\./.+)$")
-SKIP_DIRS = frozenset({".git", "__pycache__", ".pytest_cache", ".hypothesis", ".mypy_cache", ".ruff_cache", ".claude",
-                       ".gpurun", "gpurun_out", "_work", "build", "obj"})
-SKIP_PATHS = frozenset({"baseline/_ref"})
+# always left out, whatever the tree says: version control, interpreter and tool caches, built objects
+SKIP_DIRS = frozenset({".git", "__pycache__", ".pytest_cache", ".hypothesis", ".mypy_cache", ".ruff_cache", "obj"})
 SKIP_SUFFIXES = (".pyc", ".pyo", ".so", ".o", ".a", ".cubin", ".fatbin", ".tmp")
-SKIP_FILES = frozenset({"ds41rt.pid", "ds41rt.log", "PROGRESS.jsonl", "COPYCHECK.json", "MEASURED_PEAKS.json",
-                        "ds41_core_selftest"})
+
+
+class Ignore:
+    """The tree's own `.gitignore`, read for the pattern forms it uses: `name/` and `name` (anywhere), `/name` and
+    `dir/sub/` (from the root), `*.ext` and other single-star names; `#` comments.  Negations (`!`) are not supported
+    and raise, so that a manifest is never silently wider or narrower than the repository."""
+
+    def __init__(self, root: Path):
+        self.anywhere, self.rooted, self.globs = set(), set(), []
+        f = root / ".gitignore"
+        if not f.is_file():
+            return
+        for raw in f.read_text().splitlines():
+            pat = raw.strip()
+            if not pat or pat.startswith("#"):
+                continue
+            if pat.startswith("!"):
+                raise ManifestError(f".gitignore: negated pattern {pat!r} is not supported")
+            body = pat.rstrip("/")
+            if "*" in body or "?" in body or "[" in body:
+                self.globs.append(body.lstrip("/"))
+            elif "/" in body:
+                self.rooted.add(body.lstrip("/"))
+            else:
+                self.anywhere.add(body)
+
+    def match(self, rel: PurePosixPath) -> bool:
+        import fnmatch
+        if rel.name in self.anywhere or rel.as_posix() in self.rooted:
+            return True
+        return any(fnmatch.fnmatch(rel.name, g) or fnmatch.fnmatch(rel.as_posix(), g) for g in self.globs)
 
 
 class ManifestError(RuntimeError):
@@ -50,17 +78,18 @@ def file_sha256(path: Path) -> str:
     return h.hexdigest()
 
 
-def _skip_dir(rel: PurePosixPath) -> bool:
-    return rel.name in SKIP_DIRS or rel.name.endswith(".egg-info") or rel.as_posix() in SKIP_PATHS
+def _skip_dir(rel: PurePosixPath, ignore: Ignore) -> bool:
+    return rel.name in SKIP_DIRS or ignore.match(rel)
 
 
-def _skip_file(rel: PurePosixPath) -> bool:
-    return rel.name in SKIP_FILES or rel.name.endswith(SKIP_SUFFIXES)
+def _skip_file(rel: PurePosixPath, ignore: Ignore) -> bool:
+    return rel.name.endswith(SKIP_SUFFIXES) or ignore.match(rel)
 
 
 def inventory(root: Path, manifest_name: Optional[str] = None) -> Dict[str, Path]:
     """`./relative/path` -> file to hash, for every build-relevant file under `root`."""
     root = root.resolve()
+    ignore = Ignore(root)
     found: Dict[str, Path] = {}
     bad: List[str] = []
     for cur, dirs, files in os.walk(root, topdown=True, followlinks=False):
@@ -68,7 +97,7 @@ def inventory(root: Path, manifest_name: Optional[str] = None) -> Dict[str, Path
         keep = []
         for d in sorted(dirs):
             rel = PurePosixPath(*(rel_root / d).parts)
-            if _skip_dir(rel):
+            if _skip_dir(rel, ignore):
                 continue
             if (Path(cur) / d).is_symlink():
                 bad.append(f"./{rel.as_posix()} (directory symlink)")
@@ -77,7 +106,7 @@ def inventory(root: Path, manifest_name: Optional[str] = None) -> Dict[str, Path
         dirs[:] = keep
         for name in sorted(files):
             rel = PurePosixPath(*(rel_root / name).parts)
-            if _skip_file(rel) or (manifest_name and rel.as_posix() == manifest_name):
+            if _skip_file(rel, ignore) or (manifest_name and rel.as_posix() == manifest_name):
                 continue
             path = Path(cur) / name
             mode = path.lstat().st_mode

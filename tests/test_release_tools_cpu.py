@@ -120,6 +120,8 @@ def tree(tmp_path):
     (root / "pkg" / "lib.so").write_bytes(b"\x7fELF")
     (root / "_work" / "probe.py").write_text("print(1)\n")
     (root / "README.md").write_text("hello\n")
+    (root / "server.log").write_text("noise\n")
+    (root / ".gitignore").write_text("# working files\n/_work/\n*.log\n")
     return root
 
 
@@ -127,15 +129,31 @@ def test_manifest_lists_sources_only_and_verifies(tmp_path):
     root = tree(tmp_path)
     n, digest = M.write(root, root / "SOURCE-MANIFEST.sha256")
     lines = (root / "SOURCE-MANIFEST.sha256").read_text().splitlines()
-    assert n == 3 and [l.split("  ")[1] for l in lines] == ["./README.md", "./csrc/kernels/a.cu", "./pkg/m.py"]
+    assert n == 4 and [l.split("  ")[1] for l in lines] == ["./.gitignore", "./README.md", "./csrc/kernels/a.cu",
+                                                            "./pkg/m.py"]
     rep = M.verify(root, root / "SOURCE-MANIFEST.sha256")
-    assert rep["ok"] and rep["tree"] == digest and rep["files"] == 3
+    assert rep["ok"] and rep["tree"] == digest and rep["files"] == 4
     # the format is the one `sha256sum -c` reads
     chk = subprocess.run(["sha256sum", "-c", "--quiet", "SOURCE-MANIFEST.sha256"], cwd=root, capture_output=True)
     assert chk.returncode == 0
     # same content elsewhere -> same digest; built files and working folders do not enter it
     (root / "pkg" / "other.o").write_bytes(b"obj")
     assert M.tree_digest(M.digests(root, "SOURCE-MANIFEST.sha256")) == digest
+
+
+def test_manifest_covers_exactly_what_the_repository_tracks():
+    """What the tree's .gitignore leaves out is left out here too: the inventory of this checkout is git's file list."""
+    if not (ROOT / ".git").exists():
+        pytest.skip("not a git checkout")
+    def git(*a):
+        return set(subprocess.run(["git", "-C", str(ROOT), *a], capture_output=True, text=True).stdout.split("\n")) - {""}
+    tracked, untracked = git("ls-files"), git("ls-files", "--others", "--exclude-standard")
+    assert {k[2:] for k in M.inventory(ROOT)} == (tracked | untracked)
+    with pytest.raises(M.ManifestError, match="negated"):
+        import tempfile
+        with tempfile.TemporaryDirectory() as d:
+            (Path(d) / ".gitignore").write_text("*.log\n!keep.log\n")
+            M.inventory(Path(d))
 
 
 def test_manifest_reports_changed_missing_and_unlisted_files(tmp_path):
