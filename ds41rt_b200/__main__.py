@@ -18,6 +18,7 @@
   select-gpus                which GPUs of this node have room for an N-rank launch (reads nvidia-smi only)
   source-manifest            write / verify the sha256 manifest of the source tree; identity of tree and toolchain
   release-report             results report (tables, scaling, clocks, provenance) recomputed from raw bench records
+  audit-checkpoint           header-level audit of a checkpoint directory (structure, index agreement, identity digests)
   api-smoke                  protocol battery against a running server (health, chat, streaming, stop, seed, JSON, tools)
 
 `serve` reads its options in three tiers: a KEY=VALUE settings file (`--settings`, default ./ds41rt.config), the
@@ -386,7 +387,7 @@ FORWARDED = {"bench-kernels": ".utils.kernel_case", "campaign": ".utils.http_cam
              "convert-checkpoint": ".loader.convert", "convert-engram-table": ".runtime.ple_convert",
              "engram-io-bench": ".runtime.engram_io", "select-gpus": ".utils.select_gpus",
              "source-manifest": ".utils.source_manifest", "release-report": ".utils.release_report",
-             "api-smoke": ".utils.api_smoke"}
+             "api-smoke": ".utils.api_smoke", "audit-checkpoint": ".loader.audit"}
 
 
 def _engram_table_meta(args, i: int) -> dict:

@@ -282,3 +282,51 @@ def test_offline_conversion_to_the_nvfp4_variant_resumes_and_validates(tmp_path)
     eager = load_official(b)
     ref = w[name + ".weight"]
     assert float((eager[name + ".weight"] - ref).abs().max()) < 0.3 * float(ref.abs().max())
+
+
+def test_checkpoint_audit_reads_headers_only_and_names_what_is_inconsistent(tmp_path):
+    """The header-level audit: identity digests that do not depend on where the checkpoint lies, catalog agreement, and
+    a named error for an index that disagrees with the shards."""
+    import json
+    import shutil
+    from ds41rt_b200.loader.audit import AuditError, audit, main
+    cfg = ModelConfig.tiny()
+    src = str(tmp_path / "src")
+    export_official(cfg, init_weights(cfg, seed=2), src, variant="mxfp4", shards=3)
+    rep = audit(src, payload_hashes=True, cfg=cfg, variant="mxfp4", with_vision=False, with_engram=False)
+    assert rep["catalog"]["ok"] and len(rep["shards"]) == 3 and rep["tensors"] == sum(s["tensors"] for s in rep["shards"])
+    assert rep["shard_bytes"] > sum(rep["bytes_by_dtype"].values()) > 0 and "I8" in rep["bytes_by_dtype"]
+    assert all(len(s["file_sha256"]) == 64 for s in rep["shards"])
+    copy = str(tmp_path / "elsewhere")
+    shutil.copytree(src, copy)
+    again = audit(copy)
+    assert again["headers_sha256"] == rep["headers_sha256"] and again["index_sha256"] == rep["index_sha256"]
+    assert "file_sha256" not in again["shards"][0] and "catalog" not in again
+    assert audit(src, cfg=cfg, variant="nvfp4", with_vision=False, with_engram=False)["catalog"]["ok"] is False
+    assert main([src, "--model", "tiny", "--no-vision", "--no-engram"]) == 0
+    # an index that points a tensor at another shard, names a tensor nobody stores, or leaves the directory
+    idx_path = os.path.join(copy, "model.safetensors.index.json")
+    idx = json.load(open(idx_path))
+    names = sorted(idx["weight_map"])
+    shards = sorted(set(idx["weight_map"].values()))
+    bad = json.loads(json.dumps(idx))
+    bad["weight_map"][names[0]] = [s for s in shards if s != idx["weight_map"][names[0]]][0]
+    json.dump(bad, open(idx_path, "w"))
+    with pytest.raises(AuditError, match="the index says"):
+        audit(copy)
+    bad = json.loads(json.dumps(idx))
+    bad["weight_map"]["ghost.weight"] = shards[0]
+    json.dump(bad, open(idx_path, "w"))
+    with pytest.raises(AuditError, match="in no shard"):
+        audit(copy)
+    bad = json.loads(json.dumps(idx))
+    bad["weight_map"][names[0]] = "../" + shards[0]
+    json.dump(bad, open(idx_path, "w"))
+    with pytest.raises(AuditError, match="plain file name"):
+        audit(copy)
+    json.dump(idx, open(idx_path, "w"))
+    with open(os.path.join(copy, shards[0]), "ab") as f:                        # trailing bytes: the payload no longer tiles
+        f.write(b"\0" * 16)
+    with pytest.raises(AuditError, match="trailing bytes"):
+        audit(copy)
+    assert main([copy]) == 1
