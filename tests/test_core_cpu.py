@@ -60,6 +60,95 @@ def test_uniform_depends_only_on_seed_and_position():
     assert K.sample_uniform(8, 0) != a[0]
 
 
+def _sample_statement(logits, mask, temperature, top_k, top_p, min_p, u):
+    """The sampling contract written out with numpy, independently of the library: masked softmax at the temperature,
+    min_p against the best candidate, top-k (ties to the lower id), nucleus over what is left, inverse CDF at u."""
+    n = len(logits)
+    ok = np.ones(n, bool) if mask is None else np.array([(int(mask[i // 32]) >> (i % 32)) & 1 for i in range(n)], bool)
+    if temperature < 1e-5 or top_k == 1:
+        cand = np.where(ok)[0]
+        return int(cand[np.argmax(logits[cand])])                   # argmax returns the first (lowest id) maximum
+    scaled = (logits * np.float32(1.0 / np.float32(temperature))).astype(np.float32)
+    top = scaled[ok].max()
+    if min_p > 0:
+        ok = ok & (scaled >= np.float32(top + np.float32(np.log(np.float32(min_p)))))
+    cand = np.where(ok)[0]
+    u = min(max(float(np.float32(u)), 0.0), 0.99999994)
+    if top_k <= 0 and top_p >= 1.0:
+        w = np.exp((scaled[cand] - top).astype(np.float64))          # token order
+        run = np.cumsum(w)
+        hit = np.where((run >= u * run[-1]) & (run > 0))[0]
+        return int(cand[hit[0]]) if len(hit) else int(cand[-1])
+    order = sorted(cand, key=lambda i: (-scaled[i], i))
+    if 0 < top_k < len(order):
+        order = order[:top_k]
+    w = np.exp((scaled[order] - top).astype(np.float64))
+    run = np.cumsum(w)
+    keep, mass = len(order), run[-1]
+    if top_p < 1.0:
+        keep = int(np.where(run >= float(np.float32(top_p)) * run[-1])[0][0]) + 1
+        mass = run[keep - 1]
+    hit = np.where(run[:keep] >= u * mass)[0]
+    return int(order[hit[0]]) if len(hit) else int(order[keep - 1])
+
+
+def test_sampler_agrees_with_an_independent_statement_on_a_random_and_adversarial_corpus():
+    rng = np.random.default_rng(5)
+    checked = 0
+    for case in range(600):
+        n = int(rng.choice([3, 31, 32, 33, 64, 257, 300, 1000]))
+        kind = case % 6
+        logits = rng.normal(scale=3.0, size=n).astype(np.float32)
+        if kind == 1:                                    # many exact ties, also at the top-k cut
+            logits = rng.integers(-2, 3, size=n).astype(np.float32)
+        elif kind == 2:                                  # a flat row: every weight equal
+            logits[:] = 0.25
+        elif kind == 3:                                  # huge spread: most weights underflow to subnormals or zero
+            logits = (rng.normal(size=n) * 60).astype(np.float32)
+        elif kind == 4:                                  # masked-out entries may be -inf
+            logits[rng.random(n) < 0.2] = -np.inf
+        mask = None
+        if kind in (4, 5) or rng.random() < 0.3:
+            bits = rng.random(n) < 0.6
+            if kind == 4:
+                bits &= np.isfinite(logits)
+            if not bits.any():
+                bits[int(np.argmax(np.where(np.isfinite(logits), logits, -1e30)))] = True
+            mask = np.zeros((n + 31) // 32, dtype=np.uint32)
+            for i in np.where(bits)[0]:
+                mask[i // 32] |= np.uint32(1 << (i % 32))
+        elif kind == 4:
+            logits[~np.isfinite(logits)] = -50.0
+        temperature = float(rng.choice([0.0, 0.3, 0.7, 1.0, 1.5]))
+        top_k = int(rng.choice([0, 1, 2, 5, 40, 256, 257, 500]))
+        top_p = float(rng.choice([1.0, 0.95, 0.5, 0.1, 1e-6]))
+        min_p = float(rng.choice([0.0, 0.05, 0.5, 1.0]))
+        u = float(rng.choice([0.0, rng.random(), rng.random(), 0.9999999, 1.0]))
+        if kind == 4 and (temperature < 1e-5 or top_k == 1):
+            continue                                     # the greedy path wants a finite row even under the mask
+        got = K.sample_token(logits, mask, temperature, top_k, top_p, min_p, u)
+        want = _sample_statement(logits, mask, temperature, top_k, top_p, min_p, u)
+        assert got == want, (case, n, temperature, top_k, top_p, min_p, u)
+        if mask is not None:
+            assert (int(mask[got // 32]) >> (got % 32)) & 1
+        checked += 1
+    assert checked > 500
+    # the corners by hand: a tie at the top-k cut keeps the lower id; a nucleus of tiny top_p is the single best token;
+    # min_p = 1 keeps only the best (and its exact ties); u = 1 is clamped into the last surviving token
+    tie = np.array([1.0, 2.0, 2.0, 2.0, 0.0], dtype=np.float32)
+    assert {K.sample_token(tie, temperature=1.0, top_k=2, uniform=u) for u in (0.0, 0.3, 0.6, 0.99)} == {1, 2}
+    assert K.sample_token(tie, temperature=1.0, top_p=1e-6, uniform=0.999) == 1
+    assert {K.sample_token(tie, temperature=1.0, min_p=1.0, uniform=u) for u in (0.0, 0.5, 0.99)} == {1, 2, 3}
+    assert K.sample_token(tie, temperature=1.0, uniform=1.0) == 4
+    # everything masked, +inf and NaN among the allowed entries are errors, never a token
+    with pytest.raises(K.SamplingError, match="empty"):
+        K.sample_token(tie, np.zeros(1, dtype=np.uint32), temperature=1.0, uniform=0.5)
+    with pytest.raises(K.SamplingError, match="nonfinite"):
+        K.sample_token(np.array([0.0, np.inf], dtype=np.float32), temperature=1.0, uniform=0.5)
+    with pytest.raises(K.SamplingError, match="empty"):
+        K.sample_token(np.array([-np.inf, -np.inf], dtype=np.float32), temperature=1.0, uniform=0.5)
+
+
 # ---------------------------------------------------------------------------------------------- verification
 def test_verify_accept_prefix():
     r = K.verify_greedy([10, 11, 12, 13], [11, 12, 99, 14], eos=1, remaining=100)
