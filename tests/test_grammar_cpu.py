@@ -174,3 +174,76 @@ def test_triggered_tool_grammar_leaves_text_free_until_the_tag():
     # inside the block only the declared tool's invoke line can follow (or a piece that is a prefix of it)
     assert f'{C.DSML_OPEN} invoke name="get_weather">\n' in allowed and not mask_allows(mask, 0)
     assert all(f'{C.DSML_OPEN} invoke name="get_weather">\n'.startswith(p) for p in allowed)
+
+
+def _random_schema(rng, depth=0):
+    """A schema from the supported subset and a generator of valid instances for it."""
+    kinds = ["string", "integer", "number", "boolean", "null", "enum", "nullable"]
+    if depth < 3:
+        kinds += ["object", "object", "array", "anyOf"]
+    kind = kinds[rng.integers(len(kinds))]
+    if kind == "string":
+        alphabet = ["a", "Z", " ", "é", "✓", '"', "\\", "\n", "\t", "/", "0", "😀"]
+        return {"type": "string"}, lambda: "".join(alphabet[i] for i in rng.integers(len(alphabet), size=rng.integers(0, 6)))
+    if kind == "integer":
+        return {"type": "integer"}, lambda: int(rng.integers(-10 ** 6, 10 ** 6)) if rng.random() < 0.8 else 0
+    if kind == "number":
+        return {"type": "number"}, lambda: [0.5, -1.25e-7, 3.0e12, 7, -0.0, 1e-05][rng.integers(6)]
+    if kind == "boolean":
+        return {"type": "boolean"}, lambda: bool(rng.integers(2))
+    if kind == "null":
+        return {"type": "null"}, lambda: None
+    if kind == "enum":
+        values = [["red", "green", "blue"], [1, 2, 3], ["a b", "a"], [True, None, "x"]][rng.integers(4)]
+        return {"enum": values}, lambda: values[rng.integers(len(values))]
+    if kind == "nullable":
+        return {"type": ["integer", "null"]}, lambda: None if rng.random() < 0.5 else int(rng.integers(100))
+    if kind == "array":
+        item, gen = _random_schema(rng, depth + 1)
+        cap = int(rng.integers(1, 4))
+        return {"type": "array", "items": item, "maxItems": cap}, lambda: [gen() for _ in range(rng.integers(0, cap + 1))]
+    if kind == "anyOf":
+        (a, ga), (b, gb) = _random_schema(rng, depth + 1), _random_schema(rng, depth + 1)
+        return {"anyOf": [a, b]}, lambda: ga() if rng.random() < 0.5 else gb()
+    names = [f"k{i}" for i in range(rng.integers(1, 5))]
+    parts = {n: _random_schema(rng, depth + 1) for n in names}
+    required = [n for n in names if rng.random() < 0.6]
+    schema = {"type": "object", "properties": {n: parts[n][0] for n in names}, "required": required}
+
+    def gen():
+        return {n: parts[n][1]() for n in names if n in required or rng.random() < 0.5}      # declared order
+    return schema, gen
+
+
+def test_random_schemas_accept_their_instances_byte_by_byte_and_refuse_broken_ones():
+    """Property test over the supported schema subset: every generated instance is accepted with every one of its byte
+    prefixes on the way, compact or indented, ASCII-escaped or raw UTF-8; a truncated document cannot finish; a document
+    without one of its required properties, or with a value of another type in place of a leaf, is refused."""
+    rng = np.random.default_rng(11)
+    docs = broken = 0
+    for _ in range(60):
+        schema, gen = _random_schema(rng, 0)
+        if schema.get("type") != "object":
+            schema, gen = {"type": "object", "properties": {"v": schema}, "required": ["v"]}, (lambda g=gen: {"v": g()})
+        g = Grammar.json_schema(schema)
+        for _ in range(4):
+            value = gen()
+            for text in (json.dumps(value), json.dumps(value, ensure_ascii=False), json.dumps(value, indent=1)):
+                data = text.encode()
+                m = Matcher(g)
+                for i in range(len(data)):
+                    assert m.accept_bytes(data[i:i + 1]), (schema, text, i)
+                    if i < len(data) - 1:
+                        assert not m.can_finish or text[: i + 1].rstrip() != text[: i + 1], (schema, text, i)
+                assert m.can_finish, (schema, text)
+                docs += 1
+            for name in schema["required"]:
+                cut = {k: v for k, v in value.items() if k != name}
+                assert not _complete(g, json.dumps(cut)), (schema, cut)
+                broken += 1
+            for name, sub in schema["properties"].items():
+                if name in value and sub.get("type") in ("integer", "boolean", "null", "string"):
+                    wrong = {"integer": "7", "boolean": 1, "null": 0, "string": 5}[sub["type"]]
+                    assert not _complete(g, json.dumps(dict(value, **{name: wrong}))), (schema, name)
+                    broken += 1
+    assert docs >= 700 and broken > 100
