@@ -280,3 +280,121 @@ def test_philox_vectors_and_reservations():
     assert rng.reserve(8, 5) == (3, 0) and rng.reserve(7, 1) == (1, 150)
     assert rng.release(9) and not rng.release(9)
     rng.close()
+
+
+def test_kv_allocator_against_a_reference_model_under_random_traffic():
+    """Random admissions, growth, snapshots (retain), restores (share), copy-on-write and retirements, mirrored in a
+    plain Python model: page reference counts, free-page count and every slot's page list must agree after each step;
+    a page is never handed out while something still points at it; stale leases are refused."""
+    import random
+    rng = random.Random(3)
+    N_PAGES, N_SLOTS, P = 24, 4, 16
+    kv = K.KvAllocator(N_PAGES, N_SLOTS, page_tokens=P)
+    ref = [0] * N_PAGES                                   # model: reference count per page
+    slots = {}                                            # slot -> (gen, [pages])
+    snaps = []                                            # retained page lists
+    stale = []
+    steps = {"admit": 0, "grow": 0, "retain": 0, "share": 0, "cow": 0, "retire": 0, "drop": 0, "oom": 0}
+
+    def check():
+        assert kv.free_pages == sum(1 for r in ref if r == 0)
+        for pg in range(N_PAGES):
+            assert kv.page_ref(pg) == ref[pg], pg
+        for s, (g, pages) in slots.items():
+            assert kv.generation(s) == g and kv.pages(s) == pages
+        for s in range(N_SLOTS):
+            if s not in slots:
+                assert kv.generation(s) == 0 and kv.page_count(s) == 0
+
+    for _ in range(3000):
+        op = rng.choice(["admit", "grow", "grow", "retain", "share", "cow", "retire", "drop"])
+        if op == "admit":
+            got = kv.admit()
+            if len(slots) == N_SLOTS:
+                assert got is None
+            else:
+                s, g = got
+                assert s not in slots and g != 0
+                slots[s] = (g, [])
+                steps["admit"] += 1
+        elif op == "grow" and slots:
+            s = rng.choice(list(slots))
+            g, pages = slots[s]
+            want = rng.randint(1, 9 * P)
+            need = max(0, (want + P - 1) // P - len(pages))
+            free = sum(1 for r in ref if r == 0)
+            if need > free:
+                with pytest.raises(MemoryError):
+                    kv.ensure(s, g, want)
+                steps["oom"] += 1
+            else:
+                new = kv.ensure(s, g, want)
+                assert len(new) == need
+                for idx, pg in new:
+                    assert ref[pg] == 0 and idx == len(pages)          # a free page, appended in order
+                    ref[pg] = 1
+                    pages.append(pg)
+                steps["grow"] += 1
+        elif op == "retain" and slots:
+            s = rng.choice(list(slots))
+            g, pages = slots[s]
+            n = rng.randint(0, len(pages))
+            got = kv.retain(s, g, n)
+            assert got == pages[:n]
+            for pg in got:
+                ref[pg] += 1
+            if got:
+                snaps.append(got)
+            steps["retain"] += 1
+        elif op == "share" and snaps:
+            empty = [s for s, (g, pages) in slots.items() if not pages]
+            if empty:
+                s = rng.choice(empty)
+                snap = rng.choice(snaps)
+                kv.share(s, slots[s][0], snap)
+                for pg in snap:
+                    ref[pg] += 1
+                slots[s] = (slots[s][0], list(snap))
+                steps["share"] += 1
+        elif op == "cow" and slots:
+            s = rng.choice(list(slots))
+            g, pages = slots[s]
+            if pages:
+                i = rng.randrange(len(pages))
+                free = sum(1 for r in ref if r == 0)
+                if ref[pages[i]] == 1:
+                    assert kv.make_private(s, g, i) is None                # already private: nothing to copy
+                elif free == 0:
+                    with pytest.raises(MemoryError):
+                        kv.make_private(s, g, i)
+                else:
+                    src, dst = kv.make_private(s, g, i)
+                    assert src == pages[i] and ref[dst] == 0
+                    ref[src] -= 1
+                    ref[dst] = 1
+                    pages[i] = dst
+                    steps["cow"] += 1
+        elif op == "retire" and slots:
+            s = rng.choice(list(slots))
+            g, pages = slots.pop(s)
+            assert kv.retire(s, g)
+            for pg in pages:
+                ref[pg] -= 1
+            stale.append((s, g))
+            steps["retire"] += 1
+        elif op == "drop" and snaps:
+            snap = snaps.pop(rng.randrange(len(snaps)))
+            kv.release_pages(snap)
+            for pg in snap:
+                ref[pg] -= 1
+            steps["drop"] += 1
+        if stale and rng.random() < 0.05:
+            s, g = rng.choice(stale)
+            if s not in slots or slots[s][0] != g:                         # an old lease of a slot, possibly re-leased
+                with pytest.raises(KeyError):
+                    kv.ensure(s, g, 1)
+                assert not kv.retire(s, g)
+        assert all(r >= 0 for r in ref)
+        check()
+    low = {k: v for k, v in steps.items() if v < 5}
+    assert not low, low
