@@ -146,8 +146,14 @@ def test_manifest_covers_exactly_what_the_repository_tracks():
     if not (ROOT / ".git").exists():
         pytest.skip("not a git checkout")
     def git(*a):
-        return set(subprocess.run(["git", "-C", str(ROOT), *a], capture_output=True, text=True).stdout.split("\n")) - {""}
+        r = subprocess.run(["git", "-C", str(ROOT), *a], capture_output=True, text=True)
+        if r.returncode != 0:
+            pytest.skip(f"git {a[0]} does not work here: {r.stderr.strip()[:80]}")
+        return set(r.stdout.split("\n")) - {""}
     tracked, untracked = git("ls-files"), git("ls-files", "--others", "--exclude-standard")
+    if not tracked:
+        pytest.skip("git lists no tracked files here")
+    tracked = {f for f in tracked if (ROOT / f).exists()}                       # deleted but not yet committed
     assert {k[2:] for k in M.inventory(ROOT)} == (tracked | untracked)
     with pytest.raises(M.ManifestError, match="negated"):
         import tempfile
